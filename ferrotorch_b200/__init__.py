@@ -1,0 +1,15 @@
+"""ferrotorch_b200 -- a Blackwell-native deep-learning framework with the capability set of
+ferrotorch (ferrotorch/src/lib.rs:59-177 is the reference's umbrella crate).
+
+PyTorch is the tensor / autograd / module layer; this package adds hand-written sm_100a
+kernels (``ops``), layers built on them (``nn``), flat-arena fused optimizers (``optim``),
+the parallel runtime (``parallel``), model families (``models``), a trace-and-fuse JIT
+(``jit``), checkpoint formats (``serialize``), a training loop (``train``) and a profiler
+(``profiler``).
+"""
+__version__ = "0.1.0"
+
+from . import _native  # noqa: F401
+from . import ops  # noqa: F401
+
+__all__ = ["ops", "__version__"]

@@ -1,0 +1,407 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM),
+// operands staged in shared memory by TMA through an mbarrier pipeline.
+//
+//   C[M,N] (+)= A[M,K] * B[N,K]^T (+ bias[N])
+//
+// Both operands may be stored K-major (row-major [rows, K], the nn.Linear layout)
+// or MN-major (row-major [K, rows]); the four combinations cover the forward
+// (X W^T), data-gradient (dY W) and weight-gradient (dY^T X) products of a linear
+// layer without any transposed copy.  This replaces the cuBLAS GemmEx calls of the
+// reference (ferrotorch-gpu/src/blas.rs:3186-3306, 2769-2886) and its separate
+// bias launch (ferrotorch-core/src/grad_fns/linalg.rs:1643-1655).
+//
+// Kernel structure (one persistent CTA per SM, 256 threads):
+//   warp 0    TMA producer: one elected thread fills a STAGES-deep ring of
+//             {A 128x64, B BNx64} bf16 tiles (128-byte swizzle)
+//   warp 1    MMA issuer: one thread issues 4 x tcgen05.mma (128 x BN x 16) per
+//             stage and commits the stage's "empty" barrier; after the last
+//             k-block it commits the accumulator's "full" barrier
+//   warp 2    allocates / frees tensor memory (2 accumulators of BN columns so the
+//             epilogue of tile i overlaps the main loop of tile i+1)
+//   warps 4-7 epilogue: tcgen05.ld -> fp32 registers -> (+C, +bias) -> bf16/fp32
+//             -> global
+// Every wait is bounded; a wait that runs out aborts the CTA cleanly and reports
+// through the device status word.
+#include "ft_host.h"
+#include "ft_ptx.cuh"
+
+namespace ft {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 256;
+constexpr int GEMM_GROUP_M = 16;
+
+enum GemmFlags : int {
+  GEMM_OUT_F32 = 1,     // C is fp32 (default bf16)
+  GEMM_ACCUMULATE = 2,  // C += A B^T
+  GEMM_BIAS = 4,        // + bias[N] (bf16)
+  GEMM_BIAS_F32 = 8,    // bias is fp32
+  GEMM_RELU = 16,       // activation fused in the epilogue (after bias)
+  GEMM_GELU = 32,
+  GEMM_SILU = 64,
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  // stages + barriers (full, empty, tmem_full[2], tmem_empty[2]) + tmem ptr + abort + align slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+struct GemmParams {
+  void* C;
+  const void* bias;
+  int M, N, K;
+  long long ldc;
+  int flags;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
+  const int group_tiles = GEMM_GROUP_M * n_blocks;
+  const int g = tile / group_tiles;
+  const int first_m = g * GEMM_GROUP_M;
+  const int gm = min(GEMM_GROUP_M, m_blocks - first_m);
+  const int r = tile - g * group_tiles;
+  mb = first_m + (r % gm);
+  nb = r / gm;
+}
+
+__device__ __forceinline__ float apply_act(float v, int flags) {
+  if (flags & GEMM_RELU) return fmaxf(v, 0.f);
+  if (flags & GEMM_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (flags & GEMM_SILU) return v / (1.f + __expf(-v));
+  return v;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  const int m_blocks = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        const int m0 = mb * GEMM_BM, n0 = nb * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+          const int k0 = kb * GEMM_BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sA, &tmA, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d(sA + c * (GEMM_BK * 128), &tmA, full_bar(stage), m0 + c * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sB, &tmB, full_bar(stage), k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * (GEMM_BK * 128), &tmB, full_bar(stage), n0 + c * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Drain: give the loads already issued a bounded time to land before the
+        // CTA's shared memory is released.
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(GEMM_BM, BN, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_word, FT_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(sA + k * 2048, GEMM_BK * 128, 1024)
+                                        : make_smem_desc_sw128(sA + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sB + k * 2048, GEMM_BK * 128, 1024)
+                                        : make_smem_desc_sw128(sB + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue
+    const int ew = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
+    const bool accumulate = (p.flags & GEMM_ACCUMULATE) != 0;
+    const bool has_bias = (p.flags & (GEMM_BIAS | GEMM_BIAS_F32)) != 0;
+    const bool has_act = (p.flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      const int m0 = mb * GEMM_BM, n0 = nb * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int row = m0 + ew * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (has_bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col < p.N) {
+              v[j] += (p.flags & GEMM_BIAS_F32)
+                          ? static_cast<const float*>(p.bias)[col]
+                          : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+            }
+          }
+        }
+        if (out_f32) {
+          float* crow = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 + 4 <= p.N) {
+              float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+              if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(crow + g * 4);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              if (has_act) {
+                o.x = apply_act(o.x, p.flags); o.y = apply_act(o.y, p.flags);
+                o.z = apply_act(o.z, p.flags); o.w = apply_act(o.w, p.flags);
+              }
+              *reinterpret_cast<float4*>(crow + g * 4) = o;
+            }
+          }
+        } else {
+          __nv_bfloat16* crow =
+              static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 + 8 <= p.N) {
+              float* vv = v + g * 8;
+              if (accumulate) {
+                const uint4 old = *reinterpret_cast<const uint4*>(crow + g * 8);
+                const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y),
+                             o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
+                vv[0] += o0.x; vv[1] += o0.y; vv[2] += o1.x; vv[3] += o1.y;
+                vv[4] += o2.x; vv[5] += o2.y; vv[6] += o3.x; vv[7] += o3.y;
+              }
+              if (has_act) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) vv[j] = apply_act(vv[j], p.flags);
+              }
+              uint4 o;
+              o.x = pack_bf16x2(vv[0], vv[1]);
+              o.y = pack_bf16x2(vv[2], vv[3]);
+              o.z = pack_bf16x2(vv[4], vv[5]);
+              o.w = pack_bf16x2(vv[6], vv[7]);
+              *reinterpret_cast<uint4*>(crow + g * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int device,
+                       int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[device]) {
+    FT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES));
+    attr_set[device] = true;
+  }
+  const int m_blocks = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  int grid = m_blocks * n_blocks;
+  int sms = sm_count(device);
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (grid > sms) grid = sms;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+template <int BN>
+static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                          const GemmParams& p, int device, int max_ctas, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(tmA, tmB, p, device, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(tmA, tmB, p, device, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_gemm<BN, true, false>(tmA, tmB, p, device, max_ctas, stream);
+  return launch_gemm<BN, true, true>(tmA, tmB, p, device, max_ctas, stream);
+}
+
+}  // namespace ft
+
+// C[M,N] (+)= A * B^T (+bias).  A is [M,K] (a_mn_major = 0, row stride lda) or stored
+// transposed as [K,M] (a_mn_major = 1); B is [N,K] (b_mn_major = 0) or stored as
+// [K,N] (b_mn_major = 1).  Strides are in elements.  bn = 0 picks the N tile
+// automatically; max_ctas > 0 limits the persistent grid (used to leave SMs to a
+// concurrent communication kernel).  Returns 0 or a negative error code
+// (ft_last_error() has the text).
+FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                        long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                        int flags, int bn, int max_ctas, int device, cudaStream_t stream) {
+  using namespace ft;
+  FT_REQUIRE(A && B && C, "ft_gemm_bf16: null operand");
+  FT_REQUIRE(M > 0 && N > 0 && K > 0, "ft_gemm_bf16: empty problem %dx%dx%d", M, N, K);
+  FT_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "ft_gemm_bf16: lda/ldb must be multiples of 8 elements");
+  const bool out_f32 = flags & GEMM_OUT_F32;
+  FT_REQUIRE(N % 8 == 0 && ldc % (out_f32 ? 4 : 8) == 0,
+             "ft_gemm_bf16: N (%d) must be a multiple of 8 and ldc 16-byte aligned", N);
+  FT_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0, "ft_gemm_bf16: C must be 16-byte aligned");
+  FT_REQUIRE(!(flags & (GEMM_BIAS | GEMM_BIAS_F32)) || bias, "ft_gemm_bf16: bias flag without bias");
+  if (bn == 0) {
+    const int sms = sm_count(device);
+    const long long mb = (M + GEMM_BM - 1) / GEMM_BM;
+    bn = 256;
+    while (bn > 32 && mb * ((N + bn - 1) / bn) < sms) bn >>= 1;
+    if (N <= 32) bn = 32; else if (N <= 64 && bn > 64) bn = 64; else if (N <= 128 && bn > 128) bn = 128;
+  }
+  FT_REQUIRE(bn == 256 || bn == 128 || bn == 64 || bn == 32, "ft_gemm_bf16: bad N tile %d", bn);
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn_major)
+    rc = make_tmap_2d(&tmA, A, 2, K, M, lda * 2, GEMM_BK, GEMM_BM, 3);
+  else
+    rc = make_tmap_2d(&tmA, A, 2, M, K, lda * 2, 64, GEMM_BK, 3);
+  if (rc) return rc;
+  if (!b_mn_major)
+    rc = make_tmap_2d(&tmB, B, 2, K, N, ldb * 2, GEMM_BK, bn, 3);
+  else
+    rc = make_tmap_2d(&tmB, B, 2, N, K, ldb * 2, 64, GEMM_BK, 3);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags;
+  p.status = device_status_word(device);
+  switch (bn) {
+    case 256: return dispatch_major<256>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
+    case 128: return dispatch_major<128>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
+    case 64: return dispatch_major<64>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
+    default: return dispatch_major<32>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
+  }
+}

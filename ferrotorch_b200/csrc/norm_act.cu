@@ -1,0 +1,442 @@
+// Memory-bound transformer kernels for sm_100a: RMSNorm (+ fused residual add)
+// forward/backward, rotary embedding (both pair conventions) forward/backward,
+// SwiGLU forward/backward, embedding gather / scatter-add.
+//
+// Semantics follow the reference: RMSNorm = x * rsqrt(mean(x^2) + eps) * w with fp32
+// statistics (ferrotorch-gpu/src/bf16.rs:1340-1346, kernels.rs:10578, 10725); RoPE
+// rotates the pair (d, d + D/2) ("half" / HF convention, bf16.rs:1850-1855) or
+// (2d, 2d+1) (interleaved, ferrotorch-nn/src/transformer.rs:66-72) with the backward
+// of transformer.rs:132-156; SwiGLU = silu(gate) * up (ferrotorch-llama/src/gpu.rs:696-703).
+// Unlike the reference (one launch per op, 256-thread 1-D grids) every kernel moves
+// 16-byte vectors, keeps the row in registers between the statistics pass and the
+// scale pass, and fuses the neighbouring residual add / gate multiply.
+#include "ft_host.h"
+#include "ft_ptx.cuh"
+
+namespace ft {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_VEC = 4;  // 4 vec * 8 elems * 256 thr = rows up to 8192 wide in registers
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : -INFINITY;
+  if (w == 0) {
+    t = warp_max(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// ---------------------------------------------------------------- RMSNorm forward
+// y = (x [+ delta]) * rstd * w ; if delta != null also writes res_out = x + delta.
+// One block per row, grid-stride over rows. H % 8 == 0.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows, int H,
+                   float eps) {
+  __shared__ float red[32];
+  const int nvec = H >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+    const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + static_cast<size_t>(row) * H) : nullptr;
+    float vals[NORM_MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        unpack8(xr[v], vals[i]);
+        if (dr) {
+          float d[8];
+          unpack8(dr[v], d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += d[j];
+          if (res_out) {
+            // round the residual stream to bf16 once; the statistics use the rounded value
+            uint4 packed = pack8(vals[i]);
+            reinterpret_cast<uint4*>(res_out + static_cast<size_t>(row) * H)[v] = packed;
+            unpack8(packed, vals[i]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float rstd = rsqrtf(tot / static_cast<float>(H) + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        float wv[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[v], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
+        reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H)[v] = pack8(o);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- RMSNorm backward
+// dx = rstd * (g - xhat * mean(g * xhat)) [+ dres], g = dy * w, xhat = x * rstd.
+// dw partial sums: each block keeps its columns' sums in registers over the rows it
+// owns and writes one fp32 row of the scratch [gridDim.x, H]; rmsnorm_dw_reduce sums it.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int H) {
+  __shared__ float red[32];
+  const int nvec = H >> 3;
+  float dwacc[NORM_MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    float g[NORM_MAX_VEC][8], xh[NORM_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        float dyv[8], wv[8];
+        unpack8(reinterpret_cast<const uint4*>(dy + off)[v], dyv);
+        unpack8(reinterpret_cast<const uint4*>(x + off)[v], xh[i]);
+        unpack8(reinterpret_cast<const uint4*>(w)[v], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rstd;
+          g[i][j] = dyv[j] * wv[j];
+          dot += g[i][j] * xh[i][j];
+          dwacc[i][j] += dyv[j] * xh[i][j];
+        }
+      }
+    }
+    const float mean_dot = block_sum(dot, red) / static_cast<float>(H);
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * mean_dot);
+        if (dres) {
+          float r[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + off)[v], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        reinterpret_cast<uint4*>(dx + off)[v] = pack8(o);
+      }
+    }
+  }
+  if (dw_partial) {
+    float* out = dw_partial + static_cast<size_t>(blockIdx.x) * H;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        reinterpret_cast<float4*>(out)[2 * v] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+        reinterpret_cast<float4*>(out)[2 * v + 1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+      }
+    }
+  }
+}
+
+// dw[h] (+)= sum_b partial[b, h]; writes bf16 or fp32.
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, void* __restrict__ dw,
+                                         int nblocks, int H, int out_f32, int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<size_t>(b) * H + h];
+  if (out_f32) {
+    float* o = static_cast<float*>(dw);
+    o[h] = accumulate ? o[h] + s : s;
+  } else {
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(dw);
+    o[h] = __float2bfloat16(accumulate ? __bfloat162float(o[h]) + s : s);
+  }
+}
+
+// ---------------------------------------------------------------- RoPE
+// x: [T, n_heads_total, D] with row stride `ld` (elements) between tokens; rotates
+// heads [0, n_rot_heads).  cos/sin: fp32 [max_pos, D/2].  pos: int32 [T] or null
+// (then position = (t % seq_len) + pos_offset).  sign = +1 forward, -1 backward.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, const int* __restrict__ pos, int T,
+                            int n_rot_heads, int D, long long ld, int seq_len, int pos_offset,
+                            int interleaved, float sign) {
+  const int half = D >> 1;
+  const int pairs_per_tok = n_rot_heads * half;
+  const long long total = static_cast<long long>(T) * (pairs_per_tok >> 1);  // 2 pairs / thread
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / (pairs_per_tok >> 1));
+    const int r = static_cast<int>(i - static_cast<long long>(t) * (pairs_per_tok >> 1)) * 2;
+    const int h = r / half, d = r - h * half;  // d even
+    const int p = pos ? pos[t] : (t % seq_len) + pos_offset;
+    const float2 c = *reinterpret_cast<const float2*>(cos_t + static_cast<size_t>(p) * half + d);
+    float2 s = *reinterpret_cast<const float2*>(sin_t + static_cast<size_t>(p) * half + d);
+    s.x *= sign; s.y *= sign;
+    __nv_bfloat16* base = x + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D;
+    if (!interleaved) {
+      __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(base + d);
+      __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(base + d + half);
+      const float2 a = __bfloat1622float2(*p1), b = __bfloat1622float2(*p2);
+      *p1 = __floats2bfloat162_rn(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
+      *p2 = __floats2bfloat162_rn(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
+    } else {
+      uint2* pp = reinterpret_cast<uint2*>(base + 2 * d);
+      uint2 u = *pp;
+      const float2 e0 = unpack_bf16x2(u.x), e1 = unpack_bf16x2(u.y);  // (x0,x1), (x2,x3)
+      u.x = pack_bf16x2(e0.x * c.x - e0.y * s.x, e0.y * c.x + e0.x * s.x);
+      u.y = pack_bf16x2(e1.x * c.y - e1.y * s.y, e1.y * c.y + e1.x * s.y);
+      *pp = u;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// gu: [T, 2F] (gate = [:, :F], up = [:, F:]), out: [T, F].  act: 0 silu, 1 relu, 2 gelu(tanh).
+__device__ __forceinline__ float act_fwd(float g, int act) {
+  if (act == 0) return g / (1.f + __expf(-g));
+  if (act == 1) return fmaxf(g, 0.f);
+  const float k = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  return 0.5f * g * (1.f + tanhf(k));
+}
+__device__ __forceinline__ float act_bwd(float g, int act) {
+  if (act == 0) {
+    const float s = 1.f / (1.f + __expf(-g));
+    return s * (1.f + g * (1.f - s));
+  }
+  if (act == 1) return g > 0.f ? 1.f : 0.f;
+  const float k = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  const float t = tanhf(k);
+  return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * g * g);
+}
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                  long long T, int F, long long ld_gu, int act) {
+  const int fv = F >> 3;
+  const long long total = T * fv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / fv;
+    const int v = static_cast<int>(i - t * fv);
+    const uint4* row = reinterpret_cast<const uint4*>(gu + t * ld_gu);
+    float g[8], u[8], o[8];
+    unpack8(row[v], g);
+    unpack8(row[fv + v], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], act) * u[j];
+    reinterpret_cast<uint4*>(out + t * F)[v] = pack8(o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int F, long long ld_gu,
+                                  int act) {
+  const int fv = F >> 3;
+  const long long total = T * fv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / fv;
+    const int v = static_cast<int>(i - t * fv);
+    const uint4* row = reinterpret_cast<const uint4*>(gu + t * ld_gu);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(row[v], g);
+    unpack8(row[fv + v], u);
+    unpack8(reinterpret_cast<const uint4*>(dy + t * F)[v], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dg[j] = d[j] * u[j] * act_bwd(g[j], act);
+      du[j] = d[j] * act_fwd(g[j], act);
+    }
+    uint4* orow = reinterpret_cast<uint4*>(dgu + t * ld_gu);
+    orow[v] = pack8(dg);
+    orow[fv + v] = pack8(du);
+  }
+}
+
+// ---------------------------------------------------------------- embedding
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
+                                     __nv_bfloat16* __restrict__ out, int T, int H, int vocab) {
+  const int hv = H >> 3;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;  // host validates; never read out of range
+    const uint4* src = reinterpret_cast<const uint4*>(w + static_cast<size_t>(id) * H);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+    for (int v = threadIdx.x; v < hv; v += blockDim.x) dst[v] = src[v];
+  }
+}
+__global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dy,
+                                     __nv_bfloat16* __restrict__ dw, int T, int H, int vocab) {
+  const int h2 = H >> 1;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long long id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(dy + static_cast<size_t>(t) * H);
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(dw + static_cast<size_t>(id) * H);
+    for (int v = threadIdx.x; v < h2; v += blockDim.x) atomicAdd(dst + v, src[v]);
+  }
+}
+
+static inline int blocks_for(long long work, int threads, int device, int per_sm = 8) {
+  long long b = (work + threads - 1) / threads;
+  const long long cap = static_cast<long long>(sm_count(device)) * per_sm;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+FT_API int ft_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* y, void* res_out,
+                          float* rstd, int rows, int H, float eps, int device, cudaStream_t stream) {
+  FT_REQUIRE(x && w && y, "ft_rmsnorm_fwd: null pointer");
+  FT_REQUIRE(H % 8 == 0 && H <= NORM_THREADS * NORM_MAX_VEC * 8, "ft_rmsnorm_fwd: H=%d unsupported", H);
+  if (rows <= 0) return FT_E_OK;
+  const int grid = rows < sm_count(device) * 8 ? rows : sm_count(device) * 8;
+  rmsnorm_fwd_kernel<<<grid, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+      static_cast<__nv_bfloat16*>(res_out), rstd, rows, H, eps);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+// Number of fp32 scratch rows ft_rmsnorm_bwd needs for `rows` (scratch = n * H floats).
+FT_API int ft_rmsnorm_bwd_scratch_rows(int rows, int device) {
+  const int cap = sm_count(device) * 2;
+  return rows < cap ? (rows > 0 ? rows : 1) : cap;
+}
+
+// dw may be null (then scratch may be null too).  dw_flags: bit0 fp32 output, bit1 accumulate.
+FT_API int ft_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                          const void* dres, void* dx, void* dw, float* scratch, int rows, int H,
+                          int dw_flags, int device, cudaStream_t stream) {
+  FT_REQUIRE(dy && x && w && rstd && dx, "ft_rmsnorm_bwd: null pointer");
+  FT_REQUIRE(H % 8 == 0 && H <= NORM_THREADS * NORM_MAX_VEC * 8, "ft_rmsnorm_bwd: H=%d unsupported", H);
+  FT_REQUIRE(!dw || scratch, "ft_rmsnorm_bwd: dw requested without scratch");
+  if (rows <= 0) return FT_E_OK;
+  const int grid = ft_rmsnorm_bwd_scratch_rows(rows, device);
+  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
+      static_cast<__nv_bfloat16*>(dx), dw ? scratch : nullptr, rows, H);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  if (dw) {
+    rmsnorm_dw_reduce_kernel<<<(H + 127) / 128, 128, 0, stream>>>(scratch, dw, grid, H, dw_flags & 1,
+                                                                  (dw_flags >> 1) & 1);
+    FT_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+  }
+  return FT_E_OK;
+}
+
+FT_API int ft_rope(void* x, const float* cos_t, const float* sin_t, const int* pos, int T,
+                   int n_rot_heads, int D, long long ld, int seq_len, int pos_offset, int interleaved,
+                   int backward, int device, cudaStream_t stream) {
+  FT_REQUIRE(x && cos_t && sin_t, "ft_rope: null pointer");
+  FT_REQUIRE(D % 4 == 0 && ld % 4 == 0, "ft_rope: head_dim and row stride must be multiples of 4");
+  FT_REQUIRE(pos || seq_len > 0, "ft_rope: need positions or seq_len");
+  if (T <= 0 || n_rot_heads <= 0) return FT_E_OK;
+  const long long work = static_cast<long long>(T) * n_rot_heads * (D / 4);
+  rope_kernel<<<blocks_for(work, 256, device), 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(x), cos_t, sin_t, pos, T, n_rot_heads, D, ld, seq_len, pos_offset,
+      interleaved, backward ? -1.f : 1.f);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+FT_API int ft_swiglu_fwd(const void* gu, void* out, long long T, int F, long long ld_gu, int act,
+                         int device, cudaStream_t stream) {
+  FT_REQUIRE(gu && out, "ft_swiglu_fwd: null pointer");
+  FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_fwd: F must be a multiple of 8");
+  if (T <= 0) return FT_E_OK;
+  swiglu_fwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+FT_API int ft_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long T, int F, long long ld_gu,
+                         int act, int device, cudaStream_t stream) {
+  FT_REQUIRE(dy && gu && dgu, "ft_swiglu_bwd: null pointer");
+  FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_bwd: F must be a multiple of 8");
+  if (T <= 0) return FT_E_OK;
+  swiglu_bwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
+      static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+FT_API int ft_embedding_fwd(const long long* ids, const void* w, void* out, int T, int H, int vocab,
+                            int device, cudaStream_t stream) {
+  FT_REQUIRE(ids && w && out && H % 8 == 0, "ft_embedding_fwd: bad arguments");
+  if (T <= 0) return FT_E_OK;
+  const int grid = T < sm_count(device) * 16 ? T : sm_count(device) * 16;
+  embedding_fwd_kernel<<<grid, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(w),
+                                                 static_cast<__nv_bfloat16*>(out), T, H, vocab);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+FT_API int ft_embedding_bwd(const long long* ids, const void* dy, void* dw, int T, int H, int vocab,
+                            int device, cudaStream_t stream) {
+  FT_REQUIRE(ids && dy && dw && H % 2 == 0, "ft_embedding_bwd: bad arguments");
+  if (T <= 0) return FT_E_OK;
+  const int grid = T < sm_count(device) * 16 ? T : sm_count(device) * 16;
+  embedding_bwd_kernel<<<grid, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(dy),
+                                                 static_cast<__nv_bfloat16*>(dw), T, H, vocab);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
