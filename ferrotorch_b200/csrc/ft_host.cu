@@ -44,6 +44,18 @@ int* device_status_word(int device) {
   return g_status[device];
 }
 
+int ensure_device(int device) {
+  static thread_local int current = -1;
+  if (current == device) return FT_E_OK;
+  if (cudaSetDevice(device) != cudaSuccess) {
+    set_last_error("cudaSetDevice(%d) failed", device);
+    return FT_E_CUDA;
+  }
+  cudaFree(0);  // binds the primary context to this thread
+  current = device;
+  return FT_E_OK;
+}
+
 int sm_count(int device) {
   if (device < 0 || device >= 64) return 148;
   if (!g_sms[device]) {

@@ -46,6 +46,11 @@ int make_tmap_4d(CUtensorMap* out, const void* base, int dtype_bytes, uint64_t d
 
 int sm_count(int device);
 
+// Make `device` current for this library's CUDA runtime on the calling thread (cached per
+// thread).  Needed because worker threads (e.g. an autograd engine thread) start with no
+// CUDA context bound, and driver entry points such as the tensor-map encoder require one.
+int ensure_device(int device);
+
 #define FT_CUDA_CHECK(expr)                                                        \
   do {                                                                             \
     cudaError_t _e = (expr);                                                       \

@@ -364,6 +364,7 @@ static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CU
 FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                         long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
                         int flags, int bn, int max_ctas, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   using namespace ft;
   FT_REQUIRE(A && B && C, "ft_gemm_bf16: null operand");
   FT_REQUIRE(M > 0 && N > 0 && K > 0, "ft_gemm_bf16: empty problem %dx%dx%d", M, N, K);
@@ -381,6 +382,8 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
     if (N <= 32) bn = 32; else if (N <= 64 && bn > 64) bn = 64; else if (N <= 128 && bn > 128) bn = 128;
   }
   FT_REQUIRE(bn == 256 || bn == 128 || bn == 64 || bn == 32, "ft_gemm_bf16: bad N tile %d", bn);
+  // an MN-major B tile is loaded in 64-element (128-byte swizzle) column chunks
+  if (b_mn_major && bn < 64) bn = 64;
 
   CUtensorMap tmA, tmB;
   int rc;

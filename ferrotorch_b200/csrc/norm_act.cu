@@ -333,6 +333,7 @@ using namespace ft;
 
 FT_API int ft_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* y, void* res_out,
                           float* rstd, int rows, int H, float eps, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(x && w && y, "ft_rmsnorm_fwd: null pointer");
   FT_REQUIRE(H % 8 == 0 && H <= NORM_THREADS * NORM_MAX_VEC * 8, "ft_rmsnorm_fwd: H=%d unsupported", H);
   if (rows <= 0) return FT_E_OK;
@@ -356,6 +357,7 @@ FT_API int ft_rmsnorm_bwd_scratch_rows(int rows, int device) {
 FT_API int ft_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
                           const void* dres, void* dx, void* dw, float* scratch, int rows, int H,
                           int dw_flags, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(dy && x && w && rstd && dx, "ft_rmsnorm_bwd: null pointer");
   FT_REQUIRE(H % 8 == 0 && H <= NORM_THREADS * NORM_MAX_VEC * 8, "ft_rmsnorm_bwd: H=%d unsupported", H);
   FT_REQUIRE(!dw || scratch, "ft_rmsnorm_bwd: dw requested without scratch");
@@ -379,6 +381,7 @@ FT_API int ft_rmsnorm_bwd(const void* dy, const void* x, const void* w, const fl
 FT_API int ft_rope(void* x, const float* cos_t, const float* sin_t, const int* pos, int T,
                    int n_rot_heads, int D, long long ld, int seq_len, int pos_offset, int interleaved,
                    int backward, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(x && cos_t && sin_t, "ft_rope: null pointer");
   FT_REQUIRE(D % 4 == 0 && ld % 4 == 0, "ft_rope: head_dim and row stride must be multiples of 4");
   FT_REQUIRE(pos || seq_len > 0, "ft_rope: need positions or seq_len");
@@ -394,6 +397,7 @@ FT_API int ft_rope(void* x, const float* cos_t, const float* sin_t, const int* p
 
 FT_API int ft_swiglu_fwd(const void* gu, void* out, long long T, int F, long long ld_gu, int act,
                          int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(gu && out, "ft_swiglu_fwd: null pointer");
   FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_fwd: F must be a multiple of 8");
   if (T <= 0) return FT_E_OK;
@@ -406,6 +410,7 @@ FT_API int ft_swiglu_fwd(const void* gu, void* out, long long T, int F, long lon
 
 FT_API int ft_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long T, int F, long long ld_gu,
                          int act, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(dy && gu && dgu, "ft_swiglu_bwd: null pointer");
   FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_bwd: F must be a multiple of 8");
   if (T <= 0) return FT_E_OK;
@@ -419,6 +424,7 @@ FT_API int ft_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long T,
 
 FT_API int ft_embedding_fwd(const long long* ids, const void* w, void* out, int T, int H, int vocab,
                             int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(ids && w && out && H % 8 == 0, "ft_embedding_fwd: bad arguments");
   if (T <= 0) return FT_E_OK;
   const int grid = T < sm_count(device) * 16 ? T : sm_count(device) * 16;
@@ -431,6 +437,7 @@ FT_API int ft_embedding_fwd(const long long* ids, const void* w, void* out, int 
 
 FT_API int ft_embedding_bwd(const long long* ids, const void* dy, void* dw, int T, int H, int vocab,
                             int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(ids && dy && dw && H % 2 == 0, "ft_embedding_bwd: bad arguments");
   if (T <= 0) return FT_E_OK;
   const int grid = T < sm_count(device) * 16 ? T : sm_count(device) * 16;

@@ -268,6 +268,7 @@ FT_API int ft_adamw_flat(float* master, float* m, float* v, const void* grad, vo
                          int grad_f32, const float* grad_scale, float lr, float beta1, float beta2,
                          float eps, float weight_decay, int step, int adam_l2, int device,
                          cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(master && m && v && grad, "ft_adamw_flat: null pointer");
   FT_REQUIRE(n % 4 == 0 && step >= 1, "ft_adamw_flat: n must be a multiple of 4 and step >= 1");
   if (n == 0) return FT_E_OK;
@@ -287,6 +288,7 @@ FT_API int ft_sgd_flat(float* master, float* mom, const void* grad, void* p_lp, 
                        int grad_f32, const float* grad_scale, float lr, float momentum, float dampening,
                        float weight_decay, int nesterov, int first_step, int device,
                        cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(master && grad, "ft_sgd_flat: null pointer");
   FT_REQUIRE(n % 4 == 0, "ft_sgd_flat: n must be a multiple of 4");
   FT_REQUIRE(momentum == 0.f || mom, "ft_sgd_flat: momentum without buffer");
@@ -309,6 +311,7 @@ FT_API int ft_grad_norm_scratch(int device) { return sm_count(device) * 4; }
 FT_API int ft_grad_norm(const void* grad, long long n, int grad_f32, float* partial,
                         const float* extra_sumsq, float max_norm, float* out, int device,
                         cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(grad && partial && out && n % 4 == 0, "ft_grad_norm: bad arguments");
   const int blocks = ft_grad_norm_scratch(device);
   sumsq_partial_kernel<<<blocks, 256, 0, stream>>>(grad, n, grad_f32, partial);
@@ -322,6 +325,7 @@ FT_API int ft_grad_norm(const void* grad, long long n, int grad_f32, float* part
 FT_API int ft_cross_entropy(void* logits, const long long* target, float* loss, int rows, int V,
                             long long ld, float grad_scale, long long ignore_index, int write_grad,
                             int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(logits && target && loss, "ft_cross_entropy: null pointer");
   FT_REQUIRE(ld % 8 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0,
              "ft_cross_entropy: rows must be 16-byte aligned");

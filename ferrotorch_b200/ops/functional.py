@@ -476,3 +476,39 @@ def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, target: torch.Te
         z = torch.nn.functional.linear(h2, weight)
         return torch.nn.functional.cross_entropy(z.float(), t2, ignore_index=ignore_index, reduction="sum") / n
     return _LinearCrossEntropyFn.apply(h2.contiguous(), weight, t2, ignore_index, chunk_rows, n)
+
+
+# --------------------------------------------------------------------------- flash attention
+_native.register_protos({
+    "ft_flash_attn_fwd": (_native._i, [_native._vp] * 5 + [_native._i] * 6 + [_native._ll] * 4 +
+                          [_native._f, _native._i, _native._i, _native._i, _native._vp]),
+})
+
+
+def _tok_stride(t: torch.Tensor) -> int:
+    """Token stride of a [B, S, H, D] tensor whose heads are packed (head stride == D)."""
+    B, S, H, D = t.shape
+    assert t.stride(3) == 1 and (H == 1 or t.stride(2) == D), "attention: heads must be packed"
+    ld = t.stride(1) if S > 1 else max(t.stride(1), H * D)
+    assert B == 1 or t.stride(0) == S * ld, "attention: batch stride must be seq * token stride"
+    return ld
+
+
+def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
+                   scale: float | None = None, causal_offset: int | None = None, return_lse: bool = True):
+    """Forward only: ``q [B,Sq,Hq,D]``, ``k/v [B,Sk,Hkv,D]`` (may be slices of a packed QKV buffer).
+    Returns ``(out [B,Sq,Hq,D], lse [B,Hq,Sq] fp32)``."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else D ** -0.5
+    off = (Sk - Sq) if causal_offset is None else causal_offset
+    if not q.is_cuda:
+        return ref.attention(q, k, v, causal, scale, off)
+    out = torch.empty((B, Sq, Hq, D), device=q.device, dtype=q.dtype)
+    lse = torch.empty((B, Hq, Sq), device=q.device, dtype=torch.float32) if return_lse else None
+    rc = _native.kernels().ft_flash_attn_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+        B, Sq, Sk, Hq, Hkv, D, _tok_stride(q), _tok_stride(k), _tok_stride(v), Hq * D, float(scale),
+        int(causal), off, _dev(q), _stream())
+    _native.check(rc, "ft_flash_attn_fwd")
+    return out, lse

@@ -1,0 +1,52 @@
+"""Flash-attention kernels against the fp32 PyTorch attention of ops.reference."""
+import pytest
+import torch
+
+from ferrotorch_b200 import _native
+from ferrotorch_b200.ops import functional as F
+from ferrotorch_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _close(got, want, atol, rtol, what):
+    err = (got.float() - want.float()).abs()
+    tol = atol + rtol * want.float().abs()
+    assert not (err > tol).any(), "%s: max err %.4g" % (what, float(err.max()))
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", [
+    (1, 128, 128, 2, 2, 128, True),
+    (2, 256, 256, 4, 2, 128, True),
+    (1, 384, 384, 4, 1, 128, False),
+    (2, 200, 200, 4, 2, 128, True),     # ragged: tile tails in q and kv
+    (1, 100, 333, 2, 1, 128, True),     # query block is the tail of a longer key sequence
+    (1, 1024, 1024, 8, 2, 128, True),
+    (2, 256, 256, 4, 4, 64, True),
+    (1, 130, 190, 2, 2, 64, False),
+])
+def test_flash_fwd(B, Sq, Sk, Hq, Hkv, D, causal):
+    torch.manual_seed(Sq + Sk + Hq)
+    q, k, v = _rand(B, Sq, Hq, D), _rand(B, Sk, Hkv, D), _rand(B, Sk, Hkv, D)
+    out, lse = F.flash_attn_fwd(q, k, v, causal)
+    torch.cuda.synchronize()
+    assert _native.device_status(0) == 0
+    want, lse_w = R.attention(q, k, v, causal)
+    _close(out, want, 2e-2, 2e-2, "attention out")
+    _close(lse, lse_w, 2e-2, 1e-3, "attention lse")
+
+
+def test_flash_fwd_packed_qkv():
+    torch.manual_seed(0)
+    B, S, Hq, Hkv, D = 2, 256, 8, 2, 128
+    qkv = _rand(B, S, Hq + 2 * Hkv, D)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    out, _ = F.flash_attn_fwd(q, k, v, True)
+    want, _ = R.attention(q, k, v, True)
+    _close(out, want, 2e-2, 2e-2, "packed qkv")
+    assert _native.device_status(0) == 0
