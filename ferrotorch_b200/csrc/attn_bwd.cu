@@ -1,0 +1,497 @@
+// Flash-attention backward on tcgen05 / TMEM for sm_100a (bf16, head_dim 64/128, causal or
+// full, GQA).  The reference has no GPU attention backward at all (its flash kernel is
+// forward-only, ferrotorch-gpu/src/flash_attention.rs:628-687; the CPU backward is
+// ferrotorch-nn/src/flash_attention.rs:59-647), so the math below is the standard
+// recompute-from-LSE formulation of that CPU backward:
+//     P  = exp(S * scale - lse)          S  = Q K^T
+//     dP = dO V^T                        dS = P * (dP - delta) * scale,  delta = rowsum(dO * O)
+//     dV = P^T dO      dK = dS^T Q       dQ = dS K
+//
+// Two launches of one templated kernel, each CTA owning a resident 128-row tile (TMEM lanes)
+// and streaming 64-row blocks of the other side through a 2-stage TMA ring:
+//   dK/dV pass: resident = keys j (K_j, V_j); streamed = queries (Q_c, dO_c) of every query
+//               head in the KV group, so the GQA reduction happens in the TMEM accumulators.
+//               Scores are computed transposed (S^T = K Q^T), so a thread owns a key row and
+//               P^T / dS^T rows land in shared memory as K-major A operands.
+//   dQ pass:    resident = queries i (Q_i, dO_i); streamed = keys (K_c, V_c); dQ += dS K_c.
+// Per step: 2 score MMAs (128x64xD) into double-buffered TMEM, the softmax warps turn them
+// into bf16 P / dS tiles (one 128-byte swizzled row per thread), then 1-2 accumulate MMAs
+// (128xDx64) whose B operand is the streamed tile read MN-major.  All waits are bounded.
+#include "ft_host.h"
+#include "ft_ptx.cuh"
+
+namespace ft {
+
+constexpr int AB_R = 128;  // resident rows
+constexpr int AB_C = 64;   // streamed block rows
+constexpr int AB_THREADS = 384;  // 4 role warps + 8 softmax warps (2 per TMEM lane quarter)
+constexpr int AB_SPLIT = 2;      // column halves of a score tile, one per softmax warpgroup
+
+template <int HD, bool IS_DQ>
+struct AttBwdCfg {
+  static constexpr int R_TILE = AB_R * HD * 2;          // one resident operand
+  static constexpr int C_TILE = AB_C * HD * 2;          // one streamed operand
+  static constexpr int PS_TILE = AB_R * AB_C * 2;       // P^T or dS tile (128 rows x 128 bytes)
+  static constexpr int N_PS = IS_DQ ? 1 : 2;
+  static constexpr int OFF_R = 0;
+  static constexpr int OFF_C = 2 * R_TILE;
+  static constexpr int OFF_PS = OFF_C + 2 * 2 * C_TILE;                 // 2 stages x 2 operands
+  static constexpr int OFF_LD = OFF_PS + 2 * N_PS * PS_TILE;           // 2 buffers
+  static constexpr int OFF_BAR = OFF_LD + 2 * 2 * AB_C * 4;            // lse/delta, 2 buffers
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  // TMEM columns: S[2] (64 each), dP[2] (64 each), accumulators of HD columns
+  static constexpr int COL_S = 0, COL_DP = 128, COL_ACC0 = 256, COL_ACC1 = 256 + HD;
+};
+
+struct AttBwdParams {
+  __nv_bfloat16* out0;  // dQ pass: dQ;  dK/dV pass: dK
+  __nv_bfloat16* out1;  // dK/dV pass: dV
+  long long ld0, ld1;   // token strides of out0 / out1
+  const float* lse;     // [B, Hq, Sq] log-sum-exp in base 2 (+inf for fully masked rows)
+  const float* delta;   // [B, Hq, Sq]
+  int B, Sq, Sk, Hq, Hkv;
+  int causal, causal_offset;
+  float scale, scale_log2;
+  int* status;
+};
+
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; one warp per (token, head) row.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  const float* __restrict__ lse, float* __restrict__ delta,
+                                  float* __restrict__ lse2, int B, int Sq, int Hq, int D, long long ldo,
+                                  long long lddo) {
+  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * Sq * Hq;
+  if (w >= total) return;
+  const int h = static_cast<int>(w % Hq);
+  const long long tok = w / Hq;
+  const __nv_bfloat16* op = o + tok * ldo + static_cast<long long>(h) * D;
+  const __nv_bfloat16* dp = dout + tok * lddo + static_cast<long long>(h) * D;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + d));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + d));
+    s += a.x * b.x + a.y * b.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const int b_ = static_cast<int>(tok / Sq), i = static_cast<int>(tok % Sq);
+    const long long idx = (static_cast<long long>(b_) * Hq + h) * Sq + i;
+    delta[idx] = s;
+    const float l = lse[idx];
+    // base-2 log-sum-exp; a fully masked row (lse = -inf) gets +inf so that P = exp2(s - lse) = 0
+    lse2[idx] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+  }
+}
+
+// tmR1/tmR2: resident operands (dK/dV: K, V; dQ: Q, dO); tmC1/tmC2: streamed (dK/dV: Q, dO;
+// dQ: K, V).  All are 3-D maps {heads*D, seq, batch} with 64-element (128-byte) boxes.
+template <int HD, bool IS_DQ>
+__global__ void __launch_bounds__(AB_THREADS, 1)
+flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
+                         const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
+                         const AttBwdParams p) {
+  using Cfg = AttBwdCfg<HD, IS_DQ>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sR1 = sbase + Cfg::OFF_R, sR2 = sR1 + Cfg::R_TILE;
+  const uint32_t sC = sbase + Cfg::OFF_C;    // stage s: C1 at sC + s*2*C_TILE, C2 right after
+  const uint32_t sPS = sbase + Cfg::OFF_PS;  // buffer b: tiles at sPS + b*N_PS*PS_TILE
+  enum { R_FULL = 0, C_FULL = 1, C_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, P_EMPTY = 11,
+         ACC_FULL = 13, NBARS = 14 };
+  const uint32_t bar0 = sbase + Cfg::OFF_BAR;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 8 * NBARS);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int batch = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  // resident tile index; heavy tiles first under a causal mask
+  int rblk, head_r;  // head_r: kv head (dK/dV) or q head (dQ)
+  head_r = blockIdx.y;
+  int c_begin, c_end, n_heads_iter;
+  if constexpr (IS_DQ) {
+    const int nb = (p.Sq + AB_R - 1) / AB_R;
+    rblk = nb - 1 - blockIdx.x;
+    c_begin = 0;
+    int kv_end = p.Sk;
+    if (p.causal) kv_end = min(p.Sk, rblk * AB_R + AB_R + p.causal_offset);
+    c_end = kv_end > 0 ? (kv_end + AB_C - 1) / AB_C : 0;
+    n_heads_iter = 1;
+  } else {
+    rblk = blockIdx.x;
+    c_end = (p.Sq + AB_C - 1) / AB_C;
+    c_begin = 0;
+    if (p.causal) {
+      const int first_q = rblk * AB_R - p.causal_offset;  // first query that sees key rblk*128
+      c_begin = first_q > 0 ? first_q / AB_C : 0;
+    }
+    if (c_begin > c_end) c_begin = c_end;
+    n_heads_iter = group;
+  }
+  const int r0 = rblk * AB_R;
+  const int n_c = c_end - c_begin;
+  const int n_iter = n_c * n_heads_iter;
+  const int kv_head = IS_DQ ? head_r / group : head_r;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    mbar_init(bar(R_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(C_FULL + s), 1);
+      mbar_init(bar(C_EMPTY + s), 1);
+      mbar_init(bar(S_FULL + s), 1);
+      mbar_init(bar(S_EMPTY + s), 4 * AB_SPLIT);
+      mbar_init(bar(P_FULL + s), 4 * AB_SPLIT);
+      mbar_init(bar(P_EMPTY + s), 1);
+    }
+    mbar_init(bar(ACC_FULL), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmR1);
+    tma_prefetch_desc(&tmR2);
+    tma_prefetch_desc(&tmC1);
+    tma_prefetch_desc(&tmC2);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // iteration t -> (query head, streamed block)
+  auto iter_head = [&](int t) { return IS_DQ ? head_r : head_r * group + t / n_c; };
+  auto iter_cblk = [&](int t) { return c_begin + (IS_DQ ? t : t % n_c); };
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      // resident operands: for dQ they belong to query head head_r, for dK/dV to kv head head_r
+      mbar_expect_tx(bar(R_FULL), 2 * Cfg::R_TILE);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_3d(sR1 + c * (AB_R * 128), &tmR1, bar(R_FULL), head_r * HD + c * 64, r0, batch);
+        tma_load_3d(sR2 + c * (AB_R * 128), &tmR2, bar(R_FULL), head_r * HD + c * 64, r0, batch);
+      }
+      for (int t = 0; t < n_iter; ++t) {
+        const int st = t & 1;
+        if (!mbar_wait(bar(C_EMPTY + st), ((t >> 1) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) break;
+        const int hc = IS_DQ ? kv_head : iter_head(t);
+        const int row = iter_cblk(t) * AB_C;
+        const uint32_t c1 = sC + st * 2 * Cfg::C_TILE, c2 = c1 + Cfg::C_TILE;
+        mbar_expect_tx(bar(C_FULL + st), 2 * Cfg::C_TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_3d(c1 + c * (AB_C * 128), &tmC1, bar(C_FULL + st), hc * HD + c * 64, row, batch);
+          tma_load_3d(c2 + c * (AB_C * 128), &tmC2, bar(C_FULL + st), hc * HD + c * 64, row, batch);
+        }
+      }
+      if (*abort_word) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(AB_R, AB_C, 1, 0, 0);   // 128 x 64, K-major both
+      constexpr uint32_t idesc_acc = make_idesc_f16(AB_R, HD, 1, 0, 1);   // 128 x HD, B MN-major
+      auto issue_scores = [&](int t) {
+        const int st = t & 1;
+        const uint32_t c1 = sC + st * 2 * Cfg::C_TILE, c2 = c1 + Cfg::C_TILE;
+        const uint32_t dS_ = tmem_base + Cfg::COL_S + st * AB_C;
+        const uint32_t dP_ = tmem_base + Cfg::COL_DP + st * AB_C;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t ro = (kk >> 2) * (AB_R * 128) + (kk & 3) * 32;
+          const uint32_t co = (kk >> 2) * (AB_C * 128) + (kk & 3) * 32;
+          umma_f16_ss(dS_, make_smem_desc_sw128(sR1 + ro, 16, 1024), make_smem_desc_sw128(c1 + co, 16, 1024),
+                      idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t ro = (kk >> 2) * (AB_R * 128) + (kk & 3) * 32;
+          const uint32_t co = (kk >> 2) * (AB_C * 128) + (kk & 3) * 32;
+          umma_f16_ss(dP_, make_smem_desc_sw128(sR2 + ro, 16, 1024), make_smem_desc_sw128(c2 + co, 16, 1024),
+                      idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(S_FULL + st));
+      };
+      bool ok = mbar_wait(bar(R_FULL), 0, abort_word, FT_ERR_TIMEOUT_MMA) &&
+                mbar_wait(bar(C_FULL + 0), 0, abort_word, FT_ERR_TIMEOUT_MMA);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int t = 0; t < n_iter && ok; ++t) {
+        if (t + 1 < n_iter) {
+          const int tn = t + 1, st = tn & 1;
+          ok = mbar_wait(bar(C_FULL + st), (tn >> 1) & 1, abort_word, FT_ERR_TIMEOUT_MMA) &&
+               mbar_wait(bar(S_EMPTY + st), ((tn >> 1) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(tn);
+        }
+        const int st = t & 1;
+        if (!mbar_wait(bar(P_FULL + st), (t >> 1) & 1, abort_word, FT_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t c1 = sC + st * 2 * Cfg::C_TILE, c2 = c1 + Cfg::C_TILE;
+        const uint32_t ps = sPS + st * Cfg::N_PS * Cfg::PS_TILE;
+        // the streamed tile as an MN-major B operand: 64-column chunks of [64 rows x 128 B]
+#pragma unroll
+        for (int kk = 0; kk < AB_C / 16; ++kk) {
+          if constexpr (IS_DQ) {
+            // dQ += dS K_c
+            umma_f16_ss(tmem_base + Cfg::COL_ACC0, make_smem_desc_sw128(ps + kk * 32, 16, 1024),
+                        make_smem_desc_sw128(c1 + kk * 2048, AB_C * 128, 1024), idesc_acc,
+                        (t > 0 || kk > 0) ? 1u : 0u);
+          } else {
+            // dK += dS^T Q_c ; dV += P^T dO_c
+            umma_f16_ss(tmem_base + Cfg::COL_ACC0,
+                        make_smem_desc_sw128(ps + Cfg::PS_TILE + kk * 32, 16, 1024),
+                        make_smem_desc_sw128(c1 + kk * 2048, AB_C * 128, 1024), idesc_acc,
+                        (t > 0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss(tmem_base + Cfg::COL_ACC1, make_smem_desc_sw128(ps + kk * 32, 16, 1024),
+                        make_smem_desc_sw128(c2 + kk * 2048, AB_C * 128, 1024), idesc_acc,
+                        (t > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(bar(P_EMPTY + st));
+        umma_commit(bar(C_EMPTY + st));
+      }
+      if (ok) umma_commit(bar(ACC_FULL));
+    }
+  } else if (warp >= 4) {
+    const int ew = warp & 3;             // TMEM lane quarter
+    const int half = (warp - 4) >> 2;    // which 32 of the 64 score columns this warp handles
+    const int r = ew * 32 + lane;
+    const int grow = r0 + r;             // global row on the resident side
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
+    float my_lse = INFINITY, my_delta = 0.f;
+    if constexpr (IS_DQ) {
+      if (grow < p.Sq) {
+        const long long idx = (static_cast<long long>(batch) * p.Hq + head_r) * p.Sq + grow;
+        my_lse = p.lse[idx];
+        my_delta = p.delta[idx];
+      }
+    }
+    const bool vec_ok = (p.Sq & 3) == 0;
+    bool ok = true;
+    for (int t = 0; t < n_iter && ok; ++t) {
+      const int st = t & 1;
+      const int c0 = iter_cblk(t) * AB_C + half * 32;  // first global column of this thread
+      // statistics of the 32 columns (dK/dV pass: columns are queries)
+      float lse_c[32], delta_c[32];
+      if constexpr (!IS_DQ) {
+        const long long idx = (static_cast<long long>(batch) * p.Hq + iter_head(t)) * p.Sq + c0;
+        if (vec_ok && c0 + 32 <= p.Sq) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(p.lse + idx) + i);
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.delta + idx) + i);
+            lse_c[4 * i] = a.x; lse_c[4 * i + 1] = a.y; lse_c[4 * i + 2] = a.z; lse_c[4 * i + 3] = a.w;
+            delta_c[4 * i] = b.x; delta_c[4 * i + 1] = b.y; delta_c[4 * i + 2] = b.z; delta_c[4 * i + 3] = b.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const bool in = c0 + i < p.Sq;
+            lse_c[i] = in ? __ldg(p.lse + idx + i) : INFINITY;
+            delta_c[i] = in ? __ldg(p.delta + idx + i) : 0.f;
+          }
+        }
+      }
+      // does any element of this 128 x 32 slab need masking?  (uniform per warp)
+      bool need_mask;
+      if constexpr (IS_DQ) {
+        const int last_vis = p.causal ? min(p.Sk - 1, r0 + ew * 32 + p.causal_offset) : p.Sk - 1;
+        need_mask = c0 + 31 > last_vis;
+      } else {
+        need_mask = (r0 + ew * 32 + 31 >= p.Sk) || (p.causal && r0 + ew * 32 + 31 > c0 + p.causal_offset);
+      }
+      if (!mbar_wait(bar(S_FULL + st), (t >> 1) & 1, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t a[32], b[32];
+      tmem_ld_32x32(lane_addr + Cfg::COL_S + st * AB_C + half * 32, a);
+      tmem_ld_32x32(lane_addr + Cfg::COL_DP + st * AB_C + half * 32, b);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_EMPTY + st));
+
+      uint32_t pk[16], dk[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float lse_v = IS_DQ ? my_lse : lse_c[c + e];
+          const float delta_v = IS_DQ ? my_delta : delta_c[c + e];
+          float pe = fast_exp2(fmaf(__uint_as_float(a[c + e]), p.scale_log2, -lse_v));
+          if (need_mask) {
+            const int col = c0 + c + e;
+            const bool visible = IS_DQ ? (col < p.Sk && (!p.causal || col <= grow + p.causal_offset))
+                                       : (grow < p.Sk && (!p.causal || grow <= col + p.causal_offset));
+            pe = visible ? pe : 0.f;
+          }
+          pv[e] = pe;
+          dv[e] = pe * (__uint_as_float(b[c + e]) - delta_v) * p.scale;
+        }
+        pk[c >> 1] = pack_bf16x2(pv[0], pv[1]);
+        dk[c >> 1] = pack_bf16x2(dv[0], dv[1]);
+      }
+      // the P / dS buffers of this stage must have been consumed by the MMAs of step t-2
+      if (!mbar_wait(bar(P_EMPTY + st), ((t >> 1) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      const uint32_t ps = sPS + st * Cfg::N_PS * Cfg::PS_TILE;
+#pragma unroll
+      for (int uu = 0; uu < 4; ++uu) {
+        const int u = half * 4 + uu;
+        const uint32_t off = r * 128 + ((u ^ (r & 7)) << 4);
+        if constexpr (IS_DQ) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + off), "r"(dk[uu * 4]),
+                       "r"(dk[uu * 4 + 1]), "r"(dk[uu * 4 + 2]), "r"(dk[uu * 4 + 3]) : "memory");
+        } else {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + off), "r"(pk[uu * 4]),
+                       "r"(pk[uu * 4 + 1]), "r"(pk[uu * 4 + 2]), "r"(pk[uu * 4 + 3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + Cfg::PS_TILE + off),
+                       "r"(dk[uu * 4]), "r"(dk[uu * 4 + 1]), "r"(dk[uu * 4 + 2]), "r"(dk[uu * 4 + 3]) : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + st));
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (ok && n_iter > 0) {
+      ok = mbar_wait(bar(ACC_FULL), 0, abort_word, FT_ERR_TIMEOUT_EPILOGUE);
+      tc_fence_after();
+    }
+    if (ok) {
+      const int s_lim = IS_DQ ? p.Sq : p.Sk;
+      const bool row_ok = grow < s_lim;
+      const long long tok = static_cast<long long>(batch) * s_lim + grow;
+#pragma unroll
+      for (int acc = 0; acc < (IS_DQ ? 1 : 2); ++acc) {
+        __nv_bfloat16* orow = (acc == 0 ? p.out0 + tok * p.ld0 : p.out1 + tok * p.ld1) +
+                              static_cast<long long>(head_r) * HD;
+        const uint32_t col = acc == 0 ? Cfg::COL_ACC0 : Cfg::COL_ACC1;
+        // the two warps of a lane quarter split the HD columns
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          const int cc = half * (HD / 64) + c;  // 32-column chunk index
+          uint32_t t32[32];
+          if (n_iter > 0) {
+            tmem_ld_32x32(lane_addr + col + cc * 32, t32);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t32[i] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(t32[g * 8 + 0]), __uint_as_float(t32[g * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(t32[g * 8 + 2]), __uint_as_float(t32[g * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(t32[g * 8 + 4]), __uint_as_float(t32[g * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(t32[g * 8 + 6]), __uint_as_float(t32[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status) atomicCAS(p.status, 0, *abort_word);
+}
+
+template <int HD, bool IS_DQ>
+static int launch_bwd(const CUtensorMap& r1, const CUtensorMap& r2, const CUtensorMap& c1,
+                      const CUtensorMap& c2, const AttBwdParams& p, int device, cudaStream_t stream) {
+  using Cfg = AttBwdCfg<HD, IS_DQ>;
+  auto kern = flash_bwd_tcgen05_kernel<HD, IS_DQ>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[device]) {
+    FT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    attr_set[device] = true;
+  }
+  dim3 grid(IS_DQ ? (p.Sq + AB_R - 1) / AB_R : (p.Sk + AB_R - 1) / AB_R, IS_DQ ? p.Hq : p.Hkv, p.B);
+  kern<<<grid, AB_THREADS, Cfg::SMEM_BYTES, stream>>>(r1, r2, c1, c2, p);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+}  // namespace ft
+
+// Gradients of ft_flash_attn_fwd.  q/k/v/o/dout/dq/dk/dv are [B, S, H, D] with packed heads and
+// the given token strides (elements); lse [B, Hq, Sq] from the forward; delta_scratch: 2*B*Hq*Sq
+// floats of scratch (16-byte aligned).  dq/dk/dv are fully overwritten.
+FT_API int ft_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                             const float* lse, void* dq, void* dk, void* dv, float* delta_scratch, int B,
+                             int Sq, int Sk, int Hq, int Hkv, int D, long long ldq, long long ldk,
+                             long long ldv, long long ldo, long long lddq, long long lddk, long long lddv,
+                             float scale, int causal, int causal_offset, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  using namespace ft;
+  FT_REQUIRE(q && k && v && o && dout && lse && dq && dk && dv && delta_scratch, "ft_flash_attn_bwd: null pointer");
+  FT_REQUIRE(D == 64 || D == 128, "ft_flash_attn_bwd: head_dim %d not supported (64, 128)", D);
+  FT_REQUIRE(B > 0 && Sq > 0 && Sk > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "ft_flash_attn_bwd: bad shape");
+  FT_REQUIRE(ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 && ldo % 8 == 0 && lddq % 8 == 0 &&
+                 lddk % 8 == 0 && lddv % 8 == 0,
+             "ft_flash_attn_bwd: token strides must be multiples of 8 elements");
+  {
+    const long long rows = static_cast<long long>(B) * Sq * Hq;
+    const int threads = 256;
+    const long long blocks = (rows * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, delta_scratch,
+        delta_scratch + rows, B, Sq, Hq, D, ldo, static_cast<long long>(Hq) * D);
+    FT_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+  }
+  CUtensorMap tq_r, tdo_r, tk_r, tv_r, tq_c, tdo_c, tk_c, tv_c;
+  const long long lddo = static_cast<long long>(Hq) * D;
+  auto mk = [&](CUtensorMap* m, const void* base, int H, int S, long long ld, int box_rows) {
+    return make_tmap_3d(m, base, 2, static_cast<uint64_t>(H) * D, S, B, ld * 2,
+                        static_cast<uint64_t>(S) * ld * 2, 64, box_rows, 1, 3);
+  };
+  int rc;
+  if ((rc = mk(&tk_r, k, Hkv, Sk, ldk, AB_R))) return rc;
+  if ((rc = mk(&tv_r, v, Hkv, Sk, ldv, AB_R))) return rc;
+  if ((rc = mk(&tq_c, q, Hq, Sq, ldq, AB_C))) return rc;
+  if ((rc = mk(&tdo_c, dout, Hq, Sq, lddo, AB_C))) return rc;
+  if ((rc = mk(&tq_r, q, Hq, Sq, ldq, AB_R))) return rc;
+  if ((rc = mk(&tdo_r, dout, Hq, Sq, lddo, AB_R))) return rc;
+  if ((rc = mk(&tk_c, k, Hkv, Sk, ldk, AB_C))) return rc;
+  if ((rc = mk(&tv_c, v, Hkv, Sk, ldv, AB_C))) return rc;
+
+  AttBwdParams p;
+  p.lse = delta_scratch + static_cast<long long>(B) * Sq * Hq; p.delta = delta_scratch;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
+  p.causal = causal; p.causal_offset = causal_offset;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = device_status_word(device);
+  // dK / dV
+  p.out0 = static_cast<__nv_bfloat16*>(dk); p.ld0 = lddk;
+  p.out1 = static_cast<__nv_bfloat16*>(dv); p.ld1 = lddv;
+  rc = D == 128 ? launch_bwd<128, false>(tk_r, tv_r, tq_c, tdo_c, p, device, stream)
+                : launch_bwd<64, false>(tk_r, tv_r, tq_c, tdo_c, p, device, stream);
+  if (rc) return rc;
+  // dQ
+  p.out0 = static_cast<__nv_bfloat16*>(dq); p.ld0 = lddq;
+  p.out1 = nullptr; p.ld1 = 0;
+  return D == 128 ? launch_bwd<128, true>(tq_r, tdo_r, tk_c, tv_c, p, device, stream)
+                  : launch_bwd<64, true>(tq_r, tdo_r, tk_c, tv_c, p, device, stream);
+}

@@ -1,0 +1,171 @@
+"""Transformer building blocks on the native kernels.
+
+Module names and parameter layouts follow the reference's ``ferrotorch-nn`` so checkpoints
+load unchanged: ``Linear.weight`` is ``[out, in]`` (ferrotorch-nn/src/linear.rs:101),
+``RMSNorm.weight`` is ``[hidden]`` (norm.rs:1222), RoPE has the two pair conventions and the
+scaling modes of transformer.rs:66-326, ``SwiGLU`` is ``down(act(gate(x)) * up(x))``
+(transformer.rs:693-764) and ``KVCache`` appends along the sequence (transformer.rs:864-928).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from ..ops import functional as F
+from ..ops import reference as ref
+
+
+class Linear(nn.Linear):
+    """``y = x W^T + b`` on the tcgen05 GEMM (bf16 CUDA inputs); any other input uses torch."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.weight, self.bias)
+
+
+class FusedLinearActivation(nn.Module):
+    """Linear followed by relu / gelu / silu in the GEMM epilogue -- the pattern the reference's
+    JIT rewrites to ``FusedLinearActivation`` (ferrotorch-jit/src/optimize.rs:523-601).
+    Inference only (no autograd formula); training code uses ``Linear`` + activation."""
+
+    def __init__(self, in_features: int, out_features: int, activation: str = "relu", bias: bool = True):
+        super().__init__()
+        self.linear = Linear(in_features, out_features, bias=bias)
+        self.activation = activation
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w, b = self.linear.weight, self.linear.bias
+        if x.is_cuda and x.dtype == torch.bfloat16 and not torch.is_grad_enabled():
+            y = F.gemm_nt(x.reshape(-1, x.shape[-1]), w, bias=b, activation=self.activation)
+            return y.view(*x.shape[:-1], w.shape[0])
+        return getattr(torch.nn.functional, self.activation)(torch.nn.functional.linear(x, w, b))
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
+        """With ``residual`` returns ``(norm(x + residual), x + residual)`` from one kernel."""
+        return F.rmsnorm(x, self.weight, self.eps, residual)
+
+    def extra_repr(self) -> str:
+        return "%d, eps=%g" % (self.weight.numel(), self.eps)
+
+
+class RotaryPositionEmbedding(nn.Module):
+    """cos/sin tables + in-place rotation.  ``scaling``: None | {"type": "linear"|"ntk"|"yarn"|"llama3", ...}."""
+
+    def __init__(self, head_dim: int, max_position_embeddings: int = 8192, theta: float = 10000.0,
+                 interleaved: bool = False, scaling: dict | None = None):
+        super().__init__()
+        self.head_dim, self.max_pos, self.theta = head_dim, max_position_embeddings, theta
+        self.interleaved, self.scaling = interleaved, scaling
+        cos, sin = ref.rope_tables(head_dim, max_position_embeddings, theta, scaling)
+        self.register_buffer("cos", cos, persistent=False)
+        self.register_buffer("sin", sin, persistent=False)
+
+    def _tables(self, device):
+        if self.cos.device != device or self.cos.dtype != torch.float32:
+            self.cos = self.cos.to(device=device, dtype=torch.float32)
+            self.sin = self.sin.to(device=device, dtype=torch.float32)
+        return self.cos, self.sin
+
+    def forward(self, x: torch.Tensor, *, positions: torch.Tensor | None = None, seq_len: int = 0,
+                pos_offset: int = 0, n_rot_heads: int | None = None) -> torch.Tensor:
+        cos, sin = self._tables(x.device)
+        return F.rope_(x, cos, sin, positions=positions, n_rot_heads=n_rot_heads, seq_len=seq_len,
+                       pos_offset=pos_offset, interleaved=self.interleaved)
+
+
+class SwiGLU(nn.Module):
+    """Gated MLP with one fused ``[gate | up]`` projection (2F x H) so that the activation kernel
+    reads one GEMM output."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
+        super().__init__()
+        self.gate_up_proj = Linear(hidden_size, 2 * intermediate_size, bias=bias)
+        self.down_proj = Linear(intermediate_size, hidden_size, bias=bias)
+        self.activation = activation
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(F.swiglu(self.gate_up_proj(x), self.activation))
+
+
+class KVCache:
+    """Contiguous per-layer cache ``[B, max_len, Hkv, D]`` with an append cursor
+    (ferrotorch-nn/src/transformer.rs:864-928; ferrotorch-llama/src/kv_cache.rs:37-136)."""
+
+    def __init__(self, batch: int, max_len: int, n_kv_heads: int, head_dim: int, device=None,
+                 dtype=torch.bfloat16):
+        self.k = torch.zeros(batch, max_len, n_kv_heads, head_dim, device=device, dtype=dtype)
+        self.v = torch.zeros_like(self.k)
+        self.len = 0
+
+    def append(self, k: torch.Tensor, v: torch.Tensor):
+        n = k.shape[1]
+        if self.len + n > self.k.shape[1]:
+            raise ValueError("KVCache overflow: %d + %d > %d" % (self.len, n, self.k.shape[1]))
+        self.k[:, self.len:self.len + n].copy_(k)
+        self.v[:, self.len:self.len + n].copy_(v)
+        self.len += n
+        return self.k[:, :self.len], self.v[:, :self.len]
+
+    def reset(self):
+        self.len = 0
+
+
+def repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
+    """``[B, Hkv, S, D] -> [B, Hkv * n_rep, S, D]`` (ferrotorch-nn/src/attention.rs:682)."""
+    return ref.repeat_kv(x, n_rep)
+
+
+def scaled_dot_product_attention(q, k, v, causal: bool = True, scale: float | None = None):
+    """Attention on ``[B, S, H, D]`` tensors (differentiable; GQA when ``k`` has fewer heads)."""
+    from ..ops.attention import flash_attention
+
+    return flash_attention(q, k, v, causal=causal, scale=scale)
+
+
+class GQAAttention(nn.Module):
+    """Grouped-query self-attention with a fused QKV projection and in-place RoPE on the packed
+    buffer (ferrotorch-llama/src/attention.rs:213-280 runs q/k/v as three GEMMs, three layout
+    transposes, two RoPE launches and two repeat_kv copies; here: one GEMM, one RoPE launch,
+    flash attention reading the packed buffer, one output GEMM)."""
+
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int | None = None,
+                 rope: RotaryPositionEmbedding | None = None, bias: bool = False):
+        super().__init__()
+        self.n_heads, self.n_kv_heads = n_heads, n_kv_heads
+        self.head_dim = head_dim or hidden_size // n_heads
+        self.qkv_proj = Linear(hidden_size, (n_heads + 2 * n_kv_heads) * self.head_dim, bias=bias)
+        self.o_proj = Linear(n_heads * self.head_dim, hidden_size, bias=bias)
+        self.rope = rope
+
+    def forward(self, x: torch.Tensor, *, cache: KVCache | None = None, positions: torch.Tensor | None = None,
+                causal: bool = True) -> torch.Tensor:
+        from ..ops.attention import flash_attention
+
+        B, S, _ = x.shape
+        Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        qkv = self.qkv_proj(x).view(B, S, Hq + 2 * Hkv, D)
+        if self.rope is not None:
+            off = cache.len if cache is not None else 0
+            qkv = self.rope(qkv, positions=positions, seq_len=S, pos_offset=off, n_rot_heads=Hq + Hkv)
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        if cache is not None:
+            k, v = cache.append(k, v)
+        o = flash_attention(q, k, v, causal=causal)
+        return self.o_proj(o.reshape(B, S, Hq * D))
+
+
+def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
+    """Global-norm clipping; returns the pre-clip norm (ferrotorch-nn/src/utils.rs:148-240)."""
+    return torch.nn.utils.clip_grad_norm_(parameters, max_norm, norm_type)
+
+
+def clip_grad_value_(parameters, clip_value: float) -> None:
+    torch.nn.utils.clip_grad_value_(parameters, clip_value)

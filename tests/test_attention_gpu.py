@@ -50,3 +50,47 @@ def test_flash_fwd_packed_qkv():
     want, _ = R.attention(q, k, v, True)
     _close(out, want, 2e-2, 2e-2, "packed qkv")
     assert _native.device_status(0) == 0
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", [
+    (1, 128, 128, 2, 2, 128, True),
+    (2, 256, 256, 4, 2, 128, True),
+    (1, 320, 320, 4, 1, 128, False),
+    (2, 200, 200, 4, 2, 128, True),
+    (1, 100, 333, 2, 1, 128, True),
+    (1, 1024, 1024, 8, 2, 128, True),
+    (2, 256, 256, 4, 4, 64, True),
+    (1, 130, 190, 2, 2, 64, False),
+])
+def test_flash_bwd(B, Sq, Sk, Hq, Hkv, D, causal):
+    from ferrotorch_b200.ops.attention import flash_attention
+
+    torch.manual_seed(Sq * 3 + Sk + Hq)
+    q, k, v = (_rand(B, Sq, Hq, D).requires_grad_(), _rand(B, Sk, Hkv, D).requires_grad_(),
+               _rand(B, Sk, Hkv, D).requires_grad_())
+    do = _rand(B, Sq, Hq, D, scale=0.5)
+    out = flash_attention(q, k, v, causal=causal)
+    out.backward(do)
+    torch.cuda.synchronize()
+    assert _native.device_status(0) == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    want, _ = R.attention(qr, kr, vr, causal)
+    want.backward(do.float())
+    _close(q.grad, qr.grad, 3e-2, 3e-2, "dq")
+    _close(k.grad, kr.grad, 3e-2, 3e-2, "dk")
+    _close(v.grad, vr.grad, 3e-2, 3e-2, "dv")
+
+
+def test_flash_bwd_packed_qkv_grad_layout():
+    from ferrotorch_b200.ops.attention import flash_attention
+
+    torch.manual_seed(2)
+    B, S, Hq, Hkv, D = 1, 256, 8, 2, 128
+    qkv = _rand(B, S, Hq + 2 * Hkv, D).requires_grad_()
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    do = _rand(B, S, Hq, D, scale=0.5)
+    flash_attention(q, k, v, causal=True).backward(do)
+    ref_in = qkv.detach().float().requires_grad_()
+    qr, kr, vr = ref_in[:, :, :Hq], ref_in[:, :, Hq:Hq + Hkv], ref_in[:, :, Hq + Hkv:]
+    R.attention(qr, kr, vr, True)[0].backward(do.float())
+    _close(qkv.grad, ref_in.grad, 3e-2, 3e-2, "packed dqkv")
