@@ -1,0 +1,10 @@
+"""Layers.  Everything in :mod:`torch.nn` is re-exported under the same names (the reference's
+``ferrotorch-nn`` mirrors that surface: activations, convolutions, norms, pools, RNNs,
+transformer blocks, losses, containers, init), and the layers that have a native sm_100a
+kernel are replaced by the versions in :mod:`ferrotorch_b200.nn.layers`."""
+from torch.nn import *  # noqa: F401,F403
+from torch.nn import functional, init, utils  # noqa: F401
+
+from .layers import (FusedLinearActivation, GQAAttention, KVCache, Linear, RMSNorm,  # noqa: F401
+                     RotaryPositionEmbedding, SwiGLU, clip_grad_norm_, clip_grad_value_, repeat_kv,
+                     scaled_dot_product_attention)

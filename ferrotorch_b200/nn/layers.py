@@ -64,15 +64,18 @@ class RotaryPositionEmbedding(nn.Module):
         super().__init__()
         self.head_dim, self.max_pos, self.theta = head_dim, max_position_embeddings, theta
         self.interleaved, self.scaling = interleaved, scaling
-        cos, sin = ref.rope_tables(head_dim, max_position_embeddings, theta, scaling)
-        self.register_buffer("cos", cos, persistent=False)
-        self.register_buffer("sin", sin, persistent=False)
+        # fp32 tables kept outside the module's buffers so that ``module.to(bfloat16)`` cannot
+        # round them; one copy per device, created on first use
+        self._tables_cpu = ref.rope_tables(head_dim, max_position_embeddings, theta, scaling)
+        self._tables_dev: dict = {}
 
     def _tables(self, device):
-        if self.cos.device != device or self.cos.dtype != torch.float32:
-            self.cos = self.cos.to(device=device, dtype=torch.float32)
-            self.sin = self.sin.to(device=device, dtype=torch.float32)
-        return self.cos, self.sin
+        key = str(device)
+        t = self._tables_dev.get(key)
+        if t is None:
+            t = tuple(x.to(device) for x in self._tables_cpu)
+            self._tables_dev[key] = t
+        return t
 
     def forward(self, x: torch.Tensor, *, positions: torch.Tensor | None = None, seq_len: int = 0,
                 pos_offset: int = 0, n_rot_heads: int | None = None) -> torch.Tensor:
@@ -147,10 +150,16 @@ class GQAAttention(nn.Module):
 
     def forward(self, x: torch.Tensor, *, cache: KVCache | None = None, positions: torch.Tensor | None = None,
                 causal: bool = True) -> torch.Tensor:
-        from ..ops.attention import flash_attention
+        from ..ops.attention import flash_attention, qkv_attention
 
         B, S, _ = x.shape
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        if cache is None and positions is None:
+            cos, sin = self.rope._tables(x.device) if self.rope is not None else (None, None)
+            o = qkv_attention(x, self.qkv_proj.weight, self.qkv_proj.bias, cos, sin, n_heads=Hq,
+                              n_kv_heads=Hkv, head_dim=D, causal=causal,
+                              interleaved=self.rope.interleaved if self.rope is not None else False)
+            return self.o_proj(o)
         qkv = self.qkv_proj(x).view(B, S, Hq + 2 * Hkv, D)
         if self.rope is not None:
             off = cache.len if cache is not None else 0

@@ -79,3 +79,79 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal
         off = causal_offset
         return ref.attention(q, k, v, causal, scale, off)[0]
     return _FlashAttnFn.apply(q, k, v, causal, scale, causal_offset)
+
+
+class _QKVAttentionFn(torch.autograd.Function):
+    """QKV projection + in-place RoPE + flash attention as one autograd node.
+
+    Keeping the packed ``[B, S, Hq + 2 Hkv, D]`` buffer private to the node means RoPE runs in
+    place with no autograd bookkeeping and the backward writes one packed gradient buffer that
+    feeds the projection's dgrad / wgrad GEMMs directly (no per-slice zero-fill and add)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, cos, sin, Hq, Hkv, D, causal, interleaved):
+        B, S, H = x.shape
+        x2 = x.reshape(B * S, H)
+        qkv = torch.empty((B, S, Hq + 2 * Hkv, D), device=x.device, dtype=x.dtype)
+        F.gemm_nt(x2, w, bias=bias, out=qkv.view(B * S, -1))
+        if cos is not None:
+            F._rope_launch(qkv, cos, sin, None, Hq + Hkv, S, 0, interleaved, False)
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        out, lse = F.flash_attn_fwd(q, k, v, causal)
+        ctx.save_for_backward(x2, w, qkv, out, lse, cos if cos is not None else x.new_empty(0),
+                              sin if sin is not None else x.new_empty(0))
+        ctx.cfg = (Hq, Hkv, D, causal, interleaved, bias is not None, cos is not None, x.shape)
+        return out.view(B, S, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, w, qkv, out, lse, cos, sin = ctx.saved_tensors
+        Hq, Hkv, D, causal, interleaved, has_bias, has_rope, xshape = ctx.cfg
+        B, S = qkv.shape[0], qkv.shape[1]
+        dout = dout.reshape(B, S, Hq, D)
+        dout = dout if dout.is_contiguous() else dout.contiguous()
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
+        ld = (Hq + 2 * Hkv) * D
+        lib = _native.kernels()
+        rc = lib.ft_flash_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            F._get_scratch("attn_delta", 2 * B * Hq * S, q.device).data_ptr(),
+            B, S, S, Hq, Hkv, D, ld, ld, ld, Hq * D, ld, ld, ld, float(D ** -0.5), int(causal), 0,
+            F._dev(q), F._stream())
+        _native.check(rc, "ft_flash_attn_bwd")
+        if has_rope:
+            F._rope_launch(dqkv, cos, sin, None, Hq + Hkv, S, 0, interleaved, True)
+        d2 = dqkv.view(B * S, -1)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = F.gemm_nt(d2, w.t()).view(xshape)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                F.gemm_nt(d2.t(), x2.t(), out=mg, accumulate=True)
+                hook = getattr(w, "grad_ready_hook", None)
+                if hook is not None:
+                    hook(w)
+            else:
+                dw = F.gemm_nt(d2.t(), x2.t())
+        if has_bias and ctx.needs_input_grad[2]:
+            db = d2.float().sum(0).to(d2.dtype)
+        return dx, dw, db, None, None, None, None, None, None, None
+
+
+def qkv_attention(x: torch.Tensor, w_qkv: torch.Tensor, bias: torch.Tensor | None, cos, sin, *,
+                  n_heads: int, n_kv_heads: int, head_dim: int, causal: bool = True,
+                  interleaved: bool = False) -> torch.Tensor:
+    """Self-attention core from the normed hidden states: ``attn(rope(x W_qkv^T))`` -> ``[B, S, Hq*D]``."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and head_dim in (64, 128):
+        return _QKVAttentionFn.apply(x, w_qkv, bias, cos, sin, n_heads, n_kv_heads, head_dim, causal,
+                                     interleaved)
+    B, S, _ = x.shape
+    qkv = torch.nn.functional.linear(x, w_qkv, bias).view(B, S, n_heads + 2 * n_kv_heads, head_dim)
+    if cos is not None:
+        qkv = F.rope_(qkv, cos, sin, n_rot_heads=n_heads + n_kv_heads, seq_len=S, interleaved=interleaved)
+    q, k, v = qkv[:, :, :n_heads], qkv[:, :, n_heads:n_heads + n_kv_heads], qkv[:, :, n_heads + n_kv_heads:]
+    return flash_attention(q, k, v, causal=causal).reshape(B, S, n_heads * head_dim)

@@ -116,11 +116,14 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, bias):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        y = gemm_nt(x2, w, bias=bias)
+        # the output is allocated in its final shape (not returned as a view) so that callers
+        # may modify it in place
+        y = torch.empty((*shp[:-1], w.shape[0]), device=x.device, dtype=x.dtype)
+        gemm_nt(x2, w, bias=bias, out=y.view(-1, w.shape[0]))
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.in_shape = shp
-        return y.view(*shp[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
