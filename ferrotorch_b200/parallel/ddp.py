@@ -1,0 +1,220 @@
+"""Data-parallel training with the gradient all-reduce fused into the optimizer update.
+
+``FusedDDP`` plugs into :class:`ferrotorch_b200.train.engine.FlatTrainer`.  The parameter and
+gradient arenas are allocated in symmetric memory (every rank can address every peer's copy
+over NVLink).  The arena is cut into buckets in reverse parameter order like the reference's
+``compute_buckets`` (ferrotorch-distributed/src/ddp.rs:230-258, 25 MB default there); when the
+last weight-gradient kernel of a bucket has been enqueued, one ``ft_ddp_reduce_update`` launch
+on a side stream pulls this rank's 1/W slice of the bucket from every rank, averages it in fp32
+in rank order, applies AdamW / SGD to the fp32 master weights and moments of the slice and pushes
+the new bf16 weights to every rank -- overlapped with the rest of backward.  Every element is
+reduced and updated by exactly one rank, so replicas stay bitwise identical.
+
+``mode="nccl"`` is the baseline path: bucketed ``all_reduce`` (average) through NCCL on the
+side stream, then the local full-arena update.
+
+The reference's DDP synchronises after ``backward()`` returns, through host memory
+(ddp.rs:117-123, 265-311); ``broadcast_parameters`` mirrors ddp.rs:176-186.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+
+_i, _ll, _f, _vp, _u = _native._i, _native._ll, _native._f, _native._vp, ctypes.c_uint
+_native.register_protos({
+    "ft_comm_flag_count": (_ll, [_i]),
+    "ft_ddp_reduce_update": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _u, _f, _i, _i,
+                                  _f, _f, _f, _f, _f, _i, _f, _f, _i, _i, _ll, _i, _vp]),
+    "ft_comm_wait": (_i, [_vp, _i, _i, _i, _i, _i, _u, _ll, _i, _vp]),
+    "ft_comm_signal": (_i, [_vp, _i, _i, _i, _i, _i, _u, _i, _vp]),
+    "ft_allgather": (_i, [_vp, _vp, _ll, _vp, _i, _i, _i, _i, _u, _ll, _i, _vp]),
+})
+
+
+def _ptr_array(ptrs):
+    arr = (ctypes.c_void_p * 8)()
+    for i, p in enumerate(ptrs):
+        arr[i] = p
+    return arr
+
+
+class SymmetricBuffer:
+    """A tensor in symmetric memory plus the table of peer pointers to it."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, group, device):
+        import torch.distributed._symmetric_memory as symm
+
+        self.tensor = symm.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.ptr_array = _ptr_array(self.ptrs)
+
+
+def compute_buckets(ranges, slots, bucket_elems: int, align: int):
+    """Cut the arena ranges into buckets of ``bucket_elems`` elements (boundaries multiples of
+    ``align``; a bucket never straddles a parameter-group boundary).  Returned in reverse arena
+    order -- the order in which backward produces gradients -- each with the parameters that
+    overlap it (a large parameter belongs to several buckets)."""
+    cuts = []
+    for _, (s, e) in ranges.items():
+        lo = s
+        while lo < e:
+            hi = min(e, lo + bucket_elems)
+            cuts.append((lo, hi))
+            lo = hi
+    out = []
+    for lo, hi in sorted(cuts, reverse=True):
+        assert lo % align == 0 and (hi - lo) % align == 0, "arena ranges must be multiples of %d" % align
+        members = [p for _, p, o, k in slots if o < hi and o + k > lo]
+        out.append({"lo": lo, "hi": hi, "params": members})
+    return out
+
+
+class FusedDDP:
+    def __init__(self, group=None, mode: str = "fused", bucket_mb: float = 256.0, comm_blocks: int = 32,
+                 timeout_ms: int | None = None, late_params=()):
+        assert mode in ("fused", "nccl")
+        self.group = group if group is not None else dist.group.WORLD
+        self.mode = mode
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.bucket_mb = bucket_mb
+        self.comm_blocks = comm_blocks
+        self.timeout_ms = timeout_ms or int(os.environ.get("FT_COMM_TIMEOUT_MS", "30000"))
+        self.fused_update = mode == "fused"
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.stream = torch.cuda.Stream(self.device)
+        self.epoch = 0
+        self._symm: list[SymmetricBuffer] = []
+        self.late = {id(p) for p in late_params}
+        self.last_micro_batch = True
+        self.exposed_ms: list[float] = []
+
+    # the trainer allocates its arenas through this (symmetric memory in fused mode)
+    def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        if self.mode != "fused":
+            return torch.zeros(numel, device=self.device, dtype=dtype)
+        pad = 8 * self.world * 64
+        n = (numel + pad - 1) // pad * pad
+        buf = SymmetricBuffer(n, dtype, self.group, self.device)
+        self._symm.append(buf)
+        return buf.tensor[:numel]
+
+    def _symm_of(self, t: torch.Tensor) -> SymmetricBuffer:
+        for b in self._symm:
+            if b.tensor.data_ptr() == t.data_ptr():
+                return b
+        raise KeyError("tensor is not one of this DDP's symmetric buffers")
+
+    def attach(self, trainer) -> None:
+        a = trainer.arena
+        self.trainer = trainer
+        align = 8 * self.world
+        elems = max(align, int(self.bucket_mb * 1024 * 1024 / a.params.element_size()) // align * align)
+        self.buckets = compute_buckets(a.ranges, a.slots, elems, align)
+        self.n_slots = len(self.buckets)
+        assert 64 % align == 0, "fused data parallelism needs a world size of 1, 2, 4 or 8"
+        self._buckets_of: dict[int, list[int]] = {}
+        for bi, b in enumerate(self.buckets):
+            for p in b["params"]:
+                self._buckets_of.setdefault(id(p), []).append(bi)
+                p.grad_ready_hook = self._on_grad_ready
+        if self.mode == "fused":
+            lib = _native.kernels()
+            self.p_buf, self.g_buf = self._symm_of(a.params), self._symm_of(a.grads)
+            self.flags = SymmetricBuffer(int(lib.ft_comm_flag_count(self.n_slots)), torch.int32, self.group,
+                                         self.device)
+            self.counters = torch.zeros(self.n_slots, device=self.device, dtype=torch.int32)
+        dist.barrier(self.group)
+
+    # ------------------------------------------------------------------ per step
+    def begin_step(self) -> None:
+        self.epoch += 1
+        self._pending = [len([p for p in b["params"] if id(p) not in self.late]) for b in self.buckets]
+        self._launched = [False] * self.n_slots
+        self.last_micro_batch = self.trainer.micro_batches == 1
+        self._mb_seen = 0
+
+    def note_micro_batch(self, index: int, total: int) -> None:
+        self.last_micro_batch = index == total - 1
+
+    def _on_grad_ready(self, p) -> None:
+        if not self.last_micro_batch or id(p) in self.late:
+            return
+        for bi in self._buckets_of[id(p)]:
+            self._pending[bi] -= 1
+            if self._pending[bi] == 0 and not self._launched[bi]:
+                self._launch(bi)
+
+    def _launch(self, bi: int) -> None:
+        self._launched[bi] = True
+        b = self.buckets[bi]
+        tr = self.trainer
+        cur = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self.stream.wait_event(ev)
+        lo, hi = b["lo"], b["hi"]
+        n_pad = hi - lo
+        if self.mode == "nccl":
+            with torch.cuda.stream(self.stream):
+                dist.all_reduce(tr.arena.grads[lo:hi], op=dist.ReduceOp.AVG, group=self.group)
+            return
+        wd = tr.weight_decay if self._group_of(lo) == "decay" else 0.0
+        kind = {"adamw": 1, "adam": 2, "sgd": 3}[tr.kind]
+        lib = _native.kernels()
+        rc = lib.ft_ddp_reduce_update(
+            self.g_buf.ptr_array, self.p_buf.ptr_array, self.flags.ptr_array,
+            tr.master.data_ptr(), tr.exp_avg.data_ptr() if tr.exp_avg is not None else None,
+            tr.exp_avg_sq.data_ptr() if tr.exp_avg_sq is not None else None, self.counters.data_ptr(),
+            lo, n_pad, self.rank, self.world, bi, self.n_slots, self.epoch, 1.0 / self.world,
+            int(tr.arena.grads.dtype == torch.float32), kind, tr.lr, tr.betas[0], tr.betas[1], tr.eps, wd,
+            tr.step_count + 1, tr.momentum, tr.dampening, int(tr.nesterov), self.comm_blocks,
+            self.timeout_ms, self.device.index, self.stream.cuda_stream)
+        _native.check(rc, "ft_ddp_reduce_update")
+
+    def _group_of(self, offset: int) -> str:
+        for g, (s, e) in self.trainer.arena.ranges.items():
+            if s <= offset < e:
+                return g
+        return "decay"
+
+    def finish_step(self, trainer) -> None:
+        """Launch what backward did not trigger, then make the compute stream wait for the
+        whole exchange (all peers' slices written into this rank's parameter arena)."""
+        self.last_micro_batch = True
+        for bi in range(self.n_slots):
+            if not self._launched[bi]:
+                self._launch(bi)
+        if self.mode == "fused":
+            lib = _native.kernels()
+            rc = lib.ft_comm_wait(self.flags.ptrs[self.rank], 1, 0, self.n_slots, self.n_slots, self.world,
+                                  self.epoch, self.timeout_ms, self.device.index, self.stream.cuda_stream)
+            _native.check(rc, "ft_comm_wait")
+        ev = torch.cuda.Event()
+        ev.record(self.stream)
+        torch.cuda.current_stream(self.device).wait_event(ev)
+
+    def broadcast_parameters(self, trainer, root: int = 0) -> None:
+        """Make every replica start from rank ``root``'s weights and optimizer state."""
+        for t in (trainer.arena.params, trainer.master, trainer.exp_avg, trainer.exp_avg_sq):
+            if t is not None:
+                dist.broadcast(t, src=dist.get_global_rank(self.group, root), group=self.group)
+        torch.cuda.synchronize()
+
+    def check_status(self) -> None:
+        code = _native.device_status(self.device.index)
+        if code != 0:
+            raise CommTimeout("a device-side wait on a peer ran out (status %d)" % code)
+
+
+class CommTimeout(RuntimeError):
+    """A bounded device-side wait on a peer's flag ran out (mirrors the reference's
+    ``DistributedError::Timeout``, ferrotorch-distributed/src/error.rs:21-66)."""

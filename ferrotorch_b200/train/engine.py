@@ -136,6 +136,8 @@ class FlatTrainer:
         denom = targets.numel()
         for i in range(mb):
             x, y = inputs[i * per:(i + 1) * per], targets[i * per:(i + 1) * per]
+            if self.ddp is not None:
+                self.ddp.note_micro_batch(i, mb)
             if self.loss_fn is not None:
                 loss = self.loss_fn(self.model, x, y) / mb
             else:
