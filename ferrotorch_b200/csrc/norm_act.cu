@@ -447,3 +447,57 @@ FT_API int ft_embedding_bwd(const long long* ids, const void* dy, void* dw, int 
   count_launch();
   return FT_E_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate (declaration and contract: ft_noalloc.h).
+// The partial sums of dw go to this fixed array instead of caller-provided scratch.  In host
+// code the name below is only a handle for cudaGetSymbolAddress, never a device pointer.
+#include "ft_noalloc.h"
+
+static __device__ __align__(256) float g_rmsnorm_noalloc_scratch[FT_NOALLOC_RMSNORM_ROWS * FT_NOALLOC_RMSNORM_MAX_H];
+
+FT_API int ft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                  const void* dres, void* dx, void* dw, int rows, int H, int dw_flags,
+                                  int device, cudaStream_t stream) {
+  FT_REQUIRE(dy && x && w && rstd && dx, "ft_rmsnorm_bwd_noalloc: null pointer");
+  FT_REQUIRE(device >= 0 && device < 64, "ft_rmsnorm_bwd_noalloc: bad device %d", device);
+  FT_REQUIRE(H > 0 && H % 8 == 0, "ft_rmsnorm_bwd_noalloc: H=%d must be a positive multiple of 8", H);
+  if (H > FT_NOALLOC_RMSNORM_MAX_H) {
+    set_last_error("ft_rmsnorm_bwd_noalloc: H=%d exceeds the fixed scratch (max %d); use ft_rmsnorm_bwd "
+                   "with caller-provided scratch", H, FT_NOALLOC_RMSNORM_MAX_H);
+    return FT_E_TOO_LARGE;
+  }
+  if (rows <= 0) return FT_E_OK;
+  // once per device, with that device current: resolve the device address of the array
+  static float* scratch_of[64] = {nullptr};
+  if (!scratch_of[device]) {
+    int prev = -1;
+    FT_CUDA_CHECK(cudaGetDevice(&prev));
+    if (prev != device) FT_CUDA_CHECK(cudaSetDevice(device));
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_rmsnorm_noalloc_scratch);
+    if (prev != device) cudaSetDevice(prev);
+    if (e != cudaSuccess || !ptr) {
+      set_last_error("ft_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return FT_E_CUDA;
+    }
+    scratch_of[device] = ptr;
+  }
+  float* scratch = scratch_of[device];
+  const int grid = rows < FT_NOALLOC_RMSNORM_ROWS ? rows : FT_NOALLOC_RMSNORM_ROWS;
+  // every partial row [0, grid) x [0, H) is written by the first kernel before the second reads
+  // it, so the previous call's contents never leak into the result
+  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
+      static_cast<__nv_bfloat16*>(dx), dw ? scratch : nullptr, rows, H);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  if (dw) {
+    rmsnorm_dw_reduce_kernel<<<(H + 127) / 128, 128, 0, stream>>>(scratch, dw, grid, H, dw_flags & 1,
+                                                                  (dw_flags >> 1) & 1);
+    FT_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+  }
+  return FT_E_OK;
+}
