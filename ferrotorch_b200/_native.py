@@ -86,7 +86,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    tmp = KERNELS_SO.with_suffix(".so.tmp")
+    tmp = KERNELS_SO.with_suffix(".so.tmp%d" % os.getpid())
     _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
     os.replace(tmp, KERNELS_SO)
     return KERNELS_SO
@@ -104,7 +104,7 @@ def build_host(force: bool = False) -> Path:
     if cxx is None:
         raise RuntimeError("g++ not found; cannot build libft_host.so")
     OUT.mkdir(exist_ok=True)
-    tmp = HOST_SO.with_suffix(".so.tmp")
+    tmp = HOST_SO.with_suffix(".so.tmp%d" % os.getpid())
     _run([cxx, *CXX_FLAGS, "-shared", "-o", str(tmp), *map(str, srcs), "-I", str(CSRC / "host")])
     os.replace(tmp, HOST_SO)
     return HOST_SO

@@ -6,6 +6,15 @@ import pytest
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def pytest_sessionstart(session):
+    # build the native libraries once, before any test spawns worker processes
+    from ferrotorch_b200 import _native
+
+    _native.build_host()
+    if _native._nvcc() is not None:
+        _native.build_kernels()
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (run on a B200)")
     config.addinivalue_line("markers", "multigpu: test needs >= 2 CUDA devices")

@@ -1,0 +1,166 @@
+"""Host-side communication: simulated in-process ranks, loopback TCP between processes,
+timeouts / size mismatches / a rank that leaves, and the CPU plumbing config (tiny Llama,
+DDP world 2, bitwise-equal losses and reduced gradients).  No GPU involved."""
+import multiprocessing as mp
+import socket
+
+import pytest
+import torch
+
+from ferrotorch_b200.parallel import backend as B
+from ferrotorch_b200.parallel.host_ddp import DDP, compute_buckets
+
+import dist_workers as W
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _spawn(fn, world, *extra, timeout=180):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=fn, args=(r, world, port, q) + extra) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = {}
+    for _ in range(world):
+        r, v = q.get(timeout=timeout)
+        out[r] = v
+    for p in procs:
+        p.join(30)
+    for v in out.values():
+        assert not (isinstance(v, str) and v.startswith("ERR")), v
+    return out
+
+
+# ----------------------------------------------------------------------------- simulated group
+def test_simulated_collectives_four_ranks():
+    def body(g):
+        r, w = g.rank, g.world_size
+        s = g.all_reduce(torch.full((3,), float(r + 1)), "sum")
+        m = g.all_reduce(torch.full((3,), float(r + 1)), "mean")
+        b = g.broadcast(torch.full((2,), float(r)), 2)
+        ag = g.all_gather(torch.tensor([float(r)]))
+        rs = g.reduce_scatter(torch.arange(w, dtype=torch.float32))
+        a2a = g.all_to_all(torch.arange(w, dtype=torch.float32) + 10 * r)
+        un = g.all_to_all(torch.arange(sum(range(1, w + 1)), dtype=torch.float32) + 100 * r,
+                          send_counts=[p + 1 for p in range(w)], recv_counts=[r + 1] * w)
+        g.barrier()
+        return s, m, b, ag, rs, a2a, un
+
+    res = B.run_simulated(4, body)
+    for r, (s, m, b, ag, rs, a2a, un) in enumerate(res):
+        assert s.tolist() == [10.0] * 3 and m.tolist() == [2.5] * 3
+        assert b.tolist() == [2.0, 2.0]
+        assert ag.tolist() == [0.0, 1.0, 2.0, 3.0]
+        assert rs.tolist() == [4.0 * r]
+        assert a2a.tolist() == [r + 10.0 * p for p in range(4)]
+        assert un.numel() == 4 * (r + 1)
+
+
+def test_simulated_errors():
+    gs = B.SimulatedGroup.create_group(2, timeout=0.2)
+    with pytest.raises(B.SelfSend):
+        gs[0].send(torch.zeros(1), 0)
+    with pytest.raises(B.InvalidRank):
+        gs[0].send(torch.zeros(1), 5)
+    with pytest.raises(B.Timeout):
+        gs[0].recv(torch.zeros(1), 1)
+    gs[1].send(torch.zeros(8), 0)
+    with pytest.raises(B.SizeMismatch):
+        gs[0].recv(torch.zeros(4), 1)
+    with pytest.raises(B.InvalidWorldSize):
+        B.SimulatedGroup.create_group(0)
+    with pytest.raises(B.SizeMismatch):
+        B.run_simulated(2, lambda g: g.reduce_scatter(torch.zeros(3)))
+    with pytest.raises(B.BackendUnavailable):
+        B.init_group("mpi")
+
+
+def test_subgroup_maps_ranks():
+    def body(g):
+        if g.rank in (1, 3):
+            sg = B.SubGroup(g, [3, 1, 3])
+            v = sg.all_reduce(torch.tensor([float(g.rank)]), "sum")
+            return sg.rank, sg.world_size, sg.global_rank(1), v.item()
+        return None
+
+    res = B.run_simulated(4, body)
+    assert res[1] == (0, 2, 3, 4.0) and res[3] == (1, 2, 3, 4.0)
+    gs = B.SimulatedGroup.create_group(2)
+    with pytest.raises(B.InvalidRank):
+        B.SubGroup(gs[0], [1])
+
+
+def test_ddp_buckets_and_sync_simulated():
+    p = [torch.nn.Parameter(torch.zeros(n)) for n in (10, 20, 30, 40)]
+    assert compute_buckets(p, 50 * 4) == [[3], [2, 1], [0]]  # reverse order, <= 200 bytes each
+
+    def body(g):
+        torch.manual_seed(g.rank)
+        m = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.ReLU(), torch.nn.Linear(8, 2))
+        d = DDP(m, g, bucket_size_bytes=64)
+        d.broadcast_parameters(0)
+        x = torch.full((3, 4), float(g.rank + 1))
+        d(x).sum().backward()
+        local = [q.grad.clone() for q in m.parameters()]
+        d.sync_gradients()
+        return [q.detach().clone() for q in m.parameters()], local, [q.grad.clone() for q in m.parameters()]
+
+    res = B.run_simulated(3, body)
+    for k in range(4):
+        want = (res[0][1][k] + res[1][1][k] + res[2][1][k]) / 3
+        for r in range(3):
+            assert torch.equal(res[r][0][k], res[0][0][k])          # broadcast parameters
+            assert torch.equal(res[r][2][k], res[0][2][k])          # bitwise-equal reduced grads
+            assert torch.allclose(res[r][2][k], want, atol=1e-6)
+
+
+# ----------------------------------------------------------------------------- loopback TCP
+@pytest.mark.parametrize("world", [2, 3])
+def test_tcp_collectives(world):
+    out = _spawn(W.collectives, world)
+    tot = float(sum(range(1, world + 1)))
+    for r in range(world):
+        o = out[r]
+        assert o["sum"] == [tot] * 5
+        assert o["mean"] == [i * tot / world for i in range(4)]
+        assert o["bcast"] == [1.0] * 3
+        assert o["gather"] == [[float(k), 1.0] for k in range(world)]
+        assert o["rs"] == [world * (2.0 * r), world * (2.0 * r + 1)]
+        assert o["a2a"] == [r + 10.0 * p for p in range(world)]
+        assert o["ring"] == [tot, 999 * tot]
+        assert o["f64"] == [0.5 * tot] * 3
+    assert out[world - 1]["p2p"] == 42.0
+
+
+def test_tcp_recv_timeout_is_an_error_not_a_hang():
+    out = _spawn(W.timeout_case, 2)
+    assert out[0].startswith("timeout") and float(out[0].split()[1]) < 2.0
+
+
+def test_tcp_size_mismatch():
+    out = _spawn(W.size_mismatch_case, 2)
+    assert out[0] == "size mismatch"
+
+
+def test_tcp_rank_that_leaves_is_detected():
+    out = _spawn(W.dead_peer_case, 2)
+    assert out[1] == "left" and out[0].startswith("error")
+
+
+# ----------------------------------------------------------------------------- config 0
+@pytest.mark.parametrize("backend", ["tcp", "gloo"])
+def test_config0_tiny_llama_ddp_bitwise(backend):
+    steps = 20 if backend == "tcp" else 4
+    out = _spawn(W.config0, 2, steps, backend, timeout=600)
+    a, b = out[0], out[1]
+    assert a["losses"] == b["losses"], "rank losses differ bitwise"
+    assert a["grads"] == b["grads"], "post-all-reduce gradients differ bitwise"
+    assert a["last"] < a["first"]
