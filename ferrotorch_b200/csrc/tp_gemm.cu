@@ -1,0 +1,542 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a).
+//
+// The reference has no tensor / sequence parallelism (design only,
+// .design/phase-7-distributed.md:269-307); a Megatron-style block needs two fused ops:
+//
+//   ft_tp_ag_gemm   Y[M, N_loc] = allgather_rows(X)[M, K] * W_loc[N_loc, K]^T
+//       (column-parallel: QKV, gate/up).  Activations are sequence-sharded: rank s owns rows
+//       [s*Ms, (s+1)*Ms) of a symmetric buffer Xg[M, K] and has written them before the call.
+//       Inside ONE kernel, a few "copy" CTAs pull the other ranks' rows from peer memory into
+//       the local Xg (each remote row crosses NVLink exactly once) and publish per-128-row
+//       block counters; the persistent tcgen05 GEMM CTAs start with the rows this rank already
+//       owns and their TMA producers wait (bounded) on the block counter of each later tile,
+//       so the transfer overlaps the math tile by tile.
+//   ft_tp_gemm_rs   Out[Ms, N] (+ residual) = reduce_scatter_rows(X_loc[M, K_loc] * W_loc[N, K_loc]^T)
+//       (row-parallel: o_proj, down_proj).  The epilogue stores each row of the partial product
+//       straight into the staging buffer of the rank that owns the row (peer stores), tiles for
+//       other ranks first; per-owner counters raise a system-scope flag on the owner when a
+//       source has delivered everything; the same kernel then sums the W staged partials in
+//       rank order in fp32, adds the residual and writes the owner's rows.
+//
+// Loads from peer memory are plain ld.global / non-multicast; TMA only ever reads this GPU's
+// own memory here.  Every wait (mbarrier, block counter, peer flag) is bounded and reports
+// through the device status word.
+#include "ft_host.h"
+#include "ft_ptx.cuh"
+
+namespace ft {
+
+constexpr int TP_BM = 128;
+constexpr int TP_BK = 64;
+constexpr int TP_THREADS = 256;
+constexpr int TP_MAX_RANKS = 8;
+
+struct TpPeers {
+  void* ptr[TP_MAX_RANKS];
+};
+
+template <int BN>
+struct TpCfg {
+  static constexpr int A_BYTES = TP_BM * TP_BK * 2;
+  static constexpr int B_BYTES = BN * TP_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+struct TpParams {
+  int mode;  // 0 = all-gather -> GEMM, 1 = GEMM -> reduce-scatter
+  int M, N, K;
+  int rank, world, rows_per_rank;
+  // mode 0
+  __nv_bfloat16* C; long long ldc;       // local output [M, N]
+  const void* bias;                      // optional bf16 [N]
+  TpPeers xg; long long ldx;             // symmetric gathered-activation buffers [M, K]
+  uint32_t* blk_ready;                   // local counters, one per 128-row block, zero at entry
+  int n_copy;                            // copy CTAs
+  // mode 1
+  TpPeers stage;                         // symmetric staging [world, rows_per_rank, N] bf16
+  __nv_bfloat16* out; long long ldo;     // local output rows [rows_per_rank, N]
+  const __nv_bfloat16* residual; long long ldr;
+  unsigned int* owner_counter;           // local [world], zero at entry
+  // both
+  unsigned int* done_counter;            // local, zero at entry
+  TpPeers flags; int slot, n_slots; uint32_t epoch;
+  unsigned long long limit_ns;
+  int* status;
+};
+
+__device__ __forceinline__ void tp_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t tp_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t tp_ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tp_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ size_t tp_flag_index(int kind, int slot, int src, int n_slots) {
+  return (static_cast<size_t>(kind) * n_slots + slot) * TP_MAX_RANKS + src;
+}
+// Bounded spin of ONE thread until *p >= want (acquire at the given scope).
+template <bool SYS>
+__device__ __forceinline__ bool tp_spin_ge(const uint32_t* p, uint32_t want, unsigned long long limit_ns,
+                                           volatile int* abort_word) {
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t backoff = 32;
+  while (static_cast<int32_t>((SYS ? tp_ld_acquire_sys(p) : tp_ld_acquire_gpu(p)) - want) < 0) {
+    if (*abort_word) return false;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      *abort_word = FT_ERR_TIMEOUT_PEER;
+      return false;
+    }
+    __nanosleep(backoff);
+    if (backoff < 512) backoff <<= 1;
+  }
+  return true;
+}
+
+// number of remote ranks whose row shard overlaps 128-row block mb
+__device__ __forceinline__ int remote_pieces(int mb, int rows_per_rank, int M, int rank) {
+  const int lo = mb * TP_BM, hi = min(M, lo + TP_BM) - 1;
+  const int s0 = lo / rows_per_rank, s1 = hi / rows_per_rank;
+  int n = s1 - s0 + 1;
+  if (rank >= s0 && rank <= s1) --n;
+  return n;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TP_THREADS, 1)
+tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const TpParams p) {
+  using Cfg = TpCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  const int m_blocks = (p.M + TP_BM - 1) / TP_BM;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (p.K + TP_BK - 1) / TP_BK;
+  const int n_copy = p.mode == 0 ? p.n_copy : 0;
+  const bool is_copy_cta = static_cast<int>(blockIdx.x) < n_copy;
+  const int n_gemm = static_cast<int>(gridDim.x) - n_copy;
+  const int cta = static_cast<int>(blockIdx.x) - n_copy;
+  uint32_t* my_flags = static_cast<uint32_t*>(p.flags.ptr[p.rank]);
+  // rotation so that the rows this rank already holds (mode 0) come first and the rows this rank
+  // owns (mode 1) come last
+  const int own_block = (p.rank * p.rows_per_rank) / TP_BM;
+  const int own_end_block = min(m_blocks, ((p.rank + 1) * p.rows_per_rank + TP_BM - 1) / TP_BM);
+  const int first_block = p.mode == 0 ? own_block : (own_end_block % m_blocks);
+  auto tile_coords = [&](int tile, int& mb, int& nb) {
+    mb = (first_block + tile / n_blocks) % m_blocks;
+    nb = tile % n_blocks;
+  };
+
+  if (threadIdx.x == 0) *abort_word = 0;
+  if (!is_copy_cta) {
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(full_bar(s), 1);
+        mbar_init(empty_bar(s), 1);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(tfull_bar(a), 1);
+        mbar_init(tempty_bar(a), 4);
+      }
+      fence_mbar_init();
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+    }
+    if (warp == 2) {
+      tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (is_copy_cta) {
+    // ------------------------------------------------------------ all-gather by pull
+    __shared__ int s_ok;
+    __nv_bfloat16* dst_base = static_cast<__nv_bfloat16*>(p.xg.ptr[p.rank]);
+    int piece = 0;
+    for (int i = 1; i < p.world; ++i) {
+      const int s = (p.rank + i) % p.world;
+      if (threadIdx.x == 0)
+        s_ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, s, p.n_slots), p.epoch, p.limit_ns, abort_word) ? 1 : 0;
+      __syncthreads();
+      if (!s_ok) break;
+      const __nv_bfloat16* src_base = static_cast<const __nv_bfloat16*>(p.xg.ptr[s]);
+      const int row_lo = s * p.rows_per_rank, row_hi = min(p.M, row_lo + p.rows_per_rank);
+      for (int mb = row_lo / TP_BM; mb * TP_BM < row_hi; ++mb, ++piece) {
+        if (piece % n_copy != static_cast<int>(blockIdx.x)) continue;
+        const int r0 = max(row_lo, mb * TP_BM), r1 = min(row_hi, (mb + 1) * TP_BM);
+        const int vec_per_row = p.K >> 3;
+        const long long total = static_cast<long long>(r1 - r0) * vec_per_row;
+        for (long long v = threadIdx.x; v < total; v += blockDim.x) {
+          const int r = r0 + static_cast<int>(v / vec_per_row), c = static_cast<int>(v % vec_per_row) << 3;
+          uint4 val;
+          asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                       : "l"(src_base + static_cast<long long>(r) * p.ldx + c) : "memory");
+          *reinterpret_cast<uint4*>(dst_base + static_cast<long long>(r) * p.ldx + c) = val;
+        }
+        __threadfence();
+        tp_fence_proxy_async();  // the consumers read these rows through TMA (async proxy)
+        __syncthreads();
+        if (threadIdx.x == 0) atomicAdd(p.blk_ready + mb, 1u);
+      }
+    }
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += n_gemm) {
+        int mb, nb;
+        tile_coords(tile, mb, nb);
+        if (p.mode == 0) {
+          const int need = remote_pieces(mb, p.rows_per_rank, p.M, p.rank);
+          if (need > 0) {
+            if (!tp_spin_ge<false>(p.blk_ready + mb, static_cast<uint32_t>(need), p.limit_ns, abort_word)) break;
+            tp_fence_proxy_async();
+          }
+        }
+        const int m0 = mb * TP_BM, n0 = nb * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
+          mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+          tma_load_2d(sA, &tmA, full_bar(stage), kb * TP_BK, m0);
+          tma_load_2d(sB, &tmB, full_bar(stage), kb * TP_BK, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (*abort_word) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t tmem_base = *tmem_slot;
+      constexpr uint32_t idesc = make_idesc_f16(TP_BM, BN, 1, 0, 0);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += n_gemm) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_word, FT_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TP_BK / 16; ++k)
+            umma_f16_ss(d_tmem, make_smem_desc_sw128(sA + k * 32, 16, 1024),
+                        make_smem_desc_sw128(sB + k * 32, 16, 1024), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const uint32_t tmem_base = *tmem_slot;
+    const int ew = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    if (p.mode == 1 && p.epoch > 1) {
+      // the owners must have finished reducing the previous use of their staging buffers
+      if (lane < p.world)
+        ok = tp_spin_ge<true>(my_flags + tp_flag_index(1, p.slot, lane, p.n_slots), p.epoch - 1, p.limit_ns, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    for (int tile = cta; tile < num_tiles && ok; tile += n_gemm) {
+      int mb, nb;
+      tile_coords(tile, mb, nb);
+      const int m0 = mb * TP_BM, n0 = nb * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + ew * 32 + lane;
+      const bool row_ok = row < p.M;
+      __nv_bfloat16* drow = nullptr;
+      if (row_ok) {
+        if (p.mode == 0) {
+          drow = p.C + static_cast<long long>(row) * p.ldc;
+        } else {
+          const int owner = row / p.rows_per_rank, rl = row - owner * p.rows_per_rank;
+          drow = static_cast<__nv_bfloat16*>(p.stage.ptr[owner]) +
+                 (static_cast<long long>(p.rank) * p.rows_per_rank + rl) * p.N;
+        }
+      }
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 + 8 <= p.N) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+            if (p.mode == 0 && p.bias) {
+              const uint4 bb = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.bias) + col0 + g * 8);
+              const float2 b0 = unpack_bf16x2(bb.x), b1 = unpack_bf16x2(bb.y), b2 = unpack_bf16x2(bb.z), b3 = unpack_bf16x2(bb.w);
+              v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y; v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(drow + col0 + g * 8) = o;
+          }
+        }
+      }
+      tc_fence_before();
+      if (p.mode == 1) {
+        // account this warp's share of the tile towards every owner the tile overlaps; the last
+        // contribution for an owner raises this source's flag on that owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int o0 = m0 / p.rows_per_rank, o1 = (min(p.M, m0 + TP_BM) - 1) / p.rows_per_rank;
+          for (int o = o0; o <= o1; ++o) {
+            const int blk0 = (o * p.rows_per_rank) / TP_BM;
+            const int blk1 = (min(p.M, (o + 1) * p.rows_per_rank) - 1) / TP_BM;
+            const unsigned int expected = static_cast<unsigned int>((blk1 - blk0 + 1) * n_blocks * 4);
+            const unsigned int v = atomicAdd(p.owner_counter + o, 1u);
+            if (v + 1 == expected) {
+              p.owner_counter[o] = 0u;
+              __threadfence_system();
+              tp_st_release_sys(static_cast<uint32_t*>(p.flags.ptr[o]) + tp_flag_index(0, p.slot, p.rank, p.n_slots), p.epoch);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (p.mode == 1 && ok) {
+      // ---------------------------------------------------------- reduce the staged partials
+      if (lane < p.world)
+        ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, lane, p.n_slots), p.epoch, p.limit_ns, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        const __nv_bfloat16* st = static_cast<const __nv_bfloat16*>(p.stage.ptr[p.rank]);
+        const int rows = min(p.rows_per_rank, p.M - p.rank * p.rows_per_rank);
+        const int vec_per_row = p.N >> 3;
+        const long long total = static_cast<long long>(rows > 0 ? rows : 0) * vec_per_row;
+        const long long slot_stride = static_cast<long long>(p.rows_per_rank) * p.N;
+        const long long tid = static_cast<long long>(cta) * 128 + (warp - 4) * 32 + lane;
+        for (long long v = tid; v < total; v += static_cast<long long>(n_gemm) * 128) {
+          const int r = static_cast<int>(v / vec_per_row), c = static_cast<int>(v % vec_per_row) << 3;
+          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < p.world; ++s) {
+            uint4 x;
+            asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w)
+                         : "l"(st + s * slot_stride + static_cast<long long>(r) * p.N + c) : "memory");
+            const float2 f0 = unpack_bf16x2(x.x), f1 = unpack_bf16x2(x.y), f2 = unpack_bf16x2(x.z), f3 = unpack_bf16x2(x.w);
+            acc8[0] += f0.x; acc8[1] += f0.y; acc8[2] += f1.x; acc8[3] += f1.y;
+            acc8[4] += f2.x; acc8[5] += f2.y; acc8[6] += f3.x; acc8[7] += f3.y;
+          }
+          if (p.residual) {
+            const uint4 x = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(r) * p.ldr + c);
+            const float2 f0 = unpack_bf16x2(x.x), f1 = unpack_bf16x2(x.y), f2 = unpack_bf16x2(x.z), f3 = unpack_bf16x2(x.w);
+            acc8[0] += f0.x; acc8[1] += f0.y; acc8[2] += f1.x; acc8[3] += f1.y;
+            acc8[4] += f2.x; acc8[5] += f2.y; acc8[6] += f3.x; acc8[7] += f3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc8[0], acc8[1]); o.y = pack_bf16x2(acc8[2], acc8[3]);
+          o.z = pack_bf16x2(acc8[4], acc8[5]); o.w = pack_bf16x2(acc8[6], acc8[7]);
+          *reinterpret_cast<uint4*>(p.out + static_cast<long long>(r) * p.ldo + c) = o;
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (!is_copy_cta && warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(*tmem_slot, Cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0) {
+    if (*abort_word != 0 && p.status) atomicCAS(p.status, 0, *abort_word);
+    __threadfence();
+    const unsigned int done = atomicAdd(p.done_counter, 1u);
+    if (done == gridDim.x - 1) {
+      // last CTA: reset the local counters for the next launch and tell every peer that this
+      // rank no longer reads their buffers (mode 0) / has consumed its staging buffer (mode 1)
+      *p.done_counter = 0u;
+      if (p.mode == 0)
+        for (int mb = 0; mb < m_blocks; ++mb) p.blk_ready[mb] = 0u;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        tp_st_release_sys(static_cast<uint32_t*>(p.flags.ptr[r]) + tp_flag_index(1, p.slot, p.rank, p.n_slots), p.epoch);
+    }
+  }
+}
+
+template <int BN>
+static int launch_tp(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p, int device, int ctas,
+                     cudaStream_t stream) {
+  using Cfg = TpCfg<BN>;
+  auto kern = tp_gemm_kernel<BN>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[device]) {
+    FT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    attr_set[device] = true;
+  }
+  kern<<<ctas, TP_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+static int pick_bn(int M, int N, int sms) {
+  const long long mb = (M + TP_BM - 1) / TP_BM;
+  int bn = 256;
+  while (bn > 64 && mb * ((N + bn - 1) / bn) < sms) bn >>= 1;
+  return bn;
+}
+
+static int fill_peers(TpPeers& t, void* const* ptrs, int world) {
+  for (int i = 0; i < TP_MAX_RANKS; ++i) t.ptr[i] = (ptrs && i < world) ? ptrs[i] : nullptr;
+  if (!ptrs) return FT_E_BAD_ARG;
+  for (int i = 0; i < world; ++i)
+    if (!ptrs[i] || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15)) return FT_E_BAD_ARG;
+  return FT_E_OK;
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+// Scratch words (uint32) the TP kernels need locally: counters[0] = done counter,
+// counters[1 .. 1+8) = owner counters, counters[16 ...) = per-128-row-block counters.
+FT_API long long ft_tp_counter_words(int M) { return 16 + (M + TP_BM - 1) / TP_BM; }
+
+// Y[M, N] = allgather_rows(Xg)[M, K] * W[N, K]^T (+ bias).  xg_ptrs: every rank's symmetric
+// [M, K] buffer (row stride ldx); this rank's rows [rank*rows_per_rank, ...) must already be in
+// its own buffer and every rank must have raised flag (kind 0, slot) to `epoch` after writing
+// them (ft_comm_signal).  counters: ft_tp_counter_words(M) zeroed uint32 words, reused across
+// calls.  The kernel raises flag (kind 1, slot) = epoch on every peer when it no longer reads
+// their buffers.
+FT_API int ft_tp_ag_gemm(void* const* xg_ptrs, const void* w, void* y, const void* bias, int M, int N, int K,
+                         long long ldx, long long ldw, long long ldy, int rank, int world, int rows_per_rank,
+                         unsigned int* counters, void* const* flag_ptrs, int slot, int n_slots,
+                         unsigned int epoch, int n_copy, long long timeout_ms, int device,
+                         cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  FT_REQUIRE(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world, "ft_tp_ag_gemm: bad rank/world");
+  FT_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0,
+             "ft_tp_ag_gemm: N, K and strides must be multiples of 8");
+  FT_REQUIRE(rows_per_rank > 0 && rows_per_rank * world >= M, "ft_tp_ag_gemm: rows_per_rank * world < M");
+  FT_REQUIRE(counters && w && y, "ft_tp_ag_gemm: null pointer");
+  TpParams p{};
+  FT_REQUIRE(fill_peers(p.xg, xg_ptrs, world) == 0 && fill_peers(p.flags, flag_ptrs, world) == 0,
+             "ft_tp_ag_gemm: bad peer pointers");
+  for (int i = 0; i < TP_MAX_RANKS; ++i) p.stage.ptr[i] = nullptr;
+  const int sms = sm_count(device);
+  if (world == 1) n_copy = 0;
+  else if (n_copy <= 0) n_copy = 16;
+  if (n_copy > sms / 2) n_copy = sms / 2;
+  p.mode = 0; p.M = M; p.N = N; p.K = K; p.rank = rank; p.world = world; p.rows_per_rank = rows_per_rank;
+  p.C = static_cast<__nv_bfloat16*>(y); p.ldc = ldy; p.bias = bias; p.ldx = ldx;
+  p.blk_ready = counters + 16; p.n_copy = n_copy; p.done_counter = counters; p.owner_counter = counters + 1;
+  p.slot = slot; p.n_slots = n_slots; p.epoch = epoch;
+  p.limit_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
+  p.status = device_status_word(device);
+  const int bn = pick_bn(M, N, sms - n_copy);
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, xg_ptrs[rank], 2, K, M, ldx * 2, TP_BK, TP_BM, 3);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, w, 2, K, N, ldw * 2, TP_BK, bn, 3);
+  if (rc) return rc;
+  const int tiles = ((M + TP_BM - 1) / TP_BM) * ((N + bn - 1) / bn);
+  int gemm_ctas = tiles < sms - n_copy ? tiles : sms - n_copy;
+  const int ctas = n_copy + gemm_ctas;
+  switch (bn) {
+    case 256: return launch_tp<256>(tmA, tmB, p, device, ctas, stream);
+    case 128: return launch_tp<128>(tmA, tmB, p, device, ctas, stream);
+    default: return launch_tp<64>(tmA, tmB, p, device, ctas, stream);
+  }
+}
+
+// Out[rows_per_rank, N] (+ residual) = reduce_scatter_rows(X[M, K] * W[N, K]^T) over ranks.
+// stage_ptrs: every rank's symmetric staging buffer of world * rows_per_rank * N bf16.
+// out / residual are local [rows_per_rank, N] (row strides ldo / ldr).
+FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, void* out, const void* residual,
+                         int M, int N, int K, long long ldx, long long ldw, long long ldo, long long ldr,
+                         int rank, int world, int rows_per_rank, unsigned int* counters,
+                         void* const* flag_ptrs, int slot, int n_slots, unsigned int epoch,
+                         long long timeout_ms, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  FT_REQUIRE(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world, "ft_tp_gemm_rs: bad rank/world");
+  FT_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldo % 8 == 0 &&
+                 ldr % 8 == 0,
+             "ft_tp_gemm_rs: N, K and strides must be multiples of 8");
+  FT_REQUIRE(rows_per_rank > 0 && rows_per_rank * world >= M, "ft_tp_gemm_rs: rows_per_rank * world < M");
+  FT_REQUIRE(counters && x && w && out, "ft_tp_gemm_rs: null pointer");
+  TpParams p{};
+  FT_REQUIRE(fill_peers(p.stage, stage_ptrs, world) == 0 && fill_peers(p.flags, flag_ptrs, world) == 0,
+             "ft_tp_gemm_rs: bad peer pointers");
+  for (int i = 0; i < TP_MAX_RANKS; ++i) p.xg.ptr[i] = nullptr;
+  const int sms = sm_count(device);
+  p.mode = 1; p.M = M; p.N = N; p.K = K; p.rank = rank; p.world = world; p.rows_per_rank = rows_per_rank;
+  p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.done_counter = counters; p.owner_counter = counters + 1; p.blk_ready = counters + 16; p.n_copy = 0;
+  p.slot = slot; p.n_slots = n_slots; p.epoch = epoch;
+  p.limit_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
+  p.status = device_status_word(device);
+  const int bn = pick_bn(M, N, sms);
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, x, 2, K, M, ldx * 2, TP_BK, TP_BM, 3);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, w, 2, K, N, ldw * 2, TP_BK, bn, 3);
+  if (rc) return rc;
+  const int tiles = ((M + TP_BM - 1) / TP_BM) * ((N + bn - 1) / bn);
+  const int ctas = tiles < sms ? tiles : sms;
+  switch (bn) {
+    case 256: return launch_tp<256>(tmA, tmB, p, device, ctas, stream);
+    case 128: return launch_tp<128>(tmA, tmB, p, device, ctas, stream);
+    default: return launch_tp<64>(tmA, tmB, p, device, ctas, stream);
+  }
+}
