@@ -1,0 +1,243 @@
+"""Batched Llama inference engine: prefill + paged-KV greedy decode, single GPU or tensor parallel.
+
+The reference's GPU inferencer is batch-1 and cache-less -- every new token re-runs the whole
+prefix through 9 GEMMs + 16 elementwise launches per layer
+(ferrotorch-llama/src/gpu.rs:300-334, 549-788) -- and ``GraphedDecoder`` captures that seq=1
+forward in a CUDA graph (gpu.rs:896-994).  This engine keeps a paged KV cache on the device
+(block 16), prefills with flash attention, decodes one token per sequence per step with the
+paged decode kernel, and shards the model Megatron-style across a tensor-parallel group:
+
+    residual stream rows sharded by rank (sequence parallel)
+    RMSNorm(own rows) -> gather buffer -> [all-gather -> QKV GEMM] -> RoPE -> KV append
+      -> attention (local heads) -> [o_proj GEMM -> reduce-scatter + residual]
+      -> RMSNorm -> [all-gather -> gate/up GEMM] -> SwiGLU -> [down GEMM -> reduce-scatter + residual]
+
+Bracketed steps are single fused kernels (``csrc/tp_gemm.cu``).  With one rank the same kernels
+run with an empty collective part.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..nn.paged import PagedAttentionManager, PagedKVCache
+from ..ops import functional as F
+from ..ops import reference as ref
+from ..parallel.tensor_parallel import TPContext
+from .llama import LlamaConfig
+
+
+def _shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[0] // world
+    return w[rank * n:(rank + 1) * n]
+
+
+class LlamaEngine:
+    def __init__(self, cfg: LlamaConfig, tp: TPContext | None = None, *, max_batch: int = 64,
+                 max_seq_len: int = 4096, block_size: int = 16, weights: dict | None = None, seed: int = 0,
+                 device=None, prefill_chunk_tokens: int = 16384):
+        self.cfg = cfg
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.tp = tp if tp is not None else TPContext(None, self.device)
+        W, r = self.tp.world, self.tp.rank
+        self.W, self.r = W, r
+        assert cfg.num_attention_heads % W == 0 and cfg.num_key_value_heads % W == 0 and cfg.intermediate_size % W == 0
+        self.Hq, self.Hkv, self.D = cfg.num_attention_heads // W, cfg.num_key_value_heads // W, cfg.head_dim
+        self.F = cfg.intermediate_size // W
+        self.H = cfg.hidden_size
+        self.Vloc = (cfg.vocab_size + W - 1) // W
+        self.prefill_chunk_tokens = prefill_chunk_tokens
+        self.max_batch = max_batch
+        self.cos, self.sin = ref.rope_tables(cfg.head_dim, max(max_seq_len, 16), cfg.rope_theta, cfg.rope_scaling,
+                                             device=self.device)
+        n_blocks = max_batch * ((max_seq_len + block_size - 1) // block_size)
+        self.cache = PagedKVCache(cfg.num_hidden_layers, self.Hkv, self.D, n_blocks, max_batch, max_seq_len,
+                                  block_size, self.device)
+        self.manager = PagedAttentionManager(self.cache)
+        self._load(weights, seed)
+
+    # ------------------------------------------------------------------ weights
+    def _load(self, sd: dict | None, seed: int) -> None:
+        cfg, dev, W, r = self.cfg, self.device, self.W, self.r
+        std = cfg.initializer_range
+        g = torch.Generator(device=dev)
+
+        def rnd(shape, tag):
+            g.manual_seed(hash((seed, tag)) % (2 ** 31))
+            return (torch.randn(shape, device=dev, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
+
+        def get(name, shape, tag, shard=None):
+            if sd is None:
+                return rnd(shape, tag)
+            w = sd[name].to(dev, torch.bfloat16)
+            return shard(w).contiguous() if shard is not None else w.contiguous()
+
+        D, nq, nkv = self.D, cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+        self.embed = get("model.embed_tokens.weight", (cfg.vocab_size, self.H), ("embed",))
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            pre = "model.layers.%d." % i
+            if sd is None:
+                qkv = rnd(((self.Hq + 2 * self.Hkv) * D, self.H), (i, "qkv", r))
+                gu = rnd((2 * self.F, self.H), (i, "gu", r))
+                o = rnd((self.H, self.Hq * D), (i, "o", r))
+                dn = rnd((self.H, self.F), (i, "down", r))
+                n1 = torch.ones(self.H, device=dev, dtype=torch.bfloat16)
+                n2 = torch.ones(self.H, device=dev, dtype=torch.bfloat16)
+            else:
+                q = _shard_rows(sd[pre + "self_attn.q_proj.weight"], r, W)
+                k = _shard_rows(sd[pre + "self_attn.k_proj.weight"], r, W)
+                v = _shard_rows(sd[pre + "self_attn.v_proj.weight"], r, W)
+                qkv = torch.cat([q, k, v], 0).to(dev, torch.bfloat16).contiguous()
+                gu = torch.cat([_shard_rows(sd[pre + "mlp.gate_proj.weight"], r, W),
+                                _shard_rows(sd[pre + "mlp.up_proj.weight"], r, W)], 0).to(dev, torch.bfloat16).contiguous()
+                ow = sd[pre + "self_attn.o_proj.weight"]
+                o = ow[:, r * self.Hq * D:(r + 1) * self.Hq * D].to(dev, torch.bfloat16).contiguous()
+                dw = sd[pre + "mlp.down_proj.weight"]
+                dn = dw[:, r * self.F:(r + 1) * self.F].to(dev, torch.bfloat16).contiguous()
+                n1 = sd[pre + "input_layernorm.weight"].to(dev, torch.bfloat16)
+                n2 = sd[pre + "post_attention_layernorm.weight"].to(dev, torch.bfloat16)
+            self.layers.append(dict(qkv=qkv, gu=gu, o=o, down=dn, n1=n1, n2=n2))
+        self.norm = (torch.ones(self.H, device=dev, dtype=torch.bfloat16) if sd is None
+                     else sd["model.norm.weight"].to(dev, torch.bfloat16))
+        if sd is None:
+            self.lm_head = rnd((self.Vloc, self.H), ("lm_head", r))
+        else:
+            full = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
+            lo = r * self.Vloc
+            shard = full[lo:lo + self.Vloc].to(dev, torch.bfloat16)
+            if shard.shape[0] < self.Vloc:  # pad the last shard; padded rows can never win the argmax
+                shard = torch.cat([shard, torch.zeros(self.Vloc - shard.shape[0], self.H, device=dev, dtype=torch.bfloat16)])
+            self.lm_head = shard.contiguous()
+
+    # ------------------------------------------------------------------ one transformer pass
+    def _rows(self, M: int):
+        ms = self.tp.rows_per_rank(M)
+        lo = min(M, self.r * ms)
+        return lo, min(M, lo + ms)
+
+    def _norm_into(self, slot: int, x_rows: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, M: int):
+        """RMSNorm of this rank's rows (optionally fused with a residual add) written straight into
+        the gather buffer of ``slot``; returns the updated residual rows."""
+        dst = self.tp.my_rows(slot, M, self.H)
+        self.tp.wait_gather_buffer_free(slot)
+        rows = x_rows.shape[0]
+        if rows == 0:
+            return x_rows
+        lib = _native.kernels()
+        if delta is None:
+            rc = lib.ft_rmsnorm_fwd(x_rows.data_ptr(), None, w.data_ptr(), dst.data_ptr(), None, None, rows, self.H,
+                                    self.cfg.rms_norm_eps, self.device.index, F._stream())
+            out = x_rows
+        else:
+            out = torch.empty_like(x_rows)
+            rc = lib.ft_rmsnorm_fwd(x_rows.data_ptr(), delta.data_ptr(), w.data_ptr(), dst.data_ptr(), out.data_ptr(),
+                                    None, rows, self.H, self.cfg.rms_norm_eps, self.device.index, F._stream())
+        _native.check(rc, "ft_rmsnorm_fwd")
+        return out
+
+    def _forward(self, tokens: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor | None,
+                 B: int, S: int, decode: bool, ctx_len: torch.Tensor | None) -> torch.Tensor:
+        """tokens: flat [M] ids.  Returns this rank's rows of the final hidden state [rows, H]
+        (before the final norm) and leaves nothing else behind."""
+        M = tokens.numel()
+        lo, hi = self._rows(M)
+        x = F.embedding(tokens[lo:hi], self.embed) if hi > lo else torch.empty((0, self.H), device=self.device, dtype=torch.bfloat16)
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        nh = Hq + 2 * Hkv
+        for li, L in enumerate(self.layers):
+            self._norm_into(0, x, None, L["n1"], M)
+            qkv = self.tp.ag_gemm(0, M, L["qkv"]).view(M, nh, D)
+            F._rope_launch(qkv, self.cos, self.sin, positions, Hq + Hkv, S, 0, False, False)
+            k, v = qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
+            self.cache.append(li, k, v, positions, seq_ids, tokens_per_seq=S)
+            if decode:
+                attn = self.cache.decode(li, qkv[:, :Hq], ctx_len)
+            else:
+                q4 = qkv.view(B, S, nh, D)
+                attn, _ = F.flash_attn_fwd(q4[:, :, :Hq], q4[:, :, Hq:Hq + Hkv], q4[:, :, Hq + Hkv:], True,
+                                           return_lse=False)
+            # o_proj + reduce-scatter + residual add  -> new residual rows
+            x = self.tp.gemm_rs(1, attn.reshape(M, Hq * D), L["o"], residual=x)
+            self._norm_into(2, x, None, L["n2"], M)
+            gu = self.tp.ag_gemm(2, M, L["gu"])
+            act = torch.empty((M, self.F), device=self.device, dtype=torch.bfloat16)
+            rc = _native.kernels().ft_swiglu_fwd(gu.data_ptr(), act.data_ptr(), M, self.F, gu.stride(0), 0,
+                                                 self.device.index, F._stream())
+            _native.check(rc, "ft_swiglu_fwd")
+            x = self.tp.gemm_rs(3, act, L["down"], residual=x)
+        return x
+
+    def _next_tokens(self, h_rows: torch.Tensor, M: int) -> torch.Tensor:
+        """Final norm + vocab-parallel lm_head + greedy argmax over all shards -> [M] token ids."""
+        self._norm_into(4, h_rows, None, self.norm, M)
+        logits = self.tp.ag_gemm(4, M, self.lm_head).float()
+        if self.cfg.vocab_size % self.W and self.r == self.W - 1:
+            logits[:, self.cfg.vocab_size - self.r * self.Vloc:] = -float("inf")
+        val, idx = logits.max(dim=-1)
+        idx = idx + self.r * self.Vloc
+        if self.W == 1:
+            return idx
+        pair = torch.stack([val, idx.float()], dim=-1).contiguous()
+        allp = torch.empty((self.W,) + tuple(pair.shape), device=self.device, dtype=pair.dtype)
+        dist.all_gather_into_tensor(allp, pair, group=self.tp.group)
+        best = allp[..., 0].argmax(dim=0)
+        return allp[..., 1].gather(0, best[None]).squeeze(0).long()
+
+    # ------------------------------------------------------------------ public API
+    @torch.no_grad()
+    def prefill(self, prompts: torch.Tensor) -> torch.Tensor:
+        """``prompts [B, S]`` token ids (all sequences the same length).  Fills the KV cache and
+        returns the first generated token of every sequence ``[B]``."""
+        B, S = prompts.shape
+        for b in list(self.manager.active):
+            self.manager.remove_sequence(b)
+        self.seqs = [self.manager.add_sequence(S) for _ in range(B)]
+        assert self.seqs == list(range(B)), "sequence slots must be 0..B-1 after a reset"
+        self.lengths = torch.full((B,), S, device=self.device, dtype=torch.int32)
+        per = max(1, self.prefill_chunk_tokens // S)
+        firsts = []
+        for b0 in range(0, B, per):
+            b1 = min(B, b0 + per)
+            nb = b1 - b0
+            toks = prompts[b0:b1].reshape(-1).to(self.device)
+            pos = torch.arange(S, device=self.device, dtype=torch.int32).repeat(nb)
+            sid = torch.arange(b0, b1, device=self.device, dtype=torch.int32).repeat_interleave(S)
+            h = self._forward(toks, pos, sid, nb, S, False, None)
+            # last-token rows of this chunk -> [nb, H] on every rank (rows live on different ranks)
+            M = nb * S
+            lo, hi = self._rows(M)
+            last = torch.zeros((nb, self.H), device=self.device, dtype=torch.float32)
+            want = torch.arange(nb, device=self.device) * S + (S - 1)
+            mine = (want >= lo) & (want < hi)
+            if bool(mine.any()):
+                last[mine] = h[(want[mine] - lo)].float()
+            if self.W > 1:
+                dist.all_reduce(last, group=self.tp.group)
+            lo2, hi2 = self._rows(nb)
+            firsts.append(self._next_tokens(last[lo2:hi2].to(torch.bfloat16).contiguous(), nb))
+        return torch.cat(firsts)
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """One greedy step: ``tokens [B]`` (the previous step's output) -> next tokens ``[B]``."""
+        B = tokens.numel()
+        for s in self.seqs:
+            self.manager.extend(s, 1)
+        pos = self.lengths.clone()          # position of the new token
+        self.lengths += 1
+        sid = torch.arange(B, device=self.device, dtype=torch.int32)
+        h = self._forward(tokens.to(self.device), pos, sid, B, 1, True, self.lengths)
+        return self._next_tokens(h, B)
+
+    @torch.no_grad()
+    def generate(self, prompts: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        tok = self.prefill(prompts)
+        out = [tok]
+        for _ in range(max_new_tokens - 1):
+            tok = self.decode_step(tok)
+            out.append(tok)
+        return torch.stack(out, dim=1)

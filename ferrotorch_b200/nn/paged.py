@@ -1,0 +1,199 @@
+"""Paged KV cache: host-side page bookkeeping + device-side storage consumed by kernels.
+
+Bookkeeping mirrors the reference (ferrotorch-nn/src/paged_attention.rs:155-532): a
+``PagePool`` with O(1) allocate / free, a per-sequence page list, and a manager that adds,
+extends and drops sequences.  Unlike the reference, the pages are device memory
+(``[num_blocks, block_size, n_kv_heads, head_dim]`` for K and for V, per layer) and the block
+table is a device tensor read by ``ft_kv_append`` / ``ft_paged_decode`` (``csrc/paged_attn.cu``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from ..ops import functional as F
+
+_i, _ll, _f, _vp = _native._i, _native._ll, _native._f, _native._vp
+_native.register_protos({
+    "ft_kv_append": (_i, [_vp] * 7 + [_i, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp]),
+    "ft_paged_decode_scratch": (_ll, [_i, _i, _i, _i]),
+    "ft_paged_decode": (_i, [_vp] * 7 + [_i, _i, _i, _i, _ll, _ll, _i, _i, _i, _f, _i, _i, _vp]),
+})
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PagePool:
+    """Free-list of page ids (paged_attention.rs:155-260)."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self._free = list(range(num_pages - 1, -1, -1))
+
+    def allocate(self) -> int:
+        if not self._free:
+            raise OutOfPages("page pool exhausted (%d pages)" % self.num_pages)
+        return self._free.pop()
+
+    def free(self, page: int) -> None:
+        if not 0 <= page < self.num_pages:
+            raise ValueError("page %d out of range" % page)
+        self._free.append(page)
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+
+class PagedKVCache:
+    """Block tables for up to ``max_seqs`` sequences over one :class:`PagePool`, plus the device
+    K/V pages of every layer.  ``block_size`` tokens per page (16 in the benchmark configs)."""
+
+    def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, num_blocks: int, max_seqs: int,
+                 max_seq_len: int, block_size: int = 16, device="cuda", dtype=torch.bfloat16):
+        self.n_layers, self.n_kv_heads, self.head_dim = n_layers, n_kv_heads, head_dim
+        self.block_size, self.num_blocks, self.max_seqs = block_size, num_blocks, max_seqs
+        self.max_blocks = (max_seq_len + block_size - 1) // block_size
+        self.device = torch.device(device)
+        self.pool = PagePool(num_blocks)
+        shape = (num_blocks, block_size, n_kv_heads, head_dim)
+        self.k = [torch.zeros(shape, device=self.device, dtype=dtype) for _ in range(n_layers)]
+        self.v = [torch.zeros(shape, device=self.device, dtype=dtype) for _ in range(n_layers)]
+        self._table_host = torch.full((max_seqs, self.max_blocks), -1, dtype=torch.int32)
+        self.block_table = self._table_host.to(self.device)
+        self._pages: list[list[int]] = [[] for _ in range(max_seqs)]
+        self.lengths = [0] * max_seqs
+        self._dirty = False
+
+    # ------------------------------------------------------------------ bookkeeping (host)
+    def reserve(self, seq: int, new_len: int) -> None:
+        """Make sure sequence ``seq`` has pages for ``new_len`` tokens."""
+        need = (new_len + self.block_size - 1) // self.block_size
+        if need > self.max_blocks:
+            raise ValueError("sequence length %d exceeds max_seq_len" % new_len)
+        pages = self._pages[seq]
+        while len(pages) < need:
+            p = self.pool.allocate()
+            self._table_host[seq, len(pages)] = p
+            pages.append(p)
+            self._dirty = True
+        self.lengths[seq] = max(self.lengths[seq], new_len)
+
+    def free_sequence(self, seq: int) -> None:
+        for p in self._pages[seq]:
+            self.pool.free(p)
+        self._pages[seq] = []
+        self._table_host[seq].fill_(-1)
+        self.lengths[seq] = 0
+        self._dirty = True
+
+    def sync_table(self) -> torch.Tensor:
+        if self._dirty:
+            self.block_table.copy_(self._table_host, non_blocking=True)
+            self._dirty = False
+        return self.block_table
+
+    # ------------------------------------------------------------------ device ops
+    def append(self, layer: int, k_new: torch.Tensor, v_new: torch.Tensor, positions: torch.Tensor,
+               seq_ids: torch.Tensor | None = None, tokens_per_seq: int = 1) -> None:
+        """Write ``k_new / v_new [T, Hkv, D]`` at ``positions [T]`` (int32).  Token i belongs to
+        sequence ``seq_ids[i]`` or ``i // tokens_per_seq``.  Pages must have been reserved."""
+        T = k_new.shape[0]
+        table = self.sync_table()
+        if not k_new.is_cuda:
+            sid = seq_ids if seq_ids is not None else torch.arange(T) // tokens_per_seq
+            for i in range(T):
+                p = int(positions[i])
+                blk = int(self._table_host[int(sid[i]), p // self.block_size])
+                self.k[layer][blk, p % self.block_size] = k_new[i]
+                self.v[layer][blk, p % self.block_size] = v_new[i]
+            return
+        ldk = k_new.stride(0)
+        ldv = v_new.stride(0)
+        rc = _native.kernels().ft_kv_append(
+            k_new.data_ptr(), v_new.data_ptr(), self.k[layer].data_ptr(), self.v[layer].data_ptr(),
+            table.data_ptr(), positions.data_ptr(), seq_ids.data_ptr() if seq_ids is not None else None, T,
+            tokens_per_seq, self.n_kv_heads, self.head_dim, ldk, ldv, self.block_size, self.max_blocks,
+            self.num_blocks, F._dev(k_new), F._stream())
+        _native.check(rc, "ft_kv_append")
+
+    def decode(self, layer: int, q: torch.Tensor, ctx_len: torch.Tensor, scale: float | None = None,
+               n_splits: int = 0) -> torch.Tensor:
+        """One query token per sequence: ``q [B, Hq, D]``, ``ctx_len [B]`` int32 -> ``[B, Hq, D]``."""
+        B, Hq, D = q.shape
+        scale = scale if scale is not None else D ** -0.5
+        table = self.sync_table()
+        if not q.is_cuda:
+            return self._decode_reference(layer, q, ctx_len, scale)
+        lib = _native.kernels()
+        if n_splits <= 0:
+            ctas = B * self.n_kv_heads
+            n_splits = 1 if ctas >= 256 else max(1, min(8, 296 // max(ctas, 1)))
+        out = torch.empty(q.shape, device=q.device, dtype=q.dtype)
+        n_scr = int(lib.ft_paged_decode_scratch(B, Hq, D, n_splits))
+        scratch = F._get_scratch("paged_decode", n_scr, q.device) if n_scr else None
+        rc = lib.ft_paged_decode(q.data_ptr(), self.k[layer].data_ptr(), self.v[layer].data_ptr(), table.data_ptr(),
+                                 ctx_len.data_ptr(), out.data_ptr(), scratch.data_ptr() if scratch is not None else None,
+                                 B, Hq, self.n_kv_heads, D, q.stride(0), out.stride(0), self.block_size,
+                                 self.max_blocks, self.num_blocks, float(scale), n_splits, F._dev(q), F._stream())
+        _native.check(rc, "ft_paged_decode")
+        return out
+
+    def gather(self, layer: int, seq: int, length: int):
+        """Contiguous ``[length, Hkv, D]`` K and V of one sequence (debug / reference path;
+        paged_attention.rs ``get_keys`` / ``get_values``)."""
+        pages = self._pages[seq][: (length + self.block_size - 1) // self.block_size]
+        idx = torch.tensor(pages, device=self.k[layer].device, dtype=torch.long)
+        k = self.k[layer][idx].reshape(-1, self.n_kv_heads, self.head_dim)[:length]
+        v = self.v[layer][idx].reshape(-1, self.n_kv_heads, self.head_dim)[:length]
+        return k, v
+
+    def _decode_reference(self, layer, q, ctx_len, scale):
+        from ..ops import reference as ref
+
+        outs = []
+        for b in range(q.shape[0]):
+            k, v = self.gather(layer, b, int(ctx_len[b]))
+            o, _ = ref.attention(q[b][None, None], k[None], v[None], causal=False, scale=scale)
+            outs.append(o[0, 0])
+        return torch.stack(outs)
+
+
+class PagedAttentionManager:
+    """Multi-sequence front end: hands out sequence slots, grows and frees them
+    (paged_attention.rs:447-532)."""
+
+    def __init__(self, cache: PagedKVCache):
+        self.cache = cache
+        self._free_slots = list(range(cache.max_seqs - 1, -1, -1))
+        self.active: dict[int, int] = {}
+
+    def add_sequence(self, prompt_len: int) -> int:
+        if not self._free_slots:
+            raise OutOfPages("no free sequence slot")
+        s = self._free_slots.pop()
+        try:
+            self.cache.reserve(s, prompt_len)
+        except OutOfPages:
+            self.cache.free_sequence(s)
+            self._free_slots.append(s)
+            raise
+        self.active[s] = prompt_len
+        return s
+
+    def extend(self, seq: int, n_tokens: int = 1) -> int:
+        new_len = self.active[seq] + n_tokens
+        self.cache.reserve(seq, new_len)
+        self.active[seq] = new_len
+        return new_len
+
+    def remove_sequence(self, seq: int) -> None:
+        self.cache.free_sequence(seq)
+        del self.active[seq]
+        self._free_slots.append(seq)
+
+    @property
+    def free_pages(self) -> int:
+        return self.cache.pool.num_free

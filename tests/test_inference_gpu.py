@@ -1,0 +1,84 @@
+"""Paged KV cache kernels and the inference engine."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from ferrotorch_b200 import _native
+from ferrotorch_b200.nn.paged import OutOfPages, PagedAttentionManager, PagedKVCache
+from ferrotorch_b200.ops import reference as R
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,Hq,Hkv,splits", [(128, 8, 2, 1), (128, 8, 2, 3), (64, 4, 4, 2), (128, 4, 1, 0)])
+def test_paged_decode_matches_reference(D, Hq, Hkv, splits):
+    torch.manual_seed(D + Hq + splits)
+    B, bs = 5, 16
+    lens = [1, 17, 64, 100, 333]
+    cache = PagedKVCache(1, Hkv, D, num_blocks=64, max_seqs=B, max_seq_len=512, block_size=bs)
+    mgr = PagedAttentionManager(cache)
+    ks, vs = [], []
+    for b, n in enumerate(lens):
+        assert mgr.add_sequence(n) == b
+        k = torch.randn(n, Hkv, D, device="cuda").to(torch.bfloat16)
+        v = torch.randn(n, Hkv, D, device="cuda").to(torch.bfloat16)
+        ks.append(k), vs.append(v)
+        pos = torch.arange(n, device="cuda", dtype=torch.int32)
+        sid = torch.full((n,), b, device="cuda", dtype=torch.int32)
+        cache.append(0, k, v, pos, sid)
+    q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+    out = cache.decode(0, q, torch.tensor(lens, device="cuda", dtype=torch.int32), n_splits=splits)
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        gk, gv = cache.gather(0, b, n)
+        assert torch.equal(gk, ks[b]) and torch.equal(gv, vs[b])
+        want, _ = R.attention(q[b][None, None], ks[b][None], vs[b][None], causal=False)
+        err = (out[b].float() - want[0, 0].float()).abs().max().item()
+        assert err < 2e-2, "seq %d len %d err %g" % (b, n, err)
+
+
+def test_page_pool_bookkeeping():
+    cache = PagedKVCache(1, 1, 8, num_blocks=4, max_seqs=2, max_seq_len=64, block_size=16, device="cpu",
+                         dtype=torch.float32)
+    mgr = PagedAttentionManager(cache)
+    a = mgr.add_sequence(20)            # 2 pages
+    assert mgr.free_pages == 2
+    b = mgr.add_sequence(16)            # 1 page
+    mgr.extend(b, 1)                    # 17 tokens -> 2 pages
+    assert mgr.free_pages == 0
+    with pytest.raises(OutOfPages):
+        mgr.extend(a, 20)
+    mgr.remove_sequence(a)
+    assert mgr.free_pages == 2 and a not in mgr.active
+    k = torch.arange(17 * 8, dtype=torch.float32).view(17, 1, 8)
+    cache.append(0, k, -k, torch.arange(17, dtype=torch.int32), torch.full((17,), b, dtype=torch.int32))
+    gk, gv = cache.gather(0, b, 17)
+    assert torch.equal(gk, k) and torch.equal(gv, -k)
+    out = cache.decode(0, torch.ones(2, 1, 8), torch.tensor([0, 17], dtype=torch.int32))
+    assert out.shape == (2, 1, 8)
+
+
+def _run(nproc, port):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    script = os.path.join(HERE, "engine_worker.py")
+    cmd = [sys.executable, script] if nproc == 1 else [
+        sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
+        "--master-addr", "127.0.0.1", "--master-port", str(port), script]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "ok" in proc.stdout
+
+
+@pytest.mark.gpu
+def test_engine_single_gpu():
+    _run(1, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_engine_tensor_parallel_2():
+    _run(2, 29551)
