@@ -1,0 +1,146 @@
+#!/usr/bin/env python
+"""Per-kernel micro-benchmarks with roofline fractions against MEASURED_PEAKS.json.
+
+    python benchmarks/bench_kernels.py [--small] [--only gemm,attn,norm,optim,decode]
+
+Timing: CUDA events, 3+ warm-up runs, a 256 MiB buffer is rewritten between timed runs to flush
+the 126 MB L2, median of the timed runs.  ``--small`` keeps every case to a few launches and
+under ~2 GB (the shape used under ncu).  Prints one JSON line per case.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from ferrotorch_b200 import _native  # noqa: E402
+from ferrotorch_b200.ops import functional as F  # noqa: E402
+from ferrotorch_b200.ops.attention import flash_attention  # noqa: E402
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def bench(fn, iters=10, warm=3):
+    flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def emit(name, ms, flops=None, nbytes=None, **extra):
+    hbm, tf, kind = peaks()
+    out = {"kernel": name, "ms": round(ms, 4), **extra}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out["frac_of_%s_bf16_peak" % kind] = round(flops / ms / 1e9 / tf, 3)
+    if nbytes:
+        out["gbs"] = round(nbytes / ms / 1e6, 1)
+        out["frac_of_%s_hbm" % kind] = round(nbytes / ms / 1e6 / hbm, 3)
+    print(json.dumps(out), flush=True)
+
+
+def r(*s):
+    return torch.randn(*s, device="cuda", dtype=torch.bfloat16)
+
+
+def run_gemm(small):
+    shapes = [(4096, 4096, 4096)] if small else [(8192, 8192, 8192), (4096, 6144, 4096), (4096, 28672, 4096),
+                                                 (4096, 4096, 14336), (16384, 4096, 4096), (64, 28672, 4096)]
+    for M, N, K in shapes:
+        a, b, c = r(M, K), r(N, K), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        emit("gemm_nt %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(a, b, out=c)), fl)
+        if not small:
+            emit("torch.matmul %dx%dx%d" % (M, N, K), bench(lambda: torch.matmul(a, b.t(), out=c)), fl)
+            bt, at = r(K, N).t(), r(K, M).t()
+            emit("gemm_nn(dgrad) %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(a, bt, out=c)), fl)
+            emit("gemm_tn(wgrad) %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(at, bt, out=c)), fl)
+
+
+def run_attn(small):
+    B, S, Hq, Hkv, D = (1, 2048, 16, 4, 128) if small else (4, 4096, 32, 8, 128)
+    q, k, v = r(B, S, Hq, D).requires_grad_(), r(B, S, Hkv, D).requires_grad_(), r(B, S, Hkv, D).requires_grad_()
+    fl = 4.0 * B * Hq * S * S * D / 2
+    emit("flash_fwd B%d S%d" % (B, S), bench(lambda: F.flash_attn_fwd(q, k, v, True)), fl)
+    o = flash_attention(q, k, v, causal=True)
+    do = r(B, S, Hq, D)
+    emit("flash_bwd B%d S%d" % (B, S), bench(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True)), 2.5 * fl)
+    if not small:
+        qt, kt, vt = (x.detach().transpose(1, 2) for x in (q, k, v))
+        emit("sdpa_fwd (library)", bench(lambda: torch.nn.functional.scaled_dot_product_attention(
+            qt, kt, vt, is_causal=True, enable_gqa=True)), fl)
+
+
+def run_norm(small):
+    T, H, Fd = (16384, 4096, 14336) if not small else (8192, 4096, 14336)
+    x, w = r(T, H), r(H)
+    emit("rmsnorm_fwd %dx%d" % (T, H), bench(lambda: F.rmsnorm(x, w)), nbytes=4.0 * T * H)
+    gu = r(T, 2 * Fd)
+    emit("swiglu_fwd %dx%d" % (T, Fd), bench(lambda: F.swiglu(gu)), nbytes=6.0 * T * Fd)
+    qkv = r(T, 48, 128)
+    cos, sin = (t.cuda() for t in __import__("ferrotorch_b200.ops.reference", fromlist=["x"]).rope_tables(128, 4096, 5e5))
+    emit("rope %d tokens" % T, bench(lambda: F._rope_launch(qkv, cos, sin, None, 40, 4096, 0, False, False)),
+         nbytes=4.0 * T * 40 * 128)
+    V = 128256
+    z, tgt = r(2048, V), torch.randint(0, V, (2048,), device="cuda")
+    emit("cross_entropy 2048x%d" % V, bench(lambda: F.cross_entropy_fwd_bwd_(z, tgt, 1.0)), nbytes=6.0 * 2048 * V)
+
+
+def run_optim(small):
+    n = (1 << 26) if small else (1 << 29)
+    lib = _native.kernels()
+    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    g, lp = torch.zeros(n, device="cuda", dtype=torch.bfloat16), torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    st = torch.cuda.current_stream().cuda_stream
+    emit("adamw_flat %d" % n, bench(lambda: lib.ft_adamw_flat(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(),
+                                                             lp.data_ptr(), n, 0, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 0, 0, st)),
+         nbytes=28.0 * n)
+
+
+def run_decode(small):
+    from ferrotorch_b200.nn.paged import PagedAttentionManager, PagedKVCache
+
+    B, ctx, Hq, Hkv, D = (16, 1024, 32, 8, 128) if small else (64, 2304, 32, 8, 128)
+    cache = PagedKVCache(1, Hkv, D, num_blocks=B * (ctx // 16 + 1), max_seqs=B, max_seq_len=ctx + 16)
+    mgr = PagedAttentionManager(cache)
+    for _ in range(B):
+        mgr.add_sequence(ctx)
+    cache.k[0].normal_()
+    cache.v[0].normal_()
+    q = r(B, Hq, D)
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    emit("paged_decode B%d ctx%d" % (B, ctx), bench(lambda: cache.decode(0, q, lens)), nbytes=4.0 * B * ctx * Hkv * D)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--only", default="gemm,attn,norm,optim,decode")
+    a = ap.parse_args()
+    for name in a.only.split(","):
+        {"gemm": run_gemm, "attn": run_attn, "norm": run_norm, "optim": run_optim, "decode": run_decode}[name](a.small)
+    print(json.dumps({"device_status": _native.device_status(0)}))

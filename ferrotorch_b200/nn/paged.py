@@ -193,6 +193,7 @@ class PagedAttentionManager:
         self.cache.free_sequence(seq)
         del self.active[seq]
         self._free_slots.append(seq)
+        self._free_slots.sort(reverse=True)  # lowest free slot is handed out first
 
     @property
     def free_pages(self) -> int:
