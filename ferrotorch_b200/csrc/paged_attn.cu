@@ -51,26 +51,29 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const 
 
 // grid (n_splits, Hkv, B).  Each CTA covers tiles of 32 keys, strided over its warps, inside its
 // slice of the context; partial (m, l, o) per (b, q head, split) go to scratch when n_splits > 1.
-template <int D>
+// Scores: lane j owns key j of the tile and reads its whole row (all loads issued before the
+// math).  PV: the two half-warps take even / odd keys, each lane owns 8 (D=128) or 4 (D=64)
+// output dims, V rows are read 8 keys at a time with 16-byte (8-byte) loads.
+template <int D, int G>
 __global__ void __launch_bounds__(PD_THREADS)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                     const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int Hq, int Hkv, long long ldq, long long ldo, int block_size,
                     int max_blocks, int num_blocks, float scale_log2, int n_splits) {
-  constexpr int DV = D / 32;  // dims per lane in the PV phase
+  constexpr int DV = D / 16;  // dims per lane in the PV phase (half-warp covers D)
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int G = Hq / Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int half = lane >> 4, hl = lane & 15;
   const int len = ctx_len[b];
   const int tiles_total = (len + 31) >> 5;
   const int tiles_per_split = (tiles_total + n_splits - 1) / n_splits;
   const int tile_lo = split * tiles_per_split, tile_hi = min(tiles_total, tile_lo + tiles_per_split);
 
-  __shared__ __align__(16) float s_q[PD_MAX_G][D];          // q * scale * log2(e)
-  __shared__ float s_p[PD_WARPS][PD_MAX_G][32];             // probabilities of the current tile
-  __shared__ float s_m[PD_WARPS][PD_MAX_G], s_l[PD_WARPS][PD_MAX_G];
-  __shared__ __align__(16) float s_o[PD_WARPS][PD_MAX_G][D];
+  __shared__ __align__(16) float s_q[G][D];          // q * scale * log2(e)
+  __shared__ float s_p[PD_WARPS][G][32];             // probabilities of the current tile
+  __shared__ float s_m[PD_WARPS][G], s_l[PD_WARPS][G];
+  __shared__ __align__(16) float s_o[PD_WARPS][G][D];
 
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
@@ -78,98 +81,115 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
   __syncthreads();
 
-  float m[PD_MAX_G], l[PD_MAX_G], o[PD_MAX_G][DV];
+  float m[G], l[G], o[G][DV];
 #pragma unroll
-  for (int g = 0; g < PD_MAX_G; ++g) {
+  for (int g = 0; g < G; ++g) {
     m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
     for (int j = 0; j < DV; ++j) o[g][j] = 0.f;
   }
   const int* bt = block_table + static_cast<long long>(b) * max_blocks;
   const long long row_stride = static_cast<long long>(Hkv) * D;
+  const long long head_off = static_cast<long long>(kvh) * D;
 
   for (int tile = tile_lo + warp; tile < tile_hi; tile += PD_WARPS) {
-    // ---- scores: lane j owns key tile*32 + j
-    const int key = (tile << 5) + lane;
+    const int key0 = tile << 5;
+    // ---- scores: lane j owns key key0 + j; issue the whole row's loads, then the dot products
+    const int key = key0 + lane;
     const bool valid = key < len;
-    float s[PD_MAX_G];
+    float s[G];
 #pragma unroll
-    for (int g = 0; g < PD_MAX_G; ++g) s[g] = 0.f;
-    if (valid) {
-      int blk = bt[key / block_size];
+    for (int g = 0; g < G; ++g) s[g] = 0.f;
+    {
+      const int kk = valid ? key : key0;
+      int blk = bt[kk / block_size];
       blk = min(max(blk, 0), num_blocks - 1);
       const uint4* kr = reinterpret_cast<const uint4*>(
-          k_cache + (static_cast<long long>(blk) * block_size + key % block_size) * row_stride + static_cast<long long>(kvh) * D);
-#pragma unroll 4
-      for (int c = 0; c < D / 8; ++c) {
-        const uint4 kv = __ldg(kr + c);
-        const float2 k0 = unpack_bf16x2(kv.x), k1 = unpack_bf16x2(kv.y), k2 = unpack_bf16x2(kv.z), k3 = unpack_bf16x2(kv.w);
+          k_cache + (static_cast<long long>(blk) * block_size + kk % block_size) * row_stride + head_off);
+      uint4 kv[D / 8];
 #pragma unroll
-        for (int g = 0; g < PD_MAX_G; ++g) {
-          if (g < G) {
-            const float4 qa = *reinterpret_cast<const float4*>(&s_q[g][c * 8]);
-            const float4 qb = *reinterpret_cast<const float4*>(&s_q[g][c * 8 + 4]);
-            s[g] += k0.x * qa.x + k0.y * qa.y + k1.x * qa.z + k1.y * qa.w + k2.x * qb.x + k2.y * qb.y + k3.x * qb.z + k3.y * qb.w;
-          }
+      for (int c = 0; c < D / 8; ++c) kv[c] = __ldg(kr + c);
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        const float2 k0 = unpack_bf16x2(kv[c].x), k1 = unpack_bf16x2(kv[c].y), k2 = unpack_bf16x2(kv[c].z),
+                     k3 = unpack_bf16x2(kv[c].w);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float4 qa = *reinterpret_cast<const float4*>(&s_q[g][c * 8]);
+          const float4 qb = *reinterpret_cast<const float4*>(&s_q[g][c * 8 + 4]);
+          s[g] += k0.x * qa.x + k0.y * qa.y + k1.x * qa.z + k1.y * qa.w + k2.x * qb.x + k2.y * qb.y + k3.x * qb.z + k3.y * qb.w;
         }
       }
     }
     // ---- online softmax per head across the 32 lanes
-    float alpha[PD_MAX_G];
+    float alpha[G];
 #pragma unroll
-    for (int g = 0; g < PD_MAX_G; ++g) {
-      if (g < G) {
-        const float sv = valid ? s[g] : -INFINITY;
-        const float mx = warp_max(sv);
-        const float m_new = fmaxf(m[g], mx);
-        const float pv = valid ? fast_exp2(sv - m_new) : 0.f;
-        alpha[g] = fast_exp2(m[g] - m_new);  // exp2(-inf) = 0 on the first tile
-        l[g] = l[g] * alpha[g] + warp_sum(pv);
-        m[g] = m_new;
-        s_p[warp][g][lane] = pv;
-      }
+    for (int g = 0; g < G; ++g) {
+      const float sv = valid ? s[g] : -INFINITY;
+      const float mx = warp_max(sv);
+      const float m_new = fmaxf(m[g], mx);
+      const float pv = valid ? fast_exp2(sv - m_new) : 0.f;
+      alpha[g] = fast_exp2(m[g] - m_new);  // exp2(-inf) = 0 on the first tile
+      l[g] = l[g] * alpha[g] + warp_sum(pv);
+      m[g] = m_new;
+      s_p[warp][g][lane] = pv;
+#pragma unroll
+      for (int j = 0; j < DV; ++j) o[g][j] *= alpha[g];
     }
     __syncwarp();
-    // ---- O += P V: lanes own DV dims; one V row per step (coalesced 2*D bytes per warp)
+    // ---- O += P V: half-warp `half` takes keys key0 + 2*i + half; 8 keys (per half) in flight
+    const int n_keys = min(32, len - key0);
+    for (int i0 = 0; i0 < 16; i0 += 8) {
+      if (2 * i0 >= n_keys) break;
+      uint4 vv[8];
 #pragma unroll
-    for (int g = 0; g < PD_MAX_G; ++g)
-      if (g < G) {
-#pragma unroll
-        for (int j = 0; j < DV; ++j) o[g][j] *= alpha[g];
-      }
-    const int n_keys = min(32, len - (tile << 5));
-    for (int j = 0; j < n_keys; ++j) {
-      const int kj = (tile << 5) + j;
-      int blk = bt[kj / block_size];
-      blk = min(max(blk, 0), num_blocks - 1);
-      const __nv_bfloat16* vr = v_cache + (static_cast<long long>(blk) * block_size + kj % block_size) * row_stride +
-                                static_cast<long long>(kvh) * D + lane * DV;
-      float vv[DV];
-      if constexpr (DV == 4) {
-        const uint2 x = __ldg(reinterpret_cast<const uint2*>(vr));
-        const float2 a = unpack_bf16x2(x.x), c2 = unpack_bf16x2(x.y);
-        vv[0] = a.x; vv[1] = a.y; vv[2] = c2.x; vv[3] = c2.y;
-      } else {
-        const uint32_t x = __ldg(reinterpret_cast<const uint32_t*>(vr));
-        const float2 a = unpack_bf16x2(x);
-        vv[0] = a.x; vv[1] = a.y;
-      }
-#pragma unroll
-      for (int g = 0; g < PD_MAX_G; ++g)
-        if (g < G) {
-          const float pj = s_p[warp][g][j];
-#pragma unroll
-          for (int e = 0; e < DV; ++e) o[g][e] += pj * vv[e];
+      for (int i = 0; i < 8; ++i) {
+        const int j = 2 * (i0 + i) + half;
+        const int kj = key0 + min(j, n_keys - 1);
+        int blk = bt[kj / block_size];
+        blk = min(max(blk, 0), num_blocks - 1);
+        const __nv_bfloat16* vr = v_cache + (static_cast<long long>(blk) * block_size + kj % block_size) * row_stride +
+                                  head_off + hl * DV;
+        if constexpr (DV == 8) {
+          vv[i] = __ldg(reinterpret_cast<const uint4*>(vr));
+        } else {
+          const uint2 t = __ldg(reinterpret_cast<const uint2*>(vr));
+          vv[i] = make_uint4(t.x, t.y, 0u, 0u);
         }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j = 2 * (i0 + i) + half;
+        if (j < n_keys) {
+          float f[8];
+          const float2 a0 = unpack_bf16x2(vv[i].x), a1 = unpack_bf16x2(vv[i].y);
+          f[0] = a0.x; f[1] = a0.y; f[2] = a1.x; f[3] = a1.y;
+          if constexpr (DV == 8) {
+            const float2 a2 = unpack_bf16x2(vv[i].z), a3 = unpack_bf16x2(vv[i].w);
+            f[4] = a2.x; f[5] = a2.y; f[6] = a3.x; f[7] = a3.y;
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pj = s_p[warp][g][j];
+#pragma unroll
+            for (int e = 0; e < DV; ++e) o[g][e] += pj * f[e];
+          }
+        }
+      }
     }
     __syncwarp();
   }
 
-  // ---- combine the warps of this CTA
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+  // ---- combine the two half-warps, then the warps of this CTA
 #pragma unroll
-    for (int e = 0; e < DV; ++e) s_o[warp][g][lane * DV + e] = o[g][e];
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int e = 0; e < DV; ++e) o[g][e] += __shfl_xor_sync(0xffffffffu, o[g][e], 16);
+    if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    if (half == 0) {
+#pragma unroll
+      for (int e = 0; e < DV; ++e) s_o[warp][g][hl * DV + e] = o[g][e];
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
@@ -258,16 +278,25 @@ FT_API int ft_paged_decode(const void* q, const void* k_cache, const void* v_cac
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + static_cast<long long>(B) * Hq * n_splits * D : nullptr;
   dim3 grid(n_splits, Hkv, B);
-  if (D == 128)
-    paged_decode_kernel<128><<<grid, PD_THREADS, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
-        static_cast<const __nv_bfloat16*>(v_cache), block_table, ctx_len, static_cast<__nv_bfloat16*>(out), part_o,
-        part_ml, Hq, Hkv, ldq, ldo, block_size, max_blocks, num_blocks, sl2, n_splits);
-  else
-    paged_decode_kernel<64><<<grid, PD_THREADS, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
-        static_cast<const __nv_bfloat16*>(v_cache), block_table, ctx_len, static_cast<__nv_bfloat16*>(out), part_o,
-        part_ml, Hq, Hkv, ldq, ldo, block_size, max_blocks, num_blocks, sl2, n_splits);
+  const int G = Hq / Hkv;
+#define FT_PD_LAUNCH(DD, GG)                                                                                   \
+  paged_decode_kernel<DD, GG><<<grid, PD_THREADS, 0, stream>>>(                                                \
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),                        \
+      static_cast<const __nv_bfloat16*>(v_cache), block_table, ctx_len, static_cast<__nv_bfloat16*>(out),      \
+      part_o, part_ml, Hq, Hkv, ldq, ldo, block_size, max_blocks, num_blocks, sl2, n_splits)
+#define FT_PD_BY_G(DD)                                             \
+  switch (G) {                                                     \
+    case 1: FT_PD_LAUNCH(DD, 1); break;                            \
+    case 2: FT_PD_LAUNCH(DD, 2); break;                            \
+    case 4: FT_PD_LAUNCH(DD, 4); break;                            \
+    case 8: FT_PD_LAUNCH(DD, 8); break;                            \
+    default:                                                       \
+      set_last_error("ft_paged_decode: group size %d not supported (1, 2, 4, 8)", G); \
+      return FT_E_BAD_ARG;                                         \
+  }
+  if (D == 128) { FT_PD_BY_G(128) } else { FT_PD_BY_G(64) }
+#undef FT_PD_BY_G
+#undef FT_PD_LAUNCH
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   if (n_splits > 1) {

@@ -1,0 +1,187 @@
+"""GGUF checkpoints: native mmap reader (``csrc/host/gguf.cpp``), dequantisation, the
+GGUF -> HF key map for Llama, and a small writer / Q4_0 quantiser used by tests and benchmarks.
+
+Reference: ferrotorch-serialize/src/gguf.rs:56-927 (types, block layouts, ``load_gguf_state_dict``)
+and ferrotorch-llama/src/gguf_remap.rs:23-52 (``token_embd -> model.embed_tokens``, ``blk.{i}.attn_q
+-> model.layers.{i}.self_attn.q_proj`` ...).
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import re
+import struct
+
+import numpy as np
+import torch
+
+from .. import _native
+
+GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q8_0, GGML_Q8_1, GGML_BF16 = 0, 1, 2, 3, 6, 7, 8, 9, 30
+_BLOCK = {GGML_F32: (1, 4), GGML_F16: (1, 2), GGML_BF16: (1, 2), GGML_Q4_0: (32, 18), GGML_Q4_1: (32, 20),
+          GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q8_0: (32, 34), GGML_Q8_1: (32, 36)}
+_ready = False
+
+
+def _lib():
+    global _ready
+    lib = _native.host()
+    if not _ready:
+        vp, ll, cp = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_char_p
+        lib.ftg_open.restype, lib.ftg_open.argtypes = vp, [cp]
+        lib.ftg_error.restype, lib.ftg_error.argtypes = cp, [vp]
+        lib.ftg_close.argtypes = [vp]
+        lib.ftg_version.argtypes = [vp]
+        lib.ftg_n_tensors.restype, lib.ftg_n_tensors.argtypes = ll, [vp]
+        lib.ftg_metadata_json.restype, lib.ftg_metadata_json.argtypes = cp, [vp]
+        lib.ftg_tensor_name.restype, lib.ftg_tensor_name.argtypes = cp, [vp, ll]
+        lib.ftg_tensor_info.argtypes = [vp, ll, vp]
+        lib.ftg_tensor_data.restype, lib.ftg_tensor_data.argtypes = vp, [vp, ll]
+        lib.ftg_dequantize.argtypes = [ctypes.c_uint, vp, vp, ll]
+        lib.ftg_split_q4_0.argtypes = [vp, ll, ll, vp, vp]
+        _ready = True
+    return lib
+
+
+class GgufFile:
+    """An open GGUF file.  ``tensors`` maps name -> (ggml_type, shape (outermost first), nbytes)."""
+
+    def __init__(self, path: str):
+        self._lib = _lib()
+        self._h = self._lib.ftg_open(path.encode())
+        err = self._lib.ftg_error(self._h)
+        if err:
+            msg = err.decode()
+            self.close()
+            raise ValueError("GGUF %s: %s" % (path, msg))
+        self.version = self._lib.ftg_version(self._h)
+        self.metadata = json.loads(self._lib.ftg_metadata_json(self._h).decode(errors="replace"))
+        self.tensors, self._index = {}, {}
+        info = (ctypes.c_ulonglong * 8)()
+        for i in range(self._lib.ftg_n_tensors(self._h)):
+            name = self._lib.ftg_tensor_name(self._h, i).decode()
+            self._lib.ftg_tensor_info(self._h, i, info)
+            nd = int(info[1])
+            shape = tuple(int(info[2 + d]) for d in range(nd))[::-1]  # GGUF stores innermost first
+            self.tensors[name] = (int(info[0]), shape, int(info[6]))
+            self._index[name] = i
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.ftg_close(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def raw(self, name: str) -> torch.Tensor:
+        """The tensor's bytes as a uint8 tensor (copied out of the mapping)."""
+        t, shape, nbytes = self.tensors[name]
+        ptr = self._lib.ftg_tensor_data(self._h, self._index[name])
+        buf = (ctypes.c_ubyte * nbytes).from_address(ptr)
+        return torch.frombuffer(bytearray(buf), dtype=torch.uint8)
+
+    def dequantize(self, name: str, dtype=torch.float32) -> torch.Tensor:
+        t, shape, nbytes = self.tensors[name]
+        n = int(np.prod(shape)) if shape else 1
+        out = torch.empty(n, dtype=torch.float32)
+        rc = self._lib.ftg_dequantize(t, self._lib.ftg_tensor_data(self._h, self._index[name]), out.data_ptr(), n)
+        if rc != 0:
+            raise ValueError("unsupported ggml type %d for %s" % (t, name))
+        return out.view(shape).to(dtype)
+
+    def q4_0_planes(self, name: str):
+        """``(scales fp16 [rows, cols/32], nibbles uint8 [rows, cols/2])`` of a Q4_0 matrix."""
+        t, shape, _ = self.tensors[name]
+        assert t == GGML_Q4_0 and len(shape) == 2, "%s is not a Q4_0 matrix" % name
+        rows, cols = shape
+        scales = torch.empty((rows, cols // 32), dtype=torch.float16)
+        nib = torch.empty((rows, cols // 2), dtype=torch.uint8)
+        rc = self._lib.ftg_split_q4_0(self._lib.ftg_tensor_data(self._h, self._index[name]), rows, cols,
+                                      scales.data_ptr(), nib.data_ptr())
+        assert rc == 0
+        return scales, nib
+
+
+_LAYER_MAP = {"attn_norm": "input_layernorm", "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj",
+              "attn_v": "self_attn.v_proj", "attn_output": "self_attn.o_proj", "ffn_norm": "post_attention_layernorm",
+              "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj"}
+_TOP_MAP = {"token_embd": "model.embed_tokens", "output_norm": "model.norm", "output": "lm_head"}
+
+
+def gguf_key_to_hf(key: str) -> str | None:
+    """``blk.3.attn_q.weight`` -> ``model.layers.3.self_attn.q_proj.weight`` (None if unknown)."""
+    m = re.fullmatch(r"blk\.(\d+)\.([a-z_]+)\.(weight|bias)", key)
+    if m and m.group(2) in _LAYER_MAP:
+        return "model.layers.%s.%s.%s" % (m.group(1), _LAYER_MAP[m.group(2)], m.group(3))
+    m = re.fullmatch(r"([a-z_]+)\.(weight|bias)", key)
+    if m and m.group(1) in _TOP_MAP:
+        return "%s.%s" % (_TOP_MAP[m.group(1)], m.group(2))
+    return None
+
+
+def load_gguf_state_dict(path: str, dtype=torch.bfloat16, remap: bool = True) -> dict[str, torch.Tensor]:
+    """Dequantise every tensor to ``dtype`` (HF key names when ``remap``)."""
+    out = {}
+    with GgufFile(path) as f:
+        for name in f.tensors:
+            key = gguf_key_to_hf(name) if remap else name
+            out[key or name] = f.dequantize(name, dtype)
+    return out
+
+
+# --------------------------------------------------------------------------- writer / quantiser
+def quantize_q4_0(w: torch.Tensor) -> torch.Tensor:
+    """Quantise a float matrix ``[rows, cols]`` (cols % 32 == 0) to Q4_0 blocks, returned as a
+    uint8 tensor ``[rows * cols / 32, 18]``.  ggml rule: ``d = max_abs_signed / -8``,
+    ``q = clamp(round(x / d) + 8, 0, 15)``."""
+    x = w.detach().float().cpu().reshape(-1, 32)
+    idx = x.abs().argmax(dim=1, keepdim=True)
+    mx = x.gather(1, idx)
+    d = mx / -8.0
+    inv = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+    q = (x * inv + 8.5).floor().clamp(0, 15).to(torch.uint8)
+    packed = q[:, :16] | (q[:, 16:] << 4)
+    dh = d.to(torch.float16).view(torch.uint8).reshape(-1, 2)
+    return torch.cat([dh, packed], dim=1).contiguous()
+
+
+def _kv_bytes(key: str, value) -> bytes:
+    kb = key.encode()
+    out = struct.pack("<Q", len(kb)) + kb
+    if isinstance(value, bool):
+        return out + struct.pack("<IB", 7, int(value))
+    if isinstance(value, int):
+        return out + struct.pack("<II", 4, value) if 0 <= value < 2 ** 32 else out + struct.pack("<Iq", 11, value)
+    if isinstance(value, float):
+        return out + struct.pack("<If", 6, value)
+    if isinstance(value, str):
+        vb = value.encode()
+        return out + struct.pack("<IQ", 8, len(vb)) + vb
+    raise TypeError("unsupported metadata value %r" % (value,))
+
+
+def write_gguf(path: str, tensors: dict[str, tuple[int, tuple, bytes]], metadata: dict | None = None,
+               alignment: int = 32) -> None:
+    """``tensors``: name -> (ggml_type, shape (outermost first), raw bytes)."""
+    metadata = dict(metadata or {})
+    metadata.setdefault("general.alignment", alignment)
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(metadata))
+    for k, v in metadata.items():
+        head += _kv_bytes(k, v)
+    off, blobs = 0, []
+    for name, (t, shape, raw) in tensors.items():
+        nb = name.encode()
+        head += struct.pack("<Q", len(nb)) + nb + struct.pack("<I", len(shape))
+        for d in reversed(shape):
+            head += struct.pack("<Q", d)
+        head += struct.pack("<IQ", t, off)
+        pad = (-len(raw)) % alignment
+        blobs.append(raw + b"\0" * pad)
+        off += len(raw) + pad
+    pad = (-len(head)) % alignment
+    with open(path, "wb") as f:
+        f.write(head + b"\0" * pad + b"".join(blobs))

@@ -1,0 +1,274 @@
+"""State-dict and checkpoint formats.
+
+Covers the reference's ``ferrotorch-serialize``:
+
+* SafeTensors single / sharded (``model.safetensors.index.json``) / filtered load and save,
+  optional down-cast on load (safetensors_io.rs:129-916);
+* PyTorch ``.pt`` / ``.bin`` import and export (pytorch_import.rs:938, pytorch_export.rs:235) --
+  ``torch.load(weights_only=True)`` is the pickle VM here;
+* the native state-dict format: JSON-lines header, ``\\n---\\n``, raw little-endian bytes
+  (state_dict.rs:1-17, 74, 176);
+* training checkpoints: three length-prefixed sections -- metadata JSON, optimizer-state JSON,
+  binary state dict (checkpoint.rs:1-17, 59-123) -- plus an asynchronous writer that snapshots
+  to pinned host memory and writes on a thread (checkpoint.rs:575).
+"""
+from __future__ import annotations
+
+import io
+import json
+import os
+import struct
+import threading
+from typing import Callable, Iterable
+
+import torch
+
+_DT = {"F32": torch.float32, "F64": torch.float64, "F16": torch.float16, "BF16": torch.bfloat16,
+       "I64": torch.int64, "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8,
+       "BOOL": torch.bool}
+_DT_INV = {v: k for k, v in _DT.items()}
+
+
+# --------------------------------------------------------------------------- SafeTensors
+def save_safetensors(state: dict[str, torch.Tensor], path: str, metadata: dict | None = None) -> None:
+    from safetensors.torch import save_file
+
+    save_file({k: v.detach().contiguous().cpu() for k, v in state.items()}, path, metadata=metadata)
+
+
+def load_safetensors(path: str, device="cpu", dtype: torch.dtype | None = None,
+                     key_filter: Callable[[str], bool] | None = None) -> dict[str, torch.Tensor]:
+    """Memory-mapped load; ``key_filter`` selects tensors, ``dtype`` down-casts floating tensors."""
+    from safetensors import safe_open
+
+    out = {}
+    with safe_open(path, framework="pt", device=str(device)) as f:
+        for k in f.keys():
+            if key_filter is not None and not key_filter(k):
+                continue
+            t = f.get_tensor(k)
+            if dtype is not None and t.is_floating_point():
+                t = t.to(dtype)
+            out[k] = t
+    return out
+
+
+def save_safetensors_sharded(state: dict[str, torch.Tensor], directory: str, max_shard_bytes: int = 5 << 30,
+                             prefix: str = "model") -> str:
+    """Write ``prefix-0000i-of-0000n.safetensors`` + ``prefix.safetensors.index.json``."""
+    os.makedirs(directory, exist_ok=True)
+    shards, cur, cur_bytes = [], {}, 0
+    for k, v in state.items():
+        nb = v.numel() * v.element_size()
+        if cur and cur_bytes + nb > max_shard_bytes:
+            shards.append(cur)
+            cur, cur_bytes = {}, 0
+        cur[k] = v
+        cur_bytes += nb
+    if cur:
+        shards.append(cur)
+    weight_map, total = {}, 0
+    for i, sh in enumerate(shards):
+        name = "%s-%05d-of-%05d.safetensors" % (prefix, i + 1, len(shards))
+        save_safetensors(sh, os.path.join(directory, name))
+        for k, v in sh.items():
+            weight_map[k] = name
+            total += v.numel() * v.element_size()
+    index = os.path.join(directory, prefix + ".safetensors.index.json")
+    with open(index, "w") as f:
+        json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=1)
+    return index
+
+
+def load_safetensors_sharded(index_path: str, device="cpu", dtype: torch.dtype | None = None,
+                             key_filter: Callable[[str], bool] | None = None,
+                             progress: Callable[[int, int], None] | None = None) -> dict[str, torch.Tensor]:
+    with open(index_path) as f:
+        index = json.load(f)
+    by_file: dict[str, list[str]] = {}
+    for k, fn in index["weight_map"].items():
+        if key_filter is None or key_filter(k):
+            by_file.setdefault(fn, []).append(k)
+    out, base = {}, os.path.dirname(index_path)
+    for i, (fn, keys) in enumerate(sorted(by_file.items())):
+        ks = set(keys)
+        out.update(load_safetensors(os.path.join(base, fn), device, dtype, lambda k: k in ks))
+        if progress is not None:
+            progress(i + 1, len(by_file))
+    return out
+
+
+# --------------------------------------------------------------------------- PyTorch .pt
+def load_pytorch_state_dict(path: str, device="cpu") -> dict[str, torch.Tensor]:
+    sd = torch.load(path, map_location=device, weights_only=True)
+    if isinstance(sd, dict) and "state_dict" in sd and isinstance(sd["state_dict"], dict):
+        sd = sd["state_dict"]
+    return {k: v for k, v in sd.items() if isinstance(v, torch.Tensor)}
+
+
+def save_pytorch(state: dict[str, torch.Tensor], path: str) -> None:
+    torch.save({k: v.detach().cpu() for k, v in state.items()}, path)
+
+
+# --------------------------------------------------------------------------- native state dict
+def _to_bytes(t: torch.Tensor) -> bytes:
+    t = t.detach().contiguous().cpu().reshape(-1)
+    return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+
+
+def dumps_state_dict(state: dict[str, torch.Tensor]) -> bytes:
+    header, blobs, off = [], [], 0
+    for k, v in state.items():
+        b = _to_bytes(v)
+        header.append(json.dumps({"name": k, "dtype": _DT_INV[v.dtype], "shape": list(v.shape), "offset": off,
+                                  "nbytes": len(b)}))
+        blobs.append(b)
+        off += len(b)
+    return ("\n".join(header)).encode() + b"\n---\n" + b"".join(blobs)
+
+
+def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
+    sep = buf.index(b"\n---\n")
+    body = memoryview(buf)[sep + 5:]
+    out = {}
+    for line in buf[:sep].decode().splitlines():
+        if not line.strip():
+            continue
+        e = json.loads(line)
+        raw = bytes(body[e["offset"]:e["offset"] + e["nbytes"]])
+        t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(_DT[e["dtype"]]) if raw else \
+            torch.empty(0, dtype=_DT[e["dtype"]])
+        out[e["name"]] = t.reshape(e["shape"]).to(device)
+    return out
+
+
+def save_state_dict(state: dict[str, torch.Tensor], path: str) -> None:
+    with open(path, "wb") as f:
+        f.write(dumps_state_dict(state))
+
+
+def load_state_dict(path: str, device="cpu") -> dict[str, torch.Tensor]:
+    with open(path, "rb") as f:
+        return loads_state_dict(f.read(), device)
+
+
+# --------------------------------------------------------------------------- training checkpoint
+MAGIC = b"FTCK1\n"
+
+
+def _flatten_opt(obj, prefix=""):
+    """Split an optimizer state into JSON-able scalars and a tensor dict."""
+    tensors, meta = {}, None
+    if isinstance(obj, torch.Tensor):
+        tensors[prefix] = obj
+        meta = {"__tensor__": prefix}
+    elif isinstance(obj, dict):
+        meta = {}
+        for k, v in obj.items():
+            t, m = _flatten_opt(v, "%s/%s" % (prefix, k) if prefix else str(k))
+            tensors.update(t)
+            meta[str(k)] = m
+    elif isinstance(obj, (list, tuple)):
+        meta = []
+        for i, v in enumerate(obj):
+            t, m = _flatten_opt(v, "%s/%d" % (prefix, i))
+            tensors.update(t)
+            meta.append(m)
+    else:
+        meta = obj
+    return tensors, meta
+
+
+def _unflatten_opt(meta, tensors):
+    if isinstance(meta, dict):
+        if "__tensor__" in meta and len(meta) == 1:
+            return tensors[meta["__tensor__"]]
+        return {(int(k) if k.lstrip("-").isdigit() else k): _unflatten_opt(v, tensors) for k, v in meta.items()}
+    if isinstance(meta, list):
+        return [_unflatten_opt(v, tensors) for v in meta]
+    return meta
+
+
+def save_checkpoint(path: str, model_state: dict[str, torch.Tensor], optimizer_state: dict | None = None,
+                    epoch: int = 0, step: int = 0, extra: dict | None = None) -> None:
+    """``TrainingCheckpoint`` (model + optimizer + epoch + step + extra such as scaler / RNG state)."""
+    opt_tensors, opt_meta = _flatten_opt(optimizer_state or {})
+    sections = [json.dumps({"epoch": epoch, "step": step, "extra": extra or {}}).encode(),
+                json.dumps(opt_meta).encode(),
+                dumps_state_dict({**{"model/" + k: v for k, v in model_state.items()},
+                                  **{"optim/" + k: v for k, v in opt_tensors.items()}})]
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        f.write(MAGIC)
+        for s in sections:
+            f.write(struct.pack("<Q", len(s)))
+            f.write(s)
+    os.replace(tmp, path)
+
+
+def load_checkpoint(path: str, device="cpu") -> dict:
+    with open(path, "rb") as f:
+        if f.read(len(MAGIC)) != MAGIC:
+            raise ValueError("%s is not a ferrotorch_b200 checkpoint" % path)
+        secs = []
+        for _ in range(3):
+            (n,) = struct.unpack("<Q", f.read(8))
+            secs.append(f.read(n))
+    meta, opt_meta = json.loads(secs[0]), json.loads(secs[1])
+    tensors = loads_state_dict(secs[2], device)
+    model = {k[6:]: v for k, v in tensors.items() if k.startswith("model/")}
+    opt_t = {k[6:]: v for k, v in tensors.items() if k.startswith("optim/")}
+    return {"model": model, "optimizer": _unflatten_opt(opt_meta, opt_t), "epoch": meta["epoch"],
+            "step": meta["step"], "extra": meta["extra"]}
+
+
+class CheckpointFuture:
+    def __init__(self, thread: threading.Thread, box: list):
+        self._t, self._box = thread, box
+
+    def is_done(self) -> bool:
+        return not self._t.is_alive()
+
+    def wait(self) -> None:
+        self._t.join()
+        if self._box:
+            raise self._box[0]
+
+
+class AsyncCheckpointer:
+    """Snapshot tensors to (pinned) host memory on the caller's thread, write the file on a
+    background thread (checkpoint.rs:575; distributed variant checkpoint.rs:686-910)."""
+
+    def __init__(self):
+        self._last: CheckpointFuture | None = None
+
+    def save_async(self, path: str, model_state: dict, optimizer_state: dict | None = None, **kw) -> CheckpointFuture:
+        if self._last is not None:
+            self._last.wait()
+
+        def snap(o):
+            if isinstance(o, torch.Tensor):
+                h = torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=o.is_cuda)
+                h.copy_(o.detach(), non_blocking=o.is_cuda)
+                return h
+            if isinstance(o, dict):
+                return {k: snap(v) for k, v in o.items()}
+            if isinstance(o, (list, tuple)):
+                return [snap(v) for v in o]
+            return o
+
+        m, opt = snap(model_state), snap(optimizer_state)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        box: list = []
+
+        def work():
+            try:
+                save_checkpoint(path, m, opt, **kw)
+            except BaseException as e:  # noqa: BLE001
+                box.append(e)
+
+        t = threading.Thread(target=work, daemon=True)
+        t.start()
+        self._last = CheckpointFuture(t, box)
+        return self._last

@@ -1,0 +1,174 @@
+"""Checkpoint formats round-trip on CPU: SafeTensors (single, sharded, filtered), .pt, native
+state dict, training checkpoint (sync + async), GGUF (all block types vs a NumPy restatement),
+Llama HF key layout."""
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from ferrotorch_b200 import serialize as S
+from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+from ferrotorch_b200.ops import reference as R
+
+
+def _state():
+    torch.manual_seed(0)
+    return {"a.weight": torch.randn(5, 7), "b": torch.randn(3).to(torch.bfloat16), "c": torch.arange(6).view(2, 3),
+            "empty": torch.zeros(0)}
+
+
+def _same(x, y):
+    assert x.keys() == y.keys()
+    for k in x:
+        assert x[k].dtype == y[k].dtype and x[k].shape == y[k].shape and torch.equal(x[k], y[k]), k
+
+
+def test_safetensors_single_sharded_filtered(tmp_path):
+    sd = _state()
+    p = str(tmp_path / "m.safetensors")
+    S.save_safetensors(sd, p)
+    _same(S.load_safetensors(p), sd)
+    assert set(S.load_safetensors(p, key_filter=lambda k: k.startswith("a"))) == {"a.weight"}
+    assert S.load_safetensors(p, dtype=torch.bfloat16)["a.weight"].dtype == torch.bfloat16
+    idx = S.save_safetensors_sharded(sd, str(tmp_path / "sh"), max_shard_bytes=64)
+    seen = []
+    _same(S.load_safetensors_sharded(idx, progress=lambda i, n: seen.append((i, n))), sd)
+    assert seen and seen[-1][0] == seen[-1][1] > 1
+
+
+def test_pt_and_native_state_dict(tmp_path):
+    sd = _state()
+    S.save_pytorch(sd, str(tmp_path / "m.pt"))
+    _same(S.load_pytorch_state_dict(str(tmp_path / "m.pt")), sd)
+    torch.save({"state_dict": sd, "epoch": 3}, str(tmp_path / "wrapped.pt"))
+    _same(S.load_pytorch_state_dict(str(tmp_path / "wrapped.pt")), sd)
+    _same(S.loads_state_dict(S.dumps_state_dict(sd)), sd)
+    S.save_state_dict(sd, str(tmp_path / "m.ftsd"))
+    _same(S.load_state_dict(str(tmp_path / "m.ftsd")), sd)
+
+
+def test_training_checkpoint_sync_and_async(tmp_path):
+    model = torch.nn.Linear(4, 3)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    model(torch.randn(2, 4)).sum().backward()
+    opt.step()
+    p = str(tmp_path / "ck.ftc")
+    S.save_checkpoint(p, model.state_dict(), opt.state_dict(), epoch=2, step=17, extra={"scaler": {"scale": 65536.0}})
+    ck = S.load_checkpoint(p)
+    assert ck["epoch"] == 2 and ck["step"] == 17 and ck["extra"]["scaler"]["scale"] == 65536.0
+    _same(ck["model"], dict(model.state_dict()))
+    opt2 = torch.optim.AdamW(torch.nn.Linear(4, 3).parameters(), lr=1e-2)
+    opt2.load_state_dict(ck["optimizer"])
+    assert torch.equal(opt2.state_dict()["state"][0]["exp_avg"], opt.state_dict()["state"][0]["exp_avg"])
+    fut = S.AsyncCheckpointer().save_async(str(tmp_path / "a.ftc"), model.state_dict(), opt.state_dict(), epoch=1)
+    fut.wait()
+    assert fut.is_done() and S.load_checkpoint(str(tmp_path / "a.ftc"))["epoch"] == 1
+    with open(str(tmp_path / "bad"), "wb") as f:
+        f.write(b"nope")
+    with pytest.raises(ValueError):
+        S.load_checkpoint(str(tmp_path / "bad"))
+
+
+def _np_dequant(t, raw, n):
+    b = np.frombuffer(raw, dtype=np.uint8)
+    if t == S.gguf.GGML_F32:
+        return b.view(np.float32).copy()
+    if t == S.gguf.GGML_F16:
+        return b.view(np.float16).astype(np.float32)
+    be, bb = S.gguf._BLOCK[t]
+    blk = b.reshape(-1, bb)
+    d = blk[:, :2].copy().view(np.float16).astype(np.float32)
+    out = np.zeros((blk.shape[0], 32), np.float32)
+    if t in (S.gguf.GGML_Q4_0, S.gguf.GGML_Q4_1):
+        o = 2 if t == S.gguf.GGML_Q4_0 else 4
+        m = 0 if t == S.gguf.GGML_Q4_0 else blk[:, 2:4].copy().view(np.float16).astype(np.float32)
+        lo, hi = (blk[:, o:o + 16] & 15).astype(np.float32), (blk[:, o:o + 16] >> 4).astype(np.float32)
+        q = np.concatenate([lo, hi], 1)
+        out = (q - 8) * d if t == S.gguf.GGML_Q4_0 else q * d + m
+    elif t in (S.gguf.GGML_Q5_0, S.gguf.GGML_Q5_1):
+        o = 2 if t == S.gguf.GGML_Q5_0 else 4
+        m = 0 if t == S.gguf.GGML_Q5_0 else blk[:, 2:4].copy().view(np.float16).astype(np.float32)
+        qh = blk[:, o:o + 4].copy().view(np.uint32)
+        qs = blk[:, o + 4:o + 20]
+        j = np.arange(16, dtype=np.uint32)
+        h0 = (((qh >> j) << 4) & 0x10).astype(np.uint8)
+        h1 = ((qh >> (j + 12)) & 0x10).astype(np.uint8)
+        q = np.concatenate([(qs & 15) | h0, (qs >> 4) | h1], 1).astype(np.float32)
+        out = (q - 16) * d if t == S.gguf.GGML_Q5_0 else q * d + m
+    else:
+        o = 2 if t == S.gguf.GGML_Q8_0 else 4
+        out = blk[:, o:o + 32].copy().view(np.int8).astype(np.float32) * d
+    return out.reshape(-1)[:n]
+
+
+def test_gguf_reader_all_block_types(tmp_path):
+    rng = np.random.default_rng(0)
+    tensors, want = {}, {}
+    for t, (be, bb) in S.gguf._BLOCK.items():
+        if t == S.gguf.GGML_BF16:
+            continue
+        shape = (4, 64)
+        n = 4 * 64
+        raw = rng.integers(0, 256, n // be * bb, dtype=np.uint8)
+        if be == 32:  # keep the fp16 scale fields finite
+            blk = raw.reshape(-1, bb)
+            blk[:, :2] = np.array([0.5], np.float16).view(np.uint8)
+            if t in (S.gguf.GGML_Q4_1, S.gguf.GGML_Q5_1, S.gguf.GGML_Q8_1):
+                blk[:, 2:4] = np.array([-1.25], np.float16).view(np.uint8)
+        elif t == S.gguf.GGML_F16:
+            raw = rng.standard_normal(n).astype(np.float16).view(np.uint8)
+        else:
+            raw = rng.standard_normal(n).astype(np.float32).view(np.uint8)
+        tensors["t%d.weight" % t] = (t, shape, raw.tobytes())
+        want["t%d.weight" % t] = _np_dequant(t, raw.tobytes(), n).reshape(shape)
+    p = str(tmp_path / "x.gguf")
+    S.write_gguf(p, tensors, {"general.architecture": "llama", "llama.block_count": 2, "x.f": 1.5, "x.b": True})
+    with S.GgufFile(p) as f:
+        assert f.version == 3 and f.metadata["general.architecture"] == "llama" and f.metadata["llama.block_count"] == 2
+        for name, w in want.items():
+            got = f.dequantize(name).numpy()
+            assert got.shape == w.shape and np.array_equal(got, w), name
+    with open(str(tmp_path / "bad.gguf"), "wb") as fh:
+        fh.write(b"GGUF" + struct.pack("<I", 99) + b"\0" * 32)
+    with pytest.raises(ValueError):
+        S.GgufFile(str(tmp_path / "bad.gguf"))
+
+
+def test_q4_0_quantise_roundtrip_and_key_map(tmp_path):
+    torch.manual_seed(1)
+    w = torch.randn(8, 128)
+    blocks = S.quantize_q4_0(w)
+    deq = R.dequant_q4_0(blocks).view(8, 128)
+    assert (deq - w).abs().max() < w.abs().max() / 7
+    p = str(tmp_path / "q.gguf")
+    S.write_gguf(p, {"blk.0.attn_q.weight": (S.gguf.GGML_Q4_0, (8, 128), blocks.numpy().tobytes()),
+                     "token_embd.weight": (S.gguf.GGML_F32, (4, 8), torch.ones(4, 8).numpy().tobytes())})
+    sd = S.load_gguf_state_dict(p, dtype=torch.float32)
+    assert set(sd) == {"model.layers.0.self_attn.q_proj.weight", "model.embed_tokens.weight"}
+    assert torch.equal(sd["model.layers.0.self_attn.q_proj.weight"], deq)
+    with S.GgufFile(p) as f:
+        scales, nib = f.q4_0_planes("blk.0.attn_q.weight")
+    assert scales.shape == (8, 4) and nib.shape == (8, 64)
+    lo, hi = (nib.view(8, 4, 16) & 15).float() - 8, (nib.view(8, 4, 16) >> 4).float() - 8
+    assert torch.equal((torch.cat([lo, hi], -1) * scales.float()[..., None]).view(8, 128), deq)
+    assert S.gguf_key_to_hf("output.weight") == "lm_head.weight" and S.gguf_key_to_hf("rope_freqs.weight") is None
+
+
+def test_llama_hf_state_dict_roundtrip_through_safetensors(tmp_path):
+    cfg = LlamaConfig.tiny()
+    cfg.num_hidden_layers = 1
+    torch.manual_seed(2)
+    m = LlamaForCausalLM(cfg)
+    sd = m.hf_state_dict()
+    assert "model.layers.0.self_attn.k_proj.weight" in sd and "model.layers.0.mlp.up_proj.weight" in sd
+    S.save_safetensors(sd, str(tmp_path / "llama.safetensors"))
+    m2 = LlamaForCausalLM(cfg)
+    m2.load_hf_state_dict(S.load_safetensors(str(tmp_path / "llama.safetensors")))
+    x = torch.randint(0, cfg.vocab_size, (1, 9))
+    assert torch.equal(m(x), m2(x))
+    bad = dict(sd)
+    del bad["model.layers.0.self_attn.v_proj.weight"]
+    with pytest.raises(KeyError):
+        m2.load_hf_state_dict(bad)
