@@ -1,0 +1,170 @@
+"""Mesh / DTensor / pipeline / FSDP / SyncBatchNorm on simulated CPU ranks, and the optimizers."""
+import copy
+
+import pytest
+import torch
+from torch import nn
+
+from ferrotorch_b200 import optim as O
+from ferrotorch_b200.parallel import (DDP, FSDP, DeviceMesh, DTensor, InvalidRank, Partial, Pipeline, Replicate, Shard,
+                                      ShardingStrategy, SyncBatchNorm2d, run_simulated)
+
+
+def test_device_mesh_maps():
+    m = DeviceMesh((2, 4), ("dp", "tp"))
+    assert m.size == 8 and m.coords(5) == (1, 1) and m.rank_of((1, 1)) == 5
+    assert m.ranks_along_dim(5, "tp") == [4, 5, 6, 7] and m.ranks_along_dim(5, "dp") == [1, 5]
+    assert m.groups_along_dim("dp") == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    with pytest.raises(InvalidRank):
+        m.coords(8)
+    with pytest.raises(InvalidRank):
+        m.rank_of((2, 0))
+
+
+def test_dtensor_redistribute_moves_data():
+    full = torch.arange(24, dtype=torch.float32).view(4, 6)
+
+    def body(g):
+        d = DTensor.from_global(full, g, Shard(0))
+        assert d.local.shape == (2, 6)
+        rep = d.redistribute(Replicate())
+        col = d.redistribute(Shard(1))
+        part = DTensor(torch.full((2, 2), float(g.rank + 1)), g, Partial("sum"))
+        return rep.local, col.local, part.redistribute(Replicate()).local, part.redistribute(Shard(0)).local, \
+            rep.redistribute(Shard(0)).local
+
+    res = run_simulated(2, body)
+    for r, (rep, col, ar, rs, back) in enumerate(res):
+        assert torch.equal(rep, full) and torch.equal(col, full[:, r * 3:(r + 1) * 3])
+        assert torch.equal(ar, torch.full((2, 2), 3.0)) and torch.equal(rs, torch.full((1, 2), 3.0))
+        assert torch.equal(back, full[r * 2:(r + 1) * 2])
+
+
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+def test_pipeline_matches_single_process(schedule):
+    torch.manual_seed(0)
+    stages = [nn.Sequential(nn.Linear(6, 8), nn.Tanh()), nn.Sequential(nn.Linear(8, 8), nn.Tanh()), nn.Linear(8, 3)]
+    x, y = torch.randn(8, 6), torch.randn(8, 3)
+    ref = copy.deepcopy(nn.Sequential(*stages))
+    loss_ref = nn.functional.mse_loss(ref(x), y)
+    loss_ref.backward()
+
+    def body(g):
+        m = copy.deepcopy(stages[g.rank])
+        p = Pipeline(m, g, n_micro=4, schedule=schedule, loss_fn=nn.functional.mse_loss)
+        loss = p.train_step(x if g.rank == 0 else None, y if g.rank == 2 else None)
+        return loss, [q.grad.clone() for q in m.parameters()]
+
+    res = run_simulated(3, body)
+    assert abs(float(res[2][0]) - float(loss_ref)) < 1e-6
+    for s in range(3):
+        for got, want in zip(res[s][1], [q.grad for q in ref[s].parameters()]):
+            assert torch.allclose(got, want, atol=1e-6), "stage %d input gradients must be real, not zeros" % s
+
+
+@pytest.mark.parametrize("strategy,intra", [(ShardingStrategy.FULL_SHARD, None), (ShardingStrategy.SHARD_GRAD_OP, None),
+                                            (ShardingStrategy.NO_SHARD, None), (ShardingStrategy.HYBRID_SHARD, 2)])
+def test_fsdp_matches_ddp(strategy, intra):
+    torch.manual_seed(1)
+    base = nn.Sequential(nn.Linear(5, 7), nn.ReLU(), nn.Linear(7, 3))
+    xs = torch.randn(4, 6, 5)
+
+    def run(g, use_fsdp):
+        m = copy.deepcopy(base)
+        if use_fsdp:
+            w = FSDP(m, g, strategy, intra_node_size=intra)
+            opt = torch.optim.SGD(w.shard_parameters(), lr=0.1)
+        else:
+            w = DDP(m, g)
+            opt = torch.optim.SGD(m.parameters(), lr=0.1)
+        for _ in range(2):
+            opt.zero_grad()
+            w(xs[g.rank]).pow(2).mean().backward()
+            w.sync_gradients()
+            opt.step()
+        return w.full_state_dict() if use_fsdp else {k: v.clone() for k, v in m.state_dict().items()}
+
+    a, b = run_simulated(4, run, True), run_simulated(4, run, False)
+    for r in range(4):
+        for k in b[0]:
+            assert torch.allclose(a[r][k], b[0][k], atol=1e-6), (strategy, k)
+
+
+def test_sync_batch_norm_equals_big_batch():
+    torch.manual_seed(2)
+    x = torch.randn(8, 3, 4, 4)
+    bn = nn.BatchNorm2d(3)
+    xr = x.clone().requires_grad_()
+    want = bn(xr)
+    want.square().sum().backward()
+
+    def body(g):
+        m = SyncBatchNorm2d(3, g)
+        xi = x[g.rank * 4:(g.rank + 1) * 4].clone().requires_grad_()
+        out = m(xi)
+        out.square().sum().backward()
+        return out.detach(), xi.grad, m.running_mean.clone(), m.running_var.clone(), m.weight.grad
+
+    res = run_simulated(2, body)
+    out = torch.cat([r[0] for r in res])
+    assert torch.allclose(out, want.detach(), atol=1e-5)
+    assert torch.allclose(torch.cat([r[1] for r in res]), xr.grad, atol=1e-4)
+    assert torch.allclose(res[0][2], bn.running_mean, atol=1e-6) and torch.allclose(res[0][3], bn.running_var, atol=1e-5)
+    assert torch.allclose(res[0][4] + res[1][4], bn.weight.grad, atol=1e-4)
+
+
+def test_fused_optimizers_match_torch_on_cpu():
+    torch.manual_seed(3)
+    for ours, theirs in [(lambda p: O.FusedAdamW(p, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1),
+                          lambda p: torch.optim.AdamW(p, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)),
+                         (lambda p: O.FusedSGD(p, lr=0.1, momentum=0.9, weight_decay=1e-4, nesterov=True),
+                          lambda p: torch.optim.SGD(p, lr=0.1, momentum=0.9, weight_decay=1e-4, nesterov=True))]:
+        a = nn.Sequential(nn.Linear(4, 5), nn.Linear(5, 2))
+        b = copy.deepcopy(a)
+        oa, ob = ours(a.parameters()), theirs(b.parameters())
+        for _ in range(3):
+            x = torch.randn(6, 4)
+            for m, o in ((a, oa), (b, ob)):
+                o.zero_grad()
+                m(x).square().mean().backward()
+                o.step()
+        for p, q in zip(a.parameters(), b.parameters()):
+            assert torch.allclose(p, q, atol=1e-6)
+        sd = oa.state_dict()
+        oa.load_state_dict(sd)
+
+
+def test_extra_optimizers_and_schedules_reduce_loss():
+    torch.manual_seed(4)
+    x, y = torch.randn(64, 8), torch.randn(64, 1)
+    for make in (lambda p: O.Muon(p, lr=0.02), lambda p: O.Adafactor(p, lr=1e-2), lambda p: O.NaturalGradient(p, lr=1e-2)):
+        m = nn.Sequential(nn.Linear(8, 16), nn.Tanh(), nn.Linear(16, 1))
+        opt = make(m.parameters())
+        first = None
+        for _ in range(60):
+            opt.zero_grad()
+            loss = nn.functional.mse_loss(m(x), y)
+            loss.backward()
+            opt.step()
+            first = first if first is not None else float(loss)
+        assert float(loss) < first
+    m = nn.Linear(2, 2)
+    opt = torch.optim.SGD(m.parameters(), lr=1.0)
+    sch = O.cosine_warmup_scheduler(opt, warmup_steps=2, total_steps=6, min_ratio=0.1)
+    lrs = []
+    for _ in range(7):
+        lrs.append(opt.param_groups[0]["lr"])
+        opt.step()
+        sch.step()
+    assert lrs[0] == 0.0 and lrs[2] == 1.0 and abs(lrs[6] - 0.1) < 1e-6 and lrs[3] > lrs[4] > lrs[5]
+    ema = O.EMA(m, decay=0.5)
+    with torch.no_grad():
+        m.weight.add_(2.0)
+    ema.update()
+    ema.apply()
+    applied = m.weight.detach().clone()
+    ema.restore()
+    assert torch.allclose(applied + 1.0, m.weight)
+    acc = O.GradientAccumulator(3)
+    assert [acc.backward(m(torch.ones(1, 2)).sum()) for _ in range(3)] == [False, False, True]
+    assert O.StepLR is torch.optim.lr_scheduler.StepLR and O.GradScaler is not None
