@@ -123,6 +123,7 @@ _KERNEL_PROTOS = {
     "ft_last_error": (ctypes.c_char_p, []),
     "ft_read_device_status": (_i, [_i]),
     "ft_abi_version": (_i, []),
+    "ft_count_external_launch": (None, [_i]),
     "ft_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _vp]),
     "ft_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "ft_rmsnorm_bwd_scratch_rows": (_i, [_i, _i]),

@@ -1,0 +1,21 @@
+"""Trace-and-fuse JIT: ``trace`` / ``compile`` -> IR -> passes -> generated sm_100a kernels."""
+from .codegen import compile_cubin, generate_source, run_fused, run_program_torch  # noqa: F401
+from .ir import (IrGraph, Node, OptimizationConfig, constant_fold, dead_code_eliminate, fuse_elementwise,  # noqa: F401
+                 optimize, pattern_fuse, plan_memory)
+from .module import (Autotuner, CompileConfig, EagerFallback, JitError, TracedModule, apply_fused, compile,  # noqa: F401
+                     trace, with_fusion)
+
+
+def script(fn):
+    """Decorator form (the reference's ``#[script]`` proc-macro, ferrotorch-jit-script/src/lib.rs):
+    compiles on first call with that call's arguments as the example inputs."""
+    cache = {}
+
+    def wrapper(*args):
+        key = tuple((tuple(a.shape), a.dtype) if hasattr(a, "shape") else a for a in args)
+        if key not in cache:
+            cache[key] = compile(fn, args)
+        return cache[key](*args)
+
+    wrapper.__wrapped__ = fn
+    return wrapper

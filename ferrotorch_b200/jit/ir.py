@@ -1,0 +1,260 @@
+"""Graph IR of the JIT and its optimisation passes.
+
+Mirrors the reference's ``IrGraph`` / ``IrOpKind`` (ferrotorch-jit/src/graph.rs:37-172, including
+``FusedElementwise{ops}``, ``FusedLinearActivation{activation}`` and ``FusedAttention``) and its
+pass pipeline ``constant_fold -> dead_code_eliminate -> fuse_elementwise -> pattern_fuse ->
+plan_memory`` (optimize.rs:61, 230, 352, 405, 523; memory_plan.rs).  The fusible op set is the
+reference's ``FusedOp`` list (fusion.rs:112-135) plus broadcasting binary inputs.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+
+import torch
+
+UNARY = ("neg", "relu", "sigmoid", "tanh", "gelu", "silu", "sqrt", "abs", "exp", "log")
+BINARY = ("add", "sub", "mul", "div")
+SCALAR = ("add_c", "mul_c", "pow_c", "rsub_c", "rdiv_c")  # c on the right: x+c, x*c, x**c, c-x, c/x
+ELEMENTWISE = UNARY + BINARY + SCALAR
+
+
+@dataclass
+class Node:
+    id: int
+    op: str                      # input | const | call | fused_elementwise | fused_linear_act | fused_attention | <elementwise>
+    inputs: list[int] = field(default_factory=list)
+    attrs: dict = field(default_factory=dict)
+    shape: tuple | None = None
+    dtype: torch.dtype | None = None
+
+
+class IrGraph:
+    def __init__(self):
+        self.nodes: dict[int, Node] = {}
+        self.order: list[int] = []
+        self.outputs: list[int] = []
+        self.output_spec = None      # how to rebuild the python return value
+        self._next = 0
+
+    def add(self, op: str, inputs=(), **attrs) -> Node:
+        n = Node(self._next, op, list(inputs), attrs)
+        self._next += 1
+        self.nodes[n.id] = n
+        self.order.append(n.id)
+        return n
+
+    def users(self) -> dict[int, list[int]]:
+        u: dict[int, list[int]] = {i: [] for i in self.nodes}
+        for i in self.order:
+            for j in self.nodes[i].inputs:
+                u[j].append(i)
+        return u
+
+    def count(self, op: str) -> int:
+        return sum(1 for i in self.order if self.nodes[i].op == op)
+
+    def ops(self) -> list[str]:
+        return [self.nodes[i].op for i in self.order]
+
+    # ---- serialisation (the reference has a binary IR format; structure only, constants and
+    # opaque call targets are referenced by name)
+    def to_json(self) -> str:
+        def enc(v):
+            if isinstance(v, torch.Tensor):
+                return {"__tensor__": list(v.shape), "dtype": str(v.dtype)}
+            if isinstance(v, (int, float, str, bool, type(None))):
+                return v
+            if isinstance(v, (list, tuple)):
+                return [enc(x) for x in v]
+            if isinstance(v, dict):
+                return {str(k): enc(x) for k, x in v.items()}
+            return {"__opaque__": getattr(v, "__name__", type(v).__name__)}
+
+        return json.dumps({"nodes": [{"id": n.id, "op": n.op, "inputs": n.inputs, "attrs": enc(n.attrs),
+                                      "shape": list(n.shape) if n.shape is not None else None,
+                                      "dtype": str(n.dtype) if n.dtype is not None else None}
+                                     for n in (self.nodes[i] for i in self.order)], "outputs": self.outputs})
+
+
+# --------------------------------------------------------------------------- passes
+def constant_fold(g: IrGraph) -> int:
+    """Evaluate elementwise nodes whose inputs are all constants."""
+    from .codegen import eval_elementwise
+
+    folded = 0
+    for i in list(g.order):
+        n = g.nodes[i]
+        if n.op in ELEMENTWISE and n.inputs and all(g.nodes[j].op == "const" for j in n.inputs):
+            val = eval_elementwise(n.op, [g.nodes[j].attrs["value"] for j in n.inputs], n.attrs.get("c"))
+            n.op, n.inputs, n.attrs = "const", [], {"value": val}
+            folded += 1
+    return folded
+
+
+def dead_code_eliminate(g: IrGraph) -> int:
+    live, stack = set(), list(g.outputs)
+    while stack:
+        i = stack.pop()
+        if i not in live:
+            live.add(i)
+            stack.extend(g.nodes[i].inputs)
+    dead = [i for i in g.order if i not in live and g.nodes[i].op != "input"]
+    for i in dead:
+        del g.nodes[i]
+    g.order = [i for i in g.order if i in g.nodes]
+    return len(dead)
+
+
+def fuse_elementwise(g: IrGraph) -> int:
+    """Merge connected elementwise nodes into ``fused_elementwise`` nodes.  A producer joins its
+    consumer's group when the consumer is its only user and both produce the same shape."""
+    users = g.users()
+    group_of: dict[int, int] = {}
+    groups: dict[int, list[int]] = {}
+    for i in g.order:
+        n = g.nodes[i]
+        if n.op not in ELEMENTWISE or n.shape is None:
+            continue
+        gid = None
+        for j in n.inputs:
+            p = g.nodes[j]
+            if j in group_of and len(users[j]) == 1 and j not in g.outputs and p.shape == n.shape:
+                if gid is None:
+                    gid = group_of[j]
+                elif group_of[j] != gid:          # merge two groups feeding one node
+                    old = group_of[j]
+                    for k in groups.pop(old):
+                        group_of[k] = gid
+                        groups[gid].append(k)
+        if gid is None:
+            gid = i
+            groups[gid] = []
+        groups[gid].append(i)
+        group_of[i] = gid
+    made = 0
+    for gid, members in groups.items():
+        if len(members) < 2:
+            continue
+        members = [i for i in g.order if i in set(members)]
+        mset, ext, program = set(members), [], []
+        reg = {}
+        for i in members:
+            n = g.nodes[i]
+            srcs = []
+            for j in n.inputs:
+                if j in mset:
+                    srcs.append(("r", reg[j]))
+                else:
+                    if j not in ext:
+                        ext.append(j)
+                    srcs.append(("x", ext.index(j)))
+            reg[i] = len(program)
+            program.append({"op": n.op, "src": srcs, "c": n.attrs.get("c")})
+        last = members[-1]
+        fused = g.nodes[last]
+        fused.op, fused.inputs, fused.attrs = "fused_elementwise", ext, {"program": program}
+        for i in members[:-1]:
+            del g.nodes[i]
+        g.order = [i for i in g.order if i in g.nodes]
+        made += 1
+    return made
+
+
+def pattern_fuse(g: IrGraph) -> int:
+    """Linear + {relu, gelu, silu, sigmoid, tanh} -> ``fused_linear_act``; ``softmax(q k^T * s) v``
+    -> ``fused_attention`` (optimize.rs:523-601)."""
+    users, made = g.users(), 0
+    for i in list(g.order):
+        n = g.nodes.get(i)
+        if n is None or n.op not in ("relu", "gelu", "silu", "sigmoid", "tanh") or len(n.inputs) != 1:
+            continue
+        p = g.nodes[n.inputs[0]]
+        if p.op == "call" and p.attrs.get("kind") == "linear" and len(users[p.id]) == 1 and p.id not in g.outputs:
+            n.attrs = {"activation": n.op, "kind": "linear", "module": p.attrs.get("module", p.attrs.get("target"))}
+            n.op, n.inputs = "fused_linear_act", list(p.inputs)
+            del g.nodes[p.id]
+            made += 1
+    g.order = [i for i in g.order if i in g.nodes]
+    users = g.users()
+    for i in list(g.order):
+        n = g.nodes.get(i)
+        if n is None or n.op != "call" or n.attrs.get("kind") != "matmul":
+            continue
+        sm = g.nodes.get(n.inputs[0])
+        if sm is None or sm.op != "call" or sm.attrs.get("kind") != "softmax" or len(users[sm.id]) != 1:
+            continue
+        sc = g.nodes[sm.inputs[0]]
+        scale = 1.0
+        if sc.op == "mul_c" and len(users[sc.id]) == 1:
+            scale, sc_in = sc.attrs["c"], g.nodes[sc.inputs[0]]
+        else:
+            sc_in = sc
+        if sc_in.op != "call" or sc_in.attrs.get("kind") != "matmul" or len(users[sc_in.id]) != 1:
+            continue
+        kt = g.nodes[sc_in.inputs[1]]
+        if kt.op != "call" or kt.attrs.get("kind") != "transpose_last":
+            continue
+        q, k, v = sc_in.inputs[0], kt.inputs[0], n.inputs[1]
+        for d in {sm.id, sc.id, sc_in.id, kt.id} - {n.id}:
+            if d in g.nodes and not [u for u in users[d] if u in g.nodes and u not in (sm.id, sc.id, sc_in.id, n.id)]:
+                del g.nodes[d]
+        n.op, n.inputs, n.attrs = "fused_attention", [q, k, v], {"scale": scale}
+        made += 1
+    g.order = [i for i in g.order if i in g.nodes]
+    return made
+
+
+def plan_memory(g: IrGraph) -> dict:
+    """Liveness-based buffer assignment: every node output gets a slot, a slot is reused once its
+    last user has run.  Returns ``{"slot_of": {node: slot}, "n_slots": k, "peak_bytes": b}``."""
+    last_use = {}
+    for pos, i in enumerate(g.order):
+        for j in g.nodes[i].inputs:
+            last_use[j] = pos
+    for o in g.outputs:
+        last_use[o] = len(g.order)
+    free, slot_of, sizes, n_slots, peak, live_bytes = [], {}, {}, 0, 0, 0
+    for pos, i in enumerate(g.order):
+        n = g.nodes[i]
+        if n.op in ("input", "const") or n.shape is None:
+            continue
+        nbytes = int(torch.tensor(n.shape).prod()) * (torch.empty(0, dtype=n.dtype).element_size() if n.dtype else 4)
+        s = free.pop() if free else n_slots
+        if s == n_slots:
+            n_slots += 1
+        slot_of[i], sizes[i] = s, nbytes
+        live_bytes += nbytes
+        peak = max(peak, live_bytes)
+        for j in set(n.inputs):
+            if last_use.get(j) == pos and j in slot_of:
+                free.append(slot_of[j])
+                live_bytes -= sizes[j]
+    return {"slot_of": slot_of, "n_slots": n_slots, "peak_bytes": peak}
+
+
+@dataclass
+class OptimizationConfig:
+    constant_folding: bool = True
+    dead_code_elimination: bool = True
+    elementwise_fusion: bool = True
+    pattern_fusion: bool = True
+    memory_planning: bool = True
+
+
+def optimize(g: IrGraph, cfg: OptimizationConfig | None = None) -> dict:
+    cfg = cfg or OptimizationConfig()
+    stats = {}
+    if cfg.constant_folding:
+        stats["folded"] = constant_fold(g)
+    if cfg.dead_code_elimination:
+        stats["dead"] = dead_code_eliminate(g)
+    if cfg.pattern_fusion:
+        stats["patterns"] = pattern_fuse(g)
+    if cfg.elementwise_fusion:
+        stats["fused_groups"] = fuse_elementwise(g)
+    if cfg.dead_code_elimination:
+        stats["dead"] = stats.get("dead", 0) + dead_code_eliminate(g)
+    if cfg.memory_planning:
+        stats["memory"] = plan_memory(g)
+    return stats

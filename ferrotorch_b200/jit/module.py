@@ -1,0 +1,284 @@
+"""``trace`` / ``compile``: torch.fx capture -> IR -> passes -> interpreter with fused kernels.
+
+Reference surface: ``trace`` (ferrotorch-jit/src/trace.rs:297), ``compile`` -> ``TracedModule``
+(module.rs:103-281), ``CompileConfig`` (module.rs:43), graph breaks that fall back to eager
+(graph_break.rs), shape guards (symbolic.rs), ``Autotuner`` (autotune.rs), ``with_fusion``
+(fusion.rs:86), ``export`` / IR serialisation.  The reference traces by walking ``grad_fn``s
+after an eager run; here ``torch.fx`` symbolic tracing produces the graph and one eager run on
+the example inputs supplies shapes and dtypes.
+"""
+from __future__ import annotations
+
+import contextlib
+import operator
+from dataclasses import dataclass, field
+
+import torch
+import torch.fx
+from torch import nn
+
+from . import codegen
+from .ir import BINARY, ELEMENTWISE, IrGraph, OptimizationConfig, optimize
+
+
+class JitError(RuntimeError):
+    pass
+
+
+@dataclass
+class CompileConfig:
+    optimization: OptimizationConfig = field(default_factory=OptimizationConfig)
+    fallback_to_eager: bool = True      # on an untraceable callable or a failed guard
+    block_size: int = 256
+
+
+_FN_UNARY = {torch.relu: "relu", nn.functional.relu: "relu", torch.sigmoid: "sigmoid", nn.functional.sigmoid: "sigmoid",
+             torch.tanh: "tanh", nn.functional.tanh: "tanh", nn.functional.gelu: "gelu", nn.functional.silu: "silu",
+             torch.sqrt: "sqrt", torch.abs: "abs", torch.exp: "exp", torch.log: "log", torch.neg: "neg",
+             operator.neg: "neg", operator.abs: "abs"}
+_FN_BINARY = {operator.add: "add", torch.add: "add", operator.sub: "sub", torch.sub: "sub", operator.mul: "mul",
+              torch.mul: "mul", operator.truediv: "div", torch.div: "div", torch.true_divide: "div"}
+_MOD_UNARY = {nn.ReLU: "relu", nn.Sigmoid: "sigmoid", nn.Tanh: "tanh", nn.GELU: "gelu", nn.SiLU: "silu"}
+_METHOD = {"relu": "relu", "sigmoid": "sigmoid", "tanh": "tanh", "sqrt": "sqrt", "abs": "abs", "exp": "exp",
+           "log": "log", "neg": "neg", "add": "add", "sub": "sub", "mul": "mul", "div": "div"}
+_SCALAR_OF = {"add": "add_c", "mul": "mul_c", "sub": None, "div": None}
+
+
+def _is_num(x) -> bool:
+    return isinstance(x, (int, float)) and not isinstance(x, bool)
+
+
+def _lower_binary(g: IrGraph, op: str, a, b):
+    """Tensor-tensor or tensor-scalar binary op -> IR node."""
+    if _is_num(b) and not _is_num(a):
+        if op == "add":
+            return g.add("add_c", [a.id], c=float(b))
+        if op == "sub":
+            return g.add("add_c", [a.id], c=-float(b))
+        if op == "mul":
+            return g.add("mul_c", [a.id], c=float(b))
+        return g.add("mul_c", [a.id], c=1.0 / float(b))
+    if _is_num(a) and not _is_num(b):
+        if op == "add":
+            return g.add("add_c", [b.id], c=float(a))
+        if op == "mul":
+            return g.add("mul_c", [b.id], c=float(a))
+        if op == "sub":
+            return g.add("rsub_c", [b.id], c=float(a))
+        return g.add("rdiv_c", [b.id], c=float(a))
+    return g.add(op, [a.id, b.id])
+
+
+def trace(fn, example_inputs) -> IrGraph:
+    """Capture ``fn`` (a module or function of tensors) as an :class:`IrGraph` with shapes."""
+    example_inputs = tuple(example_inputs)
+    try:
+        gm = torch.fx.symbolic_trace(fn)
+    except Exception as e:  # noqa: BLE001
+        raise JitError("cannot trace %r: %s" % (fn, e)) from e
+    g = IrGraph()
+    env: dict = {}
+    mods = dict(gm.named_modules())
+
+    def val(a):
+        return env[a] if isinstance(a, torch.fx.Node) else a
+
+    n_in = 0
+    for node in gm.graph.nodes:
+        args = [val(a) for a in node.args]
+        if node.op == "placeholder":
+            env[node] = g.add("input", index=n_in)
+            n_in += 1
+        elif node.op == "get_attr":
+            t = gm
+            for part in node.target.split("."):
+                t = getattr(t, part)
+            env[node] = g.add("const", value=t)
+        elif node.op == "call_function" and node.target in _FN_UNARY and not node.kwargs.get("approximate", "none") != "none":
+            env[node] = g.add(_FN_UNARY[node.target], [args[0].id])
+        elif node.op == "call_function" and node.target in _FN_BINARY and len(args) == 2 and not node.kwargs:
+            env[node] = _lower_binary(g, _FN_BINARY[node.target], args[0], args[1])
+        elif node.op == "call_function" and node.target in (operator.pow, torch.pow) and _is_num(args[1]):
+            env[node] = g.add("pow_c", [args[0].id], c=float(args[1]))
+        elif node.op == "call_method" and node.target in _METHOD and not node.kwargs:
+            op = _METHOD[node.target]
+            env[node] = _lower_binary(g, op, args[0], args[1]) if op in BINARY else g.add(op, [args[0].id])
+        elif node.op == "call_module" and type(mods[node.target]) in _MOD_UNARY and \
+                getattr(mods[node.target], "approximate", "none") == "none":
+            env[node] = g.add(_MOD_UNARY[type(mods[node.target])], [args[0].id])
+        elif node.op == "output":
+            flat, spec = torch.utils._pytree.tree_flatten(node.args[0])
+            g.outputs = [env[a].id for a in flat]
+            g.output_spec = spec
+        else:
+            # everything else runs as an opaque call; a few kinds are tagged for pattern fusion
+            kind = None
+            tgt = mods[node.target] if node.op == "call_module" else node.target
+            if node.op == "call_module" and isinstance(tgt, nn.Linear):
+                kind = "linear"
+            elif tgt in (torch.matmul, operator.matmul, torch.bmm) or (node.op == "call_method" and tgt == "matmul"):
+                kind = "matmul"
+            elif tgt in (torch.softmax, nn.functional.softmax) or (node.op == "call_method" and tgt == "softmax"):
+                kind = "softmax"
+            elif node.op == "call_method" and tgt == "transpose" and tuple(args[1:]) in ((-1, -2), (-2, -1)):
+                kind = "transpose_last"
+            tens = [a for a in torch.utils._pytree.tree_flatten((args, dict(node.kwargs)))[0] if hasattr(a, "id")]
+            env[node] = g.add("call", [t.id for t in tens], fx_op=node.op, target=tgt,
+                              args=tuple(args), kwargs={k: val(v) for k, v in node.kwargs.items()}, kind=kind)
+    # shape / dtype propagation with one eager run
+    values = _interpret(g, example_inputs, record=True)
+    del values
+    return g
+
+
+def _call_node(n, env):
+    def sub(a):
+        return env[a.id] if hasattr(a, "id") and hasattr(a, "op") else a
+
+    args = torch.utils._pytree.tree_map(sub, n.attrs["args"])
+    kwargs = torch.utils._pytree.tree_map(sub, n.attrs["kwargs"])
+    t = n.attrs["target"]
+    if n.attrs["fx_op"] == "call_method":
+        return getattr(args[0], t)(*args[1:], **kwargs)
+    return t(*args, **kwargs)
+
+
+def _interpret(g: IrGraph, inputs, record: bool = False, block: int = 256):
+    env: dict = {}
+    for i in g.order:
+        n = g.nodes[i]
+        if n.op == "input":
+            v = inputs[n.attrs["index"]]
+        elif n.op == "const":
+            v = n.attrs["value"]
+        elif n.op == "call":
+            v = _call_node(n, env)
+        elif n.op == "fused_elementwise":
+            ins = [env[j] for j in n.inputs]
+            shape = n.shape if n.shape is not None else torch.broadcast_shapes(*[t.shape for t in ins])
+            v = codegen.run_fused(n.attrs["program"], ins, tuple(shape), block)
+        elif n.op == "fused_linear_act":
+            from ..nn.layers import FusedLinearActivation  # noqa: F401
+            from ..ops import functional as F
+
+            x, lin = env[n.inputs[0]], n.attrs["module"]
+            if x.is_cuda and x.dtype == torch.bfloat16 and not torch.is_grad_enabled():
+                v = F.gemm_nt(x.reshape(-1, x.shape[-1]), lin.weight, bias=lin.bias,
+                              activation=n.attrs["activation"]).view(*x.shape[:-1], lin.out_features)
+            else:
+                v = codegen.eval_elementwise(n.attrs["activation"], [lin(x)])
+        elif n.op == "fused_attention":
+            q, k, v_ = (env[j] for j in n.inputs)
+            v = nn.functional.scaled_dot_product_attention(q, k, v_, scale=n.attrs["scale"] if n.attrs["scale"] != 1.0 else 1.0)
+        elif n.op in ELEMENTWISE:
+            v = codegen.eval_elementwise(n.op, [env[j] for j in n.inputs], n.attrs.get("c"))
+        else:
+            raise JitError("unknown IR op %s" % n.op)
+        env[i] = v
+        if record and isinstance(v, torch.Tensor):
+            n.shape, n.dtype = tuple(v.shape), v.dtype
+    return env
+
+
+class TracedModule(nn.Module):
+    """Runs the optimised graph; guards on the example inputs' shapes and dtypes."""
+
+    def __init__(self, graph: IrGraph, original, example_inputs, cfg: CompileConfig, stats: dict):
+        super().__init__()
+        self.graph, self.original, self.cfg, self.stats = graph, original, cfg, stats
+        self.guard = tuple((tuple(t.shape), t.dtype) for t in example_inputs if isinstance(t, torch.Tensor))
+        self.guard_failures = 0
+
+    def forward(self, *inputs):
+        sig = tuple((tuple(t.shape), t.dtype) for t in inputs if isinstance(t, torch.Tensor))
+        if sig != self.guard:
+            self.guard_failures += 1
+            if not self.cfg.fallback_to_eager:
+                raise JitError("input signature %r does not match the traced %r" % (sig, self.guard))
+            return self.original(*inputs)
+        env = _interpret(self.graph, inputs, block=self.cfg.block_size)
+        outs = [env[i] for i in self.graph.outputs]
+        return torch.utils._pytree.tree_unflatten(outs, self.graph.output_spec)
+
+
+class EagerFallback(nn.Module):
+    """What ``compile`` returns when the callable cannot be traced (a whole-function graph break)."""
+
+    def __init__(self, fn, reason: str):
+        super().__init__()
+        self.fn, self.reason = fn, reason
+        self.stats = {"graph_break": reason}
+
+    def forward(self, *a, **kw):
+        return self.fn(*a, **kw)
+
+
+def compile(fn, example_inputs, config: CompileConfig | None = None):  # noqa: A001
+    cfg = config or CompileConfig()
+    try:
+        g = trace(fn, example_inputs)
+    except JitError as e:
+        if not cfg.fallback_to_eager:
+            raise
+        return EagerFallback(fn, str(e))
+    # fused_linear_act needs the Linear module: stash it before the call node disappears
+    for n in g.nodes.values():
+        if n.op == "call" and n.attrs.get("kind") == "linear":
+            n.attrs["module"] = n.attrs["target"]
+    stats = optimize(g, cfg.optimization)
+    for n in g.nodes.values():
+        if n.op == "fused_linear_act" and "module" not in n.attrs:
+            raise JitError("internal: fused linear lost its module")
+    return TracedModule(g, fn, example_inputs, cfg, stats)
+
+
+_fusion_enabled = True
+
+
+@contextlib.contextmanager
+def with_fusion(enabled: bool = True):
+    """Scope in which :func:`apply_fused` may use generated kernels (fusion.rs:86)."""
+    global _fusion_enabled
+    prev, _fusion_enabled = _fusion_enabled, enabled
+    try:
+        yield
+    finally:
+        _fusion_enabled = prev
+
+
+def apply_fused(ops, x: torch.Tensor) -> torch.Tensor:
+    """Apply a chain of unary / scalar ops, e.g. ``[("mul_c", 2.0), "relu", "exp"]``, in one kernel."""
+    program = []
+    for k, o in enumerate(ops):
+        name, c = (o, None) if isinstance(o, str) else o
+        program.append({"op": name, "src": [("x", 0)] if k == 0 else [("r", k - 1)], "c": c})
+    if not _fusion_enabled:
+        return codegen.run_program_torch(program, [x])
+    return codegen.run_fused(program, [x], tuple(x.shape))
+
+
+class Autotuner:
+    """Pick the fastest launch block size for a compiled module on given inputs (autotune.rs)."""
+
+    def __init__(self, candidates=(128, 256, 512)):
+        self.candidates = candidates
+
+    def tune(self, module: TracedModule, inputs, iters: int = 5) -> int:
+        if not torch.cuda.is_available():
+            return module.cfg.block_size
+        best, best_t = module.cfg.block_size, float("inf")
+        for b in self.candidates:
+            module.cfg.block_size = b
+            module(*inputs)
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                module(*inputs)
+            e.record()
+            torch.cuda.synchronize()
+            t = s.elapsed_time(e)
+            if t < best_t:
+                best, best_t = b, t
+        module.cfg.block_size = best
+        return best
