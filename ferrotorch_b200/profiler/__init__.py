@@ -1,0 +1,211 @@
+"""Profiler: op / kernel ranges timed with CUDA events, a wait-warmup-active schedule, memory
+records, FLOP estimates, table / Chrome-trace / TensorBoard output.
+
+Reference: ``with_profiler`` (ferrotorch-profiler/src/profiler.rs:459), CUDA-event kernel scopes
+flushed after a synchronise (cuda_timing.rs:71-119, profiler.rs:302-329), ``ProfileSchedule``
+(schedule.rs:74-200), reports (report.rs:259, 446-478, 524), ``flops::estimate`` (flops.rs:53).
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass
+class ProfileEvent:
+    name: str
+    category: str
+    start_us: float
+    dur_us: float
+    device: str = "cpu"
+    shapes: tuple = ()
+    flops: float | None = None
+    bytes: int | None = None
+
+
+@dataclass
+class ProfileConfig:
+    record_shapes: bool = True
+    record_memory: bool = False
+    with_flops: bool = True
+    cuda_events: bool = True
+
+
+class ProfileSchedule:
+    """``wait`` steps idle, ``warmup`` steps running but discarded, ``active`` steps recorded,
+    repeated ``repeat`` times (0 = forever); ``on_trace_ready(profiler)`` fires after each cycle."""
+
+    def __init__(self, wait: int = 0, warmup: int = 0, active: int = 1, repeat: int = 1, on_trace_ready=None):
+        self.wait, self.warmup, self.active, self.repeat, self.on_trace_ready = wait, warmup, active, repeat, on_trace_ready
+        self.step_num = 0
+
+    def state(self) -> str:
+        cycle = self.wait + self.warmup + self.active
+        if self.repeat and self.step_num >= cycle * self.repeat:
+            return "done"
+        pos = self.step_num % cycle
+        return "wait" if pos < self.wait else "warmup" if pos < self.wait + self.warmup else "active"
+
+    def cycle_finished(self) -> bool:
+        cycle = self.wait + self.warmup + self.active
+        return self.step_num > 0 and self.step_num % cycle == 0
+
+
+def estimate_flops(op: str, shapes) -> float | None:
+    """FLOPs from shapes for the common ops (flops.rs:53)."""
+    try:
+        if op in ("matmul", "mm", "linear", "gemm"):
+            a, b = shapes[0], shapes[1]
+            m = 1
+            for d in a[:-1]:
+                m *= d
+            n = b[0] if op == "linear" else b[-1]
+            return 2.0 * m * a[-1] * n
+        if op == "attention":
+            b, s, h, d = shapes[0]
+            sk = shapes[1][1]
+            return 4.0 * b * h * s * sk * d
+        if op in ("add", "mul", "relu", "sub", "div"):
+            n = 1
+            for d in shapes[0]:
+                n *= d
+            return float(n)
+    except Exception:  # noqa: BLE001
+        return None
+    return None
+
+
+class Profiler:
+    _current: "Profiler | None" = None
+
+    def __init__(self, config: ProfileConfig | None = None, schedule: ProfileSchedule | None = None):
+        self.cfg, self.schedule = config or ProfileConfig(), schedule
+        self.events: list[ProfileEvent] = []
+        self.memory: list[tuple[float, str, int]] = []
+        self._pending: list = []
+        self._t0 = time.perf_counter()
+
+    # ---- recording
+    def _recording(self) -> bool:
+        return self.schedule is None or self.schedule.state() == "active"
+
+    def _now_us(self) -> float:
+        return (time.perf_counter() - self._t0) * 1e6
+
+    @contextlib.contextmanager
+    def scope(self, name: str, category: str = "op", shapes=(), op: str | None = None, nbytes: int | None = None):
+        """Time a region.  On CUDA the region is bracketed by events on the current stream; the
+        elapsed time is read at :meth:`flush` (no synchronisation inside the region)."""
+        if not self._recording():
+            yield
+            return
+        use_cuda = self.cfg.cuda_events and torch.cuda.is_available() and category in ("kernel", "cuda", "op")
+        start = self._now_us()
+        if use_cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        try:
+            yield
+        finally:
+            flops = estimate_flops(op or name, shapes) if self.cfg.with_flops and shapes else None
+            ev = ProfileEvent(name, category, start, self._now_us() - start, "cpu",
+                              tuple(shapes) if self.cfg.record_shapes else (), flops, nbytes)
+            self.events.append(ev)
+            if use_cuda:
+                e1.record()
+                self._pending.append((ev, e0, e1))
+            if self.cfg.record_memory and torch.cuda.is_available():
+                self.record_memory(name, torch.cuda.memory_allocated())
+
+    def record(self, name: str, dur_us: float, category: str = "manual") -> None:
+        self.events.append(ProfileEvent(name, category, self._now_us(), dur_us))
+
+    def record_memory(self, tag: str, nbytes: int) -> None:
+        self.memory.append((self._now_us(), tag, int(nbytes)))
+
+    def flush(self) -> None:
+        """Synchronise and convert pending CUDA event pairs into device durations."""
+        if self._pending:
+            torch.cuda.synchronize()
+            for ev, e0, e1 in self._pending:
+                self.events.append(ProfileEvent(ev.name, ev.category, ev.start_us, e0.elapsed_time(e1) * 1e3, "cuda",
+                                                ev.shapes, ev.flops, ev.bytes))
+            self._pending.clear()
+
+    def step(self) -> None:
+        if self.schedule is None:
+            return
+        self.schedule.step_num += 1
+        if self.schedule.cycle_finished():
+            self.flush()
+            if self.schedule.on_trace_ready is not None:
+                self.schedule.on_trace_ready(self)
+
+    # ---- reports
+    def summary(self) -> dict:
+        self.flush()
+        agg: dict = {}
+        for e in self.events:
+            k = (e.name, e.device)
+            a = agg.setdefault(k, {"name": e.name, "device": e.device, "count": 0, "total_us": 0.0, "flops": 0.0})
+            a["count"] += 1
+            a["total_us"] += e.dur_us
+            a["flops"] += e.flops or 0.0
+        return agg
+
+    def table(self, sort_by: str = "total_us") -> str:
+        rows = sorted(self.summary().values(), key=lambda a: -a[sort_by])
+        out = ["%-32s %-5s %8s %12s %12s %10s" % ("name", "dev", "calls", "total us", "avg us", "TFLOP/s")]
+        for a in rows:
+            tf = a["flops"] / a["total_us"] / 1e6 if a["flops"] and a["total_us"] else 0.0
+            out.append("%-32s %-5s %8d %12.1f %12.1f %10.2f" % (a["name"][:32], a["device"], a["count"], a["total_us"],
+                                                                  a["total_us"] / a["count"], tf))
+        return "\n".join(out)
+
+    def chrome_trace_json(self) -> str:
+        self.flush()
+        ev = [{"name": e.name, "cat": e.category, "ph": "X", "ts": e.start_us, "dur": e.dur_us,
+               "pid": 0, "tid": 1 if e.device == "cuda" else 0, "args": {"shapes": list(e.shapes), "flops": e.flops}}
+              for e in self.events]
+        ev += [{"name": "memory", "ph": "C", "ts": t, "pid": 0, "args": {tag: b}} for t, tag, b in self.memory]
+        return json.dumps({"traceEvents": ev, "displayTimeUnit": "ms"})
+
+    def export_chrome_trace(self, path: str) -> None:
+        with open(path, "w") as f:
+            f.write(self.chrome_trace_json())
+
+    def export_tensorboard(self, log_dir: str, step: int = 0) -> None:
+        from ..train.tensorboard import TensorBoardWriter
+
+        w = TensorBoardWriter(log_dir)
+        for a in self.summary().values():
+            w.add_scalar("profile/%s/%s_us" % (a["device"], a["name"]), a["total_us"], step)
+        w.close()
+
+
+@contextlib.contextmanager
+def profile_op_scope(name: str, category: str = "op", shapes=(), op: str | None = None):
+    """Hook used by instrumented ops: a no-op unless a profiler is installed
+    (ferrotorch-core/src/profiler_hook.rs:49-97)."""
+    p = Profiler._current
+    if p is None:
+        yield
+    else:
+        with p.scope(name, category, shapes, op):
+            yield
+
+
+def with_profiler(fn, config: ProfileConfig | None = None, schedule: ProfileSchedule | None = None):
+    """Run ``fn(profiler)`` with a profiler installed; returns ``(result, profiler)``."""
+    p = Profiler(config, schedule)
+    prev, Profiler._current = Profiler._current, p
+    try:
+        r = fn(p)
+    finally:
+        Profiler._current = prev
+        p.flush()
+    return r, p

@@ -1,0 +1,324 @@
+"""``Learner``: fit / evaluate loop with AMP, clipping, EMA, schedulers, callbacks, metrics,
+history and per-epoch checkpoints (ferrotorch-train/src/learner.rs:479-790, callback.rs:41-220,
+metric.rs:36-301, history.rs:34-203, amp.rs:86-130).
+
+Differences from the reference's loop: the loss is read back once per ``log_every`` batches
+instead of every step (learner.rs:581 synchronises each step), EMA stays on the device, and a
+:class:`ferrotorch_b200.parallel.host_ddp.DDP` wrapper or a ``FlatTrainer`` plugs in directly
+(the reference leaves DDP to the user, ddp.rs:43-54).
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import os
+from dataclasses import dataclass, field
+
+import torch
+from torch import nn
+
+from ..serialize import load_checkpoint, save_checkpoint
+
+
+# --------------------------------------------------------------------------- metrics
+class Metric:
+    name = "metric"
+
+    def reset(self): ...
+    def update(self, output, target, loss): ...
+    def compute(self) -> float: ...
+
+
+class LossMetric(Metric):
+    name = "loss"
+
+    def reset(self):
+        self.total, self.n = 0.0, 0
+
+    def update(self, output, target, loss):
+        b = target.shape[0] if hasattr(target, "shape") and target.dim() else 1
+        self.total += float(loss) * b
+        self.n += b
+
+    def compute(self):
+        return self.total / max(self.n, 1)
+
+
+class TopKAccuracy(Metric):
+    def __init__(self, k: int = 1):
+        self.k, self.name = k, "accuracy" if k == 1 else "top%d_accuracy" % k
+        self.reset()
+
+    def reset(self):
+        self.correct, self.n = 0, 0
+
+    def update(self, output, target, loss):
+        top = output.detach().topk(self.k, dim=-1).indices
+        self.correct += int((top == target.unsqueeze(-1)).any(-1).sum())
+        self.n += target.numel()
+
+    def compute(self):
+        return self.correct / max(self.n, 1)
+
+
+def AccuracyMetric():
+    return TopKAccuracy(1)
+
+
+class RunningAverage(Metric):
+    def __init__(self, momentum: float = 0.98, name: str = "running_loss"):
+        self.momentum, self.name = momentum, name
+        self.reset()
+
+    def reset(self):
+        self.value = None
+
+    def update(self, output, target, loss):
+        v = float(loss)
+        self.value = v if self.value is None else self.momentum * self.value + (1 - self.momentum) * v
+
+    def compute(self):
+        return self.value if self.value is not None else float("nan")
+
+
+# --------------------------------------------------------------------------- history / callbacks
+@dataclass
+class EpochResult:
+    epoch: int
+    train: dict
+    val: dict | None = None
+    lr: float | None = None
+
+
+@dataclass
+class TrainingHistory:
+    epochs: list[EpochResult] = field(default_factory=list)
+
+    def append(self, r: EpochResult):
+        self.epochs.append(r)
+
+    def best(self, key: str = "loss", split: str = "val", mode: str = "min"):
+        vals = [(getattr(e, split) or {}).get(key) for e in self.epochs]
+        vals = [(v, i) for i, v in enumerate(vals) if v is not None]
+        if not vals:
+            return None
+        v, i = (min if mode == "min" else max)(vals)
+        return self.epochs[i]
+
+    def series(self, key: str, split: str = "train") -> list:
+        return [(getattr(e, split) or {}).get(key) for e in self.epochs]
+
+
+class Callback:
+    def on_train_start(self, learner): ...
+    def on_epoch_start(self, learner, epoch): ...
+    def on_batch_end(self, learner, epoch, batch_idx, loss): ...
+    def on_epoch_end(self, learner, result: EpochResult): ...
+    def on_train_end(self, learner): ...
+
+
+class EarlyStopping(Callback):
+    def __init__(self, monitor: str = "loss", patience: int = 3, mode: str = "min", min_delta: float = 0.0):
+        self.monitor, self.patience, self.mode, self.min_delta = monitor, patience, mode, min_delta
+        self.best, self.bad = None, 0
+
+    def on_epoch_end(self, learner, result):
+        v = (result.val or result.train).get(self.monitor)
+        if v is None:
+            return
+        better = self.best is None or (v < self.best - self.min_delta if self.mode == "min" else v > self.best + self.min_delta)
+        if better:
+            self.best, self.bad = v, 0
+        else:
+            self.bad += 1
+            if self.bad >= self.patience:
+                learner.should_stop = True
+
+
+class ProgressLogger(Callback):
+    def __init__(self, every: int = 50, sink=print):
+        self.every, self.sink = every, sink
+
+    def on_batch_end(self, learner, epoch, batch_idx, loss):
+        if (batch_idx + 1) % self.every == 0:
+            self.sink("epoch %d batch %d loss %.4f" % (epoch, batch_idx + 1, float(loss)))
+
+    def on_epoch_end(self, learner, result):
+        self.sink("epoch %d train %s val %s" % (result.epoch, result.train, result.val))
+
+
+class EMACallback(Callback):
+    def __init__(self, decay: float = 0.999):
+        self.decay, self.ema = decay, None
+
+    def on_train_start(self, learner):
+        from ..optim import EMA
+
+        self.ema = EMA(learner.model, self.decay)
+
+    def on_batch_end(self, learner, epoch, batch_idx, loss):
+        self.ema.update()
+
+
+class TensorBoardCallback(Callback):
+    def __init__(self, log_dir: str):
+        from .tensorboard import TensorBoardWriter
+
+        self.w = TensorBoardWriter(log_dir)
+
+    def on_epoch_end(self, learner, result):
+        self.w.add_scalars("train", result.train, result.epoch)
+        if result.val:
+            self.w.add_scalars("val", result.val, result.epoch)
+        self.w.flush()
+
+    def on_train_end(self, learner):
+        self.w.close()
+
+
+# --------------------------------------------------------------------------- AMP
+class AmpContext:
+    """Autocast + GradScaler in one object (amp.rs:86-130): ``backward_step`` = scale -> backward
+    -> unscale -> (clip) -> step (skipped on inf/nan) -> update."""
+
+    def __init__(self, dtype=torch.bfloat16, device_type: str = "cuda", use_scaler: bool | None = None):
+        self.dtype, self.device_type = dtype, device_type
+        use = (dtype == torch.float16) if use_scaler is None else use_scaler
+        self.scaler = torch.amp.GradScaler(device_type, enabled=use and device_type == "cuda")
+
+    def autocast(self):
+        return torch.autocast(self.device_type, dtype=self.dtype)
+
+    def backward_step(self, loss, optimizer, params=None, max_grad_norm: float | None = None):
+        self.scaler.scale(loss).backward()
+        if max_grad_norm is not None and params is not None:
+            self.scaler.unscale_(optimizer)
+            nn.utils.clip_grad_norm_(params, max_grad_norm)
+        self.scaler.step(optimizer)
+        self.scaler.update()
+
+
+# --------------------------------------------------------------------------- Learner
+class Learner:
+    def __init__(self, model: nn.Module, optimizer, loss_fn, *, scheduler=None, metrics=None, callbacks=None,
+                 amp: AmpContext | None = None, max_grad_norm: float | None = None, ddp=None, device=None,
+                 checkpoint_dir: str | None = None, log_every: int = 10):
+        self.model, self.optimizer, self.loss_fn = model, optimizer, loss_fn
+        self.scheduler, self.amp, self.max_grad_norm, self.ddp = scheduler, amp, max_grad_norm, ddp
+        self.metrics = metrics if metrics is not None else [LossMetric()]
+        self.callbacks = callbacks or []
+        self.device = device
+        self.checkpoint_dir, self.log_every = checkpoint_dir, log_every
+        self.history = TrainingHistory()
+        self.epoch, self.global_step, self.should_stop = 0, 0, False
+
+    def with_checkpointing(self, directory: str) -> "Learner":
+        self.checkpoint_dir = directory
+        return self
+
+    def _to_device(self, t):
+        return t.to(self.device, non_blocking=True) if self.device is not None and hasattr(t, "to") else t
+
+    def _forward(self, x, y):
+        ctx = self.amp.autocast() if self.amp is not None else contextlib.nullcontext()
+        with ctx:
+            out = self.model(x)
+            loss = self.loss_fn(out, y)
+        return out, loss
+
+    def _run_epoch(self, data, train: bool) -> dict:
+        for m in self.metrics:
+            m.reset()
+        self.model.train(train)
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        for bi, (x, y) in enumerate(data):
+            x, y = self._to_device(x), self._to_device(y)
+            if train:
+                self.optimizer.zero_grad(set_to_none=True)
+                out, loss = self._forward(x, y)
+                if self.amp is not None and self.ddp is None:
+                    self.amp.backward_step(loss, self.optimizer, params, self.max_grad_norm)
+                else:
+                    loss.backward()
+                    if self.ddp is not None:
+                        self.ddp.sync_gradients()
+                    if self.max_grad_norm is not None:
+                        nn.utils.clip_grad_norm_(params, self.max_grad_norm)
+                    self.optimizer.step()
+                self.global_step += 1
+                for cb in self.callbacks:
+                    cb.on_batch_end(self, self.epoch, bi, loss.detach())
+            else:
+                with torch.no_grad():
+                    out, loss = self._forward(x, y)
+            for m in self.metrics:
+                m.update(out, y, loss.detach())
+        return {m.name: m.compute() for m in self.metrics}
+
+    def fit(self, train_data, val_data=None, epochs: int = 1) -> TrainingHistory:
+        for cb in self.callbacks:
+            cb.on_train_start(self)
+        start = self.epoch
+        for epoch in range(start, start + epochs):
+            self.epoch = epoch
+            for cb in self.callbacks:
+                cb.on_epoch_start(self, epoch)
+            tr = self._run_epoch(train_data() if callable(train_data) else train_data, True)
+            va = self._run_epoch(val_data() if callable(val_data) else val_data, False) if val_data is not None else None
+            if self.scheduler is not None:
+                if isinstance(self.scheduler, torch.optim.lr_scheduler.ReduceLROnPlateau):
+                    self.scheduler.step((va or tr)["loss"])
+                else:
+                    self.scheduler.step()
+            res = EpochResult(epoch, tr, va, self.optimizer.param_groups[0]["lr"])
+            self.history.append(res)
+            if self.checkpoint_dir:
+                os.makedirs(self.checkpoint_dir, exist_ok=True)
+                self.save_checkpoint(os.path.join(self.checkpoint_dir, "checkpoint_epoch_%d.ftc" % epoch))
+            for cb in self.callbacks:
+                cb.on_epoch_end(self, res)
+            self.epoch = epoch + 1
+            if self.should_stop:
+                break
+        for cb in self.callbacks:
+            cb.on_train_end(self)
+        return self.history
+
+    def evaluate(self, data) -> dict:
+        return self._run_epoch(data() if callable(data) else data, False)
+
+    def save_checkpoint(self, path: str) -> None:
+        extra = {"rng": torch.get_rng_state().tolist()}
+        if self.amp is not None:
+            extra["scaler"] = self.amp.scaler.state_dict()
+        save_checkpoint(path, self.model.state_dict(), self.optimizer.state_dict(), epoch=self.epoch,
+                        step=self.global_step, extra=extra)
+
+    def load_checkpoint(self, path: str) -> None:
+        ck = load_checkpoint(path)
+        self.model.load_state_dict(ck["model"])
+        self.optimizer.load_state_dict(ck["optimizer"])
+        self.epoch, self.global_step = ck["epoch"] + 1, ck["step"]
+        if "rng" in ck["extra"]:
+            torch.set_rng_state(torch.tensor(ck["extra"]["rng"], dtype=torch.uint8))
+        if self.amp is not None and ck["extra"].get("scaler"):
+            self.amp.scaler.load_state_dict(ck["extra"]["scaler"])
+
+
+def checkpoint_sequential(functions, segments: int, x: torch.Tensor) -> torch.Tensor:
+    """Activation checkpointing over a list of layers in ``segments`` chunks
+    (ferrotorch-train/src/checkpoint.rs:113)."""
+    from torch.utils.checkpoint import checkpoint
+
+    fns = list(functions)
+    per = math.ceil(len(fns) / segments)
+    for s in range(0, len(fns), per):
+        chunk = fns[s:s + per]
+
+        def run(inp, chunk=chunk):
+            for f in chunk:
+                inp = f(inp)
+            return inp
+
+        x = checkpoint(run, x, use_reentrant=False) if s + per < len(fns) else run(x)
+    return x

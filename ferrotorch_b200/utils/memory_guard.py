@@ -1,0 +1,141 @@
+"""GPU memory guard: budget, reservation, OOM policy, pre-OOM hooks by priority, pressure
+listeners and a watchdog thread (ferrotorch-gpu/src/memory_guard.rs:76-1305).
+
+The guard sits on top of an ``allocator`` object with ``used_bytes()`` / ``total_bytes()`` /
+``empty_cache()``; the default one reads ``torch.cuda`` (``mem_get_info``, the caching
+allocator's statistics).  Tests use a fake allocator with a budget, never real exhaustion.
+"""
+from __future__ import annotations
+
+import enum
+import threading
+import time
+from typing import Callable
+
+
+class OomPolicy(enum.Enum):
+    FAIL = "fail"                  # raise immediately
+    RUN_HOOKS_THEN_FAIL = "hooks"  # run pre-OOM hooks (free caches, offload), retry once, then raise
+    WAIT = "wait"                  # block (bounded) until pressure drops, e.g. another job frees memory
+
+
+class MemoryBudgetExceeded(MemoryError):
+    pass
+
+
+class TorchCudaAllocator:
+    def __init__(self, device: int = 0):
+        self.device = device
+
+    def used_bytes(self) -> int:
+        import torch
+
+        return int(torch.cuda.memory_reserved(self.device))
+
+    def total_bytes(self) -> int:
+        import torch
+
+        return int(torch.cuda.mem_get_info(self.device)[1])
+
+    def empty_cache(self) -> None:
+        import torch
+
+        torch.cuda.empty_cache()
+
+
+class MemoryGuard:
+    def __init__(self, allocator=None, budget_bytes: int | None = None, reserve_bytes: int = 0,
+                 policy: OomPolicy = OomPolicy.RUN_HOOKS_THEN_FAIL, pressure_threshold: float = 0.9,
+                 wait_timeout_s: float = 5.0):
+        self.alloc = allocator or TorchCudaAllocator()
+        self.budget = budget_bytes if budget_bytes is not None else self.alloc.total_bytes()
+        self.reserve, self.policy = reserve_bytes, policy
+        self.pressure_threshold, self.wait_timeout_s = pressure_threshold, wait_timeout_s
+        self._hooks: list[tuple[int, str, Callable[[int], int]]] = []
+        self._listeners: list[Callable[[float], None]] = []
+        self._emergency: Callable[[], None] | None = None
+        self._watchdog: threading.Thread | None = None
+        self._stop = threading.Event()
+        self.paused = threading.Event()
+        self.stats = {"checks": 0, "hook_runs": 0, "freed_by_hooks": 0, "failures": 0, "pauses": 0}
+
+    # ---- configuration
+    def add_pre_oom_hook(self, fn: Callable[[int], int], priority: int = 0, name: str = "") -> None:
+        """``fn(bytes_needed) -> bytes_freed``; hooks run in descending priority until enough is free."""
+        self._hooks.append((priority, name or getattr(fn, "__name__", "hook"), fn))
+        self._hooks.sort(key=lambda h: -h[0])
+
+    def add_pressure_listener(self, fn: Callable[[float], None]) -> None:
+        self._listeners.append(fn)
+
+    def set_emergency_checkpoint(self, fn: Callable[[], None]) -> None:
+        self._emergency = fn
+
+    # ---- queries
+    def available(self) -> int:
+        return self.budget - self.reserve - self.alloc.used_bytes()
+
+    def pressure(self) -> float:
+        return self.alloc.used_bytes() / max(1, self.budget - self.reserve)
+
+    # ---- the check callers make before a large allocation
+    def ensure(self, nbytes: int) -> None:
+        self.stats["checks"] += 1
+        if nbytes <= self.available():
+            return
+        if self.policy == OomPolicy.FAIL:
+            return self._fail(nbytes)
+        if self.policy == OomPolicy.WAIT:
+            deadline = time.time() + self.wait_timeout_s
+            while time.time() < deadline:
+                if nbytes <= self.available():
+                    return
+                time.sleep(0.01)
+        need = nbytes - self.available()
+        for _, _, fn in self._hooks:
+            self.stats["hook_runs"] += 1
+            self.stats["freed_by_hooks"] += int(fn(need) or 0)
+            need = nbytes - self.available()
+            if need <= 0:
+                return
+        self.alloc.empty_cache()
+        if nbytes <= self.available():
+            return
+        self._fail(nbytes)
+
+    def _fail(self, nbytes: int):
+        self.stats["failures"] += 1
+        if self._emergency is not None:
+            self._emergency()
+        raise MemoryBudgetExceeded("need %d bytes, %d available (budget %d, reserved %d)" %
+                                   (nbytes, self.available(), self.budget, self.reserve))
+
+    # ---- watchdog: pauses training (``guard.paused`` is set) while pressure is above the threshold
+    def start_watchdog(self, interval_s: float = 0.05) -> None:
+        def run():
+            while not self._stop.wait(interval_s):
+                p = self.pressure()
+                if p >= self.pressure_threshold:
+                    if not self.paused.is_set():
+                        self.paused.set()
+                        self.stats["pauses"] += 1
+                    for fn in self._listeners:
+                        fn(p)
+                else:
+                    self.paused.clear()
+
+        self._stop.clear()
+        self._watchdog = threading.Thread(target=run, daemon=True)
+        self._watchdog.start()
+
+    def stop_watchdog(self) -> None:
+        self._stop.set()
+        if self._watchdog is not None:
+            self._watchdog.join(2.0)
+
+    def wait_if_paused(self, timeout_s: float = 1.0) -> bool:
+        """Training loops call this between steps; returns False if still paused after the timeout."""
+        deadline = time.time() + timeout_s
+        while self.paused.is_set() and time.time() < deadline:
+            time.sleep(0.005)
+        return not self.paused.is_set()

@@ -1,0 +1,174 @@
+"""Learner, callbacks, metrics, TensorBoard writer, profiler, memory guard, data utilities."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+from torch import nn
+
+from ferrotorch_b200 import data as D
+from ferrotorch_b200 import profiler as P
+from ferrotorch_b200 import train as T
+from ferrotorch_b200.train import tensorboard as TB
+from ferrotorch_b200.utils.memory_guard import MemoryBudgetExceeded, MemoryGuard, OomPolicy
+
+
+def _loaders():
+    torch.manual_seed(0)
+    x = torch.randn(96, 8)
+    y = (x[:, 0] + x[:, 1] > 0).long()
+    ds = D.TensorDataset(x, y)
+    return D.DataLoader(ds, batch_size=16, shuffle=False), D.DataLoader(ds, batch_size=32)
+
+
+def test_learner_fit_checkpoint_resume_and_callbacks(tmp_path):
+    tr, va = _loaders()
+    model = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 2))
+    opt = torch.optim.Adam(model.parameters(), lr=5e-2)
+    logs = []
+    learner = T.Learner(model, opt, nn.CrossEntropyLoss(), scheduler=torch.optim.lr_scheduler.StepLR(opt, 2, 0.5),
+                        metrics=[T.LossMetric(), T.AccuracyMetric(), T.TopKAccuracy(2), T.RunningAverage()],
+                        callbacks=[T.ProgressLogger(3, logs.append), T.EMACallback(0.9),
+                                   T.TensorBoardCallback(str(tmp_path / "tb")), T.EarlyStopping("accuracy", 50, "max")],
+                        max_grad_norm=1.0, checkpoint_dir=str(tmp_path / "ck"))
+    hist = learner.fit(tr, va, epochs=4)
+    assert len(hist.epochs) == 4 and hist.epochs[-1].train["loss"] < hist.epochs[0].train["loss"]
+    assert hist.epochs[-1].val["accuracy"] > 0.8 and hist.epochs[-1].val["top2_accuracy"] == 1.0
+    assert hist.epochs[2].lr == pytest.approx(5e-2 * 0.5) and hist.best("accuracy", "val", "max") is not None
+    assert logs and os.path.exists(str(tmp_path / "ck" / "checkpoint_epoch_3.ftc"))
+    recs = TB.read_records(learner.callbacks[2].w.path)
+    assert b"brain.Event:2" in recs[0] and any(b"train/loss" in r for r in recs)
+    # resume into a fresh learner: same weights, epoch counter continues
+    model2 = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 2))
+    l2 = T.Learner(model2, torch.optim.Adam(model2.parameters(), lr=5e-2), nn.CrossEntropyLoss())
+    l2.load_checkpoint(str(tmp_path / "ck" / "checkpoint_epoch_3.ftc"))
+    assert l2.epoch == 4 and l2.global_step == learner.global_step
+    for a, b in zip(model.parameters(), model2.parameters()):
+        assert torch.equal(a, b)
+    assert l2.evaluate(va)["loss"] == pytest.approx(hist.epochs[-1].val["loss"], rel=1e-5)
+
+
+def test_early_stopping_and_checkpoint_sequential():
+    tr, va = _loaders()
+    model = nn.Linear(8, 2)
+    learner = T.Learner(model, torch.optim.SGD(model.parameters(), lr=0.0), nn.CrossEntropyLoss(),
+                        callbacks=[T.EarlyStopping("loss", patience=2)])
+    assert len(learner.fit(tr, va, epochs=10).epochs) == 3
+    layers = [nn.Linear(4, 4) for _ in range(5)]
+    x = torch.randn(3, 4, requires_grad=True)
+    y = T.checkpoint_sequential(layers, 2, x)
+    ref = x
+    for l in layers:
+        ref = l(ref)
+    assert torch.allclose(y, ref)
+    y.sum().backward()
+    assert x.grad is not None
+
+
+def test_tensorboard_record_format():
+    assert TB.crc32c(b"123456789") == 0xE3069283
+    ev = TB.encode_scalar_event("loss", 1.5, 7, 100.0)
+    rec = TB.record(ev)
+    (n,) = struct.unpack_from("<Q", rec, 0)
+    assert n == len(ev) and struct.unpack_from("<I", rec, 8)[0] == TB.masked_crc(rec[:8])
+    assert b"loss" in ev and struct.pack("<f", 1.5) in ev
+
+
+def test_profiler_scopes_schedule_and_reports(tmp_path):
+    ready = []
+    sched = P.ProfileSchedule(wait=1, warmup=1, active=2, repeat=1, on_trace_ready=lambda p: ready.append(len(p.events)))
+
+    def work(p):
+        for _ in range(5):
+            with P.profile_op_scope("matmul", shapes=((8, 16), (16, 4))):
+                torch.randn(8, 16) @ torch.randn(16, 4)
+            p.step()
+        p.record("manual", 12.0)
+        p.record_memory("after", 1024)
+        return 42
+
+    r, prof = P.with_profiler(work, P.ProfileConfig(), sched)
+    assert r == 42 and ready and sched.state() == "done"
+    s = prof.summary()[("matmul", "cpu")]
+    assert s["count"] == 2 and s["flops"] == 2 * (2.0 * 8 * 16 * 4)   # only the two active steps
+    assert "matmul" in prof.table()
+    trace = json.loads(prof.chrome_trace_json())
+    assert any(e["name"] == "matmul" and e["ph"] == "X" for e in trace["traceEvents"])
+    prof.export_chrome_trace(str(tmp_path / "t.json"))
+    prof.export_tensorboard(str(tmp_path / "tb"))
+    assert P.estimate_flops("attention", ((2, 128, 8, 64), (2, 256, 2, 64))) == 4.0 * 2 * 8 * 128 * 256 * 64
+    with P.profile_op_scope("nothing installed"):
+        pass
+
+
+class _FakeAlloc:
+    def __init__(self, total):
+        self.total, self.used, self.cache = total, 0, 0
+
+    def used_bytes(self):
+        return self.used + self.cache
+
+    def total_bytes(self):
+        return self.total
+
+    def empty_cache(self):
+        self.cache = 0
+
+
+def test_memory_guard_policies_hooks_watchdog():
+    a = _FakeAlloc(1000)
+    g = MemoryGuard(a, reserve_bytes=100, policy=OomPolicy.RUN_HOOKS_THEN_FAIL, pressure_threshold=0.8)
+    a.used, a.cache = 500, 200
+    assert g.available() == 200
+    order = []
+    g.add_pre_oom_hook(lambda need: order.append("low") or 0, priority=1)
+
+    def free_acts(need):
+        if "high" in order:
+            return 0
+        order.append("high")
+        a.used -= 150
+        return 150
+
+    g.add_pre_oom_hook(free_acts, priority=10)
+    g.ensure(300)                       # high-priority hook frees enough
+    assert order == ["high"] and g.stats["freed_by_hooks"] == 150
+    g.ensure(500)                       # hooks not enough, empty_cache makes room
+    assert a.cache == 0
+    called = []
+    g.set_emergency_checkpoint(lambda: called.append(1))
+    with pytest.raises(MemoryBudgetExceeded):
+        g.ensure(5000)
+    assert called and g.stats["failures"] == 1
+    with pytest.raises(MemoryBudgetExceeded):
+        MemoryGuard(a, policy=OomPolicy.FAIL).ensure(10_000)
+    seen = []
+    g.add_pressure_listener(seen.append)
+    a.used = 850
+    g.start_watchdog(0.01)
+    import time
+
+    time.sleep(0.15)
+    assert not g.wait_if_paused(0.2) and seen and g.stats["pauses"] >= 1
+    a.used = 100
+    assert g.wait_if_paused(1.0)
+    g.stop_watchdog()
+    w = MemoryGuard(a, policy=OomPolicy.WAIT, wait_timeout_s=0.05)
+    with pytest.raises(MemoryBudgetExceeded):
+        w.ensure(10_000)
+
+
+def test_data_utilities():
+    ds = D.SyntheticTokens(100, 16, 10, seed=3)
+    x, y = ds[4]
+    x2, _ = ds[4]
+    assert x.shape == (16,) and torch.equal(x[1:], y[:-1]) and torch.equal(x, x2)
+    img, label = D.SyntheticImages(4, num_classes=10, size=8)[1]
+    assert img.shape == (3, 8, 8) and 0 <= label < 10
+    assert sorted(D.shuffle_with_seed(10, 1)) == list(range(10)) and D.shuffle_with_seed(10, 1) == D.shuffle_with_seed(10, 1)
+    s0 = list(D.DistributedSampler(ds, num_replicas=2, rank=0, shuffle=False))
+    s1 = list(D.DistributedSampler(ds, num_replicas=2, rank=1, shuffle=False))
+    assert sorted(s0 + s1) == list(range(10))
+    batches = list(D.DevicePrefetcher(D.DataLoader(ds, batch_size=4), "cpu"))
+    assert len(batches) == 3 and batches[0][0].shape == (4, 16)
