@@ -1,0 +1,138 @@
+"""ResNet-18 / 34 / 50 (ferrotorch-vision/src/models/resnet.rs:325 ``Bottleneck``, :565 ``ResNet``,
+:1071 ``resnet50``) and a small model registry (models/registry.rs).
+
+Layers are torch.nn (cuDNN convolutions and batch norm as the library baseline for the conv
+path); the data-parallel gradient exchange and the SGD update run through the fused
+``ft_ddp_reduce_update`` kernel when trained with ``FlatTrainer`` + ``FusedDDP``.  State-dict
+keys match torchvision's (``conv1.weight``, ``layer1.0.conv1.weight``, ``fc.weight`` ...).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+
+class BasicBlock(nn.Module):
+    expansion = 1
+
+    def __init__(self, inplanes, planes, stride=1, downsample=None, dilation=1):
+        super().__init__()
+        self.conv1 = nn.Conv2d(inplanes, planes, 3, stride, dilation, dilation=dilation, bias=False)
+        self.bn1 = nn.BatchNorm2d(planes)
+        self.relu = nn.ReLU(inplace=True)
+        self.conv2 = nn.Conv2d(planes, planes, 3, 1, dilation, dilation=dilation, bias=False)
+        self.bn2 = nn.BatchNorm2d(planes)
+        self.downsample = downsample
+
+    def forward(self, x):
+        idt = x if self.downsample is None else self.downsample(x)
+        out = self.relu(self.bn1(self.conv1(x)))
+        out = self.bn2(self.conv2(out))
+        return self.relu(out + idt)
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, inplanes, planes, stride=1, downsample=None, dilation=1):
+        super().__init__()
+        self.conv1 = nn.Conv2d(inplanes, planes, 1, bias=False)
+        self.bn1 = nn.BatchNorm2d(planes)
+        self.conv2 = nn.Conv2d(planes, planes, 3, stride, dilation, dilation=dilation, bias=False)
+        self.bn2 = nn.BatchNorm2d(planes)
+        self.conv3 = nn.Conv2d(planes, planes * 4, 1, bias=False)
+        self.bn3 = nn.BatchNorm2d(planes * 4)
+        self.relu = nn.ReLU(inplace=True)
+        self.downsample = downsample
+
+    def forward(self, x):
+        idt = x if self.downsample is None else self.downsample(x)
+        out = self.relu(self.bn1(self.conv1(x)))
+        out = self.relu(self.bn2(self.conv2(out)))
+        out = self.bn3(self.conv3(out))
+        return self.relu(out + idt)
+
+
+class ResNet(nn.Module):
+    def __init__(self, block, layers, num_classes: int = 1000, replace_stride_with_dilation=(False, False, False),
+                 zero_init_residual: bool = False):
+        super().__init__()
+        self.inplanes, self.dilation = 64, 1
+        self.conv1 = nn.Conv2d(3, 64, 7, 2, 3, bias=False)
+        self.bn1 = nn.BatchNorm2d(64)
+        self.relu = nn.ReLU(inplace=True)
+        self.maxpool = nn.MaxPool2d(3, 2, 1)
+        self.layer1 = self._make_layer(block, 64, layers[0])
+        self.layer2 = self._make_layer(block, 128, layers[1], 2, replace_stride_with_dilation[0])
+        self.layer3 = self._make_layer(block, 256, layers[2], 2, replace_stride_with_dilation[1])
+        self.layer4 = self._make_layer(block, 512, layers[3], 2, replace_stride_with_dilation[2])
+        self.avgpool = nn.AdaptiveAvgPool2d(1)
+        self.fc = nn.Linear(512 * block.expansion, num_classes)
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.ones_(m.weight)
+                nn.init.zeros_(m.bias)
+        if zero_init_residual:
+            for m in self.modules():
+                if isinstance(m, Bottleneck):
+                    nn.init.zeros_(m.bn3.weight)
+                elif isinstance(m, BasicBlock):
+                    nn.init.zeros_(m.bn2.weight)
+
+    def _make_layer(self, block, planes, blocks, stride=1, dilate=False):
+        prev_dilation = self.dilation
+        if dilate:
+            self.dilation *= stride
+            stride = 1
+        down = None
+        if stride != 1 or self.inplanes != planes * block.expansion:
+            down = nn.Sequential(nn.Conv2d(self.inplanes, planes * block.expansion, 1, stride, bias=False),
+                                 nn.BatchNorm2d(planes * block.expansion))
+        layers = [block(self.inplanes, planes, stride, down, prev_dilation)]
+        self.inplanes = planes * block.expansion
+        layers += [block(self.inplanes, planes, dilation=self.dilation) for _ in range(1, blocks)]
+        return nn.Sequential(*layers)
+
+    def forward(self, x):
+        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        return self.fc(torch.flatten(self.avgpool(x), 1))
+
+
+def resnet18(**kw):
+    return ResNet(BasicBlock, [2, 2, 2, 2], **kw)
+
+
+def resnet34(**kw):
+    return ResNet(BasicBlock, [3, 4, 6, 3], **kw)
+
+
+def resnet50(**kw):
+    return ResNet(Bottleneck, [3, 4, 6, 3], **kw)
+
+
+_REGISTRY = {"resnet18": resnet18, "resnet34": resnet34, "resnet50": resnet50}
+
+
+def register_model(name: str, ctor) -> None:
+    _REGISTRY[name] = ctor
+
+
+def list_models() -> list[str]:
+    return sorted(_REGISTRY)
+
+
+def create_model(name: str, **kw) -> nn.Module:
+    """Registry lookup; names not registered here are looked up in torchvision (VGG, ViT, ConvNeXt,
+    Swin, MobileNet, DenseNet, EfficientNet, Inception and the detection / segmentation families
+    of ferrotorch-vision/src/models are served by that package)."""
+    if name in _REGISTRY:
+        return _REGISTRY[name](**kw)
+    try:
+        import torchvision.models as tvm
+
+        return tvm.get_model(name, weights=None, **kw)
+    except Exception as e:  # noqa: BLE001
+        raise KeyError("unknown model %r (registered: %s)" % (name, list_models())) from e

@@ -126,6 +126,16 @@ class FusedDDP:
             for p in b["params"]:
                 self._buckets_of.setdefault(id(p), []).append(bi)
                 p.grad_ready_hook = self._on_grad_ready
+        # parameters whose gradient comes from a plain torch op (no main_grad epilogue): fold
+        # ``.grad`` into the arena as soon as autograd has accumulated it, then count it as ready
+        def _fold(p):
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = None
+                self._on_grad_ready(p)
+
+        for p in {id(q): q for b in self.buckets for q in b["params"]}.values():
+            p.register_post_accumulate_grad_hook(_fold)
         if self.mode == "fused":
             lib = _native.kernels()
             self.p_buf, self.g_buf = self._symm_of(a.params), self._symm_of(a.grads)

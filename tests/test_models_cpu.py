@@ -1,0 +1,83 @@
+"""Model families on CPU: ResNet shapes / registry, Llama generation utilities (sampling filters,
+cached generate == full recompute, beam search, speculative decoding == greedy)."""
+import pytest
+import torch
+
+from ferrotorch_b200.models import generation as G
+from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+from ferrotorch_b200.models.resnet import create_model, list_models, resnet18, resnet50
+from ferrotorch_b200.train import FlatTrainer
+
+
+def test_resnet_shapes_registry_and_training_step():
+    m = resnet50(num_classes=10)
+    assert sum(p.numel() for p in m.parameters()) == 23_528_522
+    assert m(torch.randn(2, 3, 64, 64)).shape == (2, 10)
+    assert "resnet50" in list_models() and isinstance(create_model("resnet18", num_classes=3), type(resnet18()))
+    with pytest.raises(KeyError):
+        create_model("no_such_model")
+    small = resnet18(num_classes=4)
+    tr = FlatTrainer(small, optimizer="sgd", lr=0.05, momentum=0.9, weight_decay=1e-4,
+                     loss_fn=lambda mod, x, y: torch.nn.functional.cross_entropy(mod(x), y))
+    x, y = torch.randn(8, 3, 32, 32), torch.randint(0, 4, (8,))
+    losses = [float(tr.step(x, y)) for _ in range(6)]
+    assert losses[-1] < losses[0]
+
+
+def _tiny():
+    cfg = LlamaConfig.tiny()
+    cfg.num_hidden_layers = 2
+    torch.manual_seed(0)
+    return LlamaForCausalLM(cfg).eval()
+
+
+def test_sampling_filters():
+    logits = torch.tensor([[1.0, 3.0, 2.0, 0.0]])
+    assert G.filter_top_k_top_p(logits, top_k=2).isinf().sum() == 2
+    kept = G.filter_top_k_top_p(logits, top_p=0.7)
+    assert not kept[0, 1].isinf() and not kept[0, 2].isinf() and kept[0, 3].isinf()
+    pen = G.apply_repetition_penalty(torch.tensor([[2.0, -2.0, 1.0]]), torch.tensor([[0, 1]]), 2.0)
+    assert pen.tolist() == [[1.0, -4.0, 1.0]]
+    cfg = G.GenerationConfig(do_sample=True, temperature=0.7, top_k=3, seed=1)
+    g = torch.Generator().manual_seed(1)
+    t = G.sample_next(torch.randn(5, 50), cfg, generator=g)
+    assert t.shape == (5,)
+
+
+def test_cached_generate_matches_full_recompute_and_streams():
+    m = _tiny()
+    ids = torch.randint(0, 4096, (2, 7), generator=torch.Generator().manual_seed(3))
+    seen = []
+    out = G.generate(m, ids, G.GenerationConfig(max_new_tokens=5), streamer=seen.append)
+    ref = ids
+    with torch.no_grad():
+        for _ in range(5):
+            ref = torch.cat([ref, m(ref, last_token_only=True)[:, -1].argmax(-1)[:, None]], 1)
+    assert torch.equal(out, ref) and len(seen) == 5
+    eos = int(out[0, 8])
+    stopped = G.generate(m, ids[:1], G.GenerationConfig(max_new_tokens=5, eos_token_id=eos))
+    assert stopped.shape[1] <= 12 and int(stopped[0, -1]) == eos
+
+
+def test_beam_search_and_speculative_decoding():
+    m = _tiny()
+    ids = torch.randint(0, 4096, (1, 5), generator=torch.Generator().manual_seed(4))
+    greedy = G.generate(m, ids, G.GenerationConfig(max_new_tokens=6))
+    beam1 = G.beam_search(m, ids, num_beams=1, max_new_tokens=6)
+    assert torch.equal(beam1, greedy)
+    beam4 = G.beam_search(m, ids, num_beams=4, max_new_tokens=6)
+
+    def logp(seq):
+        with torch.no_grad():
+            lp = m(seq[:, :-1]).float().log_softmax(-1)
+        return float(lp[0, 4:].gather(-1, seq[0, 5:, None]).sum())
+
+    assert logp(beam4) >= logp(greedy) - 1e-4
+    cfg2 = LlamaConfig.tiny()
+    cfg2.num_hidden_layers = 1
+    torch.manual_seed(9)
+    draft = LlamaForCausalLM(cfg2).eval()
+    out, stats = G.speculative_decode(m, draft, ids, max_new_tokens=6, gamma=3)
+    assert torch.equal(out, greedy) and stats["proposed"] >= stats["accepted"] and stats["target_calls"] <= 6
+    out2, stats2 = G.speculative_decode(m, m, ids, max_new_tokens=6, gamma=3)
+    assert torch.equal(out2, greedy) and stats2["accepted"] == stats2["proposed"]
