@@ -1,0 +1,305 @@
+// GEMMs whose weight operand is expanded on the fly inside the tcgen05 main loop (sm_100a):
+//
+//   mode Q4_0   Y[M,N] = X[M,K] * dequant(Wq)[N,K]^T, GGUF Q4_0 weights (32-element blocks, fp16
+//               scale + 16 nibble bytes; element j = low nibble of byte j, element j+16 = high
+//               nibble, value = (q - 8) * d -- ferrotorch-serialize/src/gguf.rs:543-577).  The
+//               reference dequantises the whole tensor to f32 on the GPU, bounces it through the
+//               host and stores bf16 (ferrotorch-llama/src/gpu_gguf.rs:14-27); it has no fused
+//               dequant-GEMM.  Here the weights stay 4-bit in HBM (0.5625 bytes / element).
+//   mode SP24   Y = X * W^T with W in 2:4 semi-structured form: per group of 4 consecutive K
+//               elements two kept values (bf16) and two 2-bit positions (one metadata nibble per
+//               group).  The reference calls cuSPARSELt (ferrotorch-gpu/src/cusparselt.rs:547-932);
+//               this kernel keeps the compressed form in HBM (0.5625 bytes / element-slot) and
+//               expands tiles in the producer, so memory-bound shapes gain the bandwidth while the
+//               math runs as dense MMAs.
+//
+// Structure = the dense GEMM (gemm_tcgen05.cu) with the B-side TMA load replaced by four
+// "expander" warps: thread r owns row r of the 128 x 64 B tile, reads its compressed bytes with
+// plain loads, expands to 64 bf16 in registers and writes one 128-byte row in the swizzled
+// K-major layout the MMA descriptor expects (fence.proxy.async, then arrive on the stage's
+// full barrier).  A comes by TMA.  All waits are bounded.
+#include "ft_host.h"
+#include "ft_ptx.cuh"
+
+namespace ft {
+
+constexpr int QG_BM = 128, QG_BN = 128, QG_BK = 64;
+constexpr int QG_THREADS = 384;
+constexpr int QG_A_BYTES = QG_BM * QG_BK * 2, QG_B_BYTES = QG_BN * QG_BK * 2;
+constexpr int QG_STAGE = QG_A_BYTES + QG_B_BYTES;
+constexpr int QG_STAGES = 6;
+constexpr int QG_SMEM = QG_STAGES * QG_STAGE + 1024 + 256;
+
+struct QgParams {
+  int mode;  // 0 = Q4_0, 1 = SP24
+  void* C; long long ldc; int out_f32;
+  const void* bias;
+  int M, N, K;
+  // Q4_0: nibbles [N, K/2] u8, scales [N, K/32] fp16.  SP24: values [N, K/2] bf16, meta [N, K/8] u8
+  const uint8_t* w0;
+  const uint8_t* w1;
+  int* status;
+};
+
+__device__ __forceinline__ void store_row_unit(uint32_t row_base, int r, int u, uint4 v) {
+  const uint32_t addr = row_base + ((u ^ (r & 7)) << 4);
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__global__ void __launch_bounds__(QG_THREADS, 1)
+expand_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const QgParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + QG_STAGES * QG_STAGE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * QG_STAGES + 4);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem), bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (QG_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * QG_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * QG_STAGES + 2 + a); };
+  const int m_blocks = (p.M + QG_BM - 1) / QG_BM, n_blocks = (p.N + QG_BN - 1) / QG_BN;
+  const int num_tiles = m_blocks * n_blocks, k_blocks = (p.K + QG_BK - 1) / QG_BK;
+  // m fastest: consecutive CTAs share the (expensive to expand) weight rows through L2
+  auto coords = [&](int t, int& mb, int& nb) { mb = t % m_blocks; nb = t / m_blocks; };
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < QG_STAGES; ++s) { mbar_init(full_bar(s), 1 + 4); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+  }
+  if (warp == 2) { tmem_alloc(smem_u32(tmem_slot), 2 * QG_BN); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb; coords(tile, mb, nb);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), QG_A_BYTES);
+          tma_load_2d(smem_base + stage * QG_STAGE, &tmA, full_bar(stage), kb * QG_BK, mb * QG_BM);
+          if (++stage == QG_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (*abort_word) { const unsigned long long t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000); }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(QG_BM, QG_BN, 1, 0, 0);
+      int stage = 0, acc = 0; uint32_t phase = 0, acc_phase = 0; bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * QG_BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_word, FT_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * QG_STAGE, sB = sA + QG_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < QG_BK / 16; ++k)
+            umma_f16_ss(d, make_smem_desc_sw128(sA + k * 32, 16, 1024), make_smem_desc_sw128(sB + k * 32, 16, 1024),
+                        idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(stage));
+          if (++stage == QG_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 8) {
+    // ---------------------------------------------------------------- expander warps
+    const int r = (warp - 8) * 32 + lane;  // row of the B tile
+    int stage = 0; uint32_t phase = 0; bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int mb, nb; coords(tile, mb, nb);
+      const int n = nb * QG_BN + r;
+      const bool row_ok = n < p.N;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int k0 = kb * QG_BK;
+        // fetch the compressed bytes first, then wait for the slot
+        uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0, q2 = q0, q3 = q0;
+        uint32_t aux0 = 0, aux1 = 0;
+        const bool k_ok = k0 + QG_BK <= p.K;  // K is a multiple of 64 (checked by the host)
+        if (row_ok && k_ok) {
+          if (p.mode == 0) {
+            const uint8_t* nb_ptr = p.w0 + static_cast<long long>(n) * (p.K >> 1) + (k0 >> 1);
+            q0 = __ldg(reinterpret_cast<const uint4*>(nb_ptr));
+            q1 = __ldg(reinterpret_cast<const uint4*>(nb_ptr) + 1);
+            aux0 = __ldg(reinterpret_cast<const uint32_t*>(p.w1 + (static_cast<long long>(n) * (p.K >> 5) + (k0 >> 5)) * 2));
+          } else {
+            const uint8_t* v_ptr = p.w0 + (static_cast<long long>(n) * (p.K >> 1) + (k0 >> 1)) * 2;
+            q0 = __ldg(reinterpret_cast<const uint4*>(v_ptr));
+            q1 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 1);
+            q2 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 2);
+            q3 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 3);
+            const uint2 mt = __ldg(reinterpret_cast<const uint2*>(p.w1 + static_cast<long long>(n) * (p.K >> 3) + (k0 >> 3)));
+            aux0 = mt.x; aux1 = mt.y;
+          }
+        }
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+        const uint32_t row_base = smem_base + stage * QG_STAGE + QG_A_BYTES + r * 128;
+        if (p.mode == 0) {
+          const uint32_t nib[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(blk ? (aux0 >> 16) : (aux0 & 0xFFFF))));
+#pragma unroll
+            for (int hi = 0; hi < 2; ++hi) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                // 8 elements: nibbles (low or high) of bytes [half*8, half*8+8) of this block
+                const uint32_t w0 = nib[blk * 4 + half * 2] >> (hi * 4), w1 = nib[blk * 4 + half * 2 + 1] >> (hi * 4);
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[j] = (static_cast<float>((w0 >> (8 * j)) & 0xF) - 8.f) * d;
+                  f[4 + j] = (static_cast<float>((w1 >> (8 * j)) & 0xF) - 8.f) * d;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                store_row_unit(row_base, r, blk * 4 + hi * 2 + half, o);
+              }
+            }
+          }
+        } else {
+          // 16 groups of 4 slots; group g: two bf16 values vals[2g], vals[2g+1] at slots (m & 3), (m >> 2)
+          const uint32_t vals[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                     q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {        // one 16-byte unit = 8 slots = 2 groups
+            uint32_t outw[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int gg = 0; gg < 2; ++gg) {
+              const int g = u * 2 + gg;
+              const uint32_t m4 = ((g < 8 ? aux0 : aux1) >> ((g & 7) * 4)) & 0xF;
+              const uint32_t pair = vals[g];
+              const uint32_t v_lo = pair & 0xFFFFu, v_hi = pair >> 16;
+              const int p0 = m4 & 3, p1 = m4 >> 2;
+              // slot s of the group lives in half-word (s & 1) of word gg*2 + (s >> 1)
+              outw[gg * 2 + (p0 >> 1)] |= v_lo << ((p0 & 1) * 16);
+              outw[gg * 2 + (p1 >> 1)] |= v_hi << ((p1 & 1) * 16);
+            }
+            store_row_unit(row_base, r, u, make_uint4(outw[0], outw[1], outw[2], outw[3]));
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(stage));
+        if (++stage == QG_STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int mb, nb; coords(tile, mb, nb);
+      const int m0 = mb * QG_BM, n0 = nb * QG_BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int row = m0 + ew * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * QG_BN;
+#pragma unroll 1
+      for (int c = 0; c < QG_BN / 32; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_row + c * 32, rr);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row >= p.M || col0 >= p.N) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 + 8 > p.N) continue;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[j] = __uint_as_float(rr[g * 8 + j]);
+            if (p.bias) v[j] += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col0 + g * 8 + j]);
+          }
+          if (p.out_f32) {
+            float* o = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0 + g * 8;
+            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0 + g * 8) = o;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * QG_BN); }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status) atomicCAS(p.status, 0, *abort_word);
+}
+
+static int launch_expand(const void* x, const QgParams& p0, long long ldx, int device, cudaStream_t stream) {
+  QgParams p = p0;
+  CUtensorMap tmA;
+  int rc = make_tmap_2d(&tmA, x, 2, p.K, p.M, ldx * 2, QG_BK, QG_BM, 3);
+  if (rc) return rc;
+  static bool attr_set[64] = {false};
+  if (!attr_set[device]) {
+    FT_CUDA_CHECK(cudaFuncSetAttribute(expand_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QG_SMEM));
+    attr_set[device] = true;
+  }
+  p.status = device_status_word(device);
+  const int tiles = ((p.M + QG_BM - 1) / QG_BM) * ((p.N + QG_BN - 1) / QG_BN);
+  const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+  expand_gemm_tcgen05_kernel<<<grid, QG_THREADS, QG_SMEM, stream>>>(tmA, p);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+// y[M,N] = x[M,K] (bf16, row stride ldx) * dequant_q4_0(nibbles [N, K/2], scales fp16 [N, K/32])^T (+ bias).
+FT_API int ft_q4_0_gemm(const void* x, const void* nibbles, const void* scales, void* y, const void* bias, int M,
+                        int N, int K, long long ldx, long long ldy, int out_f32, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  FT_REQUIRE(x && nibbles && scales && y, "ft_q4_0_gemm: null pointer");
+  FT_REQUIRE(M > 0 && N > 0 && K > 0 && K % 64 == 0 && N % 8 == 0 && ldx % 8 == 0 && ldy % (out_f32 ? 4 : 8) == 0,
+             "ft_q4_0_gemm: K must be a multiple of 64, N of 8");
+  FT_REQUIRE((reinterpret_cast<uintptr_t>(nibbles) & 15) == 0 && (reinterpret_cast<uintptr_t>(scales) & 3) == 0,
+             "ft_q4_0_gemm: nibble plane must be 16-byte aligned");
+  QgParams p{};
+  p.mode = 0; p.C = y; p.ldc = ldy; p.out_f32 = out_f32; p.bias = bias; p.M = M; p.N = N; p.K = K;
+  p.w0 = static_cast<const uint8_t*>(nibbles); p.w1 = static_cast<const uint8_t*>(scales);
+  return launch_expand(x, p, ldx, device, stream);
+}
+
+// y[M,N] = x[M,K] * W^T with W 2:4-compressed: values bf16 [N, K/2], meta u8 [N, K/8] (one nibble
+// per group of 4: bits 0-1 = slot of the first kept value, bits 2-3 = slot of the second).
+FT_API int ft_sparse24_gemm(const void* x, const void* values, const void* meta, void* y, const void* bias, int M,
+                            int N, int K, long long ldx, long long ldy, int out_f32, int device,
+                            cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  FT_REQUIRE(x && values && meta && y, "ft_sparse24_gemm: null pointer");
+  FT_REQUIRE(M > 0 && N > 0 && K > 0 && K % 64 == 0 && N % 8 == 0 && ldx % 8 == 0 && ldy % (out_f32 ? 4 : 8) == 0,
+             "ft_sparse24_gemm: K must be a multiple of 64, N of 8");
+  FT_REQUIRE((reinterpret_cast<uintptr_t>(values) & 15) == 0 && (reinterpret_cast<uintptr_t>(meta) & 7) == 0,
+             "ft_sparse24_gemm: value plane must be 16-byte aligned, metadata 8-byte aligned");
+  QgParams p{};
+  p.mode = 1; p.C = y; p.ldc = ldy; p.out_f32 = out_f32; p.bias = bias; p.M = M; p.N = N; p.K = K;
+  p.w0 = static_cast<const uint8_t*>(values); p.w1 = static_cast<const uint8_t*>(meta);
+  return launch_expand(x, p, ldx, device, stream);
+}
