@@ -109,7 +109,7 @@ def reference_unavailable() -> None:
     print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
-def build_model(args, device):
+def build_model(args, device, dtype=None):
     import torch
 
     from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
@@ -126,7 +126,7 @@ def build_model(args, device):
         cfg.num_hidden_layers = args.layers
     cfg.max_position_embeddings = max(args.seq_len, 2048)
     prev = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)
+    torch.set_default_dtype(dtype or torch.bfloat16)
     try:
         with torch.device(device):
             model = LlamaForCausalLM(cfg)
@@ -134,6 +134,74 @@ def build_model(args, device):
         torch.set_default_dtype(prev)
     model.model.checkpoint_layers = args.checkpoint
     return cfg, model
+
+
+def run_torch_baseline(args, cfg, model, device, world, rank, local_rank) -> None:
+    """Same model, same data, same step, in plain PyTorch on the same box: fp32 parameters with
+    bf16 autocast (cuBLAS GEMMs, SDPA attention, torch RMSNorm / cross-entropy),
+    ``torch.optim.AdamW(fused=True)``, DistributedDataParallel over NCCL for N > 1."""
+    import contextlib
+
+    import torch
+    import torch.distributed as dist
+
+    from ferrotorch_b200.ops import functional as F
+
+    F.set_native(False)
+    model = model.float()
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank]) if world > 1 else model
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
+    B, S, V, mb = args.batch_per_gpu, args.seq_len, cfg.vocab_size, args.micro_batches
+    gen = torch.Generator().manual_seed(rank)
+    host = [torch.randint(0, V, (B, S + 1), generator=gen).pin_memory() for _ in range(3)]
+    dev = [t.to(device) for t in host]
+    per = B // mb
+
+    def step(t):
+        opt.zero_grad(set_to_none=True)
+        total = 0.0
+        for i in range(mb):
+            x, y = t[i * per:(i + 1) * per, :-1], t[i * per:(i + 1) * per, 1:]
+            sync = contextlib.nullcontext() if (world == 1 or i == mb - 1) else net.no_sync()
+            with sync:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = net(x, labels=y, loss_denominator=B * S)
+                loss.backward()
+            total = total + loss.detach()
+        opt.step()
+        return total
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(dev[i % 3])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        loss = step(dev[i % 3])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t)
+    if rank == 0:
+        print(json.dumps({"metric": "llama3_8b_train_tokens_per_s", "impl": "torch", "value": B * S * world * args.steps / (ms / 1e3),
+                          "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms / args.steps, "dtype": "bf16 autocast, fp32 params", "data": "synthetic",
+                          "config": {"model": "Llama-3-8B" if args.layers is None else "layers=%d" % cfg.num_hidden_layers,
+                                     "global_batch": B * world, "seq_len": S, "micro_batches": mb},
+                          "clocks": clocks, "loss": float(loss), "gpu_launches": 0}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main() -> None:
@@ -160,10 +228,14 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=device)
 
     torch.manual_seed(1234 + rank)
-    cfg, model = build_model(args, device)
+    cfg, model = build_model(args, device, dtype=torch.float32 if args.impl == "torch" else torch.bfloat16)
     model.train()
 
     from ferrotorch_b200.train.engine import FlatTrainer
+
+    if args.impl == "torch":
+        run_torch_baseline(args, cfg, model, device, world, rank, local_rank)
+        return
 
     ddp = None
     if world > 1:

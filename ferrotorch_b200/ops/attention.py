@@ -66,7 +66,7 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal
     """``softmax(q k^T * scale + mask) v`` for ``q [B,Sq,Hq,D]``, ``k/v [B,Sk,Hkv,D]``; returns
     ``[B,Sq,Hq,D]``.  ``Hq`` must be a multiple of ``Hkv`` (query head h uses kv head
     ``h // (Hq/Hkv)``, the ``repeat_kv`` order of ferrotorch-gpu/src/bf16.rs:2405-2410)."""
-    native = q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+    native = F.native_enabled() and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
     if not native:
         if q.is_cuda:
             # head dims without a native kernel: library attention, explicit and counted
@@ -146,7 +146,7 @@ def qkv_attention(x: torch.Tensor, w_qkv: torch.Tensor, bias: torch.Tensor | Non
                   n_heads: int, n_kv_heads: int, head_dim: int, causal: bool = True,
                   interleaved: bool = False) -> torch.Tensor:
     """Self-attention core from the normed hidden states: ``attn(rope(x W_qkv^T))`` -> ``[B, S, Hq*D]``."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and head_dim in (64, 128):
+    if F.native_enabled() and x.is_cuda and x.dtype == torch.bfloat16 and head_dim in (64, 128):
         return _QKVAttentionFn.apply(x, w_qkv, bias, cos, sin, n_heads, n_kv_heads, head_dim, causal,
                                      interleaved)
     B, S, _ = x.shape

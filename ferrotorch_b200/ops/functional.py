@@ -24,6 +24,21 @@ _ACT_FLAGS = {None: 0, "relu": GEMM_RELU, "gelu": GEMM_GELU, "silu": GEMM_SILU}
 
 stats = {"gemm_native": 0, "gemm_library": 0}
 
+_NATIVE = True
+
+
+def set_native(enabled: bool) -> bool:
+    """Route every op of this module to its plain-PyTorch path (``False``) or back to the native
+    kernels (``True``).  Used to measure a same-model PyTorch baseline; returns the old setting."""
+    global _NATIVE
+    old, _NATIVE = _NATIVE, bool(enabled)
+    return old
+
+
+def native_enabled() -> bool:
+    return _NATIVE
+
+
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
@@ -151,7 +166,7 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T + bias`` with ``w [out, in]`` (ferrotorch-nn/src/linear.rs:166-211)."""
-    if not x.is_cuda or x.dtype != torch.bfloat16:
+    if not _NATIVE or not x.is_cuda or x.dtype != torch.bfloat16:
         return torch.nn.functional.linear(x, w, bias)
     return _LinearFn.apply(x, w, bias)
 
@@ -239,7 +254,13 @@ class _RMSNormFn(torch.autograd.Function):
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5,
             residual: torch.Tensor | None = None):
     """RMSNorm; with ``residual`` returns ``(norm(x + residual), x + residual)`` from one kernel."""
-    if not x.is_cuda or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+    if not _NATIVE and x.is_cuda:
+        # plain-PyTorch baseline path: torch's own fused RMSNorm
+        if residual is not None:
+            x = x + residual
+        y = torch.nn.functional.rms_norm(x, (x.shape[-1],), weight.to(x.dtype), eps)
+        return (y, x) if residual is not None else y
+    if not _NATIVE or not x.is_cuda or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         return ref.rmsnorm(x, weight, eps, residual)
     return _RMSNormFn.apply(x, weight, eps, residual)
 
@@ -287,7 +308,7 @@ def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, positions: t
     from ``positions`` (int tensor ``[T]``) or ``(t % seq_len) + pos_offset``."""
     H = x.shape[-2]
     n_rot = H if n_rot_heads is None else n_rot_heads
-    if not x.is_cuda or x.dtype != torch.bfloat16:
+    if not _NATIVE or not x.is_cuda or x.dtype != torch.bfloat16:
         T = x.numel() // (x.shape[-1] * H)
         if positions is None:
             positions = (torch.arange(T, device=x.device) % seq_len) + pos_offset
@@ -334,7 +355,7 @@ _ACT_ID = {"silu": 0, "relu": 1, "gelu": 2}
 def swiglu(gu: torch.Tensor, activation: str = "silu") -> torch.Tensor:
     """``act(gate) * up`` for a packed ``[..., 2F]`` projection output."""
     act = _ACT_ID[activation]
-    if not gu.is_cuda or gu.dtype != torch.bfloat16 or (gu.shape[-1] // 2) % 8:
+    if not _NATIVE or not gu.is_cuda or gu.dtype != torch.bfloat16 or (gu.shape[-1] // 2) % 8:
         return ref.swiglu(gu, act)
     return _SwiGLUFn.apply(gu, act)
 
@@ -380,7 +401,7 @@ class _EmbeddingFn(torch.autograd.Function):
 
 def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """Row gather ``weight[ids]`` (ferrotorch-gpu/src/bf16.rs:1065); the backward scatter-adds rows."""
-    if not weight.is_cuda or weight.dtype != torch.bfloat16 or weight.shape[1] % 8:
+    if not _NATIVE or not weight.is_cuda or weight.dtype != torch.bfloat16 or weight.shape[1] % 8:
         return torch.nn.functional.embedding(ids, weight)
     return _EmbeddingFn.apply(ids, weight)
 
@@ -475,7 +496,7 @@ def linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, target: torch.Te
     h2 = h.reshape(-1, h.shape[-1])
     t2 = target.reshape(-1)
     n = num_valid if num_valid is not None else t2.numel()
-    if not h.is_cuda or h.dtype != torch.bfloat16:
+    if not _NATIVE or not h.is_cuda or h.dtype != torch.bfloat16:
         z = torch.nn.functional.linear(h2, weight)
         return torch.nn.functional.cross_entropy(z.float(), t2, ignore_index=ignore_index, reduction="sum") / n
     return _LinearCrossEntropyFn.apply(h2.contiguous(), weight, t2, ignore_index, chunk_rows, n)
