@@ -46,7 +46,7 @@ def parse_args():
                     "the JSON line then reports the reduced model and is not a headline number)")
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--batch-per-gpu", type=int, default=4)
-    ap.add_argument("--micro-batches", type=int, default=4)
+    ap.add_argument("--micro-batches", type=int, default=2)
     ap.add_argument("--checkpoint", action="store_true", help="recompute each decoder layer in backward")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
