@@ -375,3 +375,56 @@ FT_API int ft_allgather(void* const* src_ptrs, void* out, long long bytes_per_ra
   count_launch(2);
   return FT_E_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Device-resident epochs.  A kernel argument is frozen when a CUDA graph is captured, so the
+// graph-replayable variants keep each slot's epoch in device memory: the signal kernel
+// increments it and publishes the new value, the wait kernel compares against the current
+// value.  All ranks run the same launch sequence, so their counters advance in lockstep.
+namespace ft {
+__global__ void comm_signal_dev_kernel(PeerTable flags, int kind, int slot, int n_slots, int rank, int world,
+                                       uint32_t* epoch_dev) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_dev + 1u;
+    *epoch_dev = s_epoch;
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(flags.ptr[threadIdx.x]) + flag_index(kind, slot, rank, n_slots), s_epoch);
+  }
+}
+__global__ void comm_wait_dev_kernel(const uint32_t* my_flags, int kind, int slot, int n_slots, int world,
+                                     const uint32_t* epoch_dev, unsigned long long limit_ns, int* status) {
+  const uint32_t epoch = *epoch_dev;
+  if (epoch == 0u) return;  // slot never used
+  wait_flags(my_flags + flag_index(kind, slot, 0, n_slots), world, epoch, limit_ns, status);
+}
+}  // namespace ft
+
+// Raise flag (kind, slot) on every peer to ++(*epoch_dev).
+FT_API int ft_comm_signal_dev(void* const* flag_ptrs, int kind, int slot, int n_slots, int rank, int world,
+                              unsigned int* epoch_dev, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  PeerTable t;
+  FT_REQUIRE(epoch_dev && world >= 1 && world <= COMM_MAX_RANKS && fill_table(t, flag_ptrs, world) == 0,
+             "ft_comm_signal_dev: bad arguments");
+  comm_signal_dev_kernel<<<1, 32, 0, stream>>>(t, kind, slot, n_slots, rank, world, epoch_dev);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+// Wait until every peer raised flag (kind, slot) to the current *epoch_dev (no-op while it is 0).
+FT_API int ft_comm_wait_dev(const void* my_flags, int kind, int slot, int n_slots, int world,
+                            const unsigned int* epoch_dev, long long timeout_ms, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  FT_REQUIRE(my_flags && epoch_dev && slot >= 0 && slot < n_slots, "ft_comm_wait_dev: bad arguments");
+  const unsigned long long limit = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
+  comm_wait_dev_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t*>(my_flags), kind, slot, n_slots, world,
+                                            epoch_dev, limit, device_status_word(device));
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}

@@ -64,6 +64,7 @@ struct TpParams {
   // both
   unsigned int* done_counter;            // local, zero at entry
   TpPeers flags; int slot, n_slots; uint32_t epoch;
+  uint32_t* epoch_dev;                   // optional device-resident epoch (CUDA-graph replay), see below
   unsigned long long limit_ns;
   int* status;
 };
@@ -116,6 +117,10 @@ template <int BN>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const TpParams p) {
+  // With a device-resident epoch the value is read here instead of from the (frozen) argument:
+  // mode 0 uses the value its signal kernel just published, mode 1 uses current + 1 and the
+  // last CTA publishes it at the end.
+  const uint32_t epoch = p.epoch_dev ? *p.epoch_dev + (p.mode == 1 ? 1u : 0u) : p.epoch;
   using Cfg = TpCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -183,7 +188,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int i = 1; i < p.world; ++i) {
       const int s = (p.rank + i) % p.world;
       if (threadIdx.x == 0)
-        s_ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, s, p.n_slots), p.epoch, p.limit_ns, abort_word) ? 1 : 0;
+        s_ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, s, p.n_slots), epoch, p.limit_ns, abort_word) ? 1 : 0;
       __syncthreads();
       if (!s_ok) break;
       const __nv_bfloat16* src_base = static_cast<const __nv_bfloat16*>(p.xg.ptr[s]);
@@ -193,13 +198,22 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int r0 = max(row_lo, mb * TP_BM), r1 = min(row_hi, (mb + 1) * TP_BM);
         const int vec_per_row = p.K >> 3;
         const long long total = static_cast<long long>(r1 - r0) * vec_per_row;
-        for (long long v = threadIdx.x; v < total; v += blockDim.x) {
-          const int r = r0 + static_cast<int>(v / vec_per_row), c = static_cast<int>(v % vec_per_row) << 3;
-          uint4 val;
-          asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
-                       : "l"(src_base + static_cast<long long>(r) * p.ldx + c) : "memory");
-          *reinterpret_cast<uint4*>(dst_base + static_cast<long long>(r) * p.ldx + c) = val;
+        // 4 independent 16-byte peer loads in flight per thread before the first store
+        for (long long v0 = threadIdx.x; v0 < total; v0 += 4LL * blockDim.x) {
+          uint4 val[4];
+          long long off[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const long long v = v0 + static_cast<long long>(u) * blockDim.x;
+            const long long vv = v < total ? v : v0;
+            off[u] = static_cast<long long>(r0 + static_cast<int>(vv / vec_per_row)) * p.ldx + (static_cast<int>(vv % vec_per_row) << 3);
+            asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(val[u].x), "=r"(val[u].y), "=r"(val[u].z), "=r"(val[u].w)
+                         : "l"(src_base + off[u]) : "memory");
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + static_cast<long long>(u) * blockDim.x < total) *reinterpret_cast<uint4*>(dst_base + off[u]) = val[u];
         }
         __threadfence();
         tp_fence_proxy_async();  // the consumers read these rows through TMA (async proxy)
@@ -274,10 +288,10 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    if (p.mode == 1 && p.epoch > 1) {
+    if (p.mode == 1 && epoch > 1) {
       // the owners must have finished reducing the previous use of their staging buffers
       if (lane < p.world)
-        ok = tp_spin_ge<true>(my_flags + tp_flag_index(1, p.slot, lane, p.n_slots), p.epoch - 1, p.limit_ns, abort_word);
+        ok = tp_spin_ge<true>(my_flags + tp_flag_index(1, p.slot, lane, p.n_slots), epoch - 1, p.limit_ns, abort_word);
       ok = __all_sync(0xffffffffu, ok);
     }
     for (int tile = cta; tile < num_tiles && ok; tile += n_gemm) {
@@ -340,7 +354,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (v + 1 == expected) {
               p.owner_counter[o] = 0u;
               __threadfence_system();
-              tp_st_release_sys(static_cast<uint32_t*>(p.flags.ptr[o]) + tp_flag_index(0, p.slot, p.rank, p.n_slots), p.epoch);
+              tp_st_release_sys(static_cast<uint32_t*>(p.flags.ptr[o]) + tp_flag_index(0, p.slot, p.rank, p.n_slots), epoch);
             }
           }
         }
@@ -353,7 +367,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (p.mode == 1 && ok) {
       // ---------------------------------------------------------- reduce the staged partials
       if (lane < p.world)
-        ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, lane, p.n_slots), p.epoch, p.limit_ns, abort_word);
+        ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, lane, p.n_slots), epoch, p.limit_ns, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         const __nv_bfloat16* st = static_cast<const __nv_bfloat16*>(p.stage.ptr[p.rank]);
@@ -404,11 +418,12 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // last CTA: reset the local counters for the next launch and tell every peer that this
       // rank no longer reads their buffers (mode 0) / has consumed its staging buffer (mode 1)
       *p.done_counter = 0u;
+      if (p.epoch_dev && p.mode == 1) *p.epoch_dev = epoch;
       if (p.mode == 0)
         for (int mb = 0; mb < m_blocks; ++mb) p.blk_ready[mb] = 0u;
       __threadfence_system();
       for (int r = 0; r < p.world; ++r)
-        tp_st_release_sys(static_cast<uint32_t*>(p.flags.ptr[r]) + tp_flag_index(1, p.slot, p.rank, p.n_slots), p.epoch);
+        tp_st_release_sys(static_cast<uint32_t*>(p.flags.ptr[r]) + tp_flag_index(1, p.slot, p.rank, p.n_slots), epoch);
     }
   }
 }
@@ -461,8 +476,8 @@ FT_API long long ft_tp_counter_words(int M) { return 16 + (M + TP_BM - 1) / TP_B
 FT_API int ft_tp_ag_gemm(void* const* xg_ptrs, const void* w, void* y, const void* bias, int M, int N, int K,
                          long long ldx, long long ldw, long long ldy, int rank, int world, int rows_per_rank,
                          unsigned int* counters, void* const* flag_ptrs, int slot, int n_slots,
-                         unsigned int epoch, int n_copy, long long timeout_ms, int device,
-                         cudaStream_t stream) {
+                         unsigned int epoch, unsigned int* epoch_dev, int n_copy, long long timeout_ms,
+                         int device, cudaStream_t stream) {
   if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world, "ft_tp_ag_gemm: bad rank/world");
   FT_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0,
@@ -475,12 +490,12 @@ FT_API int ft_tp_ag_gemm(void* const* xg_ptrs, const void* w, void* y, const voi
   for (int i = 0; i < TP_MAX_RANKS; ++i) p.stage.ptr[i] = nullptr;
   const int sms = sm_count(device);
   if (world == 1) n_copy = 0;
-  else if (n_copy <= 0) n_copy = 16;
+  else if (n_copy <= 0) n_copy = 32;
   if (n_copy > sms / 2) n_copy = sms / 2;
   p.mode = 0; p.M = M; p.N = N; p.K = K; p.rank = rank; p.world = world; p.rows_per_rank = rows_per_rank;
   p.C = static_cast<__nv_bfloat16*>(y); p.ldc = ldy; p.bias = bias; p.ldx = ldx;
   p.blk_ready = counters + 16; p.n_copy = n_copy; p.done_counter = counters; p.owner_counter = counters + 1;
-  p.slot = slot; p.n_slots = n_slots; p.epoch = epoch;
+  p.slot = slot; p.n_slots = n_slots; p.epoch = epoch; p.epoch_dev = epoch_dev;
   p.limit_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
   p.status = device_status_word(device);
   const int bn = pick_bn(M, N, sms - n_copy);
@@ -506,7 +521,7 @@ FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, 
                          int M, int N, int K, long long ldx, long long ldw, long long ldo, long long ldr,
                          int rank, int world, int rows_per_rank, unsigned int* counters,
                          void* const* flag_ptrs, int slot, int n_slots, unsigned int epoch,
-                         long long timeout_ms, int device, cudaStream_t stream) {
+                         unsigned int* epoch_dev, long long timeout_ms, int device, cudaStream_t stream) {
   if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world, "ft_tp_gemm_rs: bad rank/world");
   FT_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldo % 8 == 0 &&
@@ -523,7 +538,7 @@ FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, 
   p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
   p.done_counter = counters; p.owner_counter = counters + 1; p.blk_ready = counters + 16; p.n_copy = 0;
-  p.slot = slot; p.n_slots = n_slots; p.epoch = epoch;
+  p.slot = slot; p.n_slots = n_slots; p.epoch = epoch; p.epoch_dev = epoch_dev;
   p.limit_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
   p.status = device_status_word(device);
   const int bn = pick_bn(M, N, sms);

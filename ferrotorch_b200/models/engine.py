@@ -38,7 +38,7 @@ def _shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 class LlamaEngine:
     def __init__(self, cfg: LlamaConfig, tp: TPContext | None = None, *, max_batch: int = 64,
                  max_seq_len: int = 4096, block_size: int = 16, weights: dict | None = None, seed: int = 0,
-                 device=None, prefill_chunk_tokens: int = 16384):
+                 device=None, prefill_chunk_tokens: int = 16384, cuda_graph: bool = False):
         self.cfg = cfg
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.tp = tp if tp is not None else TPContext(None, self.device)
@@ -50,6 +50,8 @@ class LlamaEngine:
         self.H = cfg.hidden_size
         self.Vloc = (cfg.vocab_size + W - 1) // W
         self.prefill_chunk_tokens = prefill_chunk_tokens
+        self.cuda_graph = cuda_graph
+        self._graph, self._graph_batch, self._eager_steps = None, 0, 0
         self.max_batch = max_batch
         self.cos, self.sin = ref.rope_tables(cfg.head_dim, max(max_seq_len, 16), cfg.rope_theta, cfg.rope_scaling,
                                              device=self.device)
@@ -197,7 +199,11 @@ class LlamaEngine:
             self.manager.remove_sequence(b)
         self.seqs = [self.manager.add_sequence(S) for _ in range(B)]
         assert self.seqs == list(range(B)), "sequence slots must be 0..B-1 after a reset"
-        self.lengths = torch.full((B,), S, device=self.device, dtype=torch.int32)
+        if getattr(self, "lengths", None) is not None and self.lengths.numel() == B:
+            self.lengths.fill_(S)           # keep the tensor a captured graph refers to
+        else:
+            self.lengths = torch.full((B,), S, device=self.device, dtype=torch.int32)
+            self._graph = None
         per = max(1, self.prefill_chunk_tokens // S)
         firsts = []
         for b0 in range(0, B, per):
@@ -221,17 +227,45 @@ class LlamaEngine:
             firsts.append(self._next_tokens(last[lo2:hi2].to(torch.bfloat16).contiguous(), nb))
         return torch.cat(firsts)
 
-    @torch.no_grad()
-    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
-        """One greedy step: ``tokens [B]`` (the previous step's output) -> next tokens ``[B]``."""
+    def _decode_device(self, tokens: torch.Tensor) -> torch.Tensor:
+        """The device part of a decode step (everything a CUDA graph captures)."""
         B = tokens.numel()
-        for s in self.seqs:
-            self.manager.extend(s, 1)
         pos = self.lengths.clone()          # position of the new token
         self.lengths += 1
-        sid = torch.arange(B, device=self.device, dtype=torch.int32)
-        h = self._forward(tokens.to(self.device), pos, sid, B, 1, True, self.lengths)
+        h = self._forward(tokens, pos, self._sid, B, 1, True, self.lengths)
         return self._next_tokens(h, B)
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """One greedy step: ``tokens [B]`` (the previous step's output) -> next tokens ``[B]``.
+
+        With ``cuda_graph=True`` the device part is captured once (after two eager steps that size
+        every buffer) and replayed: the reference's ``GraphedDecoder`` idea
+        (ferrotorch-llama/src/gpu.rs:896-994) extended to the tensor-parallel step -- the fused
+        collective kernels keep their epochs in device memory, so a replay stays in step with
+        the other ranks."""
+        B = tokens.numel()
+        for s in self.seqs:
+            self.manager.extend(s, 1)       # host bookkeeping: new pages when a block fills up
+        self.cache.sync_table()
+        if getattr(self, "_sid", None) is None or self._sid.numel() != B:
+            self._sid = torch.arange(B, device=self.device, dtype=torch.int32)
+        tokens = tokens.to(self.device)
+        if not self.cuda_graph:
+            return self._decode_device(tokens)
+        if self._graph is not None and self._graph_batch == B:
+            self._tok_in.copy_(tokens)
+            self._graph.replay()
+            return self._tok_out.clone()
+        self._eager_steps += 1
+        if self._eager_steps <= 2:
+            return self._decode_device(tokens)
+        self._tok_in = tokens.clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._tok_out = self._decode_device(self._tok_in)
+        self._graph, self._graph_batch = g, B
+        return self._tok_out.clone()
 
     @torch.no_grad()
     def generate(self, prompts: torch.Tensor, max_new_tokens: int) -> torch.Tensor:

@@ -29,10 +29,12 @@ from .ddp import SymmetricBuffer, _ptr_array, CommTimeout
 _i, _ll, _f, _vp, _u = _native._i, _native._ll, _native._f, _native._vp, ctypes.c_uint
 _native.register_protos({
     "ft_tp_counter_words": (_ll, [_i]),
-    "ft_tp_ag_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _i, _i, _u, _i,
-                           _ll, _i, _vp]),
+    "ft_tp_ag_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _i, _i, _u, _vp,
+                           _i, _ll, _i, _vp]),
     "ft_tp_gemm_rs": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _i,
-                           _i, _u, _ll, _i, _vp]),
+                           _i, _u, _vp, _ll, _i, _vp]),
+    "ft_comm_signal_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "ft_comm_wait_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _ll, _i, _vp]),
 })
 
 
@@ -48,7 +50,7 @@ class _LocalBuffer:
 class TPContext:
     N_SLOTS = 8
 
-    def __init__(self, group=None, device=None, timeout_ms: int | None = None, n_copy: int = 16):
+    def __init__(self, group=None, device=None, timeout_ms: int | None = None, n_copy: int = 32):
         self.group = group
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
@@ -57,7 +59,9 @@ class TPContext:
         self.n_copy = n_copy
         lib = _native.kernels()
         self.flags = self._alloc(int(2 * self.N_SLOTS * 8), torch.int32)
-        self._epoch = [0] * self.N_SLOTS
+        # per-slot epochs live in device memory: the kernels advance them themselves, so a captured
+        # CUDA graph of a decode step replays correctly (a host-side epoch would be frozen in it)
+        self.epochs = torch.zeros(self.N_SLOTS, device=self.device, dtype=torch.int32)
         self._buffers: dict = {}
         self._counters: dict = {}
 
@@ -101,13 +105,16 @@ class TPContext:
     def wait_gather_buffer_free(self, slot: int) -> None:
         """Enqueue a wait until every peer has finished reading this rank's rows from the previous
         :meth:`ag_gemm` on ``slot`` (call before overwriting :meth:`my_rows`)."""
-        if self.world == 1 or self._epoch[slot] == 0:
+        if self.world == 1:
             return
         lib = _native.kernels()
-        rc = lib.ft_comm_wait(self.flags.ptrs[self.rank], 1, slot, 1, self.N_SLOTS, self.world,
-                              self._epoch[slot], self.timeout_ms, self.device.index,
-                              torch.cuda.current_stream().cuda_stream)
-        _native.check(rc, "ft_comm_wait")
+        rc = lib.ft_comm_wait_dev(self.flags.ptrs[self.rank], 1, slot, self.N_SLOTS, self.world,
+                                  self._epoch_ptr(slot), self.timeout_ms, self.device.index,
+                                  torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "ft_comm_wait_dev")
+
+    def _epoch_ptr(self, slot: int) -> int:
+        return self.epochs.data_ptr() + 4 * slot
 
     def ag_gemm(self, slot: int, M: int, w: torch.Tensor, bias: torch.Tensor | None = None,
                 out: torch.Tensor | None = None) -> torch.Tensor:
@@ -115,21 +122,18 @@ class TPContext:
         of ``slot``.  ``w``: ``[N_loc, K]``.  Returns ``[M, N_loc]``."""
         N, K = w.shape
         lib = _native.kernels()
-        self._epoch[slot] += 1
-        epoch = self._epoch[slot]
         stream = torch.cuda.current_stream().cuda_stream
         xg = self.buffer(("xg", slot), M * K)
-        if self.world > 1:
-            rc = lib.ft_comm_signal(self.flags.ptr_array, 0, slot, self.N_SLOTS, self.rank, self.world, epoch,
-                                    self.device.index, stream)
-            _native.check(rc, "ft_comm_signal")
+        rc = lib.ft_comm_signal_dev(self.flags.ptr_array, 0, slot, self.N_SLOTS, self.rank, self.world,
+                                    self._epoch_ptr(slot), self.device.index, stream)
+        _native.check(rc, "ft_comm_signal_dev")
         if out is None:
             out = torch.empty((M, N), device=self.device, dtype=torch.bfloat16)
         rc = lib.ft_tp_ag_gemm(xg.ptr_array, w.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
                                M, N, K, K, w.stride(0), out.stride(0), self.rank, self.world,
                                self.rows_per_rank(M), self.counters(("ag", slot), M).data_ptr(),
-                               self.flags.ptr_array, slot, self.N_SLOTS, epoch, self.n_copy, self.timeout_ms,
-                               self.device.index, stream)
+                               self.flags.ptr_array, slot, self.N_SLOTS, 0, self._epoch_ptr(slot), self.n_copy,
+                               self.timeout_ms, self.device.index, stream)
         _native.check(rc, "ft_tp_ag_gemm")
         return out
 
@@ -142,8 +146,6 @@ class TPContext:
         N = w.shape[0]
         ms = self.rows_per_rank(M)
         lib = _native.kernels()
-        self._epoch[slot] += 1
-        epoch = self._epoch[slot]
         stage = self.buffer(("stage", slot), self.world * ms * N)
         rows = max(0, min(ms, M - self.rank * ms))
         if out is None:
@@ -152,7 +154,7 @@ class TPContext:
                                residual.data_ptr() if residual is not None else None, M, N, K, x.stride(0),
                                w.stride(0), out.stride(0), residual.stride(0) if residual is not None else N,
                                self.rank, self.world, ms, self.counters(("rs", slot), M).data_ptr(),
-                               self.flags.ptr_array, slot, self.N_SLOTS, epoch, self.timeout_ms,
+                               self.flags.ptr_array, slot, self.N_SLOTS, 0, self._epoch_ptr(slot), self.timeout_ms,
                                self.device.index, torch.cuda.current_stream().cuda_stream)
         _native.check(rc, "ft_tp_gemm_rs")
         return out

@@ -62,8 +62,8 @@ def test_page_pool_bookkeeping():
     assert out.shape == (2, 1, 8)
 
 
-def _run(nproc, port):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+def _run(nproc, port, graph=False):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", FT_TEST_GRAPH="1" if graph else "0")
     script = os.path.join(HERE, "engine_worker.py")
     cmd = [sys.executable, script] if nproc == 1 else [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
@@ -82,3 +82,14 @@ def test_engine_single_gpu():
 @pytest.mark.multigpu
 def test_engine_tensor_parallel_2():
     _run(2, 29551)
+
+
+@pytest.mark.gpu
+def test_engine_single_gpu_cuda_graph():
+    _run(1, 0, graph=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_engine_tensor_parallel_2_cuda_graph():
+    _run(2, 29552, graph=True)
