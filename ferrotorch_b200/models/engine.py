@@ -265,6 +265,7 @@ class LlamaEngine:
         with torch.cuda.graph(g):
             self._tok_out = self._decode_device(self._tok_in)
         self._graph, self._graph_batch = g, B
+        g.replay()                           # capture only records; this executes the step
         return self._tok_out.clone()
 
     @torch.no_grad()
