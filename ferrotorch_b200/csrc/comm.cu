@@ -70,7 +70,8 @@ __device__ __forceinline__ bool wait_flags(const uint32_t* flags, int n, uint32_
     const unsigned long long t0 = globaltimer_ns();
     uint32_t backoff = 32;
     while (static_cast<int32_t>(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
-      if (globaltimer_ns() - t0 > limit_ns) {
+      // also give up at once when an earlier kernel already reported a lost peer
+      if ((status && *reinterpret_cast<const volatile int*>(status) != 0) || globaltimer_ns() - t0 > limit_ns) {
         s_fail = 1;
         if (status) atomicCAS(status, 0, FT_ERR_TIMEOUT_PEER);
         break;

@@ -89,12 +89,14 @@ __device__ __forceinline__ size_t tp_flag_index(int kind, int slot, int src, int
 // Bounded spin of ONE thread until *p >= want (acquire at the given scope).
 template <bool SYS>
 __device__ __forceinline__ bool tp_spin_ge(const uint32_t* p, uint32_t want, unsigned long long limit_ns,
-                                           volatile int* abort_word) {
+                                           volatile int* abort_word, const int* status = nullptr) {
   const unsigned long long t0 = globaltimer_ns();
   uint32_t backoff = 32;
   while (static_cast<int32_t>((SYS ? tp_ld_acquire_sys(p) : tp_ld_acquire_gpu(p)) - want) < 0) {
     if (*abort_word) return false;
-    if (globaltimer_ns() - t0 > limit_ns) {
+    // fail fast once any kernel on this device has reported a lost peer: later waits would only
+    // repeat the same time-out one after the other
+    if ((status && *reinterpret_cast<const volatile int*>(status) != 0) || globaltimer_ns() - t0 > limit_ns) {
       *abort_word = FT_ERR_TIMEOUT_PEER;
       return false;
     }
@@ -188,7 +190,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int i = 1; i < p.world; ++i) {
       const int s = (p.rank + i) % p.world;
       if (threadIdx.x == 0)
-        s_ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, s, p.n_slots), epoch, p.limit_ns, abort_word) ? 1 : 0;
+        s_ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, s, p.n_slots), epoch, p.limit_ns, abort_word, p.status) ? 1 : 0;
       __syncthreads();
       if (!s_ok) break;
       const __nv_bfloat16* src_base = static_cast<const __nv_bfloat16*>(p.xg.ptr[s]);
@@ -233,7 +235,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (p.mode == 0) {
           const int need = remote_pieces(mb, p.rows_per_rank, p.M, p.rank);
           if (need > 0) {
-            if (!tp_spin_ge<false>(p.blk_ready + mb, static_cast<uint32_t>(need), p.limit_ns, abort_word)) break;
+            if (!tp_spin_ge<false>(p.blk_ready + mb, static_cast<uint32_t>(need), p.limit_ns, abort_word, p.status)) break;
             tp_fence_proxy_async();
           }
         }
@@ -291,7 +293,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (p.mode == 1 && epoch > 1) {
       // the owners must have finished reducing the previous use of their staging buffers
       if (lane < p.world)
-        ok = tp_spin_ge<true>(my_flags + tp_flag_index(1, p.slot, lane, p.n_slots), epoch - 1, p.limit_ns, abort_word);
+        ok = tp_spin_ge<true>(my_flags + tp_flag_index(1, p.slot, lane, p.n_slots), epoch - 1, p.limit_ns, abort_word, p.status);
       ok = __all_sync(0xffffffffu, ok);
     }
     for (int tile = cta; tile < num_tiles && ok; tile += n_gemm) {
@@ -367,7 +369,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (p.mode == 1 && ok) {
       // ---------------------------------------------------------- reduce the staged partials
       if (lane < p.world)
-        ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, lane, p.n_slots), epoch, p.limit_ns, abort_word);
+        ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, lane, p.n_slots), epoch, p.limit_ns, abort_word, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         const __nv_bfloat16* st = static_cast<const __nv_bfloat16*>(p.stage.ptr[p.rank]);

@@ -173,21 +173,27 @@ class LlamaEngine:
             x = self.tp.gemm_rs(3, act, L["down"], residual=x)
         return x
 
-    def _next_tokens(self, h_rows: torch.Tensor, M: int) -> torch.Tensor:
-        """Final norm + vocab-parallel lm_head + greedy argmax over all shards -> [M] token ids."""
+    def _local_argmax(self, h_rows: torch.Tensor, M: int) -> torch.Tensor:
+        """Final norm + this rank's vocabulary shard of the lm_head -> ``[M, 2]`` (best logit, global id)."""
         self._norm_into(4, h_rows, None, self.norm, M)
         logits = self.tp.ag_gemm(4, M, self.lm_head).float()
         if self.cfg.vocab_size % self.W and self.r == self.W - 1:
             logits[:, self.cfg.vocab_size - self.r * self.Vloc:] = -float("inf")
         val, idx = logits.max(dim=-1)
-        idx = idx + self.r * self.Vloc
+        return torch.stack([val, (idx + self.r * self.Vloc).float()], dim=-1).contiguous()
+
+    def _combine_argmax(self, pair: torch.Tensor) -> torch.Tensor:
+        """Greedy token over all vocabulary shards (a 512-byte all-gather; kept outside any
+        captured graph so that the graph holds only this library's kernels and torch ops)."""
         if self.W == 1:
-            return idx
-        pair = torch.stack([val, idx.float()], dim=-1).contiguous()
+            return pair[:, 1].long()
         allp = torch.empty((self.W,) + tuple(pair.shape), device=self.device, dtype=pair.dtype)
         dist.all_gather_into_tensor(allp, pair, group=self.tp.group)
         best = allp[..., 0].argmax(dim=0)
         return allp[..., 1].gather(0, best[None]).squeeze(0).long()
+
+    def _next_tokens(self, h_rows: torch.Tensor, M: int) -> torch.Tensor:
+        return self._combine_argmax(self._local_argmax(h_rows, M))
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()
@@ -233,7 +239,7 @@ class LlamaEngine:
         pos = self.lengths.clone()          # position of the new token
         self.lengths += 1
         h = self._forward(tokens, pos, self._sid, B, 1, True, self.lengths)
-        return self._next_tokens(h, B)
+        return self._local_argmax(h, B)
 
     @torch.no_grad()
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -252,21 +258,21 @@ class LlamaEngine:
             self._sid = torch.arange(B, device=self.device, dtype=torch.int32)
         tokens = tokens.to(self.device)
         if not self.cuda_graph:
-            return self._decode_device(tokens)
+            return self._combine_argmax(self._decode_device(tokens))
         if self._graph is not None and self._graph_batch == B:
             self._tok_in.copy_(tokens)
             self._graph.replay()
-            return self._tok_out.clone()
+            return self._combine_argmax(self._pair_out)
         self._eager_steps += 1
         if self._eager_steps <= 2:
-            return self._decode_device(tokens)
+            return self._combine_argmax(self._decode_device(tokens))
         self._tok_in = tokens.clone()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._tok_out = self._decode_device(self._tok_in)
+            self._pair_out = self._decode_device(self._tok_in)
         self._graph, self._graph_batch = g, B
         g.replay()                           # capture only records; this executes the step
-        return self._tok_out.clone()
+        return self._combine_argmax(self._pair_out)
 
     @torch.no_grad()
     def generate(self, prompts: torch.Tensor, max_new_tokens: int) -> torch.Tensor:

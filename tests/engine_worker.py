@@ -29,7 +29,7 @@ def main():
     torch.manual_seed(3)
     model = LlamaForCausalLM(cfg).to(dev, torch.bfloat16).eval()
     sd = model.hf_state_dict()
-    eng = LlamaEngine(cfg, TPContext(group, dev, timeout_ms=20000), max_batch=4, max_seq_len=128, weights=sd,
+    eng = LlamaEngine(cfg, TPContext(group, dev), max_batch=4, max_seq_len=128, weights=sd,
                       prefill_chunk_tokens=96, cuda_graph=os.environ.get("FT_TEST_GRAPH") == "1")
     B, S, new = 4, 48, 8
     prompts = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1)).to(dev)

@@ -63,12 +63,13 @@ def test_page_pool_bookkeeping():
 
 
 def _run(nproc, port, graph=False):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", FT_TEST_GRAPH="1" if graph else "0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", FT_TEST_GRAPH="1" if graph else "0",
+               FT_COMM_TIMEOUT_MS="5000")
     script = os.path.join(HERE, "engine_worker.py")
     cmd = [sys.executable, script] if nproc == 1 else [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
         "--master-addr", "127.0.0.1", "--master-port", str(port), script]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "ok" in proc.stdout
 
