@@ -1,0 +1,308 @@
+"""CPU tests: sharded checkpoints with resharding, async collectives, RPC, the small model zoo,
+tokenizer / hub / grammar helpers, ML metrics and the distributions re-export."""
+import json
+import os
+
+import pytest
+import torch
+
+from ferrotorch_b200.models import zoo
+from ferrotorch_b200.parallel import dist_checkpoint as dc
+from ferrotorch_b200.parallel.backend import SizeMismatch
+from ferrotorch_b200.utils import ml, text
+
+
+# --------------------------------------------------------------------------- distributed checkpoint
+def _full_state():
+    g = torch.Generator().manual_seed(3)
+    return {"w": torch.randn(8, 6, generator=g), "b": torch.randn(6, generator=g), "col": torch.randn(4, 8, generator=g)}
+
+
+DIMS = {"w": 0, "b": None, "col": 1}
+
+
+def _save(tmp, world):
+    full = _full_state()
+    for r in range(world):
+        local = {k: (v if DIMS[k] is None else v.chunk(world, dim=DIMS[k])[r].contiguous()) for k, v in full.items()}
+        dc.save_distributed(str(tmp), local, DIMS, rank=r, world_size=world, extra={"step": 7})
+    return full
+
+
+def test_dist_checkpoint_same_world(tmp_path):
+    full = _save(tmp_path, 2)
+    for r in range(2):
+        st, extra = dc.load_distributed(str(tmp_path), r, 2)
+        assert extra == {"step": 7}
+        assert torch.equal(st["w"], full["w"].chunk(2, 0)[r])
+        assert torch.equal(st["col"], full["col"].chunk(2, 1)[r])
+        assert torch.equal(st["b"], full["b"])
+
+
+@pytest.mark.parametrize("new_world", [1, 4])
+def test_dist_checkpoint_reshard(tmp_path, new_world):
+    full = _save(tmp_path, 2)
+    for r in range(new_world):
+        st, _ = dc.load_distributed(str(tmp_path), r, new_world)
+        assert torch.equal(st["w"], full["w"].chunk(new_world, 0)[r])
+        assert torch.equal(st["col"], full["col"].chunk(new_world, 1)[r])
+        assert torch.equal(st["b"], full["b"])
+
+
+def test_dist_checkpoint_reshard_indivisible(tmp_path):
+    _save(tmp_path, 2)
+    with pytest.raises(SizeMismatch):
+        dc.load_distributed(str(tmp_path), 0, 3)
+
+
+def test_async_dist_checkpointer(tmp_path):
+    full = _full_state()
+    ck = dc.AsyncDistributedCheckpointer()
+    local = dict(full)
+    ck.save_async(str(tmp_path), local, {k: None for k in full}, 0, 1)
+    local["w"].zero_()          # the snapshot was taken before the writer started
+    ck.wait()
+    assert ck.is_done()
+    st, _ = dc.load_distributed(str(tmp_path), 0, 1)
+    assert torch.equal(st["w"], _full_state()["w"])
+
+
+def test_async_checkpointer_reports_errors(tmp_path):
+    blocker = tmp_path / "file"
+    blocker.write_text("x")
+    ck = dc.AsyncDistributedCheckpointer()
+    ck.save_async(str(blocker), {"a": torch.zeros(1)}, {"a": None}, 0, 1)
+    with pytest.raises(OSError):
+        ck.wait()
+
+
+def test_pending_collective():
+    p = dc.PendingCollective(lambda a, b: a + b, 2, 3)
+    assert p.wait(5) == 5 and p.is_done()
+    bad = dc.PendingCollective(lambda: 1 / 0)
+    with pytest.raises(ZeroDivisionError):
+        bad.wait(5)
+
+
+def test_async_collectives_simulated():
+    from ferrotorch_b200.parallel.backend import run_simulated
+
+    def body(g):
+        # one collective in flight per group at a time: their order across ranks must match
+        red = dc.all_reduce_async(g, torch.full((4,), float(g.rank + 1))).wait(10)
+        return red, dc.all_gather_async(g, torch.tensor([float(g.rank)])).wait(10)
+
+    for red, gathered in run_simulated(3, body):
+        assert torch.equal(red, torch.full((4,), 6.0))
+        got = torch.cat(list(gathered)) if isinstance(gathered, (list, tuple)) else gathered.flatten()
+        assert got.tolist() == [0.0, 1.0, 2.0]
+
+
+def test_rpc_agent():
+    a = dc.RpcAgent("worker0")
+    try:
+        a.register("add", lambda x, y=0: x + y)
+        a.register("tensor", lambda t: t * 2)
+        assert dc.RpcAgent.rpc_sync(a.address, "add", 2, y=5) == 7
+        assert torch.equal(dc.RpcAgent.rpc_sync(a.address, "tensor", torch.ones(3)), torch.full((3,), 2.0))
+        assert dc.RpcAgent.rpc_async(a.address, "add", 1, y=1).wait(10) == 2
+        with pytest.raises(RuntimeError, match="no handler"):
+            dc.RpcAgent.rpc_sync(a.address, "missing")
+        a.register("boom", lambda: 1 / 0)
+        with pytest.raises(RuntimeError, match="ZeroDivisionError"):
+            dc.RpcAgent.rpc_sync(a.address, "boom")
+    finally:
+        a.shutdown()
+
+
+# --------------------------------------------------------------------------- model zoo
+def test_bert_and_sentence_embeddings():
+    torch.manual_seed(0)
+    bert = zoo.BertModel(vocab_size=100, hidden=32, layers=2, heads=4, intermediate=64, max_pos=16).eval()
+    ids = torch.randint(0, 100, (2, 10))
+    mask = torch.ones(2, 10, dtype=torch.long)
+    mask[1, 6:] = 0
+    h, pooled = bert(ids, mask)
+    assert h.shape == (2, 10, 32) and pooled.shape == (2, 32)
+    emb = zoo.SentenceTransformer(bert)(ids, mask)
+    assert torch.allclose(emb.norm(dim=-1), torch.ones(2), atol=1e-5)
+    ids2 = ids.clone()
+    ids2[1, 6:] = 5          # padding content must not change the embedding
+    assert torch.allclose(zoo.SentenceTransformer(bert)(ids2, mask)[1], emb[1], atol=1e-5)
+
+
+def test_whisper_front_end_and_encoder():
+    audio = torch.sin(torch.arange(16000) * 2 * torch.pi * 440 / 16000)[None]
+    mel = zoo.log_mel_spectrogram(audio)
+    assert mel.shape == (1, 80, 100)
+    assert float(mel.max() - mel.min()) <= 2.0 + 1e-5       # 8 dB-decades clamp, divided by 4
+    enc = zoo.WhisperEncoder(d_model=64, heads=4, layers=1, n_ctx=64).eval()
+    assert enc(mel).shape == (1, 50, 64)
+
+
+def test_gcn_normalisation_and_training_step():
+    adj = torch.tensor([[0, 1, 0], [1, 0, 1], [0, 1, 0]], dtype=torch.float32)
+    an = zoo.GcnConv.normalize(adj)
+    assert torch.allclose(an, an.T)
+    assert torch.allclose(an[0, 0], torch.tensor(0.5))
+    assert torch.allclose(zoo.GcnConv.normalize(adj.to_sparse()), an)
+    net = zoo.Gcn(5, 8, 2, dropout=0.0)
+    x, y = torch.randn(3, 5), torch.tensor([0, 1, 0])
+    opt = torch.optim.Adam(net.parameters(), 0.05)
+    first = None
+    for _ in range(30):
+        loss = torch.nn.functional.cross_entropy(net(x, an), y)
+        first = first or float(loss)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert float(loss) < first
+
+
+@pytest.mark.parametrize("discrete", [False, True])
+def test_mlp_policy_and_ppo_loss(discrete):
+    torch.manual_seed(0)
+    pol = zoo.MlpPolicy(4, 3, discrete=discrete)
+    obs = torch.randn(16, 4)
+    act, val, logp = pol(obs)
+    assert val.shape == (16,) and logp.shape == (16,)
+    assert act.shape == ((16,) if discrete else (16, 3))
+    det1, _, _ = pol(obs, deterministic=True)
+    det2, _, _ = pol(obs, deterministic=True)
+    assert torch.equal(det1, det2)
+    loss = zoo.ppo_loss(pol, obs, act, logp.detach(), torch.randn(16), torch.randn(16), ent_coef=0.01)
+    loss.backward()
+    assert all(p.grad is not None for p in pol.actor.parameters())
+
+
+def test_ddim_scheduler_and_unet():
+    torch.manual_seed(0)
+    sch = zoo.DDIMScheduler()
+    x0, noise = torch.randn(2, 4, 8, 8), torch.randn(2, 4, 8, 8)
+    sch.set_timesteps(10)
+    t = int(sch.timesteps[0])
+    xt = sch.add_noise(x0, noise, torch.tensor([t, t]))
+    # with the true noise, stepping from the last-but-zero timestep chain recovers x0 at t=0
+    x = xt
+    for step_t in sch.timesteps.tolist():
+        a = sch.alphas_cumprod[step_t]
+        eps = (x - a.sqrt() * x0) / (1 - a).sqrt()
+        x = sch.step(eps, step_t, x)
+    assert torch.allclose(x, x0, atol=1e-4)
+    unet = zoo.TinyUNet(channels=4, base=16, ctx_dim=12).eval()
+    out = unet(xt, torch.tensor([t, t]), torch.randn(2, 5, 12))
+    assert out.shape == xt.shape
+    img = zoo.ddim_sample(zoo.TinyUNet(channels=4, base=16).eval(), sch, (1, 4, 8, 8), steps=3,
+                          generator=torch.Generator().manual_seed(1))
+    assert img.shape == (1, 4, 8, 8) and torch.isfinite(img).all()
+
+
+# --------------------------------------------------------------------------- text utilities
+def test_json_grammar_prefixes():
+    g = text.JsonGrammar()
+    for s in ["", "{", '{"a', '{"a":', '{"a": 1,', "[1,", "tr", "-", "-1.5e", '"abc', '{"a": {"b": null}}', "[[],[]]"]:
+        assert g.accepts_prefix(s), s
+    for s in ["}", "{1", '{"a" 1', "[,", '{"a":}', "01", "[1 2]", '{"a":1,}', "[]]", "1 2"]:
+        assert not g.accepts_prefix(s), s
+    assert g.is_complete('{"a": [1, 2]}') and not g.is_complete('{"a": [1, 2]')
+
+
+def test_token_mask_drives_valid_json():
+    g = text.JsonGrammar()
+    vocab = ["{", "}", '"k"', ":", "1", ",", "[", "]", "x", "<eos>"]
+    eos = 9
+    m = text.token_mask(g, "", vocab, eos)
+    assert m.tolist() == [True, False, True, False, True, False, True, False, False, False]
+    m = text.token_mask(g, '{"k"', vocab, eos)
+    assert [vocab[i] for i in m.nonzero().flatten().tolist()] == [":"]
+    m = text.token_mask(g, '{"k":1}', vocab, eos)
+    assert m.nonzero().flatten().tolist() == [eos]
+    # greedy decode with adversarial logits still ends as valid JSON
+    torch.manual_seed(0)
+    out = ""
+    for _ in range(40):
+        logits = torch.randn(len(vocab))
+        logits[eos] += 1.0
+        tok = int(text.apply_token_mask(logits, text.token_mask(g, out, vocab, eos)).argmax())
+        if tok == eos:
+            break
+        out += vocab[tok]
+    if g.is_complete(out):
+        json.loads(out)
+    else:
+        assert g.accepts_prefix(out)
+
+
+def test_chat_templates():
+    msgs = [{"role": "system", "content": "s"}, {"role": "user", "content": "hi"}]
+    t = text.apply_chat_template(msgs)
+    assert t.startswith("<|begin_of_text|><|start_header_id|>system<|end_header_id|>\n\ns<|eot_id|>")
+    assert t.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    c = text.apply_chat_template(msgs, "chatml", add_generation_prompt=False)
+    assert c == "<|im_start|>system\ns<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n"
+    with pytest.raises(ValueError):
+        text.apply_chat_template(msgs, "nope")
+
+
+def test_tokenizer_round_trip(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import models, pre_tokenizers
+
+    tok = tokenizers.Tokenizer(models.WordLevel({"hello": 0, "world": 1, "[UNK]": 2}, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    p = tmp_path / "tokenizer.json"
+    tok.save(str(p))
+    t = text.load_tokenizer(str(p))
+    ids = text.encode(t, "hello world foo")
+    assert ids == [0, 1, 2]
+    assert text.decode(t, ids[:2]) == "hello world"
+
+
+def test_hub_offline(tmp_path, monkeypatch):
+    monkeypatch.setenv("HF_HOME", str(tmp_path))
+    with pytest.raises(FileNotFoundError):
+        text.hf_download_model("org/model")
+    snap = tmp_path / "hub" / "models--org--model" / "snapshots" / "abc"
+    snap.mkdir(parents=True)
+    (snap / "config.json").write_text(json.dumps({
+        "model_type": "llama", "vocab_size": 1000, "hidden_size": 64, "intermediate_size": 128,
+        "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "rms_norm_eps": 1e-5,
+        "rope_theta": 10000.0, "max_position_embeddings": 256}))
+    d = text.hf_download_model("org/model")
+    assert d == str(snap)
+    cfg = text.HfTransformerConfig.from_file(os.path.join(d, "config.json"))
+    assert cfg.model_type == "llama"
+    lc = cfg.to_llama()
+    assert lc.hidden_size == 64 and lc.num_key_value_heads == 2
+
+
+# --------------------------------------------------------------------------- metrics / distributions
+def test_ml_metrics():
+    yt = torch.tensor([0, 1, 2, 2, 1, 0])
+    yp = torch.tensor([0, 2, 2, 2, 1, 1])
+    cm = ml.confusion_matrix(yt, yp)
+    assert cm.tolist() == [[1, 1, 0], [0, 1, 1], [0, 0, 2]]
+    assert ml.accuracy_score(yt, yp) == pytest.approx(4 / 6)
+    p, r, f = ml.precision_recall_f1(yt, yp, "micro")
+    assert p == pytest.approx(4 / 6) and r == pytest.approx(4 / 6) and f == pytest.approx(4 / 6)
+    p, r, f = ml.precision_recall_f1(yt, yp, "macro")
+    assert p == pytest.approx((1 + 0.5 + 2 / 3) / 3) and r == pytest.approx((0.5 + 0.5 + 1) / 3)
+    a, b = torch.tensor([1.0, 2.0, 3.0]), torch.tensor([1.0, 2.0, 5.0])
+    assert ml.mean_squared_error(a, b) == pytest.approx(4 / 3)
+    assert ml.mean_absolute_error(a, b) == pytest.approx(2 / 3)
+    assert ml.r2_score(a, a) == pytest.approx(1.0)
+    assert ml.roc_auc_score(torch.tensor([0, 0, 1, 1]), torch.tensor([0.1, 0.4, 0.35, 0.8])) == pytest.approx(0.75)
+    assert ml.roc_auc_score(torch.tensor([0, 1]), torch.tensor([0.5, 0.5])) == pytest.approx(0.5)
+    xtr, xte, ytr, yte = ml.train_test_split(torch.arange(20), torch.arange(20) * 2, test_size=0.25)
+    assert len(xtr) == 15 and len(xte) == 5 and torch.equal(ytr, xtr * 2)
+    assert sorted(torch.cat([xtr, xte]).tolist()) == list(range(20))
+
+
+def test_distributions_reexport():
+    from ferrotorch_b200 import distributions as D
+
+    n = D.Normal(torch.zeros(3), torch.ones(3))
+    assert D.kl_divergence(n, n).abs().max() == 0
+    assert D.constraints.positive.check(torch.tensor(1.0))
+    t = D.TransformedDistribution(n, [D.transforms.ExpTransform()])
+    assert (t.sample() > 0).all()
