@@ -115,7 +115,10 @@ __device__ __forceinline__ int remote_pieces(int mb, int rows_per_rank, int M, i
   return n;
 }
 
-template <int BN>
+// B_MN: the B operand is stored [K, N] (N contiguous) instead of [N, K]; its tiles are loaded as
+// 64-column chunks and read through an MN-major descriptor, so the backward GEMMs (dY * W) use
+// the weight as it is stored.
+template <int BN, bool B_MN>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const TpParams p) {
@@ -245,7 +248,13 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
           mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
           tma_load_2d(sA, &tmA, full_bar(stage), kb * TP_BK, m0);
-          tma_load_2d(sB, &tmB, full_bar(stage), kb * TP_BK, n0);
+          if constexpr (!B_MN) {
+            tma_load_2d(sB, &tmB, full_bar(stage), kb * TP_BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * (TP_BK * 128), &tmB, full_bar(stage), n0 + c * 64, kb * TP_BK);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -258,7 +267,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t tmem_base = *tmem_slot;
-      constexpr uint32_t idesc = make_idesc_f16(TP_BM, BN, 1, 0, 0);
+      constexpr uint32_t idesc = make_idesc_f16(TP_BM, BN, 1, 0, B_MN ? 1 : 0);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -271,9 +280,12 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_after();
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
 #pragma unroll
-          for (int k = 0; k < TP_BK / 16; ++k)
-            umma_f16_ss(d_tmem, make_smem_desc_sw128(sA + k * 32, 16, 1024),
-                        make_smem_desc_sw128(sB + k * 32, 16, 1024), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < TP_BK / 16; ++k) {
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sB + k * 2048, TP_BK * 128, 1024)
+                                        : make_smem_desc_sw128(sB + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, make_smem_desc_sw128(sA + k * 32, 16, 1024), bdesc, idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -430,11 +442,11 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
-template <int BN>
+template <int BN, bool B_MN>
 static int launch_tp(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p, int device, int ctas,
                      cudaStream_t stream) {
   using Cfg = TpCfg<BN>;
-  auto kern = tp_gemm_kernel<BN>;
+  auto kern = tp_gemm_kernel<BN, B_MN>;
   static bool attr_set[64] = {false};
   if (!attr_set[device]) {
     FT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -444,6 +456,22 @@ static int launch_tp(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpPar
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
+}
+
+static int dispatch_tp(int bn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p,
+                       int device, int ctas, cudaStream_t stream) {
+  if (!b_mn) {
+    switch (bn) {
+      case 256: return launch_tp<256, false>(tmA, tmB, p, device, ctas, stream);
+      case 128: return launch_tp<128, false>(tmA, tmB, p, device, ctas, stream);
+      default: return launch_tp<64, false>(tmA, tmB, p, device, ctas, stream);
+    }
+  }
+  switch (bn) {
+    case 256: return launch_tp<256, true>(tmA, tmB, p, device, ctas, stream);
+    case 128: return launch_tp<128, true>(tmA, tmB, p, device, ctas, stream);
+    default: return launch_tp<64, true>(tmA, tmB, p, device, ctas, stream);
+  }
 }
 
 static int pick_bn(int M, int N, int sms) {
@@ -469,23 +497,28 @@ using namespace ft;
 // counters[1 .. 1+8) = owner counters, counters[16 ...) = per-128-row-block counters.
 FT_API long long ft_tp_counter_words(int M) { return 16 + (M + TP_BM - 1) / TP_BM; }
 
-// Y[M, N] = allgather_rows(Xg)[M, K] * W[N, K]^T (+ bias).  xg_ptrs: every rank's symmetric
-// [M, K] buffer (row stride ldx); this rank's rows [rank*rows_per_rank, ...) must already be in
-// its own buffer and every rank must have raised flag (kind 0, slot) to `epoch` after writing
-// them (ft_comm_signal).  counters: ft_tp_counter_words(M) zeroed uint32 words, reused across
-// calls.  The kernel raises flag (kind 1, slot) = epoch on every peer when it no longer reads
-// their buffers.
-FT_API int ft_tp_ag_gemm(void* const* xg_ptrs, const void* w, void* y, const void* bias, int M, int N, int K,
-                         long long ldx, long long ldw, long long ldy, int rank, int world, int rows_per_rank,
-                         unsigned int* counters, void* const* flag_ptrs, int slot, int n_slots,
-                         unsigned int epoch, unsigned int* epoch_dev, int n_copy, long long timeout_ms,
-                         int device, cudaStream_t stream) {
+// Y[M, N] = allgather_rows(Xg)[M, K] * B (+ bias), where B is W[N, K]^T (b_mn_major = 0, row
+// stride ldw) or W stored as [K, N] (b_mn_major = 1).  xg_ptrs: every rank's symmetric [M, K]
+// buffer (row stride ldx); this rank's rows [rank*rows_per_rank, ...) must already be in its own
+// buffer and every rank must have raised flag (kind 0, slot) after writing them
+// (ft_comm_signal / ft_comm_signal_dev).  counters: ft_tp_counter_words(M) zeroed uint32 words,
+// reused across calls.  The kernel raises flag (kind 1, slot) on every peer when it no longer
+// reads their buffers.  With w == NULL only the gather runs (copy CTAs alone): afterwards the
+// local buffer holds all M rows.
+FT_API int ft_tp_ag_gemm2(void* const* xg_ptrs, const void* w, void* y, const void* bias, int M, int N, int K,
+                          long long ldx, long long ldw, long long ldy, int b_mn_major, int rank, int world,
+                          int rows_per_rank, unsigned int* counters, void* const* flag_ptrs, int slot,
+                          int n_slots, unsigned int epoch, unsigned int* epoch_dev, int n_copy,
+                          long long timeout_ms, int device, cudaStream_t stream) {
   if (int _rc = ft::ensure_device(device)) return _rc;
+  const bool gather_only = (w == nullptr);
   FT_REQUIRE(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world, "ft_tp_ag_gemm: bad rank/world");
-  FT_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0,
-             "ft_tp_ag_gemm: N, K and strides must be multiples of 8");
+  FT_REQUIRE(M > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0, "ft_tp_ag_gemm: K and ldx must be multiples of 8");
+  FT_REQUIRE(gather_only || (N > 0 && N % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0 && y),
+             "ft_tp_ag_gemm: N and strides must be multiples of 8");
   FT_REQUIRE(rows_per_rank > 0 && rows_per_rank * world >= M, "ft_tp_ag_gemm: rows_per_rank * world < M");
-  FT_REQUIRE(counters && w && y, "ft_tp_ag_gemm: null pointer");
+  FT_REQUIRE(counters, "ft_tp_ag_gemm: null pointer");
+  if (gather_only && world == 1) return FT_E_OK;
   TpParams p{};
   FT_REQUIRE(fill_peers(p.xg, xg_ptrs, world) == 0 && fill_peers(p.flags, flag_ptrs, world) == 0,
              "ft_tp_ag_gemm: bad peer pointers");
@@ -494,36 +527,51 @@ FT_API int ft_tp_ag_gemm(void* const* xg_ptrs, const void* w, void* y, const voi
   if (world == 1) n_copy = 0;
   else if (n_copy <= 0) n_copy = 32;
   if (n_copy > sms / 2) n_copy = sms / 2;
+  if (gather_only) N = 64;
   p.mode = 0; p.M = M; p.N = N; p.K = K; p.rank = rank; p.world = world; p.rows_per_rank = rows_per_rank;
   p.C = static_cast<__nv_bfloat16*>(y); p.ldc = ldy; p.bias = bias; p.ldx = ldx;
   p.blk_ready = counters + 16; p.n_copy = n_copy; p.done_counter = counters; p.owner_counter = counters + 1;
   p.slot = slot; p.n_slots = n_slots; p.epoch = epoch; p.epoch_dev = epoch_dev;
   p.limit_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
   p.status = device_status_word(device);
-  const int bn = pick_bn(M, N, sms - n_copy);
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, xg_ptrs[rank], 2, K, M, ldx * 2, TP_BK, TP_BM, 3);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmB, w, 2, K, N, ldw * 2, TP_BK, bn, 3);
+  if (gather_only) {
+    // no GEMM CTA exists in this launch, so the B map is never used
+    return launch_tp<64, false>(tmA, tmA, p, device, n_copy, stream);
+  }
+  const int bn = pick_bn(M, N, sms - n_copy);
+  if (!b_mn_major)
+    rc = make_tmap_2d(&tmB, w, 2, K, N, ldw * 2, TP_BK, bn, 3);
+  else
+    rc = make_tmap_2d(&tmB, w, 2, N, K, ldw * 2, 64, TP_BK, 3);
   if (rc) return rc;
   const int tiles = ((M + TP_BM - 1) / TP_BM) * ((N + bn - 1) / bn);
-  int gemm_ctas = tiles < sms - n_copy ? tiles : sms - n_copy;
-  const int ctas = n_copy + gemm_ctas;
-  switch (bn) {
-    case 256: return launch_tp<256>(tmA, tmB, p, device, ctas, stream);
-    case 128: return launch_tp<128>(tmA, tmB, p, device, ctas, stream);
-    default: return launch_tp<64>(tmA, tmB, p, device, ctas, stream);
-  }
+  const int gemm_ctas = tiles < sms - n_copy ? tiles : sms - n_copy;
+  return dispatch_tp(bn, b_mn_major != 0, tmA, tmB, p, device, n_copy + gemm_ctas, stream);
 }
 
-// Out[rows_per_rank, N] (+ residual) = reduce_scatter_rows(X[M, K] * W[N, K]^T) over ranks.
-// stage_ptrs: every rank's symmetric staging buffer of world * rows_per_rank * N bf16.
-// out / residual are local [rows_per_rank, N] (row strides ldo / ldr).
-FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, void* out, const void* residual,
-                         int M, int N, int K, long long ldx, long long ldw, long long ldo, long long ldr,
-                         int rank, int world, int rows_per_rank, unsigned int* counters,
-                         void* const* flag_ptrs, int slot, int n_slots, unsigned int epoch,
-                         unsigned int* epoch_dev, long long timeout_ms, int device, cudaStream_t stream) {
+FT_API int ft_tp_ag_gemm(void* const* xg_ptrs, const void* w, void* y, const void* bias, int M, int N, int K,
+                         long long ldx, long long ldw, long long ldy, int rank, int world, int rows_per_rank,
+                         unsigned int* counters, void* const* flag_ptrs, int slot, int n_slots,
+                         unsigned int epoch, unsigned int* epoch_dev, int n_copy, long long timeout_ms,
+                         int device, cudaStream_t stream) {
+  FT_REQUIRE(w != nullptr, "ft_tp_ag_gemm: null weight");
+  return ft_tp_ag_gemm2(xg_ptrs, w, y, bias, M, N, K, ldx, ldw, ldy, 0, rank, world, rows_per_rank, counters,
+                        flag_ptrs, slot, n_slots, epoch, epoch_dev, n_copy, timeout_ms, device, stream);
+}
+
+// Out[rows_per_rank, N] (+ residual) = reduce_scatter_rows(X[M, K] * B) over ranks, B as in
+// ft_tp_ag_gemm2.  stage_ptrs: every rank's symmetric staging buffer of
+// world * rows_per_rank * N bf16.  out / residual are local [rows_per_rank, N] (row strides
+// ldo / ldr).  max_ctas > 0 limits the grid (leaves SMs to a concurrent gather).
+FT_API int ft_tp_gemm_rs2(const void* x, const void* w, void* const* stage_ptrs, void* out, const void* residual,
+                          int M, int N, int K, long long ldx, long long ldw, long long ldo, long long ldr,
+                          int b_mn_major, int max_ctas, int rank, int world, int rows_per_rank,
+                          unsigned int* counters, void* const* flag_ptrs, int slot, int n_slots,
+                          unsigned int epoch, unsigned int* epoch_dev, long long timeout_ms, int device,
+                          cudaStream_t stream) {
   if (int _rc = ft::ensure_device(device)) return _rc;
   FT_REQUIRE(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world, "ft_tp_gemm_rs: bad rank/world");
   FT_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldo % 8 == 0 &&
@@ -535,7 +583,8 @@ FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, 
   FT_REQUIRE(fill_peers(p.stage, stage_ptrs, world) == 0 && fill_peers(p.flags, flag_ptrs, world) == 0,
              "ft_tp_gemm_rs: bad peer pointers");
   for (int i = 0; i < TP_MAX_RANKS; ++i) p.xg.ptr[i] = nullptr;
-  const int sms = sm_count(device);
+  int sms = sm_count(device);
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   p.mode = 1; p.M = M; p.N = N; p.K = K; p.rank = rank; p.world = world; p.rows_per_rank = rows_per_rank;
   p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
@@ -547,13 +596,22 @@ FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, 
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, x, 2, K, M, ldx * 2, TP_BK, TP_BM, 3);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmB, w, 2, K, N, ldw * 2, TP_BK, bn, 3);
+  if (!b_mn_major)
+    rc = make_tmap_2d(&tmB, w, 2, K, N, ldw * 2, TP_BK, bn, 3);
+  else
+    rc = make_tmap_2d(&tmB, w, 2, N, K, ldw * 2, 64, TP_BK, 3);
   if (rc) return rc;
   const int tiles = ((M + TP_BM - 1) / TP_BM) * ((N + bn - 1) / bn);
   const int ctas = tiles < sms ? tiles : sms;
-  switch (bn) {
-    case 256: return launch_tp<256>(tmA, tmB, p, device, ctas, stream);
-    case 128: return launch_tp<128>(tmA, tmB, p, device, ctas, stream);
-    default: return launch_tp<64>(tmA, tmB, p, device, ctas, stream);
-  }
+  return dispatch_tp(bn, b_mn_major != 0, tmA, tmB, p, device, ctas, stream);
+}
+
+FT_API int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptrs, void* out, const void* residual,
+                         int M, int N, int K, long long ldx, long long ldw, long long ldo, long long ldr,
+                         int rank, int world, int rows_per_rank, unsigned int* counters,
+                         void* const* flag_ptrs, int slot, int n_slots, unsigned int epoch,
+                         unsigned int* epoch_dev, long long timeout_ms, int device, cudaStream_t stream) {
+  return ft_tp_gemm_rs2(x, w, stage_ptrs, out, residual, M, N, K, ldx, ldw, ldo, ldr, 0, 0, rank, world,
+                        rows_per_rank, counters, flag_ptrs, slot, n_slots, epoch, epoch_dev, timeout_ms, device,
+                        stream);
 }

@@ -155,3 +155,57 @@ def qkv_attention(x: torch.Tensor, w_qkv: torch.Tensor, bias: torch.Tensor | Non
         qkv = F.rope_(qkv, cos, sin, n_rot_heads=n_heads + n_kv_heads, seq_len=S, interleaved=interleaved)
     q, k, v = qkv[:, :, :n_heads], qkv[:, :, n_heads:n_heads + n_kv_heads], qkv[:, :, n_heads + n_kv_heads:]
     return flash_attention(q, k, v, causal=causal).reshape(B, S, n_heads * head_dim)
+
+
+class _PackedAttentionFn(torch.autograd.Function):
+    """In-place RoPE + flash attention on an already projected packed ``[B, S, Hq + 2 Hkv, D]``
+    buffer (the tensor-parallel block produces it with the fused all-gather GEMM).  The buffer is
+    rotated in place and kept for the backward; the gradient comes back packed the same way."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, Hq, Hkv, D, causal, interleaved):
+        B, S = qkv.shape[0], qkv.shape[1]
+        if cos is not None:
+            F._rope_launch(qkv, cos, sin, None, Hq + Hkv, S, 0, interleaved, False)
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        out, lse = F.flash_attn_fwd(q, k, v, causal)
+        ctx.save_for_backward(qkv, out, lse, cos if cos is not None else qkv.new_empty(0),
+                              sin if sin is not None else qkv.new_empty(0))
+        ctx.cfg = (Hq, Hkv, D, causal, interleaved, cos is not None)
+        return out.view(B, S, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, cos, sin = ctx.saved_tensors
+        Hq, Hkv, D, causal, interleaved, has_rope = ctx.cfg
+        B, S = qkv.shape[0], qkv.shape[1]
+        dout = dout.reshape(B, S, Hq, D)
+        dout = dout if dout.is_contiguous() else dout.contiguous()
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
+        ld = (Hq + 2 * Hkv) * D
+        rc = _native.kernels().ft_flash_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            F._get_scratch("attn_delta", 2 * B * Hq * S, q.device).data_ptr(),
+            B, S, S, Hq, Hkv, D, ld, ld, ld, Hq * D, ld, ld, ld, float(D ** -0.5), int(causal), 0,
+            F._dev(q), F._stream())
+        _native.check(rc, "ft_flash_attn_bwd")
+        if has_rope:
+            F._rope_launch(dqkv, cos, sin, None, Hq + Hkv, S, 0, interleaved, True)
+        return dqkv, None, None, None, None, None, None, None
+
+
+def packed_attention(qkv: torch.Tensor, cos, sin, *, n_heads: int, n_kv_heads: int, head_dim: int,
+                     causal: bool = True, interleaved: bool = False) -> torch.Tensor:
+    """``attn(rope(qkv))`` for a packed projection output ``[B, S, Hq + 2 Hkv, D]`` -> ``[B, S, Hq*D]``.
+    On the native path ``qkv`` is rotated in place."""
+    B, S = qkv.shape[0], qkv.shape[1]
+    if F.native_enabled() and qkv.is_cuda and qkv.dtype == torch.bfloat16 and head_dim in (64, 128) \
+            and qkv.is_contiguous():
+        return _PackedAttentionFn.apply(qkv, cos, sin, n_heads, n_kv_heads, head_dim, causal, interleaved)
+    if cos is not None:
+        qkv = F.rope_(qkv, cos, sin, n_rot_heads=n_heads + n_kv_heads, seq_len=S, interleaved=interleaved)
+    q, k, v = qkv[:, :, :n_heads], qkv[:, :, n_heads:n_heads + n_kv_heads], qkv[:, :, n_heads + n_kv_heads:]
+    return flash_attention(q, k, v, causal=causal).reshape(B, S, n_heads * head_dim)

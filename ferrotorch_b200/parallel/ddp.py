@@ -96,6 +96,7 @@ class FusedDDP:
         self.late = {id(p) for p in late_params}
         self.last_micro_batch = True
         self.exposed_ms: list[float] = []
+        self.reduce_only = False
 
     # the trainer allocates its arenas through this (symmetric memory in fused mode)
     def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -116,6 +117,14 @@ class FusedDDP:
     def attach(self, trainer) -> None:
         a = trainer.arena
         self.trainer = trainer
+        if self.mode == "fused" and trainer.max_grad_norm:
+            # Global-norm clipping needs the norm of the fully reduced gradient before any element
+            # is updated, so the bucket kernels only reduce (the averaged gradient lands in every
+            # rank's arena, still overlapped with backward) and the norm + clipped update run
+            # locally afterwards.  Every value is still produced by exactly one rank, so the
+            # replicas stay bitwise identical.
+            self.reduce_only = True
+            self.fused_update = False
         align = 8 * self.world
         elems = max(align, int(self.bucket_mb * 1024 * 1024 / a.params.element_size()) // align * align)
         self.buckets = compute_buckets(a.ranges, a.slots, elems, align)
@@ -178,7 +187,7 @@ class FusedDDP:
                 dist.all_reduce(tr.arena.grads[lo:hi], op=dist.ReduceOp.AVG, group=self.group)
             return
         wd = tr.weight_decay if self._group_of(lo) == "decay" else 0.0
-        kind = {"adamw": 1, "adam": 2, "sgd": 3}[tr.kind]
+        kind = 0 if self.reduce_only else {"adamw": 1, "adam": 2, "sgd": 3}[tr.kind]
         lib = _native.kernels()
         rc = lib.ft_ddp_reduce_update(
             self.g_buf.ptr_array, self.p_buf.ptr_array, self.flags.ptr_array,

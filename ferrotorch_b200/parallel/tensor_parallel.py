@@ -33,6 +33,10 @@ _native.register_protos({
                            _i, _ll, _i, _vp]),
     "ft_tp_gemm_rs": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _i, _i, _vp, _vp, _i,
                            _i, _u, _vp, _ll, _i, _vp]),
+    "ft_tp_ag_gemm2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _vp, _vp, _i, _i, _u, _vp,
+                            _i, _ll, _i, _vp]),
+    "ft_tp_gemm_rs2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _i, _i, _i, _i, _vp, _vp,
+                            _i, _i, _u, _vp, _ll, _i, _vp]),
     "ft_comm_signal_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "ft_comm_wait_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _ll, _i, _vp]),
 })
@@ -48,7 +52,7 @@ class _LocalBuffer:
 
 
 class TPContext:
-    N_SLOTS = 8
+    N_SLOTS = 16
 
     def __init__(self, group=None, device=None, timeout_ms: int | None = None, n_copy: int = 32):
         self.group = group
@@ -64,6 +68,15 @@ class TPContext:
         self.epochs = torch.zeros(self.N_SLOTS, device=self.device, dtype=torch.int32)
         self._buffers: dict = {}
         self._counters: dict = {}
+        self._side_stream = None
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    @property
+    def side_stream(self) -> "torch.cuda.Stream":
+        """Stream for collectives that overlap a GEMM on the main stream (backward re-gathers)."""
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        return self._side_stream
 
     def _alloc(self, numel: int, dtype):
         if self.world == 1:
@@ -117,10 +130,15 @@ class TPContext:
         return self.epochs.data_ptr() + 4 * slot
 
     def ag_gemm(self, slot: int, M: int, w: torch.Tensor, bias: torch.Tensor | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, w_is_kn: bool = False) -> torch.Tensor:
         """``allgather_rows(X) @ w.T`` where this rank's rows of X are already in the gather buffer
-        of ``slot``.  ``w``: ``[N_loc, K]``.  Returns ``[M, N_loc]``."""
-        N, K = w.shape
+        of ``slot``.  ``w``: ``[N_loc, K]``, or ``[K, N_loc]`` with ``w_is_kn`` (then the product
+        is ``allgather_rows(X) @ w``, the form the backward GEMMs need).  Returns ``[M, N_loc]``."""
+        if w_is_kn:
+            K, N = w.shape
+        else:
+            N, K = w.shape
+        assert w.stride(1) == 1
         lib = _native.kernels()
         stream = torch.cuda.current_stream().cuda_stream
         xg = self.buffer(("xg", slot), M * K)
@@ -129,34 +147,54 @@ class TPContext:
         _native.check(rc, "ft_comm_signal_dev")
         if out is None:
             out = torch.empty((M, N), device=self.device, dtype=torch.bfloat16)
-        rc = lib.ft_tp_ag_gemm(xg.ptr_array, w.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
-                               M, N, K, K, w.stride(0), out.stride(0), self.rank, self.world,
-                               self.rows_per_rank(M), self.counters(("ag", slot), M).data_ptr(),
-                               self.flags.ptr_array, slot, self.N_SLOTS, 0, self._epoch_ptr(slot), self.n_copy,
-                               self.timeout_ms, self.device.index, stream)
-        _native.check(rc, "ft_tp_ag_gemm")
+        rc = lib.ft_tp_ag_gemm2(xg.ptr_array, w.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                M, N, K, K, w.stride(0), out.stride(0), int(w_is_kn), self.rank, self.world,
+                                self.rows_per_rank(M), self.counters(("ag", slot), M).data_ptr(),
+                                self.flags.ptr_array, slot, self.N_SLOTS, 0, self._epoch_ptr(slot), self.n_copy,
+                                self.timeout_ms, self.device.index, stream)
+        _native.check(rc, "ft_tp_ag_gemm2")
         return out
+
+    def all_gather_rows(self, slot: int, M: int, K: int) -> torch.Tensor:
+        """Gather every rank's rows of the ``slot`` buffer into the local copy (the copy CTAs of
+        the fused kernel running alone); this rank's rows must already be in :meth:`my_rows`.
+        Returns the full ``[M, K]`` buffer."""
+        lib = _native.kernels()
+        stream = torch.cuda.current_stream().cuda_stream
+        xg = self.buffer(("xg", slot), M * K)
+        rc = lib.ft_comm_signal_dev(self.flags.ptr_array, 0, slot, self.N_SLOTS, self.rank, self.world,
+                                    self._epoch_ptr(slot), self.device.index, stream)
+        _native.check(rc, "ft_comm_signal_dev")
+        rc = lib.ft_tp_ag_gemm2(xg.ptr_array, None, None, None, M, 0, K, K, 0, 0, 0, self.rank, self.world,
+                                self.rows_per_rank(M), self.counters(("ag", slot), M).data_ptr(),
+                                self.flags.ptr_array, slot, self.N_SLOTS, 0, self._epoch_ptr(slot), self.n_copy,
+                                self.timeout_ms, self.device.index, stream)
+        _native.check(rc, "ft_tp_ag_gemm2")
+        return xg.tensor[: M * K].view(M, K)
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
     def gemm_rs(self, slot: int, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
-        """``reduce_scatter_rows(x @ w.T) (+ residual)``: ``x [M, K_loc]``, ``w [N, K_loc]``; returns
-        this rank's ``[Ms, N]`` rows.  ``out`` may be this rank's rows of a gather buffer."""
+                out: torch.Tensor | None = None, w_is_kn: bool = False, max_ctas: int = 0) -> torch.Tensor:
+        """``reduce_scatter_rows(x @ w.T) (+ residual)``: ``x [M, K_loc]``, ``w [N, K_loc]`` (or
+        ``[K_loc, N]`` with ``w_is_kn``: the product is ``x @ w``); returns this rank's ``[Ms, N]``
+        rows.  ``out`` may be this rank's rows of a gather buffer."""
         M, K = x.shape
-        N = w.shape[0]
+        N = w.shape[1] if w_is_kn else w.shape[0]
+        assert w.shape[0 if w_is_kn else 1] == K and w.stride(1) == 1 and x.stride(1) == 1
         ms = self.rows_per_rank(M)
         lib = _native.kernels()
         stage = self.buffer(("stage", slot), self.world * ms * N)
         rows = max(0, min(ms, M - self.rank * ms))
         if out is None:
             out = torch.empty((rows, N), device=self.device, dtype=torch.bfloat16)
-        rc = lib.ft_tp_gemm_rs(x.data_ptr(), w.data_ptr(), stage.ptr_array, out.data_ptr(),
-                               residual.data_ptr() if residual is not None else None, M, N, K, x.stride(0),
-                               w.stride(0), out.stride(0), residual.stride(0) if residual is not None else N,
-                               self.rank, self.world, ms, self.counters(("rs", slot), M).data_ptr(),
-                               self.flags.ptr_array, slot, self.N_SLOTS, 0, self._epoch_ptr(slot), self.timeout_ms,
-                               self.device.index, torch.cuda.current_stream().cuda_stream)
-        _native.check(rc, "ft_tp_gemm_rs")
+        rc = lib.ft_tp_gemm_rs2(x.data_ptr(), w.data_ptr(), stage.ptr_array, out.data_ptr(),
+                                residual.data_ptr() if residual is not None else None, M, N, K, x.stride(0),
+                                w.stride(0), out.stride(0), residual.stride(0) if residual is not None else N,
+                                int(w_is_kn), max_ctas, self.rank, self.world, ms,
+                                self.counters(("rs", slot), M).data_ptr(), self.flags.ptr_array, slot, self.N_SLOTS,
+                                0, self._epoch_ptr(slot), self.timeout_ms, self.device.index,
+                                torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "ft_tp_gemm_rs2")
         return out
 
     def check_status(self) -> None:

@@ -121,6 +121,12 @@ class FlatTrainer:
             self._norm_partial = torch.empty(lib.ft_grad_norm_scratch(a.device.index or 0), device=a.device,
                                              dtype=torch.float32)
         self.ddp = ddp
+        # called after the last backward and before the update (tensor parallelism sums the
+        # gradients of replicated parameters here)
+        self.pre_update: Callable[[], None] | None = None
+        # model-parallel group whose ranks hold different shards of the "decay" parameters and
+        # full copies of the "no_decay" ones: the clipping norm is then taken over the whole model
+        self.model_parallel_group = None
         if ddp is not None:
             ddp.attach(self)
 
@@ -171,9 +177,23 @@ class FlatTrainer:
             self._norm_out[0] = n
             self._norm_out[1] = torch.clamp(self.max_grad_norm / (n + 1e-6), max=1.0) if self.max_grad_norm else 1.0
             self._norm_out[2] = n * n
+        if self.model_parallel_group is not None:
+            import torch.distributed as dist
+
+            s, e = a.ranges.get("no_decay", (0, 0))
+            rep = a.grads[s:e].float().pow(2).sum()
+            sharded = self._norm_out[2] - rep
+            dist.all_reduce(sharded, group=self.model_parallel_group)
+            total = (sharded + rep).clamp_min(0)
+            n = total.sqrt()
+            self._norm_out[0] = n
+            self._norm_out[1] = torch.clamp(self.max_grad_norm / (n + 1e-6), max=1.0) if self.max_grad_norm else 1.0
+            self._norm_out[2] = total
         return self._norm_out
 
     def optimizer_step(self) -> None:
+        if self.pre_update is not None:
+            self.pre_update()
         if self.ddp is not None and self.ddp.fused_update:
             self.step_count += 1
             self.ddp.finish_step(self)

@@ -25,6 +25,10 @@ def make_model(cfg, device):
 
 def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    clip = None
+    if mode == "fused_clip":
+        # gradient clipping: reduce-only bucket kernels, then the norm and the clipped update
+        mode, clip = "fused", 0.05
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
@@ -32,7 +36,7 @@ def main():
     dist.init_process_group("nccl", device_id=device)
     cfg = LlamaConfig(vocab_size=2048, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=256)
-    hp = dict(optimizer="adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    hp = dict(optimizer="adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=clip)
     B, S, steps = 2, 128, 3
     g = torch.Generator().manual_seed(0)
     data = torch.randint(0, cfg.vocab_size, (steps, world * B, S + 1), generator=g).to(device)

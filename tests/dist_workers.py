@@ -160,3 +160,67 @@ def config0(rank, world, port, q, steps=20, backend="tcp"):
         import traceback
 
         q.put((rank, "ERR %r %s" % (e, traceback.format_exc())))
+
+
+def vocab_parallel_case(rank, world, port, q):
+    """Vocabulary-parallel embedding + cross-entropy over gloo against the unsharded math."""
+    try:
+        import os
+
+        import torch
+        import torch.distributed as dist
+
+        from ferrotorch_b200.parallel.tp_layers import (VocabParallelEmbedding, all_reduce_replicated_grads,
+                                                        vocab_parallel_cross_entropy)
+
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        g = torch.Generator().manual_seed(4)
+        V, H, M = 32, 8, 12
+        table = torch.randn(V, H, generator=g)
+        ids = torch.randint(0, V, (M,), generator=g)
+        upstream = torch.randn(M, H, generator=g)
+        logits = torch.randn(M, V, generator=g) * 3
+        tgt = torch.randint(0, V, (M,), generator=g)
+        tgt[3] = -100
+        vl, ms = V // world, M // world
+        errs = []
+
+        # ---- embedding: rows of the unsharded lookup, and the table gradient of this shard
+        t_ref = table.clone().requires_grad_()
+        (torch.nn.functional.embedding(ids, t_ref) * upstream).sum().backward()
+        emb = VocabParallelEmbedding(vl, H, dist.group.WORLD, rank, world, dtype=torch.float32)
+        with torch.no_grad():
+            emb.weight.copy_(table[rank * vl:(rank + 1) * vl])
+        rows = emb(ids)
+        if not torch.allclose(rows, table[ids][rank * ms:(rank + 1) * ms], atol=1e-6):
+            errs.append("embedding rows")
+        (rows * upstream[rank * ms:(rank + 1) * ms]).sum().backward()
+        if not torch.allclose(emb.weight.grad, t_ref.grad[rank * vl:(rank + 1) * vl], atol=1e-5):
+            errs.append("embedding grad")
+
+        # ---- cross-entropy over vocabulary shards
+        l_ref = logits.clone().requires_grad_()
+        loss_ref = torch.nn.functional.cross_entropy(l_ref, tgt, ignore_index=-100)
+        loss_ref.backward()
+        l_loc = logits[:, rank * vl:(rank + 1) * vl].clone().requires_grad_()
+        loss = vocab_parallel_cross_entropy(l_loc, tgt, dist.group.WORLD, rank, world)
+        (loss * 2.0).backward()
+        if abs(float(loss) - float(loss_ref)) > 1e-5:
+            errs.append("loss %g vs %g" % (float(loss), float(loss_ref)))
+        if not torch.allclose(l_loc.grad, 2.0 * l_ref.grad[:, rank * vl:(rank + 1) * vl], atol=1e-6):
+            errs.append("logit grad")
+
+        # ---- replicated-parameter reduction
+        p = torch.nn.Parameter(torch.zeros(4))
+        p.main_grad = torch.full((4,), float(rank + 1))
+        all_reduce_replicated_grads([p], dist.group.WORLD)
+        if p.main_grad.tolist() != [float(sum(range(1, world + 1)))] * 4:
+            errs.append("replicated grads")
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok" if not errs else "ERR " + ", ".join(errs)))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "ERR " + traceback.format_exc()[-1500:]))

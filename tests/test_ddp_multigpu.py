@@ -19,7 +19,7 @@ def _run(mode: str, nproc: int):
     assert "ok" in proc.stdout
 
 
-@pytest.mark.parametrize("mode", ["fused", "nccl"])
+@pytest.mark.parametrize("mode", ["fused", "nccl", "fused_clip"])
 def test_ddp_two_gpus(mode):
     _run(mode, 2)
 

@@ -164,3 +164,8 @@ def test_config0_tiny_llama_ddp_bitwise(backend):
     assert a["losses"] == b["losses"], "rank losses differ bitwise"
     assert a["grads"] == b["grads"], "post-all-reduce gradients differ bitwise"
     assert a["last"] < a["first"]
+
+
+def test_vocab_parallel_embedding_and_cross_entropy_gloo():
+    out = _spawn(W.vocab_parallel_case, 2)
+    assert all(v == "ok" for v in out.values()), out
