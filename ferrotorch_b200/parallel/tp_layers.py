@@ -79,8 +79,7 @@ class _ColumnParallelFn(torch.autograd.Function):
                 xg = x_rows
         dx = None
         if ctx.needs_input_grad[0]:
-            cap = tp.sm_count - tp.n_copy if (tp.world > 1 and need_w) else 0
-            dx = tp.gemm_rs(b_rs, dy, w, w_is_kn=True, max_ctas=cap)
+            dx = tp.gemm_rs(b_rs, dy, w, w_is_kn=True)
         dw = db = None
         if need_w:
             if tp.world > 1:
