@@ -101,6 +101,11 @@ def run_norm(small):
     emit("rmsnorm_fwd %dx%d" % (T, H), bench(lambda: F.rmsnorm(x, w)), nbytes=4.0 * T * H)
     gu = r(T, 2 * Fd)
     emit("swiglu_fwd %dx%d" % (T, Fd), bench(lambda: F.swiglu(gu)), nbytes=6.0 * T * Fd)
+    gur = gu.clone().requires_grad_()
+    act_out = F.swiglu(gur)
+    dact = r(T, Fd)
+    emit("swiglu_bwd %dx%d" % (T, Fd), bench(lambda: torch.autograd.grad(act_out, gur, dact, retain_graph=True)),
+         nbytes=14.0 * T * Fd)
     qkv = r(T, 48, 128)
     cos, sin = (t.cuda() for t in __import__("ferrotorch_b200.ops.reference", fromlist=["x"]).rope_tables(128, 4096, 5e5))
     emit("rope %d tokens" % T, bench(lambda: F._rope_launch(qkv, cos, sin, None, 40, 4096, 0, False, False)),

@@ -1,6 +1,8 @@
 // Implementation of the host-side helpers declared in ft_host.h.
 #include "ft_host.h"
 
+#include <cstdlib>
+
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -54,6 +56,14 @@ int ensure_device(int device) {
   cudaFree(0);  // binds the primary context to this thread
   current = device;
   return FT_E_OK;
+}
+
+int mem_variant() {
+  static const int v = [] {
+    const char* e = getenv("FT_MEM_VARIANT");
+    return e ? atoi(e) : 1;
+  }();
+  return v;
 }
 
 int sm_count(int device) {

@@ -235,6 +235,61 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
+// Vector version: one thread rotates 8 pairs.  Half-rotation layout: 16 bytes from the first
+// half of a head and the 16 bytes that pair with them in the second half; interleaved layout:
+// 32 contiguous bytes.  cos/sin come as two float4 each.  Needs D % 16 == 0 and 16-byte
+// aligned rows (checked by the launcher).
+__global__ void rope_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t,
+                                const float* __restrict__ sin_t, const int* __restrict__ pos, int T,
+                                int n_rot_heads, int D, long long ld, int seq_len, int pos_offset,
+                                int interleaved, float sign) {
+  const int half = D >> 1;
+  const int groups_per_head = half >> 3;                       // 8 pairs per group
+  const int groups_per_tok = n_rot_heads * groups_per_head;
+  const long long total = static_cast<long long>(T) * groups_per_tok;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / groups_per_tok);
+    const int r = static_cast<int>(i - static_cast<long long>(t) * groups_per_tok);
+    const int h = r / groups_per_head, d = (r - h * groups_per_head) << 3;   // first pair index
+    const int p = pos ? pos[t] : (t % seq_len) + pos_offset;
+    const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * half + d);
+    const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * half + d);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x * sign, s0.y * sign, s0.z * sign, s0.w * sign,
+                         s1.x * sign, s1.y * sign, s1.z * sign, s1.w * sign};
+    __nv_bfloat16* base = x + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D;
+    float a[8], b[8], oa[8], ob[8];
+    if (!interleaved) {
+      uint4* p1 = reinterpret_cast<uint4*>(base + d);
+      uint4* p2 = reinterpret_cast<uint4*>(base + d + half);
+      unpack8(*p1, a);
+      unpack8(*p2, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        oa[j] = a[j] * c[j] - b[j] * sn[j];
+        ob[j] = b[j] * c[j] + a[j] * sn[j];
+      }
+      *p1 = pack8(oa);
+      *p2 = pack8(ob);
+    } else {
+      uint4* pp = reinterpret_cast<uint4*>(base + 2 * d);
+      unpack8(pp[0], a);      // pairs 0..3 as (even, odd)
+      unpack8(pp[1], b);      // pairs 4..7
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        oa[2 * j] = a[2 * j] * c[j] - a[2 * j + 1] * sn[j];
+        oa[2 * j + 1] = a[2 * j + 1] * c[j] + a[2 * j] * sn[j];
+        ob[2 * j] = b[2 * j] * c[4 + j] - b[2 * j + 1] * sn[4 + j];
+        ob[2 * j + 1] = b[2 * j + 1] * c[4 + j] + b[2 * j] * sn[4 + j];
+      }
+      pp[0] = pack8(oa);
+      pp[1] = pack8(ob);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // gu: [T, 2F] (gate = [:, :F], up = [:, F:]), out: [T, F].  act: 0 silu, 1 relu, 2 gelu(tanh).
 __device__ __forceinline__ float act_fwd(float g, int act) {
@@ -292,6 +347,72 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __
     uint4* orow = reinterpret_cast<uint4*>(dgu + t * ld_gu);
     orow[v] = pack8(dg);
     orow[fv + v] = pack8(du);
+  }
+}
+
+// Two vectors per thread with all loads issued first and streaming (evict-first) hints on the
+// inputs, which are read exactly once.
+__global__ void swiglu_fwd2_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                   long long T, int F, long long ld_gu, int act) {
+  const int fv = F >> 3;
+  const long long total = T * fv;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += 2 * stride) {
+    const long long i1 = i0 + stride < total ? i0 + stride : i0;
+    const long long t0 = i0 / fv, t1 = i1 / fv;
+    const int v0 = static_cast<int>(i0 - t0 * fv), v1 = static_cast<int>(i1 - t1 * fv);
+    const uint4* r0 = reinterpret_cast<const uint4*>(gu + t0 * ld_gu);
+    const uint4* r1 = reinterpret_cast<const uint4*>(gu + t1 * ld_gu);
+    const uint4 g0 = __ldcs(r0 + v0), u0 = __ldcs(r0 + fv + v0), g1 = __ldcs(r1 + v1), u1 = __ldcs(r1 + fv + v1);
+    float g[8], u[8], o[8];
+    unpack8(g0, g);
+    unpack8(u0, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], act) * u[j];
+    reinterpret_cast<uint4*>(out + t0 * F)[v0] = pack8(o);
+    if (i1 != i0) {
+      unpack8(g1, g);
+      unpack8(u1, u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], act) * u[j];
+      reinterpret_cast<uint4*>(out + t1 * F)[v1] = pack8(o);
+    }
+  }
+}
+__global__ void swiglu_bwd2_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gu,
+                                   __nv_bfloat16* __restrict__ dgu, long long T, int F, long long ld_gu,
+                                   int act) {
+  const int fv = F >> 3;
+  const long long total = T * fv;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += 2 * stride) {
+    const long long i1 = i0 + stride < total ? i0 + stride : i0;
+    const long long tt[2] = {i0 / fv, i1 / fv};
+    const int vv[2] = {static_cast<int>(i0 - tt[0] * fv), static_cast<int>(i1 - tt[1] * fv)};
+    uint4 gq[2], uq[2], dq[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint4* row = reinterpret_cast<const uint4*>(gu + tt[k] * ld_gu);
+      gq[k] = __ldcs(row + vv[k]);
+      uq[k] = __ldcs(row + fv + vv[k]);
+      dq[k] = __ldcs(reinterpret_cast<const uint4*>(dy + tt[k] * F) + vv[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (k == 1 && i1 == i0) break;
+      float g[8], u[8], d[8], dg[8], du[8];
+      unpack8(gq[k], g);
+      unpack8(uq[k], u);
+      unpack8(dq[k], d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dg[j] = d[j] * u[j] * act_bwd(g[j], act);
+        du[j] = d[j] * act_fwd(g[j], act);
+      }
+      uint4* orow = reinterpret_cast<uint4*>(dgu + tt[k] * ld_gu);
+      orow[vv[k]] = pack8(dg);
+      orow[fv + vv[k]] = pack8(du);
+    }
   }
 }
 
@@ -387,9 +508,15 @@ FT_API int ft_rope(void* x, const float* cos_t, const float* sin_t, const int* p
   FT_REQUIRE(pos || seq_len > 0, "ft_rope: need positions or seq_len");
   if (T <= 0 || n_rot_heads <= 0) return FT_E_OK;
   const long long work = static_cast<long long>(T) * n_rot_heads * (D / 4);
-  rope_kernel<<<blocks_for(work, 256, device), 256, 0, stream>>>(
-      static_cast<__nv_bfloat16*>(x), cos_t, sin_t, pos, T, n_rot_heads, D, ld, seq_len, pos_offset,
-      interleaved, backward ? -1.f : 1.f);
+  if (mem_variant() != 0 && D % 16 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0)
+    rope_vec_kernel<<<blocks_for(work / 4, 256, device), 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(x), cos_t, sin_t, pos, T, n_rot_heads, D, ld, seq_len, pos_offset,
+        interleaved, backward ? -1.f : 1.f);
+  else
+    rope_kernel<<<blocks_for(work, 256, device), 256, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(x), cos_t, sin_t, pos, T, n_rot_heads, D, ld, seq_len, pos_offset,
+        interleaved, backward ? -1.f : 1.f);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
@@ -401,8 +528,12 @@ FT_API int ft_swiglu_fwd(const void* gu, void* out, long long T, int F, long lon
   FT_REQUIRE(gu && out, "ft_swiglu_fwd: null pointer");
   FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_fwd: F must be a multiple of 8");
   if (T <= 0) return FT_E_OK;
-  swiglu_fwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
+  if (mem_variant() != 0)
+    swiglu_fwd2_kernel<<<blocks_for(T * (F / 8) / 2 + 1, 256, device), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
+  else
+    swiglu_fwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
@@ -414,9 +545,14 @@ FT_API int ft_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long T,
   FT_REQUIRE(dy && gu && dgu, "ft_swiglu_bwd: null pointer");
   FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_bwd: F must be a multiple of 8");
   if (T <= 0) return FT_E_OK;
-  swiglu_bwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
-      static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
+  if (mem_variant() != 0)
+    swiglu_bwd2_kernel<<<blocks_for(T * (F / 8) / 2 + 1, 256, device), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
+        static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
+  else
+    swiglu_bwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
+        static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
