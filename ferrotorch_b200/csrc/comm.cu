@@ -273,6 +273,69 @@ allgather_pull_kernel(PeerTable src, uint8_t* out, long long bytes_per_rank, con
   }
 }
 
+// General pull exchange (all-gather, all-to-all, uneven all-to-all): from every rank r copy
+// bytes[r] bytes at offset src_off[r] of r's symmetric send buffer to out + dst_off[r].
+// Raises this rank's ready flag first (its own send buffer is final in stream order), waits for
+// every peer's, pulls in rotated rank order, and the last block raises the done flag on every
+// peer: "this rank no longer reads your send buffer".
+struct ExchangeArgs {
+  PeerTable src;
+  uint8_t* out;
+  long long src_off[COMM_MAX_RANKS], dst_off[COMM_MAX_RANKS], bytes[COMM_MAX_RANKS];
+  PeerTable flags;
+  unsigned int* block_counter;
+  int rank, world, slot, n_slots;
+  uint32_t epoch;
+  unsigned long long limit_ns;
+  int* status;
+};
+
+__global__ void __launch_bounds__(COMM_THREADS) exchange_pull_kernel(const ExchangeArgs a) {
+  const uint32_t* my_flags = static_cast<const uint32_t*>(a.flags.ptr[a.rank]);
+  if (blockIdx.x == 0 && threadIdx.x < a.world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(a.flags.ptr[threadIdx.x]) + flag_index(0, a.slot, a.rank, a.n_slots),
+                   a.epoch);
+  }
+  if (!wait_flags(my_flags + flag_index(0, a.slot, 0, a.n_slots), a.world, a.epoch, a.limit_ns, a.status)) return;
+  for (int k = 0; k < a.world; ++k) {
+    const int r = (a.rank + k) % a.world;
+    const uint8_t* s = static_cast<const uint8_t*>(a.src.ptr[r]) + a.src_off[r];
+    uint8_t* d = a.out + a.dst_off[r];
+    const long long nvec = a.bytes[r] >> 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const long long i = i0 + q * stride;
+        v[q] = ld_cg_u4(s + ((i < nvec ? i : i0) << 4));
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const long long i = i0 + q * stride;
+        if (i < nvec) *reinterpret_cast<uint4*>(d + (i << 4)) = v[q];
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned int s_last;
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(a.block_counter + a.slot, 1u);
+    s_last = (done == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) a.block_counter[a.slot] = 0u;
+    if (threadIdx.x < a.world) {
+      __threadfence_system();
+      st_release_sys(static_cast<uint32_t*>(a.flags.ptr[threadIdx.x]) + flag_index(1, a.slot, a.rank, a.n_slots),
+                     a.epoch);
+    }
+  }
+}
+
 static int fill_table(PeerTable& t, void* const* ptrs, int world) {
   for (int i = 0; i < COMM_MAX_RANKS; ++i) t.ptr[i] = i < world ? ptrs[i] : nullptr;
   for (int i = 0; i < world; ++i)
@@ -374,6 +437,43 @@ FT_API int ft_allgather(void* const* src_ptrs, void* out, long long bytes_per_ra
       world, epoch, limit, device_status_word(device));
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch(2);
+  return FT_E_OK;
+}
+
+// Pull exchange over symmetric send buffers (see exchange_pull_kernel).  src_off / dst_off /
+// bytes: host arrays of `world` entries, all multiples of 16.  block_counter: n_slots zeroed
+// uint32 words in local memory.  Before the send buffer is written again the caller waits for
+// flag (kind 1, slot) == epoch of this call (ft_comm_wait).
+FT_API int ft_peer_exchange(void* const* src_ptrs, void* out, const long long* src_off, const long long* dst_off,
+                            const long long* bytes, void* const* flag_ptrs, unsigned int* block_counter,
+                            int slot, int n_slots, int rank, int world, unsigned int epoch, int blocks,
+                            long long timeout_ms, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  ExchangeArgs a;
+  FT_REQUIRE(world >= 1 && world <= COMM_MAX_RANKS && rank >= 0 && rank < world && out && block_counter &&
+                 fill_table(a.src, src_ptrs, world) == 0 && fill_table(a.flags, flag_ptrs, world) == 0,
+             "ft_peer_exchange: bad arguments");
+  FT_REQUIRE(slot >= 0 && slot < n_slots && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "ft_peer_exchange: bad slot or unaligned output");
+  long long most = 0;
+  for (int r = 0; r < COMM_MAX_RANKS; ++r) {
+    a.src_off[r] = r < world ? src_off[r] : 0;
+    a.dst_off[r] = r < world ? dst_off[r] : 0;
+    a.bytes[r] = r < world ? bytes[r] : 0;
+    FT_REQUIRE(((a.src_off[r] | a.dst_off[r] | a.bytes[r]) & 15) == 0 && a.bytes[r] >= 0,
+               "ft_peer_exchange: offsets and sizes must be multiples of 16 bytes");
+    if (a.bytes[r] > most) most = a.bytes[r];
+  }
+  a.out = static_cast<uint8_t*>(out); a.block_counter = block_counter;
+  a.rank = rank; a.world = world; a.slot = slot; a.n_slots = n_slots; a.epoch = epoch;
+  a.limit_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 20000) * 1000000ull;
+  a.status = device_status_word(device);
+  long long grid = ((most >> 4) + 4LL * COMM_THREADS - 1) / (4LL * COMM_THREADS);
+  const long long cap = blocks > 0 ? blocks : sm_count(device);
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  exchange_pull_kernel<<<static_cast<unsigned>(grid), COMM_THREADS, 0, stream>>>(a);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   return FT_E_OK;
 }
 

@@ -1,15 +1,25 @@
 """ResNet-18 / 34 / 50 (ferrotorch-vision/src/models/resnet.rs:325 ``Bottleneck``, :565 ``ResNet``,
 :1071 ``resnet50``) and a small model registry (models/registry.rs).
 
-Layers are torch.nn (cuDNN convolutions and batch norm as the library baseline for the conv
-path); the data-parallel gradient exchange and the SGD update run through the fused
-``ft_ddp_reduce_update`` kernel when trained with ``FlatTrainer`` + ``FusedDDP``.  State-dict
+Convolutions are torch.nn (cuDNN, channels-last); every batch norm runs fused with the ReLU and
+the residual add that follow it (``ops/batchnorm.py``: two reads and one write of the activation
+in the forward, no stored ReLU mask); the data-parallel gradient exchange and the SGD update run
+through the fused ``ft_ddp_reduce_update`` kernel when trained with ``FlatTrainer`` + ``FusedDDP``.  State-dict
 keys match torchvision's (``conv1.weight``, ``layer1.0.conv1.weight``, ``fc.weight`` ...).
 """
 from __future__ import annotations
 
 import torch
 from torch import nn
+
+from ..ops.batchnorm import batch_norm_act as _bn
+
+
+def _downsample(seq: nn.Sequential, x: torch.Tensor) -> torch.Tensor:
+    """The projection shortcut ``Sequential(conv, bn)`` with the fused batch norm (no ReLU)."""
+    if len(seq) == 2 and isinstance(seq[1], nn.BatchNorm2d):
+        return _bn(seq[0](x), seq[1], relu=False)
+    return seq(x)
 
 
 class BasicBlock(nn.Module):
@@ -25,10 +35,9 @@ class BasicBlock(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        idt = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
-        return self.relu(out + idt)
+        idt = x if self.downsample is None else _downsample(self.downsample, x)
+        out = _bn(self.conv1(x), self.bn1)
+        return _bn(self.conv2(out), self.bn2, residual=idt)
 
 
 class Bottleneck(nn.Module):
@@ -46,11 +55,10 @@ class Bottleneck(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        idt = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
-        return self.relu(out + idt)
+        idt = x if self.downsample is None else _downsample(self.downsample, x)
+        out = _bn(self.conv1(x), self.bn1)
+        out = _bn(self.conv2(out), self.bn2)
+        return _bn(self.conv3(out), self.bn3, residual=idt)
 
 
 class ResNet(nn.Module):
@@ -96,7 +104,7 @@ class ResNet(nn.Module):
         return nn.Sequential(*layers)
 
     def forward(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(_bn(self.conv1(x), self.bn1))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(torch.flatten(self.avgpool(x), 1))
 
