@@ -9,7 +9,8 @@
 // residual was added), so no mask tensor is stored.
 //
 // All reductions are deterministic: per-block partial sums in a scratch buffer, combined in
-// double precision by a one-thread-per-channel finalize kernel.
+// double precision and in a fixed order by a small finalize kernel, which also adds dgamma /
+// dbeta straight into the trainer's gradient arena when there is one.
 #include "ft_host.h"
 #include "ft_ptx.cuh"
 
@@ -133,21 +134,44 @@ bn_colsum_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   }
 }
 
-// Forward finalize: one thread per channel.  Writes mean, invstd (kept for the backward),
-// scale = gamma * invstd, shift = beta - mean * scale, and updates the running statistics
-// (unbiased variance) when they are given.
-__global__ void bn_fwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long R, int C,
-                                       const void* gamma, const void* beta, int affine_f32, void* running_mean,
-                                       void* running_var, int running_f32, float momentum, float eps,
-                                       float* __restrict__ mean, float* __restrict__ invstd,
-                                       float* __restrict__ scale, float* __restrict__ shift) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0.0, q = 0.0;
-  for (int b = 0; b < blocks; ++b) {
-    s += partial[(static_cast<size_t>(b) * 2) * C + c];
-    q += partial[(static_cast<size_t>(b) * 2 + 1) * C + c];
+// Sum the per-block partials of 32 channels: blockDim = (32 channels, BN_FIN_GROUPS); group g adds
+// the partials b = g, g + G, ... in double, then the groups are combined in a fixed order.
+// Returns the two totals to the threads with threadIdx.y == 0.
+constexpr int BN_FIN_GROUPS = 32;
+__device__ __forceinline__ void bn_reduce_partials(const float* __restrict__ partial, int blocks, int C, int c,
+                                                   double& s, double& q) {
+  __shared__ double red[2][BN_FIN_GROUPS][33];
+  double a0 = 0.0, a1 = 0.0;
+  if (c < C) {
+    for (int b = threadIdx.y; b < blocks; b += BN_FIN_GROUPS) {
+      a0 += partial[(static_cast<size_t>(b) * 2) * C + c];
+      a1 += partial[(static_cast<size_t>(b) * 2 + 1) * C + c];
+    }
   }
+  red[0][threadIdx.y][threadIdx.x] = a0;
+  red[1][threadIdx.y][threadIdx.x] = a1;
+  __syncthreads();
+  s = q = 0.0;
+  if (threadIdx.y == 0) {
+    for (int g = 0; g < BN_FIN_GROUPS; ++g) {
+      s += red[0][g][threadIdx.x];
+      q += red[1][g][threadIdx.x];
+    }
+  }
+}
+
+// Forward finalize.  Writes mean, invstd (kept for the backward), scale = gamma * invstd,
+// shift = beta - mean * scale, and updates the running statistics (unbiased variance) when given.
+__global__ void __launch_bounds__(32 * BN_FIN_GROUPS)
+bn_fwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long R, int C,
+                       const void* gamma, const void* beta, int affine_f32, void* running_mean,
+                       void* running_var, int running_f32, float momentum, float eps,
+                       float* __restrict__ mean, float* __restrict__ invstd,
+                       float* __restrict__ scale, float* __restrict__ shift) {
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  double s, q;
+  bn_reduce_partials(partial, blocks, C, c, s, q);
+  if (threadIdx.y != 0 || c >= C) return;
   const double m = s / static_cast<double>(R);
   double var = q / static_cast<double>(R) - m * m;
   if (var < 0.0) var = 0.0;
@@ -217,20 +241,30 @@ bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
-// Backward finalize: dgamma, dbeta (fp32) and the per-channel coefficients of
+// Backward finalize: dgamma, dbeta and the per-channel coefficients of
 //   dx = c1 * (dz - c2 - xhat * c3),  c1 = gamma * invstd, c2 = dbeta / R, c3 = dgamma / R.
-__global__ void bn_bwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long R, int C,
-                                       const float* __restrict__ scale, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta, float* __restrict__ coef) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double db = 0.0, dg = 0.0;
-  for (int b = 0; b < blocks; ++b) {
-    db += partial[(static_cast<size_t>(b) * 2) * C + c];
-    dg += partial[(static_cast<size_t>(b) * 2 + 1) * C + c];
+// grad_kind 0: dgamma / dbeta are stored as fp32; 1: added to bf16 accumulators; 2: added to
+// fp32 accumulators (the gradient arena of the flat-parameter trainer).
+__global__ void __launch_bounds__(32 * BN_FIN_GROUPS)
+bn_bwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long R, int C,
+                       const float* __restrict__ scale, void* dgamma, void* dbeta, int grad_kind,
+                       float* __restrict__ coef) {
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  double db, dg;
+  bn_reduce_partials(partial, blocks, C, c, db, dg);
+  if (threadIdx.y != 0 || c >= C) return;
+  if (grad_kind == 1) {
+    __nv_bfloat16* g = static_cast<__nv_bfloat16*>(dgamma);
+    __nv_bfloat16* b = static_cast<__nv_bfloat16*>(dbeta);
+    if (g) g[c] = __float2bfloat16(__bfloat162float(g[c]) + static_cast<float>(dg));
+    if (b) b[c] = __float2bfloat16(__bfloat162float(b[c]) + static_cast<float>(db));
+  } else if (grad_kind == 2) {
+    if (dgamma) static_cast<float*>(dgamma)[c] += static_cast<float>(dg);
+    if (dbeta) static_cast<float*>(dbeta)[c] += static_cast<float>(db);
+  } else {
+    if (dgamma) static_cast<float*>(dgamma)[c] = static_cast<float>(dg);
+    if (dbeta) static_cast<float*>(dbeta)[c] = static_cast<float>(db);
   }
-  dbeta[c] = static_cast<float>(db);
-  dgamma[c] = static_cast<float>(dg);
   coef[c] = scale[c];
   coef[C + c] = static_cast<float>(db / static_cast<double>(R));
   coef[2 * C + c] = static_cast<float>(dg / static_cast<double>(R));
@@ -291,7 +325,7 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 static int bn_blocks(long long R, int C, int device) {
   const int rows_per_pass = BN_THREADS / (C >> 3);
   long long b = (R + 2LL * rows_per_pass - 1) / (2LL * rows_per_pass);
-  long long cap = static_cast<long long>(sm_count(device)) * 4;
+  long long cap = static_cast<long long>(sm_count(device)) * 2;
   if (cap > BN_MAX_BLOCKS) cap = BN_MAX_BLOCKS;
   if (b > cap) b = cap;
   return b < 1 ? 1 : static_cast<int>(b);
@@ -324,7 +358,7 @@ FT_API int ft_bn_act_fwd(const void* x, const void* residual, void* y, const voi
   bn_colsum_kernel<0><<<blocks, BN_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), nullptr, nullptr,
                                                          nullptr, nullptr, nullptr, nullptr, 0, R, C, scratch);
   FT_CUDA_CHECK(cudaGetLastError());
-  bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, blocks, R, C, gamma, beta, affine_f32,
+  bn_fwd_finalize_kernel<<<(C + 31) / 32, dim3(32, BN_FIN_GROUPS), 0, stream>>>(scratch, blocks, R, C, gamma, beta, affine_f32,
                                                               running_mean, running_var, running_f32, momentum, eps,
                                                               stats, stats + C, stats + 2 * C, stats + 3 * C);
   FT_CUDA_CHECK(cudaGetLastError());
@@ -355,12 +389,14 @@ FT_API int ft_bn_act_apply(const void* x, const void* residual, void* y, const f
 
 // Training backward.  y is the forward output, needed only when a residual was added before
 // the ReLU (else pass null and the mask is recomputed from x).  dres (optional): gradient of the
-// residual branch.  dgamma_dbeta: 2 * C floats out.  coef: 3 * C floats of scratch.
+// residual branch.  dgamma / dbeta (each optional): [C]; grad_kind 0 = fp32 store, 1 = bf16
+// accumulate, 2 = fp32 accumulate.  coef: 3 * C floats of scratch.
 FT_API int ft_bn_act_bwd(const void* x, const void* dy, const void* y, const float* stats, int relu, long long R,
-                         int C, void* dx, void* dres, float* dgamma_dbeta, float* coef, float* scratch, int device,
-                         cudaStream_t stream) {
+                         int C, void* dx, void* dres, void* dgamma, void* dbeta, int grad_kind, float* coef,
+                         float* scratch, int device, cudaStream_t stream) {
   if (int _rc = ft::ensure_device(device)) return _rc;
-  FT_REQUIRE(x && dy && stats && dx && dgamma_dbeta && coef && scratch, "ft_bn_act_bwd: null pointer");
+  FT_REQUIRE(x && dy && stats && dx && coef && scratch, "ft_bn_act_bwd: null pointer");
+  FT_REQUIRE(grad_kind >= 0 && grad_kind <= 2, "ft_bn_act_bwd: bad grad_kind");
   FT_REQUIRE(R > 0 && C >= 8 && C % 8 == 0 && C <= BN_MAX_C, "ft_bn_act_bwd: C must be a multiple of 8 in [8, 2048]");
   const float *mean = stats, *invstd = stats + C, *scale = stats + 2 * C, *shift = stats + 3 * C;
   const int blocks = bn_blocks(R, C, device);
@@ -368,8 +404,8 @@ FT_API int ft_bn_act_bwd(const void* x, const void* dy, const void* y, const flo
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
       static_cast<const __nv_bfloat16*>(y), mean, invstd, scale, shift, relu, R, C, scratch);
   FT_CUDA_CHECK(cudaGetLastError());
-  bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, blocks, R, C, scale, dgamma_dbeta,
-                                                              dgamma_dbeta + C, coef);
+  bn_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, BN_FIN_GROUPS), 0, stream>>>(scratch, blocks, R, C, scale, dgamma,
+                                                                                  dbeta, grad_kind, coef);
   FT_CUDA_CHECK(cudaGetLastError());
   const long long total_vec = R * (C >> 3);
   bn_bwd_apply_kernel<<<bn_elem_blocks(total_vec, device), BN_THREADS, 0, stream>>>(

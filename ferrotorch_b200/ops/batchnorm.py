@@ -23,7 +23,7 @@ _native.register_protos({
     "ft_bn_scratch_floats": (_ll, [_i]),
     "ft_bn_act_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _f, _f, _i, _ll, _i, _vp, _vp, _i, _vp]),
     "ft_bn_act_apply": (_i, [_vp, _vp, _vp, _vp, _i, _ll, _i, _i, _vp]),
-    "ft_bn_act_bwd": (_i, [_vp, _vp, _vp, _vp, _i, _ll, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "ft_bn_act_bwd": (_i, [_vp, _vp, _vp, _vp, _i, _ll, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp]),
 })
 
 MAX_C = 2048
@@ -70,14 +70,15 @@ class _BatchNormActFn(torch.autograd.Function):
         _native.check(rc, "ft_bn_act_fwd")
         keep_y = relu and residual is not None
         ctx.save_for_backward(x, y if keep_y else x.new_empty(0), stats)
-        ctx.cfg = (bool(relu), residual is not None, keep_y, weight.dtype if weight is not None else None,
-                   weight is not None, bias is not None)
+        ctx.cfg = (bool(relu), residual is not None, keep_y)
+        ctx.affine = (weight, bias)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, y, stats = ctx.saved_tensors
-        relu, has_res, keep_y, wdtype, has_w, has_b = ctx.cfg
+        relu, has_res, keep_y = ctx.cfg
+        weight, bias = ctx.affine
         C = x.shape[1]
         R = x.numel() // C
         if dy.stride() != x.stride():
@@ -85,14 +86,35 @@ class _BatchNormActFn(torch.autograd.Function):
         dx = torch.empty_like(x)
         # without a ReLU the residual branch's gradient is dy itself
         dres = torch.empty_like(x) if (has_res and relu) else None
-        dgdb = torch.empty(2 * C, device=x.device, dtype=torch.float32)
         coef = torch.empty(3 * C, device=x.device, dtype=torch.float32)
+        need_w = weight is not None and ctx.needs_input_grad[1]
+        need_b = bias is not None and ctx.needs_input_grad[2]
+        # the flat-arena trainer owns the gradients: the finalize kernel adds into its arena
+        wg = getattr(weight, "main_grad", None) if need_w else None
+        bg = getattr(bias, "main_grad", None) if need_b else None
+        arena = (wg is not None or not need_w) and (bg is not None or not need_b) and (need_w or need_b) and \
+            all(g is None or g.dtype in (torch.bfloat16, torch.float32) for g in (wg, bg)) and \
+            (wg is None or bg is None or wg.dtype == bg.dtype)
+        dgdb = None
+        if arena:
+            gp, bp = _ptr(wg), _ptr(bg)
+            kind = 1 if (wg if wg is not None else bg).dtype == torch.bfloat16 else 2
+        else:
+            dgdb = torch.empty(2 * C, device=x.device, dtype=torch.float32)
+            gp, bp, kind = dgdb.data_ptr(), dgdb.data_ptr() + 4 * C, 0
         rc = _native.kernels().ft_bn_act_bwd(
             x.data_ptr(), dy.data_ptr(), y.data_ptr() if keep_y else None, stats.data_ptr(), int(relu), R, C,
-            dx.data_ptr(), _ptr(dres), dgdb.data_ptr(), coef.data_ptr(), _scratch(x).data_ptr(), F._dev(x), F._stream())
+            dx.data_ptr(), _ptr(dres), gp, bp, kind, coef.data_ptr(), _scratch(x).data_ptr(), F._dev(x), F._stream())
         _native.check(rc, "ft_bn_act_bwd")
-        dw = dgdb[:C].to(wdtype) if has_w and ctx.needs_input_grad[1] else None
-        db = dgdb[C:].to(wdtype) if has_b and ctx.needs_input_grad[2] else None
+        dw = db = None
+        if arena:
+            for p in (weight if need_w else None, bias if need_b else None):
+                hook = getattr(p, "grad_ready_hook", None) if p is not None else None
+                if hook is not None:
+                    hook(p)
+        else:
+            dw = dgdb[:C].to(weight.dtype) if need_w else None
+            db = dgdb[C:].to(bias.dtype) if need_b else None
         if has_res:
             dres = dres if relu else dy
         return dx, dw, db, (dres if has_res else None), None, None, None, None, None
