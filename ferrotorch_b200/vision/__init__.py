@@ -1,0 +1,93 @@
+"""Vision: models, transforms, datasets and detection ops.
+
+The reference's ``ferrotorch-vision`` has ten classifier families, seven detectors, four
+segmenters, a model registry, MNIST / CIFAR / ImageFolder readers, 17 transforms, image IO and
+NMS / RoIAlign (ferrotorch-vision/src/models/*, datasets/*, transforms/*, ops/*).  Here the ResNet
+family is this package's own (``models/resnet.py``: channels-last bf16 with the fused batch-norm
+kernels); everything else comes from ``torchvision`` as part of the framework layer and is
+re-exported under the reference's names through one registry.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ..models.resnet import create_model, list_models, register_model, resnet18, resnet34, resnet50  # noqa: F401
+
+try:
+    import torchvision
+    from torchvision import datasets, io, ops, transforms  # noqa: F401
+    from torchvision.datasets import CIFAR10, CIFAR100, MNIST, ImageFolder  # noqa: F401
+    from torchvision.ops import box_iou, nms, roi_align  # noqa: F401
+
+    HAVE_TORCHVISION = True
+except Exception:  # noqa: BLE001
+    torchvision = None
+    HAVE_TORCHVISION = False
+
+# reference name -> torchvision constructor name
+CLASSIFIERS = {"vgg11": "vgg11", "vgg16": "vgg16", "vit_b_16": "vit_b_16", "efficientnet_b0": "efficientnet_b0",
+               "convnext_tiny": "convnext_tiny", "swin_t": "swin_t", "mobilenet_v2": "mobilenet_v2",
+               "mobilenet_v3_small": "mobilenet_v3_small", "mobilenet_v3_large": "mobilenet_v3_large",
+               "densenet121": "densenet121", "inception_v3": "inception_v3"}
+DETECTORS = {"faster_rcnn": "fasterrcnn_resnet50_fpn", "mask_rcnn": "maskrcnn_resnet50_fpn",
+             "keypoint_rcnn": "keypointrcnn_resnet50_fpn", "retinanet": "retinanet_resnet50_fpn",
+             "fcos": "fcos_resnet50_fpn", "ssd300": "ssd300_vgg16", "ssdlite": "ssdlite320_mobilenet_v3_large"}
+SEGMENTERS = {"deeplabv3": "deeplabv3_resnet50", "fcn": "fcn_resnet50", "lraspp": "lraspp_mobilenet_v3_large"}
+
+
+def _tv(name: str, **kw) -> nn.Module:
+    if not HAVE_TORCHVISION:
+        raise ImportError("torchvision is needed for %r" % name)
+    kw.setdefault("weights", None)
+    if name in DETECTORS.values() or name in SEGMENTERS.values():
+        kw.setdefault("weights_backbone", None)
+    return torchvision.models.get_model(name, **kw)
+
+
+def build(name: str, **kw) -> nn.Module:
+    """One constructor for every model name of the reference's registry."""
+    if name in list_models():
+        return create_model(name, **kw)
+    for table in (CLASSIFIERS, DETECTORS, SEGMENTERS):
+        if name in table:
+            return _tv(table[name], **kw)
+    if name == "unet":
+        return UNet(**kw)
+    return create_model(name, **kw)
+
+
+def available() -> list[str]:
+    return sorted(set(list_models()) | set(CLASSIFIERS) | set(DETECTORS) | set(SEGMENTERS) | {"unet"})
+
+
+class UNet(nn.Module):
+    """Encoder-decoder with skip connections (ferrotorch-vision/src/models/segmentation/unet.rs);
+    torchvision has no UNet, so this one is written out."""
+
+    def __init__(self, in_channels: int = 3, num_classes: int = 2, base: int = 32, depth: int = 4):
+        super().__init__()
+
+        def block(i, o):
+            return nn.Sequential(nn.Conv2d(i, o, 3, padding=1, bias=False), nn.BatchNorm2d(o), nn.ReLU(inplace=True),
+                                 nn.Conv2d(o, o, 3, padding=1, bias=False), nn.BatchNorm2d(o), nn.ReLU(inplace=True))
+
+        chans = [base * 2 ** i for i in range(depth + 1)]
+        self.down = nn.ModuleList(block(in_channels if i == 0 else chans[i - 1], chans[i]) for i in range(depth + 1))
+        self.up = nn.ModuleList(nn.ConvTranspose2d(chans[i + 1], chans[i], 2, stride=2) for i in reversed(range(depth)))
+        self.dec = nn.ModuleList(block(2 * chans[i], chans[i]) for i in reversed(range(depth)))
+        self.head = nn.Conv2d(chans[0], num_classes, 1)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        skips = []
+        for i, d in enumerate(self.down):
+            x = d(x if i == 0 else nn.functional.max_pool2d(x, 2))
+            skips.append(x)
+        skips.pop()
+        for up, dec in zip(self.up, self.dec):
+            x = up(x)
+            s = skips.pop()
+            if x.shape[-2:] != s.shape[-2:]:
+                x = nn.functional.interpolate(x, size=s.shape[-2:], mode="nearest")
+            x = dec(torch.cat([s, x], 1))
+        return self.head(x)

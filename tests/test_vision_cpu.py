@@ -1,0 +1,59 @@
+"""Vision registry: every model family of the reference constructs and runs a forward on CPU."""
+import pytest
+import torch
+
+from ferrotorch_b200 import vision
+
+tv = pytest.mark.skipif(not vision.HAVE_TORCHVISION, reason="torchvision not installed")
+
+
+def test_registry_lists_every_family():
+    names = vision.available()
+    for n in ["resnet18", "resnet50", "vgg16", "vit_b_16", "efficientnet_b0", "convnext_tiny", "swin_t", "mobilenet_v2",
+              "densenet121", "inception_v3", "faster_rcnn", "mask_rcnn", "retinanet", "fcos", "ssd300", "deeplabv3",
+              "fcn", "lraspp", "unet"]:
+        assert n in names, n
+
+
+@tv
+@pytest.mark.parametrize("name,size", [("vgg11", 64), ("mobilenet_v2", 64), ("densenet121", 64), ("convnext_tiny", 64),
+                                       ("efficientnet_b0", 64), ("swin_t", 64), ("vit_b_16", 224)])
+def test_classifiers_forward(name, size):
+    m = vision.build(name, num_classes=7).eval()
+    with torch.no_grad():
+        assert m(torch.randn(1, 3, size, size)).shape == (1, 7)
+
+
+@tv
+def test_segmenters_and_unet_forward():
+    x = torch.randn(1, 3, 64, 64)
+    with torch.no_grad():
+        assert vision.build("fcn", num_classes=5).eval()(x)["out"].shape == (1, 5, 64, 64)
+        assert vision.build("lraspp", num_classes=5).eval()(x)["out"].shape == (1, 5, 64, 64)
+        assert vision.build("unet", num_classes=3, base=8, depth=3).eval()(x).shape == (1, 3, 64, 64)
+        assert vision.build("unet", num_classes=3, base=8, depth=3).eval()(torch.randn(1, 3, 50, 70)).shape == (1, 3, 50, 70)
+
+
+@tv
+def test_detector_and_ops():
+    m = vision.build("retinanet", num_classes=4).eval()
+    with torch.no_grad():
+        out = m([torch.rand(3, 128, 128)])
+    assert set(out[0]) == {"boxes", "scores", "labels"}
+    boxes = torch.tensor([[0.0, 0, 10, 10], [1, 1, 11, 11], [50, 50, 60, 60]])
+    keep = vision.nms(boxes, torch.tensor([0.9, 0.8, 0.7]), 0.5)
+    assert keep.tolist() == [0, 2]
+    assert vision.box_iou(boxes[:1], boxes[:1]).item() == pytest.approx(1.0)
+    feats = torch.arange(16.0).view(1, 1, 4, 4)
+    assert vision.roi_align(feats, [torch.tensor([[0.0, 0, 4, 4]])], output_size=2).shape == (1, 1, 2, 2)
+
+
+def test_own_resnet_keys_match_torchvision():
+    if not vision.HAVE_TORCHVISION:
+        pytest.skip("torchvision not installed")
+    import torchvision
+
+    ours = vision.build("resnet50").state_dict()
+    theirs = torchvision.models.resnet50(weights=None).state_dict()
+    assert set(ours) == set(theirs)
+    assert all(ours[k].shape == theirs[k].shape for k in ours)
