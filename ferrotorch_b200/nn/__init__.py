@@ -8,3 +8,5 @@ from torch.nn import functional, init, utils  # noqa: F401
 from .layers import (FusedLinearActivation, GQAAttention, KVCache, Linear, RMSNorm,  # noqa: F401
                      RotaryPositionEmbedding, SwiGLU, clip_grad_norm_, clip_grad_value_, repeat_kv,
                      scaled_dot_product_attention)
+
+from ..ops.batchnorm import BatchNormAct2d, batch_norm_act  # noqa: F401,E402

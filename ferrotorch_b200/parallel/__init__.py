@@ -7,3 +7,18 @@ from .fsdp import FSDP, ShardingStrategy, SyncBatchNorm2d  # noqa: F401
 from .host_ddp import DDP  # noqa: F401
 from .mesh import DeviceMesh, DTensor, Partial, Replicate, Shard  # noqa: F401
 from .pipeline import Pipeline  # noqa: F401
+from .dist_checkpoint import (AsyncDistributedCheckpointer, PendingCollective, RpcAgent, all_gather_async,  # noqa: F401,E402
+                              all_reduce_async, load_distributed, save_distributed)
+
+
+def __getattr__(name):
+    """GPU-side classes are imported on first use (they load the kernel library)."""
+    lazy = {"FusedDDP": "ddp", "SymmetricBuffer": "ddp", "CommTimeout": "ddp", "TPContext": "tensor_parallel",
+            "ColumnParallelLinear": "tp_layers", "RowParallelLinear": "tp_layers",
+            "VocabParallelEmbedding": "tp_layers", "vocab_parallel_cross_entropy": "tp_layers",
+            "PeerCollectives": "peer_collectives"}
+    if name in lazy:
+        import importlib
+
+        return getattr(importlib.import_module("." + lazy[name], __name__), name)
+    raise AttributeError(name)
