@@ -63,9 +63,13 @@ def sample_next(logits: torch.Tensor, cfg: GenerationConfig, prev_tokens: torch.
 
 @torch.no_grad()
 def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None,
-             streamer: Callable[[torch.Tensor], None] | None = None) -> torch.Tensor:
+             streamer: Callable[[torch.Tensor], None] | None = None,
+             logits_processor: Callable[[torch.Tensor, torch.Tensor], torch.Tensor] | None = None) -> torch.Tensor:
     """``input_ids [B, S]`` -> ``[B, S + new]``.  ``model(ids, caches=..., last_token_only=True)`` must
-    return logits and append to the caches it is given (``model.make_caches``)."""
+    return logits and append to the caches it is given (``model.make_caches``).
+    ``logits_processor(generated_ids [B, n], logits [B, V]) -> logits`` runs before sampling, e.g. a
+    :class:`GrammarLogitsProcessor` for grammar-constrained decoding
+    (ferrotorch-llama/src/grammar_decode.rs masks the logits the same way)."""
     cfg = cfg or GenerationConfig()
     B, S = input_ids.shape
     dev = input_ids.device
@@ -77,6 +81,8 @@ def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None
     out = input_ids
     done = torch.zeros(B, dtype=torch.bool, device=dev)
     for _ in range(cfg.max_new_tokens):
+        if logits_processor is not None:
+            logits = logits_processor(out[:, S:], logits.float())
         tok = sample_next(logits, cfg, out, gen)
         if cfg.eos_token_id is not None:
             tok = torch.where(done, torch.full_like(tok, cfg.eos_token_id), tok)
@@ -88,6 +94,24 @@ def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None
             break
         logits = model(tok[:, None], caches=caches, last_token_only=True)[:, -1]
     return out
+
+
+class GrammarLogitsProcessor:
+    """Mask the logits so that every sequence stays a valid prefix of the grammar (and may only
+    end once it is complete).  ``vocab[i]`` is the text of token ``i``; the per-step mask is built
+    on the host from the grammar state and applied on the logits' device."""
+
+    def __init__(self, grammar, vocab: list[str], eos_token_id: int | None = None):
+        self.grammar, self.vocab, self.eos = grammar, vocab, eos_token_id
+
+    def __call__(self, generated: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        from ..utils.text import apply_token_mask, token_mask
+
+        rows = []
+        for ids in generated.tolist():
+            text = "".join(self.vocab[t] for t in ids if t != self.eos)
+            rows.append(token_mask(self.grammar, text, self.vocab, self.eos))
+        return apply_token_mask(logits, torch.stack(rows))
 
 
 @torch.no_grad()

@@ -81,3 +81,28 @@ def test_beam_search_and_speculative_decoding():
     assert torch.equal(out, greedy) and stats["proposed"] >= stats["accepted"] and stats["target_calls"] <= 6
     out2, stats2 = G.speculative_decode(m, m, ids, max_new_tokens=6, gamma=3)
     assert torch.equal(out2, greedy) and stats2["accepted"] == stats2["proposed"]
+
+
+def test_grammar_constrained_generate_yields_valid_json():
+    import json
+
+    from ferrotorch_b200.models.generation import GenerationConfig, GrammarLogitsProcessor, generate
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.utils.text import JsonGrammar
+
+    vocab = ["{", "}", '"a"', '"b"', ":", ",", "1", "2", "[", "]", "true", " ", "<eos>", "x", "y", "z"]
+    cfg = LlamaConfig(vocab_size=len(vocab), hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                      num_attention_heads=2, num_key_value_heads=1, head_dim=16, max_position_embeddings=128)
+    torch.manual_seed(3)
+    model = LlamaForCausalLM(cfg).eval()
+    eos = vocab.index("<eos>")
+    proc = GrammarLogitsProcessor(JsonGrammar(), vocab, eos)
+    g = JsonGrammar()
+    for seed in range(4):
+        out = generate(model, torch.tensor([[0, 4, 6]]), GenerationConfig(max_new_tokens=24, do_sample=True, seed=seed,
+                                                                          temperature=1.5, eos_token_id=eos),
+                       logits_processor=proc)
+        text = "".join(vocab[t] for t in out[0, 3:].tolist() if t != eos)
+        assert g.accepts_prefix(text), text
+        if eos in out[0, 3:].tolist():
+            json.loads(text)
