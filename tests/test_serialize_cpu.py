@@ -172,3 +172,33 @@ def test_llama_hf_state_dict_roundtrip_through_safetensors(tmp_path):
     del bad["model.layers.0.self_attn.v_proj.weight"]
     with pytest.raises(KeyError):
         m2.load_hf_state_dict(bad)
+
+
+def test_int4_checkpoint_layouts_round_trip():
+    import torch
+
+    from ferrotorch_b200.serialize import quant_loaders as Q
+
+    torch.manual_seed(0)
+    w = torch.randn(64, 256) * 0.1
+    for pack, deq in ((Q.pack_gptq, Q.dequantize_gptq), (Q.pack_awq, Q.dequantize_awq)):
+        qw, qz, sc = pack(w, 128)
+        assert qw.dtype == torch.int32 and qz.dtype == torch.int32 and sc.dtype == torch.float16
+        d = deq(qw, qz, sc, group_size=128)
+        assert d.shape == w.shape and float((d - w).abs().max()) <= float(sc.float().max()) * 0.51 + 1e-3
+    # GPTQ with an explicit (permuted) group index
+    qw, qz, sc = Q.pack_gptq(w, 128)
+    g_idx = torch.arange(256) // 128
+    assert torch.equal(Q.dequantize_gptq(qw, qz, sc, g_idx), Q.dequantize_gptq(qw, qz, sc, group_size=128))
+    wq, s, z = Q.pack_hqq(w, 64)
+    assert wq.dtype == torch.uint8 and wq.numel() == w.numel() // 2
+    d = Q.dequantize_hqq(wq, s, z, (64, 256), 64)
+    assert float((d - w).abs().max()) <= float(s.max()) * 0.51
+    # the AWQ interleave: nibble j of a word holds column [0, 2, 4, 6, 1, 3, 5, 7][j]
+    word = int(Q._pack_int32(torch.arange(8, dtype=torch.int32).reshape(1, 8), 1, Q._AWQ_ORDER)[0, 0])
+    assert [(word >> (4 * j)) & 0xF for j in range(8)] == [0, 2, 4, 6, 1, 3, 5, 7]
+    # on to the fused dequant-GEMM's layout
+    lin = Q.to_q4_linear(d)
+    x = torch.randn(3, 256)
+    ref = x @ d.t()
+    assert float((lin(x) - ref).norm() / ref.norm()) < 0.15      # a second 4-bit rounding
