@@ -10,3 +10,4 @@ from .layers import (FusedLinearActivation, GQAAttention, KVCache, Linear, RMSNo
                      scaled_dot_product_attention)
 
 from ..ops.batchnorm import BatchNormAct2d, batch_norm_act  # noqa: F401,E402
+from .fake_quant import FakeQuantize, MinMaxObserver, MovingAverageObserver, QatLinear, prepare_qat  # noqa: F401,E402

@@ -172,3 +172,54 @@ def test_data_utilities():
     assert sorted(s0 + s1) == list(range(10))
     batches = list(D.DevicePrefetcher(D.DataLoader(ds, batch_size=4), "cpu"))
     assert len(batches) == 3 and batches[0][0].shape == (4, 16)
+
+
+def test_observers_fake_quant_and_qat():
+    import torch
+    from torch import nn
+
+    from ferrotorch_b200.nn import fake_quant as qat
+
+    obs = qat.MinMaxObserver(8, symmetric=False)
+    obs(torch.tensor([-1.0, 0.5, 3.0]))
+    obs(torch.tensor([-2.0, 1.0]))
+    scale, zero, qmin, qmax = obs.qparams()
+    assert (qmin, qmax) == (0, 255) and float(scale) == pytest.approx(5.0 / 255) and float(zero) == round(2.0 / (5.0 / 255))
+    pc = qat.MinMaxObserver(8, True, ch_axis=0)
+    pc(torch.tensor([[1.0, -4.0], [0.5, 0.25]]))
+    assert pc.qparams()[0].tolist() == pytest.approx([4.0 / 127, 0.5 / 127])
+    ma = qat.MovingAverageObserver(momentum=0.5)
+    ma(torch.tensor([0.0, 2.0]))
+    ma(torch.tensor([0.0, 4.0]))
+    assert float(ma.max_val) == pytest.approx(3.0)
+
+    # straight-through gradient: 1 inside the range, 0 where the value was clipped
+    fq = qat.FakeQuantize(4, True)
+    fq.observer(torch.tensor([-1.0, 1.0]))
+    fq.observe = False
+    x = torch.tensor([0.3, 5.0, -0.7], requires_grad=True)
+    y = fq(x)
+    y.sum().backward()
+    assert x.grad.tolist() == [1.0, 0.0, 1.0]
+    assert float((y[0] - 0.3).abs()) <= float(fq.observer.qparams()[0]) / 2 + 1e-6
+
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+    ref = [p.detach().clone() for p in net.parameters()]
+    qat.prepare_qat(net)
+    assert isinstance(net[0], qat.QatLinear) and isinstance(net[2], qat.QatLinear)
+    assert all(torch.equal(a, b) for a, b in zip(ref, [net[0].weight, net[0].bias, net[2].weight, net[2].bias]))
+    opt = torch.optim.SGD(net.parameters(), 0.05)
+    xs, ys = torch.randn(64, 16), torch.randint(0, 4, (64,))
+    first = None
+    for _ in range(40):
+        loss = nn.functional.cross_entropy(net(xs), ys)
+        first = first if first is not None else float(loss)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert float(loss) < first
+    ints = qat.convert(net)
+    q, sc, b = ints["0"]
+    assert q.dtype == torch.int8 and q.shape == (32, 16)
+    assert float((q.float() * sc[:, None] - net[0].weight).abs().max()) <= float(sc.max()) / 2 + 1e-6
