@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Per-kernel micro-benchmarks with roofline fractions against MEASURED_PEAKS.json.
 
-    python benchmarks/bench_kernels.py [--small] [--only gemm,attn,norm,optim,decode]
+    python benchmarks/bench_kernels.py [--small] [--only gemm,attn,norm,optim,decode,quant,jit,bn,tp]
 
 Timing: CUDA events, 3+ warm-up runs, a 256 MiB buffer is rewritten between timed runs to flush
 the 126 MB L2, median of the timed runs.  ``--small`` keeps every case to a few launches and
@@ -141,11 +141,77 @@ def run_decode(small):
     emit("paged_decode B%d ctx%d" % (B, ctx), bench(lambda: cache.decode(0, q, lens)), nbytes=4.0 * B * ctx * Hkv * D)
 
 
+def run_quant(small):
+    from ferrotorch_b200.ops import quant as Q
+
+    M, N, K = (256, 4096, 4096) if small else (64, 28672, 8192)
+    x, w = r(M, K), r(N, K) * 0.05
+    nib, sc = Q.requantize_q4_0(w.float().cpu())
+    nib, sc = nib.cuda(), sc.cuda()
+    # weight-bound at small M: bytes = the 4-bit weight + its scales
+    emit("q4_0_gemm %dx%dx%d" % (M, N, K), bench(lambda: Q.q4_0_linear(x, nib, sc)), 2.0 * M * N * K,
+         nbytes=N * K * 0.5 + N * (K // 32) * 2 + 2.0 * M * (N + K))
+    vals, meta = Q.pack_2_4(Q.apply_2_4_mask(w.float().cpu()).to(torch.bfloat16))
+    vals, meta = vals.cuda(), meta.cuda()
+    emit("sparse24_gemm %dx%dx%d" % (M, N, K), bench(lambda: Q.sparse24_linear(x, vals, meta)), 2.0 * M * N * K,
+         nbytes=N * K * 1.0 + N * K / 8 + 2.0 * M * (N + K))
+    emit("gemm_nt (dense bf16 weight) %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(x, w)), 2.0 * M * N * K,
+         nbytes=2.0 * N * K + 2.0 * M * (N + K))
+
+
+def run_jit(small):
+    from ferrotorch_b200 import jit
+
+    n = (1 << 24) if small else (1 << 27)
+    a, b = r(n), r(n)
+
+    def chain(x, y):
+        return torch.nn.functional.silu(x * 1.5 + y) * y - torch.tanh(x)
+
+    fn = jit.compile(chain, (a, b))
+    fn(a, b)
+    emit("jit fused elementwise (5 ops) n=%d" % n, bench(lambda: fn(a, b)), nbytes=6.0 * n)
+    emit("eager torch, same chain n=%d" % n, bench(lambda: chain(a, b)), nbytes=6.0 * n)
+
+
+def run_bn(small):
+    from torch import nn
+
+    from ferrotorch_b200.ops.batchnorm import batch_norm_act
+
+    N, C, H = (64, 256, 56) if small else (256, 256, 56)
+    x = r(N, C, H, H).contiguous(memory_format=torch.channels_last)
+    res, dy = torch.randn_like(x), torch.randn_like(x)
+    bn = nn.BatchNorm2d(C).cuda().to(torch.bfloat16)
+    tot = 2.0 * x.numel()
+    emit("bn+relu fwd %dx%dx%dx%d" % (N, C, H, H), bench(lambda: batch_norm_act(x, bn, None, True)), nbytes=3 * tot)
+    emit("bn+add+relu fwd", bench(lambda: batch_norm_act(x, bn, res, True)), nbytes=4 * tot)
+    xs = x.clone().requires_grad_()
+    y = batch_norm_act(xs, bn, None, True)
+    emit("bn+relu bwd", bench(lambda: torch.autograd.grad(y, xs, dy, retain_graph=True)), nbytes=5 * tot)
+    emit("torch bn+relu fwd (library)", bench(lambda: torch.relu(bn(x))), nbytes=3 * tot)
+
+
+def run_tp(small):
+    """The fused tensor-parallel kernels at world size 1 (collective parts idle): their GEMM core."""
+    from ferrotorch_b200.parallel.tensor_parallel import TPContext
+
+    tp = TPContext(None, torch.device("cuda", 0))
+    M, N, K = (4096, 4096, 4096) if small else (16384, 6144, 4096)
+    x, w, wk = r(M, K), r(N, K), r(K, N)
+    tp.my_rows(0, M, K).copy_(x)
+    fl = 2.0 * M * N * K
+    emit("tp ag_gemm (W=1) %dx%dx%d" % (M, N, K), bench(lambda: tp.ag_gemm(0, M, w)), fl)
+    emit("tp ag_gemm [K,N] weight (W=1)", bench(lambda: tp.ag_gemm(0, M, wk, w_is_kn=True)), fl)
+    emit("tp gemm_rs (W=1) %dx%dx%d" % (M, N, K), bench(lambda: tp.gemm_rs(1, x, w)), fl)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default="gemm,attn,norm,optim,decode")
     a = ap.parse_args()
     for name in a.only.split(","):
-        {"gemm": run_gemm, "attn": run_attn, "norm": run_norm, "optim": run_optim, "decode": run_decode}[name](a.small)
+        {"gemm": run_gemm, "attn": run_attn, "norm": run_norm, "optim": run_optim, "decode": run_decode,
+         "quant": run_quant, "jit": run_jit, "bn": run_bn, "tp": run_tp}[name](a.small)
     print(json.dumps({"device_status": _native.device_status(0)}))
