@@ -298,3 +298,13 @@ def test_grad_norm_and_clip_coef():
     nrm = float(g.float().norm())
     assert abs(float(out[0]) - nrm) / nrm < 1e-4
     assert abs(float(out[1]) - min(1.0, 1.0 / (nrm + 1e-6))) < 1e-6
+
+
+@pytest.mark.gpu
+def test_parity_sweep_on_gpu():
+    """Every op of the sweep harness: native bf16 kernel against the fp32 oracle."""
+    from ferrotorch_b200.utils import parity
+
+    rows = parity.sweep(None, "cuda")
+    bad = [r for r in rows if not r["ok"]]
+    assert not bad, bad

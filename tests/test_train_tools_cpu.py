@@ -223,3 +223,11 @@ def test_observers_fake_quant_and_qat():
     q, sc, b = ints["0"]
     assert q.dtype == torch.int8 and q.shape == (32, 16)
     assert float((q.float() * sc[:, None] - net[0].weight).abs().max()) <= float(sc.max()) / 2 + 1e-6
+
+
+def test_parity_sweep_harness_cpu():
+    from ferrotorch_b200.utils import parity
+
+    rows = parity.sweep(["rmsnorm", "swiglu", "attention"], "cpu")
+    assert [r["op"] for r in rows] == ["rmsnorm", "swiglu", "attention"]
+    assert all(r["ok"] and r["shapes"] >= 2 for r in rows)
