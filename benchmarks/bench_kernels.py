@@ -33,7 +33,11 @@ def peaks():
         return 6650.0, 1590.0, "fallback"
 
 
-def bench(fn, iters=10, warm=3):
+ITERS, WARM = 10, 3
+
+
+def bench(fn, iters=None, warm=None):
+    iters, warm = iters or ITERS, warm or WARM
     flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
     for _ in range(warm):
         fn()
@@ -210,7 +214,10 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default="gemm,attn,norm,optim,decode")
+    ap.add_argument("--iters", type=int, default=10, help="timed runs per case (1-2 under ncu)")
+    ap.add_argument("--warm", type=int, default=3)
     a = ap.parse_args()
+    ITERS, WARM = a.iters, a.warm
     for name in a.only.split(","):
         {"gemm": run_gemm, "attn": run_attn, "norm": run_norm, "optim": run_optim, "decode": run_decode,
          "quant": run_quant, "jit": run_jit, "bn": run_bn, "tp": run_tp}[name](a.small)
