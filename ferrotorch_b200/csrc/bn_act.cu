@@ -35,55 +35,53 @@ __device__ __forceinline__ void bn_load8f(const float* p, float* f) {
   f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
-// Column sums of up to two per-element quantities over the rows of a [R, C] tensor.
-//   MODE 0 (forward):  q0 = x,   q1 = x * x
-//   MODE 1 (backward): q0 = dz,  q1 = dz * xhat     with dz = dy * mask
+// Column sums of two per-element quantities over the rows of a [R, C] tensor.
+//   MODE 0 (forward):  q0 = x,   q1 = x * x          (4 rows per thread in flight)
+//   MODE 1 (backward): q0 = dz,  q1 = dz * x         with dz = dy * mask (2 rows in flight);
+//                      the finalize kernel turns them into dbeta and dgamma = invstd * (q1 - mean * q0)
 // Thread layout: tc = C / 8 threads across the channels, BN_THREADS / tc rows per pass.
 // partial: [gridDim.x, 2, C] floats.
 template <int MODE>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_colsum_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
-                 const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
-                 const float* __restrict__ invstd, const float* __restrict__ scale,
+                 const __nv_bfloat16* __restrict__ y, const float* __restrict__ scale,
                  const float* __restrict__ shift, int relu, long long R, int C, float* __restrict__ partial) {
+  constexpr int U = MODE == 0 ? 4 : 2;
   __shared__ float red[2][BN_THREADS][9];   // padded: 8 values per thread
   const int tc = C >> 3;
   const int rows_per_pass = BN_THREADS / tc;
   const int rg = threadIdx.x / tc, cv = threadIdx.x - rg * tc;
   const bool active = rg < rows_per_pass;
+  const bool recompute_mask = MODE == 1 && relu && !y;
   float s0[8], s1[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) s0[j] = s1[j] = 0.f;
-  float mu[8], is[8], sc[8], sh[8];
-  if (MODE == 1 && active) {
-    bn_load8f(mean + cv * 8, mu);
-    bn_load8f(invstd + cv * 8, is);
-    if (relu && !y) {
-      bn_load8f(scale + cv * 8, sc);
-      bn_load8f(shift + cv * 8, sh);
-    }
+  float sc[8], sh[8];
+  if (recompute_mask && active) {
+    bn_load8f(scale + cv * 8, sc);
+    bn_load8f(shift + cv * 8, sh);
   }
   if (active) {
     const long long stride = static_cast<long long>(gridDim.x) * rows_per_pass;
-    for (long long r0 = static_cast<long long>(blockIdx.x) * rows_per_pass + rg; r0 < R; r0 += 2 * stride) {
-      const long long r1 = r0 + stride < R ? r0 + stride : r0;
-      const long long o0 = r0 * C + cv * 8, o1 = r1 * C + cv * 8;
-      const uint4 xa = __ldcs(reinterpret_cast<const uint4*>(x + o0));
-      const uint4 xb = __ldcs(reinterpret_cast<const uint4*>(x + o1));
-      uint4 da, db, ya, yb;
-      if (MODE == 1) {
-        da = __ldcs(reinterpret_cast<const uint4*>(dy + o0));
-        db = __ldcs(reinterpret_cast<const uint4*>(dy + o1));
-        if (relu && y) {
-          ya = __ldcs(reinterpret_cast<const uint4*>(y + o0));
-          yb = __ldcs(reinterpret_cast<const uint4*>(y + o1));
+    for (long long r0 = static_cast<long long>(blockIdx.x) * rows_per_pass + rg; r0 < R; r0 += U * stride) {
+      uint4 xq[U], dq[U], yq[U];
+      bool ok[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long r = r0 + u * stride;
+        ok[u] = r < R;
+        const long long o = (ok[u] ? r : r0) * C + cv * 8;
+        xq[u] = __ldcs(reinterpret_cast<const uint4*>(x + o));
+        if (MODE == 1) {
+          dq[u] = __ldcs(reinterpret_cast<const uint4*>(dy + o));
+          if (relu && y) yq[u] = __ldcs(reinterpret_cast<const uint4*>(y + o));
         }
       }
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        if (k == 1 && r1 == r0) break;
+      for (int u = 0; u < U; ++u) {
+        if (!ok[u]) continue;
         float xv[8];
-        bn_unpack8(k == 0 ? xa : xb, xv);
+        bn_unpack8(xq[u], xv);
         if (MODE == 0) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -92,15 +90,15 @@ bn_colsum_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
           }
         } else {
           float dv[8], yv[8];
-          bn_unpack8(k == 0 ? da : db, dv);
-          if (relu && y) bn_unpack8(k == 0 ? ya : yb, yv);
+          bn_unpack8(dq[u], dv);
+          if (relu && y) bn_unpack8(yq[u], yv);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             bool on = true;
             if (relu) on = y ? (yv[j] > 0.f) : (__fmaf_rn(xv[j], sc[j], sh[j]) > 0.f);
             const float dz = on ? dv[j] : 0.f;
             s0[j] += dz;
-            s1[j] = __fmaf_rn(dz, (xv[j] - mu[j]) * is[j], s1[j]);
+            s1[j] = __fmaf_rn(dz, xv[j], s1[j]);
           }
         }
       }
@@ -202,11 +200,20 @@ bn_fwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long 
 }
 
 // y = act(x * scale[c] + shift[c] (+ residual)), 8 channels per thread, two vectors in flight.
+// When BN_THREADS is a multiple of tc = C / 8 (every power-of-two C up to 2048) a thread always
+// meets the same 8 channels, so their scale / shift are loaded once instead of per vector.
 __global__ void __launch_bounds__(BN_THREADS)
 bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                 const float* __restrict__ scale, const float* __restrict__ shift, __nv_bfloat16* __restrict__ y,
                 int relu, long long total_vec, int tc) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool fixed = (BN_THREADS % tc) == 0;
+  float sc[8], sh[8];
+  if (fixed) {
+    const int cv = threadIdx.x % tc;
+    bn_load8f(scale + cv * 8, sc);
+    bn_load8f(shift + cv * 8, sh);
+  }
   for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total_vec; i0 += 2 * stride) {
     const long long i1 = i0 + stride < total_vec ? i0 + stride : i0;
     const uint4 xa = __ldcs(reinterpret_cast<const uint4*>(x) + i0), xb = __ldcs(reinterpret_cast<const uint4*>(x) + i1);
@@ -219,11 +226,13 @@ bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     for (int k = 0; k < 2; ++k) {
       if (k == 1 && i1 == i0) break;
       const long long i = k == 0 ? i0 : i1;
-      const int cv = static_cast<int>(i % tc);
-      float xv[8], sc[8], sh[8], o[8];
+      if (!fixed) {
+        const int cv = static_cast<int>(i % tc);
+        bn_load8f(scale + cv * 8, sc);
+        bn_load8f(shift + cv * 8, sh);
+      }
+      float xv[8], o[8];
       bn_unpack8(k == 0 ? xa : xb, xv);
-      bn_load8f(scale + cv * 8, sc);
-      bn_load8f(shift + cv * 8, sh);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = __fmaf_rn(xv[j], sc[j], sh[j]);
       if (residual) {
@@ -242,17 +251,20 @@ bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 }
 
 // Backward finalize: dgamma, dbeta and the per-channel coefficients of
-//   dx = c1 * (dz - c2 - xhat * c3),  c1 = gamma * invstd, c2 = dbeta / R, c3 = dgamma / R.
+//   dx = gamma * invstd * (dz - dbeta / R - xhat * dgamma / R) = A * dz + B * x + D
+// with A = gamma * invstd, B = -A * invstd * dgamma / R, D = -A * dbeta / R - B * mean.
 // grad_kind 0: dgamma / dbeta are stored as fp32; 1: added to bf16 accumulators; 2: added to
 // fp32 accumulators (the gradient arena of the flat-parameter trainer).
 __global__ void __launch_bounds__(32 * BN_FIN_GROUPS)
 bn_bwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long R, int C,
+                       const float* __restrict__ mean, const float* __restrict__ invstd,
                        const float* __restrict__ scale, void* dgamma, void* dbeta, int grad_kind,
                        float* __restrict__ coef) {
   const int c = blockIdx.x * 32 + threadIdx.x;
-  double db, dg;
-  bn_reduce_partials(partial, blocks, C, c, db, dg);
+  double db, q1;
+  bn_reduce_partials(partial, blocks, C, c, db, q1);
   if (threadIdx.y != 0 || c >= C) return;
+  const double dg = static_cast<double>(invstd[c]) * (q1 - static_cast<double>(mean[c]) * db);
   if (grad_kind == 1) {
     __nv_bfloat16* g = static_cast<__nv_bfloat16*>(dgamma);
     __nv_bfloat16* b = static_cast<__nv_bfloat16*>(dbeta);
@@ -265,20 +277,35 @@ bn_bwd_finalize_kernel(const float* __restrict__ partial, int blocks, long long 
     if (dgamma) static_cast<float*>(dgamma)[c] = static_cast<float>(dg);
     if (dbeta) static_cast<float*>(dbeta)[c] = static_cast<float>(db);
   }
-  coef[c] = scale[c];
-  coef[C + c] = static_cast<float>(db / static_cast<double>(R));
-  coef[2 * C + c] = static_cast<float>(dg / static_cast<double>(R));
+  const double A = scale[c];
+  const double B = -A * static_cast<double>(invstd[c]) * dg / static_cast<double>(R);
+  coef[c] = static_cast<float>(A);
+  coef[C + c] = static_cast<float>(B);
+  coef[2 * C + c] = static_cast<float>(-A * db / static_cast<double>(R) - B * static_cast<double>(mean[c]));
 }
 
-// dx = c1 * (dz - c2 - xhat * c3); with a residual branch dres = dz.
+// dx = A * dz + B * x + D; with a residual branch dres = dz.  Per-channel values are loaded once
+// per thread when BN_THREADS is a multiple of tc (see bn_apply_kernel).
 __global__ void __launch_bounds__(BN_THREADS)
 bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
-                    const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
-                    const float* __restrict__ invstd, const float* __restrict__ scale,
+                    const __nv_bfloat16* __restrict__ y, const float* __restrict__ scale,
                     const float* __restrict__ shift, const float* __restrict__ coef, int relu,
                     __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dres, long long total_vec,
                     int tc, int C) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool fixed = (BN_THREADS % tc) == 0;
+  const bool recompute_mask = relu && !y;
+  float cA[8], cB[8], cD[8], sc[8], sh[8];
+  auto load_coefs = [&](int cv) {
+    bn_load8f(coef + cv * 8, cA);
+    bn_load8f(coef + C + cv * 8, cB);
+    bn_load8f(coef + 2 * C + cv * 8, cD);
+    if (recompute_mask) {
+      bn_load8f(scale + cv * 8, sc);
+      bn_load8f(shift + cv * 8, sh);
+    }
+  };
+  if (fixed) load_coefs(threadIdx.x % tc);
   for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total_vec; i0 += 2 * stride) {
     const long long i1 = i0 + stride < total_vec ? i0 + stride : i0;
     const uint4 xa = __ldcs(reinterpret_cast<const uint4*>(x) + i0), xb = __ldcs(reinterpret_cast<const uint4*>(x) + i1);
@@ -292,29 +319,17 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     for (int k = 0; k < 2; ++k) {
       if (k == 1 && i1 == i0) break;
       const long long i = k == 0 ? i0 : i1;
-      const int cv = static_cast<int>(i % tc);
-      float xv[8], dv[8], yv[8], mu[8], is[8], c1[8], c2[8], c3[8], sc[8], sh[8], o[8], dz[8];
+      if (!fixed) load_coefs(static_cast<int>(i % tc));
+      float xv[8], dv[8], yv[8], o[8], dz[8];
       bn_unpack8(k == 0 ? xa : xb, xv);
       bn_unpack8(k == 0 ? da : db, dv);
-      bn_load8f(mean + cv * 8, mu);
-      bn_load8f(invstd + cv * 8, is);
-      bn_load8f(coef + cv * 8, c1);
-      bn_load8f(coef + C + cv * 8, c2);
-      bn_load8f(coef + 2 * C + cv * 8, c3);
-      if (relu) {
-        if (y) {
-          bn_unpack8(k == 0 ? ya : yb, yv);
-        } else {
-          bn_load8f(scale + cv * 8, sc);
-          bn_load8f(shift + cv * 8, sh);
-        }
-      }
+      if (relu && y) bn_unpack8(k == 0 ? ya : yb, yv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         bool on = true;
         if (relu) on = y ? (yv[j] > 0.f) : (__fmaf_rn(xv[j], sc[j], sh[j]) > 0.f);
         dz[j] = on ? dv[j] : 0.f;
-        o[j] = c1[j] * (dz[j] - c2[j] - (xv[j] - mu[j]) * is[j] * c3[j]);
+        o[j] = __fmaf_rn(cA[j], dz[j], __fmaf_rn(cB[j], xv[j], cD[j]));
       }
       reinterpret_cast<uint4*>(dx)[i] = bn_pack8(o);
       if (dres) reinterpret_cast<uint4*>(dres)[i] = bn_pack8(dz);
@@ -325,7 +340,7 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 static int bn_blocks(long long R, int C, int device) {
   const int rows_per_pass = BN_THREADS / (C >> 3);
   long long b = (R + 2LL * rows_per_pass - 1) / (2LL * rows_per_pass);
-  long long cap = static_cast<long long>(sm_count(device)) * 2;
+  long long cap = static_cast<long long>(sm_count(device)) * 4;
   if (cap > BN_MAX_BLOCKS) cap = BN_MAX_BLOCKS;
   if (b > cap) b = cap;
   return b < 1 ? 1 : static_cast<int>(b);
@@ -356,7 +371,7 @@ FT_API int ft_bn_act_fwd(const void* x, const void* residual, void* y, const voi
   FT_REQUIRE(R > 0 && C >= 8 && C % 8 == 0 && C <= BN_MAX_C, "ft_bn_act_fwd: C must be a multiple of 8 in [8, 2048]");
   const int blocks = bn_blocks(R, C, device);
   bn_colsum_kernel<0><<<blocks, BN_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), nullptr, nullptr,
-                                                         nullptr, nullptr, nullptr, nullptr, 0, R, C, scratch);
+                                                         nullptr, nullptr, 0, R, C, scratch);
   FT_CUDA_CHECK(cudaGetLastError());
   bn_fwd_finalize_kernel<<<(C + 31) / 32, dim3(32, BN_FIN_GROUPS), 0, stream>>>(scratch, blocks, R, C, gamma, beta, affine_f32,
                                                               running_mean, running_var, running_f32, momentum, eps,
@@ -402,15 +417,15 @@ FT_API int ft_bn_act_bwd(const void* x, const void* dy, const void* y, const flo
   const int blocks = bn_blocks(R, C, device);
   bn_colsum_kernel<1><<<blocks, BN_THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
-      static_cast<const __nv_bfloat16*>(y), mean, invstd, scale, shift, relu, R, C, scratch);
+      static_cast<const __nv_bfloat16*>(y), scale, shift, relu, R, C, scratch);
   FT_CUDA_CHECK(cudaGetLastError());
-  bn_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, BN_FIN_GROUPS), 0, stream>>>(scratch, blocks, R, C, scale, dgamma,
-                                                                                  dbeta, grad_kind, coef);
+  bn_bwd_finalize_kernel<<<(C + 31) / 32, dim3(32, BN_FIN_GROUPS), 0, stream>>>(scratch, blocks, R, C, mean, invstd,
+                                                                                  scale, dgamma, dbeta, grad_kind, coef);
   FT_CUDA_CHECK(cudaGetLastError());
   const long long total_vec = R * (C >> 3);
   bn_bwd_apply_kernel<<<bn_elem_blocks(total_vec, device), BN_THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
-      static_cast<const __nv_bfloat16*>(y), mean, invstd, scale, shift, coef, relu,
+      static_cast<const __nv_bfloat16*>(y), scale, shift, coef, relu,
       static_cast<__nv_bfloat16*>(dx), static_cast<__nv_bfloat16*>(dres), total_vec, C >> 3, C);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch(3);
