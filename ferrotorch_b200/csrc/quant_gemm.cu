@@ -13,9 +13,11 @@
 //               expands tiles in the producer, so memory-bound shapes gain the bandwidth while the
 //               math runs as dense MMAs.
 //
-// Structure = the dense GEMM (gemm_tcgen05.cu) with the B-side TMA load replaced by four
-// "expander" warps: thread r owns row r of the 128 x 64 B tile, reads its compressed bytes with
-// plain loads, expands to 64 bf16 in registers and writes one 128-byte row in the swizzled
+// Structure = the dense GEMM (gemm_tcgen05.cu) with the B-side TMA load replaced by eight
+// "expander" warps in two groups that alternate k-blocks: a thread owns row r of the 128 x 64 B
+// tile, reads its compressed bytes with plain loads (several of its k-blocks ahead, so that HBM
+// latency is paid once per tile, not per k-block), expands to 64 bf16 in registers and writes
+// one 128-byte row in the swizzled
 // K-major layout the MMA descriptor expects (fence.proxy.async, then arrive on the stage's
 // full barrier).  A comes by TMA.  All waits are bounded.
 #include "ft_host.h"
@@ -24,7 +26,7 @@
 namespace ft {
 
 constexpr int QG_BM = 128, QG_BN = 128, QG_BK = 64;
-constexpr int QG_THREADS = 384;
+constexpr int QG_THREADS = 512;   // TMA, MMA, TMEM, idle, 4 epilogue, 8 expander warps
 constexpr int QG_A_BYTES = QG_BM * QG_BK * 2, QG_B_BYTES = QG_BN * QG_BK * 2;
 constexpr int QG_STAGE = QG_A_BYTES + QG_B_BYTES;
 constexpr int QG_STAGES = 6;
@@ -46,6 +48,7 @@ __device__ __forceinline__ void store_row_unit(uint32_t row_base, int r, int u, 
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+template <int MODE>   // 0 = Q4_0, 1 = SP24 (a template so that each form only carries its own prefetch registers)
 __global__ void __launch_bounds__(QG_THREADS, 1)
 expand_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const QgParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -117,85 +120,107 @@ expand_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const QgPara
     }
   } else if (warp >= 8) {
     // ---------------------------------------------------------------- expander warps
-    const int r = (warp - 8) * 32 + lane;  // row of the B tile
-    int stage = 0; uint32_t phase = 0; bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    // Two groups of four warps; group g expands the k-blocks whose running number is g (mod 2),
+    // thread r of a group owns row r of the 128 x 64 B tile.  The chain wait -> expand -> store ->
+    // proxy fence -> arrive of one k-block therefore overlaps with the other group's k-block.
+    const int grp = (warp - 8) >> 2;
+    const int r = ((warp - 8) & 3) * 32 + lane;
+    // compressed bytes of one 64-wide k-block of this thread's row
+    struct Comp { uint4 q0, q1, q2, q3; uint32_t aux0, aux1; };
+    constexpr int PF = MODE == 0 ? 3 : 2;  // own k-blocks fetched ahead (every second k-block is this group's)
+    long long seq0 = 0;                    // running number of the tile's first k-block
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, seq0 += k_blocks) {
       int mb, nb; coords(tile, mb, nb);
       const int n = nb * QG_BN + r;
       const bool row_ok = n < p.N;
-      for (int kb = 0; kb < k_blocks; ++kb) {
+      auto fetch = [&](int kb, Comp& c) {
+        c.q0 = c.q1 = c.q2 = c.q3 = make_uint4(0, 0, 0, 0);
+        c.aux0 = c.aux1 = 0;
         const int k0 = kb * QG_BK;
-        // fetch the compressed bytes first, then wait for the slot
-        uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0, q2 = q0, q3 = q0;
-        uint32_t aux0 = 0, aux1 = 0;
-        const bool k_ok = k0 + QG_BK <= p.K;  // K is a multiple of 64 (checked by the host)
-        if (row_ok && k_ok) {
-          if (p.mode == 0) {
-            const uint8_t* nb_ptr = p.w0 + static_cast<long long>(n) * (p.K >> 1) + (k0 >> 1);
-            q0 = __ldg(reinterpret_cast<const uint4*>(nb_ptr));
-            q1 = __ldg(reinterpret_cast<const uint4*>(nb_ptr) + 1);
-            aux0 = __ldg(reinterpret_cast<const uint32_t*>(p.w1 + (static_cast<long long>(n) * (p.K >> 5) + (k0 >> 5)) * 2));
-          } else {
-            const uint8_t* v_ptr = p.w0 + (static_cast<long long>(n) * (p.K >> 1) + (k0 >> 1)) * 2;
-            q0 = __ldg(reinterpret_cast<const uint4*>(v_ptr));
-            q1 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 1);
-            q2 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 2);
-            q3 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 3);
-            const uint2 mt = __ldg(reinterpret_cast<const uint2*>(p.w1 + static_cast<long long>(n) * (p.K >> 3) + (k0 >> 3)));
-            aux0 = mt.x; aux1 = mt.y;
-          }
+        if (!row_ok || kb >= k_blocks || k0 + QG_BK > p.K) return;  // K is a multiple of 64 (checked by the host)
+        if (MODE == 0) {
+          const uint8_t* nb_ptr = p.w0 + static_cast<long long>(n) * (p.K >> 1) + (k0 >> 1);
+          c.q0 = __ldg(reinterpret_cast<const uint4*>(nb_ptr));
+          c.q1 = __ldg(reinterpret_cast<const uint4*>(nb_ptr) + 1);
+          c.aux0 = __ldg(reinterpret_cast<const uint32_t*>(p.w1 + (static_cast<long long>(n) * (p.K >> 5) + (k0 >> 5)) * 2));
+        } else {
+          const uint8_t* v_ptr = p.w0 + (static_cast<long long>(n) * (p.K >> 1) + (k0 >> 1)) * 2;
+          c.q0 = __ldg(reinterpret_cast<const uint4*>(v_ptr));
+          c.q1 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 1);
+          c.q2 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 2);
+          c.q3 = __ldg(reinterpret_cast<const uint4*>(v_ptr) + 3);
+          const uint2 mt = __ldg(reinterpret_cast<const uint2*>(p.w1 + static_cast<long long>(n) * (p.K >> 3) + (k0 >> 3)));
+          c.aux0 = mt.x; c.aux1 = mt.y;
         }
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
-        const uint32_t row_base = smem_base + stage * QG_STAGE + QG_A_BYTES + r * 128;
-        if (p.mode == 0) {
-          const uint32_t nib[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      };
+      const int kb_first = static_cast<int>((grp - seq0) & 1);   // first k-block of this tile that is ours
+      Comp buf[PF];
 #pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(blk ? (aux0 >> 16) : (aux0 & 0xFFFF))));
+      for (int i = 0; i < PF; ++i) fetch(kb_first + 2 * i, buf[i]);
+      for (int kb0 = kb_first; kb0 < k_blocks && ok; kb0 += 2 * PF) {
 #pragma unroll
-            for (int hi = 0; hi < 2; ++hi) {
+        for (int j = 0; j < PF; ++j) {
+          const int kb = kb0 + 2 * j;
+          if (kb >= k_blocks || !ok) break;
+          const uint4 q0 = buf[j].q0, q1 = buf[j].q1, q2 = buf[j].q2, q3 = buf[j].q3;
+          const uint32_t aux0 = buf[j].aux0, aux1 = buf[j].aux1;
+          fetch(kb + 2 * PF, buf[j]);
+          const long long seq = seq0 + kb;
+          const int stage = static_cast<int>(seq % QG_STAGES);
+          const uint32_t phase = static_cast<uint32_t>((seq / QG_STAGES) & 1);
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          const uint32_t row_base = smem_base + stage * QG_STAGE + QG_A_BYTES + r * 128;
+          if (MODE == 0) {
+            const uint32_t nib[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                // 8 elements: nibbles (low or high) of bytes [half*8, half*8+8) of this block
-                const uint32_t w0 = nib[blk * 4 + half * 2] >> (hi * 4), w1 = nib[blk * 4 + half * 2 + 1] >> (hi * 4);
-                float f[8];
+            for (int blk = 0; blk < 2; ++blk) {
+              const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(blk ? (aux0 >> 16) : (aux0 & 0xFFFF))));
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  f[j] = (static_cast<float>((w0 >> (8 * j)) & 0xF) - 8.f) * d;
-                  f[4 + j] = (static_cast<float>((w1 >> (8 * j)) & 0xF) - 8.f) * d;
+              for (int hi = 0; hi < 2; ++hi) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                  // 8 elements: nibbles (low or high) of bytes [half*8, half*8+8) of this block
+                  const uint32_t w0 = nib[blk * 4 + half * 2] >> (hi * 4), w1 = nib[blk * 4 + half * 2 + 1] >> (hi * 4);
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    // 0x4B000000 | q is the float 2^23 + q: the nibble becomes a float without an I2F
+                    f[e] = (__uint_as_float(((w0 >> (8 * e)) & 0xFu) | 0x4B000000u) - 8388616.f) * d;
+                    f[4 + e] = (__uint_as_float(((w1 >> (8 * e)) & 0xFu) | 0x4B000000u) - 8388616.f) * d;
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                  o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                  store_row_unit(row_base, r, blk * 4 + hi * 2 + half, o);
                 }
-                uint4 o;
-                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-                store_row_unit(row_base, r, blk * 4 + hi * 2 + half, o);
               }
             }
-          }
-        } else {
-          // 16 groups of 4 slots; group g: two bf16 values vals[2g], vals[2g+1] at slots (m & 3), (m >> 2)
-          const uint32_t vals[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
-                                     q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+          } else {
+            // 16 groups of 4 slots; group g: two bf16 values (one word) at slots (m & 3), (m >> 2)
+            const uint32_t vals[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                       q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {        // one 16-byte unit = 8 slots = 2 groups
-            uint32_t outw[4] = {0u, 0u, 0u, 0u};
+            for (int u = 0; u < 8; ++u) {        // one 16-byte unit = 8 slots = 2 groups
+              uint32_t outw[4];
 #pragma unroll
-            for (int gg = 0; gg < 2; ++gg) {
-              const int g = u * 2 + gg;
-              const uint32_t m4 = ((g < 8 ? aux0 : aux1) >> ((g & 7) * 4)) & 0xF;
-              const uint32_t pair = vals[g];
-              const uint32_t v_lo = pair & 0xFFFFu, v_hi = pair >> 16;
-              const int p0 = m4 & 3, p1 = m4 >> 2;
-              // slot s of the group lives in half-word (s & 1) of word gg*2 + (s >> 1)
-              outw[gg * 2 + (p0 >> 1)] |= v_lo << ((p0 & 1) * 16);
-              outw[gg * 2 + (p1 >> 1)] |= v_hi << ((p1 & 1) * 16);
+              for (int gg = 0; gg < 2; ++gg) {
+                const int g = u * 2 + gg;
+                const uint32_t m4 = ((g < 8 ? aux0 : aux1) >> ((g & 7) * 4)) & 0xF;
+                const uint32_t v_lo = vals[g] & 0xFFFFu, v_hi = vals[g] >> 16;
+                const uint32_t p0 = m4 & 3u, p1 = m4 >> 2;
+                // slot s of the group lives in half-word (s & 1) of word (s >> 1): build both words
+                // with selects instead of indexing a register array by a run-time value
+                outw[gg * 2] = (p0 == 0u ? v_lo : 0u) | (p0 == 1u ? v_lo << 16 : 0u) | (p1 == 1u ? v_hi << 16 : 0u);
+                outw[gg * 2 + 1] = (p0 == 2u ? v_lo : 0u) | (p1 == 2u ? v_hi : 0u) | (p1 == 3u ? v_hi << 16 : 0u);
+              }
+              store_row_unit(row_base, r, u, make_uint4(outw[0], outw[1], outw[2], outw[3]));
             }
-            store_row_unit(row_base, r, u, make_uint4(outw[0], outw[1], outw[2], outw[3]));
           }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full_bar(stage));
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(stage));
-        if (++stage == QG_STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp >= 4) {
@@ -256,13 +281,17 @@ static int launch_expand(const void* x, const QgParams& p0, long long ldx, int d
   if (rc) return rc;
   static bool attr_set[64] = {false};
   if (!attr_set[device]) {
-    FT_CUDA_CHECK(cudaFuncSetAttribute(expand_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QG_SMEM));
+    FT_CUDA_CHECK(cudaFuncSetAttribute(expand_gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QG_SMEM));
+    FT_CUDA_CHECK(cudaFuncSetAttribute(expand_gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, QG_SMEM));
     attr_set[device] = true;
   }
   p.status = device_status_word(device);
   const int tiles = ((p.M + QG_BM - 1) / QG_BM) * ((p.N + QG_BN - 1) / QG_BN);
   const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
-  expand_gemm_tcgen05_kernel<<<grid, QG_THREADS, QG_SMEM, stream>>>(tmA, p);
+  if (p.mode == 0)
+    expand_gemm_tcgen05_kernel<0><<<grid, QG_THREADS, QG_SMEM, stream>>>(tmA, p);
+  else
+    expand_gemm_tcgen05_kernel<1><<<grid, QG_THREADS, QG_SMEM, stream>>>(tmA, p);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
