@@ -231,3 +231,48 @@ def test_parity_sweep_harness_cpu():
     rows = parity.sweep(["rmsnorm", "swiglu", "attention"], "cpu")
     assert [r["op"] for r in rows] == ["rmsnorm", "swiglu", "attention"]
     assert all(r["ok"] and r["shapes"] >= 2 for r in rows)
+
+
+def test_resume_after_the_trainer_process_dies(tmp_path):
+    """Kill the training process between steps (os._exit, no clean-up); a new process resumes from
+    the last asynchronously written checkpoint and ends with the same weights as an unbroken run."""
+    import subprocess
+    import sys
+    import textwrap
+
+    script = tmp_path / "train.py"
+    script.write_text(textwrap.dedent('''
+        import os, sys
+        sys.path.insert(0, %r)
+        import torch
+        from ferrotorch_b200.serialize.state import AsyncCheckpointer, load_checkpoint
+
+        ckpt, die_at, total = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 1))
+        opt = torch.optim.AdamW(model.parameters(), lr=0.05)
+        step = 0
+        if os.path.exists(ckpt):
+            ck = load_checkpoint(ckpt)
+            model.load_state_dict(ck["model"])
+            opt.load_state_dict(ck["optimizer"])
+            step = ck["step"]
+        writer = AsyncCheckpointer()
+        g = torch.Generator().manual_seed(123)
+        data = [(torch.randn(32, 8, generator=g), torch.randn(32, 1, generator=g)) for _ in range(total)]
+        while step < total:
+            x, y = data[step]
+            loss = torch.nn.functional.mse_loss(model(x), y)
+            opt.zero_grad(); loss.backward(); opt.step()
+            step += 1
+            writer.save_async(ckpt, model.state_dict(), opt.state_dict(), step=step).wait()
+            if step == die_at:
+                os._exit(17)
+        torch.save([p.detach() for p in model.parameters()], ckpt + ".final")
+    ''') % os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    run = lambda ck, die: subprocess.run([sys.executable, str(script), str(ck), str(die), "8"], timeout=120).returncode  # noqa: E731
+    assert run(tmp_path / "a.ckpt", 5) == 17          # died after step 5
+    assert run(tmp_path / "a.ckpt", -1) == 0          # resumed at step 5, ran to 8
+    assert run(tmp_path / "b.ckpt", -1) == 0          # unbroken reference
+    wa, wb = torch.load(str(tmp_path / "a.ckpt") + ".final"), torch.load(str(tmp_path / "b.ckpt") + ".final")
+    assert all(torch.equal(x, y) for x, y in zip(wa, wb))
