@@ -76,6 +76,25 @@ class IrGraph:
                                       "dtype": str(n.dtype) if n.dtype is not None else None}
                                      for n in (self.nodes[i] for i in self.order)], "outputs": self.outputs})
 
+    @classmethod
+    def from_json(cls, text: str, constants: dict | None = None) -> "IrGraph":
+        """Rebuild the structure written by :meth:`to_json`.  Tensor constants and opaque call
+        targets were saved by name / shape only: pass them back in ``constants`` (node id ->
+        attrs to merge); nodes without an entry keep the placeholder dictionaries."""
+        d = json.loads(text)
+        g = cls()
+        for nd in d["nodes"]:
+            dt = getattr(torch, nd["dtype"].split(".")[-1]) if nd["dtype"] else None
+            n = Node(nd["id"], nd["op"], list(nd["inputs"]), dict(nd["attrs"]),
+                     tuple(nd["shape"]) if nd["shape"] is not None else None, dt)
+            if constants and n.id in constants:
+                n.attrs.update(constants[n.id])
+            g.nodes[n.id] = n
+            g.order.append(n.id)
+            g._next = max(g._next, n.id + 1)
+        g.outputs = list(d["outputs"])
+        return g
+
 
 # --------------------------------------------------------------------------- passes
 def constant_fold(g: IrGraph) -> int:

@@ -114,3 +114,27 @@ def test_fused_kernel_numerics_gpu(dtype):
     z = torch.randn(1001, device="cuda", dtype=dtype)  # odd length: scalar-width kernel
     got = J.apply_fused([("mul_c", 0.5), "tanh", ("add_c", 2.0), "sqrt"], z)
     assert torch.allclose(got.float(), torch.sqrt(torch.tanh(z.float() * 0.5) + 2.0), atol=tol, rtol=tol)
+
+
+def test_ir_json_round_trip():
+    import torch
+
+    from ferrotorch_b200.jit.ir import IrGraph, dead_code_eliminate, fuse_elementwise
+
+    g = IrGraph()
+    a, b = g.add("input", name="a"), g.add("input", name="b")
+    c = g.add("const", value=torch.ones(4))
+    s = g.add("add", [a.id, b.id])
+    m = g.add("mul", [s.id, c.id])
+    r = g.add("relu", [m.id])
+    g.add("neg", [a.id])                      # dead
+    g.outputs = [r.id]
+    text = g.to_json()
+    h = IrGraph.from_json(text, constants={c.id: {"value": torch.ones(4)}})
+    assert h.ops() == g.ops() and h.outputs == g.outputs
+    assert [h.nodes[i].inputs for i in h.order] == [g.nodes[i].inputs for i in g.order]
+    assert torch.equal(h.nodes[c.id].attrs["value"], torch.ones(4))
+    assert dead_code_eliminate(h) == dead_code_eliminate(g)
+    assert fuse_elementwise(h) == fuse_elementwise(g)
+    assert h.ops() == g.ops()
+    assert IrGraph.from_json(h.to_json()).ops() == h.ops()
