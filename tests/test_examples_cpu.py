@@ -1,0 +1,21 @@
+"""The scripts under examples/ run to completion on CPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("script,args", [
+    ("train_tiny_llama.py", ["--steps", "8", "--device", "cpu"]),
+    ("generate_text.py", []),
+    ("compile_and_checkpoint.py", ["--device", "cpu"]),
+    ("ddp_over_tcp.py", []),
+])
+def test_example_runs(script, args):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "examples", script), *args], env=env,
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
