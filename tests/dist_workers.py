@@ -56,7 +56,7 @@ def timeout_case(rank, world, port, q):
     from ferrotorch_b200.parallel.backend import Timeout
 
     try:
-        g = _group(rank, world, port, timeout=1.0)
+        g = _group(rank, world, port, timeout=30.0)      # generous rendezvous: a cold process start is slow
         if rank == 0:
             t0 = time.time()
             try:
