@@ -92,3 +92,5 @@ class DevicePrefetcher:
 
     def __len__(self):
         return len(self.loader)
+
+from .token_loader import TokenFileLoader, write_token_file  # noqa: F401,E402

@@ -276,3 +276,49 @@ def test_resume_after_the_trainer_process_dies(tmp_path):
     assert run(tmp_path / "b.ckpt", -1) == 0          # unbroken reference
     wa, wb = torch.load(str(tmp_path / "a.ckpt") + ".final"), torch.load(str(tmp_path / "b.ckpt") + ".final")
     assert all(torch.equal(x, y) for x, y in zip(wa, wb))
+
+
+def test_native_token_loader(tmp_path):
+    from ferrotorch_b200.data import TokenFileLoader, write_token_file
+
+    S, B = 16, 4
+    n_samples = 50
+    ids = torch.arange(n_samples * S + 1) % 60000
+    path = str(tmp_path / "tokens.bin")
+    assert write_token_file(path, ids) == 2
+
+    def epoch_samples(loader):
+        out = []
+        for x, y in loader:
+            assert x.shape == (B, S) and y.shape == (B, S) and x.dtype == torch.int64
+            assert torch.equal(x[:, 1:], y[:, :-1])                       # labels are the inputs shifted by one
+            assert torch.equal(x, (x[:, :1] + torch.arange(S)) % 60000)   # a window of the file
+            out += (x[:, 0] // S).tolist()
+        return out
+
+    a = TokenFileLoader(path, S, B, num_workers=1, prefetch=2, seed=7)
+    b = TokenFileLoader(path, S, B, num_workers=6, prefetch=5, seed=7)
+    assert a.num_samples == n_samples and len(a) == n_samples // B
+    e0a, e0b = epoch_samples(a), epoch_samples(b)
+    assert e0a == e0b                                   # thread count does not change the order
+    assert len(set(e0a)) == len(e0a) == (n_samples // B) * B and set(e0a) <= set(range(n_samples))
+    e1a, e1b = epoch_samples(a), epoch_samples(b)
+    assert e1a == e1b and e1a != e0a and a.epoch == 1   # a new permutation every epoch
+    assert epoch_samples(TokenFileLoader(path, S, B, seed=8)) != e0a
+    assert epoch_samples(TokenFileLoader(path, S, B, shuffle=False)) == list(range((n_samples // B) * B))
+
+    # rank sharding: disjoint, and together one permutation prefix
+    r0 = epoch_samples(TokenFileLoader(path, S, B, seed=7, rank=0, world_size=2))
+    r1 = epoch_samples(TokenFileLoader(path, S, B, seed=7, rank=1, world_size=2))
+    assert not set(r0) & set(r1) and len(r0) == len(r1) == (n_samples // (2 * B)) * B
+
+    # uint32 ids and errors
+    big = torch.tensor([70000, 1, 2, 3, 4, 5, 6, 7, 8], dtype=torch.int64)
+    p2 = str(tmp_path / "big.bin")
+    assert write_token_file(p2, big) == 4
+    x, y = TokenFileLoader(p2, 4, 2, dtype_bytes=4, shuffle=False).next_batch()
+    assert x.tolist() == [[70000, 1, 2, 3], [4, 5, 6, 7]] and y.tolist() == [[1, 2, 3, 4], [5, 6, 7, 8]]
+    with pytest.raises(ValueError):
+        TokenFileLoader(p2, 4, 64, dtype_bytes=4)
+    with pytest.raises(ValueError):
+        TokenFileLoader(str(tmp_path / "missing.bin"), 4, 2)
