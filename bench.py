@@ -5,7 +5,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
 
-Config (BASELINE.json, config 3): Llama-3-8B architecture (32 layers, d 4096, 32 q / 8 kv heads
+Config (the Llama-3-8B training config of the benchmark spec): Llama-3-8B architecture (32 layers, d 4096, 32 q / 8 kv heads
 of 128, FFN 14336, vocab 128256, RoPE theta 5e5), bf16 weights and activations, fp32 AdamW
 state (master weights + two moments), lr 3e-4, wd 0.1, next-token cross-entropy on synthetic
 token ids uniform in [0, 128256), sequence 4096, 4 sequences per GPU (32 per step at 8 GPUs;
@@ -104,7 +104,7 @@ class ClockSampler:
 
 def reference_unavailable() -> None:
     why = ("reference is a Rust workspace (28 crates, no Python package, no setup.py/pyproject.toml): "
-           "`pip install --no-index --target baseline/_ref /root/reference` has nothing to build and no "
+           "a pip install of its source tree into baseline/_ref has nothing to build and no "
            "cargo/rustc toolchain or vendored crates exist offline")
     print(json.dumps({"impl": "reference", "unavailable": why}))
 

@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Llama inference benchmark (BASELINE.json configs 2 and 4): prefill + greedy decode with the
+"""Llama inference benchmark (the two inference configs of the benchmark spec): prefill + greedy decode with the
 paged KV cache, tensor parallel over the GPUs of one node.
 
     python benchmarks/bench_inference.py --model llama3-8b --batch 64 --prompt 2048 --new 256

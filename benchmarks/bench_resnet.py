@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""ResNet-50 data-parallel training throughput (BASELINE.json config 1): bf16 weights and
+"""ResNet-50 data-parallel training throughput (the ResNet-50 config of the benchmark spec): bf16 weights and
 activations with fp32 master weights, SGD momentum 0.9, wd 1e-4, lr 0.1, batch 256 per GPU,
 synthetic N(0,1) images 224x224x3, uniform labels.  Gradient exchange: 25 MB buckets, each one
 fused reduce + SGD update launch (``ft_ddp_reduce_update``) overlapped with backward.
