@@ -3,6 +3,7 @@ parallelism, device meshes and distributed tensors."""
 from .backend import (BackendUnavailable, DistributedError, Group, InvalidRank, InvalidWorldSize, IoError,  # noqa: F401
                       NoConnection, SelfSend, SimulatedGroup, SizeMismatch, SubGroup, TcpGroup, Timeout, TorchGroup,
                       UnsupportedOp, init_group, run_simulated)
+from .elastic import FileStore, Heartbeat, RankFailure, TorchStore, survivors  # noqa: F401
 from .fsdp import FSDP, ShardingStrategy, SyncBatchNorm2d  # noqa: F401
 from .host_ddp import DDP  # noqa: F401
 from .mesh import DeviceMesh, DTensor, Partial, Replicate, Shard  # noqa: F401

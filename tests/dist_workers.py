@@ -224,3 +224,51 @@ def vocab_parallel_case(rank, world, port, q):
         import traceback
 
         q.put((rank, "ERR " + traceback.format_exc()[-1500:]))
+
+
+def elastic_case(rank, world, port, q, root):
+    """Three ranks train a row-sharded vector and checkpoint every step; rank 2 dies without a
+    word after step 3.  The others notice through the heartbeat before their next step, regroup
+    as a world of two, reload the last complete checkpoint resharded 3 -> 2 and finish."""
+    try:
+        import os
+
+        import torch
+
+        from ferrotorch_b200.parallel import dist_checkpoint as dc
+        from ferrotorch_b200.parallel.elastic import FileStore, Heartbeat, RankFailure, barrier, survivors
+
+        store = FileStore(os.path.join(root, "store"))
+        hb = Heartbeat(store, rank, world, interval=0.05, timeout=0.5)
+        hb.wait_for_all(30.0)
+        w = torch.zeros(12 // world) + 100.0 * rank            # this rank's rows
+        step, detected, my_rank, my_world = 0, None, rank, world
+        total_steps = 6
+        while step < total_steps:
+            try:
+                if my_world == world:
+                    hb.check()
+            except RankFailure as f:
+                detected = f.ranks
+                alive = survivors(world, f)
+                barrier(store, "regroup", rank, alive, limit=20.0)
+                my_rank, my_world = alive.index(rank), len(alive)
+                last = max(s for s in range(step + 1) if all(
+                    os.path.exists(os.path.join(root, "ckpt_%d" % s, "shard_%d.safetensors" % r)) for r in range(world)))
+                state, extra = dc.load_distributed(os.path.join(root, "ckpt_%d" % last), my_rank, my_world)
+                w, step = state["w"], extra["step"]
+                continue
+            w = w + 1.0
+            step += 1
+            if my_world == world:
+                dc.save_distributed(os.path.join(root, "ckpt_%d" % step), {"w": w}, {"w": 0}, rank=rank,
+                                    world_size=world, extra={"step": step})
+                if rank == 2 and step == 3:
+                    os._exit(0)                                 # no leave(), no clean-up
+                time.sleep(0.4)                                 # a step takes a while
+        hb.stop()
+        q.put((rank, (detected, my_rank, my_world, w.tolist())))
+    except BaseException:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "ERR " + traceback.format_exc()[-1500:]))

@@ -169,3 +169,40 @@ def test_config0_tiny_llama_ddp_bitwise(backend):
 def test_vocab_parallel_embedding_and_cross_entropy_gloo():
     out = _spawn(W.vocab_parallel_case, 2)
     assert all(v == "ok" for v in out.values()), out
+
+
+def test_heartbeat_detects_a_dead_rank_and_survivors_reshard(tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=W.elastic_case, args=(r, 3, 0, q, str(tmp_path))) for r in range(3)]
+    for p in procs:
+        p.start()
+    out = dict(q.get(timeout=120) for _ in range(2))           # rank 2 never reports
+    for p in procs:
+        p.join(30)
+    assert set(out) == {0, 1}, out
+    for r, v in out.items():
+        assert not isinstance(v, str), v
+        detected, new_rank, new_world, rows = v
+        assert detected == [2] and new_world == 2 and new_rank == r
+    # global vector after 3 steps at world 3 (rows of rank k start at 100 k) and 3 more at world 2
+    full = out[0][3] + out[1][3]
+    assert full == [6.0] * 4 + [106.0] * 4 + [206.0] * 4
+
+
+def test_heartbeat_clean_leave_and_store_barrier(tmp_path):
+    from ferrotorch_b200.parallel.elastic import FileStore, Heartbeat, RankFailure, barrier, survivors
+
+    store = FileStore(str(tmp_path))
+    a, b = Heartbeat(store, 0, 2, interval=0.02, timeout=0.3), Heartbeat(store, 1, 2, interval=0.02, timeout=0.3)
+    a.wait_for_all(5.0)
+    a.check()
+    b.check()
+    b.leave()
+    with pytest.raises(RankFailure) as e:
+        a.check()
+    assert e.value.left == [1] and e.value.ranks == [] and survivors(2, e.value) == [0]
+    a.stop()
+    barrier(store, "solo", 0, [0], limit=1.0)
+    with pytest.raises(RankFailure):
+        barrier(store, "pair", 0, [0, 1], limit=0.2)
