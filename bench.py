@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--micro-batches", type=int, default=2)
     ap.add_argument("--checkpoint", action="store_true", help="recompute each decoder layer in backward")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--measure-exposed", action="store_true",
+                    help="record how long the compute stream waits for the gradient exchange at the end of a step")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     return ap.parse_args()
 
@@ -242,6 +244,7 @@ def main() -> None:
         from ferrotorch_b200.parallel.ddp import FusedDDP
 
         ddp = FusedDDP(dist.group.WORLD, mode=args.comm)
+        ddp.measure_exposed = args.measure_exposed
     alloc = ddp.allocator if ddp is not None else None
     trainer = FlatTrainer(model, optimizer="adamw", lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
                           micro_batches=args.micro_batches, ddp=ddp, allocator=alloc)
@@ -325,6 +328,9 @@ def main() -> None:
         }
         if e2e is not None:
             out["e2e"] = e2e
+        if ddp is not None and args.measure_exposed:
+            ex = ddp.exposed_ms()[-args.steps:]
+            out["exposed_comm_ms_per_step"] = sum(ex) / max(1, len(ex))
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

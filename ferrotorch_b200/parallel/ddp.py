@@ -95,7 +95,10 @@ class FusedDDP:
         self._symm: list[SymmetricBuffer] = []
         self.late = {id(p) for p in late_params}
         self.last_micro_batch = True
-        self.exposed_ms: list[float] = []
+        # with measure_exposed the time the compute stream spends blocked on the exchange at the
+        # end of a step is recorded with CUDA events (read it with exposed_ms())
+        self.measure_exposed = False
+        self._exposed_events: list = []
         self.reduce_only = False
 
     # the trainer allocates its arenas through this (symmetric memory in fused mode)
@@ -219,7 +222,21 @@ class FusedDDP:
             _native.check(rc, "ft_comm_wait")
         ev = torch.cuda.Event()
         ev.record(self.stream)
-        torch.cuda.current_stream(self.device).wait_event(ev)
+        cur = torch.cuda.current_stream(self.device)
+        if self.measure_exposed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(cur)
+            cur.wait_event(ev)
+            e1.record(cur)
+            self._exposed_events.append((e0, e1))
+        else:
+            cur.wait_event(ev)
+
+    def exposed_ms(self) -> list[float]:
+        """Per finished step: milliseconds the compute stream waited for the gradient exchange
+        after backward had ended (synchronises; needs ``measure_exposed = True``)."""
+        torch.cuda.synchronize(self.device)
+        return [a.elapsed_time(b) for a, b in self._exposed_events]
 
     def broadcast_parameters(self, trainer, root: int = 0) -> None:
         """Make every replica start from rank ``root``'s weights and optimizer state."""
