@@ -106,3 +106,39 @@ def test_grammar_constrained_generate_yields_valid_json():
         assert g.accepts_prefix(text), text
         if eos in out[0, 3:].tolist():
             json.loads(text)
+
+
+def test_flat_trainer_trajectory_matches_torch_adamw_with_clipping():
+    """Five optimizer steps of the flat-arena trainer (micro-batches, global-norm clipping, decay only
+    on matrices) against the same loop written with torch.optim.AdamW + clip_grad_norm_."""
+    import copy
+
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.train.engine import FlatTrainer
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=8, max_position_embeddings=64)
+    ours = LlamaForCausalLM(cfg)
+    ref = copy.deepcopy(ours)
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    tr = FlatTrainer(ours, optimizer="adamw", weight_decay=0.1, max_grad_norm=0.5, micro_batches=2, **hp)
+    decay = [p for p in ref.parameters() if p.dim() >= 2]
+    no_decay = [p for p in ref.parameters() if p.dim() < 2]
+    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": no_decay, "weight_decay": 0.0}], **hp)
+    g = torch.Generator().manual_seed(1)
+    for step in range(5):
+        t = torch.randint(0, cfg.vocab_size, (4, 17), generator=g)
+        x, y = t[:, :-1], t[:, 1:]
+        loss = tr.step(x, y)
+        opt.zero_grad()
+        total = 0.0
+        for i in range(2):                                   # the same two micro-batches
+            l = ref(x[2 * i:2 * i + 2], labels=y[2 * i:2 * i + 2], loss_denominator=y.numel())
+            l.backward()
+            total += float(l)
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        opt.step()
+        assert abs(float(loss) - total) < 1e-5, (step, float(loss), total)
+    for (n, p), q in zip(ours.named_parameters(), ref.parameters()):
+        assert torch.allclose(p, q, atol=2e-5), (n, float((p - q).abs().max()))
