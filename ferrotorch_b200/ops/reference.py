@@ -46,6 +46,10 @@ def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, scaling: di
     if kind == "linear":
         pos = pos / float(scaling["factor"])
     elif kind == "yarn":
+        # The reference's schedule (transformer.rs:357-392): correction range found on the full
+        # dimension and halved onto the inv_freq index space, no attention temperature.  The
+        # Hugging Face variant differs in both points: ``"hf_range": True`` keeps the range
+        # un-halved, ``"mscale": True`` multiplies cos / sin by 0.1 ln(factor) + 1.
         f = float(scaling["factor"])
         orig = float(scaling.get("original_max", max_pos))
         bf, bs = float(scaling.get("beta_fast", 32.0)), float(scaling.get("beta_slow", 1.0))
@@ -53,12 +57,17 @@ def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, scaling: di
         def corr_dim(n_rot):
             return (head_dim * math.log(orig / (n_rot * 2 * math.pi))) / (2 * math.log(theta))
 
-        low = max(math.floor(corr_dim(bf)), 0)
-        high = min(math.ceil(corr_dim(bs)), half - 1)
-        ramp = ((idx - low) / max(high - low, 1e-3)).clamp(0, 1)
+        low = max(float(math.floor(corr_dim(bf))), 0.0)
+        high = min(float(math.ceil(corr_dim(bs))), float(head_dim - 1))
+        if scaling.get("hf_range", False):
+            high = min(high, float(half - 1))
+        else:
+            low, high = low / 2.0, high / 2.0
+        denom = 0.001 if high == low else high - low
+        ramp = ((idx - low) / denom).clamp(0, 1)
         mask = 1.0 - ramp  # 1 -> keep extrapolated (high freq), 0 -> interpolate
         inv_freq = inv_freq / f * (1 - mask) + inv_freq * mask
-        mscale = 0.1 * math.log(f) + 1.0 if f > 1 else 1.0
+        mscale = 0.1 * math.log(f) + 1.0 if (scaling.get("mscale", False) and f > 1) else 1.0
     elif kind == "llama3":
         f = float(scaling.get("factor", 8.0))
         lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
