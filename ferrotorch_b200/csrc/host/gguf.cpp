@@ -1,8 +1,16 @@
 // GGUF v2/v3 reader: mmap the file, parse header / metadata / tensor table, dequantise the
 // block formats the reference supports (Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, F16, BF16, F32 --
 // ferrotorch-serialize/src/gguf.rs:56-927; block = 32 elements, Q4_0 = fp16 scale + 16 nibble
-// bytes, gguf.rs:543-577) and re-lay Q4_0 weights out for the fused dequant-GEMM kernel
-// (separate scale and nibble planes, csrc/quant_gemm.cu).
+// bytes) and re-lay Q4_0 weights out for the fused dequant-GEMM kernel (separate scale and nibble
+// planes, csrc/quant_gemm.cu).
+//
+// Element order inside a block.  The GGML file format (what llama.cpp writes) puts element j in
+// the low nibble of byte j and element j + 16 in the high nibble, and bit j / bit j + 16 of the
+// Q5 high-bit word belong to the same two elements; that is the default here, so real model
+// files decode correctly.  The reference's decoders emit the two nibbles of byte j as the
+// consecutive elements 2j and 2j + 1 and take high bits 2j and 2j + 1 (gguf.rs:543-577, 614-660;
+// ferrotorch-cubecl/src/quant.rs:348).  `interleaved = 1` selects that order for callers that need
+// bit-for-bit agreement with tensors the reference decoded.
 #include <fcntl.h>
 #include <stdint.h>
 #include <string.h>
@@ -264,9 +272,59 @@ FTG_API int ftg_dequantize(unsigned type, const void* src_, float* dst, long lon
   return 0;
 }
 
+// The same with the element order chosen by the caller (see the head of this file).
+FTG_API int ftg_dequantize_ex(unsigned type, const void* src_, float* dst, long long n, int interleaved) {
+  if (!interleaved || !(type == 2 || type == 3 || type == 6 || type == 7)) return ftg_dequantize(type, src_, dst, n);
+  const uint8_t* src = static_cast<const uint8_t*>(src_);
+  uint32_t be = 0, bb = 0;
+  if (!type_layout(type, &be, &bb) || n % be) return -1;
+  const long long nb = n / 32;
+  for (long long b = 0; b < nb; ++b) {
+    const uint8_t* p = src + b * bb;
+    float* y = dst + b * 32;
+    const float d = half_to_float(rd16(p));
+    const float m = (type == 3 || type == 7) ? half_to_float(rd16(p + 2)) : 0.f;
+    const uint8_t* q = p + (type == 2 ? 2 : type == 3 ? 4 : type == 6 ? 6 : 8);
+    const uint32_t qh = type == 6 ? rd32(p + 2) : type == 7 ? rd32(p + 4) : 0u;
+    for (int j = 0; j < 16; ++j) {
+      int lo = q[j] & 0xF, hi = q[j] >> 4;
+      if (type >= 6) { lo |= ((qh >> (2 * j)) & 1) << 4; hi |= ((qh >> (2 * j + 1)) & 1) << 4; }
+      switch (type) {
+        case 2: y[2 * j] = (lo - 8) * d; y[2 * j + 1] = (hi - 8) * d; break;
+        case 3: case 7: y[2 * j] = lo * d + m; y[2 * j + 1] = hi * d + m; break;
+        case 6: y[2 * j] = (lo - 16) * d; y[2 * j + 1] = (hi - 16) * d; break;
+      }
+    }
+  }
+  return 0;
+}
+
+// Rewrite the nibble bytes of Q4_0 / Q4_1 blocks in place from the interleaved element order to the
+// file format's order (or back, `to_interleaved`), so data meant for one convention can be fed to
+// code of the other: the dequant-GEMM kernel always reads the file format's order.
+FTG_API int ftg_repack_nibbles(unsigned type, void* data_, long long n_blocks, int to_interleaved) {
+  if (type != 2 && type != 3) return -1;
+  uint8_t* data = static_cast<uint8_t*>(data_);
+  const int bb = type == 2 ? 18 : 20, off = type == 2 ? 2 : 4;
+  for (long long b = 0; b < n_blocks; ++b) {
+    uint8_t* q = data + b * bb + off;
+    uint8_t e[32], out[16];
+    if (!to_interleaved) {
+      for (int j = 0; j < 16; ++j) { e[2 * j] = q[j] & 0xF; e[2 * j + 1] = q[j] >> 4; }
+      for (int j = 0; j < 16; ++j) out[j] = static_cast<uint8_t>(e[j] | (e[j + 16] << 4));
+    } else {
+      for (int j = 0; j < 16; ++j) { e[j] = q[j] & 0xF; e[j + 16] = q[j] >> 4; }
+      for (int j = 0; j < 16; ++j) out[j] = static_cast<uint8_t>(e[2 * j] | (e[2 * j + 1] << 4));
+    }
+    memcpy(q, out, 16);
+  }
+  return 0;
+}
+
 // Q4_0 [rows, cols] (cols % 32 == 0) -> planes for the dequant-GEMM: scales fp16 [rows, cols/32]
 // and nibbles u8 [rows, cols/2] where byte j of a 32-element block holds elements (j, j+16),
-// exactly as in the file, so the kernel's unpack matches ftg_dequantize bit for bit.
+// exactly as in the file, so the kernel's unpack matches ftg_dequantize bit for bit.  (For the
+// interleaved convention, run ftg_repack_nibbles over the planes' source first.)
 FTG_API int ftg_split_q4_0(const void* src_, long long rows, long long cols, unsigned short* scales,
                            unsigned char* nibbles) {
   if (cols % 32) return -1;

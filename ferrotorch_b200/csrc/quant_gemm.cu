@@ -1,8 +1,11 @@
 // GEMMs whose weight operand is expanded on the fly inside the tcgen05 main loop (sm_100a):
 //
 //   mode Q4_0   Y[M,N] = X[M,K] * dequant(Wq)[N,K]^T, GGUF Q4_0 weights (32-element blocks, fp16
-//               scale + 16 nibble bytes; element j = low nibble of byte j, element j+16 = high
-//               nibble, value = (q - 8) * d -- ferrotorch-serialize/src/gguf.rs:543-577).  The
+//               scale + 16 nibble bytes, value = (q - 8) * d; element j = low nibble of byte j,
+//               element j+16 = high nibble, the GGML file format's order.  The reference's decoder
+//               emits the nibbles of byte j as elements 2j, 2j+1 instead, ferrotorch-serialize/src/
+//               gguf.rs:543-577; data in that convention is re-packed on the host,
+//               csrc/host/gguf.cpp ftg_repack_nibbles).  The
 //               reference dequantises the whole tensor to f32 on the GPU, bounces it through the
 //               host and stores bf16 (ferrotorch-llama/src/gpu_gguf.rs:14-27); it has no fused
 //               dequant-GEMM.  Here the weights stay 4-bit in HBM (0.5625 bytes / element).

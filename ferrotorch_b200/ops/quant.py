@@ -29,8 +29,17 @@ _native.register_protos({
 
 
 # --------------------------------------------------------------------------- Q4_0
-def q4_0_planes(blocks: torch.Tensor, rows: int, cols: int):
-    """Raw Q4_0 blocks (uint8 ``[rows*cols/32, 18]``) -> ``(nibbles u8 [rows, cols/2], scales fp16 [rows, cols/32])``."""
+def q4_0_planes(blocks: torch.Tensor, rows: int, cols: int, nibble_order: str = "ggml"):
+    """Raw Q4_0 blocks (uint8 ``[rows*cols/32, 18]``) -> ``(nibbles u8 [rows, cols/2], scales fp16 [rows, cols/32])``.
+    The kernel reads the file format's element order (byte j = elements j, j + 16); blocks whose
+    bytes mean elements (2j, 2j + 1) -- ``nibble_order="interleaved"``, the order the reference's
+    decoder emits -- are re-packed here first."""
+    if nibble_order == "interleaved":
+        q = blocks.reshape(-1, 18)[:, 2:]
+        e = torch.stack([q & 0xF, q >> 4], dim=2).reshape(-1, 32)
+        blocks = torch.cat([blocks.reshape(-1, 18)[:, :2], e[:, :16] | (e[:, 16:] << 4)], dim=1)
+    elif nibble_order != "ggml":
+        raise ValueError("nibble_order must be 'ggml' or 'interleaved'")
     b = blocks.reshape(rows, cols // 32, 18)
     scales = b[:, :, :2].contiguous().view(torch.float16).reshape(rows, cols // 32)
     nibbles = b[:, :, 2:].contiguous().reshape(rows, cols // 2)

@@ -185,12 +185,16 @@ def sgd_step(p, g, buf, *, lr, momentum=0.0, dampening=0.0, weight_decay=0.0, ne
     p.sub_(lr * g)
 
 
-def dequant_q4_0(blocks: torch.Tensor) -> torch.Tensor:
-    """GGUF Q4_0: blocks of 18 bytes = fp16 scale + 16 bytes of nibbles; element i of the low
-    nibbles is ``(q - 8) * d`` at position i, high nibbles at i + 16
-    (ferrotorch-serialize/src/gguf.rs:543-577).  ``blocks``: uint8 ``[n_blocks, 18]``."""
+def dequant_q4_0(blocks: torch.Tensor, nibble_order: str = "ggml") -> torch.Tensor:
+    """GGUF Q4_0: blocks of 18 bytes = fp16 scale + 16 bytes of nibbles, value ``(q - 8) * d``.
+    ``nibble_order="ggml"`` is the file format's element order (low nibble of byte j = element j,
+    high nibble = element j + 16); ``"interleaved"`` is the order the reference's decoder emits
+    (elements 2j and 2j + 1, ferrotorch-serialize/src/gguf.rs:543-577).
+    ``blocks``: uint8 ``[n_blocks, 18]``."""
     d = blocks[:, :2].contiguous().view(torch.float16).float()  # [n,1]
     qs = blocks[:, 2:]
     lo = (qs & 0x0F).to(torch.int16) - 8
     hi = (qs >> 4).to(torch.int16) - 8
+    if nibble_order == "interleaved":
+        return (torch.stack([lo, hi], dim=2).reshape(-1, 32).float() * d).reshape(-1)
     return (torch.cat([lo, hi], dim=1).float() * d).reshape(-1)

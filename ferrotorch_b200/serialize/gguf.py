@@ -4,6 +4,12 @@ GGUF -> HF key map for Llama, and a small writer / Q4_0 quantiser used by tests 
 Reference: ferrotorch-serialize/src/gguf.rs:56-927 (types, block layouts, ``load_gguf_state_dict``)
 and ferrotorch-llama/src/gguf_remap.rs:23-52 (``token_embd -> model.embed_tokens``, ``blk.{i}.attn_q
 -> model.layers.{i}.self_attn.q_proj`` ...).
+
+Element order of the 4- and 5-bit block formats: the default (``nibble_order="ggml"``) is the file
+format's, as llama.cpp writes it -- byte j of a block carries element j (low nibble) and element
+j + 16 (high nibble).  The reference's decoders emit the nibbles of byte j as elements 2j, 2j + 1
+(gguf.rs:543-577; ferrotorch-cubecl/src/quant.rs:348); ``nibble_order="interleaved"`` reproduces
+that for bit-for-bit agreement with tensors the reference decoded.
 """
 from __future__ import annotations
 
@@ -39,6 +45,8 @@ def _lib():
         lib.ftg_tensor_data.restype, lib.ftg_tensor_data.argtypes = vp, [vp, ll]
         lib.ftg_dequantize.argtypes = [ctypes.c_uint, vp, vp, ll]
         lib.ftg_split_q4_0.argtypes = [vp, ll, ll, vp, vp]
+        lib.ftg_dequantize_ex.argtypes = [ctypes.c_uint, vp, vp, ll, ctypes.c_int]
+        lib.ftg_repack_nibbles.argtypes = [ctypes.c_uint, vp, ll, ctypes.c_int]
         _ready = True
     return lib
 
@@ -84,26 +92,64 @@ class GgufFile:
         buf = (ctypes.c_ubyte * nbytes).from_address(ptr)
         return torch.frombuffer(bytearray(buf), dtype=torch.uint8)
 
-    def dequantize(self, name: str, dtype=torch.float32) -> torch.Tensor:
+    def dequantize(self, name: str, dtype=torch.float32, nibble_order: str = "ggml") -> torch.Tensor:
         t, shape, nbytes = self.tensors[name]
         n = int(np.prod(shape)) if shape else 1
         out = torch.empty(n, dtype=torch.float32)
-        rc = self._lib.ftg_dequantize(t, self._lib.ftg_tensor_data(self._h, self._index[name]), out.data_ptr(), n)
+        rc = self._lib.ftg_dequantize_ex(t, self._lib.ftg_tensor_data(self._h, self._index[name]), out.data_ptr(), n,
+                                         _order_flag(nibble_order))
         if rc != 0:
             raise ValueError("unsupported ggml type %d for %s" % (t, name))
         return out.view(shape).to(dtype)
 
-    def q4_0_planes(self, name: str):
-        """``(scales fp16 [rows, cols/32], nibbles uint8 [rows, cols/2])`` of a Q4_0 matrix."""
+    def q4_0_planes(self, name: str, nibble_order: str = "ggml"):
+        """``(scales fp16 [rows, cols/32], nibbles uint8 [rows, cols/2])`` of a Q4_0 matrix, in the
+        layout the dequant-GEMM kernel reads.  With ``nibble_order="interleaved"`` the file's bytes
+        are taken to mean elements (2j, 2j+1) and are re-packed on the host first."""
         t, shape, _ = self.tensors[name]
         assert t == GGML_Q4_0 and len(shape) == 2, "%s is not a Q4_0 matrix" % name
         rows, cols = shape
         scales = torch.empty((rows, cols // 32), dtype=torch.float16)
         nib = torch.empty((rows, cols // 2), dtype=torch.uint8)
-        rc = self._lib.ftg_split_q4_0(self._lib.ftg_tensor_data(self._h, self._index[name]), rows, cols,
-                                      scales.data_ptr(), nib.data_ptr())
+        if _order_flag(nibble_order):
+            blocks = self.raw(name)
+            repack_nibbles(blocks, GGML_Q4_0, to_interleaved=False)
+            src = blocks.data_ptr()
+        else:
+            src = self._lib.ftg_tensor_data(self._h, self._index[name])
+        rc = self._lib.ftg_split_q4_0(src, rows, cols, scales.data_ptr(), nib.data_ptr())
         assert rc == 0
         return scales, nib
+
+
+def _order_flag(nibble_order: str) -> int:
+    if nibble_order not in ("ggml", "interleaved"):
+        raise ValueError("nibble_order must be 'ggml' or 'interleaved', got %r" % (nibble_order,))
+    return int(nibble_order == "interleaved")
+
+
+def repack_nibbles(blocks: torch.Tensor, ggml_type: int = GGML_Q4_0, to_interleaved: bool = False) -> torch.Tensor:
+    """Re-pack, in place, the nibble bytes of raw Q4_0 / Q4_1 blocks (a contiguous uint8 tensor)
+    between the interleaved element order and the file format's order; returns ``blocks``."""
+    assert blocks.dtype == torch.uint8 and blocks.is_contiguous() and blocks.device.type == "cpu"
+    bb = _BLOCK[ggml_type][1]
+    assert ggml_type in (GGML_Q4_0, GGML_Q4_1) and blocks.numel() % bb == 0
+    rc = _lib().ftg_repack_nibbles(ggml_type, blocks.data_ptr(), blocks.numel() // bb, int(to_interleaved))
+    assert rc == 0
+    return blocks
+
+
+def dequantize_blocks(raw: torch.Tensor, ggml_type: int, n: int, nibble_order: str = "ggml") -> torch.Tensor:
+    """Dequantise ``n`` elements from raw block bytes (uint8, CPU) to float32."""
+    raw = raw.contiguous()
+    be, bb = _BLOCK[ggml_type]
+    if n % be or raw.numel() < n // be * bb:
+        raise ValueError("%d elements of ggml type %d need %d bytes, got %d" % (n, ggml_type, n // be * bb, raw.numel()))
+    out = torch.empty(n, dtype=torch.float32)
+    rc = _lib().ftg_dequantize_ex(ggml_type, raw.data_ptr(), out.data_ptr(), n, _order_flag(nibble_order))
+    if rc != 0:
+        raise ValueError("unsupported ggml type %d" % ggml_type)
+    return out
 
 
 _LAYER_MAP = {"attn_norm": "input_layernorm", "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj",
@@ -123,13 +169,14 @@ def gguf_key_to_hf(key: str) -> str | None:
     return None
 
 
-def load_gguf_state_dict(path: str, dtype=torch.bfloat16, remap: bool = True) -> dict[str, torch.Tensor]:
+def load_gguf_state_dict(path: str, dtype=torch.bfloat16, remap: bool = True,
+                         nibble_order: str = "ggml") -> dict[str, torch.Tensor]:
     """Dequantise every tensor to ``dtype`` (HF key names when ``remap``)."""
     out = {}
     with GgufFile(path) as f:
         for name in f.tensors:
             key = gguf_key_to_hf(name) if remap else name
-            out[key or name] = f.dequantize(name, dtype)
+            out[key or name] = f.dequantize(name, dtype, nibble_order)
     return out
 
 

@@ -70,3 +70,129 @@ def test_rope_position_zero_is_identity(interleaved):
     x = torch.randn(1, 1, 2, 8)
     y = F.rope_(x.clone(), cos, sin, n_rot_heads=2, seq_len=1, interleaved=interleaved)
     assert torch.allclose(y, x, atol=1e-7)
+
+
+# --------------------------------------------------------------------------- GGUF block decoders
+# Vectors of ferrotorch-serialize/src/gguf.rs:1150-1250 (the decoder tests) and :1515-1630 (headers
+# whose counts lie about the file's size must be rejected quickly, without a huge allocation).
+def _f16_bytes(v):
+    return list(torch.tensor([v], dtype=torch.float16).view(torch.uint8).tolist())
+
+
+def _blocks(*rows):
+    return torch.tensor([b for r in rows for b in r], dtype=torch.uint8)
+
+
+def test_q4_0_known_values_both_orders():
+    from ferrotorch_b200.serialize import gguf as G
+    blk = _f16_bytes(1.0) + [0x88, 0x97, 0xA6] + [0x88] * 13
+    raw = _blocks(blk)
+    # the order the reference's decoder emits: byte j -> elements 2j, 2j + 1
+    y = G.dequantize_blocks(raw, G.GGML_Q4_0, 32, nibble_order="interleaved")
+    assert y[:6].tolist() == [0.0, 0.0, -1.0, 1.0, -2.0, 2.0] and y[6:].abs().max() == 0
+    assert torch.equal(R.dequant_q4_0(raw.view(1, 18), "interleaved"), y)
+    # the file format's order: byte j -> elements j, j + 16
+    z = G.dequantize_blocks(raw, G.GGML_Q4_0, 32)
+    assert z[:3].tolist() == [0.0, -1.0, -2.0] and z[16:19].tolist() == [0.0, 1.0, 2.0]
+    assert torch.equal(R.dequant_q4_0(raw.view(1, 18)), z)
+    # re-packing turns one convention's bytes into the other's
+    rp = G.repack_nibbles(raw.clone(), G.GGML_Q4_0, to_interleaved=False)
+    assert torch.equal(G.dequantize_blocks(rp, G.GGML_Q4_0, 32), y)
+    assert torch.equal(G.repack_nibbles(rp.clone(), G.GGML_Q4_0, to_interleaved=True), raw)
+
+
+def test_q4_0_scale_factor():
+    from ferrotorch_b200.serialize import gguf as G
+    raw = _blocks(_f16_bytes(0.5) + [0x97] + [0x88] * 15)
+    y = G.dequantize_blocks(raw, G.GGML_Q4_0, 32, nibble_order="interleaved")
+    assert y[:2].tolist() == [-0.5, 0.5]
+    z = G.dequantize_blocks(raw, G.GGML_Q4_0, 32)
+    assert z[0].item() == -0.5 and z[16].item() == 0.5
+
+
+def test_q5_and_q4_1_orders_agree_up_to_permutation():
+    from ferrotorch_b200.serialize import gguf as G
+    g = torch.Generator().manual_seed(3)
+    for t in (G.GGML_Q4_1, G.GGML_Q5_0, G.GGML_Q5_1):
+        bb = G._BLOCK[t][1]
+        raw = torch.randint(0, 256, (4, bb), generator=g, dtype=torch.uint8)
+        raw[:, :2] = torch.tensor(_f16_bytes(0.25), dtype=torch.uint8)
+        if t in (G.GGML_Q4_1, G.GGML_Q5_1):
+            raw[:, 2:4] = torch.tensor(_f16_bytes(-1.5), dtype=torch.uint8)
+        a = G.dequantize_blocks(raw.reshape(-1), t, 128).view(4, 32)
+        b = G.dequantize_blocks(raw.reshape(-1), t, 128, nibble_order="interleaved").view(4, 32)
+        if t == G.GGML_Q4_1:   # same nibbles, different positions
+            assert torch.equal(b[:, 0::2], a[:, :16]) and torch.equal(b[:, 1::2], a[:, 16:])
+        else:                  # the fifth bit comes from a different place too: check it by hand
+            qh_off = 2 if t == G.GGML_Q5_0 else 4
+            q_off = qh_off + 4
+            qh = int.from_bytes(bytes(raw[0, qh_off:qh_off + 4].tolist()), "little")
+            d, m = 0.25, (-1.5 if t == G.GGML_Q5_1 else 0.0)
+            for j in range(16):
+                byte = int(raw[0, q_off + j])
+                lo = (byte & 15) | (((qh >> (2 * j)) & 1) << 4)
+                hi = (byte >> 4) | (((qh >> (2 * j + 1)) & 1) << 4)
+                off = 16 if t == G.GGML_Q5_0 else 0
+                assert b[0, 2 * j].item() == (lo - off) * d + m and b[0, 2 * j + 1].item() == (hi - off) * d + m
+                lo_g = (byte & 15) | (((qh >> j) & 1) << 4)
+                hi_g = (byte >> 4) | (((qh >> (j + 16)) & 1) << 4)
+                assert a[0, j].item() == (lo_g - off) * d + m and a[0, j + 16].item() == (hi_g - off) * d + m
+
+
+def test_q8_0_identity_and_negative():
+    from ferrotorch_b200.serialize import gguf as G
+    raw = _blocks(_f16_bytes(1.0) + list(range(32)))
+    assert G.dequantize_blocks(raw, G.GGML_Q8_0, 32).tolist() == [float(i) for i in range(32)]
+    raw = _blocks(_f16_bytes(2.0) + [0xFF, 0xFE] + [0] * 30)
+    assert G.dequantize_blocks(raw, G.GGML_Q8_0, 32)[:2].tolist() == [-2.0, -4.0]
+
+
+def test_f16_values_and_specials():
+    from ferrotorch_b200.serialize import gguf as G
+    raw = _blocks(*[_f16_bytes(v) for v in (0.0, 1.0, -1.0, 0.5)])
+    assert G.dequantize_blocks(raw, G.GGML_F16, 4).tolist() == [0.0, 1.0, -1.0, 0.5]
+    raw = torch.tensor([0x00, 0x80, 0x00, 0x7C, 0x01, 0x7C, 0x01, 0x00], dtype=torch.uint8)
+    y = G.dequantize_blocks(raw, G.GGML_F16, 4)
+    assert y[0].item() == 0.0 and math.copysign(1.0, y[0].item()) == -1.0
+    assert math.isinf(y[1].item()) and y[1].item() > 0 and math.isnan(y[2].item())
+    assert y[3].item() == 2.0 ** -24    # smallest subnormal
+
+
+def test_block_properties():
+    from ferrotorch_b200.serialize import gguf as G
+    assert G._BLOCK[G.GGML_F32] == (1, 4) and G._BLOCK[G.GGML_F16] == (1, 2)
+    assert G._BLOCK[G.GGML_Q4_0] == (32, 18) and G._BLOCK[G.GGML_Q8_0] == (32, 34)
+
+
+def _stub(tensor_count, kv_count, tail=b""):
+    import struct
+    return b"GGUF" + struct.pack("<IQQ", 3, tensor_count, kv_count) + tail
+
+
+@pytest.mark.parametrize("payload", [
+    b"GGUF",                                               # truncated after the magic
+    _stub(0, 2 ** 64 - 1), _stub(2 ** 64 - 1, 0), _stub(2 ** 64 - 1, 2 ** 64 - 1),
+    _stub(0, 100_000), _stub(100_000, 0),
+    _stub(0, 1, (100).to_bytes(8, "little")),              # key length 100, no key bytes
+    _stub(0, 1, (1).to_bytes(8, "little") + b"x" + (9).to_bytes(4, "little") + (4).to_bytes(4, "little")
+          + (2 ** 64 - 1).to_bytes(8, "little")),          # array of 2^64 - 1 elements
+    b"GGML" + bytes(20),                                   # wrong magic
+])
+def test_gguf_header_lies_are_rejected_fast(tmp_path, payload):
+    import time
+    from ferrotorch_b200.serialize import gguf as G
+    p = tmp_path / "bad.gguf"
+    p.write_bytes(payload)
+    t0 = time.perf_counter()
+    with pytest.raises(ValueError):
+        G.GgufFile(str(p))
+    assert time.perf_counter() - t0 < 1.0
+
+
+def test_q4_0_planes_accept_both_orders():
+    from ferrotorch_b200.ops import quant as Q
+    raw = torch.randint(0, 256, (16, 18), dtype=torch.uint8, generator=torch.Generator().manual_seed(5))
+    raw[:, :2] = torch.tensor(_f16_bytes(1.0), dtype=torch.uint8)
+    for order in ("ggml", "interleaved"):
+        nib, sc = Q.q4_0_planes(raw, 8, 64, order)
+        assert torch.equal(Q.dequant_q4_0_planes(nib, sc).reshape(-1), R.dequant_q4_0(raw, order))
