@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--warmup-steps", type=int, default=8)
     ap.add_argument("--graph", action="store_true", help="capture the decode step in a CUDA graph")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "q4_0"],
+                    help="q4_0: the same random weights quantised to GGUF Q4_0 planes (dequant-GEMM path)")
     args = ap.parse_args()
 
     import torch
@@ -54,7 +56,8 @@ def main():
                                         head_dim=128)}[args.model]()
     if args.layers:
         cfg.num_hidden_layers = args.layers
-    eng = LlamaEngine(cfg, TPContext(group, dev), max_batch=args.batch, max_seq_len=args.prompt + args.new + 32, cuda_graph=args.graph)
+    eng = LlamaEngine(cfg, TPContext(group, dev), max_batch=args.batch, max_seq_len=args.prompt + args.new + 32, cuda_graph=args.graph,
+                      weight_format=args.weights)
     prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt), generator=torch.Generator().manual_seed(0))
 
     def sync():
@@ -99,7 +102,7 @@ def main():
             "prefill_tokens_per_s": args.batch * args.prompt / (ms_prefill / 1e3), "prefill_ms": ms_prefill,
             "decode_tokens_per_s": args.batch * args.new / (ms_decode / 1e3),
             "decode_ms_per_step": ms_decode / args.new, "cuda_graph": bool(args.graph), "gpu_launches_decode": launches, "device_status": status,
-            "dtype": "bf16", "data": "synthetic"}))
+            "dtype": "bf16", "weights": args.weights, "data": "synthetic"}))
     if world > 1:
         dist.destroy_process_group()
 

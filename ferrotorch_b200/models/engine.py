@@ -14,6 +14,13 @@ paged decode kernel, and shards the model Megatron-style across a tensor-paralle
 
 Bracketed steps are single fused kernels (``csrc/tp_gemm.cu``).  With one rank the same kernels
 run with an empty collective part.
+
+``weight_format="q4_0"`` keeps the linear weights as GGUF Q4_0 planes (0.5625 bytes per element,
+ferrotorch-serialize/src/gguf.rs:543-545; the reference dequantises whole tensors to bf16 at load
+time, ferrotorch-llama/src/gpu_gguf.rs:336).  The column-parallel layers then run as this
+library's gather kernel followed by the dequant-GEMM (``csrc/quant_gemm.cu``) on the gathered
+rows, the row-parallel ones as the dequant-GEMM followed by an NCCL reduce-scatter and the
+residual add: two launches per layer instead of one fused kernel.
 """
 from __future__ import annotations
 
@@ -26,6 +33,7 @@ from .. import _native
 from ..nn.paged import PagedAttentionManager, PagedKVCache
 from ..ops import functional as F
 from ..ops import reference as ref
+from ..ops.quant import q4_0_linear, quantize_q4_0_planes
 from ..parallel.tensor_parallel import TPContext
 from .llama import LlamaConfig
 
@@ -38,7 +46,10 @@ def _shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 class LlamaEngine:
     def __init__(self, cfg: LlamaConfig, tp: TPContext | None = None, *, max_batch: int = 64,
                  max_seq_len: int = 4096, block_size: int = 16, weights: dict | None = None, seed: int = 0,
-                 device=None, prefill_chunk_tokens: int = 16384, cuda_graph: bool = False):
+                 device=None, prefill_chunk_tokens: int = 16384, cuda_graph: bool = False,
+                 weight_format: str = "bf16"):
+        assert weight_format in ("bf16", "q4_0")
+        self.weight_format = weight_format
         self.cfg = cfg
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.tp = tp if tp is not None else TPContext(None, self.device)
@@ -102,6 +113,8 @@ class LlamaEngine:
                 dn = dw[:, r * self.F:(r + 1) * self.F].to(dev, torch.bfloat16).contiguous()
                 n1 = sd[pre + "input_layernorm.weight"].to(dev, torch.bfloat16)
                 n2 = sd[pre + "post_attention_layernorm.weight"].to(dev, torch.bfloat16)
+            if self.weight_format == "q4_0":
+                qkv, gu, o, dn = (quantize_q4_0_planes(w) for w in (qkv, gu, o, dn))
             self.layers.append(dict(qkv=qkv, gu=gu, o=o, down=dn, n1=n1, n2=n2))
         self.norm = (torch.ones(self.H, device=dev, dtype=torch.bfloat16) if sd is None
                      else sd["model.norm.weight"].to(dev, torch.bfloat16))
@@ -114,6 +127,11 @@ class LlamaEngine:
             if shard.shape[0] < self.Vloc:  # pad the last shard; padded rows can never win the argmax
                 shard = torch.cat([shard, torch.zeros(self.Vloc - shard.shape[0], self.H, device=dev, dtype=torch.bfloat16)])
             self.lm_head = shard.contiguous()
+        if self.weight_format == "q4_0":
+            if self.Vloc % 8:                   # the dequant-GEMM wants N % 8 == 0: pad with zero rows
+                pad = 8 - self.Vloc % 8
+                self.lm_head = torch.cat([self.lm_head, torch.zeros(pad, self.H, device=dev, dtype=torch.bfloat16)])
+            self.lm_head = quantize_q4_0_planes(self.lm_head)
 
     # ------------------------------------------------------------------ one transformer pass
     def _rows(self, M: int):
@@ -141,6 +159,27 @@ class LlamaEngine:
         _native.check(rc, "ft_rmsnorm_fwd")
         return out
 
+    def _col(self, slot: int, M: int, w) -> torch.Tensor:
+        """Column-parallel linear on the gather buffer of ``slot``: ``[M, N_loc]``."""
+        if not isinstance(w, tuple):
+            return self.tp.ag_gemm(slot, M, w)
+        xg = self.tp.gather_buffer(slot, M, self.H) if self.W == 1 else self.tp.all_gather_rows(slot, M, self.H)
+        return q4_0_linear(xg, w[0], w[1])
+
+    def _row(self, slot: int, a: torch.Tensor, w, residual: torch.Tensor) -> torch.Tensor:
+        """Row-parallel linear + reduce-scatter + residual add: this rank's rows ``[rows, H]``."""
+        if not isinstance(w, tuple):
+            return self.tp.gemm_rs(slot, a, w, residual=residual)
+        y = q4_0_linear(a, w[0], w[1])
+        if self.W == 1:
+            return y.add_(residual)
+        M, ms = a.shape[0], self.tp.rows_per_rank(a.shape[0])
+        if M < self.W * ms:
+            y = torch.cat([y, y.new_zeros(self.W * ms - M, self.H)])
+        mine = torch.empty((ms, self.H), device=self.device, dtype=y.dtype)
+        dist.reduce_scatter_tensor(mine, y, group=self.tp.group)
+        return mine[:residual.shape[0]].add_(residual)
+
     def _forward(self, tokens: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor | None,
                  B: int, S: int, decode: bool, ctx_len: torch.Tensor | None) -> torch.Tensor:
         """tokens: flat [M] ids.  Returns this rank's rows of the final hidden state [rows, H]
@@ -152,7 +191,7 @@ class LlamaEngine:
         nh = Hq + 2 * Hkv
         for li, L in enumerate(self.layers):
             self._norm_into(0, x, None, L["n1"], M)
-            qkv = self.tp.ag_gemm(0, M, L["qkv"]).view(M, nh, D)
+            qkv = self._col(0, M, L["qkv"]).view(M, nh, D)
             F._rope_launch(qkv, self.cos, self.sin, positions, Hq + Hkv, S, 0, False, False)
             k, v = qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
             self.cache.append(li, k, v, positions, seq_ids, tokens_per_seq=S)
@@ -163,20 +202,20 @@ class LlamaEngine:
                 attn, _ = F.flash_attn_fwd(q4[:, :, :Hq], q4[:, :, Hq:Hq + Hkv], q4[:, :, Hq + Hkv:], True,
                                            return_lse=False)
             # o_proj + reduce-scatter + residual add  -> new residual rows
-            x = self.tp.gemm_rs(1, attn.reshape(M, Hq * D), L["o"], residual=x)
+            x = self._row(1, attn.reshape(M, Hq * D), L["o"], x)
             self._norm_into(2, x, None, L["n2"], M)
-            gu = self.tp.ag_gemm(2, M, L["gu"])
+            gu = self._col(2, M, L["gu"])
             act = torch.empty((M, self.F), device=self.device, dtype=torch.bfloat16)
             rc = _native.kernels().ft_swiglu_fwd(gu.data_ptr(), act.data_ptr(), M, self.F, gu.stride(0), 0,
                                                  self.device.index, F._stream())
             _native.check(rc, "ft_swiglu_fwd")
-            x = self.tp.gemm_rs(3, act, L["down"], residual=x)
+            x = self._row(3, act, L["down"], x)
         return x
 
     def _local_argmax(self, h_rows: torch.Tensor, M: int) -> torch.Tensor:
         """Final norm + this rank's vocabulary shard of the lm_head -> ``[M, 2]`` (best logit, global id)."""
         self._norm_into(4, h_rows, None, self.norm, M)
-        logits = self.tp.ag_gemm(4, M, self.lm_head).float()
+        logits = self._col(4, M, self.lm_head)[:, :self.Vloc].float()
         if self.cfg.vocab_size % self.W and self.r == self.W - 1:
             logits[:, self.cfg.vocab_size - self.r * self.Vloc:] = -float("inf")
         val, idx = logits.max(dim=-1)

@@ -73,6 +73,27 @@ def q4_0_linear(x: torch.Tensor, nibbles: torch.Tensor, scales: torch.Tensor, bi
     return y.view(*x.shape[:-1], N)
 
 
+def quantize_q4_0_planes(w: torch.Tensor, chunk_rows: int = 8192):
+    """Quantise a float matrix ``[N, K]`` (K % 32 == 0) straight to the kernel's planes
+    ``(nibbles u8 [N, K/2], scales fp16 [N, K/32])`` on the tensor's own device, ``chunk_rows``
+    rows at a time (ggml rule: ``d = signed value of largest magnitude / -8``,
+    ``q = clamp(floor(x / d + 8.5), 0, 15)``; same result as ``serialize.gguf.quantize_q4_0``)."""
+    N, K = w.shape
+    assert K % 32 == 0
+    nib = torch.empty((N, K // 2), device=w.device, dtype=torch.uint8)
+    sc = torch.empty((N, K // 32), device=w.device, dtype=torch.float16)
+    for r0 in range(0, N, chunk_rows):
+        x = w[r0:r0 + chunk_rows].detach().float().reshape(-1, 32)
+        mx = x.gather(1, x.abs().argmax(dim=1, keepdim=True))
+        d = mx / -8.0
+        inv = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+        q = (x * inv + 8.5).floor_().clamp_(0, 15).to(torch.uint8)
+        rows = min(chunk_rows, N - r0)
+        nib[r0:r0 + rows] = (q[:, :16] | (q[:, 16:] << 4)).reshape(rows, K // 2)
+        sc[r0:r0 + rows] = d.to(torch.float16).reshape(rows, K // 32)
+    return nib, sc
+
+
 def requantize_q4_0(w: torch.Tensor):
     """Any float weight ``[N, K]`` (e.g. a dequantised GPTQ / AWQ / HQQ tensor) -> Q4_0 planes."""
     from ..serialize.gguf import quantize_q4_0

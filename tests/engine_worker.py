@@ -28,9 +28,20 @@ def main():
                       initializer_range=0.08)
     torch.manual_seed(3)
     model = LlamaForCausalLM(cfg).to(dev, torch.bfloat16).eval()
+    fmt = os.environ.get("FT_TEST_WEIGHTS", "bf16")
+    if fmt == "q4_0":
+        # the oracle gets the same rounding: every linear weight goes through Q4_0 and back (twice:
+        # the second pass sees bf16 inputs like the engine does, and is a fixed point)
+        from ferrotorch_b200.ops.quant import dequant_q4_0_planes, quantize_q4_0_planes
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                if p.dim() == 2 and "embed_tokens" not in name:
+                    for _ in range(2):
+                        p.copy_(dequant_q4_0_planes(*quantize_q4_0_planes(p)).to(p.dtype))
     sd = model.hf_state_dict()
     eng = LlamaEngine(cfg, TPContext(group, dev), max_batch=4, max_seq_len=128, weights=sd,
-                      prefill_chunk_tokens=96, cuda_graph=os.environ.get("FT_TEST_GRAPH") == "1")
+                      prefill_chunk_tokens=96, cuda_graph=os.environ.get("FT_TEST_GRAPH") == "1",
+                      weight_format=fmt)
     B, S, new = 4, 48, 8
     prompts = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1)).to(dev)
     got = eng.generate(prompts, new)

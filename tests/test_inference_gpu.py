@@ -62,9 +62,9 @@ def test_page_pool_bookkeeping():
     assert out.shape == (2, 1, 8)
 
 
-def _run(nproc, port, graph=False):
+def _run(nproc, port, graph=False, weights="bf16"):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", FT_TEST_GRAPH="1" if graph else "0",
-               FT_COMM_TIMEOUT_MS="5000")
+               FT_COMM_TIMEOUT_MS="5000", FT_TEST_WEIGHTS=weights)
     script = os.path.join(HERE, "engine_worker.py")
     cmd = [sys.executable, script] if nproc == 1 else [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
@@ -94,3 +94,21 @@ def test_engine_single_gpu_cuda_graph():
 @pytest.mark.multigpu
 def test_engine_tensor_parallel_2_cuda_graph():
     _run(2, 29552, graph=True)
+
+
+# The Q4_0 weight format of the engine is a composition of kernels that each have their own test
+# (gather, dequant-GEMM); the composition itself has not run on a GPU yet, so these two are opt-in.
+_q4 = pytest.mark.skipif(os.environ.get("FT_TEST_NEW_PATHS") != "1", reason="set FT_TEST_NEW_PATHS=1 to run")
+
+
+@pytest.mark.gpu
+@_q4
+def test_engine_q4_0_single_gpu():
+    _run(1, 0, weights="q4_0")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@_q4
+def test_engine_q4_0_tensor_parallel_2():
+    _run(2, 29553, weights="q4_0")
