@@ -416,3 +416,44 @@ FTC_API int ftc_ring_allreduce_f32(void* h, float* data, long long n, int mean) 
   }
   return FTC_OK;
 }
+
+// Broadcast down a binary tree laid over the mesh (gloo_native/collectives.rs:232-275): with
+// v = (rank - root) mod W a rank's parent is (v - 1) / 2 and its children are 2v + 1 and 2v + 2,
+// so the depth is ceil(log2 W) instead of the star's W - 1 sequential sends from rank 0.
+FTC_API int ftc_tree_broadcast(void* h, void* buf, long long nbytes, int root) {
+  Comm* c = static_cast<Comm*>(h);
+  const int W = c->world;
+  if (root < 0 || root >= W) return FTC_INVALID_RANK;
+  if (W == 1) return FTC_OK;
+  int rc = ftc_connect_mesh(h);
+  if (rc) return rc;
+  const int v = (c->rank - root + W) % W;
+  auto real = [&](int tree_rank) { return (tree_rank + root) % W; };
+  if (v != 0 && (rc = recv_frame(c->mesh[real((v - 1) / 2)], buf, nbytes, c->timeout_ms))) return rc;
+  for (int child = 2 * v + 1; child <= 2 * v + 2 && child < W; ++child)
+    if ((rc = send_frame(c->mesh[real(child)], buf, nbytes))) return rc;
+  return FTC_OK;
+}
+
+// Barrier without a coordinator: a one-byte token travels the ring twice
+// (gloo_native/collectives.rs:285-320).  The first lap proves that every rank has arrived, the
+// second releases them; nobody leaves before everybody has entered.
+FTC_API int ftc_ring_barrier(void* h) {
+  Comm* c = static_cast<Comm*>(h);
+  const int W = c->world, r = c->rank;
+  if (W == 1) return FTC_OK;
+  int rc = ftc_connect_mesh(h);
+  if (rc) return rc;
+  const int next = c->mesh[(r + 1) % W], prev = c->mesh[(r + W - 1) % W];
+  char token = 1, got = 0;
+  for (int lap = 0; lap < 2; ++lap) {
+    if (r == 0) {
+      if ((rc = send_frame(next, &token, 1))) return rc;
+      if ((rc = recv_frame(prev, &got, 1, c->timeout_ms))) return rc;
+    } else {
+      if ((rc = recv_frame(prev, &got, 1, c->timeout_ms))) return rc;
+      if ((rc = send_frame(next, &token, 1))) return rc;
+    }
+  }
+  return FTC_OK;
+}

@@ -207,7 +207,8 @@ def _host_lib():
                            ("ftc_barrier", [vp]), ("ftc_broadcast", [vp, vp, ll, ci]),
                            ("ftc_allreduce_f32", [vp, vp, ll, ci]), ("ftc_allreduce_f64", [vp, vp, ll, ci]),
                            ("ftc_allgather", [vp, vp, vp, ll]), ("ftc_connect_mesh", [vp]),
-                           ("ftc_ring_allreduce_f32", [vp, vp, ll, ci])):
+                           ("ftc_ring_allreduce_f32", [vp, vp, ll, ci]),
+                           ("ftc_tree_broadcast", [vp, vp, ll, ci]), ("ftc_ring_barrier", [vp])):
             fn = getattr(lib, name)
             fn.restype = ci
             fn.argtypes = args
@@ -259,12 +260,21 @@ class TcpGroup(Group):
         ms = -1 if timeout is None else int(timeout * 1000)
         _raise(self._lib.ftc_recv(self._h, t.data_ptr(), t.numel() * t.element_size(), src, ms), "recv")
 
-    def barrier(self) -> None:
-        _raise(self._lib.ftc_barrier(self._h), "barrier")
+    def barrier(self, algorithm: str = "star") -> None:
+        """``"star"``: gather at rank 0, then release; ``"ring"``: a token goes round the ring of
+        the full mesh twice, no coordinator."""
+        assert algorithm in ("star", "ring")
+        _raise((self._lib.ftc_ring_barrier if algorithm == "ring" else self._lib.ftc_barrier)(self._h), "barrier")
 
-    def broadcast(self, t: torch.Tensor, root: int = 0) -> torch.Tensor:
+    def broadcast(self, t: torch.Tensor, root: int = 0, algorithm: str = "star") -> torch.Tensor:
+        """``"star"`` relays through rank 0; ``"tree"`` forwards down a binary tree rooted at
+        ``root`` over the full mesh (log2 W hops)."""
+        assert algorithm in ("star", "tree")
+        if not 0 <= root < self.world_size:
+            raise InvalidRank("root %d outside a world of %d" % (root, self.world_size))
         buf = t if t.is_contiguous() else t.contiguous()
-        _raise(self._lib.ftc_broadcast(self._h, buf.data_ptr(), buf.numel() * buf.element_size(), root), "broadcast")
+        fn = self._lib.ftc_tree_broadcast if algorithm == "tree" else self._lib.ftc_broadcast
+        _raise(fn(self._h, buf.data_ptr(), buf.numel() * buf.element_size(), root), "broadcast")
         if buf.data_ptr() != t.data_ptr():
             t.copy_(buf)
         return t

@@ -42,6 +42,16 @@ def collectives(rank, world, port, q):
             x = torch.zeros(1)
             g.recv(x, 0)
             out["p2p"] = x.item()
+        for root in range(world):
+            tb = torch.full((7,), float(rank * 10 + root))
+            g.broadcast(tb, root, algorithm="tree")
+            out["tree%d" % root] = tb.tolist()
+        g.barrier(algorithm="ring")
+        try:
+            g.broadcast(torch.zeros(1), world, algorithm="tree")
+            out["bad_root"] = "accepted"
+        except Exception as e:  # noqa: BLE001
+            out["bad_root"] = type(e).__name__
         g.barrier()
         g.close()
         q.put((rank, out))

@@ -123,7 +123,7 @@ def test_ddp_buckets_and_sync_simulated():
 
 
 # ----------------------------------------------------------------------------- loopback TCP
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 5])
 def test_tcp_collectives(world):
     out = _spawn(W.collectives, world)
     tot = float(sum(range(1, world + 1)))
@@ -137,6 +137,9 @@ def test_tcp_collectives(world):
         assert o["a2a"] == [r + 10.0 * p for p in range(world)]
         assert o["ring"] == [tot, 999 * tot]
         assert o["f64"] == [0.5 * tot] * 3
+        for root in range(world):                      # binary-tree broadcast from every root
+            assert o["tree%d" % root] == [float(root * 10 + root)] * 7
+        assert o["bad_root"] == "InvalidRank"
     assert out[world - 1]["p2p"] == 42.0
 
 
@@ -153,6 +156,63 @@ def test_tcp_size_mismatch():
 def test_tcp_rank_that_leaves_is_detected():
     out = _spawn(W.dead_peer_case, 2)
     assert out[1] == "left" and out[0].startswith("error")
+
+
+def _hostile_peer(port, announce, frames, close_after=None):
+    """A raw socket that plays rank 1 badly: sends ``announce`` as its rank, then ``frames``."""
+    import struct
+    import threading
+    import time
+
+    def run():
+        deadline = time.time() + 20
+        while True:
+            try:
+                s = socket.create_connection(("127.0.0.1", port), timeout=1)
+                break
+            except OSError:
+                if time.time() > deadline:
+                    return
+                time.sleep(0.05)
+        s.sendall(struct.pack("<Q", announce))
+        for f in frames:
+            s.sendall(f)
+        time.sleep(close_after if close_after is not None else 3.0)
+        s.close()
+
+    t = threading.Thread(target=run, daemon=True)
+    t.start()
+    return t
+
+
+def test_tcp_hostile_peer_is_rejected_with_typed_errors():
+    import struct
+    import time
+
+    # a peer that announces a rank outside the world never gets into the group
+    port = _free_port()
+    _hostile_peer(port, 99, [])
+    with pytest.raises(B.InvalidRank):
+        B.TcpGroup(0, 2, "127.0.0.1", port, timeout=10)
+    # a length prefix that disagrees with what the receiver expects (here: 2^60 bytes) is an
+    # error at once, not an allocation or a long read
+    port = _free_port()
+    _hostile_peer(port, 1, [struct.pack("<Q", 1 << 60) + b"junk"])
+    g = B.TcpGroup(0, 2, "127.0.0.1", port, timeout=10)
+    t0 = time.perf_counter()
+    with pytest.raises(B.SizeMismatch):
+        g.recv(torch.zeros(4), 1, timeout=5.0)
+    assert time.perf_counter() - t0 < 2.0
+    g.close()
+    # a peer that hangs up in the middle of a payload: an error, not a hang
+    port = _free_port()
+    _hostile_peer(port, 1, [struct.pack("<Q", 16) + b"only8byt"], close_after=0.2)
+    g = B.TcpGroup(0, 2, "127.0.0.1", port, timeout=10)
+    t0 = time.perf_counter()
+    with pytest.raises(B.DistributedError):
+        g.recv(torch.zeros(4), 1, timeout=5.0)
+    assert time.perf_counter() - t0 < 4.0
+    g.close()
 
 
 # ----------------------------------------------------------------------------- config 0
