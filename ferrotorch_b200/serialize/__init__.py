@@ -2,7 +2,7 @@
 from .gguf import GgufFile, gguf_key_to_hf, load_gguf_state_dict, quantize_q4_0, write_gguf  # noqa: F401
 from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_checkpoint,  # noqa: F401
                     load_pytorch_state_dict, load_safetensors, load_safetensors_sharded, load_state_dict,
-                    loads_state_dict, save_checkpoint, save_pytorch, save_safetensors, save_safetensors_sharded,
+                    loads_state_dict, save_checkpoint, save_reference_checkpoint, save_pytorch, save_safetensors, save_safetensors_sharded,
                     save_state_dict)
 
 

@@ -116,28 +116,56 @@ def _to_bytes(t: torch.Tensor) -> bytes:
     return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
 
 
+_TAG = {torch.float32: "f32", torch.float64: "f64", torch.float16: "f16", torch.bfloat16: "bf16",
+        torch.int64: "i64", torch.int32: "i32", torch.int16: "i16", torch.int8: "i8", torch.uint8: "u8",
+        torch.bool: "bool"}
+_TAG_INV = {v: k for k, v in _TAG.items()}
+
+
 def dumps_state_dict(state: dict[str, torch.Tensor]) -> bytes:
+    """The reference's layout byte for byte (state_dict.rs:74-165): one JSON line per tensor, keys
+    sorted, fields ``name, shape, dtype, byte_offset, byte_length`` without spaces, every line
+    ended by a newline, then the separator, then the raw little-endian bytes.  An f32 / f64 file
+    written here loads in the reference; the other dtype tags (bf16, f16, i64 ...) extend it."""
     header, blobs, off = [], [], 0
-    for k, v in state.items():
+    for k in sorted(state):
+        v = state[k]
         b = _to_bytes(v)
-        header.append(json.dumps({"name": k, "dtype": _DT_INV[v.dtype], "shape": list(v.shape), "offset": off,
-                                  "nbytes": len(b)}))
+        header.append('{"name":%s,"shape":[%s],"dtype":"%s","byte_offset":%d,"byte_length":%d}\n'
+                      % (json.dumps(k), ",".join(str(int(d)) for d in v.shape), _TAG[v.dtype], off, len(b)))
         blobs.append(b)
         off += len(b)
-    return ("\n".join(header)).encode() + b"\n---\n" + b"".join(blobs)
+    return "".join(header).encode() + b"\n---\n" + b"".join(blobs)
 
 
 def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
-    sep = buf.index(b"\n---\n")
-    body = memoryview(buf)[sep + 5:]
+    """Reads the layout above, files the reference wrote, and the first layout of this package
+    (fields ``offset`` / ``nbytes``, upper-case dtype names)."""
+    head_end = 0 if buf.startswith(b"---\n") else buf.find(b"\n---\n") + 1
+    if head_end == 0 and not buf.startswith(b"---\n"):
+        raise ValueError("state dict: no separator line")
+    body = memoryview(buf)[head_end + 4:]
     out = {}
-    for line in buf[:sep].decode().splitlines():
+    for line in buf[:head_end].decode().splitlines():
         if not line.strip():
             continue
         e = json.loads(line)
-        raw = bytes(body[e["offset"]:e["offset"] + e["nbytes"]])
-        t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(_DT[e["dtype"]]) if raw else \
-            torch.empty(0, dtype=_DT[e["dtype"]])
+        off = e["byte_offset"] if "byte_offset" in e else e["offset"]
+        n = e["byte_length"] if "byte_length" in e else e["nbytes"]
+        tag = e["dtype"]
+        dt = _TAG_INV.get(tag) or _DT.get(tag)
+        if dt is None:
+            raise ValueError("state dict: unknown dtype %r for %s" % (tag, e["name"]))
+        if off < 0 or n < 0 or off + n > len(body):
+            raise ValueError("state dict: tensor %r needs bytes [%d, %d) of a %d-byte body"
+                             % (e["name"], off, off + n, len(body)))
+        numel = 1
+        for d in e["shape"]:
+            numel *= int(d)
+        if numel * torch.empty(0, dtype=dt).element_size() != n:
+            raise ValueError("state dict: shape %s of %r does not match %d bytes" % (e["shape"], e["name"], n))
+        raw = bytes(body[off:off + n])
+        t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dt) if raw else torch.empty(0, dtype=dt)
         out[e["name"]] = t.reshape(e["shape"]).to(device)
     return out
 
@@ -206,10 +234,53 @@ def save_checkpoint(path: str, model_state: dict[str, torch.Tensor], optimizer_s
     os.replace(tmp, path)
 
 
+def _read_sections(f, path: str, n_sections: int = 3) -> list[bytes]:
+    size = os.fstat(f.fileno()).st_size
+    secs = []
+    for _ in range(n_sections):
+        head = f.read(8)
+        if len(head) != 8:
+            raise ValueError("%s: truncated checkpoint (section length)" % path)
+        (n,) = struct.unpack("<Q", head)
+        if n > size - f.tell():
+            raise ValueError("%s: a section claims %d bytes, the file has %d left" % (path, n, size - f.tell()))
+        secs.append(f.read(n))
+    return secs
+
+
+def save_reference_checkpoint(path: str, model_state: dict[str, torch.Tensor],
+                              optimizer_state: dict[str, dict[str, list[float]]] | None = None,
+                              epoch: int = 0, step: int = 0) -> None:
+    """A checkpoint in the reference's own ``.ftc`` layout (checkpoint.rs:1-17, 86-123): three
+    sections with 8-byte little-endian lengths -- ``{"epoch":E,"step":S}``, the optimizer state
+    as ``{param: {slot: [floats]}}`` with sorted keys, and the state-dict bytes.  No magic, no
+    extras: use it to hand a model back to the reference."""
+    opt = optimizer_state or {}
+    opt_json = "{%s}" % ",".join(
+        '%s:{%s}' % (json.dumps(k), ",".join('%s:[%s]' % (json.dumps(ik), ",".join(repr(float(x)) for x in opt[k][ik]))
+                                             for ik in sorted(opt[k]))) for k in sorted(opt))
+    sections = [('{"epoch":%d,"step":%d}' % (epoch, step)).encode(), opt_json.encode(), dumps_state_dict(model_state)]
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        for sec in sections:
+            f.write(struct.pack("<Q", len(sec)))
+            f.write(sec)
+    os.replace(tmp, path)
+
+
 def load_checkpoint(path: str, device="cpu") -> dict:
+    """Loads a checkpoint of this package (magic ``FTCK1``) or one the reference wrote (no magic:
+    the file starts with the length of its metadata JSON)."""
     with open(path, "rb") as f:
         if f.read(len(MAGIC)) != MAGIC:
-            raise ValueError("%s is not a ferrotorch_b200 checkpoint" % path)
+            f.seek(0)
+            meta_b, opt_b, sd_b = _read_sections(f, path)
+            try:
+                meta, opt = json.loads(meta_b), json.loads(opt_b)
+            except ValueError as e:
+                raise ValueError("%s is neither a ferrotorch_b200 nor a ferrotorch checkpoint: %s" % (path, e))
+            return {"model": loads_state_dict(sd_b, device), "optimizer": opt, "epoch": int(meta["epoch"]),
+                    "step": int(meta["step"]), "extra": {}}
         secs = []
         for _ in range(3):
             (n,) = struct.unpack("<Q", f.read(8))

@@ -196,3 +196,67 @@ def test_q4_0_planes_accept_both_orders():
     for order in ("ggml", "interleaved"):
         nib, sc = Q.q4_0_planes(raw, 8, 64, order)
         assert torch.equal(Q.dequant_q4_0_planes(nib, sc).reshape(-1), R.dequant_q4_0(raw, order))
+
+
+# --------------------------------------------------------------------------- native formats
+# Layouts of ferrotorch-serialize/src/state_dict.rs:74-165 and checkpoint.rs:86-200: files the
+# reference wrote must load here, and f32 files written here must be laid out the same way.
+def _reference_state_dict_bytes():
+    import struct
+    head = ('{"name":"fc.bias","shape":[2],"dtype":"f32","byte_offset":0,"byte_length":8}\n'
+            '{"name":"fc.weight","shape":[2,3],"dtype":"f32","byte_offset":8,"byte_length":24}\n')
+    body = struct.pack("<2f", 0.5, -1.0) + struct.pack("<6f", *range(6))
+    return head.encode() + b"\n---\n" + body
+
+
+def test_native_state_dict_layout_matches_the_reference_writer():
+    from ferrotorch_b200.serialize import state as S
+    raw = _reference_state_dict_bytes()
+    sd = S.loads_state_dict(raw)
+    assert sd["fc.bias"].tolist() == [0.5, -1.0]
+    assert sd["fc.weight"].tolist() == [[0.0, 1.0, 2.0], [3.0, 4.0, 5.0]]
+    # written in insertion order "weight, bias": the writer sorts, so the bytes come out identical
+    again = S.dumps_state_dict({"fc.weight": sd["fc.weight"], "fc.bias": sd["fc.bias"]})
+    assert again == raw
+    assert S.dumps_state_dict({}) == b"\n---\n" and S.loads_state_dict(b"\n---\n") == {}
+    f64 = S.loads_state_dict(b'{"name":"s","shape":[],"dtype":"f64","byte_offset":0,"byte_length":8}\n\n---\n'
+                             + __import__("struct").pack("<d", 1.25))
+    assert f64["s"].dtype == torch.float64 and f64["s"].item() == 1.25 and f64["s"].dim() == 0
+
+
+@pytest.mark.parametrize("line,err", [
+    ('{"name":"w","shape":[4],"dtype":"f32","byte_offset":0,"byte_length":16}', "needs bytes"),      # body too short
+    ('{"name":"w","shape":[3],"dtype":"f32","byte_offset":0,"byte_length":8}', "does not match"),    # shape vs bytes
+    ('{"name":"w","shape":[2],"dtype":"q7","byte_offset":0,"byte_length":8}', "unknown dtype"),
+])
+def test_native_state_dict_rejects_inconsistent_headers(line, err):
+    from ferrotorch_b200.serialize import state as S
+    with pytest.raises(ValueError, match=err):
+        S.loads_state_dict(line.encode() + b"\n\n---\n" + bytes(8))
+    with pytest.raises(ValueError, match="separator"):
+        S.loads_state_dict(line.encode())
+
+
+def test_reference_checkpoint_layout_round_trip(tmp_path):
+    import struct
+    from ferrotorch_b200.serialize import state as S
+    sd = _reference_state_dict_bytes()
+    meta = b'{"epoch":3,"step":1200}'
+    opt = b'{"fc.weight":{"exp_avg":[0.1,0.2,0.3,0.4,0.5,0.6],"step":[1200]}}'
+    blob = b"".join(struct.pack("<Q", len(x)) + x for x in (meta, opt, sd))
+    p = tmp_path / "checkpoint_epoch_3.ftc"
+    p.write_bytes(blob)
+    ck = S.load_checkpoint(str(p))
+    assert ck["epoch"] == 3 and ck["step"] == 1200
+    assert ck["optimizer"]["fc.weight"]["step"] == [1200] and len(ck["optimizer"]["fc.weight"]["exp_avg"]) == 6
+    assert ck["model"]["fc.weight"].shape == (2, 3)
+    q = tmp_path / "back.ftc"
+    S.save_reference_checkpoint(str(q), ck["model"], ck["optimizer"], epoch=3, step=1200)
+    raw = q.read_bytes()
+    assert raw[8:8 + len(meta)] == meta and raw.endswith(sd)
+    again = S.load_checkpoint(str(q))
+    assert again["optimizer"] == {"fc.weight": {"exp_avg": [0.1, 0.2, 0.3, 0.4, 0.5, 0.6], "step": [1200.0]}}
+    # a section length that lies about the file's size is an error, not an allocation
+    (tmp_path / "lie.ftc").write_bytes(struct.pack("<Q", 1 << 60) + b"{}")
+    with pytest.raises(ValueError, match="claims"):
+        S.load_checkpoint(str(tmp_path / "lie.ftc"))
