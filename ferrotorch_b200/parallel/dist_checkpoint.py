@@ -1,9 +1,12 @@
 """Sharded (per-rank) checkpoints with resharding and an asynchronous writer, plus async
 collective handles and a small RPC layer.
 
-Reference: ``save_distributed`` writes ``shard_{rank}.safetensors`` + a rank-0 ``metadata.json``
-with ``TensorShardSpec{global_shape, shard_dim}``; ``load_distributed`` reshards when the world
-size changed (ferrotorch-distributed/src/checkpoint.rs:107-140, 359-573); ``AsyncCheckpointer``
+Reference: ``save_distributed`` writes one SafeTensors file per rank (``rank_{r}.safetensors``)
+and a rank-0 ``metadata.json`` = ``{num_ranks, tensor_specs: {name: {full_shape, shard_dim,
+shard_sizes}}}``; ``load_distributed`` reshards when the world size changed, giving the first
+``total % world`` ranks one row more (ferrotorch-distributed/src/checkpoint.rs:107-140, 359-573).
+This module writes ``shard_{r}.safetensors`` and a richer ``metadata.json`` (replicated tensors,
+dtypes, free-form extras) and reads both layouts.  ``AsyncCheckpointer``
 (:686-910); ``PendingCollective`` (async_collective.rs:59-145); ``RpcAgent`` with a name ->
 handler registry, length-prefixed frames capped at 1 GiB, ``rpc_sync`` / ``rpc_async``
 (rpc.rs:44-607).
@@ -49,31 +52,82 @@ def save_distributed(directory: str, local_state: dict[str, torch.Tensor], shard
         group.barrier()
 
 
-def load_distributed(directory: str, rank: int, world_size: int, device="cpu") -> tuple[dict, dict]:
+def shard_sizes(total: int, parts: int) -> list[int]:
+    """Sizes of ``parts`` contiguous shards of ``total`` rows: the first ``total % parts`` get one
+    more (checkpoint.rs ``compute_shard_sizes``)."""
+    base, rem = divmod(total, parts)
+    return [base + (1 if i < rem else 0) for i in range(parts)]
+
+
+def _take(full: torch.Tensor, d: int, rank: int, world_size: int, name: str, uneven: bool) -> torch.Tensor:
+    if full.shape[d] % world_size and not uneven:
+        raise SizeMismatch("%s: dim %d (%d) not divisible by new world size %d" % (name, d, full.shape[d], world_size))
+    sizes = shard_sizes(full.shape[d], world_size)
+    return full.narrow(d, sum(sizes[:rank]), sizes[rank]).contiguous()
+
+
+def load_distributed(directory: str, rank: int, world_size: int, device="cpu", uneven: bool = False) -> tuple[dict, dict]:
     """Load this rank's shards, resharding when ``world_size`` differs from the saved one.
-    Returns ``(state, extra)``."""
+    Returns ``(state, extra)``.  A dimension that does not divide by the new world size is an
+    error unless ``uneven`` (then the split follows :func:`shard_sizes`).  A directory written by
+    the reference (``num_ranks`` / ``tensor_specs`` metadata, ``rank_{r}.safetensors``) loads too;
+    its rule is the uneven one."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError("rank %d outside a world of %d" % (rank, world_size))
     with open(os.path.join(directory, "metadata.json")) as f:
         meta = json.load(f)
-    saved = meta["world_size"]
+    if "tensor_specs" in meta:                        # the reference's layout
+        saved, specs, extra, pattern, uneven = meta["num_ranks"], meta["tensor_specs"], {}, "rank_%d.safetensors", True
+    else:
+        saved, specs, extra, pattern = meta["world_size"], meta["tensors"], meta["extra"], "shard_%d.safetensors"
+
+    def shard_file(r):
+        path = os.path.join(directory, pattern % r)
+        if not os.path.exists(path):
+            raise FileNotFoundError("missing shard %s" % path)
+        return path
+
     if saved == world_size:
-        st = load_safetensors(os.path.join(directory, "shard_%d.safetensors" % rank), device)
+        if not specs and not os.path.exists(os.path.join(directory, pattern % rank)):
+            return {}, extra
+        st = load_safetensors(shard_file(rank), device)
         if rank != 0:
-            rep = {k for k, s in meta["tensors"].items() if s["shard_dim"] is None}
+            rep = {k for k, s in specs.items() if s["shard_dim"] is None}
             if rep:
-                st.update(load_safetensors(os.path.join(directory, "shard_0.safetensors"), device, key_filter=lambda k: k in rep))
-        return st, meta["extra"]
-    shards = [load_safetensors(os.path.join(directory, "shard_%d.safetensors" % r), "cpu") for r in range(saved)]
+                st.update(load_safetensors(shard_file(0), device, key_filter=lambda k: k in rep))
+        return st, extra
+    shards = [load_safetensors(shard_file(r), "cpu") for r in range(saved)]
     out = {}
-    for name, spec in meta["tensors"].items():
+    for name, spec in specs.items():
         d = spec["shard_dim"]
         if d is None:
             out[name] = shards[0][name].to(device)
             continue
-        full = torch.cat([s[name] for s in shards], dim=d)
-        if full.shape[d] % world_size:
-            raise SizeMismatch("%s: dim %d (%d) not divisible by new world size %d" % (name, d, full.shape[d], world_size))
-        out[name] = full.chunk(world_size, dim=d)[rank].contiguous().to(device)
-    return out, meta["extra"]
+        for r, sh in enumerate(shards):
+            if name not in sh:
+                raise KeyError("tensor %r missing from the shard of rank %d" % (name, r))
+        full = torch.cat([sh[name] for sh in shards], dim=d)
+        want = spec.get("full_shape") or spec.get("global_shape")
+        if want is not None and list(full.shape) != list(want):
+            raise SizeMismatch("%s: shards add up to %s, metadata says %s" % (name, list(full.shape), list(want)))
+        out[name] = _take(full, d, rank, world_size, name, uneven).to(device)
+    return out, extra
+
+
+def save_reference_distributed(directory: str, local_state: dict[str, torch.Tensor], shard_dim: dict[str, int],
+                               sizes: dict[str, list[int]], rank: int, world_size: int) -> None:
+    """Write this rank's part of a checkpoint in the reference's layout (every tensor sharded;
+    ``sizes[name]`` = size along ``shard_dim[name]`` on every rank)."""
+    os.makedirs(directory, exist_ok=True)
+    save_safetensors(local_state, os.path.join(directory, "rank_%d.safetensors" % rank))
+    if rank == 0:
+        specs = {}
+        for k, v in local_state.items():
+            full = list(v.shape)
+            full[shard_dim[k]] = sum(sizes[k])
+            specs[k] = {"full_shape": full, "shard_dim": shard_dim[k], "shard_sizes": list(sizes[k])}
+        with open(os.path.join(directory, "metadata.json"), "w") as f:
+            json.dump({"num_ranks": world_size, "tensor_specs": specs}, f, indent=2)
 
 
 class AsyncDistributedCheckpointer:

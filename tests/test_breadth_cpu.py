@@ -306,3 +306,30 @@ def test_distributions_reexport():
     assert D.constraints.positive.check(torch.tensor(1.0))
     t = D.TransformedDistribution(n, [D.transforms.ExpTransform()])
     assert (t.sample() > 0).all()
+
+
+def test_dist_checkpoint_uneven_reshard_and_reference_layout(tmp_path):
+    """The reference's directory layout (rank_{r}.safetensors, num_ranks / tensor_specs) loads, and
+    a world size that does not divide a dimension gives the first ranks one row more
+    (ferrotorch-distributed/src/checkpoint.rs: compute_shard_sizes)."""
+    assert dc.shard_sizes(8, 3) == [3, 3, 2] and dc.shard_sizes(2, 4) == [1, 1, 0, 0]
+    full = _save(tmp_path / "ours", 2)
+    got = [dc.load_distributed(str(tmp_path / "ours"), r, 3, uneven=True)[0]["w"] for r in range(3)]
+    assert [g.shape[0] for g in got] == [3, 3, 2] and torch.equal(torch.cat(got), full["w"])
+    # the reference's layout, written with uneven shards 5 + 3
+    w = full["w"]
+    ref = tmp_path / "ref"
+    parts = [w[:5].contiguous(), w[5:].contiguous()]
+    for r in range(2):
+        dc.save_reference_distributed(str(ref), {"w": parts[r]}, {"w": 0}, {"w": [5, 3]}, r, 2)
+    import json
+    meta = json.loads((ref / "metadata.json").read_text())
+    assert meta == {"num_ranks": 2, "tensor_specs": {"w": {"full_shape": [8, 6], "shard_dim": 0, "shard_sizes": [5, 3]}}}
+    assert torch.equal(dc.load_distributed(str(ref), 1, 2)[0]["w"], parts[1])
+    got = [dc.load_distributed(str(ref), r, 3)[0]["w"] for r in range(3)]
+    assert torch.equal(torch.cat(got), w) and [g.shape[0] for g in got] == [3, 3, 2]
+    (ref / "rank_1.safetensors").unlink()
+    with pytest.raises(FileNotFoundError):
+        dc.load_distributed(str(ref), 0, 4)
+    with pytest.raises(ValueError):
+        dc.load_distributed(str(ref), 4, 4)
