@@ -49,6 +49,8 @@ class LlamaEngine:
                  device=None, prefill_chunk_tokens: int = 16384, cuda_graph: bool = False,
                  weight_format: str = "bf16"):
         assert weight_format in ("bf16", "q4_0")
+        if cfg.hidden_act not in F._ACT_ID:
+            raise NotImplementedError("LlamaEngine: hidden_act %r has no fused kernel (use LlamaForCausalLM)" % cfg.hidden_act)
         self.weight_format = weight_format
         self.cfg = cfg
         self.device = device or torch.device("cuda", torch.cuda.current_device())
@@ -206,7 +208,8 @@ class LlamaEngine:
             self._norm_into(2, x, None, L["n2"], M)
             gu = self._col(2, M, L["gu"])
             act = torch.empty((M, self.F), device=self.device, dtype=torch.bfloat16)
-            rc = _native.kernels().ft_swiglu_fwd(gu.data_ptr(), act.data_ptr(), M, self.F, gu.stride(0), 0,
+            rc = _native.kernels().ft_swiglu_fwd(gu.data_ptr(), act.data_ptr(), M, self.F, gu.stride(0),
+                                                 F._ACT_ID[self.cfg.hidden_act],
                                                  self.device.index, F._stream())
             _native.check(rc, "ft_swiglu_fwd")
             x = self._row(3, act, L["down"], x)

@@ -37,7 +37,8 @@ class LlamaConfig:
     rope_theta: float = 500000.0
     rope_scaling: dict | None = None
     tie_word_embeddings: bool = False
-    hidden_act: str = "silu"
+    hidden_act: str = "silu"            # "silu", "relu" (ReluLLaMA), "gelu", "fatrelu" (ProSparse)
+    hidden_act_param: float | None = None   # FatReLU threshold (0.01 when absent, config.rs:137-140)
     attention_bias: bool = False
     mlp_bias: bool = False
     initializer_range: float = 0.02
@@ -56,6 +57,20 @@ class LlamaConfig:
         return cls(hidden_size=8192, intermediate_size=28672, num_hidden_layers=80, num_attention_heads=64,
                    num_key_value_heads=8, max_position_embeddings=131072)
 
+    llama3_3_70b_instruct = llama3_70b
+
+    @classmethod
+    def llama2_7b(cls) -> "LlamaConfig":
+        return cls(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                   num_attention_heads=32, num_key_value_heads=32, max_position_embeddings=4096, rope_theta=10000.0)
+
+    @classmethod
+    def prosparse_7b(cls) -> "LlamaConfig":
+        """Llama-2-7B shape with ``fatrelu(gate, 0.01) * up`` in the MLP (config.rs:85-90)."""
+        c = cls.llama2_7b()
+        c.hidden_act, c.hidden_act_param = "fatrelu", 0.01
+        return c
+
     @classmethod
     def tiny(cls) -> "LlamaConfig":
         """The CPU plumbing config: 4 layers, d 256, 4 q / 2 kv heads of 64, FFN 688, vocab 4096."""
@@ -69,7 +84,16 @@ class LlamaConfig:
         if isinstance(cfg, str):
             with open(cfg) as f:
                 cfg = json.load(f)
-        known = {k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg}
+        known = {k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg and cfg[k] is not None}
+        if "num_key_value_heads" not in known and "num_attention_heads" in known:
+            known["num_key_value_heads"] = known["num_attention_heads"]      # plain multi-head attention
+        act = known.get("hidden_act", "silu")
+        act = "silu" if act == "swish" else act
+        if act not in ("silu", "relu", "gelu", "fatrelu"):
+            raise ValueError("LlamaConfig: unsupported hidden_act %r" % (act,))
+        known["hidden_act"] = act
+        if act == "fatrelu":
+            known["hidden_act_param"] = float(known.get("hidden_act_param", 0.01))
         rs = known.get("rope_scaling")
         if rs:
             kind = rs.get("rope_type", rs.get("type"))
@@ -77,10 +101,30 @@ class LlamaConfig:
                                      "original_max": rs.get("original_max_position_embeddings", 8192),
                                      "low_freq_factor": rs.get("low_freq_factor", 1.0),
                                      "high_freq_factor": rs.get("high_freq_factor", 4.0)}
-        return cls(**known)
+        out = cls(**known)
+        out.validate()
+        return out
 
     def to_dict(self) -> dict:
         return asdict(self)
+
+    def kv_group_size(self) -> int:
+        return self.num_attention_heads // self.num_key_value_heads
+
+    def validate(self) -> None:
+        """The reference's checks (config.rs:160-215): positive sizes, heads divide the hidden
+        size (when no explicit head_dim is given they must), KV heads divide the query heads."""
+        for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                  "num_key_value_heads", "max_position_embeddings", "head_dim"):
+            if int(getattr(self, k)) <= 0:
+                raise ValueError("LlamaConfig: %s must be positive" % k)
+        if self.num_attention_heads % self.num_key_value_heads:
+            raise ValueError("LlamaConfig: num_attention_heads (%d) must be divisible by num_key_value_heads (%d)"
+                             % (self.num_attention_heads, self.num_key_value_heads))
+        if self.head_dim % 2:
+            raise ValueError("LlamaConfig: head_dim (%d) must be even for rotary embeddings" % self.head_dim)
+        if not (self.rms_norm_eps > 0 and self.rope_theta > 0):
+            raise ValueError("LlamaConfig: rms_norm_eps and rope_theta must be positive")
 
     def num_parameters(self) -> int:
         h, f, v, L = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
@@ -97,7 +141,8 @@ class LlamaDecoderLayer(nn.Module):
         self.self_attn = GQAAttention(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
                                       cfg.head_dim, rope, bias=cfg.attention_bias)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
-        self.mlp = SwiGLU(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, bias=cfg.mlp_bias)
+        self.mlp = SwiGLU(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act, bias=cfg.mlp_bias,
+                          activation_param=cfg.hidden_act_param)
 
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None, *, cache: KVCache | None = None,
                 positions: torch.Tensor | None = None):

@@ -39,7 +39,7 @@ class TPLlamaBlock(nn.Module):
         self.hq, self.hkv, self.d = cfg.num_attention_heads // W, cfg.num_key_value_heads // W, cfg.head_dim
         self.i_loc = cfg.intermediate_size // W
         H = cfg.hidden_size
-        self.rope, self.act = rope, cfg.hidden_act
+        self.rope, self.act, self.act_param = rope, cfg.hidden_act, cfg.hidden_act_param
         self.input_layernorm = RMSNorm(H, cfg.rms_norm_eps).to(device=device, dtype=torch.bfloat16)
         self.post_attention_layernorm = RMSNorm(H, cfg.rms_norm_eps).to(device=device, dtype=torch.bfloat16)
         self.qkv_proj = ColumnParallelLinear(H, (self.hq + 2 * self.hkv) * self.d, tp, SLOTS_QKV, device=device)
@@ -56,7 +56,7 @@ class TPLlamaBlock(nn.Module):
                              interleaved=self.rope.interleaved)
         x_rows = self.o_proj(a.view(M, self.hq * self.d), M, x_rows)
         h = self.post_attention_layernorm(x_rows)
-        act = F.swiglu(self.gate_up_proj(h, M), self.act)
+        act = F.swiglu(self.gate_up_proj(h, M), self.act, self.act_param)
         return self.down_proj(act, M, x_rows)
 
 

@@ -88,14 +88,15 @@ class SwiGLU(nn.Module):
     """Gated MLP with one fused ``[gate | up]`` projection (2F x H) so that the activation kernel
     reads one GEMM output."""
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False,
+                 activation_param: float | None = None):
         super().__init__()
         self.gate_up_proj = Linear(hidden_size, 2 * intermediate_size, bias=bias)
         self.down_proj = Linear(intermediate_size, hidden_size, bias=bias)
-        self.activation = activation
+        self.activation, self.activation_param = activation, activation_param
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(F.swiglu(self.gate_up_proj(x), self.activation))
+        return self.down_proj(F.swiglu(self.gate_up_proj(x), self.activation, self.activation_param))
 
 
 class KVCache:

@@ -352,8 +352,12 @@ class _SwiGLUFn(torch.autograd.Function):
 _ACT_ID = {"silu": 0, "relu": 1, "gelu": 2}
 
 
-def swiglu(gu: torch.Tensor, activation: str = "silu") -> torch.Tensor:
-    """``act(gate) * up`` for a packed ``[..., 2F]`` projection output."""
+def swiglu(gu: torch.Tensor, activation: str = "silu", param: float | None = None) -> torch.Tensor:
+    """``act(gate) * up`` for a packed ``[..., 2F]`` projection output.  ``"fatrelu"`` (ProSparse:
+    the gate passes where it is >= ``param``, default 0.01, else 0 -- ferrotorch-llama/src/mlp.rs:60-71)
+    runs as torch ops; silu / relu / gelu have the fused kernel."""
+    if activation == "fatrelu":
+        return ref.fatrelu_glu(gu, 0.01 if param is None else param)
     act = _ACT_ID[activation]
     if not _NATIVE or not gu.is_cuda or gu.dtype != torch.bfloat16 or (gu.shape[-1] // 2) % 8:
         return ref.swiglu(gu, act)

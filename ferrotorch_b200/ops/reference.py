@@ -117,6 +117,13 @@ def swiglu(gu: torch.Tensor, act: int = 0) -> torch.Tensor:
     return (_ACTS[act](g) * u).to(gu.dtype)
 
 
+def fatrelu_glu(gu: torch.Tensor, threshold: float = 0.01) -> torch.Tensor:
+    """``fatrelu(gate, t) * up`` with ``fatrelu(x, t) = x if x >= t else 0``
+    (ferrotorch-llama/src/mlp.rs:60-71); differentiable."""
+    g, u = gu.chunk(2, dim=-1)
+    return torch.where(g >= threshold, g, torch.zeros_like(g)) * u
+
+
 def repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
     """``[B, Hkv, S, D] -> [B, Hkv*n_rep, S, D]``; output head h reads input head h // n_rep
     (ferrotorch-gpu/src/bf16.rs:2405-2410)."""

@@ -260,3 +260,45 @@ def test_reference_checkpoint_layout_round_trip(tmp_path):
     (tmp_path / "lie.ftc").write_bytes(struct.pack("<Q", 1 << 60) + b"{}")
     with pytest.raises(ValueError, match="claims"):
         S.load_checkpoint(str(tmp_path / "lie.ftc"))
+
+
+# --------------------------------------------------------------------------- Llama configuration
+# ferrotorch-llama/src/config.rs:50-215 (presets, from_hf, validate) and mlp.rs:57-72 (activations).
+def test_llama_presets_and_from_hf_follow_the_reference():
+    from ferrotorch_b200.models.llama import LlamaConfig
+    c = LlamaConfig.llama3_8b()
+    assert (c.vocab_size, c.hidden_size, c.intermediate_size, c.num_hidden_layers, c.num_attention_heads,
+            c.num_key_value_heads, c.rope_theta, c.max_position_embeddings, c.tie_word_embeddings) == \
+        (128256, 4096, 14336, 32, 32, 8, 500000.0, 8192, False)
+    c = LlamaConfig.llama3_3_70b_instruct()
+    assert (c.hidden_size, c.intermediate_size, c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads,
+            c.max_position_embeddings, c.head_dim, c.kv_group_size()) == (8192, 28672, 80, 64, 8, 131072, 128, 8)
+    c = LlamaConfig.llama2_7b()
+    assert (c.vocab_size, c.intermediate_size, c.num_key_value_heads, c.rope_theta, c.max_position_embeddings) == \
+        (32000, 11008, 32, 10000.0, 4096)
+    p = LlamaConfig.prosparse_7b()
+    assert p.hidden_act == "fatrelu" and p.hidden_act_param == 0.01 and p.intermediate_size == 11008
+    base = {"vocab_size": 100, "hidden_size": 64, "intermediate_size": 96, "num_hidden_layers": 2,
+            "num_attention_heads": 4}
+    assert LlamaConfig.from_hf(dict(base)).num_key_value_heads == 4          # absent -> multi-head
+    assert LlamaConfig.from_hf(dict(base, hidden_act="swish")).hidden_act == "silu"
+    assert LlamaConfig.from_hf(dict(base, hidden_act="fatrelu")).hidden_act_param == 0.01
+    assert LlamaConfig.from_hf(dict(base, hidden_act="fatrelu", hidden_act_param=0.05)).hidden_act_param == 0.05
+    for bad in (dict(base, hidden_act="tanh"), dict(base, num_key_value_heads=3), dict(base, vocab_size=0)):
+        with pytest.raises(ValueError):
+            LlamaConfig.from_hf(bad)
+
+
+def test_fatrelu_gate_matches_its_definition_and_trains():
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.ops import functional as F
+    gu = torch.tensor([[0.005, 0.01, -1.0, 2.0, 3.0, 3.0, 3.0, 3.0]])
+    assert torch.allclose(F.swiglu(gu, "fatrelu", 0.01), torch.tensor([[0.0, 0.03, 0.0, 6.0]]), atol=1e-7)
+    assert F.swiglu(gu, "fatrelu").tolist() == F.swiglu(gu, "fatrelu", 0.01).tolist()
+    cfg = LlamaConfig.from_hf({"vocab_size": 64, "hidden_size": 32, "intermediate_size": 48, "num_hidden_layers": 1,
+                               "num_attention_heads": 2, "hidden_act": "fatrelu"})
+    m = LlamaForCausalLM(cfg)
+    ids = torch.randint(0, 64, (2, 6))
+    m(ids).float().logsumexp(-1).sum().backward()
+    g = m.model.layers[0].mlp.gate_up_proj.weight.grad
+    assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
