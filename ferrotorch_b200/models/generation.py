@@ -25,6 +25,35 @@ class GenerationConfig:
     do_sample: bool = False
     eos_token_id: int | None = None
     seed: int | None = None
+    eos_token_ids: tuple = ()          # any of these ends a sequence (generation.rs:39-41)
+
+    # named constructors of the reference (generation.rs:65-92)
+    @classmethod
+    def greedy(cls, max_new_tokens: int) -> "GenerationConfig":
+        return cls(max_new_tokens=max_new_tokens, temperature=0.0)
+
+    @classmethod
+    def sampling(cls, max_new_tokens: int, temperature: float) -> "GenerationConfig":
+        return cls(max_new_tokens=max_new_tokens, temperature=temperature, do_sample=temperature > 0)
+
+    @classmethod
+    def nucleus(cls, max_new_tokens: int, top_p: float, temperature: float) -> "GenerationConfig":
+        return cls(max_new_tokens=max_new_tokens, temperature=temperature, top_p=top_p, do_sample=temperature > 0)
+
+    def stop_ids(self) -> list[int]:
+        ids = list(self.eos_token_ids)
+        if self.eos_token_id is not None and self.eos_token_id not in ids:
+            ids.append(self.eos_token_id)
+        return ids
+
+    def validate(self) -> None:
+        """The argument checks of generation.rs:108-135."""
+        if self.temperature < 0.0:
+            raise ValueError("generate: temperature must be >= 0, got %r" % (self.temperature,))
+        if not 0.0 <= self.top_p <= 1.0:
+            raise ValueError("generate: top_p must be in [0, 1], got %r" % (self.top_p,))
+        if self.repetition_penalty <= 0.0:
+            raise ValueError("generate: repetition_penalty must be > 0, got %r" % (self.repetition_penalty,))
 
 
 def apply_repetition_penalty(logits: torch.Tensor, prev_tokens: torch.Tensor, penalty: float) -> torch.Tensor:
@@ -71,8 +100,13 @@ def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None
     :class:`GrammarLogitsProcessor` for grammar-constrained decoding
     (ferrotorch-llama/src/grammar_decode.rs masks the logits the same way)."""
     cfg = cfg or GenerationConfig()
+    cfg.validate()
+    if input_ids.dim() != 2 or input_ids.shape[1] == 0:
+        raise ValueError("generate: input_ids must be [B, S] with S >= 1")
     B, S = input_ids.shape
     dev = input_ids.device
+    stops = cfg.stop_ids()
+    stop_t = torch.tensor(stops, device=dev, dtype=input_ids.dtype) if stops else None
     gen = None
     if cfg.seed is not None:
         gen = torch.Generator(device=dev).manual_seed(cfg.seed)
@@ -84,13 +118,13 @@ def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None
         if logits_processor is not None:
             logits = logits_processor(out[:, S:], logits.float())
         tok = sample_next(logits, cfg, out, gen)
-        if cfg.eos_token_id is not None:
-            tok = torch.where(done, torch.full_like(tok, cfg.eos_token_id), tok)
-            done |= tok == cfg.eos_token_id
+        if stop_t is not None:
+            tok = torch.where(done, torch.full_like(tok, stops[0]), tok)   # finished rows are padded with a stop id
+            done |= (tok[:, None] == stop_t[None]).any(-1)
         out = torch.cat([out, tok[:, None]], dim=1)
-        if streamer is not None:
-            streamer(tok)
-        if cfg.eos_token_id is not None and bool(done.all()):
+        if streamer is not None and streamer(tok) is False:     # a streamer that returns False stops the run
+            break
+        if stop_t is not None and bool(done.all()):
             break
         logits = model(tok[:, None], caches=caches, last_token_only=True)[:, -1]
     return out

@@ -302,3 +302,33 @@ def test_fatrelu_gate_matches_its_definition_and_trains():
     m(ids).float().logsumexp(-1).sum().backward()
     g = m.model.layers[0].mlp.gate_up_proj.weight.grad
     assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
+
+
+# ferrotorch-llama/src/generation.rs:20-228: config constructors, argument checks, stop rules
+def test_generation_config_constructors_checks_and_stop_rules():
+    from ferrotorch_b200.models.generation import GenerationConfig, generate
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    g = GenerationConfig.greedy(5)
+    assert (g.max_new_tokens, g.temperature, g.top_k, g.top_p, g.repetition_penalty) == (5, 0.0, 0, 1.0, 1.0)
+    n = GenerationConfig.nucleus(7, 0.9, 0.8)
+    assert (n.top_p, n.temperature, n.do_sample) == (0.9, 0.8, True)
+    assert GenerationConfig.sampling(3, 0.0).do_sample is False
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(LlamaConfig(vocab_size=32, hidden_size=32, intermediate_size=48, num_hidden_layers=1,
+                                     num_attention_heads=2, num_key_value_heads=1)).eval()
+    ids = torch.randint(0, 32, (2, 4))
+    for bad in (GenerationConfig(temperature=-1.0), GenerationConfig(top_p=1.5), GenerationConfig(repetition_penalty=0.0)):
+        with pytest.raises(ValueError):
+            generate(m, ids, bad)
+    with pytest.raises(ValueError):
+        generate(m, ids[:, :0], g)
+    full = generate(m, ids, GenerationConfig.greedy(6))
+    assert full.shape == (2, 10)
+    # any id of eos_token_ids ends a row; the run stops when every row has ended
+    first = full[:, 4].tolist()
+    out = generate(m, ids, GenerationConfig(max_new_tokens=6, temperature=0.0, eos_token_ids=tuple(set(first))))
+    assert out.shape == (2, 5)
+    # a streamer that returns False stops after that token
+    seen = []
+    out = generate(m, ids, GenerationConfig.greedy(6), streamer=lambda t: (seen.append(t.tolist()), len(seen) < 2)[1])
+    assert out.shape == (2, 6) and len(seen) == 2 and torch.equal(out, full[:, :6])
