@@ -50,19 +50,89 @@ def apply_chat_template(messages: list[dict], template: str = "llama3", add_gene
 # --------------------------------------------------------------------------- hub (offline)
 @dataclass
 class HfTransformerConfig:
-    model_type: str = "llama"
+    """The fields of a Hugging Face ``config.json`` that a decoder-only transformer needs
+    (ferrotorch-hub/src/hf_config.rs:60-120), with the same defaults: ``rms_norm_eps`` 1e-6,
+    ``rope_theta`` 10000, ``hidden_act`` "silu", untied embeddings.  ``raw`` keeps everything."""
+    hidden_size: int = 0
+    num_hidden_layers: int = 0
+    num_attention_heads: int = 0
+    num_key_value_heads_: int | None = None
+    intermediate_size: int = 0
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 0
+    vocab_size: int = 0
+    tie_word_embeddings: bool = False
+    hidden_act: str = "silu"
+    hidden_act_param: float | None = None
+    torch_dtype: str | None = None
+    architectures: list = field(default_factory=list)
+    rope_scaling: dict | None = None
+    model_type: str | None = None
     raw: dict = field(default_factory=dict)
+
+    _REQUIRED = ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size",
+                 "max_position_embeddings", "vocab_size")
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "HfTransformerConfig":
+        missing = [k for k in cls._REQUIRED if k not in raw]
+        if missing:
+            raise ValueError("failed to parse HF config JSON: missing field(s) %s" % ", ".join(missing))
+        kw = {k: raw[k] for k in ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size",
+                                  "rms_norm_eps", "rope_theta", "max_position_embeddings", "vocab_size",
+                                  "tie_word_embeddings", "hidden_act", "hidden_act_param", "torch_dtype",
+                                  "architectures", "rope_scaling", "model_type") if raw.get(k) is not None}
+        return cls(num_key_value_heads_=raw.get("num_key_value_heads"), raw=dict(raw), **kw)
+
+    @classmethod
+    def from_json_str(cls, s: str) -> "HfTransformerConfig":
+        try:
+            raw = json.loads(s)
+        except ValueError as e:
+            raise ValueError("failed to parse HF config JSON: %s" % e)
+        if not isinstance(raw, dict):
+            raise ValueError("failed to parse HF config JSON: not an object")
+        return cls.from_dict(raw)
 
     @classmethod
     def from_file(cls, path: str) -> "HfTransformerConfig":
-        with open(path) as f:
-            raw = json.load(f)
-        return cls(raw.get("model_type", "unknown"), raw)
+        with open(path, encoding="utf-8") as f:
+            return cls.from_json_str(f.read())
+
+    def num_key_value_heads(self) -> int:
+        return self.num_key_value_heads_ if self.num_key_value_heads_ is not None else self.num_attention_heads
+
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    def is_gqa(self) -> bool:
+        return self.num_key_value_heads() < self.num_attention_heads
+
+    def validate(self) -> None:
+        if min(self.hidden_size, self.num_attention_heads, self.num_hidden_layers, self.intermediate_size,
+               self.vocab_size) <= 0:
+            raise ValueError("HfTransformerConfig: hidden_size / num_attention_heads / num_hidden_layers / "
+                             "intermediate_size / vocab_size must all be positive")
+        if self.hidden_size % self.num_attention_heads:
+            raise ValueError("HfTransformerConfig: hidden_size (%d) must be divisible by num_attention_heads (%d)"
+                             % (self.hidden_size, self.num_attention_heads))
+        kv = self.num_key_value_heads()
+        if kv <= 0 or self.num_attention_heads % kv:
+            raise ValueError("HfTransformerConfig: num_attention_heads (%d) must be divisible by a positive "
+                             "num_key_value_heads (%d)" % (self.num_attention_heads, kv))
+        if self.hidden_act not in ("silu", "swish", "gelu", "gelu_new", "relu", "fatrelu"):
+            raise ValueError("HfTransformerConfig: unsupported hidden_act %r (supported: silu, swish, gelu, "
+                             "gelu_new, relu, fatrelu)" % (self.hidden_act,))
 
     def to_llama(self):
         from ..models.llama import LlamaConfig
 
-        return LlamaConfig.from_hf(self.raw)
+        self.validate()
+        raw = dict(self.raw)
+        raw.setdefault("rms_norm_eps", self.rms_norm_eps)
+        raw.setdefault("rope_theta", self.rope_theta)
+        return LlamaConfig.from_hf(raw)
 
 
 def hf_cache_path(repo_id: str) -> str:

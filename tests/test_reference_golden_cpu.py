@@ -332,3 +332,41 @@ def test_generation_config_constructors_checks_and_stop_rules():
     seen = []
     out = generate(m, ids, GenerationConfig.greedy(6), streamer=lambda t: (seen.append(t.tolist()), len(seen) < 2)[1])
     assert out.shape == (2, 6) and len(seen) == 2 and torch.equal(out, full[:, :6])
+
+
+# ferrotorch-hub/src/hf_config.rs: the Llama-3-8B config.json of its tests, defaults, validation
+_LLAMA3_8B_JSON = """{
+  "architectures": ["LlamaForCausalLM"], "attention_bias": false, "attention_dropout": 0.0,
+  "bos_token_id": 128000, "eos_token_id": 128001, "hidden_act": "silu", "hidden_size": 4096,
+  "initializer_range": 0.02, "intermediate_size": 14336, "max_position_embeddings": 8192,
+  "model_type": "llama", "num_attention_heads": 32, "num_hidden_layers": 32, "num_key_value_heads": 8,
+  "pretraining_tp": 1, "rms_norm_eps": 1e-05, "rope_scaling": null, "rope_theta": 500000.0,
+  "tie_word_embeddings": false, "torch_dtype": "bfloat16", "transformers_version": "4.40.0.dev0",
+  "use_cache": true, "vocab_size": 128256}"""
+
+
+def test_hf_transformer_config_parses_and_validates():
+    from ferrotorch_b200.models.llama import LlamaConfig
+    from ferrotorch_b200.utils.text import HfTransformerConfig
+    c = HfTransformerConfig.from_json_str(_LLAMA3_8B_JSON)
+    assert (c.hidden_size, c.num_hidden_layers, c.num_attention_heads, c.num_key_value_heads(), c.intermediate_size,
+            c.max_position_embeddings, c.vocab_size, c.tie_word_embeddings, c.hidden_act, c.torch_dtype,
+            c.architectures, c.model_type) == (4096, 32, 32, 8, 14336, 8192, 128256, False, "silu", "bfloat16",
+                                               ["LlamaForCausalLM"], "llama")
+    assert abs(c.rms_norm_eps - 1e-5) < 1e-12 and c.rope_theta == 500000.0 and c.head_dim() == 128 and c.is_gqa()
+    assert c.to_llama() == LlamaConfig.llama3_8b()
+    small = {"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4, "intermediate_size": 128,
+             "max_position_embeddings": 256, "vocab_size": 100}
+    d = HfTransformerConfig.from_dict(small)
+    assert (d.rms_norm_eps, d.rope_theta, d.hidden_act, d.num_key_value_heads(), d.is_gqa()) == \
+        (1e-6, 10000.0, "silu", 4, False)
+    ll = d.to_llama()
+    assert (ll.rms_norm_eps, ll.rope_theta) == (1e-6, 10000.0)
+    with pytest.raises(ValueError, match="missing"):
+        HfTransformerConfig.from_dict({k: v for k, v in small.items() if k != "vocab_size"})
+    with pytest.raises(ValueError, match="parse"):
+        HfTransformerConfig.from_json_str("{not json")
+    for bad in (dict(small, hidden_size=66), dict(small, num_key_value_heads=3), dict(small, hidden_act="mish"),
+                dict(small, vocab_size=0)):
+        with pytest.raises(ValueError):
+            HfTransformerConfig.from_dict(bad).validate()
