@@ -8,7 +8,8 @@
 * ``JsonGrammar`` + ``token_mask`` / ``apply_token_mask``: a JSON prefix validator drives a per-step
   mask over the vocabulary so that generation can only produce valid JSON
   (ferrotorch-grammar/src/state.rs; the mask is applied on the logits' device like the
-  reference's ``compute_mask_gpu`` / ``kernel_apply_token_mask``).
+  reference's ``compute_mask_gpu`` / ``kernel_apply_token_mask``).  Decoding under a JSON *schema*
+  (``JsonSchemaProcessor``, ``TokenMask``, ``TokenTransitionCache``) lives in ``utils.grammar``.
 """
 from __future__ import annotations
 

@@ -1,0 +1,168 @@
+"""JSON-Schema-constrained decoding: schema subset, character matcher, token masks, generate hook.
+Behaviours follow ferrotorch-grammar (schema.rs, state.rs, json_schema.rs)."""
+import json
+
+import pytest
+import torch
+
+from ferrotorch_b200.utils import grammar as G
+
+PERSON = {"type": "object",
+          "properties": {"name": {"type": "string", "minLength": 1, "maxLength": 5},
+                         "age": {"type": "integer", "minimum": 0, "maximum": 150},
+                         "tags": {"type": "array", "items": {"enum": ["a", "ab", 1, 12]}, "maxItems": 3},
+                         "x": {"type": ["number", "null"]}, "ok": {"type": "boolean"}},
+          "required": ["name", "age"]}
+
+
+@pytest.mark.parametrize("text,want", [
+    ('{"name":"bob","age":42}', True), ('{"age":42,"name":"bob"}', True),      # any key order
+    ('{"name":"","age":1}', False), ('{"name":"toolong","age":1}', False),      # minLength / maxLength
+    ('{"name":"b","age":151}', False), ('{"name":"b","age":-1}', False),        # maximum / minimum
+    ('{"name":"b","age":150,"tags":["a","ab",12]}', True),                      # enum with shared prefixes
+    ('{"name":"b","age":15,"tags":[1,1,1,1]}', False),                          # maxItems
+    ('{"name":"b","age":1,"x":null,"ok":false}', True), ('{"name":"b","age":1,"x":-1.5e3}', True),
+    ('{"name":"b"}', False),                                                    # required
+    ('{"name":"b","age":1,"age":2}', False),                                    # a key only once
+    ('{"name":"b","age":01}', False),                                           # no leading zeros
+    ('{"name":"b\\u00e9\\n","age":7}', True), ('{"name":"b\\x","age":7}', False),   # escapes
+    ('{"name":"b","age":1,"zz":1}', False),                                     # only listed properties
+    ('{"name":"b","age":1.0}', False), ('{"name":"b","age":1e2}', False),       # integers are plain digits
+    ('{ "name" : "b" ,\n "age" : 1 }', True),
+])
+def test_matcher_against_hand_checked_texts(text, want):
+    assert G.validate(PERSON, text) is want
+    if want:                                       # every accepted text is real JSON
+        json.loads(text)
+
+
+def test_whitespace_is_opt_in_and_next_chars():
+    assert not G.validate(PERSON, '{ "name":"b","age":1}', whitespace_permissive=False)
+    g = G.SchemaGrammar(PERSON)
+    assert g.valid_next_chars() == ["{"] and not g.is_whitespace_permissive()
+    g.step_text('{"')
+    assert g.valid_next_chars() == ["a", "n", "o", "t", "x"]          # first letters of the five names
+    g.step_text('age":1')
+    assert "}" not in g.valid_next_chars() and "," in g.valid_next_chars()   # "name" is still owed
+    with pytest.raises(G.GrammarError):
+        g.step_char("}")
+    g.step_text(',"name":"z"}')
+    assert g.is_complete() and g.valid_next_chars() == []
+    assert g.with_whitespace_permissive(True).is_whitespace_permissive()
+
+
+def test_number_forms_and_constraints():
+    num = {"type": "number"}
+    for t, w in [("0", True), ("-0.5", True), ("1e5", True), ("-3.14E+2", True), ("0.5e-10", True), ("01", False),
+                 ("1.", False), (".5", False), ("-", False), ("1e", False), ("+1", False), ("1e+", False)]:
+        assert G.validate(num, t) is w, t
+    assert G.validate({"type": "number", "multipleOf": 0.5}, "2.5") and not G.validate({"type": "number", "multipleOf": 0.5}, "2.4")
+    assert G.validate({"type": "integer", "multipleOf": 3}, "12") and not G.validate({"type": "integer", "multipleOf": 3}, "13")
+    g = G.SchemaGrammar({"type": "integer", "minimum": 5, "maximum": 99})
+    g.step_text("12")
+    assert g.is_complete() and g.valid_next_chars() == []             # a third digit cannot meet the bound
+    g = G.SchemaGrammar({"type": "integer", "minimum": 0, "maximum": 150})
+    g.step_text("15")
+    assert g.valid_next_chars() == ["0"]                              # 151..159 could never be completed
+    g = G.SchemaGrammar({"type": "integer", "minimum": -20, "maximum": -5})
+    assert g.valid_next_chars() == ["-"]
+    g.step_text("-")
+    assert g.valid_next_chars() == ["1", "2", "5", "6", "7", "8", "9"]
+    assert not G.SchemaGrammar({"type": "integer", "minimum": 1}).accepts("-")
+
+
+def test_overlapping_alternatives_stay_alive():
+    """Both branches start with a digit; the text decides later (the reference would commit to
+    the first branch, schema.rs:33-41)."""
+    s = {"oneOf": [{"type": "integer", "maximum": 5}, {"type": "number", "minimum": 2.5}]}
+    assert G.validate(s, "3") and G.validate(s, "2.75") and G.validate(s, "7") and not G.validate(s, "2.25")
+    s = {"anyOf": [{"type": "string", "maxLength": 2}, {"enum": ["hello"]}, {"type": "null"}]}
+    assert G.validate(s, '"hi"') and G.validate(s, '"hello"') and G.validate(s, "null") and not G.validate(s, '"hey"')
+
+
+def test_schema_subset_and_errors():
+    s = {"type": "object", "properties": {"p": {"$ref": "#/$defs/point"}, "q": {"$ref": "#/definitions/flag"}},
+         "required": ["p"], "$defs": {"point": {"type": "array", "items": {"type": "number"}, "minItems": 2, "maxItems": 2}},
+         "definitions": {"flag": {"const": True}}, "title": "ignored", "additionalProperties": True}
+    assert G.validate(s, '{"p":[1,2.5],"q":true}') and not G.validate(s, '{"p":[1]}') and not G.validate(s, '{"p":[1,2],"q":false}')
+    for bad, msg in [({"allOf": [{"type": "string"}]}, "allOf"), ({"type": "string", "pattern": "a+"}, "pattern"),
+                     ({"$ref": "#/$defs/a", "$defs": {"a": {"type": "array", "items": {"$ref": "#/$defs/a"}}}}, "recursive"),
+                     ({"$ref": "http://x/y"}, "inside the document"), ({"$ref": "#/$defs/nope"}, "unresolvable"),
+                     ({"type": "object", "properties": {}, "required": ["a"]}, "not declared"), ({"type": "tuple"}, "unsupported type"),
+                     ({}, "without a type"), ({"enum": []}, "non-empty"), ({"type": "string", "minLength": 3, "maxLength": 1}, "maxLength"),
+                     ({"type": "array"}, "needs items"), ("{oops", "not valid JSON")]:
+        with pytest.raises(G.SchemaError, match=msg):
+            G.Schema.from_json_schema(bad)
+    assert isinstance(G.SchemaError("x"), ValueError)
+
+
+VOCAB = ["<eos>", "{", "}", '"', ":", ",", "name", "age", '{"', '":', '","', "bob", "42", "4", "2", '"name"', '"age":',
+         '":"', " ", "x", "na", "me", "ag", "e", "1500", "", '"}', "}x", "[", "]"]
+SMALL = {"type": "object", "properties": {"name": {"type": "string", "maxLength": 8},
+                                          "age": {"type": "integer", "minimum": 0, "maximum": 150}},
+         "required": ["name", "age"]}
+
+
+def test_token_masks_follow_the_characters():
+    p = G.JsonSchemaProcessor(SMALL, VOCAB, eos_token_id=0)
+    assert p.vocab_len() == len(VOCAB) and not p.is_complete()
+    m = p.compute_mask()
+    assert sorted(VOCAB[i] for i in m.allowed_ids()) == ["{", '{"'] and m.num_allowed() == 2
+    assert m.packed().tolist() == [(1 << 1) | (1 << 8)]                # 32 ids per word, bit i = id i
+    assert not m.is_allowed(0) and not m.is_allowed(VOCAB.index("")) and not m.is_allowed(10 ** 6)
+    for piece in ['{"', "na", "me", '":"', "bob", '","', "age", '":', "4", "2"]:
+        i = VOCAB.index(piece)
+        assert p.compute_mask().is_allowed(i), piece
+        p.step_token(i)
+    m = p.compute_mask()
+    assert not m.is_allowed(VOCAB.index("1500")) and not m.is_allowed(VOCAB.index("}x")) and m.is_allowed(VOCAB.index("}"))
+    with pytest.raises(G.GrammarError):
+        p.step_token(0)                                                # no end of sequence inside the object
+    with pytest.raises(G.GrammarError):
+        p.step_token(VOCAB.index("x"))
+    p.step_token(VOCAB.index("}"))
+    assert p.is_complete() and p.compute_mask().allowed_ids() == [0]
+    p.step_token(0)
+    logits = torch.zeros(2, len(VOCAB))
+    out = p.compute_mask().apply(logits)
+    assert out[0, 0] == 0 and torch.isinf(out[:, 1:]).all()
+    assert G.TokenMask.allow_all(40).num_allowed() == 40 and G.TokenMask.allow_all(40).packed().tolist() == [-1, 255]
+
+
+def test_mask_cache_counts_hits_by_state():
+    p = G.JsonSchemaProcessor({"type": "array", "items": {"type": "string"}}, VOCAB, eos_token_id=0)
+    cache = G.TokenTransitionCache()
+    assert cache.is_empty()
+    for t in ["[", '"', "bob", "x"]:
+        p.compute_mask_cached(cache)
+        p.step_token(VOCAB.index(t))
+    p.compute_mask_cached(cache)          # still inside an unbounded string: same state as one step ago
+    assert (cache.hits(), cache.misses(), len(cache)) == (2, 3, 3)
+    a, b = p.compute_mask_cached(cache), p.compute_mask()
+    assert torch.equal(a.bits, b.bits)
+    cache.reset_counters()
+    cache.clear()
+    assert cache.hits() == 0 and cache.is_empty()
+
+
+def test_generate_under_a_schema_yields_valid_json():
+    from ferrotorch_b200.models.generation import GenerationConfig, generate
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    pieces = ["<eos>"] + list('{}[]":,-.0123456789abcdefghijklmnopqrstuvwxyz ') + ['"name"', '"age"', "true", "false", "null", '":', '{"']
+    torch.manual_seed(1)
+    m = LlamaForCausalLM(LlamaConfig(vocab_size=len(pieces), hidden_size=32, intermediate_size=48, num_hidden_layers=1,
+                                     num_attention_heads=2, num_key_value_heads=1)).eval()
+    proc = G.SchemaLogitsProcessor(SMALL, pieces, eos_token_id=0)
+    ids = torch.randint(1, len(pieces), (3, 4))
+    cfg = GenerationConfig(max_new_tokens=80, temperature=1.0, do_sample=True, seed=3, eos_token_id=0)
+    out = generate(m, ids, cfg, logits_processor=proc)
+    done = 0
+    for row in out[:, 4:].tolist():
+        text = "".join(pieces[t] for t in row if t != 0)
+        if 0 in row:                                  # finished rows are complete, valid values
+            v = json.loads(text)
+            assert set(v) == {"name", "age"} and 0 <= v["age"] <= 150 and len(v["name"]) <= 8
+            done += 1
+        else:                                         # the others are valid prefixes
+            assert G.SchemaGrammar(SMALL).accepts(text)
+    assert done >= 1 and proc.cache.hits() > 0
