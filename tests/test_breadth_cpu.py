@@ -333,3 +333,41 @@ def test_dist_checkpoint_uneven_reshard_and_reference_layout(tmp_path):
         dc.load_distributed(str(ref), 0, 4)
     with pytest.raises(ValueError):
         dc.load_distributed(str(ref), 4, 4)
+
+
+def test_ml_bridge_covers_the_reference_surface():
+    """Every public function of ferrotorch-ml (metrics.rs, datasets.rs, adapter.rs) exists here and
+    a few agree with values worked out by hand."""
+    names = """accuracy_score adjusted_mutual_info_score adjusted_rand_score array1_to_tensor array1_usize_to_tensor
+    array2_to_tensor average_precision_score balanced_accuracy_score brier_score_loss calinski_harabasz_score
+    cohen_kappa_score completeness_score confusion_matrix coverage_error d2_brier_score davies_bouldin_score dcg_score
+    explained_variance_score f1_score fowlkes_mallows_score hamming_loss homogeneity_score
+    label_ranking_average_precision_score label_ranking_loss load_breast_cancer load_iris load_wine log_loss make_blobs
+    make_circles make_classification make_moons make_regression matthews_corrcoef max_error mean_absolute_error
+    mean_absolute_percentage_error mean_squared_error median_absolute_error ndcg_score normalized_mutual_info_score
+    precision_score r2_score recall_score roc_auc_score root_mean_squared_error silhouette_score tensor_to_array1
+    tensor_to_array1_usize tensor_to_array2 top_k_accuracy_score v_measure_score zero_one_loss""".split()
+    assert all(callable(getattr(ml, n)) for n in names)
+    yt, yp = torch.tensor([0, 1, 2, 2, 1, 0]), torch.tensor([0, 2, 2, 2, 1, 1])
+    assert ml.zero_one_loss(yt, yp) == pytest.approx(2 / 6) and ml.hamming_loss(yt, yp) == pytest.approx(2 / 6)
+    assert ml.f1_score(yt, yp, average="macro") == pytest.approx(ml.precision_recall_f1(yt, yp)[2])
+    assert ml.balanced_accuracy_score(yt, yp) == pytest.approx((0.5 + 0.5 + 1.0) / 3)
+    a, b = torch.tensor([1.0, 2.0, 3.0]), torch.tensor([1.0, 2.0, 5.0])
+    assert ml.max_error(a, b) == 2.0 and ml.root_mean_squared_error(a, b) == pytest.approx((4 / 3) ** 0.5)
+    assert ml.median_absolute_error(a, b) == 0.0 and ml.mean_absolute_percentage_error(a, b) == pytest.approx(2 / 9)
+    assert ml.adjusted_rand_score(yt, yt) == 1.0 and ml.v_measure_score(yt, yt) == pytest.approx(1.0)
+    y, pr = torch.tensor([0, 1, 1, 0]), torch.tensor([0.1, 0.9, 0.8, 0.3])
+    assert ml.brier_score_loss(y, pr) == pytest.approx(0.0375) and ml.d2_brier_score(y, pr) == pytest.approx(0.85)
+    assert ml.average_precision_score(y, pr) == 1.0
+    with pytest.raises(ValueError):
+        ml.f1_score(torch.tensor([0.5, 1.0]), torch.tensor([0, 1]))          # labels must be integral
+    with pytest.raises(ValueError):
+        ml.tensor_to_array2(torch.zeros(3))
+    x, t = ml.load_iris()
+    assert x.shape == (150, 4) and t.unique().tolist() == [0.0, 1.0, 2.0] and ml.silhouette_score(x, t) > 0.4
+    assert ml.load_wine()[0].shape == (178, 13) and ml.load_breast_cancer()[0].shape == (569, 30)
+    X, Y = ml.make_moons(40, noise=0.1, seed=0)
+    X2, _ = ml.make_moons(40, noise=0.1, seed=0)
+    assert X.shape == (40, 2) and torch.equal(X, X2) and Y.unique().tolist() == [0.0, 1.0]
+    assert ml.make_regression(20, 5, 3, seed=1)[0].shape == (20, 5) and ml.make_classification(30, 8, seed=1)[1].shape == (30,)
+    assert ml.make_blobs(30, centers=4, seed=2)[1].unique().numel() == 4 and ml.make_circles(10, seed=0)[0].shape == (10, 2)
