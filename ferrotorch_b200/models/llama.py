@@ -84,6 +84,18 @@ class LlamaConfig:
         if isinstance(cfg, str):
             with open(cfg) as f:
                 cfg = json.load(f)
+        cfg = dict(cfg)
+        rp = cfg.get("rope_parameters")
+        if isinstance(rp, dict):
+            # newer config.json files keep the rotary settings in one "rope_parameters" object
+            if "rope_theta" in rp:
+                cfg.setdefault("rope_theta", rp["rope_theta"])
+            if rp.get("rope_type", rp.get("type", "default")) != "default" and not cfg.get("rope_scaling"):
+                cfg["rope_scaling"] = rp
+        # what a config.json may leave out takes the Hugging Face defaults, not the Llama-3 preset's
+        # (ferrotorch-hub/src/hf_config.rs: rms_norm_eps 1e-6, rope_theta 10000)
+        cfg.setdefault("rope_theta", 10000.0)
+        cfg.setdefault("rms_norm_eps", 1e-6)
         known = {k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg and cfg[k] is not None}
         if "num_key_value_heads" not in known and "num_attention_heads" in known:
             known["num_key_value_heads"] = known["num_attention_heads"]      # plain multi-head attention

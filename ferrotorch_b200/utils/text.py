@@ -84,6 +84,12 @@ class HfTransformerConfig:
                                   "rms_norm_eps", "rope_theta", "max_position_embeddings", "vocab_size",
                                   "tie_word_embeddings", "hidden_act", "hidden_act_param", "torch_dtype",
                                   "architectures", "rope_scaling", "model_type") if raw.get(k) is not None}
+        rp = raw.get("rope_parameters")
+        if isinstance(rp, dict):                      # newer files: rotary settings in one object
+            if "rope_theta" not in kw and "rope_theta" in rp:
+                kw["rope_theta"] = rp["rope_theta"]
+            if "rope_scaling" not in kw and rp.get("rope_type", "default") != "default":
+                kw["rope_scaling"] = rp
         return cls(num_key_value_heads_=raw.get("num_key_value_heads"), raw=dict(raw), **kw)
 
     @classmethod
