@@ -57,3 +57,32 @@ def test_own_resnet_keys_match_torchvision():
     theirs = torchvision.models.resnet50(weights=None).state_dict()
     assert set(ours) == set(theirs)
     assert all(ours[k].shape == theirs[k].shape for k in ours)
+
+
+@pytest.mark.parametrize("name", ["resnet18", "resnet50"])
+def test_own_resnet_computes_what_torchvision_computes(name):
+    """Same weights, same input -> same logits (train and eval mode), same running statistics and
+    the same gradients: the fused BN + residual + ReLU blocks are a re-arrangement, not a new model."""
+    if not vision.HAVE_TORCHVISION:
+        pytest.skip("torchvision not installed")
+    import torchvision
+
+    torch.manual_seed(0)
+    theirs = getattr(torchvision.models, name)(weights=None)
+    ours = vision.build(name)
+    ours.load_state_dict(theirs.state_dict())
+    x = torch.randn(4, 3, 64, 64)
+    y = torch.randint(0, 1000, (4,))
+    for mode in ("train", "eval"):
+        getattr(theirs, mode)()
+        getattr(ours, mode)()
+        a, b = theirs(x), ours(x).float()
+        assert torch.allclose(a, b, atol=2e-4, rtol=1e-4), (mode, (a - b).abs().max())
+    k = "layer2.0.bn1.running_var"
+    assert torch.allclose(theirs.state_dict()[k], ours.state_dict()[k], atol=1e-5)
+    theirs.train(), ours.train()
+    torch.nn.functional.cross_entropy(theirs(x), y).backward()
+    torch.nn.functional.cross_entropy(ours(x).float(), y).backward()
+    ga, gb = dict(theirs.named_parameters()), dict(ours.named_parameters())
+    for k in ("conv1.weight", "layer1.0.bn1.weight", "layer3.1.conv2.weight", "fc.bias"):
+        assert torch.allclose(ga[k].grad, gb[k].grad, atol=5e-4, rtol=1e-3), (k, (ga[k].grad - gb[k].grad).abs().max())
