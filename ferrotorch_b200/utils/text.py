@@ -35,17 +35,102 @@ def decode(tok, ids, skip_special_tokens: bool = True) -> str:
     return tok.decode(list(ids), skip_special_tokens=skip_special_tokens)
 
 
-def apply_chat_template(messages: list[dict], template: str = "llama3", add_generation_prompt: bool = True) -> str:
-    """Render ``[{"role": ..., "content": ...}]`` with the Llama-3 or ChatML layout."""
-    if template == "llama3":
-        out = "<|begin_of_text|>"
-        for m in messages:
-            out += "<|start_header_id|>%s<|end_header_id|>\n\n%s<|eot_id|>" % (m["role"], m["content"])
-        return out + ("<|start_header_id|>assistant<|end_header_id|>\n\n" if add_generation_prompt else "")
-    if template == "chatml":
-        out = "".join("<|im_start|>%s\n%s<|im_end|>\n" % (m["role"], m["content"]) for m in messages)
-        return out + ("<|im_start|>assistant\n" if add_generation_prompt else "")
-    raise ValueError("unknown chat template %r" % template)
+def encode_batch(tok, texts: list[str], add_special_tokens: bool = True) -> list[list[int]]:
+    return [e.ids for e in tok.encode_batch(list(texts), add_special_tokens=add_special_tokens)]
+
+
+def vocab_size(tok, with_added_tokens: bool = True) -> int:
+    return tok.get_vocab_size(with_added_tokens=with_added_tokens)
+
+
+def token_to_id(tok, token: str) -> int | None:
+    return tok.token_to_id(token)
+
+
+def id_to_token(tok, idx: int) -> str | None:
+    return tok.id_to_token(idx)
+
+
+@dataclass
+class ChatMessage:
+    """One turn; ``extra`` carries whatever else a template reads (``tool_calls``, ``name`` ...)
+    and is flattened next to ``role`` / ``content`` (ferrotorch-tokenize/src/lib.rs:203-225)."""
+    role: str
+    content: str
+    extra: dict = field(default_factory=dict)
+
+    def to_dict(self) -> dict:
+        return {**self.extra, "role": self.role, "content": self.content}
+
+
+_BUILTIN_TEMPLATES = {
+    "llama3": ("{{ bos_token if bos_token else '<|begin_of_text|>' }}"
+               "{% for m in messages %}<|start_header_id|>{{ m['role'] }}<|end_header_id|>\n\n{{ m['content'] }}<|eot_id|>{% endfor %}"
+               "{% if add_generation_prompt %}<|start_header_id|>assistant<|end_header_id|>\n\n{% endif %}"),
+    "chatml": ("{% for m in messages %}<|im_start|>{{ m['role'] }}\n{{ m['content'] }}<|im_end|>\n{% endfor %}"
+               "{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}"),
+}
+
+
+def apply_chat_template(messages, template: str = "llama3", add_generation_prompt: bool = True,
+                        bos_token: str | None = None, eos_token: str | None = None) -> str:
+    """Render a conversation with a Jinja chat template, the kind ``tokenizer_config.json`` carries
+    (ferrotorch-tokenize/src/lib.rs:247-330: variables ``messages``, ``add_generation_prompt``,
+    ``bos_token``, ``eos_token``; helpers ``raise_exception(msg)`` and ``strftime_now(fmt)``).
+    ``template`` is the template text, or ``"llama3"`` / ``"chatml"`` for the two built-in layouts.
+    Messages are dicts or :class:`ChatMessage`.  Templates run in Jinja's sandbox."""
+    import datetime
+
+    import jinja2
+    from jinja2.sandbox import ImmutableSandboxedEnvironment
+
+    def raise_exception(msg):
+        raise jinja2.exceptions.TemplateError(msg)
+
+    def strftime_now(fmt):
+        return datetime.datetime.now().strftime(fmt)
+
+    env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+    env.globals.update(raise_exception=raise_exception, strftime_now=strftime_now)
+    text = _BUILTIN_TEMPLATES.get(template, template)
+    try:
+        tmpl = env.from_string(text)
+    except jinja2.exceptions.TemplateSyntaxError as e:
+        raise ValueError("invalid chat template: %s" % e)
+    msgs = [m.to_dict() if isinstance(m, ChatMessage) else dict(m) for m in messages]
+    try:
+        return tmpl.render(messages=msgs, add_generation_prompt=add_generation_prompt, bos_token=bos_token or "",
+                           eos_token=eos_token or "")
+    except jinja2.exceptions.TemplateError as e:
+        raise ValueError("chat template render failed: %s" % e)
+
+
+def apply_chat_template_to_ids(tok, template: str, messages, add_generation_prompt: bool = True,
+                               bos_token: str | None = None, eos_token: str | None = None,
+                               add_special_tokens: bool = False) -> tuple[str, list[int]]:
+    """Render, then tokenise: ``(prompt, ids)``."""
+    prompt = apply_chat_template(messages, template, add_generation_prompt, bos_token, eos_token)
+    return prompt, encode(tok, prompt, add_special_tokens)
+
+
+def load_chat_template(tokenizer_config_path: str) -> str | None:
+    """The ``chat_template`` of a ``tokenizer_config.json``: a string, or the first entry of a list
+    of ``{"name", "template"}`` objects; ``None`` when the file has none."""
+    with open(tokenizer_config_path, "rb") as f:
+        data = f.read()
+    try:
+        value = json.loads(data)
+    except ValueError as e:
+        raise ValueError("failed to parse tokenizer_config %s: %s" % (tokenizer_config_path, e))
+    t = value.get("chat_template") if isinstance(value, dict) else None
+    if t is None or isinstance(t, str):
+        return t
+    if isinstance(t, list):
+        for entry in t:
+            if isinstance(entry, dict) and isinstance(entry.get("template"), str):
+                return entry["template"]
+        return None
+    raise ValueError("tokenizer_config %s has chat_template of unexpected type" % tokenizer_config_path)
 
 
 # --------------------------------------------------------------------------- hub (offline)
