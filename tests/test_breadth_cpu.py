@@ -240,8 +240,7 @@ def test_chat_templates():
     assert t.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
     c = text.apply_chat_template(msgs, "chatml", add_generation_prompt=False)
     assert c == "<|im_start|>system\ns<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n"
-    with pytest.raises(ValueError):
-        text.apply_chat_template(msgs, "nope")
+    assert text.apply_chat_template(msgs, "{{ messages | length }} turns") == "2 turns"    # any other string is a Jinja template
 
 
 def test_tokenizer_round_trip(tmp_path):
