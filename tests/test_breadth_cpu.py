@@ -370,3 +370,45 @@ def test_ml_bridge_covers_the_reference_surface():
     assert X.shape == (40, 2) and torch.equal(X, X2) and Y.unique().tolist() == [0.0, 1.0]
     assert ml.make_regression(20, 5, 3, seed=1)[0].shape == (20, 5) and ml.make_classification(30, 8, seed=1)[1].shape == (30,)
     assert ml.make_blobs(30, centers=4, seed=2)[1].unique().numel() == 4 and ml.make_circles(10, seed=0)[0].shape == (10, 2)
+
+
+def test_lora_se_and_hooked_module():
+    import ferrotorch_b200.nn as fnn
+
+    torch.manual_seed(0)
+    base = torch.nn.Linear(6, 4)
+    lora = fnn.LoRALinear(base, rank=2, alpha=4.0)
+    x = torch.randn(3, 6)
+    assert torch.equal(lora(x), base(x))                               # B starts at zero
+    assert not base.weight.requires_grad and lora.lora_a.shape == (2, 6) and lora.lora_b.shape == (4, 2)
+    assert (lora.rank(), lora.alpha(), lora.base()) == (2, 4.0, base)
+    with torch.no_grad():
+        lora.lora_b.normal_()
+    want = lora(x)
+    assert torch.allclose(want, base(x) + 2.0 * x @ lora.lora_a.t() @ lora.lora_b.t(), atol=1e-6)
+    want.sum().backward()
+    assert lora.lora_a.grad is not None and base.weight.grad is None
+    lora.merge()
+    assert torch.allclose(lora.into_base()(x), want, atol=1e-5) and float(lora.lora_b.abs().sum()) == 0.0
+    with pytest.raises(ValueError):
+        fnn.LoRALinear(base, 0)
+    se = fnn.SqueezeExcitation(8, 2)
+    img = torch.randn(2, 8, 5, 5)
+    gate = torch.sigmoid(se.fc2(torch.relu(se.fc1(img.mean((2, 3), keepdim=True)))))
+    assert torch.allclose(se(img), img * gate, atol=1e-6) and sorted(se.state_dict()) == ["fc1.bias", "fc1.weight", "fc2.bias", "fc2.weight"]
+    with pytest.raises(ValueError):
+        fnn.SqueezeExcitation(0, 2)
+    hm = fnn.HookedModule(torch.nn.Linear(3, 3))
+    seen = []
+    h1 = hm.register_forward_pre_hook(lambda i: i * 2)
+    h2 = hm.register_forward_hook(lambda i, o: seen.append(o.shape))
+    h3 = hm.register_backward_hook(lambda g: g * 0)
+    inp = torch.ones(2, 3, requires_grad=True)
+    out = hm(inp)
+    assert torch.allclose(out, hm.inner()(torch.full((2, 3), 2.0))) and seen == [(2, 3)] and h1.id() != h2.id()
+    out.sum().backward()
+    assert float(inp.grad.abs().sum()) == 0.0                           # the backward hook replaced the gradient
+    for h in (h1, h2, h3):
+        h.remove()
+    assert torch.allclose(hm(inp), hm.inner()(inp)) and len(seen) == 1
+    assert fnn.PagedKVCache is not None and fnn.PagedAttentionManager is not None
