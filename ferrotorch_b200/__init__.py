@@ -11,5 +11,6 @@ __version__ = "0.1.0"
 
 from . import _native  # noqa: F401
 from . import ops  # noqa: F401
+from . import autograd, core  # noqa: F401,E402
 
-__all__ = ["ops", "__version__"]
+__all__ = ["ops", "autograd", "core", "__version__"]

@@ -1,0 +1,87 @@
+"""Tensor vocabulary of the reference's core crate, mapped onto torch
+(ferrotorch-core/src/{tensor,dtype,device}.rs and the tensor families listed in its lib.rs).
+
+Nothing here re-implements a tensor: the names resolve to the torch types and constructors that
+play the same role, so code written against the reference's nouns has something to import."""
+from __future__ import annotations
+
+import enum
+
+import torch
+from torch import Tensor, einsum  # noqa: F401
+from torch.masked import MaskedTensor, masked_tensor  # noqa: F401
+from torch.nested import nested_tensor  # noqa: F401
+
+from .ops.quant import SemiStructuredLinear, apply_2_4_mask, pack_2_4  # noqa: F401
+
+BoolTensor, IntTensor, LongTensor = torch.BoolTensor, torch.IntTensor, torch.LongTensor
+f32, f64, bf16, f16 = torch.float32, torch.float64, torch.bfloat16, torch.float16
+
+
+class MemoryFormat(enum.Enum):
+    """tensor.rs:50-59."""
+    Contiguous = torch.contiguous_format
+    ChannelsLast = torch.channels_last
+    ChannelsLast3d = torch.channels_last_3d
+
+
+class Device:
+    """``Device.Cpu``, ``Device.Cuda(n)``, ``Device.Meta`` (device.rs:28-47).  The Xpu and Mps
+    variants of the reference have no counterpart: this package targets CUDA on sm_100a only."""
+    Cpu = torch.device("cpu")
+    Meta = torch.device("meta")
+
+    @staticmethod
+    def Cuda(index: int = 0) -> torch.device:
+        return torch.device("cuda", index)
+
+    @staticmethod
+    def Xpu(index: int = 0):
+        raise NotImplementedError("Device.Xpu: this package has no Intel back-end")
+
+    @staticmethod
+    def Mps(index: int = 0):
+        raise NotImplementedError("Device.Mps: this package has no Metal back-end")
+
+
+def ComplexTensor(real: Tensor, imag: Tensor) -> Tensor:
+    return torch.complex(real, imag)
+
+
+def SparseTensor(indices: Tensor, values: Tensor, size) -> Tensor:
+    """COO sparse tensor; ``.to_sparse_csr()`` / ``.to_sparse_csc()`` give the other layouts."""
+    return torch.sparse_coo_tensor(indices, values, size).coalesce()
+
+
+def NestedTensor(tensors, **kw) -> Tensor:
+    return torch.nested.nested_tensor(list(tensors), **kw)
+
+
+def NamedTensor(data: Tensor, names) -> Tensor:
+    return data.refine_names(*names)
+
+
+def QuantizedTensor(data: Tensor, scale: float, zero_point: int = 0, dtype=torch.qint8) -> Tensor:
+    """Per-tensor affine quantisation (quantize.rs); ``.dequantize()`` goes back."""
+    return torch.quantize_per_tensor(data.float(), scale, zero_point, dtype)
+
+
+def rearrange(tensor: Tensor, pattern: str, **axes) -> Tensor:
+    import einops
+
+    return einops.rearrange(tensor, pattern, **axes)
+
+
+def flex_attention(q: Tensor, k: Tensor, v: Tensor, score_mod=None, scale: float | None = None) -> Tensor:
+    """Attention with a user function applied to the scores before the softmax:
+    ``score_mod(score, batch, head, q_index, kv_index) -> score`` (flex_attention.rs).  Dense
+    evaluation; use the flash kernels of :mod:`ferrotorch_b200.ops` for the standard masks."""
+    B, H, S, D = q.shape
+    s = (q.float() @ k.float().transpose(-1, -2)) * (scale if scale is not None else D ** -0.5)
+    if score_mod is not None:
+        b = torch.arange(B, device=q.device).view(B, 1, 1, 1)
+        h = torch.arange(H, device=q.device).view(1, H, 1, 1)
+        qi = torch.arange(S, device=q.device).view(1, 1, S, 1)
+        ki = torch.arange(k.shape[2], device=q.device).view(1, 1, 1, -1)
+        s = score_mod(s, b, h, qi, ki)
+    return (s.softmax(-1) @ v.float()).to(q.dtype)
