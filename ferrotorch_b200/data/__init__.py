@@ -94,3 +94,6 @@ class DevicePrefetcher:
         return len(self.loader)
 
 from .token_loader import TokenFileLoader, write_token_file  # noqa: F401,E402
+
+from .interop import (dataframe_to_tensor, record_batch_to_tensor, tensor_from_arrow_array,  # noqa: F401,E402
+                      tensor_to_arrow_array, tensor_to_arrow_arrayref)

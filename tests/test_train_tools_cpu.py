@@ -322,3 +322,31 @@ def test_native_token_loader(tmp_path):
         TokenFileLoader(p2, 4, 64, dtype_bytes=4)
     with pytest.raises(ValueError):
         TokenFileLoader(str(tmp_path / "missing.bin"), 4, 2)
+
+
+def test_arrow_and_dataframe_interop():
+    pa = pytest.importorskip("pyarrow")
+    pd = pytest.importorskip("pandas")
+    from ferrotorch_b200 import data as D
+
+    t = torch.arange(5, dtype=torch.float64)
+    arr = D.tensor_to_arrow_array(t)
+    assert str(arr.type) == "double" and arr.to_pylist() == [0.0, 1.0, 2.0, 3.0, 4.0]
+    back = D.tensor_from_arrow_array(arr)
+    assert back.dtype == torch.float64 and torch.equal(back, t)
+    assert D.tensor_from_arrow_array(pa.chunked_array([[1, 2], [3]]), torch.float32).tolist() == [1.0, 2.0, 3.0]
+    with pytest.raises(ValueError, match="nulls"):
+        D.tensor_from_arrow_array(pa.array([1.0, None]))
+    with pytest.raises(ValueError, match="unsupported"):
+        D.tensor_from_arrow_array(pa.array(["a"]))
+    with pytest.raises(ValueError):
+        D.tensor_to_arrow_array(torch.zeros(2, 2))
+    rb = pa.record_batch({"a": [1, 2, 3], "b": [0.5, 1.5, 2.5]})
+    assert D.record_batch_to_tensor(rb).tolist() == [[1.0, 0.5], [2.0, 1.5], [3.0, 2.5]]
+    assert D.record_batch_to_tensor(pa.Table.from_batches([rb, rb])).shape == (6, 2)
+    df = pd.DataFrame({"x": [1, 2], "y": [0.25, 0.75]})
+    assert D.dataframe_to_tensor(df, torch.float64).tolist() == [[1.0, 0.25], [2.0, 0.75]]
+    with pytest.raises(ValueError, match="non-numeric"):
+        D.dataframe_to_tensor(pd.DataFrame({"x": ["a"]}))
+    with pytest.raises(ValueError, match="missing"):
+        D.dataframe_to_tensor(pd.DataFrame({"x": [1.0, None]}))
