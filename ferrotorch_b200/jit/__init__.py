@@ -3,7 +3,11 @@ from .codegen import compile_cubin, generate_source, run_fused, run_program_torc
 from .ir import (IrGraph, Node, OptimizationConfig, constant_fold, dead_code_eliminate, fuse_elementwise,  # noqa: F401
                  optimize, pattern_fuse, plan_memory)
 from .module import (Autotuner, CompileConfig, EagerFallback, JitError, TracedModule, apply_fused, compile,  # noqa: F401
-                     trace, with_fusion)
+                     lower_fx, trace, with_fusion)
+from .advanced import (AotGraphPair, AotModule, DimSpec, ExportedProgram, ExportedProgramMetadata, GraphSegment,  # noqa: F401
+                       Guard, InputSpec, SegmentedModule, ShapeSignature, SymbolicDim, SymbolicTracedModule,
+                       compile_aot, compile_symbolic, decompose_forward_backward, export,
+                       patch_reshape_for_symbolic_dims, trace_with_breaks)
 
 
 def script(fn):

@@ -69,6 +69,15 @@ def _lower_binary(g: IrGraph, op: str, a, b):
     return g.add(op, [a.id, b.id])
 
 
+def _aten_tables():
+    a = torch.ops.aten
+    unary = {a.relu.default: "relu", a.sigmoid.default: "sigmoid", a.tanh.default: "tanh", a.silu.default: "silu",
+             a.sqrt.default: "sqrt", a.abs.default: "abs", a.exp.default: "exp", a.log.default: "log", a.neg.default: "neg"}
+    binary = {a.add.Tensor: "add", a.sub.Tensor: "sub", a.mul.Tensor: "mul", a.div.Tensor: "div",
+              a.add.Scalar: "add", a.sub.Scalar: "sub", a.mul.Scalar: "mul", a.div.Scalar: "div"}
+    return unary, binary
+
+
 def trace(fn, example_inputs) -> IrGraph:
     """Capture ``fn`` (a module or function of tensors) as an :class:`IrGraph` with shapes."""
     example_inputs = tuple(example_inputs)
@@ -76,6 +85,15 @@ def trace(fn, example_inputs) -> IrGraph:
         gm = torch.fx.symbolic_trace(fn)
     except Exception as e:  # noqa: BLE001
         raise JitError("cannot trace %r: %s" % (fn, e)) from e
+    return lower_fx(gm, example_inputs)
+
+
+def lower_fx(gm: torch.fx.GraphModule, example_inputs) -> IrGraph:
+    """An fx graph (from ``symbolic_trace``, or an ATen-level one from ``make_fx``) -> IR; one
+    eager run on ``example_inputs`` records shapes and dtypes."""
+    example_inputs = tuple(example_inputs)
+    aten_unary, aten_binary = _aten_tables()
+    fn_unary, fn_binary = {**_FN_UNARY, **aten_unary}, {**_FN_BINARY, **aten_binary}
     g = IrGraph()
     env: dict = {}
     mods = dict(gm.named_modules())
@@ -94,10 +112,12 @@ def trace(fn, example_inputs) -> IrGraph:
             for part in node.target.split("."):
                 t = getattr(t, part)
             env[node] = g.add("const", value=t)
-        elif node.op == "call_function" and node.target in _FN_UNARY and not node.kwargs.get("approximate", "none") != "none":
-            env[node] = g.add(_FN_UNARY[node.target], [args[0].id])
-        elif node.op == "call_function" and node.target in _FN_BINARY and len(args) == 2 and not node.kwargs:
-            env[node] = _lower_binary(g, _FN_BINARY[node.target], args[0], args[1])
+        elif node.op == "call_function" and node.target in fn_unary and hasattr(args[0], "id") and \
+                not node.kwargs.get("approximate", "none") != "none":
+            env[node] = g.add(fn_unary[node.target], [args[0].id])
+        elif node.op == "call_function" and node.target in fn_binary and len(args) == 2 and not node.kwargs and \
+                (hasattr(args[0], "id") or hasattr(args[1], "id")) and all(hasattr(x, "id") or _is_num(x) for x in args):
+            env[node] = _lower_binary(g, fn_binary[node.target], args[0], args[1])
         elif node.op == "call_function" and node.target in (operator.pow, torch.pow) and _is_num(args[1]):
             env[node] = g.add("pow_c", [args[0].id], c=float(args[1]))
         elif node.op == "call_method" and node.target in _METHOD and not node.kwargs:
