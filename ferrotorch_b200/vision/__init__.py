@@ -91,3 +91,8 @@ class UNet(nn.Module):
                 x = nn.functional.interpolate(x, size=s.shape[-2:], mode="nearest")
             x = dec(torch.cat([s, x], 1))
         return self.head(x)
+
+
+from .io import (GaussianNoise, RandomGaussianBlur, RawImage, VisionNormalize, VisionToTensor,  # noqa: F401,E402
+                 raw_image_to_tensor, read_image, read_image_as_tensor, read_image_rgba, tensor_to_raw_image,
+                 vision_manual_seed, write_image, write_tensor_as_image)

@@ -86,3 +86,42 @@ def test_own_resnet_computes_what_torchvision_computes(name):
     ga, gb = dict(theirs.named_parameters()), dict(ours.named_parameters())
     for k in ("conv1.weight", "layer1.0.bn1.weight", "layer3.1.conv2.weight", "fc.bias"):
         assert torch.allclose(ga[k].grad, gb[k].grad, atol=5e-4, rtol=1e-3), (k, (ga[k].grad - gb[k].grad).abs().max())
+
+
+def test_image_io_and_extra_transforms(tmp_path):
+    pytest.importorskip("PIL")
+    torch.manual_seed(0)
+    img = torch.rand(3, 9, 7)
+    p = tmp_path / "a.png"
+    vision.write_tensor_as_image(str(p), img)
+    raw = vision.read_image(str(p))
+    assert (raw.width, raw.height, raw.channels, len(raw.data)) == (7, 9, 3, 7 * 9 * 3)
+    back = vision.read_image_as_tensor(str(p))
+    assert back.shape == (3, 9, 7) and (back - img).abs().max() <= 0.5 / 255 + 1e-6        # PNG is lossless: only the rounding
+    rgba = vision.read_image_rgba(str(p))
+    assert rgba.channels == 4 and vision.raw_image_to_tensor(rgba)[3].min() == 1.0           # opaque alpha
+    vision.write_image(str(tmp_path / "b.jpg"), rgba)                                        # alpha dropped for JPEG
+    assert vision.read_image(str(tmp_path / "b.jpg")).channels == 3
+    assert vision.tensor_to_raw_image(torch.tensor([[[2.0]], [[-1.0]], [[0.5]]])).data == bytes([255, 0, 128])
+    for bad in (torch.zeros(9, 7), torch.zeros(2, 9, 7)):
+        with pytest.raises(ValueError):
+            vision.tensor_to_raw_image(bad)
+    with pytest.raises(ValueError):
+        vision.RawImage(b"123", 2, 2, 3)
+    with pytest.raises(OSError):
+        vision.read_image(str(tmp_path / "missing.png"))
+    assert torch.equal(vision.VisionToTensor()(raw), back)
+    n = vision.VisionNormalize([0.5, 0.5, 0.5], [0.25, 0.5, 1.0])(torch.full((3, 2, 2), 1.0))
+    assert n[:, 0, 0].tolist() == [2.0, 1.0, 0.5]
+    with pytest.raises(ValueError):
+        vision.VisionNormalize([0.0], [0.0])
+    vision.vision_manual_seed(7)
+    a = vision.GaussianNoise(sigma=0.2)(img)
+    vision.vision_manual_seed(7)
+    b = vision.GaussianNoise(sigma=0.2)(img)
+    assert torch.equal(a, b) and not torch.equal(a, img) and 0 <= a.min() and a.max() <= 1
+    blur = vision.RandomGaussianBlur(5, (1.0, 1.0), p=1.0)(img)
+    assert blur.shape == img.shape and blur.var() < img.var() and abs(float(blur.mean() - img.mean())) < 0.02
+    assert torch.equal(vision.RandomGaussianBlur(3, p=0.0)(img), img)
+    with pytest.raises(ValueError):
+        vision.RandomGaussianBlur(4)
