@@ -26,3 +26,8 @@ except ImportError:  # pragma: no cover
 from .extra import (EMA, Adafactor, GradientAccumulator, Muon, NaturalGradient, WarmupLR,  # noqa: F401
                     cosine_warmup_scheduler)
 from .fused import FusedAdamW, FusedSGD  # noqa: F401
+
+
+ExponentialMovingAverage = EMA          # noqa: F405  (ferrotorch-optim/src/ema.rs)
+Kfac = NaturalGradient                  # noqa: F405  (natural_gradient.rs)
+from .extra import diff_sgd_momentum_step, diff_sgd_step  # noqa: F401,E402

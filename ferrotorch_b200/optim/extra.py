@@ -175,3 +175,18 @@ def cosine_warmup_scheduler(optimizer, warmup_steps: int, total_steps: int, min_
         return min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * t))
 
     return LambdaLR(optimizer, f)
+
+
+
+def diff_sgd_step(params, grads, lr: float):
+    """One SGD step as a differentiable function of the parameters, the gradients and ``lr``:
+    returns new tensors instead of updating in place, so an outer loss can be differentiated
+    through the update (meta-learning; ferrotorch-optim/src/differentiable.rs)."""
+    return [p - lr * g for p, g in zip(params, grads)]
+
+
+def diff_sgd_momentum_step(params, grads, bufs, lr: float, momentum: float = 0.9):
+    """The same with momentum: ``buf' = momentum * buf + g``, ``p' = p - lr * buf'``; returns
+    ``(new_params, new_bufs)``."""
+    new_bufs = [momentum * b + g for b, g in zip(bufs, grads)]
+    return [p - lr * b for p, b in zip(params, new_bufs)], new_bufs

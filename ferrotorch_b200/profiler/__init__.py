@@ -157,6 +157,9 @@ class Profiler:
             a["flops"] += e.flops or 0.0
         return agg
 
+    def report(self) -> "ProfileReport":
+        return ProfileReport(self)
+
     def table(self, sort_by: str = "total_us") -> str:
         rows = sorted(self.summary().values(), key=lambda a: -a[sort_by])
         out = ["%-32s %-5s %8s %12s %12s %10s" % ("name", "dev", "calls", "total us", "avg us", "TFLOP/s")]
@@ -185,6 +188,91 @@ class Profiler:
         for a in self.summary().values():
             w.add_scalar("profile/%s/%s_us" % (a["device"], a["name"]), a["total_us"], step)
         w.close()
+
+
+# --------------------------------------------------------------------------- report objects
+class SchedulePhase:
+    """The states :meth:`ProfileSchedule.state` returns (schedule.rs ``SchedulePhase``)."""
+    WAIT, WARMUP, ACTIVE, DONE = "wait", "warmup", "active", "done"
+
+
+class MemoryCategory:
+    """Tags for :meth:`Profiler.record_memory` (event.rs ``MemoryCategory``)."""
+    PARAMETERS, GRADIENTS, OPTIMIZER_STATE, ACTIVATIONS, TEMPORARY, OTHER = (
+        "parameters", "gradients", "optimizer_state", "activations", "temporary", "other")
+
+
+@dataclass
+class OpSummary:
+    name: str
+    device: str
+    count: int
+    total_us: float
+    flops: float = 0.0
+
+    @property
+    def avg_us(self) -> float:
+        return self.total_us / self.count if self.count else 0.0
+
+    @property
+    def tflops(self) -> float:
+        return self.flops / self.total_us / 1e6 if self.flops and self.total_us else 0.0
+
+
+class ProfileReport:
+    """The events of a run and their per-op totals, detached from the profiler that took them
+    (report.rs ``ProfileReport``): ``ops()``, ``top(n)``, ``total_us()``, ``table()``,
+    ``chrome_trace_json()``, ``save_chrome_trace(path)``."""
+
+    def __init__(self, profiler: "Profiler"):
+        profiler.flush()
+        self.events = list(profiler.events)
+        self.memory = list(profiler.memory)
+        self._ops = [OpSummary(a["name"], a["device"], a["count"], a["total_us"], a["flops"])
+                     for a in profiler.summary().values()]
+        self._table, self._trace = profiler.table(), profiler.chrome_trace_json()
+
+    def ops(self) -> list[OpSummary]:
+        return sorted(self._ops, key=lambda o: -o.total_us)
+
+    def top(self, n: int = 10) -> list[OpSummary]:
+        return self.ops()[:n]
+
+    def total_us(self, device: str | None = None) -> float:
+        return sum(o.total_us for o in self._ops if device is None or o.device == device)
+
+    def table(self) -> str:
+        return self._table
+
+    def chrome_trace_json(self) -> str:
+        return self._trace
+
+    def save_chrome_trace(self, path: str) -> None:
+        with open(path, "w") as f:
+            f.write(self._trace)
+
+
+class CudaKernelScope:
+    """Times a region on the device with a pair of CUDA events on the current stream; ``stop()``
+    queues the pair, the profiler's ``flush()`` turns it into an event after one synchronise
+    (cuda_timing.rs:71-119).  On a machine without CUDA it falls back to the host clock."""
+
+    def __init__(self, profiler: "Profiler", name: str, category: str = "kernel"):
+        self.p, self.name, self.category = profiler, name, category
+        self._cm = profiler.scope(name, category)
+        self._cm.__enter__()
+        self._open = True
+
+    def stop(self) -> None:
+        if self._open:
+            self._cm.__exit__(None, None, None)
+            self._open = False
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.stop()
 
 
 @contextlib.contextmanager

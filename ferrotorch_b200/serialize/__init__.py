@@ -2,8 +2,15 @@
 from .gguf import GgufFile, gguf_key_to_hf, load_gguf_state_dict, quantize_q4_0, write_gguf  # noqa: F401
 from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_checkpoint,  # noqa: F401
                     load_pytorch_state_dict, load_safetensors, load_safetensors_sharded, load_state_dict,
+                    ShardProgress, load_safetensors_auto, load_safetensors_mmap, load_safetensors_sharded_filtered,
+                    load_safetensors_sharded_mmap, load_safetensors_sharded_with_progress, validate_checkpoint,
                     loads_state_dict, save_checkpoint, save_reference_checkpoint, save_pytorch, save_safetensors, save_safetensors_sharded,
                     save_state_dict)
+
+
+class OnnxExportConfig(dict):
+    """Keyword arguments for :func:`export_onnx` (``opset_version``, ``input_names``,
+    ``output_names``, ``dynamic_axes`` ...), the counterpart of onnx_export.rs ``OnnxExportConfig``."""
 
 
 def export_onnx(model, example_inputs, path: str, **kw) -> None:

@@ -15,6 +15,7 @@ Covers the reference's ``ferrotorch-serialize``:
 from __future__ import annotations
 
 import io
+from dataclasses import dataclass
 import json
 import os
 import struct
@@ -96,6 +97,64 @@ def load_safetensors_sharded(index_path: str, device="cpu", dtype: torch.dtype |
         if progress is not None:
             progress(i + 1, len(by_file))
     return out
+
+
+@dataclass
+class ShardProgress:
+    """Passed to the progress callback of :func:`load_safetensors_sharded_with_progress`."""
+    shard_index: int
+    shard_count: int
+    shard_file: str
+    tensors_loaded: int
+
+
+def load_safetensors_mmap(path: str, device="cpu", **kw) -> dict[str, torch.Tensor]:
+    """Same as :func:`load_safetensors`: the file is always memory-mapped (safetensors_io.rs)."""
+    return load_safetensors(path, device, **kw)
+
+
+def load_safetensors_sharded_filtered(index_path: str, key_filter: Callable[[str], bool], device="cpu",
+                                      dtype: torch.dtype | None = None) -> dict[str, torch.Tensor]:
+    """Only the tensors ``key_filter`` accepts; shards without any of them are not opened."""
+    return load_safetensors_sharded(index_path, device, dtype, key_filter)
+
+
+load_safetensors_sharded_mmap = load_safetensors_sharded
+
+
+def load_safetensors_sharded_with_progress(index_path: str, on_progress: Callable[[ShardProgress], None],
+                                           device="cpu", dtype: torch.dtype | None = None) -> dict[str, torch.Tensor]:
+    with open(index_path) as f:
+        files = sorted(set(json.load(f)["weight_map"].values()))
+    out, base = {}, os.path.dirname(index_path)
+    for i, fn in enumerate(files):
+        out.update(load_safetensors(os.path.join(base, fn), device, dtype))
+        on_progress(ShardProgress(i, len(files), fn, len(out)))
+    return out
+
+
+def load_safetensors_auto(path: str, device="cpu", dtype: torch.dtype | None = None) -> dict[str, torch.Tensor]:
+    """A ``.safetensors`` file, a ``*.index.json`` of a sharded checkpoint, or a directory that
+    holds ``model.safetensors`` or ``model.safetensors.index.json``."""
+    if os.path.isdir(path):
+        for cand in ("model.safetensors.index.json", "model.safetensors"):
+            if os.path.exists(os.path.join(path, cand)):
+                return load_safetensors_auto(os.path.join(path, cand), device, dtype)
+        raise FileNotFoundError("no model.safetensors[.index.json] under %s" % path)
+    if path.endswith(".json"):
+        return load_safetensors_sharded(path, device, dtype)
+    return load_safetensors(path, device, dtype)
+
+
+def validate_checkpoint(path: str) -> dict:
+    """Check that a ``.pt`` / ``.bin`` file is a plain state dict a safe loader accepts (tensors
+    only, no arbitrary pickled objects); returns ``{"tensors", "parameters", "dtypes"}``
+    (pytorch_export.rs ``validate_checkpoint``)."""
+    sd = load_pytorch_state_dict(path)
+    if not sd:
+        raise ValueError("%s holds no tensors" % path)
+    return {"tensors": len(sd), "parameters": sum(v.numel() for v in sd.values()),
+            "dtypes": sorted({str(v.dtype) for v in sd.values()})}
 
 
 # --------------------------------------------------------------------------- PyTorch .pt

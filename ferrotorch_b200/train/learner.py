@@ -91,6 +91,16 @@ class EpochResult:
 
 
 @dataclass
+class EvalResult:
+    """What ``Learner.evaluate`` measured (history.rs ``EvalResult``)."""
+    metrics: dict
+    num_batches: int = 0
+
+    def get(self, key: str, default=None):
+        return self.metrics.get(key, default)
+
+
+@dataclass
 class TrainingHistory:
     epochs: list[EpochResult] = field(default_factory=list)
 

@@ -350,3 +350,61 @@ def test_arrow_and_dataframe_interop():
         D.dataframe_to_tensor(pd.DataFrame({"x": ["a"]}))
     with pytest.raises(ValueError, match="missing"):
         D.dataframe_to_tensor(pd.DataFrame({"x": [1.0, None]}))
+
+
+def test_name_level_parity_helpers(tmp_path):
+    """Small pieces that exist so that every public name of the reference's train / profiler /
+    serialize / optim crates has a counterpart."""
+    import ferrotorch_b200.optim as O
+    import ferrotorch_b200.serialize as S
+
+    # train
+    assert T.EmaCallback is T.EMACallback and T.EvalResult({"loss": 0.5}, 3).get("loss") == 0.5
+    lin = nn.Linear(3, 3)
+    x = torch.randn(2, 3, requires_grad=True)
+    T.checkpoint(lambda t: lin(t).relu(), x).sum().backward()
+    assert x.grad is not None and float(T.clip_grad_norm_(lin.parameters(), 1e-3)) > 0
+    T.clip_grad_value_(lin.parameters(), 1e-4)
+    assert float(lin.weight.grad.abs().max()) <= 1e-4
+    # profiler
+    prof = P.Profiler()
+    with P.CudaKernelScope(prof, "step", "kernel"):
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    prof.record("copy", 12.0)
+    prof.record_memory(P.MemoryCategory.ACTIVATIONS, 1024)
+    rep = prof.report()
+    names = [o.name for o in rep.ops()]
+    assert set(names) == {"step", "copy"} and rep.top(1)[0].count == 1 and rep.total_us() >= 12.0
+    assert "step" in rep.table() and json.loads(rep.chrome_trace_json())["traceEvents"]
+    rep.save_chrome_trace(str(tmp_path / "t.json"))
+    assert P.SchedulePhase.ACTIVE == P.ProfileSchedule(0, 0, 1).state() and P.OpSummary("a", "cpu", 2, 10.0).avg_us == 5.0
+    # serialize
+    sd = {"a.w": torch.randn(2, 2), "b.w": torch.randn(3)}
+    S.save_safetensors_sharded(sd, str(tmp_path / "ck"), max_shard_bytes=16)
+    idx = str(tmp_path / "ck" / "model.safetensors.index.json")
+    seen = []
+    full = S.load_safetensors_sharded_with_progress(idx, seen.append)
+    assert set(full) == set(sd) and seen[-1].tensors_loaded == 2 and seen[-1].shard_count == len(seen) == 2
+    assert list(S.load_safetensors_sharded_filtered(idx, lambda k: k.startswith("b."))) == ["b.w"]
+    assert set(S.load_safetensors_auto(str(tmp_path / "ck"))) == set(sd) and set(S.load_safetensors_auto(idx)) == set(sd)
+    S.save_safetensors(sd, str(tmp_path / "one.safetensors"))
+    assert torch.equal(S.load_safetensors_auto(str(tmp_path / "one.safetensors"))["b.w"], sd["b.w"])
+    assert torch.equal(S.load_safetensors_mmap(str(tmp_path / "one.safetensors"))["a.w"], sd["a.w"])
+    with pytest.raises(FileNotFoundError):
+        S.load_safetensors_auto(str(tmp_path))
+    S.save_pytorch(sd, str(tmp_path / "m.pt"))
+    assert S.validate_checkpoint(str(tmp_path / "m.pt")) == {"tensors": 2, "parameters": 7, "dtypes": ["torch.float32"]}
+    torch.save({"evil": object()}, str(tmp_path / "bad.pt"))
+    with pytest.raises(Exception):
+        S.validate_checkpoint(str(tmp_path / "bad.pt"))                # arbitrary pickled objects are refused
+    assert isinstance(S.OnnxExportConfig(opset_version=17), dict)
+    # optim: differentiable steps let an outer loss see through the update
+    assert O.ExponentialMovingAverage is O.EMA and O.Kfac is O.NaturalGradient
+    w = torch.tensor([1.0, -2.0], requires_grad=True)
+    lr = torch.tensor(0.1, requires_grad=True)
+    (g,) = torch.autograd.grad((w ** 2).sum(), w, create_graph=True)
+    (w1,) = O.diff_sgd_step([w], [g], lr)
+    (w1 ** 2).sum().backward()
+    assert lr.grad.item() == pytest.approx(-2 * (1 - 0.2) * 2 * 5.0, rel=1e-5)      # d/dlr sum((w (1 - 2 lr))^2)
+    (w2,), (b2,) = O.diff_sgd_momentum_step([w.detach()], [g.detach()], [torch.ones(2)], 0.1, 0.5)
+    assert torch.allclose(b2, 0.5 + g.detach()) and torch.allclose(w2, w.detach() - 0.1 * b2)
