@@ -130,6 +130,58 @@ def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None
     return out
 
 
+# ---- the sampling primitives under the reference's names (generation.rs:230-345), on tensors
+def apply_temperature(logits: torch.Tensor, temperature: float) -> torch.Tensor:
+    if temperature <= 0:
+        raise ValueError("apply_temperature: temperature must be > 0 (use argmax for greedy decoding)")
+    return logits / temperature
+
+
+def top_k_filter(logits: torch.Tensor, k: int) -> torch.Tensor:
+    return filter_top_k_top_p(logits, top_k=k)
+
+
+def top_p_filter(logits: torch.Tensor, p: float) -> torch.Tensor:
+    return filter_top_k_top_p(logits, top_p=p)
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    return logits.argmax(-1)
+
+
+def sample_softmax(logits: torch.Tensor, generator: torch.Generator | None = None) -> torch.Tensor:
+    return torch.multinomial(logits.float().softmax(-1), 1, generator=generator).squeeze(-1)
+
+
+def generate_with_streamer(model, input_ids: torch.Tensor, cfg: GenerationConfig | None, streamer, **kw) -> torch.Tensor:
+    """:func:`generate` with the streamer as a required argument: it sees every new token ``[B]``
+    and stops the run by returning ``False``."""
+    return generate(model, input_ids, cfg, streamer=streamer, **kw)
+
+
+@dataclass
+class SpecDecodeConfig:
+    max_new_tokens: int = 32
+    gamma: int = 4                       # draft tokens proposed per target pass
+    eos_token_id: int | None = None
+
+
+@dataclass
+class SpecDecodeOutput:
+    tokens: torch.Tensor
+    proposed: int
+    accepted: int
+    target_calls: int
+
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.proposed if self.proposed else 0.0
+
+
+def speculative_decode_with_config(target, draft, input_ids: torch.Tensor, cfg: SpecDecodeConfig) -> SpecDecodeOutput:
+    ids, st = speculative_decode(target, draft, input_ids, cfg.max_new_tokens, cfg.gamma, cfg.eos_token_id)
+    return SpecDecodeOutput(ids, st["proposed"], st["accepted"], st["target_calls"])
+
+
 class GrammarLogitsProcessor:
     """Mask the logits so that every sequence stays a valid prefix of the grammar (and may only
     end once it is complete).  ``vocab[i]`` is the text of token ``i``; the per-step mask is built

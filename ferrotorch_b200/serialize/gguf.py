@@ -169,6 +169,12 @@ def gguf_key_to_hf(key: str) -> str | None:
     return None
 
 
+def gguf_to_hf_state_dict(state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """Rename the keys of an already loaded GGUF state dict to the HF names; keys without a mapping
+    are kept (ferrotorch-llama/src/gguf_remap.rs ``gguf_to_hf_state_dict``)."""
+    return {(gguf_key_to_hf(k) or k): v for k, v in state.items()}
+
+
 def load_gguf_state_dict(path: str, dtype=torch.bfloat16, remap: bool = True,
                          nibble_order: str = "ggml") -> dict[str, torch.Tensor]:
     """Dequantise every tensor to ``dtype`` (HF key names when ``remap``)."""

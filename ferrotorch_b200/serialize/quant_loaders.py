@@ -126,3 +126,22 @@ def to_q4_linear(weight: torch.Tensor, bias: torch.Tensor | None = None):
 
     nib, sc = requantize_q4_0(weight)
     return Q4Linear(nib, sc, bias)
+
+
+# names of the reference's loaders (ferrotorch-llama/src/quant_loaders.rs:41-670)
+dequantize_gptq_q4, dequantize_awq_q4, dequantize_hqq_q4_axis1 = dequantize_gptq, dequantize_awq, dequantize_hqq
+hqq_q4_axis1_to_dense = dequantize_hqq
+
+
+def hqq_state_dict_to_dense(sd: dict, dtype=torch.float32) -> dict:
+    """Replace every HQQ-quantised linear of a state dict (keys ``<name>.W_q``, ``<name>.scale``,
+    ``<name>.zero``, ``<name>.shape``) by a dense ``<name>.weight``; other entries pass through."""
+    out, done = {}, set()
+    for k in sd:
+        if k.endswith(".W_q"):
+            base = k[:-4]
+            shape = tuple(int(v) for v in sd[base + ".shape"].tolist())
+            out[base + ".weight"] = dequantize_hqq(sd[k], sd[base + ".scale"], sd[base + ".zero"], shape).to(dtype)
+            done.update({k, base + ".scale", base + ".zero", base + ".shape"})
+    out.update({k: v for k, v in sd.items() if k not in done})
+    return out

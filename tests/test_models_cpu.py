@@ -142,3 +142,27 @@ def test_flat_trainer_trajectory_matches_torch_adamw_with_clipping():
         assert abs(float(loss) - total) < 1e-5, (step, float(loss), total)
     for (n, p), q in zip(ours.named_parameters(), ref.parameters()):
         assert torch.allclose(p, q, atol=2e-5), (n, float((p - q).abs().max()))
+
+
+def test_generation_primitives_and_loader_aliases():
+    from ferrotorch_b200.models import generation as G
+    from ferrotorch_b200.serialize import gguf, quant_loaders as Q
+
+    logits = torch.tensor([[1.0, 3.0, 2.0, 0.0]])
+    assert G.argmax(logits).tolist() == [1] and torch.equal(G.apply_temperature(logits, 2.0), logits / 2)
+    assert torch.isinf(G.top_k_filter(logits, 2)).sum() == 2 and G.top_k_filter(logits, 2)[0, 1] == 3.0
+    kept = G.top_p_filter(logits, 0.6)
+    assert kept[0, 1] == 3.0 and torch.isinf(kept[0, 3]) and torch.isinf(kept[0, 0])
+    assert G.sample_softmax(torch.tensor([[0.0, 50.0]])).tolist() == [1]
+    with pytest.raises(ValueError):
+        G.apply_temperature(logits, 0.0)
+    out = G.SpecDecodeOutput(torch.zeros(1, 3), proposed=8, accepted=6, target_calls=2)
+    assert out.acceptance_rate() == 0.75 and G.SpecDecodeConfig().gamma == 4
+    sd = gguf.gguf_to_hf_state_dict({"blk.0.attn_q.weight": torch.zeros(1), "token_embd.weight": torch.zeros(1), "x": torch.zeros(1)})
+    assert set(sd) == {"model.layers.0.self_attn.q_proj.weight", "model.embed_tokens.weight", "x"}
+    assert Q.dequantize_gptq_q4 is Q.dequantize_gptq and Q.dequantize_awq_q4 is Q.dequantize_awq
+    w = torch.randn(8, 64)
+    wq, scale, zero = Q.pack_hqq(w)[:3]
+    dense = Q.hqq_state_dict_to_dense({"l.W_q": wq, "l.scale": scale, "l.zero": zero, "l.shape": torch.tensor([8, 64]),
+                                       "norm.weight": torch.ones(3)})
+    assert set(dense) == {"l.weight", "norm.weight"} and (dense["l.weight"] - w).abs().max() < 0.5

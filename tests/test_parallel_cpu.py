@@ -168,3 +168,34 @@ def test_extra_optimizers_and_schedules_reduce_loss():
     acc = O.GradientAccumulator(3)
     assert [acc.backward(m(torch.ones(1, 2)).sum()) for _ in range(3)] == [False, False, True]
     assert O.StepLR is torch.optim.lr_scheduler.StepLR and O.GradScaler is not None
+
+
+def test_p2p_verbs_probes_and_aliases():
+    import ferrotorch_b200.parallel as P
+    from ferrotorch_b200.parallel.backend import SelfSend, UnsupportedOp, run_simulated
+
+    def body(g):
+        peer = 1 - g.rank
+        got = P.sendrecv(g, torch.full((3,), float(g.rank)), peer)
+        if g.rank == 0:
+            P.send(g, torch.arange(4.0), 1)
+            extra = None
+        else:
+            extra = P.recv(g, (4,), 0)
+        rs = P.async_reduce_scatter(g, torch.arange(4.0) * (g.rank + 1)).wait(10)
+        try:
+            P.send(g, torch.zeros(1), g.rank)
+            own = "sent"
+        except SelfSend:
+            own = "refused"
+        return got, extra, rs, own
+
+    r0, r1 = run_simulated(2, body)
+    assert r0[0].tolist() == [1.0] * 3 and r1[0].tolist() == [0.0] * 3 and r1[1].tolist() == [0.0, 1.0, 2.0, 3.0]
+    assert r0[2].tolist() == [0.0, 3.0] and r1[2].tolist() == [6.0, 9.0] and r0[3] == r1[3] == "refused"
+    assert P.is_gloo_available() and isinstance(P.is_nccl_available(), bool) and isinstance(P.is_ucc_available(), bool)
+    assert isinstance(P.is_mpi_available(), bool)
+    assert P.PipelineSchedule.OneFOneB.value == "1f1b" and P.Placement.Shard is P.Shard and P.async_all_gather is P.all_gather_async
+    for fn in (P.gpu_allreduce, P.gpu_broadcast):
+        with pytest.raises(UnsupportedOp):
+            fn(torch.zeros(2))                      # host tensors are not silently bounced through the CPU path
