@@ -46,6 +46,14 @@ class PagePool:
     def num_free(self) -> int:
         return len(self._free)
 
+    @property
+    def num_used(self) -> int:
+        return self.num_pages - len(self._free)
+
+    @property
+    def num_total(self) -> int:
+        return self.num_pages
+
 
 class PagedKVCache:
     """Block tables for up to ``max_seqs`` sequences over one :class:`PagePool`, plus the device
@@ -198,3 +206,14 @@ class PagedAttentionManager:
     @property
     def free_pages(self) -> int:
         return self.cache.pool.num_free
+
+    def num_sequences(self) -> int:
+        return len(self.active)
+
+    def pool_utilization(self) -> float:
+        """Fraction of the pages in use, 0.0 .. 1.0 (paged_attention.rs:525)."""
+        pool = self.cache.pool
+        return pool.num_used / pool.num_total if pool.num_total else 0.0
+
+    def pool(self) -> PagePool:
+        return self.cache.pool

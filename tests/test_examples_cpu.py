@@ -13,6 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("generate_text.py", []),
     ("compile_and_checkpoint.py", ["--device", "cpu"]),
     ("ddp_over_tcp.py", []),
+    ("constrained_json.py", []),
+    ("tiny_text_to_image.py", ["--steps", "3", "--size", "32"]),
 ])
 def test_example_runs(script, args):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")

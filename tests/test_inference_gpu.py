@@ -52,8 +52,9 @@ def test_page_pool_bookkeeping():
     assert mgr.free_pages == 0
     with pytest.raises(OutOfPages):
         mgr.extend(a, 20)
+    assert mgr.num_sequences() == 2 and mgr.pool_utilization() == 1.0 and mgr.pool().num_used == 4 == mgr.pool().num_total
     mgr.remove_sequence(a)
-    assert mgr.free_pages == 2 and a not in mgr.active
+    assert mgr.free_pages == 2 and a not in mgr.active and mgr.pool_utilization() == 0.5
     k = torch.arange(17 * 8, dtype=torch.float32).view(17, 1, 8)
     cache.append(0, k, -k, torch.arange(17, dtype=torch.int32), torch.full((17,), b, dtype=torch.int32))
     gk, gv = cache.gather(0, b, 17)
