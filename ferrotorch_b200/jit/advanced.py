@@ -385,6 +385,7 @@ class ExportedProgram:
     def __init__(self, program, meta: ExportedProgramMetadata):
         self.program, self.meta = program, meta
         self._module = program.module()
+        self.ir_graph = None
 
     # -- running
     def check_inputs(self, *inputs) -> None:
@@ -481,12 +482,15 @@ def export(module: nn.Module, example_inputs, input_specs: list[InputSpec] | Non
                 raise JitError("export: spec says %d for a dimension of size %d" % (d.size, t.shape[k]))
         dynamic.append(entry or None)
     try:
-        ir_ops = trace(module, example_inputs).ops()
+        ir_graph = trace(module, example_inputs)
+        ir_ops = ir_graph.ops()
     except JitError:
-        ir_ops = []
+        ir_graph, ir_ops = None, []
     program = torch.export.export(module, example_inputs, dynamic_shapes=tuple(dynamic) if dims else None)
     with torch.no_grad():
         out = module(*example_inputs)
     meta = ExportedProgramMetadata(list(specs), [str(t.dtype) for t in example_inputs],
                                    list(out.shape) if isinstance(out, torch.Tensor) else [], ir_ops)
-    return ExportedProgram(program, meta)
+    ep = ExportedProgram(program, meta)
+    ep.ir_graph = ir_graph          # kept in memory only (ONNX export uses it); a loaded program has none
+    return ep

@@ -8,14 +8,5 @@ from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_
                     save_state_dict)
 
 
-class OnnxExportConfig(dict):
-    """Keyword arguments for :func:`export_onnx` (``opset_version``, ``input_names``,
-    ``output_names``, ``dynamic_axes`` ...), the counterpart of onnx_export.rs ``OnnxExportConfig``."""
-
-
-def export_onnx(model, example_inputs, path: str, **kw) -> None:
-    """ONNX export through ``torch.onnx`` (the reference hand-rolls the protobuf,
-    ferrotorch-serialize/src/onnx_export.rs:1084)."""
-    import torch
-
-    torch.onnx.export(model, example_inputs, path, **kw)
+from .onnx import (OnnxExportConfig, OnnxExportError, export_from_program, export_ir_graph_to_onnx, export_onnx,  # noqa: F401,E402
+                   ir_graph_to_onnx, load_onnx, run_onnx)

@@ -1,0 +1,501 @@
+"""ONNX export of a traced graph with a hand-written protobuf encoder, plus a small decoder and
+reference evaluator so an exported file can be checked without any ONNX package.
+
+The reference does the same (ferrotorch-serialize/src/onnx_export.rs:68-1182: ``ProtobufWriter``,
+``encode_*`` builders, ``map_ir_op``, SiLU / GELU decomposed for opset 17, ``OnnxDimSpec`` for
+dynamic axes, ``ir_graph_to_onnx``, ``export_onnx``, ``export_ir_graph_to_onnx``).  ``torch.onnx``
+needs the ``onnxscript`` package, which is not part of every install; this path needs nothing.
+
+Supported graph content: the IR's elementwise ops, ``nn.Linear`` (MatMul + Add), ``matmul``,
+``softmax``, transposes of the last two axes, ``reshape`` / ``view`` / ``flatten``.  Anything else
+raises :class:`OnnxExportError` naming the node.
+"""
+from __future__ import annotations
+
+import math
+import struct
+from dataclasses import dataclass, field
+
+import torch
+from torch import nn
+
+ONNX_FLOAT, ONNX_UINT8, ONNX_INT8, ONNX_INT32, ONNX_INT64, ONNX_BOOL, ONNX_FLOAT16, ONNX_DOUBLE, ONNX_BFLOAT16 = 1, 2, 3, 6, 7, 9, 10, 11, 16
+_DTYPE = {torch.float32: ONNX_FLOAT, torch.float64: ONNX_DOUBLE, torch.float16: ONNX_FLOAT16, torch.bfloat16: ONNX_BFLOAT16,
+          torch.int64: ONNX_INT64, torch.int32: ONNX_INT32, torch.int8: ONNX_INT8, torch.uint8: ONNX_UINT8, torch.bool: ONNX_BOOL}
+_DTYPE_INV = {v: k for k, v in _DTYPE.items()}
+
+
+class OnnxExportError(ValueError):
+    pass
+
+
+@dataclass
+class OnnxExportConfig:
+    opset_version: int = 17
+    model_name: str = "ferrotorch_b200_model"
+    producer_name: str = "ferrotorch_b200"
+    producer_version: str = "0.1.0"
+    input_names: list | None = None
+    output_names: list | None = None
+    dynamic_axes: dict = field(default_factory=dict)     # input / output name -> {axis: symbol}
+
+
+# --------------------------------------------------------------------------- protobuf wire format
+class ProtobufWriter:
+    """Varints, tags and length-delimited fields: all the wire format ONNX needs."""
+
+    def __init__(self):
+        self.buf = bytearray()
+
+    @staticmethod
+    def varint(n: int) -> bytes:
+        if n < 0:
+            n += 1 << 64                      # negative int64 values are ten-byte two's-complement varints
+        out = bytearray()
+        while True:
+            b = n & 0x7F
+            n >>= 7
+            out.append(b | (0x80 if n else 0))
+            if not n:
+                return bytes(out)
+
+    def _tag(self, fieldno: int, wire: int) -> None:
+        self.buf += self.varint((fieldno << 3) | wire)
+
+    def int(self, fieldno: int, value: int) -> "ProtobufWriter":
+        self._tag(fieldno, 0)
+        self.buf += self.varint(int(value))
+        return self
+
+    def float(self, fieldno: int, value: float) -> "ProtobufWriter":
+        self._tag(fieldno, 5)
+        self.buf += struct.pack("<f", value)
+        return self
+
+    def bytes(self, fieldno: int, data) -> "ProtobufWriter":
+        data = data.encode() if isinstance(data, str) else bytes(data)
+        self._tag(fieldno, 2)
+        self.buf += self.varint(len(data)) + data
+        return self
+
+    string = bytes
+
+    def message(self, fieldno: int, sub: "ProtobufWriter") -> "ProtobufWriter":
+        return self.bytes(fieldno, sub.buf)
+
+    def packed_ints(self, fieldno: int, values) -> "ProtobufWriter":
+        return self.bytes(fieldno, b"".join(self.varint(int(v)) for v in values))
+
+    def finish(self) -> bytes:
+        return bytes(self.buf)
+
+
+def read_message(data: bytes) -> list[tuple[int, int, object]]:
+    """Decode one message level into ``(field, wire type, value)`` triples; nested messages stay
+    bytes (call again on them)."""
+    out, i, n = [], 0, len(data)
+
+    def varint():
+        nonlocal i
+        shift = v = 0
+        while True:
+            if i >= n:
+                raise OnnxExportError("protobuf: truncated varint")
+            b = data[i]
+            i += 1
+            v |= (b & 0x7F) << shift
+            if not b & 0x80:
+                return v
+            shift += 7
+            if shift > 63:
+                raise OnnxExportError("protobuf: varint longer than 10 bytes")
+
+    while i < n:
+        key = varint()
+        f, w = key >> 3, key & 7
+        if w == 0:
+            out.append((f, w, varint()))
+        elif w == 2:
+            ln = varint()
+            if i + ln > n:
+                raise OnnxExportError("protobuf: length-delimited field overruns the buffer")
+            out.append((f, w, data[i:i + ln]))
+            i += ln
+        elif w == 5:
+            out.append((f, w, struct.unpack_from("<f", data, i)[0]))
+            i += 4
+        elif w == 1:
+            out.append((f, w, struct.unpack_from("<d", data, i)[0]))
+            i += 8
+        else:
+            raise OnnxExportError("protobuf: unsupported wire type %d" % w)
+    return out
+
+
+# --------------------------------------------------------------------------- ONNX message builders
+def encode_tensor(name: str, t: torch.Tensor) -> ProtobufWriter:
+    if t.dtype not in _DTYPE:
+        raise OnnxExportError("tensor %s: dtype %s has no ONNX counterpart" % (name, t.dtype))
+    w = ProtobufWriter()
+    for d in t.shape:
+        w.int(1, d)
+    w.int(2, _DTYPE[t.dtype]).string(8, name)
+    c = t.detach().cpu().contiguous()
+    raw = c.reshape(-1).view(torch.uint8).numpy().tobytes() if c.numel() else b""
+    return w.bytes(9, raw)
+
+
+def encode_value_info(name: str, dtype: torch.dtype, shape, dynamic: dict | None = None) -> ProtobufWriter:
+    shp = ProtobufWriter()
+    for axis, d in enumerate(shape):
+        dim = ProtobufWriter()
+        if dynamic and axis in dynamic:
+            dim.string(2, dynamic[axis])          # dim_param
+        else:
+            dim.int(1, d)                         # dim_value
+        shp.message(1, dim)
+    tensor_type = ProtobufWriter().int(1, _DTYPE[dtype]).message(2, shp)
+    return ProtobufWriter().string(1, name).message(2, ProtobufWriter().message(1, tensor_type))
+
+
+def encode_attribute(name: str, value) -> ProtobufWriter:
+    a = ProtobufWriter().string(1, name)
+    if isinstance(value, bool) or isinstance(value, int):
+        return a.int(3, int(value)).int(20, 2)                     # INT
+    if isinstance(value, float):
+        return a.float(2, value).int(20, 1)                        # FLOAT
+    if isinstance(value, (list, tuple)) and all(isinstance(v, int) for v in value):
+        for v in value:
+            a.int(8, v)
+        return a.int(20, 7)                                        # INTS
+    if isinstance(value, torch.Tensor):
+        return a.message(5, encode_tensor("", value)).int(20, 4)   # TENSOR
+    raise OnnxExportError("attribute %s: unsupported value %r" % (name, value))
+
+
+def encode_node(op_type: str, inputs, outputs, name: str = "", **attrs) -> ProtobufWriter:
+    n = ProtobufWriter()
+    for i in inputs:
+        n.string(1, i)
+    for o in outputs:
+        n.string(2, o)
+    n.string(3, name or outputs[0]).string(4, op_type)
+    for k, v in attrs.items():
+        n.message(5, encode_attribute(k, v))
+    return n
+
+
+# --------------------------------------------------------------------------- IR -> ONNX
+_SIMPLE_UNARY = {"neg": "Neg", "relu": "Relu", "sigmoid": "Sigmoid", "tanh": "Tanh", "sqrt": "Sqrt", "abs": "Abs",
+                 "exp": "Exp", "log": "Log"}
+_SIMPLE_BINARY = {"add": "Add", "sub": "Sub", "mul": "Mul", "div": "Div"}
+
+
+class _Builder:
+    def __init__(self, cfg: OnnxExportConfig):
+        self.cfg = cfg
+        self.nodes: list[ProtobufWriter] = []
+        self.inits: list[ProtobufWriter] = []
+        self._n = 0
+
+    def fresh(self, hint: str = "t") -> str:
+        self._n += 1
+        return "%s_%d" % (hint, self._n)
+
+    def const(self, value: torch.Tensor, hint: str = "c") -> str:
+        name = self.fresh(hint)
+        self.inits.append(encode_tensor(name, value))
+        return name
+
+    def scalar(self, v: float, dtype: torch.dtype) -> str:
+        return self.const(torch.tensor(v, dtype=dtype), "s")
+
+    def node(self, op: str, inputs, out: str | None = None, **attrs) -> str:
+        out = out or self.fresh(op.lower())
+        self.nodes.append(encode_node(op, inputs, [out], **attrs))
+        return out
+
+
+def _emit(b: _Builder, n, names: dict, out: str) -> None:
+    """Append the ONNX nodes of IR node ``n``; its result must be called ``out``."""
+    ins = [names[i] for i in n.inputs]
+    dt = n.dtype or torch.float32
+    op = n.op
+    if op in _SIMPLE_UNARY:
+        b.node(_SIMPLE_UNARY[op], ins, out)
+    elif op in _SIMPLE_BINARY:
+        b.node(_SIMPLE_BINARY[op], ins, out)
+    elif op == "silu":                                   # x * sigmoid(x): no Silu operator before opset 22
+        b.node("Mul", [ins[0], b.node("Sigmoid", ins)], out)
+    elif op == "gelu":                                   # 0.5 x (1 + erf(x / sqrt 2)): no Gelu before opset 20
+        e = b.node("Erf", [b.node("Mul", [ins[0], b.scalar(1.0 / math.sqrt(2.0), dt)])])
+        half = b.node("Mul", [ins[0], b.scalar(0.5, dt)])
+        b.node("Mul", [half, b.node("Add", [e, b.scalar(1.0, dt)])], out)
+    elif op in ("add_c", "mul_c", "pow_c", "rsub_c", "rdiv_c"):
+        c = b.scalar(float(n.attrs["c"]), dt)
+        kind, args = {"add_c": ("Add", [ins[0], c]), "mul_c": ("Mul", [ins[0], c]), "pow_c": ("Pow", [ins[0], c]),
+                      "rsub_c": ("Sub", [c, ins[0]]), "rdiv_c": ("Div", [c, ins[0]])}[op]
+        b.node(kind, args, out)
+    elif op == "call":
+        _emit_call(b, n, names, out)
+    else:
+        raise OnnxExportError("node %d: IR op %r cannot be exported (export the un-optimised trace)" % (n.id, op))
+
+
+def _emit_call(b: _Builder, n, names: dict, out: str) -> None:
+    tgt, kind, args, kwargs = n.attrs["target"], n.attrs.get("kind"), n.attrs["args"], n.attrs["kwargs"]
+    ins = [names[i] for i in n.inputs]
+
+    def plain(a):
+        return a if not hasattr(a, "id") else None
+
+    if kind == "linear":
+        w = b.const(tgt.weight.detach().t().contiguous(), "weight")
+        y = b.node("MatMul", [ins[0], w], None if tgt.bias is not None else out)
+        if tgt.bias is not None:
+            b.node("Add", [y, b.const(tgt.bias.detach(), "bias")], out)
+    elif kind == "matmul":
+        b.node("MatMul", ins[:2], out)
+    elif kind == "softmax":
+        dim = kwargs.get("dim", plain(args[1]) if len(args) > 1 else -1)
+        b.node("Softmax", ins[:1], out, axis=int(dim))
+    elif kind == "transpose_last":
+        rank = len(n.shape)
+        perm = list(range(rank))
+        perm[-1], perm[-2] = perm[-2], perm[-1]
+        b.node("Transpose", ins[:1], out, perm=perm)
+    elif tgt in ("reshape", "view", torch.reshape, "flatten", torch.flatten) or isinstance(tgt, nn.Flatten):
+        b.node("Reshape", [ins[0], b.const(torch.tensor(list(n.shape), dtype=torch.int64), "shape")], out)
+    elif isinstance(tgt, nn.Dropout) or tgt in (nn.functional.dropout, "contiguous", "detach") or isinstance(tgt, nn.Identity):
+        b.node("Identity", ins[:1], out)
+    else:
+        raise OnnxExportError("node %d: call to %r has no ONNX mapping" % (n.id, getattr(tgt, "__name__", tgt)))
+
+
+def ir_graph_to_onnx(graph, config: OnnxExportConfig | None = None) -> bytes:
+    """Serialise an :class:`~ferrotorch_b200.jit.ir.IrGraph` (as ``jit.trace`` returns it) to the
+    bytes of an ONNX ``ModelProto``."""
+    cfg = config or OnnxExportConfig()
+    b = _Builder(cfg)
+    names: dict[int, str] = {}
+    inputs, n_in = [], 0
+    out_names = {}
+    for k, oid in enumerate(graph.outputs):
+        out_names[oid] = (cfg.output_names[k] if cfg.output_names and k < len(cfg.output_names) else "output_%d" % k)
+    for i in graph.order:
+        n = graph.nodes[i]
+        if n.op == "input":
+            nm = cfg.input_names[n_in] if cfg.input_names and n_in < len(cfg.input_names) else "input_%d" % n_in
+            n_in += 1
+            names[i] = nm
+            inputs.append(encode_value_info(nm, n.dtype, n.shape, cfg.dynamic_axes.get(nm)))
+        elif n.op == "const":
+            names[i] = b.const(n.attrs["value"].detach(), "const")
+        else:
+            names[i] = out_names.get(i) or b.fresh("n%d" % i)
+            _emit(b, n, names, names[i])
+    g = ProtobufWriter()
+    for nd in b.nodes:
+        g.message(1, nd)
+    g.string(2, cfg.model_name)
+    for t in b.inits:
+        g.message(5, t)
+    for vi in inputs:
+        g.message(11, vi)
+    for oid, nm in out_names.items():
+        n = graph.nodes[oid]
+        if n.op in ("input", "const"):                       # an output that is an input / constant: route it through Identity
+            g.message(1, encode_node("Identity", [names[oid]], [nm]))
+        g.message(12, encode_value_info(nm, n.dtype, n.shape, cfg.dynamic_axes.get(nm)))
+    model = ProtobufWriter().int(1, 8).string(2, cfg.producer_name).string(3, cfg.producer_version)
+    model.message(7, g).message(8, ProtobufWriter().string(1, "").int(2, cfg.opset_version))
+    return model.finish()
+
+
+def export_ir_graph_to_onnx(graph, path: str, config: OnnxExportConfig | None = None) -> None:
+    data = ir_graph_to_onnx(graph, config)
+    with open(path, "wb") as f:
+        f.write(data)
+
+
+def export_onnx(model, example_inputs, path: str, config: OnnxExportConfig | None = None) -> None:
+    """Trace ``model`` on ``example_inputs`` and write the ONNX file."""
+    from ..jit.module import trace
+
+    was_training = getattr(model, "training", False)
+    if isinstance(model, nn.Module):
+        model.eval()
+    try:
+        export_ir_graph_to_onnx(trace(model, tuple(example_inputs)), path, config)
+    finally:
+        if isinstance(model, nn.Module) and was_training:
+            model.train()
+
+
+def export_from_program(program, path: str, config: OnnxExportConfig | None = None) -> None:
+    """Export what :func:`ferrotorch_b200.jit.export` froze; its dynamic dimensions become
+    ``dim_param`` entries of the ONNX inputs."""
+    from ..jit.module import trace
+
+    cfg = config or OnnxExportConfig()
+    names = cfg.input_names or ["input_%d" % i for i in range(len(program.meta.input_specs))]
+    dyn = dict(cfg.dynamic_axes)
+    for nm, spec in zip(names, program.meta.input_specs):
+        axes = {k: d.name for k, d in enumerate(spec.shape) if d.is_dynamic()}
+        if axes:
+            dyn.setdefault(nm, axes)
+    cfg = OnnxExportConfig(cfg.opset_version, cfg.model_name, cfg.producer_name, cfg.producer_version, names,
+                           cfg.output_names, dyn)
+    graph = getattr(program, "ir_graph", None)
+    if graph is None:
+        raise OnnxExportError("export_from_program: this program carries no IR graph (it was loaded from bytes); "
+                              "export the module it came from with export_onnx")
+    export_ir_graph_to_onnx(graph, path, cfg)
+
+
+# --------------------------------------------------------------------------- reading back
+@dataclass
+class OnnxNode:
+    op_type: str
+    inputs: list
+    outputs: list
+    attrs: dict
+
+
+@dataclass
+class OnnxModel:
+    ir_version: int
+    producer_name: str
+    opset_version: int
+    graph_name: str
+    nodes: list
+    initializers: dict
+    inputs: list            # (name, dtype, shape) with a str for symbolic dimensions
+    outputs: list
+
+
+def _decode_tensor(data: bytes):
+    dims, dt, name, raw = [], ONNX_FLOAT, "", b""
+    for f, _, v in read_message(data):
+        if f == 1:
+            dims.append(v)
+        elif f == 2:
+            dt = v
+        elif f == 8:
+            name = v.decode()
+        elif f == 9:
+            raw = v
+    dtype = _DTYPE_INV[dt]
+    t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dtype) if raw else torch.empty(0, dtype=dtype)
+    return name, t.reshape(dims)
+
+
+def _decode_value_info(data: bytes):
+    name, dtype, shape = "", torch.float32, []
+    for f, _, v in read_message(data):
+        if f == 1:
+            name = v.decode()
+        elif f == 2:
+            for f2, _, tt in read_message(v):
+                if f2 != 1:
+                    continue
+                for f3, _, x in read_message(tt):
+                    if f3 == 1:
+                        dtype = _DTYPE_INV[x]
+                    elif f3 == 2:
+                        for _, _, dim in read_message(x):
+                            d = read_message(dim)
+                            shape.append(d[0][2].decode() if d and d[0][0] == 2 else (d[0][2] if d else 0))
+    return name, dtype, shape
+
+
+def _decode_node(data: bytes) -> OnnxNode:
+    n = OnnxNode("", [], [], {})
+    for f, _, v in read_message(data):
+        if f == 1:
+            n.inputs.append(v.decode())
+        elif f == 2:
+            n.outputs.append(v.decode())
+        elif f == 4:
+            n.op_type = v.decode()
+        elif f == 5:
+            name, val, ints = "", None, []
+            for fa, _, x in read_message(v):
+                if fa == 1:
+                    name = x.decode()
+                elif fa == 2:
+                    val = x
+                elif fa == 3:
+                    val = x - (1 << 64) if x >= 1 << 63 else x
+                elif fa == 5:
+                    val = _decode_tensor(x)[1]
+                elif fa == 8:
+                    ints.append(x - (1 << 64) if x >= 1 << 63 else x)
+            n.attrs[name] = ints if ints else val
+    return n
+
+
+def load_onnx(data) -> OnnxModel:
+    """Parse the subset of ``ModelProto`` this module writes (bytes or a path)."""
+    if isinstance(data, str):
+        with open(data, "rb") as f:
+            data = f.read()
+    m = OnnxModel(0, "", 0, "", [], {}, [], [])
+    for f, _, v in read_message(data):
+        if f == 1:
+            m.ir_version = v
+        elif f == 2:
+            m.producer_name = v.decode()
+        elif f == 8:
+            for f2, _, x in read_message(v):
+                if f2 == 2:
+                    m.opset_version = x
+        elif f == 7:
+            for f2, _, x in read_message(v):
+                if f2 == 1:
+                    m.nodes.append(_decode_node(x))
+                elif f2 == 2:
+                    m.graph_name = x.decode()
+                elif f2 == 5:
+                    name, t = _decode_tensor(x)
+                    m.initializers[name] = t
+                elif f2 == 11:
+                    m.inputs.append(_decode_value_info(x))
+                elif f2 == 12:
+                    m.outputs.append(_decode_value_info(x))
+    if not m.nodes and not m.outputs:
+        raise OnnxExportError("not an ONNX model this module can read")
+    return m
+
+
+_EVAL = {
+    "Neg": torch.neg, "Relu": torch.relu, "Sigmoid": torch.sigmoid, "Tanh": torch.tanh, "Sqrt": torch.sqrt, "Abs": torch.abs,
+    "Exp": torch.exp, "Log": torch.log, "Erf": torch.erf, "Add": torch.add, "Sub": torch.sub, "Mul": torch.mul,
+    "Div": torch.div, "Pow": torch.pow, "MatMul": torch.matmul, "Identity": lambda x: x,
+}
+
+
+def run_onnx(model: OnnxModel, *inputs: torch.Tensor) -> list[torch.Tensor]:
+    """Evaluate the model with torch operators, following the ONNX operator definitions: a
+    reference run for checking an export where no ONNX runtime is installed."""
+    if len(inputs) != len(model.inputs):
+        raise OnnxExportError("the model takes %d inputs, got %d" % (len(model.inputs), len(inputs)))
+    env = dict(model.initializers)
+    for (name, dtype, shape), t in zip(model.inputs, inputs):
+        if t.dtype != dtype or len(shape) != t.dim() or any(isinstance(d, int) and d != s for d, s in zip(shape, t.shape)):
+            raise OnnxExportError("input %s: expected %s %s, got %s %s" % (name, dtype, shape, t.dtype, tuple(t.shape)))
+        env[name] = t
+    for n in model.nodes:
+        xs = [env[i] for i in n.inputs]
+        if n.op_type in _EVAL:
+            y = _EVAL[n.op_type](*xs)
+        elif n.op_type == "Softmax":
+            y = torch.softmax(xs[0], dim=n.attrs.get("axis", -1))
+        elif n.op_type == "Transpose":
+            y = xs[0].permute(*n.attrs["perm"])
+        elif n.op_type == "Reshape":
+            y = xs[0].reshape([int(v) for v in xs[1].tolist()])
+        else:
+            raise OnnxExportError("reference evaluator: operator %s is not implemented" % n.op_type)
+        env[n.outputs[0]] = y
+    return [env[name] for name, _, _ in model.outputs]

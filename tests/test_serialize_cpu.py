@@ -202,3 +202,61 @@ def test_int4_checkpoint_layouts_round_trip():
     x = torch.randn(3, 256)
     ref = x @ d.t()
     assert float((lin(x) - ref).norm() / ref.norm()) < 0.15      # a second 4-bit rounding
+
+
+def test_onnx_export_round_trip_without_an_onnx_package(tmp_path):
+    """The hand-written protobuf encoder: export, parse back, evaluate with the reference
+    evaluator, compare with the module."""
+    import ferrotorch_b200.serialize as S
+    from ferrotorch_b200.serialize import onnx as O
+    from torch import nn
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.v, self.o = nn.Linear(8, 8), nn.Linear(8, 8, bias=False), nn.Linear(8, 8), nn.Linear(8, 4)
+
+        def forward(self, x):
+            a = torch.softmax(torch.matmul(self.q(x), self.k(x).transpose(-1, -2)) * 0.35, dim=-1)
+            h = torch.matmul(a, self.v(x))
+            h = torch.nn.functional.gelu(h) + torch.nn.functional.silu(x) - torch.tanh(x) / 2.0
+            return self.o(h.reshape(2, 5, 8)).relu(), (1.0 - h).abs().sqrt()
+
+    torch.manual_seed(0)
+    m, x = Net().eval(), torch.randn(2, 5, 8)
+    path = str(tmp_path / "m.onnx")
+    cfg = S.OnnxExportConfig(input_names=["x"], output_names=["y", "z"], dynamic_axes={"x": {0: "batch"}})
+    S.export_onnx(m, (x,), path, cfg)
+    model = S.load_onnx(path)
+    assert (model.ir_version, model.opset_version, model.producer_name) == (8, 17, "ferrotorch_b200")
+    assert model.inputs == [("x", torch.float32, ["batch", 5, 8])]
+    assert model.outputs == [("y", torch.float32, [2, 5, 4]), ("z", torch.float32, [2, 5, 8])]
+    ops = {n.op_type for n in model.nodes}
+    assert {"MatMul", "Softmax", "Transpose", "Erf", "Sigmoid", "Reshape", "Relu"} <= ops and "Gelu" not in ops   # opset 17
+    assert sum(1 for t in model.initializers.values() if t.dim() == 2) == 4                                       # the four weights
+    y, z = S.run_onnx(model, x)
+    wy, wz = m(x)
+    assert torch.allclose(y, wy, atol=1e-6) and torch.allclose(z, wz, atol=1e-6)
+    with pytest.raises(O.OnnxExportError):
+        S.run_onnx(model, x.double())
+    with pytest.raises(O.OnnxExportError, match="no ONNX mapping"):
+        S.export_onnx(lambda t: torch.cumsum(t, 0), (x,), str(tmp_path / "bad.onnx"))
+    # wire format primitives
+    w = O.ProtobufWriter().int(1, 300).int(2, -1).string(3, "ab").float(4, 1.5)
+    assert w.finish()[:3] == bytes([0x08, 0xAC, 0x02])
+    fields = O.read_message(w.finish())
+    assert fields[0] == (1, 0, 300) and fields[1][2] == (1 << 64) - 1 and fields[2] == (3, 2, b"ab") and fields[3] == (4, 5, 1.5)
+    for junk in (bytes([0x08]), bytes([0x0A, 0x05, 0x01]), bytes([0x0B])):
+        with pytest.raises(O.OnnxExportError):
+            O.read_message(junk)
+    # an exported program carries its dynamic dimensions into the ONNX inputs
+    from ferrotorch_b200 import jit as J
+    lin = nn.Sequential(nn.Linear(4, 3), nn.Tanh()).eval()
+    ep = J.export(lin, (torch.randn(3, 4),), [J.InputSpec([J.DimSpec.dynamic_range("n", 2, 16), J.DimSpec.static(4)])])
+    S.export_from_program(ep, str(tmp_path / "p.onnx"))
+    pm = S.load_onnx(str(tmp_path / "p.onnx"))
+    assert pm.inputs[0][2] == ["n", 4]
+    t = torch.randn(7, 4)
+    assert torch.allclose(S.run_onnx(pm, t)[0], lin(t), atol=1e-6)
+    with pytest.raises(O.OnnxExportError, match="no IR graph"):
+        S.export_from_program(J.ExportedProgram.deserialize(ep.serialize()), str(tmp_path / "q.onnx"))
