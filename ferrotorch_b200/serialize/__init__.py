@@ -4,6 +4,7 @@ from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_
                     load_pytorch_state_dict, load_safetensors, load_safetensors_sharded, load_state_dict,
                     ShardProgress, load_safetensors_auto, load_safetensors_mmap, load_safetensors_sharded_filtered,
                     load_safetensors_sharded_mmap, load_safetensors_sharded_with_progress, validate_checkpoint,
+                    load_pytorch_state_dict_mmap, parse_pickle, pickle_imports,
                     loads_state_dict, save_checkpoint, save_reference_checkpoint, save_pytorch, save_safetensors, save_safetensors_sharded,
                     save_state_dict)
 

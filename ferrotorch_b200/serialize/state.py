@@ -165,6 +165,49 @@ def load_pytorch_state_dict(path: str, device="cpu") -> dict[str, torch.Tensor]:
     return {k: v for k, v in sd.items() if isinstance(v, torch.Tensor)}
 
 
+def load_pytorch_state_dict_mmap(path: str) -> dict[str, torch.Tensor]:
+    """The same with the tensor data memory-mapped from the file instead of read into memory
+    (zip-format checkpoints only; pytorch_import.rs ``load_pytorch_state_dict_mmap``)."""
+    sd = torch.load(path, map_location="cpu", weights_only=True, mmap=True)
+    if isinstance(sd, dict) and "state_dict" in sd and isinstance(sd["state_dict"], dict):
+        sd = sd["state_dict"]
+    return {k: v for k, v in sd.items() if isinstance(v, torch.Tensor)}
+
+
+def parse_pickle(data: bytes) -> list[tuple[str, object]]:
+    """The opcodes of a pickle stream as ``(name, argument)`` pairs, without executing anything:
+    for inspecting what a checkpoint would import before loading it (the reference walks the same
+    stream with its own pickle machine, pytorch_import.rs:154)."""
+    import pickletools
+
+    try:
+        return [(op.name, arg) for op, arg, _ in pickletools.genops(data)]
+    except Exception as e:  # noqa: BLE001
+        raise ValueError("not a well-formed pickle stream: %s" % e)
+
+
+def pickle_imports(path: str) -> list[str]:
+    """``module.name`` of every global a ``.pt`` file's pickle refers to (zip or legacy format)."""
+    import zipfile
+
+    if zipfile.is_zipfile(path):
+        with zipfile.ZipFile(path) as z:
+            name = next(n for n in z.namelist() if n.endswith("data.pkl"))
+            data = z.read(name)
+    else:
+        with open(path, "rb") as f:
+            data = f.read()
+    out, strings = [], []
+    for op, arg in parse_pickle(data):
+        if op == "GLOBAL":
+            out.append(str(arg).replace(" ", "."))
+        elif op in ("SHORT_BINUNICODE", "BINUNICODE", "UNICODE"):
+            strings.append(str(arg))
+        elif op == "STACK_GLOBAL" and len(strings) >= 2:
+            out.append("%s.%s" % (strings[-2], strings[-1]))
+    return sorted(set(out))
+
+
 def save_pytorch(state: dict[str, torch.Tensor], path: str) -> None:
     torch.save({k: v.detach().cpu() for k, v in state.items()}, path)
 

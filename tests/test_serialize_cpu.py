@@ -260,3 +260,23 @@ def test_onnx_export_round_trip_without_an_onnx_package(tmp_path):
     assert torch.allclose(S.run_onnx(pm, t)[0], lin(t), atol=1e-6)
     with pytest.raises(O.OnnxExportError, match="no IR graph"):
         S.export_from_program(J.ExportedProgram.deserialize(ep.serialize()), str(tmp_path / "q.onnx"))
+
+
+def test_pickle_inspection_and_mmap_load(tmp_path):
+    import ferrotorch_b200.serialize as S
+
+    sd = {"w": torch.arange(6.0).view(2, 3), "b": torch.ones(2, dtype=torch.bfloat16)}
+    p = str(tmp_path / "m.pt")
+    S.save_pytorch(sd, p)
+    mm = S.load_pytorch_state_dict_mmap(p)
+    assert torch.equal(mm["w"], sd["w"]) and mm["b"].dtype == torch.bfloat16
+    imports = S.pickle_imports(p)
+    assert "torch._utils._rebuild_tensor_v2" in imports and all(i.startswith(("torch.", "collections.")) for i in imports)
+    import pickle
+    ops = S.parse_pickle(pickle.dumps({"a": 1}, protocol=2))
+    assert ops[0][0] == "PROTO" and ops[-1][0] == "STOP" and ("BININT1", 1) in ops
+    with pytest.raises(ValueError):
+        S.parse_pickle(b"\x80\x02}q\x00(X\x01")            # truncated stream
+    evil = str(tmp_path / "evil.pt")
+    torch.save({"x": os.path.join}, evil)                  # a function reference: visible before anything is loaded
+    assert any("join" in i for i in S.pickle_imports(evil))
