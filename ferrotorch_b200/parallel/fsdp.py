@@ -73,8 +73,32 @@ class FSDP(nn.Module):
             p.data = full[: shape.numel()].view(shape)
         self._gathered = True
 
+    def prefetch_forward_params(self):
+        """Start the all-gather of every parameter on a helper thread and return the handle; the
+        next ``forward`` waits for it instead of gathering itself, so the gather overlaps whatever
+        the caller does in between -- the data loading of the next batch, the optimizer step of
+        another module (fsdp.rs:341-368).  One collective is in flight per group at a time: do not
+        issue other collectives on the shard group before the forward."""
+        from .dist_checkpoint import PendingCollective
+
+        if self.strategy == ShardingStrategy.NO_SHARD:
+            return None
+
+        def gather_all():
+            return [self.shard_group.all_gather(sh.detach()) for sh in self.shards]
+
+        self._prefetch = PendingCollective(gather_all)
+        return self._prefetch
+
     def forward(self, *a, **kw):
-        if not self._gathered or self.strategy == ShardingStrategy.SHARD_GRAD_OP:
+        pending = getattr(self, "_prefetch", None)
+        if pending is not None:
+            fulls = pending.wait()
+            self._prefetch = None
+            for p, full, shape in zip(self.params, fulls, self.shapes):
+                p.data = full[: shape.numel()].view(shape)
+            self._gathered = True
+        elif not self._gathered or self.strategy == ShardingStrategy.SHARD_GRAD_OP:
             self.gather_parameters()
         return self.module(*a, **kw)
 

@@ -199,3 +199,57 @@ def test_p2p_verbs_probes_and_aliases():
     for fn in (P.gpu_allreduce, P.gpu_broadcast):
         with pytest.raises(UnsupportedOp):
             fn(torch.zeros(2))                      # host tensors are not silently bounced through the CPU path
+
+
+@pytest.mark.parametrize("world", [2, 3, 5])
+def test_portable_ring_algorithms_on_simulated_ranks(world):
+    from ferrotorch_b200.parallel import ring
+    from ferrotorch_b200.parallel.backend import InvalidRank, run_simulated
+
+    def body(g):
+        t = torch.arange(11, dtype=torch.float64) * (g.rank + 1)
+        s = ring.ring_all_reduce(g, t.clone(), "sum")
+        m = ring.ring_all_reduce(g, t.clone().view(11, 1), "mean")
+        outs = []
+        for root in range(g.world_size):
+            b = torch.full((4,), float(g.rank))
+            outs.append(ring.tree_broadcast(g, b, root).tolist())
+        ring.ring_barrier(g)
+        try:
+            ring.tree_broadcast(g, torch.zeros(1), g.world_size)
+            bad = "accepted"
+        except InvalidRank:
+            bad = "refused"
+        return s, m, outs, bad
+
+    tot = world * (world + 1) / 2
+    for s, m, outs, bad in run_simulated(world, body):
+        assert torch.allclose(s, torch.arange(11, dtype=torch.float64) * tot)
+        assert torch.allclose(m.view(-1), torch.arange(11, dtype=torch.float64) * tot / world) and m.shape == (11, 1)
+        assert outs == [[float(root)] * 4 for root in range(world)] and bad == "refused"
+
+
+def test_fsdp_prefetch_overlaps_the_gather():
+    from ferrotorch_b200.parallel.backend import run_simulated
+    from ferrotorch_b200.parallel.fsdp import FSDP, ShardingStrategy
+
+    import copy
+
+    torch.manual_seed(0)
+    proto = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 3))
+
+    def body(g):
+        m = copy.deepcopy(proto)                                     # every rank starts from the same weights
+        ref = [p.detach().clone() for p in m.parameters()]
+        f = FSDP(m, g, ShardingStrategy.FULL_SHARD)
+        assert all(p.numel() == 0 for p in m.parameters())           # sharded: the full weights are gone
+        h = f.prefetch_forward_params()
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(g.rank))
+        y = f(x)                                                     # waits for the handle, gathers nothing itself
+        assert h.is_done() and f._prefetch is None
+        want = torch.nn.functional.linear(torch.tanh(torch.nn.functional.linear(x, ref[0], ref[1])), ref[2], ref[3])
+        y.sum().backward()
+        f.sync_gradients()
+        return torch.allclose(y, want, atol=1e-6), all(s.grad is not None for s in f.shard_parameters())
+
+    assert all(a and b for a, b in run_simulated(2, body))
