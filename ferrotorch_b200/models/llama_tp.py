@@ -173,3 +173,58 @@ def make_tp_trainer(model: TPLlamaForCausalLM, **kw):
     if model.tp.world > 1:
         tr.model_parallel_group = model.tp.group
     return tr
+
+
+def hybrid_groups(tp_size: int, backend: str | None = None):
+    """Split the default process group into a ``dp x tp`` mesh, rank ``= dp_index * tp_size +
+    tp_index`` (tensor-parallel peers are neighbours, i.e. share a node's NVLink domain).  Every
+    rank must call this; returns ``(tp_group, dp_group)`` of the calling rank
+    (device_mesh.rs:37-203 gives the same row-major rank <-> coordinate maps)."""
+    import torch.distributed as dist
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if tp_size <= 0 or world % tp_size:
+        raise ValueError("hybrid_groups: world size %d is not a multiple of tp_size %d" % (world, tp_size))
+    dp_size = world // tp_size
+    mine_tp = mine_dp = None
+    for d in range(dp_size):
+        ranks = list(range(d * tp_size, (d + 1) * tp_size))
+        g = dist.new_group(ranks, backend=backend)
+        if rank in ranks:
+            mine_tp = g
+    for t in range(tp_size):
+        ranks = list(range(t, world, tp_size))
+        g = dist.new_group(ranks, backend=backend)
+        if rank in ranks:
+            mine_dp = g
+    return mine_tp, mine_dp
+
+
+def add_data_parallel(trainer, dp_group):
+    """Average the gradient arena of a :class:`FlatTrainer` over ``dp_group`` before every update
+    (after whatever ``pre_update`` hook it already has, before the norm / clip).  With a
+    tensor-parallel trainer this gives TP x DP: the TP collectives are the fused kernels, the DP
+    reduction is one all-reduce of the arena on the process group's own back-end."""
+    import torch.distributed as dist
+
+    inner = trainer.pre_update
+
+    def hook():
+        if inner is not None:
+            inner()
+        n = dist.get_world_size(dp_group)
+        if n > 1:
+            g = trainer.arena.grads
+            if g.is_cuda:
+                dist.all_reduce(g, op=dist.ReduceOp.AVG, group=dp_group)
+            else:                                   # gloo has no AVG
+                dist.all_reduce(g, group=dp_group)
+                g.div_(n)
+
+    trainer.pre_update = hook
+    return trainer
+
+
+def make_hybrid_trainer(model: TPLlamaForCausalLM, dp_group, **kw):
+    """:func:`make_tp_trainer` plus data parallelism across ``dp_group`` (see :func:`hybrid_groups`)."""
+    return add_data_parallel(make_tp_trainer(model, **kw), dp_group)

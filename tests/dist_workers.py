@@ -282,3 +282,49 @@ def elastic_case(rank, world, port, q, root):
         import traceback
 
         q.put((rank, "ERR " + traceback.format_exc()[-1500:]))
+
+
+def hybrid_case(rank, world, port, q):
+    """dp x tp process groups over gloo, and data parallelism added to a flat trainer: two replicas
+    with half the batch each follow the same trajectory as one process with the whole batch."""
+    try:
+        import os
+
+        import torch
+        import torch.distributed as dist
+
+        from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+        from ferrotorch_b200.models.llama_tp import add_data_parallel, hybrid_groups
+        from ferrotorch_b200.train.engine import FlatTrainer
+
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        tp, dp = hybrid_groups(2)
+        a = torch.tensor([float(rank)])
+        b = a.clone()
+        dist.all_reduce(a, group=tp)                  # world 4, tp 2: tp groups {0,1} {2,3}, dp groups {0,2} {1,3}
+        dist.all_reduce(b, group=dp)
+        sums = (a.item(), b.item(), dist.get_world_size(tp), dist.get_world_size(dp))
+        cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1,
+                          num_attention_heads=2, num_key_value_heads=1)
+        torch.manual_seed(0)
+        model = LlamaForCausalLM(cfg)
+        tr = add_data_parallel(FlatTrainer(model, lr=1e-2, weight_decay=0.0, max_grad_norm=1.0), dp)
+        g = torch.Generator().manual_seed(5)
+        tokens = torch.randint(0, 64, (4, 9), generator=g)            # the global batch of the dp group
+        k = dist.get_rank(dp)
+        mine = tokens[2 * k:2 * k + 2]
+        losses = [float(tr.step(mine[:, :-1], mine[:, 1:])) for _ in range(3)]
+        torch.manual_seed(0)
+        ref_model = LlamaForCausalLM(cfg)
+        ref = FlatTrainer(ref_model, lr=1e-2, weight_decay=0.0, max_grad_norm=1.0)
+        for _ in range(3):
+            ref.step(tokens[:, :-1], tokens[:, 1:])
+        diff = max(float((p - r).abs().max()) for p, r in zip(model.parameters(), ref_model.parameters()))
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, (sums, diff, losses)))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "ERR %r %s" % (e, traceback.format_exc())))

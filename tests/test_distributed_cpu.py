@@ -266,3 +266,13 @@ def test_heartbeat_clean_leave_and_store_barrier(tmp_path):
     barrier(store, "solo", 0, [0], limit=1.0)
     with pytest.raises(RankFailure):
         barrier(store, "pair", 0, [0, 1], limit=0.2)
+
+
+def test_hybrid_mesh_groups_and_data_parallel_trainer_gloo():
+    out = _spawn(W.hybrid_case, 4)
+    want = {0: (1.0, 2.0), 1: (1.0, 4.0), 2: (5.0, 2.0), 3: (5.0, 4.0)}
+    for r in range(4):
+        (tp_sum, dp_sum, tp_n, dp_n), diff, losses = out[r]
+        assert (tp_sum, dp_sum) == want[r] and (tp_n, dp_n) == (2, 2)
+        assert diff < 2e-5, diff                       # two half-batch replicas == one full-batch process
+        assert losses[-1] < losses[0]
