@@ -253,3 +253,34 @@ def test_fsdp_prefetch_overlaps_the_gather():
         return torch.allclose(y, want, atol=1e-6), all(s.grad is not None for s in f.shard_parameters())
 
     assert all(a and b for a, b in run_simulated(2, body))
+
+
+@pytest.mark.parametrize("world,causal", [(2, True), (4, True), (4, False), (3, True)])
+def test_ring_and_ulysses_attention_equal_full_attention(world, causal):
+    from ferrotorch_b200.ops import reference as R
+    from ferrotorch_b200.parallel import context_parallel as CP
+    from ferrotorch_b200.parallel.backend import run_simulated
+
+    torch.manual_seed(0)
+    B, S_loc, Hq, Hkv, D = 2, 5, 12, 12 if world == 3 else 4, 8
+    S = world * S_loc
+    q, k, v = torch.randn(B, S, Hq, D), torch.randn(B, S, Hkv, D), torch.randn(B, S, Hkv, D)
+    want, _ = R.attention(q, k, v, causal=causal)
+
+    def body(g):
+        sl = slice(g.rank * S_loc, (g.rank + 1) * S_loc)
+        ring = CP.ring_attention(q[:, sl], k[:, sl], v[:, sl], g, causal)
+        uly = CP.ulysses_attention(q[:, sl], k[:, sl], v[:, sl], g, causal) if Hkv % g.world_size == 0 else None
+        return ring, uly
+
+    for r, (ring, uly) in enumerate(run_simulated(world, body)):
+        sl = slice(r * S_loc, (r + 1) * S_loc)
+        assert torch.allclose(ring, want[:, sl], atol=1e-5), (r, (ring - want[:, sl]).abs().max())
+        if uly is not None:
+            assert torch.allclose(uly, want[:, sl], atol=1e-5), (r, (uly - want[:, sl]).abs().max())
+    o1, l1 = R.attention(q, k[:, :7], v[:, :7], causal=False)
+    o2, l2 = R.attention(q, k[:, 7:], v[:, 7:], causal=False)
+    merged, _ = CP.merge_attention(o1, l1, o2, l2)
+    assert torch.allclose(merged, R.attention(q, k, v, causal=False)[0], atol=1e-5)
+    with pytest.raises(ValueError):
+        run_simulated(2, lambda g: CP.ulysses_attention(q[:, :2, :3], k[:, :2, :1], v[:, :2, :1], g))
