@@ -232,3 +232,83 @@ class DualTensor:
 
     def sum(self):
         return DualTensor(self.primal.sum(), self.tangent.sum())
+
+
+# --------------------------------------------------------------------------- autocast policy and debug events
+class AutocastCategory:
+    """How an op treats its inputs under autocast (autocast_ops.rs:30-58)."""
+    ReducedPrecision, FullPrecision, Passthrough = "reduced_precision", "full_precision", "passthrough"
+
+
+_REDUCED = {"mm", "matmul", "bmm", "linear", "conv1d", "conv2d", "conv3d", "conv_transpose2d", "addmm", "einsum",
+            "scaled_dot_product_attention"}
+_FULL = {"sum", "mean", "prod", "softmax", "log_softmax", "layer_norm", "batch_norm", "group_norm", "rms_norm",
+         "cross_entropy", "mse_loss", "bce_with_logits", "exp", "log", "pow"}
+
+
+def autocast_category(op_name: str) -> str:
+    """The policy table: GEMM-shaped ops run in the autocast dtype, reductions / normalisations /
+    losses stay in fp32, everything else follows its inputs."""
+    if op_name in _REDUCED:
+        return AutocastCategory.ReducedPrecision
+    if op_name in _FULL:
+        return AutocastCategory.FullPrecision
+    return AutocastCategory.Passthrough
+
+
+def is_autocast_enabled(device_type: str | None = None) -> bool:
+    if device_type is not None:
+        return torch.is_autocast_enabled(device_type)
+    return torch.is_autocast_enabled("cuda") or torch.is_autocast_enabled("cpu")
+
+
+def should_cast_to_reduced(op_name: str) -> bool:
+    return is_autocast_enabled() and autocast_category(op_name) == AutocastCategory.ReducedPrecision
+
+
+def should_keep_full_precision(op_name: str) -> bool:
+    return is_autocast_enabled() and autocast_category(op_name) == AutocastCategory.FullPrecision
+
+
+_autocast_debug = False
+_autocast_events: list = []
+_autocast_mode = None
+
+
+class _AutocastRecorder(torch.utils._python_dispatch.TorchDispatchMode):
+    """Sees every ATen call below autocast: records the op with the dtypes that reached it."""
+
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        out = func(*args, **(kwargs or {}))
+        if is_autocast_enabled():
+            name = func.overloadpacket.__name__
+            ins = [str(a.dtype).replace("torch.", "") for a in torch.utils._pytree.tree_flatten((args, kwargs or {}))[0]
+                   if isinstance(a, torch.Tensor)]
+            o = out if isinstance(out, torch.Tensor) else None
+            _autocast_events.append({"op": name, "category": autocast_category(name), "inputs": ins,
+                                     "output": str(o.dtype).replace("torch.", "") if o is not None else None})
+        return out
+
+
+def set_autocast_debug(on: bool) -> None:
+    """While on, every op executed inside an ``autocast`` region is logged with its policy category
+    and the dtypes it actually ran in; :func:`drain_autocast_events` returns and clears the log
+    (autocast_ops.rs:86-132)."""
+    global _autocast_debug, _autocast_mode
+    if on and not _autocast_debug:
+        _autocast_mode = _AutocastRecorder()
+        _autocast_mode.__enter__()
+    elif not on and _autocast_debug and _autocast_mode is not None:
+        _autocast_mode.__exit__(None, None, None)
+        _autocast_mode = None
+    _autocast_debug = bool(on)
+
+
+def is_autocast_debug() -> bool:
+    return _autocast_debug
+
+
+def drain_autocast_events() -> list:
+    out = list(_autocast_events)
+    _autocast_events.clear()
+    return out

@@ -130,3 +130,32 @@ def test_core_vocabulary():
     assert torch.allclose(causal, want, atol=1e-5)
     alibi = C.flex_attention(qq, kk, vv, lambda s, b, h, i, j: s - (h + 1) * (i - j).abs())
     assert not torch.allclose(alibi, C.flex_attention(qq, kk, vv), atol=1e-3)
+
+
+def test_autocast_policy_table_and_debug_events():
+    assert A.autocast_category("matmul") == A.AutocastCategory.ReducedPrecision
+    assert A.autocast_category("softmax") == A.AutocastCategory.FullPrecision
+    assert A.autocast_category("relu") == A.AutocastCategory.Passthrough
+    assert not A.should_cast_to_reduced("matmul") and not A.is_autocast_enabled()
+    lin = torch.nn.Linear(4, 4)
+    x = torch.randn(2, 4)
+    A.set_autocast_debug(True)
+    try:
+        lin(x)                                           # outside autocast: nothing is logged
+        assert A.drain_autocast_events() == []
+        with A.autocast("cpu", dtype=torch.bfloat16):
+            assert A.should_cast_to_reduced("linear") and A.should_keep_full_precision("layer_norm")
+            y = lin(x)
+            z = torch.softmax(y, -1)
+        ev = A.drain_autocast_events()
+    finally:
+        A.set_autocast_debug(False)
+    assert y.dtype == torch.bfloat16 and not A.is_autocast_debug()
+    gemm = [e for e in ev if e["op"] in ("addmm", "mm", "linear")]
+    assert gemm and gemm[0]["category"] == A.AutocastCategory.ReducedPrecision and set(gemm[0]["inputs"]) == {"bfloat16"}
+    soft = [e for e in ev if e["op"] in ("_softmax", "softmax")]
+    # the log shows what really ran: on CUDA the softmax is promoted to fp32, the CPU autocast leaves it
+    assert soft and soft[0]["category"] == A.AutocastCategory.FullPrecision and soft[0]["output"] == str(z.dtype)[6:]
+    assert A.drain_autocast_events() == []
+    lin(x)
+    assert A.drain_autocast_events() == []               # recorder is off again
