@@ -26,7 +26,6 @@ no_grad, enable_grad, inference_mode, set_grad_enabled = (torch.no_grad, torch.e
                                                           torch.set_grad_enabled)
 is_grad_enabled, is_inference_mode = torch.is_grad_enabled, torch.is_inference_mode_enabled
 detect_anomaly = torch.autograd.detect_anomaly
-autocast = torch.autocast
 jacobian = torch.autograd.functional.jacobian
 
 
@@ -235,6 +234,27 @@ class DualTensor:
 
 
 # --------------------------------------------------------------------------- autocast policy and debug events
+_autocast_depth = 0
+
+
+class autocast(torch.autocast):
+    """``torch.autocast`` that also tells the debug recorder when a region is active (inside a
+    dispatch-mode handler torch reports autocast as off, so the recorder cannot ask torch)."""
+
+    def __enter__(self):
+        global _autocast_depth
+        r = super().__enter__()
+        if self._enabled:
+            _autocast_depth += 1
+        return r
+
+    def __exit__(self, *exc):
+        global _autocast_depth
+        if self._enabled:
+            _autocast_depth -= 1
+        return super().__exit__(*exc)
+
+
 class AutocastCategory:
     """How an op treats its inputs under autocast (autocast_ops.rs:30-58)."""
     ReducedPrecision, FullPrecision, Passthrough = "reduced_precision", "full_precision", "passthrough"
@@ -249,6 +269,7 @@ _FULL = {"sum", "mean", "prod", "softmax", "log_softmax", "layer_norm", "batch_n
 def autocast_category(op_name: str) -> str:
     """The policy table: GEMM-shaped ops run in the autocast dtype, reductions / normalisations /
     losses stay in fp32, everything else follows its inputs."""
+    op_name = op_name.lstrip("_")              # ATen spells some of them "_softmax", "_log_softmax"
     if op_name in _REDUCED:
         return AutocastCategory.ReducedPrecision
     if op_name in _FULL:
@@ -280,7 +301,7 @@ class _AutocastRecorder(torch.utils._python_dispatch.TorchDispatchMode):
 
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
         out = func(*args, **(kwargs or {}))
-        if is_autocast_enabled():
+        if _autocast_depth > 0:
             name = func.overloadpacket.__name__
             ins = [str(a.dtype).replace("torch.", "") for a in torch.utils._pytree.tree_flatten((args, kwargs or {}))[0]
                    if isinstance(a, torch.Tensor)]
