@@ -33,6 +33,7 @@ class ProfileConfig:
     record_memory: bool = False
     with_flops: bool = True
     cuda_events: bool = True
+    nvtx: bool = False          # also open an NVTX range per scope (shows up in Nsight timelines)
 
 
 class ProfileSchedule:
@@ -108,9 +109,14 @@ class Profiler:
         if use_cuda:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
+        nvtx = self.cfg.nvtx and torch.cuda.is_available()
+        if nvtx:
+            torch.cuda.nvtx.range_push("%s:%s" % (category, name))
         try:
             yield
         finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
             flops = estimate_flops(op or name, shapes) if self.cfg.with_flops and shapes else None
             ev = ProfileEvent(name, category, start, self._now_us() - start, "cpu",
                               tuple(shapes) if self.cfg.record_shapes else (), flops, nbytes)
