@@ -397,7 +397,7 @@ def test_name_level_parity_helpers(tmp_path):
     torch.save({"evil": object()}, str(tmp_path / "bad.pt"))
     with pytest.raises(Exception):
         S.validate_checkpoint(str(tmp_path / "bad.pt"))                # arbitrary pickled objects are refused
-    assert isinstance(S.OnnxExportConfig(opset_version=17), dict)
+    assert S.OnnxExportConfig(opset_version=17).opset_version == 17
     # optim: differentiable steps let an outer loss see through the update
     assert O.ExponentialMovingAverage is O.EMA and O.Kfac is O.NaturalGradient
     w = torch.tensor([1.0, -2.0], requires_grad=True)
