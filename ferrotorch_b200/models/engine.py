@@ -24,7 +24,6 @@ residual add: two launches per layer instead of one fused kernel.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.distributed as dist

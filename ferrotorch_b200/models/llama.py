@@ -14,7 +14,7 @@ GGUF checkpoints load unchanged.
 from __future__ import annotations
 
 import json
-from dataclasses import asdict, dataclass, field
+from dataclasses import asdict, dataclass
 
 import torch
 from torch import nn

@@ -8,7 +8,6 @@ scaling modes of transformer.rs:66-326, ``SwiGLU`` is ``down(act(gate(x)) * up(x
 """
 from __future__ import annotations
 
-import math
 
 import torch
 from torch import nn

@@ -19,7 +19,6 @@ from torch import nn
 
 from .. import _native
 from . import functional as F
-from . import reference as ref
 
 _i, _ll, _vp = _native._i, _native._ll, _native._vp
 _native.register_protos({

@@ -10,7 +10,6 @@ generic path for modules that do not go through the flat-arena trainer; GPU trai
 """
 from __future__ import annotations
 
-import threading
 
 import torch
 from torch import nn

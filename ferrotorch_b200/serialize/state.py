@@ -14,13 +14,12 @@ Covers the reference's ``ferrotorch-serialize``:
 """
 from __future__ import annotations
 
-import io
 from dataclasses import dataclass
 import json
 import os
 import struct
 import threading
-from typing import Callable, Iterable
+from typing import Callable
 
 import torch
 

@@ -16,8 +16,7 @@ pair, one update launch per parameter group.
 """
 from __future__ import annotations
 
-import math
-from typing import Callable, Iterable
+from typing import Callable
 
 import torch
 from torch import nn
