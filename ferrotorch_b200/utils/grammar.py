@@ -446,6 +446,7 @@ class SchemaGrammar:
         self.schema = schema if isinstance(schema, Schema) else Schema.from_json_schema(schema)
         self._m = _Machine(self.schema, whitespace_permissive)
         self.states: frozenset = frozenset([self._m.start()])
+        self._memo: dict = {}          # (state set, character) -> state set; the mask walk repeats these endlessly
 
     def with_whitespace_permissive(self, on: bool) -> "SchemaGrammar":
         g = SchemaGrammar(self.schema, on)
@@ -461,10 +462,18 @@ class SchemaGrammar:
         return any(self._m.complete(s) for s in self.states)
 
     def _advance(self, states, c: str) -> frozenset:
+        key = (states, c)
+        hit = self._memo.get(key)
+        if hit is not None:
+            return hit
         out = set()
         for s in states:
             out.update(self._m.step(s, c))
-        return frozenset(out)
+        res = frozenset(out)
+        if len(self._memo) > 200_000:
+            self._memo.clear()
+        self._memo[key] = res
+        return res
 
     def accepts(self, text: str) -> bool:
         """Would ``text`` be admitted from the current position?  (Does not move.)"""
