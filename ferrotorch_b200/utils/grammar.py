@@ -12,7 +12,9 @@ differs in two ways:
   apart (the reference commits to the first branch whose start accepts the character,
   schema.rs:33-41);
 * the token mask is computed by walking a **trie of the vocabulary** once per matcher state, so
-  tokens that share a prefix share the work, and masks are cached per state.
+  tokens that share a prefix share the work, and masks are cached per state; the walk itself runs in
+  C++ (``csrc/host/grammar_mask.cpp``) and calls back into the matcher only for (state, character)
+  pairs it has not seen, with a pure-Python walk as the fallback.
 
 Supported schema keywords: ``type`` (object, array, string, number, integer, boolean, null, or a
 list of them), ``properties`` + ``required`` (only listed properties may appear, in any order),
@@ -610,6 +612,84 @@ def _build_trie(vocab: list[str], skip: set) -> _Trie:
     return root
 
 
+class _NativeMasker:
+    """The vocabulary trie and the walk in C++ (``csrc/host/grammar_mask.cpp``); the matcher is
+    asked for a transition through a callback only the first time a (state, character) pair comes
+    up.  State sets get integer ids here; one masker serves every processor of the same schema and
+    vocabulary."""
+
+    def __init__(self, grammar: "SchemaGrammar", vocab: list[str], skip: set):
+        import ctypes
+
+        import numpy as np
+
+        from .. import _native
+
+        lib = _native.host()
+        lib.ftgm_create.restype = ctypes.c_void_p
+        lib.ftgm_create.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        self._cb_type = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_int, ctypes.c_uint)
+        lib.ftgm_mask.restype = ctypes.c_longlong
+        lib.ftgm_mask.argtypes = [ctypes.c_void_p, ctypes.c_int, self._cb_type, ctypes.c_void_p]
+        lib.ftgm_destroy.argtypes = [ctypes.c_void_p]
+        lib.ftgm_num_nodes.restype = lib.ftgm_num_transitions.restype = ctypes.c_longlong
+        lib.ftgm_num_nodes.argtypes = lib.ftgm_num_transitions.argtypes = [ctypes.c_void_p]
+        self._lib, self._g = lib, grammar
+        offs = np.zeros(len(vocab) + 1, dtype=np.int64)
+        for i, piece in enumerate(vocab):
+            offs[i + 1] = offs[i] + len(piece)
+        cps = np.fromiter((ord(c) for piece in vocab for c in piece), dtype=np.uint32, count=int(offs[-1]))
+        skip_arr = np.zeros(len(vocab), dtype=np.uint8)
+        for i in skip:
+            if 0 <= i < len(vocab):
+                skip_arr[i] = 1
+        self._h = lib.ftgm_create(cps.ctypes.data, offs.ctypes.data, len(vocab), skip_arr.ctypes.data)
+        if not self._h:
+            raise RuntimeError("grammar mask: could not build the vocabulary trie")
+        self.n = len(vocab)
+        self._ids: dict = {}
+        self._sets: list = []
+        self._error: list = []
+
+        def step(state: int, cp: int) -> int:
+            try:
+                nxt = grammar._advance(self._sets[state], chr(cp))
+                return self.state_id(nxt) if nxt else -1
+            except BaseException as e:  # noqa: BLE001   (must not propagate through the C frame)
+                self._error.append(e)
+                return -2
+
+        self._cb = self._cb_type(step)
+
+    def state_id(self, states: frozenset) -> int:
+        i = self._ids.get(states)
+        if i is None:
+            i = self._ids[states] = len(self._sets)
+            self._sets.append(states)
+        return i
+
+    def mask(self, states: frozenset) -> torch.Tensor:
+        bits = torch.zeros(self.n, dtype=torch.uint8)
+        rc = self._lib.ftgm_mask(self._h, self.state_id(states), self._cb, bits.data_ptr())
+        if self._error:
+            raise self._error.pop()
+        if rc < 0:
+            raise RuntimeError("grammar mask: native walk failed (%d)" % rc)
+        return bits.bool()
+
+    def stats(self) -> dict:
+        return {"trie_nodes": int(self._lib.ftgm_num_nodes(self._h)), "transitions": int(self._lib.ftgm_num_transitions(self._h)),
+                "states": len(self._sets)}
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self._lib.ftgm_destroy(self._h)
+                self._h = None
+        except Exception:  # noqa: BLE001
+            pass
+
+
 class JsonSchemaProcessor:
     """Token-level constrained decoding for one sequence (json_schema.rs:171-300).
 
@@ -619,11 +699,27 @@ class JsonSchemaProcessor:
     state set, so a shared prefix is matched once."""
 
     def __init__(self, schema, vocab: list[str], eos_token_id: int | None = None,
-                 whitespace_permissive: bool = False):
+                 whitespace_permissive: bool = False, native: bool | None = None, share: "JsonSchemaProcessor | None" = None):
+        """``native``: walk the vocabulary in C++ (default: when the host library is available).
+        ``share``: another processor of the same schema and vocabulary whose trie and transition
+        tables this one reuses (one per batch row costs nothing extra)."""
         self.grammar_ = SchemaGrammar(schema, whitespace_permissive)
-        self.vocab = list(vocab)
+        self.vocab = list(vocab) if share is None else share.vocab
         self.eos = eos_token_id
-        self._trie = _build_trie(self.vocab, {eos_token_id} if eos_token_id is not None else set())
+        skip = {eos_token_id} if eos_token_id is not None else set()
+        if share is not None:
+            self.grammar_._memo = share.grammar_._memo          # same schema: transitions are shared too
+            self._native, self._trie = share._native, share._trie
+            return
+        self._native, self._trie = None, None
+        if native is None or native:
+            try:
+                self._native = _NativeMasker(self.grammar_, self.vocab, skip)
+            except Exception:  # noqa: BLE001
+                if native:
+                    raise
+        if self._native is None:
+            self._trie = _build_trie(self.vocab, skip)
 
     @classmethod
     def from_compiled(cls, schema: Schema, vocab: list[str], **kw) -> "JsonSchemaProcessor":
@@ -642,6 +738,12 @@ class JsonSchemaProcessor:
         self.grammar_.reset()
 
     def _mask_for(self, states: frozenset) -> TokenMask:
+        if self._native is not None:
+            bits = self._native.mask(states)
+            if self.eos is not None and 0 <= self.eos < len(self.vocab):
+                m = self.grammar_._m
+                bits[self.eos] = any(m.complete(s) for s in states)
+            return TokenMask(bits)
         bits = torch.zeros(len(self.vocab), dtype=torch.bool)
         allowed: list[int] = []
         adv = self.grammar_._advance
@@ -693,8 +795,9 @@ class SchemaLogitsProcessor:
 
     def __init__(self, schema, vocab: list[str], eos_token_id: int | None = None,
                  whitespace_permissive: bool = False):
-        self._make = lambda: JsonSchemaProcessor(compiled, vocab, eos_token_id, whitespace_permissive)
         compiled = schema if isinstance(schema, Schema) else Schema.from_json_schema(schema)
+        self._proto = JsonSchemaProcessor(compiled, vocab, eos_token_id, whitespace_permissive)
+        self._make = lambda: JsonSchemaProcessor(compiled, vocab, eos_token_id, whitespace_permissive, share=self._proto)
         self.eos = eos_token_id
         self.cache = TokenTransitionCache()
         self.rows: list[JsonSchemaProcessor] = []

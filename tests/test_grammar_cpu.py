@@ -166,3 +166,33 @@ def test_generate_under_a_schema_yields_valid_json():
         else:                                         # the others are valid prefixes
             assert G.SchemaGrammar(SMALL).accepts(text)
     assert done >= 1 and proc.cache.hits() > 0
+
+
+def test_native_mask_walk_equals_the_python_walk_and_is_shared():
+    import random
+    import string
+
+    random.seed(1)
+    vocab = ["<eos>", ""] + ["".join(random.choice(string.ascii_lowercase + string.digits + ' {}[]":,.-é\\') for _ in range(random.randint(1, 5)))
+                            for _ in range(3000)] + ['"name"', '"age"', '":', '{"', '",', "}", ":"]
+    nat = G.JsonSchemaProcessor(SMALL, vocab, eos_token_id=0, native=True)
+    py = G.JsonSchemaProcessor(SMALL, vocab, eos_token_id=0, native=False)
+    assert nat._native is not None and py._native is None
+    for piece in ["", '{"', "name", '":"', "ab", '",', '"age"', ":", "15", "0", "}"]:
+        if piece:
+            nat.grammar().step_text(piece)
+            py.grammar().step_text(piece)
+        a, b = nat.compute_mask(), py.compute_mask()
+        assert torch.equal(a.bits, b.bits), piece
+    assert nat.is_complete() and nat.compute_mask().allowed_ids() == [0]
+    st = nat._native.stats()
+    assert st["trie_nodes"] > 3000 and st["transitions"] > 0 and st["states"] > 5
+    twin = G.JsonSchemaProcessor(SMALL, vocab, eos_token_id=0, share=nat)           # a second row: same trie, same tables
+    assert twin._native is nat._native and twin.vocab is nat.vocab
+    assert torch.equal(twin.compute_mask().bits, G.JsonSchemaProcessor(SMALL, vocab, 0, native=False).compute_mask().bits)
+    # an exception inside the matcher callback surfaces as a Python exception, not a crash
+    broken = G.JsonSchemaProcessor({"type": "string"}, vocab, eos_token_id=0, native=True)
+    broken.grammar()._m.step = lambda *_: (_ for _ in ()).throw(RuntimeError("boom"))
+    broken.grammar()._memo.clear()
+    with pytest.raises(RuntimeError, match="boom"):
+        broken.compute_mask()
