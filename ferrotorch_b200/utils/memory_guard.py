@@ -139,3 +139,129 @@ class MemoryGuard:
         while self.paused.is_set() and time.time() < deadline:
             time.sleep(0.005)
         return not self.paused.is_set()
+
+
+# --------------------------------------------------------------------------- the reference's vocabulary
+# (memory_guard.rs: OomPolicy::{Fail, RetryAfterFree, WaitAndRetry, CheckpointAndFail}, PressureLevel,
+#  MemoryStats, MemoryGuardBuilder, register_hook / remove_hook, reservations, safe_alloc)
+OomPolicy.Fail = OomPolicy.FAIL
+OomPolicy.RetryAfterFree = OomPolicy.RUN_HOOKS_THEN_FAIL
+OomPolicy.WaitAndRetry = OomPolicy.WAIT
+OomPolicy.CheckpointAndFail = OomPolicy.FAIL        # with an emergency-checkpoint callback installed
+
+
+class PressureLevel(enum.IntEnum):
+    NONE = 0        # < 50 % of the usable budget
+    LOW = 1         # 50 - 70 %
+    MEDIUM = 2      # 70 - 85 %
+    HIGH = 3        # 85 - 95 %
+    CRITICAL = 4    # >= 95 %
+
+    @classmethod
+    def of(cls, pressure: float) -> "PressureLevel":
+        for level, lo in ((cls.CRITICAL, 0.95), (cls.HIGH, 0.85), (cls.MEDIUM, 0.70), (cls.LOW, 0.50)):
+            if pressure >= lo:
+                return level
+        return cls.NONE
+
+
+def _pressure_level(self) -> PressureLevel:
+    return PressureLevel.of(self.pressure())
+
+
+def _notify_level_change(self) -> PressureLevel:
+    """Call the ``(old, new)`` listeners when the level moved since the last call."""
+    new, old = self.pressure_level(), getattr(self, "_last_level", PressureLevel.NONE)
+    if new != old:
+        self._last_level = new
+        for fn in getattr(self, "_level_listeners", []):
+            fn(old, new)
+    return new
+
+
+def _add_level_listener(self, fn) -> None:
+    self.__dict__.setdefault("_level_listeners", []).append(fn)
+
+
+def _register_hook(self, fn, priority: int = 0, name: str = "") -> int:
+    self.add_pre_oom_hook(fn, priority, name)
+    ids = self.__dict__.setdefault("_hook_ids", {})
+    hid = self.__dict__["_next_hook"] = self.__dict__.get("_next_hook", 0) + 1
+    ids[hid] = fn
+    return hid
+
+
+def _remove_hook(self, hid: int) -> bool:
+    fn = self.__dict__.get("_hook_ids", {}).pop(hid, None)
+    if fn is None:
+        return False
+    self._hooks = [h for h in self._hooks if h[2] is not fn]
+    return True
+
+
+def _memory_stats(self) -> dict:
+    used = self.alloc.used_bytes()
+    self.__dict__["_peak"] = max(self.__dict__.get("_peak", 0), used)
+    return {"used_bytes": used, "peak_bytes": self.__dict__["_peak"], "budget_bytes": self.budget,
+            "reserved_bytes": self.reserve, "available_bytes": self.available(), "pressure": self.pressure(),
+            "level": self.pressure_level().name, **self.stats}
+
+
+def _reset_peak_stats(self) -> None:
+    self.__dict__["_peak"] = self.alloc.used_bytes()
+
+
+def _safe_alloc(self, shape, dtype=None, device=None):
+    """``torch.empty`` behind the guard: the size is checked against the budget (running hooks /
+    waiting / failing by policy) before the allocator is asked."""
+    import math
+
+    import torch
+
+    dtype = dtype or torch.float32
+    self.ensure(math.prod(shape) * torch.empty(0, dtype=dtype).element_size())
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
+MemoryGuard.pressure_level = _pressure_level
+MemoryGuard.notify_pressure_change = _notify_level_change
+MemoryGuard.add_level_listener = _add_level_listener
+MemoryGuard.register_hook = _register_hook
+MemoryGuard.remove_hook = _remove_hook
+MemoryGuard.memory_stats = _memory_stats
+MemoryGuard.reset_peak_stats = _reset_peak_stats
+MemoryGuard.safe_alloc = _safe_alloc
+MemoryGuard.set_budget = lambda self, nbytes: setattr(self, "budget", int(nbytes))
+MemoryGuard.set_oom_policy = lambda self, policy: setattr(self, "policy", policy)
+MemoryGuard.has_reservation = lambda self: self.reserve > 0
+MemoryGuard.release_reservation = lambda self: setattr(self, "reserve", 0)
+MemoryGuard.reserved_bytes = lambda self: self.reserve
+
+
+class MemoryGuardBuilder:
+    """``MemoryGuardBuilder().budget_bytes(n).reserve_bytes(m).oom_policy(p).build(allocator)``."""
+
+    def __init__(self):
+        self._kw: dict = {}
+
+    def budget_bytes(self, n: int) -> "MemoryGuardBuilder":
+        self._kw["budget_bytes"] = int(n)
+        return self
+
+    def reserve_bytes(self, n: int) -> "MemoryGuardBuilder":
+        self._kw["reserve_bytes"] = int(n)
+        return self
+
+    def oom_policy(self, policy: OomPolicy) -> "MemoryGuardBuilder":
+        self._kw["policy"] = policy
+        return self
+
+    def pressure_threshold(self, frac: float) -> "MemoryGuardBuilder":
+        self._kw["pressure_threshold"] = float(frac)
+        return self
+
+    def build(self, allocator=None) -> MemoryGuard:
+        if self._kw.get("reserve_bytes", 0) and self._kw.get("budget_bytes") is not None and \
+                self._kw["reserve_bytes"] >= self._kw["budget_bytes"]:
+            raise ValueError("MemoryGuardBuilder: the reservation must be smaller than the budget")
+        return MemoryGuard(allocator, **self._kw)

@@ -408,3 +408,55 @@ def test_name_level_parity_helpers(tmp_path):
     assert lr.grad.item() == pytest.approx(-2 * (1 - 0.2) * 2 * 5.0, rel=1e-5)      # d/dlr sum((w (1 - 2 lr))^2)
     (w2,), (b2,) = O.diff_sgd_momentum_step([w.detach()], [g.detach()], [torch.ones(2)], 0.1, 0.5)
     assert torch.allclose(b2, 0.5 + g.detach()) and torch.allclose(w2, w.detach() - 0.1 * b2)
+
+
+def test_memory_guard_builder_levels_hooks_and_safe_alloc():
+    from ferrotorch_b200.utils.memory_guard import (MemoryBudgetExceeded, MemoryGuardBuilder, OomPolicy, PressureLevel)
+
+    class Fake:
+        used = 0
+
+        def used_bytes(self):
+            return self.used
+
+        def total_bytes(self):
+            return 1000
+
+        def empty_cache(self):
+            pass
+
+    a = Fake()
+    g = MemoryGuardBuilder().budget_bytes(1000).reserve_bytes(200).oom_policy(OomPolicy.RetryAfterFree).build(a)
+    assert g.has_reservation() and g.reserved_bytes() == 200 and g.available() == 800
+    assert [PressureLevel.of(p) for p in (0.1, 0.5, 0.7, 0.85, 0.95)] == list(PressureLevel)
+    moves = []
+    g.add_level_listener(lambda old, new: moves.append((old.name, new.name)))
+    a.used = 600                                        # 600 / 800 usable = 75 %
+    assert g.notify_pressure_change() == PressureLevel.MEDIUM and g.notify_pressure_change() == PressureLevel.MEDIUM
+    a.used = 790
+    g.notify_pressure_change()
+    assert moves == [("NONE", "MEDIUM"), ("MEDIUM", "CRITICAL")]
+    freed = []
+
+    def drop_cache(need):
+        freed.append(need)
+        a.used -= 500
+        return 500
+
+    hid = g.register_hook(drop_cache, priority=5, name="cache")
+    t = g.safe_alloc((50,), torch.float32)              # 200 bytes: needs the hook (only 10 available)
+    assert t.shape == (50,) and freed == [190] and a.used == 290
+    st = g.memory_stats()
+    assert st["peak_bytes"] >= 290 and st["level"] == "NONE" and st["hook_runs"] == 1 and st["budget_bytes"] == 1000
+    assert g.remove_hook(hid) and not g.remove_hook(hid)
+    with pytest.raises(MemoryBudgetExceeded):
+        g.safe_alloc((1000,), torch.float32)
+    g.release_reservation()
+    assert not g.has_reservation() and g.available() == 710
+    g.set_budget(2000)
+    g.set_oom_policy(OomPolicy.Fail)
+    assert g.available() == 1710 and g.policy is OomPolicy.FAIL
+    g.reset_peak_stats()
+    assert g.memory_stats()["peak_bytes"] == 290
+    with pytest.raises(ValueError):
+        MemoryGuardBuilder().budget_bytes(100).reserve_bytes(100).build(a)
