@@ -242,10 +242,13 @@ def dumps_state_dict(state: dict[str, torch.Tensor]) -> bytes:
 def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
     """Reads the layout above, files the reference wrote, and the first layout of this package
     (fields ``offset`` / ``nbytes``, upper-case dtype names)."""
+    if not isinstance(buf, bytearray):
+        buf = bytearray(buf)                    # one copy; the tensors below are views into it
     head_end = 0 if buf.startswith(b"---\n") else buf.find(b"\n---\n") + 1
     if head_end == 0 and not buf.startswith(b"---\n"):
         raise ValueError("state dict: no separator line")
-    body = memoryview(buf)[head_end + 4:]
+    body_start = head_end + 4
+    body = memoryview(buf)[body_start:]
     out = {}
     for line in buf[:head_end].decode().splitlines():
         if not line.strip():
@@ -265,20 +268,40 @@ def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
             numel *= int(d)
         if numel * torch.empty(0, dtype=dt).element_size() != n:
             raise ValueError("state dict: shape %s of %r does not match %d bytes" % (e["shape"], e["name"], n))
-        raw = bytes(body[off:off + n])
-        t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dt) if raw else torch.empty(0, dtype=dt)
+        if n:
+            t8 = torch.frombuffer(buf, dtype=torch.uint8, count=n, offset=body_start + off)
+            item = torch.empty(0, dtype=dt).element_size()
+            t = (t8 if t8.data_ptr() % item == 0 else t8.clone()).view(dt)     # views need aligned storage
+        else:
+            t = torch.empty(0, dtype=dt)
         out[e["name"]] = t.reshape(e["shape"]).to(device)
     return out
 
 
 def save_state_dict(state: dict[str, torch.Tensor], path: str) -> None:
+    """Streams: the header first, then every tensor's bytes straight from its storage (no
+    concatenated copy of the whole checkpoint in memory)."""
+    keys = sorted(state)
+    header, off, views = [], 0, []
+    for k in keys:
+        v = state[k].detach().contiguous().cpu()
+        nbytes = v.numel() * v.element_size()
+        header.append('{"name":%s,"shape":[%s],"dtype":"%s","byte_offset":%d,"byte_length":%d}\n'
+                      % (json.dumps(k), ",".join(str(int(d)) for d in v.shape), _TAG[v.dtype], off, nbytes))
+        views.append(v)
+        off += nbytes
     with open(path, "wb") as f:
-        f.write(dumps_state_dict(state))
+        f.write("".join(header).encode() + b"\n---\n")
+        for v in views:
+            if v.numel():
+                f.write(memoryview(v.reshape(-1).view(torch.uint8).numpy()))
 
 
 def load_state_dict(path: str, device="cpu") -> dict[str, torch.Tensor]:
+    buf = bytearray(os.path.getsize(path))
     with open(path, "rb") as f:
-        return loads_state_dict(f.read(), device)
+        f.readinto(buf)
+    return loads_state_dict(buf, device)
 
 
 # --------------------------------------------------------------------------- training checkpoint
