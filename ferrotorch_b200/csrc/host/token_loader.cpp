@@ -221,7 +221,11 @@ FTD_API long long ftd_next(void* h, long long* out) {
   const long long want = L->next_to_serve;
   Slot& slot = L->ring[static_cast<size_t>(want % static_cast<long long>(L->ring.size()))];
   L->cv_ready.wait(lk, [&] { return slot.batch == want && slot.ready; });
+  // the slot is ours until it is marked free: copy without holding the lock, so the workers can
+  // keep claiming and filling other slots meanwhile
+  lk.unlock();
   std::memcpy(out, slot.data.data(), slot.data.size() * sizeof(int64_t));
+  lk.lock();
   slot.batch = -1;
   slot.ready = false;
   ++L->next_to_serve;
