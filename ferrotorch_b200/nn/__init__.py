@@ -11,5 +11,7 @@ from .layers import (FusedLinearActivation, GQAAttention, KVCache, Linear, RMSNo
 
 from ..ops.batchnorm import BatchNormAct2d, batch_norm_act  # noqa: F401,E402
 from .fake_quant import FakeQuantize, MinMaxObserver, MovingAverageObserver, QatLinear, prepare_qat  # noqa: F401,E402
-from .extra import HookedModule, HookHandle, LoRALinear, SqueezeExcitation  # noqa: F401,E402
+from .extra import (HookedModule, HookHandle, LoRALinear, SqueezeExcitation, flash_attention,  # noqa: F401,E402
+                    standard_attention)
+from ..core import flex_attention  # noqa: F401,E402
 from .paged import OutOfPages, PagedAttentionManager, PagedKVCache  # noqa: F401,E402

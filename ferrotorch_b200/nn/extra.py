@@ -129,3 +129,87 @@ class HookedModule(nn.Module):
                 return g
             y.register_hook(run)
         return y
+
+
+# --------------------------------------------------------------------------- tiled attention on any device
+def _check_attn(q, k, v, block_size):
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        raise ValueError("attention: expected [B, N, d] tensors")
+    if q.shape[0] != k.shape[0] or k.shape[0] != v.shape[0] or q.shape[2] != k.shape[2] or k.shape[1] != v.shape[1]:
+        raise ValueError("attention: incompatible shapes %s %s %s" % (tuple(q.shape), tuple(k.shape), tuple(v.shape)))
+    if block_size <= 0:
+        raise ValueError("attention: block_size must be positive")
+
+
+def standard_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, causal: bool = False) -> torch.Tensor:
+    """``softmax(Q K^T / sqrt(d)) V`` with the whole score matrix in memory; ``causal`` hides keys
+    ``j > i`` (ferrotorch-nn/src/flash_attention.rs:647)."""
+    _check_attn(query, key, value, 1)
+    s = query @ key.transpose(1, 2) / math.sqrt(query.shape[2])
+    if causal:
+        i = torch.arange(query.shape[1], device=query.device)[:, None]
+        j = torch.arange(key.shape[1], device=query.device)[None, :]
+        s = s.masked_fill(j > i, float("-inf"))
+    return torch.softmax(s, dim=-1) @ value
+
+
+class _TiledAttention(torch.autograd.Function):
+    """Online-softmax attention over key blocks: memory O(N block) instead of O(N^2); the backward
+    recomputes each block's probabilities from the saved row log-sum-exp."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, block):
+        B, Nq, d = q.shape
+        scale = 1.0 / math.sqrt(d)
+        out = torch.zeros(B, Nq, v.shape[2], dtype=torch.float32, device=q.device)
+        m = torch.full((B, Nq), float("-inf"), dtype=torch.float32, device=q.device)
+        l = torch.zeros(B, Nq, dtype=torch.float32, device=q.device)
+        rows = torch.arange(Nq, device=q.device)[:, None]
+        for j0 in range(0, k.shape[1], block):
+            kb, vb = k[:, j0:j0 + block].float(), v[:, j0:j0 + block].float()
+            s = q.float() @ kb.transpose(1, 2) * scale
+            if causal:
+                cols = torch.arange(j0, j0 + kb.shape[1], device=q.device)[None, :]
+                s = s.masked_fill(cols > rows, float("-inf"))
+            m_new = torch.maximum(m, s.amax(-1))
+            safe = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)      # rows that have seen no key yet
+            p = torch.exp(s - safe[..., None])
+            alpha = torch.exp(torch.where(torch.isinf(m), torch.full_like(m, float("-inf")), m - safe))
+            l = alpha * l + p.sum(-1)
+            out = alpha[..., None] * out + p @ vb
+            m = m_new
+        out = out / l[..., None]
+        lse = torch.where(torch.isinf(m), m, m + torch.log(l))
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.block = causal, block
+        return out.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        scale = 1.0 / math.sqrt(q.shape[2])
+        dq, dk, dv = torch.zeros_like(q, dtype=torch.float32), torch.zeros_like(k, dtype=torch.float32), torch.zeros_like(v, dtype=torch.float32)
+        do = dout.float()
+        delta = (do * out).sum(-1)                          # rowsum(dO * O)
+        rows = torch.arange(q.shape[1], device=q.device)[:, None]
+        for j0 in range(0, k.shape[1], ctx.block):
+            kb, vb = k[:, j0:j0 + ctx.block].float(), v[:, j0:j0 + ctx.block].float()
+            s = q.float() @ kb.transpose(1, 2) * scale
+            if ctx.causal:
+                cols = torch.arange(j0, j0 + kb.shape[1], device=q.device)[None, :]
+                s = s.masked_fill(cols > rows, float("-inf"))
+            p = torch.exp(s - lse[..., None])
+            dv[:, j0:j0 + ctx.block] = p.transpose(1, 2) @ do
+            ds = p * (do @ vb.transpose(1, 2) - delta[..., None]) * scale
+            dq += ds @ kb
+            dk[:, j0:j0 + ctx.block] = ds.transpose(1, 2) @ q.float()
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None
+
+
+def flash_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, causal: bool = False,
+                    block_size: int = 64) -> torch.Tensor:
+    """Tiled attention with forward and backward on ``[B, N, d]`` tensors of any device
+    (ferrotorch-nn/src/flash_attention.rs:59-640).  The GPU kernels for bf16 multi-head inputs
+    are :func:`ferrotorch_b200.ops.functional.flash_attention` / ``packed_attention``."""
+    _check_attn(query, key, value, block_size)
+    return _TiledAttention.apply(query, key, value, causal, block_size)

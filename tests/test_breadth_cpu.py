@@ -412,3 +412,30 @@ def test_lora_se_and_hooked_module():
         h.remove()
     assert torch.allclose(hm(inp), hm.inner()(inp)) and len(seen) == 1
     assert fnn.PagedKVCache is not None and fnn.PagedAttentionManager is not None
+
+
+@pytest.mark.parametrize("causal,nq,nk,block", [(False, 7, 13, 4), (True, 9, 9, 4), (True, 5, 11, 16), (False, 6, 6, 1)])
+def test_tiled_attention_forward_and_backward(causal, nq, nk, block):
+    import ferrotorch_b200.nn as fnn
+
+    torch.manual_seed(0)
+    q = torch.randn(2, nq, 8, dtype=torch.float64, requires_grad=True)
+    k = torch.randn(2, nk, 8, dtype=torch.float64, requires_grad=True)
+    v = torch.randn(2, nk, 5, dtype=torch.float64, requires_grad=True)
+    want = fnn.standard_attention(q, k, v, causal)
+    got = fnn.flash_attention(q, k, v, causal, block)
+    assert torch.allclose(got, want, atol=1e-6)
+    w = torch.randn_like(want)
+    g1 = torch.autograd.grad((want * w).sum(), (q, k, v))
+    g2 = torch.autograd.grad((got * w).sum(), (q, k, v))
+    for a, b in zip(g1, g2):
+        assert torch.allclose(a, b, atol=1e-5), (a - b).abs().max()
+    if not causal:
+        sdpa = torch.nn.functional.scaled_dot_product_attention(q[:, None], k[:, None], v[:, None])[:, 0]
+        assert torch.allclose(got, sdpa, atol=1e-6)
+    for bad in ((q[0], k, v), (q, k[:, :, :4], v), (q, k, v[:, :3])):
+        with pytest.raises(ValueError):
+            fnn.flash_attention(*bad)
+    with pytest.raises(ValueError):
+        fnn.flash_attention(q, k, v, causal, 0)
+    assert fnn.flex_attention is not None
