@@ -72,12 +72,56 @@ def rearrange(tensor: Tensor, pattern: str, **axes) -> Tensor:
     return einops.rearrange(tensor, pattern, **axes)
 
 
-def flex_attention(q: Tensor, k: Tensor, v: Tensor, score_mod=None, scale: float | None = None) -> Tensor:
+def reduce(tensor: Tensor, pattern: str, reduction: str, **axes) -> Tensor:
+    import einops
+
+    return einops.reduce(tensor, pattern, reduction, **axes)
+
+
+def repeat(tensor: Tensor, pattern: str, **axes) -> Tensor:
+    import einops
+
+    return einops.repeat(tensor, pattern, **axes)
+
+
+class BlockMask:
+    """Block-sparse visibility for :func:`flex_attention`: ``keep[i, j]`` says whether query block i
+    may see key block j at all (flex_attention.rs ``BlockMask``).  Built from an element-level
+    predicate ``mask_fn(q_index, kv_index) -> bool`` evaluated once per block pair."""
+
+    def __init__(self, keep: Tensor, block: int, q_len: int, kv_len: int):
+        self.keep, self.block, self.q_len, self.kv_len = keep, block, q_len, kv_len
+
+    @classmethod
+    def from_fn(cls, mask_fn, q_len: int, kv_len: int, block: int = 64) -> "BlockMask":
+        qi, ki = torch.arange(q_len)[:, None], torch.arange(kv_len)[None, :]
+        dense = mask_fn(qi, ki).expand(q_len, kv_len)
+        nq, nk = -(-q_len // block), -(-kv_len // block)
+        pad = torch.zeros(nq * block, nk * block, dtype=torch.bool)
+        pad[:q_len, :kv_len] = dense
+        keep = pad.view(nq, block, nk, block).permute(0, 2, 1, 3).flatten(2).any(-1)
+        return cls(keep, block, q_len, kv_len)
+
+    def sparsity(self) -> float:
+        return 1.0 - float(self.keep.float().mean())
+
+    def dense(self) -> Tensor:
+        m = self.keep.repeat_interleave(self.block, 0).repeat_interleave(self.block, 1)
+        return m[: self.q_len, : self.kv_len]
+
+
+def flex_attention(q: Tensor, k: Tensor, v: Tensor, score_mod=None, scale: float | None = None,
+                   block_mask: "BlockMask | None" = None) -> Tensor:
     """Attention with a user function applied to the scores before the softmax:
-    ``score_mod(score, batch, head, q_index, kv_index) -> score`` (flex_attention.rs).  Dense
-    evaluation; use the flash kernels of :mod:`ferrotorch_b200.ops` for the standard masks."""
+    ``score_mod(score, batch, head, q_index, kv_index) -> score`` and an optional block-sparse
+    mask (flex_attention.rs:56, 482).  Dense evaluation; use the flash kernels of
+    :mod:`ferrotorch_b200.ops` for the standard masks."""
     B, H, S, D = q.shape
     s = (q.float() @ k.float().transpose(-1, -2)) * (scale if scale is not None else D ** -0.5)
+    if block_mask is not None:
+        if (block_mask.q_len, block_mask.kv_len) != (S, k.shape[2]):
+            raise ValueError("flex_attention: the block mask was built for %dx%d scores" % (block_mask.q_len, block_mask.kv_len))
+        s = s.masked_fill(~block_mask.dense().to(s.device), float("-inf"))
     if score_mod is not None:
         b = torch.arange(B, device=q.device).view(B, 1, 1, 1)
         h = torch.arange(H, device=q.device).view(1, H, 1, 1)

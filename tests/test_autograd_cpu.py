@@ -159,3 +159,20 @@ def test_autocast_policy_table_and_debug_events():
     assert A.drain_autocast_events() == []
     lin(x)
     assert A.drain_autocast_events() == []               # recorder is off again
+
+
+def test_block_masks_and_einops_helpers():
+    from ferrotorch_b200 import core as C
+
+    torch.manual_seed(0)
+    q, k, v = torch.randn(1, 2, 8, 4), torch.randn(1, 2, 8, 4), torch.randn(1, 2, 8, 4)
+    bm = C.BlockMask.from_fn(lambda i, j: j <= i, 8, 8, block=4)                 # causal: the upper-right block drops out
+    assert bm.keep.tolist() == [[True, False], [True, True]] and bm.sparsity() == 0.25
+    out = C.flex_attention(q, k, v, lambda s, b, h, i, j: s.masked_fill(j > i, float("-inf")), block_mask=bm)
+    assert torch.allclose(out, torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True), atol=1e-5)
+    window = C.BlockMask.from_fn(lambda i, j: (i - j).abs() < 4, 8, 8, block=4)
+    assert window.keep.all() and window.dense().shape == (8, 8)
+    with pytest.raises(ValueError):
+        C.flex_attention(q[:, :, :4], k, v, block_mask=bm)
+    x = torch.arange(12.0).view(3, 4)
+    assert C.reduce(x, "a b -> a", "sum").tolist() == [6.0, 22.0, 38.0] and C.repeat(x, "a b -> a b c", c=2).shape == (3, 4, 2)
