@@ -1,0 +1,174 @@
+"""Device runtime vocabulary of the reference's ``ferrotorch-gpu`` crate on top of ``torch.cuda``:
+devices, transfers, the caching allocator's statistics, CUDA graphs with private pools, RNG
+fork / join, and the memory guard (lib.rs:245-357: ``GpuDevice``, ``cuda`` / ``tensor_to_gpu`` /
+``tensor_to_cpu``, ``alloc_zeros``, ``empty_cache`` / ``cached_bytes``, ``CapturedGraph`` /
+``begin_capture`` / ``end_capture`` / ``make_graphed_callable`` / ``graph_pool_handle``,
+``fork_rng`` / ``join_rng``).  The kernels themselves are in :mod:`ferrotorch_b200.ops`."""
+from __future__ import annotations
+
+import contextlib
+
+import torch
+
+from .utils.memory_guard import (MemoryBudgetExceeded, MemoryGuard, MemoryGuardBuilder, OomPolicy,  # noqa: F401
+                                 PressureLevel)
+
+
+class GpuError(RuntimeError):
+    pass
+
+
+def is_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def _need():
+    if not torch.cuda.is_available():
+        raise GpuError("no CUDA device is available")
+
+
+class GpuDevice:
+    """One ordinal: its properties, default stream and memory figures (device.rs:40-117)."""
+
+    def __init__(self, ordinal: int = 0):
+        _need()
+        if not 0 <= ordinal < torch.cuda.device_count():
+            raise GpuError("device %d outside 0..%d" % (ordinal, torch.cuda.device_count() - 1))
+        self.ordinal, self.device = ordinal, torch.device("cuda", ordinal)
+
+    def name(self) -> str:
+        return torch.cuda.get_device_name(self.ordinal)
+
+    def compute_capability(self) -> tuple:
+        return torch.cuda.get_device_capability(self.ordinal)
+
+    def sm_count(self) -> int:
+        return torch.cuda.get_device_properties(self.ordinal).multi_processor_count
+
+    def memory_info(self) -> tuple:
+        """``(free_bytes, total_bytes)`` as the driver reports them."""
+        return tuple(int(v) for v in torch.cuda.mem_get_info(self.ordinal))
+
+    def default_stream(self):
+        return torch.cuda.default_stream(self.ordinal)
+
+    def synchronize(self) -> None:
+        torch.cuda.synchronize(self.ordinal)
+
+
+def get_cuda_device(ordinal: int = 0) -> GpuDevice:
+    return GpuDevice(ordinal)
+
+
+def cuda(tensor: torch.Tensor, ordinal: int = 0, non_blocking: bool = False) -> torch.Tensor:
+    _need()
+    return tensor.to(torch.device("cuda", ordinal), non_blocking=non_blocking)
+
+
+cuda_default = tensor_to_gpu = cpu_to_gpu = cuda
+
+
+def tensor_to_cpu(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor.cpu()
+
+
+gpu_to_cpu = tensor_to_cpu
+
+
+def alloc_zeros(shape, dtype: torch.dtype = torch.float32, ordinal: int = 0) -> torch.Tensor:
+    _need()
+    return torch.zeros(tuple(shape), dtype=dtype, device=torch.device("cuda", ordinal))
+
+
+def empty_cache() -> None:
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+
+
+empty_cache_all = empty_cache
+
+
+def cached_bytes(ordinal: int = 0) -> int:
+    """Bytes the caching allocator holds but no tensor uses (pool.rs ``cached_bytes``)."""
+    if not torch.cuda.is_available():
+        return 0
+    return int(torch.cuda.memory_reserved(ordinal) - torch.cuda.memory_allocated(ordinal))
+
+
+def round_len(nbytes: int) -> int:
+    """The size class of the caching allocator (allocator.rs: 512-byte granules below 1 MiB,
+    2 MiB granules from there on)."""
+    if nbytes <= 0:
+        return 512
+    if nbytes < (1 << 20):
+        return (nbytes + 511) // 512 * 512
+    return (nbytes + (2 << 20) - 1) // (2 << 20) * (2 << 20)
+
+
+# --------------------------------------------------------------------------- CUDA graphs
+def graph_pool_handle():
+    _need()
+    return torch.cuda.graph_pool_handle()
+
+
+class CapturedGraph:
+    """A captured graph and its replay counter (graph.rs:97-500)."""
+
+    def __init__(self, graph: "torch.cuda.CUDAGraph"):
+        self.graph, self.num_replays = graph, 0
+
+    def launch(self) -> None:
+        self.graph.replay()
+        self.num_replays += 1
+
+    replay = launch
+
+    def reset(self) -> None:
+        self.graph.reset()
+
+
+@contextlib.contextmanager
+def capture(pool=None, stream=None, capture_error_mode: str = "global"):
+    """``with capture() as holder: ...`` records the block into a graph whose memory comes from a
+    private pool (so replays cannot collide with the eager allocator); ``holder.captured`` is the
+    :class:`CapturedGraph` afterwards (graph.rs ``capture_into_private_pool``)."""
+    _need()
+    g = torch.cuda.CUDAGraph()
+
+    class Holder:
+        captured: CapturedGraph | None = None
+
+    h = Holder()
+    with torch.cuda.graph(g, pool=pool, stream=stream, capture_error_mode=capture_error_mode):
+        yield h
+    h.captured = CapturedGraph(g)
+
+
+def is_stream_capturing() -> bool:
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+
+
+def make_graphed_callable(fn, sample_args, num_warmup_iters: int = 3):
+    """Capture ``fn`` (a module or function of tensors) into forward and backward graphs
+    (graph.rs ``make_graphed_callable``)."""
+    _need()
+    return torch.cuda.make_graphed_callables(fn, tuple(sample_args), num_warmup_iters=num_warmup_iters)
+
+
+# --------------------------------------------------------------------------- RNG
+def fork_rng(devices=None):
+    """Context manager: RNG state of the CPU and the given devices is restored on exit
+    (rng.rs ``fork_rng`` / ``join_rng``)."""
+    if devices is None:
+        devices = list(range(torch.cuda.device_count())) if torch.cuda.is_available() else []
+    return torch.random.fork_rng(devices=devices)
+
+
+def cuda_rng_state(ordinal: int = 0) -> torch.Tensor:
+    _need()
+    return torch.cuda.get_rng_state(ordinal)
+
+
+def set_cuda_rng_state(state: torch.Tensor, ordinal: int = 0) -> None:
+    _need()
+    torch.cuda.set_rng_state(state, ordinal)

@@ -460,3 +460,26 @@ def test_memory_guard_builder_levels_hooks_and_safe_alloc():
     assert g.memory_stats()["peak_bytes"] == 290
     with pytest.raises(ValueError):
         MemoryGuardBuilder().budget_bytes(100).reserve_bytes(100).build(a)
+
+
+def test_cuda_vocabulary_degrades_cleanly_without_a_gpu():
+    from ferrotorch_b200 import cuda as C
+
+    assert [C.round_len(n) for n in (0, 1, 512, 513, (1 << 20) - 1, 1 << 20, (2 << 20) + 1)] == \
+        [512, 512, 512, 1024, 1 << 20, 2 << 20, 4 << 20]
+    assert C.MemoryGuardBuilder is not None and C.PressureLevel.CRITICAL == 4
+    a = torch.rand(3)
+    with C.fork_rng():
+        torch.manual_seed(5)
+        inside = torch.rand(3)
+    after = torch.rand(3)
+    torch.manual_seed(5)
+    assert torch.equal(inside, torch.rand(3)) and not torch.equal(after, inside) and a is not None
+    if not C.is_available():
+        assert C.cached_bytes() == 0 and not C.is_stream_capturing()
+        C.empty_cache()
+        for call in (lambda: C.GpuDevice(0), lambda: C.cuda(a), lambda: C.alloc_zeros((2,)), C.graph_pool_handle,
+                     lambda: C.make_graphed_callable(lambda t: t, (a,))):
+            with pytest.raises(C.GpuError):
+                call()
+    assert torch.equal(C.tensor_to_cpu(a), a)
