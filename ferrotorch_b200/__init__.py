@@ -13,4 +13,16 @@ from . import _native  # noqa: F401
 from . import ops  # noqa: F401
 from . import autograd, core  # noqa: F401,E402
 
-__all__ = ["ops", "autograd", "core", "__version__"]
+_SUBMODULES = ("nn", "optim", "data", "train", "vision", "jit", "serialize", "parallel", "models", "profiler", "hub",
+               "cuda", "distributions", "utils")
+__all__ = ["ops", "autograd", "core", "__version__", *_SUBMODULES]
+
+
+def __getattr__(name):
+    """``import ferrotorch_b200 as ft; ft.nn.Linear`` -- sub-packages load on first use, like the
+    umbrella crate's re-exports (ferrotorch/src/lib.rs:59-177) without its compile-time cost."""
+    if name in _SUBMODULES:
+        import importlib
+
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))
