@@ -1,7 +1,7 @@
 """Parallel runtime: back-ends and collectives, data / tensor / pipeline / fully-sharded
 parallelism, device meshes and distributed tensors."""
 from .backend import (BackendUnavailable, DistributedError, Group, InvalidRank, InvalidWorldSize, IoError,  # noqa: F401
-                      NoConnection, SelfSend, SimulatedGroup, SizeMismatch, SubGroup, TcpGroup, Timeout, TorchGroup,
+                      NoConnection, RendezvousConfig, SelfSend, SimulatedGroup, SizeMismatch, SubGroup, TcpGroup, Timeout, TorchGroup,
                       UnsupportedOp, init_group, run_simulated)
 from .elastic import FileStore, Heartbeat, RankFailure, TorchStore, survivors  # noqa: F401
 from .fsdp import FSDP, ShardingStrategy, SyncBatchNorm2d  # noqa: F401

@@ -22,6 +22,7 @@ import ctypes
 import os
 import queue
 import threading
+from dataclasses import dataclass
 from typing import Sequence
 
 import torch
@@ -454,10 +455,51 @@ class TorchGroup(Group):
         return out
 
 
+@dataclass
+class RendezvousConfig:
+    """Where and who: read from the launcher's environment (gloo_native/connect.rs:116
+    ``RendezvousConfig::from_env``).  ``RANK`` / ``WORLD_SIZE`` are what ``torchrun`` sets; the Open
+    MPI and PMI names are accepted as well, so a job started by ``mpirun`` or a PMI launcher needs
+    no wrapper (mpi_backend.rs reads the same variables)."""
+    master_addr: str
+    master_port: int
+    rank: int
+    world_size: int
+
+    @classmethod
+    def from_env(cls, env=None) -> "RendezvousConfig":
+        env = os.environ if env is None else env
+
+        def first(names, what):
+            for n in names:
+                v = env.get(n)
+                if v not in (None, ""):
+                    try:
+                        return int(v)
+                    except ValueError:
+                        raise InvalidRank("%s=%r is not an integer" % (n, v))
+            raise NoConnection("none of %s is set: cannot tell the %s" % (", ".join(names), what))
+
+        rank = first(("RANK", "OMPI_COMM_WORLD_RANK", "PMI_RANK"), "rank")
+        world = first(("WORLD_SIZE", "OMPI_COMM_WORLD_SIZE", "PMI_SIZE"), "world size")
+        if world < 1:
+            raise InvalidWorldSize("world size %d" % world)
+        if not 0 <= rank < world:
+            raise InvalidRank("rank %d outside a world of %d" % (rank, world))
+        try:
+            port = int(env.get("MASTER_PORT", "29500"))
+        except ValueError:
+            raise NoConnection("MASTER_PORT=%r is not a port number" % env.get("MASTER_PORT"))
+        return cls(env.get("MASTER_ADDR", "127.0.0.1"), port, rank, world)
+
+
 def init_group(backend: str = "tcp", **kw) -> Group:
     """``backend``: "tcp" (native), "gloo" / "nccl" (torch.distributed, initialised here when
     needed), "simulated" is created with :func:`SimulatedGroup.create_group`."""
     if backend == "tcp":
+        if "rank" not in kw and "world_size" not in kw:
+            rc = RendezvousConfig.from_env()
+            kw = dict(rank=rc.rank, world_size=rc.world_size, master_addr=rc.master_addr, master_port=rc.master_port, **kw)
         return TcpGroup(**kw)
     if backend in ("gloo", "nccl"):
         import torch.distributed as dist

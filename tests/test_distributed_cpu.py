@@ -276,3 +276,18 @@ def test_hybrid_mesh_groups_and_data_parallel_trainer_gloo():
         assert (tp_sum, dp_sum) == want[r] and (tp_n, dp_n) == (2, 2)
         assert diff < 2e-5, diff                       # two half-batch replicas == one full-batch process
         assert losses[-1] < losses[0]
+
+
+def test_rendezvous_config_from_launcher_environments():
+    R = B.RendezvousConfig
+    c = R.from_env({"RANK": "1", "WORLD_SIZE": "4", "MASTER_ADDR": "10.0.0.1", "MASTER_PORT": "1234"})
+    assert (c.master_addr, c.master_port, c.rank, c.world_size) == ("10.0.0.1", 1234, 1, 4)
+    c = R.from_env({"OMPI_COMM_WORLD_RANK": "2", "OMPI_COMM_WORLD_SIZE": "3"})          # started by mpirun
+    assert (c.rank, c.world_size, c.master_addr, c.master_port) == (2, 3, "127.0.0.1", 29500)
+    assert R.from_env({"PMI_RANK": "0", "PMI_SIZE": "1"}).world_size == 1
+    assert R.from_env({"RANK": "0", "OMPI_COMM_WORLD_RANK": "5", "WORLD_SIZE": "2"}).rank == 0   # torchrun's names win
+    for env, err in (({}, B.NoConnection), ({"RANK": "0"}, B.NoConnection), ({"RANK": "x", "WORLD_SIZE": "2"}, B.InvalidRank),
+                     ({"RANK": "2", "WORLD_SIZE": "2"}, B.InvalidRank), ({"RANK": "0", "WORLD_SIZE": "0"}, B.InvalidWorldSize),
+                     ({"RANK": "0", "WORLD_SIZE": "1", "MASTER_PORT": "http"}, B.NoConnection)):
+        with pytest.raises(err):
+            R.from_env(env)
