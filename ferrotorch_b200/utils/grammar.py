@@ -548,6 +548,41 @@ class TokenMask:
         """``logits [..., V]`` with every disallowed entry set to -inf (on the logits' device)."""
         return logits.masked_fill(~self.bits.to(logits.device), float("-inf"))
 
+    def apply_(self, logits: torch.Tensor) -> torch.Tensor:
+        """In place through :func:`apply_packed_mask_` (one mask row for every logits row)."""
+        return apply_packed_mask_(logits, self.packed()[None])
+
+
+def unpack_mask(packed: torch.Tensor, vocab: int) -> torch.Tensor:
+    """``int32 [rows, ceil(V / 32)]`` -> bool ``[rows, V]`` (bit i of word w is id ``32 w + i``)."""
+    w = packed.to(torch.int64) & 0xFFFFFFFF
+    bits = (w[..., None] >> torch.arange(32, device=packed.device)) & 1
+    return bits.flatten(-2)[..., :vocab].bool()
+
+
+def apply_packed_mask_(logits: torch.Tensor, packed: torch.Tensor) -> torch.Tensor:
+    """Set ``logits[b, v] = -inf`` wherever bit v of ``packed[b]`` (or of ``packed[0]`` when it has
+    one row) is clear, in place.  ``logits [rows, V]`` bf16 / fp32 with unit inner stride.  On a GPU
+    this is one launch of ``ft_apply_token_mask`` (``csrc/token_mask.cu``) and the mask crosses PCIe
+    as 1 bit per id; elsewhere the bits are unpacked with torch ops."""
+    if logits.dim() != 2 or packed.dim() != 2 or packed.shape[0] not in (1, logits.shape[0]) or \
+            packed.shape[1] != (logits.shape[1] + 31) // 32:
+        raise ValueError("apply_packed_mask_: logits %s and packed mask %s do not fit" % (tuple(logits.shape), tuple(packed.shape)))
+    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(1) == 1:
+        from .. import _native
+
+        _native.register_protos({"ft_apply_token_mask": (_native._i, [_native._vp, _native._vp, _native._ll, _native._ll,
+                                                                       _native._ll, _native._i, _native._i, _native._i,
+                                                                       _native._vp])})
+        m = packed.to(device=logits.device, dtype=torch.int32, non_blocking=True).contiguous()
+        rc = _native.kernels().ft_apply_token_mask(logits.data_ptr(), m.data_ptr(), logits.shape[0], logits.shape[1],
+                                                   logits.stride(0), m.shape[0], int(logits.dtype == torch.float32),
+                                                   logits.device.index or 0, torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "ft_apply_token_mask")
+        return logits
+    keep = unpack_mask(packed.to(logits.device), logits.shape[1])
+    return logits.masked_fill_(~keep.expand_as(logits), float("-inf"))
+
 
 class TokenTransitionCache:
     """Masks by matcher state (json_schema.rs:111-165): decoding revisits the same states (inside

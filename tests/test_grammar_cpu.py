@@ -196,3 +196,33 @@ def test_native_mask_walk_equals_the_python_walk_and_is_shared():
     broken.grammar()._memo.clear()
     with pytest.raises(RuntimeError, match="boom"):
         broken.compute_mask()
+
+
+def test_packed_masks_round_trip_and_apply_in_place():
+    torch.manual_seed(0)
+    bits = torch.rand(3, 70) > 0.5
+    packed = torch.stack([G.TokenMask(b).packed() for b in bits])
+    assert packed.shape == (3, 3) and packed.dtype == torch.int32
+    assert torch.equal(G.unpack_mask(packed, 70), bits)
+    logits = torch.randn(3, 70)
+    want = logits.masked_fill(~bits, float("-inf"))
+    assert torch.equal(G.apply_packed_mask_(logits.clone(), packed), want)
+    one = G.apply_packed_mask_(logits.clone(), packed[:1])                   # one mask row for every logits row
+    assert torch.equal(one, logits.masked_fill(~bits[:1].expand(3, 70), float("-inf")))
+    assert torch.equal(G.TokenMask(bits[0]).apply_(logits.clone()), one)
+    for bad in (packed[:2], packed[:, :2]):
+        with pytest.raises(ValueError):
+            G.apply_packed_mask_(logits.clone(), bad)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(__import__("os").environ.get("FT_TEST_NEW_PATHS") != "1", reason="set FT_TEST_NEW_PATHS=1 to run")
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_packed_mask_kernel_matches_torch(dtype):
+    torch.manual_seed(0)
+    bits = torch.rand(5, 128257) > 0.3
+    packed = torch.stack([G.TokenMask(b).packed() for b in bits])
+    logits = torch.randn(5, 128257, device="cuda").to(dtype)
+    want = logits.masked_fill(~bits.cuda(), float("-inf"))
+    assert torch.equal(G.apply_packed_mask_(logits.clone(), packed), want)
+    assert torch.equal(G.apply_packed_mask_(logits.clone(), packed[:1]), logits.masked_fill(~bits[:1].cuda(), float("-inf")))
