@@ -483,3 +483,26 @@ def test_cuda_vocabulary_degrades_cleanly_without_a_gpu():
             with pytest.raises(C.GpuError):
                 call()
     assert torch.equal(C.tensor_to_cpu(a), a)
+
+
+def test_parity_sweep_extended_cases_and_audit_file(tmp_path):
+    import subprocess
+    import sys
+
+    from ferrotorch_b200.utils import parity
+
+    rows = parity.sweep(["linear_bwd", "rope", "q4_0_linear", "linear_cross_entropy"], "cpu", random_shapes=1)
+    assert [r["op"] for r in rows] == ["linear_bwd", "rope", "q4_0_linear", "linear_cross_entropy"] and all(r["ok"] for r in rows)
+    assert rows[0]["shapes"] == 3 and rows[2]["shapes"] == 2            # tile-edge shapes only where the op takes any size
+    assert len(parity.sweep(None, "cpu")) == 5 and len(parity.sweep(None, "cpu", extended=True)) == 14
+    with pytest.raises(KeyError):
+        parity.sweep(["nope"], "cpu")
+    shapes = parity._edge_shapes((300, 264, 16), 5, seed=1)
+    assert all(s[2] == 16 and s[1] % 8 == 0 and abs((s[0] + 3) % 128 - 3) <= 3 for s in shapes)
+    out = tmp_path / "audit.json"
+    proc = subprocess.run([sys.executable, "-m", "ferrotorch_b200.utils.parity", "--device", "cpu", "--ops", "swiglu_bwd",
+                           "--out", str(out)], capture_output=True, text=True, timeout=300,
+                          cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    audit = json.loads(out.read_text())
+    assert audit["rows"][0]["op"] == "swiglu_bwd" and audit["rows"][0]["ok"]
