@@ -238,6 +238,82 @@ class LlamaForCausalLM(nn.Module):
         return [KVCache(batch, max_len, c.num_key_value_heads, c.head_dim, device, dtype)
                 for _ in range(c.num_hidden_layers)]
 
+    # ------------------------------------------------------------------ model directories and files
+    @classmethod
+    def from_pretrained(cls, path: str, dtype: torch.dtype = torch.bfloat16, device="cpu") -> "LlamaForCausalLM":
+        """Build the model a Hugging Face directory describes (``config.json`` plus
+        ``model.safetensors``, a sharded ``model.safetensors.index.json`` or ``pytorch_model.bin``)
+        and load its weights; a tied checkpoint without ``lm_head.weight`` shares the embedding
+        (ferrotorch-llama/src/model.rs:382-386)."""
+        import os
+
+        from ..serialize.state import load_pytorch_state_dict, load_safetensors_auto
+
+        cfg = LlamaConfig.from_hf(os.path.join(path, "config.json"))
+        model = cls(cfg).to(device=device, dtype=dtype)
+        if any(os.path.exists(os.path.join(path, f)) for f in ("model.safetensors", "model.safetensors.index.json")):
+            sd = load_safetensors_auto(path, dtype=dtype)
+        elif os.path.exists(os.path.join(path, "pytorch_model.bin")):
+            sd = load_pytorch_state_dict(os.path.join(path, "pytorch_model.bin"))
+        else:
+            raise FileNotFoundError("no model.safetensors[.index.json] or pytorch_model.bin under %s" % path)
+        if "lm_head.weight" not in sd and "model.embed_tokens.weight" in sd:
+            sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
+        model.load_hf_state_dict(sd)
+        if cfg.tie_word_embeddings:
+            model.lm_head.weight = model.model.embed_tokens.weight
+        return model
+
+    def save_pretrained(self, path: str, max_shard_bytes: int | None = None) -> None:
+        """Write ``config.json`` and the weights under their Hugging Face names (one
+        ``model.safetensors``, or shards plus an index when ``max_shard_bytes`` is given)."""
+        import json as _json
+        import os
+
+        from ..serialize.state import save_safetensors, save_safetensors_sharded
+
+        os.makedirs(path, exist_ok=True)
+        cfg = {k: v for k, v in self.config.to_dict().items() if v is not None}
+        cfg.update(architectures=["LlamaForCausalLM"], model_type="llama")
+        with open(os.path.join(path, "config.json"), "w") as f:
+            _json.dump(cfg, f, indent=2)
+        sd = self.hf_state_dict()
+        if self.config.tie_word_embeddings:
+            sd.pop("lm_head.weight", None)
+        if max_shard_bytes:
+            save_safetensors_sharded(sd, path, max_shard_bytes=max_shard_bytes)
+        else:
+            save_safetensors(sd, os.path.join(path, "model.safetensors"))
+
+    @classmethod
+    def from_gguf(cls, path: str, dtype: torch.dtype = torch.bfloat16, device="cpu", nibble_order: str = "ggml") -> "LlamaForCausalLM":
+        """Build from a GGUF file: the ``llama.*`` metadata gives the configuration, the tensors are
+        dequantised on the host and renamed to the Hugging Face keys
+        (ferrotorch-serialize/src/gguf.rs:909, ferrotorch-llama/src/gguf_remap.rs:23-52)."""
+        from ..serialize.gguf import GgufFile, gguf_key_to_hf
+
+        with GgufFile(path) as f:
+            md = f.metadata
+            arch = md.get("general.architecture", "llama")
+            g = lambda k, default=None: md.get("%s.%s" % (arch, k), default)      # noqa: E731
+            emb = f.tensors.get("token_embd.weight")
+            heads = int(g("attention.head_count"))
+            cfg = LlamaConfig(vocab_size=int(g("vocab_size", emb[1][0] if emb else 0)), hidden_size=int(g("embedding_length")),
+                              intermediate_size=int(g("feed_forward_length")), num_hidden_layers=int(g("block_count")),
+                              num_attention_heads=heads, num_key_value_heads=int(g("attention.head_count_kv", heads)),
+                              max_position_embeddings=int(g("context_length", 8192)),
+                              rms_norm_eps=float(g("attention.layer_norm_rms_epsilon", 1e-5)),
+                              rope_theta=float(g("rope.freq_base", 10000.0)), tie_word_embeddings="output.weight" not in f.tensors)
+            cfg.validate()
+            sd = {(gguf_key_to_hf(n) or n): f.dequantize(n, dtype, nibble_order) for n in f.tensors}
+        if "lm_head.weight" not in sd:
+            sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
+        model = cls(cfg).to(device=device, dtype=dtype)
+        model.load_hf_state_dict({k: v for k, v in sd.items() if k.startswith(("model.", "lm_head."))})
+        if cfg.tie_word_embeddings:
+            model.lm_head.weight = model.model.embed_tokens.weight
+        return model
+
     # ------------------------------------------------------------------ HF key layout
     def hf_state_dict(self) -> dict[str, torch.Tensor]:
         """State dict with HF-native keys (separate q/k/v and gate/up projections)."""

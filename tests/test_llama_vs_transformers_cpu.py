@@ -59,3 +59,56 @@ def test_state_dict_round_trip_keeps_hf_names():
     assert set(back) == set(ref)
     for k in ref:
         assert torch.equal(back[k], ref[k]), k
+
+
+def test_from_pretrained_reads_a_transformers_directory_and_round_trips(tmp_path):
+    hf, _ = _pair(tie_word_embeddings=True)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    ours = LlamaForCausalLM.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    ids = torch.randint(0, 128, (2, 11), generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        assert torch.allclose(ours(ids).float(), hf(input_ids=ids).logits, atol=2e-4)
+    assert ours.lm_head.weight is ours.model.embed_tokens.weight              # tied, as the config says
+    ours.save_pretrained(str(tmp_path / "back"))
+    again = tr.LlamaForCausalLM.from_pretrained(str(tmp_path / "back")).eval()   # and transformers reads ours
+    with torch.no_grad():
+        assert torch.allclose(again(input_ids=ids).logits, hf(input_ids=ids).logits, atol=1e-5)
+    ours.save_pretrained(str(tmp_path / "sharded"), max_shard_bytes=64 << 10)
+    sharded = LlamaForCausalLM.from_pretrained(str(tmp_path / "sharded"), dtype=torch.float32).eval()
+    with torch.no_grad():
+        assert torch.equal(sharded(ids), ours(ids))
+    with pytest.raises(FileNotFoundError):
+        (tmp_path / "empty").mkdir()
+        (tmp_path / "empty" / "config.json").write_text((tmp_path / "back" / "config.json").read_text())
+        LlamaForCausalLM.from_pretrained(str(tmp_path / "empty"))
+
+
+def test_from_gguf_builds_the_model_the_file_describes(tmp_path):
+    from ferrotorch_b200.serialize import gguf as G
+
+    hf, ours = _pair()
+    sd = ours.hf_state_dict()
+    inv = {"model.embed_tokens": "token_embd", "model.norm": "output_norm", "lm_head": "output"}
+    layer = {v: k for k, v in G._LAYER_MAP.items()}
+    tensors = {}
+    for k, v in sd.items():
+        base, kind = k.rsplit(".", 1)
+        if base in inv:
+            name = "%s.%s" % (inv[base], kind)
+        else:
+            _, _, i, rest = base.split(".", 3)
+            name = "blk.%s.%s.%s" % (i, layer[rest], kind)
+        if v.dim() == 2 and "token_embd" not in name:
+            tensors[name] = (G.GGML_F16, tuple(v.shape), v.to(torch.float16).numpy().tobytes())
+        else:
+            tensors[name] = (G.GGML_F32, tuple(v.shape), v.float().numpy().tobytes())
+    md = {"general.architecture": "llama", "llama.embedding_length": 64, "llama.feed_forward_length": 112, "llama.block_count": 2,
+          "llama.attention.head_count": 4, "llama.attention.head_count_kv": 2, "llama.context_length": 256,
+          "llama.attention.layer_norm_rms_epsilon": 1e-5, "llama.rope.freq_base": 10000.0, "llama.vocab_size": 128}
+    path = str(tmp_path / "m.gguf")
+    G.write_gguf(path, tensors, md)
+    model = LlamaForCausalLM.from_gguf(path, dtype=torch.float32).eval()
+    assert (model.config.num_key_value_heads, model.config.intermediate_size, model.config.tie_word_embeddings) == (2, 112, False)
+    ids = torch.randint(0, 128, (1, 9), generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        assert torch.allclose(model(ids).float(), ours(ids).float(), atol=5e-3)       # weights went through fp16
