@@ -73,6 +73,20 @@ class LlamaEngine:
         self.manager = PagedAttentionManager(self.cache)
         self._load(weights, seed)
 
+    @classmethod
+    def from_pretrained(cls, path: str, tp: TPContext | None = None, **kw) -> "LlamaEngine":
+        """An engine over the weights of a Hugging Face model directory (``config.json`` and
+        SafeTensors, single file or sharded); every rank reads the files and keeps its shard."""
+        import os
+
+        from ..serialize.state import load_safetensors_auto
+
+        cfg = LlamaConfig.from_hf(os.path.join(path, "config.json"))
+        sd = load_safetensors_auto(path)
+        if "lm_head.weight" not in sd:
+            sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
+        return cls(cfg, tp, weights=sd, **kw)
+
     # ------------------------------------------------------------------ weights
     def _load(self, sd: dict | None, seed: int) -> None:
         cfg, dev, W, r = self.cfg, self.device, self.W, self.r
