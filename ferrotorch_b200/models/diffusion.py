@@ -798,3 +798,63 @@ class StableDiffusionPipeline:
 def to_uint8(image: torch.Tensor) -> torch.Tensor:
     """Decoder output ``[B, 3, H, W]`` in [-1, 1] -> ``[B, H, W, 3]`` bytes."""
     return ((image.float() / 2 + 0.5).clamp(0, 1) * 255).round().to(torch.uint8).permute(0, 2, 3, 1).contiguous()
+
+
+def load_stable_diffusion(path: str, dtype: torch.dtype = torch.float32, device="cpu") -> StableDiffusionPipeline:
+    """Assemble the pipeline from a diffusers-style model directory::
+
+        text_encoder/config.json + model.safetensors
+        unet/config.json         + diffusion_pytorch_model.safetensors
+        vae/config.json          + diffusion_pytorch_model.safetensors
+        scheduler/scheduler_config.json          (optional)
+
+    (ferrotorch-diffusion/src/safetensors_loader.rs reads the same three weight files.)"""
+    import os
+
+    from ..serialize.state import load_safetensors
+
+    def part(sub, names):
+        for n in names:
+            p = os.path.join(path, sub, n)
+            if os.path.exists(p):
+                return p
+        raise FileNotFoundError("no %s under %s" % (" / ".join(names), os.path.join(path, sub)))
+
+    def cfg(cls, sub, rename=None):
+        p = os.path.join(path, sub, "config.json")
+        return _from_json(cls, p, rename) if os.path.exists(p) else cls()
+
+    clip = ClipTextEncoder(cfg(ClipTextConfig, "text_encoder"))
+    clip.load_hf_state_dict(load_safetensors(part("text_encoder", ["model.safetensors"])))
+    unet = UNet2DConditionModel(cfg(UNet2DConditionConfig, "unet"))
+    unet.load_state_dict(load_safetensors(part("unet", ["diffusion_pytorch_model.safetensors", "model.safetensors"])))
+    vae = AutoencoderKL(cfg(VaeConfig, "vae"))
+    vae.load_hf_state_dict(load_safetensors(part("vae", ["diffusion_pytorch_model.safetensors", "model.safetensors"])))
+    sched_cfg = DDIMConfig()
+    sp = os.path.join(path, "scheduler", "scheduler_config.json")
+    if os.path.exists(sp):
+        with open(sp) as f:
+            raw = json.load(f)
+        sched_cfg = DDIMConfig(**{k: raw[k] for k in DDIMConfig.__dataclass_fields__ if k in raw})
+    for m in (clip, unet, vae):
+        m.to(device=device, dtype=dtype).eval()
+    return StableDiffusionPipeline(clip, unet, vae, DDIMScheduler(sched_cfg))
+
+
+def save_stable_diffusion(pipe: StableDiffusionPipeline, path: str) -> None:
+    """Write the directory layout :func:`load_stable_diffusion` reads."""
+    import os
+    from dataclasses import asdict
+
+    from ..serialize.state import save_safetensors
+
+    for sub, module, fname in (("text_encoder", pipe.text_encoder, "model.safetensors"),
+                               ("unet", pipe.unet, "diffusion_pytorch_model.safetensors"),
+                               ("vae", pipe.vae, "diffusion_pytorch_model.safetensors")):
+        os.makedirs(os.path.join(path, sub), exist_ok=True)
+        with open(os.path.join(path, sub, "config.json"), "w") as f:
+            json.dump({k: (list(v) if isinstance(v, tuple) else v) for k, v in asdict(module.config).items()}, f, indent=2)
+        save_safetensors(module.state_dict(), os.path.join(path, sub, fname))
+    os.makedirs(os.path.join(path, "scheduler"), exist_ok=True)
+    with open(os.path.join(path, "scheduler", "scheduler_config.json"), "w") as f:
+        json.dump(asdict(pipe.scheduler.config), f, indent=2)

@@ -548,3 +548,73 @@ class MlpPolicy(nn.Module):
 
     def load_hf_state_dict(self, sd: dict, strict: bool = True) -> DropReport:
         return _load(self, sd, strip=("policy.",), strict=strict)
+
+
+# --------------------------------------------------------------------------- loaders (safetensors_loader.rs of each crate)
+def _read_weights(path: str) -> dict:
+    """A SafeTensors file, a ``.pt`` / ``.bin`` state dict, or a model directory."""
+    import os
+
+    from ..serialize.state import load_pytorch_state_dict, load_safetensors, load_safetensors_auto
+
+    if os.path.isdir(path):
+        if any(os.path.exists(os.path.join(path, f)) for f in ("model.safetensors", "model.safetensors.index.json")):
+            return load_safetensors_auto(path)
+        for f in ("pytorch_model.bin", "policy.pth", "model.pt"):
+            if os.path.exists(os.path.join(path, f)):
+                return load_pytorch_state_dict(os.path.join(path, f))
+        raise FileNotFoundError("no weights (model.safetensors, pytorch_model.bin ...) under %s" % path)
+    if path.endswith(".safetensors"):
+        return load_safetensors(path)
+    return load_pytorch_state_dict(path)
+
+
+def _config_path(path: str) -> str | None:
+    import os
+
+    p = os.path.join(path, "config.json") if os.path.isdir(path) else os.path.join(os.path.dirname(path), "config.json")
+    return p if os.path.exists(p) else None
+
+
+def load_bert_model(path: str, config: BertConfig | None = None) -> tuple[BertModel, DropReport]:
+    """``(model, report)`` from a Hugging Face BERT directory or weight file; the configuration
+    comes from the neighbouring ``config.json`` unless given."""
+    cfg_file = _config_path(path)
+    cfg = config or (BertConfig.from_hf(cfg_file) if cfg_file else BertConfig())
+    model = BertModel(cfg).eval()
+    return model, model.load_hf_state_dict(_read_weights(path))
+
+
+def load_sentence_transformer(path: str, config: BertConfig | None = None, normalize: bool = True):
+    cfg_file = _config_path(path)
+    cfg = config or (BertConfig.from_hf(cfg_file) if cfg_file else BertConfig())
+    model = SentenceTransformer(cfg, normalize).eval()
+    return model, model.load_hf_state_dict(_read_weights(path))
+
+
+def load_whisper_encoder(path: str, config: WhisperConfig | None = None):
+    cfg_file = _config_path(path)
+    cfg = config or (WhisperConfig.from_hf(cfg_file) if cfg_file else WhisperConfig())
+    model = WhisperEncoder(cfg).eval()
+    return model, model.load_hf_state_dict(_read_weights(path))
+
+
+def load_gcn_net(path: str, in_features: int | None = None, hidden: int | None = None, num_classes: int | None = None):
+    """The layer sizes are read off the weights (``conv1.lin.weight [hidden, in]``,
+    ``conv2.lin.weight [classes, hidden]``) unless given."""
+    sd = _read_weights(path)
+    h, i = sd["conv1.lin.weight"].shape
+    c = sd["conv2.lin.weight"].shape[0]
+    model = GcnNet(in_features or i, hidden or h, num_classes or c).eval()
+    return model, model.load_hf_state_dict(sd)
+
+
+def load_ppo_policy(path: str, config: MlpPolicyConfig | None = None):
+    """An SB3 ``policy.pth`` / SafeTensors export; sizes come from the weights unless given."""
+    sd = _read_weights(path)
+    sd = {(k[7:] if k.startswith("policy.") else k): v for k, v in sd.items()}
+    if config is None:
+        hid, obs = sd["mlp_extractor.policy_net.0.weight"].shape
+        config = MlpPolicyConfig(obs, hid, sd["action_net.weight"].shape[0])
+    model = MlpPolicy(config).eval()
+    return model, model.load_hf_state_dict(sd)

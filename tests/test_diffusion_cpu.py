@@ -172,3 +172,21 @@ def test_pipeline_guidance_and_determinism():
         pipe.generate(cond, unc[:, :3], lat, 2)
     with pytest.raises(ValueError):
         pipe(ids, height=30, width=32)
+
+
+def test_pipeline_directory_round_trip(tmp_path):
+    clip, unet, vae = _tiny()
+    pipe = D.StableDiffusionPipeline(clip, unet, vae, D.DDIMScheduler(D.DDIMConfig(set_alpha_to_one=True)))
+    D.save_stable_diffusion(pipe, str(tmp_path / "sd"))
+    for rel in ("text_encoder/model.safetensors", "unet/diffusion_pytorch_model.safetensors", "vae/config.json",
+                "scheduler/scheduler_config.json"):
+        assert (tmp_path / "sd" / rel).exists(), rel
+    back = D.load_stable_diffusion(str(tmp_path / "sd"))
+    assert back.scheduler.config.set_alpha_to_one and back.unet.config.block_out_channels == (16, 32)
+    ids = torch.randint(2, 100, (1, 5))
+    a = pipe(ids, height=32, width=32, num_inference_steps=2, seed=1)
+    b = back(ids, height=32, width=32, num_inference_steps=2, seed=1)
+    assert torch.allclose(a, b, atol=1e-6)
+    (tmp_path / "sd" / "unet" / "diffusion_pytorch_model.safetensors").unlink()
+    with pytest.raises(FileNotFoundError):
+        D.load_stable_diffusion(str(tmp_path / "sd"))

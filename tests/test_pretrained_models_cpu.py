@@ -141,3 +141,42 @@ def test_sb3_policy_layout():
     assert (p.mlp_extractor.obs_dim(), p.mlp_extractor.hidden(), p.config().n_actions) == (4, 64, 2)
     with pytest.raises(ValueError):
         p(torch.randn(3, 5))
+
+
+def test_loaders_read_model_directories_and_files(tmp_path):
+    from ferrotorch_b200.serialize.state import save_pytorch, save_safetensors
+
+    hf = tr.BertModel(tr.BertConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                    intermediate_size=64, max_position_embeddings=20)).eval()
+    hf.save_pretrained(str(tmp_path / "bert"), safe_serialization=True)
+    model, rep = P.load_bert_model(str(tmp_path / "bert"))
+    assert rep.missing == [] and model.config.hidden_size == 32
+    ids = torch.randint(0, 100, (2, 7))
+    with torch.no_grad():
+        assert torch.allclose(model(ids)[0], hf(input_ids=ids).last_hidden_state, atol=1e-5)
+    st, rep = P.load_sentence_transformer(str(tmp_path / "bert" / "model.safetensors"))       # file + neighbouring config
+    assert rep.missing == [] and torch.allclose(st.encode(ids).norm(dim=-1), torch.ones(2), atol=1e-6)
+    hc = tr.WhisperConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=4, encoder_ffn_dim=64,
+                          max_source_positions=20, decoder_layers=1, decoder_attention_heads=4, decoder_ffn_dim=64,
+                          vocab_size=60, max_target_positions=10, pad_token_id=0, bos_token_id=1, eos_token_id=2,
+                          decoder_start_token_id=1)
+    wm = tr.WhisperModel(hc).eval()
+    wm.save_pretrained(str(tmp_path / "whisper"), safe_serialization=True)
+    enc, rep = P.load_whisper_encoder(str(tmp_path / "whisper"))
+    mel = torch.randn(1, 16, 40)          # the HF encoder insists on exactly 2 * max_source_positions frames
+    with torch.no_grad():
+        assert rep.missing == [] and torch.allclose(enc(mel), wm.encoder(mel).last_hidden_state, atol=1e-5)
+    g = P.GcnNet(7, 5, 3)
+    save_safetensors(g.state_dict(), str(tmp_path / "gcn.safetensors"))
+    g2, rep = P.load_gcn_net(str(tmp_path / "gcn.safetensors"))
+    assert (g2.in_features(), g2.hidden(), g2.num_classes()) == (7, 5, 3) and rep.missing == []
+    pol = P.MlpPolicy(P.MlpPolicyConfig(6, 16, 3))
+    sd = {"policy." + k: v for k, v in pol.state_dict().items()}
+    sd["policy.log_std"] = torch.zeros(3)
+    save_pytorch(sd, str(tmp_path / "policy.pth"))
+    p2, rep = P.load_ppo_policy(str(tmp_path / "policy.pth"))
+    obs = torch.randn(2, 6)
+    assert p2.config() == P.MlpPolicyConfig(6, 16, 3) and rep.dropped == ["log_std"] and torch.equal(p2(obs).value, pol.eval()(obs).value)
+    with pytest.raises(FileNotFoundError):
+        (tmp_path / "none").mkdir()
+        P.load_bert_model(str(tmp_path / "none"))
