@@ -212,7 +212,12 @@ class AmpContext:
 class Learner:
     def __init__(self, model: nn.Module, optimizer, loss_fn, *, scheduler=None, metrics=None, callbacks=None,
                  amp: AmpContext | None = None, max_grad_norm: float | None = None, ddp=None, device=None,
-                 checkpoint_dir: str | None = None, log_every: int = 10):
+                 checkpoint_dir: str | None = None, log_every: int = 10, trainer=None):
+        """``trainer``: a :class:`~ferrotorch_b200.train.engine.FlatTrainer` (plain, data-parallel,
+        tensor-parallel or hybrid) that owns forward, backward, clipping and the fused update; the
+        Learner then drives epochs, callbacks, metrics on the loss, schedules and checkpoints around
+        ``trainer.step`` and ``optimizer`` / ``loss_fn`` may be ``None``."""
+        self.trainer = trainer
         self.model, self.optimizer, self.loss_fn = model, optimizer, loss_fn
         self.scheduler, self.amp, self.max_grad_norm, self.ddp = scheduler, amp, max_grad_norm, ddp
         self.metrics = metrics if metrics is not None else [LossMetric()]
@@ -243,7 +248,13 @@ class Learner:
         params = [p for p in self.model.parameters() if p.requires_grad]
         for bi, (x, y) in enumerate(data):
             x, y = self._to_device(x), self._to_device(y)
-            if train:
+            if train and self.trainer is not None:
+                loss = self.trainer.step(x, y)
+                out = None
+                self.global_step += 1
+                for cb in self.callbacks:
+                    cb.on_batch_end(self, self.epoch, bi, loss.detach())
+            elif train:
                 self.optimizer.zero_grad(set_to_none=True)
                 out, loss = self._forward(x, y)
                 if self.amp is not None and self.ddp is None:
@@ -258,12 +269,29 @@ class Learner:
                 self.global_step += 1
                 for cb in self.callbacks:
                     cb.on_batch_end(self, self.epoch, bi, loss.detach())
+            elif self.trainer is not None:
+                with torch.no_grad():
+                    out, loss = None, self.trainer.evaluate(x, y) if hasattr(self.trainer, "evaluate") else self._trainer_loss(x, y)
             else:
                 with torch.no_grad():
                     out, loss = self._forward(x, y)
             for m in self.metrics:
-                m.update(out, y, loss.detach())
+                if out is not None or isinstance(m, (LossMetric, RunningAverage)):
+                    m.update(out, y, loss.detach())
         return {m.name: m.compute() for m in self.metrics}
+
+    def _trainer_loss(self, x, y):
+        """Evaluation loss through the trainer's model: ``model(x, labels=y)`` convention of the
+        language models, else ``loss_fn(model(x), y)``."""
+        out = self.model(x)
+        if self.loss_fn is not None:
+            return self.loss_fn(out, y)
+        return nn.functional.cross_entropy(out.float().reshape(-1, out.shape[-1]), y.reshape(-1))
+
+    def _lr(self):
+        if self.trainer is not None:
+            return float(getattr(self.trainer, "lr", 0.0))
+        return self.optimizer.param_groups[0]["lr"]
 
     def fit(self, train_data, val_data=None, epochs: int = 1) -> TrainingHistory:
         for cb in self.callbacks:
@@ -280,7 +308,7 @@ class Learner:
                     self.scheduler.step((va or tr)["loss"])
                 else:
                     self.scheduler.step()
-            res = EpochResult(epoch, tr, va, self.optimizer.param_groups[0]["lr"])
+            res = EpochResult(epoch, tr, va, self._lr())
             self.history.append(res)
             if self.checkpoint_dir:
                 os.makedirs(self.checkpoint_dir, exist_ok=True)
@@ -301,13 +329,16 @@ class Learner:
         extra = {"rng": torch.get_rng_state().tolist()}
         if self.amp is not None:
             extra["scaler"] = self.amp.scaler.state_dict()
-        save_checkpoint(path, self.model.state_dict(), self.optimizer.state_dict(), epoch=self.epoch,
-                        step=self.global_step, extra=extra)
+        opt_state = self.trainer.state_dict() if self.trainer is not None else self.optimizer.state_dict()
+        save_checkpoint(path, self.model.state_dict(), opt_state, epoch=self.epoch, step=self.global_step, extra=extra)
 
     def load_checkpoint(self, path: str) -> None:
         ck = load_checkpoint(path)
         self.model.load_state_dict(ck["model"])
-        self.optimizer.load_state_dict(ck["optimizer"])
+        if self.trainer is not None:
+            self.trainer.load_state_dict(ck["optimizer"])
+        else:
+            self.optimizer.load_state_dict(ck["optimizer"])
         self.epoch, self.global_step = ck["epoch"] + 1, ck["step"]
         if "rng" in ck["extra"]:
             torch.set_rng_state(torch.tensor(ck["extra"]["rng"], dtype=torch.uint8))

@@ -506,3 +506,38 @@ def test_parity_sweep_extended_cases_and_audit_file(tmp_path):
     assert proc.returncode == 0, proc.stderr[-2000:]
     audit = json.loads(out.read_text())
     assert audit["rows"][0]["op"] == "swiglu_bwd" and audit["rows"][0]["ok"]
+
+
+def test_learner_drives_a_flat_trainer(tmp_path):
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.train.engine import FlatTrainer
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                      num_key_value_heads=1)
+    model = LlamaForCausalLM(cfg)
+    trainer = FlatTrainer(model, lr=5e-3, weight_decay=0.0, max_grad_norm=1.0)
+    g = torch.Generator().manual_seed(1)
+    batches = [torch.randint(0, 64, (4, 9), generator=g) for _ in range(4)]
+    data = [(b[:, :-1], b[:, 1:]) for b in batches]
+    seen = []
+
+    class Spy(T.Callback):
+        def on_batch_end(self, learner, epoch, batch, loss):
+            seen.append(float(loss))
+
+    lr = T.Learner(model, None, None, trainer=trainer, callbacks=[Spy()], checkpoint_dir=str(tmp_path))
+    hist = lr.fit(data, val_data=data, epochs=3)
+    assert len(seen) == 12 and lr.global_step == 12 and len(hist.epochs) == 3
+    assert hist.epochs[-1].train["loss"] < hist.epochs[0].train["loss"] and hist.epochs[-1].val["loss"] < hist.epochs[0].val["loss"]
+    assert hist.epochs[0].lr == 5e-3 and (tmp_path / "checkpoint_epoch_2.ftc").exists()
+    # resume: a fresh model + trainer continue from the checkpoint with the same next-step loss
+    torch.manual_seed(0)
+    model2 = LlamaForCausalLM(cfg)
+    trainer2 = FlatTrainer(model2, lr=5e-3, weight_decay=0.0, max_grad_norm=1.0)
+    lr2 = T.Learner(model2, None, None, trainer=trainer2)
+    lr2.load_checkpoint(str(tmp_path / "checkpoint_epoch_2.ftc"))
+    assert lr2.epoch == 3 and lr2.global_step == 12
+    a = float(trainer.step(*data[0]))
+    b = float(trainer2.step(*data[0]))
+    assert a == pytest.approx(b, rel=1e-5)
