@@ -1,0 +1,54 @@
+"""Convolution binding: the kernel's tile arithmetic restated on the CPU against torch's conv2d,
+the flipped-filter identity the input gradient relies on, fallbacks and the module rewrite."""
+import pytest
+import torch
+import torch.nn.functional as tF
+
+from ferrotorch_b200.ops import conv as C
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,hw", [
+    (64, 16, 3, 1, 1, 1, (9, 7)), (128, 8, 3, 2, 1, 1, (10, 11)), (64, 24, 1, 1, 0, 1, (5, 6)),
+    (64, 8, 1, 2, 0, 1, (8, 8)), (64, 8, 3, 1, 2, 2, (9, 9)), (64, 8, 7, 2, 3, 1, (15, 13)), (4, 8, 3, 1, (1, 0), 1, (6, 6)),
+])
+def test_tile_arithmetic_equals_conv2d(cin, cout, k, stride, pad, dil, hw):
+    torch.manual_seed(0)
+    x, w = torch.randn(3, cin, *hw), torch.randn(cout, cin, k, k) * 0.1
+    ref = tF.conv2d(x, w, None, stride, pad, dil)
+    got = C.implicit_gemm_reference(x, w, stride, pad, dil)
+    assert got.shape == ref.shape
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("k,pad,dil", [(3, 1, 1), (3, 0, 1), (1, 0, 1), (3, 2, 2), (5, 2, 1)])
+def test_input_gradient_is_a_convolution_with_the_flipped_filter(k, pad, dil):
+    torch.manual_seed(1)
+    x, w = torch.randn(2, 6, 9, 8), torch.randn(5, 6, k, k)
+    gy = torch.randn_like(tF.conv2d(x, w, None, 1, pad, dil))
+    ref = torch.nn.grad.conv2d_input(x.shape, w, gy, 1, pad, dil)
+    bp = dil * (k - 1) - pad
+    wt = w.flip(2, 3).transpose(0, 1)
+    torch.testing.assert_close(tF.conv2d(gy, wt, None, 1, bp, dil), ref, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(C.implicit_gemm_reference(gy, wt, 1, bp, dil), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_fallback_module_and_rewrite():
+    torch.manual_seed(2)
+    net = torch.nn.Sequential(torch.nn.Conv2d(8, 16, 3, 1, 1), torch.nn.ReLU(), torch.nn.Conv2d(16, 4, 1, bias=False))
+    x = torch.randn(2, 8, 6, 6, requires_grad=True)
+    ref = net(x)
+    keys = list(net.state_dict())
+    assert C.convert_convs(net) == 2 and isinstance(net[0], C.IgemmConv2d) and list(net.state_dict()) == keys
+    prev = C.use_native_conv(True)                              # CPU tensors: not supported, so torch runs
+    try:
+        out = net(x)
+        assert not C.supported(x, net[0].weight, 1, 1, 1)
+    finally:
+        C.use_native_conv(prev)
+    torch.testing.assert_close(out, ref)
+    out.sum().backward()
+    assert x.grad is not None
+    res = torch.randn(2, 16, 6, 6)
+    fused = net[0](x, residual=res, relu=True)
+    torch.testing.assert_close(fused, torch.relu(tF.conv2d(x, net[0].weight, net[0].bias, 1, 1) + res))
+    assert C.out_size(224, 7, 2, 3, 1) == 112 and C.out_size(56, 3, 1, 1, 1) == 56
