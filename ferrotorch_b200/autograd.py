@@ -40,6 +40,16 @@ def backward_with_grad(tensor: torch.Tensor, grad_output: torch.Tensor, retain_g
     tensor.backward(grad_output, retain_graph=retain_graph)
 
 
+def backward_parallel(tensor: torch.Tensor, grad_output: torch.Tensor | None = None, retain_graph: bool = False) -> None:
+    """Reverse pass with independent branches run concurrently (graph.rs:415).  torch's engine
+    already runs one worker thread per device and overlaps ready nodes across them, so this is
+    ``backward`` with the optional seed gradient; it exists so that callers of the reference
+    keep their call."""
+    if grad_output is None and tensor.numel() != 1:
+        raise ValueError("backward_parallel: a root with more than one element needs grad_output")
+    tensor.backward(grad_output, retain_graph=retain_graph)
+
+
 def checkpoint(fn: Callable, *args, preserve_rng_state: bool = True, **kw):
     """Recompute ``fn`` in backward instead of keeping its activations; CPU / CUDA RNG state and the
     autocast state at call time are restored for the recomputation (checkpoint.rs:76-121)."""

@@ -1,6 +1,6 @@
 """Parallel runtime: back-ends and collectives, data / tensor / pipeline / fully-sharded
 parallelism, device meshes and distributed tensors."""
-from .backend import (BackendUnavailable, DistributedError, Group, InvalidRank, InvalidWorldSize, IoError,  # noqa: F401
+from .backend import (BackendUnavailable, DistributedError, Group, HybridGroup, InvalidRank, InvalidWorldSize, IoError,  # noqa: F401
                       NoConnection, RendezvousConfig, SelfSend, SimulatedGroup, SizeMismatch, SubGroup, TcpGroup, Timeout, TorchGroup,
                       UnsupportedOp, init_group, run_simulated)
 from .elastic import FileStore, Heartbeat, RankFailure, TorchStore, survivors  # noqa: F401

@@ -455,6 +455,62 @@ class TorchGroup(Group):
         return out
 
 
+class HybridGroup(Group):
+    """Two transports under one group (ferrotorch-distributed/src/hybrid_backend.rs:49-120): a
+    ``control`` group (TCP) carries point-to-point messages, barriers and collectives on host
+    tensors, a ``data`` group (NCCL) carries collectives on device tensors.  The control group is
+    built first, so a rank that cannot rendezvous fails before any NCCL communicator exists."""
+
+    def __init__(self, control: Group, data: Group):
+        if (control.rank, control.world_size) != (data.rank, data.world_size):
+            raise InvalidRank("HybridGroup: control is rank %d of %d but data is rank %d of %d"
+                              % (control.rank, control.world_size, data.rank, data.world_size))
+        self.control, self.data = control, data
+        self.rank, self.world_size = control.rank, control.world_size
+
+    def tcp(self) -> Group:
+        return self.control
+
+    def nccl(self) -> Group:
+        return self.data
+
+    def _for(self, t: torch.Tensor) -> Group:
+        return self.data if t.is_cuda else self.control
+
+    def send(self, t, dst):
+        self.control.send(t, dst)
+
+    def recv(self, t, src, timeout=None):
+        self.control.recv(t, src, timeout)
+
+    def barrier(self):
+        self.control.barrier()
+
+    def all_reduce(self, t, op="sum"):
+        return self._for(t).all_reduce(t, op)
+
+    def broadcast(self, t, root=0):
+        return self._for(t).broadcast(t, root)
+
+    def all_gather(self, t):
+        return self._for(t).all_gather(t)
+
+    def reduce_scatter(self, t, op="sum"):
+        return self._for(t).reduce_scatter(t, op)
+
+    def all_to_all(self, t, send_counts=None, recv_counts=None):
+        return self._for(t).all_to_all(t, send_counts, recv_counts)
+
+    def synchronize_data(self) -> None:
+        """Wait for the data transport's device work (the reference's ``synchronize_nccl``)."""
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+
+    def close(self) -> None:
+        if hasattr(self.control, "close"):
+            self.control.close()
+
+
 @dataclass
 class RendezvousConfig:
     """Where and who: read from the launcher's environment (gloo_native/connect.rs:116
@@ -508,4 +564,8 @@ def init_group(backend: str = "tcp", **kw) -> Group:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             dist.init_process_group(backend, **kw)
         return TorchGroup()
-    raise BackendUnavailable("unknown backend %r (tcp, gloo, nccl)" % backend)
+    if backend == "hybrid":
+        tcp_kw = {k: kw.pop(k) for k in ("rank", "world_size", "master_addr", "master_port", "timeout") if k in kw}
+        control = init_group("tcp", **tcp_kw)                    # first: fails fast on a bad rendezvous
+        return HybridGroup(control, init_group(kw.pop("data_backend", "nccl"), **kw))
+    raise BackendUnavailable("unknown backend %r (tcp, gloo, nccl, hybrid)" % backend)

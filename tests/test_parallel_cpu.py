@@ -284,3 +284,62 @@ def test_ring_and_ulysses_attention_equal_full_attention(world, causal):
     assert torch.allclose(merged, R.attention(q, k, v, causal=False)[0], atol=1e-5)
     with pytest.raises(ValueError):
         run_simulated(2, lambda g: CP.ulysses_attention(q[:, :2, :3], k[:, :2, :1], v[:, :2, :1], g))
+
+
+def test_hybrid_group_routes_by_device_and_checks_ranks():
+    from ferrotorch_b200.parallel import backend as B
+
+    class Recorder(B.Group):
+        def __init__(self, rank, world):
+            self.rank, self.world_size, self.calls = rank, world, []
+
+        def send(self, t, dst):
+            self.calls.append(("send", dst))
+
+        def recv(self, t, src, timeout=None):
+            self.calls.append(("recv", src))
+
+        def barrier(self):
+            self.calls.append(("barrier",))
+
+        def all_reduce(self, t, op="sum"):
+            self.calls.append(("all_reduce", op))
+            return t
+
+    ctl, dat = Recorder(1, 4), Recorder(1, 4)
+    h = B.HybridGroup(ctl, dat)
+    assert (h.rank, h.world_size) == (1, 4) and h.tcp() is ctl and h.nccl() is dat
+    x = torch.ones(3)
+    h.send(x, 0), h.recv(x, 2), h.barrier(), h.all_reduce(x, "mean")
+    assert ctl.calls == [("send", 0), ("recv", 2), ("barrier",), ("all_reduce", "mean")] and dat.calls == []
+
+    class FakeCuda(torch.Tensor):
+        is_cuda = True
+
+    h.all_reduce(torch.ones(2).as_subclass(FakeCuda))
+    assert dat.calls == [("all_reduce", "sum")]
+    h.synchronize_data()
+    with pytest.raises(B.InvalidRank):
+        B.HybridGroup(Recorder(0, 2), Recorder(1, 2))
+    with pytest.raises(B.BackendUnavailable):
+        B.init_group("ucc")
+
+
+def test_hybrid_group_over_simulated_transports():
+    from ferrotorch_b200.parallel import backend as B
+
+    ctl, dat = B.SimulatedGroup.create_group(3), B.SimulatedGroup.create_group(3)
+    out = [None] * 3
+
+    def work(r):
+        h = B.HybridGroup(ctl[r], dat[r])
+        t = torch.full((4,), float(r + 1))
+        h.all_reduce(t, "sum")
+        h.barrier()
+        out[r] = t
+
+    import threading
+    ts = [threading.Thread(target=work, args=(r,)) for r in range(3)]
+    [t.start() for t in ts]
+    [t.join(30) for t in ts]
+    assert all(o is not None and torch.equal(o, torch.full((4,), 6.0)) for o in out)
