@@ -8,6 +8,11 @@ from .advanced import (AotGraphPair, AotModule, DimSpec, ExportedProgram, Export
                        Guard, InputSpec, SegmentedModule, ShapeSignature, SymbolicDim, SymbolicTracedModule,
                        compile_aot, compile_symbolic, decompose_forward_backward, export,
                        patch_reshape_for_symbolic_dims, trace_with_breaks)
+from .backends import (BinOpKind, Codegen, CompiledGraph, CpuCodegen, Expr, FusedChain, FusedOp, GpuCodegen,  # noqa: F401,E402
+                       InductorBackend, InductorCompileStatus, InductorTarget, InterpreterBackend, LoopIR, MemoryPlan,
+                       NativeBackend, ReductionKind, UnaryOpKind, compile_loop_ir_kernel, compile_with_config,
+                       estimate_numel_for_inputs, generate_reduction_source, interpret, interpret_multi,
+                       interpret_multi_with_captures, is_fusion_enabled, reduce_reference)
 
 
 def script(fn):

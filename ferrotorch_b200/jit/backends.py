@@ -1,0 +1,422 @@
+"""Execution back-ends for an optimised IR graph and the loop-level IR under the code generator
+(ferrotorch-jit/src/codegen.rs: ``Codegen`` / ``InterpreterBackend`` / ``NativeBackend`` /
+``InductorBackend``; codegen_ir.rs: ``Expr`` / ``LoopIR``; interpreter.rs; fusion.rs:
+``FusedOp`` / ``FusedChain`` / ``ReductionKind``; memory_plan.rs).
+
+* :func:`interpret` / :func:`interpret_multi` walk the graph node by node.
+* :class:`NativeBackend` resolves every node to a closure once, so a call is a flat list of
+  Python calls without any dispatch on op names.
+* :class:`InductorBackend` lowers every fused elementwise group to :class:`LoopIR` and from there
+  to source text: CUDA C for sm_100a (``InductorTarget.GpuCuda``; compiled by NVRTC the first
+  time the group runs on a device) or Python over torch scalars-as-tensors
+  (``InductorTarget.CpuTorch``; what the CPU tests execute).  Reductions over the last axis have
+  their own generator (:func:`generate_reduction_source`).
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+
+import torch
+
+from . import codegen
+from .ir import IrGraph, plan_memory
+from .module import CompileConfig, JitError, TracedModule, _call_node, _interpret, compile as _compile
+from . import module as _module
+
+
+# --------------------------------------------------------------------------- interpreter
+def interpret_multi(graph: IrGraph, inputs) -> list:
+    """All outputs of the graph, in ``graph.outputs`` order."""
+    env = _interpret(graph, list(inputs))
+    return [env[i] for i in graph.outputs]
+
+
+def interpret(graph: IrGraph, inputs):
+    """The single output of a single-output graph."""
+    outs = interpret_multi(graph, inputs)
+    if len(outs) != 1:
+        raise JitError("interpret: the graph has %d outputs; use interpret_multi" % len(outs))
+    return outs[0]
+
+
+def interpret_multi_with_captures(graph: IrGraph, inputs, capture_ids) -> tuple:
+    """Outputs plus the values of the listed intermediate nodes (used by the AOT backward split)."""
+    env = _interpret(graph, list(inputs))
+    return [env[i] for i in graph.outputs], [env[i] for i in capture_ids]
+
+
+def is_fusion_enabled() -> bool:
+    return _module._fusion_enabled
+
+
+def compile_with_config(fn, example_inputs, config: CompileConfig):
+    return _compile(fn, example_inputs, config)
+
+
+def estimate_numel_for_inputs(shapes) -> int:
+    """Element count of the broadcast of ``shapes`` (what one fused launch has to cover)."""
+    out = torch.broadcast_shapes(*[tuple(s) for s in shapes]) if shapes else ()
+    n = 1
+    for d in out:
+        n *= int(d)
+    return n
+
+
+@dataclass
+class MemoryPlan:
+    slot_of: dict
+    n_slots: int
+    peak_bytes: int
+
+    @classmethod
+    def of(cls, graph: IrGraph) -> "MemoryPlan":
+        return cls(**plan_memory(graph))
+
+    def reuse_count(self) -> int:
+        return len(self.slot_of) - self.n_slots
+
+
+# --------------------------------------------------------------------------- loop IR
+class UnaryOpKind(enum.Enum):
+    Neg = "neg"; Relu = "relu"; Sigmoid = "sigmoid"; Tanh = "tanh"; Gelu = "gelu"; Silu = "silu"  # noqa: E702
+    Sqrt = "sqrt"; Abs = "abs"; Exp = "exp"; Log = "log"  # noqa: E702
+
+
+class BinOpKind(enum.Enum):
+    Add = "add"; Sub = "sub"; Mul = "mul"; Div = "div"; Pow = "pow"  # noqa: E702
+
+
+@dataclass(frozen=True)
+class Expr:
+    """``kind``: "load" (input ``index``), "const" (``value``), "unary" (``op``, one arg), "binary" (``op``, two args)."""
+    kind: str
+    op: object = None
+    args: tuple = ()
+    index: int = -1
+    value: float = 0.0
+
+    @staticmethod
+    def load(index: int) -> "Expr":
+        return Expr("load", index=index)
+
+    @staticmethod
+    def const(value: float) -> "Expr":
+        return Expr("const", value=float(value))
+
+    @staticmethod
+    def unary(op: UnaryOpKind, a: "Expr") -> "Expr":
+        return Expr("unary", op, (a,))
+
+    @staticmethod
+    def binary(op: BinOpKind, a: "Expr", b: "Expr") -> "Expr":
+        return Expr("binary", op, (a, b))
+
+    def depth(self) -> int:
+        return 1 + max((a.depth() for a in self.args), default=0)
+
+    def loads(self) -> set:
+        return {self.index} if self.kind == "load" else set().union(*[a.loads() for a in self.args]) if self.args else set()
+
+
+@dataclass
+class LoopIR:
+    """One parallel loop ``for i in range(numel): out[i] = body`` over ``n_inputs`` operands."""
+    n_inputs: int
+    body: Expr
+
+    @classmethod
+    def from_program(cls, program, n_inputs: int) -> "LoopIR":
+        """Lower a fused program (the IR node's register machine) to one expression tree."""
+        regs: list[Expr] = []
+        for ins in program:
+            src = [Expr.load(i) if kind == "x" else regs[i] for kind, i in ins["src"]]
+            op, c = ins["op"], ins.get("c")
+            if op in ("add", "sub", "mul", "div"):
+                e = Expr.binary(BinOpKind(op), src[0], src[1])
+            elif op == "add_c":
+                e = Expr.binary(BinOpKind.Add, src[0], Expr.const(c))
+            elif op == "mul_c":
+                e = Expr.binary(BinOpKind.Mul, src[0], Expr.const(c))
+            elif op == "pow_c":
+                e = Expr.binary(BinOpKind.Pow, src[0], Expr.const(c))
+            elif op == "rsub_c":
+                e = Expr.binary(BinOpKind.Sub, Expr.const(c), src[0])
+            elif op == "rdiv_c":
+                e = Expr.binary(BinOpKind.Div, Expr.const(c), src[0])
+            else:
+                e = Expr.unary(UnaryOpKind(op), src[0])
+            regs.append(e)
+        return cls(n_inputs, regs[-1])
+
+
+_PY_UNARY = {"neg": "(-{a})", "relu": "torch.relu({a})", "sigmoid": "torch.sigmoid({a})", "tanh": "torch.tanh({a})",
+             "gelu": "torch.nn.functional.gelu({a})", "silu": "torch.nn.functional.silu({a})", "sqrt": "torch.sqrt({a})",
+             "abs": "torch.abs({a})", "exp": "torch.exp({a})", "log": "torch.log({a})"}
+_BIN_SYM = {"add": "+", "sub": "-", "mul": "*", "div": "/"}
+
+
+class CpuCodegen:
+    """LoopIR -> Python source over torch tensors (the loop is the tensor op)."""
+
+    def expr(self, e: Expr) -> str:
+        if e.kind == "load":
+            return "x%d" % e.index
+        if e.kind == "const":
+            return repr(e.value)
+        if e.kind == "unary":
+            return _PY_UNARY[e.op.value].format(a=self.expr(e.args[0]))
+        a, b = self.expr(e.args[0]), self.expr(e.args[1])
+        return "(%s ** %s)" % (a, b) if e.op is BinOpKind.Pow else "(%s %s %s)" % (a, _BIN_SYM[e.op.value], b)
+
+    def generate(self, ir: LoopIR, name: str = "fused") -> str:
+        args = ", ".join("x%d" % i for i in range(ir.n_inputs))
+        return "def %s(%s):\n    return %s\n" % (name, args, self.expr(ir.body))
+
+    def compile(self, ir: LoopIR, name: str = "fused"):
+        scope = {"torch": torch}
+        exec(self.generate(ir, name), scope)  # noqa: S102 - source generated here from a closed op set
+        return scope[name]
+
+
+class GpuCodegen:
+    """LoopIR -> CUDA C for sm_100a: fp32 math, one element per thread and grid-stride step.  The
+    vectorised, broadcast-aware kernels that actually run come from ``codegen.generate_source``;
+    this generator is the plain form of the same loop, kept for inspection and as a second oracle."""
+
+    _UNARY = codegen._UNARY_C
+
+    def expr(self, e: Expr) -> str:
+        if e.kind == "load":
+            return "v%d" % e.index
+        if e.kind == "const":
+            return codegen._cfloat(e.value)
+        if e.kind == "unary":
+            return "(" + self._UNARY[e.op.value].format(a=self.expr(e.args[0])) + ")"
+        a, b = self.expr(e.args[0]), self.expr(e.args[1])
+        return "powf(%s, %s)" % (a, b) if e.op is BinOpKind.Pow else "(%s %s %s)" % (a, _BIN_SYM[e.op.value], b)
+
+    def generate(self, ir: LoopIR, name: str = "fused_loop") -> str:
+        params = ", ".join("const float* __restrict__ x%d" % i for i in range(ir.n_inputs))
+        loads = "".join("    const float v%d = x%d[i];\n" % (i, i) for i in sorted(ir.body.loads()))
+        return ('extern "C" __global__ void %s(%s%sfloat* __restrict__ out, long long n) {\n'
+                "  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {\n"
+                "%s    out[i] = %s;\n  }\n}\n") % (name, params, ", " if params else "", loads, self.expr(ir.body))
+
+
+# --------------------------------------------------------------------------- fused chains, reductions
+class FusedOp(enum.Enum):
+    """The unary / scalar ops a fused chain may hold (fusion.rs:112)."""
+    Neg = "neg"; Relu = "relu"; Sigmoid = "sigmoid"; Tanh = "tanh"; Gelu = "gelu"; Silu = "silu"  # noqa: E702
+    Sqrt = "sqrt"; Abs = "abs"; Exp = "exp"; Log = "log"  # noqa: E702
+    AddScalar = "add_c"; MulScalar = "mul_c"; PowScalar = "pow_c"  # noqa: E702
+
+
+@dataclass
+class FusedChain:
+    """A straight chain of unary / scalar ops applied to one tensor in one kernel."""
+    ops: list = field(default_factory=list)     # FusedOp or (FusedOp, scalar)
+
+    def push(self, op: FusedOp, scalar: float | None = None) -> "FusedChain":
+        needs = op.value.endswith("_c")
+        if needs != (scalar is not None):
+            raise JitError("FusedChain: %s %s a scalar" % (op.name, "needs" if needs else "does not take"))
+        self.ops.append((op, scalar) if needs else op)
+        return self
+
+    def __len__(self) -> int:
+        return len(self.ops)
+
+    def _plain(self) -> list:
+        return [(o[0].value, o[1]) if isinstance(o, tuple) else o.value for o in self.ops]
+
+    def program(self) -> list:
+        return [{"op": (o if isinstance(o, str) else o[0]), "src": [("x", 0)] if k == 0 else [("r", k - 1)],
+                 "c": None if isinstance(o, str) else o[1]} for k, o in enumerate(self._plain())]
+
+    def loop_ir(self) -> LoopIR:
+        return LoopIR.from_program(self.program(), 1)
+
+    def execute(self, x: torch.Tensor) -> torch.Tensor:
+        return _module.apply_fused(self._plain(), x)
+
+    def generate_source(self, dtype: torch.dtype = torch.float32, vec: int = 4) -> str:
+        return codegen.generate_source(self.program(), [dtype], ["full"], dtype, vec)
+
+
+class ReductionKind(enum.Enum):
+    Sum = "sum"; Mean = "mean"; Max = "max"; Min = "min"; Prod = "prod"  # noqa: E702
+
+
+_RED = {ReductionKind.Sum: ("0.f", "a + b"), ReductionKind.Mean: ("0.f", "a + b"), ReductionKind.Prod: ("1.f", "a * b"),
+        ReductionKind.Max: ("__int_as_float(0xff800000)", "fmaxf(a, b)"),
+        ReductionKind.Min: ("__int_as_float(0x7f800000)", "fminf(a, b)")}
+
+
+def generate_reduction_source(kind: ReductionKind, pre: FusedChain | None = None, name: str = "fused_reduce") -> str:
+    """CUDA C for ``out[row] = reduce(pre(x[row, :]))`` over the last axis: one warp per row,
+    lanes stride the row, a shuffle tree combines them (the reference's
+    ``generate_reduction_ptx`` emits the block-per-row PTX equivalent, fusion.rs)."""
+    init, comb = _RED[kind]
+    body = GpuCodegen().expr(pre.loop_ir().body) if pre is not None and len(pre) else "v0"
+    return ('extern "C" __global__ void %s(const float* __restrict__ x, float* __restrict__ out, long long rows, int cols) {\n'
+            "  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;\n"
+            "  const int lane = threadIdx.x & 31;\n"
+            "  if (row >= rows) return;\n"
+            "  float acc = %s;\n"
+            "  for (int c = lane; c < cols; c += 32) {\n"
+            "    const float v0 = x[row * cols + c];\n"
+            "    const float a = acc, b = %s;\n"
+            "    acc = %s;\n  }\n"
+            "  for (int s = 16; s > 0; s >>= 1) {\n"
+            "    const float a = acc, b = __shfl_xor_sync(0xffffffffu, acc, s);\n"
+            "    acc = %s;\n  }\n"
+            "  if (lane == 0) out[row] = acc%s;\n}\n") % (name, init, body, comb, comb,
+                                                       " / (float)cols" if kind is ReductionKind.Mean else "")
+
+
+def reduce_reference(kind: ReductionKind, x: torch.Tensor, pre: FusedChain | None = None) -> torch.Tensor:
+    """What the generated reduction computes, with torch ops."""
+    if pre is not None and len(pre):
+        x = codegen.run_program_torch(pre.program(), [x])
+    return {ReductionKind.Sum: lambda t: t.sum(-1), ReductionKind.Mean: lambda t: t.mean(-1),
+            ReductionKind.Prod: lambda t: t.prod(-1), ReductionKind.Max: lambda t: t.amax(-1),
+            ReductionKind.Min: lambda t: t.amin(-1)}[kind](x)
+
+
+# --------------------------------------------------------------------------- graph back-ends
+class CompiledGraph:
+    """A graph bound to a way of running it: ``execute(inputs) -> list of outputs``."""
+
+    def __init__(self, graph: IrGraph, steps, backend: str, sources: dict | None = None):
+        self.graph, self._steps, self.backend, self.sources = graph, steps, backend, sources or {}
+
+    def execute(self, inputs) -> list:
+        env: dict = {}
+        for node_id, fn in self._steps:
+            env[node_id] = fn(env, inputs)
+        return [env[i] for i in self.graph.outputs]
+
+    def __call__(self, inputs) -> list:
+        return self.execute(inputs)
+
+
+class Codegen:
+    """Back-end protocol: ``compile(graph) -> CompiledGraph``."""
+    name = "abstract"
+
+    def compile(self, graph: IrGraph) -> CompiledGraph:
+        raise NotImplementedError
+
+
+class InterpreterBackend(Codegen):
+    name = "interpreter"
+
+    def compile(self, graph: IrGraph) -> CompiledGraph:
+        class _Whole(CompiledGraph):
+            def execute(self, inputs):
+                return interpret_multi(self.graph, inputs)
+
+        return _Whole(graph, [], self.name)
+
+
+def _node_closure(graph: IrGraph, n, fused_runner):
+    ins = tuple(n.inputs)
+    if n.op == "input":
+        idx = n.attrs["index"]
+        return lambda env, inputs: inputs[idx]
+    if n.op == "const":
+        val = n.attrs["value"]
+        return lambda env, inputs: val
+    if n.op == "call":
+        return lambda env, inputs: _call_node(n, env)
+    if n.op == "fused_elementwise":
+        return fused_runner(n)
+    if n.op in ("fused_linear_act", "fused_attention"):
+        return lambda env, inputs: _interpret_one(graph, n, env)
+    if n.op in _module.ELEMENTWISE:
+        op, c = n.op, n.attrs.get("c")
+        return lambda env, inputs: codegen.eval_elementwise(op, [env[j] for j in ins], c)
+    raise JitError("unknown IR op %s" % n.op)
+
+
+def _interpret_one(graph: IrGraph, n, env):
+    """Evaluate one node with the interpreter's semantics given its inputs in ``env``."""
+    seeded = IrGraph()                                          # the inputs enter as constants
+    for j in n.inputs:
+        seeded.nodes[j] = type(n)(j, "const", [], {"value": env[j]})
+        seeded.order.append(j)
+    seeded.nodes[n.id] = n
+    seeded.order.append(n.id)
+    return _interpret(seeded, [])[n.id]
+
+
+class NativeBackend(Codegen):
+    """Every node resolved to a closure ahead of time; fused groups run the generated kernels on
+    CUDA tensors and the torch program elsewhere (``codegen.run_fused`` decides)."""
+    name = "native"
+
+    def compile(self, graph: IrGraph) -> CompiledGraph:
+        def fused(n):
+            ins, prog, shape = tuple(n.inputs), n.attrs["program"], n.shape
+
+            def run(env, inputs):
+                xs = [env[j] for j in ins]
+                return codegen.run_fused(prog, xs, tuple(shape) if shape is not None
+                                         else tuple(torch.broadcast_shapes(*[t.shape for t in xs])))
+            return run
+
+        return CompiledGraph(graph, [(i, _node_closure(graph, graph.nodes[i], fused)) for i in graph.order], self.name)
+
+
+class InductorTarget(enum.Enum):
+    CpuTorch = "cpu"
+    GpuCuda = "cuda"
+
+
+class InductorCompileStatus(enum.Enum):
+    Compiled = "compiled"            # every fused group went through LoopIR -> source
+    Partial = "partial"              # some groups were left to the native runner
+    Interpreted = "interpreted"      # nothing to generate
+
+
+class InductorBackend(Codegen):
+    """Fused groups -> :class:`LoopIR` -> source for the target; the rest of the graph as in
+    :class:`NativeBackend`.  ``sources`` of the result maps node id -> generated text."""
+    name = "inductor"
+
+    def __init__(self, target: InductorTarget = InductorTarget.CpuTorch):
+        self.target, self.status = target, InductorCompileStatus.Interpreted
+
+    def compile(self, graph: IrGraph) -> CompiledGraph:
+        sources, done, total = {}, 0, 0
+
+        def fused(n):
+            nonlocal done, total
+            total += 1
+            ins, prog, shape = tuple(n.inputs), n.attrs["program"], n.shape
+            ir = LoopIR.from_program(prog, len(ins))
+            if self.target is InductorTarget.CpuTorch:
+                sources[n.id] = CpuCodegen().generate(ir, "fused_%d" % n.id)
+                fn = CpuCodegen().compile(ir, "fused_%d" % n.id)
+                done += 1
+                return lambda env, inputs: fn(*[env[j] for j in ins])
+            sources[n.id] = GpuCodegen().generate(ir, "fused_%d" % n.id)
+            done += 1
+
+            def run(env, inputs):                                # the vectorised kernel of the same program
+                xs = [env[j] for j in ins]
+                return codegen.run_fused(prog, xs, tuple(shape) if shape is not None
+                                         else tuple(torch.broadcast_shapes(*[t.shape for t in xs])))
+            return run
+
+        steps = [(i, _node_closure(graph, graph.nodes[i], fused)) for i in graph.order]
+        self.status = (InductorCompileStatus.Interpreted if total == 0 else
+                       InductorCompileStatus.Compiled if done == total else InductorCompileStatus.Partial)
+        return CompiledGraph(graph, steps, self.name, sources)
+
+
+def compile_loop_ir_kernel(ir: LoopIR, name: str = "fused_loop"):
+    """LoopIR -> (source, cubin bytes) for sm_100a through NVRTC (codegen_jit.rs ``compile_loop_ir_kernel``)."""
+    src = GpuCodegen().generate(ir, name)
+    return src, codegen.compile_cubin(src, name)
