@@ -1,0 +1,182 @@
+"""Names of the reference's ``ferrotorch-nn`` surface that torch spells differently or keeps in
+sub-modules (ferrotorch-nn/src/lib.rs re-exports): functional forms at package level, option
+enums, score modifiers for ``flex_attention`` (flex_attention.rs:723-784), head reshapes
+(attention.rs:606-660), packed sequences (rnn_utils.rs)."""
+from __future__ import annotations
+
+import enum
+from typing import Callable, Dict
+
+import torch
+from torch import nn
+from torch.nn.functional import (adaptive_avg_pool1d, adaptive_avg_pool2d, adaptive_avg_pool3d,  # noqa: F401
+                                 adaptive_max_pool1d, adaptive_max_pool2d, adaptive_max_pool3d, affine_grid,
+                                 avg_pool1d, avg_pool2d, avg_pool3d, fold, grid_sample, interpolate, lp_pool1d,
+                                 lp_pool2d, max_pool1d, max_pool2d, max_pool3d, max_unpool2d, pixel_shuffle,
+                                 pixel_unshuffle, unfold)
+from torch.nn.utils.rnn import PackedSequence, pack_padded_sequence, pad_packed_sequence, pad_sequence  # noqa: F401
+
+from .fake_quant import convert as _convert_qat, prepare_qat as _prepare_qat
+from .paged import PagePool  # noqa: F401
+
+HardSigmoid, HardSwish = nn.Hardsigmoid, nn.Hardswish
+StateDict = Dict[str, torch.Tensor]
+ForwardHook = Callable[[nn.Module, tuple, object], object]
+ForwardPreHook = Callable[[nn.Module, tuple], object]
+BackwardHook = Callable[[nn.Module, tuple, tuple], object]
+
+
+class _StrEnum(str, enum.Enum):
+    def __str__(self) -> str:          # usable wherever torch wants the option string
+        return self.value
+
+
+class Reduction(_StrEnum):
+    Mean = "mean"; Sum = "sum"; NoReduction = "none"  # noqa: E702
+
+
+class PaddingMode(_StrEnum):
+    Zeros = "zeros"; Reflect = "reflect"; Replicate = "replicate"; Circular = "circular"  # noqa: E702
+
+
+class StringPadding(_StrEnum):
+    Valid = "valid"; Same = "same"  # noqa: E702
+
+
+class InterpolateMode(_StrEnum):
+    Nearest = "nearest"; Bilinear = "bilinear"; Bicubic = "bicubic"; Linear = "linear"; Trilinear = "trilinear"; Area = "area"  # noqa: E702
+
+
+class GridSampleMode(_StrEnum):
+    Bilinear = "bilinear"; Nearest = "nearest"; Bicubic = "bicubic"  # noqa: E702
+
+
+class GridSamplePaddingMode(_StrEnum):
+    Zeros = "zeros"; Border = "border"; Reflection = "reflection"  # noqa: E702
+
+
+class GeluApproximate(_StrEnum):
+    NoApproximation = "none"; Tanh = "tanh"  # noqa: E702
+
+
+class EmbeddingBagMode(_StrEnum):
+    Sum = "sum"; Mean = "mean"; Max = "max"  # noqa: E702
+
+
+class RNNNonlinearity(_StrEnum):
+    Tanh = "tanh"; ReLU = "relu"  # noqa: E702
+
+
+class FanMode(_StrEnum):
+    FanIn = "fan_in"; FanOut = "fan_out"  # noqa: E702
+
+
+class NonLinearity(_StrEnum):
+    Linear = "linear"; ReLU = "relu"; LeakyReLU = "leaky_relu"; Tanh = "tanh"; Sigmoid = "sigmoid"; SELU = "selu"  # noqa: E702
+
+    def gain(self, param: float | None = None) -> float:
+        return nn.init.calculate_gain(self.value, param)
+
+
+class ObserverType(_StrEnum):
+    MinMax = "minmax"; MovingAverage = "moving_average"  # noqa: E702
+
+
+class RoPEConvention(_StrEnum):
+    HalfRotation = "half"; Interleaved = "interleaved"  # noqa: E702
+
+
+class RoPEScaling:
+    """Constructors for the ``scaling`` dictionary of ``RotaryPositionEmbedding``
+    (transformer.rs:227-278: None / Linear / NTK-aware / YaRN)."""
+
+    NoScaling = None
+
+    @staticmethod
+    def Linear(factor: float) -> dict:
+        return {"type": "linear", "factor": float(factor)}
+
+    @staticmethod
+    def NtkAware(factor: float) -> dict:
+        return {"type": "ntk", "factor": float(factor)}
+
+    @staticmethod
+    def Yarn(factor: float, original_max_pos_embeddings: int, beta_fast: float = 32.0, beta_slow: float = 1.0) -> dict:
+        return {"type": "yarn", "factor": float(factor), "original_max": int(original_max_pos_embeddings),
+                "beta_fast": float(beta_fast), "beta_slow": float(beta_slow)}
+
+
+# --------------------------------------------------------------------------- flex_attention score modifiers
+# called with broadcastable index tensors, so each works on the whole score matrix at once
+def causal_score_mod():
+    return lambda score, b, h, q_idx, kv_idx: torch.where(q_idx >= kv_idx, score, torch.full_like(score, -1e30))
+
+
+def alibi_score_mod(slope):
+    """``score + slope * (q - k)``; ``slope`` a number or one value per head ``[H]``."""
+    def mod(score, b, h, q_idx, kv_idx):
+        s = slope[h] if isinstance(slope, torch.Tensor) and slope.dim() else slope
+        return score + s * (q_idx - kv_idx).to(score.dtype)
+    return mod
+
+
+def relative_position_bias_score_mod(bias_table: torch.Tensor, max_dist: int):
+    """``score + table[clamp(q - k, -max_dist, max_dist) + max_dist]``."""
+    def mod(score, b, h, q_idx, kv_idx):
+        idx = ((q_idx - kv_idx).clamp(-max_dist, max_dist) + max_dist).clamp(max=bias_table.numel() - 1)
+        return score + bias_table.to(score.device, score.dtype)[idx.long()]
+    return mod
+
+
+# --------------------------------------------------------------------------- head reshapes
+def reshape_to_heads(t: torch.Tensor, num_heads: int, seq_len: int, head_dim: int) -> torch.Tensor:
+    """``[S, H*D] -> [H, S, D]``."""
+    return t.reshape(seq_len, num_heads, head_dim).transpose(0, 1).contiguous()
+
+
+def transpose_heads_to_2d(t: torch.Tensor, num_heads: int, seq_len: int, head_dim: int) -> torch.Tensor:
+    """``[H, S, D] -> [S, H*D]``."""
+    return t.reshape(num_heads, seq_len, head_dim).transpose(0, 1).reshape(seq_len, num_heads * head_dim).contiguous()
+
+
+# --------------------------------------------------------------------------- QAT wrappers
+class QatConfig:
+    def __init__(self, weight_bits: int = 8, activation_bits: int = 8, observer: ObserverType = ObserverType.MinMax,
+                 skip: tuple = ()):
+        self.weight_bits, self.activation_bits, self.observer, self.skip = weight_bits, activation_bits, observer, tuple(skip)
+
+
+class QuantizedModel:
+    """Result of :meth:`QatModel.convert`: ``{layer name: (int8 weight, scale, zero point)}``."""
+
+    def __init__(self, layers: dict):
+        self.layers = layers
+
+    def __len__(self) -> int:
+        return len(self.layers)
+
+    def dequantized_state_dict(self) -> dict:
+        out = {}
+        for name, (q, scale, zp) in self.layers.items():
+            s = scale.reshape(-1, *[1] * (q.dim() - 1)) if scale.numel() > 1 else scale
+            z = zp.reshape(-1, *[1] * (q.dim() - 1)) if zp.numel() > 1 else zp
+            out[name + ".weight"] = (q.float() - z.float()) * s.float()
+        return out
+
+
+class QatModel(nn.Module):
+    """A model prepared for quantisation-aware training (qat.rs:182 ``prepare_qat``)."""
+
+    def __init__(self, model: nn.Module, config: QatConfig | None = None):
+        super().__init__()
+        self.config = config or QatConfig()
+        self.model = _prepare_qat(model, self.config.weight_bits, self.config.activation_bits, self.config.skip)
+
+    def forward(self, *a, **kw):
+        return self.model(*a, **kw)
+
+    def convert(self) -> QuantizedModel:
+        return QuantizedModel(_convert_qat(self.model))
+
+
+KVPage = tuple      # (layer, page index): pages are slices of the pool's device tensors, addressed by index

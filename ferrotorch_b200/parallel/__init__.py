@@ -15,6 +15,7 @@ from .p2p import (PipelineSchedule, Placement, async_reduce_scatter, gpu_allredu
                   recv_into_with_timeout, recv_with_timeout, send, sendrecv)
 
 async_all_gather = all_gather_async
+from .functional import *  # noqa: F401,F403,E402
 
 
 def __getattr__(name):

@@ -228,6 +228,7 @@ class TcpGroup(Group):
         addr = master_addr or env.get("MASTER_ADDR", "127.0.0.1")
         port = int(master_port or env.get("MASTER_PORT", "29500"))
         self._lib = _host_lib()
+        self.timeout = float(timeout)
         self._h = self._lib.ftc_create(addr.encode(), port, self.rank, self.world_size, int(timeout * 1000))
         if not self._h:
             _raise(self._lib.ftc_last_error_code() or -6, "rendezvous")
@@ -248,6 +249,7 @@ class TcpGroup(Group):
             pass
 
     def set_timeout(self, seconds: float) -> None:
+        self.timeout = float(seconds)
         self._lib.ftc_set_timeout(self._h, int(seconds * 1000))
 
     def send(self, t: torch.Tensor, dst: int) -> None:

@@ -439,3 +439,32 @@ def test_tiled_attention_forward_and_backward(causal, nq, nk, block):
     with pytest.raises(ValueError):
         fnn.flash_attention(q, k, v, causal, 0)
     assert fnn.flex_attention is not None
+
+
+def test_nn_reference_names_and_score_mods():
+    import ferrotorch_b200.nn as fnn
+    from ferrotorch_b200.core import flex_attention
+
+    q, k, v = torch.randn(2, 2, 6, 8), torch.randn(2, 2, 6, 8), torch.randn(2, 2, 6, 8)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    torch.testing.assert_close(flex_attention(q, k, v, fnn.causal_score_mod()), ref, rtol=1e-5, atol=1e-5)
+    qi, ki = torch.arange(6).view(6, 1), torch.arange(6).view(1, 6)
+    slopes = torch.tensor([0.5, 0.25])
+    bias = slopes.view(1, 2, 1, 1) * (qi - ki).float()
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=bias)
+    torch.testing.assert_close(flex_attention(q, k, v, fnn.alibi_score_mod(slopes)), ref, rtol=1e-5, atol=1e-5)
+    table = torch.randn(7)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=table[(qi - ki).clamp(-3, 3) + 3])
+    torch.testing.assert_close(flex_attention(q, k, v, fnn.relative_position_bias_score_mod(table, 3)), ref, rtol=1e-5, atol=1e-5)
+    x = torch.randn(5, 16)
+    heads = fnn.reshape_to_heads(x, 2, 5, 8)
+    assert heads.shape == (2, 5, 8) and torch.equal(heads[1, 3], x[3, 8:]) and torch.equal(fnn.transpose_heads_to_2d(heads, 2, 5, 8), x)
+    assert fnn.HardSwish is torch.nn.Hardswish and str(fnn.Reduction.Sum) == "sum" and fnn.FanMode.FanOut == "fan_out"
+    assert torch.nn.functional.mse_loss(x, x + 1, reduction=fnn.Reduction.Sum).item() == pytest.approx(80.0)
+    fnn.RotaryPositionEmbedding(8, 32, scaling=fnn.RoPEScaling.Yarn(4.0, 16))
+    fnn.RotaryPositionEmbedding(8, 32, scaling=fnn.RoPEScaling.NtkAware(2.0))
+    packed = fnn.pack_padded_sequence(fnn.pad_sequence([torch.ones(3, 2), torch.ones(2, 2)], batch_first=True), [3, 2], batch_first=True)
+    assert isinstance(packed, fnn.PackedSequence) and fnn.max_pool2d(torch.randn(1, 1, 4, 4), 2).shape == (1, 1, 2, 2)
+    qm = fnn.QatModel(torch.nn.Sequential(torch.nn.Linear(8, 4)), fnn.QatConfig(weight_bits=8))
+    qm(torch.randn(2, 8))
+    assert list(qm.convert().dequantized_state_dict()) == ["0.weight"]

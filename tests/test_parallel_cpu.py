@@ -343,3 +343,50 @@ def test_hybrid_group_over_simulated_transports():
     [t.start() for t in ts]
     [t.join(30) for t in ts]
     assert all(o is not None and torch.equal(o, torch.full((4,), 6.0)) for o in out)
+
+
+def test_function_style_collectives_and_reference_names(tmp_path):
+    import ferrotorch_b200.parallel as P
+
+    def work(g):
+        r, w = g.rank, g.world_size
+        x = torch.full((4,), float(r + 1))
+        s = P.allreduce(x, g, P.ReduceOp.Sum)
+        m = P.allreduce_with_timeout(x, g, P.ReduceOp.Mean, timeout=20.0)
+        assert torch.equal(x, torch.full((4,), float(r + 1)))            # input untouched
+        gathered = P.all_gather_with_timeout(x[:1], g, timeout=20.0)
+        rs = P.reduce_scatter(torch.arange(2.0 * w), g)
+        b = P.broadcast(x, g, root=1)
+        a2a = P.all_to_all(torch.arange(float(w)) + 10 * r, g)
+        send = [1] * w
+        un = P.all_to_all_single_uneven(torch.arange(float(w)) + 10 * r, send, send, g)
+        P.barrier(g)
+        assert g.timeout == 30.0                                          # restored after the bounded calls
+        with pytest.raises(P.SizeMismatch):
+            P.reduce_scatter(torch.ones(w + 1), g)
+        return s, m, gathered, rs, b, a2a, un
+
+    outs = P.run_simulated(3, work)
+    for r, (s, m, gathered, rs, b, a2a, un) in enumerate(outs):
+        assert torch.equal(s, torch.full((4,), 6.0)) and torch.equal(m, torch.full((4,), 2.0))
+        assert torch.equal(gathered, torch.tensor([1.0, 2.0, 3.0])) and torch.equal(rs, torch.tensor([3.0 * 2 * r, 3.0 * (2 * r + 1)]))
+        assert torch.equal(b, torch.full((4,), 2.0)) and torch.equal(a2a, torch.tensor([r, 10.0 + r, 20.0 + r])) and torch.equal(un, a2a)
+    assert P.Backend is P.Group and P.TcpBackend is P.TcpGroup and P.HybridBackend is P.HybridGroup and P.DEFAULT_COLLECTIVE_TIMEOUT == 60.0
+    for ctor in (P.MpiBackend, P.UccBackend, P.NcclBackend, P.GlooBackend):
+        with pytest.raises(P.BackendUnavailable):
+            ctor()
+    with pytest.raises(P.UnsupportedOp):
+        P.nccl_allreduce(torch.ones(2), None)
+    # checkpoint types: flat shards written by 2 ranks, read back by 1 and by 3
+    full = {"w": torch.arange(12.0)}
+    meta = P.flat_shard_metadata({"w": full["w"][:6]}, 2)
+    assert meta.tensor_specs["w"].full_shape == [12] and meta.to_json()["num_ranks"] == 2
+    from ferrotorch_b200.parallel.dist_checkpoint import save_reference_distributed
+    for r in range(2):
+        save_reference_distributed(str(tmp_path), {"w": full["w"][6 * r:6 * r + 6]}, {"w": 0}, {"w": [6, 6]}, r, 2)
+    ck = P.DistributedCheckpoint.open(str(tmp_path))
+    assert ck.shard_metadata.num_ranks == 2 and torch.equal(ck.load(0, 1)["w"], full["w"])
+    parts = [P.reshard(str(tmp_path), 2, 3, r)["w"] for r in range(3)]
+    assert torch.equal(torch.cat(parts), full["w"]) and [p.numel() for p in parts] == [4, 4, 4]
+    with pytest.raises(P.DistCheckpointError):
+        P.DistributedCheckpoint.open(str(tmp_path / "nope"))
