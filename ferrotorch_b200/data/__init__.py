@@ -97,3 +97,8 @@ from .token_loader import TokenFileLoader, write_token_file  # noqa: F401,E402
 
 from .interop import (dataframe_to_tensor, record_batch_to_tensor, tensor_from_arrow_array,  # noqa: F401,E402
                       tensor_to_arrow_array, tensor_to_arrow_arrayref)
+
+
+from .compat import (BatchIter, ChainDataset, CollatedIter, Compose, ConcatDataset, MappedDataset, MultiWorkerIter,  # noqa: F401,E402
+                     Normalize, PrefetchIter, RandomCrop, RandomHorizontalFlip, ToDevice, ToTensor, Transform, VecDataset,
+                     WorkerInfo, WorkerMode, default_collate, default_collate_pair, manual_seed)

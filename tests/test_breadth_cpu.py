@@ -468,3 +468,60 @@ def test_nn_reference_names_and_score_mods():
     qm = fnn.QatModel(torch.nn.Sequential(torch.nn.Linear(8, 4)), fnn.QatConfig(weight_bits=8))
     qm(torch.randn(2, 8))
     assert list(qm.convert().dequantized_state_dict()) == ["0.weight"]
+
+
+def test_optim_configs_and_data_reference_names():
+    import numpy as np
+
+    import ferrotorch_b200.data as D
+    import ferrotorch_b200.optim as O
+
+    w = [torch.nn.Parameter(torch.randn(4, 4))]
+    opt = O.AdamWConfig(lr=3e-4).build(w)
+    assert isinstance(opt, O.AdamW) and opt.defaults["lr"] == 3e-4 and opt.defaults["weight_decay"] == 0.01
+    assert O.AdamWConfig().betas == (0.9, 0.999) and O.AdamWConfig().eps == 1e-8
+    sgd = O.SgdConfig()
+    assert (sgd.momentum, sgd.dampening, sgd.weight_decay, sgd.nesterov, sgd.maximize) == (0, 0, 0, False, False)
+    assert O.RmspropConfig().alpha == 0.99 and O.LbfgsConfig().history_size == 100 and O.Sgd is O.SGD
+    assert O.LbfgsConfig(line_search_fn=O.LineSearchFn.StrongWolfe).build(w).defaults["line_search_fn"] == "strong_wolfe"
+    for cfg in (O.AdamConfig, O.AdamaxConfig, O.NAdamConfig, O.RAdamConfig, O.AdagradConfig, O.AdadeltaConfig, O.AdafactorConfig,
+                O.RpropConfig, O.AsgdConfig, O.MuonConfig, O.KfacConfig):
+        o = cfg().build(w)
+        w[0].grad = torch.randn(4, 4)
+        o.step()
+    gs = O.GradScalerConfig()
+    assert (gs.init_scale, gs.growth_factor, gs.backoff_factor, gs.growth_interval, gs.enabled) == (65536.0, 2.0, 0.5, 2000, True)
+    sch = O.OneCycleLR(opt, 0.1, total_steps=10, anneal_strategy=O.AnnealStrategy.Linear)
+    assert isinstance(sch, O.LrScheduler) and O.SequentialLr is O.SequentialLR and O.CyclicMode.ExpRange == "exp_range"
+
+    D.manual_seed(3)
+    a = torch.rand(2)
+    D.manual_seed(3)
+    assert torch.equal(a, torch.rand(2))
+    ds = D.MappedDataset(D.VecDataset([1, 2, 3, 4, 5]), lambda v: torch.tensor(float(v)) * 2)
+    assert len(ds) == 5 and ds[4].item() == 10.0
+    with pytest.raises(IndexError):
+        D.VecDataset([1])[3]
+    it = D.CollatedIter(D.BatchIter(ds, [0, 1, 2, 3, 4], 2))
+    batches = list(D.PrefetchIter(it, 2))
+    assert [b.tolist() for b in batches] == [[2.0, 4.0], [6.0, 8.0], [10.0]] and len(D.BatchIter(ds, range(5), 2, drop_last=True)) == 2
+
+    def boom():
+        yield 1
+        raise RuntimeError("producer failed")
+
+    with pytest.raises(RuntimeError, match="producer failed"):
+        list(D.PrefetchIter(boom()))
+    img = np.arange(2 * 3 * 3, dtype=np.uint8).reshape(2, 3, 3)          # H, W, C
+    t = D.Compose([D.ToTensor(), D.Normalize([0.5, 0.5, 0.5], [0.5, 0.5, 0.5])])(img)
+    assert t.shape == (3, 2, 3) and t[0, 0, 0].item() == pytest.approx(-1.0)
+    g = torch.Generator().manual_seed(0)
+    x = torch.arange(16.0).view(1, 4, 4)
+    assert D.RandomCrop(2, generator=g)(x).shape == (1, 2, 2) and D.RandomCrop(4, padding=1, generator=g)(x).shape == (1, 4, 4)
+    assert torch.equal(D.RandomHorizontalFlip(1.0)(x), x.flip(-1)) and torch.equal(D.RandomHorizontalFlip(0.0)(x), x)
+    moved = D.ToDevice("cpu")({"a": [x, 3], "b": (x,)})
+    assert moved["a"][1] == 3 and moved["b"][0] is x
+    xs, ys = D.default_collate_pair([(torch.ones(2), 0), (torch.zeros(2), 1)])
+    assert xs.shape == (2, 2) and ys.tolist() == [0, 1]
+    assert list(D.WorkerInfo(1, 3).shard(10)) == [4, 5, 6] and D.WorkerInfo.current() is None and D.WorkerMode.CrossBatch
+    assert len(list(D.MultiWorkerIter(ds, 2, 0))) == 3 and len(D.ConcatDataset([ds, ds])) == 10
