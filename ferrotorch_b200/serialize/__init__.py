@@ -1,5 +1,8 @@
 """Checkpoint formats: SafeTensors, PyTorch .pt, native state dicts, training checkpoints, GGUF."""
-from .gguf import GgufFile, gguf_key_to_hf, load_gguf_state_dict, quantize_q4_0, write_gguf  # noqa: F401
+from .gguf import (GgmlType, GgufFile, GgufMetadata, GgufTensorInfo, GgufValue, dequantize_gguf_tensor, gguf_key_to_hf,  # noqa: F401
+                   gguf_to_hf_state_dict, load_gguf, load_gguf_mmap, load_gguf_state_dict, load_gguf_state_dict_mmap,
+                   parse_gguf_bytes, quantize_q4_0, tensor_infos, write_gguf)
+from .state import PickleValue, TrainingCheckpoint  # noqa: F401
 from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_checkpoint,  # noqa: F401
                     load_pytorch_state_dict, load_safetensors, load_safetensors_sharded, load_state_dict,
                     ShardProgress, load_safetensors_auto, load_safetensors_mmap, load_safetensors_sharded_filtered,

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import ctypes
 import json
+import os
 import re
 import struct
 
@@ -238,3 +239,87 @@ def write_gguf(path: str, tensors: dict[str, tuple[int, tuple, bytes]], metadata
     pad = (-len(head)) % alignment
     with open(path, "wb") as f:
         f.write(head + b"\0" * pad + b"".join(blobs))
+
+
+# --------------------------------------------------------------------------- the reference's type and function names
+import enum as _enum  # noqa: E402
+from dataclasses import dataclass as _dataclass  # noqa: E402
+
+
+class GgmlType(_enum.IntEnum):
+    """Tensor encodings this reader understands (ferrotorch-serialize/src/gguf.rs:56)."""
+    F32 = GGML_F32
+    F16 = GGML_F16
+    Q4_0 = GGML_Q4_0
+    Q4_1 = GGML_Q4_1
+    Q5_0 = GGML_Q5_0
+    Q5_1 = GGML_Q5_1
+    Q8_0 = GGML_Q8_0
+    Q8_1 = GGML_Q8_1
+    BF16 = GGML_BF16
+
+    @property
+    def block_size(self) -> int:
+        """Elements per block."""
+        return _BLOCK[int(self)][0]
+
+    @property
+    def type_size(self) -> int:
+        """Bytes per block."""
+        return _BLOCK[int(self)][1]
+
+    def nbytes(self, n_elements: int) -> int:
+        if n_elements % self.block_size:
+            raise ValueError("%d elements are not a whole number of %s blocks" % (n_elements, self.name))
+        return n_elements // self.block_size * self.type_size
+
+
+GgufValue = object           # metadata values arrive as plain Python (int / float / bool / str / list)
+GgufMetadata = dict
+
+
+@_dataclass(frozen=True)
+class GgufTensorInfo:
+    name: str
+    ggml_type: GgmlType
+    shape: tuple             # outermost dimension first
+    nbytes: int
+
+    def numel(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+
+def tensor_infos(f: GgufFile) -> list:
+    return [GgufTensorInfo(k, GgmlType(t), shape, nb) for k, (t, shape, nb) in f.tensors.items()]
+
+
+def load_gguf(path: str) -> GgufFile:
+    """Open a GGUF file: header, metadata and tensor directory parsed, tensor data memory-mapped."""
+    return GgufFile(path)
+
+
+load_gguf_mmap = load_gguf   # the reader always maps the file; the name exists for the reference's callers
+
+
+def parse_gguf_bytes(data: bytes) -> GgufFile:
+    """Parse a GGUF image held in memory (written to an anonymous temporary file and mapped)."""
+    import tempfile
+
+    with tempfile.NamedTemporaryFile(suffix=".gguf", delete=False) as tmp:
+        tmp.write(data)
+        path = tmp.name
+    try:
+        return GgufFile(path)
+    finally:
+        os.unlink(path)      # the mapping keeps the pages alive
+
+
+def dequantize_gguf_tensor(f: GgufFile, name: str, dtype=torch.float32, nibble_order: str = "ggml") -> torch.Tensor:
+    return f.dequantize(name, dtype, nibble_order)
+
+
+def load_gguf_state_dict_mmap(path: str, dtype=torch.bfloat16, remap: bool = True, **kw) -> dict:
+    return load_gguf_state_dict(path, dtype, remap, **kw)

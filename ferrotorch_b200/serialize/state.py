@@ -417,6 +417,28 @@ def load_checkpoint(path: str, device="cpu") -> dict:
             "step": meta["step"], "extra": meta["extra"]}
 
 
+@dataclass
+class TrainingCheckpoint:
+    """Model + optimizer + progress in one object (ferrotorch-serialize/src/checkpoint.rs:59);
+    ``save`` / ``load`` are :func:`save_checkpoint` / :func:`load_checkpoint`."""
+    model_state: dict
+    optimizer_state: dict | None = None
+    epoch: int = 0
+    step: int = 0
+    extra: dict | None = None
+
+    def save(self, path: str) -> None:
+        save_checkpoint(path, self.model_state, self.optimizer_state, self.epoch, self.step, self.extra)
+
+    @classmethod
+    def load(cls, path: str, device="cpu") -> "TrainingCheckpoint":
+        d = load_checkpoint(path, device)
+        return cls(d["model"], d["optimizer"], int(d["epoch"]), int(d["step"]), d.get("extra") or {})
+
+
+PickleValue = object      # what ``parse_pickle`` yields as values: plain Python objects and tensor stubs
+
+
 class CheckpointFuture:
     def __init__(self, thread: threading.Thread, box: list):
         self._t, self._box = thread, box

@@ -96,3 +96,9 @@ class UNet(nn.Module):
 from .io import (GaussianNoise, RandomGaussianBlur, RawImage, VisionNormalize, VisionToTensor,  # noqa: F401,E402
                  raw_image_to_tensor, read_image, read_image_as_tensor, read_image_rgba, tensor_to_raw_image,
                  vision_manual_seed, write_image, write_tensor_as_image)
+
+if HAVE_TORCHVISION:
+    from .compat import *  # noqa: F401,F403,E402
+    from .compat import (FPN_OUT_CHANNELS, IMAGENET_MEAN, IMAGENET_STD, SSD_ANCHORS_PER_SCALE, SSD_FM_SIZES,  # noqa: F401,E402
+                         SSD_TOTAL_ANCHORS, CifarSample, Detections, MaskDetections, MnistSample, ModelConstructor,
+                         SsdDetections)

@@ -280,3 +280,33 @@ def test_pickle_inspection_and_mmap_load(tmp_path):
     evil = str(tmp_path / "evil.pt")
     torch.save({"x": os.path.join}, evil)                  # a function reference: visible before anything is loaded
     assert any("join" in i for i in S.pickle_imports(evil))
+
+
+def test_gguf_and_checkpoint_reference_names(tmp_path):
+    import ferrotorch_b200.serialize as S
+
+    w = torch.randn(4, 64)
+    blocks = S.quantize_q4_0(w)
+    path = str(tmp_path / "m.gguf")
+    S.write_gguf(path, {"blk.0.attn_q.weight": (int(S.GgmlType.Q4_0), (4, 64), bytes(blocks.reshape(-1).tolist())),
+                        "output_norm.weight": (int(S.GgmlType.F32), (64,), torch.ones(64).numpy().tobytes())},
+                 {"general.architecture": "llama"})
+    f = S.load_gguf(path)
+    infos = {i.name: i for i in S.tensor_infos(f)}
+    q = infos["blk.0.attn_q.weight"]
+    assert q.ggml_type is S.GgmlType.Q4_0 and q.shape == (4, 64) and q.numel() == 256 and q.nbytes == S.GgmlType.Q4_0.nbytes(256) == 144
+    assert (S.GgmlType.Q4_0.block_size, S.GgmlType.Q4_0.type_size) == (32, 18) and f.metadata["general.architecture"] == "llama"
+    deq = S.dequantize_gguf_tensor(f, "blk.0.attn_q.weight")
+    assert deq.shape == (4, 64) and (deq - w).abs().max() < 0.5
+    with open(path, "rb") as fh:
+        g = S.parse_gguf_bytes(fh.read())
+    torch.testing.assert_close(g.dequantize("blk.0.attn_q.weight"), deq)
+    sd = S.load_gguf_state_dict_mmap(path, torch.float32)
+    assert set(sd) == {"model.layers.0.self_attn.q_proj.weight", "model.norm.weight"}
+    with pytest.raises(ValueError):
+        S.GgmlType.Q4_0.nbytes(33)
+    ck = S.TrainingCheckpoint({"w": w}, {"state": {}, "param_groups": [{"lr": 0.1, "params": [0]}]}, epoch=3, step=40, extra={"note": "x"})
+    ck.save(str(tmp_path / "c.ftck"))
+    back = S.TrainingCheckpoint.load(str(tmp_path / "c.ftck"))
+    assert back.epoch == 3 and back.step == 40 and back.extra == {"note": "x"} and torch.equal(back.model_state["w"], w)
+    assert back.optimizer_state["param_groups"][0]["lr"] == 0.1

@@ -125,3 +125,23 @@ def test_image_io_and_extra_transforms(tmp_path):
     assert torch.equal(vision.RandomGaussianBlur(3, p=0.0)(img), img)
     with pytest.raises(ValueError):
         vision.RandomGaussianBlur(4)
+
+
+def test_reference_vision_names():
+    import ferrotorch_b200.vision as V
+
+    assert V.SSD_TOTAL_ANCHORS == 8732 and V.IMAGENET_MEAN == (0.485, 0.456, 0.406) and V.Split.Train.train
+    assert V.get_model("resnet18", num_classes=5)(torch.randn(1, 3, 64, 64)).shape == (1, 5)
+    reg = V.ModelRegistry()
+    reg.register("tiny", lambda **kw: torch.nn.Linear(2, 2))
+    assert reg.contains("tiny") and reg.contains("faster_rcnn") and isinstance(reg.get("tiny"), torch.nn.Linear)
+    with pytest.raises(ValueError):
+        reg.register("resnet50", lambda: None)
+    net = V.ResNet50Dilated(num_classes=3)
+    feats = V.create_feature_extractor(net, {"layer2": "c3", "layer4": "c5"})(torch.randn(1, 3, 64, 64))
+    assert feats["c3"].shape[-1] == 8 and feats["c5"].shape[-1] == 8 and feats["c5"].shape[1] == 2048   # stride stays 8
+    seg = V.fcn_resnet50(num_classes=4).eval()
+    assert isinstance(seg, V.Fcn) and seg(torch.randn(1, 3, 64, 64))["out"].shape == (1, 4, 64, 64)
+    assert V.Resize(8)(torch.rand(3, 16, 16)).shape == (3, 8, 8) and V.CenterCrop(4)(torch.rand(3, 8, 8)).shape == (3, 4, 4)
+    rpn = V.RpnConfig(nms_thresh=0.6).build(V.AnchorGenerator(((32,),), ((1.0,),)), V.RpnHead(8, 1))
+    assert isinstance(rpn, V.Rpn) and rpn.nms_thresh == 0.6
