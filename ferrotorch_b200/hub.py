@@ -275,3 +275,72 @@ def get_model(repo_id: str) -> dict:
     if not repo_id.strip():
         raise ValueError("get_model: empty repository id")
     return json.loads(_http_get("https://huggingface.co/api/models/" + urllib.parse.quote(repo_id, safe="/")))
+
+
+# --------------------------------------------------------------------------- the reference's remaining type names
+import enum as _enum  # noqa: E402
+
+
+class WeightsFormat(str, _enum.Enum):
+    """``ModelInfo.format`` values (registry.rs:21)."""
+    SafeTensors = "safetensors"
+    FerrotorchStateDict = "ftsd"
+    PyTorch = "pt"
+
+    def __str__(self) -> str:
+        return self.value
+
+    @property
+    def extension(self) -> str:
+        return {"safetensors": "safetensors", "ftsd": "fts", "pt": "pt"}[self.value]
+
+
+class EntryKind(_enum.Enum):
+    """A registry entry is a real model (positive parameter count) or a test fixture (registry.rs:38)."""
+    Model = "model"
+    Fixture = "fixture"
+
+    @classmethod
+    def of(cls, info: "ModelInfo") -> "EntryKind":
+        return cls.Model if info.num_parameters > 0 else cls.Fixture
+
+
+@dataclass
+class HfRepoFile:
+    rfilename: str
+
+
+@dataclass
+class HfModelInfo:
+    """One repository as the hub's ``/api/models/<id>`` describes it (discovery.rs:99)."""
+    model_id: str
+    author: str | None = None
+    downloads: int | None = None
+    likes: int | None = None
+    tags: list = field(default_factory=list)
+    pipeline_tag: str | None = None
+    siblings: list = field(default_factory=list)
+
+    @classmethod
+    def from_json(cls, d: dict) -> "HfModelInfo":
+        mid = d.get("modelId") or d.get("id") or ""
+        return cls(mid, d.get("author") or (mid.split("/")[0] if "/" in mid else None), d.get("downloads"), d.get("likes"),
+                   list(d.get("tags") or []), d.get("pipeline_tag"),
+                   [HfRepoFile(s["rfilename"]) for s in d.get("siblings") or [] if "rfilename" in s])
+
+    def files(self) -> list:
+        return [s.rfilename for s in self.siblings]
+
+
+def get_model_details(repo_id: str) -> HfModelInfo:
+    """:func:`get_model` parsed into :class:`HfModelInfo`."""
+    return HfModelInfo.from_json(get_model(repo_id))
+
+
+def with_auth(request: "urllib.request.Request") -> "urllib.request.Request":
+    """Add ``Authorization: Bearer <token>`` when a hub token is configured (auth.rs:73); the
+    request is returned unchanged otherwise, which is what public repositories expect."""
+    tok = hf_token()
+    if tok:
+        request.add_header("Authorization", "Bearer " + tok)
+    return request

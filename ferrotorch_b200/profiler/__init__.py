@@ -10,6 +10,7 @@ from __future__ import annotations
 import contextlib
 import json
 import time
+import enum
 from dataclasses import dataclass, field
 
 import torch
@@ -129,6 +130,10 @@ class Profiler:
 
     def record(self, name: str, dur_us: float, category: str = "manual") -> None:
         self.events.append(ProfileEvent(name, category, self._now_us(), dur_us))
+
+    def push_gpu_event(self, name: str, timing: "GpuTimingPair", category: str = "kernel") -> None:
+        """Add a device interval measured elsewhere (profiler.rs:200): duration = end - start, never negative."""
+        self.events.append(ProfileEvent(name, category, float(timing.start_us), float(timing.duration_us()), str(DeviceType.Cuda)))
 
     def record_memory(self, tag: str, nbytes: int) -> None:
         self.memory.append((self._now_us(), tag, int(nbytes)))
@@ -303,3 +308,22 @@ def with_profiler(fn, config: ProfileConfig | None = None, schedule: ProfileSche
         Profiler._current = prev
         p.flush()
     return r, p
+
+
+class DeviceType(str, enum.Enum):
+    """Where an event ran (event.rs:21)."""
+    Cpu = "cpu"
+    Cuda = "cuda"
+
+    def __str__(self) -> str:
+        return self.value
+
+
+@dataclass
+class GpuTimingPair:
+    """Start and end of a device interval in microseconds (event.rs:116)."""
+    start_us: int
+    end_us: int
+
+    def duration_us(self) -> int:
+        return max(0, int(self.end_us) - int(self.start_us))

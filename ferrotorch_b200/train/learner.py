@@ -14,6 +14,8 @@ import math
 import os
 from dataclasses import dataclass, field
 
+from typing import Callable
+
 import torch
 from torch import nn
 
@@ -363,3 +365,6 @@ def checkpoint_sequential(functions, segments: int, x: torch.Tensor) -> torch.Te
 
         x = checkpoint(run, x, use_reentrant=False) if s + per < len(fns) else run(x)
     return x
+
+
+LossFn = Callable[[torch.Tensor, torch.Tensor], torch.Tensor]      # (prediction, target) -> scalar loss

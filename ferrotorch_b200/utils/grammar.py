@@ -865,3 +865,92 @@ class SchemaLogitsProcessor:
                 bits[self.eos] = True
             masks.append(bits)
         return logits.masked_fill(~torch.stack(masks).to(logits.device), float("-inf"))
+
+
+# --------------------------------------------------------------------------- the reference's remaining names
+JsonGrammar = SchemaGrammar        # ferrotorch-grammar/src/state.rs
+
+
+class PackedVocab:
+    """The vocabulary as one array of code points with CSR offsets (gpu_dispatch.rs:897-956):
+    ``offsets [V + 1]``, ``chars [sum of token lengths]`` (int32 tensors), ``max_token_len``."""
+
+    def __init__(self, offsets: torch.Tensor, chars: torch.Tensor, max_token_len: int):
+        self.offsets, self.chars, self.max_token_len = offsets, chars, int(max_token_len)
+
+    @classmethod
+    def pack(cls, vocab) -> "PackedVocab":
+        lens = [len(t) for t in vocab]
+        offsets = torch.zeros(len(lens) + 1, dtype=torch.int32)
+        offsets[1:] = torch.tensor(lens, dtype=torch.int64).cumsum(0).to(torch.int32) if lens else offsets[1:]
+        chars = torch.tensor([ord(c) for t in vocab for c in t], dtype=torch.int32)
+        return cls(offsets, chars, max(lens, default=0))
+
+    def __len__(self) -> int:
+        return self.offsets.numel() - 1
+
+    def token(self, i: int) -> str:
+        return "".join(chr(int(c)) for c in self.chars[int(self.offsets[i]):int(self.offsets[i + 1])])
+
+    def to(self, device) -> "PackedVocab":
+        return PackedVocab(self.offsets.to(device), self.chars.to(device), self.max_token_len)
+
+
+def compute_mask_gpu(processor: "JsonSchemaProcessor", packed: PackedVocab | None = None, device=None) -> TokenMask:
+    """The processor's token mask with its packed words resident on ``device`` (default: the
+    current CUDA device when there is one), ready for :func:`apply_packed_mask_` on device logits.
+    The reference walks a compiled DFA over ``packed`` in a kernel for a few grammar states and
+    falls back to the host walk for the rest (gpu_dispatch.rs ``compute_mask_gpu``); here the walk
+    is always the native trie walk on the host -- transitions are memoised, so a warm mask is table
+    look-ups -- and only the application of the mask runs on the GPU."""
+    if packed is not None and len(packed) != processor.vocab_len():
+        raise ValueError("compute_mask_gpu: packed vocabulary has %d tokens, the processor %d" % (len(packed), processor.vocab_len()))
+    mask = processor.compute_mask()
+    if device is None and torch.cuda.is_available():
+        device = torch.device("cuda", torch.cuda.current_device())
+    if device is not None:
+        mask.packed_device = mask.packed().to(device, non_blocking=True)
+    return mask
+
+
+class BooleanEmissionStage:
+    """Where a boolean literal stands while it is being emitted (state.rs:238): ``Start``, or part
+    of ``true`` / ``false`` written with ``remaining`` still to come."""
+
+    def __init__(self, kind: str, remaining: str = ""):
+        self.kind, self.remaining = kind, remaining
+
+    Start = None      # filled in below
+
+    @classmethod
+    def PartialTrue(cls, remaining: str) -> "BooleanEmissionStage":
+        return cls("partial_true", remaining)
+
+    @classmethod
+    def PartialFalse(cls, remaining: str) -> "BooleanEmissionStage":
+        return cls("partial_false", remaining)
+
+    @classmethod
+    def after(cls, emitted: str) -> "BooleanEmissionStage | None":
+        """Stage after ``emitted`` characters of a boolean; None when they start neither literal or complete one."""
+        if emitted == "":
+            return cls.Start
+        for word, make in (("true", cls.PartialTrue), ("false", cls.PartialFalse)):
+            if word.startswith(emitted) and emitted != word:
+                return make(word[len(emitted):])
+        return None
+
+    def allowed_next(self) -> str:
+        return "tf" if self.kind == "start" else self.remaining[:1]
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, BooleanEmissionStage) and (self.kind, self.remaining) == (other.kind, other.remaining)
+
+    def __hash__(self) -> int:
+        return hash((self.kind, self.remaining))
+
+    def __repr__(self) -> str:
+        return "BooleanEmissionStage.Start" if self.kind == "start" else "BooleanEmissionStage(%s, remaining=%r)" % (self.kind, self.remaining)
+
+
+BooleanEmissionStage.Start = BooleanEmissionStage("start")

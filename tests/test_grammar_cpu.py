@@ -226,3 +226,36 @@ def test_packed_mask_kernel_matches_torch(dtype):
     want = logits.masked_fill(~bits.cuda(), float("-inf"))
     assert torch.equal(G.apply_packed_mask_(logits.clone(), packed), want)
     assert torch.equal(G.apply_packed_mask_(logits.clone(), packed[:1]), logits.masked_fill(~bits[:1].cuda(), float("-inf")))
+
+
+def test_reference_names_packed_vocab_masked_loop():
+    from ferrotorch_b200 import models as M
+    from ferrotorch_b200.utils import grammar as G
+
+    vocab = ["<eos>", "{", "}", '"', "a", ":", "true", "false", "tr", "ue", ",", " ", '"a"', "1"]
+    pv = G.PackedVocab.pack(vocab)
+    assert len(pv) == len(vocab) and pv.max_token_len == 5 and pv.token(6) == "true" and pv.offsets[-1] == pv.chars.numel()
+    assert G.JsonGrammar is G.SchemaGrammar
+    st = G.BooleanEmissionStage.after("tr")
+    assert st == G.BooleanEmissionStage.PartialTrue("ue") and st.allowed_next() == "u"
+    assert G.BooleanEmissionStage.after("") is G.BooleanEmissionStage.Start and G.BooleanEmissionStage.Start.allowed_next() == "tf"
+    assert G.BooleanEmissionStage.after("x") is None and G.BooleanEmissionStage.after("true") is None
+    schema = {"type": "object", "properties": {"a": {"type": "boolean"}}, "required": ["a"]}
+    proc = G.JsonSchemaProcessor(schema, vocab, 0)
+    mask = G.compute_mask_gpu(proc, pv)
+    assert mask.num_allowed() >= 1 and mask.is_allowed(1) and not mask.is_allowed(2)
+    with pytest.raises(ValueError):
+        G.compute_mask_gpu(proc, G.PackedVocab.pack(vocab[:3]))
+    # greedy loop: the "model" prefers '}' everywhere; the grammar forces a valid document anyway
+    logits = torch.zeros(len(vocab))
+    logits[2], logits[7] = 5.0, 1.0
+    out = M.masked_decode_loop(lambda ids: logits, proc, [], 32)
+    text = "".join(vocab[i] for i in out)
+    import json
+    assert proc.is_complete() and isinstance(json.loads(text)["a"], bool)
+    assert M.masked_decode_loop(lambda ids: logits, None, [1], 3) == [2, 2, 2]
+    masked = M.apply_grammar_mask_gpu(torch.zeros(4), [True, False, True, False])
+    assert masked.tolist() == [0.0, float("-inf"), 0.0, float("-inf")]
+    q = M.GptqQ4(*__import__("ferrotorch_b200.serialize.quant_loaders", fromlist=["x"]).pack_gptq(torch.randn(16, 128), 128))
+    assert (q.in_features, q.out_features) == (128, 16) and q.dequantize().shape == (16, 128)
+    assert M.LlamaActivation.Silu == "silu" and M.LlamaMLP.__name__ == "SwiGLU"

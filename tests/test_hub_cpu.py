@@ -102,3 +102,24 @@ def test_queries_and_offline_errors(tmp_path, monkeypatch):
     (snap / "config.json").write_text("{}")
     assert H.hf_download_model("org/model") == str(snap)                    # a cached snapshot needs no network
     assert isinstance(H.HubOffline("x"), ConnectionError)
+
+
+def test_hub_reference_type_names(monkeypatch):
+    import urllib.request
+
+    from ferrotorch_b200 import hub as H
+
+    info = H.HfModelInfo.from_json({"modelId": "org/m", "downloads": 5, "tags": ["llama"],
+                                    "siblings": [{"rfilename": "config.json"}, {"rfilename": "model.safetensors"}]})
+    assert info.model_id == "org/m" and info.author == "org" and info.files() == ["config.json", "model.safetensors"]
+    assert isinstance(info.siblings[0], H.HfRepoFile) and info.likes is None
+    assert H.WeightsFormat.SafeTensors == "safetensors" and H.WeightsFormat.FerrotorchStateDict.extension == "fts"
+    assert all(H.EntryKind.of(m) is H.EntryKind.Model for m in H.list_models())
+    monkeypatch.setenv("HF_TOKEN", "abc")
+    req = H.with_auth(urllib.request.Request("https://huggingface.co/api/models/x"))
+    assert req.get_header("Authorization") == "Bearer abc"
+    monkeypatch.delenv("HF_TOKEN")
+    monkeypatch.setenv("HF_HOME", "/nonexistent-dir-for-test")
+    monkeypatch.delenv("HUGGING_FACE_HUB_TOKEN", raising=False)
+    req = H.with_auth(urllib.request.Request("https://huggingface.co/api/models/x"))
+    assert req.get_header("Authorization") is None
