@@ -14,7 +14,7 @@ from . import ops  # noqa: F401
 from . import autograd, core  # noqa: F401,E402
 
 _SUBMODULES = ("nn", "optim", "data", "train", "vision", "jit", "serialize", "parallel", "models", "profiler", "hub",
-               "cuda", "distributions", "utils")
+               "cuda", "distributions", "utils", "tensor_ops")
 __all__ = ["ops", "autograd", "core", "__version__", *_SUBMODULES]
 
 
@@ -25,4 +25,20 @@ def __getattr__(name):
         import importlib
 
         return importlib.import_module("." + name, __name__)
+    if not name.startswith("_"):
+        # the flat tensor API of the reference's core crate: its own spellings first, torch's second
+        import importlib
+
+        import torch
+
+        ops_mod = importlib.import_module(".tensor_ops", __name__)
+        try:
+            return getattr(ops_mod, name)
+        except AttributeError:
+            pass
+        from .ops import ptq
+
+        for home in (core, autograd, ptq, torch):
+            if hasattr(home, name):
+                return getattr(home, name)
     raise AttributeError("module %r has no attribute %r" % (__name__, name))
