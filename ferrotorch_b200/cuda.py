@@ -172,3 +172,196 @@ def cuda_rng_state(ordinal: int = 0) -> torch.Tensor:
 def set_cuda_rng_state(state: torch.Tensor, ordinal: int = 0) -> None:
     _need()
     torch.cuda.set_rng_state(state, ordinal)
+
+
+# --------------------------------------------------------------------------- explicit begin / end capture, pools
+import enum as _enum  # noqa: E402
+
+
+class CaptureMode(str, _enum.Enum):
+    """How strictly other threads' CUDA calls are policed during capture (graph.rs ``CaptureMode``)."""
+    Global = "global"
+    ThreadLocal = "thread_local"
+    Relaxed = "relaxed"
+
+    def __str__(self) -> str:
+        return self.value
+
+
+class CaptureStatus(_enum.Enum):
+    NotCapturing = "none"
+    Active = "active"
+
+
+def capture_status() -> CaptureStatus:
+    return CaptureStatus.Active if is_stream_capturing() else CaptureStatus.NotCapturing
+
+
+class GraphPoolHandle:
+    """A graph memory pool that several captures may share (graph.rs ``GraphPoolHandle``)."""
+
+    def __init__(self, handle=None):
+        self.handle = handle if handle is not None else graph_pool_handle()
+
+
+CapturePool = PrivateMemPool = GraphPoolHandle
+_live_pools: dict = {}
+
+
+def capture_pool_for_handle(handle) -> GraphPoolHandle:
+    key = id(handle) if not isinstance(handle, tuple) else handle
+    return _live_pools.setdefault(key, GraphPoolHandle(handle))
+
+
+def release_graph_pool_handle(pool: GraphPoolHandle) -> None:
+    """Forget a pool; its memory returns to the allocator once the graphs that used it are gone."""
+    for k, v in list(_live_pools.items()):
+        if v is pool:
+            del _live_pools[k]
+
+
+class GraphCaptureGuard:
+    """``begin_capture`` .. ``end_capture`` as an object: capture starts on construction, ``end()``
+    (or leaving the ``with`` block) finishes it and yields the :class:`CapturedGraph`.  An
+    exception inside the block still ends the capture, so the stream is never left capturing."""
+
+    def __init__(self, pool: GraphPoolHandle | None = None, mode: CaptureMode = CaptureMode.Global, stream=None):
+        _need()
+        self._g = torch.cuda.CUDAGraph()
+        self._cm = torch.cuda.graph(self._g, pool=pool.handle if pool is not None else None, stream=stream,
+                                    capture_error_mode=str(mode))
+        self._cm.__enter__()
+        self.captured: CapturedGraph | None = None
+
+    def end(self) -> CapturedGraph:
+        if self.captured is None:
+            self._cm.__exit__(None, None, None)
+            self.captured = CapturedGraph(self._g)
+        return self.captured
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, et, ev, tb):
+        if self.captured is None:
+            self._cm.__exit__(et, ev, tb)
+            if et is None:
+                self.captured = CapturedGraph(self._g)
+        return False
+
+
+def begin_capture() -> GraphCaptureGuard:
+    return GraphCaptureGuard()
+
+
+def begin_capture_with_mode(mode: CaptureMode) -> GraphCaptureGuard:
+    return GraphCaptureGuard(mode=mode)
+
+
+def begin_capture_with_pool(pool: GraphPoolHandle) -> GraphCaptureGuard:
+    return GraphCaptureGuard(pool)
+
+
+def begin_capture_with_pool_mode(pool: GraphPoolHandle, mode: CaptureMode) -> GraphCaptureGuard:
+    return GraphCaptureGuard(pool, mode)
+
+
+def end_capture(guard: GraphCaptureGuard) -> CapturedGraph:
+    return guard.end()
+
+
+end_capture_with_pool = end_capture
+
+
+def capture_into_private_pool(fn, *args, pool: GraphPoolHandle | None = None):
+    """Run ``fn(*args)`` under capture with memory from ``pool`` (a fresh one by default);
+    returns ``(captured graph, fn's outputs)`` -- the outputs are the static tensors replays fill."""
+    g = GraphCaptureGuard(pool or GraphPoolHandle())
+    with g:
+        out = fn(*args)
+    return g.captured, out
+
+
+class MemPoolScope:
+    """Allocations inside the block come from ``pool`` (``torch.cuda.use_mem_pool``)."""
+
+    def __init__(self, pool=None):
+        _need()
+        self.pool = pool if pool is not None else torch.cuda.MemPool()
+        self._cm = torch.cuda.use_mem_pool(self.pool)
+
+    def __enter__(self):
+        self._cm.__enter__()
+        return self.pool
+
+    def __exit__(self, *exc):
+        return self._cm.__exit__(*exc)
+
+
+# --------------------------------------------------------------------------- remaining type names of the GPU crate
+GpuTensor = CudaBuffer = torch.Tensor          # device memory is a torch tensor on a CUDA device
+GpuFloat = (torch.float32, torch.float64, torch.bfloat16, torch.float16)
+GpuResult = object
+
+
+def alloc_zeros_f32(n: int, ordinal: int = 0) -> torch.Tensor:
+    return alloc_zeros((n,), torch.float32, ordinal)
+
+
+def alloc_zeros_f64(n: int, ordinal: int = 0) -> torch.Tensor:
+    return alloc_zeros((n,), torch.float64, ordinal)
+
+
+def alloc_zeros_bf16(n: int, ordinal: int = 0) -> torch.Tensor:
+    return alloc_zeros((n,), torch.bfloat16, ordinal)
+
+
+def init_cuda_backend(ordinal: int = 0) -> GpuDevice:
+    """Make the device current, create its context and load the kernel library; idempotent."""
+    _need()
+    torch.cuda.set_device(ordinal)
+    torch.cuda.init()
+    from . import _native
+
+    _native.kernels()
+    return get_cuda_device(ordinal)
+
+
+class CudaAllocator:
+    """Statistics and controls of the caching allocator that serves device tensors (torch's)."""
+
+    def __init__(self, ordinal: int = 0):
+        self.ordinal = ordinal
+
+    def allocated_bytes(self) -> int:
+        return torch.cuda.memory_allocated(self.ordinal) if is_available() else 0
+
+    def reserved_bytes(self) -> int:
+        return torch.cuda.memory_reserved(self.ordinal) if is_available() else 0
+
+    def peak_bytes(self) -> int:
+        return torch.cuda.max_memory_allocated(self.ordinal) if is_available() else 0
+
+    def reset_peak_stats(self) -> None:
+        if is_available():
+            torch.cuda.reset_peak_memory_stats(self.ordinal)
+
+    def empty_cache(self) -> None:
+        empty_cache()
+
+    @staticmethod
+    def round_len(nbytes: int) -> int:
+        return round_len(nbytes)
+
+
+def __getattr__(name):
+    """Memory-guard types are defined in ``utils.memory_guard``."""
+    table = {"MemoryGuardedDevice": "MemoryGuard", "MemoryWatchdog": "MemoryGuard", "MemoryStats": "MemoryStats",
+             "MemoryReservation": "MemoryReservation", "MemoryHook": "MemoryHook",
+             "MemoryPressureListener": "MemoryPressureListener", "MemoryGuard": "MemoryGuard",
+             "MemoryGuardBuilder": "MemoryGuardBuilder", "PressureLevel": "PressureLevel", "OomPolicy": "OomPolicy"}
+    if name in table:
+        from .utils import memory_guard
+
+        return getattr(memory_guard, table[name])
+    raise AttributeError(name)

@@ -12,7 +12,10 @@ from .backends import (BinOpKind, Codegen, CompiledGraph, CpuCodegen, Expr, Fuse
                        InductorBackend, InductorCompileStatus, InductorTarget, InterpreterBackend, LoopIR, MemoryPlan,
                        NativeBackend, ReductionKind, UnaryOpKind, compile_loop_ir_kernel, compile_with_config,
                        estimate_numel_for_inputs, generate_reduction_source, interpret, interpret_multi,
-                       interpret_multi_with_captures, is_fusion_enabled, reduce_reference)
+                       interpret_multi_with_captures, is_fusion_enabled, reduce_reference,
+                       AotCompiledModule, AutotuneCandidate, AutotuneKey, AutotuneResult, FusionGroup, FusionGroupKind,
+                       JitCompiledKernel, TraceResult, autotune, estimate_matmul_dims, export_with_dynamic_shapes,
+                       generate_reduction_ptx, generate_reduction_rust)
 
 
 def script(fn):

@@ -420,3 +420,123 @@ def compile_loop_ir_kernel(ir: LoopIR, name: str = "fused_loop"):
     """LoopIR -> (source, cubin bytes) for sm_100a through NVRTC (codegen_jit.rs ``compile_loop_ir_kernel``)."""
     src = GpuCodegen().generate(ir, name)
     return src, codegen.compile_cubin(src, name)
+
+
+# --------------------------------------------------------------------------- remaining names of the reference's JIT
+from . import advanced as _adv  # noqa: E402
+
+AotCompiledModule = _adv.AotModule
+TraceResult = _adv.SegmentedModule            # what ``trace_with_breaks`` returns
+JitCompiledKernel = codegen.CompiledKernel
+
+
+def export_with_dynamic_shapes(module, example_inputs, dynamic_dims: dict):
+    """``export`` with ``{input index: {dim index: name}}`` naming the dimensions that may vary."""
+    specs = []
+    for i, t in enumerate(example_inputs):
+        names = dynamic_dims.get(i, {})
+        specs.append(_adv.InputSpec([_adv.DimSpec.dynamic(names[d]) if d in names else _adv.DimSpec.static(int(s))
+                                     for d, s in enumerate(t.shape)]))
+    return _adv.export(module, example_inputs, specs)
+
+
+def estimate_matmul_dims(shapes) -> tuple:
+    """``(M, N, K)`` of ``a @ b`` for operand shapes ``[..., M, K]`` and ``[..., K, N]`` (batch folded into M)."""
+    a, b = tuple(shapes[0]), tuple(shapes[1])
+    if len(a) < 2 or len(b) < 2 or a[-1] != b[-2]:
+        raise JitError("estimate_matmul_dims: %s @ %s" % (a, b))
+    m = a[-2]
+    for d in a[:-2]:
+        m *= d
+    return int(m), int(b[-1]), int(a[-1])
+
+
+class FusionGroupKind(enum.Enum):
+    Elementwise = "fused_elementwise"
+    LinearActivation = "fused_linear_act"
+    Attention = "fused_attention"
+
+
+@dataclass
+class FusionGroup:
+    """One fused node of an optimised graph: its kind, the node id, how many primitive ops it absorbed."""
+    kind: FusionGroupKind
+    node_id: int
+    n_ops: int
+
+    @classmethod
+    def of(cls, graph: IrGraph) -> list:
+        out = []
+        for i in graph.order:
+            n = graph.nodes[i]
+            if n.op in (k.value for k in FusionGroupKind):
+                out.append(cls(FusionGroupKind(n.op), i, len(n.attrs.get("program", ())) or 2))
+        return out
+
+
+@dataclass(frozen=True)
+class AutotuneKey:
+    """What a tuning result is valid for: the graph's op sequence and the input signature."""
+    ops: tuple
+    signature: tuple
+
+    @classmethod
+    def of(cls, module: TracedModule) -> "AutotuneKey":
+        return cls(tuple(module.graph.ops()), tuple(module.guard))
+
+
+@dataclass
+class AutotuneCandidate:
+    block_size: int
+    ms: float = float("nan")
+
+
+@dataclass
+class AutotuneResult:
+    key: AutotuneKey
+    best: AutotuneCandidate
+    candidates: list
+
+
+def autotune(module: TracedModule, inputs, candidates=(128, 256, 512), iters: int = 5, cache: dict | None = None) -> AutotuneResult:
+    """Time every candidate block size (CUDA events; on the CPU nothing is timed and the module's
+    current block size stands) and keep the best; ``cache`` (key -> result) skips repeated tuning."""
+    key = AutotuneKey.of(module)
+    if cache is not None and key in cache:
+        module.cfg.block_size = cache[key].best.block_size
+        return cache[key]
+    cands = []
+    if torch.cuda.is_available() and any(isinstance(t, torch.Tensor) and t.is_cuda for t in inputs):
+        for b in candidates:
+            module.cfg.block_size = b
+            module(*inputs)
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                module(*inputs)
+            e.record()
+            torch.cuda.synchronize()
+            cands.append(AutotuneCandidate(b, s.elapsed_time(e) / iters))
+        best = min(cands, key=lambda c: c.ms)
+    else:
+        best = AutotuneCandidate(module.cfg.block_size)
+        cands = [best]
+    module.cfg.block_size = best.block_size
+    res = AutotuneResult(key, best, cands)
+    if cache is not None:
+        cache[key] = res
+    return res
+
+
+def generate_reduction_ptx(kind: ReductionKind, pre: FusedChain | None = None, name: str = "fused_reduce") -> str:
+    """The reference emits PTX text here; this build's generated kernels are CUDA C compiled for
+    sm_100a by NVRTC, so this returns that source (:func:`generate_reduction_source`)."""
+    return generate_reduction_source(kind, pre, name)
+
+
+def generate_reduction_rust(kind: ReductionKind, pre: FusedChain | None = None, name: str = "fused_reduce") -> str:
+    """Host-side counterpart of :func:`generate_reduction_ptx`: Python source over torch ops."""
+    body = CpuCodegen().expr(pre.loop_ir().body) if pre is not None and len(pre) else "x0"
+    red = {"sum": "sum(-1)", "mean": "mean(-1)", "prod": "prod(-1)", "max": "amax(-1)", "min": "amin(-1)"}[kind.value]
+    return "def %s(x0):\n    return (%s).%s\n" % (name, body, red)

@@ -858,3 +858,97 @@ def save_stable_diffusion(pipe: StableDiffusionPipeline, path: str) -> None:
     os.makedirs(os.path.join(path, "scheduler"), exist_ok=True)
     with open(os.path.join(path, "scheduler", "scheduler_config.json"), "w") as f:
         json.dump(asdict(pipe.scheduler.config), f, indent=2)
+
+
+# --------------------------------------------------------------------------- the reference's block and loader names
+import enum as _enum  # noqa: E402
+
+from .pretrained import DropReport  # noqa: E402,F401  (what a partial load reports: loaded / dropped / missing keys)
+
+Attention, FeedForward, AttnBlock2D = _Attention, _FeedForward, _VaeAttention
+ClipSelfAttention, ClipMlp, ClipEncoderLayer, ClipTextEmbeddings, ClipEncoder = (_ClipAttention, _ClipMlp, _ClipLayer,
+                                                                                  _ClipEmbeddings, _ClipEncoder)
+TimestepEmbedding, ResnetBlock2DTime = _TimestepEmbedding, ResnetBlock2D
+Downsample2D, Upsample2D = _Down, _Up
+# one block class covers the plain and the cross-attention variants (``attn`` switches the transformer on)
+DownBlock2D = CrossAttnDownBlock2D = UpBlock2D = CrossAttnUpBlock2D = AnyDownBlock = AnyUpBlock = _UNetBlock
+UNetMidBlock2DCrossAttn = UNetMidBlock2D = _UNetMid
+DownEncoderBlock2D = UpDecoderBlock2D = _VaeStage
+VaeEncoder, VaeDecoder = Encoder, Decoder
+
+
+class Timesteps(nn.Module):
+    """Sinusoidal timestep features (the function :func:`timestep_embedding` as a module)."""
+
+    def __init__(self, dim: int, flip_sin_to_cos: bool = True, shift: float = 0.0):
+        super().__init__()
+        self.dim, self.flip, self.shift = dim, flip_sin_to_cos, shift
+
+    def forward(self, t: torch.Tensor) -> torch.Tensor:
+        return timestep_embedding(t, self.dim, self.flip, self.shift)
+
+
+class BetaSchedule(str, _enum.Enum):
+    Linear = "linear"
+    ScaledLinear = "scaled_linear"
+    SquaredCosCapV2 = "squaredcos_cap_v2"
+
+    def __str__(self) -> str:
+        return self.value
+
+
+class PredictionType(str, _enum.Enum):
+    Epsilon = "epsilon"
+    VPrediction = "v_prediction"
+    Sample = "sample"
+
+    def __str__(self) -> str:
+        return self.value
+
+
+class TimestepSpacing(str, _enum.Enum):
+    Leading = "leading"
+    Trailing = "trailing"
+    Linspace = "linspace"
+
+    def __str__(self) -> str:
+        return self.value
+
+
+def _load_part(cls_model, cls_cfg, path: str, weight_names, hf: bool, dtype, device, pick=None):
+    import os
+
+    from ..serialize.state import load_safetensors
+
+    cfg_path = os.path.join(path, "config.json")
+    model = cls_model(_from_json(cls_cfg, cfg_path) if os.path.exists(cfg_path) else cls_cfg())
+    for n in weight_names:
+        p = os.path.join(path, n)
+        if os.path.exists(p):
+            sd = load_safetensors(p)
+            model.load_hf_state_dict(sd) if hf else model.load_state_dict(sd)
+            break
+    else:
+        raise FileNotFoundError("no %s under %s" % (" / ".join(weight_names), path))
+    model.to(device=device, dtype=dtype).eval()
+    return pick(model) if pick else model
+
+
+_W = ("diffusion_pytorch_model.safetensors", "model.safetensors")
+
+
+def load_clip_text_encoder(path: str, dtype=torch.float32, device="cpu") -> ClipTextEncoder:
+    """``path``: a directory with ``config.json`` and ``model.safetensors`` (a pipeline's ``text_encoder/``)."""
+    return _load_part(ClipTextEncoder, ClipTextConfig, path, ("model.safetensors",), True, dtype, device)
+
+
+def load_unet(path: str, dtype=torch.float32, device="cpu") -> UNet2DConditionModel:
+    return _load_part(UNet2DConditionModel, UNet2DConditionConfig, path, _W, False, dtype, device)
+
+
+def load_vae_decoder(path: str, dtype=torch.float32, device="cpu") -> Decoder:
+    return _load_part(AutoencoderKL, VaeConfig, path, _W, True, dtype, device, pick=lambda m: m.decoder)
+
+
+def load_vae_encoder(path: str, dtype=torch.float32, device="cpu") -> Encoder:
+    return _load_part(AutoencoderKL, VaeConfig, path, _W, True, dtype, device, pick=lambda m: m.encoder)

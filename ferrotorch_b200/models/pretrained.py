@@ -618,3 +618,42 @@ def load_ppo_policy(path: str, config: MlpPolicyConfig | None = None):
         config = MlpPolicyConfig(obs, hid, sd["action_net.weight"].shape[0])
     model = MlpPolicy(config).eval()
     return model, model.load_hf_state_dict(sd)
+
+
+# --------------------------------------------------------------------------- the reference's remaining names
+HfBertConfig, HfWhisperConfig = BertConfig, WhisperConfig     # the config classes read Hugging Face's config.json as is
+WhisperEncoderSelfAttention = _WhisperAttention
+N_MELS, N_FRAMES = 80, CHUNK_SECONDS * SAMPLE_RATE // HOP_LENGTH      # 80 mel bins, 3000 frames per 30 s chunk
+
+
+@dataclass
+class BertOutput:
+    last_hidden_state: torch.Tensor
+    pooler_output: torch.Tensor
+
+    @classmethod
+    def of(cls, model: BertModel, input_ids, attention_mask=None, token_type_ids=None) -> "BertOutput":
+        return cls(*model(input_ids, attention_mask, token_type_ids))
+
+
+class WhisperConvStem(nn.Module):
+    """The two GELU convolutions in front of the encoder (the second halves the frame rate), as a
+    module over an encoder's own weights."""
+
+    def __init__(self, encoder: WhisperEncoder):
+        super().__init__()
+        self.conv1, self.conv2 = encoder.conv1, encoder.conv2
+
+    def forward(self, mel: torch.Tensor) -> torch.Tensor:
+        return F.gelu(self.conv2(F.gelu(self.conv1(mel)))).transpose(1, 2)
+
+
+class ActionNet(nn.Linear):
+    """Policy head: latent -> action logits (``MlpPolicy.action_net``)."""
+
+
+class ValueHead(nn.Linear):
+    """Critic head: latent -> state value (``MlpPolicy.value_net``)."""
+
+    def __init__(self, in_features: int, out_features: int = 1, **kw):
+        super().__init__(in_features, out_features, **kw)

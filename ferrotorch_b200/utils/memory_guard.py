@@ -265,3 +265,50 @@ class MemoryGuardBuilder:
                 self._kw["reserve_bytes"] >= self._kw["budget_bytes"]:
             raise ValueError("MemoryGuardBuilder: the reservation must be smaller than the budget")
         return MemoryGuard(allocator, **self._kw)
+
+
+# --------------------------------------------------------------------------- small types of the reference's guard
+from dataclasses import dataclass as _dataclass  # noqa: E402
+from typing import Callable as _Callable  # noqa: E402
+
+MemoryHook = _Callable[[int], int]                  # bytes needed -> bytes freed
+MemoryPressureListener = _Callable[[float], None]   # called with the pressure ratio when it crosses the threshold
+
+
+@_dataclass
+class MemoryStats:
+    used_bytes: int
+    peak_bytes: int
+    budget_bytes: int
+    reserved_bytes: int
+    available_bytes: int
+    pressure: float
+    level: str
+
+    @classmethod
+    def of(cls, guard: MemoryGuard) -> "MemoryStats":
+        d = guard.memory_stats()
+        return cls(*[d[k] for k in ("used_bytes", "peak_bytes", "budget_bytes", "reserved_bytes", "available_bytes",
+                                    "pressure", "level")])
+
+
+class MemoryReservation:
+    """Headroom held back from the budget for the lifetime of the object (or the ``with`` block)."""
+
+    def __init__(self, guard: MemoryGuard, nbytes: int):
+        if nbytes < 0 or guard.reserve + nbytes >= guard.budget:
+            raise ValueError("MemoryReservation: %d bytes do not fit under the budget of %d" % (nbytes, guard.budget))
+        self.guard, self.nbytes, self._held = guard, int(nbytes), True
+        guard.reserve += self.nbytes
+
+    def release(self) -> None:
+        if self._held:
+            self.guard.reserve -= self.nbytes
+            self._held = False
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.release()
+        return False

@@ -423,3 +423,12 @@ def token_mask(grammar: JsonGrammar, generated: str, vocab: list[str], eos_id: i
 def apply_token_mask(logits: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
     """Set disallowed logits to -inf on the logits' device."""
     return logits.masked_fill(~mask.to(logits.device), float("-inf"))
+
+
+def __getattr__(name):
+    """``Tokenizer`` is the Hugging Face ``tokenizers`` class itself, imported on first use."""
+    if name == "Tokenizer":
+        from tokenizers import Tokenizer
+
+        return Tokenizer
+    raise AttributeError(name)

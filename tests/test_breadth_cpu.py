@@ -525,3 +525,39 @@ def test_optim_configs_and_data_reference_names():
     assert xs.shape == (2, 2) and ys.tolist() == [0, 1]
     assert list(D.WorkerInfo(1, 3).shard(10)) == [4, 5, 6] and D.WorkerInfo.current() is None and D.WorkerMode.CrossBatch
     assert len(list(D.MultiWorkerIter(ds, 2, 0))) == 3 and len(D.ConcatDataset([ds, ds])) == 10
+
+
+def test_gpu_crate_names_without_a_gpu():
+    from ferrotorch_b200 import cuda as C
+    from ferrotorch_b200.utils import memory_guard as MG
+
+    assert C.capture_status() is C.CaptureStatus.NotCapturing and str(C.CaptureMode.ThreadLocal) == "thread_local"
+    assert C.GpuTensor is torch.Tensor and C.MemoryWatchdog is MG.MemoryGuard and C.MemoryStats is MG.MemoryStats
+    alloc = C.CudaAllocator()
+    assert alloc.allocated_bytes() == 0 and alloc.round_len(1000) == 1024 and alloc.round_len(3 << 20) == 4 << 20
+    if not torch.cuda.is_available():
+        with pytest.raises(C.GpuError):
+            C.begin_capture()
+        with pytest.raises(C.GpuError):
+            C.init_cuda_backend()
+
+    class FakeAlloc:
+        used = 100
+
+        def total_bytes(self):
+            return 1000
+
+        def used_bytes(self):
+            return self.used
+
+        def empty_cache(self):
+            pass
+
+    g = MG.MemoryGuard(FakeAlloc(), budget_bytes=1000)
+    with MG.MemoryReservation(g, 400) as r:
+        assert g.available() == 500 and r.nbytes == 400
+        st = MG.MemoryStats.of(g)
+        assert (st.used_bytes, st.reserved_bytes, st.available_bytes, st.budget_bytes) == (100, 400, 500, 1000)
+    assert g.available() == 900
+    with pytest.raises(ValueError):
+        MG.MemoryReservation(g, 1000)

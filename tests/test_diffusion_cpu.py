@@ -190,3 +190,29 @@ def test_pipeline_directory_round_trip(tmp_path):
     (tmp_path / "sd" / "unet" / "diffusion_pytorch_model.safetensors").unlink()
     with pytest.raises(FileNotFoundError):
         D.load_stable_diffusion(str(tmp_path / "sd"))
+
+
+def test_reference_block_names_and_part_loaders(tmp_path):
+    import json
+    import os
+
+    from ferrotorch_b200.models import diffusion as D
+    from ferrotorch_b200.serialize.state import save_safetensors
+
+    assert D.CrossAttnDownBlock2D is D.DownBlock2D and D.VaeDecoder is D.Decoder and D.Attention is not None
+    assert str(D.PredictionType.VPrediction) == "v_prediction" and D.TimestepSpacing.Leading == "leading"
+    t = torch.tensor([0.0, 10.0])
+    torch.testing.assert_close(D.Timesteps(16)(t), D.timestep_embedding(t, 16))
+    cfg = D.VaeConfig(block_out_channels=(8, 16), layers_per_block=1, norm_num_groups=4, latent_channels=4)
+    vae = D.AutoencoderKL(cfg)
+    d = tmp_path / "vae"
+    os.makedirs(d)
+    with open(d / "config.json", "w") as f:
+        json.dump({"block_out_channels": [8, 16], "layers_per_block": 1, "norm_num_groups": 4, "latent_channels": 4}, f)
+    save_safetensors(vae.state_dict(), str(d / "diffusion_pytorch_model.safetensors"))
+    dec, enc = D.load_vae_decoder(str(d)), D.load_vae_encoder(str(d))
+    z = torch.randn(1, 4, 4, 4)
+    torch.testing.assert_close(dec(z), vae.eval().decoder(z))
+    assert isinstance(enc, D.VaeEncoder)
+    with pytest.raises(FileNotFoundError):
+        D.load_unet(str(tmp_path))

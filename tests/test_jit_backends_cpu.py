@@ -97,3 +97,27 @@ def test_generated_sources_compile_for_sm_100a():
     torch.testing.assert_close(B.reduce_reference(B.ReductionKind.Mean, x), x.mean(-1))
     src, cubin = B.compile_loop_ir_kernel(ch.loop_ir(), "loop_k")
     assert "loop_k" in src and len(cubin) > 500
+
+
+def test_remaining_reference_names():
+    fn, g, ins = _graph()
+    groups = B.FusionGroup.of(g)
+    assert groups and all(gr.kind is B.FusionGroupKind.Elementwise and gr.n_ops >= 2 for gr in groups)
+    assert B.estimate_matmul_dims([(4, 3, 8), (8, 5)]) == (12, 5, 8)
+    with pytest.raises(jit.JitError):
+        B.estimate_matmul_dims([(3, 8), (7, 5)])
+    net = nn.Sequential(nn.Linear(8, 4), nn.ReLU())
+    x = torch.randn(3, 8)
+    m = jit.compile(net, (x,))
+    cache = {}
+    r = B.autotune(m, (x,), cache=cache)
+    assert r.best.block_size == m.cfg.block_size and B.autotune(m, (x,), cache=cache) is r and r.key == B.AutotuneKey.of(m)
+    prog = B.export_with_dynamic_shapes(net, (x,), {0: {0: "batch"}})
+    assert prog.meta.input_specs[0].has_dynamic_dims() and prog.run(torch.randn(5, 8)).shape == (5, 4)
+    ch = B.FusedChain().push(B.FusedOp.Exp)
+    src = B.generate_reduction_rust(B.ReductionKind.Sum, ch, "r")
+    scope = {"torch": torch}
+    exec(src, scope)
+    t = torch.randn(3, 7)
+    torch.testing.assert_close(scope["r"](t), t.exp().sum(-1))
+    assert "__global__" in B.generate_reduction_ptx(B.ReductionKind.Max) and jit.AotCompiledModule is jit.AotModule

@@ -180,3 +180,23 @@ def test_loaders_read_model_directories_and_files(tmp_path):
     with pytest.raises(FileNotFoundError):
         (tmp_path / "none").mkdir()
         P.load_bert_model(str(tmp_path / "none"))
+
+
+def test_reference_names_of_small_models():
+    from ferrotorch_b200.models import pretrained as P
+    from ferrotorch_b200.utils import text
+
+    assert P.N_FRAMES == 3000 and P.N_MELS == 80 and P.HfBertConfig is P.BertConfig and text.Tokenizer.__name__ == "Tokenizer"
+    cfg = P.BertConfig(vocab_size=50, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32,
+                       max_position_embeddings=16)
+    m = P.BertModel(cfg).eval()
+    ids = torch.randint(0, 50, (2, 6))
+    out = P.BertOutput.of(m, ids)
+    assert out.last_hidden_state.shape == (2, 6, 16) and out.pooler_output.shape == (2, 16)
+    wc = P.WhisperConfig(num_mel_bins=8, d_model=16, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_dim=32,
+                         max_source_positions=10)
+    enc = P.WhisperEncoder(wc).eval()
+    stem = P.WhisperConvStem(enc)
+    mel = torch.randn(1, 8, 20)
+    assert stem(mel).shape == (1, 10, 16) and isinstance(enc.layers[0].self_attn, P.WhisperEncoderSelfAttention)
+    assert P.ValueHead(8).out_features == 1 and P.ActionNet(8, 3).out_features == 3
