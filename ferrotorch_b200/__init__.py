@@ -15,7 +15,12 @@ from . import autograd, core  # noqa: F401,E402
 
 _SUBMODULES = ("nn", "optim", "data", "train", "vision", "jit", "serialize", "parallel", "models", "profiler", "hub",
                "cuda", "distributions", "utils", "tensor_ops")
-__all__ = ["ops", "autograd", "core", "__version__", *_SUBMODULES]
+# module names of the reference's umbrella crate (ferrotorch/src/lib.rs:72-177) that live elsewhere here
+_ALIASES = {"gpu": "cuda", "distributed": "parallel", "llama": "models.llama_api", "ml": "utils.ml", "tokenize": "utils.text",
+            "grammar": "utils.grammar", "jit_script": "jit", "prelude": "prelude", "bert": "models.pretrained",
+            "whisper": "models.pretrained", "graph": "models.pretrained", "rl": "models.pretrained",
+            "diffusion": "models.diffusion"}
+__all__ = ["ops", "autograd", "core", "__version__", *_SUBMODULES, *_ALIASES]
 
 
 def __getattr__(name):
@@ -25,6 +30,10 @@ def __getattr__(name):
         import importlib
 
         return importlib.import_module("." + name, __name__)
+    if name in _ALIASES:
+        import importlib
+
+        return importlib.import_module("." + _ALIASES[name], __name__)
     if not name.startswith("_"):
         # the flat tensor API of the reference's core crate: its own spellings first, torch's second
         import importlib

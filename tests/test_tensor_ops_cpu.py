@@ -93,3 +93,19 @@ def test_fft_special_masked_dual_sparse():
         T.check_gradient_anomaly(d)
     nq = torch.nested.nested_tensor([torch.randn(2, 3, 4), torch.randn(2, 5, 4)])
     assert T.nested_scaled_dot_product_attention(nq, nq, nq).unbind()[1].shape == (2, 5, 4)
+
+
+def test_umbrella_aliases_and_prelude():
+    import importlib
+
+    ns = {}
+    exec("from ferrotorch_b200.prelude import *", ns)
+    for name in ("Linear", "Conv2d", "BatchNorm2d", "LayerNorm", "Dropout", "Module", "Parameter", "Sequential", "CrossEntropyLoss",
+                 "MSELoss", "GELU", "ReLU", "SiLU", "Sigmoid", "Softmax", "Tanh", "GRU", "LSTM", "Adam", "AdamW", "Optimizer",
+                 "Sgd", "zeros", "Tensor", "no_grad", "sum_dim", "Device"):
+        assert name in ns, name
+    assert ft.gpu is ft.cuda and ft.distributed is ft.parallel and ft.tokenize is importlib.import_module("ferrotorch_b200.utils.text")
+    assert ft.llama.LlamaConfig is ft.models.LlamaConfig and callable(ft.llama.generate) and ft.llama.GptqQ4 and ft.llama.masked_decode_loop
+    assert ft.llama.LlamaKvCache is ft.nn.KVCache and ft.grammar.JsonSchemaProcessor and ft.ml.accuracy_score
+    assert ft.bert.BertModel and ft.whisper.WhisperEncoder and ft.graph.GcnConv and ft.rl.MlpPolicy and ft.diffusion.DDIMScheduler
+    assert ft.jit_script.script is ft.jit.script
