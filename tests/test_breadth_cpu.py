@@ -561,3 +561,18 @@ def test_gpu_crate_names_without_a_gpu():
     assert g.available() == 900
     with pytest.raises(ValueError):
         MG.MemoryReservation(g, 1000)
+
+
+def test_bregman_kl_matches_closed_forms():
+    import ferrotorch_b200.distributions as D
+
+    pairs = [(D.Normal(torch.tensor([0.0, 1.0]), torch.tensor([1.0, 2.0])), D.Normal(torch.tensor([0.5, 0.0]), torch.tensor([1.5, 1.0]))),
+             (D.Gamma(torch.tensor(2.0), torch.tensor(3.0)), D.Gamma(torch.tensor(1.5), torch.tensor(1.0))),
+             (D.Bernoulli(torch.tensor([0.2, 0.7])), D.Bernoulli(torch.tensor([0.4, 0.6]))),
+             (D.Poisson(torch.tensor(3.0)), D.Poisson(torch.tensor(5.0))),
+             (D.Exponential(torch.tensor(2.0)), D.Exponential(torch.tensor(0.5)))]
+    for p, q in pairs:
+        torch.testing.assert_close(D.kl_expfamily_expfamily(p, q), D.kl_divergence(p, q), rtol=1e-5, atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        D.kl_expfamily_expfamily(pairs[0][0], pairs[1][0])
+    assert D.ExpRelaxedCategorical and D.DistConstraint is D.constraints.Constraint
