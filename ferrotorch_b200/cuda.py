@@ -354,8 +354,115 @@ class CudaAllocator:
         return round_len(nbytes)
 
 
+# --------------------------------------------------------------------------- typed launcher names (``gpu_<op>_<dtype>``)
+# The reference exports one launcher per op and dtype (ferrotorch-gpu/src/lib.rs: gpu_add,
+# gpu_relu_bf16, gpu_matmul_bf16_bf16_nt, gpu_topk_f32 ...).  Device tensors carry their dtype here,
+# so one function per op serves every suffix; ops that have a kernel of this framework go to it.
+def _gpu_op_table() -> dict:
+    F = torch.nn.functional
+
+    def native(name):
+        def call(*a, **kw):
+            from .ops import functional as ops_f
+
+            return getattr(ops_f, name)(*a, **kw)
+        return call
+
+    return {
+        "add": torch.add, "sub": torch.sub, "mul": torch.mul, "neg": torch.neg, "relu": torch.relu, "gelu": F.gelu,
+        "silu": F.silu, "softmax": lambda x, dim=-1: torch.softmax(x, dim), "dropout": F.dropout,
+        "scale": lambda x, s: x * s, "add_scaled": lambda a, b, s: torch.add(a, b, alpha=s),
+        "broadcast_add": torch.add, "broadcast_sub": torch.sub, "broadcast_mul": torch.mul,
+        "div_rounding": lambda a, b, mode=None: torch.div(a, b, rounding_mode=mode), "broadcast_div_rounding":
+        lambda a, b, mode=None: torch.div(a, b, rounding_mode=mode),
+        "matmul": torch.matmul, "matmul_nt": lambda a, b: a @ b.transpose(-1, -2), "bmm": torch.bmm, "small_matmul": torch.matmul,
+        "small_bmm": torch.bmm, "matmul_bf16_bf16": torch.matmul, "matmul_bf16_bf16_nt": native("gemm_nt"),
+        "matmul_bf16_bf16_strided_batched": torch.bmm, "matmul_f16_f16_strided_batched": torch.bmm,
+        "matmul_bf16_bf16_strided_batched_nt": lambda a, b: torch.bmm(a, b.transpose(1, 2)),
+        "broadcast_bmm_bf16_bf16": torch.matmul, "broadcast_bmm_f16_f16": torch.matmul,
+        "layernorm": lambda x, w, b, eps=1e-5: F.layer_norm(x, x.shape[-1:], w, b, eps), "rmsnorm": native("rmsnorm"),
+        "group_norm": lambda x, g, w=None, b=None, eps=1e-5: F.group_norm(x, g, w, b, eps),
+        "local_response_norm": F.local_response_norm, "rope_half": native("rope_"), "fatrelu": lambda x, t: torch.where(x > t, x, torch.zeros_like(x)),
+        "embed_lookup": lambda w, ids: F.embedding(ids, w), "embedding_gather": lambda w, ids: F.embedding(ids, w),
+        "embedding_gather_bf16_to": lambda w, ids: F.embedding(ids, w).float(),
+        "transpose_2d": lambda x: x.t().contiguous(), "permute_0213": lambda x: x.permute(0, 2, 1, 3).contiguous(),
+        "transpose_to_heads": lambda x, h: x.reshape(x.shape[0], h, -1).transpose(0, 1).contiguous(),
+        "transpose_from_heads": lambda x: x.transpose(0, 1).reshape(x.shape[1], -1).contiguous(),
+        "repeat_kv": lambda x, n, dim=0: x.repeat_interleave(n, dim), "repeat_interleave": torch.repeat_interleave,
+        "causal_mask": lambda s: s.masked_fill(torch.ones(s.shape[-2:], dtype=torch.bool, device=s.device).triu(1 + s.shape[-1] - s.shape[-2]), float("-inf")),
+        "flash_attention": lambda q, k, v, causal=False: F.scaled_dot_product_attention(q, k, v, is_causal=causal),
+        "conv2d": F.conv2d, "nearest_upsample2x": lambda x: F.interpolate(x, scale_factor=2, mode="nearest"),
+        "flip": torch.flip, "roll": torch.roll, "histc": torch.histc, "searchsorted": torch.searchsorted,
+        "topk": lambda x, k, largest=True: tuple(torch.topk(x, k, -1, largest)), "topk_nd": lambda x, k, dim=-1, largest=True: tuple(torch.topk(x, k, dim, largest)),
+        "unique": torch.unique, "unique_consecutive": torch.unique_consecutive, "meshgrid": lambda *t: torch.meshgrid(*t, indexing="ij"),
+        "gather_dim": lambda x, dim, idx: torch.gather(x, dim, idx), "scatter_dim": lambda x, dim, idx, src: x.scatter(dim, idx, src),
+        "scatter_value_dim": lambda x, dim, idx, v: x.scatter(dim, idx, v), "scatter_add_dim": lambda x, dim, idx, src: x.scatter_add(dim, idx, src),
+        "scatter_nd": lambda x, idx, src: x.index_put(tuple(idx.t()), src),
+        "scatter_add_nd": lambda x, idx, src: x.index_put(tuple(idx.t()), src, accumulate=True),
+        "scatter_value_nd": lambda x, idx, v: x.index_put(tuple(idx.t()), torch.as_tensor(v, dtype=x.dtype, device=x.device)),
+        "scatter_add_segments": lambda src, index, dim_size: torch.zeros((dim_size,) + tuple(src.shape[1:]), dtype=src.dtype,
+                                                                         device=src.device).index_add_(0, index, src),
+        "repeat_interleave_backward": lambda g, n, dim=0: g.unflatten(dim, (-1, n)).sum(dim + 1),
+        "broadcast_bool": torch.broadcast_to,
+        "slice_read": lambda x, start, n, dim=0: x.narrow(dim, start, n).contiguous(),
+        "slice_write": lambda dst, src, start, dim=0: dst.narrow(dim, start, src.shape[dim]).copy_(src),
+        "block_reduce_max_abs": lambda x: x.abs().max(), "airy_ai": torch.special.airy_ai, "entr": torch.special.entr,
+        "ndtr": torch.special.ndtr, "ndtri": torch.special.ndtri, "zeta": torch.special.zeta,
+        "spherical_bessel_j0": torch.special.spherical_bessel_j0, "chebyshev_poly": torch.special.chebyshev_polynomial_t,
+        "hermite_h_poly": torch.special.hermite_polynomial_h, "hermite_he_poly": torch.special.hermite_polynomial_he,
+        "laguerre_poly": torch.special.laguerre_polynomial_l, "legendre_poly": torch.special.legendre_polynomial_p,
+    }
+
+
+_GPU_OPS: dict | None = None
+_DTYPE_SUFFIX = {"f32": torch.float32, "f64": torch.float64, "bf16": torch.bfloat16, "f16": torch.float16}
+
+
+def _resolve_gpu_op(name: str):
+    """``gpu_<op>[_<dtype>][_into]`` -> callable; with a dtype suffix the first tensor argument is checked."""
+    global _GPU_OPS
+    if _GPU_OPS is None:
+        _GPU_OPS = _gpu_op_table()
+    base = name[4:]
+    into = base.endswith("_into") or base.endswith("_into_on_stream")
+    base = base.replace("_into_on_stream", "").replace("_into", "")
+    want = None
+    if base not in _GPU_OPS:
+        for suf, dt in _DTYPE_SUFFIX.items():
+            parts = base.split("_")
+            if suf in parts:                                      # suffix (relu_bf16) or infix (matmul_f32_nt)
+                parts.remove(suf)
+                if "_".join(parts) in _GPU_OPS:
+                    base, want = "_".join(parts), dt
+                    break
+        else:
+            if base.endswith("_u16") and base[:-4] in _GPU_OPS:      # 16-bit payloads moved without arithmetic
+                base = base[:-4]
+            else:
+                return None
+    fn = _GPU_OPS[base]
+
+    def call(*args, **kw):
+        first = next((a for a in args if isinstance(a, torch.Tensor) and a.is_floating_point()), None)
+        if want is not None and first is not None and first.dtype != want:
+            raise GpuError("%s: expected %s tensors, got %s" % (name, want, first.dtype))
+        if into:                                                  # trailing argument is the destination
+            *ins, out = args
+            out.copy_(fn(*ins, **kw))
+            return out
+        return fn(*args, **kw)
+
+    call.__name__ = name
+    return call
+
+
 def __getattr__(name):
-    """Memory-guard types are defined in ``utils.memory_guard``."""
+    """Typed launcher names resolve through the table above; memory-guard types are defined in
+    ``utils.memory_guard``."""
+    if name.startswith("gpu_") and name not in ("gpu_to_cpu",):
+        fn = _resolve_gpu_op(name)
+        if fn is not None:
+            return fn
     table = {"MemoryGuardedDevice": "MemoryGuard", "MemoryWatchdog": "MemoryGuard", "MemoryStats": "MemoryStats",
              "MemoryReservation": "MemoryReservation", "MemoryHook": "MemoryHook",
              "MemoryPressureListener": "MemoryPressureListener", "MemoryGuard": "MemoryGuard",

@@ -576,3 +576,27 @@ def test_bregman_kl_matches_closed_forms():
     with pytest.raises(NotImplementedError):
         D.kl_expfamily_expfamily(pairs[0][0], pairs[1][0])
     assert D.ExpRelaxedCategorical and D.DistConstraint is D.constraints.Constraint
+
+
+def test_typed_launcher_names_resolve():
+    from ferrotorch_b200 import cuda as C
+
+    a, b = torch.randn(3, 4), torch.randn(3, 4)
+    assert torch.equal(C.gpu_add(a, b), a + b) and torch.equal(C.gpu_relu_bf16(a.bfloat16()), a.bfloat16().relu())
+    out = torch.empty(3, 4)
+    assert C.gpu_mul_into(a, b, out) is out and torch.equal(out, a * b)
+    with pytest.raises(C.GpuError):
+        C.gpu_relu_bf16(a)                                       # the suffix names the dtype the call expects
+    torch.testing.assert_close(C.gpu_matmul_f32_nt(a, b), a @ b.t())
+    v, i = C.gpu_topk_f32(a, 2)
+    assert torch.equal(v, a.topk(2).values)
+    g = torch.arange(6.0)
+    assert torch.equal(C.gpu_repeat_interleave_backward_f32(g, 2), torch.tensor([1.0, 5.0, 9.0]))
+    x = torch.zeros(2, 3)
+    idx = torch.tensor([[0, 1], [1, 2], [0, 1]])
+    assert C.gpu_scatter_add_nd_f32(x, idx, torch.ones(3))[0, 1] == 2.0
+    assert torch.equal(C.gpu_scatter_add_segments_f32(torch.ones(4, 2), torch.tensor([0, 0, 1, 0]), 2), torch.tensor([[3.0, 3.0], [1.0, 1.0]]))
+    s = C.gpu_causal_mask_bf16(torch.zeros(3, 3, dtype=torch.bfloat16))
+    assert s[0, 1] == float("-inf") and s[2, 0] == 0
+    with pytest.raises(AttributeError):
+        C.gpu_no_such_op
