@@ -31,7 +31,7 @@ from . import functional as F
 
 _i, _vp = _native._i, _native._vp
 _native.register_protos({
-    "ft_conv2d_fprop_nhwc": (_i, [_vp] * 5 + [_i] * 14 + [_vp]),
+    "ft_conv2d_fprop_nhwc": (_i, [_vp] * 5 + [_i] * 13 + [_vp]),
 })
 
 _enabled = os.environ.get("FT_CONV_IGEMM") == "1"

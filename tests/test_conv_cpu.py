@@ -52,3 +52,18 @@ def test_fallback_module_and_rewrite():
     fused = net[0](x, residual=res, relu=True)
     torch.testing.assert_close(fused, torch.relu(tF.conv2d(x, net[0].weight, net[0].bias, 1, 1) + res))
     assert C.out_size(224, 7, 2, 3, 1) == 112 and C.out_size(56, 3, 1, 1, 1) == 56
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the failure mode of a box without a GPU")
+def test_binding_marshals_arguments_and_fails_with_the_library_error(monkeypatch):
+    from ferrotorch_b200 import _native
+    from ferrotorch_b200.ops import functional as F
+
+    if _native.kernels(required=False) is None:
+        pytest.skip("kernel library not built")
+    monkeypatch.setattr(F, "_dev", lambda t: 0)
+    monkeypatch.setattr(F, "_stream", lambda: None)
+    x = torch.randn(1, 64, 8, 8).bfloat16().contiguous(memory_format=torch.channels_last)
+    w = torch.randn(8, 64, 3, 3).bfloat16()
+    with pytest.raises(_native.NativeError, match="ft_conv2d_fprop_nhwc"):    # reached the C entry point: no ctypes TypeError
+        C._fprop(x, w, None, None, 1, (1, 1), 1, False)
