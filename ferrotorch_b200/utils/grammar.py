@@ -560,6 +560,14 @@ def unpack_mask(packed: torch.Tensor, vocab: int) -> torch.Tensor:
     return bits.flatten(-2)[..., :vocab].bool()
 
 
+def _register_token_mask_proto() -> None:
+    from .. import _native
+
+    _native.register_protos({"ft_apply_token_mask": (_native._i, [_native._vp, _native._vp, _native._ll, _native._ll,
+                                                                   _native._ll, _native._i, _native._i, _native._i,
+                                                                   _native._vp])})
+
+
 def apply_packed_mask_(logits: torch.Tensor, packed: torch.Tensor) -> torch.Tensor:
     """Set ``logits[b, v] = -inf`` wherever bit v of ``packed[b]`` (or of ``packed[0]`` when it has
     one row) is clear, in place.  ``logits [rows, V]`` bf16 / fp32 with unit inner stride.  On a GPU
@@ -571,9 +579,7 @@ def apply_packed_mask_(logits: torch.Tensor, packed: torch.Tensor) -> torch.Tens
     if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(1) == 1:
         from .. import _native
 
-        _native.register_protos({"ft_apply_token_mask": (_native._i, [_native._vp, _native._vp, _native._ll, _native._ll,
-                                                                       _native._ll, _native._i, _native._i, _native._i,
-                                                                       _native._vp])})
+        _register_token_mask_proto()
         m = packed.to(device=logits.device, dtype=torch.int32, non_blocking=True).contiguous()
         rc = _native.kernels().ft_apply_token_mask(logits.data_ptr(), m.data_ptr(), logits.shape[0], logits.shape[1],
                                                    logits.stride(0), m.shape[0], int(logits.dtype == torch.float32),
