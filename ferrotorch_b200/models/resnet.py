@@ -144,3 +144,73 @@ def create_model(name: str, **kw) -> nn.Module:
         return tvm.get_model(name, weights=None, **kw)
     except Exception as e:  # noqa: BLE001
         raise KeyError("unknown model %r (registered: %s)" % (name, list_models())) from e
+
+
+# --------------------------------------------------------------------------- inference: batch norm folded into the convolutions
+def fold_conv_bn(conv: nn.Conv2d, bn: nn.BatchNorm2d):
+    """``(weight, bias)`` of the convolution that computes ``bn(conv(x))`` with the norm's running
+    statistics: ``w' = w * g / sqrt(var + eps)`` per output channel, ``b' = beta + (b - mean) * g / sqrt(var + eps)``."""
+    scale = (bn.weight if bn.weight is not None else torch.ones_like(bn.running_var)).float() / torch.sqrt(bn.running_var.float() + bn.eps)
+    w = conv.weight.float() * scale.view(-1, 1, 1, 1)
+    b0 = conv.bias.float() if conv.bias is not None else torch.zeros_like(bn.running_mean).float()
+    b = (bn.bias.float() if bn.bias is not None else 0.0) + (b0 - bn.running_mean.float()) * scale
+    return w.to(conv.weight.dtype), b.to(conv.weight.dtype)
+
+
+class _FoldedConv(nn.Module):
+    """A convolution with its batch norm folded in; ``forward(x, residual, relu)`` is one call of
+    ``ops.conv.conv2d`` (the implicit-GEMM kernel with bias / residual / ReLU in its epilogue when
+    that kernel is switched on and takes the shape; ``torch.nn.functional.conv2d`` otherwise)."""
+
+    def __init__(self, conv: nn.Conv2d, bn: nn.BatchNorm2d):
+        super().__init__()
+        w, b = fold_conv_bn(conv, bn)
+        self.weight = nn.Parameter(w.contiguous(memory_format=torch.channels_last), requires_grad=False)
+        self.bias = nn.Parameter(b, requires_grad=False)
+        self.stride, self.padding, self.dilation, self.groups = conv.stride, conv.padding, conv.dilation, conv.groups
+
+    def forward(self, x, residual=None, relu: bool = False):
+        from ..ops.conv import conv2d
+
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups, residual, relu)
+
+
+class _FusedBlock(nn.Module):
+    def __init__(self, block):
+        super().__init__()
+        names = ("conv1", "conv2", "conv3") if isinstance(block, Bottleneck) else ("conv1", "conv2")
+        self.convs = nn.ModuleList(_FoldedConv(getattr(block, n), getattr(block, n.replace("conv", "bn"))) for n in names)
+        d = block.downsample
+        self.down = _FoldedConv(d[0], d[1]) if d is not None else None
+
+    def forward(self, x):
+        idt = x if self.down is None else self.down(x)
+        out = x
+        for c in self.convs[:-1]:
+            out = c(out, relu=True)
+        return self.convs[-1](out, residual=idt, relu=True)
+
+
+class FusedInferenceResNet(nn.Module):
+    """A trained :class:`ResNet` rewritten for inference: every batch norm is folded into the
+    convolution in front of it, so a block is two or three convolution calls whose epilogues add
+    the bias, the shortcut and apply the ReLU -- no separate normalisation, add or activation pass
+    over the activations.  Weights are copies: the source model is left as it was."""
+
+    def __init__(self, model: ResNet):
+        super().__init__()
+        if model.training:
+            raise ValueError("FusedInferenceResNet: call model.eval() first (folding uses the running statistics)")
+        self.stem = _FoldedConv(model.conv1, model.bn1)
+        self.maxpool, self.avgpool, self.fc = model.maxpool, model.avgpool, model.fc
+        self.blocks = nn.Sequential(*[_FusedBlock(b) for layer in (model.layer1, model.layer2, model.layer3, model.layer4)
+                                      for b in layer])
+
+    @torch.no_grad()
+    def forward(self, x):
+        x = self.blocks(self.maxpool(self.stem(x, relu=True)))
+        return self.fc(torch.flatten(self.avgpool(x), 1))
+
+
+def fuse_for_inference(model: ResNet) -> FusedInferenceResNet:
+    return FusedInferenceResNet(model)

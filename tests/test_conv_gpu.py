@@ -50,3 +50,22 @@ def test_backward_matches_torch():
         C.use_native_conv(prev)
     torch.testing.assert_close(xn.grad.float(), xr.grad, rtol=5e-2, atol=5e-2 * float(xr.grad.abs().max()))
     torch.testing.assert_close(wn.grad.float(), wr.grad, rtol=5e-2, atol=5e-2 * float(wr.grad.abs().max()))
+
+
+def test_folded_resnet_on_the_kernel_matches_eval_model():
+    from ferrotorch_b200.models import resnet as R
+    from ferrotorch_b200.ops import conv as C
+
+    torch.manual_seed(2)
+    m = R.resnet50(num_classes=10).cuda().bfloat16().to(memory_format=torch.channels_last).eval()
+    x = torch.randn(4, 3, 64, 64, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    fused = R.fuse_for_inference(m).cuda()
+    with torch.no_grad():
+        ref = m(x).float()
+        prev = C.use_native_conv(True)
+        try:
+            out = fused(x).float()
+        finally:
+            C.use_native_conv(prev)
+    assert torch.isfinite(out).all()
+    torch.testing.assert_close(out, ref, rtol=0.1, atol=0.1 * float(ref.abs().max()))

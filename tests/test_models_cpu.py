@@ -166,3 +166,32 @@ def test_generation_primitives_and_loader_aliases():
     dense = Q.hqq_state_dict_to_dense({"l.W_q": wq, "l.scale": scale, "l.zero": zero, "l.shape": torch.tensor([8, 64]),
                                        "norm.weight": torch.ones(3)})
     assert set(dense) == {"l.weight", "norm.weight"} and (dense["l.weight"] - w).abs().max() < 0.5
+
+
+def test_resnet_folded_for_inference_matches_eval_model():
+    from ferrotorch_b200.models import resnet as R
+
+    torch.manual_seed(0)
+    for ctor in (R.resnet18, R.resnet50):
+        m = ctor(num_classes=7)
+        for mod in m.modules():                                  # non-trivial running statistics and affine terms
+            if isinstance(mod, torch.nn.BatchNorm2d):
+                mod.running_mean.normal_(0, 0.1)
+                mod.running_var.uniform_(0.5, 1.5)
+                mod.weight.data.uniform_(0.5, 1.5)
+                mod.bias.data.normal_(0, 0.1)
+        with pytest.raises(ValueError):
+            R.fuse_for_inference(m)
+        m.eval()
+        fused = R.fuse_for_inference(m)
+        x = torch.randn(2, 3, 64, 64)
+        with torch.no_grad():
+            ref = m(x)
+        torch.testing.assert_close(fused(x), ref, rtol=1e-3, atol=1e-3)
+        assert not any(isinstance(mod, torch.nn.BatchNorm2d) for mod in fused.modules())
+    conv, bn = torch.nn.Conv2d(4, 6, 3, bias=True), torch.nn.BatchNorm2d(6).eval()
+    bn.running_mean.normal_()
+    bn.running_var.uniform_(0.5, 2.0)
+    w, b = R.fold_conv_bn(conv, bn)
+    xx = torch.randn(1, 4, 5, 5)
+    torch.testing.assert_close(torch.nn.functional.conv2d(xx, w, b), bn(conv(xx)), rtol=1e-4, atol=1e-5)
