@@ -15,6 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("ddp_over_tcp.py", []),
     ("constrained_json.py", []),
     ("tiny_text_to_image.py", ["--steps", "3", "--size", "32"]),
+    ("coming_from_ferrotorch.py", []),
 ])
 def test_example_runs(script, args):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
