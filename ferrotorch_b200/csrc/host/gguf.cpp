@@ -11,6 +11,7 @@
 // consecutive elements 2j and 2j + 1 and take high bits 2j and 2j + 1 (gguf.rs:543-577, 614-660;
 // ferrotorch-cubecl/src/quant.rs:348).  `interleaved = 1` selects that order for callers that need
 // bit-for-bit agreement with tensors the reference decoded.
+#include "../gguf_blocks.h"
 #include <fcntl.h>
 #include <stdint.h>
 #include <string.h>
@@ -269,6 +270,17 @@ FTG_API int ftg_dequantize(unsigned type, const void* src_, float* dst, long lon
         break;
     }
   }
+  return 0;
+}
+
+// The quantised block types decoded pair by pair through the header the device kernel includes
+// (csrc/gguf_dequant.cu): running this on the host checks the device arithmetic without a device.
+FTG_API int ftg_dequantize_pairwise(unsigned type, const void* src_, float* dst, long long n) {
+  const int bb = gguf_block_bytes(type);
+  if (bb == 0 || n % 32) return -1;
+  const uint8_t* src = static_cast<const uint8_t*>(src_);
+  for (long long b = 0; b < n / 32; ++b)
+    for (int i = 0; i < 16; ++i) gguf_decode_pair(type, src + b * bb, i, dst[b * 32 + i], dst[b * 32 + i + 16]);
   return 0;
 }
 

@@ -48,6 +48,7 @@ def _lib():
         lib.ftg_split_q4_0.argtypes = [vp, ll, ll, vp, vp]
         lib.ftg_dequantize_ex.argtypes = [ctypes.c_uint, vp, vp, ll, ctypes.c_int]
         lib.ftg_repack_nibbles.argtypes = [ctypes.c_uint, vp, ll, ctypes.c_int]
+        lib.ftg_dequantize_pairwise.argtypes = [ctypes.c_uint, vp, vp, ll]
         _ready = True
     return lib
 
@@ -323,3 +324,51 @@ def dequantize_gguf_tensor(f: GgufFile, name: str, dtype=torch.float32, nibble_o
 
 def load_gguf_state_dict_mmap(path: str, dtype=torch.bfloat16, remap: bool = True, **kw) -> dict:
     return load_gguf_state_dict(path, dtype, remap, **kw)
+
+
+# --------------------------------------------------------------------------- device-side dequantisation
+_QUANT_TYPES = (GGML_Q4_0, GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q8_0, GGML_Q8_1)
+
+
+def dequantize_pairwise_host(raw: torch.Tensor, ggml_type: int, n: int) -> torch.Tensor:
+    """The device kernel's decoder (``csrc/gguf_blocks.h``) run on the host: fp32 ``[n]``."""
+    out = torch.empty(n, dtype=torch.float32)
+    raw = raw.contiguous()
+    if _lib().ftg_dequantize_pairwise(int(ggml_type), raw.data_ptr(), out.data_ptr(), n) != 0:
+        raise ValueError("dequantize_pairwise_host: type %d is not a 32-element quantised block type" % ggml_type)
+    return out
+
+
+def dequantize_on_device(raw: torch.Tensor, ggml_type: int, shape, dtype=torch.bfloat16) -> torch.Tensor:
+    """Expand raw blocks (uint8, on a CUDA device) to ``dtype`` (bf16 or fp32) on that device with
+    ``ft_gguf_dequantize`` -- the quantised bytes are what crosses PCIe, not the expanded tensor."""
+    if ggml_type not in _QUANT_TYPES or dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("dequantize_on_device: quantised block types to bf16 / fp32 only")
+    n = 1
+    for d in shape:
+        n *= int(d)
+    be, bb = _BLOCK[ggml_type]
+    if not raw.is_cuda or raw.dtype != torch.uint8 or n % be or raw.numel() != n // be * bb:
+        raise ValueError("dequantize_on_device: need %d bytes of uint8 on a CUDA device for shape %s" % (n // be * bb, tuple(shape)))
+    _native.register_protos({"ft_gguf_dequantize": (_native._i, [_native._vp, _native._vp, _native._ll, _native._i, _native._i,
+                                                                  _native._i, _native._vp])})
+    raw = raw.contiguous()
+    out = torch.empty(n, dtype=dtype, device=raw.device)
+    rc = _native.kernels().ft_gguf_dequantize(raw.data_ptr(), out.data_ptr(), n // be, int(ggml_type), int(dtype == torch.float32),
+                                              raw.device.index or 0, torch.cuda.current_stream().cuda_stream)
+    _native.check(rc, "ft_gguf_dequantize")
+    return out.view(tuple(shape))
+
+
+def load_gguf_state_dict_gpu(path: str, device="cuda", dtype=torch.bfloat16, remap: bool = True) -> dict:
+    """Read a GGUF file with the quantised tensors expanded on the device (the reference's
+    ``from_gguf_gpu_dequant``, ferrotorch-llama/src/gpu_gguf.rs:336): raw blocks are uploaded and
+    dequantised there; F32 / F16 / BF16 tensors are converted with torch."""
+    out = {}
+    with GgufFile(path) as f:
+        for name, (t, shape, _) in f.tensors.items():
+            if t in _QUANT_TYPES:
+                out[name] = dequantize_on_device(f.raw(name).to(device, non_blocking=True), t, shape, dtype)
+            else:
+                out[name] = f.dequantize(name, torch.float32).to(device=device, dtype=dtype)
+    return gguf_to_hf_state_dict(out) if remap else out

@@ -310,3 +310,31 @@ def test_gguf_and_checkpoint_reference_names(tmp_path):
     back = S.TrainingCheckpoint.load(str(tmp_path / "c.ftck"))
     assert back.epoch == 3 and back.step == 40 and back.extra == {"note": "x"} and torch.equal(back.model_state["w"], w)
     assert back.optimizer_state["param_groups"][0]["lr"] == 0.1
+
+
+def test_shared_block_decoder_equals_the_host_reader_for_every_quantised_type():
+    """``gguf_blocks.h`` is what the device kernel compiles; run on the host it must reproduce the
+    reader's dequantisation bit for bit (random bytes cover every nibble / high-bit / sign case)."""
+    from ferrotorch_b200.serialize import gguf as G
+
+    g = torch.Generator().manual_seed(0)
+    for t in (G.GGML_Q4_0, G.GGML_Q4_1, G.GGML_Q5_0, G.GGML_Q5_1, G.GGML_Q8_0, G.GGML_Q8_1):
+        be, bb = G._BLOCK[t]
+        nblk = 64
+        raw = torch.randint(0, 256, (nblk, bb), dtype=torch.uint8, generator=g)
+        # finite fp16 scales / minima: rewrite the fp16 fields with values drawn from a normal range
+        scale = (torch.rand(nblk, generator=g) * 0.1 + 1e-3).to(torch.float16).view(torch.uint8).view(nblk, 2)
+        raw[:, 0:2] = scale
+        if t in (G.GGML_Q4_1, G.GGML_Q5_1, G.GGML_Q8_1):
+            raw[:, 2:4] = (torch.randn(nblk, generator=g) * 0.5).to(torch.float16).view(torch.uint8).view(nblk, 2)
+        ref = G.dequantize_blocks(raw.reshape(-1), t, nblk * be)
+        got = G.dequantize_pairwise_host(raw.reshape(-1), t, nblk * be)
+        assert torch.equal(got, ref.reshape(-1)), "type %d" % t
+    sub = torch.tensor([1, 0], dtype=torch.uint8)                     # fp16 subnormal 2^-24 as a scale
+    blk = torch.cat([sub, torch.full((16,), 0x9F, dtype=torch.uint8)])
+    v = G.dequantize_pairwise_host(blk, G.GGML_Q4_0, 32)
+    assert v[0].item() == 7 * 2.0 ** -24 and v[16].item() == 1 * 2.0 ** -24
+    with pytest.raises(ValueError):
+        G.dequantize_pairwise_host(blk, G.GGML_F16, 32)
+    with pytest.raises(ValueError):
+        G.dequantize_on_device(blk, G.GGML_Q4_0, (32,))               # a host tensor is refused before any launch
