@@ -328,6 +328,8 @@ def load_gguf_state_dict_mmap(path: str, dtype=torch.bfloat16, remap: bool = Tru
 
 # --------------------------------------------------------------------------- device-side dequantisation
 _QUANT_TYPES = (GGML_Q4_0, GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q8_0, GGML_Q8_1)
+_native.register_protos({"ft_gguf_dequantize": (_native._i, [_native._vp, _native._vp, _native._ll, _native._i, _native._i,
+                                                              _native._i, _native._vp])})
 
 
 def dequantize_pairwise_host(raw: torch.Tensor, ggml_type: int, n: int) -> torch.Tensor:
@@ -350,8 +352,6 @@ def dequantize_on_device(raw: torch.Tensor, ggml_type: int, shape, dtype=torch.b
     be, bb = _BLOCK[ggml_type]
     if not raw.is_cuda or raw.dtype != torch.uint8 or n % be or raw.numel() != n // be * bb:
         raise ValueError("dequantize_on_device: need %d bytes of uint8 on a CUDA device for shape %s" % (n // be * bb, tuple(shape)))
-    _native.register_protos({"ft_gguf_dequantize": (_native._i, [_native._vp, _native._vp, _native._ll, _native._i, _native._i,
-                                                                  _native._i, _native._vp])})
     raw = raw.contiguous()
     out = torch.empty(n, dtype=dtype, device=raw.device)
     rc = _native.kernels().ft_gguf_dequantize(raw.data_ptr(), out.data_ptr(), n // be, int(ggml_type), int(dtype == torch.float32),
