@@ -41,6 +41,26 @@ struct ConvParams {
   int* status;
 };
 
+// Index arithmetic of the gather, shared by the kernel and by a host entry point that the CPU
+// tests call: row m of the implicit matrix -> image n and the top-left input coordinate of its window.
+__host__ __device__ __forceinline__ void conv_row_origin(const ConvParams& p, int m, int& n, int& hi0, int& wi0) {
+  const int wo = m % p.Wo, ho = (m / p.Wo) % p.Ho;
+  n = m / (p.Wo * p.Ho);
+  hi0 = ho * p.stride - p.pad_h;
+  wi0 = wo * p.stride - p.pad_w;
+}
+
+// Element offset into x of the 64 channels that k-block kb contributes to a row with the given
+// origin, or -1 when the filter tap falls into the padding (the row is zero there).
+__host__ __device__ __forceinline__ long long conv_tap_offset(const ConvParams& p, int n, int hi0, int wi0, int kb) {
+  const int c_blocks = p.Cin / CV_BK;
+  const int tap = kb / c_blocks, c0 = (kb - tap * c_blocks) * CV_BK;
+  const int kh = tap / p.KW, kw = tap - kh * p.KW;
+  const int hi = hi0 + kh * p.dil, wi = wi0 + kw * p.dil;
+  if (hi < 0 || hi >= p.H || wi < 0 || wi >= p.W) return -1;
+  return ((static_cast<long long>(n) * p.H + hi) * p.W + wi) * p.Cin + c0;
+}
+
 __global__ void __launch_bounds__(CV_THREADS, 1)
 conv2d_fprop_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -56,7 +76,6 @@ conv2d_fprop_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * CV_STAGES + 2 + a); };
   const int m_blocks = (p.M + CV_BM - 1) / CV_BM, n_blocks = (p.Cout + CV_BN - 1) / CV_BN;
   const int num_tiles = m_blocks * n_blocks, k_blocks = p.K / CV_BK;
-  const int c_blocks = p.Cin / CV_BK;   // k-blocks per filter tap
   // n fastest: the CTAs that run together read the same pixels (through L2) against different
   // filter tiles; the whole filter is small enough to stay in L2 anyway
   auto coords = [&](int t, int& mb, int& nb) { nb = t % n_blocks; mb = t / n_blocks; };
@@ -125,18 +144,14 @@ conv2d_fprop_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
       int mb, nb; coords(tile, mb, nb);
       const int m = mb * CV_BM + r;
       const bool row_ok = m < p.M;
-      const int mm = row_ok ? m : 0;
-      const int wo = mm % p.Wo, ho = (mm / p.Wo) % p.Ho, n = mm / (p.Wo * p.Ho);
-      const int hi0 = ho * p.stride - p.pad_h, wi0 = wo * p.stride - p.pad_w;
-      const __nv_bfloat16* xn = p.x + static_cast<long long>(n) * p.H * p.W * p.Cin + h * 32;
+      int n, hi0, wi0;
+      conv_row_origin(p, row_ok ? m : 0, n, hi0, wi0);
       auto fetch = [&](int kb, Row& row) {
         row.v[0] = row.v[1] = row.v[2] = row.v[3] = make_uint4(0, 0, 0, 0);
         if (!row_ok || kb >= k_blocks) return;
-        const int tap = kb / c_blocks, c0 = (kb - tap * c_blocks) * CV_BK;
-        const int kh = tap / p.KW, kw = tap - kh * p.KW;
-        const int hi = hi0 + kh * p.dil, wi = wi0 + kw * p.dil;
-        if (hi < 0 || hi >= p.H || wi < 0 || wi >= p.W) return;   // padding: the row stays zero
-        const uint4* src = reinterpret_cast<const uint4*>(xn + (static_cast<long long>(hi) * p.W + wi) * p.Cin + c0);
+        const long long off = conv_tap_offset(p, n, hi0, wi0, kb);
+        if (off < 0) return;                                      // padding: the row stays zero
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + off + h * 32);
 #pragma unroll
         for (int u = 0; u < 4; ++u) row.v[u] = __ldg(src + u);
       };
@@ -273,5 +288,27 @@ FT_API int ft_conv2d_fprop_nhwc(const void* x, const void* w, const void* bias, 
   conv2d_fprop_tcgen05_kernel<<<grid, CV_THREADS, CV_SMEM, stream>>>(tmW, p);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
+  return FT_E_OK;
+}
+
+
+// Host-side view of the kernel's gather indices: offsets[m * k_blocks + kb] = element offset into x
+// (or -1 for padding) for every row m < M and k-block kb, computed by the functions the kernel calls.
+FT_API int ft_conv2d_gather_offsets_host(long long* offsets, int N, int H, int W, int Cin, int KH, int KW, int stride,
+                                         int pad_h, int pad_w, int dil) {
+  FT_REQUIRE(offsets && N > 0 && H > 0 && W > 0 && Cin > 0 && Cin % 64 == 0 && KH > 0 && KW > 0 && stride > 0 && dil > 0,
+             "ft_conv2d_gather_offsets_host: bad geometry");
+  ConvParams p{};
+  p.N = N; p.H = H; p.W = W; p.Cin = Cin; p.KH = KH; p.KW = KW; p.stride = stride; p.pad_h = pad_h; p.pad_w = pad_w; p.dil = dil;
+  p.Ho = (H + 2 * pad_h - dil * (KH - 1) - 1) / stride + 1;
+  p.Wo = (W + 2 * pad_w - dil * (KW - 1) - 1) / stride + 1;
+  p.M = N * p.Ho * p.Wo;
+  p.K = KH * KW * Cin;
+  const int k_blocks = p.K / CV_BK;
+  for (int m = 0; m < p.M; ++m) {
+    int n, hi0, wi0;
+    conv_row_origin(p, m, n, hi0, wi0);
+    for (int kb = 0; kb < k_blocks; ++kb) offsets[static_cast<long long>(m) * k_blocks + kb] = conv_tap_offset(p, n, hi0, wi0, kb);
+  }
   return FT_E_OK;
 }

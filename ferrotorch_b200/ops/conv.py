@@ -32,6 +32,7 @@ from . import functional as F
 _i, _vp = _native._i, _native._vp
 _native.register_protos({
     "ft_conv2d_fprop_nhwc": (_i, [_vp] * 5 + [_i] * 13 + [_vp]),
+    "ft_conv2d_gather_offsets_host": (_i, [_vp] + [_i] * 10),
 })
 
 _enabled = os.environ.get("FT_CONV_IGEMM") == "1"
@@ -158,6 +159,19 @@ def implicit_gemm_reference(x: torch.Tensor, weight: torch.Tensor, stride: int =
         rows = xn[n[ok], hi[ok], wi[ok], c0:c0 + bk]
         A[ok, kb * bk:(kb + 1) * bk] = rows
     return (A @ wk.t()).reshape(N, Ho, Wo, Cout).permute(0, 3, 1, 2)
+
+
+def kernel_gather_offsets(N: int, H: int, W: int, Cin: int, KH: int, KW: int, stride: int = 1, padding=0,
+                          dilation: int = 1) -> torch.Tensor:
+    """The gather indices as the kernel's own index functions compute them (they are compiled for
+    host and device; this calls the host side, no GPU needed): int64 ``[M, K / 64]``, the element
+    offset into NHWC ``x`` of the 64 channels each (row, k-block) reads, -1 where the tap is padding."""
+    ph, pw = _pair(padding)
+    M = N * out_size(H, KH, stride, ph, dilation) * out_size(W, KW, stride, pw, dilation)
+    out = torch.empty((M, KH * KW * Cin // 64), dtype=torch.int64)
+    rc = _native.kernels().ft_conv2d_gather_offsets_host(out.data_ptr(), N, H, W, Cin, KH, KW, stride, ph, pw, dilation)
+    _native.check(rc, "ft_conv2d_gather_offsets_host")
+    return out
 
 
 class IgemmConv2d(nn.Conv2d):

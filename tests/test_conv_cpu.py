@@ -67,3 +67,28 @@ def test_binding_marshals_arguments_and_fails_with_the_library_error(monkeypatch
     w = torch.randn(8, 64, 3, 3).bfloat16()
     with pytest.raises(_native.NativeError, match="ft_conv2d_fprop_nhwc"):    # reached the C entry point: no ctypes TypeError
         C._fprop(x, w, None, None, 1, (1, 1), 1, False)
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,hw", [
+    (64, 8, 3, 1, 1, 1, (7, 6)), (128, 16, 3, 2, 1, 1, (9, 10)), (64, 8, 1, 2, 0, 1, (8, 8)), (64, 8, 3, 1, 2, 2, (9, 9)),
+    (64, 8, 7, 2, 3, 1, (13, 15)), (192, 8, 3, 1, (1, 0), 1, (5, 6)),
+])
+def test_the_kernels_own_index_functions_reproduce_conv2d(cin, cout, k, stride, pad, dil, hw):
+    """The gather offsets come from the functions the CUDA kernel itself calls (compiled for host
+    too): assembling the implicit matrix from them and multiplying by the OHWI filter must give
+    ``conv2d``."""
+    from ferrotorch_b200 import _native
+
+    if _native.kernels(required=False) is None:
+        pytest.skip("kernel library not built")
+    torch.manual_seed(0)
+    n = 2
+    x, w = torch.randn(n, cin, *hw), torch.randn(cout, cin, k, k) * 0.1
+    off = C.kernel_gather_offsets(n, hw[0], hw[1], cin, k, k, stride, pad, dil)
+    flat = torch.cat([x.permute(0, 2, 3, 1).reshape(-1), torch.zeros(64)])          # NHWC, plus a zero run for padding taps
+    idx = torch.where(off >= 0, off, torch.full_like(off, flat.numel() - 64))
+    A = flat[(idx[..., None] + torch.arange(64)).reshape(off.shape[0], -1)]           # [M, K]
+    ref = torch.nn.functional.conv2d(x, w, None, stride, pad, dil)
+    got = (A @ w.permute(0, 2, 3, 1).reshape(cout, -1).t()).reshape(n, ref.shape[2], ref.shape[3], cout).permute(0, 3, 1, 2)
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
+    assert (off % 64 == 0)[off >= 0].all()                                           # every run starts on a 128-byte boundary
