@@ -43,7 +43,7 @@ _CT = {ctypes.c_void_p: "ptr", ctypes.c_char_p: "ptr", ctypes.c_longlong: "i64",
 
 def _registered() -> dict:
     for mod in ("nn.paged", "ops.attention", "ops.batchnorm", "ops.conv", "ops.functional", "ops.quant", "parallel.ddp",
-                "parallel.peer_collectives", "parallel.tensor_parallel", "utils.grammar", "serialize.gguf"):
+                "parallel.peer_collectives", "parallel.tensor_parallel", "utils.grammar", "serialize.gguf", "ops.pool"):
         importlib.import_module("ferrotorch_b200." + mod)
     importlib.import_module("ferrotorch_b200.utils.grammar")._register_token_mask_proto()
     return dict(_native._KERNEL_PROTOS)
