@@ -80,7 +80,11 @@ def main():
         folded = timed(lambda: fused(x))
         C.use_native_conv(True)
         native = timed(lambda: fused(x))
-    for name, ms in (("eval_model", base), ("folded_cudnn", folded), ("folded_igemm", native)):
+        from ferrotorch_b200.ops import pool as P
+
+        P.use_native_pool(True)
+        native_pool = timed(lambda: fused(x))
+    for name, ms in (("eval_model", base), ("folded_cudnn", folded), ("folded_igemm", native), ("folded_igemm_nhwc_pool", native_pool)):
         print(json.dumps({"bench": "resnet50_inference", "variant": name, "batch": a.batch, "ms": ms,
                           "images_per_s": a.batch / ms * 1e3, "dtype": "bf16", "l2_flush": "256 MiB write"}), flush=True)
 

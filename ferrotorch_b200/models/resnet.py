@@ -202,7 +202,11 @@ class FusedInferenceResNet(nn.Module):
         if model.training:
             raise ValueError("FusedInferenceResNet: call model.eval() first (folding uses the running statistics)")
         self.stem = _FoldedConv(model.conv1, model.bn1)
-        self.maxpool, self.avgpool, self.fc = model.maxpool, model.avgpool, model.fc
+        from ..ops.pool import MaxPool2d
+
+        mp = model.maxpool
+        self.maxpool = MaxPool2d(mp.kernel_size, mp.stride, mp.padding)     # the NHWC kernel when switched on, torch otherwise
+        self.avgpool, self.fc = model.avgpool, model.fc
         self.blocks = nn.Sequential(*[_FusedBlock(b) for layer in (model.layer1, model.layer2, model.layer3, model.layer4)
                                       for b in layer])
 
