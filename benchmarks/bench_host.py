@@ -1,6 +1,7 @@
 """Host-runtime benchmarks (no GPU): the native token loader against a torch DataLoader over the
 same file, the TCP transport's star / ring all-reduce on loopback, GGUF dequantisation, the
-grammar mask walk (native against Python) and the JSON-lines state-dict format.
+grammar mask walk (native against Python), the JSON-lines state-dict format and the host Philox
+generator.
 
     python benchmarks/bench_host.py [--quick]
 
@@ -163,6 +164,21 @@ def bench_state_dict(quick):
     os.remove(path)
 
 
+def bench_philox(quick):
+    from ferrotorch_b200.utils.philox import PhiloxGenerator
+
+    n = (1 << 20) if quick else (1 << 24)
+    g = PhiloxGenerator(1)
+    g.generate_uniform(1024)
+    t0 = time.perf_counter()
+    g.generate_uniform(n)
+    u = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    g.generate_normal(n)
+    nrm = time.perf_counter() - t0
+    emit("philox_host_generator", values=n, uniform_mvalues_per_s=n / u / 1e6, normal_mvalues_per_s=n / nrm / 1e6)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
@@ -170,7 +186,7 @@ def main():
     args = ap.parse_args()
     torch.set_num_threads(max(1, (os.cpu_count() or 2) // 2))
     benches = {"loader": bench_loader, "allreduce": bench_allreduce, "gguf": bench_gguf, "grammar": bench_grammar,
-               "state_dict": bench_state_dict}
+               "state_dict": bench_state_dict, "philox": bench_philox}
     for name, fn in benches.items():
         if not args.only or name in args.only.split(","):
             fn(args.quick)

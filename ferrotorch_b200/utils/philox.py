@@ -7,7 +7,8 @@ two zero, the seed as the key); ``next_u32`` walks the words of one counter befo
 next, ``next_f32`` keeps the top 24 bits.  Device-side random numbers of this framework come from
 torch's CUDA generator (itself Philox-4x32-10, addressed by seed and offset); this host generator
 is for reproducible streams that do not depend on a device -- data order, dropout masks in CPU
-oracles -- and is vectorised with numpy so that a million values cost milliseconds.
+oracles.  The word stream is filled by the C++ host library (``csrc/host/philox.cpp``), with a
+vectorised numpy form of the same rounds as the fallback and as the test oracle.
 """
 from __future__ import annotations
 
@@ -35,6 +36,26 @@ def philox_4x32_10(counter, key, counter_hi=0) -> np.ndarray:
                           (p0 >> np.uint64(32)) ^ c3 ^ np.uint64(k1), p0 & _MASK)
         k0, k1 = (k0 + W0) & 0xFFFFFFFF, (k1 + W1) & 0xFFFFFFFF
     return np.stack([c0, c1, c2, c3], axis=-1).astype(np.uint32)
+
+
+_fill = False          # False = not looked up yet, None = unavailable
+
+
+def _native_fill():
+    global _fill
+    if _fill is False:
+        try:
+            import ctypes
+
+            from .. import _native
+
+            lib = _native.host()
+            lib.ftp_fill_words.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p]
+            lib.ftp_fill_words.restype = ctypes.c_int
+            _fill = lib.ftp_fill_words
+        except Exception:  # noqa: BLE001 - no compiler / library: the numpy path serves
+            _fill = None
+    return _fill
 
 
 @dataclass(frozen=True)
@@ -70,12 +91,19 @@ class PhiloxGenerator:
         self.counter, self.offset = (self.counter + int(n_counters)) & (2 ** 64 - 1), 0
 
     def words(self, n: int) -> np.ndarray:
-        """The next ``n`` 32-bit words of the stream."""
+        """The next ``n`` 32-bit words of the stream (the C++ host library fills them when it is
+        built; the numpy form of the same rounds otherwise)."""
         if n <= 0:
             return np.empty(0, np.uint32)
-        blocks = (self.offset + n + 3) // 4
-        ctr = (np.arange(blocks, dtype=np.uint64) + np.uint64(self.counter))
-        out = philox_4x32_10(ctr, self.seed).reshape(-1)[self.offset:self.offset + n]
+        fill = _native_fill()
+        if fill is not None:
+            out = np.empty(n, np.uint32)
+            if fill(self.counter, self.seed, self.offset, n, out.ctypes.data) != 0:
+                raise RuntimeError("ftp_fill_words failed")
+        else:
+            blocks = (self.offset + n + 3) // 4
+            ctr = (np.arange(blocks, dtype=np.uint64) + np.uint64(self.counter))
+            out = philox_4x32_10(ctr, self.seed).reshape(-1)[self.offset:self.offset + n]
         end = self.offset + n
         self.counter, self.offset = (self.counter + end // 4) & (2 ** 64 - 1), end % 4
         return out

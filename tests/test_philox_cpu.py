@@ -72,3 +72,16 @@ def test_manager_fork_join():
     assert m.get_rng_state(1).offset == 0
     with pytest.raises(ValueError):
         P.join_rng([0], saved)
+
+
+def test_native_word_stream_equals_numpy_rounds():
+    if P._native_fill() is None:
+        pytest.skip("host library not built")
+    for seed, skip, n in ((0, 0, 17), (42, 3, 1), (2 ** 63 + 5, 6, 1001), (7, 2, 2)):
+        g = P.PhiloxGenerator(seed)
+        g.words(skip)
+        st = g.get_state()
+        got = g.words(n)
+        blocks = (st.offset + n + 3) // 4
+        ref = P.philox_4x32_10(np.arange(blocks, dtype=np.uint64) + np.uint64(st.counter), seed).reshape(-1)[st.offset:st.offset + n]
+        assert np.array_equal(got, ref) and g.get_state() == P.PhiloxState(st.counter + (st.offset + n) // 4, seed, (st.offset + n) % 4)
