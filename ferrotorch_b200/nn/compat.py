@@ -180,3 +180,6 @@ class QatModel(nn.Module):
 
 
 KVPage = tuple      # (layer, page index): pages are slices of the pool's device tensors, addressed by index
+
+__all__ = [_n for _n, _o in list(globals().items())
+           if not _n.startswith("_") and type(_o).__name__ != "module" and _n not in ("annotations", "Callable", "Dict", "Any", "Hashable")]

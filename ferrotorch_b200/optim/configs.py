@@ -139,3 +139,6 @@ class GradScalerState:
         if sd:                                              # a disabled scaler has no state
             sd.update(scale=self.scale, _growth_tracker=self.growth_tracker)
             scaler.load_state_dict(sd)
+
+__all__ = [_n for _n, _o in list(globals().items())
+           if not _n.startswith("_") and type(_o).__name__ != "module" and _n not in ("annotations", "Callable", "Dict", "Any", "Hashable")]

@@ -140,3 +140,6 @@ class FeatureExtractor(nn.Module):
 
 def create_feature_extractor(model: nn.Module, return_nodes) -> FeatureExtractor:
     return FeatureExtractor(model, return_nodes)
+
+__all__ = [_n for _n, _o in list(globals().items())
+           if not _n.startswith("_") and type(_o).__name__ != "module" and _n not in ("annotations", "Callable", "Dict", "Any", "Hashable")]
