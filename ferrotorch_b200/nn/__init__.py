@@ -15,5 +15,7 @@ from .extra import (HookedModule, HookHandle, LoRALinear, SqueezeExcitation, fla
                     standard_attention)
 from ..core import flex_attention  # noqa: F401,E402
 from .paged import OutOfPages, PagedAttentionManager, PagedKVCache  # noqa: F401,E402
+from ..ops.conv import IgemmConv2d, convert_convs  # noqa: F401,E402  (implicit-GEMM convolution; opt-in, see ops.conv)
+from ..ops.pool import MaxPool2d as NhwcMaxPool2d  # noqa: F401,E402
 from .compat import *  # noqa: F401,F403,E402
 from .compat import (BackwardHook, ForwardHook, ForwardPreHook, HardSigmoid, HardSwish, KVPage, StateDict)  # noqa: F401,E402
