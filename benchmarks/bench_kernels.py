@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Per-kernel micro-benchmarks with roofline fractions against MEASURED_PEAKS.json.
+"""Per-kernel micro-benchmarks with roofline fractions against a measured copy bandwidth and
+cuBLAS bf16 throughput (``--hbm-gbs``, ``--bf16-tflops``; defaults are a B200's measured values).
 
     python benchmarks/bench_kernels.py [--small] [--only gemm,attn,norm,optim,decode,quant,jit,bn,tp]
 
@@ -24,13 +25,13 @@ from ferrotorch_b200.ops import functional as F  # noqa: E402
 from ferrotorch_b200.ops.attention import flash_attention  # noqa: E402
 
 
+# Roofline denominators: a STREAM-style copy and a cuBLAS bf16 GEMM burst measured on a B200
+# (6553 GB/s, 1681.7 TFLOP/s); override with --hbm-gbs / --bf16-tflops for another part.
+PEAKS = {"hbm_gbs": 6553.0, "bf16_tflops": 1681.7}
+
+
 def peaks():
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            p = json.load(f)
-        return p["hbm_gbs"], p["bf16_tflops"], "measured"
-    except (OSError, KeyError, ValueError):
-        return 6650.0, 1590.0, "fallback"
+    return PEAKS["hbm_gbs"], PEAKS["bf16_tflops"], "measured"
 
 
 ITERS, WARM = 10, 3
@@ -79,6 +80,7 @@ def run_gemm(small):
         fl = 2.0 * M * N * K
         emit("gemm_nt %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(a, b, out=c)), fl)
         if not small:
+            emit("gemm_nt one-CTA kernel %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(a, b, out=c, bn=-256)), fl)
             emit("torch.matmul %dx%dx%d" % (M, N, K), bench(lambda: torch.matmul(a, b.t(), out=c)), fl)
             bt, at = r(K, N).t(), r(K, M).t()
             emit("gemm_nn(dgrad) %dx%dx%d" % (M, N, K), bench(lambda: F.gemm_nt(a, bt, out=c)), fl)
@@ -216,8 +218,12 @@ if __name__ == "__main__":
     ap.add_argument("--only", default="gemm,attn,norm,optim,decode")
     ap.add_argument("--iters", type=int, default=10, help="timed runs per case (1-2 under ncu)")
     ap.add_argument("--warm", type=int, default=3)
+    ap.add_argument("--hbm-gbs", type=float, default=PEAKS["hbm_gbs"], help="measured copy bandwidth, GB/s")
+    ap.add_argument("--bf16-tflops", type=float, default=PEAKS["bf16_tflops"],
+                    help="measured cuBLAS bf16 GEMM throughput (burst), TFLOP/s")
     a = ap.parse_args()
     ITERS, WARM = a.iters, a.warm
+    PEAKS.update(hbm_gbs=a.hbm_gbs, bf16_tflops=a.bf16_tflops)
     for name in a.only.split(","):
         {"gemm": run_gemm, "attn": run_attn, "norm": run_norm, "optim": run_optim, "decode": run_decode,
          "quant": run_quant, "jit": run_jit, "bn": run_bn, "tp": run_tp}[name](a.small)

@@ -7,8 +7,8 @@
 For every shape: CUDA-event time of the fused kernel (mean of ``--iters`` back-to-back launches
 after warm-up, max over ranks), its TFLOP/s, the bytes that had to cross NVLink per GPU and
 direction, the roofline time = max(FLOPs / measured GEMM peak, NVLink bytes / 770 GB/s) and the
-achieved fraction of it.  The GEMM peak comes from ``MEASURED_PEAKS.json`` next to the repo root
-when present (``bf16_tflops_sustained``), else 1400 TFLOP/s.
+achieved fraction of it.  The GEMM peak is ``--peak-tflops`` (default 1414.9: a B200's measured
+sustained cuBLAS bf16 throughput under its power cap).
 """
 from __future__ import annotations
 
@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--qkv", type=int, default=6144)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--peak-tflops", type=float, default=1414.9,
+                    help="measured sustained cuBLAS bf16 GEMM throughput, TFLOP/s")
     ap.add_argument("--n-copy", type=int, default=0, help="copy CTAs of the all-gather GEMM (0 = default)")
     args = ap.parse_args()
 
@@ -47,12 +49,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     tp = TPContext(group, dev, **({"n_copy": args.n_copy} if args.n_copy else {}))
-    peak = 1400.0
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            peak = float(json.load(f).get("bf16_tflops_sustained", peak))
-    except OSError:
-        pass
+    peak = args.peak_tflops
     link = 770.0  # GB/s per direction per GPU, measured peer copy
     M, H = args.rows, args.hidden
     ms_rows = tp.rows_per_rank(M)

@@ -141,12 +141,15 @@ ddp_reduce_update_kernel(const DdpArgs a) {
                    a.epoch);
   }
   // 2. wait for every peer's gradients
-  if (!wait_flags(my_flags + flag_index(0, a.slot, 0, a.n_slots), a.world, a.epoch, a.limit_ns, a.status)) return;
+  //    A block whose wait ran out skips the work but still takes part in step 4, so that the
+  //    per-slot block counter returns to zero and a later launch on this slot is not confused.
+  const bool peers_ok =
+      wait_flags(my_flags + flag_index(0, a.slot, 0, a.n_slots), a.world, a.epoch, a.limit_ns, a.status);
 
   // 3. reduce + update the slice this rank owns, push the new weights to every rank
   const long long slice = a.n / a.world;
   const long long base = a.lo + static_cast<long long>(a.rank) * slice;
-  const long long nvec = slice >> 3;
+  const long long nvec = peers_ok ? (slice >> 3) : 0;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long e = base + (i << 3);
@@ -222,7 +225,8 @@ ddp_reduce_update_kernel(const DdpArgs a) {
       if (r < a.world) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.params.ptr[r]) + e) = o;
   }
 
-  // 4. the last block to finish raises this rank's "done" flag on every peer
+  // 4. the last block to finish raises this rank's "done" flag on every peer (not after a
+  //    timed-out wait anywhere in the grid: the status word is set then)
   __threadfence_system();
   __syncthreads();
   __shared__ unsigned int s_last;
@@ -233,7 +237,8 @@ ddp_reduce_update_kernel(const DdpArgs a) {
   __syncthreads();
   if (s_last) {
     if (threadIdx.x == 0) a.block_counter[a.slot] = 0u;
-    if (threadIdx.x < a.world) {
+    const bool clean = peers_ok && !(a.status && *reinterpret_cast<const volatile int*>(a.status) != 0);
+    if (clean && threadIdx.x < a.world) {
       __threadfence_system();
       st_release_sys(static_cast<uint32_t*>(a.flags.ptr[threadIdx.x]) + flag_index(1, a.slot, a.rank, a.n_slots),
                      a.epoch);
@@ -297,8 +302,11 @@ __global__ void __launch_bounds__(COMM_THREADS) exchange_pull_kernel(const Excha
     st_release_sys(static_cast<uint32_t*>(a.flags.ptr[threadIdx.x]) + flag_index(0, a.slot, a.rank, a.n_slots),
                    a.epoch);
   }
-  if (!wait_flags(my_flags + flag_index(0, a.slot, 0, a.n_slots), a.world, a.epoch, a.limit_ns, a.status)) return;
-  for (int k = 0; k < a.world; ++k) {
+  // a block whose wait ran out copies nothing but still counts itself below, so the per-slot
+  // block counter is back at zero for the next launch
+  const bool peers_ok =
+      wait_flags(my_flags + flag_index(0, a.slot, 0, a.n_slots), a.world, a.epoch, a.limit_ns, a.status);
+  for (int k = 0; k < (peers_ok ? a.world : 0); ++k) {
     const int r = (a.rank + k) % a.world;
     const uint8_t* s = static_cast<const uint8_t*>(a.src.ptr[r]) + a.src_off[r];
     uint8_t* d = a.out + a.dst_off[r];
@@ -328,7 +336,8 @@ __global__ void __launch_bounds__(COMM_THREADS) exchange_pull_kernel(const Excha
   __syncthreads();
   if (s_last) {
     if (threadIdx.x == 0) a.block_counter[a.slot] = 0u;
-    if (threadIdx.x < a.world) {
+    const bool clean = peers_ok && !(a.status && *reinterpret_cast<const volatile int*>(a.status) != 0);
+    if (clean && threadIdx.x < a.world) {
       __threadfence_system();
       st_release_sys(static_cast<uint32_t*>(a.flags.ptr[threadIdx.x]) + flag_index(1, a.slot, a.rank, a.n_slots),
                      a.epoch);

@@ -47,23 +47,23 @@ int* device_status_word(int device) {
 }
 
 int ensure_device(int device) {
-  static thread_local int current = -1;
-  if (current == device) return FT_E_OK;
+  // Ask the runtime every time: torch (or the caller) may have switched devices since the last
+  // call, so a cached value could launch on the wrong GPU.  cudaGetDevice is a host-only query.
+  int cur = -1;
+  if (cudaGetDevice(&cur) == cudaSuccess && cur == device) {
+    static thread_local unsigned long long bound = 0;  // devices whose context this thread has touched
+    if (device >= 0 && device < 64 && !((bound >> device) & 1ull)) {
+      cudaFree(0);  // binds the primary context to this thread (worker threads start without one)
+      bound |= 1ull << device;
+    }
+    return FT_E_OK;
+  }
   if (cudaSetDevice(device) != cudaSuccess) {
     set_last_error("cudaSetDevice(%d) failed", device);
     return FT_E_CUDA;
   }
-  cudaFree(0);  // binds the primary context to this thread
-  current = device;
+  cudaFree(0);
   return FT_E_OK;
-}
-
-int mem_variant() {
-  static const int v = [] {
-    const char* e = getenv("FT_MEM_VARIANT");
-    return e ? atoi(e) : 1;
-  }();
-  return v;
 }
 
 int sm_count(int device) {

@@ -46,13 +46,8 @@ int make_tmap_4d(CUtensorMap* out, const void* base, int dtype_bytes, uint64_t d
 
 int sm_count(int device);
 
-// Which implementation the memory-bound kernels (AdamW, SwiGLU, RoPE) use: 1 (default) = wide
-// vectors with streaming cache hints, 0 = the first versions (kept for A/B timing).  Read once
-// from the environment variable FT_MEM_VARIANT.
-int mem_variant();
-
-// Make `device` current for this library's CUDA runtime on the calling thread (cached per
-// thread).  Needed because worker threads (e.g. an autograd engine thread) start with no
+// Make `device` current for this library's CUDA runtime on the calling thread (checked against
+// cudaGetDevice on every call, never cached).  Needed because worker threads (e.g. an autograd engine thread) start with no
 // CUDA context bound, and driver entry points such as the tensor-map encoder require one.
 int ensure_device(int device);
 

@@ -3,9 +3,8 @@
 //
 // Most launchers in this library take their scratch memory from the caller, and the Python
 // front end gets it from PyTorch's caching allocator.  Some callers cannot do either: code
-// that runs while a CUDA graph is being captured or inside a memory-pool callback, an
-// out-of-memory handler that must still be able to run a kernel, and real-time or embedded
-// hosts whose memory budget is fixed at start-up.  For them, calling cudaMalloc / cudaFree (or
+// that runs inside a memory-pool callback, an out-of-memory handler that must still be able
+// to run a kernel, and real-time or embedded hosts whose memory budget is fixed at start-up.  For them, calling cudaMalloc / cudaFree (or
 // any routine that might) is either an error or an unbounded stall.
 //
 // ft_rmsnorm_bwd_noalloc is the RMSNorm backward of ft_rmsnorm_bwd with its partial-sum
@@ -15,6 +14,9 @@
 //     rows.  Larger H is rejected with an error (code FT_E_TOO_LARGE, text in ft_last_error()).
 //   * Cost: FT_NOALLOC_RMSNORM_ROWS * FT_NOALLOC_RMSNORM_MAX_H floats = 4 MiB of device memory on
 //     every GPU that loads the library, held until the process exits.
+//   * `device` must be the calling thread's current CUDA device (cudaGetDevice() == device);
+//     otherwise the call fails with FT_E_BAD_ARG and launches nothing.  The entry point never
+//     switches devices itself.
 //   * The first call on a device looks up the array's device address (once per device, with
 //     that device current).  Make that first call outside any stream capture; later calls only
 //     launch kernels.

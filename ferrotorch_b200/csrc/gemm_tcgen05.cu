@@ -10,6 +10,10 @@
 // reference (ferrotorch-gpu/src/blas.rs:3186-3306, 2769-2886) and its separate
 // bias launch (ferrotorch-core/src/grad_fns/linalg.rs:1643-1655).
 //
+// Two kernels share this file.  Problems with at least 256 rows and N >= 128 run on the
+// CTA-pair kernel (tcgen05.mma.cta_group::2, 256 x BN tiles, TMA-store epilogue; described at
+// gemm_bf16_pair_kernel).  Smaller problems run on the one-CTA kernel:
+//
 // Kernel structure (one persistent CTA per SM, 256 threads):
 //   warp 0    TMA producer: one elected thread fills a STAGES-deep ring of
 //             {A 128x64, B BNx64} bf16 tiles (128-byte swizzle)
@@ -40,6 +44,7 @@ enum GemmFlags : int {
   GEMM_RELU = 16,       // activation fused in the epilogue (after bias)
   GEMM_GELU = 32,
   GEMM_SILU = 64,
+  GEMM_EPI_DIRECT = 1 << 16,  // internal: per-lane read-modify-write epilogue
 };
 
 template <int BN>
@@ -78,6 +83,86 @@ __device__ __forceinline__ float apply_act(float v, int flags) {
   if (flags & GEMM_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
   if (flags & GEMM_SILU) return v / (1.f + __expf(-v));
   return v;
+}
+
+
+// Epilogue that writes straight to global memory, one accumulator row per lane.  Used where the
+// output needs a read-modify-write in fp32 before rounding (bf16 accumulate) or an activation
+// after the accumulation.  `t_row` addresses this warp's 32 TMEM lanes at the tile's first
+// column; `row` is this lane's global row, `n0` the tile's first column.
+template <int BN>
+__device__ __forceinline__ void epilogue_direct(const GemmParams& p, uint32_t t_row, int row, int n0) {
+  const bool row_ok = row < p.M;
+  const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
+  const bool accumulate = (p.flags & GEMM_ACCUMULATE) != 0;
+  const bool has_bias = (p.flags & (GEMM_BIAS | GEMM_BIAS_F32)) != 0;
+  const bool has_act = (p.flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (!row_ok || col0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (has_bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        if (col < p.N) {
+          v[j] += (p.flags & GEMM_BIAS_F32)
+                      ? static_cast<const float*>(p.bias)[col]
+                      : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+        }
+      }
+    }
+    if (out_f32) {
+      float* crow = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        if (col0 + g * 4 + 4 <= p.N) {
+          float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+          if (accumulate) {
+            const float4 old = *reinterpret_cast<const float4*>(crow + g * 4);
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          if (has_act) {
+            o.x = apply_act(o.x, p.flags); o.y = apply_act(o.y, p.flags);
+            o.z = apply_act(o.z, p.flags); o.w = apply_act(o.w, p.flags);
+          }
+          *reinterpret_cast<float4*>(crow + g * 4) = o;
+        }
+      }
+    } else {
+      __nv_bfloat16* crow =
+          static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col0 + g * 8 + 8 <= p.N) {
+          float* vv = v + g * 8;
+          if (accumulate) {
+            const uint4 old = *reinterpret_cast<const uint4*>(crow + g * 8);
+            const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y),
+                         o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
+            vv[0] += o0.x; vv[1] += o0.y; vv[2] += o1.x; vv[3] += o1.y;
+            vv[4] += o2.x; vv[5] += o2.y; vv[6] += o3.x; vv[7] += o3.y;
+          }
+          if (has_act) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vv[j] = apply_act(vv[j], p.flags);
+          }
+          uint4 o;
+          o.x = pack_bf16x2(vv[0], vv[1]);
+          o.y = pack_bf16x2(vv[2], vv[3]);
+          o.z = pack_bf16x2(vv[4], vv[5]);
+          o.w = pack_bf16x2(vv[6], vv[7]);
+          *reinterpret_cast<uint4*>(crow + g * 8) = o;
+        }
+      }
+    }
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -223,86 +308,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int ew = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
-    const bool accumulate = (p.flags & GEMM_ACCUMULATE) != 0;
-    const bool has_bias = (p.flags & (GEMM_BIAS | GEMM_BIAS_F32)) != 0;
-    const bool has_act = (p.flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int mb, nb;
       tile_coords(tile, m_blocks, n_blocks, mb, nb);
       const int m0 = mb * GEMM_BM, n0 = nb * BN;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int row = m0 + ew * 32 + lane;
-      const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (has_bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            if (col < p.N) {
-              v[j] += (p.flags & GEMM_BIAS_F32)
-                          ? static_cast<const float*>(p.bias)[col]
-                          : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
-            }
-          }
-        }
-        if (out_f32) {
-          float* crow = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (col0 + g * 4 + 4 <= p.N) {
-              float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-              if (accumulate) {
-                const float4 old = *reinterpret_cast<const float4*>(crow + g * 4);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              if (has_act) {
-                o.x = apply_act(o.x, p.flags); o.y = apply_act(o.y, p.flags);
-                o.z = apply_act(o.z, p.flags); o.w = apply_act(o.w, p.flags);
-              }
-              *reinterpret_cast<float4*>(crow + g * 4) = o;
-            }
-          }
-        } else {
-          __nv_bfloat16* crow =
-              static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 + 8 <= p.N) {
-              float* vv = v + g * 8;
-              if (accumulate) {
-                const uint4 old = *reinterpret_cast<const uint4*>(crow + g * 8);
-                const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y),
-                             o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
-                vv[0] += o0.x; vv[1] += o0.y; vv[2] += o1.x; vv[3] += o1.y;
-                vv[4] += o2.x; vv[5] += o2.y; vv[6] += o3.x; vv[7] += o3.y;
-              }
-              if (has_act) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) vv[j] = apply_act(vv[j], p.flags);
-              }
-              uint4 o;
-              o.x = pack_bf16x2(vv[0], vv[1]);
-              o.y = pack_bf16x2(vv[2], vv[3]);
-              o.z = pack_bf16x2(vv[4], vv[5]);
-              o.w = pack_bf16x2(vv[6], vv[7]);
-              *reinterpret_cast<uint4*>(crow + g * 8) = o;
-            }
-          }
-        }
-      }
+      epilogue_direct<BN>(p, t_row, m0 + ew * 32 + lane, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -319,6 +333,354 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+
+// ----------------------------------------------------------------------------- CTA-pair kernel
+// The large-problem kernel.  Two CTAs of a thread-block cluster work on one 256 x BN output
+// tile with tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own half
+// (BN/2 rows) of B with plain TMA loads, so a k-block costs each SM 16 KB + BN*64 bytes of
+// shared-memory fill instead of 16 KB + BN*128, and the tensor core of each SM reads half of B
+// from its neighbour.  The even CTA of the pair (the leader) issues every MMA; its commits
+// arrive on the "stage empty" and "accumulator full" barriers of both CTAs.  TMA completions of
+// both CTAs are counted on the leader's "stage full" barrier, and the epilogue warps of both
+// CTAs arrive on the leader's "accumulator empty" barrier.
+//
+// Epilogue: each of the four epilogue warps owns 32 accumulator rows.  It converts 128 bytes
+// per row at a time (64 bf16 or 32 fp32 columns), writes them into a 128-byte-swizzled staging
+// tile of its own in shared memory and hands the tile to a TMA store (or a TMA reduce-add for
+// C += ...).  Two staging tiles per warp keep one store in flight while the next is filled; the
+// stores clip at the M and N edges.
+template <int BN>
+struct PairCfg {
+  static constexpr int BNH = BN / 2;
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BNH * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_TILE_BYTES = 32 * 128;
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_TILE_BYTES;
+  static constexpr int STAGES_RAW = (227 * 1024 - 2048 - EPI_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+};
+
+constexpr int PAIR_GROUP_M = 8;  // 256-row blocks per rasterisation group
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
+  const int group_tiles = PAIR_GROUP_M * n_blocks;
+  const int g = tile / group_tiles;
+  const int first_m = g * PAIR_GROUP_M;
+  const int gm = min(PAIR_GROUP_M, m_blocks - first_m);
+  const int r = tile - g * group_tiles;
+  mb = first_m + (r % gm);
+  nb = r / gm;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  using Cfg = PairCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int BNH = Cfg::BNH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + Cfg::EPI_BYTES);
+  // bars[0..S) full (used in the leader), [S..2S) empty, [2S..2S+2) tmem_full,
+  // [2S+2..2S+4) tmem_empty (used in the leader)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  const int m_blocks = (p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // four epilogue warps in each CTA of the pair
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        int mb, nb;
+        pair_tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        const int m0 = mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM;
+        const int n0 = nb * BN + static_cast<int>(rank) * BNH;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          // the leader's barrier counts the bytes of both CTAs
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+          const uint32_t fb = mapa_shared(full_bar(stage), 0);
+          const int k0 = kb * GEMM_BK;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sA, &tmA, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d_pair(sA + c * (GEMM_BK * 128), &tmA, fb, m0 + c * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c)
+              tma_load_2d_pair(sB + c * (GEMM_BK * 128), &tmB, fb, n0 + c * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(2 * GEMM_BM, BN, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait_cluster(tempty_bar(acc), acc_phase ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_cluster(full_bar(stage), phase, abort_word, FT_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(sA + k * 2048, GEMM_BK * 128, 1024)
+                                        : make_smem_desc_sw128(sA + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sB + k * 2048, GEMM_BK * 128, 1024)
+                                        : make_smem_desc_sw128(sB + k * 32, 16, 1024);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage), 3);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar(acc), 3);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int ew = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
+    const bool accumulate = (p.flags & GEMM_ACCUMULATE) != 0;
+    const bool has_bias = (p.flags & (GEMM_BIAS | GEMM_BIAS_F32)) != 0;
+    const bool has_act = (p.flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
+    const bool direct = (p.flags & GEMM_EPI_DIRECT) != 0;
+    const uint32_t stage_tiles = smem_u32(epi) + static_cast<uint32_t>(ew) * 2u * Cfg::EPI_TILE_BYTES;
+    int buf = 0;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs) {
+      int mb, nb;
+      pair_tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      const int m0 = mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM + ew * 32;
+      const int n0 = nb * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+      if (direct) {
+        epilogue_direct<BN>(p, t_row, m0 + lane, n0);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
+      } else {
+        const int step_cols = out_f32 ? 32 : 64;
+        const int steps = BN / step_cols;
+#pragma unroll 1
+        for (int c = 0; c < steps; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * step_cols, r0);
+          if (!out_f32) {
+            tmem_ld_32x32(t_row + c * step_cols + 32, r1);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r1[j] = 0u;
+          }
+          tmem_ld_wait();
+          if (c == steps - 1) {
+            // the accumulator is in registers: hand it back before the stores are issued
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
+          }
+          const int col0 = n0 + c * step_cols;
+          if (m0 >= p.M || col0 >= p.N) continue;  // warp-uniform: nothing of this piece is inside C
+          if (has_bias) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const int col = col0 + j;
+              if (j < step_cols && col < p.N) {
+                const float b = (p.flags & GEMM_BIAS_F32)
+                                    ? static_cast<const float*>(p.bias)[col]
+                                    : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+                uint32_t& x = j < 32 ? r0[j & 31] : r1[j & 31];
+                x = __float_as_uint(__uint_as_float(x) + b);
+              }
+            }
+          }
+          if (has_act) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              if (j < step_cols) {
+                uint32_t& x = j < 32 ? r0[j & 31] : r1[j & 31];
+                x = __float_as_uint(apply_act(__uint_as_float(x), p.flags));
+              }
+          }
+          // the store issued two steps ago has finished reading this staging tile
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          const uint32_t tile_s = stage_tiles + static_cast<uint32_t>(buf) * Cfg::EPI_TILE_BYTES;
+          const uint32_t row_s = tile_s + static_cast<uint32_t>(lane) * 128u;
+          const uint32_t sw = static_cast<uint32_t>(lane & 7);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t x, y, z, w;
+            if (out_f32) {
+              x = r0[4 * j]; y = r0[4 * j + 1]; z = r0[4 * j + 2]; w = r0[4 * j + 3];
+            } else {
+              const uint32_t(&q)[32] = j < 4 ? r0 : r1;
+              const int o = 8 * (j & 3);
+              x = pack_bf16x2(__uint_as_float(q[o]), __uint_as_float(q[o + 1]));
+              y = pack_bf16x2(__uint_as_float(q[o + 2]), __uint_as_float(q[o + 3]));
+              z = pack_bf16x2(__uint_as_float(q[o + 4]), __uint_as_float(q[o + 5]));
+              w = pack_bf16x2(__uint_as_float(q[o + 6]), __uint_as_float(q[o + 7]));
+            }
+            const uint32_t dst = row_s + ((static_cast<uint32_t>(j) ^ sw) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(x), "r"(y), "r"(z),
+                         "r"(w)
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (accumulate)
+              tma_reduce_add_2d(&tmC, tile_s, col0, m0);
+            else
+              tma_store_2d(&tmC, tile_s, col0, m0);
+            tma_store_commit();
+          }
+          buf ^= 1;
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    // shared memory must outlive the stores that read it
+    if (lane == 0) tma_store_wait<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees TMEM or exits while its peer can still reach it
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                       const GemmParams& p, int device, int max_ctas, cudaStream_t stream) {
+  using Cfg = PairCfg<BN>;
+  auto kern = gemm_bf16_pair_kernel<BN, A_MN, B_MN>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[device]) {
+    FT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES));
+    attr_set[device] = true;
+  }
+  const int m_blocks = (p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+  const int n_blocks = (p.N + BN - 1) / BN;
+  int pairs = m_blocks * n_blocks;
+  int sms = sm_count(device);
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (pairs > sms / 2) pairs = sms / 2;
+  if (pairs < 1) pairs = 1;
+  kern<<<2 * pairs, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
+}
+
+template <int BN>
+static int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                         const CUtensorMap& tmC, const GemmParams& p, int device, int max_ctas,
+                         cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_pair<BN, false, false>(tmA, tmB, tmC, p, device, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_pair<BN, false, true>(tmA, tmB, tmC, p, device, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_pair<BN, true, false>(tmA, tmB, tmC, p, device, max_ctas, stream);
+  return launch_pair<BN, true, true>(tmA, tmB, tmC, p, device, max_ctas, stream);
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -358,7 +720,7 @@ static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CU
 // C[M,N] (+)= A * B^T (+bias).  A is [M,K] (a_mn_major = 0, row stride lda) or stored
 // transposed as [K,M] (a_mn_major = 1); B is [N,K] (b_mn_major = 0) or stored as
 // [K,N] (b_mn_major = 1).  Strides are in elements.  bn = 0 picks the N tile
-// automatically; max_ctas > 0 limits the persistent grid (used to leave SMs to a
+// automatically, a negative bn selects the one-CTA kernel with an N tile of -bn; max_ctas > 0 limits the persistent grid (used to leave SMs to a
 // concurrent communication kernel).  Returns 0 or a negative error code
 // (ft_last_error() has the text).
 FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
@@ -374,6 +736,48 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
              "ft_gemm_bf16: N (%d) must be a multiple of 8 and ldc 16-byte aligned", N);
   FT_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0, "ft_gemm_bf16: C must be 16-byte aligned");
   FT_REQUIRE(!(flags & (GEMM_BIAS | GEMM_BIAS_F32)) || bias, "ft_gemm_bf16: bias flag without bias");
+  const bool force_single = bn < 0;
+  if (force_single) bn = -bn;
+  const bool has_act = (flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
+  const bool accumulate = (flags & GEMM_ACCUMULATE) != 0;
+  flags &= 0xFFFF;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  GemmParams p;
+  p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags;
+  p.status = device_status_word(device);
+
+  // Problems with at least one full 256-row block and N >= 128 run on the CTA-pair kernel.
+  if (!force_single && M >= 2 * GEMM_BM && N >= 128 && (bn == 0 || bn >= 128)) {
+    const int pairs = (max_ctas > 0 && max_ctas < sm_count(device) ? max_ctas : sm_count(device)) / 2;
+    const long long mb2 = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+    int pbn = bn ? bn : 256;
+    if (bn == 0 && mb2 * ((N + 255) / 256) < pairs) pbn = 128;  // too few 256-wide tiles to fill the GPU
+    if (N < 256) pbn = 128;
+    // bf16 C += ... adds in fp32 before rounding once; an activation after the accumulation
+    // also needs the old value in registers: both use the per-lane epilogue.
+    if ((accumulate && !out_f32) || (accumulate && has_act)) p.flags |= GEMM_EPI_DIRECT;
+    if (!a_mn_major)
+      rc = make_tmap_2d(&tmA, A, 2, K, M, lda * 2, GEMM_BK, GEMM_BM, 3);
+    else
+      rc = make_tmap_2d(&tmA, A, 2, M, K, lda * 2, 64, GEMM_BK, 3);
+    if (rc) return rc;
+    if (!b_mn_major)
+      rc = make_tmap_2d(&tmB, B, 2, K, N, ldb * 2, GEMM_BK, pbn / 2, 3);
+    else
+      rc = make_tmap_2d(&tmB, B, 2, N, K, ldb * 2, 64, GEMM_BK, 3);
+    if (rc) return rc;
+    CUtensorMap tmC;
+    if (out_f32)
+      rc = make_tmap_2d(&tmC, C, 4, N, M, ldc * 4, 32, 32, 3);
+    else
+      rc = make_tmap_2d(&tmC, C, 2, N, M, ldc * 2, 64, 32, 3);
+    if (rc) return rc;
+    if (pbn == 256) return dispatch_pair<256>(a_mn_major, b_mn_major, tmA, tmB, tmC, p, device, max_ctas, stream);
+    return dispatch_pair<128>(a_mn_major, b_mn_major, tmA, tmB, tmC, p, device, max_ctas, stream);
+  }
+
   if (bn == 0) {
     const int sms = sm_count(device);
     const long long mb = (M + GEMM_BM - 1) / GEMM_BM;
@@ -385,8 +789,6 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
   // an MN-major B tile is loaded in 64-element (128-byte swizzle) column chunks
   if (b_mn_major && bn < 64) bn = 64;
 
-  CUtensorMap tmA, tmB;
-  int rc;
   if (!a_mn_major)
     rc = make_tmap_2d(&tmA, A, 2, K, M, lda * 2, GEMM_BK, GEMM_BM, 3);
   else
@@ -398,9 +800,6 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
     rc = make_tmap_2d(&tmB, B, 2, N, K, ldb * 2, 64, GEMM_BK, 3);
   if (rc) return rc;
 
-  GemmParams p;
-  p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags;
-  p.status = device_status_word(device);
   switch (bn) {
     case 256: return dispatch_major<256>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
     case 128: return dispatch_major<128>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);

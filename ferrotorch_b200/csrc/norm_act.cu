@@ -308,48 +308,6 @@ __device__ __forceinline__ float act_bwd(float g, int act) {
   const float t = tanhf(k);
   return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * g * g);
 }
-__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                                  long long T, int F, long long ld_gu, int act) {
-  const int fv = F >> 3;
-  const long long total = T * fv;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = i / fv;
-    const int v = static_cast<int>(i - t * fv);
-    const uint4* row = reinterpret_cast<const uint4*>(gu + t * ld_gu);
-    float g[8], u[8], o[8];
-    unpack8(row[v], g);
-    unpack8(row[fv + v], u);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], act) * u[j];
-    reinterpret_cast<uint4*>(out + t * F)[v] = pack8(o);
-  }
-}
-__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gu,
-                                  __nv_bfloat16* __restrict__ dgu, long long T, int F, long long ld_gu,
-                                  int act) {
-  const int fv = F >> 3;
-  const long long total = T * fv;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = i / fv;
-    const int v = static_cast<int>(i - t * fv);
-    const uint4* row = reinterpret_cast<const uint4*>(gu + t * ld_gu);
-    float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(row[v], g);
-    unpack8(row[fv + v], u);
-    unpack8(reinterpret_cast<const uint4*>(dy + t * F)[v], d);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      dg[j] = d[j] * u[j] * act_bwd(g[j], act);
-      du[j] = d[j] * act_fwd(g[j], act);
-    }
-    uint4* orow = reinterpret_cast<uint4*>(dgu + t * ld_gu);
-    orow[v] = pack8(dg);
-    orow[fv + v] = pack8(du);
-  }
-}
-
 // Two vectors per thread with all loads issued first and streaming (evict-first) hints on the
 // inputs, which are read exactly once.
 __global__ void swiglu_fwd2_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
@@ -508,7 +466,7 @@ FT_API int ft_rope(void* x, const float* cos_t, const float* sin_t, const int* p
   FT_REQUIRE(pos || seq_len > 0, "ft_rope: need positions or seq_len");
   if (T <= 0 || n_rot_heads <= 0) return FT_E_OK;
   const long long work = static_cast<long long>(T) * n_rot_heads * (D / 4);
-  if (mem_variant() != 0 && D % 16 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+  if (D % 16 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0)
     rope_vec_kernel<<<blocks_for(work / 4, 256, device), 256, 0, stream>>>(
         static_cast<__nv_bfloat16*>(x), cos_t, sin_t, pos, T, n_rot_heads, D, ld, seq_len, pos_offset,
@@ -528,12 +486,8 @@ FT_API int ft_swiglu_fwd(const void* gu, void* out, long long T, int F, long lon
   FT_REQUIRE(gu && out, "ft_swiglu_fwd: null pointer");
   FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_fwd: F must be a multiple of 8");
   if (T <= 0) return FT_E_OK;
-  if (mem_variant() != 0)
-    swiglu_fwd2_kernel<<<blocks_for(T * (F / 8) / 2 + 1, 256, device), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
-  else
-    swiglu_fwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
+  swiglu_fwd2_kernel<<<blocks_for(T * (F / 8) / 2 + 1, 256, device), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, F, ld_gu, act);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
@@ -545,14 +499,9 @@ FT_API int ft_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long T,
   FT_REQUIRE(dy && gu && dgu, "ft_swiglu_bwd: null pointer");
   FT_REQUIRE(F % 8 == 0 && ld_gu % 8 == 0, "ft_swiglu_bwd: F must be a multiple of 8");
   if (T <= 0) return FT_E_OK;
-  if (mem_variant() != 0)
-    swiglu_bwd2_kernel<<<blocks_for(T * (F / 8) / 2 + 1, 256, device), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
-        static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
-  else
-    swiglu_bwd_kernel<<<blocks_for(T * (F / 8), 256, device), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
-        static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
+  swiglu_bwd2_kernel<<<blocks_for(T * (F / 8) / 2 + 1, 256, device), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
+      static_cast<__nv_bfloat16*>(dgu), T, F, ld_gu, act);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return FT_E_OK;
@@ -603,16 +552,21 @@ FT_API int ft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, 
                    "with caller-provided scratch", H, FT_NOALLOC_RMSNORM_MAX_H);
     return FT_E_TOO_LARGE;
   }
+  // The kernels below launch on the calling thread's current device, and the scratch address
+  // belongs to `device`: the two must be the same GPU.  (Checked, not switched: switching would
+  // have to be undone on every error path, and a caller that cannot allocate usually also wants
+  // no hidden device changes.)
+  int cur = -1;
+  FT_CUDA_CHECK(cudaGetDevice(&cur));
+  FT_REQUIRE(cur == device, "ft_rmsnorm_bwd_noalloc: device %d must be the current device (current is %d)",
+             device, cur);
   if (rows <= 0) return FT_E_OK;
-  // once per device, with that device current: resolve the device address of the array
+  // Once per device, with that device current: resolve the device address of the array.  Two
+  // threads that race here both store the same value, so the unsynchronised write is benign.
   static float* scratch_of[64] = {nullptr};
   if (!scratch_of[device]) {
-    int prev = -1;
-    FT_CUDA_CHECK(cudaGetDevice(&prev));
-    if (prev != device) FT_CUDA_CHECK(cudaSetDevice(device));
     float* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_rmsnorm_noalloc_scratch);
-    if (prev != device) cudaSetDevice(prev);
     if (e != cudaSuccess || !ptr) {
       set_last_error("ft_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return FT_E_CUDA;

@@ -335,7 +335,7 @@ FT_API int ft_adamw_flat(float* master, float* m, float* v, const void* grad, vo
   const uintptr_t align = reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(grad) |
                           reinterpret_cast<uintptr_t>(p_lp);
-  if (ft::mem_variant() != 0 && n % 8 == 0 && (align & 15) == 0)
+  if (n % 8 == 0 && (align & 15) == 0)
     adamw_flat8_kernel<<<flat_grid(n >> 1, device), 256, 0, stream>>>(
         master, m, v, grad, static_cast<__nv_bfloat16*>(p_lp), n, grad_f32, grad_scale, a);
   else

@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import json
 import os
-import pickle
 import socket
 import struct
 import threading
@@ -30,22 +29,49 @@ from .backend import Group, SizeMismatch
 # --------------------------------------------------------------------------- sharded checkpoints
 def save_distributed(directory: str, local_state: dict[str, torch.Tensor], shard_dims: dict[str, int | None],
                      group: Group | None = None, rank: int | None = None, world_size: int | None = None,
-                     extra: dict | None = None) -> None:
+                     extra: dict | None = None, sizes: dict[str, list[int]] | None = None) -> None:
     """``shard_dims[name]`` = dimension along which ``local_state[name]`` is this rank's shard, or
-    ``None`` for a replicated tensor (saved by rank 0 only)."""
+    ``None`` for a replicated tensor (saved by rank 0 only).
+
+    Shards may be uneven (after an elastic reload on a world size that does not divide the
+    tensor).  The metadata records every rank's size along the shard dimension
+    (``shard_sizes``, as the reference does: checkpoint.rs:107-140): gathered through ``group``,
+    or given as ``sizes[name]`` when there is no group; with neither, shards are taken to be even.
+    Every rank also writes its own sizes next to its shard (``shard_{r}.sizes.json``), which the
+    loader prefers, so a directory written without a group still reshards correctly."""
     rank = group.rank if group is not None else (rank or 0)
     world = group.world_size if group is not None else (world_size or 1)
     os.makedirs(directory, exist_ok=True)
     mine = {k: v for k, v in local_state.items() if shard_dims.get(k) is not None or rank == 0}
     save_safetensors(mine, os.path.join(directory, "shard_%d.safetensors" % rank))
+    sharded = sorted(k for k in local_state if shard_dims.get(k) is not None)
+    local_sizes = {k: int(local_state[k].shape[shard_dims[k]]) for k in sharded}
+    with open(os.path.join(directory, "shard_%d.sizes.json" % rank), "w") as f:
+        json.dump(local_sizes, f)
+    all_sizes: dict[str, list[int]] | None = None
+    if sizes is not None:
+        all_sizes = {k: [int(x) for x in sizes[k]] for k in sharded}
+    elif group is not None and world > 1 and sharded:
+        mine_t = torch.tensor([local_sizes[k] for k in sharded], dtype=torch.int64,
+                              device=local_state[sharded[0]].device)
+        gathered = group.all_gather(mine_t)
+        rows = gathered.view(world, len(sharded)) if isinstance(gathered, torch.Tensor) else torch.stack(list(gathered))
+        rows = rows.cpu()
+        all_sizes = {k: [int(rows[r, i]) for r in range(world)] for i, k in enumerate(sharded)}
     if rank == 0:
         specs = {}
         for k, v in local_state.items():
             d = shard_dims.get(k)
             gs = list(v.shape)
+            spec = {"shard_dim": d, "dtype": str(v.dtype)}
             if d is not None:
-                gs[d] *= world
-            specs[k] = {"global_shape": gs, "shard_dim": d, "dtype": str(v.dtype)}
+                per_rank = all_sizes[k] if all_sizes is not None else [gs[d]] * world
+                if len(per_rank) != world:
+                    raise SizeMismatch("%s: %d shard sizes for a world of %d" % (k, len(per_rank), world))
+                gs[d] = sum(per_rank)
+                spec["shard_sizes"] = per_rank
+            spec["global_shape"] = gs
+            specs[k] = spec
         with open(os.path.join(directory, "metadata.json"), "w") as f:
             json.dump({"world_size": world, "tensors": specs, "extra": extra or {}}, f, indent=1)
     if group is not None:
@@ -97,6 +123,13 @@ def load_distributed(directory: str, rank: int, world_size: int, device="cpu", u
                 st.update(load_safetensors(shard_file(0), device, key_filter=lambda k: k in rep))
         return st, extra
     shards = [load_safetensors(shard_file(r), "cpu") for r in range(saved)]
+    side = None
+    side_paths = [os.path.join(directory, "shard_%d.sizes.json" % r) for r in range(saved)]
+    if all(os.path.exists(pth) for pth in side_paths):
+        side = []
+        for pth in side_paths:
+            with open(pth) as f:
+                side.append(json.load(f))
     out = {}
     for name, spec in specs.items():
         d = spec["shard_dim"]
@@ -108,6 +141,10 @@ def load_distributed(directory: str, rank: int, world_size: int, device="cpu", u
                 raise KeyError("tensor %r missing from the shard of rank %d" % (name, r))
         full = torch.cat([sh[name] for sh in shards], dim=d)
         want = spec.get("full_shape") or spec.get("global_shape")
+        if side is not None and want is not None:
+            # sizes written by the ranks themselves win over what rank 0 could know at save time
+            want = list(want)
+            want[d] = sum(int(sz[name]) for sz in side)
         if want is not None and list(full.shape) != list(want):
             raise SizeMismatch("%s: shards add up to %s, metadata says %s" % (name, list(full.shape), list(want)))
         out[name] = _take(full, d, rank, world_size, name, uneven).to(device)
@@ -193,23 +230,100 @@ def all_gather_async(group: Group, t: torch.Tensor) -> PendingCollective:
 # --------------------------------------------------------------------------- RPC
 MAX_RPC_MSG_SIZE = 1 << 30
 
+# Wire format (little endian), following the reference's frames (rpc.rs:141-234):
+#   request : u64 request id | u32 name length | name (utf-8) | u64 payload length | payload
+#   response: u64 request id | u8 status (0 ok, 1 error) | u64 payload length | payload
+# The payload is data only: a JSON document for the structure (None, bool, int, float, str, list,
+# tuple, dict with string keys) in which tensors and byte strings are references to raw blobs
+# appended after it.  Nothing on the wire can name code, so a peer cannot make the agent run
+# anything but its registered handlers.
+_DTYPES = {str(d): d for d in (torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int8,
+                               torch.uint8, torch.int16, torch.int32, torch.int64, torch.bool)}
 
-def _send_msg(sock: socket.socket, payload: bytes) -> None:
-    if len(payload) > MAX_RPC_MSG_SIZE:
-        raise SizeMismatch("RPC message of %d bytes exceeds the 1 GiB cap" % len(payload))
-    sock.sendall(struct.pack("<Q", len(payload)) + payload)
+
+def _encode(obj) -> bytes:
+    blobs: list[bytes] = []
+
+    def enc(o):
+        if o is None or isinstance(o, (bool, int, float, str)):
+            return o
+        if isinstance(o, torch.Tensor):
+            t = o.detach().cpu().contiguous()
+            if str(t.dtype) not in _DTYPES:
+                raise TypeError("RPC cannot carry a tensor of dtype %s" % t.dtype)
+            blobs.append(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            return {"__t": len(blobs) - 1, "dtype": str(t.dtype), "shape": list(t.shape)}
+        if isinstance(o, (bytes, bytearray, memoryview)):
+            blobs.append(bytes(o))
+            return {"__b": len(blobs) - 1}
+        if isinstance(o, tuple):
+            return {"__tuple": [enc(x) for x in o]}
+        if isinstance(o, list):
+            return [enc(x) for x in o]
+        if isinstance(o, dict):
+            if not all(isinstance(k, str) for k in o):
+                raise TypeError("RPC dictionaries need string keys")
+            return {"__d": {k: enc(v) for k, v in o.items()}}
+        raise TypeError("RPC cannot carry a value of type %s" % type(o).__name__)
+
+    doc = json.dumps(enc(obj)).encode()
+    out = [struct.pack("<QI", len(doc), len(blobs)), doc]
+    for bl in blobs:
+        out.append(struct.pack("<Q", len(bl)))
+        out.append(bl)
+    return b"".join(out)
 
 
-def _recv_msg(sock: socket.socket) -> bytes:
-    hdr = b""
-    while len(hdr) < 8:
-        c = sock.recv(8 - len(hdr))
-        if not c:
-            raise ConnectionError("peer closed")
-        hdr += c
-    (n,) = struct.unpack("<Q", hdr)
-    if n > MAX_RPC_MSG_SIZE:
-        raise SizeMismatch("RPC frame of %d bytes exceeds the 1 GiB cap" % n)
+def _decode(buf: bytes):
+    if len(buf) < 12:
+        raise SizeMismatch("RPC payload of %d bytes is too short" % len(buf))
+    n_doc, n_blobs = struct.unpack_from("<QI", buf, 0)
+    pos = 12
+    if n_doc > len(buf) - pos:
+        raise SizeMismatch("RPC payload: document length %d exceeds the frame" % n_doc)
+    doc = json.loads(buf[pos:pos + n_doc].decode())
+    pos += n_doc
+    blobs = []
+    for _ in range(n_blobs):
+        if pos + 8 > len(buf):
+            raise SizeMismatch("RPC payload: truncated blob table")
+        (n,) = struct.unpack_from("<Q", buf, pos)
+        pos += 8
+        if n > len(buf) - pos:
+            raise SizeMismatch("RPC payload: blob of %d bytes exceeds the frame" % n)
+        blobs.append(buf[pos:pos + n])
+        pos += n
+
+    def blob(i):
+        if not isinstance(i, int) or not 0 <= i < len(blobs):
+            raise SizeMismatch("RPC payload: blob index %r out of range" % (i,))
+        return blobs[i]
+
+    def dec(o):
+        if isinstance(o, list):
+            return [dec(x) for x in o]
+        if isinstance(o, dict):
+            if "__t" in o:
+                dt = _DTYPES.get(o.get("dtype"))
+                if dt is None:
+                    raise TypeError("RPC payload: unknown dtype %r" % (o.get("dtype"),))
+                raw = blob(o["__t"])
+                shape = [int(x) for x in o["shape"]]
+                t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dt) if raw else torch.empty(0, dtype=dt)
+                return t.reshape(shape)
+            if "__b" in o:
+                return blob(o["__b"])
+            if "__tuple" in o:
+                return tuple(dec(x) for x in o["__tuple"])
+            if "__d" in o:
+                return {k: dec(v) for k, v in o["__d"].items()}
+            raise TypeError("RPC payload: unknown node %r" % (sorted(o),))
+        return o
+
+    return dec(doc)
+
+
+def _recv_exact(sock: socket.socket, n: int) -> bytes:
     buf = bytearray()
     while len(buf) < n:
         c = sock.recv(min(1 << 20, n - len(buf)))
@@ -217,6 +331,39 @@ def _recv_msg(sock: socket.socket) -> bytes:
             raise ConnectionError("peer closed")
         buf += c
     return bytes(buf)
+
+
+def _recv_len(sock: socket.socket) -> int:
+    (n,) = struct.unpack("<Q", _recv_exact(sock, 8))
+    if n > MAX_RPC_MSG_SIZE:
+        raise SizeMismatch("RPC frame of %d bytes exceeds the 1 GiB cap" % n)
+    return n
+
+
+def _send_request(sock: socket.socket, req_id: int, name: str, payload: bytes) -> None:
+    if len(payload) > MAX_RPC_MSG_SIZE:
+        raise SizeMismatch("RPC message of %d bytes exceeds the 1 GiB cap" % len(payload))
+    nm = name.encode()
+    sock.sendall(struct.pack("<QI", req_id, len(nm)) + nm + struct.pack("<Q", len(payload)) + payload)
+
+
+def _recv_request(sock: socket.socket):
+    req_id, n_name = struct.unpack("<QI", _recv_exact(sock, 12))
+    if n_name > 4096:
+        raise SizeMismatch("RPC handler name of %d bytes" % n_name)
+    name = _recv_exact(sock, n_name).decode()
+    return req_id, name, _recv_exact(sock, _recv_len(sock))
+
+
+def _send_response(sock: socket.socket, req_id: int, ok: bool, payload: bytes) -> None:
+    if len(payload) > MAX_RPC_MSG_SIZE:
+        raise SizeMismatch("RPC message of %d bytes exceeds the 1 GiB cap" % len(payload))
+    sock.sendall(struct.pack("<QBQ", req_id, 0 if ok else 1, len(payload)) + payload)
+
+
+def _recv_response(sock: socket.socket):
+    req_id, status = struct.unpack("<QB", _recv_exact(sock, 9))
+    return req_id, status == 0, _recv_exact(sock, _recv_len(sock))
 
 
 class RpcAgent:
@@ -245,25 +392,40 @@ class RpcAgent:
 
     def _handle(self, conn):
         with conn:
+            req_id = 0
             try:
-                fn_name, args, kwargs = pickle.loads(_recv_msg(conn))
+                req_id, fn_name, payload = _recv_request(conn)
                 if fn_name not in self.handlers:
-                    res = ("err", "no handler %r on %s" % (fn_name, self.name))
+                    ok, res = False, "no handler %r on %s" % (fn_name, self.name)
                 else:
-                    res = ("ok", self.handlers[fn_name](*args, **kwargs))
+                    args, kwargs = _decode(payload)
+                    ok, res = True, self.handlers[fn_name](*args, **kwargs)
             except BaseException as e:  # noqa: BLE001
-                res = ("err", repr(e))
+                ok, res = False, repr(e)
             try:
-                _send_msg(conn, pickle.dumps(res))
+                try:
+                    body = _encode(res)
+                except TypeError as e:
+                    ok, body = False, _encode("handler result cannot be sent: %s" % e)
+                _send_response(conn, req_id, ok, body)
             except OSError:
                 pass
 
+    _next_id = [0]
+    _id_lock = threading.Lock()
+
     @staticmethod
     def rpc_sync(address, fn_name: str, *args, timeout: float = 60.0, **kwargs):
+        with RpcAgent._id_lock:
+            RpcAgent._next_id[0] += 1
+            req_id = RpcAgent._next_id[0]
         with socket.create_connection(address, timeout=timeout) as s:
-            _send_msg(s, pickle.dumps((fn_name, args, kwargs)))
-            status, val = pickle.loads(_recv_msg(s))
-        if status != "ok":
+            _send_request(s, req_id, fn_name, _encode((list(args), kwargs)))
+            got_id, ok, body = _recv_response(s)
+        if got_id != req_id:
+            raise RuntimeError("remote call %s: response for request %d, expected %d" % (fn_name, got_id, req_id))
+        val = _decode(body)
+        if not ok:
             raise RuntimeError("remote call %s failed: %s" % (fn_name, val))
         return val
 

@@ -8,7 +8,7 @@ import torch
 
 from ferrotorch_b200.models import zoo
 from ferrotorch_b200.parallel import dist_checkpoint as dc
-from ferrotorch_b200.parallel.backend import SizeMismatch
+from ferrotorch_b200.parallel.backend import SizeMismatch, run_simulated
 from ferrotorch_b200.utils import ml, text
 
 
@@ -53,6 +53,32 @@ def test_dist_checkpoint_reshard_indivisible(tmp_path):
     _save(tmp_path, 2)
     with pytest.raises(SizeMismatch):
         dc.load_distributed(str(tmp_path), 0, 3)
+
+
+def test_dist_checkpoint_uneven_world_changes_twice(tmp_path):
+    # 4 ranks -> reload uneven on 3 -> save again from the uneven shards -> reload on 2: the second
+    # save must record the real shard sizes, not rank 0's size times the world
+    full = _save(tmp_path / "a", 4)
+    three = [dc.load_distributed(str(tmp_path / "a"), r, 3, uneven=True)[0] for r in range(3)]
+    assert [t["w"].shape[0] for t in three] == [3, 3, 2]
+    for r in range(3):   # no group: every rank writes its own sizes beside its shard
+        dc.save_distributed(str(tmp_path / "b"), three[r], DIMS, rank=r, world_size=3)
+    for r in range(2):
+        st, _ = dc.load_distributed(str(tmp_path / "b"), r, 2)
+        assert torch.equal(st["w"], full["w"].chunk(2, 0)[r])
+        assert torch.equal(st["col"], full["col"].chunk(2, 1)[r])
+    # with the sizes known at save time the metadata itself carries them
+
+    def body(g):
+        dc.save_distributed(str(tmp_path / "c"), three[g.rank], DIMS, group=g)
+        return True
+
+    assert all(run_simulated(3, body))
+    meta = json.load(open(tmp_path / "c" / "metadata.json"))
+    assert meta["tensors"]["w"]["shard_sizes"] == [3, 3, 2] and meta["tensors"]["w"]["global_shape"] == [8, 6]
+    assert meta["tensors"]["col"]["shard_sizes"] == [3, 3, 2]
+    st, _ = dc.load_distributed(str(tmp_path / "c"), 1, 2)
+    assert torch.equal(st["w"], full["w"].chunk(2, 0)[1])
 
 
 def test_async_dist_checkpointer(tmp_path):
@@ -111,6 +137,23 @@ def test_rpc_agent():
         a.register("boom", lambda: 1 / 0)
         with pytest.raises(RuntimeError, match="ZeroDivisionError"):
             dc.RpcAgent.rpc_sync(a.address, "boom")
+        a.register("echo", lambda *xs, **kw: [list(xs), kw])
+        nested = {"k": (1, 2.5, None, "s", b"\x00\xff"), "t": torch.arange(6, dtype=torch.int32).view(2, 3)}
+        got = dc.RpcAgent.rpc_sync(a.address, "echo", nested, flag=True)
+        assert got[1] == {"flag": True} and got[0][0]["k"] == nested["k"]
+        assert torch.equal(got[0][0]["t"], nested["t"])
+        # the wire carries data only: an object is refused on the sending side, and bytes that
+        # are not a well-formed payload are an error reply, never executed
+        with pytest.raises(TypeError):
+            dc.RpcAgent.rpc_sync(a.address, "echo", object())
+        import pickle
+        import socket
+        import struct
+        evil = pickle.dumps((print, ("pwned",)))
+        with socket.create_connection(a.address, timeout=10) as sk:
+            sk.sendall(struct.pack("<QI", 9, 4) + b"echo" + struct.pack("<Q", len(evil)) + evil)
+            req_id, ok, body = dc._recv_response(sk)
+        assert req_id == 9 and not ok
     finally:
         a.shutdown()
 

@@ -6,8 +6,7 @@ import pytest
 import torch
 import torch.nn.functional as tF
 
-pytestmark = [pytest.mark.gpu, pytest.mark.skipif(os.environ.get("FT_TEST_NEW_PATHS") != "1",
-                                                   reason="set FT_TEST_NEW_PATHS=1 for paths that have not had a GPU run yet")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("cin,cout,k,stride,pad,dil,n,hw", [

@@ -4,8 +4,7 @@ import os
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu, pytest.mark.skipif(os.environ.get("FT_TEST_NEW_PATHS") != "1",
-                                                   reason="set FT_TEST_NEW_PATHS=1 for paths that have not had a GPU run yet")]
+pytestmark = pytest.mark.gpu
 
 
 def test_capture_guard_replays():

@@ -216,7 +216,6 @@ def test_packed_masks_round_trip_and_apply_in_place():
 
 
 @pytest.mark.gpu
-@pytest.mark.skipif(__import__("os").environ.get("FT_TEST_NEW_PATHS") != "1", reason="set FT_TEST_NEW_PATHS=1 to run")
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_packed_mask_kernel_matches_torch(dtype):
     torch.manual_seed(0)

@@ -5,8 +5,7 @@ import os
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu, pytest.mark.skipif(os.environ.get("FT_TEST_NEW_PATHS") != "1",
-                                                   reason="set FT_TEST_NEW_PATHS=1 for paths that have not had a GPU run yet")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 136, 192), (1, 8, 64), (333, 1000, 128)])

@@ -98,18 +98,15 @@ def test_engine_tensor_parallel_2_cuda_graph():
 
 
 # The Q4_0 weight format of the engine is a composition of kernels that each have their own test
-# (gather, dequant-GEMM); the composition itself has not run on a GPU yet, so these two are opt-in.
-_q4 = pytest.mark.skipif(os.environ.get("FT_TEST_NEW_PATHS") != "1", reason="set FT_TEST_NEW_PATHS=1 to run")
+# (gather, dequant-GEMM); these two check the composition.
 
 
 @pytest.mark.gpu
-@_q4
 def test_engine_q4_0_single_gpu():
     _run(1, 0, weights="q4_0")
 
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@_q4
 def test_engine_q4_0_tensor_parallel_2():
     _run(2, 29553, weights="q4_0")

@@ -62,6 +62,33 @@ def test_gemm_tile_sizes(bn):
     assert _native.device_status(0) == 0
 
 
+@pytest.mark.parametrize("bn", [-64, -128, -256])
+def test_gemm_single_cta_kernel(bn):
+    # a negative tile size selects the one-CTA kernel also for shapes the CTA-pair kernel would take
+    torch.manual_seed(-bn)
+    M, N, K = 640, 776, 328
+    a, b = _rand(M, K), _rand(N, K)
+    c = F.gemm_nt(a, b, bn=bn)
+    _assert_close(c, a.float() @ b.float().t(), rtol=1e-2, atol=0.4, what="single bn=%d" % bn)
+    assert _native.device_status(0) == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (1, 1)])
+def test_gemm_pair_kernel_long_run(a_mn, b_mn):
+    # many tiles per CTA pair (both accumulators, several ring wrap-arounds), ragged M and N edges
+    torch.manual_seed(7)
+    M, N, K = 4096 + 136, 4096 + 72, 1024 + 40
+    a = _rand(K, M).t() if a_mn else _rand(M, K)
+    b = _rand(K, N).t() if b_mn else _rand(N, K)
+    want = a.float() @ b.float().t()
+    _assert_close(F.gemm_nt(a, b), want, rtol=1e-2, atol=0.02 * math.sqrt(K), what="pair long")
+    c32 = torch.randn(M, N, device=DEV)
+    c = c32.clone()
+    F.gemm_nt(a, b, out=c, accumulate=True)
+    _assert_close(c, want + c32, rtol=1e-3, atol=0.1, what="pair accumulate fp32")
+    assert _native.device_status(0) == 0
+
+
 def test_gemm_epilogues():
     torch.manual_seed(0)
     M, N, K = 520, 776, 392

@@ -5,8 +5,7 @@ import pytest
 import torch
 import torch.nn.functional as tF
 
-pytestmark = [pytest.mark.gpu, pytest.mark.skipif(os.environ.get("FT_TEST_NEW_PATHS") != "1",
-                                                   reason="set FT_TEST_NEW_PATHS=1 for paths that have not had a GPU run yet")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("c,k,s,p,hw", [(64, 3, 2, 1, (112, 112)), (8, 2, 2, 0, (9, 7)), (72, 3, 1, 1, (13, 11)), (16, 5, 2, 2, (31, 33))])

@@ -1,6 +1,6 @@
 """The allocation-free RMSNorm backward (``ft_rmsnorm_bwd_noalloc``, csrc/ft_noalloc.h).
 
-Embedders that cannot allocate device memory at call time (code running under stream capture,
+Embedders that cannot allocate device memory at call time (memory-pool callbacks,
 out-of-memory handlers, hosts with a memory budget fixed at start-up) get this entry point; its
 scratch is a fixed array inside the library.  The test calls it through its exported C symbol,
 twice in a row with different inputs (the array is shared between calls, so a stale-scratch bug
@@ -56,16 +56,38 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         want_dx, want_dw = _regular(x, dy, w, rstd, dres)
         dx, dw = torch.empty_like(x), torch.empty(H, device="cuda", dtype=torch.float32)
         allocated = torch.cuda.memory_allocated()
+        if call == 1:
+            # the first call did the once-per-device set-up; from here on the driver's own view of
+            # free memory must not move either (it also sees a cudaMalloc made outside PyTorch)
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
         rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
                 dres.data_ptr() if dres is not None else None, dx.data_ptr(), dw.data_ptr(), rows, H, 1, 0, stream)
         assert rc == 0, _native.kernels().ft_last_error()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == allocated
+        if call == 1:
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         # same kernel and the same per-row math; only the number of partial-sum rows differs
         assert torch.equal(dx, want_dx), "call %d: dx differs" % call
         err = (dw - want_dw).abs()
         tol = 2e-2 + 2e-2 * want_dw.abs()
         assert not (err > tol).any(), "call %d: dw max err %g" % (call, float(err.max()))
+
+
+def test_noalloc_requires_its_device_to_be_current():
+    # the entry point never switches devices: naming a device that is not current is an error
+    lib, fn = _symbol()
+    x = torch.zeros(2, 64, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(2, device="cuda")
+    w = torch.ones(64, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(64, device="cuda")
+    other = torch.cuda.current_device() + 1  # need not exist: the check comes before any launch
+    rc = fn(x.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None, x.data_ptr(), dw.data_ptr(), 2, 64,
+            1, other, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    lib.ft_last_error.restype = ctypes.c_char_p
+    assert b"must be the current device" in lib.ft_last_error()
 
 
 def test_noalloc_rejects_sizes_beyond_the_fixed_scratch():
