@@ -14,9 +14,13 @@
 //               Scores are computed transposed (S^T = K Q^T), so a thread owns a key row and
 //               P^T / dS^T rows land in shared memory as K-major A operands.
 //   dQ pass:    resident = queries i (Q_i, dO_i); streamed = keys (K_c, V_c); dQ += dS K_c.
-// Per step: 2 score MMAs (128x64xD) into double-buffered TMEM, the softmax warps turn them
-// into bf16 P / dS tiles (one 128-byte swizzled row per thread), then 1-2 accumulate MMAs
-// (128xDx64) whose B operand is the streamed tile read MN-major.  All waits are bounded.
+// Per step: 2 score MMAs (128x64xD) into double-buffered TMEM; the softmax warps turn them into
+// bf16 P / dS and write those back into tensor memory over the scores they came from (each warp
+// over its own 32 score columns), and the 1-2 accumulate MMAs (128xDx64) take them from there as
+// their A operand, with the streamed tile read MN-major as B.  Nothing of P / dS touches shared
+// memory.  The softmax scale is applied once, to the accumulators in the epilogue.  In the dK/dV
+// pass the per-query lse / delta of the next block are fetched one step ahead into shared memory.
+// All waits are bounded.
 #include "ft_host.h"
 #include "ft_ptx.cuh"
 
@@ -31,15 +35,15 @@ template <int HD, bool IS_DQ>
 struct AttBwdCfg {
   static constexpr int R_TILE = AB_R * HD * 2;          // one resident operand
   static constexpr int C_TILE = AB_C * HD * 2;          // one streamed operand
-  static constexpr int PS_TILE = AB_R * AB_C * 2;       // P^T or dS tile (128 rows x 128 bytes)
-  static constexpr int N_PS = IS_DQ ? 1 : 2;
+  static constexpr int STAGES = HD == 128 ? 4 : 6;      // ring of streamed {C1, C2} pairs
   static constexpr int OFF_R = 0;
   static constexpr int OFF_C = 2 * R_TILE;
-  static constexpr int OFF_PS = OFF_C + 2 * 2 * C_TILE;                 // 2 stages x 2 operands
-  static constexpr int OFF_LD = OFF_PS + 2 * N_PS * PS_TILE;           // 2 buffers
-  static constexpr int OFF_BAR = OFF_LD + 2 * 2 * AB_C * 4;            // lse/delta, 2 buffers
+  static constexpr int OFF_LD = OFF_C + STAGES * 2 * C_TILE;           // lse/delta, 2 buffers
+  static constexpr int OFF_BAR = OFF_LD + 2 * 2 * AB_C * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  // TMEM columns: S[2] (64 each), dP[2] (64 each), accumulators of HD columns
+  // TMEM columns: S[2] (64 each), dP[2] (64 each), accumulators of HD columns.  Softmax warp
+  // `half` of a score buffer writes its 32 bf16 P (dS) columns, two per 32-bit column, into the
+  // first 16 columns of its own 32-column half of S (dP).
   static constexpr int COL_S = 0, COL_DP = 128, COL_ACC0 = 256, COL_ACC1 = 256 + HD;
 };
 
@@ -99,13 +103,14 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
   const uint32_t sbase = smem_u32(smem);
   const uint32_t sR1 = sbase + Cfg::OFF_R, sR2 = sR1 + Cfg::R_TILE;
   const uint32_t sC = sbase + Cfg::OFF_C;    // stage s: C1 at sC + s*2*C_TILE, C2 right after
-  const uint32_t sPS = sbase + Cfg::OFF_PS;  // buffer b: tiles at sPS + b*N_PS*PS_TILE
-  enum { R_FULL = 0, C_FULL = 1, C_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, P_EMPTY = 11,
-         ACC_FULL = 13, NBARS = 14 };
+  constexpr int STAGES = Cfg::STAGES;
+  enum { R_FULL = 0, C_FULL = 1, C_EMPTY = C_FULL + STAGES, S_FULL = C_EMPTY + STAGES, P_FULL = S_FULL + 2,
+         ACC_FULL = P_FULL + 2, NBARS = ACC_FULL + 1 };
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 8 * NBARS);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* ld_buf = reinterpret_cast<float*>(smem + Cfg::OFF_LD);  // [2 buffers][lse | delta][AB_C]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int batch = blockIdx.z;
@@ -141,13 +146,13 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
   if (threadIdx.x == 0) {
     *abort_word = 0;
     mbar_init(bar(R_FULL), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(C_FULL + s), 1);
       mbar_init(bar(C_EMPTY + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(S_EMPTY + s), 4 * AB_SPLIT);
       mbar_init(bar(P_FULL + s), 4 * AB_SPLIT);
-      mbar_init(bar(P_EMPTY + s), 1);
     }
     mbar_init(bar(ACC_FULL), 1);
     fence_mbar_init();
@@ -179,8 +184,8 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
         tma_load_3d(sR2 + c * (AB_R * 128), &tmR2, bar(R_FULL), head_r * HD + c * 64, r0, batch);
       }
       for (int t = 0; t < n_iter; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(bar(C_EMPTY + st), ((t >> 1) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) break;
+        const int st = t % STAGES;
+        if (!mbar_wait(bar(C_EMPTY + st), ((t / STAGES) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) break;
         const int hc = IS_DQ ? kv_head : iter_head(t);
         const int row = iter_cblk(t) * AB_C;
         const uint32_t c1 = sC + st * 2 * Cfg::C_TILE, c2 = c1 + Cfg::C_TILE;
@@ -201,10 +206,10 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
       constexpr uint32_t idesc_s = make_idesc_f16(AB_R, AB_C, 1, 0, 0);   // 128 x 64, K-major both
       constexpr uint32_t idesc_acc = make_idesc_f16(AB_R, HD, 1, 0, 1);   // 128 x HD, B MN-major
       auto issue_scores = [&](int t) {
-        const int st = t & 1;
+        const int st = t % STAGES, sb = t & 1;
         const uint32_t c1 = sC + st * 2 * Cfg::C_TILE, c2 = c1 + Cfg::C_TILE;
-        const uint32_t dS_ = tmem_base + Cfg::COL_S + st * AB_C;
-        const uint32_t dP_ = tmem_base + Cfg::COL_DP + st * AB_C;
+        const uint32_t dS_ = tmem_base + Cfg::COL_S + sb * AB_C;
+        const uint32_t dP_ = tmem_base + Cfg::COL_DP + sb * AB_C;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t ro = (kk >> 2) * (AB_R * 128) + (kk & 3) * 32;
@@ -219,7 +224,7 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
           umma_f16_ss(dP_, make_smem_desc_sw128(sR2 + ro, 16, 1024), make_smem_desc_sw128(c2 + co, 16, 1024),
                       idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(bar(S_FULL + st));
+        umma_commit(bar(S_FULL + sb));
       };
       bool ok = mbar_wait(bar(R_FULL), 0, abort_word, FT_ERR_TIMEOUT_MMA) &&
                 mbar_wait(bar(C_FULL + 0), 0, abort_word, FT_ERR_TIMEOUT_MMA);
@@ -229,38 +234,41 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
       }
       for (int t = 0; t < n_iter && ok; ++t) {
         if (t + 1 < n_iter) {
-          const int tn = t + 1, st = tn & 1;
-          ok = mbar_wait(bar(C_FULL + st), (tn >> 1) & 1, abort_word, FT_ERR_TIMEOUT_MMA) &&
-               mbar_wait(bar(S_EMPTY + st), ((tn >> 1) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA);
+          // The scores of step t+1 land in the buffer whose P / dS the MMAs of step t-1 read;
+          // those were issued in the previous iteration and the tensor core runs in issue order.
+          const int tn = t + 1;
+          ok = mbar_wait(bar(C_FULL + tn % STAGES), (tn / STAGES) & 1, abort_word, FT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
           issue_scores(tn);
         }
-        const int st = t & 1;
-        if (!mbar_wait(bar(P_FULL + st), (t >> 1) & 1, abort_word, FT_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        const int st = t % STAGES, sb = t & 1;
+        if (!mbar_wait(bar(P_FULL + sb), (t >> 1) & 1, abort_word, FT_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t c1 = sC + st * 2 * Cfg::C_TILE, c2 = c1 + Cfg::C_TILE;
-        const uint32_t ps = sPS + st * Cfg::N_PS * Cfg::PS_TILE;
-        // the streamed tile as an MN-major B operand: 64-column chunks of [64 rows x 128 B]
+        const uint32_t aP = tmem_base + Cfg::COL_S + sb * AB_C;    // P^T (dK/dV pass)
+        const uint32_t aS = tmem_base + Cfg::COL_DP + sb * AB_C;   // dS (dQ pass) / dS^T
+        // the streamed tile as an MN-major B operand: 64-column chunks of [64 rows x 128 B];
+        // A comes from tensor memory: k-step kk = 16 streamed rows = 8 columns, written by
+        // softmax warp (kk >> 1) at the start of its own 32-column half
 #pragma unroll
         for (int kk = 0; kk < AB_C / 16; ++kk) {
+          const uint32_t ao = static_cast<uint32_t>(32 * (kk >> 1) + 8 * (kk & 1));
           if constexpr (IS_DQ) {
             // dQ += dS K_c
-            umma_f16_ss(tmem_base + Cfg::COL_ACC0, make_smem_desc_sw128(ps + kk * 32, 16, 1024),
+            umma_f16_ts(tmem_base + Cfg::COL_ACC0, aS + ao,
                         make_smem_desc_sw128(c1 + kk * 2048, AB_C * 128, 1024), idesc_acc,
                         (t > 0 || kk > 0) ? 1u : 0u);
           } else {
             // dK += dS^T Q_c ; dV += P^T dO_c
-            umma_f16_ss(tmem_base + Cfg::COL_ACC0,
-                        make_smem_desc_sw128(ps + Cfg::PS_TILE + kk * 32, 16, 1024),
+            umma_f16_ts(tmem_base + Cfg::COL_ACC0, aS + ao,
                         make_smem_desc_sw128(c1 + kk * 2048, AB_C * 128, 1024), idesc_acc,
                         (t > 0 || kk > 0) ? 1u : 0u);
-            umma_f16_ss(tmem_base + Cfg::COL_ACC1, make_smem_desc_sw128(ps + kk * 32, 16, 1024),
+            umma_f16_ts(tmem_base + Cfg::COL_ACC1, aP + ao,
                         make_smem_desc_sw128(c2 + kk * 2048, AB_C * 128, 1024), idesc_acc,
                         (t > 0 || kk > 0) ? 1u : 0u);
           }
         }
-        umma_commit(bar(P_EMPTY + st));
         umma_commit(bar(C_EMPTY + st));
       }
       if (ok) umma_commit(bar(ACC_FULL));
@@ -270,6 +278,7 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
     const int half = (warp - 4) >> 2;    // which 32 of the 64 score columns this warp handles
     const int r = ew * 32 + lane;
     const int grow = r0 + r;             // global row on the resident side
+    const int sidx = threadIdx.x - 128;  // 0..255 among the softmax threads
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
     float my_lse = INFINITY, my_delta = 0.f;
     if constexpr (IS_DQ) {
@@ -279,31 +288,29 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
         my_delta = p.delta[idx];
       }
     }
-    const bool vec_ok = (p.Sq & 3) == 0;
+    // dK/dV pass: the statistics of the streamed queries.  Softmax threads 0..127 fetch the 64
+    // lse and 64 delta values of step t+1 while step t is computed and publish them in shared
+    // memory; a named barrier of the 256 softmax threads separates the writes from the reads.
+    // Every softmax thread runs every iteration down to that barrier, also after a failed wait
+    // (its later waits then fail at once), so the barrier can never be left short of arrivals.
+    auto fetch_stat = [&](int t) -> float {
+      const int j = sidx & (AB_C - 1);
+      const int col = iter_cblk(t) * AB_C + j;
+      if (col >= p.Sq) return sidx < AB_C ? INFINITY : 0.f;
+      const long long idx = (static_cast<long long>(batch) * p.Hq + iter_head(t)) * p.Sq + col;
+      return sidx < AB_C ? __ldg(p.lse + idx) : __ldg(p.delta + idx);
+    };
+    if constexpr (!IS_DQ) {
+      if (sidx < 2 * AB_C && n_iter > 0) ld_buf[sidx] = fetch_stat(0);
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
     bool ok = true;
-    for (int t = 0; t < n_iter && ok; ++t) {
-      const int st = t & 1;
+    for (int t = 0; t < n_iter; ++t) {
+      const int sb = t & 1;
       const int c0 = iter_cblk(t) * AB_C + half * 32;  // first global column of this thread
-      // statistics of the 32 columns (dK/dV pass: columns are queries)
-      float lse_c[32], delta_c[32];
+      float next_stat = 0.f;
       if constexpr (!IS_DQ) {
-        const long long idx = (static_cast<long long>(batch) * p.Hq + iter_head(t)) * p.Sq + c0;
-        if (vec_ok && c0 + 32 <= p.Sq) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(p.lse + idx) + i);
-            const float4 b = __ldg(reinterpret_cast<const float4*>(p.delta + idx) + i);
-            lse_c[4 * i] = a.x; lse_c[4 * i + 1] = a.y; lse_c[4 * i + 2] = a.z; lse_c[4 * i + 3] = a.w;
-            delta_c[4 * i] = b.x; delta_c[4 * i + 1] = b.y; delta_c[4 * i + 2] = b.z; delta_c[4 * i + 3] = b.w;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const bool in = c0 + i < p.Sq;
-            lse_c[i] = in ? __ldg(p.lse + idx + i) : INFINITY;
-            delta_c[i] = in ? __ldg(p.delta + idx + i) : 0.f;
-          }
-        }
+        if (sidx < 2 * AB_C && t + 1 < n_iter) next_stat = fetch_stat(t + 1);
       }
       // does any element of this 128 x 32 slab need masking?  (uniform per warp)
       bool need_mask;
@@ -313,57 +320,58 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
       } else {
         need_mask = (r0 + ew * 32 + 31 >= p.Sk) || (p.causal && r0 + ew * 32 + 31 > c0 + p.causal_offset);
       }
-      if (!mbar_wait(bar(S_FULL + st), (t >> 1) & 1, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t a[32], b[32];
-      tmem_ld_32x32(lane_addr + Cfg::COL_S + st * AB_C + half * 32, a);
-      tmem_ld_32x32(lane_addr + Cfg::COL_DP + st * AB_C + half * 32, b);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(S_EMPTY + st));
-
-      uint32_t pk[16], dk[16];
+      if (ok && !mbar_wait(bar(S_FULL + sb), (t >> 1) & 1, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(lane_addr + Cfg::COL_S + sb * AB_C + half * 32, a);
+        tmem_ld_32x32(lane_addr + Cfg::COL_DP + sb * AB_C + half * 32, b);
+        tmem_ld_wait();
+        const float* st_lse = ld_buf + sb * 2 * AB_C + half * 32;
+        const float* st_delta = st_lse + AB_C;
+        uint32_t pk[16], dk[16];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float pv[2], dv[2];
+        for (int c = 0; c < 32; c += 4) {
+          float lse4[4], delta4[4];
+          if constexpr (IS_DQ) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float lse_v = IS_DQ ? my_lse : lse_c[c + e];
-          const float delta_v = IS_DQ ? my_delta : delta_c[c + e];
-          float pe = fast_exp2(fmaf(__uint_as_float(a[c + e]), p.scale_log2, -lse_v));
-          if (need_mask) {
-            const int col = c0 + c + e;
-            const bool visible = IS_DQ ? (col < p.Sk && (!p.causal || col <= grow + p.causal_offset))
-                                       : (grow < p.Sk && (!p.causal || grow <= col + p.causal_offset));
-            pe = visible ? pe : 0.f;
+            for (int e = 0; e < 4; ++e) { lse4[e] = my_lse; delta4[e] = my_delta; }
+          } else {
+            const float4 l4 = *reinterpret_cast<const float4*>(st_lse + c);
+            const float4 d4 = *reinterpret_cast<const float4*>(st_delta + c);
+            lse4[0] = l4.x; lse4[1] = l4.y; lse4[2] = l4.z; lse4[3] = l4.w;
+            delta4[0] = d4.x; delta4[1] = d4.y; delta4[2] = d4.z; delta4[3] = d4.w;
           }
-          pv[e] = pe;
-          dv[e] = pe * (__uint_as_float(b[c + e]) - delta_v) * p.scale;
-        }
-        pk[c >> 1] = pack_bf16x2(pv[0], pv[1]);
-        dk[c >> 1] = pack_bf16x2(dv[0], dv[1]);
-      }
-      // the P / dS buffers of this stage must have been consumed by the MMAs of step t-2
-      if (!mbar_wait(bar(P_EMPTY + st), ((t >> 1) & 1) ^ 1u, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
-      const uint32_t ps = sPS + st * Cfg::N_PS * Cfg::PS_TILE;
+          float pv[4], dv[4];
 #pragma unroll
-      for (int uu = 0; uu < 4; ++uu) {
-        const int u = half * 4 + uu;
-        const uint32_t off = r * 128 + ((u ^ (r & 7)) << 4);
-        if constexpr (IS_DQ) {
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + off), "r"(dk[uu * 4]),
-                       "r"(dk[uu * 4 + 1]), "r"(dk[uu * 4 + 2]), "r"(dk[uu * 4 + 3]) : "memory");
-        } else {
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + off), "r"(pk[uu * 4]),
-                       "r"(pk[uu * 4 + 1]), "r"(pk[uu * 4 + 2]), "r"(pk[uu * 4 + 3]) : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + Cfg::PS_TILE + off),
-                       "r"(dk[uu * 4]), "r"(dk[uu * 4 + 1]), "r"(dk[uu * 4 + 2]), "r"(dk[uu * 4 + 3]) : "memory");
+          for (int e = 0; e < 4; ++e) {
+            float pe = fast_exp2(fmaf(__uint_as_float(a[c + e]), p.scale_log2, -lse4[e]));
+            if (need_mask) {
+              const int col = c0 + c + e;
+              const bool visible = IS_DQ ? (col < p.Sk && (!p.causal || col <= grow + p.causal_offset))
+                                         : (grow < p.Sk && (!p.causal || grow <= col + p.causal_offset));
+              pe = visible ? pe : 0.f;
+            }
+            pv[e] = pe;
+            dv[e] = pe * (__uint_as_float(b[c + e]) - delta4[e]);  // the softmax scale is applied in the epilogue
+          }
+          pk[c >> 1] = pack_bf16x2(pv[0], pv[1]);
+          pk[(c >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
+          dk[c >> 1] = pack_bf16x2(dv[0], dv[1]);
+          dk[(c >> 1) + 1] = pack_bf16x2(dv[2], dv[3]);
         }
+        // P / dS over the first 16 columns of this warp's own 32 score columns
+        if constexpr (!IS_DQ) tmem_st_32x16(lane_addr + Cfg::COL_S + sb * AB_C + half * 32, pk);
+        tmem_st_32x16(lane_addr + Cfg::COL_DP + sb * AB_C + half * 32, dk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_FULL + sb));
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL + st));
+      if constexpr (!IS_DQ) {
+        if (sidx < 2 * AB_C && t + 1 < n_iter) ld_buf[(sb ^ 1) * 2 * AB_C + sidx] = next_stat;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      }
     }
     // ---------------------------------------------------------------- epilogue
     if (ok && n_iter > 0) {
@@ -379,6 +387,7 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
         __nv_bfloat16* orow = (acc == 0 ? p.out0 + tok * p.ld0 : p.out1 + tok * p.ld1) +
                               static_cast<long long>(head_r) * HD;
         const uint32_t col = acc == 0 ? Cfg::COL_ACC0 : Cfg::COL_ACC1;
+        const float osc = acc == 0 ? p.scale : 1.f;  // dQ and dK carry the softmax scale, dV does not
         // the two warps of a lane quarter split the HD columns
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {
@@ -395,10 +404,10 @@ flash_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(t32[g * 8 + 0]), __uint_as_float(t32[g * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(t32[g * 8 + 2]), __uint_as_float(t32[g * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(t32[g * 8 + 4]), __uint_as_float(t32[g * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(t32[g * 8 + 6]), __uint_as_float(t32[g * 8 + 7]));
+              o.x = pack_bf16x2(__uint_as_float(t32[g * 8 + 0]) * osc, __uint_as_float(t32[g * 8 + 1]) * osc);
+              o.y = pack_bf16x2(__uint_as_float(t32[g * 8 + 2]) * osc, __uint_as_float(t32[g * 8 + 3]) * osc);
+              o.z = pack_bf16x2(__uint_as_float(t32[g * 8 + 4]) * osc, __uint_as_float(t32[g * 8 + 5]) * osc);
+              o.w = pack_bf16x2(__uint_as_float(t32[g * 8 + 6]) * osc, __uint_as_float(t32[g * 8 + 7]) * osc);
               *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
             }
           }

@@ -91,6 +91,8 @@ class FlatTrainer:
     update kernel from a device-side coefficient.
     ``micro_batches``: the batch given to :meth:`step` is split into this many sequential
     forward/backward passes whose gradients accumulate in the arena.
+    ``grad_dtype``: dtype of the gradient arena; default fp32 when ``micro_batches > 2`` (the
+    weight-gradient GEMMs then add their tiles in fp32), else the parameter dtype.
     """
 
     def __init__(self, model: nn.Module, *, optimizer: str = "adamw", lr: float = 1e-3,
@@ -98,7 +100,8 @@ class FlatTrainer:
                  momentum: float = 0.0, dampening: float = 0.0, nesterov: bool = False,
                  max_grad_norm: float | None = None, micro_batches: int = 1,
                  no_decay: Callable[[str, nn.Parameter], bool] | None = None,
-                 loss_fn: Callable | None = None, ddp=None, allocator: Callable | None = None):
+                 loss_fn: Callable | None = None, ddp=None, allocator: Callable | None = None,
+                 grad_dtype: torch.dtype | None = None):
         self.model = model
         self.kind = optimizer
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
@@ -107,7 +110,13 @@ class FlatTrainer:
         self.micro_batches = micro_batches
         self.loss_fn = loss_fn
         nd = no_decay or (lambda name, p: p.dim() < 2)
-        self.arena = FlatArena(model, lambda n, p: "no_decay" if nd(n, p) else "decay", allocator=allocator)
+        if grad_dtype is None:
+            # every micro-batch adds into the arena; beyond two additions a bf16 arena would round
+            # away most of a late micro-batch's contribution, so the sum is kept in fp32
+            first = next(p for p in model.parameters() if p.requires_grad)
+            grad_dtype = torch.float32 if micro_batches > 2 else first.dtype
+        self.arena = FlatArena(model, lambda n, p: "no_decay" if nd(n, p) else "decay", allocator=allocator,
+                               grad_dtype=grad_dtype)
         a = self.arena
         self.master = a.params.float()
         self.exp_avg = torch.zeros_like(self.master) if optimizer != "sgd" or momentum != 0.0 else None

@@ -29,6 +29,11 @@ def _close(got, want, atol, rtol, what):
     (1, 1024, 1024, 8, 2, 128, True),
     (2, 256, 256, 4, 4, 64, True),
     (1, 130, 190, 2, 2, 64, False),
+    (1, 2048, 2048, 4, 2, 128, True),   # many key blocks per CTA: lazy rescale, ring wrap-arounds
+    (1, 640, 640, 2, 1, 128, True),     # odd number of query tiles: the last CTA has one tile only
+    (2, 513, 513, 4, 2, 128, True),
+    (1, 300, 700, 2, 2, 64, True),
+    (1, 1024, 1024, 2, 2, 64, False),
 ])
 def test_flash_fwd(B, Sq, Sk, Hq, Hkv, D, causal):
     torch.manual_seed(Sq + Sk + Hq)
@@ -39,6 +44,21 @@ def test_flash_fwd(B, Sq, Sk, Hq, Hkv, D, causal):
     want, lse_w = R.attention(q, k, v, causal)
     _close(out, want, 2e-2, 2e-2, "attention out")
     _close(lse, lse_w, 2e-2, 1e-3, "attention lse")
+
+
+def test_flash_fwd_large_scores_lazy_rescale():
+    # row maxima that keep growing along the keys (by more and by less than the lazy-rescale
+    # threshold) exercise both the rescale of O in TMEM and the stale-reference path
+    torch.manual_seed(5)
+    B, S, H, D = 1, 1024, 2, 128
+    q, k, v = _rand(B, S, H, D), _rand(B, S, H, D), _rand(B, S, H, D)
+    ramp = torch.linspace(0.2, 3.0, S, device=DEV).view(1, S, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    out, lse = F.flash_attn_fwd(q, k, v, False)
+    want, lse_w = R.attention(q, k, v, False)
+    _close(out, want, 2e-2, 2e-2, "attention out (growing maxima)")
+    _close(lse, lse_w, 2e-2, 1e-3, "attention lse (growing maxima)")
+    assert _native.device_status(0) == 0
 
 
 def test_flash_fwd_packed_qkv():
