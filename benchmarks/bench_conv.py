@@ -1,9 +1,10 @@
 #!/usr/bin/env python
 """Convolution kernel and folded-ResNet inference timings on one GPU.
 
-Per layer shape of ResNet-50 (batch 256 unless --batch): the implicit-GEMM tcgen05 kernel
-(``ops.conv``) against cuDNN through ``torch.nn.functional.conv2d``, both bf16 channels-last, CUDA
-events, an L2 flush (a 256 MiB write) between timed iterations.  With --model: images / s of
+Per layer shape of ResNet-50 (batch 256 unless --batch): this library's convolution (``ops.conv``:
+1 x 1 as a GEMM, k x k in the shifted-row form, each with its layout copies) against cuDNN through
+``torch.nn.functional.conv2d``, forward and forward + backward (all three gradients), both bf16
+channels-last, CUDA events, an L2 flush (a 256 MiB write) between timed iterations.  With --model: images / s of
 ``FusedInferenceResNet`` (batch norm folded, bias / shortcut / ReLU in the convolution epilogue)
 against the eval-mode model.  One JSON line per measurement.
 
@@ -63,12 +64,25 @@ def main():
             pad = k // 2
             ho = C.out_size(hw, k, stride, pad, 1)
             flops = 2.0 * a.batch * ho * ho * cout * cin * k * k
+            xg, wg = x.clone().requires_grad_(), w.clone().requires_grad_()
+            gy = torch.randn(a.batch, cout, ho, ho, device=dev, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+
+            def fwd_bwd(fn):
+                xg.grad = wg.grad = None
+                fn(xg, wg).backward(gy)
+
             C.use_native_conv(True)
             ours = timed(lambda: C.conv2d(x, w, None, stride, pad))
+            ours_fb = timed(lambda: fwd_bwd(lambda p, q: C.conv2d(p, q, None, stride, pad)))
+            gather = timed(lambda: C.conv2d_gather(x, w, None, stride, pad)) if k > 1 else None
             C.use_native_conv(False)
             lib = timed(lambda: F.conv2d(x, w, None, stride, pad))
-            print(json.dumps({"bench": "conv2d_fprop", "cin": cin, "cout": cout, "k": k, "stride": stride, "hw": hw, "batch": a.batch,
-                              "igemm_ms": ours, "cudnn_ms": lib, "igemm_tflops": flops / ours / 1e9, "cudnn_tflops": flops / lib / 1e9,
+            lib_fb = timed(lambda: fwd_bwd(lambda p, q: F.conv2d(p, q, None, stride, pad)))
+            print(json.dumps({"bench": "conv2d", "path": C.native_path(x, w, stride, pad, 1), "cin": cin, "cout": cout, "k": k,
+                              "stride": stride, "hw": hw, "batch": a.batch, "fwd_ms": ours, "cudnn_fwd_ms": lib,
+                              "fwd_bwd_ms": ours_fb, "cudnn_fwd_bwd_ms": lib_fb, "gather_kernel_fwd_ms": gather,
+                              "fwd_tflops": flops / ours / 1e9, "cudnn_fwd_tflops": flops / lib / 1e9,
+                              "fwd_bwd_tflops": 3 * flops / ours_fb / 1e9, "cudnn_fwd_bwd_tflops": 3 * flops / lib_fb / 1e9,
                               "l2_flush": "256 MiB write"}), flush=True)
         return
     model = R.resnet50().to(dev).bfloat16().to(memory_format=torch.channels_last).eval()
@@ -80,11 +94,7 @@ def main():
         folded = timed(lambda: fused(x))
         C.use_native_conv(True)
         native = timed(lambda: fused(x))
-        from ferrotorch_b200.ops import pool as P
-
-        P.use_native_pool(True)
-        native_pool = timed(lambda: fused(x))
-    for name, ms in (("eval_model", base), ("folded_cudnn", folded), ("folded_igemm", native), ("folded_igemm_nhwc_pool", native_pool)):
+    for name, ms in (("eval_model", base), ("folded_cudnn", folded), ("folded_native", native)):
         print(json.dumps({"bench": "resnet50_inference", "variant": name, "batch": a.batch, "ms": ms,
                           "images_per_s": a.batch / ms * 1e3, "dtype": "bf16", "l2_flush": "256 MiB write"}), flush=True)
 

@@ -59,6 +59,8 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+constexpr int GEMM_MAX_TAPS = 49;  // up to a 7 x 7 filter
+
 struct GemmParams {
   void* C;
   const void* bias;
@@ -66,6 +68,16 @@ struct GemmParams {
   long long ldc;
   int flags;
   int* status;
+  // Shifted-row GEMMs (convolutions over zero-padded, flattened NHWC activations; see
+  // gemm_bf16_pair_kernel).  taps == 0: plain GEMM.
+  int taps;                  // filter taps
+  int cblocks;               // 64-channel k-blocks per tap (fprop: K = taps * cblocks * 64)
+  int ksplit;                // filter gradient: pieces the pixel dimension is cut into
+  int shift[GEMM_MAX_TAPS];  // row offset of tap t in the flattened padded activation
+  // MODE 1 output: GEMM row p = (n * gHp + i) * gWp + j is written to row
+  // (n * cHo + i - c_oh) * cWo + j - c_ow of C when (i - c_oh, j - c_ow) lies inside the
+  // cHo x cWo window, and dropped otherwise (cHo == 0: rows are stored as they are).
+  int gHp, gWp, cHo, cWo, c_oh, c_ow;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
@@ -158,6 +170,71 @@ __device__ __forceinline__ void epilogue_direct(const GemmParams& p, uint32_t t_
           o.y = pack_bf16x2(vv[2], vv[3]);
           o.z = pack_bf16x2(vv[4], vv[5]);
           o.w = pack_bf16x2(vv[6], vv[7]);
+          *reinterpret_cast<uint4*>(crow + g * 8) = o;
+        }
+      }
+    }
+  }
+}
+
+
+// MODE 1 epilogue with the crop folded in: one accumulator row per lane, written to its pixel's
+// row of the unpadded NHWC output (rows of the padded border are dropped).  bias / activation as
+// in the other epilogues; no accumulation.
+template <int BN>
+__device__ __forceinline__ void epilogue_crop(const GemmParams& p, uint32_t t_row, int row, int n0) {
+  const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
+  const bool has_bias = (p.flags & (GEMM_BIAS | GEMM_BIAS_F32)) != 0;
+  const bool has_act = (p.flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
+  bool row_ok = row < p.M;
+  long long dst_row = 0;
+  {
+    const int plane = p.gHp * p.gWp;
+    const int n = row / plane;
+    const int r = row - n * plane;
+    const int i = r / p.gWp - p.c_oh, j = r - (r / p.gWp) * p.gWp - p.c_ow;
+    row_ok = row_ok && i >= 0 && i < p.cHo && j >= 0 && j < p.cWo;
+    dst_row = (static_cast<long long>(n) * p.cHo + i) * p.cWo + j;
+  }
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (!row_ok || col0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (has_bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        if (col < p.N)
+          v[j] += (p.flags & GEMM_BIAS_F32) ? static_cast<const float*>(p.bias)[col]
+                                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+      }
+    }
+    if (has_act) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.flags);
+    }
+    if (out_f32) {
+      float* crow = static_cast<float*>(p.C) + dst_row * p.ldc + col0;
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        if (col0 + g * 4 + 4 <= p.N)
+          *reinterpret_cast<float4*>(crow + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+    } else {
+      __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.C) + dst_row * p.ldc + col0;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col0 + g * 8 + 8 <= p.N) {
+          uint4 o;
+          o.x = pack_bf16x2(v[g * 8], v[g * 8 + 1]);
+          o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+          o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+          o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
           *reinterpret_cast<uint4*>(crow + g * 8) = o;
         }
       }
@@ -351,6 +428,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 // tile of its own in shared memory and hands the tile to a TMA store (or a TMA reduce-add for
 // C += ...).  Two staging tiles per warp keep one store in flight while the next is filled; the
 // stores clip at the M and N edges.
+//
+// MODE 1 and 2 turn the same pipeline into a convolution over activations stored zero-padded and
+// flattened to [pixels, channels] (NHWC): in that layout the input pixel a filter tap reads
+// for output pixel p is row p + shift[tap], a constant offset, so
+//   MODE 1 (forward / input gradient): C[p, co] = sum_tap sum_ci A[p + shift[tap], ci] * W[co, tap, ci]
+//          is a GEMM whose A tile of k-block (tap, 64 channels) is an ordinary 2-D TMA box at row
+//          m0 + shift[tap] (rows before the first or past the last pixel read as zeros);
+//   MODE 2 (filter gradient): dW[co, tap, ci] += sum_p dY[p, co] * X[p + shift[tap], ci], one
+//          [Cout x Cin] GEMM per tap with the pixels as the (split) contraction dimension, both
+//          operands MN-major, tiles added into an fp32 dW with the TMA reduce-add epilogue.
+// Rows of the padded border hold zeros in the input of MODE 1 / in dY of MODE 2, and the caller
+// drops the border rows of a MODE 1 output.
 template <int BN>
 struct PairCfg {
   static constexpr int BNH = BN / 2;
@@ -377,7 +466,43 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int m_blocks, int n_b
   nb = r / gm;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// Work item of a CTA pair: output block, contraction range and (MODE 2) the filter tap.
+struct PairTile {
+  int mb, nb, kb_begin, kb_end, tap;
+};
+
+template <int BN, int MODE>
+__device__ __forceinline__ int pair_num_tiles(const GemmParams& p, int m_blocks, int n_blocks) {
+  return MODE == 2 ? m_blocks * n_blocks * p.taps * p.ksplit : m_blocks * n_blocks;
+}
+
+template <int MODE>
+__device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int tile, int m_blocks, int n_blocks,
+                                              int k_blocks) {
+  PairTile t;
+  if constexpr (MODE == 2) {
+    // pixel range slowest: the tiles that run together read the same rows of dY and X
+    const int mn = m_blocks * n_blocks;
+    const int per_ks = mn * p.taps;
+    const int ks = tile / per_ks;
+    const int r = tile - ks * per_ks;
+    t.tap = r / mn;
+    const int q = r - t.tap * mn;
+    t.mb = q % m_blocks;
+    t.nb = q / m_blocks;
+    const int per = (k_blocks + p.ksplit - 1) / p.ksplit;
+    t.kb_begin = ks * per;
+    t.kb_end = min(k_blocks, t.kb_begin + per);
+  } else {
+    pair_tile_coords(tile, m_blocks, n_blocks, t.mb, t.nb);
+    t.kb_begin = 0;
+    t.kb_end = k_blocks;
+    t.tap = 0;
+  }
+  return t;
+}
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -407,8 +532,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   const int m_blocks = (p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
   const int n_blocks = (p.N + BN - 1) / BN;
-  const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int num_tiles = pair_num_tiles<BN, MODE>(p, m_blocks, n_blocks);
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -444,11 +569,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        int mb, nb;
-        pair_tile_coords(tile, m_blocks, n_blocks, mb, nb);
-        const int m0 = mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM;
-        const int n0 = nb * BN + static_cast<int>(rank) * BNH;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const PairTile t = pair_tile<MODE>(p, tile, m_blocks, n_blocks, k_blocks);
+        const int m0 = t.mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM;
+        const int n0 = t.nb * BN + static_cast<int>(rank) * BNH;
+        for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word, FT_ERR_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
@@ -459,7 +583,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (leader) mbar_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
           const uint32_t fb = mapa_shared(full_bar(stage), 0);
           const int k0 = kb * GEMM_BK;
-          if constexpr (!A_MN) {
+          if constexpr (MODE == 1) {
+            // k-block = (tap, 64 channels): A rows shifted by the tap's offset in the padded image
+            const int tap = kb / p.cblocks;
+            tma_load_2d_pair(sA, &tmA, fb, (kb - tap * p.cblocks) * GEMM_BK, m0 + p.shift[tap]);
+          } else if constexpr (!A_MN) {
             tma_load_2d_pair(sA, &tmA, fb, k0, m0);
           } else {
 #pragma unroll
@@ -469,9 +597,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if constexpr (!B_MN) {
             tma_load_2d_pair(sB, &tmB, fb, k0, n0);
           } else {
+            // MODE 2: the pixels of X that tap t pairs with the pixels [k0, k0 + 64) of dY
+            const int kx = MODE == 2 ? k0 + p.shift[t.tap] : k0;
 #pragma unroll
             for (int c = 0; c < BNH / 64; ++c)
-              tma_load_2d_pair(sB + c * (GEMM_BK * 128), &tmB, fb, n0 + c * 64, k0);
+              tma_load_2d_pair(sB + c * (GEMM_BK * 128), &tmB, fb, n0 + c * 64, kx);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -494,10 +624,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const PairTile t = pair_tile<MODE>(p, tile, m_blocks, n_blocks, k_blocks);
         if (!mbar_wait_cluster(tempty_bar(acc), acc_phase ^ 1u, abort_word, FT_ERR_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = t.kb_begin; kb < t.kb_end; ++kb) {
           if (!mbar_wait_cluster(full_bar(stage), phase, abort_word, FT_ERR_TIMEOUT_MMA)) {
             ok = false;
             break;
@@ -511,7 +642,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                         : make_smem_desc_sw128(sA + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sB + k * 2048, GEMM_BK * 128, 1024)
                                         : make_smem_desc_sw128(sB + k * 32, 16, 1024);
-            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage), 3);
           if (++stage == STAGES) {
@@ -538,15 +669,20 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t stage_tiles = smem_u32(epi) + static_cast<uint32_t>(ew) * 2u * Cfg::EPI_TILE_BYTES;
     int buf = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs) {
-      int mb, nb;
-      pair_tile_coords(tile, m_blocks, n_blocks, mb, nb);
-      const int m0 = mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM + ew * 32;
-      const int n0 = nb * BN;
+      const PairTile t = pair_tile<MODE>(p, tile, m_blocks, n_blocks, k_blocks);
+      const int m0 = t.mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM + ew * 32;
+      const int n0 = t.nb * BN;
+      const int c_off = MODE == 2 ? t.tap * p.N : 0;  // dW[co, tap, ci]: tap t starts at column t * Cin
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-      if (direct) {
+      if (MODE == 1 && p.cHo > 0) {
+        epilogue_crop<BN>(p, t_row, m0 + lane, n0);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
+      } else if (direct) {
         epilogue_direct<BN>(p, t_row, m0 + lane, n0);
         tc_fence_before();
         __syncwarp();
@@ -622,9 +758,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           __syncwarp();
           if (lane == 0) {
             if (accumulate)
-              tma_reduce_add_2d(&tmC, tile_s, col0, m0);
+              tma_reduce_add_2d(&tmC, tile_s, c_off + col0, m0);
             else
-              tma_store_2d(&tmC, tile_s, col0, m0);
+              tma_store_2d(&tmC, tile_s, c_off + col0, m0);
             tma_store_commit();
           }
           buf ^= 1;
@@ -649,11 +785,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int MODE = 0>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const GemmParams& p, int device, int max_ctas, cudaStream_t stream) {
   using Cfg = PairCfg<BN>;
-  auto kern = gemm_bf16_pair_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_pair_kernel<BN, A_MN, B_MN, MODE>;
   static bool attr_set[64] = {false};
   if (!attr_set[device]) {
     FT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -662,7 +798,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   }
   const int m_blocks = (p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
   const int n_blocks = (p.N + BN - 1) / BN;
-  int pairs = m_blocks * n_blocks;
+  int pairs = m_blocks * n_blocks * (MODE == 2 ? p.taps * p.ksplit : 1);
   int sms = sm_count(device);
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   if (pairs > sms / 2) pairs = sms / 2;
@@ -747,6 +883,8 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
   GemmParams p;
   p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags;
   p.status = device_status_word(device);
+  p.taps = 0; p.cblocks = 0; p.ksplit = 1;
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0;
 
   // Problems with at least one full 256-row block and N >= 128 run on the CTA-pair kernel.
   if (!force_single && M >= 2 * GEMM_BM && N >= 128 && (bn == 0 || bn >= 128)) {
@@ -806,4 +944,114 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
     case 64: return dispatch_major<64>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
     default: return dispatch_major<32>(a_mn_major, b_mn_major, tmA, tmB, p, device, max_ctas, stream);
   }
+}
+
+// Convolution as a shifted-row GEMM (MODE 1 of the CTA-pair kernel).  xp: the input, zero-padded
+// and flattened to [P, Cin] bf16 (P = images * padded height * padded width; row stride ldx
+// elements), w: the filter as [Cout, taps * Cin] bf16 (OHWI order: tap-major, channel-minor),
+// y: [P, Cout] bf16 (flags & 1: fp32) in the same padded pixel numbering -- rows that are padding
+// hold values the caller drops.  shift[t]: row offset of tap t, e.g. (kh - pad_h) * Wp + (kw -
+// pad_w) for a stride-1 filter.  xp has x_rows >= P rows (more when shifts reach into further
+// planes of a stride-2 parity split).  bias / ReLU flags as in ft_gemm_bf16.  Cin % 64 == 0,
+// Cout % 8 == 0.  crop (optional): {Hp, Wp, Ho, Wo, oh, ow} -- the GEMM rows form [images, Hp, Wp]
+// grids and only the Ho x Wo window at (oh, ow) of each is written, densely, as [images, Ho, Wo,
+// Cout]; y then has images * Ho * Wo rows.
+FT_API int ft_conv_shift_gemm(const void* xp, const void* w, void* y, const void* bias, long long P,
+                              long long x_rows, int Cin, int Cout, int taps, const int* shift, long long ldx,
+                              long long ldy, int flags, const int* crop, int max_ctas, int device,
+                              cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  using namespace ft;
+  FT_REQUIRE(xp && w && y && shift, "ft_conv_shift_gemm: null pointer");
+  FT_REQUIRE(P > 0 && P < (1ll << 31) - 65536 && Cin > 0 && Cin % 64 == 0 && Cout > 0 && Cout % 8 == 0,
+             "ft_conv_shift_gemm: bad shape P=%lld Cin=%d Cout=%d", P, Cin, Cout);
+  FT_REQUIRE(taps >= 1 && taps <= GEMM_MAX_TAPS, "ft_conv_shift_gemm: %d taps (1..%d)", taps, GEMM_MAX_TAPS);
+  const bool out_f32 = flags & GEMM_OUT_F32;
+  FT_REQUIRE(ldx % 8 == 0 && ldy % (out_f32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0,
+             "ft_conv_shift_gemm: strides / output must be 16-byte aligned");
+  FT_REQUIRE(!(flags & GEMM_ACCUMULATE), "ft_conv_shift_gemm: accumulation is not supported");
+  FT_REQUIRE(!(flags & (GEMM_BIAS | GEMM_BIAS_F32)) || bias, "ft_conv_shift_gemm: bias flag without bias");
+  GemmParams p;
+  p.C = y; p.bias = bias; p.M = static_cast<int>(P); p.N = Cout; p.K = taps * Cin; p.ldc = ldy;
+  p.flags = flags & 0xFFFF;
+  p.status = device_status_word(device);
+  p.taps = taps; p.cblocks = Cin / GEMM_BK; p.ksplit = 1;
+  for (int t = 0; t < GEMM_MAX_TAPS; ++t) p.shift[t] = t < taps ? shift[t] : 0;
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0;
+  long long y_rows = P;
+  if (crop) {
+    p.gHp = crop[0]; p.gWp = crop[1]; p.cHo = crop[2]; p.cWo = crop[3]; p.c_oh = crop[4]; p.c_ow = crop[5];
+    FT_REQUIRE(p.gHp > 0 && p.gWp > 0 && p.cHo > 0 && p.cWo > 0 && p.c_oh >= 0 && p.c_ow >= 0 &&
+                   p.cHo + p.c_oh <= p.gHp && p.cWo + p.c_ow <= p.gWp && P % (static_cast<long long>(p.gHp) * p.gWp) == 0,
+               "ft_conv_shift_gemm: the crop window does not fit the %d x %d grid", p.gHp, p.gWp);
+    y_rows = P / (static_cast<long long>(p.gHp) * p.gWp) * p.cHo * p.cWo;
+  }
+  const int bn = Cout >= 256 ? 256 : (Cout > 64 ? 128 : 64);
+  CUtensorMap tmA, tmB, tmC;
+  FT_REQUIRE(x_rows >= P && x_rows < (1ll << 31), "ft_conv_shift_gemm: x_rows=%lld must be >= P=%lld", x_rows, P);
+  int rc = make_tmap_2d(&tmA, xp, 2, Cin, x_rows, ldx * 2, GEMM_BK, GEMM_BM, 3);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, w, 2, static_cast<uint64_t>(taps) * Cin, Cout, static_cast<uint64_t>(taps) * Cin * 2,
+                    GEMM_BK, bn / 2, 3);
+  if (rc) return rc;
+  rc = out_f32 ? make_tmap_2d(&tmC, y, 4, Cout, y_rows, ldy * 4, 32, 32, 3)
+               : make_tmap_2d(&tmC, y, 2, Cout, y_rows, ldy * 2, 64, 32, 3);
+  if (rc) return rc;
+  if (bn == 256) return launch_pair<256, false, false, 1>(tmA, tmB, tmC, p, device, max_ctas, stream);
+  if (bn == 128) return launch_pair<128, false, false, 1>(tmA, tmB, tmC, p, device, max_ctas, stream);
+  return launch_pair<64, false, false, 1>(tmA, tmB, tmC, p, device, max_ctas, stream);
+}
+
+// Filter gradient of the same convolution (MODE 2): dw[Cout, taps * Cin] (fp32) +=
+// sum_p dyp[p, co] * xp[p + shift[t], ci].  dyp: [P, Cout] bf16 with zeros in the padding rows,
+// xp: [P, Cin] bf16.  The pixel dimension is cut into `ksplit` pieces (0 = chosen here) whose
+// tiles are added into dw by the memory system, so the summation order, and with it the last
+// bits of dw, can differ from run to run.  Cout % 64 == 0; Cin % 64 == 0 (Cin % 8 == 0 suffices
+// for a single tap, i.e. a plain dY^T X product with the pixels as the split contraction).
+FT_API int ft_conv_shift_wgrad(const void* dyp, const void* xp, float* dw, long long P, long long x_rows,
+                               int Cin, int Cout, int taps, const int* shift, long long lddy, long long ldx,
+                               int ksplit, int max_ctas, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  using namespace ft;
+  FT_REQUIRE(dyp && xp && dw && shift, "ft_conv_shift_wgrad: null pointer");
+  // with several taps, tap t's columns start at t * Cin and a 64-wide B chunk must not straddle them
+  FT_REQUIRE(P > 0 && P < (1ll << 31) - 65536 && Cin > 0 && Cin % (taps > 1 ? 64 : 8) == 0 && Cout > 0 &&
+                 Cout % 64 == 0,
+             "ft_conv_shift_wgrad: bad shape P=%lld Cin=%d Cout=%d", P, Cin, Cout);
+  FT_REQUIRE(taps >= 1 && taps <= GEMM_MAX_TAPS, "ft_conv_shift_wgrad: %d taps (1..%d)", taps, GEMM_MAX_TAPS);
+  FT_REQUIRE(lddy % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(dw) & 15) == 0,
+             "ft_conv_shift_wgrad: strides / output must be 16-byte aligned");
+  GemmParams p;
+  p.C = dw; p.bias = nullptr; p.M = Cout; p.N = Cin; p.K = static_cast<int>(P);
+  p.ldc = static_cast<long long>(taps) * Cin;
+  p.flags = GEMM_OUT_F32 | GEMM_ACCUMULATE;
+  p.status = device_status_word(device);
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0;
+  p.taps = taps; p.cblocks = Cin / GEMM_BK;
+  for (int t = 0; t < GEMM_MAX_TAPS; ++t) p.shift[t] = t < taps ? shift[t] : 0;
+  const int bn = Cin >= 256 ? 256 : 128;
+  const int k_blocks = static_cast<int>((P + GEMM_BK - 1) / GEMM_BK);
+  if (ksplit <= 0) {
+    const int pairs = (max_ctas > 0 && max_ctas < sm_count(device) ? max_ctas : sm_count(device)) / 2;
+    const int mn = ((Cout + 255) / 256) * ((Cin + bn - 1) / bn) * taps;
+    ksplit = (2 * pairs + mn - 1) / mn;          // about two tiles per CTA pair
+    const int max_split = k_blocks / 8 > 0 ? k_blocks / 8 : 1;  // at least 8 k-blocks per tile
+    if (ksplit > max_split) ksplit = max_split;
+    if (ksplit < 1) ksplit = 1;
+  }
+  if (ksplit > k_blocks) ksplit = k_blocks;
+  // no piece may be empty: an empty piece would add an unwritten accumulator into dw
+  const int per = (k_blocks + ksplit - 1) / ksplit;
+  p.ksplit = (k_blocks + per - 1) / per;
+  CUtensorMap tmA, tmB, tmC;
+  int rc = make_tmap_2d(&tmA, dyp, 2, Cout, P, lddy * 2, 64, GEMM_BK, 3);
+  if (rc) return rc;
+  FT_REQUIRE(x_rows >= P && x_rows < (1ll << 31), "ft_conv_shift_wgrad: x_rows=%lld must be >= P=%lld", x_rows, P);
+  rc = make_tmap_2d(&tmB, xp, 2, Cin, x_rows, ldx * 2, 64, GEMM_BK, 3);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmC, dw, 4, static_cast<uint64_t>(taps) * Cin, Cout, static_cast<uint64_t>(taps) * Cin * 4,
+                    32, 32, 3);
+  if (rc) return rc;
+  if (bn == 256) return launch_pair<256, true, true, 2>(tmA, tmB, tmC, p, device, max_ctas, stream);
+  return launch_pair<128, true, true, 2>(tmA, tmB, tmC, p, device, max_ctas, stream);
 }

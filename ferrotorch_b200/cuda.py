@@ -368,6 +368,49 @@ def _gpu_op_table() -> dict:
             return getattr(ops_f, name)(*a, **kw)
         return call
 
+    def _bf16_cuda(*ts):
+        return all(isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
+
+    def matmul(a, b):
+        # bf16 matrices on a GPU: this library's tcgen05 GEMM (b is read as stored, no transposed copy)
+        if _bf16_cuda(a, b) and a.dim() == 2 and b.dim() == 2:
+            from .ops import functional as ops_f
+
+            return ops_f.gemm_nt(a, b.t())
+        return torch.matmul(a, b)
+
+    def matmul_nt(a, b):
+        if _bf16_cuda(a, b) and a.dim() == 2 and b.dim() == 2:
+            from .ops import functional as ops_f
+
+            return ops_f.gemm_nt(a, b)
+        return a @ b.transpose(-1, -2)
+
+    def flash_attention(q, k, v, causal=False):
+        # [batch, heads, seq, head_dim] in and out, as the reference's launcher takes them
+        if _bf16_cuda(q, k, v) and q.dim() == 4 and q.shape[-1] in (64, 128) and q.shape[1] % k.shape[1] == 0:
+            from .ops.attention import flash_attention as fa
+
+            return fa(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=causal).transpose(1, 2)
+        return F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+
+    def conv2d(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
+        from .ops.conv import conv2d as own_conv2d    # falls back to the library for shapes it does not take
+
+        return own_conv2d(x, w, bias, stride, padding, dilation, groups)
+
+    def embedding(w, ids):
+        if _bf16_cuda(w) and ids.is_cuda:
+            from .ops import functional as ops_f
+
+            return ops_f.embedding(ids, w)
+        return F.embedding(ids, w)
+
+    def max_pool2d(x, kernel_size, stride=None, padding=0):
+        from .ops.pool import max_pool2d as own_pool
+
+        return own_pool(x, kernel_size, stride, padding)
+
     return {
         "add": torch.add, "sub": torch.sub, "mul": torch.mul, "neg": torch.neg, "relu": torch.relu, "gelu": F.gelu,
         "silu": F.silu, "softmax": lambda x, dim=-1: torch.softmax(x, dim), "dropout": F.dropout,
@@ -375,23 +418,24 @@ def _gpu_op_table() -> dict:
         "broadcast_add": torch.add, "broadcast_sub": torch.sub, "broadcast_mul": torch.mul,
         "div_rounding": lambda a, b, mode=None: torch.div(a, b, rounding_mode=mode), "broadcast_div_rounding":
         lambda a, b, mode=None: torch.div(a, b, rounding_mode=mode),
-        "matmul": torch.matmul, "matmul_nt": lambda a, b: a @ b.transpose(-1, -2), "bmm": torch.bmm, "small_matmul": torch.matmul,
-        "small_bmm": torch.bmm, "matmul_bf16_bf16": torch.matmul, "matmul_bf16_bf16_nt": native("gemm_nt"),
+        "matmul": matmul, "matmul_nt": matmul_nt, "bmm": torch.bmm, "small_matmul": matmul,
+        "small_bmm": torch.bmm, "matmul_bf16_bf16": matmul, "matmul_bf16_bf16_nt": native("gemm_nt"),
+        "swiglu": native("swiglu"), "maxpool2d": max_pool2d,
         "matmul_bf16_bf16_strided_batched": torch.bmm, "matmul_f16_f16_strided_batched": torch.bmm,
         "matmul_bf16_bf16_strided_batched_nt": lambda a, b: torch.bmm(a, b.transpose(1, 2)),
         "broadcast_bmm_bf16_bf16": torch.matmul, "broadcast_bmm_f16_f16": torch.matmul,
         "layernorm": lambda x, w, b, eps=1e-5: F.layer_norm(x, x.shape[-1:], w, b, eps), "rmsnorm": native("rmsnorm"),
         "group_norm": lambda x, g, w=None, b=None, eps=1e-5: F.group_norm(x, g, w, b, eps),
         "local_response_norm": F.local_response_norm, "rope_half": native("rope_"), "fatrelu": lambda x, t: torch.where(x > t, x, torch.zeros_like(x)),
-        "embed_lookup": lambda w, ids: F.embedding(ids, w), "embedding_gather": lambda w, ids: F.embedding(ids, w),
+        "embed_lookup": embedding, "embedding_gather": embedding,
         "embedding_gather_bf16_to": lambda w, ids: F.embedding(ids, w).float(),
         "transpose_2d": lambda x: x.t().contiguous(), "permute_0213": lambda x: x.permute(0, 2, 1, 3).contiguous(),
         "transpose_to_heads": lambda x, h: x.reshape(x.shape[0], h, -1).transpose(0, 1).contiguous(),
         "transpose_from_heads": lambda x: x.transpose(0, 1).reshape(x.shape[1], -1).contiguous(),
         "repeat_kv": lambda x, n, dim=0: x.repeat_interleave(n, dim), "repeat_interleave": torch.repeat_interleave,
         "causal_mask": lambda s: s.masked_fill(torch.ones(s.shape[-2:], dtype=torch.bool, device=s.device).triu(1 + s.shape[-1] - s.shape[-2]), float("-inf")),
-        "flash_attention": lambda q, k, v, causal=False: F.scaled_dot_product_attention(q, k, v, is_causal=causal),
-        "conv2d": F.conv2d, "nearest_upsample2x": lambda x: F.interpolate(x, scale_factor=2, mode="nearest"),
+        "flash_attention": flash_attention,
+        "conv2d": conv2d, "nearest_upsample2x": lambda x: F.interpolate(x, scale_factor=2, mode="nearest"),
         "flip": torch.flip, "roll": torch.roll, "histc": torch.histc, "searchsorted": torch.searchsorted,
         "topk": lambda x, k, largest=True: tuple(torch.topk(x, k, -1, largest)), "topk_nd": lambda x, k, dim=-1, largest=True: tuple(torch.topk(x, k, dim, largest)),
         "unique": torch.unique, "unique_consecutive": torch.unique_consecutive, "meshgrid": lambda *t: torch.meshgrid(*t, indexing="ij"),

@@ -1,8 +1,11 @@
 """ResNet-18 / 34 / 50 (ferrotorch-vision/src/models/resnet.rs:325 ``Bottleneck``, :565 ``ResNet``,
 :1071 ``resnet50``) and a small model registry (models/registry.rs).
 
-Convolutions are torch.nn (cuDNN, channels-last); every batch norm runs fused with the ReLU and
-the residual add that follow it (``ops/batchnorm.py``: two reads and one write of the activation
+Convolutions are ``nn.Conv2d`` modules re-classed to :class:`ops.conv.IgemmConv2d`: on a GPU with
+bf16 activations their forward and all three gradients run on this library's tcgen05 GEMM kernels
+(1 x 1 as plain GEMMs, k x k in the shifted-row form, the 3-channel stem through an im2col
+matrix; ``ops/conv.py``), the max pool on the NHWC kernel of ``ops/pool.py``; every batch norm
+runs fused with the ReLU and the residual add that follow it (``ops/batchnorm.py``: two reads and one write of the activation
 in the forward, no stored ReLU mask); the data-parallel gradient exchange and the SGD update run
 through the fused ``ft_ddp_reduce_update`` kernel when trained with ``FlatTrainer`` + ``FusedDDP``.  State-dict
 keys match torchvision's (``conv1.weight``, ``layer1.0.conv1.weight``, ``fc.weight`` ...).
@@ -13,6 +16,8 @@ import torch
 from torch import nn
 
 from ..ops.batchnorm import batch_norm_act as _bn
+from ..ops.conv import convert_convs as _convert_convs
+from ..ops.pool import MaxPool2d as _MaxPool2d
 
 
 def _downsample(seq: nn.Sequential, x: torch.Tensor) -> torch.Tensor:
@@ -69,7 +74,7 @@ class ResNet(nn.Module):
         self.conv1 = nn.Conv2d(3, 64, 7, 2, 3, bias=False)
         self.bn1 = nn.BatchNorm2d(64)
         self.relu = nn.ReLU(inplace=True)
-        self.maxpool = nn.MaxPool2d(3, 2, 1)
+        self.maxpool = _MaxPool2d(3, 2, 1)
         self.layer1 = self._make_layer(block, 64, layers[0])
         self.layer2 = self._make_layer(block, 128, layers[1], 2, replace_stride_with_dilation[0])
         self.layer3 = self._make_layer(block, 256, layers[2], 2, replace_stride_with_dilation[1])
@@ -88,6 +93,7 @@ class ResNet(nn.Module):
                     nn.init.zeros_(m.bn3.weight)
                 elif isinstance(m, BasicBlock):
                     nn.init.zeros_(m.bn2.weight)
+        _convert_convs(self)     # same parameters and state-dict keys; forward through ops.conv.conv2d
 
     def _make_layer(self, block, planes, blocks, stride=1, dilate=False):
         prev_dilation = self.dilation

@@ -4,7 +4,7 @@ deterministic, no atomics, neither the input nor a comparison needed.  The refer
 on the GPU in NCHW f32 and backward on the host (ferrotorch-gpu/src/kernels.rs:11265, 11410).
 
 Tensors keep torch's logical NCHW shape in ``channels_last`` memory format.  The native path needs
-CUDA, bf16 and ``C % 8 == 0``; it is opt-in (:func:`use_native_pool` or ``FT_POOL_NHWC=1``) and
+CUDA, bf16 and ``C % 8 == 0``; it is on by default (:func:`use_native_pool` or ``FT_POOL_NHWC=0`` switch it off) and
 ``torch.nn.functional.max_pool2d`` serves everything else.  :func:`max_pool2d_host` runs the
 kernels' window functions on the CPU (the library's host entry point) for the tests.
 """
@@ -26,7 +26,7 @@ _native.register_protos({
     "ft_maxpool2d_host": (_i, [_vp] * 5 + [_i] * 9),
 })
 
-_enabled = os.environ.get("FT_POOL_NHWC") == "1"
+_enabled = os.environ.get("FT_POOL_NHWC", "1") != "0"
 CL = torch.channels_last
 
 

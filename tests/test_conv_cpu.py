@@ -32,6 +32,63 @@ def test_input_gradient_is_a_convolution_with_the_flipped_filter(k, pad, dil):
     torch.testing.assert_close(C.implicit_gemm_reference(gy, wt, 1, bp, dil), ref, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("stride,pad,dil", [(1, 1, 1), (2, 1, 1), (1, 2, 2), (2, 0, 1), (1, (1, 2), 1)])
+def test_shifted_row_arithmetic_equals_conv2d(stride, pad, dil):
+    torch.manual_seed(3)
+    x, w = torch.randn(2, 8, 9, 10), torch.randn(4, 8, 3, 3)
+    torch.testing.assert_close(C.shift_conv_reference(x, w, stride, pad, dil), tF.conv2d(x, w, None, stride, pad, dil),
+                               rtol=1e-4, atol=1e-4)
+
+
+def _grads_against_torch(fn, cin, cout, k, stride, pad, dil, hw):
+    torch.manual_seed(cin + cout + k + stride)
+    x = torch.randn(2, cin, *hw).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(cout, cin, k, k) / (cin * k * k) ** 0.5).to(torch.bfloat16)
+    b = torch.randn(cout).to(torch.bfloat16)
+    xr, wr, br = x.float().requires_grad_(), w.float().requires_grad_(), b.float().requires_grad_()
+    ref = tF.conv2d(xr, wr, br, stride, pad, dil)
+    gy = torch.randn_like(ref)
+    ref.backward(gy)
+    xn, wn, bn = x.clone().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    y = fn(xn, wn, bn)
+    y.backward(gy.to(y.dtype))
+    for got, want, what in ((y, ref, "y"), (xn.grad, xr.grad, "dx"), (wn.grad, wr.grad, "dw"), (bn.grad, br.grad, "db")):
+        err = float((got.float() - want.detach()).abs().max() / (want.detach().abs().max() + 1e-6))
+        assert err < 1e-2, "%s: relative error %.3g" % (what, err)
+
+
+# The autograd functions run on CPU tensors through torch restatements of the layout kernels and
+# of the shifted-row GEMMs, so the grid / parity-plane / tap-shift arithmetic of all three
+# gradients is checked here against torch's convolution.
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,hw", [
+    (64, 64, 3, 1, 1, 1, (9, 7)), (64, 128, 3, 2, 1, 1, (10, 11)), (64, 64, 3, 2, 1, 1, (8, 8)),
+    (64, 64, 3, 1, 2, 2, (9, 9)), (64, 64, 7, 2, 3, 1, (15, 13)), (64, 64, 5, 2, 2, 1, (11, 12)),
+    (64, 64, 3, 1, 0, 1, (7, 7)), (64, 64, 3, 2, 0, 1, (9, 10)), (64, 64, 2, 2, 0, 1, (8, 8)), (64, 64, 3, 1, (1, 2), 1, (6, 9)),
+])
+def test_shift_conv_function_gradients(cin, cout, k, stride, pad, dil, hw):
+    _grads_against_torch(lambda x, w, b: C._ShiftConv.apply(x, w, b, stride, C._pair(pad), dil, False),
+                         cin, cout, k, stride, pad, dil, hw)
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_pointwise_conv_function_gradients(stride):
+    _grads_against_torch(lambda x, w, b: C._PointwiseConv.apply(x, w, b, stride, False), 64, 72, 1, stride, 0, 1, (8, 7))
+
+
+def test_im2col_conv_function_gradients():
+    _grads_against_torch(lambda x, w, b: C._Im2colConv.apply(x, w, b, 2, (3, 3), 1, False), 3, 16, 7, 2, 3, 1, (15, 13))
+
+
+def test_native_path_selection():
+    x = torch.empty(1, 64, 8, 8, dtype=torch.bfloat16)
+    assert C.native_path(x, torch.empty(64, 64, 3, 3), 1, 1, 1) is None            # CPU tensors: library
+    g = C.ShiftGeometry(2, 56, 56, 3, 3, 2, 1, 1, 1)
+    assert (g.Hp, g.Wp, g.planes, g.Ho, g.Wo) == (29, 29, 4, 28, 28) and g.x_rows == 4 * g.P
+    assert g.shifts()[4] == 3 * g.P and g.shifts()[8] == 29 + 1                     # tap (1,1): plane 3; tap (2,2): plane 0
+    g1 = C.ShiftGeometry(1, 7, 7, 3, 3, 1, 1, 1, 1)
+    assert g1.shifts() == [0, 1, 2, 9, 10, 11, 18, 19, 20]
+
+
 def test_fallback_module_and_rewrite():
     torch.manual_seed(2)
     net = torch.nn.Sequential(torch.nn.Conv2d(8, 16, 3, 1, 1), torch.nn.ReLU(), torch.nn.Conv2d(16, 4, 1, bias=False))

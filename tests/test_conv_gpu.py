@@ -1,70 +1,168 @@
-"""Implicit-GEMM convolution kernel against torch's conv2d in fp32 (forward, fused epilogue, input
-gradient on the same kernel).  First GPU run of this kernel is opt-in."""
-import os
-
+"""Convolution on this library's GEMM kernels against torch's conv2d in fp32: the three native
+paths (1 x 1 as GEMM, shifted-row k x k with stride 1 / 2, im2col for the stem), forward and all
+gradients; the older gather-based kernel; a ResNet-50 training step with no library convolution."""
 import pytest
 import torch
 import torch.nn.functional as tF
 
 pytestmark = pytest.mark.gpu
 
+CL = torch.channels_last
 
-@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,n,hw", [
-    (64, 64, 1, 1, 0, 1, 4, (56, 56)), (64, 64, 3, 1, 1, 1, 4, (56, 56)), (128, 128, 3, 2, 1, 1, 2, (28, 28)),
-    (256, 72, 3, 1, 2, 2, 1, (15, 17)), (512, 2048, 1, 1, 0, 1, 2, (7, 7)), (64, 136, 3, 1, 1, 1, 3, (9, 5)),
-])
-def test_forward_matches_torch(cin, cout, k, stride, pad, dil, n, hw):
-    from ferrotorch_b200.ops import conv as C
 
-    torch.manual_seed(0)
-    x = torch.randn(n, cin, *hw, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+def _case(cin, cout, k, n, hw, seed=0):
+    torch.manual_seed(seed)
+    x = torch.randn(n, cin, *hw, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=CL)
     w = (torch.randn(cout, cin, k, k, device="cuda") / (cin * k * k) ** 0.5).to(torch.bfloat16)
     b = torch.randn(cout, device="cuda", dtype=torch.bfloat16)
+    return x, w, b
+
+
+def _rel(got, want):
+    return float((got.float() - want).abs().max() / (want.abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,n,hw,path", [
+    (64, 64, 1, 1, 0, 1, 4, (56, 56), "pointwise"), (512, 2048, 1, 1, 0, 1, 2, (7, 7), "pointwise"),
+    (256, 512, 1, 2, 0, 1, 3, (28, 28), "pointwise"),
+    (64, 64, 3, 1, 1, 1, 4, (56, 56), "shift"), (128, 128, 3, 2, 1, 1, 2, (56, 56), "shift"),
+    (256, 320, 3, 1, 2, 2, 1, (15, 17), "shift"), (512, 512, 3, 1, 1, 1, 5, (7, 7), "shift"),
+    (64, 192, 5, 2, 2, 1, 2, (13, 11), "shift"), (64, 128, 3, 1, 0, 1, 3, (9, 5), "shift"),
+    (3, 64, 7, 2, 3, 1, 2, (64, 64), "im2col"), (16, 24, 3, 1, 1, 1, 2, (10, 9), "im2col"),
+])
+def test_forward_and_gradients_match_torch(cin, cout, k, stride, pad, dil, n, hw, path):
+    from ferrotorch_b200 import _native
+    from ferrotorch_b200.ops import conv as C
+
+    x, w, b = _case(cin, cout, k, n, hw)
+    assert C.native_conv_enabled() and C.native_path(x, w, stride, pad, dil) == path
+    xr, wr, br = x.float().requires_grad_(), w.float().requires_grad_(), b.float().requires_grad_()
+    ref = tF.conv2d(xr, wr, br, stride, pad, dil)
+    gy = torch.randn_like(ref)
+    ref.backward(gy)
+    xn, wn, bn = x.clone().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    before = _native.launch_count()
+    y = C.conv2d(xn, wn, bn, stride, pad, dil)
+    y.backward(gy.to(torch.bfloat16))
+    torch.cuda.synchronize()
+    assert _native.launch_count() > before and _native.device_status(0) == 0
+    assert y.is_contiguous(memory_format=CL) and y.dtype == torch.bfloat16
+    assert _rel(y, ref.detach()) < 2e-2
+    assert _rel(xn.grad, xr.grad) < 2e-2
+    assert _rel(wn.grad, wr.grad) < 2e-2
+    assert _rel(bn.grad, br.grad) < 2e-2
+
+
+def test_fused_epilogue_and_fp32_weights():
+    from ferrotorch_b200.ops import conv as C
+
+    x, w, b = _case(128, 128, 3, 2, (14, 14), seed=3)
+    ref = tF.conv2d(x.float(), w.float(), b.float(), 1, 1)
+    res = torch.randn_like(ref).to(torch.bfloat16).contiguous(memory_format=CL)
+    z = C.conv2d(x, w.float(), b.float(), 1, 1, residual=res, relu=True)   # fp32 parameters (autocast-style)
+    assert _rel(z, torch.relu(ref + res.float())) < 2e-2
+    r = C.conv2d(x, w, None, 1, 1, relu=True)
+    assert _rel(r, torch.relu(tF.conv2d(x.float(), w.float(), None, 1, 1))) < 2e-2
+
+
+def test_relu_backward():
+    from ferrotorch_b200.ops import conv as C
+
+    x, w, _ = _case(64, 128, 3, 2, (14, 14), seed=1)
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    torch.relu(tF.conv2d(xr, wr, None, 1, 1)).square().sum().backward()
+    xn, wn = x.clone().requires_grad_(), w.clone().requires_grad_()
+    C.conv2d(xn, wn, None, 1, 1, relu=True).float().square().sum().backward()
+    assert _rel(xn.grad, xr.grad) < 5e-2 and _rel(wn.grad, wr.grad) < 5e-2
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,n,hw", [
+    (64, 64, 3, 1, 1, 1, 4, (56, 56)), (128, 128, 3, 2, 1, 1, 2, (28, 28)), (256, 72, 3, 1, 2, 2, 1, (15, 17)),
+])
+def test_gather_kernel_forward(cin, cout, k, stride, pad, dil, n, hw):
+    from ferrotorch_b200.ops import conv as C
+
+    x, w, b = _case(cin, cout, k, n, hw)
     ref = tF.conv2d(x.float(), w.float(), b.float(), stride, pad, dil)
-    prev = C.use_native_conv(True)
-    try:
-        assert C.supported(x, w, stride, pad, dil)
-        y = C.conv2d(x, w, b, stride, pad, dil)
-        res = torch.randn_like(y)
-        z = C.conv2d(x, w, b, stride, pad, dil, residual=res, relu=True)
-    finally:
-        C.use_native_conv(prev)
+    y = C.conv2d_gather(x, w, b, stride, pad, dil)
+    res = torch.randn_like(y)
+    z = C.conv2d_gather(x, w, b, stride, pad, dil, residual=res, relu=True)
     torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(z.float(), torch.relu(ref + res.float()), rtol=2e-2, atol=3e-2)
 
 
-def test_backward_matches_torch():
+def _loss_and_grads(m, x, fn):
+    m.zero_grad(set_to_none=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = fn(m(x))
+    loss.backward()
+    return float(loss), {n: p.grad.detach().float().clone() for n, p in m.named_parameters()}
+
+
+def _cos(a, b):
+    a, b = a.flatten(), b.flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
+
+
+def test_bottleneck_block_gradients_match_the_library_path():
+    # one strided bottleneck (1x1, 3x3 stride 2, 1x1, projection shortcut; batch norm in training
+    # mode) with fp32 parameters under autocast: every gradient against the cuDNN path
+    from ferrotorch_b200.models import resnet as R
     from ferrotorch_b200.ops import conv as C
 
-    torch.manual_seed(1)
-    x = torch.randn(2, 64, 14, 14, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
-    w = (torch.randn(128, 64, 3, 3, device="cuda") / 24).to(torch.bfloat16)
-    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
-    torch.relu(tF.conv2d(xr, wr, None, 1, 1)).square().sum().backward()
-    xn, wn = x.clone().requires_grad_(), w.clone().requires_grad_()
-    prev = C.use_native_conv(True)
+    torch.manual_seed(4)
+    down = torch.nn.Sequential(torch.nn.Conv2d(256, 512, 1, 2, bias=False), torch.nn.BatchNorm2d(512))
+    blk = R.Bottleneck(256, 128, 2, down).cuda().to(memory_format=CL)
+    C.convert_convs(blk)
+    x = torch.randn(32, 256, 28, 28, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=CL)
+    tgt = torch.randn(32, 512, 14, 14, device="cuda")
+    fn = lambda y: (y.float() - tgt).square().mean()  # noqa: E731
+    l_native, g_native = _loss_and_grads(blk, x, fn)
+    prev = C.use_native_conv(False)
     try:
-        C.conv2d(xn, wn, None, 1, 1, relu=True).float().square().sum().backward()
+        l_lib, g_lib = _loss_and_grads(blk, x, fn)
     finally:
         C.use_native_conv(prev)
-    torch.testing.assert_close(xn.grad.float(), xr.grad, rtol=5e-2, atol=5e-2 * float(xr.grad.abs().max()))
-    torch.testing.assert_close(wn.grad.float(), wr.grad, rtol=5e-2, atol=5e-2 * float(wr.grad.abs().max()))
+    assert abs(l_native - l_lib) < 2e-2 * abs(l_lib)
+    for name in g_lib:
+        assert _cos(g_native[name], g_lib[name]) > 0.99, "%s: cosine %.4f" % (name, _cos(g_native[name], g_lib[name]))
 
 
-def test_folded_resnet_on_the_kernel_matches_eval_model():
+def test_resnet50_training_step_runs_no_library_convolution():
     from ferrotorch_b200.models import resnet as R
     from ferrotorch_b200.ops import conv as C
 
     torch.manual_seed(2)
-    m = R.resnet50(num_classes=10).cuda().bfloat16().to(memory_format=torch.channels_last).eval()
-    x = torch.randn(4, 3, 64, 64, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    m = R.resnet50(num_classes=10).cuda().to(memory_format=CL)
+    x = torch.randn(16, 3, 96, 96, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=CL)
+    t = torch.randint(0, 10, (16,), device="cuda")
+    for k in C.stats:
+        C.stats[k] = 0
+    fn = lambda logits: tF.cross_entropy(logits.float(), t)  # noqa: E731
+    l_native, g_native = _loss_and_grads(m, x, fn)
+    assert C.stats["library"] == 0 and C.stats["shift"] == 16 and C.stats["pointwise"] == 36 and C.stats["im2col"] == 1
+    assert all(torch.isfinite(g).all() for g in g_native.values())
+    prev = C.use_native_conv(False)
+    try:
+        l_lib, g_lib = _loss_and_grads(m, x, fn)
+    finally:
+        C.use_native_conv(prev)
+    assert abs(l_native - l_lib) < 0.05 * max(1.0, abs(l_lib))
+    # 53 layers of bf16 activations and small-batch batch norm amplify rounding differences on the
+    # way back, so only the classifier's gradient is compared here; the block test above and the
+    # per-layer tests compare every gradient of every path
+    assert _cos(g_native["fc.weight"], g_lib["fc.weight"]) > 0.9
+
+
+def test_folded_resnet_matches_eval_model():
+    from ferrotorch_b200.models import resnet as R
+
+    torch.manual_seed(2)
+    m = R.resnet50(num_classes=10).cuda().bfloat16().to(memory_format=CL).eval()
+    x = torch.randn(4, 3, 64, 64, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=CL)
     fused = R.fuse_for_inference(m).cuda()
     with torch.no_grad():
         ref = m(x).float()
-        prev = C.use_native_conv(True)
-        try:
-            out = fused(x).float()
-        finally:
-            C.use_native_conv(prev)
+        out = fused(x).float()
     assert torch.isfinite(out).all()
     torch.testing.assert_close(out, ref, rtol=0.1, atol=0.1 * float(ref.abs().max()))

@@ -41,6 +41,38 @@ def test_paged_decode_matches_reference(D, Hq, Hkv, splits):
         assert err < 2e-2, "seq %d len %d err %g" % (b, n, err)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("Hq,Hkv,splits,bs", [(8, 8, 2, 16), (8, 4, 1, 32), (16, 2, 4, 16), (32, 8, 0, 8), (8, 2, 2, 128)])
+def test_paged_decode_tensor_core_kernel_long_contexts(Hq, Hkv, splits, bs):
+    # head_dim 128 with a page size dividing 128 takes the tcgen05 kernel: group sizes 1 / 2 / 4 / 8,
+    # contexts long enough to wrap its three-stage ring several times, growing score maxima
+    # (lazy rescale of the accumulator), tails that end inside a page and inside a tile
+    torch.manual_seed(Hq + Hkv + splits + bs)
+    D = 128
+    lens = [1, 127, 129, 700, 1531]
+    B = len(lens)
+    cache = PagedKVCache(1, Hkv, D, num_blocks=sum((n + bs - 1) // bs for n in lens) + 4, max_seqs=B,
+                         max_seq_len=2048, block_size=bs)
+    mgr = PagedAttentionManager(cache)
+    ks, vs = [], []
+    for b, n in enumerate(lens):
+        assert mgr.add_sequence(n) == b
+        ramp = torch.linspace(0.3, 2.5, n, device="cuda").view(n, 1, 1)
+        k = (torch.randn(n, Hkv, D, device="cuda") * ramp).to(torch.bfloat16)
+        v = torch.randn(n, Hkv, D, device="cuda").to(torch.bfloat16)
+        ks.append(k), vs.append(v)
+        cache.append(0, k, v, torch.arange(n, device="cuda", dtype=torch.int32),
+                     torch.full((n,), b, device="cuda", dtype=torch.int32))
+    q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+    out = cache.decode(0, q, torch.tensor(lens, device="cuda", dtype=torch.int32), n_splits=splits)
+    torch.cuda.synchronize()
+    assert _native.device_status(0) == 0
+    for b, n in enumerate(lens):
+        want, _ = R.attention(q[b][None, None], ks[b][None], vs[b][None], causal=False)
+        err = (out[b].float() - want[0, 0].float()).abs().max().item()
+        assert err < 3e-2, "seq %d len %d err %g" % (b, n, err)
+
+
 def test_page_pool_bookkeeping():
     cache = PagedKVCache(1, 1, 8, num_blocks=4, max_seqs=2, max_seq_len=64, block_size=16, device="cpu",
                          dtype=torch.float32)
