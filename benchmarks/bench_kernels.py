@@ -145,6 +145,13 @@ def run_decode(small):
     q = r(B, Hq, D)
     lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
     emit("paged_decode B%d ctx%d" % (B, ctx), bench(lambda: cache.decode(0, q, lens)), nbytes=4.0 * B * ctx * Hkv * D)
+    # the four projections of a Llama-3-8B block at decode batch size: weight bytes / time
+    for N, K in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
+        x, w, out = r(B, K), r(N, K), torch.empty(B, N, device="cuda", dtype=torch.bfloat16)
+        nb = 2.0 * N * K + 2.0 * B * (N + K)
+        emit("gemm_small_m %dx%dx%d" % (B, N, K), bench(lambda: F.gemm_small_m(x, w, out=out)), 2.0 * B * N * K, nbytes=nb)
+        emit("gemm (128-row batch tile) %dx%dx%d" % (B, N, K), bench(lambda: F.gemm_nt(x, w, out=out, bn=-128)), 2.0 * B * N * K, nbytes=nb)
+        emit("torch.matmul %dx%dx%d" % (B, N, K), bench(lambda: torch.matmul(x, w.t(), out=out)), 2.0 * B * N * K, nbytes=nb)
 
 
 def run_quant(small):

@@ -45,6 +45,7 @@ enum GemmFlags : int {
   GEMM_GELU = 32,
   GEMM_SILU = 64,
   GEMM_EPI_DIRECT = 1 << 16,  // internal: per-lane read-modify-write epilogue
+  GEMM_EPI_TRANSPOSED = 1 << 17,  // internal: the tile holds C^T; lane = column of C, register = row of C
 };
 
 template <int BN>
@@ -78,6 +79,9 @@ struct GemmParams {
   // (n * cHo + i - c_oh) * cWo + j - c_ow of C when (i - c_oh, j - c_ow) lies inside the
   // cHo x cWo window, and dropped otherwise (cHo == 0: rows are stored as they are).
   int gHp, gWp, cHo, cWo, c_oh, c_ow;
+  // MODE 2 without accumulation: piece ks of the split contraction stores its tile at row
+  // ks * split_rows + m (one slice of the workspace per piece; summed later in a fixed order).
+  int split_rows;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
@@ -237,6 +241,41 @@ __device__ __forceinline__ void epilogue_crop(const GemmParams& p, uint32_t t_ro
           o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
           *reinterpret_cast<uint4*>(crow + g * 8) = o;
         }
+      }
+    }
+  }
+}
+
+
+// Epilogue for a tile that holds C^T (small-batch GEMMs are issued with the weight as the
+// 128-row MMA operand): accumulator row = column n of C, accumulator column = row m of C.  For
+// a fixed m the 32 lanes of a warp write 32 consecutive bf16 of row m: 64-byte segments.
+// p.M / p.N are the extents of the *tile space* (rows of W, batch), p.ldc the row stride of C.
+template <int BN>
+__device__ __forceinline__ void epilogue_transposed(const GemmParams& p, uint32_t t_row, int n_idx, int m0) {
+  const bool n_ok = n_idx < p.M;
+  const bool has_bias = (p.flags & (GEMM_BIAS | GEMM_BIAS_F32)) != 0;
+  const bool has_act = (p.flags & (GEMM_RELU | GEMM_GELU | GEMM_SILU)) != 0;
+  float bias = 0.f;
+  if (has_bias && n_ok)
+    bias = (p.flags & GEMM_BIAS_F32) ? static_cast<const float*>(p.bias)[n_idx]
+                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n_idx]);
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait();
+    if (!n_ok) continue;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int m = m0 + c * 32 + j;
+      if (m < p.N) {
+        float v = __uint_as_float(r[j]) + bias;
+        if (has_act) v = apply_act(v, p.flags);
+        if (p.flags & GEMM_OUT_F32)
+          static_cast<float*>(p.C)[static_cast<long long>(m) * p.ldc + n_idx] = v;
+        else
+          static_cast<__nv_bfloat16*>(p.C)[static_cast<long long>(m) * p.ldc + n_idx] = __float2bfloat16(v);
       }
     }
   }
@@ -468,7 +507,7 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int m_blocks, int n_b
 
 // Work item of a CTA pair: output block, contraction range and (MODE 2) the filter tap.
 struct PairTile {
-  int mb, nb, kb_begin, kb_end, tap;
+  int mb, nb, kb_begin, kb_end, tap, ks;
 };
 
 template <int BN, int MODE>
@@ -485,6 +524,7 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int tile, int
     const int mn = m_blocks * n_blocks;
     const int per_ks = mn * p.taps;
     const int ks = tile / per_ks;
+    t.ks = ks;
     const int r = tile - ks * per_ks;
     t.tap = r / mn;
     const int q = r - t.tap * mn;
@@ -498,6 +538,7 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int tile, int
     t.kb_begin = 0;
     t.kb_end = k_blocks;
     t.tap = 0;
+    t.ks = 0;
   }
   return t;
 }
@@ -673,12 +714,18 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int m0 = t.mb * 2 * GEMM_BM + static_cast<int>(rank) * GEMM_BM + ew * 32;
       const int n0 = t.nb * BN;
       const int c_off = MODE == 2 ? t.tap * p.N : 0;  // dW[co, tap, ci]: tap t starts at column t * Cin
+      const int r_off = MODE == 2 ? t.ks * p.split_rows : 0;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_word, FT_ERR_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
       if (MODE == 1 && p.cHo > 0) {
         epilogue_crop<BN>(p, t_row, m0 + lane, n0);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
+      } else if (p.flags & GEMM_EPI_TRANSPOSED) {
+        epilogue_transposed<BN>(p, t_row, m0 + lane, n0);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
@@ -758,9 +805,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           __syncwarp();
           if (lane == 0) {
             if (accumulate)
-              tma_reduce_add_2d(&tmC, tile_s, c_off + col0, m0);
+              tma_reduce_add_2d(&tmC, tile_s, c_off + col0, r_off + m0);
             else
-              tma_store_2d(&tmC, tile_s, c_off + col0, m0);
+              tma_store_2d(&tmC, tile_s, c_off + col0, r_off + m0);
             tma_store_commit();
           }
           buf ^= 1;
@@ -884,7 +931,7 @@ FT_API int ft_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
   p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.flags = flags;
   p.status = device_status_word(device);
   p.taps = 0; p.cblocks = 0; p.ksplit = 1;
-  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0;
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0; p.split_rows = 0;
 
   // Problems with at least one full 256-row block and N >= 128 run on the CTA-pair kernel.
   if (!force_single && M >= 2 * GEMM_BM && N >= 128 && (bn == 0 || bn >= 128)) {
@@ -977,7 +1024,7 @@ FT_API int ft_conv_shift_gemm(const void* xp, const void* w, void* y, const void
   p.status = device_status_word(device);
   p.taps = taps; p.cblocks = Cin / GEMM_BK; p.ksplit = 1;
   for (int t = 0; t < GEMM_MAX_TAPS; ++t) p.shift[t] = t < taps ? shift[t] : 0;
-  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0;
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0; p.split_rows = 0;
   long long y_rows = P;
   if (crop) {
     p.gHp = crop[0]; p.gWp = crop[1]; p.cHo = crop[2]; p.cWo = crop[3]; p.c_oh = crop[4]; p.c_ow = crop[5];
@@ -1026,7 +1073,7 @@ FT_API int ft_conv_shift_wgrad(const void* dyp, const void* xp, float* dw, long 
   p.ldc = static_cast<long long>(taps) * Cin;
   p.flags = GEMM_OUT_F32 | GEMM_ACCUMULATE;
   p.status = device_status_word(device);
-  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0;
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0; p.split_rows = 0;
   p.taps = taps; p.cblocks = Cin / GEMM_BK;
   for (int t = 0; t < GEMM_MAX_TAPS; ++t) p.shift[t] = t < taps ? shift[t] : 0;
   const int bn = Cin >= 256 ? 256 : 128;
@@ -1054,4 +1101,131 @@ FT_API int ft_conv_shift_wgrad(const void* dyp, const void* xp, float* dw, long 
   if (rc) return rc;
   if (bn == 256) return launch_pair<256, true, true, 2>(tmA, tmB, tmC, p, device, max_ctas, stream);
   return launch_pair<128, true, true, 2>(tmA, tmB, tmC, p, device, max_ctas, stream);
+}
+
+namespace ft {
+
+// ws holds the pieces of the split contraction: C^T as fp32 [ksplit][slice_rows >= N, ld_ws].  Write
+// C[m, n] = sum_ks ws[ks][n, m] (+ bias[n]) (+ residual[m, n]) as bf16; the pieces are summed in
+// index order, so the result does not depend on which CTA finished first.
+__global__ void small_m_finalize_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ C,
+                                        const __nv_bfloat16* __restrict__ residual, const void* __restrict__ bias,
+                                        int bias_f32, int M, int N, int ld_ws, int ksplit, int slice_rows,
+                                        long long ldc, long long ldr) {
+  // block = 32 x 8 threads over a 32 (n) x 32 (m) patch, transposed through shared memory
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  const long long slice = static_cast<long long>(slice_rows) * ld_ws;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int n = n0 + i, m = m0 + threadIdx.x;
+    float v = 0.f;
+    if (n < N && m < ld_ws) {
+      const float* src = ws + static_cast<long long>(n) * ld_ws + m;
+      for (int ks = 0; ks < ksplit; ++ks) v += src[ks * slice];
+    }
+    tile[i][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int m = m0 + i, n = n0 + threadIdx.x;
+    if (m < M && n < N) {
+      float v = tile[threadIdx.x][i];
+      if (bias) v += bias_f32 ? static_cast<const float*>(bias)[n] : __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
+      if (residual) v += __bfloat162float(residual[static_cast<long long>(m) * ldr + n]);
+      C[static_cast<long long>(m) * ldc + n] = __float2bfloat16(v);
+    }
+  }
+}
+
+}  // namespace ft
+
+constexpr int SMALL_M_MAX_SPLIT = 16;
+
+// Floats of workspace ft_gemm_small_m may need for an [M, N] result (its contents do not matter).
+FT_API long long ft_gemm_small_m_workspace(int M, int N) {
+  const int mpad = M <= 64 ? 64 : 128;
+  return static_cast<long long>((N + 255) / 256 * 256) * mpad * SMALL_M_MAX_SPLIT;
+}
+
+// C[M, N] = X[M, K] W[N, K]^T (+ bias[N]) (+ residual[M, N]) for a small batch M <= 128 (decode):
+// the weight is the 128-row MMA operand, so every byte of W crosses the tensor core once with all
+// 128 rows in use and the batch is only the (64- or 128-wide) N dimension of the instruction.
+// When N / 256 tiles would leave most SMs idle, the contraction is split across CTA pairs; each
+// piece stores its fp32 partial tile into its own slice of `workspace` and a second small kernel
+// sums the slices in index order (deterministic) and writes C.  workspace:
+// ft_gemm_small_m_workspace(M, N) floats, contents irrelevant (may be null when no split is
+// needed; then residual must be null).
+// All of X, W, C bf16; K-major operands; ldx, ldw, ldc, ldr in elements.
+FT_API int ft_gemm_small_m(const void* X, const void* W, void* C, const void* bias, const void* residual,
+                           float* workspace, int M, int N, int K, long long ldx, long long ldw, long long ldc,
+                           long long ldr, int flags, int ksplit, int device, cudaStream_t stream) {
+  if (int _rc = ft::ensure_device(device)) return _rc;
+  using namespace ft;
+  FT_REQUIRE(X && W && C, "ft_gemm_small_m: null operand");
+  FT_REQUIRE(M > 0 && M <= 128 && N > 0 && K > 0, "ft_gemm_small_m: M=%d must be in 1..128 (N=%d K=%d)", M, N, K);
+  FT_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && N % 8 == 0, "ft_gemm_small_m: strides and N must be multiples of 8");
+  FT_REQUIRE(!(flags & (GEMM_OUT_F32 | GEMM_ACCUMULATE)), "ft_gemm_small_m: bf16 output, no accumulation");
+  FT_REQUIRE(!(flags & (GEMM_BIAS | GEMM_BIAS_F32)) || bias, "ft_gemm_small_m: bias flag without bias");
+  const int bn = M <= 64 ? 64 : 128;
+  const int sms = sm_count(device);
+  const int pairs = sms / 2;
+  const int tiles = (N + 255) / 256;
+  const int k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  if (ksplit <= 0) {
+    ksplit = 1;
+    if (tiles < pairs && workspace) {
+      // one wave: as many pieces per tile as there are CTA pairs to take them, each piece long
+      // enough (>= 4 k-blocks) to be worth a pipeline fill
+      ksplit = pairs / tiles;
+      const int max_split = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
+      if (ksplit > max_split) ksplit = max_split;
+      if (ksplit < 1) ksplit = 1;
+    }
+  }
+  if (ksplit > SMALL_M_MAX_SPLIT) ksplit = SMALL_M_MAX_SPLIT;
+  // the residual is added by the finalize pass, which only the split path has
+  if (residual && ksplit == 1 && workspace && k_blocks >= 2) ksplit = 2;
+  FT_REQUIRE(ksplit == 1 || workspace, "ft_gemm_small_m: a split contraction needs the workspace");
+  FT_REQUIRE(ksplit > 1 || !residual, "ft_gemm_small_m: the residual is added by the split path only");
+  GemmParams p;
+  p.bias = bias; p.M = N; p.N = M; p.K = K;   // tile space: rows of W x batch
+  p.status = device_status_word(device);
+  p.taps = ksplit > 1 ? 1 : 0; p.cblocks = 0; p.ksplit = 1;
+  for (int t = 0; t < GEMM_MAX_TAPS; ++t) p.shift[t] = 0;
+  p.gHp = p.gWp = p.cHo = p.cWo = p.c_oh = p.c_ow = 0; p.split_rows = 0;
+  CUtensorMap tmA, tmB, tmC;
+  int rc = make_tmap_2d(&tmA, W, 2, K, N, ldw * 2, GEMM_BK, GEMM_BM, 3);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, X, 2, K, M, ldx * 2, GEMM_BK, bn / 2, 3);
+  if (rc) return rc;
+  if (ksplit == 1) {
+    p.C = C; p.ldc = ldc;
+    p.flags = (flags & 0xFFFF) | GEMM_EPI_TRANSPOSED;
+    // the store map is not used by the transposed epilogue; point it at W so that it is valid
+    rc = make_tmap_2d(&tmC, W, 2, K, N, ldw * 2, 64, 32, 3);
+    if (rc) return rc;
+    return bn == 64 ? launch_pair<64, false, false, 0>(tmA, tmB, tmC, p, device, 0, stream)
+                    : launch_pair<128, false, false, 0>(tmA, tmB, tmC, p, device, 0, stream);
+  }
+  const int per = (k_blocks + ksplit - 1) / ksplit;
+  p.ksplit = (k_blocks + per - 1) / per;
+  p.C = workspace; p.ldc = bn;
+  p.flags = GEMM_OUT_F32;
+  // a slice is a whole number of 256-row tiles, so a tile that hangs over the end of W stays
+  // inside its own slice
+  p.split_rows = tiles * 256;
+  rc = make_tmap_2d(&tmC, workspace, 4, bn, static_cast<uint64_t>(p.ksplit) * p.split_rows,
+                    static_cast<uint64_t>(bn) * 4, 32, 32, 3);
+  if (rc) return rc;
+  rc = bn == 64 ? launch_pair<64, false, false, 2>(tmA, tmB, tmC, p, device, 0, stream)
+                : launch_pair<128, false, false, 2>(tmA, tmB, tmC, p, device, 0, stream);
+  if (rc) return rc;
+  dim3 grid((N + 31) / 32, (M + 31) / 32), block(32, 8);
+  small_m_finalize_kernel<<<grid, block, 0, stream>>>(workspace, static_cast<__nv_bfloat16*>(C),
+                                                      static_cast<const __nv_bfloat16*>(residual), bias,
+                                                      (flags & GEMM_BIAS_F32) ? 1 : 0, M, N, bn, p.ksplit,
+                                                      p.split_rows, ldc, ldr);
+  FT_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return FT_E_OK;
 }

@@ -177,6 +177,9 @@ class LlamaEngine:
     def _col(self, slot: int, M: int, w) -> torch.Tensor:
         """Column-parallel linear on the gather buffer of ``slot``: ``[M, N_loc]``."""
         if not isinstance(w, tuple):
+            if self.W == 1 and M <= 128:
+                # one GPU, decode-sized batch: the weight-stationary small-batch GEMM
+                return F.gemm_small_m(self.tp.gather_buffer(slot, M, self.H), w)
             return self.tp.ag_gemm(slot, M, w)
         xg = self.tp.gather_buffer(slot, M, self.H) if self.W == 1 else self.tp.all_gather_rows(slot, M, self.H)
         return q4_0_linear(xg, w[0], w[1])
@@ -184,6 +187,8 @@ class LlamaEngine:
     def _row(self, slot: int, a: torch.Tensor, w, residual: torch.Tensor) -> torch.Tensor:
         """Row-parallel linear + reduce-scatter + residual add: this rank's rows ``[rows, H]``."""
         if not isinstance(w, tuple):
+            if self.W == 1 and a.shape[0] <= 128:
+                return F.gemm_small_m(a, w, residual=residual)    # residual added by its split-K finalize pass
             return self.tp.gemm_rs(slot, a, w, residual=residual)
         y = q4_0_linear(a, w[0], w[1])
         if self.W == 1:

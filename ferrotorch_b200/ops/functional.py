@@ -22,7 +22,58 @@ GEMM_OUT_F32, GEMM_ACCUMULATE, GEMM_BIAS, GEMM_BIAS_F32 = 1, 2, 4, 8
 GEMM_RELU, GEMM_GELU, GEMM_SILU = 16, 32, 64
 _ACT_FLAGS = {None: 0, "relu": GEMM_RELU, "gelu": GEMM_GELU, "silu": GEMM_SILU}
 
-stats = {"gemm_native": 0, "gemm_library": 0}
+stats = {"gemm_native": 0, "gemm_library": 0, "gemm_small_m": 0}
+
+_native.register_protos({
+    "ft_gemm_small_m": (_native._i, [_native._vp] * 6 + [_native._i] * 3 + [_native._ll] * 4 + [_native._i] * 3 + [_native._vp]),
+    "ft_gemm_small_m_workspace": (_native._ll, [_native._i, _native._i]),
+})
+_small_m_ws: dict = {}
+
+
+def _small_m_workspace(n_floats: int, device) -> torch.Tensor:
+    """fp32 workspace of the split-K small-batch GEMM for the current stream (one slice per piece
+    of the contraction; contents do not matter between calls)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _small_m_ws.get(key)
+    if buf is None or buf.numel() < n_floats:
+        buf = torch.empty(n_floats, device=device, dtype=torch.float32)
+        _small_m_ws[key] = buf
+    return buf
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
+                 residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                 activation: str | None = None, ksplit: int = 0) -> torch.Tensor:
+    """``x @ w.T (+ bias) (+ residual)`` for a small batch ``x [M <= 128, K]`` against ``w [N, K]``
+    (both bf16, row-major): the decode-time GEMM.  The weight is the 128-row operand of the MMA and
+    the contraction is split over the GPU when ``N / 256`` tiles would leave SMs idle."""
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+    flags = _ACT_FLAGS[activation]
+    bias_ptr = None
+    if bias is not None:
+        bias = bias.contiguous()
+        flags |= GEMM_BIAS_F32 if bias.dtype == torch.float32 else GEMM_BIAS
+        bias_ptr = bias.data_ptr()
+    lib = _native.kernels()
+    if activation is not None:
+        ksplit = 1                      # the activation is applied by the single-pass epilogue only
+    if residual is not None and ksplit == 1:
+        raise ValueError("gemm_small_m: a residual needs the split path (ksplit != 1)")
+    ws = None
+    if ksplit != 1:
+        ws = _small_m_workspace(int(lib.ft_gemm_small_m_workspace(M, N)), x.device)
+    rc = lib.ft_gemm_small_m(x.data_ptr(), w.data_ptr(), out.data_ptr(), bias_ptr,
+                             residual.data_ptr() if residual is not None else None,
+                             ws.data_ptr() if ws is not None else None, M, N, K, x.stride(0), w.stride(0),
+                             out.stride(0), residual.stride(0) if residual is not None else 0, flags, ksplit,
+                             _dev(x), _stream())
+    _native.check(rc, "ft_gemm_small_m")
+    stats["gemm_small_m"] += 1
+    return out
 
 _NATIVE = True
 
@@ -107,6 +158,10 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = Non
             r = getattr(torch.nn.functional, activation)(r)
         out.copy_(r.to(out.dtype))
         return out
+    if (M <= 128 and N >= 1024 and K >= 512 and not accumulate and out.dtype == torch.bfloat16 and la[0] == 0
+            and lb[0] == 0 and bn == 0 and max_ctas == 0):
+        # decode-sized batch against a large weight: the weight-stationary kernel
+        return gemm_small_m(a, b, bias=bias, out=out, activation=activation)
     flags = _ACT_FLAGS[activation]
     if out.dtype == torch.float32:
         flags |= GEMM_OUT_F32

@@ -79,7 +79,7 @@ def compute_buckets(ranges, slots, bucket_elems: int, align: int):
 
 class FusedDDP:
     def __init__(self, group=None, mode: str = "fused", bucket_mb: float = 256.0, comm_blocks: int = 32,
-                 timeout_ms: int | None = None, late_params=()):
+                 timeout_ms: int | None = None, late_params=(), tail_blocks: int | None = None):
         assert mode in ("fused", "nccl")
         self.group = group if group is not None else dist.group.WORLD
         self.mode = mode
@@ -87,6 +87,10 @@ class FusedDDP:
         self.rank = dist.get_rank(self.group)
         self.bucket_mb = bucket_mb
         self.comm_blocks = comm_blocks
+        # While backward runs, a bucket kernel is kept to ``comm_blocks`` CTAs so that it does not
+        # take SMs from the GEMMs; buckets that are still unlaunched when backward has ended (the
+        # embedding table's, whose gradient is produced last) get ``tail_blocks`` CTAs: every SM.
+        self.tail_blocks = tail_blocks or torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self.timeout_ms = timeout_ms or int(os.environ.get("FT_COMM_TIMEOUT_MS", "30000"))
         self.fused_update = mode == "fused"
         self.device = torch.device("cuda", torch.cuda.current_device())
@@ -175,7 +179,7 @@ class FusedDDP:
             if self._pending[bi] == 0 and not self._launched[bi]:
                 self._launch(bi)
 
-    def _launch(self, bi: int) -> None:
+    def _launch(self, bi: int, blocks: int | None = None) -> None:
         self._launched[bi] = True
         b = self.buckets[bi]
         tr = self.trainer
@@ -198,7 +202,7 @@ class FusedDDP:
             tr.exp_avg_sq.data_ptr() if tr.exp_avg_sq is not None else None, self.counters.data_ptr(),
             lo, n_pad, self.rank, self.world, bi, self.n_slots, self.epoch, 1.0 / self.world,
             int(tr.arena.grads.dtype == torch.float32), kind, tr.lr, tr.betas[0], tr.betas[1], tr.eps, wd,
-            tr.step_count + 1, tr.momentum, tr.dampening, int(tr.nesterov), self.comm_blocks,
+            tr.step_count + 1, tr.momentum, tr.dampening, int(tr.nesterov), blocks or self.comm_blocks,
             self.timeout_ms, self.device.index, self.stream.cuda_stream)
         _native.check(rc, "ft_ddp_reduce_update")
 
@@ -214,7 +218,7 @@ class FusedDDP:
         self.last_micro_batch = True
         for bi in range(self.n_slots):
             if not self._launched[bi]:
-                self._launch(bi)
+                self._launch(bi, self.tail_blocks)       # backward is over: nothing left to share the SMs with
         if self.mode == "fused":
             lib = _native.kernels()
             rc = lib.ft_comm_wait(self.flags.ptrs[self.rank], 1, 0, self.n_slots, self.n_slots, self.world,
