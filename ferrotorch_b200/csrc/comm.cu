@@ -130,7 +130,9 @@ __device__ __forceinline__ void apply_update(const UpdateArgs& u, float g, float
   }
 }
 
-__global__ void __launch_bounds__(COMM_THREADS)
+// Launched as clusters of two CTAs (nothing in the kernel uses the cluster): the pair occupies one
+// SM pair, so a GEMM that runs beside it on CTA-pair clusters loses whole pairs, never half of two.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(COMM_THREADS)
 ddp_reduce_update_kernel(const DdpArgs a) {
   uint32_t* my_flags = static_cast<uint32_t*>(a.flags.ptr[a.rank]);
   // 1. tell every peer that this rank's gradients of the bucket are final (they were written by
@@ -394,7 +396,8 @@ FT_API int ft_ddp_reduce_update(void* const* grad_ptrs, void* const* param_ptrs,
   long long grid = (nvec + COMM_THREADS - 1) / COMM_THREADS;
   const long long cap = blocks > 0 ? blocks : sm_count(device);
   if (grid > cap) grid = cap;
-  if (grid < 1) grid = 1;
+  grid = (grid + 1) / 2 * 2;  // clusters of two
+  if (grid < 2) grid = 2;
   ddp_reduce_update_kernel<<<static_cast<unsigned>(grid), COMM_THREADS, 0, stream>>>(a);
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();

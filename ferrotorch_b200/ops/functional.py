@@ -76,6 +76,17 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None 
     return out
 
 _NATIVE = True
+_GEMM_CTA_LIMIT = 0
+
+
+def set_gemm_cta_limit(n: int) -> int:
+    """Limit the persistent grid of every GEMM launched from here on to ``n`` CTAs (0 = all SMs);
+    returns the previous limit.  The data-parallel layer sets this while its bucket kernels share
+    the GPU with the backward pass: a persistent GEMM whose grid does not fit next to them would
+    run its left-over CTAs in a second round and take twice as long."""
+    global _GEMM_CTA_LIMIT
+    old, _GEMM_CTA_LIMIT = _GEMM_CTA_LIMIT, max(0, int(n))
+    return old
 
 
 def set_native(enabled: bool) -> bool:
@@ -175,7 +186,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = Non
         bias_ptr = bias.data_ptr()
     lib = _native.kernels()
     rc = lib.ft_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias_ptr, M, N, K, la[1], lb[1],
-                          out.stride(0), la[0], lb[0], flags, bn, max_ctas, _dev(a), _stream())
+                          out.stride(0), la[0], lb[0], flags, bn, max_ctas or _GEMM_CTA_LIMIT, _dev(a), _stream())
     _native.check(rc, "ft_gemm_bf16")
     stats["gemm_native"] += 1
     return out

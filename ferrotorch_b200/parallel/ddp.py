@@ -104,6 +104,7 @@ class FusedDDP:
         self.measure_exposed = False
         self._exposed_events: list = []
         self.reduce_only = False
+        self._limited = False
 
     # the trainer allocates its arenas through this (symmetric memory in fused mode)
     def allocator(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -181,6 +182,14 @@ class FusedDDP:
 
     def _launch(self, bi: int, blocks: int | None = None) -> None:
         self._launched[bi] = True
+        if blocks is None and self.mode == "fused" and not self._limited:
+            # From the first bucket on, the bucket kernels (clusters of two CTAs, so they take
+            # whole SM pairs) hold ``comm_blocks`` SMs until backward ends: keep the persistent
+            # GEMMs of the rest of backward to the SMs that stay free.
+            from ..ops import functional as F
+
+            F.set_gemm_cta_limit(max(2, (self.tail_blocks - self.comm_blocks) // 2 * 2))
+            self._limited = True
         b = self.buckets[bi]
         tr = self.trainer
         cur = torch.cuda.current_stream(self.device)
@@ -216,6 +225,11 @@ class FusedDDP:
         """Launch what backward did not trigger, then make the compute stream wait for the
         whole exchange (all peers' slices written into this rank's parameter arena)."""
         self.last_micro_batch = True
+        if self._limited:
+            from ..ops import functional as F
+
+            F.set_gemm_cta_limit(0)
+            self._limited = False
         for bi in range(self.n_slots):
             if not self._launched[bi]:
                 self._launch(bi, self.tail_blocks)       # backward is over: nothing left to share the SMs with

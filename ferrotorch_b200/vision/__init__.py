@@ -3,9 +3,12 @@
 The reference's ``ferrotorch-vision`` has ten classifier families, seven detectors, four
 segmenters, a model registry, MNIST / CIFAR / ImageFolder readers, 17 transforms, image IO and
 NMS / RoIAlign (ferrotorch-vision/src/models/*, datasets/*, transforms/*, ops/*).  Here the ResNet
-family is this package's own (``models/resnet.py``: channels-last bf16 with the fused batch-norm
-kernels); everything else comes from ``torchvision`` as part of the framework layer and is
-re-exported under the reference's names through one registry.
+family (``models/resnet.py``: channels-last bf16, convolutions on the tcgen05 GEMM, fused batch-norm
+kernels) and VGG-11/16, MobileNetV2, ViT-B/16, ConvNeXt-Tiny, DenseNet-121, FCN and DeepLabV3
+(``models/vision_zoo.py``; torchvision's parameter names, convolutions and attention on this
+framework's kernels) are this package's own; the remaining names (EfficientNet, Swin, Inception,
+MobileNetV3, the detectors, LRASPP) come from ``torchvision`` as part of the framework layer.  One
+registry serves all of them under the reference's names.
 """
 from __future__ import annotations
 
@@ -46,9 +49,14 @@ def _tv(name: str, **kw) -> nn.Module:
 
 
 def build(name: str, **kw) -> nn.Module:
-    """One constructor for every model name of the reference's registry."""
+    """One constructor for every model name of the reference's registry (own implementations
+    first, torchvision for the rest)."""
     if name in list_models():
         return create_model(name, **kw)
+    from ..models.vision_zoo import OWN_MODELS
+
+    if name in OWN_MODELS:
+        return OWN_MODELS[name](**kw)
     for table in (CLASSIFIERS, DETECTORS, SEGMENTERS):
         if name in table:
             return _tv(table[name], **kw)

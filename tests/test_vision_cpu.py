@@ -145,3 +145,53 @@ def test_reference_vision_names():
     assert V.Resize(8)(torch.rand(3, 16, 16)).shape == (3, 8, 8) and V.CenterCrop(4)(torch.rand(3, 8, 8)).shape == (3, 4, 4)
     rpn = V.RpnConfig(nms_thresh=0.6).build(V.AnchorGenerator(((32,),), ((1.0,),)), V.RpnHead(8, 1))
     assert isinstance(rpn, V.Rpn) and rpn.nms_thresh == 0.6
+
+
+# --------------------------------------------------------------------------- own model zoo vs torchvision
+def _same_as_torchvision(ours, tv, x, get=lambda o: o):
+    tv.eval(), ours.eval()
+    ours.load_state_dict(tv.state_dict(), strict=True)          # torchvision's parameter names
+    with torch.no_grad():
+        torch.testing.assert_close(get(ours(x)), get(tv(x)), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["vgg11", "mobilenet_v2", "convnext_tiny", "densenet121"])
+def test_own_classifiers_match_torchvision(name):
+    tvm = pytest.importorskip("torchvision.models")
+    from ferrotorch_b200.models import vision_zoo as Z
+
+    torch.manual_seed(0)
+    _same_as_torchvision(getattr(Z, name)(num_classes=7), getattr(tvm, name)(weights=None, num_classes=7),
+                         torch.randn(2, 3, 64, 64))
+
+
+def test_own_vit_matches_torchvision_and_trains():
+    tvm = pytest.importorskip("torchvision.models")
+    from ferrotorch_b200.models import vision_zoo as Z
+
+    torch.manual_seed(1)
+    ours = Z.VisionTransformer(image_size=32, patch_size=8, num_layers=2, num_heads=4, hidden_dim=64, mlp_dim=128, num_classes=5)
+    tv = tvm.VisionTransformer(image_size=32, patch_size=8, num_layers=2, num_heads=4, hidden_dim=64, mlp_dim=128, num_classes=5)
+    _same_as_torchvision(ours, tv, torch.randn(3, 3, 32, 32))
+    ours.train()
+    ours(torch.randn(2, 3, 32, 32)).sum().backward()
+    assert all(p.grad is not None for p in ours.parameters())
+
+
+@pytest.mark.parametrize("name", ["fcn_resnet50", "deeplabv3_resnet50"])
+def test_own_segmentation_models_match_torchvision(name):
+    seg = pytest.importorskip("torchvision.models.segmentation")
+    from ferrotorch_b200.models import vision_zoo as Z
+
+    torch.manual_seed(2)
+    _same_as_torchvision(getattr(Z, name)(num_classes=4),
+                         getattr(seg, name)(weights=None, weights_backbone=None, num_classes=4, aux_loss=False),
+                         torch.randn(2, 3, 64, 64), lambda o: o["out"])
+
+
+def test_registry_prefers_own_models():
+    from ferrotorch_b200 import vision as V
+    from ferrotorch_b200.models import vision_zoo as Z
+
+    assert isinstance(V.build("vgg16", num_classes=3), Z.VGG)
+    assert isinstance(V.build("deeplabv3", num_classes=3), Z.SegmentationModel)
