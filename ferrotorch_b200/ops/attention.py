@@ -1,7 +1,9 @@
 """Differentiable flash attention (GQA, causal/full) on the tcgen05 kernels.
 
-Forward: ``csrc/attn_fwd.cu``.  Backward: ``csrc/attn_bwd.cu`` (dK/dV kernel + dQ kernel that
-recompute P from the saved log-sum-exp).  CPU tensors use the PyTorch reference.
+Forward: ``csrc/attn_fwd.cu``.  Backward: ``csrc/attn_bwd.cu`` -- head_dim 128 runs one fused
+kernel that recomputes P from the saved log-sum-exp once and produces dK, dV and (through an
+fp32 accumulator) dQ; head_dim 64, or :func:`deterministic`, the dK/dV kernel + dQ kernel pair.
+CPU tensors use the PyTorch reference.
 """
 from __future__ import annotations
 
@@ -13,8 +15,27 @@ from . import reference as ref
 
 _i, _ll, _f, _vp = _native._i, _native._ll, _native._f, _native._vp
 _native.register_protos({
-    "ft_flash_attn_bwd": (_i, [_vp] * 10 + [_i] * 6 + [_ll] * 7 + [_f, _i, _i, _i, _vp]),
+    "ft_flash_attn_bwd": (_i, [_vp] * 11 + [_i] * 6 + [_ll] * 7 + [_f, _i, _i, _i, _vp]),
 })
+
+
+# The fused single-pass backward (head_dim 128) sums dQ over key tiles with fp32 atomic adds into
+# a scratch accumulator; deterministic() switches back to the bit-reproducible two-pass kernels.
+_FUSED_BWD = True
+
+
+def deterministic(on: bool = True) -> bool:
+    """Use the two-pass backward kernels (run-to-run identical dQ) instead of the fused one;
+    returns the previous setting."""
+    global _FUSED_BWD
+    old, _FUSED_BWD = not _FUSED_BWD, not on
+    return old
+
+
+def _dq_scratch(B: int, S: int, Hq: int, D: int, device):
+    if not _FUSED_BWD or D != 128:
+        return None
+    return F._get_scratch("attn_dq_acc", B * S * Hq * D, device).data_ptr()
 
 
 def native_bwd_available() -> bool:
@@ -53,7 +74,7 @@ class _FlashAttnFn(torch.autograd.Function):
         rc = lib.ft_flash_attn_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-            F._get_scratch("attn_delta", 2 * B * Hq * Sq, q.device).data_ptr(),
+            F._get_scratch("attn_delta", 2 * B * Hq * Sq, q.device).data_ptr(), _dq_scratch(B, Sq, Hq, D, q.device),
             B, Sq, Sk, Hq, Hkv, D, F._tok_stride(q), F._tok_stride(k), F._tok_stride(v), Hq * D,
             F._tok_stride(dq), F._tok_stride(dk), F._tok_stride(dv), float(sc), int(causal), off,
             F._dev(q), F._stream())
@@ -118,7 +139,7 @@ class _QKVAttentionFn(torch.autograd.Function):
         rc = lib.ft_flash_attn_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-            F._get_scratch("attn_delta", 2 * B * Hq * S, q.device).data_ptr(),
+            F._get_scratch("attn_delta", 2 * B * Hq * S, q.device).data_ptr(), _dq_scratch(B, S, Hq, D, q.device),
             B, S, S, Hq, Hkv, D, ld, ld, ld, Hq * D, ld, ld, ld, float(D ** -0.5), int(causal), 0,
             F._dev(q), F._stream())
         _native.check(rc, "ft_flash_attn_bwd")
@@ -188,7 +209,7 @@ class _PackedAttentionFn(torch.autograd.Function):
         rc = _native.kernels().ft_flash_attn_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-            F._get_scratch("attn_delta", 2 * B * Hq * S, q.device).data_ptr(),
+            F._get_scratch("attn_delta", 2 * B * Hq * S, q.device).data_ptr(), _dq_scratch(B, S, Hq, D, q.device),
             B, S, S, Hq, Hkv, D, ld, ld, ld, Hq * D, ld, ld, ld, float(D ** -0.5), int(causal), 0,
             F._dev(q), F._stream())
         _native.check(rc, "ft_flash_attn_bwd")

@@ -23,8 +23,11 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
-    cfg = LlamaConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
-                      num_attention_heads=8, num_key_value_heads=4, head_dim=64, max_position_embeddings=256,
+    # every rank needs at least one KV head: more heads (and a wider model) at 8 ranks
+    kvh = 4 if world <= 4 else 8
+    cfg = LlamaConfig(vocab_size=2048, hidden_size=512 if world <= 4 else 1024,
+                      intermediate_size=1024 if world <= 4 else 2048, num_hidden_layers=2,
+                      num_attention_heads=2 * kvh, num_key_value_heads=kvh, head_dim=64, max_position_embeddings=256,
                       initializer_range=0.08)
     torch.manual_seed(3)
     model = LlamaForCausalLM(cfg).to(dev, torch.bfloat16).eval()

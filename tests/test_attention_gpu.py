@@ -81,9 +81,25 @@ def test_flash_fwd_packed_qkv():
     (1, 1024, 1024, 8, 2, 128, True),
     (2, 256, 256, 4, 4, 64, True),
     (1, 130, 190, 2, 2, 64, False),
+    (1, 2048, 2048, 8, 2, 128, True),    # many steps per CTA: ring and double-buffer wrap-arounds, GQA group of 4
+    (2, 700, 700, 4, 4, 128, True),
+    (1, 448, 448, 2, 1, 128, False),
 ])
-def test_flash_bwd(B, Sq, Sk, Hq, Hkv, D, causal):
+@pytest.mark.parametrize("two_pass", [False, True])
+def test_flash_bwd(B, Sq, Sk, Hq, Hkv, D, causal, two_pass):
+    from ferrotorch_b200.ops import attention as A
     from ferrotorch_b200.ops.attention import flash_attention
+
+    if two_pass and D != 128:
+        pytest.skip("head_dim 64 always runs the two-pass kernels")
+    prev = A.deterministic(two_pass)
+    try:
+        _flash_bwd_case(flash_attention, B, Sq, Sk, Hq, Hkv, D, causal)
+    finally:
+        A.deterministic(prev)
+
+
+def _flash_bwd_case(flash_attention, B, Sq, Sk, Hq, Hkv, D, causal):
 
     torch.manual_seed(Sq * 3 + Sk + Hq)
     q, k, v = (_rand(B, Sq, Hq, D).requires_grad_(), _rand(B, Sk, Hkv, D).requires_grad_(),

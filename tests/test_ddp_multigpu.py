@@ -24,9 +24,10 @@ def test_ddp_two_gpus(mode):
     _run(mode, 2)
 
 
-def test_ddp_all_gpus_fused():
+@pytest.mark.parametrize("mode", ["fused", "fused_clip"])
+def test_ddp_all_gpus(mode):
     n = torch.cuda.device_count()
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     if n == 2:
         pytest.skip("covered by the two-GPU test")
-    _run("fused", n)
+    _run(mode, n)

@@ -129,6 +129,16 @@ def test_engine_tensor_parallel_2_cuda_graph():
     _run(2, 29552, graph=True)
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_engine_tensor_parallel_all_gpus_cuda_graph():
+    n = torch.cuda.device_count()
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    if n == 2:
+        pytest.skip("covered by the two-GPU test")
+    _run(n, 29553, graph=True)
+
+
 # The Q4_0 weight format of the engine is a composition of kernels that each have their own test
 # (gather, dequant-GEMM); these two check the composition.
 
