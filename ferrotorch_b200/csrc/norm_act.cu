@@ -181,13 +181,34 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// dw[h] (+)= sum_b partial[b, h]; writes bf16 or fp32.
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, void* __restrict__ dw,
-                                         int nblocks, int H, int out_f32, int accumulate) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
+// dw[h] (+)= sum_b partial[b, h]; writes bf16 or fp32.  A block owns 32 columns (one 128-byte
+// segment of every partial row); its 8 warps each walk every 8th row with four loads in flight and
+// the 8 sub-sums are added in warp order, so the result does not depend on scheduling.
+constexpr int DW_RED_COLS = 32, DW_RED_WARPS = 8;
+__global__ void __launch_bounds__(DW_RED_COLS * DW_RED_WARPS)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, void* __restrict__ dw, int nblocks, int H,
+                         int out_f32, int accumulate) {
+  __shared__ float sub[DW_RED_WARPS][DW_RED_COLS];
+  const int tx = threadIdx.x & (DW_RED_COLS - 1), ty = threadIdx.x / DW_RED_COLS;
+  const int h = blockIdx.x * DW_RED_COLS + tx;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (h < H) {
+    const float* col = partial + h;
+    int b = ty;
+    for (; b + 3 * DW_RED_WARPS < nblocks; b += 4 * DW_RED_WARPS) {
+      s0 += col[static_cast<size_t>(b) * H];
+      s1 += col[static_cast<size_t>(b + DW_RED_WARPS) * H];
+      s2 += col[static_cast<size_t>(b + 2 * DW_RED_WARPS) * H];
+      s3 += col[static_cast<size_t>(b + 3 * DW_RED_WARPS) * H];
+    }
+    for (; b < nblocks; b += DW_RED_WARPS) s0 += col[static_cast<size_t>(b) * H];
+  }
+  sub[ty][tx] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (ty != 0 || h >= H) return;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<size_t>(b) * H + h];
+#pragma unroll
+  for (int k = 0; k < DW_RED_WARPS; ++k) s += sub[k][tx];
   if (out_f32) {
     float* o = static_cast<float*>(dw);
     o[h] = accumulate ? o[h] + s : s;
@@ -449,7 +470,7 @@ FT_API int ft_rmsnorm_bwd(const void* dy, const void* x, const void* w, const fl
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   if (dw) {
-    rmsnorm_dw_reduce_kernel<<<(H + 127) / 128, 128, 0, stream>>>(scratch, dw, grid, H, dw_flags & 1,
+    rmsnorm_dw_reduce_kernel<<<(H + DW_RED_COLS - 1) / DW_RED_COLS, DW_RED_COLS * DW_RED_WARPS, 0, stream>>>(scratch, dw, grid, H, dw_flags & 1,
                                                                   (dw_flags >> 1) & 1);
     FT_CUDA_CHECK(cudaGetLastError());
     count_launch();
@@ -584,7 +605,7 @@ FT_API int ft_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, 
   FT_CUDA_CHECK(cudaGetLastError());
   count_launch();
   if (dw) {
-    rmsnorm_dw_reduce_kernel<<<(H + 127) / 128, 128, 0, stream>>>(scratch, dw, grid, H, dw_flags & 1,
+    rmsnorm_dw_reduce_kernel<<<(H + DW_RED_COLS - 1) / DW_RED_COLS, DW_RED_COLS * DW_RED_WARPS, 0, stream>>>(scratch, dw, grid, H, dw_flags & 1,
                                                                   (dw_flags >> 1) & 1);
     FT_CUDA_CHECK(cudaGetLastError());
     count_launch();

@@ -25,6 +25,8 @@ residual add: two launches per layer instead of one fused kernel.
 from __future__ import annotations
 
 
+import zlib
+
 import torch
 import torch.distributed as dist
 
@@ -94,7 +96,7 @@ class LlamaEngine:
         g = torch.Generator(device=dev)
 
         def rnd(shape, tag):
-            g.manual_seed(hash((seed, tag)) % (2 ** 31))
+            g.manual_seed(zlib.crc32(repr((seed, tag)).encode()) & 0x7FFFFFFF)   # same on every rank and run
             return (torch.randn(shape, device=dev, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
 
         def get(name, shape, tag, shard=None):
