@@ -104,6 +104,15 @@ def main():
             "decode_ms_per_step": ms_decode / args.new, "cuda_graph": bool(args.graph), "gpu_launches_decode": launches, "device_status": status,
             "dtype": "bf16", "weights": args.weights, "data": "synthetic"}))
     if world > 1:
+        # release the captured decode graph (it holds NCCL work in the Q4_0 path) before the
+        # communicator goes away; tearing the group down under a live graph can block at exit
+        dist.barrier()
+        torch.cuda.synchronize()
+        del eng
+        import gc
+
+        gc.collect()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 

@@ -448,13 +448,15 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // rank's rows over the sources in rank order, four 16-byte vectors per thread in flight
     // from each source.
     __syncthreads();
-    bool ok = (*abort_word == 0);
+    // a rank past the last row (M < (rank + 1) * rows_per_rank with nothing left for it) owns
+    // nothing: no source will ever raise its flag, so it must not wait for one
+    const int rows = min(p.rows_per_rank, p.M - p.rank * p.rows_per_rank);
+    bool ok = (*abort_word == 0) && rows > 0;
     if (ok && lane < p.world)
       ok = tp_spin_ge<true>(my_flags + tp_flag_index(0, p.slot, lane, p.n_slots), epoch, p.limit_ns, abort_word, p.status);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       const __nv_bfloat16* st = static_cast<const __nv_bfloat16*>(p.stage.ptr[p.rank]);
-      const int rows = min(p.rows_per_rank, p.M - p.rank * p.rows_per_rank);
       const int vec_per_row = p.N >> 3;
       const long long total = static_cast<long long>(rows > 0 ? rows : 0) * vec_per_row;
       const long long slot_stride = static_cast<long long>(p.rows_per_rank) * p.N;
@@ -676,7 +678,9 @@ FT_API int ft_tp_gemm_rs2(const void* x, const void* w, void* const* stage_ptrs,
                  ldr % 8 == 0,
              "ft_tp_gemm_rs: N, K and strides must be multiples of 8");
   FT_REQUIRE(rows_per_rank > 0 && rows_per_rank * world >= M, "ft_tp_gemm_rs: rows_per_rank * world < M");
-  FT_REQUIRE(counters && x && w && out, "ft_tp_gemm_rs: null pointer");
+  // a rank that owns no rows (M < rank * rows_per_rank, e.g. a decode batch smaller than the group)
+  // passes an empty output: it still computes and sends its partial products
+  FT_REQUIRE(counters && x && w && (out || M <= rank * rows_per_rank), "ft_tp_gemm_rs: null pointer");
   TpParams p{};
   FT_REQUIRE(fill_peers(p.stage, stage_ptrs, world) == 0 && fill_peers(p.flags, flag_ptrs, world) == 0,
              "ft_tp_gemm_rs: bad peer pointers");
