@@ -82,6 +82,52 @@ class _FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+def attention_block_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                             dout: torch.Tensor, causal: bool, scale: float | None = None):
+    """Gradients of attention restricted to one key block when the softmax statistics are those
+    of the **whole** key sequence: ``out`` and ``lse`` are the final output and log-sum-exp of the
+    rows (over every key block), ``k / v`` one block.  ``P = exp(q k^T scale - lse)`` is then that
+    block's share of the full probabilities and ``dS = P (dP - rowsum(dout * out))``; returns the
+    block's contribution to ``dq`` and its ``dk``, ``dv``.  This is the step a ring (context
+    parallel) backward repeats for every block it receives.  On a GPU with bf16 inputs and head
+    dim 64 / 128 it is the flash backward kernel (it takes ``out`` and ``lse`` as inputs);
+    elsewhere fp32 torch math."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    sc = scale if scale is not None else D ** -0.5
+    if F.native_enabled() and q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and native_bwd_available():
+        q, k, v, out, dout = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v, out, dout))
+        lse = lse.float().contiguous()
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        rc = _native.kernels().ft_flash_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            F._get_scratch("attn_delta", 2 * B * Hq * Sq, q.device).data_ptr(), _dq_scratch(B, Sq, Hq, D, q.device),
+            B, Sq, Sk, Hq, Hkv, D, F._tok_stride(q), F._tok_stride(k), F._tok_stride(v), Hq * D,
+            F._tok_stride(dq), F._tok_stride(dk), F._tok_stride(dv), float(sc), int(causal), Sk - Sq,
+            F._dev(q), F._stream())
+        _native.check(rc, "ft_flash_attn_bwd")
+        return dq, dk, dv
+    g = Hq // Hkv
+    qf, dof, of = (t.float().permute(0, 2, 1, 3) for t in (q, dout, out))          # [B, Hq, Sq, D]
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)                  # [B, Hq, Sk, D]
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * sc
+    if causal:
+        i = torch.arange(Sq, device=q.device)[:, None] + (Sk - Sq)
+        j = torch.arange(Sk, device=q.device)[None, :]
+        s = s.masked_fill(j > i, float("-inf"))
+    p = torch.exp(s - lse.float().unsqueeze(-1))
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (torch.matmul(dof, vf.transpose(-1, -2)) - delta)
+    dq = torch.matmul(ds, kf) * sc
+    dk = (torch.matmul(ds.transpose(-1, -2), qf) * sc).reshape(B, Hkv, g, Sk, D).sum(2)
+    dv = torch.matmul(p.transpose(-1, -2), dof).reshape(B, Hkv, g, Sk, D).sum(2)
+    return (dq.permute(0, 2, 1, 3).to(q.dtype), dk.permute(0, 2, 1, 3).to(k.dtype), dv.permute(0, 2, 1, 3).to(v.dtype))
+
+
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
                     scale: float | None = None, causal_offset: int | None = None) -> torch.Tensor:
     """``softmax(q k^T * scale + mask) v`` for ``q [B,Sq,Hq,D]``, ``k/v [B,Sk,Hkv,D]``; returns

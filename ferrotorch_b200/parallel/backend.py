@@ -82,6 +82,64 @@ def _raise(code: int, what: str):
         raise _CODES.get(code, DistributedError)("%s failed (code %d)" % (what, code))
 
 
+class PendingOp:
+    """Handle of a posted send or receive: ``wait()`` blocks until it has completed and re-raises
+    what it raised (async collectives of the reference: ferrotorch-distributed/src/async_collective.rs)."""
+
+    def __init__(self):
+        self._done = threading.Event()
+        self._error: BaseException | None = None
+
+    def _finish(self, error: BaseException | None = None) -> None:
+        self._error = error
+        self._done.set()
+
+    def is_done(self) -> bool:
+        return self._done.is_set()
+
+    def wait(self, timeout: float | None = None) -> None:
+        if not self._done.wait(timeout):
+            raise Timeout("posted operation did not complete in %.1f s" % timeout)
+        if self._error is not None:
+            raise self._error
+
+
+class _Lane:
+    """One worker thread executing posted operations in order."""
+
+    def __init__(self):
+        self._q: queue.Queue = queue.Queue()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def post(self, fn, *args) -> PendingOp:
+        op = PendingOp()
+        self._q.put((op, fn, args))
+        return op
+
+    def _run(self) -> None:
+        while True:
+            op, fn, args = self._q.get()
+            try:
+                fn(*args)
+                op._finish()
+            except BaseException as e:  # noqa: BLE001  (handed to the waiter)
+                op._finish(e)
+
+
+class _TorchWork(PendingOp):
+    def __init__(self, work, keep):
+        super().__init__()
+        self._work, self._keep = work, keep
+
+    def is_done(self) -> bool:
+        return self._work.is_completed()
+
+    def wait(self, timeout: float | None = None) -> None:
+        self._work.wait()
+        self._keep = None
+
+
 class Group:
     """Common collective implementations over ``send`` / ``recv`` (bytes-oriented)."""
 
@@ -100,6 +158,27 @@ class Group:
             raise SelfSend("rank %d cannot send to / receive from itself" % peer)
         if not 0 <= peer < self.world_size:
             raise InvalidRank("rank %d outside world of %d" % (peer, self.world_size))
+
+    # --- non-blocking point to point.  Messages to one peer leave in the order they were posted
+    # and receives from one peer complete in the order they were posted: each (peer, direction)
+    # has one worker thread with a FIFO of requests.  Back-ends with native asynchronous
+    # operations (``TorchGroup``) override both.
+    def isend(self, t: torch.Tensor, dst: int) -> "PendingOp":
+        self._check_peer(dst)
+        return self._lane(dst, "send").post(self.send, t, dst)
+
+    def irecv(self, t: torch.Tensor, src: int, timeout: float | None = None) -> "PendingOp":
+        self._check_peer(src)
+        return self._lane(src, "recv").post(self.recv, t, src, timeout)
+
+    def _lane(self, peer: int, direction: str) -> "_Lane":
+        lanes = self.__dict__.setdefault("_lanes", {})
+        lock = self.__dict__.setdefault("_lanes_lock", threading.Lock())
+        with lock:
+            lane = lanes.get((peer, direction))
+            if lane is None:
+                lane = lanes[(peer, direction)] = _Lane()
+            return lane
 
     def sendrecv(self, send_t: torch.Tensor, recv_t: torch.Tensor, peer: int) -> None:
         """Deadlock-free exchange: the lower rank sends first (p2p.rs:30-160)."""
@@ -423,6 +502,15 @@ class TorchGroup(Group):
     def recv(self, t, src, timeout=None):
         self._check_peer(src)
         self._dist.recv(t, self._g(src), group=self.pg)
+
+    def isend(self, t, dst):
+        self._check_peer(dst)
+        t = t.contiguous()
+        return _TorchWork(self._dist.isend(t, self._g(dst), group=self.pg), t)   # keeps the buffer alive
+
+    def irecv(self, t, src, timeout=None):
+        self._check_peer(src)
+        return _TorchWork(self._dist.irecv(t, self._g(src), group=self.pg), t)
 
     def barrier(self):
         self._dist.barrier(self.pg)

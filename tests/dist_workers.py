@@ -328,3 +328,63 @@ def hybrid_case(rank, world, port, q):
         import traceback
 
         q.put((rank, "ERR %r %s" % (e, traceback.format_exc())))
+
+
+def pipeline_case(rank, world, port, q, backend="tcp", schedule="1f1b"):
+    """Three pipeline stages as processes: loss and every gradient against the one-process model;
+    posted sends keep their order; the next micro-batch's receive is posted ahead of its use."""
+    import copy
+
+    import torch
+    from torch import nn
+
+    from ferrotorch_b200.parallel import Pipeline
+
+    try:
+        torch.set_num_threads(1)
+        if backend == "tcp":
+            g = _group(rank, world, port, timeout=30.0)
+            g.connect_mesh()
+        else:
+            import torch.distributed as dist
+
+            from ferrotorch_b200.parallel.backend import TorchGroup
+
+            dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+            g = TorchGroup()
+        # ordered non-blocking transfers: eight posted messages arrive in posting order
+        if rank == 0:
+            ops = [g.isend(torch.full((3,), float(i)), 1) for i in range(8)]
+            for op in ops:
+                op.wait()
+        elif rank == 1:
+            bufs = [torch.empty(3) for _ in range(8)]
+            ops = [g.irecv(b, 0) for b in bufs]
+            for op in ops:
+                op.wait()
+            assert [float(b[0]) for b in bufs] == [float(i) for i in range(8)], bufs
+        torch.manual_seed(0)
+        stages = [nn.Sequential(nn.Linear(6, 8), nn.Tanh()), nn.Sequential(nn.Linear(8, 8), nn.Tanh()), nn.Linear(8, 3)]
+        x, y = torch.randn(8, 6), torch.randn(8, 3)
+        ref = copy.deepcopy(nn.Sequential(*stages))
+        loss_ref = nn.functional.mse_loss(ref(x), y)
+        loss_ref.backward()
+        m = copy.deepcopy(stages[rank])
+        p = Pipeline(m, g, n_micro=4, schedule=schedule, loss_fn=nn.functional.mse_loss)
+        for step in range(2):                                   # second step: a fresh header, same shapes
+            m.zero_grad(set_to_none=True)
+            loss = p.train_step(x if rank == 0 else None, y if rank == world - 1 else None)
+        if rank == world - 1:
+            assert abs(float(loss) - float(loss_ref)) < 1e-6
+        for got, want in zip(m.parameters(), ref[rank].parameters()):
+            assert torch.allclose(got.grad, want.grad, atol=1e-6)
+        if rank > 0:
+            assert p.stats["prefetched_recvs"] >= 2 * 3, p.stats
+        if rank < world - 1:
+            assert p.stats["posted_sends"] >= 2 * 4, p.stats
+        g.barrier()
+        q.put((rank, "ok"))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "ERR %r %s" % (e, traceback.format_exc())))

@@ -226,6 +226,12 @@ def test_config0_tiny_llama_ddp_bitwise(backend):
     assert a["last"] < a["first"]
 
 
+@pytest.mark.parametrize("backend,schedule", [("tcp", "1f1b"), ("gloo", "1f1b"), ("gloo", "gpipe")])
+def test_pipeline_stages_as_processes_with_posted_transfers(backend, schedule):
+    out = _spawn(W.pipeline_case, 3, backend, schedule)
+    assert all(v == "ok" for v in out.values()), out
+
+
 def test_vocab_parallel_embedding_and_cross_entropy_gloo():
     out = _spawn(W.vocab_parallel_case, 2)
     assert all(v == "ok" for v in out.values()), out

@@ -286,6 +286,59 @@ def test_ring_and_ulysses_attention_equal_full_attention(world, causal):
         run_simulated(2, lambda g: CP.ulysses_attention(q[:, :2, :3], k[:, :2, :1], v[:, :2, :1], g))
 
 
+@pytest.mark.parametrize("world,causal", [(2, True), (4, True), (4, False), (3, True)])
+def test_ring_and_ulysses_attention_gradients_equal_full_attention(world, causal):
+    # backward of both schemes on simulated ranks against autograd through full attention:
+    # dq of the local queries, dk / dv of the local keys (GQA: summed over the query group)
+    from ferrotorch_b200.ops import reference as R
+    from ferrotorch_b200.parallel import context_parallel as CP
+    from ferrotorch_b200.parallel.backend import run_simulated
+
+    torch.manual_seed(1)
+    B, S_loc, Hq, Hkv, D = 2, 6, 12, 12 if world == 3 else 4, 8
+    S = world * S_loc
+    q, k, v = (torch.randn(B, S, h, D, requires_grad=True) for h in (Hq, Hkv, Hkv))
+    go = torch.randn(B, S, Hq, D)
+    R.attention(q, k, v, causal=causal)[0].backward(go)
+
+    def body(g):
+        sl = slice(g.rank * S_loc, (g.rank + 1) * S_loc)
+        res = []
+        for fn in (CP.ring_attention, CP.ulysses_attention):
+            if fn is CP.ulysses_attention and Hkv % g.world_size:
+                res.append(None)
+                continue
+            ql, kl, vl = (t[:, sl].detach().clone().requires_grad_() for t in (q, k, v))
+            fn(ql, kl, vl, g, causal).backward(go[:, sl])
+            res.append((ql.grad, kl.grad, vl.grad))
+        return res
+
+    for r, per_fn in enumerate(run_simulated(world, body)):
+        sl = slice(r * S_loc, (r + 1) * S_loc)
+        for name, grads in zip(("ring", "ulysses"), per_fn):
+            if grads is None:
+                continue
+            for got, want, what in zip(grads, (q.grad, k.grad, v.grad), "qkv"):
+                assert torch.allclose(got, want[:, sl], atol=2e-5), (name, r, what, (got - want[:, sl]).abs().max())
+
+
+def test_attention_block_backward_pieces_add_up():
+    # two key blocks with the statistics of the whole row: dq pieces add to the full dq, dk / dv are the blocks' own
+    from ferrotorch_b200.ops import reference as R
+    from ferrotorch_b200.ops.attention import attention_block_backward
+
+    torch.manual_seed(2)
+    q, k, v = (torch.randn(1, 7, h, 8, requires_grad=True) for h in (4, 2, 2))
+    go = torch.randn(1, 7, 4, 8)
+    out, lse = R.attention(q, k, v, causal=False)
+    out.backward(go)
+    dq1, dk1, dv1 = attention_block_backward(q.detach(), k.detach()[:, :3], v.detach()[:, :3], out.detach(), lse.detach(), go, False)
+    dq2, dk2, dv2 = attention_block_backward(q.detach(), k.detach()[:, 3:], v.detach()[:, 3:], out.detach(), lse.detach(), go, False)
+    assert torch.allclose(dq1 + dq2, q.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([dk1, dk2], 1), k.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([dv1, dv2], 1), v.grad, atol=1e-5)
+
+
 def test_hybrid_group_routes_by_device_and_checks_ranks():
     from ferrotorch_b200.parallel import backend as B
 
