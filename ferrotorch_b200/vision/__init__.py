@@ -5,10 +5,11 @@ segmenters, a model registry, MNIST / CIFAR / ImageFolder readers, 17 transforms
 NMS / RoIAlign (ferrotorch-vision/src/models/*, datasets/*, transforms/*, ops/*).  Here the ResNet
 family (``models/resnet.py``: channels-last bf16, convolutions on the tcgen05 GEMM, fused batch-norm
 kernels) and VGG-11/16, MobileNetV2, ViT-B/16, ConvNeXt-Tiny, DenseNet-121, FCN and DeepLabV3
-(``models/vision_zoo.py``; torchvision's parameter names, convolutions and attention on this
-framework's kernels) are this package's own; the remaining names (EfficientNet, Swin, Inception,
-MobileNetV3, the detectors, LRASPP) come from ``torchvision`` as part of the framework layer.  One
-registry serves all of them under the reference's names.
+(``models/vision_zoo.py``) and EfficientNet-B0, MobileNetV3, Inception v3, Swin-T and LRASPP
+(``models/vision_families.py``) are this package's own, with torchvision's parameter names and
+their dense convolutions and attention on this framework's kernels; the detectors come from
+``torchvision`` as part of the framework layer.  One registry serves all of them under the
+reference's names.
 """
 from __future__ import annotations
 
@@ -53,10 +54,12 @@ def build(name: str, **kw) -> nn.Module:
     first, torchvision for the rest)."""
     if name in list_models():
         return create_model(name, **kw)
+    from ..models.vision_families import OWN_MODELS as MORE
     from ..models.vision_zoo import OWN_MODELS
 
-    if name in OWN_MODELS:
-        return OWN_MODELS[name](**kw)
+    for own in (OWN_MODELS, MORE):
+        if name in own:
+            return own[name](**kw)
     for table in (CLASSIFIERS, DETECTORS, SEGMENTERS):
         if name in table:
             return _tv(table[name], **kw)

@@ -189,9 +189,45 @@ def test_own_segmentation_models_match_torchvision(name):
                          torch.randn(2, 3, 64, 64), lambda o: o["out"])
 
 
+@pytest.mark.parametrize("name,size", [("efficientnet_b0", (64, 64)), ("mobilenet_v3_large", (64, 64)),
+                                       ("mobilenet_v3_small", (64, 64)), ("inception_v3", (139, 139)), ("swin_t", (100, 84))])
+def test_own_classifier_families_match_torchvision(name, size):
+    # sizes that are not multiples of the window / stride exercise Swin's padding, shift masks and patch merging
+    tvm = pytest.importorskip("torchvision.models")
+    from ferrotorch_b200.models import vision_families as Z
+
+    torch.manual_seed(3)
+    kw = {"init_weights": False} if name == "inception_v3" else {}
+    _same_as_torchvision(getattr(Z, name)(num_classes=7), getattr(tvm, name)(weights=None, num_classes=7, **kw),
+                         torch.randn(2, 3, *size))
+
+
+def test_own_lraspp_matches_torchvision_and_families_train():
+    seg = pytest.importorskip("torchvision.models.segmentation")
+    from ferrotorch_b200.models import vision_families as Z
+
+    torch.manual_seed(4)
+    _same_as_torchvision(Z.lraspp_mobilenet_v3_large(num_classes=5),
+                         seg.lraspp_mobilenet_v3_large(weights=None, weights_backbone=None, num_classes=5),
+                         torch.randn(2, 3, 96, 80), lambda o: o["out"])
+    # training mode: stochastic depth, dropout and the auxiliary classifier are live, every parameter gets a gradient
+    net = Z.inception_v3(num_classes=3).train()
+    out, aux = net(torch.randn(2, 3, 299, 299))
+    (out.sum() + aux.sum()).backward()
+    assert all(p.grad is not None for p in net.parameters())
+    swin = Z.SwinTransformer(embed_dim=24, depths=(2, 2), heads=(2, 4), window=4, num_classes=3).train()
+    swin(torch.randn(2, 3, 40, 40)).sum().backward()
+    assert all(p.grad is not None for p in swin.parameters())
+
+
 def test_registry_prefers_own_models():
     from ferrotorch_b200 import vision as V
     from ferrotorch_b200.models import vision_zoo as Z
 
     assert isinstance(V.build("vgg16", num_classes=3), Z.VGG)
     assert isinstance(V.build("deeplabv3", num_classes=3), Z.SegmentationModel)
+    from ferrotorch_b200.models import vision_families as M
+
+    assert isinstance(V.build("efficientnet_b0", num_classes=3), M.EfficientNet)
+    assert isinstance(V.build("swin_t", num_classes=3), M.SwinTransformer)
+    assert isinstance(V.build("lraspp", num_classes=3), M.LRASPP)
