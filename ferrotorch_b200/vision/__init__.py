@@ -7,9 +7,11 @@ family (``models/resnet.py``: channels-last bf16, convolutions on the tcgen05 GE
 kernels) and VGG-11/16, MobileNetV2, ViT-B/16, ConvNeXt-Tiny, DenseNet-121, FCN and DeepLabV3
 (``models/vision_zoo.py``) and EfficientNet-B0, MobileNetV3, Inception v3, Swin-T and LRASPP
 (``models/vision_families.py``) are this package's own, with torchvision's parameter names and
-their dense convolutions and attention on this framework's kernels; the detectors come from
-``torchvision`` as part of the framework layer.  One registry serves all of them under the
-reference's names.
+their dense convolutions and attention on this framework's kernels; Faster / Mask / Keypoint
+R-CNN, RetinaNet, FCOS, SSD300 and the reference's small YOLO (``models/detection.py``) with their
+NMS / RoI-align / anchor operators (``vision/det_ops.py``) are own code as well.  Only
+``ssdlite`` (not in the reference's registry) still comes from ``torchvision``.  One registry
+serves all of them under the reference's names.
 """
 from __future__ import annotations
 
@@ -54,10 +56,11 @@ def build(name: str, **kw) -> nn.Module:
     first, torchvision for the rest)."""
     if name in list_models():
         return create_model(name, **kw)
+    from ..models.detection import OWN_MODELS as DET
     from ..models.vision_families import OWN_MODELS as MORE
     from ..models.vision_zoo import OWN_MODELS
 
-    for own in (OWN_MODELS, MORE):
+    for own in (OWN_MODELS, MORE, DET):
         if name in own:
             return own[name](**kw)
     for table in (CLASSIFIERS, DETECTORS, SEGMENTERS):

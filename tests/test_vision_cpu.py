@@ -220,6 +220,99 @@ def test_own_lraspp_matches_torchvision_and_families_train():
     assert all(p.grad is not None for p in swin.parameters())
 
 
+def test_own_detection_operators_match_torchvision():
+    O = pytest.importorskip("torchvision.ops")
+    from ferrotorch_b200.vision import det_ops as D
+
+    torch.manual_seed(5)
+
+    def rb(n, s=100.0):
+        xy, wh = torch.rand(n, 2) * s, torch.rand(n, 2) * s / 2 + 1
+        return torch.cat([xy, xy + wh], 1)
+
+    a, b, sc, idx = rb(50), rb(40), torch.rand(50), torch.randint(0, 3, (50,))
+    assert torch.allclose(D.box_iou(a, b), O.box_iou(a, b), atol=1e-6)
+    for t in (0.3, 0.5, 0.7):
+        assert torch.equal(D.nms(a, sc, t), O.nms(a, sc, t))
+    assert torch.equal(D.batched_nms(a, sc, idx, 0.5), O.batched_nms(a, sc, idx, 0.5))
+    feat = torch.randn(2, 5, 20, 24)
+    rois = torch.cat([torch.randint(0, 2, (30, 1)).float(), rb(30, 80)], 1)
+    rois[0, 1:] = torch.tensor([-20.0, -10.0, 5.0, 8.0])       # partly outside
+    rois[1, 1:] = torch.tensor([70.0, 60.0, 120.0, 130.0])     # beyond the far edge
+    rois[2, 1:] = torch.tensor([10.0, 10.0, 10.2, 10.1])       # smaller than one pixel
+    for aligned in (False, True):
+        for scale in (0.25, 1.0):
+            torch.testing.assert_close(D.roi_align(feat, rois, 7, scale, 2, aligned), O.roi_align(feat, rois, 7, scale, 2, aligned),
+                                       atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(D.roi_align(feat, rois, (3, 5), 0.5, 3), O.roi_align(feat, rois, (3, 5), 0.5, 3), atol=1e-5, rtol=1e-5)
+    feats = {str(i): torch.randn(2, 4, 64 >> i, 64 >> i) for i in range(4)}
+    boxes = [rb(20, 200), rb(15, 200)]
+    boxes[0][0], boxes[1][0] = torch.tensor([0.0, 0.0, 255.0, 255.0]), torch.tensor([5.0, 5.0, 9.0, 9.0])
+    want = O.MultiScaleRoIAlign(["0", "1", "2", "3"], 7, 2)(feats, boxes, [(256, 256), (256, 256)])
+    torch.testing.assert_close(D.MultiScaleRoIAlign(["0", "1", "2", "3"], 7, 2)(feats, boxes, (256, 256)), want, atol=1e-5, rtol=1e-5)
+
+
+def _same_detections(ours, tv, x, keys=("boxes", "scores", "labels")):
+    tv.eval(), ours.eval()
+    sd = tv.state_dict()
+    for k, v in sd.items():                                   # non-trivial batch-norm statistics
+        if k.endswith("running_mean"):
+            v.normal_(0, 0.1)
+        elif k.endswith("running_var"):
+            v.uniform_(0.5, 1.5)
+    ours.load_state_dict(sd, strict=True)                      # torchvision's parameter names
+    with torch.no_grad():
+        got, want = ours(x), tv(list(x))
+    for g, w in zip(got, want):
+        assert len(g["boxes"]) > 0
+        for k in keys:
+            if g[k].dtype.is_floating_point:
+                torch.testing.assert_close(g[k], w[k], atol=2e-3, rtol=1e-3)
+            else:
+                assert torch.equal(g[k], w[k])
+
+
+@pytest.mark.parametrize("name", ["fasterrcnn", "maskrcnn", "keypointrcnn", "retinanet", "fcos", "ssd300"])
+def test_own_detectors_match_torchvision(name):
+    # same weights, identity input transform on torchvision's side: proposals, scores, labels, masks and keypoints agree
+    TD = pytest.importorskip("torchvision.models.detection")
+    from ferrotorch_b200.models import detection as M
+
+    torch.manual_seed(6)
+    ident = dict(weights=None, weights_backbone=None, image_mean=[0.0, 0.0, 0.0], image_std=[1.0, 1.0, 1.0])
+    sized = dict(min_size=128, max_size=160, **ident)
+    x = torch.rand(2, 3, 128, 160)
+    if name == "fasterrcnn":
+        _same_detections(M.fasterrcnn_resnet50_fpn(5), TD.fasterrcnn_resnet50_fpn(num_classes=5, **sized), x)
+    elif name == "maskrcnn":
+        _same_detections(M.maskrcnn_resnet50_fpn(5), TD.maskrcnn_resnet50_fpn(num_classes=5, **sized), x,
+                         ("boxes", "scores", "labels", "masks"))
+    elif name == "keypointrcnn":
+        _same_detections(M.keypointrcnn_resnet50_fpn(2, 17), TD.keypointrcnn_resnet50_fpn(num_classes=2, num_keypoints=17, **sized),
+                         x, ("boxes", "scores", "labels", "keypoints", "keypoints_scores"))
+    elif name == "retinanet":
+        _same_detections(M.retinanet_resnet50_fpn(5, score_thresh=0.0),
+                         TD.retinanet_resnet50_fpn(num_classes=5, score_thresh=0.0, **sized), x)
+    elif name == "fcos":
+        _same_detections(M.fcos_resnet50_fpn(5, score_thresh=0.0), TD.fcos_resnet50_fpn(num_classes=5, score_thresh=0.0, **sized), x)
+    else:
+        _same_detections(M.ssd300_vgg16(5, normalize=False), TD.ssd300_vgg16(num_classes=5, **ident), torch.rand(2, 3, 300, 300))
+
+
+def test_yolo_grid_and_decoding():
+    from ferrotorch_b200.models import detection as M
+
+    torch.manual_seed(7)
+    net = M.yolo(4).eval()
+    assert sorted(net.state_dict())[:2] == ["backbone.stage1.conv.weight", "backbone.stage2.conv.weight"] and "head.bias" in net.state_dict()
+    grid = net(torch.rand(2, 3, 416, 416))
+    assert grid.shape == (2, 3 * (5 + 4), 13, 13)
+    det = net.decode(grid, [(30, 40), (80, 60), (150, 200)], (416, 416), conf_thresh=0.0, nms_thresh=0.5)
+    for d in det:
+        assert len(d["boxes"]) > 0 and d["boxes"].min() >= 0 and d["boxes"].max() <= 416
+        assert (d["scores"][:-1] >= d["scores"][1:]).all() and set(d["labels"].tolist()) <= {0, 1, 2, 3}
+
+
 def test_registry_prefers_own_models():
     from ferrotorch_b200 import vision as V
     from ferrotorch_b200.models import vision_zoo as Z
@@ -231,3 +324,6 @@ def test_registry_prefers_own_models():
     assert isinstance(V.build("efficientnet_b0", num_classes=3), M.EfficientNet)
     assert isinstance(V.build("swin_t", num_classes=3), M.SwinTransformer)
     assert isinstance(V.build("lraspp", num_classes=3), M.LRASPP)
+    from ferrotorch_b200.models import detection as Dm
+
+    assert isinstance(V.build("retinanet", num_classes=3), Dm.RetinaNet) and isinstance(V.build("yolo", num_classes=3), Dm.Yolo)
