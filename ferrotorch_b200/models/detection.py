@@ -130,10 +130,11 @@ class RegionProposalNetwork(nn.Module):
     of the image are kept."""
 
     def __init__(self, in_channels: int = 256, anchors: D.AnchorGenerator | None = None, pre_nms_top_n: int = 1000,
-                 post_nms_top_n: int = 1000, nms_thresh: float = 0.7, score_thresh: float = 0.0, min_size: float = 1e-3):
+                 post_nms_top_n: int = 1000, nms_thresh: float = 0.7, score_thresh: float = 0.0, min_size: float = 1e-3,
+                 head: RPNHead | None = None):
         super().__init__()
         self.anchor_generator = anchors or D.AnchorGenerator()
-        self.head = RPNHead(in_channels, self.anchor_generator.num_anchors_per_location()[0])
+        self.head = head or RPNHead(in_channels, self.anchor_generator.num_anchors_per_location()[0])
         self.pre_nms_top_n, self.post_nms_top_n = pre_nms_top_n, post_nms_top_n
         self.nms_thresh, self.score_thresh, self.min_size = nms_thresh, score_thresh, min_size
 
@@ -183,6 +184,17 @@ class FastRCNNPredictor(nn.Module):
     def forward(self, x):
         x = x.flatten(1)
         return self.cls_score(x), self.bbox_pred(x)
+
+
+class MaskRCNNHeads(nn.Sequential):
+    """The mask branch's tower: 3 x 3 convolutions + ReLU on the 14 x 14 pooled features."""
+
+    def __init__(self, in_channels: int, layers=(256, 256, 256, 256), dilation: int = 1):
+        blocks, cin = [], in_channels
+        for c in layers:
+            blocks.append(nn.Sequential(nn.Conv2d(cin, c, 3, padding=dilation, dilation=dilation), nn.ReLU(inplace=True)))
+            cin = c
+        super().__init__(*blocks)
 
 
 class MaskRCNNPredictor(nn.Sequential):
@@ -259,7 +271,7 @@ class RoIHeads(nn.Module):
 
     def add_mask_branch(self, num_classes: int) -> None:
         self.mask_roi_pool = D.MultiScaleRoIAlign(["0", "1", "2", "3"], 14, 2)
-        self.mask_head = nn.Sequential(*[nn.Sequential(nn.Conv2d(256, 256, 3, padding=1), nn.ReLU(inplace=True)) for _ in range(4)])
+        self.mask_head = MaskRCNNHeads(256, (256, 256, 256, 256))
         self.mask_predictor = MaskRCNNPredictor(256, 256, num_classes)
 
     def add_keypoint_branch(self, num_keypoints: int) -> None:

@@ -1,7 +1,8 @@
-"""The reference's ``ferrotorch-vision`` names over torchvision (ferrotorch-vision/src/lib.rs
-re-exports: datasets, transforms, detection / segmentation building blocks, the model registry,
-feature extraction).  Nothing here computes: each name points at the torchvision object that
-provides the behaviour, or wraps this package's registry."""
+"""The reference's ``ferrotorch-vision`` names (ferrotorch-vision/src/lib.rs re-exports: datasets,
+transforms, detection / segmentation building blocks, the model registry, feature extraction).
+Models, heads, anchors and the feature extractor point at this package's own modules
+(``models/detection.py``, ``models/vision_zoo.py``, ``vision/det_ops.py``); datasets and image
+transforms point at the torchvision objects that provide the behaviour."""
 from __future__ import annotations
 
 import enum
@@ -10,18 +11,15 @@ from typing import Callable, Dict
 import torch
 from torch import nn
 
-import torchvision
 from torchvision import transforms as T
 from torchvision.datasets import CIFAR10 as Cifar10, CIFAR100 as Cifar100, MNIST as Mnist  # noqa: F401
-from torchvision.models import detection as _det, segmentation as _seg
-from torchvision.models.detection.anchor_utils import AnchorGenerator  # noqa: F401
-from torchvision.models.detection.faster_rcnn import TwoMLPHead as TwoMlpHead  # noqa: F401
-from torchvision.models.detection.mask_rcnn import MaskRCNNHeads as MaskHead, MaskRCNNPredictor as MaskPredictor  # noqa: F401
-from torchvision.models.detection.rpn import RegionProposalNetwork as Rpn, RPNHead as RpnHead  # noqa: F401
-from torchvision.models.feature_extraction import create_feature_extractor as _tv_extractor
-from torchvision.models.segmentation.deeplabv3 import ASPP as Aspp, DeepLabHead as DeepLabV3Head  # noqa: F401
-from torchvision.models.segmentation.fcn import FCNHead as FcnHead  # noqa: F401
-from torchvision.ops import FeaturePyramidNetwork  # noqa: F401
+
+from ..models import detection as _det
+from ..models import vision_zoo as _zoo
+from ..models.detection import (FeaturePyramidNetwork, MaskRCNNHeads as MaskHead, MaskRCNNPredictor as MaskPredictor,  # noqa: F401
+                                RegionProposalNetwork as Rpn, RPNHead as RpnHead, TwoMLPHead as TwoMlpHead)
+from ..models.vision_zoo import ASPP as Aspp, DeepLabHead as DeepLabV3Head, FCNHead as FcnHead  # noqa: F401
+from .det_ops import AnchorGenerator  # noqa: F401
 
 IMAGENET_MEAN = (0.485, 0.456, 0.406)
 IMAGENET_STD = (0.229, 0.224, 0.225)
@@ -33,10 +31,9 @@ SSD_TOTAL_ANCHORS = sum(f * f * a for f, a in zip(SSD_FM_SIZES, SSD_ANCHORS_PER_
 CenterCrop, ColorJitter, RandomApply, RandomChoice = T.CenterCrop, T.ColorJitter, T.RandomApply, T.RandomChoice
 RandomResizedCrop, RandomRotation, RandomVerticalFlip, Resize = T.RandomResizedCrop, T.RandomRotation, T.RandomVerticalFlip, T.Resize
 
-from torchvision.models.detection.ssd import SSD as Ssd300  # noqa: E402
-
+Ssd300 = _det.SSD300
 FasterRcnn, MaskRcnn = _det.FasterRCNN, _det.MaskRCNN
-DeepLabV3, Fcn = _seg.DeepLabV3, _seg.FCN
+DeepLabV3 = Fcn = _zoo.SegmentationModel
 Detections = Dict[str, torch.Tensor]          # {"boxes", "labels", "scores"}: what the detectors return per image
 MaskDetections = Dict[str, torch.Tensor]      # ... plus "masks"
 SsdDetections = Dict[str, torch.Tensor]
@@ -54,43 +51,32 @@ class Split(enum.Enum):
 
 
 class RpnConfig:
-    """Keyword arguments of the region-proposal network with torchvision's Faster R-CNN defaults."""
+    """Settings of the region-proposal network (ferrotorch-vision/src/models/detection/rpn.rs
+    ``RpnConfig::default_eval``: 1000 proposals before and after NMS, NMS at 0.7, no score
+    threshold, boxes below 1e-3 pixels dropped)."""
 
-    def __init__(self, pre_nms_top_n_train=2000, pre_nms_top_n_test=1000, post_nms_top_n_train=2000,
-                 post_nms_top_n_test=1000, nms_thresh=0.7, fg_iou_thresh=0.7, bg_iou_thresh=0.3,
-                 batch_size_per_image=256, positive_fraction=0.5, score_thresh=0.0):
+    def __init__(self, pre_nms_top_n=1000, post_nms_top_n=1000, nms_thresh=0.7, score_thresh=0.0, min_size=1e-3):
         self.__dict__.update({k: v for k, v in locals().items() if k != "self"})
 
     def build(self, anchor_generator, head) -> "Rpn":
         c = self.__dict__
-        return Rpn(anchor_generator, head, c["fg_iou_thresh"], c["bg_iou_thresh"], c["batch_size_per_image"],
-                   c["positive_fraction"], {"training": c["pre_nms_top_n_train"], "testing": c["pre_nms_top_n_test"]},
-                   {"training": c["post_nms_top_n_train"], "testing": c["post_nms_top_n_test"]}, c["nms_thresh"], c["score_thresh"])
+        return Rpn(head.cls_logits.in_channels, anchor_generator, c["pre_nms_top_n"], c["post_nms_top_n"], c["nms_thresh"],
+                   c["score_thresh"], c["min_size"], head=head)
 
 
-def _no_weights(ctor):
-    def make(num_classes: int | None = None, **kw):
-        kw.setdefault("weights", None)
-        kw.setdefault("weights_backbone", None)
-        if num_classes is not None:
-            kw["num_classes"] = num_classes
-        return ctor(**kw)
-    make.__name__ = ctor.__name__
-    make.__doc__ = "``torchvision``'s %s with random weights unless ``weights=`` is given." % ctor.__name__
-    return make
-
-
-fasterrcnn_resnet50_fpn = _no_weights(_det.fasterrcnn_resnet50_fpn)
-maskrcnn_resnet50_fpn = _no_weights(_det.maskrcnn_resnet50_fpn)
-ssd300_vgg16 = _no_weights(_det.ssd300_vgg16)
-deeplabv3_resnet50 = _no_weights(_seg.deeplabv3_resnet50)
-fcn_resnet50 = _no_weights(_seg.fcn_resnet50)
+fasterrcnn_resnet50_fpn = _det.fasterrcnn_resnet50_fpn
+maskrcnn_resnet50_fpn = _det.maskrcnn_resnet50_fpn
+ssd300_vgg16 = _det.ssd300_vgg16
+deeplabv3_resnet50 = _zoo.deeplabv3_resnet50
+fcn_resnet50 = _zoo.fcn_resnet50
 
 
 def ResNet50Dilated(num_classes: int = 1000, **kw) -> nn.Module:
     """ResNet-50 with strides of the last two stages replaced by dilation (output stride 8),
     the segmentation backbone."""
-    return torchvision.models.resnet50(weights=None, num_classes=num_classes, replace_stride_with_dilation=[False, True, True], **kw)
+    from ..models.resnet import resnet50
+
+    return resnet50(num_classes=num_classes, replace_stride_with_dilation=(False, True, True), **kw)
 
 
 class ModelRegistry:
@@ -128,14 +114,29 @@ def get_model(name: str, **kw) -> nn.Module:
 
 
 class FeatureExtractor(nn.Module):
-    """Intermediate activations by node name: ``{output name: tensor}``."""
+    """Intermediate activations by sub-module name: ``{output name: tensor}``
+    (ferrotorch-vision/src/models/feature_extractor.rs).  ``return_nodes`` maps dotted sub-module
+    names (``"layer2"``, ``"features.3"``) to output names, or lists the names to keep as they
+    are; the outputs are collected by forward hooks during one ordinary forward pass."""
 
     def __init__(self, model: nn.Module, return_nodes):
         super().__init__()
-        self.body = _tv_extractor(model, return_nodes)
+        self.body = model
+        self.nodes = dict(return_nodes) if isinstance(return_nodes, dict) else {n: n for n in return_nodes}
+        for n in self.nodes:
+            model.get_submodule(n)                      # raises on an unknown name
 
     def forward(self, x: torch.Tensor) -> dict:
-        return self.body(x)
+        got, handles = {}, []
+        for node, name in self.nodes.items():
+            handles.append(self.body.get_submodule(node).register_forward_hook(
+                lambda _m, _i, out, name=name: got.__setitem__(name, out)))
+        try:
+            self.body(x)
+        finally:
+            for h in handles:
+                h.remove()
+        return {name: got[name] for name in self.nodes.values()}
 
 
 def create_feature_extractor(model: nn.Module, return_nodes) -> FeatureExtractor:
