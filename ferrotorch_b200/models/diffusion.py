@@ -20,6 +20,16 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+# Set by ``models/diffusion_gpu.py`` while one of its device twins runs: attention then goes through
+# its dispatcher (flash-attention kernel where a head size fits) instead of the library call.
+_attention_override = None
+
+
+def _sdpa(q, k, v, is_causal: bool = False):
+    if _attention_override is not None:
+        return _attention_override(q, k, v, is_causal)
+    return F.scaled_dot_product_attention(q, k, v, is_causal=is_causal)
+
 
 def _from_json(cls, src, rename: dict | None = None):
     raw = src
@@ -163,7 +173,7 @@ class _ClipAttention(nn.Module):
     def forward(self, x):
         B, S, E = x.shape
         q, k, v = (p(x).view(B, S, self.h, E // self.h).transpose(1, 2) for p in (self.q_proj, self.k_proj, self.v_proj))
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=True)       # CLIP's text tower is causal
+        o = _sdpa(q, k, v, is_causal=True)       # CLIP's text tower is causal
         return self.out_proj(o.transpose(1, 2).reshape(B, S, E))
 
 
@@ -287,7 +297,7 @@ class _Attention(nn.Module):
         ctx = x if ctx is None else ctx
         B, S, E = x.shape
         split = lambda t: t.view(B, -1, self.heads, E // self.heads).transpose(1, 2)  # noqa: E731
-        o = F.scaled_dot_product_attention(split(self.to_q(x)), split(self.to_k(ctx)), split(self.to_v(ctx)))
+        o = _sdpa(split(self.to_q(x)), split(self.to_k(ctx)), split(self.to_v(ctx)))
         return self.to_out[0](o.transpose(1, 2).reshape(B, S, E))
 
 
@@ -569,7 +579,7 @@ class _VaeAttention(nn.Module):
     def forward(self, x):
         B, C, H, W = x.shape
         h = self.group_norm(x).flatten(2).transpose(1, 2)
-        o = F.scaled_dot_product_attention(self.to_q(h)[:, None], self.to_k(h)[:, None], self.to_v(h)[:, None])[:, 0]
+        o = _sdpa(self.to_q(h)[:, None], self.to_k(h)[:, None], self.to_v(h)[:, None])[:, 0]
         return x + self.to_out[0](o).transpose(1, 2).reshape(B, C, H, W)
 
 

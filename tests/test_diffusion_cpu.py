@@ -216,3 +216,50 @@ def test_reference_block_names_and_part_loaders(tmp_path):
     assert isinstance(enc, D.VaeEncoder)
     with pytest.raises(FileNotFoundError):
         D.load_unet(str(tmp_path))
+
+
+def test_device_fast_path_pieces_on_the_host():
+    """The device twins are the plain modules plus an attention dispatcher and the Philox
+    generator: on the host they must reproduce the plain pipeline, and the head-size padding the
+    dispatcher does for the kernel must not change the result."""
+    import copy
+
+    from ferrotorch_b200.models import diffusion_gpu as G
+    from ferrotorch_b200.utils.philox import PhiloxGenerator
+
+    torch.manual_seed(11)
+    assert [G.pad_head_dim(d) for d in (8, 40, 64, 80, 128, 160, 512)] == [64, 64, 64, 128, 128, None, None]
+    for d, sq, sk, causal in ((40, 9, 9, False), (80, 7, 13, False), (64, 6, 6, True), (24, 5, 5, True)):
+        q, k, v = torch.randn(2, 3, sq, d), torch.randn(2, 3, sk, d), torch.randn(2, 3, sk, d)
+        want = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal)
+        assert torch.allclose(G.attend(q, k, v, causal, force_padded=True), want, atol=1e-5), (d, causal)
+    q = torch.randn(1, 1, 4, 160)
+    before = G.stats["library"]
+    G.attend(q, q, q, force_padded=True)                       # no kernel head size for 160: library call
+    assert G.stats["library"] == before + 1
+
+    clip, unet, vae = _tiny()
+    plain = D.StableDiffusionPipeline(copy.deepcopy(clip), copy.deepcopy(unet), copy.deepcopy(vae))
+    fast = G.GpuStableDiffusionPipeline(D.StableDiffusionPipeline(clip, unet, vae), device="cpu", dtype=torch.float32)
+    ids = torch.randint(2, 100, (2, 6))
+    lat = fast.initial_latents(2, 32, 32, seed=9)
+    g = PhiloxGenerator(9)
+    want = torch.from_numpy(g.generate_normal(lat.numel())).view_as(lat)
+    assert torch.allclose(lat, want.to(lat.dtype)), "initial latents are the host generator's normal stream"
+    assert torch.equal(lat, fast.initial_latents(2, 32, 32, seed=9)) and not torch.equal(lat, fast.initial_latents(2, 32, 32, seed=10))
+    cond, unc = fast.text_encoder(ids), fast.text_encoder(torch.full_like(ids, 1))
+    assert torch.allclose(cond, plain.encode_prompt(ids), atol=1e-5)
+    got = fast.generate(cond, unc, lat, 3, guidance_scale=5.0)
+    ref, _ = plain.generate(plain.encode_prompt(ids), plain.encode_prompt(torch.full_like(ids, 1)), lat, 3, guidance_scale=5.0)
+    assert got.shape == (2, 3, 32, 32) and torch.allclose(got, ref, atol=1e-4)
+    assert fast(ids, height=32, width=32, num_inference_steps=2, seed=3).shape == (2, 3, 32, 32)
+    enc = G.GpuVaeEncoder(copy.deepcopy(vae.encoder), device="cpu", dtype=torch.float32)
+    z1 = enc.sample(torch.randn(1, 3, 32, 32), R_gen(5))
+    assert z1.shape[1] == vae.config.latent_channels and torch.isfinite(z1).all()
+    assert D._attention_override is None, "the dispatcher is only installed while a twin runs"
+
+
+def R_gen(seed):
+    from ferrotorch_b200.ops.random import DevicePhilox
+
+    return DevicePhilox(seed, "cpu")
