@@ -7,7 +7,7 @@ The reference implements them in ``ferrotorch-vision/src/models/detection/`` (``
 ``fcos.rs``, ``ssd.rs``, ``roi_heads_postprocess.rs``) and ``models/yolo.rs``, inference only, with
 torchvision's parameter names so that torchvision checkpoints load.  The modules here keep those
 names (the tests load a torchvision state dict with ``strict=True`` and compare detections), sit on
-this package's own ResNet / VGG, and use the plain-torch operators of ``vision/det_ops.py`` (NMS,
+this package's own ResNet / VGG, and use the plain-torch operators of ``ops/det_ops.py`` (NMS,
 RoI align, box decoding, anchors).  Like the reference's ``forward`` they take a batch
 ``[B, 3, H, W]`` that is already normalised and sized (H, W multiples of 32 for the pyramid
 models; SSD resizes to 300 x 300 itself) and return one ``{"boxes", "scores", "labels", ...}``
@@ -23,7 +23,7 @@ import torch.nn.functional as tF
 from torch import nn
 
 from ..ops.conv import convert_convs
-from ..vision import det_ops as D
+from ..ops import det_ops as D
 from .resnet import resnet50
 
 

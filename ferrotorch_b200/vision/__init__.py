@@ -9,7 +9,7 @@ kernels) and VGG-11/16, MobileNetV2, ViT-B/16, ConvNeXt-Tiny, DenseNet-121, FCN 
 (``models/vision_families.py``) are this package's own, with torchvision's parameter names and
 their dense convolutions and attention on this framework's kernels; Faster / Mask / Keypoint
 R-CNN, RetinaNet, FCOS, SSD300 and the reference's small YOLO (``models/detection.py``) with their
-NMS / RoI-align / anchor operators (``vision/det_ops.py``) are own code as well.  Only
+NMS / RoI-align / anchor operators (``ops/det_ops.py``) are own code as well.  Only
 ``ssdlite`` (not in the reference's registry) still comes from ``torchvision``.  One registry
 serves all of them under the reference's names.
 """
@@ -110,6 +110,8 @@ class UNet(nn.Module):
 from .io import (GaussianNoise, RandomGaussianBlur, RawImage, VisionNormalize, VisionToTensor,  # noqa: F401,E402
                  raw_image_to_tensor, read_image, read_image_as_tensor, read_image_rgba, tensor_to_raw_image,
                  vision_manual_seed, write_image, write_tensor_as_image)
+
+from . import det_ops  # noqa: F401,E402
 
 if HAVE_TORCHVISION:
     from .compat import *  # noqa: F401,F403,E402

@@ -1,7 +1,7 @@
 """The reference's ``ferrotorch-vision`` names (ferrotorch-vision/src/lib.rs re-exports: datasets,
 transforms, detection / segmentation building blocks, the model registry, feature extraction).
 Models, heads, anchors and the feature extractor point at this package's own modules
-(``models/detection.py``, ``models/vision_zoo.py``, ``vision/det_ops.py``); datasets and image
+(``models/detection.py``, ``models/vision_zoo.py``, ``ops/det_ops.py``); datasets and image
 transforms point at the torchvision objects that provide the behaviour."""
 from __future__ import annotations
 
@@ -19,7 +19,7 @@ from ..models import vision_zoo as _zoo
 from ..models.detection import (FeaturePyramidNetwork, MaskRCNNHeads as MaskHead, MaskRCNNPredictor as MaskPredictor,  # noqa: F401
                                 RegionProposalNetwork as Rpn, RPNHead as RpnHead, TwoMLPHead as TwoMlpHead)
 from ..models.vision_zoo import ASPP as Aspp, DeepLabHead as DeepLabV3Head, FCNHead as FcnHead  # noqa: F401
-from .det_ops import AnchorGenerator  # noqa: F401
+from ..ops.det_ops import AnchorGenerator  # noqa: F401
 
 IMAGENET_MEAN = (0.485, 0.456, 0.406)
 IMAGENET_STD = (0.229, 0.224, 0.225)

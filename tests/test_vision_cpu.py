@@ -222,7 +222,7 @@ def test_own_lraspp_matches_torchvision_and_families_train():
 
 def test_own_detection_operators_match_torchvision():
     O = pytest.importorskip("torchvision.ops")
-    from ferrotorch_b200.vision import det_ops as D
+    from ferrotorch_b200.ops import det_ops as D
 
     torch.manual_seed(5)
 
