@@ -179,6 +179,31 @@ def bench_philox(quick):
     emit("philox_host_generator", values=n, uniform_mvalues_per_s=n / u / 1e6, normal_mvalues_per_s=n / nrm / 1e6)
 
 
+def bench_detection_ops(quick):
+    """Greedy NMS and RoI align of the host library against their torch formulations."""
+    import torch
+
+    from ferrotorch_b200.ops import det_ops as D
+
+    torch.manual_seed(0)
+    n = 1000 if quick else 4000
+    xy, wh = torch.rand(n, 2) * 500, torch.rand(n, 2) * 80 + 2
+    boxes, scores = torch.cat([xy, xy + wh], 1), torch.rand(n)
+    for name, fn in (("native", D.nms), ("torch", D.nms_torch)):
+        fn(boxes, scores, 0.5)
+        t0 = time.perf_counter()
+        kept = fn(boxes, scores, 0.5)
+        emit("nms_host", implementation=name, boxes=n, kept=len(kept), ms=(time.perf_counter() - t0) * 1e3)
+    feat = torch.randn(2, 256, 50, 68)
+    k = 128 if quick else 512
+    rois = torch.cat([torch.randint(0, 2, (k, 1)).float(), boxes[:k] * 0.5], 1)
+    for name, fn in (("native", D.roi_align), ("torch", D.roi_align_torch)):
+        fn(feat, rois[:8], 7, 0.25, 2)
+        t0 = time.perf_counter()
+        fn(feat, rois, 7, 0.25, 2)
+        emit("roi_align_host", implementation=name, rois=k, channels=256, ms=(time.perf_counter() - t0) * 1e3)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
@@ -186,7 +211,7 @@ def main():
     args = ap.parse_args()
     torch.set_num_threads(max(1, (os.cpu_count() or 2) // 2))
     benches = {"loader": bench_loader, "allreduce": bench_allreduce, "gguf": bench_gguf, "grammar": bench_grammar,
-               "state_dict": bench_state_dict, "philox": bench_philox}
+               "state_dict": bench_state_dict, "philox": bench_philox, "detection": bench_detection_ops}
     for name, fn in benches.items():
         if not args.only or name in args.only.split(","):
             fn(args.quick)

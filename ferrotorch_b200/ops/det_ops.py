@@ -1,6 +1,7 @@
-"""Detection operators written in plain torch: box IoU, greedy non-maximum suppression (single and
-per-class), RoI align with the sampling rules of the detectors' checkpoints, box coders, anchor and
-default-box generators.
+"""Detection operators: box IoU, greedy non-maximum suppression (single and per-class), RoI align
+with the sampling rules of the detectors' checkpoints, box coders, anchor and default-box
+generators.  The NMS sweep and the fp32 host RoI align run in the native host library
+(``csrc/host/det_ops.cpp``); everything has a torch formulation as well (any device, autograd).
 
 The reference has them in ``ferrotorch-vision/src/ops/`` (``nms``, ``roi_align``, ``box_iou``),
 ``models/detection/anchor_utils.rs`` (``AnchorGenerator``, SSD default boxes) and
@@ -31,10 +32,27 @@ def box_iou(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return inter / (box_area(a)[:, None] + box_area(b)[None, :] - inter)
 
 
-def nms(boxes: torch.Tensor, scores: torch.Tensor, iou_threshold: float) -> torch.Tensor:
-    """Indices of the kept boxes, highest score first.  One IoU matrix, then a sequential sweep over
-    the boxes in score order on a boolean "suppressed" vector (the sweep is inherently serial: a
-    box is kept only if no *kept* box before it overlaps it)."""
+def _host_lib():
+    """The native host library with the prototypes of its detection entry points set (``None`` when
+    it cannot be built or loaded)."""
+    import ctypes
+
+    from .. import _native
+
+    lib = _native.host(required=False)
+    if lib is not None and not getattr(lib, "_ftd_ready", False):
+        vp, ll, ci, cf = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+        lib.ftd_nms.restype, lib.ftd_nms.argtypes = ll, [vp, ll, cf, vp]
+        lib.ftd_roi_align.restype = ci
+        lib.ftd_roi_align.argtypes = [vp, ci, ci, ci, ci, vp, ll, ci, ci, cf, ci, ci, vp]
+        lib._ftd_ready = True
+    return lib
+
+
+def nms_torch(boxes: torch.Tensor, scores: torch.Tensor, iou_threshold: float) -> torch.Tensor:
+    """NMS in torch operations: one IoU matrix, then a sequential sweep over the boxes in score
+    order on a boolean "suppressed" vector (the sweep is inherently serial: a box is kept only if
+    no *kept* box before it overlaps it)."""
     if boxes.numel() == 0:
         return torch.empty((0,), dtype=torch.int64, device=boxes.device)
     order = scores.argsort(descending=True, stable=True)
@@ -49,6 +67,24 @@ def nms(boxes: torch.Tensor, scores: torch.Tensor, iou_threshold: float) -> torc
         keep.append(i)
         dead |= over[i]
     return order[torch.tensor(keep, dtype=torch.int64, device=boxes.device)]
+
+
+def nms(boxes: torch.Tensor, scores: torch.Tensor, iou_threshold: float) -> torch.Tensor:
+    """Indices of the kept boxes, highest score first.  The boxes are sorted on their own device and
+    the sweep runs in the native host library (``csrc/host/det_ops.cpp``: a candidate is compared
+    only with the boxes kept so far); :func:`nms_torch` is the fallback without the library."""
+    if boxes.numel() == 0:
+        return torch.empty((0,), dtype=torch.int64, device=boxes.device)
+    lib = _host_lib()
+    if lib is None:
+        return nms_torch(boxes, scores, iou_threshold)
+    order = scores.argsort(descending=True, stable=True)
+    b = boxes[order].detach().to("cpu", torch.float32).contiguous()
+    keep = torch.empty(b.shape[0], dtype=torch.int64)
+    n = lib.ftd_nms(b.data_ptr(), b.shape[0], float(iou_threshold), keep.data_ptr())
+    if n < 0:
+        raise RuntimeError("ftd_nms failed (%d)" % n)
+    return order[keep[:n].to(boxes.device)]
 
 
 def batched_nms(boxes: torch.Tensor, scores: torch.Tensor, idxs: torch.Tensor, iou_threshold: float) -> torch.Tensor:
@@ -117,10 +153,9 @@ def _bilinear(feat: torch.Tensor, y: torch.Tensor, x: torch.Tensor) -> torch.Ten
     return val.masked_fill(outside, 0)
 
 
-def roi_align(feat: torch.Tensor, rois: torch.Tensor, output_size: int | tuple[int, int], spatial_scale: float = 1.0,
-              sampling_ratio: int = 2, aligned: bool = False) -> torch.Tensor:
-    """``feat [N, C, H, W]``, ``rois [K, 5]`` (batch index, x1, y1, x2, y2 in image coordinates) ->
-    ``[K, C, ph, pw]``: every output bin is the mean of ``sampling_ratio^2`` bilinear samples."""
+def roi_align_torch(feat: torch.Tensor, rois: torch.Tensor, output_size: int | tuple[int, int], spatial_scale: float = 1.0,
+                    sampling_ratio: int = 2, aligned: bool = False) -> torch.Tensor:
+    """RoI align in torch operations (any device, differentiable in ``feat``)."""
     ph, pw = (output_size, output_size) if isinstance(output_size, int) else output_size
     assert sampling_ratio > 0, "adaptive sampling (sampling_ratio <= 0) is not implemented"
     K, s = rois.shape[0], sampling_ratio
@@ -146,6 +181,26 @@ def roi_align(feat: torch.Tensor, rois: torch.Tensor, output_size: int | tuple[i
         v = _bilinear(feat[b], yy, xx)                                                 # [C, k, ph*s, pw*s]
         v = v.reshape(v.shape[0], len(sel), ph, s, pw, s).mean((3, 5))
         out[sel] = v.permute(1, 0, 2, 3).to(out.dtype)
+    return out
+
+
+def roi_align(feat: torch.Tensor, rois: torch.Tensor, output_size: int | tuple[int, int], spatial_scale: float = 1.0,
+              sampling_ratio: int = 2, aligned: bool = False) -> torch.Tensor:
+    """``feat [N, C, H, W]``, ``rois [K, 5]`` (batch index, x1, y1, x2, y2 in image coordinates) ->
+    ``[K, C, ph, pw]``: every output bin is the mean of ``sampling_ratio^2`` bilinear samples.
+    fp32 host tensors outside autograd go through the native library (``ftd_roi_align``), everything
+    else through :func:`roi_align_torch`."""
+    lib = _host_lib() if (not feat.is_cuda and feat.dtype == torch.float32 and rois.shape[0] > 0
+                          and not (feat.requires_grad and torch.is_grad_enabled())) else None
+    if lib is None:
+        return roi_align_torch(feat, rois, output_size, spatial_scale, sampling_ratio, aligned)
+    ph, pw = (output_size, output_size) if isinstance(output_size, int) else output_size
+    f, r = feat.detach().contiguous(), rois.detach().to(torch.float32).contiguous()
+    out = torch.empty((r.shape[0], f.shape[1], ph, pw), dtype=torch.float32)
+    rc = lib.ftd_roi_align(f.data_ptr(), f.shape[0], f.shape[1], f.shape[2], f.shape[3], r.data_ptr(), r.shape[0], ph, pw,
+                           float(spatial_scale), int(sampling_ratio), int(bool(aligned)), out.data_ptr())
+    if rc != 0:
+        raise RuntimeError("ftd_roi_align failed (%d)" % rc)
     return out
 
 

@@ -233,7 +233,9 @@ def test_own_detection_operators_match_torchvision():
     a, b, sc, idx = rb(50), rb(40), torch.rand(50), torch.randint(0, 3, (50,))
     assert torch.allclose(D.box_iou(a, b), O.box_iou(a, b), atol=1e-6)
     for t in (0.3, 0.5, 0.7):
-        assert torch.equal(D.nms(a, sc, t), O.nms(a, sc, t))
+        assert torch.equal(D.nms(a, sc, t), O.nms(a, sc, t))              # sweep in the native host library
+        assert torch.equal(D.nms_torch(a, sc, t), O.nms(a, sc, t))        # torch formulation
+    assert D._host_lib() is not None, "the native host library must be the path that runs"
     assert torch.equal(D.batched_nms(a, sc, idx, 0.5), O.batched_nms(a, sc, idx, 0.5))
     feat = torch.randn(2, 5, 20, 24)
     rois = torch.cat([torch.randint(0, 2, (30, 1)).float(), rb(30, 80)], 1)
@@ -245,6 +247,12 @@ def test_own_detection_operators_match_torchvision():
             torch.testing.assert_close(D.roi_align(feat, rois, 7, scale, 2, aligned), O.roi_align(feat, rois, 7, scale, 2, aligned),
                                        atol=1e-5, rtol=1e-5)
     torch.testing.assert_close(D.roi_align(feat, rois, (3, 5), 0.5, 3), O.roi_align(feat, rois, (3, 5), 0.5, 3), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(D.roi_align_torch(feat, rois, 7, 0.25, 2, True), O.roi_align(feat, rois, 7, 0.25, 2, True), atol=1e-5, rtol=1e-5)
+    fr = feat.clone().requires_grad_()                                  # under autograd: the torch formulation, with a gradient
+    ft_ = feat.clone().requires_grad_()
+    D.roi_align(fr, rois, 7, 0.5, 2).square().sum().backward()
+    O.roi_align(ft_, rois, 7, 0.5, 2).square().sum().backward()
+    torch.testing.assert_close(fr.grad, ft_.grad, atol=1e-4, rtol=1e-4)
     feats = {str(i): torch.randn(2, 4, 64 >> i, 64 >> i) for i in range(4)}
     boxes = [rb(20, 200), rb(15, 200)]
     boxes[0][0], boxes[1][0] = torch.tensor([0.0, 0.0, 255.0, 255.0]), torch.tensor([5.0, 5.0, 9.0, 9.0])
