@@ -388,3 +388,81 @@ def pipeline_case(rank, world, port, q, backend="tcp", schedule="1f1b"):
         import traceback
 
         q.put((rank, "ERR %r %s" % (e, traceback.format_exc())))
+
+
+def torch_tp_baseline_case(rank, world, port, q):
+    """The plain-torch tensor-parallel baseline model on two gloo ranks: its sharded loss equals
+    the loss of the assembled unsharded weights, replicated parameters stay equal while training,
+    the loss falls, greedy decoding gives the same tokens on both ranks."""
+    import importlib.util
+
+    import torch
+    import torch.distributed as dist
+
+    try:
+        torch.set_num_threads(1)
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "bench_torch_tp.py")
+        spec = importlib.util.spec_from_file_location("bench_torch_tp", path)
+        B = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(B)
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+        solo = [dist.new_group([r]) for r in range(world)]
+        s = dict(B.SHAPES["tiny"])
+        torch.manual_seed(1234 + rank)
+        dev, dt = torch.device("cpu"), torch.float32
+        m = B.TPLlama(s, world, rank, dt, dev, 64)
+        for p in [m.embed, m.norm] + [t for b in m.blocks for t in (b.n1, b.n2)]:
+            dist.broadcast(p.data, 0)
+        ids = torch.randint(0, s["vocab"], (3, 17), generator=torch.Generator().manual_seed(5))
+        loss = m.loss(ids[:, :-1], ids[:, 1:], dist.group.WORLD)
+
+        def gather(t):
+            out = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(out, t.detach().contiguous())
+            return out
+
+        full = B.TPLlama(s, 1, 0, dt, dev, 64)
+        with torch.no_grad():
+            full.embed.copy_(m.embed), full.norm.copy_(m.norm)
+            full.lm_head.copy_(torch.cat(gather(m.lm_head))[: full.lm_head.shape[0]])
+            for fb, b in zip(full.blocks, m.blocks):
+                d = b.d
+                parts = [t.split([b.hq * d, b.hkv * d, b.hkv * d]) for t in gather(b.qkv)]
+                fb.qkv.copy_(torch.cat([torch.cat([p[i] for p in parts]) for i in range(3)]))
+                gu = [t.chunk(2) for t in gather(b.gate_up)]
+                fb.gate_up.copy_(torch.cat([torch.cat([p[i] for p in gu]) for i in range(2)]))
+                fb.o.copy_(torch.cat(gather(b.o), 1)), fb.down.copy_(torch.cat(gather(b.down), 1))
+                fb.n1.copy_(b.n1), fb.n2.copy_(b.n2)
+        want = full.loss(ids[:, :-1], ids[:, 1:], solo[rank])
+        assert abs(float(loss) - float(want)) < 1e-4, (float(loss), float(want))
+        # gradients of a replicated parameter agree with the unsharded model
+        loss.backward(), want.backward()
+        assert torch.allclose(m.embed.grad, full.embed.grad, atol=1e-5) and torch.allclose(m.blocks[0].n1.grad, full.blocks[0].n1.grad, atol=1e-5)
+        assert torch.allclose(m.blocks[0].o.grad, full.blocks[0].o.grad.chunk(world, 1)[rank], atol=1e-5)
+        opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+        first = last = None
+        for _ in range(6):
+            opt.zero_grad()
+            l = m.loss(ids[:, :-1], ids[:, 1:], dist.group.WORLD)
+            l.backward()
+            opt.step()
+            first, last = (float(l) if first is None else first), float(l)
+        assert last < first
+        for t in gather(m.embed):
+            assert torch.equal(t, m.embed.detach())
+        a = argparse_like(batch=2, prompt=9, new=4, prefill_seqs=1, warmup=0)
+        out = B.run_decode(a, s, m, dist.group.WORLD, dev, world)
+        assert out["decode_ms_per_step"] > 0 and out["new_tokens"] == 4
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, "ERR %r %s" % (e, traceback.format_exc())))
+
+
+def argparse_like(**kw):
+    import types
+
+    return types.SimpleNamespace(**kw)

@@ -232,6 +232,12 @@ def test_pipeline_stages_as_processes_with_posted_transfers(backend, schedule):
     assert all(v == "ok" for v in out.values()), out
 
 
+def test_plain_torch_tensor_parallel_baseline_is_a_correct_model():
+    # the baseline that the tensor-parallel benchmarks are compared with must itself compute the right thing
+    out = _spawn(W.torch_tp_baseline_case, 2)
+    assert all(v == "ok" for v in out.values()), out
+
+
 def test_vocab_parallel_embedding_and_cross_entropy_gloo():
     out = _spawn(W.vocab_parallel_case, 2)
     assert all(v == "ok" for v in out.values()), out
