@@ -16,6 +16,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("constrained_json.py", []),
     ("tiny_text_to_image.py", ["--steps", "3", "--size", "32"]),
     ("coming_from_ferrotorch.py", []),
+    ("detect_objects.py", ["--model", "fcos"]),
+    ("pipeline_and_context_parallel.py", []),
 ])
 def test_example_runs(script, args):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
