@@ -120,7 +120,8 @@ def reference_unavailable() -> None:
     why = ("reference is a Rust workspace (28 crates, no Python package, no setup.py/pyproject.toml): "
            "a pip install of its source tree into baseline/_ref has nothing to build and no "
            "cargo/rustc toolchain or vendored crates exist offline")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also under torchrun
+        print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
 def build_config(args):
