@@ -190,6 +190,8 @@ def roi_align(feat: torch.Tensor, rois: torch.Tensor, output_size: int | tuple[i
     ``[K, C, ph, pw]``: every output bin is the mean of ``sampling_ratio^2`` bilinear samples.
     fp32 host tensors outside autograd go through the native library (``ftd_roi_align``), everything
     else through :func:`roi_align_torch`."""
+    if not torch.is_tensor(rois):                       # one [k, 4] tensor per image -> [K, 5] with the image index
+        rois = torch.cat([torch.cat([b.new_full((len(b), 1), i), b], 1) for i, b in enumerate(rois)])
     lib = _host_lib() if (not feat.is_cuda and feat.dtype == torch.float32 and rois.shape[0] > 0
                           and not (feat.requires_grad and torch.is_grad_enabled())) else None
     if lib is None:

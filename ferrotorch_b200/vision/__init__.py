@@ -9,9 +9,11 @@ kernels) and VGG-11/16, MobileNetV2, ViT-B/16, ConvNeXt-Tiny, DenseNet-121, FCN 
 (``models/vision_families.py``) are this package's own, with torchvision's parameter names and
 their dense convolutions and attention on this framework's kernels; Faster / Mask / Keypoint
 R-CNN, RetinaNet, FCOS, SSD300 and the reference's small YOLO (``models/detection.py``) with their
-NMS / RoI-align / anchor operators (``ops/det_ops.py``) are own code as well.  Only
-``ssdlite`` (not in the reference's registry) still comes from ``torchvision``.  One registry
-serves all of them under the reference's names.
+NMS / RoI-align / anchor operators (``ops/det_ops.py``) are own code as well, and so are the
+MNIST / CIFAR / image-folder readers (``vision/datasets.py``) and the tensor transforms
+(``vision/own_transforms.py``, ``vision/io.py``).  Only ``ssdlite`` (not in the reference's
+registry) still comes from ``torchvision``.  One registry serves all of them under the
+reference's names.
 """
 from __future__ import annotations
 
@@ -20,11 +22,12 @@ from torch import nn
 
 from ..models.resnet import create_model, list_models, register_model, resnet18, resnet34, resnet50  # noqa: F401
 
+from ..ops.det_ops import batched_nms, box_iou, nms, roi_align  # noqa: F401,E402
+
 try:
     import torchvision
-    from torchvision import datasets, io, ops, transforms  # noqa: F401
-    from torchvision.datasets import CIFAR10, CIFAR100, MNIST, ImageFolder  # noqa: F401
-    from torchvision.ops import box_iou, nms, roi_align  # noqa: F401
+    from torchvision import transforms  # noqa: F401  (torchvision's PIL / tensor transforms, as a convenience)
+    from torchvision.datasets import CIFAR10, CIFAR100, MNIST  # noqa: F401  (its downloading dataset classes)
 
     HAVE_TORCHVISION = True
 except Exception:  # noqa: BLE001
@@ -113,8 +116,7 @@ from .io import (GaussianNoise, RandomGaussianBlur, RawImage, VisionNormalize, V
 
 from . import det_ops  # noqa: F401,E402
 
-if HAVE_TORCHVISION:
-    from .compat import *  # noqa: F401,F403,E402
-    from .compat import (FPN_OUT_CHANNELS, IMAGENET_MEAN, IMAGENET_STD, SSD_ANCHORS_PER_SCALE, SSD_FM_SIZES,  # noqa: F401,E402
-                         SSD_TOTAL_ANCHORS, CifarSample, Detections, MaskDetections, MnistSample, ModelConstructor,
-                         SsdDetections)
+from .compat import *  # noqa: F401,F403,E402
+from .compat import (FPN_OUT_CHANNELS, IMAGENET_MEAN, IMAGENET_STD, SSD_ANCHORS_PER_SCALE, SSD_FM_SIZES,  # noqa: F401,E402
+                     SSD_TOTAL_ANCHORS, CifarSample, Detections, MaskDetections, MnistSample, ModelConstructor,
+                     SsdDetections)

@@ -1,8 +1,8 @@
 """The reference's ``ferrotorch-vision`` names (ferrotorch-vision/src/lib.rs re-exports: datasets,
 transforms, detection / segmentation building blocks, the model registry, feature extraction).
-Models, heads, anchors and the feature extractor point at this package's own modules
-(``models/detection.py``, ``models/vision_zoo.py``, ``ops/det_ops.py``); datasets and image
-transforms point at the torchvision objects that provide the behaviour."""
+Every name points at this package's own code: models, heads, anchors and the feature extractor
+(``models/detection.py``, ``models/vision_zoo.py``, ``ops/det_ops.py``), the dataset readers
+(``vision/datasets.py``) and the tensor transforms (``vision/own_transforms.py``, ``vision/io.py``)."""
 from __future__ import annotations
 
 import enum
@@ -11,8 +11,10 @@ from typing import Callable, Dict
 import torch
 from torch import nn
 
-from torchvision import transforms as T
-from torchvision.datasets import CIFAR10 as Cifar10, CIFAR100 as Cifar100, MNIST as Mnist  # noqa: F401
+from .datasets import Cifar10, Cifar100, DatasetFormatError, ImageFolder, Mnist  # noqa: F401
+from .own_transforms import (CenterCrop, ColorJitter, Compose, ElasticTransform, RandomApply, RandomChoice, RandomCrop,  # noqa: F401
+                             RandomHorizontalFlip, RandomResizedCrop, RandomRotation, RandomVerticalFlip, Resize,
+                             TrivialAugmentWide)
 
 from ..models import detection as _det
 from ..models import vision_zoo as _zoo
@@ -28,8 +30,6 @@ SSD_FM_SIZES = (38, 19, 10, 5, 3, 1)
 SSD_ANCHORS_PER_SCALE = (4, 6, 6, 6, 4, 4)
 SSD_TOTAL_ANCHORS = sum(f * f * a for f, a in zip(SSD_FM_SIZES, SSD_ANCHORS_PER_SCALE))     # 8732
 
-CenterCrop, ColorJitter, RandomApply, RandomChoice = T.CenterCrop, T.ColorJitter, T.RandomApply, T.RandomChoice
-RandomResizedCrop, RandomRotation, RandomVerticalFlip, Resize = T.RandomResizedCrop, T.RandomRotation, T.RandomVerticalFlip, T.Resize
 
 Ssd300 = _det.SSD300
 FasterRcnn, MaskRcnn = _det.FasterRCNN, _det.MaskRCNN
