@@ -139,9 +139,10 @@ def list_models() -> list[str]:
 
 
 def create_model(name: str, **kw) -> nn.Module:
-    """Registry lookup; names not registered here are looked up in torchvision (VGG, ViT, ConvNeXt,
-    Swin, MobileNet, DenseNet, EfficientNet, Inception and the detection / segmentation families
-    of ferrotorch-vision/src/models are served by that package)."""
+    """Registry lookup for the ResNet family and anything added with :func:`register_model`
+    (``vision.build`` serves the other families of ferrotorch-vision/src/models from this package's
+    own modules and only then falls back to this function); a name unknown here is finally tried
+    as a torchvision constructor name."""
     if name in _REGISTRY:
         return _REGISTRY[name](**kw)
     try:
