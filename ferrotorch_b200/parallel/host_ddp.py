@@ -35,14 +35,54 @@ def compute_buckets(params, bucket_size_bytes: int = DEFAULT_BUCKET_SIZE_BYTES) 
 
 
 class DDP(nn.Module):
-    def __init__(self, module: nn.Module, group: Group, bucket_size_bytes: int = DEFAULT_BUCKET_SIZE_BYTES):
+    """``overlap=True`` starts a bucket's all-reduce as soon as the backward pass has produced its
+    last gradient (a hook per parameter counts them down) on one worker thread, in the order the
+    buckets complete, which is the same on every rank because the model and the autograd order
+    are; ``sync_gradients`` then only waits for what is still in flight and handles buckets that
+    never completed (parameters without a gradient).  Results are identical to the sequential
+    form: the same buckets, the same flattening, the same reduction."""
+
+    def __init__(self, module: nn.Module, group: Group, bucket_size_bytes: int = DEFAULT_BUCKET_SIZE_BYTES,
+                 overlap: bool = False):
         super().__init__()
         self.module, self.group = module, group
         self.params = [p for p in module.parameters() if p.requires_grad]
         self.buckets = compute_buckets(self.params, bucket_size_bytes)
+        self.overlap, self._sync_enabled = overlap, True
+        if overlap:
+            from .backend import _Lane
+
+            self._lane = _Lane()
+            self._bucket_of = {i: b for b, idxs in enumerate(self.buckets) for i in idxs}
+            self._left = [len(idxs) for idxs in self.buckets]
+            self._ops: dict[int, object] = {}
+            for i, p in enumerate(self.params):
+                p.register_post_accumulate_grad_hook(lambda _p, i=i: self._grad_ready(i))
 
     def forward(self, *a, **kw):
         return self.module(*a, **kw)
+
+    def no_sync(self):
+        """Context manager: backward passes inside it only accumulate (gradient accumulation)."""
+        ddp = self
+
+        class _NoSync:
+            def __enter__(self):
+                self.prev, ddp._sync_enabled = ddp._sync_enabled, False
+
+            def __exit__(self, *exc):
+                ddp._sync_enabled = self.prev
+                return False
+
+        return _NoSync()
+
+    def _grad_ready(self, i: int) -> None:
+        if not self._sync_enabled:
+            return
+        b = self._bucket_of[i]
+        self._left[b] -= 1
+        if self._left[b] == 0:
+            self._ops[b] = self._lane.post(self._sync_bucket, self.buckets[b])
 
     def _sync_bucket(self, idxs) -> None:
         ps = [self.params[i] for i in idxs]
@@ -60,8 +100,19 @@ class DDP(nn.Module):
 
     def sync_gradients(self) -> None:
         """Average gradients across ranks, bucket by bucket (call after ``backward``)."""
-        for b in self.buckets:
-            self._sync_bucket(b)
+        if not self.overlap:
+            for b in self.buckets:
+                self._sync_bucket(b)
+            return
+        # every rank posts the buckets that did not complete in the same (index) order, after the
+        # ones that did; then everything is awaited
+        for b in range(len(self.buckets)):
+            if b not in self._ops:
+                self._ops[b] = self._lane.post(self._sync_bucket, self.buckets[b])
+        for b in sorted(self._ops):
+            self._ops[b].wait()
+        self._ops = {}
+        self._left = [len(idxs) for idxs in self.buckets]
 
     def broadcast_parameters(self, root: int = 0) -> None:
         with torch.no_grad():

@@ -122,6 +122,53 @@ def test_ddp_buckets_and_sync_simulated():
             assert torch.allclose(res[r][2][k], want, atol=1e-6)
 
 
+def test_ddp_overlapped_buckets_equal_the_sequential_form():
+    # buckets reduced on a worker thread while backward still runs: same result bit for bit, also with
+    # a parameter that gets no gradient, over several steps, and with accumulation under no_sync()
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b, self.c = torch.nn.Linear(6, 16), torch.nn.Linear(16, 16), torch.nn.Linear(16, 3)
+            self.unused = torch.nn.Linear(4, 4)
+
+        def forward(self, x):
+            return self.c(torch.tanh(self.b(torch.tanh(self.a(x)))))
+
+    import copy
+
+    torch.manual_seed(7)
+    proto = Net()                                             # ranks are threads: one initialisation, copied
+
+    def body(g, overlap):
+        m = copy.deepcopy(proto)
+        d = DDP(m, g, bucket_size_bytes=300, overlap=overlap)
+        assert len(d.buckets) > 3
+        out = []
+        gen = torch.Generator().manual_seed(100 + g.rank)
+        for step in range(3):
+            m.zero_grad(set_to_none=True)
+            with d.no_sync():
+                d(torch.randn(5, 6, generator=gen)).square().sum().backward()      # accumulated, not exchanged
+            d(torch.randn(5, 6, generator=gen)).square().sum().backward()
+            d.sync_gradients()
+            out.append([None if q.grad is None else q.grad.clone() for q in m.parameters()])
+            with torch.no_grad():
+                for q in m.parameters():
+                    if q.grad is not None:
+                        q -= 0.1 * q.grad
+        return out
+
+    seq = B.run_simulated(3, body, False)
+    ovl = B.run_simulated(3, body, True)
+    for r in range(3):
+        for s_step, o_step in zip(seq[r], ovl[r]):
+            for a, b in zip(s_step, o_step):
+                assert (a is None and b is None) or torch.equal(a, b)
+    for step in range(3):                                   # and every rank holds the same reduced gradients
+        for a, b in zip(ovl[0][step], ovl[2][step]):
+            assert torch.equal(a, b)
+
+
 # ----------------------------------------------------------------------------- loopback TCP
 @pytest.mark.parametrize("world", [2, 3, 5])
 def test_tcp_collectives(world):
