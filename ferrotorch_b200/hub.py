@@ -54,6 +54,18 @@ _MODELS = [
     _vision("swin_t", "Swin-T", 28_288_354), _vision("convnext_tiny", "ConvNeXt-T", 28_589_128),
     _vision("mobilenet_v2", "MobileNetV2", 3_504_872), _vision("mobilenet_v3_small", "MobileNetV3-Small", 2_542_856),
     _vision("densenet121", "DenseNet-121", 7_978_856), _vision("inception_v3", "Inception v3", 27_161_264),
+    _vision("mobilenet_v3_large", "MobileNetV3-Large", 5_483_032),
+    # detectors and segmenters: counts with trainable batch-norm affine parameters (checkpoints that freeze
+    # them list 53 120 fewer) and without the auxiliary segmentation head
+    _vision("fasterrcnn_resnet50_fpn", "Faster R-CNN, ResNet-50 FPN, 91 classes", 41_808_406),
+    _vision("maskrcnn_resnet50_fpn", "Mask R-CNN, ResNet-50 FPN, 91 classes", 44_454_513),
+    _vision("keypointrcnn_resnet50_fpn", "Keypoint R-CNN, ResNet-50 FPN, 17 keypoints", 59_190_378),
+    _vision("retinanet_resnet50_fpn", "RetinaNet, ResNet-50 FPN, 91 classes", 34_068_119),
+    _vision("fcos_resnet50_fpn", "FCOS, ResNet-50 FPN, 91 classes", 32_322_720),
+    _vision("ssd300_vgg16", "SSD300, VGG-16, 91 classes", 35_641_826),
+    _vision("fcn_resnet50", "FCN, dilated ResNet-50, 21 classes", 32_957_013),
+    _vision("deeplabv3_resnet50", "DeepLabV3, dilated ResNet-50, 21 classes", 39_638_869),
+    _vision("lraspp_mobilenet_v3_large", "LR-ASPP, MobileNetV3-Large, 21 classes", 3_221_538),
     ModelInfo("llama3-8b", "Llama-3-8B decoder", "ferrotorch_b200.models.llama:LlamaConfig.llama3_8b", 8_030_261_248),
     ModelInfo("llama3.3-70b-instruct", "Llama-3.3-70B-Instruct decoder",
               "ferrotorch_b200.models.llama:LlamaConfig.llama3_3_70b_instruct", 70_553_706_496),

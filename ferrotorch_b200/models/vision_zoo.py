@@ -380,5 +380,5 @@ def deeplabv3_resnet50(num_classes: int = 21, **kw):
 
 
 OWN_MODELS = {"vgg11": vgg11, "vgg16": vgg16, "mobilenet_v2": mobilenet_v2, "vit_b_16": vit_b_16,
-              "convnext_tiny": convnext_tiny, "densenet121": densenet121, "fcn": fcn_resnet50,
-              "deeplabv3": deeplabv3_resnet50}
+              "convnext_tiny": convnext_tiny, "densenet121": densenet121, "fcn": fcn_resnet50, "fcn_resnet50": fcn_resnet50,
+              "deeplabv3": deeplabv3_resnet50, "deeplabv3_resnet50": deeplabv3_resnet50}

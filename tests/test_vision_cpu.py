@@ -335,3 +335,19 @@ def test_registry_prefers_own_models():
     from ferrotorch_b200.models import detection as Dm
 
     assert isinstance(V.build("retinanet", num_classes=3), Dm.RetinaNet) and isinstance(V.build("yolo", num_classes=3), Dm.Yolo)
+
+
+def test_every_vision_entry_of_the_hub_builds_with_its_listed_size():
+    # the registry's parameter counts are the published sizes of these architectures
+    from ferrotorch_b200 import hub
+    from ferrotorch_b200 import vision as V
+
+    seen = 0
+    for info in hub.list_models():
+        if "vision:build" not in info.builder:
+            continue
+        net = V.build(info.name)
+        assert sum(p.numel() for p in net.parameters()) == info.num_parameters, info.name
+        assert type(net).__module__.startswith("ferrotorch_b200."), "%s is not this package's own module" % info.name
+        seen += 1
+    assert seen >= 23
