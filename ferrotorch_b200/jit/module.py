@@ -98,12 +98,10 @@ def lower_fx(gm: torch.fx.GraphModule, example_inputs) -> IrGraph:
     env: dict = {}
     mods = dict(gm.named_modules())
 
-    def val(a):
-        return env[a] if isinstance(a, torch.fx.Node) else a
-
     n_in = 0
     for node in gm.graph.nodes:
-        args = [val(a) for a in node.args]
+        # map_arg also reaches nodes nested in lists / tuples (torch.cat([a, b]), x.view((n, m)) ...)
+        args = list(torch.fx.node.map_arg(tuple(node.args), lambda a: env[a]))
         if node.op == "placeholder":
             env[node] = g.add("input", index=n_in)
             n_in += 1
@@ -144,7 +142,7 @@ def lower_fx(gm: torch.fx.GraphModule, example_inputs) -> IrGraph:
                 kind = "transpose_last"
             tens = [a for a in torch.utils._pytree.tree_flatten((args, dict(node.kwargs)))[0] if hasattr(a, "id")]
             env[node] = g.add("call", [t.id for t in tens], fx_op=node.op, target=tgt,
-                              args=tuple(args), kwargs={k: val(v) for k, v in node.kwargs.items()}, kind=kind)
+                              args=tuple(args), kwargs=torch.fx.node.map_arg(dict(node.kwargs), lambda a: env[a]), kind=kind)
     # shape / dtype propagation with one eager run
     values = _interpret(g, example_inputs, record=True)
     del values

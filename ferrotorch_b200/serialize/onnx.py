@@ -249,7 +249,11 @@ def _emit_call(b: _Builder, n, names: dict, out: str) -> None:
     def plain(a):
         return a if not hasattr(a, "id") else None
 
-    if kind == "linear":
+    if kind == "linear" and n.shape is not None and len(n.shape) == 2:
+        # a matrix times a weight: one Gemm with the weight as stored (transB), as the reference emits
+        w = [ins[0], b.const(tgt.weight.detach(), "weight")] + ([b.const(tgt.bias.detach(), "bias")] if tgt.bias is not None else [])
+        b.node("Gemm", w, out, transB=1)
+    elif kind == "linear":
         w = b.const(tgt.weight.detach().t().contiguous(), "weight")
         y = b.node("MatMul", [ins[0], w], None if tgt.bias is not None else out)
         if tgt.bias is not None:
@@ -268,8 +272,94 @@ def _emit_call(b: _Builder, n, names: dict, out: str) -> None:
         b.node("Reshape", [ins[0], b.const(torch.tensor(list(n.shape), dtype=torch.int64), "shape")], out)
     elif isinstance(tgt, nn.Dropout) or tgt in (nn.functional.dropout, "contiguous", "detach") or isinstance(tgt, nn.Identity):
         b.node("Identity", ins[:1], out)
+    elif _emit_structural(b, n, tgt, args, kwargs, ins, out):
+        pass
     else:
         raise OnnxExportError("node %d: call to %r has no ONNX mapping" % (n.id, getattr(tgt, "__name__", tgt)))
+
+
+def _axes(v, rank: int) -> list[int]:
+    v = [v] if isinstance(v, int) else list(v)
+    return [a % rank for a in v]
+
+
+def _emit_structural(b: _Builder, n, tgt, args, kwargs, ins, out) -> bool:
+    """Reductions, log-softmax, squeeze / unsqueeze, concatenation, general transposes and the
+    layers of a convolutional network (the operator list of the reference's exporter,
+    ferrotorch-serialize/src/onnx_export.rs:528-716, plus Conv / pooling / batch norm).  Returns
+    False when ``tgt`` is none of them."""
+    plain = [a for a in args if not hasattr(a, "id")]
+    first = args[0] if args else None
+    in_rank = len(first.shape) if hasattr(first, "shape") and first.shape is not None else None
+    i64 = lambda v: b.const(torch.tensor(list(v), dtype=torch.int64), "axes")  # noqa: E731
+    red = {torch.sum: "ReduceSum", "sum": "ReduceSum", torch.mean: "ReduceMean", "mean": "ReduceMean", torch.prod: "ReduceProd",
+           "prod": "ReduceProd"}
+    if tgt in red:
+        dim = kwargs.get("dim", plain[0] if plain else None)
+        keep = int(bool(kwargs.get("keepdim", plain[1] if len(plain) > 1 else False)))
+        op = red[tgt]
+        if dim is None:
+            b.node(op, ins[:1], out, keepdims=0)
+        elif op == "ReduceSum":                                   # axes are an input since opset 13
+            b.node(op, [ins[0], i64(_axes(dim, in_rank))], out, keepdims=keep)
+        else:                                                     # ... and an attribute until opset 18
+            b.node(op, ins[:1], out, axes=_axes(dim, in_rank), keepdims=keep)
+        return True
+    if tgt in (torch.log_softmax, nn.functional.log_softmax, "log_softmax") or isinstance(tgt, nn.LogSoftmax):
+        dim = tgt.dim if isinstance(tgt, nn.LogSoftmax) else kwargs.get("dim", plain[0] if plain else -1)
+        b.node("LogSoftmax", ins[:1], out, axis=int(dim))
+        return True
+    if tgt in (torch.squeeze, "squeeze", torch.unsqueeze, "unsqueeze"):
+        dim = kwargs.get("dim", plain[0] if plain else None)
+        if tgt in (torch.squeeze, "squeeze"):
+            b.node("Squeeze", ins[:1] if dim is None else [ins[0], i64(_axes(dim, in_rank))], out)
+        else:
+            b.node("Unsqueeze", [ins[0], i64([dim % (in_rank + 1)])], out)
+        return True
+    if tgt in (torch.cat, torch.concat):
+        dim = kwargs.get("dim", args[1] if len(args) > 1 else 0)
+        b.node("Concat", ins, out, axis=int(dim) % len(n.shape))
+        return True
+    if tgt in ("permute", torch.permute):
+        perm = plain[0] if len(plain) == 1 and isinstance(plain[0], (list, tuple)) else plain
+        b.node("Transpose", ins[:1], out, perm=_axes(perm, in_rank))
+        return True
+    if tgt in ("transpose", torch.transpose, "t"):
+        perm = list(range(in_rank))
+        a0, a1 = (0, 1) if tgt == "t" else (plain[0] % in_rank, plain[1] % in_rank)
+        perm[a0], perm[a1] = perm[a1], perm[a0]
+        b.node("Transpose", ins[:1], out, perm=perm)
+        return True
+    if isinstance(tgt, nn.Conv2d):
+        if isinstance(tgt.padding, str) or tgt.padding_mode != "zeros":
+            raise OnnxExportError("Conv2d with padding %r / mode %r cannot be exported" % (tgt.padding, tgt.padding_mode))
+        w = [ins[0], b.const(tgt.weight.detach(), "weight")] + ([b.const(tgt.bias.detach(), "bias")] if tgt.bias is not None else [])
+        b.node("Conv", w, out, kernel_shape=list(tgt.kernel_size), strides=list(tgt.stride), pads=list(tgt.padding) * 2,
+               dilations=list(tgt.dilation), group=int(tgt.groups))
+        return True
+    if isinstance(tgt, nn.BatchNorm2d):
+        if tgt.training or tgt.running_mean is None:
+            raise OnnxExportError("BatchNorm2d is exported in eval mode with running statistics")
+        ones, zeros = torch.ones_like(tgt.running_mean), torch.zeros_like(tgt.running_mean)
+        b.node("BatchNormalization", [ins[0], b.const((tgt.weight if tgt.weight is not None else ones).detach(), "scale"),
+                                      b.const((tgt.bias if tgt.bias is not None else zeros).detach(), "bias"),
+                                      b.const(tgt.running_mean.detach(), "mean"), b.const(tgt.running_var.detach(), "var")],
+               out, epsilon=float(tgt.eps))
+        return True
+    if isinstance(tgt, (nn.MaxPool2d, nn.AvgPool2d)):
+        pair = lambda v: [v, v] if isinstance(v, int) else list(v)  # noqa: E731
+        k, st, pd = pair(tgt.kernel_size), pair(tgt.stride or tgt.kernel_size), pair(tgt.padding)
+        extra = {"ceil_mode": int(tgt.ceil_mode)}
+        if isinstance(tgt, nn.AvgPool2d):
+            extra["count_include_pad"] = int(tgt.count_include_pad)
+        elif pair(tgt.dilation) != [1, 1]:
+            extra["dilations"] = pair(tgt.dilation)
+        b.node("MaxPool" if isinstance(tgt, nn.MaxPool2d) else "AveragePool", ins[:1], out, kernel_shape=k, strides=st, pads=pd * 2, **extra)
+        return True
+    if isinstance(tgt, nn.AdaptiveAvgPool2d) and tgt.output_size in (1, (1, 1)):
+        b.node("GlobalAveragePool", ins[:1], out)
+        return True
+    return False
 
 
 def ir_graph_to_onnx(graph, config: OnnxExportConfig | None = None) -> bytes:
@@ -475,6 +565,10 @@ _EVAL = {
 }
 
 
+def _ints(v) -> list[int]:
+    return [int(v)] if isinstance(v, int) else [int(x) for x in v]
+
+
 def run_onnx(model: OnnxModel, *inputs: torch.Tensor) -> list[torch.Tensor]:
     """Evaluate the model with torch operators, following the ONNX operator definitions: a
     reference run for checking an export where no ONNX runtime is installed."""
@@ -495,6 +589,48 @@ def run_onnx(model: OnnxModel, *inputs: torch.Tensor) -> list[torch.Tensor]:
             y = xs[0].permute(*n.attrs["perm"])
         elif n.op_type == "Reshape":
             y = xs[0].reshape([int(v) for v in xs[1].tolist()])
+        elif n.op_type in ("ReduceSum", "ReduceMean", "ReduceProd"):
+            axes = [int(v) for v in xs[1].tolist()] if len(xs) > 1 else n.attrs.get("axes")
+            axes = ([axes] if isinstance(axes, int) else axes) or list(range(xs[0].dim()))
+            keep = bool(n.attrs.get("keepdims", 1))
+            if n.op_type == "ReduceProd":
+                y = xs[0]
+                for a in sorted(axes, reverse=True):
+                    y = y.prod(a, keepdim=keep)
+            else:
+                y = (torch.sum if n.op_type == "ReduceSum" else torch.mean)(xs[0], dim=axes, keepdim=keep)
+        elif n.op_type == "LogSoftmax":
+            y = torch.log_softmax(xs[0], dim=n.attrs.get("axis", -1))
+        elif n.op_type == "Squeeze":
+            y = xs[0].squeeze() if len(xs) == 1 else xs[0].squeeze(tuple(int(v) for v in xs[1].tolist()))
+        elif n.op_type == "Unsqueeze":
+            y = xs[0]
+            for a in sorted(int(v) for v in xs[1].tolist()):
+                y = y.unsqueeze(a)
+        elif n.op_type == "Concat":
+            y = torch.cat(xs, dim=n.attrs["axis"])
+        elif n.op_type == "Gemm":
+            a_, b_ = (xs[0].t() if n.attrs.get("transA") else xs[0]), (xs[1].t() if n.attrs.get("transB") else xs[1])
+            y = float(n.attrs.get("alpha", 1.0)) * (a_ @ b_)
+            if len(xs) > 2:
+                y = y + float(n.attrs.get("beta", 1.0)) * xs[2]
+        elif n.op_type == "Conv":
+            pads = _ints(n.attrs.get("pads", [0, 0, 0, 0]))
+            if pads[:2] != pads[2:]:
+                raise OnnxExportError("reference evaluator: asymmetric Conv padding")
+            y = nn.functional.conv2d(xs[0], xs[1], xs[2] if len(xs) > 2 else None, _ints(n.attrs.get("strides", [1, 1])), pads[:2],
+                                     _ints(n.attrs.get("dilations", [1, 1])), int(n.attrs.get("group", 1)))
+        elif n.op_type == "BatchNormalization":
+            y = nn.functional.batch_norm(xs[0], xs[3], xs[4], xs[1], xs[2], False, 0.0, float(n.attrs.get("epsilon", 1e-5)))
+        elif n.op_type in ("MaxPool", "AveragePool"):
+            k, st, pads = _ints(n.attrs["kernel_shape"]), _ints(n.attrs.get("strides", [1, 1])), _ints(n.attrs.get("pads", [0, 0, 0, 0]))
+            ceil = bool(n.attrs.get("ceil_mode", 0))
+            if n.op_type == "MaxPool":
+                y = nn.functional.max_pool2d(xs[0], k, st, pads[:2], _ints(n.attrs.get("dilations", [1, 1])), ceil)
+            else:
+                y = nn.functional.avg_pool2d(xs[0], k, st, pads[:2], ceil, bool(n.attrs.get("count_include_pad", 0)))
+        elif n.op_type == "GlobalAveragePool":
+            y = xs[0].mean((2, 3), keepdim=True)
         else:
             raise OnnxExportError("reference evaluator: operator %s is not implemented" % n.op_type)
         env[n.outputs[0]] = y

@@ -338,3 +338,60 @@ def test_shared_block_decoder_equals_the_host_reader_for_every_quantised_type():
         G.dequantize_pairwise_host(blk, G.GGML_F16, 32)
     with pytest.raises(ValueError):
         G.dequantize_on_device(blk, G.GGML_Q4_0, (32,))               # a host tensor is refused before any launch
+
+
+def test_onnx_export_of_reductions_shape_ops_and_convolutional_layers(tmp_path):
+    """The rest of the reference exporter's operator list (reductions, LogSoftmax, Squeeze /
+    Unsqueeze, Concat, general Transpose, Gemm) and the layers of a small CNN (Conv, batch norm in
+    eval mode, max / average / global pooling), checked with the reference evaluator."""
+    import ferrotorch_b200.serialize as S
+    from ferrotorch_b200.serialize import onnx as O
+    from torch import nn
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv, self.bn = nn.Conv2d(3, 8, 3, 2, 1), nn.BatchNorm2d(8)
+            self.dw = nn.Conv2d(8, 8, 3, padding=2, dilation=2, groups=8, bias=False)
+            self.pool, self.avg, self.gap = nn.MaxPool2d(3, 2, 1), nn.AvgPool2d(2), nn.AdaptiveAvgPool2d(1)
+            self.fc, self.ls = nn.Linear(8, 5), nn.LogSoftmax(dim=-1)
+
+        def forward(self, x):
+            h = self.dw(torch.relu(self.bn(self.conv(x))))
+            h = self.gap(self.avg(self.pool(h))).flatten(1)
+            z = self.fc(h)
+            total, mean = z.sum(1, keepdim=True), z.mean(dim=-1)
+            both = torch.cat([z, total], 1)
+            moved = both.unsqueeze(0).permute(1, 0, 2).squeeze(1).transpose(0, 1)
+            return self.ls(z), moved, mean, torch.prod(z, 1), z.sum()
+
+    torch.manual_seed(0)
+    net = Net().eval()
+    with torch.no_grad():
+        net.bn.running_mean.normal_()
+        net.bn.running_var.uniform_(0.5, 1.5)
+    x = torch.randn(2, 3, 20, 20)
+    path = str(tmp_path / "cnn.onnx")
+    S.export_onnx(net, (x,), path)
+    model = S.load_onnx(path)
+    ops = {n.op_type for n in model.nodes}
+    assert {"Conv", "BatchNormalization", "MaxPool", "AveragePool", "GlobalAveragePool", "Gemm", "LogSoftmax", "ReduceSum", "ReduceMean",
+            "ReduceProd", "Concat", "Unsqueeze", "Squeeze", "Transpose"} <= ops
+    conv = [n for n in model.nodes if n.op_type == "Conv"]
+    assert conv[0].attrs["strides"] == [2, 2] and conv[0].attrs["pads"] == [1, 1, 1, 1] and conv[1].attrs["group"] == 8 \
+        and conv[1].attrs["dilations"] == [2, 2]
+    with torch.no_grad():
+        want = net(x)
+    for got, w in zip(S.run_onnx(model, x), want):
+        assert got.shape == w.shape and torch.allclose(got, w, atol=1e-5)
+    # export_onnx switches a training-mode model to eval for the trace and back afterwards; a graph traced in
+    # training mode by hand is refused (batch norm would use batch statistics)
+    net.train()
+    S.export_onnx(net, (x,), str(tmp_path / "train.onnx"))
+    assert net.training
+    for got, w in zip(S.run_onnx(S.load_onnx(str(tmp_path / "train.onnx")), x), want):
+        assert torch.allclose(got, w, atol=1e-5)
+    from ferrotorch_b200.jit.module import trace
+
+    with pytest.raises(O.OnnxExportError, match="eval mode"):
+        S.export_ir_graph_to_onnx(trace(net, (x,)), str(tmp_path / "bad.onnx"))
