@@ -21,7 +21,8 @@ def worker(rank, world, port, q, steps):
     group = TcpGroup(rank, world, "127.0.0.1", port, timeout=30.0)
     torch.manual_seed(0)
     cfg = LlamaConfig.tiny()
-    model = DDP(LlamaForCausalLM(cfg), group)
+    # 4 MB buckets leave on a worker thread while backward is still running
+    model = DDP(LlamaForCausalLM(cfg), group, bucket_size_bytes=4 << 20, overlap=True)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-3, betas=(0.9, 0.95), weight_decay=0.1)
     g = torch.Generator().manual_seed(100 + rank)
     losses = []
