@@ -149,18 +149,47 @@ def bench_grammar(quick):
 def bench_state_dict(quick):
     from ferrotorch_b200.serialize import state as S
 
-    n = 8 if quick else 32
+    n = 8 if quick else 256
     sd = {"layer%d.weight" % i: torch.randn(1024, 1024) for i in range(n)}
     base = "/dev/shm" if os.path.isdir("/dev/shm") else None       # memory-backed: measures the code, not the disk
     path = os.path.join(tempfile.mkdtemp(dir=base), "m.ftsd")
+    S.save_state_dict(sd, path)                                  # first write allocates the file's pages
     t0 = time.perf_counter()
     S.save_state_dict(sd, path)
     w = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    S.load_state_dict(path)
-    r = time.perf_counter() - t0
     mb = n * 4
-    emit("native_state_dict", megabytes=mb, write_mb_per_s=mb / w, read_mb_per_s=mb / r, filesystem=base or "tmp")
+    rates = {}
+    for threads in (1, 4, 8):
+        S.load_state_dict(path, threads=threads)
+        t0 = time.perf_counter()
+        S.load_state_dict(path, threads=threads)
+        rates["read_mb_per_s_%d_threads" % threads] = mb / (time.perf_counter() - t0)
+    t0 = time.perf_counter()
+    lazy = S.load_state_dict(path, mmap=True)
+    rates["mmap_open_ms"] = (time.perf_counter() - t0) * 1e3
+    t0 = time.perf_counter()
+    sum(float(v.sum()) for v in lazy.values())
+    rates["mmap_first_touch_mb_per_s"] = mb / (time.perf_counter() - t0)
+    del lazy
+    t0 = time.perf_counter()
+    buf = bytearray(os.path.getsize(path))
+    with open(path, "rb") as f:
+        f.readinto(buf)
+    S.loads_state_dict(buf)
+    rates["read_mb_per_s_single_readinto"] = mb / (time.perf_counter() - t0)
+    emit("native_state_dict", megabytes=mb, write_mb_per_s=mb / w, filesystem=base or "tmp", **rates)
+    try:
+        from safetensors.torch import load_file, save_file
+
+        st = path + ".safetensors"
+        save_file(sd, st)
+        load_file(st)
+        t0 = time.perf_counter()
+        load_file(st)
+        emit("safetensors_library_load", megabytes=mb, read_mb_per_s=mb / (time.perf_counter() - t0))
+        os.remove(st)
+    except Exception:  # noqa: BLE001
+        pass
     os.remove(path)
 
 

@@ -242,15 +242,27 @@ def dumps_state_dict(state: dict[str, torch.Tensor]) -> bytes:
 def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
     """Reads the layout above, files the reference wrote, and the first layout of this package
     (fields ``offset`` / ``nbytes``, upper-case dtype names)."""
-    if not isinstance(buf, bytearray):
-        buf = bytearray(buf)                    # one copy; the tensors below are views into it
-    head_end = 0 if buf.startswith(b"---\n") else buf.find(b"\n---\n") + 1
-    if head_end == 0 and not buf.startswith(b"---\n"):
+    base = None
+    if isinstance(buf, torch.Tensor):           # a uint8 tensor (read_file_parallel): views come straight from it
+        base = buf
+        raw = memoryview(buf.numpy())
+        window = 1 << 16                                    # the header is at the front: copy only as much as holds it
+        while True:
+            probe = bytes(raw[:min(len(raw), window)])
+            if probe.startswith(b"---\n") or b"\n---\n" in probe or window >= len(raw):
+                break
+            window <<= 2
+    else:
+        if not isinstance(buf, bytearray):
+            buf = bytearray(buf)                # one copy; the tensors below are views into it
+        raw, probe = memoryview(buf), buf
+    head_end = 0 if probe.startswith(b"---\n") else probe.find(b"\n---\n") + 1
+    if head_end == 0 and not probe.startswith(b"---\n"):
         raise ValueError("state dict: no separator line")
     body_start = head_end + 4
-    body = memoryview(buf)[body_start:]
+    body = raw[body_start:]
     out = {}
-    for line in buf[:head_end].decode().splitlines():
+    for line in bytes(probe[:head_end]).decode().splitlines():
         if not line.strip():
             continue
         e = json.loads(line)
@@ -269,7 +281,8 @@ def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
         if numel * torch.empty(0, dtype=dt).element_size() != n:
             raise ValueError("state dict: shape %s of %r does not match %d bytes" % (e["shape"], e["name"], n))
         if n:
-            t8 = torch.frombuffer(buf, dtype=torch.uint8, count=n, offset=body_start + off)
+            t8 = (base[body_start + off:body_start + off + n] if base is not None
+                  else torch.frombuffer(buf, dtype=torch.uint8, count=n, offset=body_start + off))
             item = torch.empty(0, dtype=dt).element_size()
             t = (t8 if t8.data_ptr() % item == 0 else t8.clone()).view(dt)     # views need aligned storage
         else:
@@ -278,29 +291,77 @@ def loads_state_dict(buf: bytes, device="cpu") -> dict[str, torch.Tensor]:
     return out
 
 
-def save_state_dict(state: dict[str, torch.Tensor], path: str) -> None:
+def save_state_dict(state: dict[str, torch.Tensor], path: str, align: int = 64) -> None:
     """Streams: the header first, then every tensor's bytes straight from its storage (no
-    concatenated copy of the whole checkpoint in memory)."""
+    concatenated copy of the whole checkpoint in memory).  With ``align`` the last header line is
+    padded with spaces (insignificant JSON white space, also for the reference's reader) so that
+    the tensor bytes start on an ``align``-byte file offset, and every tensor is placed on a
+    multiple of 8 bytes: a loader can then hand out views of one buffer or of a memory map without
+    copying.  ``align=0`` writes the dense layout of :func:`dumps_state_dict`."""
     keys = sorted(state)
     header, off, views = [], 0, []
     for k in keys:
         v = state[k].detach().contiguous().cpu()
         nbytes = v.numel() * v.element_size()
+        if align and off % 8:
+            views.append(torch.zeros(8 - off % 8, dtype=torch.uint8))           # gap: no header entry points at it
+            off += 8 - off % 8
         header.append('{"name":%s,"shape":[%s],"dtype":"%s","byte_offset":%d,"byte_length":%d}\n'
                       % (json.dumps(k), ",".join(str(int(d)) for d in v.shape), _TAG[v.dtype], off, nbytes))
         views.append(v)
         off += nbytes
+    head = "".join(header).encode()
+    if align and header:
+        pad = -(len(head) + 5) % align                                         # + len("\n---\n")
+        head = head[:-1] + b" " * pad + b"\n"
+    # one streaming writer: positional writes from several threads were measured slower than this
+    # on a memory-backed file system (2.4 GB/s streamed against 0.4-1.0 GB/s with eight writers)
     with open(path, "wb") as f:
-        f.write("".join(header).encode() + b"\n---\n")
+        f.write(head + b"\n---\n")
         for v in views:
             if v.numel():
                 f.write(memoryview(v.reshape(-1).view(torch.uint8).numpy()))
 
 
-def load_state_dict(path: str, device="cpu") -> dict[str, torch.Tensor]:
-    buf = bytearray(os.path.getsize(path))
-    with open(path, "rb") as f:
-        f.readinto(buf)
+def read_file_parallel(path: str, offset: int = 0, nbytes: int | None = None, threads: int = 8, pin: bool = False) -> torch.Tensor:
+    """``nbytes`` of ``path`` from ``offset`` as one uint8 tensor, filled by ``threads`` positional
+    reads of the native host library (``csrc/host/io_parallel.cpp``); ``pin`` allocates page-locked
+    memory so that a following copy to a GPU is asynchronous.  Falls back to one ``readinto``
+    when the library is not available."""
+    import ctypes
+
+    from .. import _native
+
+    size = os.path.getsize(path)
+    nbytes = size - offset if nbytes is None else nbytes
+    if offset < 0 or nbytes < 0 or offset + nbytes > size:
+        raise ValueError("read_file_parallel: bytes [%d, %d) of a %d-byte file" % (offset, offset + nbytes, size))
+    out = torch.empty(nbytes, dtype=torch.uint8, pin_memory=pin and torch.cuda.is_available())
+    if nbytes == 0:
+        return out
+    lib = _native.host(required=False)
+    if lib is None or not hasattr(lib, "ftio_read"):
+        with open(path, "rb") as f:
+            f.seek(offset)
+            f.readinto(memoryview(out.numpy()))
+        return out
+    lib.ftio_read.restype = ctypes.c_int
+    lib.ftio_read.argtypes = [ctypes.c_char_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int]
+    rc = lib.ftio_read(os.fsencode(path), offset, nbytes, out.data_ptr(), int(threads))
+    if rc != 0:
+        raise OSError(-rc if rc < -1 else 5, "reading %s failed (%d)" % (path, rc))
+    return out
+
+
+def load_state_dict(path: str, device="cpu", threads: int = 8, mmap: bool = False) -> dict[str, torch.Tensor]:
+    """The file is read once, in parallel, into one buffer (page-locked when ``device`` is a GPU);
+    the tensors are views into it (``device='cpu'``) or asynchronous copies from it.  ``mmap=True``
+    maps the file instead (private, copy-on-write): nothing is read until a tensor is touched, and
+    the tensors stay valid only while the file does."""
+    if mmap and os.path.getsize(path) > 0:
+        buf = torch.from_file(path, shared=False, size=os.path.getsize(path), dtype=torch.uint8)
+    else:
+        buf = read_file_parallel(path, threads=threads, pin=torch.device(device).type == "cuda")
     return loads_state_dict(buf, device)
 
 

@@ -395,3 +395,44 @@ def test_onnx_export_of_reductions_shape_ops_and_convolutional_layers(tmp_path):
 
     with pytest.raises(O.OnnxExportError, match="eval mode"):
         S.export_ir_graph_to_onnx(trace(net, (x,)), str(tmp_path / "bad.onnx"))
+
+
+def test_state_dict_files_are_aligned_and_load_as_views(tmp_path):
+    """Files written by ``save_state_dict`` start their tensor bytes on a 64-byte offset and place
+    every tensor on a multiple of 8, so the parallel reader and the memory map both hand out views;
+    the dense layout (``align=0``) stays byte-identical to ``dumps_state_dict``."""
+    from ferrotorch_b200.serialize import state as S
+
+    torch.manual_seed(0)
+    sd = {"w": torch.randn(33, 7), "odd": torch.arange(5, dtype=torch.uint8), "h": torch.randn(3).bfloat16(), "i": torch.arange(7),
+          "empty": torch.zeros(0), "b": torch.tensor([True, False, True])}
+    path = str(tmp_path / "m.ftsd")
+    S.save_state_dict(sd, path)
+    raw = open(path, "rb").read()
+    body = raw.find(b"\n---\n") + 5
+    assert body % 64 == 0
+    import json
+
+    for line in raw[:body - 5].decode().splitlines():
+        if line.strip():
+            assert json.loads(line)["byte_offset"] % 8 == 0
+    for kw in ({}, {"threads": 1}, {"mmap": True}):
+        back = S.load_state_dict(path, **kw)
+        assert set(back) == set(sd)
+        for k, v in sd.items():
+            assert back[k].dtype == v.dtype and back[k].shape == v.shape and torch.equal(back[k], v), (kw, k)
+    eager = S.load_state_dict(path)
+    assert eager["w"].untyped_storage().data_ptr() == eager["i"].untyped_storage().data_ptr(), "views of one buffer, not copies"
+    S.save_state_dict(sd, path, align=0)
+    assert open(path, "rb").read() == S.dumps_state_dict(sd)
+    assert all(torch.equal(S.load_state_dict(path)[k], v) for k, v in sd.items())
+    # the parallel reader: any region, and typed failures
+    blob = bytes(range(256)) * 1000
+    p2 = tmp_path / "blob.bin"
+    p2.write_bytes(blob)
+    for off, n in ((0, len(blob)), (3, 1000), (255999, 1), (100, 0)):
+        assert bytes(S.read_file_parallel(str(p2), off, n, threads=3).numpy()) == blob[off:off + n]
+    with pytest.raises(ValueError):
+        S.read_file_parallel(str(p2), 10, len(blob))
+    with pytest.raises(OSError):
+        S.read_file_parallel(str(tmp_path / "missing.bin"))
