@@ -4,7 +4,7 @@ from .gguf import (GgmlType, GgufFile, GgufMetadata, GgufTensorInfo, GgufValue, 
                    parse_gguf_bytes, quantize_q4_0, tensor_infos, write_gguf)
 from .state import PickleValue, TrainingCheckpoint  # noqa: F401
 from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_checkpoint,  # noqa: F401
-                    load_pytorch_state_dict, load_safetensors, load_safetensors_sharded, load_state_dict,
+                    load_pytorch_state_dict, load_safetensors, load_safetensors_parallel, read_file_parallel, read_safetensors_header, load_safetensors_sharded, load_state_dict,
                     ShardProgress, load_safetensors_auto, load_safetensors_mmap, load_safetensors_sharded_filtered,
                     load_safetensors_sharded_mmap, load_safetensors_sharded_with_progress, validate_checkpoint,
                     load_pytorch_state_dict_mmap, parse_pickle, pickle_imports,

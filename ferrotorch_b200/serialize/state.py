@@ -53,6 +53,68 @@ def load_safetensors(path: str, device="cpu", dtype: torch.dtype | None = None,
     return out
 
 
+_ST_DTYPES = {"F64": torch.float64, "F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "I64": torch.int64,
+              "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8, "BOOL": torch.bool}
+
+
+def read_safetensors_header(path: str) -> tuple[dict, int]:
+    """``(header, data_offset)`` of a SafeTensors file: 8 bytes little-endian header length, the
+    JSON header (``name -> {dtype, shape, data_offsets}`` plus ``__metadata__``), then the data."""
+    size = os.path.getsize(path)
+    with open(path, "rb") as f:
+        raw = f.read(8)
+        if len(raw) != 8:
+            raise ValueError("safetensors: %s is shorter than its length field" % path)
+        n = int.from_bytes(raw, "little")
+        if n <= 0 or 8 + n > size:
+            raise ValueError("safetensors: header length %d in a %d-byte file" % (n, size))
+        header = json.loads(f.read(n))
+    return header, 8 + n
+
+
+def load_safetensors_parallel(path: str, device="cpu", dtype: torch.dtype | None = None,
+                              key_filter: Callable[[str], bool] | None = None, threads: int = 8) -> dict[str, torch.Tensor]:
+    """The eager counterpart of :func:`load_safetensors` for checkpoints that go to a GPU anyway:
+    the span of the file that holds the selected tensors is read by ``threads`` positional reads
+    into one (page-locked) buffer, the tensors are views into it, and their copies to ``device`` are
+    asynchronous.  Offsets, sizes and dtypes of the header are validated before anything is read."""
+    header, base = read_safetensors_header(path)
+    size = os.path.getsize(path)
+    want = {}
+    for k, e in header.items():
+        if k == "__metadata__" or (key_filter is not None and not key_filter(k)):
+            continue
+        dt = _ST_DTYPES.get(e.get("dtype"))
+        if dt is None:
+            raise ValueError("safetensors: dtype %r of %s is not supported" % (e.get("dtype"), k))
+        lo, hi = (int(v) for v in e["data_offsets"])
+        numel = 1
+        for d in e["shape"]:
+            numel *= int(d)
+        if lo < 0 or hi < lo or base + hi > size or numel * torch.empty(0, dtype=dt).element_size() != hi - lo:
+            raise ValueError("safetensors: tensor %s: offsets [%d, %d) do not fit shape %s / file size" % (k, lo, hi, e["shape"]))
+        want[k] = (dt, [int(d) for d in e["shape"]], lo, hi)
+    if not want:
+        return {}
+    first, last = min(v[2] for v in want.values()), max(v[3] for v in want.values())
+    dev = torch.device(device)
+    buf = read_file_parallel(path, base + first, last - first, threads=threads, pin=dev.type == "cuda")
+    out = {}
+    for k, (dt, shape, lo, hi) in want.items():
+        if hi == lo:
+            t = torch.empty(shape, dtype=dt)
+        else:
+            t8 = buf[lo - first:hi - first]
+            item = torch.empty(0, dtype=dt).element_size()
+            t = (t8 if t8.data_ptr() % item == 0 else t8.clone()).view(dt).reshape(shape)
+        if dtype is not None and t.is_floating_point():
+            t = t.to(dtype)
+        out[k] = t.to(dev, non_blocking=True) if dev.type != "cpu" else t
+    if dev.type == "cuda":
+        torch.cuda.current_stream(dev).synchronize()      # the page-locked buffer is released after this call
+    return out
+
+
 def save_safetensors_sharded(state: dict[str, torch.Tensor], directory: str, max_shard_bytes: int = 5 << 30,
                              prefix: str = "model") -> str:
     """Write ``prefix-0000i-of-0000n.safetensors`` + ``prefix.safetensors.index.json``."""

@@ -436,3 +436,40 @@ def test_state_dict_files_are_aligned_and_load_as_views(tmp_path):
         S.read_file_parallel(str(p2), 10, len(blob))
     with pytest.raises(OSError):
         S.read_file_parallel(str(tmp_path / "missing.bin"))
+
+
+def test_safetensors_parallel_loader_equals_the_library_loader(tmp_path):
+    from ferrotorch_b200.serialize import state as S
+
+    torch.manual_seed(1)
+    sd = {"a.weight": torch.randn(17, 9), "a.bias": torch.randn(9).bfloat16(), "ids": torch.arange(11), "flag": torch.tensor([True, False]),
+          "half": torch.randn(4, 4).half(), "empty": torch.zeros(0, 3), "bytes": torch.arange(7, dtype=torch.uint8)}
+    path = str(tmp_path / "m.safetensors")
+    S.save_safetensors(sd, path, metadata={"format": "pt"})
+    lib = S.load_safetensors(path)
+    for threads in (1, 4):
+        got = S.load_safetensors_parallel(path, threads=threads)
+        assert set(got) == set(sd)
+        for k in sd:
+            assert got[k].dtype == lib[k].dtype and got[k].shape == lib[k].shape and torch.equal(got[k], lib[k]), k
+    only = S.load_safetensors_parallel(path, key_filter=lambda k: k.startswith("a."), dtype=torch.float16)
+    assert set(only) == {"a.weight", "a.bias"} and only["a.weight"].dtype == torch.float16
+    header, base = S.read_safetensors_header(path)
+    assert header["__metadata__"] == {"format": "pt"} and header["ids"]["dtype"] == "I64" and base > 8
+    # hostile headers: a length field larger than the file, offsets past the end, a shape that does not match its bytes
+    raw = bytearray(open(path, "rb").read())
+    bad = tmp_path / "bad.safetensors"
+    bad.write_bytes((1 << 40).to_bytes(8, "little") + bytes(raw[8:]))
+    with pytest.raises(ValueError):
+        S.load_safetensors_parallel(str(bad))
+    import json
+
+    n = int.from_bytes(raw[:8], "little")
+    hdr = json.loads(bytes(raw[8:8 + n]))
+    for mutate in (lambda h: h["ids"].__setitem__("data_offsets", [0, 1 << 30]), lambda h: h["ids"].__setitem__("shape", [12])):
+        h2 = json.loads(json.dumps(hdr))
+        mutate(h2)
+        blob = json.dumps(h2).encode()
+        bad.write_bytes(len(blob).to_bytes(8, "little") + blob + bytes(raw[8 + n:]))
+        with pytest.raises(ValueError):
+            S.load_safetensors_parallel(str(bad))
