@@ -75,7 +75,13 @@ def build(name: str, **kw) -> nn.Module:
 
 
 def available() -> list[str]:
-    return sorted(set(list_models()) | set(CLASSIFIERS) | set(DETECTORS) | set(SEGMENTERS) | {"unet"})
+    """Every name :func:`build` accepts."""
+    from ..models.detection import OWN_MODELS as DET
+    from ..models.vision_families import OWN_MODELS as MORE
+    from ..models.vision_zoo import OWN_MODELS
+
+    return sorted(set(list_models()) | set(OWN_MODELS) | set(MORE) | set(DET) | set(CLASSIFIERS) | set(DETECTORS) | set(SEGMENTERS)
+                  | {"unet"})
 
 
 class UNet(nn.Module):

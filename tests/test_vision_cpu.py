@@ -351,3 +351,17 @@ def test_every_vision_entry_of_the_hub_builds_with_its_listed_size():
         assert type(net).__module__.startswith("ferrotorch_b200."), "%s is not this package's own module" % info.name
         seen += 1
     assert seen >= 23
+
+
+def test_every_name_of_the_reference_registry_builds_as_an_own_module():
+    # the model names registered in ferrotorch-vision/src/models/registry.rs
+    from ferrotorch_b200 import vision as V
+
+    names = ["convnext_tiny", "deeplabv3_resnet50", "densenet121", "efficientnet_b0", "fasterrcnn_resnet50_fpn", "fcn_resnet50",
+             "fcos_resnet50_fpn", "inception_v3", "keypointrcnn_resnet50_fpn", "lraspp_mobilenet_v3_large", "maskrcnn_resnet50_fpn",
+             "mobilenet_v2", "mobilenet_v3_small", "resnet18", "resnet34", "resnet50", "retinanet_resnet50_fpn", "ssd300_vgg16",
+             "swin_tiny", "unet", "vgg11", "vgg16", "vit_b_16", "yolo"]
+    for n in names:
+        net = V.build(n)
+        assert type(net).__module__.startswith("ferrotorch_b200."), n
+    assert set(names) <= set(V.available())
