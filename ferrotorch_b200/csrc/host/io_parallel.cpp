@@ -5,24 +5,16 @@
 // here they are views into the one buffer this call fills.
 //
 //   ftio_read(path, offset, nbytes, dst, threads) -> 0, or -errno / -1 (short file)
-//   ftio_file_size(path) -> size or -errno
 #include <algorithm>
 #include <atomic>
 #include <cerrno>
 #include <cstdint>
 #include <fcntl.h>
-#include <sys/stat.h>
 #include <thread>
 #include <unistd.h>
 #include <vector>
 
 #define FTIO_API extern "C" __attribute__((visibility("default")))
-
-FTIO_API long long ftio_file_size(const char* path) {
-  struct stat st;
-  if (stat(path, &st) != 0) return -static_cast<long long>(errno);
-  return static_cast<long long>(st.st_size);
-}
 
 FTIO_API int ftio_read(const char* path, long long offset, long long nbytes, void* dst, int threads) {
   if (!path || !dst || offset < 0 || nbytes < 0) return -EINVAL;
