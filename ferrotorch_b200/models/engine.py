@@ -337,10 +337,41 @@ class LlamaEngine:
         return self._combine_argmax(self._pair_out)
 
     @torch.no_grad()
-    def generate(self, prompts: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+    def sample_step(self, tokens: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0,
+                    seed: int = 0) -> torch.Tensor:
+        """One decode step that samples instead of taking the arg-max: temperature, top-k and
+        nucleus sampling on the vocabulary-sharded logits (``parallel/vocab_sampling.py``: candidates
+        and softmax normaliser are exchanged, never the ``[B, V]`` logits; every rank draws the same
+        token from ``(seed, step)``).  Runs eagerly (the candidate exchange is a library collective,
+        which stays outside captured graphs here)."""
+        from ..parallel.backend import SimulatedGroup, TorchGroup
+        from ..parallel.vocab_sampling import sample_vocab_parallel, shared_uniform
+
+        B = tokens.numel()
+        for s in self.seqs:
+            self.manager.extend(s, 1)
+        self.cache.sync_table()
+        if getattr(self, "_sid", None) is None or self._sid.numel() != B:
+            self._sid = torch.arange(B, device=self.device, dtype=torch.int32)
+        pos = self.lengths.clone()
+        self.lengths += 1
+        h = self._forward(tokens.to(self.device), pos, self._sid, B, 1, True, self.lengths)
+        self._norm_into(4, h, None, self.norm, B)
+        logits = self._col(4, B, self.lm_head)[:, :self.Vloc]
+        group = TorchGroup(self.tp.group) if self.W > 1 else SimulatedGroup.create_group(1)[0]
+        valid = min(self.Vloc, max(0, self.cfg.vocab_size - self.r * self.Vloc))
+        self._sample_steps = getattr(self, "_sample_steps", 0) + 1
+        u = shared_uniform(B, seed, self._sample_steps, self.device)
+        return sample_vocab_parallel(logits, group, self.r * self.Vloc, u, temperature, top_k, top_p, valid=valid)
+
+    @torch.no_grad()
+    def generate(self, prompts: torch.Tensor, max_new_tokens: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+                 seed: int = 0) -> torch.Tensor:
+        """Greedy by default (graph-replayed decode steps); ``temperature > 0`` samples every token
+        after the first with :meth:`sample_step`."""
         tok = self.prefill(prompts)
         out = [tok]
         for _ in range(max_new_tokens - 1):
-            tok = self.decode_step(tok)
+            tok = self.decode_step(tok) if temperature <= 0.0 else self.sample_step(tok, temperature, top_k, top_p, seed)
             out.append(tok)
         return torch.stack(out, dim=1)

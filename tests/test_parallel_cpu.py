@@ -443,3 +443,43 @@ def test_function_style_collectives_and_reference_names(tmp_path):
     assert torch.equal(torch.cat(parts), full["w"]) and [p.numel() for p in parts] == [4, 4, 4]
     with pytest.raises(P.DistCheckpointError):
         P.DistributedCheckpoint.open(str(tmp_path / "nope"))
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_vocabulary_parallel_sampling_equals_single_device_sampling(world):
+    # temperature / top-k / top-p on logits sharded over the vocabulary pick exactly the tokens the
+    # single-device procedure picks from the full logits with the same uniform numbers; the last shard
+    # is padded; a nucleus wider than the first candidate list makes the call widen it
+    from ferrotorch_b200.parallel import vocab_sampling as VS
+    from ferrotorch_b200.parallel.backend import run_simulated
+
+    torch.manual_seed(0)
+    B, V = 64, 1000
+    Vl = (V + world - 1) // world
+    logits = torch.randn(B, V) * 3.0
+    logits[:8] *= 0.05                      # nearly flat rows: very wide nuclei
+    logits[8:16, :300] += 6.0               # rows whose probable tokens all sit in the first shard
+    padded = torch.cat([logits, torch.zeros(B, Vl * world - V)], 1)
+    cases = [(1.0, 0, 1.0), (0.7, 50, 1.0), (1.3, 0, 0.9), (1.0, 40, 0.8), (0.0, 0, 1.0), (1.0, 0, 0.999), (2.0, 5, 0.5)]
+
+    def body(g):
+        out = []
+        for step, (temp, k, p) in enumerate(cases):
+            u = VS.shared_uniform(B, 7, step)
+            lo = g.rank * Vl
+            out.append(VS.sample_vocab_parallel(padded[:, lo:lo + Vl], g, lo, u, temp, k, p, candidates=16, valid=max(0, min(Vl, V - lo))))
+        return out
+
+    res = run_simulated(world, body)
+    for step, (temp, k, p) in enumerate(cases):
+        u = VS.shared_uniform(B, 7, step)
+        want = logits.argmax(-1) if temp == 0.0 else VS.sample_reference(logits, u, temp, k, p)
+        for r in range(world):
+            assert torch.equal(res[r][step], want), (world, step, (res[r][step] != want).sum())
+        assert int(want.max()) < V
+    # the draws follow the distribution: frequencies of a small vocabulary against its softmax
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).expand(4000, 4).contiguous()
+    g1 = run_simulated(2, lambda g: VS.sample_vocab_parallel(small[:, g.rank * 2:(g.rank + 1) * 2], g, g.rank * 2,
+                                                             VS.shared_uniform(4000, 3, 0)))[0]
+    freq = torch.bincount(g1, minlength=4).float() / 4000
+    assert torch.allclose(freq, small[0].softmax(-1), atol=0.03)
