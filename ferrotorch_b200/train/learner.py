@@ -250,6 +250,7 @@ class Learner:
         params = [p for p in self.model.parameters() if p.requires_grad]
         for bi, (x, y) in enumerate(data):
             x, y = self._to_device(x), self._to_device(y)
+            self.last_batch_size = int(x.shape[0]) if hasattr(x, "shape") and x.dim() else 1
             if train and self.trainer is not None:
                 loss = self.trainer.step(x, y)
                 out = None

@@ -2,6 +2,7 @@
 import json
 import os
 import struct
+import time
 
 import pytest
 import torch
@@ -541,3 +542,59 @@ def test_learner_drives_a_flat_trainer(tmp_path):
     a = float(trainer.step(*data[0]))
     b = float(trainer2.step(*data[0]))
     assert a == pytest.approx(b, rel=1e-5)
+
+
+# --------------------------------------------------------------------------- run metrics (JSON lines per rank)
+def test_metrics_logger_reports_job_rate_from_the_slowest_rank(tmp_path):
+    import threading
+
+    from ferrotorch_b200.parallel.backend import SimulatedGroup
+    from ferrotorch_b200.train import MetricsLogger, read_metrics
+
+    groups = SimulatedGroup.create_group(2)
+    out = {}
+
+    def rank(r):
+        log = MetricsLogger(str(tmp_path), group=groups[r], unit="tokens", every=4, flops_per_item=100.0, peak_flops=1e6)
+        for _ in range(8):
+            log.begin_step()
+            time.sleep(0.004 * (1 + r))                  # rank 1 is twice as slow
+            log.end_step(items=1000, loss=torch.tensor(2.5), exposed_comm_ms=1.0)
+        log.close()
+        out[r] = log.reports
+
+    ts = [threading.Thread(target=rank, args=(r,)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert len(out[0]) == len(out[1]) == 2
+    for a, b in zip(out[0], out[1]):
+        # both ranks report the same job: the slowest rank's step time, the sum of the items
+        assert a.ms_per_step_max_over_ranks == b.ms_per_step_max_over_ranks == max(a.ms_per_step, b.ms_per_step)
+        assert a.items_per_s == b.items_per_s
+        assert abs(a.items_per_s - 2 * 4 * 1000 / (4 * a.ms_per_step_max_over_ranks / 1e3)) < 1e-6 * a.items_per_s
+        assert a.ms_per_step < b.ms_per_step
+        assert abs(a.flop_utilisation - a.items_per_s * 100.0 / 2e6) < 1e-12
+        assert 0 < b.exposed_comm_frac < a.exposed_comm_frac < 1
+    for r in range(2):
+        rows = read_metrics(str(tmp_path / ("metrics_rank%d.jsonl" % r)))
+        assert [row["step"] for row in rows] == [4, 8] and rows[0]["rank"] == r and rows[0]["unit"] == "tokens/s"
+        assert rows[0]["loss"] == 2.5 and rows[0]["world_size"] == 2
+
+
+def test_metrics_callback_logs_learner_batches_and_tensorboard_scalars(tmp_path):
+    from ferrotorch_b200.train import Learner, MetricsCallback, MetricsLogger, TensorBoardWriter, read_metrics
+
+    torch.manual_seed(0)
+    model = torch.nn.Linear(6, 3)
+    data = [(torch.randn(5, 6), torch.randint(0, 3, (5,))) for _ in range(6)]
+    tb = TensorBoardWriter(str(tmp_path / "tb"))
+    log = MetricsLogger(str(tmp_path), unit="samples", every=3, tensorboard=tb)
+    Learner(model, torch.optim.SGD(model.parameters(), lr=0.1), torch.nn.functional.cross_entropy, callbacks=[MetricsCallback(log)],
+            device="cpu").fit(data, epochs=2)
+    tb.close()
+    rows = read_metrics(log.path)
+    assert [r["step"] for r in rows] == [3, 6, 9, 12] and all(r["steps_in_window"] == 3 for r in rows)
+    assert all(r["items_per_s"] > 0 and r["ms_per_step"] == r["ms_per_step_max_over_ranks"] for r in rows)
+    assert {r["epoch"] for r in rows} == {0, 1} and "exposed_comm_frac" not in rows[0]
+    blob = b"".join(open(os.path.join(tmp_path / "tb", f), "rb").read() for f in os.listdir(tmp_path / "tb"))
+    assert b"throughput/samples_per_s" in blob and b"train/loss" in blob
