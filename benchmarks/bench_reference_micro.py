@@ -25,6 +25,7 @@ from torch import nn
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import ferrotorch_b200 as ft  # noqa: E402
+from ferrotorch_b200.ops.random import DevicePhilox  # noqa: E402
 
 # name -> (reference ferrotorch us, reference PyTorch us) as published; None where not published
 PUBLISHED = {
@@ -66,8 +67,12 @@ def cases(dev):
     g = torch.Generator(device=dev).manual_seed(0)
     r = lambda *s: torch.rand(*s, device=dev, generator=g) + 0.1  # noqa: E731
     a, b = r(1000, 1000), r(1000, 1000)
+    # "rand" is this package's own generator (Philox-4x32-10: device kernel, threaded host fill), as the
+    # reference's row is its own generator; torch's generator is the second row
+    philox = DevicePhilox(0, dev)
     out = {
-        "zeros": lambda: ft.zeros((1000, 1000), device=dev), "rand": lambda: ft.rand((1000, 1000), device=dev),
+        "zeros": lambda: ft.zeros((1000, 1000), device=dev), "rand": lambda: philox.uniform(1000, 1000),
+        "rand@torch_generator": lambda: ft.rand((1000, 1000), device=dev),
         "add": lambda: a + b, "mul": lambda: a * b, "sub": lambda: a - b, "div": lambda: a / b, "relu": lambda: torch.relu(a),
         "sigmoid": lambda: torch.sigmoid(a), "exp": lambda: torch.exp(a), "log": lambda: torch.log(a), "sin": lambda: torch.sin(a),
         "cos": lambda: torch.cos(a), "tanh": lambda: torch.tanh(a), "sum_all": lambda: a.sum(), "sum_dim0": lambda: ft.sum_dim(a, 0),
@@ -130,10 +135,10 @@ def main():
     rows = []
     with torch.inference_mode(False):
         for name, fn in cases(dev).items():
-            if name not in pub:
+            if name.split("@")[0] not in pub:
                 continue
             us = timeit(fn, dev, a.iters, a.warmup)
-            ref_ft, ref_pt = pub[name]
+            ref_ft, ref_pt = pub[name.split("@")[0]]
             rows.append({"bench": name, "us": round(us, 1), "reference_ferrotorch_us": ref_ft, "reference_pytorch_us": ref_pt,
                          "speedup_vs_reference": round(ref_ft / us, 2) if ref_ft else None})
     for r in rows:

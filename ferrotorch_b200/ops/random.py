@@ -37,6 +37,22 @@ WORDS, UNIFORM, NORMAL = 0, 1, 2
 _MASK64 = 2 ** 64 - 1
 
 
+_fill_f32 = False        # False = not looked up yet, None = host library unavailable
+
+
+def _host_fill():
+    global _fill_f32
+    if _fill_f32 is False:
+        try:
+            lib = _native.host()
+            lib.ftp_fill_f32.argtypes = [_u64, _u64, _ll, _i, _f, _f, _vp, _i]
+            lib.ftp_fill_f32.restype = _i
+            _fill_f32 = lib.ftp_fill_f32
+        except Exception:  # noqa: BLE001 - no compiler / library: the numpy path serves
+            _fill_f32 = None
+    return _fill_f32
+
+
 def _host_words(n: int, seed: int, counter: int) -> np.ndarray:
     ctr = np.arange((n + 3) // 4, dtype=np.uint64) + np.uint64(counter & _MASK64)
     return philox_4x32_10(ctr, seed).reshape(-1)[:n]
@@ -78,6 +94,16 @@ class DevicePhilox:
         n = out.numel()
         c = self.reserve(n)
         if not out.is_cuda:
+            fill = _host_fill() if kind != WORDS else None
+            if fill is not None:
+                # the host library's threaded fill: same stream positions and the same word -> value
+                # arithmetic as the device kernel
+                buf = out if (out.dtype == torch.float32 and out.is_contiguous()) else torch.empty(n, dtype=torch.float32)
+                if fill(c, self.seed, n, kind, float(a), float(b), buf.data_ptr(), torch.get_num_threads()) != 0:
+                    raise RuntimeError("ftp_fill_f32 failed")
+                if buf is not out:
+                    out.copy_(buf.view(out.shape))
+                return out
             if kind == WORDS:
                 out.copy_(torch.from_numpy(_host_words(n, self.seed, c).astype(np.int64)).view(out.shape))
             elif kind == UNIFORM:

@@ -43,6 +43,31 @@ def test_cpu_generator_matches_host_stream_and_dropout_regenerates_its_mask():
     assert R.dropout(x, 0.4, training=False) is x
 
 
+@pytest.mark.parametrize("n", [1, 3, 4, 5, 31, 32, 33, 70001, 300003])
+def test_threaded_host_fill_follows_the_stream_of_the_scalar_generator(n):
+    """The host library's fill (eight counters per trip, several threads above 32 K values) against
+    the numpy form of the rounds: uniforms bitwise, normals to the rounding of log / sin / cos, for
+    sizes around the group width and the thread split, and across the 2^32 counter carry."""
+    start = 2 ** 32 - 7
+    g = R.DevicePhilox(4242, "cpu")
+    g.counter = start
+    u = g.uniform(n, low=-1.0, high=3.0)
+    assert g.counter == start + (n + 3) // 4
+    ref = -1.0 + 4.0 * R._host_u01(n, 4242, start)
+    assert torch.equal(u, ref)
+    g.counter = start
+    z = g.normal(n, mean=0.5, std=1.5)
+    h = PhiloxGenerator(4242)
+    h.counter = start
+    zr = 0.5 + 1.5 * torch.from_numpy(h.generate_normal(4 * ((n + 3) // 4))[:n])
+    torch.testing.assert_close(z, zr, rtol=0, atol=3e-6)
+    g.counter = start
+    zb = g.normal(n, mean=0.5, std=1.5, dtype=torch.bfloat16)          # other dtypes go through an fp32 buffer
+    assert torch.equal(zb, z.to(torch.bfloat16))
+    if n > 60000:
+        assert abs(float(z.mean()) - 0.5) < 0.03 and abs(float(z.std()) - 1.5) < 0.03
+
+
 @pytest.mark.gpu
 def test_device_words_and_uniform_equal_the_host_generator_bitwise():
     n = 1 << 20
