@@ -19,7 +19,7 @@ _SUBMODULES = ("nn", "optim", "data", "train", "vision", "jit", "serialize", "pa
 _ALIASES = {"gpu": "cuda", "distributed": "parallel", "llama": "models.llama_api", "ml": "utils.ml", "tokenize": "utils.text",
             "grammar": "utils.grammar", "jit_script": "jit", "prelude": "prelude", "bert": "models.pretrained",
             "whisper": "models.pretrained", "graph": "models.pretrained", "rl": "models.pretrained",
-            "diffusion": "models.diffusion"}
+            "diffusion": "models.diffusion", "cubecl": "utils.portable_kernels"}
 __all__ = ["ops", "autograd", "core", "__version__", *_SUBMODULES, *_ALIASES]
 
 

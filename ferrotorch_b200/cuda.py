@@ -411,7 +411,58 @@ def _gpu_op_table() -> dict:
 
         return own_pool(x, kernel_size, stride, padding)
 
+    def batch_norm_backward(x, grad_out, weight, running_mean, running_var, eps=1e-5, training=True):
+        """(grad_input, grad_weight, grad_bias) of a [N, C, ...] batch norm; batch statistics in training,
+        the running ones in evaluation (ferrotorch-gpu/src/group_norm.rs:1449)."""
+        dims = [0] + list(range(2, x.dim()))
+        shape = [1, -1] + [1] * (x.dim() - 2)
+        if training:
+            mean, var = x.mean(dims), x.var(dims, unbiased=False)
+        else:
+            mean, var = running_mean, running_var
+        inv = torch.rsqrt(var + eps)
+        xhat = (x - mean.view(shape)) * inv.view(shape)
+        gw, gb = (grad_out * xhat).sum(dims), grad_out.sum(dims)
+        gx = grad_out * (weight * inv).view(shape)
+        if training:
+            m = x.numel() // x.shape[1]
+            gx = gx - ((weight * inv).view(shape) / m) * (gb.view(shape) + xhat * gw.view(shape))
+        return gx, gw, gb
+
+    def lrn_denominator(x, size, alpha=1e-4, beta=0.75, k=1.0):
+        sq = F.pad(x.pow(2).unsqueeze(1), (0, 0) * (x.dim() - 2) + (size // 2, (size - 1) // 2))
+        win = sq.unfold(2, size, 1).sum(-1).squeeze(1)
+        return k + alpha / size * win
+
+    def local_response_norm_backward(x, grad_out, denom, size, alpha=1e-4, beta=0.75):
+        """Input gradient of ``x * denom^-beta`` with ``denom = k + alpha / size * window_sum(x^2)`` over the
+        channel window (ferrotorch-gpu/src/group_norm.rs:1963): the direct term plus the window sum of
+        ``grad * x * denom^(-beta-1)`` seen from every channel that has this one in its window."""
+        t = grad_out * x * denom.pow(-beta - 1.0)
+        tp = F.pad(t.unsqueeze(1), (0, 0) * (x.dim() - 2) + ((size - 1) // 2, size // 2))
+        back = tp.unfold(2, size, 1).sum(-1).squeeze(1)
+        return grad_out * denom.pow(-beta) - (2.0 * alpha * beta / size) * x * back
+
+    def scatter_reduce_nd(x, dim, idx, src, reduce="sum", include_self=True):
+        names = {0: "sum", 1: "prod", 2: "amax", 3: "amin", 4: "mean"}
+        return x.scatter_reduce(dim, idx, src, names.get(reduce, reduce), include_self=include_self)
+
+    def slice_write_indirect(src, dst, pos):
+        """``dst[:, pos] = src`` with the position read on the device (no host read: usable inside a
+        captured graph; ferrotorch-gpu/src/kernels.rs:31594)."""
+        return dst.index_copy_(1, pos.reshape(1).long(), src.unsqueeze(1))
+
+    def causal_mask_indirect(total_len, n_head, max_pos):
+        """``[n_head, max_pos]``: 0 where the column is below the device-resident length, else -1e9
+        (ferrotorch-gpu/src/kernels.rs:31670)."""
+        col = torch.arange(max_pos, device=total_len.device)
+        row = torch.where(col < total_len.reshape(1), 0.0, -1e9).to(torch.float32)
+        return row.expand(n_head, max_pos).contiguous()
+
     return {
+        "batch_norm_backward": batch_norm_backward, "local_response_norm_backward": local_response_norm_backward,
+        "local_response_norm_denominator": lrn_denominator, "scatter_reduce_nd": scatter_reduce_nd,
+        "slice_write_indirect": slice_write_indirect, "causal_mask_indirect": causal_mask_indirect,
         "add": torch.add, "sub": torch.sub, "mul": torch.mul, "neg": torch.neg, "relu": torch.relu, "gelu": F.gelu,
         "silu": F.silu, "softmax": lambda x, dim=-1: torch.softmax(x, dim), "dropout": F.dropout,
         "scale": lambda x, s: x * s, "add_scaled": lambda a, b, s: torch.add(a, b, alpha=s),
@@ -515,4 +566,29 @@ def __getattr__(name):
         from .utils import memory_guard
 
         return getattr(memory_guard, table[name])
+    if name in ("PhiloxGenerator", "PhiloxState", "CudaRngManager", "cuda_rng_manager", "fork_rng", "join_rng"):
+        from .utils import philox
+
+        return getattr(philox, name)
+    if name == "CudaBackendImpl":
+        return CudaBackendImpl
     raise AttributeError(name)
+
+
+class CudaBackendImpl:
+    """The reference's backend object (ferrotorch-gpu/src/backend_impl.rs:88: one method per typed
+    kernel behind the core crate's dispatch trait) as a namespace over this module's launcher
+    table: ``CudaBackendImpl().relu_bf16(x)`` is ``gpu_relu_bf16(x)``.  There is no second back-end
+    to dispatch between here, so the object holds only the device ordinal it was made for."""
+
+    def __init__(self, ordinal: int = 0):
+        self.ordinal = ordinal
+
+    def __getattr__(self, name):
+        fn = _resolve_gpu_op("gpu_" + name)
+        if fn is None:
+            raise AttributeError("no launcher named gpu_%s" % name)
+        return fn
+
+    def __repr__(self) -> str:
+        return "CudaBackendImpl(ordinal=%d)" % self.ordinal

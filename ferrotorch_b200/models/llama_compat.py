@@ -91,6 +91,69 @@ class HqqQ4Axis1:
         return _q.to_q4_linear(self.dequantize())
 
 
+@dataclass(frozen=True)
+class LayerKvCache:
+    """One layer's keys (after RoPE) and values, ``[num_kv_heads, seq_len, head_dim]``, as a value:
+    ``append`` returns a new cache and leaves this one untouched (ferrotorch-llama/src/kv_cache.rs:
+    37-150).  The pre-allocated in-place cache that the models use is ``nn.layers.KVCache``; the
+    paged one ``nn.paged``; this is the reference's functional form, for code written against it."""
+    k: torch.Tensor
+    v: torch.Tensor
+
+    def __post_init__(self):
+        if self.k.dim() != 3 or self.k.shape != self.v.shape:
+            raise ValueError("LayerKvCache: k and v must both be [num_kv_heads, seq_len, head_dim], got %s and %s"
+                             % (tuple(self.k.shape), tuple(self.v.shape)))
+
+    def seq_len(self) -> int:
+        return int(self.k.shape[1])
+
+    def append(self, new_k: torch.Tensor, new_v: torch.Tensor) -> "LayerKvCache":
+        if new_k.dim() != 3 or new_k.shape != new_v.shape or new_k.shape[0] != self.k.shape[0] or new_k.shape[2] != self.k.shape[2]:
+            raise ValueError("LayerKvCache.append: new block %s does not extend %s" % (tuple(new_k.shape), tuple(self.k.shape)))
+        return LayerKvCache(torch.cat([self.k, new_k], 1), torch.cat([self.v, new_v], 1))
+
+    @classmethod
+    def from_single_token(cls, new_k: torch.Tensor, new_v: torch.Tensor) -> "LayerKvCache":
+        return cls(new_k, new_v)
+
+
+@dataclass(frozen=True)
+class LlamaKvCache:
+    """One :class:`LayerKvCache` per decoder layer (kv_cache.rs:157-260); ``extend`` appends one
+    ``(k, v)`` block per layer and returns the longer cache."""
+    layers: tuple = ()
+    seq_len: int = 0
+
+    @classmethod
+    def empty(cls) -> "LlamaKvCache":
+        return cls()
+
+    def __len__(self) -> int:
+        return self.seq_len
+
+    def len(self) -> int:
+        return self.seq_len
+
+    def is_empty(self) -> bool:
+        return self.seq_len == 0
+
+    def extend(self, new_layer_kv) -> "LlamaKvCache":
+        new_layer_kv = list(new_layer_kv)
+        if self.layers and len(new_layer_kv) != len(self.layers):
+            raise ValueError("LlamaKvCache.extend: %d layers given, cache has %d" % (len(new_layer_kv), len(self.layers)))
+        if not new_layer_kv:
+            raise ValueError("LlamaKvCache.extend: no layers given")
+        if self.layers:
+            layers = tuple(c.append(k, v) for c, (k, v) in zip(self.layers, new_layer_kv))
+        else:
+            layers = tuple(LayerKvCache.from_single_token(k, v) for k, v in new_layer_kv)
+        lens = {c.seq_len() for c in layers}
+        if len(lens) != 1:
+            raise ValueError("LlamaKvCache.extend: layers disagree on the sequence length: %s" % sorted(lens))
+        return LlamaKvCache(layers, lens.pop())
+
+
 @dataclass
 class ProfiledForwardResult:
     """Logits plus wall time per named phase, as returned by a profiled forward."""

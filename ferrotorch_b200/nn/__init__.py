@@ -13,7 +13,7 @@ from ..ops.batchnorm import BatchNormAct2d, batch_norm_act  # noqa: F401,E402
 from .fake_quant import FakeQuantize, MinMaxObserver, MovingAverageObserver, QatLinear, prepare_qat  # noqa: F401,E402
 from .extra import (HookedModule, HookHandle, LoRALinear, SqueezeExcitation, flash_attention,  # noqa: F401,E402
                     standard_attention)
-from ..core import flex_attention  # noqa: F401,E402
+from ..core import BlockMask, flex_attention  # noqa: F401,E402
 from .paged import OutOfPages, PagedAttentionManager, PagedKVCache  # noqa: F401,E402
 from ..ops.conv import IgemmConv2d, convert_convs  # noqa: F401,E402  (implicit-GEMM convolution; opt-in, see ops.conv)
 from ..ops.pool import MaxPool2d as NhwcMaxPool2d  # noqa: F401,E402

@@ -643,3 +643,39 @@ def test_typed_launcher_names_resolve():
     assert s[0, 1] == float("-inf") and s[2, 0] == 0
     with pytest.raises(AttributeError):
         C.gpu_no_such_op
+
+
+def test_launchers_added_for_graph_capture_and_normalisation_gradients():
+    from ferrotorch_b200 import cuda as C
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 6, 5, 5, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(6, dtype=torch.float64, requires_grad=True)
+    b = torch.zeros(6, dtype=torch.float64, requires_grad=True)
+    rm, rv = torch.randn(6, dtype=torch.float64), torch.rand(6, dtype=torch.float64) + 0.5
+    for training in (True, False):
+        y = torch.nn.functional.batch_norm(x, rm.clone(), rv.clone(), w, b, training, 0.1, 1e-5)
+        g = torch.randn_like(y)
+        want = torch.autograd.grad(y, (x, w, b), g)
+        got = C.gpu_batch_norm_backward_f64(x.detach(), g, w.detach(), rm, rv, 1e-5, training)
+        for a, e in zip(got, want):
+            torch.testing.assert_close(a, e)
+    for size in (3, 4, 5):
+        y = torch.nn.functional.local_response_norm(x, size, 1e-2, 0.75, 2.0)
+        g = torch.randn_like(y)
+        den = C.gpu_local_response_norm_denominator(x.detach(), size, 1e-2, 0.75, 2.0)
+        torch.testing.assert_close(x.detach() * den.pow(-0.75), y.detach())
+        torch.testing.assert_close(C.gpu_local_response_norm_backward_f64(x.detach(), g, den, size, 1e-2, 0.75),
+                                   torch.autograd.grad(y, x, g)[0])
+    # positions and lengths that live in device memory (nothing is read back: usable under graph capture)
+    dst, src = torch.zeros(2, 7, 3), torch.randn(2, 3)
+    C.gpu_slice_write_indirect(src, dst, torch.tensor([4], dtype=torch.int32))
+    assert torch.equal(dst[:, 4], src) and int((dst != 0).sum()) == 6
+    m = C.gpu_causal_mask_indirect(torch.tensor([3]), 2, 5)
+    assert m.shape == (2, 5) and m[1].tolist() == [0.0, 0.0, 0.0, -1e9, -1e9]
+    inp, idx, s2 = torch.zeros(3, 4), torch.tensor([[0, 1, 0, 1], [2, 2, 2, 2]]), torch.arange(8.0).view(2, 4)
+    assert torch.equal(C.gpu_scatter_reduce_nd_f32(inp, 0, idx, s2, 2, False), inp.scatter_reduce(0, idx, s2, "amax", include_self=False))
+    be = C.CudaBackendImpl(0)
+    assert torch.equal(be.relu_f32(torch.tensor([-1.0, 2.0])), torch.tensor([0.0, 2.0])) and "ordinal=0" in repr(be)
+    with pytest.raises(AttributeError):
+        be.no_such_kernel

@@ -258,3 +258,48 @@ def test_reference_names_packed_vocab_masked_loop():
     q = M.GptqQ4(*__import__("ferrotorch_b200.serialize.quant_loaders", fromlist=["x"]).pack_gptq(torch.randn(16, 128), 128))
     assert (q.in_features, q.out_features) == (128, 16) and q.dequantize().shape == (16, 128)
     assert M.LlamaActivation.Silu == "silu" and M.LlamaMLP.__name__ == "SwiGLU"
+
+
+# --------------------------------------------------------------------------- automaton walk over the whole vocabulary
+def test_dfa_token_mask_equals_brute_force_and_the_schema_processor():
+    import torch
+
+    from ferrotorch_b200 import cubecl
+    from ferrotorch_b200.utils.dfa_mask import DfaMaskInputs, compute_token_mask_dfa, literal_dfa
+    from ferrotorch_b200.utils.grammar import JsonSchemaProcessor, PackedVocab
+
+    vocab = ["t", "tr", "true", "rue", "e", "f", "false", "als", "alse", "x", "truex", "tru", "ue", "se", "fa", "T", "n", "null",
+             "ull", "l", "u", "r", "a", "s", "", "é", "tré"]
+    pv = PackedVocab.pack(vocab)
+    for lits in (["true", "false"], ["null"], ["red", "rose", "ruse", "true"]):
+        for emitted in ("", "t", "tr", "fal", "nul", "r", "ro", "true"):
+            d = literal_dfa(lits, emitted)
+            if d is None:
+                assert not any(w.startswith(emitted) for w in lits)
+                continue
+            inp = DfaMaskInputs.new(d[0], d[1], pv.offsets, pv.chars, d[2], d[3], d[4], pv.max_token_len, vocab_size=len(vocab))
+            got = compute_token_mask_dfa(inp)
+            want = [bool(t) and any(w.startswith(emitted + t) for w in lits) for t in vocab]      # empty token: rejected
+            assert got.tolist() == want, (lits, emitted)
+    # the same masks as the general schema processor gives in its literal states
+    plain = [t for t in vocab if t and t.isascii()]
+    ppv = PackedVocab.pack(plain)
+    for schema, lits in (({"type": "boolean"}, ["true", "false"]), ({"type": "null"}, ["null"])):
+        for toks in ([], [lits[0][0]], [lits[0][0], lits[0][1]], [lits[-1][:2]] if lits[-1][:2] in plain else []):
+            p = JsonSchemaProcessor(schema, plain)
+            for t in toks:
+                p.step_token(plain.index(t))
+            d = literal_dfa(lits, "".join(toks))
+            inp = DfaMaskInputs.new(d[0], d[1], ppv.offsets, ppv.chars, d[2], d[3], d[4], ppv.max_token_len)
+            assert torch.equal(compute_token_mask_dfa(inp), p.compute_mask().bits), (schema, toks)
+    # validation and the bounded loop
+    d = literal_dfa(["true", "false"])
+    assert DfaMaskInputs.new(d[0], d[1], pv.offsets[:-1], pv.chars, d[2], d[3], d[4], 5, vocab_size=len(vocab)) is None     # no sentinel
+    assert DfaMaskInputs.new(d[0].reshape(-1)[:-1], d[1], pv.offsets, pv.chars, d[2], d[3], d[4], 5) is None                 # ragged table
+    assert DfaMaskInputs.new(d[0], d[1], pv.offsets, pv.chars, d[2], 99, d[4], 5) is None                                    # bad start
+    assert literal_dfa(["café"]) is None and literal_dfa([]) is None
+    short = DfaMaskInputs.new(d[0], d[1], pv.offsets, pv.chars, d[2], d[3], d[4], 2)
+    assert bool(compute_token_mask_dfa(short)[vocab.index("truex")])                 # walked two characters only, like the bounded kernel loop
+    assert "vocab=%d" % len(vocab) in repr(short)
+    assert cubecl.compute_token_mask_dfa_to_gpu is not None and cubecl.DfaMaskInputs is DfaMaskInputs
+    assert torch.equal(cubecl.compute_token_mask_dfa_to_gpu(inp, device="cpu"), compute_token_mask_dfa(inp))

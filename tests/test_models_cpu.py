@@ -195,3 +195,64 @@ def test_resnet_folded_for_inference_matches_eval_model():
     w, b = R.fold_conv_bn(conv, bn)
     xx = torch.randn(1, 4, 5, 5)
     torch.testing.assert_close(torch.nn.functional.conv2d(xx, w, b), bn(conv(xx)), rtol=1e-4, atol=1e-5)
+
+
+# --------------------------------------------------------------------------- speculative sampling (rejection step)
+def test_speculative_sampling_keeps_the_target_distribution_and_repeats_by_seed():
+    from ferrotorch_b200.models.spec_decode import (FunctionHandle, LlamaHandle, ModelHandle, SpecSamplingConfig,
+                                                    residual_distribution, speculative_sample)
+
+    V = 4
+    g = torch.Generator().manual_seed(3)
+    T, D = torch.randn(V, V, generator=g, dtype=torch.float64) * 1.5, torch.randn(V, V, generator=g, dtype=torch.float64) * 1.5
+    target, draft = FunctionHandle(lambda ids: T[ids[-1]], V), FunctionHandle(lambda ids: D[ids[-1]], V)
+    # exact joint distribution of two tokens sampled from the target after the prompt token 1
+    P = torch.softmax(T, -1)
+    joint = P[1][:, None] * P
+    counts = torch.zeros(V, V, dtype=torch.float64)
+    n, acc, prop = 6000, 0, 0
+    for seed in range(n):
+        o = speculative_sample(target, draft, [0, 1], SpecSamplingConfig(draft_k=2, max_new_tokens=2, seed=seed))
+        assert len(o.tokens) == 2 and o.target_calls <= 2
+        counts[o.tokens[0], o.tokens[1]] += 1
+        acc, prop = acc + o.accepted_count, prop + o.proposed_count
+    tv = 0.5 * (counts / n - joint).abs().sum()
+    assert float(tv) < 0.035, float(tv)                  # sampling noise of 6000 draws over 16 cells is about 0.02
+    assert 0.2 < acc / prop < 0.95                       # a different draft is sometimes rejected
+    # the draft's own distribution is clearly different, so the match above is the rejection step's doing
+    Q = torch.softmax(D, -1)
+    assert float(0.5 * (Q[1][:, None] * Q - joint).abs().sum()) > 0.15
+    # draft == target: everything is accepted
+    o = speculative_sample(target, target, [2], SpecSamplingConfig(draft_k=3, max_new_tokens=9, seed=1))
+    assert o.accepted_count == o.proposed_count and o.acceptance_rate() == 1.0 and len(o.tokens) == 9
+    # same seed, same tokens; eos stops; validation
+    a = speculative_sample(target, draft, [0], SpecSamplingConfig(draft_k=3, max_new_tokens=12, seed=5)).tokens
+    assert a == speculative_sample(target, draft, [0], SpecSamplingConfig(draft_k=3, max_new_tokens=12, seed=5)).tokens
+    assert a != speculative_sample(target, draft, [0], SpecSamplingConfig(draft_k=3, max_new_tokens=12, seed=6)).tokens
+    e = speculative_sample(target, draft, [0], SpecSamplingConfig(draft_k=3, max_new_tokens=50, seed=5, eos_token_ids=[a[3]])).tokens
+    assert e == a[:a.index(a[3]) + 1]
+    with pytest.raises(ValueError):
+        speculative_sample(target, draft, [0], SpecSamplingConfig(draft_k=0))
+    with pytest.raises(ValueError):
+        speculative_sample(target, FunctionHandle(lambda ids: torch.zeros(5), 5), [0])
+    p, q = torch.tensor([0.5, 0.5, 0.0]), torch.tensor([0.2, 0.7, 0.1])
+    assert torch.allclose(residual_distribution(p, q), torch.tensor([1.0, 0.0, 0.0]))
+    assert torch.equal(residual_distribution(p, p), p)
+    # the default all-positions path (one call per prefix) agrees with a single-pass handle
+    class Slow(ModelHandle):
+        def forward_ids(self, ids):
+            return T[ids[-1]]
+
+        def vocab_size(self):
+            return V
+    assert torch.equal(Slow().forward_ids_all_positions([0, 3, 2]), T[[0, 3, 2]])
+    # a real model behind LlamaHandle: with the model as its own draft every token is accepted and the
+    # handle's last-position logits equal the model's
+    cfg = LlamaConfig.tiny()
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg).eval()
+    h = LlamaHandle(m)
+    ids = [5, 9, 2, 7]
+    torch.testing.assert_close(h.forward_ids(ids), m(torch.tensor([ids]))[0, -1].double())
+    o = speculative_sample(h, h, ids, SpecSamplingConfig(draft_k=3, max_new_tokens=7, seed=11))
+    assert o.acceptance_rate() == 1.0 and len(o.tokens) == 7 and h.vocab_size() == cfg.vocab_size

@@ -473,3 +473,41 @@ def test_safetensors_parallel_loader_equals_the_library_loader(tmp_path):
         bad.write_bytes(len(blob).to_bytes(8, "little") + blob + bytes(raw[8 + n:]))
         with pytest.raises(ValueError):
             S.load_safetensors_parallel(str(bad))
+
+
+# --------------------------------------------------------------------------- GGUF blocks as planes
+@pytest.mark.parametrize("kind_name", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q8_1"])
+def test_gguf_plane_split_and_expansion_equal_the_block_decoder(kind_name):
+    """split on the host + torch expansion (the reference's split_q*_blocks / dequantize_q*_to_gpu
+    pair) against the native decoder of raw blocks, bitwise, in both element orders."""
+    import numpy as np
+
+    import ferrotorch_b200 as ft
+    from ferrotorch_b200.serialize import gguf as G
+    from ferrotorch_b200.serialize import gguf_planes as P
+
+    kind = P.GgufBlockKind[kind_name]
+    assert kind.block_elements == 32 and kind.block_bytes == G._BLOCK[int(kind)][1]
+    rng = np.random.default_rng(int(kind))
+    nb = 41
+    raw = rng.integers(0, 256, (nb, kind.block_bytes), dtype=np.uint8)
+    raw[:, 0:2] = rng.standard_normal(nb).astype(np.float16).view(np.uint8).reshape(nb, 2)      # finite scales
+    if kind.has_min or kind == P.GgufBlockKind.Q8_1:
+        raw[:, 2:4] = rng.standard_normal(nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    t = torch.from_numpy(raw.reshape(-1).copy())
+    split = getattr(ft.cubecl, "split_%s_blocks" % kind_name.lower())
+    to_dev = getattr(ft.cubecl, "dequantize_%s_to_gpu" % kind_name.lower())
+    planes = split(t, nb)
+    assert len(planes) == 2 + int(kind.has_min) + int(kind.has_high_bits)
+    assert planes[-1].shape == (nb, 8 if kind_name.startswith("Q8") else 4) and int(planes[-1].max()) < 2 ** 32
+    for order in ("ggml", "interleaved"):
+        want = G.dequantize_blocks(t, int(kind), nb * 32, order)
+        assert torch.equal(to_dev(*planes, nb * 32, device="cpu", nibble_order=order), want)
+    assert to_dev(*planes, nb * 32, device="cpu", dtype=torch.bfloat16).dtype == torch.bfloat16
+    assert torch.equal(split(bytes(raw.reshape(-1)), nb)[0], planes[0])                        # bytes in, same planes
+    with pytest.raises(ValueError):
+        split(t[:-1], nb)
+    with pytest.raises(ValueError):
+        to_dev(*planes, nb * 32 - 32, device="cpu")
+    with pytest.raises(TypeError):
+        to_dev(planes[0], nb * 32, device="cpu")
