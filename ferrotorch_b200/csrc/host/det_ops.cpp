@@ -1,5 +1,5 @@
 // Detection operators on the host: greedy non-maximum suppression and RoI align over fp32 data
-// (the reference keeps them native too: ferrotorch-vision/src/ops/nms.rs, roi_align.rs).
+// (the reference keeps them native too: ferrotorch-vision/src/ops.rs:209 ``nms``, :751 ``roi_align``).
 //
 //   ftd_nms        boxes [n, 4] (x1, y1, x2, y2) already sorted by score, highest first; writes
 //                  the positions of the kept boxes in that order and returns their number.  A box

@@ -98,7 +98,7 @@ def generate(model, input_ids: torch.Tensor, cfg: GenerationConfig | None = None
     return logits and append to the caches it is given (``model.make_caches``).
     ``logits_processor(generated_ids [B, n], logits [B, V]) -> logits`` runs before sampling, e.g. a
     :class:`GrammarLogitsProcessor` for grammar-constrained decoding
-    (ferrotorch-llama/src/grammar_decode.rs masks the logits the same way)."""
+    (ferrotorch-llama/src/gpu_gguf.rs:444 ``apply_grammar_mask_gpu`` masks the logits the same way)."""
     cfg = cfg or GenerationConfig()
     cfg.validate()
     if input_ids.dim() != 2 or input_ids.shape[1] == 0:

@@ -85,7 +85,7 @@ def available() -> list[str]:
 
 
 class UNet(nn.Module):
-    """Encoder-decoder with skip connections (ferrotorch-vision/src/models/segmentation/unet.rs);
+    """Encoder-decoder with skip connections (ferrotorch-vision/src/models/unet.rs);
     torchvision has no UNet, so this one is written out."""
 
     def __init__(self, in_channels: int = 3, num_classes: int = 2, base: int = 32, depth: int = 4):

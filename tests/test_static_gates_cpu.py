@@ -149,3 +149,25 @@ def test_every_exported_native_function_has_a_python_caller():
     accessors = {"ftc_rank", "ftc_world"}          # plain getters of the TCP group handle, kept for embedders
     missing = sorted(n for n in exported - accessors if n not in python)
     assert not missing, missing
+
+
+def test_citations_of_the_reference_point_at_existing_files_and_lines():
+    """Docstrings cite the reference as ``crate/src/file.rs:line``.  With the reference's tree at
+    ``$FERROTORCH_REFERENCE_DIR`` every cited file must exist and be at least that long (the reference
+    keeps a comparable gate, ``tooling/fix-cite-drift.py``); without the tree the gate is skipped."""
+    tree = os.environ.get("FERROTORCH_REFERENCE_DIR", "")
+    if not tree or not os.path.isdir(tree):
+        pytest.skip("FERROTORCH_REFERENCE_DIR is not set")
+    pat = re.compile(r"(ferrotorch(?:-[a-z\-]+)?/(?:src|tests|examples|benches)/[A-Za-z0-9_/.\-]+\.(?:rs|metal|py|toml))(?::(\d+))?")
+    seen, bad = 0, []
+    for p in _files(CODE_EXT):
+        for m in pat.finditer(_read(p)):
+            seen += 1
+            target = os.path.join(tree, m.group(1))
+            if not os.path.exists(target):
+                bad.append((os.path.relpath(p, ROOT), m.group(0), "no such file"))
+            elif m.group(2):
+                with open(target, errors="replace") as f:
+                    if sum(1 for _ in f) < int(m.group(2)):
+                        bad.append((os.path.relpath(p, ROOT), m.group(0), "file is shorter"))
+    assert seen > 100 and not bad, bad
