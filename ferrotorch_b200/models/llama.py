@@ -233,6 +233,38 @@ class LlamaForCausalLM(nn.Module):
             h = h[:, -1:]
         return self.lm_head(h)
 
+    # ------------------------------------------------------------------ the reference's id-level entry points
+    def forward_from_ids(self, ids) -> torch.Tensor:
+        """Logits ``[1, S, V]`` for one sequence of token ids (ferrotorch-llama/src/model.rs:223)."""
+        dev = self.model.embed_tokens.weight.device
+        return self(torch.as_tensor(list(ids), dtype=torch.long, device=dev)[None])
+
+    @torch.no_grad()
+    def forward_one_with_cache(self, token: int, cache):
+        """One decode step on a value cache (model.rs:284): ``(logits [V] float64, longer cache)``.
+        ``cache`` is a :class:`~ferrotorch_b200.models.llama_compat.LlamaKvCache` (empty for the
+        first token); it is not modified.  Decoding a sequence token by token this way gives the
+        logits of :meth:`forward_from_ids` at every position.  The pre-allocated in-place caches of
+        :meth:`make_caches` are what ``generate`` uses; this form is for code written against the
+        reference's functional cache."""
+        from .llama_compat import LlamaKvCache, _GrowingLayerCache
+
+        n_layers = len(self.model.layers)
+        if cache.layers and len(cache.layers) != n_layers:
+            raise ValueError("forward_one_with_cache: cache has %d layers but model has %d" % (len(cache.layers), n_layers))
+        dev = self.model.embed_tokens.weight.device
+        grow = [_GrowingLayerCache(cache.layers[i] if cache.layers else None) for i in range(n_layers)]
+        logits = self(torch.tensor([[int(token)]], dtype=torch.long, device=dev), caches=grow, last_token_only=True)
+        new = LlamaKvCache(tuple(g.as_layer() for g in grow), len(cache) + 1)
+        return logits[0, -1].double(), new
+
+    def load_hqq_state_dict(self, hqq_state: dict, strict: bool = True) -> None:
+        """Load a checkpoint whose linears are HQQ 4-bit (``W_q`` / ``scale`` / ``zero`` / ``shape``
+        per layer): expanded to dense weights, then :meth:`load_hf_state_dict` (model.rs:414)."""
+        from ..serialize.quant_loaders import hqq_state_dict_to_dense
+
+        self.load_hf_state_dict(hqq_state_dict_to_dense(hqq_state), strict)
+
     def make_caches(self, batch: int, max_len: int, device=None, dtype=torch.bfloat16) -> list[KVCache]:
         c = self.config
         return [KVCache(batch, max_len, c.num_key_value_heads, c.head_dim, device, dtype)

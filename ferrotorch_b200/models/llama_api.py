@@ -19,4 +19,4 @@ from ..utils.grammar import JsonSchemaProcessor, SchemaLogitsProcessor, TokenMas
 def __getattr__(name):
     from .. import models
 
-    return getattr(models, name)          # LlamaEngine / LlamaGpuInferencer / GraphedDecoder
+    return getattr(models, name)          # LlamaEngine / LlamaGpuInferencer / GraphedDecoder / ProfiledForwardResult

@@ -154,14 +154,23 @@ class LlamaKvCache:
         return LlamaKvCache(layers, lens.pop())
 
 
-@dataclass
-class ProfiledForwardResult:
-    """Logits plus wall time per named phase, as returned by a profiled forward."""
-    logits: torch.Tensor
-    phase_ms: dict
+class _GrowingLayerCache:
+    """The cache protocol of the attention layer (``len``, ``append(k, v) -> all keys, all values``
+    on ``[1, S, Hkv, D]``) on top of a :class:`LayerKvCache` value (``[Hkv, S, D]``)."""
 
-    def total_ms(self) -> float:
-        return float(sum(self.phase_ms.values()))
+    def __init__(self, layer: LayerKvCache | None):
+        self.k = layer.k.transpose(0, 1)[None] if layer is not None else None
+        self.v = layer.v.transpose(0, 1)[None] if layer is not None else None
+        self.len = layer.seq_len() if layer is not None else 0
+
+    def append(self, k: torch.Tensor, v: torch.Tensor):
+        self.k = k if self.k is None else torch.cat([self.k.to(k.dtype), k], 1)
+        self.v = v if self.v is None else torch.cat([self.v.to(v.dtype), v], 1)
+        self.len = self.k.shape[1]
+        return self.k, self.v
+
+    def as_layer(self) -> LayerKvCache:
+        return LayerKvCache(self.k[0].transpose(0, 1).contiguous(), self.v[0].transpose(0, 1).contiguous())
 
 
 def apply_grammar_mask_gpu(logits: torch.Tensor, allow, device_ordinal: int | None = None) -> torch.Tensor:

@@ -82,6 +82,50 @@ class RotaryPositionEmbedding(nn.Module):
         return F.rope_(x, cos, sin, positions=positions, n_rot_heads=n_rot_heads, seq_len=seq_len,
                        pos_offset=pos_offset, interleaved=self.interleaved)
 
+    # ---- the reference's constructors and accessors (ferrotorch-nn/src/transformer.rs:209-420)
+    @classmethod
+    def with_convention(cls, dim: int, max_seq_len: int, base: float = 10000.0, convention="half") -> "RotaryPositionEmbedding":
+        """``convention``: ``"half"`` (LLaMA / GPT-NeoX: element i pairs with i + dim/2) or
+        ``"interleaved"`` (elements 2i, 2i + 1)."""
+        return cls.with_scaling(dim, max_seq_len, base, convention, None)
+
+    @classmethod
+    def with_scaling(cls, dim: int, max_seq_len: int, base: float = 10000.0, convention="half", scaling: dict | None = None
+                     ) -> "RotaryPositionEmbedding":
+        conv = str(getattr(convention, "value", convention))
+        if conv not in ("half", "interleaved"):
+            raise ValueError("RoPE convention must be 'half' or 'interleaved', got %r" % (convention,))
+        if dim <= 0 or dim % 2 or max_seq_len <= 0:
+            raise ValueError("RoPE needs an even positive dim and a positive max_seq_len, got %d and %d" % (dim, max_seq_len))
+        return cls(dim, max_seq_len, base, interleaved=conv == "interleaved", scaling=scaling)
+
+    @property
+    def dim(self) -> int:
+        return self.head_dim
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.max_pos
+
+    @property
+    def base(self) -> float:
+        return self.theta
+
+    @property
+    def convention(self) -> str:
+        return "interleaved" if self.interleaved else "half"
+
+    def apply(self, x: torch.Tensor, seq_offset: int = 0) -> torch.Tensor:
+        """Rotated copy of ``x [..., seq, dim]`` with positions ``seq_offset ..`` (transformer.rs ``apply``);
+        :meth:`forward` is the in-place form on ``[B, S, heads, dim]`` that the models use."""
+        S, D = x.shape[-2], x.shape[-1]
+        if D != self.head_dim:
+            raise ValueError("RoPE.apply: last dimension %d, expected %d" % (D, self.head_dim))
+        if seq_offset + S > self.max_pos:
+            raise ValueError("RoPE.apply: positions %d .. %d exceed max_seq_len %d" % (seq_offset, seq_offset + S, self.max_pos))
+        y = x.reshape(-1, S, 1, D).clone()
+        return self.forward(y, seq_len=S, pos_offset=seq_offset).reshape(x.shape)
+
 
 class SwiGLU(nn.Module):
     """Gated MLP with one fused ``[gate | up]`` projection (2F x H) so that the activation kernel
@@ -119,6 +163,40 @@ class KVCache:
 
     def reset(self):
         self.len = 0
+
+    # ---- the reference's method set (ferrotorch-nn/src/transformer.rs:864-1010): tensors are
+    # ``[B, num_kv_heads, seq, head_dim]`` there, ``[B, seq, num_kv_heads, head_dim]`` in this class
+    @classmethod
+    def with_dims(cls, max_seq_len: int, batch: int, num_kv_heads: int, head_dim: int, device=None, dtype=torch.bfloat16) -> "KVCache":
+        """``with_dims(max_seq_len, 1, 8, 128)`` for Llama-3-8B."""
+        return cls(batch, max_seq_len, num_kv_heads, head_dim, device, dtype)
+
+    def update(self, key: torch.Tensor, value: torch.Tensor):
+        """Append ``key`` / ``value`` given as ``[B, num_kv_heads, new_seq, head_dim]``; returns the full
+        keys and values in the same layout."""
+        want = (self.k.shape[0], self.k.shape[2], self.k.shape[3])
+        if key.dim() != 4 or key.shape != value.shape or (key.shape[0], key.shape[1], key.shape[3]) != want:
+            raise ValueError("KVCache.update: got %s, cache holds [B=%d, kv_heads=%d, _, head_dim=%d]" % ((tuple(key.shape),) + want))
+        k, v = self.append(key.transpose(1, 2), value.transpose(1, 2))
+        return k.transpose(1, 2), v.transpose(1, 2)
+
+    def seq_len(self) -> int:
+        return self.len
+
+    def is_empty(self) -> bool:
+        return self.len == 0
+
+    def max_seq_len(self) -> int:
+        return self.k.shape[1]
+
+    def num_kv_heads(self) -> int:
+        return self.k.shape[2]
+
+    def head_dim(self) -> int:
+        return self.k.shape[3]
+
+    def batch_size(self) -> int:
+        return self.k.shape[0]
 
 
 def repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:

@@ -158,6 +158,30 @@ class PagedKVCache:
         v = self.v[layer][idx].reshape(-1, self.n_kv_heads, self.head_dim)[:length]
         return k, v
 
+    # ---- accessors under the reference's names (paged_attention.rs:359-395; there one object per
+    # sequence, here one per model, hence the ``seq`` argument)
+    def get_keys(self, seq: int, layer: int = 0) -> torch.Tensor:
+        return self.gather(layer, seq, self.lengths[seq])[0]
+
+    def get_values(self, seq: int, layer: int = 0) -> torch.Tensor:
+        return self.gather(layer, seq, self.lengths[seq])[1]
+
+    def len(self, seq: int | None = None) -> int:
+        """Tokens of one sequence, or of all sequences together."""
+        return self.lengths[seq] if seq is not None else sum(self.lengths)
+
+    def is_empty(self, seq: int | None = None) -> bool:
+        return self.len(seq) == 0
+
+    def num_pages(self, seq: int | None = None) -> int:
+        """Pages held by one sequence, or by all of them."""
+        return len(self._pages[seq]) if seq is not None else self.pool.num_used
+
+    def free_all(self) -> None:
+        for s in range(self.max_seqs):
+            if self._pages[s]:
+                self.free_sequence(s)
+
     def _decode_reference(self, layer, q, ctx_len, scale):
         from ..ops import reference as ref
 
@@ -177,8 +201,9 @@ class PagedAttentionManager:
         self.cache = cache
         self._free_slots = list(range(cache.max_seqs - 1, -1, -1))
         self.active: dict[int, int] = {}
+        self._filled: dict[int, dict[int, int]] = {}        # tokens written through append_kv, per sequence and layer
 
-    def add_sequence(self, prompt_len: int) -> int:
+    def add_sequence(self, prompt_len: int = 0) -> int:
         if not self._free_slots:
             raise OutOfPages("no free sequence slot")
         s = self._free_slots.pop()
@@ -200,6 +225,7 @@ class PagedAttentionManager:
     def remove_sequence(self, seq: int) -> None:
         self.cache.free_sequence(seq)
         del self.active[seq]
+        self._filled.pop(seq, None)
         self._free_slots.append(seq)
         self._free_slots.sort(reverse=True)  # lowest free slot is handed out first
 
@@ -217,3 +243,32 @@ class PagedAttentionManager:
 
     def pool(self) -> PagePool:
         return self.cache.pool
+
+    # ---- the reference's data-carrying calls (paged_attention.rs:485-510): its manager owns one
+    # cache per sequence; here one paged cache serves every layer, hence the ``layer`` argument
+    def append_kv(self, seq_id: int, key: torch.Tensor, value: torch.Tensor, layer: int = 0) -> None:
+        """Append ``key`` / ``value`` (``[new_tokens, num_kv_heads, head_dim]``, or flat with that many
+        elements) to sequence ``seq_id``.  Layer 0 grows the sequence (pages are taken from the pool as
+        needed); other layers write the same positions, so append layer 0 first."""
+        if seq_id not in self.active:
+            raise ValueError("PagedAttentionManager: invalid sequence id %d" % seq_id)
+        c = self.cache
+        key, value = key.reshape(-1, c.n_kv_heads, c.head_dim), value.reshape(-1, c.n_kv_heads, c.head_dim)
+        if key.shape != value.shape:
+            raise ValueError("append_kv: key %s and value %s differ" % (tuple(key.shape), tuple(value.shape)))
+        n = key.shape[0]
+        filled = self._filled.setdefault(seq_id, {})
+        start = filled.get(layer, 0)
+        if start + n > self.active[seq_id]:
+            self.extend(seq_id, start + n - self.active[seq_id])
+        dev = c.k[layer].device
+        pos = torch.arange(start, start + n, dtype=torch.int32, device=dev)
+        sid = torch.full((n,), seq_id, dtype=torch.int32, device=dev)
+        c.append(layer, key.to(device=dev, dtype=c.k[layer].dtype), value.to(device=dev, dtype=c.v[layer].dtype), pos, sid)
+        filled[layer] = start + n
+
+    def get_kv(self, seq_id: int, layer: int = 0):
+        """``(keys, values)`` of a sequence as contiguous ``[tokens, num_kv_heads, head_dim]`` tensors."""
+        if seq_id not in self.active:
+            raise ValueError("PagedAttentionManager: invalid sequence id %d" % seq_id)
+        return self.cache.gather(layer, seq_id, self._filled.get(seq_id, {}).get(layer, self.active[seq_id]))

@@ -679,3 +679,54 @@ def test_launchers_added_for_graph_capture_and_normalisation_gradients():
     assert torch.equal(be.relu_f32(torch.tensor([-1.0, 2.0])), torch.tensor([0.0, 2.0])) and "ordinal=0" in repr(be)
     with pytest.raises(AttributeError):
         be.no_such_kernel
+
+
+def test_cache_and_rope_objects_answer_the_reference_method_names():
+    from ferrotorch_b200 import nn as N
+
+    r = N.RotaryPositionEmbedding.with_convention(16, 64, 10000.0, N.RoPEConvention.Interleaved)
+    assert (r.dim, r.max_seq_len, r.base, r.convention, r.scaling) == (16, 64, 10000.0, "interleaved", None)
+    x = torch.randn(2, 3, 5, 16)
+    y = r.apply(x, 7)
+    cos, sin = r._tables("cpu")
+    c, s = cos[7:12], sin[7:12]
+    xe, xo = x[..., 0::2], x[..., 1::2]
+    torch.testing.assert_close(y, torch.stack([xe * c - xo * s, xe * s + xo * c], -1).flatten(-2))
+    half = N.RotaryPositionEmbedding.with_scaling(16, 64, 10000.0, "half", N.RoPEScaling.Linear(2.0))
+    assert half.convention == "half" and half.scaling == {"type": "linear", "factor": 2.0}
+    h = half.apply(x, 0)
+    ch, sh = half._tables("cpu")
+    x1, x2 = x[..., :8], x[..., 8:]
+    torch.testing.assert_close(h, torch.cat([x1 * ch[:5] - x2 * sh[:5], x2 * ch[:5] + x1 * sh[:5]], -1))
+    for bad in (lambda: N.RotaryPositionEmbedding.with_convention(15, 64), lambda: r.apply(x, 60), lambda: r.apply(torch.randn(1, 2, 8)),
+                lambda: N.RotaryPositionEmbedding.with_convention(16, 64, 1e4, "spiral")):
+        with pytest.raises(ValueError):
+            bad()
+    kv = N.KVCache.with_dims(32, 1, 2, 16, dtype=torch.float32)
+    assert kv.is_empty() and (kv.max_seq_len(), kv.batch_size(), kv.num_kv_heads(), kv.head_dim()) == (32, 1, 2, 16)
+    k1, v1 = torch.randn(1, 2, 3, 16), torch.randn(1, 2, 3, 16)
+    k, v = kv.update(k1, v1)
+    k2, _ = kv.update(k1 * 2, v1)
+    assert torch.equal(k, k1) and torch.equal(k2, torch.cat([k1, k1 * 2], 2)) and kv.seq_len() == 6 and not kv.is_empty()
+    with pytest.raises(ValueError):
+        kv.update(torch.randn(1, 3, 1, 16), torch.randn(1, 3, 1, 16))
+    kv.reset()
+    assert kv.is_empty()
+    # paged cache: data in and out through the manager
+    cache = N.PagedKVCache(2, 2, 8, num_blocks=16, max_seqs=4, max_seq_len=64, block_size=4, device="cpu", dtype=torch.float32)
+    m = N.PagedAttentionManager(cache)
+    a, b = m.add_sequence(), m.add_sequence()
+    ka, va = torch.randn(6, 2, 8), torch.randn(6, 2, 8)
+    m.append_kv(a, ka[:5], va[:5])
+    m.append_kv(b, torch.ones(3, 2, 8), torch.ones(3, 2, 8))
+    m.append_kv(a, ka[5:].reshape(-1), va[5:].reshape(-1))            # flat, as the reference takes it
+    m.append_kv(a, ka * 2, va * 2, layer=1)
+    assert all(torch.equal(p, q) for p, q in zip(m.get_kv(a), (ka, va))) and torch.equal(m.get_kv(a, 1)[0], ka * 2)
+    assert (cache.len(a), cache.len(), cache.num_pages(a), cache.num_pages()) == (6, 9, 2, 3) and cache.is_empty(3)
+    assert torch.equal(cache.get_keys(a), ka) and torch.equal(cache.get_values(b), torch.ones(3, 2, 8))
+    m.remove_sequence(a)
+    assert cache.num_pages() == 1
+    with pytest.raises(ValueError):
+        m.get_kv(a)
+    cache.free_all()
+    assert cache.is_empty() and cache.num_pages() == 0

@@ -112,3 +112,74 @@ def test_from_gguf_builds_the_model_the_file_describes(tmp_path):
     ids = torch.randint(0, 128, (1, 9), generator=torch.Generator().manual_seed(4))
     with torch.no_grad():
         assert torch.allclose(model(ids).float(), ours(ids).float(), atol=5e-3)       # weights went through fp16
+
+
+def test_inferencer_logits_and_sparsity_profile_match_hooks_on_transformers():
+    """``LlamaGpuInferencer`` (on the host here): last-position and all-position logits, and the
+    profiled forward's per-head / per-block magnitudes and bootstrap state against the same
+    quantities tapped from the ``transformers`` twin with hooks on ``o_proj`` / ``down_proj``."""
+    from ferrotorch_b200.models.inferencer import GraphedDecoder, LlamaGpuInferencer
+
+    hf, ours = _pair()
+    inf = LlamaGpuInferencer(ours, device="cpu")
+    ids = torch.randint(0, 128, (11,), generator=torch.Generator().manual_seed(4)).tolist()
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([ids])).logits[0]
+    assert torch.allclose(inf.forward_logits_from_ids_all(ids), want, atol=2e-4, rtol=1e-4)
+    assert torch.allclose(inf.forward_from_ids(ids), want[-1], atol=2e-4, rtol=1e-4)
+    # taps on the twin
+    S, Hq, D, I = len(ids), 4, 16, 112
+    attn_in, mlp_in, layer_out = [], [], []
+    hs = []
+    for layer in hf.model.layers:
+        hs.append(layer.self_attn.o_proj.register_forward_pre_hook(lambda m, a: attn_in.append(a[0].detach())))
+        hs.append(layer.mlp.down_proj.register_forward_pre_hook(lambda m, a: mlp_in.append(a[0].detach())))
+        hs.append(layer.register_forward_hook(lambda m, a, o: layer_out.append((o[0] if isinstance(o, tuple) else o).detach())))
+    with torch.no_grad():
+        hf(input_ids=torch.tensor([ids]))
+    for h in hs:
+        h.remove()
+    block, nb = 16, 7
+    prof = inf.forward_from_ids_profiled_with_bootstrap(ids, block, nb, bootstrap_k=1)
+    assert prof.seq_len == S and prof.hidden_size == 64 and prof.bootstrap_k == 1
+    assert prof.attn_magnitudes.shape == (S, 2, Hq) and prof.mlp_magnitudes.shape == (S, 2, nb)
+    for li in range(2):
+        a = attn_in[li].reshape(S, Hq, D).abs().amax(-1)
+        m = mlp_in[li].reshape(S, nb, block).abs().amax(-1)
+        assert torch.allclose(prof.attn_magnitudes[:, li], a, atol=1e-4, rtol=1e-4)
+        assert torch.allclose(prof.mlp_magnitudes[:, li], m, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(prof.bootstrap_hidden, layer_out[0].reshape(S, 64), atol=1e-4, rtol=1e-4)
+    assert prof.attn_at(3, 1, 2) == float(prof.attn_magnitudes[3, 1, 2])
+    # the local plain-act variant: |gated * (y @ W_down)| per block, y the layer's output
+    pl = inf.forward_from_ids_profiled_with_bootstrap(ids, block, nb, None, True)
+    for li, layer in enumerate(hf.model.layers):
+        z = layer_out[li].reshape(S, 64) @ layer.mlp.down_proj.weight.detach()
+        m = (mlp_in[li].reshape(S, I) * z).reshape(S, nb, block).abs().amax(-1)
+        assert torch.allclose(pl.mlp_magnitudes[:, li], m, atol=1e-4, rtol=1e-3)
+    assert pl.bootstrap_hidden is None and torch.equal(pl.attn_magnitudes, prof.attn_magnitudes)
+    assert inf.forward_from_ids_profiled(ids, block, nb).bootstrap_hidden is None
+    for bad in ((0, 7), (16, 6), (16, 0)):
+        with pytest.raises(ValueError):
+            inf.forward_from_ids_profiled(ids, *bad)
+    with pytest.raises(ValueError):
+        inf.forward_from_ids_profiled_with_bootstrap(ids, block, nb, 3)
+    with pytest.raises(ValueError):
+        inf.forward_from_ids([128])
+    # the decoder object: same logits as the single-token forward, calls counted
+    dec = GraphedDecoder.capture(inf, warmup_token=1)
+    for i, tok in enumerate((5, 99, 5)):
+        assert torch.equal(dec.decode_step(tok), inf.forward_from_ids([tok])) and dec.num_replays() == i + 1
+    with pytest.raises(ValueError):
+        dec.decode_step(1000)
+    assert "num_replays=3" in repr(dec)
+    # the value cache walks to the same logits, and the 4-bit HQQ container loads
+    from ferrotorch_b200.models.llama_compat import LlamaKvCache
+
+    cache = LlamaKvCache.empty()
+    for i, tok in enumerate(ids[:5]):
+        logits, cache = ours.forward_one_with_cache(tok, cache)
+        assert torch.allclose(logits.float(), want[i], atol=2e-4, rtol=1e-4) and len(cache) == i + 1
+    assert cache.layers[0].k.shape == (2, 5, 16)
+    assert ours.forward_from_ids(ids).shape == (1, S, 128)
+    with pytest.raises(ValueError):
+        ours.forward_one_with_cache(1, LlamaKvCache.empty().extend([(torch.zeros(2, 1, 16), torch.zeros(2, 1, 16))] * 3))
