@@ -16,14 +16,14 @@ from torch.optim.lr_scheduler import (ChainedScheduler, ConstantLR, CosineAnneal
                                       CosineAnnealingWarmRestarts, CyclicLR, ExponentialLR, LambdaLR, LinearLR,
                                       MultiplicativeLR, MultiStepLR, OneCycleLR, PolynomialLR, ReduceLROnPlateau,
                                       SequentialLR, StepLR)
-from torch.optim.swa_utils import SWALR, AveragedModel  # noqa: F401
+from torch.optim.swa_utils import SWALR  # noqa: F401
 
 try:  # torch >= 2.3
     from torch.amp import GradScaler  # noqa: F401
 except ImportError:  # pragma: no cover
     from torch.cuda.amp import GradScaler  # noqa: F401
 
-from .extra import (EMA, Adafactor, GradientAccumulator, Muon, NaturalGradient, WarmupLR,  # noqa: F401
+from .extra import (EMA, Adafactor, AveragedModel, GradientAccumulator, Muon, NaturalGradient, WarmupLR,  # noqa: F401
                     cosine_warmup_scheduler)
 from .fused import FusedAdamW, FusedSGD  # noqa: F401
 

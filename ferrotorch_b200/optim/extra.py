@@ -106,33 +106,78 @@ class NaturalGradient(Optimizer):
 
 
 class EMA:
-    """Exponential moving average of a module's parameters, kept on the parameters' device (the
-    reference's EMA callback pulls every parameter to the host each step,
-    ferrotorch-train/src/learner.rs:625-637)."""
+    """Exponential moving average of parameters, kept on the parameters' device and updated with
+    multi-tensor ops (the reference's EMA callback pulls every parameter to the host each step,
+    ferrotorch-train/src/learner.rs:625-637; its ``ExponentialMovingAverage`` is
+    ferrotorch-optim/src/ema.rs:93-400, whose method names this class answers to).  Built from a
+    module or from a list of parameters; the methods that take ``params`` default to the ones given
+    at construction."""
 
-    def __init__(self, module: torch.nn.Module, decay: float = 0.999):
+    def __init__(self, module_or_params, decay: float = 0.999):
+        if not 0.0 <= decay <= 1.0:
+            raise ValueError("EMA decay must be in [0, 1], got %r" % (decay,))
         self.decay = decay
-        self.params = [p for p in module.parameters() if p.requires_grad]
+        ps = module_or_params.parameters() if isinstance(module_or_params, torch.nn.Module) else module_or_params
+        self.params = [p for p in ps if p.requires_grad]
         self.shadow = [p.detach().clone().float() for p in self.params]
         self._backup = None
+        self._n = 0
+        self._warmup = False
+
+    def with_foreach(self, params=None) -> "EMA":
+        """The shadow tensors already live on the parameters' device and are updated with foreach ops."""
+        return self
+
+    def with_decay_warmup(self, use_warmup: bool = True) -> "EMA":
+        """Ramp the decay as ``min(decay, (1 + n) / (10 + n))`` over the first updates."""
+        self._warmup = bool(use_warmup)
+        return self
+
+    def num_updates(self) -> int:
+        return self._n
+
+    def effective_decay(self) -> float:
+        return min(self.decay, (1.0 + self._n) / (10.0 + self._n)) if self._warmup else self.decay
+
+    def _check(self, params):
+        params = self.params if params is None else list(params)
+        if len(params) != len(self.shadow):
+            raise ValueError("EMA: %d parameters given, %d tracked" % (len(params), len(self.shadow)))
+        return params
 
     @torch.no_grad()
-    def update(self) -> None:
-        torch._foreach_mul_(self.shadow, self.decay)
-        torch._foreach_add_(self.shadow, [p.detach().float() for p in self.params], alpha=1 - self.decay)
+    def update(self, params=None) -> None:
+        params = self._check(params)
+        self._n += 1
+        d = self.effective_decay()
+        torch._foreach_mul_(self.shadow, d)
+        torch._foreach_add_(self.shadow, [p.detach().float() for p in params], alpha=1 - d)
 
     @torch.no_grad()
-    def apply(self) -> None:
-        self._backup = [p.detach().clone() for p in self.params]
-        for p, s in zip(self.params, self.shadow):
+    def apply(self, params=None) -> None:
+        """Swap the averaged weights in (the originals are kept for :meth:`restore`)."""
+        params = self._check(params)
+        self._backup = [p.detach().clone() for p in params]
+        for p, s in zip(params, self.shadow):
             p.copy_(s.to(p.dtype))
 
+    apply_shadow = apply
+
     @torch.no_grad()
-    def restore(self) -> None:
+    def restore(self, params=None) -> None:
+        params = self._check(params)
         if self._backup is not None:
-            for p, b in zip(self.params, self._backup):
+            for p, b in zip(params, self._backup):
                 p.copy_(b)
             self._backup = None
+
+    def shadow_params(self) -> list:
+        return self.shadow
+
+    def shadow_values(self, index: int) -> torch.Tensor:
+        if not 0 <= index < len(self.shadow):
+            raise IndexError("EMA.shadow_values: index %d of %d" % (index, len(self.shadow)))
+        return self.shadow[index]
 
     def state_dict(self):
         return {"decay": self.decay, "shadow": self.shadow}
@@ -190,3 +235,57 @@ def diff_sgd_momentum_step(params, grads, bufs, lr: float, momentum: float = 0.9
     ``(new_params, new_bufs)``."""
     new_bufs = [momentum * b + g for b, g in zip(bufs, grads)]
     return [p - lr * b for p, b in zip(params, new_bufs)], new_bufs
+
+
+
+class AveragedModel(torch.optim.swa_utils.AveragedModel):
+    """torch's averaged model (a deep copy whose parameters are the running average) with the
+    reference's entry points on top (ferrotorch-optim/src/swa.rs:133-400): built ``from_module`` with an
+    :class:`~ferrotorch_b200.optim.configs.AveragingStrategy`, updated from a module or from a parameter
+    list, and written back into a module or a parameter list."""
+
+    def __init__(self, model, device=None, avg_fn=None, multi_avg_fn=None, use_buffers=False, strategy=None, decay: float = 0.999):
+        from .configs import AveragingStrategy
+
+        if isinstance(strategy, tuple):
+            strategy, decay = strategy
+        if strategy is not None and multi_avg_fn is None and avg_fn is None:
+            if strategy is AveragingStrategy.Ema and not 0.0 <= decay <= 1.0:
+                raise ValueError("AveragedModel: EMA decay must be in [0, 1], got %r" % (decay,))
+            multi_avg_fn = strategy.avg_fn(decay)
+        super().__init__(model, device, avg_fn, multi_avg_fn, use_buffers)
+        self._strategy = strategy if strategy is not None else AveragingStrategy.Swa
+
+    @classmethod
+    def from_module(cls, module, strategy=None, decay: float = 0.999) -> "AveragedModel":
+        return cls(module, strategy=strategy, decay=decay)
+
+    def strategy(self):
+        return self._strategy
+
+    def with_foreach(self, params=None) -> "AveragedModel":
+        return self                      # the average is updated with multi-tensor ops already
+
+    def update_parameters_from_module(self, module) -> None:
+        self.update_parameters(module)
+
+    def averaged_params(self) -> list:
+        return [p.detach() for p in self.module.parameters()]
+
+    def averaged_values(self, index: int) -> torch.Tensor:
+        ps = self.averaged_params()
+        if not 0 <= index < len(ps):
+            raise IndexError("AveragedModel.averaged_values: index %d of %d" % (index, len(ps)))
+        return ps[index]
+
+    @torch.no_grad()
+    def apply_to(self, params) -> None:
+        """Copy the averaged values into ``params`` (same order as the module's parameters)."""
+        params, avg = list(params), self.averaged_params()
+        if len(params) != len(avg):
+            raise ValueError("AveragedModel.apply_to: %d parameters given, %d averaged" % (len(params), len(avg)))
+        for p, a in zip(params, avg):
+            p.copy_(a.to(p.dtype))
+
+    def apply_to_module(self, module) -> None:
+        self.apply_to(module.parameters())

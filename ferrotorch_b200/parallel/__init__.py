@@ -6,7 +6,7 @@ from .backend import (BackendUnavailable, DistributedError, Group, HybridGroup, 
 from .elastic import FileStore, Heartbeat, RankFailure, TorchStore, survivors  # noqa: F401
 from .fsdp import FSDP, ShardingStrategy, SyncBatchNorm2d  # noqa: F401
 from .host_ddp import DDP  # noqa: F401
-from .mesh import DeviceMesh, DTensor, Partial, Replicate, Shard  # noqa: F401
+from .mesh import DeviceMesh, DTensor, MeshTensor, Partial, Replicate, Shard  # noqa: F401
 from .pipeline import Pipeline  # noqa: F401
 from .vocab_sampling import sample_reference, sample_vocab_parallel, shared_uniform  # noqa: F401
 from .dist_checkpoint import (AsyncDistributedCheckpointer, PendingCollective, RpcAgent, all_gather_async,  # noqa: F401,E402

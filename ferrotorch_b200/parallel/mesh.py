@@ -28,6 +28,32 @@ class DeviceMesh:
         for s in self.shape:
             self.size *= s
 
+    @classmethod
+    def new(cls, shape: Sequence[int], world_size: int) -> "DeviceMesh":
+        """Validating constructor (device_mesh.rs:48): the mesh must cover exactly ``world_size`` ranks."""
+        m = cls(shape)
+        if m.size != world_size:
+            raise ValueError("mesh %r covers %d ranks, world size is %d" % (tuple(shape), m.size, world_size))
+        return m
+
+    @classmethod
+    def new_with_names(cls, shape: Sequence[int], dim_names: Sequence[str], world_size: int) -> "DeviceMesh":
+        if len(set(dim_names)) != len(tuple(dim_names)):
+            raise ValueError("mesh dimension names must be distinct: %r" % (tuple(dim_names),))
+        m = cls(shape, dim_names)
+        if m.size != world_size:
+            raise ValueError("mesh %r covers %d ranks, world size is %d" % (tuple(shape), m.size, world_size))
+        return m
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    def dim_index(self, name: str) -> int:
+        if name not in self.dim_names:
+            raise ValueError("mesh has no dimension named %r (names: %r)" % (name, self.dim_names))
+        return self.dim_names.index(name)
+
     def _dim(self, dim) -> int:
         return self.dim_names.index(dim) if isinstance(dim, str) else int(dim)
 
@@ -158,3 +184,105 @@ class DTensor:
 
     def full_tensor(self) -> torch.Tensor:
         return self.redistribute(Replicate()).local
+
+    # ---- the reference's accessors (dtensor.rs:162-190) for the one-axis form
+    def to_local(self) -> torch.Tensor:
+        return self.local
+
+    @property
+    def shape(self) -> tuple:
+        return self.global_shape
+
+    @property
+    def placements(self) -> list:
+        return [self.placement]
+
+    def numel(self) -> int:
+        n = 1
+        for d in self.global_shape:
+            n *= d
+        return n
+
+    @staticmethod
+    def from_local(local: torch.Tensor, mesh: DeviceMesh, placements, global_shape: Sequence[int] | None = None, groups=None
+                   ) -> "MeshTensor":
+        """A tensor laid out over every axis of ``mesh`` (dtensor.rs:115): one placement per mesh
+        dimension.  ``groups`` (one :class:`~.backend.Group` per mesh dimension, e.g.
+        ``[mesh.subgroup(world, d) for d in range(mesh.ndim)]``) makes ``redistribute`` move data;
+        without them it rewrites the placement list only, as the reference does."""
+        return MeshTensor(local, mesh, list(placements), global_shape, groups)
+
+    @staticmethod
+    def from_local_replicated(local: torch.Tensor, mesh: DeviceMesh, groups=None) -> "MeshTensor":
+        return MeshTensor(local, mesh, [Replicate()] * mesh.ndim, tuple(local.shape), groups)
+
+
+class MeshTensor:
+    """A local shard, a mesh, and one placement per mesh dimension (the reference's ``DTensor``,
+    ferrotorch-distributed/src/dtensor.rs:88-230).  A tensor dimension may be sharded by at most one
+    mesh dimension.  ``redistribute`` goes mesh dimension by mesh dimension, each step a collective
+    on that dimension's group (all-gather, reduce-scatter, all-reduce or a local slice)."""
+
+    def __init__(self, local: torch.Tensor, mesh: DeviceMesh, placements, global_shape=None, groups=None):
+        if len(placements) != mesh.ndim:
+            raise ValueError("DTensor.from_local: %d placements for a mesh of %d dimensions" % (len(placements), mesh.ndim))
+        if groups is not None:
+            groups = list(groups)
+            if len(groups) != mesh.ndim or any(g.world_size != n for g, n in zip(groups, mesh.shape)):
+                raise ValueError("one group per mesh dimension, sized like it: mesh %r" % (mesh.shape,))
+        sharded = [p.dim for p in placements if isinstance(p, Shard)]
+        if len(set(sharded)) != len(sharded):
+            raise ValueError("a tensor dimension is sharded by two mesh dimensions: %r" % (placements,))
+        for mi, p in enumerate(placements):
+            if isinstance(p, Shard) and not 0 <= p.dim < local.dim():
+                raise ValueError("mesh dim %d shards tensor dim %d of a %d-d tensor" % (mi, p.dim, local.dim()))
+        if global_shape is None:
+            gs = list(local.shape)
+            for p, n in zip(placements, mesh.shape):
+                if isinstance(p, Shard):
+                    gs[p.dim] *= n
+            global_shape = gs
+        self.local, self.mesh, self._placements, self.global_shape, self.groups = local, mesh, list(placements), tuple(global_shape), groups
+
+    def to_local(self) -> torch.Tensor:
+        return self.local
+
+    @property
+    def shape(self) -> tuple:
+        return self.global_shape
+
+    @property
+    def placements(self) -> list:
+        return list(self._placements)
+
+    def numel(self) -> int:
+        n = 1
+        for d in self.global_shape:
+            n *= d
+        return n
+
+    def redistribute(self, target_placements) -> "MeshTensor":
+        target = list(target_placements)
+        if len(target) != self.mesh.ndim:
+            raise ValueError("redistribute: %d placements for a mesh of %d dimensions" % (len(target), self.mesh.ndim))
+        for mi, p in enumerate(target):
+            if isinstance(p, Shard) and not 0 <= p.dim < len(self.global_shape):
+                raise ValueError("mesh dim %d shards tensor dim %d of a %d-d tensor" % (mi, p.dim, len(self.global_shape)))
+        if self.groups is None:
+            return MeshTensor(self.local, self.mesh, target, self.global_shape, None)
+        local, cur = self.local, list(self._placements)
+        # first every step that frees a tensor dimension (to Replicate), then the ones that shard, so that a
+        # tensor dimension handed from one mesh dimension to another is never sharded twice on the way
+        order = [i for i in range(self.mesh.ndim) if not isinstance(target[i], Shard)] + \
+                [i for i in range(self.mesh.ndim) if isinstance(target[i], Shard)]
+        for mi in order:
+            if cur[mi] == target[mi]:
+                continue
+            if isinstance(target[mi], Shard) and any(isinstance(c, Shard) and c.dim == target[mi].dim for j, c in enumerate(cur) if j != mi):
+                raise ValueError("tensor dim %d would be sharded by two mesh dimensions" % target[mi].dim)
+            local = DTensor(local, self.groups[mi], cur[mi]).redistribute(target[mi]).local
+            cur[mi] = target[mi]
+        return MeshTensor(local, self.mesh, cur, self.global_shape, self.groups)
+
+    def full_tensor(self) -> torch.Tensor:
+        return self.redistribute([Replicate()] * self.mesh.ndim).local

@@ -56,6 +56,32 @@ class ProfileSchedule:
         cycle = self.wait + self.warmup + self.active
         return self.step_num > 0 and self.step_num % cycle == 0
 
+    # ---- the reference's accessors (schedule.rs:163-240)
+    def set_on_trace_ready(self, callback) -> None:
+        """``callback(cycle_number)`` after the last active step of every cycle (zero-based)."""
+        self._cycle_cb = callback
+
+    def phase(self) -> str:
+        return self.state()
+
+    def is_active(self) -> bool:
+        return self.state() == "active"
+
+    def current_step(self) -> int:
+        return self.step_num
+
+    def current_cycle(self) -> int:
+        return self.step_num // (self.wait + self.warmup + self.active)
+
+    def step(self) -> str:
+        """Advance one step; returns the phase the schedule is in afterwards."""
+        self.step_num += 1
+        cycle = self.wait + self.warmup + self.active
+        cb = getattr(self, "_cycle_cb", None)
+        if cb is not None and self.cycle_finished() and (not self.repeat or self.step_num <= cycle * self.repeat):
+            cb(self.step_num // cycle - 1)
+        return self.state()
+
 
 def estimate_flops(op: str, shapes) -> float | None:
     """FLOPs from shapes for the common ops (flops.rs:53)."""
@@ -88,12 +114,21 @@ class Profiler:
         self.cfg, self.schedule = config or ProfileConfig(), schedule
         self.events: list[ProfileEvent] = []
         self.memory: list[tuple[float, str, int]] = []
+        self.memory_categories: list[tuple[str, int]] = []
         self._pending: list = []
         self._t0 = time.perf_counter()
+        self._stopped = False
 
     # ---- recording
     def _recording(self) -> bool:
-        return self.schedule is None or self.schedule.state() == "active"
+        return not self._stopped and (self.schedule is None or self.schedule.state() == "active")
+
+    def is_active(self) -> bool:
+        return self._recording()
+
+    def stop(self) -> None:
+        """Later ``scope`` / ``record*`` calls record nothing; what was recorded stays (profiler.rs:263)."""
+        self._stopped = True
 
     def _now_us(self) -> float:
         return (time.perf_counter() - self._t0) * 1e6
@@ -129,7 +164,26 @@ class Profiler:
                 self.record_memory(name, torch.cuda.memory_allocated())
 
     def record(self, name: str, dur_us: float, category: str = "manual") -> None:
-        self.events.append(ProfileEvent(name, category, self._now_us(), dur_us))
+        if self._recording():
+            self.events.append(ProfileEvent(name, category, self._now_us(), dur_us))
+
+    def record_with_duration(self, name: str, category: str, duration_us: float) -> None:
+        """The reference's argument order (profiler.rs:155)."""
+        self.record(name, duration_us, category)
+
+    def record_memory_categorized(self, name: str, nbytes: int, category: str = "other") -> None:
+        """A memory event (positive = allocation, negative = free) filed under a
+        :class:`MemoryCategory`; :meth:`ProfileReport.memory_by_category` nets them per category."""
+        if self._recording():
+            self.memory.append((self._now_us(), name, int(nbytes)))
+            self.memory_categories.append((str(category), int(nbytes)))
+
+    def flush_cuda_kernels(self) -> None:
+        self.flush()
+
+    def pending_cuda_count(self) -> int:
+        """Device scopes recorded but not yet read back (read by :meth:`flush`)."""
+        return len(self._pending)
 
     def push_gpu_event(self, name: str, timing: "GpuTimingPair", category: str = "kernel") -> None:
         """Add a device interval measured elsewhere (profiler.rs:200): duration = end - start, never negative."""
@@ -150,7 +204,7 @@ class Profiler:
     def step(self) -> None:
         if self.schedule is None:
             return
-        self.schedule.step_num += 1
+        self.schedule.step()
         if self.schedule.cycle_finished():
             self.flush()
             if self.schedule.on_trace_ready is not None:
@@ -239,6 +293,7 @@ class ProfileReport:
         profiler.flush()
         self.events = list(profiler.events)
         self.memory = list(profiler.memory)
+        self._memory_categories = list(profiler.memory_categories)
         self._ops = [OpSummary(a["name"], a["device"], a["count"], a["total_us"], a["flops"])
                      for a in profiler.summary().values()]
         self._table, self._trace = profiler.table(), profiler.chrome_trace_json()
@@ -261,6 +316,50 @@ class ProfileReport:
     def save_chrome_trace(self, path: str) -> None:
         with open(path, "w") as f:
             f.write(self._trace)
+
+    # ---- the reference's accessors (report.rs:94-560)
+    def top_ops(self, n: int = 10) -> list[OpSummary]:
+        return self.top(n)
+
+    def total_time_us(self) -> float:
+        return self.total_us()
+
+    def has_gpu_events(self) -> bool:
+        return any(e.device == "cuda" for e in self.events)
+
+    def has_stack_traces(self) -> bool:
+        return False                      # ranges are named by the caller; no stacks are collected
+
+    def total_flops(self) -> float:
+        """FLOPs of the recorded ranges; a range timed on both clocks is counted once."""
+        seen_dev = {(e.name, e.start_us) for e in self.events if e.device == "cuda"}
+        return float(sum(e.flops or 0.0 for e in self.events if e.device == "cuda" or (e.name, e.start_us) not in seen_dev))
+
+    def flops_per_second(self) -> float:
+        """Total FLOPs over the time of the ranges that carry a FLOP count (device time where there is one)."""
+        seen_dev = {(e.name, e.start_us) for e in self.events if e.device == "cuda"}
+        us = sum(e.dur_us for e in self.events if e.flops and (e.device == "cuda" or (e.name, e.start_us) not in seen_dev))
+        return self.total_flops() / (us * 1e-6) if us > 0 else 0.0
+
+    def memory_by_category(self) -> list[tuple[str, int]]:
+        """Net bytes per category, largest magnitude first."""
+        net: dict = {}
+        for cat, b in self._memory_categories:
+            net[cat] = net.get(cat, 0) + b
+        return sorted(net.items(), key=lambda kv: -abs(kv[1]))
+
+    def save_tensorboard_trace(self, logdir: str, run_id: str | None = None, hostname: str | None = None) -> str:
+        """Write the Chrome trace where TensorBoard's profile plugin looks for it:
+        ``<logdir>/plugins/profile/<run_id>/<hostname>.pt.trace.json``; returns that path."""
+        import os
+        import socket
+
+        target = os.path.join(logdir, "plugins", "profile", run_id or "run0")
+        os.makedirs(target, exist_ok=True)
+        path = os.path.join(target, "%s.pt.trace.json" % (hostname or socket.gethostname() or "localhost"))
+        with open(path, "w") as f:
+            f.write(self._trace)
+        return os.path.abspath(path)
 
 
 class CudaKernelScope:

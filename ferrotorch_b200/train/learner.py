@@ -120,6 +120,40 @@ class TrainingHistory:
     def series(self, key: str, split: str = "train") -> list:
         return [(getattr(e, split) or {}).get(key) for e in self.epochs]
 
+    # ---- the reference's accessors (ferrotorch-train/src/history.rs:158-210)
+    def push(self, result: EpochResult) -> None:
+        self.epochs.append(result)
+
+    def __len__(self) -> int:
+        return len(self.epochs)
+
+    def len(self) -> int:
+        return len(self.epochs)
+
+    def is_empty(self) -> bool:
+        return not self.epochs
+
+    def train_losses(self) -> list:
+        return self.series("loss", "train")
+
+    def val_losses(self) -> list:
+        """One entry per epoch; ``None`` where an epoch had no validation pass."""
+        return self.series("loss", "val")
+
+    def _best_loss(self, split: str):
+        vals = [(v, i) for i, v in enumerate(self.series("loss", split)) if v is not None]
+        if not vals:
+            return None
+        v, i = min(vals)
+        return i, v
+
+    def best_train_loss(self):
+        """``(epoch index, loss)`` of the lowest training loss, or ``None`` for an empty history."""
+        return self._best_loss("train")
+
+    def best_val_loss(self):
+        return self._best_loss("val")
+
 
 class Callback:
     def on_train_start(self, learner): ...

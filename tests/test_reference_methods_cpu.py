@@ -1,0 +1,167 @@
+"""Method-level parity: classes that share a name with a reference type answer the reference's
+method names with the reference's meaning (each block cites the file whose ``impl`` it follows)."""
+import json
+import threading
+
+import pytest
+import torch
+
+from ferrotorch_b200 import optim as O
+from ferrotorch_b200 import profiler as P
+from ferrotorch_b200 import train as T
+
+
+def test_exponential_moving_average_methods():
+    # ferrotorch-optim/src/ema.rs:93-400
+    m = torch.nn.Linear(3, 2)
+    w0 = m.weight.detach().clone()
+    e = O.ExponentialMovingAverage(list(m.parameters()), 0.9).with_foreach().with_decay_warmup(True)
+    assert e.num_updates() == 0 and e.decay == 0.9
+    with torch.no_grad():
+        m.weight += 1
+    e.update()
+    assert e.num_updates() == 1 and abs(e.effective_decay() - 2 / 11) < 1e-12          # min(0.9, (1 + 1) / (10 + 1))
+    torch.testing.assert_close(e.shadow_values(0), w0 * (2 / 11) + (w0 + 1) * (9 / 11))
+    assert len(e.shadow_params()) == 2
+    e.apply_shadow()
+    torch.testing.assert_close(m.weight.detach(), e.shadow_values(0))
+    e.restore()
+    torch.testing.assert_close(m.weight.detach(), w0 + 1)
+    other = torch.nn.Linear(3, 2)
+    e.apply_shadow(list(other.parameters()))                                           # an explicit parameter list
+    torch.testing.assert_close(other.weight.detach(), e.shadow_values(0))
+    with pytest.raises(ValueError):
+        e.update(list(m.parameters())[:1])
+    with pytest.raises(IndexError):
+        e.shadow_values(2)
+    with pytest.raises(ValueError):
+        O.ExponentialMovingAverage(m, 1.5)
+    plain = O.ExponentialMovingAverage(m, 0.5)                                          # a module works too; no warm-up
+    plain.update()
+    assert plain.effective_decay() == 0.5
+
+
+def test_averaged_model_methods():
+    # ferrotorch-optim/src/swa.rs:133-400
+    m = torch.nn.Linear(3, 2)
+    w0 = m.weight.detach().clone()
+    a = O.AveragedModel.from_module(m, O.AveragingStrategy.Swa).with_foreach()
+    for _ in range(2):
+        with torch.no_grad():
+            m.weight += 2
+        a.update_parameters_from_module(m)
+    assert int(a.n_averaged) == 2 and a.strategy() is O.AveragingStrategy.Swa
+    torch.testing.assert_close(a.averaged_values(0), w0 + 3)                            # mean of w0 + 2 and w0 + 4
+    assert len(a.averaged_params()) == 2
+    m2 = torch.nn.Linear(3, 2)
+    a.apply_to_module(m2)
+    torch.testing.assert_close(m2.weight.detach(), w0 + 3)
+    m3 = torch.nn.Linear(3, 2)
+    a.apply_to(m3.parameters())
+    torch.testing.assert_close(m3.bias.detach(), m.bias.detach())
+    ema = O.AveragedModel(m, strategy=(O.AveragingStrategy.Ema, 0.5))
+    ema.update_parameters(m)                                                            # first update copies
+    with torch.no_grad():
+        m.weight += 2
+    ema.update_parameters(m)
+    torch.testing.assert_close(ema.averaged_values(0), w0 + 5)                          # 0.5 * (w0 + 4) + 0.5 * (w0 + 6)
+    with pytest.raises(ValueError):
+        a.apply_to(list(m.parameters())[:1])
+    with pytest.raises(ValueError):
+        O.AveragedModel(m, strategy=(O.AveragingStrategy.Ema, 2.0))
+    assert torch.equal(a(torch.ones(1, 3)), a.module(torch.ones(1, 3)))                 # still torch's callable wrapper
+
+
+def test_training_history_methods():
+    # ferrotorch-train/src/history.rs:158-210
+    h = T.TrainingHistory()
+    assert h.is_empty() and h.len() == 0 and h.best_val_loss() is None and h.best_train_loss() is None
+    h.push(T.EpochResult(0, {"loss": 2.0}, {"loss": 2.5}))
+    h.push(T.EpochResult(1, {"loss": 1.0}))
+    h.push(T.EpochResult(2, {"loss": 1.5}, {"loss": 1.2}))
+    assert len(h) == 3 and h.train_losses() == [2.0, 1.0, 1.5] and h.val_losses() == [2.5, None, 1.2]
+    assert h.best_train_loss() == (1, 1.0) and h.best_val_loss() == (2, 1.2)
+
+
+def test_profile_schedule_profiler_and_report_methods(tmp_path):
+    # ferrotorch-profiler/src/schedule.rs:138-240, profiler.rs:121-330, report.rs:94-560
+    calls = []
+    s = P.ProfileSchedule(1, 1, 2, 2)
+    s.set_on_trace_ready(calls.append)
+    phases = [s.phase()] + [s.step() for _ in range(9)]
+    assert phases == ["wait", "warmup", "active", "active", "wait", "warmup", "active", "active", "done", "done"]
+    assert calls == [0, 1] and s.current_step() == 9 and s.current_cycle() == 2 and not s.is_active()
+    pr = P.Profiler(P.ProfileConfig(cuda_events=False))
+    with pr.scope("mm", shapes=[(4, 8), (8, 16)], op="matmul"):
+        pass
+    pr.record_with_duration("x", "manual", 12.0)
+    pr.record_memory_categorized("w", 1000, P.MemoryCategory.PARAMETERS)
+    pr.record_memory_categorized("a", 500, P.MemoryCategory.ACTIVATIONS)
+    pr.record_memory_categorized("a", -200, P.MemoryCategory.ACTIVATIONS)
+    assert pr.is_active() and pr.pending_cuda_count() == 0
+    pr.flush_cuda_kernels()
+    pr.stop()
+    pr.record_with_duration("late", "manual", 5.0)
+    pr.record_memory_categorized("late", 7, P.MemoryCategory.OTHER)
+    assert not pr.is_active() and [e.name for e in pr.events] == ["mm", "x"]
+    r = pr.report()
+    assert r.total_flops() == 2 * 4 * 8 * 16 and r.flops_per_second() > 0
+    assert r.memory_by_category() == [("parameters", 1000), ("activations", 300)]
+    assert not r.has_gpu_events() and not r.has_stack_traces()
+    assert [o.name for o in r.top_ops(5)] == ["x", "mm"] or [o.name for o in r.top_ops(5)] == ["mm", "x"]
+    assert abs(r.total_time_us() - sum(e.dur_us for e in r.events)) < 1e-6
+    path = r.save_tensorboard_trace(str(tmp_path), None, "nodeA")
+    assert path.endswith("plugins/profile/run0/nodeA.pt.trace.json") and "traceEvents" in json.load(open(path))
+    assert r.save_tensorboard_trace(str(tmp_path), "second").startswith(str(tmp_path / "plugins" / "profile" / "second"))
+    # a schedule driven through the profiler still hands the profiler to its callback
+    seen = []
+    pr2 = P.Profiler(P.ProfileConfig(cuda_events=False), P.ProfileSchedule(0, 0, 1, 2, on_trace_ready=seen.append))
+    for _ in range(3):
+        pr2.step()
+    assert seen == [pr2, pr2, pr2][:len(seen)] and len(seen) >= 2
+
+
+def test_device_mesh_and_mesh_tensor_methods():
+    # ferrotorch-distributed/src/device_mesh.rs:48-203, dtensor.rs:88-230
+    from ferrotorch_b200.parallel import DeviceMesh, DTensor, Partial, Replicate, Shard
+    from ferrotorch_b200.parallel.backend import SimulatedGroup
+
+    mesh = DeviceMesh.new_with_names([2, 2], ["dp", "tp"], 4)
+    assert (mesh.ndim, mesh.size, mesh.shape, mesh.dim_index("tp")) == (2, 4, (2, 2), 1)
+    for bad in (lambda: DeviceMesh.new([2, 2], 6), lambda: DeviceMesh.new_with_names([2, 2], ["a", "a"], 4), lambda: mesh.dim_index("pp")):
+        with pytest.raises(ValueError):
+            bad()
+    world = SimulatedGroup.create_group(4)
+    full = torch.arange(48.0).reshape(8, 6)
+    res = {}
+
+    def run(r):
+        groups = [mesh.subgroup(world[r], d) for d in range(2)]
+        c = mesh.coords(r)
+        local = full.chunk(2, 0)[c[0]].chunk(2, 1)[c[1]].contiguous()
+        t = DTensor.from_local(local, mesh, [Shard(0), Shard(1)], groups=groups)
+        assert t.shape == (8, 6) and t.numel() == 48 and t.placements == [Shard(0), Shard(1)] and t.mesh is mesh
+        assert t.to_local() is local
+        a = t.redistribute([Replicate(), Shard(1)])
+        b = a.redistribute([Shard(1), Replicate()])             # tensor dim 1 handed from mesh dim 1 to mesh dim 0
+        p = DTensor.from_local(torch.ones(2, 2) * (r + 1), mesh, [Partial(), Replicate()], groups=groups)
+        rep = DTensor.from_local_replicated(full, mesh, groups=groups).redistribute([Shard(0), Shard(1)])
+        res[r] = (a.local, b.local, b.full_tensor(), p.redistribute([Replicate(), Replicate()]).local, rep.local, local)
+
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(4)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    for r in range(4):
+        c = mesh.coords(r)
+        a, b, f, p, rep, local = res[r]
+        assert torch.equal(a, full.chunk(2, 1)[c[1]]) and torch.equal(b, full.chunk(2, 1)[c[0]]) and torch.equal(f, full)
+        assert float(p[0, 0]) == (4.0 if c[1] == 0 else 6.0) and torch.equal(rep, local)
+    # without groups the placement list is rewritten and nothing moves, as in the reference
+    meta = DTensor.from_local(full, mesh, [Replicate(), Replicate()]).redistribute([Shard(0), Replicate()])
+    assert meta.placements == [Shard(0), Replicate()] and meta.to_local() is full
+    for bad in (lambda: DTensor.from_local(full, mesh, [Replicate()]), lambda: DTensor.from_local(full, mesh, [Shard(0), Shard(0)]),
+                lambda: DTensor.from_local(full, mesh, [Shard(2), Replicate()]), lambda: meta.redistribute([Shard(5), Replicate()])):
+        with pytest.raises(ValueError):
+            bad()
+    one = DTensor(full.chunk(2, 0)[0], world[0].__class__.create_group(1)[0], Replicate())
+    assert one.shape == (4, 6) and one.numel() == 24 and one.placements == [Replicate()] and one.to_local().shape == (4, 6)
