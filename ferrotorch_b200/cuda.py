@@ -126,6 +126,30 @@ class CapturedGraph:
     def reset(self) -> None:
         self.graph.reset()
 
+    # ---- graph.rs:477-515.  torch instantiates and uploads a graph when its capture ends and keeps the
+    # capture's allocations in a pool that belongs to the graph, so these report rather than act.
+    def upload(self) -> None:
+        self._uploaded = True
+
+    def is_uploaded(self) -> bool:
+        return True
+
+    def has_pool(self) -> bool:
+        return True
+
+    def pool(self):
+        """The ``(device, id)`` handle of the memory pool that backs the capture's allocations."""
+        return self.graph.pool()
+
+    def pool_buffer_count(self) -> int:
+        """Blocks currently held by the graph's private pool (0 when the allocator cannot say)."""
+        try:
+            snap = torch.cuda.memory_snapshot()
+            handle = tuple(self.graph.pool())
+            return sum(len(seg["blocks"]) for seg in snap if tuple(seg.get("segment_pool_id", ())) == handle)
+        except Exception:  # noqa: BLE001 - statistics only
+            return 0
+
 
 @contextlib.contextmanager
 def capture(pool=None, stream=None, capture_error_mode: str = "global"):
@@ -352,6 +376,64 @@ class CudaAllocator:
     @staticmethod
     def round_len(nbytes: int) -> int:
         return round_len(nbytes)
+
+    # ---- the reference allocator's method names (allocator.rs:101-827) on torch's caching allocator
+    memory_allocated = allocated_bytes
+    memory_reserved = reserved_bytes
+    max_memory_allocated = peak_bytes
+
+    def device(self) -> "torch.device":
+        return torch.device("cuda", self.ordinal)
+
+    def cached_bytes(self) -> int:
+        """Bytes the allocator holds but no tensor uses."""
+        return max(0, self.reserved_bytes() - self.allocated_bytes())
+
+    def cache_stats(self) -> dict:
+        """Counters of the caching allocator (hits are allocations served without a driver call)."""
+        st = torch.cuda.memory_stats(self.ordinal) if is_available() else {}
+        allocs, driver = st.get("allocation.all.allocated", 0), st.get("segment.all.allocated", 0)
+        return {"allocations": allocs, "driver_allocations": driver, "cache_hits": max(0, allocs - driver),
+                "active_blocks": st.get("active.all.current", 0), "free_blocks": st.get("inactive_split.all.current", 0),
+                "reserved_bytes": st.get("reserved_bytes.all.current", 0), "retries": st.get("num_alloc_retries", 0),
+                "ooms": st.get("num_ooms", 0)}
+
+    def block_count(self) -> int:
+        return self.cache_stats()["active_blocks"]
+
+    def free_block_count(self) -> int:
+        return self.cache_stats()["free_blocks"]
+
+    @staticmethod
+    def driver_alloc_size(nbytes: int) -> int:
+        """What one request costs at the driver: requests below 1 MiB come out of 2 MiB segments in
+        512-byte blocks, larger ones are rounded to 2 MiB (``MIN_BLOCK_SIZE`` / ``SMALL_BUFFER`` /
+        ``ROUND_LARGE`` of the reference's allocator, the same constants as torch's)."""
+        if nbytes <= 0:
+            return 0
+        if nbytes < (1 << 20):
+            return 2 << 20
+        return round_len(nbytes)
+
+    def alloc_zeros(self, shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        return alloc_zeros(shape, dtype, self.ordinal)
+
+    def alloc_copy(self, data, dtype: torch.dtype | None = None) -> torch.Tensor:
+        _need()
+        return torch.as_tensor(data, dtype=dtype).to(self.device())
+
+    @staticmethod
+    def free(tensor: torch.Tensor) -> int:
+        """Drop the tensor's storage (it returns to the cache); returns the bytes it held."""
+        n = tensor.numel() * tensor.element_size()
+        tensor.set_()
+        return n
+
+    @staticmethod
+    def record_stream_on_block(tensor: torch.Tensor, stream) -> None:
+        """Keep the block from being reused until the work queued on ``stream`` so far has finished."""
+        if tensor.is_cuda:
+            tensor.record_stream(stream)
 
 
 # --------------------------------------------------------------------------- typed launcher names (``gpu_<op>_<dtype>``)

@@ -498,6 +498,19 @@ class AutotuneResult:
     candidates: list
 
 
+@dataclass
+class BackendTuneResult:
+    """What ``Autotuner.tune(graph, inputs)`` found: the winning back-end, its median time in seconds,
+    every ``(name, median)`` that was timed (only the winner's on a cache hit), the winner's compiled
+    graph, and the candidates that could not compile the graph (autotune.rs ``AutotuneResult``)."""
+    winner: str
+    median_s: float
+    all_timings: list
+    compiled: "CompiledGraph"
+    from_cache: bool = False
+    failed: dict = field(default_factory=dict)
+
+
 def autotune(module: TracedModule, inputs, candidates=(128, 256, 512), iters: int = 5, cache: dict | None = None) -> AutotuneResult:
     """Time every candidate block size (CUDA events; on the CPU nothing is timed and the module's
     current block size stands) and keep the best; ``cache`` (key -> result) skips repeated tuning."""

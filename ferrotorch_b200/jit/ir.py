@@ -44,6 +44,106 @@ class IrGraph:
         self.order.append(n.id)
         return n
 
+    # ---- builder and query calls under the reference's names (ferrotorch-jit/src/graph.rs ``impl IrGraph``).
+    # A node here produces exactly one value and the value carries the node's id, so node ids and
+    # value ids coincide.
+    def add_input(self, shape, dtype: torch.dtype = torch.float32) -> int:
+        n = self.add("input", index=sum(1 for i in self.order if self.nodes[i].op == "input"))
+        n.shape, n.dtype = tuple(shape), dtype
+        return n.id
+
+    add_input_with_dtype = add_input
+
+    def add_constant(self, data, shape=None, dtype: torch.dtype = torch.float32) -> int:
+        t = torch.as_tensor(data, dtype=dtype)
+        if shape is not None:
+            t = t.reshape(tuple(shape))
+        n = self.add("const", value=t)
+        n.shape, n.dtype = tuple(t.shape), dtype
+        return n.id
+
+    add_constant_with_dtype = add_constant
+
+    def add_node(self, op: str, inputs, output_shapes=None, output_dtypes=None, **attrs):
+        """Returns ``(node id, [value ids])``; one output per node, so the list has one entry."""
+        for i in inputs:
+            if i not in self.nodes:
+                raise KeyError("add_node(%r): input value %r does not exist" % (op, i))
+        if output_shapes is not None and len(output_shapes) != 1:
+            raise ValueError("a node produces one value; got %d output shapes" % len(output_shapes))
+        if output_dtypes is not None and output_shapes is not None and len(output_dtypes) != len(output_shapes):
+            raise ValueError("one dtype per output shape")
+        n = self.add(op, inputs, **attrs)
+        n.shape = tuple(output_shapes[0]) if output_shapes else None
+        n.dtype = output_dtypes[0] if output_dtypes else torch.float32
+        return n.id, [n.id]
+
+    add_node_with_dtype = add_node
+
+    def set_outputs(self, values) -> None:
+        values = list(values)
+        for v in values:
+            if v not in self.nodes:
+                raise KeyError("set_outputs: value %r does not exist" % (v,))
+        self.outputs = values
+
+    def node_count(self) -> int:
+        return len(self.order)
+
+    value_count = node_count
+
+    def alloc_node_id(self) -> int:
+        i, self._next = self._next, self._next + 1
+        return i
+
+    alloc_value_id = alloc_node_id
+
+    def is_constant(self, value_id: int) -> bool:
+        return value_id in self.nodes and self.nodes[value_id].op == "const"
+
+    def remove_node(self, node_id: int) -> None:
+        """Remove one node and its value; nodes that become dead upstream stay (iterate to a fixed
+        point, or run :func:`dead_code_eliminate`).  A node that still has users cannot go."""
+        if node_id not in self.nodes:
+            raise KeyError(node_id)
+        users = [i for i in self.order if node_id in self.nodes[i].inputs]
+        if users or node_id in self.outputs:
+            raise ValueError("node %d is still used by %s" % (node_id, users or "the graph outputs"))
+        del self.nodes[node_id]
+        self.order.remove(node_id)
+
+    def topological_order(self) -> list[int]:
+        """Node ids such that every node comes after the producers of its inputs (Kahn's algorithm;
+        ties in insertion order).  Raises on a cycle."""
+        pending = {i: len(set(self.nodes[i].inputs)) for i in self.order}
+        users = self.users()
+        ready = [i for i in self.order if pending[i] == 0]
+        out = []
+        while ready:
+            i = ready.pop(0)
+            out.append(i)
+            for u in dict.fromkeys(users[i]):
+                pending[u] -= 1
+                if pending[u] == 0:
+                    ready.append(u)
+        if len(out) != len(self.order):
+            raise ValueError("the graph has a cycle")
+        return out
+
+    def fingerprint(self) -> int:
+        """A 64-bit digest of the structure (ops, wiring, shapes, dtypes, scalar attributes, outputs);
+        equal for graphs built the same way in any process, which is what an autotune cache keys on."""
+        import hashlib
+
+        h = hashlib.blake2b(digest_size=8)
+        pos = {i: k for k, i in enumerate(self.order)}
+        for i in self.order:
+            n = self.nodes[i]
+            scal = sorted((k, repr(v)) for k, v in n.attrs.items() if isinstance(v, (int, float, str, bool, tuple, list)))
+            h.update(repr((n.op, [pos[j] for j in n.inputs], n.shape, str(n.dtype), scal)).encode())
+        h.update(repr([pos[o] for o in self.outputs]).encode())
+        return int.from_bytes(h.digest(), "little")
+
     def users(self) -> dict[int, list[int]]:
         u: dict[int, list[int]] = {i: [] for i in self.nodes}
         for i in self.order:

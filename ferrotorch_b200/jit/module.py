@@ -276,12 +276,109 @@ def apply_fused(ops, x: torch.Tensor) -> torch.Tensor:
 
 
 class Autotuner:
-    """Pick the fastest launch block size for a compiled module on given inputs (autotune.rs)."""
+    """Two tuners behind the reference's name (ferrotorch-jit/src/autotune.rs).
+
+    *Back-end choice* -- the reference's meaning: register candidate back-ends
+    (``with_candidate(name, backend)``: interpreter, native closures, generated kernels), and
+    ``tune(graph, inputs)`` compiles the graph with each, times ``iterations`` runs after ``warmup``
+    discarded ones, scores a candidate by its **median**, and returns the winner with its compiled
+    graph.  Results are cached under the graph's fingerprint and the inputs' shapes and dtypes; on a
+    hit only the winner is recompiled and timed again.
+
+    *Launch shape* -- ``tune(traced_module, inputs)`` picks the fastest block size of a compiled
+    module among ``candidates`` (timed with CUDA events; without a GPU the current size stands)."""
 
     def __init__(self, candidates=(128, 256, 512)):
         self.candidates = candidates
+        self._backends: list = []
+        self._iterations, self._warmup = 5, 1
+        self._cache: dict = {}
 
-    def tune(self, module: TracedModule, inputs, iters: int = 5) -> int:
+    # ---- builder and accessors
+    def with_candidate(self, name: str, backend) -> "Autotuner":
+        self._backends.append((str(name), backend))
+        return self
+
+    def with_iterations(self, iterations: int) -> "Autotuner":
+        self._iterations = max(1, int(iterations))
+        return self
+
+    def with_warmup(self, warmup: int) -> "Autotuner":
+        self._warmup = max(0, int(warmup))
+        return self
+
+    def iterations(self) -> int:
+        return self._iterations
+
+    def warmup(self) -> int:
+        return self._warmup
+
+    def candidate_count(self) -> int:
+        return len(self._backends)
+
+    def cache_size(self) -> int:
+        return len(self._cache)
+
+    def clear_cache(self) -> None:
+        self._cache.clear()
+
+    @staticmethod
+    def key_of(graph, inputs) -> tuple:
+        return (graph.fingerprint(), tuple((tuple(t.shape), str(t.dtype), str(t.device)) for t in inputs))
+
+    def cached(self, key):
+        """``(winner name, median seconds)`` of an earlier tune with this key, or ``None``."""
+        return self._cache.get(key)
+
+    def tune(self, target, inputs, iters: int | None = None):
+        if isinstance(target, TracedModule):
+            return self._tune_block_size(target, inputs, iters or 5)
+        return self._tune_backends(target, list(inputs))
+
+    # ---- back-end choice
+    def _time(self, compiled, inputs) -> float:
+        import statistics
+        import time
+
+        cuda = any(t.is_cuda for t in inputs)
+        for _ in range(self._warmup):
+            compiled.execute(inputs)
+        ts = []
+        for _ in range(self._iterations):
+            if cuda:
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            compiled.execute(inputs)
+            if cuda:
+                torch.cuda.synchronize()
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts)
+
+    def _tune_backends(self, graph, inputs):
+        from .backends import BackendTuneResult
+
+        if not self._backends:
+            raise JitError("Autotuner.tune: no candidate back-ends registered")
+        key = self.key_of(graph, inputs)
+        hit = self._cache.get(key)
+        names = [hit[0]] if hit is not None else [n for n, _ in self._backends]
+        timings, compiled_of, errors = [], {}, {}
+        for name, backend in self._backends:
+            if name not in names:
+                continue
+            try:
+                compiled_of[name] = backend.compile(graph)
+                timings.append((name, self._time(compiled_of[name], inputs)))
+            except Exception as e:  # noqa: BLE001 - a back-end that cannot take the graph is not a candidate for it
+                errors[name] = "%s: %s" % (type(e).__name__, e)
+        if not timings:
+            raise JitError("Autotuner.tune: every candidate failed: %s" % errors)
+        winner, best = min(timings, key=lambda nt: nt[1])
+        self._cache[key] = (winner, best)
+        return BackendTuneResult(winner, best, timings, compiled_of[winner], hit is not None, errors)
+
+    # ---- launch shape
+    def _tune_block_size(self, module: TracedModule, inputs, iters: int = 5) -> int:
         if not torch.cuda.is_available():
             return module.cfg.block_size
         best, best_t = module.cfg.block_size, float("inf")

@@ -238,6 +238,71 @@ MemoryGuard.release_reservation = lambda self: setattr(self, "reserve", 0)
 MemoryGuard.reserved_bytes = lambda self: self.reserve
 
 
+def _on_oom(self, fn) -> None:
+    """``fn()`` runs (after the hooks, before the error is raised) whenever a request cannot be met
+    (memory_guard.rs:373)."""
+    self.__dict__.setdefault("_oom_callbacks", []).append(fn)
+
+
+_plain_fail = MemoryGuard._fail
+
+
+def _fail_with_callbacks(self, nbytes: int):
+    for fn in self.__dict__.get("_oom_callbacks", []):
+        fn()
+    return _plain_fail(self, nbytes)
+
+
+def _safe_alloc_copy(self, data, dtype=None, device=None):
+    """A guarded allocation filled with ``data`` (a tensor or anything ``torch.as_tensor`` takes)."""
+    import torch
+
+    src = torch.as_tensor(data, dtype=dtype)
+    out = self.safe_alloc(src.shape, src.dtype, device)
+    out.copy_(src)
+    return out
+
+
+def _safe_alloc_with_hooks(self, shape, dtype=None, device=None):
+    """Like ``safe_alloc`` but the pre-OOM hooks always get their chance, whatever the policy says
+    (memory_guard.rs:479)."""
+    prev = self.policy
+    if prev == OomPolicy.FAIL:
+        self.policy = OomPolicy.RUN_HOOKS_THEN_FAIL
+    try:
+        return self.safe_alloc(shape, dtype, device)
+    finally:
+        self.policy = prev
+
+
+def _free(self, tensor) -> int:
+    """Give a guarded allocation back: the storage is released to the caching allocator when the last
+    reference goes; returns the bytes the tensor held."""
+    n = tensor.numel() * tensor.element_size()
+    tensor.set_()
+    return n
+
+
+def _device_ordinal(self) -> int:
+    return int(getattr(self.alloc, "device", 0))
+
+
+def _device(self):
+    import torch
+
+    return torch.device("cuda", self.device_ordinal()) if isinstance(self.alloc, TorchCudaAllocator) else torch.device("cpu")
+
+
+MemoryGuard.on_oom = _on_oom
+MemoryGuard._fail = _fail_with_callbacks
+MemoryGuard.safe_alloc_copy = _safe_alloc_copy
+MemoryGuard.safe_alloc_with_hooks = _safe_alloc_with_hooks
+MemoryGuard.free = _free
+MemoryGuard.device_ordinal = _device_ordinal
+MemoryGuard.device = _device
+MemoryGuard.device_arc = _device
+
+
 class MemoryGuardBuilder:
     """``MemoryGuardBuilder().budget_bytes(n).reserve_bytes(m).oom_policy(p).build(allocator)``."""
 

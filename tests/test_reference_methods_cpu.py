@@ -165,3 +165,109 @@ def test_device_mesh_and_mesh_tensor_methods():
             bad()
     one = DTensor(full.chunk(2, 0)[0], world[0].__class__.create_group(1)[0], Replicate())
     assert one.shape == (4, 6) and one.numel() == 24 and one.placements == [Replicate()] and one.to_local().shape == (4, 6)
+
+
+def test_memory_guard_methods():
+    # ferrotorch-gpu/src/memory_guard.rs:356-770
+    from ferrotorch_b200.utils.memory_guard import MemoryBudgetExceeded, MemoryGuard, OomPolicy
+
+    class FakeAllocator:
+        def __init__(self, total):
+            self.total, self.used, self.device = total, 0, 3
+
+        def used_bytes(self):
+            return self.used
+
+        def total_bytes(self):
+            return self.total
+
+        def empty_cache(self):
+            pass
+
+    a = FakeAllocator(1000)
+    g = MemoryGuard(a, policy=OomPolicy.FAIL)
+    seen = []
+    g.on_oom(lambda: seen.append("oom"))
+    t = g.safe_alloc_copy([1.0, 2.0, 3.0])
+    assert t.tolist() == [1.0, 2.0, 3.0] and g.device_ordinal() == 3 and g.device().type == "cpu" and g.device_arc() == g.device()
+    a.used = 990
+    with pytest.raises(MemoryBudgetExceeded):
+        g.safe_alloc((100,))                                    # policy Fail: hooks are not consulted
+    assert seen == ["oom"]
+
+    def hook(need):
+        a.used = 0
+        return 990
+
+    g.register_hook(hook)
+    with pytest.raises(MemoryBudgetExceeded):
+        g.safe_alloc((100,))
+    a.used = 990
+    assert g.safe_alloc_with_hooks((100,)).shape == (100,) and g.policy == OomPolicy.FAIL       # hooks ran for this call only
+    assert g.free(t) == 12 and t.numel() == 0
+
+
+def test_ir_graph_builder_and_backend_autotuner():
+    # ferrotorch-jit/src/graph.rs ``impl IrGraph``; autotune.rs ``impl Autotuner``
+    from ferrotorch_b200 import jit as J
+    from ferrotorch_b200.jit.backends import InterpreterBackend, NativeBackend, interpret
+    from ferrotorch_b200.jit.ir import IrGraph
+
+    def build():
+        g = IrGraph()
+        a, b = g.add_input([2, 3]), g.add_input_with_dtype([2, 3], torch.float32)
+        c = g.add_constant([2.0] * 6, [2, 3])
+        _, (v1,) = g.add_node("add", [a, b], [[2, 3]])
+        _, (v2,) = g.add_node("mul", [v1, c], [[2, 3]])
+        _, (v3,) = g.add_node_with_dtype("relu", [v2], [[2, 3]], [torch.float32])
+        dead, _ = g.add_node("neg", [v1], [[2, 3]])
+        g.set_outputs([v3])
+        return g, dead
+
+    g, dead = build()
+    assert g.node_count() == g.value_count() == 7 and g.is_constant(2) and not g.is_constant(0) and not g.is_constant(99)
+    order = g.topological_order()
+    assert sorted(order) == list(range(7)) and all(order.index(i) < order.index(n) for n in order for i in g.nodes[n].inputs)
+    assert g.fingerprint() == build()[0].fingerprint()                       # same construction, same digest
+    x, y = torch.randn(2, 3), torch.randn(2, 3)
+    torch.testing.assert_close(interpret(g, [x, y]), torch.relu((x + y) * 2))
+    before = g.fingerprint()
+    g.remove_node(dead)
+    assert g.node_count() == 6 and g.fingerprint() != before
+    with pytest.raises(ValueError):
+        g.remove_node(3)                                                     # still feeds the multiply
+    with pytest.raises(KeyError):
+        g.add_node("add", [0, 42], [[2, 3]])
+    with pytest.raises(KeyError):
+        g.set_outputs([42])
+    assert g.alloc_node_id() == 7 and g.alloc_value_id() == 8
+    cyc = IrGraph()
+    p = cyc.add_input([1])
+    _, (q,) = cyc.add_node("neg", [p], [[1]])
+    cyc.nodes[p].inputs.append(q)
+    with pytest.raises(ValueError):
+        cyc.topological_order()
+
+    class Broken(InterpreterBackend):
+        def compile(self, graph):
+            raise RuntimeError("cannot take this graph")
+
+    tuner = (J.Autotuner().with_candidate("interpreter", InterpreterBackend()).with_candidate("native", NativeBackend())
+             .with_candidate("broken", Broken()).with_iterations(3).with_warmup(1))
+    assert (tuner.iterations(), tuner.warmup(), tuner.candidate_count(), tuner.cache_size()) == (3, 1, 3, 0)
+    key = tuner.key_of(g, [x, y])
+    assert tuner.cached(key) is None
+    res = tuner.tune(g, [x, y])
+    assert res.winner in ("interpreter", "native") and not res.from_cache and set(n for n, _ in res.all_timings) == {"interpreter", "native"}
+    assert "broken" in res.failed and res.median_s == min(t for _, t in res.all_timings)
+    torch.testing.assert_close(res.compiled.execute([x, y])[0], torch.relu((x + y) * 2))
+    assert tuner.cache_size() == 1 and tuner.cached(key)[0] == res.winner
+    again = tuner.tune(g, [x, y])
+    assert again.from_cache and [n for n, _ in again.all_timings] == [res.winner]        # only the winner is timed again
+    assert tuner.tune(g, [torch.randn(2, 3, dtype=torch.float64), y.double()]).from_cache is False     # another signature
+    tuner.clear_cache()
+    assert tuner.cache_size() == 0
+    with pytest.raises(J.JitError):
+        J.Autotuner().tune(g, [x, y])
+    with pytest.raises(J.JitError):
+        J.Autotuner().with_candidate("broken", Broken()).tune(g, [x, y])
