@@ -23,13 +23,12 @@ try:  # torch >= 2.3
 except ImportError:  # pragma: no cover
     from torch.cuda.amp import GradScaler  # noqa: F401
 
-from .extra import (EMA, Adafactor, AveragedModel, GradientAccumulator, Muon, NaturalGradient, WarmupLR,  # noqa: F401
+from .extra import (EMA, Adafactor, AveragedModel, Kfac, GradientAccumulator, Muon, NaturalGradient, WarmupLR,  # noqa: F401
                     cosine_warmup_scheduler)
 from .fused import FusedAdamW, FusedSGD  # noqa: F401
 
 
 ExponentialMovingAverage = EMA          # noqa: F405  (ferrotorch-optim/src/ema.rs)
-Kfac = NaturalGradient                  # noqa: F405  (natural_gradient.rs)
 from .extra import diff_sgd_momentum_step, diff_sgd_step  # noqa: F401,E402
 from .configs import *  # noqa: F401,F403,E402
 from .configs import (ParamGroup, ParamKey, OptimizerState, Sgd, Asgd, Lbfgs, Rmsprop, LrScheduler, SequentialLr,  # noqa: F401,E402

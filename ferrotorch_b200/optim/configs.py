@@ -17,7 +17,16 @@ from torch.optim import (ASGD, LBFGS, SGD, Adadelta, Adagrad, Adam, Adamax, Adam
                          SparseAdam, lr_scheduler)
 from torch.optim.swa_utils import SWALR
 
-from .extra import Adafactor, Muon, NaturalGradient, WarmupLR
+from .extra import Adafactor, Kfac, Muon, NaturalGradient, WarmupLR
+
+
+# the reference's setter names that do not spell a keyword of the optimizer here: name -> (field, how the
+# field's new value follows from the config and the argument)
+_BUILDER_ALIASES = {
+    "AdafactorConfig": {"eps_sq": ("eps", lambda c, v: (v, c.eps[1])), "eps_rms": ("eps", lambda c, v: (c.eps[0], v)),
+                        "decay_rate": ("beta2_decay", lambda c, v: -abs(v))},
+    "RpropConfig": {"cpu_fallback": ("foreach", lambda c, v: None if v else c.foreach)},
+}
 
 
 def _config_for(opt_cls, name: str):
@@ -38,7 +47,15 @@ def _config_for(opt_cls, name: str):
     def to_dict(self) -> dict:
         return dataclasses.asdict(self)
 
-    cls = dataclasses.make_dataclass(name, fields, namespace={"build": build, "to_dict": to_dict, "optimizer": opt_cls})
+    ns = {"build": build, "to_dict": to_dict, "optimizer": opt_cls}
+    # builder-style setters, ``AdamWConfig().with_lr(3e-4).with_betas((0.9, 0.95))``, as the reference's
+    # configs are written (adamw.rs ``with_lr`` ...); each returns a changed copy
+    for fname, _t, _f in fields:
+        ns["with_" + fname] = (lambda f: lambda self, value: dataclasses.replace(self, **{f: value}))(fname)
+    for alias, target in _BUILDER_ALIASES.get(name, {}).items():
+        if any(f[0] == target[0] for f in fields):
+            ns["with_" + alias] = (lambda t: lambda self, value=True: dataclasses.replace(self, **{t[0]: t[1](self, value)}))(target)
+    cls = dataclasses.make_dataclass(name, fields, namespace=ns)
     cls.__doc__ = "Keyword arguments of :class:`%s` with its defaults." % opt_cls.__name__
     cls.__module__ = __name__
     return cls
@@ -59,7 +76,8 @@ AsgdConfig = _config_for(ASGD, "AsgdConfig")
 SparseAdamConfig = _config_for(SparseAdam, "SparseAdamConfig")
 LbfgsConfig = _config_for(LBFGS, "LbfgsConfig")
 MuonConfig = _config_for(Muon, "MuonConfig")
-KfacConfig = _config_for(NaturalGradient, "KfacConfig")
+KfacConfig = _config_for(Kfac, "KfacConfig")
+NaturalGradientConfig = _config_for(NaturalGradient, "NaturalGradientConfig")
 
 Sgd, Asgd, Lbfgs, Rmsprop = SGD, ASGD, LBFGS, RMSprop
 LrScheduler = lr_scheduler.LRScheduler
@@ -122,6 +140,10 @@ class GradScalerConfig:
         from torch.amp import GradScaler
 
         return GradScaler(device, **dataclasses.asdict(self))
+
+
+for _f in dataclasses.fields(GradScalerConfig):
+    setattr(GradScalerConfig, "with_" + _f.name, (lambda f: lambda self, value: dataclasses.replace(self, **{f: value}))(_f.name))
 
 
 @dataclasses.dataclass

@@ -9,9 +9,14 @@ from torch.optim import Optimizer
 from torch.optim.lr_scheduler import LambdaLR
 
 
-def _newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
-    """Quintic Newton-Schulz iteration that orthogonalises a matrix (Muon)."""
-    a, b, c = 3.4445, -4.7750, 2.0315
+QUINTIC_NS = (3.4445, -4.7750, 2.0315)      # Keller Jordan's Muon coefficients (torch/optim/_muon.py)
+CUBIC_NS = (1.5, -0.5, 0.0)                  # G (3 I - G^T G) / 2, the reference's historic default (muon.rs)
+
+
+def _newton_schulz(g: torch.Tensor, steps: int = 5, coefficients=QUINTIC_NS) -> torch.Tensor:
+    """Newton-Schulz iteration ``X <- a X + b (X X^T) X + c (X X^T)^2 X`` that drives the singular
+    values of a matrix towards one (Muon's orthogonalisation)."""
+    a, b, c = coefficients
     x = g.float()
     transposed = x.shape[0] > x.shape[1]
     if transposed:
@@ -24,11 +29,26 @@ def _newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
 
 
 class Muon(Optimizer):
-    """Momentum + orthogonalised update for 2-D parameters; other shapes fall back to SGD-momentum."""
+    """Momentum + orthogonalised update for 2-D parameters (ferrotorch-optim/src/muon.rs).
 
-    def __init__(self, params, lr=0.02, momentum=0.95, nesterov=True, ns_steps=5, weight_decay=0.0):
+    ``ns_coefficients``: the polynomial of the Newton-Schulz step (quintic by default; the
+    reference's default is the cubic ``CUBIC_NS``).  ``decoupled_weight_decay``: shrink the weights by
+    ``1 - lr * wd`` (default, as torch's Muon) or, when false, fold ``wd * p`` into the gradient before
+    the orthogonalisation (the reference's default).  ``strict_2d``: refuse parameters that are not
+    matrices instead of giving them plain momentum SGD.  ``maximize`` negates the gradient."""
+
+    def __init__(self, params, lr=0.02, momentum=0.95, nesterov=True, ns_steps=5, weight_decay=0.0, maximize=False,
+                 ns_coefficients=QUINTIC_NS, decoupled_weight_decay=True, strict_2d=False):
+        if len(tuple(ns_coefficients)) != 3:
+            raise ValueError("Muon: ns_coefficients must be three numbers (a, b, c)")
         super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps,
-                                      weight_decay=weight_decay))
+                                      weight_decay=weight_decay, maximize=maximize, ns_coefficients=tuple(ns_coefficients),
+                                      decoupled_weight_decay=decoupled_weight_decay, strict_2d=strict_2d))
+        for g in self.param_groups:
+            if g["strict_2d"]:
+                bad = [tuple(p.shape) for p in g["params"] if p.dim() != 2]
+                if bad:
+                    raise ValueError("Muon only supports 2D parameters with strict_2d; got shapes %s" % bad)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -37,24 +57,33 @@ class Muon(Optimizer):
             for p in g["params"]:
                 if p.grad is None:
                     continue
+                grad = -p.grad if g["maximize"] else p.grad
+                if g["weight_decay"] and not g["decoupled_weight_decay"]:
+                    grad = grad.add(p, alpha=g["weight_decay"])
                 st = self.state[p]
                 buf = st.setdefault("momentum_buffer", torch.zeros_like(p))
-                buf.mul_(g["momentum"]).add_(p.grad)
-                upd = p.grad.add(buf, alpha=g["momentum"]) if g["nesterov"] else buf
+                buf.mul_(g["momentum"]).add_(grad)
+                upd = grad.add(buf, alpha=g["momentum"]) if g["nesterov"] else buf
                 if p.dim() == 2:
-                    upd = _newton_schulz(upd, g["ns_steps"]) * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
-                if g["weight_decay"]:
+                    upd = _newton_schulz(upd, g["ns_steps"], g["ns_coefficients"]) * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
+                if g["weight_decay"] and g["decoupled_weight_decay"]:
                     p.mul_(1 - g["lr"] * g["weight_decay"])
                 p.add_(upd, alpha=-g["lr"])
         return loss
 
 
 class Adafactor(Optimizer):
-    """Factored second moments for matrices (row / column statistics), Adam-style otherwise."""
+    """Factored second moments for matrices (row / column statistics), Adam-style otherwise
+    (ferrotorch-optim/src/adafactor.rs).  ``beta1`` adds a first moment of the clipped update;
+    ``relative_step`` replaces ``lr`` by ``min(cap, 1 / sqrt(step)) * max(eps[1], rms(p))`` with
+    ``cap = 1e-2``, or ``1e-6 * step`` under ``warmup_init`` (Shazeer & Stern, section 8)."""
 
-    def __init__(self, params, lr=1e-3, beta2_decay=-0.8, eps=(1e-30, 1e-3), clip_threshold=1.0, weight_decay=0.0):
+    def __init__(self, params, lr=1e-3, beta2_decay=-0.8, eps=(1e-30, 1e-3), clip_threshold=1.0, weight_decay=0.0,
+                 beta1=None, relative_step=False, warmup_init=False):
+        if lr is None:
+            relative_step = True
         super().__init__(params, dict(lr=lr, beta2_decay=beta2_decay, eps=eps, clip_threshold=clip_threshold,
-                                      weight_decay=weight_decay))
+                                      weight_decay=weight_decay, beta1=beta1, relative_step=relative_step, warmup_init=warmup_init))
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -79,9 +108,17 @@ class Adafactor(Optimizer):
                     v.mul_(beta2).add_(sq, alpha=1 - beta2)
                 u = grad / v.sqrt()
                 u = u / max(1.0, float(u.pow(2).mean().sqrt()) / g["clip_threshold"])
+                if g["beta1"] is not None:
+                    m = st.setdefault("exp_avg", torch.zeros_like(u))
+                    m.mul_(g["beta1"]).add_(u, alpha=1 - g["beta1"])
+                    u = m
+                lr = g["lr"]
+                if g["relative_step"]:
+                    cap = 1e-6 * st["step"] if g["warmup_init"] else 1e-2
+                    lr = min(cap, 1.0 / math.sqrt(st["step"])) * max(g["eps"][1], float(p.float().pow(2).mean().sqrt()))
                 if g["weight_decay"]:
-                    p.mul_(1 - g["lr"] * g["weight_decay"])
-                p.add_(u.to(p.dtype), alpha=-g["lr"])
+                    p.mul_(1 - lr * g["weight_decay"])
+                p.add_(u.to(p.dtype), alpha=-lr)
         return loss
 
 
@@ -102,6 +139,108 @@ class NaturalGradient(Optimizer):
                 f = self.state[p].setdefault("fisher", torch.zeros_like(p))
                 f.mul_(g["decay"]).addcmul_(p.grad, p.grad, value=1 - g["decay"])
                 p.addcdiv_(p.grad, f + g["damping"], value=-g["lr"])
+        return loss
+
+
+class Kfac(Optimizer):
+    """K-FAC natural gradient for dense layers (Martens & Grosse 2015; ferrotorch-optim/src/natural_gradient.rs:
+    92-700).  The Fisher block of a weight ``W [out, in]`` is approximated by ``A (x) G`` with
+    ``A = E[a a^T]`` over the layer's inputs and ``G = E[g g^T]`` over the gradients of its outputs, so the
+    preconditioned gradient is ``(G + damping I)^-1 grad (A + damping I)^-1``.
+
+    Curvature comes in through :meth:`update_factors` (``weight``, inputs ``[batch, in]``, output
+    gradients ``[batch, out]``) or, automatically, from hooks installed by :meth:`watch` on every
+    ``nn.Linear`` of a module.  The first update seeds a factor with the batch estimate, later ones blend
+    with ``stat_decay``; inverses are recomputed every ``update_freq`` steps.  Parameters without
+    factors (biases, anything not registered) get the plain gradient.  ``momentum`` acts on the
+    preconditioned gradient; ``weight_decay`` is L2 (added to the gradient before preconditioning);
+    ``maximize`` negates the gradient."""
+
+    def __init__(self, params, lr=1e-3, damping=1e-3, momentum=0.9, stat_decay=0.95, update_freq=10, weight_decay=0.0,
+                 maximize=False):
+        if update_freq < 1:
+            raise ValueError("Kfac: update_freq must be >= 1")
+        super().__init__(params, dict(lr=lr, damping=damping, momentum=momentum, stat_decay=stat_decay, update_freq=update_freq,
+                                      weight_decay=weight_decay, maximize=maximize))
+        self._factors: dict = {}          # id(weight) -> {"A", "G", "A_inv", "G_inv"}
+        self._steps = 0
+        self._hooks: list = []
+
+    def _stat_decay(self) -> float:
+        return self.param_groups[0]["stat_decay"]
+
+    @torch.no_grad()
+    def update_factors(self, weight: torch.Tensor, input_activation: torch.Tensor, output_gradient: torch.Tensor) -> None:
+        a, g = input_activation.detach(), output_gradient.detach()
+        if a.dim() != 2 or g.dim() != 2:
+            raise ValueError("update_factors expects 2-D tensors, got activation %s and gradient %s" % (tuple(a.shape), tuple(g.shape)))
+        if a.shape[0] != g.shape[0] or tuple(weight.shape) != (g.shape[1], a.shape[1]):
+            raise ValueError("update_factors: activation %s and gradient %s do not belong to a weight of shape %s"
+                             % (tuple(a.shape), tuple(g.shape), tuple(weight.shape)))
+        a, g = a.float(), g.float()
+        A, G = a.t() @ a / a.shape[0], g.t() @ g / g.shape[0]
+        f = self._factors.get(id(weight))
+        if f is None:
+            self._factors[id(weight)] = {"A": A, "G": G, "A_inv": None, "G_inv": None}
+        else:
+            d = self._stat_decay()
+            f["A"].mul_(d).add_(A, alpha=1 - d)
+            f["G"].mul_(d).add_(G, alpha=1 - d)
+
+    def watch(self, module: torch.nn.Module) -> "Kfac":
+        """Collect the factors of every ``nn.Linear`` in ``module`` during its forward and backward passes.
+        Output gradients are multiplied by the batch size, which undoes the ``1 / batch`` of a mean loss
+        (the convention of the K-FAC reference implementations)."""
+        def pre(m, args):
+            m._kfac_input = args[0].detach().reshape(-1, args[0].shape[-1])
+
+        def back(m, grad_in, grad_out):
+            g = grad_out[0].detach().reshape(-1, grad_out[0].shape[-1])
+            self.update_factors(m.weight, m._kfac_input, g * g.shape[0])
+
+        for m in module.modules():
+            if isinstance(m, torch.nn.Linear):
+                self._hooks += [m.register_forward_pre_hook(pre), m.register_full_backward_hook(back)]
+        return self
+
+    def unwatch(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+    def preconditioned(self, weight: torch.Tensor, grad: torch.Tensor, damping: float, refresh: bool = True) -> torch.Tensor:
+        """``(G + damping I)^-1 grad (A + damping I)^-1`` for a registered weight (the plain gradient otherwise)."""
+        f = self._factors.get(id(weight))
+        if f is None or grad.dim() != 2:
+            return grad
+        if refresh or f["A_inv"] is None:
+            eye_a = torch.eye(f["A"].shape[0], device=f["A"].device)
+            eye_g = torch.eye(f["G"].shape[0], device=f["G"].device)
+            f["A_inv"] = torch.linalg.solve(f["A"] + damping * eye_a, eye_a)
+            f["G_inv"] = torch.linalg.solve(f["G"] + damping * eye_g, eye_g)
+        return (f["G_inv"] @ grad.float() @ f["A_inv"]).to(grad.dtype)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        self._steps += 1
+        for g in self.param_groups:
+            refresh = self._steps == 1 or self._steps % g["update_freq"] == 0
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = -p.grad if g["maximize"] else p.grad
+                if g["weight_decay"]:
+                    grad = grad.add(p, alpha=g["weight_decay"])
+                upd = self.preconditioned(p, grad, g["damping"], refresh)
+                if g["momentum"] > 0:
+                    st = self.state[p]
+                    if "momentum_buf" not in st:
+                        st["momentum_buf"] = upd.clone()
+                    else:
+                        st["momentum_buf"].mul_(g["momentum"]).add_(upd)
+                    upd = st["momentum_buf"]
+                p.add_(upd, alpha=-g["lr"])
         return loss
 
 

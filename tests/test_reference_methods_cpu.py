@@ -271,3 +271,109 @@ def test_ir_graph_builder_and_backend_autotuner():
         J.Autotuner().tune(g, [x, y])
     with pytest.raises(J.JitError):
         J.Autotuner().with_candidate("broken", Broken()).tune(g, [x, y])
+
+
+def test_kfac_preconditioner_equals_the_dense_kronecker_fisher_and_trains():
+    # ferrotorch-optim/src/natural_gradient.rs: F_W ~ A (x) G, natural gradient = G_d^-1 grad A_d^-1
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(5, 3)
+    a, g = torch.randn(16, 5), torch.randn(16, 3)
+    opt = O.Kfac(lin.parameters(), lr=0.1, damping=0.05, momentum=0.0, stat_decay=0.5, update_freq=1)
+    opt.update_factors(lin.weight, a, g)
+    A, G = a.t() @ a / 16, g.t() @ g / 16
+    grad = torch.randn(3, 5)
+    # row-major vec: (G_d^-1 (x) A_d^-1) vec(grad) = vec(G_d^-1 grad A_d^-1)
+    dense = torch.kron(G + 0.05 * torch.eye(3), A + 0.05 * torch.eye(5))
+    want = torch.linalg.solve(dense, grad.reshape(-1)).reshape(3, 5)
+    torch.testing.assert_close(opt.preconditioned(lin.weight, grad, 0.05), want, rtol=1e-4, atol=1e-5)
+    # the first update seeds, later ones blend with stat_decay
+    a2, g2 = torch.randn(16, 5), torch.randn(16, 3)
+    opt.update_factors(lin.weight, a2, g2)
+    torch.testing.assert_close(opt._factors[id(lin.weight)]["A"], 0.5 * A + 0.5 * (a2.t() @ a2 / 16))
+    # a step: the weight moves along the preconditioned gradient, the bias (no factors) along the plain one
+    w0, b0 = lin.weight.detach().clone(), lin.bias.detach().clone()
+    lin.weight.grad, lin.bias.grad = grad.clone(), torch.ones(3)
+    pre = opt.preconditioned(lin.weight, grad, 0.05)
+    opt.step()
+    torch.testing.assert_close(lin.weight.detach(), w0 - 0.1 * pre)
+    torch.testing.assert_close(lin.bias.detach(), b0 - 0.1)
+    with pytest.raises(ValueError):
+        opt.update_factors(lin.weight, a[:, :4], g)
+    with pytest.raises(ValueError):
+        opt.update_factors(lin.weight, a[0], g[0])
+    # hooks: factors of every Linear are collected during forward / backward; the loss goes down
+    torch.manual_seed(1)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh(), torch.nn.Linear(8, 2))
+    x, y = torch.randn(64, 6), torch.randn(64, 2)
+    cfg = O.KfacConfig().with_lr(0.05).with_damping(1e-2).with_momentum(0.5).with_update_freq(2).with_weight_decay(1e-4)
+    k = cfg.build(net.parameters()).watch(net)
+    losses = []
+    for _ in range(25):
+        k.zero_grad()
+        loss = torch.nn.functional.mse_loss(net(x), y)
+        loss.backward()
+        k.step()
+        losses.append(float(loss.detach()))
+    assert len(k._factors) == 2 and losses[-1] < 0.6 * losses[0]
+    k.unwatch()
+    # maximize climbs
+    p = torch.nn.Parameter(torch.tensor([1.0]))
+    up = O.Kfac([p], lr=0.1, momentum=0.0, maximize=True)
+    p.grad = torch.tensor([2.0])
+    up.step()
+    assert float(p) == pytest.approx(1.2)
+
+
+def test_muon_and_adafactor_options():
+    # ferrotorch-optim/src/muon.rs (ns_coefficients, decoupled_weight_decay, strict_2d, maximize); adafactor.rs
+    from ferrotorch_b200.optim.extra import CUBIC_NS, QUINTIC_NS, _newton_schulz
+
+    torch.manual_seed(0)
+    m = torch.randn(6, 4)
+    for coeff, steps in ((CUBIC_NS, 30), (QUINTIC_NS, 8)):
+        q = _newton_schulz(m, steps, coeff)
+        sv = torch.linalg.svdvals(q)
+        assert float(sv.min()) > 0.6 and float(sv.max()) < 1.3            # singular values driven towards one
+    cubic = _newton_schulz(m, 1, CUBIC_NS)
+    x = m / (m.norm() + 1e-7)
+    torch.testing.assert_close(cubic, 1.5 * x - 0.5 * x @ (x.t() @ x))          # one cubic step: G (3 I - G^T G) / 2
+    w = torch.nn.Parameter(torch.randn(4, 3))
+    b = torch.nn.Parameter(torch.randn(4))
+    with pytest.raises(ValueError):
+        O.Muon([w, b], strict_2d=True)
+    with pytest.raises(ValueError):
+        O.Muon([w], ns_coefficients=(1.0, 2.0))
+    # folded (L2) weight decay goes through the orthogonalisation, decoupled decay shrinks the weight directly
+    g = torch.randn(4, 3)
+    outs = {}
+    for dec in (True, False):
+        p = torch.nn.Parameter(w.detach().clone())
+        opt = O.MuonConfig().with_lr(0.1).with_momentum(0.0).with_nesterov(False).with_weight_decay(0.5) \
+            .with_decoupled_weight_decay(dec).build([p])
+        p.grad = g.clone()
+        opt.step()
+        outs[dec] = p.detach().clone()
+    scale = max(1.0, 4 / 3) ** 0.5
+    torch.testing.assert_close(outs[True], w.detach() * (1 - 0.05) - 0.1 * scale * _newton_schulz(g, 5))
+    torch.testing.assert_close(outs[False], w.detach() - 0.1 * scale * _newton_schulz(g + 0.5 * w.detach(), 5))
+    pm = torch.nn.Parameter(w.detach().clone())
+    om = O.Muon([pm], lr=0.1, momentum=0.0, nesterov=False, maximize=True)
+    pm.grad = g.clone()
+    om.step()
+    torch.testing.assert_close(pm.detach(), w.detach() + 0.1 * scale * _newton_schulz(g, 5))
+    # Adafactor: relative step size and first moment
+    p = torch.nn.Parameter(torch.full((3, 2), 2.0))
+    af = O.AdafactorConfig().with_lr(None).with_relative_step(True).with_warmup_init(True).with_beta1(0.9).build([p])
+    p.grad = torch.ones(3, 2)
+    af.step()
+    # step 1: u = g / sqrt(v) clipped to rms 1 -> ones; first moment 0.1 * u; lr = min(1e-6, 1) * max(1e-3, rms(p) = 2)
+    torch.testing.assert_close(p.detach(), torch.full((3, 2), 2.0 - 2e-6 * 0.1), rtol=0, atol=1e-9)
+    assert "exp_avg" in af.state[p]
+    p2 = torch.nn.Parameter(torch.full((3, 2), 2.0))
+    af2 = O.Adafactor([p2], lr=None)
+    p2.grad = torch.ones(3, 2)
+    af2.step()
+    torch.testing.assert_close(p2.detach(), torch.full((3, 2), 2.0 - 1e-2 * 2.0), rtol=1e-5, atol=1e-6)
+    assert O.AdafactorConfig().with_decay_rate(0.7).beta2_decay == -0.7 and O.AdafactorConfig().with_eps_rms(0.5).eps == (1e-30, 0.5)
+    assert O.GradScalerConfig().with_init_scale(128.0).with_enabled(False).init_scale == 128.0
+    assert O.AdamWConfig().with_lr(3e-4).with_betas((0.9, 0.95)).build([p]).defaults["betas"] == (0.9, 0.95)
