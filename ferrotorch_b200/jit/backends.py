@@ -69,12 +69,26 @@ class MemoryPlan:
     n_slots: int
     peak_bytes: int
 
+    naive_bytes: int = 0
+
     @classmethod
     def of(cls, graph: IrGraph) -> "MemoryPlan":
-        return cls(**plan_memory(graph))
+        naive = 0
+        for i in graph.order:
+            n = graph.nodes[i]
+            if n.op not in ("input", "const") and n.shape is not None:
+                numel = 1
+                for d in n.shape:
+                    numel *= int(d)
+                naive += numel * torch.empty(0, dtype=n.dtype or torch.float32).element_size()
+        return cls(**plan_memory(graph), naive_bytes=naive)
 
     def reuse_count(self) -> int:
         return len(self.slot_of) - self.n_slots
+
+    def savings_percent(self) -> float:
+        """How much smaller the planned peak is than one buffer per intermediate value, in percent."""
+        return 100.0 * (1.0 - self.peak_bytes / self.naive_bytes) if self.naive_bytes else 0.0
 
 
 # --------------------------------------------------------------------------- loop IR
@@ -111,6 +125,44 @@ class Expr:
     @staticmethod
     def binary(op: BinOpKind, a: "Expr", b: "Expr") -> "Expr":
         return Expr("binary", op, (a, b))
+
+    # the reference's constructor names (ferrotorch-jit/src/codegen_ir.rs ``impl Expr``)
+    @staticmethod
+    def var(index: int) -> "Expr":
+        return Expr.load(index)
+
+    @staticmethod
+    def constant(value: float) -> "Expr":
+        return Expr.const(value)
+
+    @staticmethod
+    def int(value) -> "Expr":
+        return Expr.const(float(value))
+
+    @staticmethod
+    def bin(op, a: "Expr", b: "Expr") -> "Expr":
+        return Expr.binary(op if isinstance(op, BinOpKind) else BinOpKind(op), a, b)
+
+    @staticmethod
+    def call(fn, a: "Expr") -> "Expr":
+        """A unary function by kind or by name (``"exp"``, ``"relu"`` ...)."""
+        return Expr.unary(fn if isinstance(fn, UnaryOpKind) else UnaryOpKind(fn), a)
+
+    @staticmethod
+    def sum(terms) -> "Expr":
+        terms = list(terms)
+        out = terms[0] if terms else Expr.const(0.0)
+        for t in terms[1:]:
+            out = Expr.binary(BinOpKind.Add, out, t)
+        return out
+
+    @staticmethod
+    def prod(terms) -> "Expr":
+        terms = list(terms)
+        out = terms[0] if terms else Expr.const(1.0)
+        for t in terms[1:]:
+            out = Expr.binary(BinOpKind.Mul, out, t)
+        return out
 
     def depth(self) -> int:
         return 1 + max((a.depth() for a in self.args), default=0)
@@ -243,6 +295,30 @@ class FusedChain:
     def generate_source(self, dtype: torch.dtype = torch.float32, vec: int = 4) -> str:
         return codegen.generate_source(self.program(), [dtype], ["full"], dtype, vec)
 
+    # the reference's names (fusion.rs ``impl FusedChain``).  Its device code is PTX text and its host code
+    # Rust text; here both generators emit what this package compiles: CUDA C for sm_100a and a Python
+    # function over torch ops.
+    def len(self) -> int:
+        return len(self.ops)
+
+    def is_empty(self) -> bool:
+        return not self.ops
+
+    def execute_cpu(self, x: torch.Tensor) -> torch.Tensor:
+        return CpuCodegen().compile(self.loop_ir(), "fused_chain")(x.detach().cpu())
+
+    def generate_ptx(self) -> str:
+        return self.generate_source(torch.float32)
+
+    def generate_ptx_named(self, name: str) -> str:
+        return GpuCodegen().generate(self.loop_ir(), name)
+
+    def generate_ptx_f64_named(self, name: str) -> str:
+        return GpuCodegen().generate(self.loop_ir(), name).replace("float", "double")
+
+    def generate_rust(self) -> str:
+        return CpuCodegen().generate(self.loop_ir(), "fused_chain")
+
 
 class ReductionKind(enum.Enum):
     Sum = "sum"; Mean = "mean"; Max = "max"; Min = "min"; Prod = "prod"  # noqa: E702
@@ -299,6 +375,13 @@ class CompiledGraph:
 
     def __call__(self, inputs) -> list:
         return self.execute(inputs)
+
+    def num_inputs(self) -> int:
+        return self.graph.count("input")
+
+    def output_shape(self):
+        n = self.graph.nodes[self.graph.outputs[0]]
+        return tuple(n.shape) if n.shape is not None else None
 
 
 class Codegen:
@@ -380,6 +463,30 @@ class InductorCompileStatus(enum.Enum):
     Interpreted = "interpreted"      # nothing to generate
 
 
+InductorCompileStatus.is_compiled = lambda self: self is InductorCompileStatus.Compiled
+InductorCompileStatus.is_fallback = lambda self: self is not InductorCompileStatus.Compiled
+
+
+@dataclass
+class InductorCompileOutcome:
+    """What ``InductorBackend.compile_with_status`` returns: the runnable graph and how much of it went
+    through generated source (codegen.rs ``InductorCompileStatus::{Compiled, Fallback}``)."""
+    status: InductorCompileStatus
+    graph: "CompiledGraph"
+    reason: str = ""
+
+    def is_compiled(self) -> bool:
+        return self.status.is_compiled()
+
+    def is_fallback(self) -> bool:
+        return self.status.is_fallback()
+
+    def compiled_graph(self) -> "CompiledGraph":
+        return self.graph
+
+    into_compiled_graph = compiled_graph
+
+
 class InductorBackend(Codegen):
     """Fused groups -> :class:`LoopIR` -> source for the target; the rest of the graph as in
     :class:`NativeBackend`.  ``sources`` of the result maps node id -> generated text."""
@@ -414,6 +521,28 @@ class InductorBackend(Codegen):
         self.status = (InductorCompileStatus.Interpreted if total == 0 else
                        InductorCompileStatus.Compiled if done == total else InductorCompileStatus.Partial)
         return CompiledGraph(graph, steps, self.name, sources)
+
+
+def _inductor_with_block_size(self, block_size: int) -> "InductorBackend":
+    self.block_size = int(block_size)
+    return self
+
+
+def _inductor_compile_with_status(self, graph: IrGraph) -> InductorCompileOutcome:
+    compiled = self.compile(graph)
+    reason = {InductorCompileStatus.Compiled: "", InductorCompileStatus.Partial: "some fused groups run through the native runner",
+              InductorCompileStatus.Interpreted: "the graph has no fused group to generate code for"}[self.status]
+    return InductorCompileOutcome(self.status, compiled, reason)
+
+
+def _inductor_generate(self, graph: IrGraph) -> dict:
+    """Generated source per fused node, without keeping the runnable graph."""
+    return dict(self.compile(graph).sources)
+
+
+InductorBackend.with_block_size = _inductor_with_block_size
+InductorBackend.compile_with_status = _inductor_compile_with_status
+InductorBackend.generate = _inductor_generate
 
 
 def compile_loop_ir_kernel(ir: LoopIR, name: str = "fused_loop"):
@@ -484,11 +613,19 @@ class AutotuneKey:
     def of(cls, module: TracedModule) -> "AutotuneKey":
         return cls(tuple(module.graph.ops()), tuple(module.guard))
 
+    @classmethod
+    def from_graph(cls, graph: IrGraph, inputs=()) -> "AutotuneKey":
+        return cls(tuple(graph.ops()) + (graph.fingerprint(),), tuple((tuple(t.shape), t.dtype) for t in inputs))
+
 
 @dataclass
 class AutotuneCandidate:
     block_size: int
     ms: float = float("nan")
+
+    @property
+    def name(self) -> str:
+        return "block_size=%d" % self.block_size
 
 
 @dataclass
@@ -496,6 +633,16 @@ class AutotuneResult:
     key: AutotuneKey
     best: AutotuneCandidate
     candidates: list
+
+    def winner_name(self) -> str:
+        return self.best.name
+
+    def winner_time(self) -> float:
+        """Seconds per call of the winner (NaN when nothing was timed)."""
+        return self.best.ms * 1e-3
+
+    def all_timings(self) -> list:
+        return [(c.name, c.ms * 1e-3) for c in self.candidates]
 
 
 @dataclass
@@ -509,6 +656,15 @@ class BackendTuneResult:
     compiled: "CompiledGraph"
     from_cache: bool = False
     failed: dict = field(default_factory=dict)
+
+    def winner_name(self) -> str:
+        return self.winner
+
+    def winner_time(self) -> float:
+        return self.median_s
+
+    def winner_compiled(self) -> "CompiledGraph":
+        return self.compiled
 
 
 def autotune(module: TracedModule, inputs, candidates=(128, 256, 512), iters: int = 5, cache: dict | None = None) -> AutotuneResult:

@@ -157,6 +157,29 @@ class CompiledKernel:
         if err != driver.CUresult.CUDA_SUCCESS:
             raise RuntimeError("cuModuleGetFunction failed: %s" % err)
 
+    n_inputs: int | None = None        # set by the generator that built the kernel, when it knows
+
+    def num_inputs(self) -> int | None:
+        return self.n_inputs
+
+    @staticmethod
+    def output_len(*inputs: torch.Tensor) -> int:
+        """Elements of the output for these operands: the broadcast of their shapes."""
+        n = 1
+        for d in torch.broadcast_shapes(*[t.shape for t in inputs]):
+            n *= int(d)
+        return n
+
+    def execute(self, inputs, out: torch.Tensor | None = None, block: int = 256) -> torch.Tensor:
+        """Launch over contiguous device operands of the output's shape (one row of ``row = 1`` columns)."""
+        shape = torch.broadcast_shapes(*[t.shape for t in inputs])
+        xs = [t.expand(shape).contiguous() for t in inputs]
+        out = out if out is not None else torch.empty(shape, dtype=xs[0].dtype, device=xs[0].device)
+        n = out.numel()
+        self.launch([t.data_ptr() for t in xs] + [out.data_ptr()], n, 1, max(1, (n + block - 1) // block), block,
+                    torch.cuda.current_stream(out.device).cuda_stream)
+        return out
+
     def launch(self, ptrs, n: int, row: int, grid: int, block: int, stream: int) -> None:
         import ctypes
 

@@ -29,6 +29,34 @@ class Node:
     dtype: torch.dtype | None = None
 
 
+_FUNCTION_HOMES = ("torch", "torch.nn.functional", "operator", "_operator", "torch.linalg", "torch.special", "math")
+
+
+def _function_reference(fn) -> str | None:
+    """``"module:name"`` for a function of torch / operator / math that can be found again by that name."""
+    import importlib
+
+    name, mod = getattr(fn, "__name__", None), getattr(fn, "__module__", None)
+    if not callable(fn) or name is None:
+        return None
+    for home in ((mod,) if mod in _FUNCTION_HOMES else ()) + _FUNCTION_HOMES:
+        try:
+            if getattr(importlib.import_module(home), name, None) is fn:
+                return "%s:%s" % (home, name)
+        except ImportError:
+            continue
+    return None
+
+
+def _resolve_function(ref: str):
+    import importlib
+
+    home, name = ref.split(":", 1)
+    if home not in _FUNCTION_HOMES:
+        raise ValueError("serialised graph names a function outside the allowed modules: %r" % ref)
+    return getattr(importlib.import_module(home), name)
+
+
 class IrGraph:
     def __init__(self):
         self.nodes: dict[int, Node] = {}
@@ -137,10 +165,23 @@ class IrGraph:
 
         h = hashlib.blake2b(digest_size=8)
         pos = {i: k for k, i in enumerate(self.order)}
+
+        def canon(v):
+            if isinstance(v, (int, float, str, bool, type(None))):
+                return v
+            if isinstance(v, (list, tuple)):
+                return tuple(canon(x) for x in v)
+            if isinstance(v, dict):
+                return tuple(sorted((str(k), canon(x)) for k, x in v.items()))
+            if isinstance(v, Node):
+                return ("node", pos.get(v.id, -1))
+            if isinstance(v, torch.Tensor):
+                return ("tensor", tuple(v.shape), str(v.dtype))
+            return ("object", _function_reference(v) or type(v).__name__)
+
         for i in self.order:
             n = self.nodes[i]
-            scal = sorted((k, repr(v)) for k, v in n.attrs.items() if isinstance(v, (int, float, str, bool, tuple, list)))
-            h.update(repr((n.op, [pos[j] for j in n.inputs], n.shape, str(n.dtype), scal)).encode())
+            h.update(repr((n.op, [pos[j] for j in n.inputs], n.shape, str(n.dtype), canon(n.attrs))).encode())
         h.update(repr([pos[o] for o in self.outputs]).encode())
         return int.from_bytes(h.digest(), "little")
 
@@ -159,22 +200,39 @@ class IrGraph:
 
     # ---- serialisation (the reference has a binary IR format; structure only, constants and
     # opaque call targets are referenced by name)
-    def to_json(self) -> str:
+    def to_json(self, strict: bool = False) -> str:
+        """``strict``: raise on a value that cannot be found again in another process (a Python object
+        that is neither a tensor, a node, plain data nor a named torch / operator function) instead of
+        writing a placeholder."""
         def enc(v):
             if isinstance(v, torch.Tensor):
                 return {"__tensor__": list(v.shape), "dtype": str(v.dtype)}
+            if isinstance(v, Node):
+                return {"__node__": v.id}
             if isinstance(v, (int, float, str, bool, type(None))):
                 return v
             if isinstance(v, (list, tuple)):
                 return [enc(x) for x in v]
             if isinstance(v, dict):
                 return {str(k): enc(x) for k, x in v.items()}
+            if isinstance(v, torch.dtype):
+                return {"__dtype__": str(v)}
+            ref = _function_reference(v)
+            if ref is not None:
+                return {"__fn__": ref}
+            if strict:
+                raise ValueError("%s object %r" % (type(v).__name__, getattr(v, "__name__", v)))
             return {"__opaque__": getattr(v, "__name__", type(v).__name__)}
 
-        return json.dumps({"nodes": [{"id": n.id, "op": n.op, "inputs": n.inputs, "attrs": enc(n.attrs),
-                                      "shape": list(n.shape) if n.shape is not None else None,
-                                      "dtype": str(n.dtype) if n.dtype is not None else None}
-                                     for n in (self.nodes[i] for i in self.order)], "outputs": self.outputs})
+        rows = []
+        for n in (self.nodes[i] for i in self.order):
+            try:
+                attrs = enc(n.attrs)
+            except ValueError as e:
+                raise ValueError("cannot serialise a graph that calls opaque objects: node %d (%s): %s" % (n.id, n.op, e)) from None
+            rows.append({"id": n.id, "op": n.op, "inputs": n.inputs, "attrs": attrs,
+                         "shape": list(n.shape) if n.shape is not None else None, "dtype": str(n.dtype) if n.dtype is not None else None})
+        return json.dumps({"nodes": rows, "outputs": self.outputs})
 
     @classmethod
     def from_json(cls, text: str, constants: dict | None = None) -> "IrGraph":
@@ -183,9 +241,23 @@ class IrGraph:
         attrs to merge); nodes without an entry keep the placeholder dictionaries."""
         d = json.loads(text)
         g = cls()
+
+        def dec(v):
+            if isinstance(v, dict):
+                if "__fn__" in v:
+                    return _resolve_function(v["__fn__"])
+                if "__node__" in v:
+                    return g.nodes[v["__node__"]]                   # producers come before their users
+                if "__dtype__" in v:
+                    return getattr(torch, v["__dtype__"].split(".")[-1])
+                return {k: dec(x) for k, x in v.items()}
+            if isinstance(v, list):
+                return tuple(dec(x) for x in v)
+            return v
+
         for nd in d["nodes"]:
             dt = getattr(torch, nd["dtype"].split(".")[-1]) if nd["dtype"] else None
-            n = Node(nd["id"], nd["op"], list(nd["inputs"]), dict(nd["attrs"]),
+            n = Node(nd["id"], nd["op"], list(nd["inputs"]), dec(nd["attrs"]),
                      tuple(nd["shape"]) if nd["shape"] is not None else None, dt)
             if constants and n.id in constants:
                 n.attrs.update(constants[n.id])
@@ -194,6 +266,45 @@ class IrGraph:
             g._next = max(g._next, n.id + 1)
         g.outputs = list(d["outputs"])
         return g
+
+
+    # ---- binary form (the reference's ``IrGraph::serialize`` / ``deserialize``, ferrotorch-jit/src/serialize.rs):
+    # ``FTIR``, a version word, the length of the structure, the structure as JSON, then every tensor
+    # constant in the state-dict byte layout.  Graphs that still call opaque Python objects cannot be
+    # written: their targets do not exist in another process.
+    _MAGIC = b"FTIR"
+
+    def serialize(self) -> bytes:
+        import struct
+
+        from ..serialize.state import dumps_state_dict
+
+        consts = {}
+        for i in self.order:
+            for k, v in self.nodes[i].attrs.items():
+                if isinstance(v, torch.Tensor):
+                    consts["%d.%s" % (i, k)] = v.detach().contiguous()
+        js = self.to_json(strict=True).encode()
+        return self._MAGIC + struct.pack("<IQ", 1, len(js)) + js + dumps_state_dict(consts)
+
+    @classmethod
+    def deserialize(cls, data: bytes) -> "IrGraph":
+        import struct
+
+        from ..serialize.state import loads_state_dict
+
+        if len(data) < 16 or data[:4] != cls._MAGIC:
+            raise ValueError("not a serialised IR graph (bad magic)")
+        version, n = struct.unpack("<IQ", data[4:16])
+        if version != 1:
+            raise ValueError("IR graph format version %d is not supported" % version)
+        if 16 + n > len(data):
+            raise ValueError("serialised IR graph is truncated")
+        consts: dict = {}
+        for name, t in loads_state_dict(bytes(data[16 + n:])).items():
+            nid, key = name.split(".", 1)
+            consts.setdefault(int(nid), {})[key] = t.clone()
+        return cls.from_json(data[16:16 + n].decode(), consts)
 
 
 # --------------------------------------------------------------------------- passes

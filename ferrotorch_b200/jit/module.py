@@ -31,6 +31,10 @@ class CompileConfig:
     fallback_to_eager: bool = True      # on an untraceable callable or a failed guard
     block_size: int = 256
 
+    @classmethod
+    def from_optimization(cls, optimization: OptimizationConfig) -> "CompileConfig":
+        return cls(optimization=optimization)
+
 
 _FN_UNARY = {torch.relu: "relu", nn.functional.relu: "relu", torch.sigmoid: "sigmoid", nn.functional.sigmoid: "sigmoid",
              torch.tanh: "tanh", nn.functional.tanh: "tanh", nn.functional.gelu: "gelu", nn.functional.silu: "silu",
@@ -217,6 +221,68 @@ class TracedModule(nn.Module):
         env = _interpret(self.graph, inputs, block=self.cfg.block_size)
         outs = [env[i] for i in self.graph.outputs]
         return torch.utils._pytree.tree_unflatten(outs, self.graph.output_spec)
+
+    # ---- the reference's accessors and persistence (ferrotorch-jit/src/module.rs ``impl TracedModule``)
+    def input_count(self) -> int:
+        return len(self.guard)
+
+    def output_shape(self):
+        """Shape of the (first) output as traced, when the graph recorded it."""
+        n = self.graph.nodes[self.graph.outputs[0]]
+        return tuple(n.shape) if n.shape is not None else None
+
+    def forward_multi(self, inputs) -> list:
+        """Every graph output as a flat list (``forward`` rebuilds the traced function's return structure)."""
+        sig = tuple((tuple(t.shape), t.dtype) for t in inputs if isinstance(t, torch.Tensor))
+        if sig != self.guard:
+            raise JitError("input signature %r does not match the traced %r" % (sig, self.guard))
+        env = _interpret(self.graph, list(inputs), block=self.cfg.block_size)
+        return [env[i] for i in self.graph.outputs]
+
+    def to_bytes(self) -> bytes:
+        """The optimised graph with its constants, the input guard and the output structure.  A module
+        whose graph still calls Python objects (an untraced sub-module) cannot be written."""
+        import json
+        import struct
+
+        try:
+            body = self.graph.serialize()
+        except ValueError as e:
+            raise JitError(str(e)) from e
+        meta = json.dumps({"guard": [[list(s), str(d)] for s, d in self.guard], "block_size": self.cfg.block_size,
+                           "output_spec": torch.utils._pytree.treespec_dumps(self.graph.output_spec)}).encode()
+        return b"FTJM" + struct.pack("<Q", len(meta)) + meta + body
+
+    @classmethod
+    def from_bytes(cls, data: bytes) -> "TracedModule":
+        import json
+        import struct
+
+        if len(data) < 12 or data[:4] != b"FTJM":
+            raise JitError("not a serialised traced module (bad magic)")
+        (n,) = struct.unpack("<Q", data[4:12])
+        meta = json.loads(data[12:12 + n].decode())
+        try:
+            graph = IrGraph.deserialize(data[12 + n:])
+        except ValueError as e:
+            raise JitError(str(e)) from e
+        graph.output_spec = torch.utils._pytree.treespec_loads(meta["output_spec"])
+        m = cls.__new__(cls)
+        nn.Module.__init__(m)
+        m.graph, m.original, m.stats = graph, None, {}
+        m.cfg = CompileConfig(fallback_to_eager=False, block_size=int(meta["block_size"]))
+        m.guard = tuple((tuple(s), getattr(torch, d.split(".")[-1])) for s, d in meta["guard"])
+        m.guard_failures = 0
+        return m
+
+    def save(self, path: str) -> None:
+        with open(path, "wb") as f:
+            f.write(self.to_bytes())
+
+    @classmethod
+    def load(cls, path: str) -> "TracedModule":
+        with open(path, "rb") as f:
+            return cls.from_bytes(f.read())
 
 
 class EagerFallback(nn.Module):
