@@ -342,6 +342,27 @@ class GradientAccumulator:
             return True
         return False
 
+    # ---- grad_accumulator.rs: the pieces of ``backward`` for loops that call ``backward`` themselves
+    def accumulation_steps(self) -> int:
+        return self.steps
+
+    def current_step(self) -> int:
+        return self._n
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return loss / self.steps
+
+    def should_step(self) -> bool:
+        """Count one micro-batch; true when the optimizer should step now (the counter starts over)."""
+        self._n += 1
+        if self._n >= self.steps:
+            self._n = 0
+            return True
+        return False
+
+    def reset(self) -> None:
+        self._n = 0
+
 
 class WarmupLR(LambdaLR):
     """Linear warm-up from ``start_factor`` to 1 over ``warmup_steps``."""

@@ -23,7 +23,7 @@ from concurrent.futures import Future
 import torch
 
 from ..serialize.state import load_safetensors, save_safetensors
-from .backend import Group, SizeMismatch
+from .backend import Group, InvalidRank, SizeMismatch
 
 
 # --------------------------------------------------------------------------- sharded checkpoints
@@ -168,9 +168,32 @@ def save_reference_distributed(directory: str, local_state: dict[str, torch.Tens
 
 
 class AsyncDistributedCheckpointer:
-    def __init__(self):
+    """Sharded saves on a helper thread from a host snapshot of the tensors.  Built empty (every
+    ``save_async`` names its directory and rank) or, as the reference's ``AsyncCheckpointer::new``
+    (ferrotorch-distributed/src/checkpoint.rs:757), bound to ``(directory, rank, world_size)`` so that
+    ``save(state, shard_dims)`` needs nothing else."""
+
+    def __init__(self, directory: str | None = None, rank: int = 0, world_size: int = 1):
         self._thread: threading.Thread | None = None
         self._err: list = []
+        self._dir, self._rank, self._world = directory, rank, world_size
+
+    def dir(self) -> str | None:
+        return self._dir
+
+    def rank(self) -> int:
+        return self._rank
+
+    def world_size(self) -> int:
+        return self._world
+
+    def save(self, local_state, shard_dims, extra=None) -> "AsyncDistributedCheckpointer":
+        if self._dir is None:
+            raise ValueError("AsyncDistributedCheckpointer.save: built without a directory; use save_async")
+        return self.save_async(self._dir, local_state, shard_dims, self._rank, self._world, extra)
+
+    def is_saving(self) -> bool:
+        return not self.is_done()
 
     def save_async(self, directory, local_state, shard_dims, rank, world_size, extra=None) -> "AsyncDistributedCheckpointer":
         self.wait()
@@ -201,8 +224,9 @@ class AsyncDistributedCheckpointer:
 class PendingCollective:
     """A collective running on a helper thread; ``wait()`` returns its result or re-raises."""
 
-    def __init__(self, fn, *args):
+    def __init__(self, fn, *args, op_name: str | None = None):
         self._fut: Future = Future()
+        self._op_name = op_name or getattr(fn, "__name__", "collective")
 
         def run():
             try:
@@ -214,6 +238,9 @@ class PendingCollective:
 
     def is_done(self) -> bool:
         return self._fut.done()
+
+    def op_name(self) -> str:
+        return self._op_name
 
     def wait(self, timeout: float | None = None):
         return self._fut.result(timeout)
@@ -366,10 +393,48 @@ def _recv_response(sock: socket.socket):
     return req_id, status == 0, _recv_exact(sock, _recv_len(sock))
 
 
-class RpcAgent:
-    """Serve registered handlers on a TCP port and call handlers of other agents by name."""
+class _ByteSource:
+    """``recv`` over a bytes object, so that the frame parsers also read frames held in memory."""
 
-    def __init__(self, name: str, host: str = "127.0.0.1", port: int = 0):
+    def __init__(self, data: bytes):
+        self._data, self._pos = bytes(data), 0
+
+    def recv(self, n: int) -> bytes:
+        out = self._data[self._pos:self._pos + n]
+        self._pos += len(out)
+        return out
+
+
+class _ByteSink:
+    def __init__(self):
+        self.data = bytearray()
+
+    def sendall(self, b: bytes) -> None:
+        self.data += b
+
+
+def encode_rpc_request(req_id: int, fn_name: str, *args, **kwargs) -> bytes:
+    """One request frame (what ``rpc_sync`` puts on the wire) as bytes."""
+    sink = _ByteSink()
+    _send_request(sink, req_id, fn_name, _encode((list(args), kwargs)))
+    return bytes(sink.data)
+
+
+def decode_rpc_response(frame: bytes):
+    """``(request id, ok, value)`` of a response frame."""
+    req_id, ok, body = _recv_response(_ByteSource(frame))
+    return req_id, ok, _decode(body)
+
+
+class RpcAgent:
+    """Serve registered handlers on a TCP port and call handlers of other agents by name.  ``rank`` /
+    ``world_size`` label the agent inside a job (the reference's agent sits on a rank-addressed
+    back-end, ferrotorch-distributed/src/rpc.rs:372-610; this one is addressed by ``(host, port)``)."""
+
+    def __init__(self, name: str, host: str = "127.0.0.1", port: int = 0, rank: int = 0, world_size: int = 1):
+        if not 0 <= rank < world_size:
+            raise InvalidRank("rank %d outside a world of %d" % (rank, world_size))
+        self._rank, self._world = rank, world_size
         self.name, self.handlers = name, {}
         self._srv = socket.socket()
         self._srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
@@ -381,6 +446,34 @@ class RpcAgent:
 
     def register(self, fn_name: str, fn) -> None:
         self.handlers[fn_name] = fn
+
+    def rank(self) -> int:
+        return self._rank
+
+    def world_size(self) -> int:
+        return self._world
+
+    def handle_request(self, src_rank: int, request_data: bytes) -> bytes:
+        """Server-side dispatch of one request frame held in memory (rpc.rs:561): looks the handler up,
+        runs it, and returns the response frame that would go back to ``src_rank``.  Failures (unknown
+        handler, handler exception, malformed frame) come back as an error response, not as an exception."""
+        req_id = 0
+        try:
+            req_id, fn_name, payload = _recv_request(_ByteSource(request_data))
+            if fn_name not in self.handlers:
+                ok, res = False, "no handler %r on %s (request from rank %d)" % (fn_name, self.name, src_rank)
+            else:
+                args, kwargs = _decode(payload)
+                ok, res = True, self.handlers[fn_name](*args, **kwargs)
+        except BaseException as e:  # noqa: BLE001 - reported to the caller in the response
+            ok, res = False, repr(e)
+        sink = _ByteSink()
+        try:
+            body = _encode(res)
+        except TypeError as e:
+            ok, body = False, _encode("handler result cannot be sent: %s" % e)
+        _send_response(sink, req_id, ok, body)
+        return bytes(sink.data)
 
     def _serve(self):
         while not self._stop:

@@ -82,6 +82,11 @@ class RunningAverage(Metric):
     def compute(self):
         return self.value if self.value is not None else float("nan")
 
+    def window_size(self) -> int:
+        """The number of recent values that carry most of the weight: ``1 / (1 - momentum)`` (the
+        reference's metric is a plain window of that many values, metric.rs ``RunningAverage``)."""
+        return max(1, round(1.0 / max(1e-12, 1.0 - self.momentum)))
+
 
 # --------------------------------------------------------------------------- history / callbacks
 @dataclass
@@ -90,6 +95,10 @@ class EpochResult:
     train: dict
     val: dict | None = None
     lr: float | None = None
+
+    @classmethod
+    def new_with_defaults(cls, epoch: int, train_loss: float, val_loss: float | None = None, lr: float | None = None) -> "EpochResult":
+        return cls(epoch, {"loss": float(train_loss)}, {"loss": float(val_loss)} if val_loss is not None else None, lr)
 
 
 @dataclass
@@ -100,6 +109,10 @@ class EvalResult:
 
     def get(self, key: str, default=None):
         return self.metrics.get(key, default)
+
+    @classmethod
+    def new_with_defaults(cls, loss: float) -> "EvalResult":
+        return cls({"loss": float(loss)})
 
 
 @dataclass
@@ -180,6 +193,14 @@ class EarlyStopping(Callback):
             if self.bad >= self.patience:
                 learner.should_stop = True
 
+    def best_loss(self):
+        """The best monitored value so far (``None`` before the first epoch)."""
+        return self.best
+
+    def wait(self) -> int:
+        """Epochs since the monitored value last improved."""
+        return self.bad
+
 
 class ProgressLogger(Callback):
     def __init__(self, every: int = 50, sink=print):
@@ -204,6 +225,26 @@ class EMACallback(Callback):
 
     def on_batch_end(self, learner, epoch, batch_idx, loss):
         self.ema.update()
+
+    # ---- the reference's accessors (callback.rs ``EmaCallback``): usable without a Learner
+    def init_from_params(self, params) -> None:
+        from ..optim import EMA
+
+        self.ema = EMA(list(params), self.decay)
+
+    def is_initialized(self) -> bool:
+        return self.ema is not None
+
+    def update_from_params(self, params=None) -> None:
+        if self.ema is None:
+            self.init_from_params(params)
+        self.ema.update(params)
+
+    def num_updates(self) -> int:
+        return self.ema.num_updates() if self.ema is not None else 0
+
+    def shadow_params(self) -> list:
+        return self.ema.shadow_params() if self.ema is not None else []
 
 
 class TensorBoardCallback(Callback):
@@ -242,6 +283,29 @@ class AmpContext:
             nn.utils.clip_grad_norm_(params, max_grad_norm)
         self.scaler.step(optimizer)
         self.scaler.update()
+
+    # ---- amp.rs:86-200
+    def is_enabled(self) -> bool:
+        """Whether reduced-precision autocast is in effect on this device type."""
+        return self.dtype in (torch.bfloat16, torch.float16)
+
+    def autocast_forward(self, fn, *args, **kwargs):
+        """Run ``fn`` under autocast and return its result."""
+        with self.autocast():
+            return fn(*args, **kwargs)
+
+    def get_scale(self) -> float:
+        return float(self.scaler.get_scale()) if self.scaler.is_enabled() else 1.0
+
+    def scaler_mut(self):
+        return self.scaler
+
+    def scaler_state_dict(self) -> dict:
+        return self.scaler.state_dict()
+
+    def load_scaler_state_dict(self, state: dict) -> None:
+        if state:
+            self.scaler.load_state_dict(state)
 
 
 # --------------------------------------------------------------------------- Learner

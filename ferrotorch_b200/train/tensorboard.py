@@ -84,9 +84,13 @@ def read_records(path: str) -> list[bytes]:
 class TensorBoardWriter:
     def __init__(self, log_dir: str):
         os.makedirs(log_dir, exist_ok=True)
+        self._log_dir = log_dir
         self.path = os.path.join(log_dir, "events.out.tfevents.%d.%s" % (int(time.time()), socket.gethostname()))
         self._f = open(self.path, "wb")
         self._f.write(record(encode_file_version_event(time.time())))
+
+    def log_dir(self) -> str:
+        return self._log_dir
 
     def add_scalar(self, tag: str, value: float, step: int) -> None:
         self._f.write(record(encode_scalar_event(tag, float(value), int(step), time.time())))

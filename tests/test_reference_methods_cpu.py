@@ -439,3 +439,72 @@ def test_jit_persistence_and_accessor_methods(tmp_path):
     tuned = J.autotune(m, (x, y))
     assert tuned.winner_name().startswith("block_size=") and len(tuned.all_timings()) == len(tuned.candidates)
     assert J.JitCompiledKernel.output_len(torch.zeros(3, 1), torch.zeros(1, 4)) == 12
+
+
+def test_train_and_distributed_accessor_methods(tmp_path):
+    # ferrotorch-train/src/{amp,callback,metric,history,tensorboard}.rs; ferrotorch-optim/src/grad_accumulator.rs;
+    # ferrotorch-distributed/src/{rpc,checkpoint,async_collective}.rs
+    from ferrotorch_b200.parallel import dist_checkpoint as DC
+
+    amp = T.AmpContext(torch.bfloat16, "cpu")
+    assert amp.is_enabled() and amp.get_scale() == 1.0 and amp.scaler_mut() is amp.scaler
+    out = amp.autocast_forward(lambda a, b: a @ b, torch.randn(4, 4), torch.randn(4, 4))
+    assert out.dtype == torch.bfloat16
+    amp.load_scaler_state_dict(amp.scaler_state_dict())
+    assert not T.AmpContext(torch.float32, "cpu").is_enabled()
+    lin = torch.nn.Linear(2, 2)
+    cb = T.EMACallback(0.5)
+    assert not cb.is_initialized() and cb.num_updates() == 0 and cb.shadow_params() == []
+    cb.init_from_params(lin.parameters())
+    w0 = lin.weight.detach().clone()
+    with torch.no_grad():
+        lin.weight += 2
+    cb.update_from_params(list(lin.parameters()))
+    assert cb.is_initialized() and cb.num_updates() == 1
+    torch.testing.assert_close(cb.shadow_params()[0], w0 + 1)
+    es = T.EarlyStopping(patience=2)
+
+    class L:
+        should_stop = False
+
+    for i, v in enumerate((1.0, 0.5, 0.7, 0.8)):
+        es.on_epoch_end(L, T.EpochResult.new_with_defaults(i, v))
+    assert es.best_loss() == 0.5 and es.wait() == 2 and L.should_stop
+    assert T.EpochResult.new_with_defaults(0, 1.0, 2.0).val == {"loss": 2.0} and T.EvalResult.new_with_defaults(0.25).get("loss") == 0.25
+    assert T.RunningAverage(0.98).window_size() == 50
+    tbw = T.TensorBoardWriter(str(tmp_path / "tb"))
+    assert tbw.log_dir() == str(tmp_path / "tb")
+    tbw.close()
+    acc = O.GradientAccumulator(3)
+    assert acc.accumulation_steps() == 3 and float(acc.scale_loss(torch.tensor(6.0))) == 2.0
+    assert [acc.should_step() for _ in range(4)] == [False, False, True, False] and acc.current_step() == 1
+    acc.reset()
+    assert acc.current_step() == 0
+    # RPC: a request frame dispatched in memory
+    agent = DC.RpcAgent("worker", rank=1, world_size=4)
+    try:
+        agent.register("add", lambda a, b=0: a + b)
+        assert (agent.rank(), agent.world_size()) == (1, 4)
+        rid, ok, val = DC.decode_rpc_response(agent.handle_request(0, DC.encode_rpc_request(7, "add", 2, b=5)))
+        assert (rid, ok, val) == (7, True, 7)
+        rid, ok, val = DC.decode_rpc_response(agent.handle_request(2, DC.encode_rpc_request(8, "nope")))
+        assert rid == 8 and not ok and "no handler" in val and "rank 2" in val
+        rid, ok, val = DC.decode_rpc_response(agent.handle_request(0, DC.encode_rpc_request(9, "add", "x", b=1)))
+        assert rid == 9 and not ok and "TypeError" in val
+        _, ok, _ = DC.decode_rpc_response(agent.handle_request(0, b"\\x00\\x01"))
+        assert not ok
+        assert DC.RpcAgent.rpc_sync(agent.address, "add", 1, b=2) == 3              # and the same handler over TCP
+    finally:
+        agent.shutdown()
+    with pytest.raises(DC.InvalidRank):
+        DC.RpcAgent("bad", rank=4, world_size=4)
+    ck = DC.AsyncDistributedCheckpointer(str(tmp_path / "ck"), rank=0, world_size=1)
+    assert (ck.dir(), ck.rank(), ck.world_size()) == (str(tmp_path / "ck"), 0, 1)
+    ck.save({"w": torch.arange(6.0).reshape(3, 2)}, {"w": 0}).wait()
+    assert not ck.is_saving()
+    state, _ = DC.load_distributed(str(tmp_path / "ck"), 0, 1)
+    assert torch.equal(state["w"], torch.arange(6.0).reshape(3, 2))
+    with pytest.raises(ValueError):
+        DC.AsyncDistributedCheckpointer().save({}, {})
+    pend = DC.PendingCollective(lambda: 5, op_name="all_reduce")
+    assert pend.wait(5) == 5 and pend.op_name() == "all_reduce"
