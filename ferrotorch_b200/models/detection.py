@@ -80,7 +80,8 @@ class ResNetFPN(nn.Module):
         self.fpn = FeaturePyramidNetwork([256 * 2 ** (i - 1) for i in self.returned], 256, extra)
         self.out_channels = 256
 
-    def forward(self, x):
+    def forward_body(self, x) -> "OrderedDict[str, torch.Tensor]":
+        """The returned stages of the ResNet body, keyed ``"0"``, ``"1"`` ... in order."""
         from .resnet import _bn
 
         b = self.body
@@ -90,7 +91,10 @@ class ResNetFPN(nn.Module):
             x = layer(x)
             if i in self.returned:
                 feats[str(self.returned.index(i))] = x
-        return self.fpn(feats)
+        return feats
+
+    def forward(self, x):
+        return self.fpn(self.forward_body(x))
 
 
 def _as_batch(images) -> torch.Tensor:
@@ -122,6 +126,11 @@ class RPNHead(nn.Module):
     def forward(self, feats: list[torch.Tensor]):
         ts = [self.conv(f) for f in feats]
         return [self.cls_logits(t) for t in ts], [self.bbox_pred(t) for t in ts]
+
+    def forward_level(self, x: torch.Tensor):
+        """One pyramid level: ``(objectness [B, A, H, W], box deltas [B, 4 A, H, W])``."""
+        t = self.conv(x)
+        return self.cls_logits(t), self.bbox_pred(t)
 
 
 class RegionProposalNetwork(nn.Module):
@@ -330,6 +339,28 @@ class FasterRCNN(nn.Module):
         size = tuple(images.shape[-2:])
         feats = self.backbone(images)
         return self.roi_heads(feats, self.rpn(feats, size), size)
+
+    # ---- pieces of the pipeline under the reference's names (faster_rcnn.rs:278-300, 470-480), for heads
+    # that reuse the features without running detection twice
+    @torch.no_grad()
+    def forward_backbone(self, images) -> dict:
+        """ResNet stages C2 .. C5 as ``{"layer1": ..., "layer4": ...}``."""
+        feats = self.backbone.forward_body(_as_batch(images))
+        return {"layer%d" % self.backbone.returned[int(k)]: v for k, v in feats.items()}
+
+    @torch.no_grad()
+    def forward_fpn(self, backbone_features: dict) -> dict:
+        """The pyramid ``{"p2": ..., "p6": ...}`` over the output of :meth:`forward_backbone`."""
+        ordered = OrderedDict((str(i), backbone_features["layer%d" % l]) for i, l in enumerate(self.backbone.returned))
+        out = self.backbone.fpn(ordered)
+        return {"p%d" % (i + 2): v for i, v in enumerate(out.values())}
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters() if p.requires_grad)
+
+    def num_classes(self) -> int:
+        """Detection classes, background (index 0) included."""
+        return self.roi_heads.box_predictor.cls_score.out_features
 
 
 class MaskRCNN(FasterRCNN):

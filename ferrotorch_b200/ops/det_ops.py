@@ -242,6 +242,31 @@ class AnchorGenerator:
     def num_anchors_per_location(self) -> list[int]:
         return [len(s) * len(a) for s, a in zip(self.sizes, self.aspect_ratios)]
 
+    # ---- the reference's entry points (ferrotorch-vision/src/models/detection/anchor_utils.rs:50-230)
+    @classmethod
+    def default_fasterrcnn(cls) -> "AnchorGenerator":
+        """Sizes 32 .. 512, one per pyramid level p2 .. p6, aspect ratios 0.5 / 1 / 2."""
+        return cls()
+
+    CANONICAL_STRIDES = (4, 8, 16, 32, 64)
+
+    def generate_anchors(self, level: int, grid_size: tuple[int, int], stride: int | None = None, dtype=torch.float32, device="cpu"
+                         ) -> torch.Tensor:
+        """Anchors of one level on a ``(h, w)`` grid with the level's canonical square stride (4, 8, ...
+        for p2, p3, ...), ``[h * w * A, 4]``."""
+        s = stride if stride is not None else self.CANONICAL_STRIDES[level]
+        fh, fw = grid_size
+        one = AnchorGenerator((self.sizes[level],), (self.aspect_ratios[level],))
+        return one((fh * s, fw * s), [(fh, fw)], dtype, device)
+
+    def generate_anchors_for_image(self, level: int, grid_size: tuple[int, int], image_size: tuple[int, int], dtype=torch.float32,
+                                   device="cpu") -> torch.Tensor:
+        """The same with strides taken from the actual image: ``image_h // grid_h`` and ``image_w // grid_w``
+        (what ``__call__`` does for every level), which differs from the canonical stride at the coarse
+        levels of images whose size is not a multiple of 64."""
+        one = AnchorGenerator((self.sizes[level],), (self.aspect_ratios[level],))
+        return one(tuple(image_size), [tuple(grid_size)], dtype, device)
+
     @staticmethod
     def _cell(scales, ratios, dtype, device):
         scales = torch.as_tensor(scales, dtype=dtype, device=device)

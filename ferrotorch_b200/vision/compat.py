@@ -58,6 +58,10 @@ class RpnConfig:
     def __init__(self, pre_nms_top_n=1000, post_nms_top_n=1000, nms_thresh=0.7, score_thresh=0.0, min_size=1e-3):
         self.__dict__.update({k: v for k, v in locals().items() if k != "self"})
 
+    @classmethod
+    def default_eval(cls) -> "RpnConfig":
+        return cls()
+
     def build(self, anchor_generator, head) -> "Rpn":
         c = self.__dict__
         return Rpn(head.cls_logits.in_channels, anchor_generator, c["pre_nms_top_n"], c["post_nms_top_n"], c["nms_thresh"],
@@ -104,6 +108,13 @@ class ModelRegistry:
         if name in self._extra:
             return self._extra[name](**kw)
         return build(name, **kw)
+
+    # the reference's method names (ferrotorch-vision/src/models/registry.rs)
+    register_model = register
+    get_model = get
+
+    def list_models(self) -> list:
+        return self.names()
 
 
 _registry = ModelRegistry()

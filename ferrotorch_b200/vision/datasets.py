@@ -210,6 +210,28 @@ class ImageFolder(Dataset):
     def __len__(self) -> int:
         return len(self.samples)
 
+    # ---- folder.rs constructors
+    @classmethod
+    def from_dir(cls, root: str, **kw) -> "ImageFolder":
+        return cls(root, **kw)
+
+    @classmethod
+    def from_dir_with_extensions(cls, root: str, extensions, **kw) -> "ImageFolder":
+        exts = tuple(e.lower() if e.startswith(".") else "." + e.lower() for e in extensions)
+        return cls(root, extensions=exts, **kw)
+
+    @classmethod
+    def from_dir_with_filter(cls, root: str, keep, **kw) -> "ImageFolder":
+        """Only the files for which ``keep(path)`` is true."""
+        ds = cls(root, **kw)
+        ds.samples = [(p, c) for p, c in ds.samples if keep(p)]
+        if not ds.samples:
+            raise FileNotFoundError("the filter left no image below %s" % root)
+        return ds
+
+    def num_classes(self) -> int:
+        return len(self.classes)
+
     def __getitem__(self, i: int):
         from .io import read_image_as_tensor
 

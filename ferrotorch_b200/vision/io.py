@@ -107,6 +107,11 @@ class VisionNormalize(nn.Module):
         self.register_buffer("mean", torch.tensor(mean, dtype=torch.float32).view(-1, 1, 1))
         self.register_buffer("std", torch.tensor(std, dtype=torch.float32).view(-1, 1, 1))
 
+    @classmethod
+    def imagenet(cls) -> "VisionNormalize":
+        """The ImageNet statistics every pretrained classifier of the zoo expects."""
+        return cls((0.485, 0.456, 0.406), (0.229, 0.224, 0.225))
+
     def forward(self, x):
         if x.shape[-3] != self.mean.shape[0]:
             raise ValueError("VisionNormalize: %d channels, %d means" % (x.shape[-3], self.mean.shape[0]))
@@ -121,6 +126,9 @@ class GaussianNoise(nn.Module):
         if sigma < 0:
             raise ValueError("GaussianNoise: sigma must be >= 0")
         self.mean, self.sigma, self.clip = mean, sigma, clip
+
+    def with_clip(self, clip: bool) -> "GaussianNoise":
+        return GaussianNoise(self.mean, self.sigma, bool(clip))
 
     def forward(self, x):
         noise = torch.randn(x.shape, generator=_gen).to(x.device, x.dtype) * self.sigma + self.mean

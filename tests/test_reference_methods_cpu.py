@@ -508,3 +508,106 @@ def test_train_and_distributed_accessor_methods(tmp_path):
         DC.AsyncDistributedCheckpointer().save({}, {})
     pend = DC.PendingCollective(lambda: 5, op_name="all_reduce")
     assert pend.wait(5) == 5 and pend.op_name() == "all_reduce"
+
+
+def test_vision_builder_and_accessor_methods(tmp_path):
+    # ferrotorch-vision/src/transforms/*.rs builders, datasets/folder.rs, models/registry.rs,
+    # models/detection/{anchor_utils,faster_rcnn,rpn}.rs
+    import torchvision.transforms.functional as TF
+    from torchvision.transforms import InterpolationMode as IM
+
+    from ferrotorch_b200 import vision as V
+    from ferrotorch_b200.ops.det_ops import AnchorGenerator
+    from ferrotorch_b200.vision import own_transforms as OT
+
+    torch.manual_seed(0)
+    x = torch.rand(3, 17, 23)
+    for ang in (30.0, -75.0, 90.0):
+        for expand in (False, True):
+            for center in (None, (5.0, 4.0)):
+                for mode, im in (("nearest", IM.NEAREST), ("bilinear", IM.BILINEAR)):
+                    a = OT.rotate(x, ang, 0.25, mode, expand, center)
+                    b = TF.rotate(x, ang, im, expand, list(center) if center else None, [0.25])
+                    assert a.shape == b.shape and float((a - b).abs().max()) < 1e-5, (ang, expand, center, mode)
+    for interp, im in (("nearest", IM.NEAREST), ("bilinear", IM.BILINEAR), ("bicubic", IM.BICUBIC)):
+        assert torch.equal(OT.Resize((9, 31)).with_interpolation(interp)(x), TF.resize(x, [9, 31], im, antialias=True))
+    with pytest.raises(ValueError):
+        OT.resize(x, 8, True, "lanczos")
+    padded = OT.CenterCrop((21, 29)).with_fill(0.5)(x)
+    assert padded.shape == (3, 21, 29) and float(padded[0, 0, 0]) == 0.5 and torch.equal(padded[:, 2:19, 3:26], x)
+    V.vision_manual_seed(3)
+    rc = OT.RandomCrop.square(20).with_padding_hw(4, 0).with_fill(0.75).with_pad_if_needed(True)
+    out = rc(x)
+    assert out.shape == (3, 20, 20) and rc.padding == (4, 0) and OT.RandomCrop.square(20).padding == 0       # builders return copies
+    assert OT.RandomCrop(8).with_padding(2).padding == 2
+    rr = OT.RandomRotation(30).with_expand(True).with_center((3, 3)).with_fill(0.1).with_interpolation("bilinear")
+    assert rr.expand and rr.center == (3.0, 3.0) and rr.mode == "bilinear" and rr(x).shape[0] == 3
+    with pytest.raises(ValueError):
+        OT.RandomRotation(30).with_interpolation("bicubic")
+    rz = OT.RandomResizedCrop(12).with_antialias(False).with_interpolation("nearest")
+    assert rz(x).shape == (3, 12, 12) and not rz.antialias
+    comp = OT.Compose([OT.RandomHorizontalFlip(1.0), OT.CenterCrop(8)])
+    assert len(comp) == comp.len() == 2 and not comp.is_empty() and OT.Compose([]).is_empty()
+    first = OT.RandomChoice([lambda t: t * 0, lambda t: t + 1]).with_p([1.0, 0.0])
+    assert float(first(x).abs().max()) == 0.0
+    with pytest.raises(ValueError):
+        OT.RandomChoice([lambda t: t]).with_p([0.5, 0.5])
+    cj = OT.ColorJitter.from_ranges(brightness=(2.0, 2.0), hue=None)
+    torch.testing.assert_close(cj(x), (x * 2).clamp(0, 1))
+    with pytest.raises(ValueError):
+        OT.ColorJitter.from_ranges(hue=(-0.7, 0.1))
+    el = OT.ElasticTransform.new_range((10.0, 20.0), (3.0, 4.0)).with_fill(0.5).with_interpolation("nearest")
+    assert el(x).shape == x.shape and el.fill == 0.5
+    with pytest.raises(ValueError):
+        OT.ElasticTransform.new_range((5.0, 1.0), (3.0, 4.0))
+    n = V.io.VisionNormalize.imagenet()
+    torch.testing.assert_close(n(torch.full((3, 2, 2), 0.485))[0], torch.zeros(2, 2))
+    assert not V.io.GaussianNoise(0.0, 0.1).with_clip(False).clip
+    # image folder constructors
+    for cls, names in (("cat", ("a.png", "b.jpg", "c.txt")), ("dog", ("d.png",))):
+        (tmp_path / cls).mkdir()
+        for nm in names:
+            if nm.endswith(".txt"):
+                (tmp_path / cls / nm).write_text("x")
+            else:
+                from PIL import Image
+
+                Image.new("RGB", (4, 4)).save(str(tmp_path / cls / nm))
+    ds = V.ImageFolder.from_dir(str(tmp_path))
+    assert len(ds) == 3 and ds.num_classes() == 2
+    assert len(V.ImageFolder.from_dir_with_extensions(str(tmp_path), ["png"])) == 2
+    assert len(V.ImageFolder.from_dir_with_filter(str(tmp_path), lambda p: "dog" in p)) == 1
+    # registry and anchors
+    reg = V.ModelRegistry()
+    reg.register_model("tiny_test_net", lambda **kw: torch.nn.Linear(2, 2))
+    assert "tiny_test_net" in reg.list_models() and isinstance(reg.get_model("tiny_test_net"), torch.nn.Linear)
+    assert V.RpnConfig.default_eval().nms_thresh == 0.7
+    g = AnchorGenerator.default_fasterrcnn()
+    grids = [(200, 272), (100, 136), (50, 68), (25, 34), (13, 17)]
+    parts = [g.generate_anchors_for_image(l, gs, (800, 1088)) for l, gs in enumerate(grids)]
+    assert torch.equal(torch.cat(parts), g((800, 1088), grids))
+    canon = g.generate_anchors(4, (13, 17))                       # p6: canonical stride 64, image-derived 61 vertically
+    assert canon.shape == parts[4].shape and not torch.equal(canon, parts[4])
+    assert torch.equal(canon[:, [0, 2]], parts[4][:, [0, 2]])     # the horizontal stride is 64 either way
+    assert torch.equal(g.generate_anchors(0, (4, 4)), g((16, 16), [(4, 4)] + [(1, 1)] * 4)[:4 * 4 * 3])
+
+
+def test_detector_pieces_under_the_reference_names():
+    from ferrotorch_b200.models.detection import FasterRCNN
+
+    torch.manual_seed(0)
+    det = FasterRCNN(num_classes=5).eval()
+    img = torch.rand(1, 3, 64, 64)
+    c = det.forward_backbone(img)
+    assert sorted(c) == ["layer1", "layer2", "layer3", "layer4"] and c["layer1"].shape == (1, 256, 16, 16) and c["layer4"].shape == (1, 2048, 2, 2)
+    p = det.forward_fpn(c)
+    assert sorted(p) == ["p2", "p3", "p4", "p5", "p6"] and all(v.shape[1] == 256 for v in p.values())
+    with torch.no_grad():
+        whole = det.backbone(img)
+    for a, b in zip(p.values(), whole.values()):
+        assert torch.equal(a, b)
+    assert det.num_classes() == 5 and det.num_parameters() == sum(q.numel() for q in det.parameters() if q.requires_grad)
+    with torch.no_grad():
+        obj, deltas = det.rpn.head.forward_level(p["p3"])
+        all_obj, all_deltas = det.rpn.head([p["p3"]])
+    assert torch.equal(obj, all_obj[0]) and torch.equal(deltas, all_deltas[0]) and deltas.shape[1] == 4 * obj.shape[1]
