@@ -35,6 +35,27 @@ class Device:
     def Cuda(index: int = 0) -> torch.device:
         return torch.device("cuda", index)
 
+    # predicates on a ``torch.device`` (the reference's ``Device::is_cpu`` ... are methods of its enum)
+    @staticmethod
+    def is_cpu(device) -> bool:
+        return torch.device(device).type == "cpu"
+
+    @staticmethod
+    def is_cuda(device) -> bool:
+        return torch.device(device).type == "cuda"
+
+    @staticmethod
+    def is_meta(device) -> bool:
+        return torch.device(device).type == "meta"
+
+    @staticmethod
+    def is_xpu(device) -> bool:
+        return torch.device(device).type == "xpu"
+
+    @staticmethod
+    def is_mps(device) -> bool:
+        return torch.device(device).type == "mps"
+
     @staticmethod
     def Xpu(index: int = 0):
         raise NotImplementedError("Device.Xpu: this package has no Intel back-end")
@@ -101,6 +122,42 @@ class BlockMask:
         pad[:q_len, :kv_len] = dense
         keep = pad.view(nq, block, nk, block).permute(0, 2, 1, 3).flatten(2).any(-1)
         return cls(keep, block, q_len, kv_len)
+
+    # ---- the reference's constructors and queries (ferrotorch-nn/src/flex_attention.rs:69-200)
+    @classmethod
+    def full_mask(cls, n_q: int, n_k: int, block_size: int = 64) -> "BlockMask":
+        """Every block takes part: no masking."""
+        if min(n_q, n_k, block_size) < 1:
+            raise ValueError("BlockMask: lengths and block size must be positive")
+        return cls(torch.ones(-(-n_q // block_size), -(-n_k // block_size), dtype=torch.bool), block_size, n_q, n_k)
+
+    @classmethod
+    def causal_mask(cls, n: int, block_size: int = 64) -> "BlockMask":
+        """Block ``(i, j)`` is active when some query of block i may see some key of block j under
+        ``q_pos >= k_pos``, i.e. ``j <= i``."""
+        return cls.from_fn(lambda q, k: q >= k, n, n, block_size)
+
+    @classmethod
+    def sliding_window_mask(cls, n: int, window_size: int, block_size: int = 64) -> "BlockMask":
+        """Queries see keys within ``window_size`` positions on either side."""
+        if window_size < 0:
+            raise ValueError("BlockMask.sliding_window_mask: window_size must be >= 0")
+        return cls.from_fn(lambda q, k: (q - k).abs() <= window_size, n, n, block_size)
+
+    def num_q_blocks(self) -> int:
+        return self.keep.shape[0]
+
+    def num_k_blocks(self) -> int:
+        return self.keep.shape[1]
+
+    def is_active(self, q_block: int, k_block: int) -> bool:
+        return bool(self.keep[q_block, k_block])
+
+    def allows_position(self, q_pos: int, k_pos: int) -> bool:
+        """Whether the pair falls in an active block (finer rules are the score function's job)."""
+        if not (0 <= q_pos < self.q_len and 0 <= k_pos < self.kv_len):
+            return False
+        return bool(self.keep[q_pos // self.block, k_pos // self.block])
 
     def sparsity(self) -> float:
         return 1.0 - float(self.keep.float().mean())

@@ -145,15 +145,67 @@ class QatConfig:
                  skip: tuple = ()):
         self.weight_bits, self.activation_bits, self.observer, self.skip = weight_bits, activation_bits, observer, tuple(skip)
 
+    # presets (ferrotorch-nn/src/qat.rs ``impl QatConfig``)
+    @classmethod
+    def default_symmetric_int8(cls) -> "QatConfig":
+        return cls(8, 8)
+
+    @classmethod
+    def per_channel_int8(cls) -> "QatConfig":
+        """8-bit weights with one scale per output channel (what ``QatLinear`` always uses) and 8-bit activations."""
+        return cls(8, 8, ObserverType.MinMax)
+
+    @classmethod
+    def int4_weight_int8_activation(cls) -> "QatConfig":
+        return cls(4, 8)
+
 
 class QuantizedModel:
     """Result of :meth:`QatModel.convert`: ``{layer name: (int8 weight, scale, zero point)}``."""
 
-    def __init__(self, layers: dict):
-        self.layers = layers
+    def __init__(self, layers: dict, config: "QatConfig | None" = None):
+        self.layers, self.config = layers, config or QatConfig()
+        self.bits = self.config.weight_bits
 
     def __len__(self) -> int:
         return len(self.layers)
+
+    # ---- qat.rs ``QuantizedModel`` accessors
+    def weight_names(self) -> list:
+        return sorted(self.layers)
+
+    def num_weights(self) -> int:
+        return len(self.layers)
+
+    def weight(self, name: str) -> torch.Tensor:
+        """The integer weight of layer ``name``."""
+        return self._entry(name)[0]
+
+    def weight_qparams(self, name: str):
+        """``(scale, zero_point)`` of layer ``name``."""
+        e = self._entry(name)
+        return e[1], e[2]
+
+    def dequantize_weight(self, name: str) -> torch.Tensor:
+        return self.dequantized_state_dict()[name + ".weight"]
+
+    def quantized_size_bytes(self) -> int:
+        """Bytes of the integer weights at their nominal width plus fp32 scales."""
+        total = 0
+        for q, scale, _zp in (self._entry(n) for n in self.layers):
+            total += (q.numel() * self.bits + 7) // 8 + scale.numel() * 4
+        return total
+
+    def compression_ratio(self) -> float:
+        """fp32 bytes of the same weights over :meth:`quantized_size_bytes`."""
+        dense = sum(self._entry(n)[0].numel() * 4 for n in self.layers)
+        return dense / self.quantized_size_bytes() if self.layers else 1.0
+
+    def _entry(self, name: str):
+        if name not in self.layers:
+            raise KeyError("no quantised layer %r (have %s)" % (name, sorted(self.layers)))
+        q, scale, zp = self.layers[name]
+        return q, scale, (zp if torch.is_tensor(zp) and zp.dtype != q.dtype and zp.numel() == scale.numel() else torch.zeros_like(scale))
 
     def dequantized_state_dict(self) -> dict:
         out = {}
@@ -176,7 +228,37 @@ class QatModel(nn.Module):
         return self.model(*a, **kw)
 
     def convert(self) -> QuantizedModel:
-        return QuantizedModel(_convert_qat(self.model))
+        return QuantizedModel(_convert_qat(self.model), self.config)
+
+    # ---- qat.rs ``QatModel``
+    def _layers(self) -> dict:
+        from .fake_quant import QatLinear
+
+        return {n: m for n, m in self.model.named_modules() if isinstance(m, QatLinear)}
+
+    def register_layer(self, name: str) -> None:
+        """Swap the ``nn.Linear`` called ``name`` (a dotted path) for its fake-quantised form, e.g. one that
+        was listed in ``skip`` when the model was prepared."""
+        from .fake_quant import QatLinear
+
+        parent, _, leaf = name.rpartition(".")
+        owner = self.model.get_submodule(parent) if parent else self.model
+        lin = getattr(owner, leaf)
+        if isinstance(lin, QatLinear):
+            return
+        if not isinstance(lin, nn.Linear):
+            raise TypeError("register_layer: %r is a %s, not a Linear" % (name, type(lin).__name__))
+        setattr(owner, leaf, QatLinear.from_float(lin, self.config.weight_bits, self.config.activation_bits))
+
+    def fake_quantize_weights(self, enabled: bool = True) -> "QatModel":
+        for m in self._layers().values():
+            m.weight_fq.enabled = bool(enabled)
+        return self
+
+    def fake_quantize_activations(self, enabled: bool = True) -> "QatModel":
+        for m in self._layers().values():
+            m.act_fq.enabled = bool(enabled)
+        return self
 
 
 KVPage = tuple      # (layer, page index): pages are slices of the pool's device tensors, addressed by index

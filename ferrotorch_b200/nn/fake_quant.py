@@ -73,6 +73,30 @@ class FakeQuantize(nn.Module):
         self.observer = MinMaxObserver(bits, symmetric, ch_axis, momentum)
         self.observe, self.enabled = True, True
 
+    # ---- torch / reference switches (quantize.rs ``FakeQuantize``)
+    def enable_observer(self) -> "FakeQuantize":
+        self.observe = True
+        return self
+
+    def disable_observer(self) -> "FakeQuantize":
+        """Freeze the range: later batches are quantised with the statistics gathered so far."""
+        self.observe = False
+        return self
+
+    def enable_fake_quant(self) -> "FakeQuantize":
+        self.enabled = True
+        return self
+
+    def disable_fake_quant(self) -> "FakeQuantize":
+        """Pass values through unchanged (the observer may keep collecting)."""
+        self.enabled = False
+        return self
+
+    def calculate_qparams(self):
+        """``(scale, zero_point)`` from the observed range."""
+        scale, zero, _, _ = self.observer.qparams()
+        return scale, zero
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.observe and self.training:
             self.observer(x.detach())

@@ -55,6 +55,15 @@ class AnomalyMode:
     def is_enabled() -> bool:
         return torch.is_anomaly_enabled()
 
+    @staticmethod
+    def enable(check_nan: bool = True) -> None:
+        """Switch anomaly detection on for the rest of the process (the context-manager form restores it)."""
+        torch.autograd.set_detect_anomaly(True, check_nan=check_nan)
+
+    @staticmethod
+    def disable() -> None:
+        torch.autograd.set_detect_anomaly(False)
+
 
 class ForwardBacktrace(list):
     """The forward-pass stack that anomaly mode records on an autograd node (anomaly.rs): a list
@@ -65,6 +74,21 @@ class ForwardBacktrace(list):
         node = getattr(tensor_or_node, "grad_fn", tensor_or_node)
         meta = getattr(node, "metadata", None) or {}
         return cls(meta.get("traceback_", []))
+
+    @classmethod
+    def capture_if_enabled(cls, tensor_or_node=None) -> "ForwardBacktrace | None":
+        """The recorded stack of a node when anomaly mode is on (the current Python stack when no node
+        is given), ``None`` when it is off."""
+        if not torch.is_anomaly_enabled():
+            return None
+        if tensor_or_node is not None:
+            return cls.of(tensor_or_node)
+        import traceback
+
+        return cls(traceback.format_stack()[:-1])
+
+    def trace(self) -> str:
+        return "".join(self)
 
 
 def check_gradient_anomaly(t: Tensor, what: str = "gradient") -> None:
@@ -119,21 +143,118 @@ class EinopsReduction(str, enum.Enum):
         return self.value
 
 
-class DispatchKey(enum.Enum):
-    """Kept as vocabulary only: this build has one back-end and no dispatcher of its own
-    (torch's dispatcher routes the custom ops); see ``Dispatcher``."""
-    Cpu = "cpu"; Cuda = "cuda"; Autograd = "autograd"; Autocast = "autocast"; Meta = "meta"  # noqa: E702
+class DispatchKey(enum.IntEnum):
+    """Dispatch keys from lowest to highest priority (ferrotorch-core/src/dispatch.rs:70-124): the three
+    back-end keys, the tensor-kind keys, then the layers that wrap an op (autocast, autograd, vmap,
+    profiler, tracer).  The value is the priority and the bit position in a :class:`DispatchKeySet`."""
+    Cpu = 0
+    Cuda = 1
+    Meta = 2
+    Sparse = 3
+    Quantized = 4
+    Nested = 5
+    Autocast = 6
+    Autograd = 7
+    Vmap = 8
+    Profiler = 9
+    Tracer = 10
+
+    def priority(self) -> int:
+        return int(self)
 
 
-DispatchKeySet = frozenset
+class DispatchKeySet:
+    """A set of keys as a bit mask; iteration and ``highest`` go from the highest priority down
+    (dispatch.rs:137-251).  Values are immutable: ``insert`` / ``remove`` return a new set."""
+
+    def __init__(self, keys=()):
+        bits = 0
+        for k in keys:
+            bits |= 1 << int(DispatchKey(k))
+        self.bits = bits
+
+    @classmethod
+    def from_keys(cls, keys) -> "DispatchKeySet":
+        return cls(keys)
+
+    @classmethod
+    def all(cls) -> "DispatchKeySet":
+        return cls(DispatchKey)
+
+    def insert(self, key) -> "DispatchKeySet":
+        out = DispatchKeySet()
+        out.bits = self.bits | (1 << int(DispatchKey(key)))
+        return out
+
+    def remove(self, key) -> "DispatchKeySet":
+        out = DispatchKeySet()
+        out.bits = self.bits & ~(1 << int(DispatchKey(key)))
+        return out
+
+    def contains(self, key) -> bool:
+        return bool(self.bits >> int(DispatchKey(key)) & 1)
+
+    __contains__ = contains
+
+    def is_empty(self) -> bool:
+        return self.bits == 0
+
+    def len(self) -> int:
+        return bin(self.bits).count("1")
+
+    __len__ = len
+
+    def highest(self):
+        return DispatchKey(self.bits.bit_length() - 1) if self.bits else None
+
+    def iter_desc(self):
+        return (k for k in sorted(DispatchKey, reverse=True) if self.contains(k))
+
+    __iter__ = iter_desc
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, DispatchKeySet) and other.bits == self.bits
+
+    def __hash__(self) -> int:
+        return hash(self.bits)
+
+    def __repr__(self) -> str:
+        return "DispatchKeySet(%s)" % ", ".join(k.name for k in self.iter_desc())
 
 
 class Dispatcher:
-    """Not reproduced (no multi-back-end dispatch): constructing one says so."""
+    """A table ``(op name, key) -> kernel`` with priority resolution (dispatch.rs:298-400): ``call`` runs
+    the kernel of the highest-priority key of ``keyset`` that has one for the op and hands it the whole
+    key set, so that a wrapping layer (autocast, autograd, a profiler) can take its own key out and
+    call again.  torch's dispatcher routes this package's kernels; this table is for code that layers
+    Python-level behaviour the same way the reference's users do."""
 
-    def __init__(self, *a, **kw):
-        raise FerrotorchError("Dispatcher: this framework has a single back-end (sm_100a) and uses torch's dispatcher; "
-                              "register custom ops with torch.library instead")
+    def __init__(self):
+        self._kernels: dict = {}
+
+    def register(self, op_name: str, key, kernel) -> None:
+        self._kernels[(str(op_name), DispatchKey(key))] = kernel
+
+    def has_kernel(self, op_name: str, key) -> bool:
+        return (str(op_name), DispatchKey(key)) in self._kernels
+
+    def kernel_count(self) -> int:
+        return len(self._kernels)
+
+    def call(self, op_name: str, inputs, keyset: DispatchKeySet):
+        if keyset.is_empty():
+            raise FerrotorchError("Dispatcher.call(%r): the key set is empty" % op_name)
+        for key in keyset.iter_desc():
+            kernel = self._kernels.get((str(op_name), key))
+            if kernel is not None:
+                return kernel(inputs, keyset)
+        raise FerrotorchError("Dispatcher.call(%r): no kernel for any key of %r" % (op_name, keyset))
+
+    def call_direct(self, op_name: str, key, inputs, keyset: DispatchKeySet | None = None):
+        kernel = self._kernels.get((str(op_name), DispatchKey(key)))
+        if kernel is None:
+            raise FerrotorchError("Dispatcher.call_direct(%r): no kernel for %s" % (op_name, DispatchKey(key).name))
+        return kernel(inputs, keyset if keyset is not None else DispatchKeySet([key]))
 
 
 Kernel = object
@@ -483,8 +604,47 @@ class MaskedTensor:
             raise FerrotorchError("MaskedTensor: mask shape %s != data shape %s" % (tuple(mask.shape), tuple(data.shape)))
         self.data, self.mask = data, mask.bool()
 
-    def filled(self, value=0.0) -> Tensor:
+    def filled(self, value=None) -> Tensor:
+        value = self._fill if value is None else value
         return torch.where(self.mask, self.data, torch.full_like(self.data, value))
+
+    # ---- masked.rs accessors
+    _fill = 0.0
+
+    @classmethod
+    def from_data(cls, data: Tensor, mask: Tensor) -> "MaskedTensor":
+        return cls(data, mask)
+
+    def with_fill_value(self, value) -> "MaskedTensor":
+        out = MaskedTensor(self.data, self.mask)
+        out._fill = value
+        return out
+
+    def fill_value(self):
+        return self._fill
+
+    def count_valid(self) -> int:
+        return int(self.mask.sum())
+
+    def count_masked(self) -> int:
+        return self.mask.numel() - self.count_valid()
+
+    def numel(self) -> int:
+        return self.data.numel()
+
+    @property
+    def shape(self):
+        return tuple(self.data.shape)
+
+    def to_tensor(self) -> Tensor:
+        """The data with the fill value where the mask is off."""
+        return self.filled()
+
+    def to_ferray(self):
+        """A ``numpy.ma`` masked array (numpy's mask marks the *invalid* entries)."""
+        import numpy as np
+
+        return np.ma.array(self.data.detach().cpu().numpy(), mask=(~self.mask).cpu().numpy(), fill_value=self._fill)
 
 
 def masked_where(data: Tensor, condition) -> MaskedTensor:
@@ -598,6 +758,52 @@ class SemiStructuredSparseTensor:
         from .ops.quant import unpack_2_4
 
         return unpack_2_4(self.values, self.meta)
+
+    # ---- sparse.rs ``SemiStructuredSparseTensor`` / ``CudaSemiStructuredSparseTensor`` accessors
+    @classmethod
+    def compress(cls, dense: Tensor) -> "SemiStructuredSparseTensor":
+        """Keep the two largest magnitudes of every group of four along the last dimension."""
+        if dense.dim() != 2 or dense.shape[1] % 8:
+            raise FerrotorchError("2:4 compression needs a matrix whose second dimension is a multiple of 8, got %s" % (tuple(dense.shape),))
+        return cls.from_dense(dense)
+
+    decompress = to_dense
+
+    def num_groups(self) -> int:
+        return self.shape[0] * self.shape[1] // 4
+
+    def compression_ratio(self) -> float:
+        """Dense bytes over compressed bytes (values + position bits)."""
+        dense = self.shape[0] * self.shape[1] * self.values.element_size()
+        return dense / (self.values.numel() * self.values.element_size() + self.meta.numel() * self.meta.element_size())
+
+    def mask(self) -> Tensor:
+        """Which dense positions are kept (exactly two per group of four)."""
+        ones = SemiStructuredSparseTensor(torch.ones_like(self.values), self.meta, self.shape)
+        return ones.to_dense() != 0
+
+    def group_mask(self, group: int) -> list:
+        """The four keep flags of group ``group`` (row-major over the groups)."""
+        if not 0 <= group < self.num_groups():
+            raise FerrotorchError("group %d of %d" % (group, self.num_groups()))
+        r, c = divmod(group, self.shape[1] // 4)
+        return self.mask()[r, 4 * c:4 * c + 4].tolist()
+
+    backend = "expand-gemm"             # one implementation here: the compressed weight is expanded inside the GEMM
+
+    @property
+    def packed(self) -> Tensor:
+        return self.values
+
+    @property
+    def indices(self) -> Tensor:
+        return self.meta
+
+    def values_shape(self) -> tuple:
+        return tuple(self.values.shape)
+
+    def indices_shape(self) -> tuple:
+        return tuple(self.meta.shape)
 
 
 CudaSemiStructuredSparseTensor = SemiStructuredSparseTensor

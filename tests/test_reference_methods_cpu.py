@@ -611,3 +611,58 @@ def test_detector_pieces_under_the_reference_names():
         obj, deltas = det.rpn.head.forward_level(p["p3"])
         all_obj, all_deltas = det.rpn.head([p["p3"]])
     assert torch.equal(obj, all_obj[0]) and torch.equal(deltas, all_deltas[0]) and deltas.shape[1] == 4 * obj.shape[1]
+
+
+def test_core_wrapper_methods():
+    # ferrotorch-core/src/{masked,sparse,dispatch,device}.rs, ferrotorch-nn/src/{flex_attention,qat}.rs, core quantize.rs
+    import ferrotorch_b200 as ft
+    from ferrotorch_b200 import nn as N
+
+    m = ft.MaskedTensor.from_data(torch.tensor([1.0, 2.0, 3.0]), torch.tensor([True, False, True])).with_fill_value(-1.0)
+    assert (m.count_valid(), m.count_masked(), m.numel(), m.shape, m.fill_value()) == (2, 1, 3, (3,), -1.0)
+    assert m.to_tensor().tolist() == [1.0, -1.0, 3.0] and m.to_ferray().mask.tolist() == [False, True, False]
+    w = torch.randn(4, 16)
+    s = ft.SemiStructuredSparseTensor.compress(w)
+    assert s.num_groups() == 16 and int(s.mask().sum()) == 32 and sum(s.group_mask(5)) == 2
+    assert torch.equal(s.decompress(), s.to_dense()) and torch.equal(s.decompress() != 0, s.mask())
+    assert s.values_shape() == (4, 8) and s.indices_shape() == tuple(s.indices.shape) and s.packed is s.values and s.compression_ratio() > 1.7
+    with pytest.raises(ft.FerrotorchError):
+        ft.SemiStructuredSparseTensor.compress(torch.randn(4, 6))
+    D = ft.Device
+    assert D.is_cpu("cpu") and D.is_cuda(D.Cuda(1)) and D.is_meta(D.Meta) and not D.is_xpu("cpu") and not D.is_mps("cpu")
+    bm = N.BlockMask.causal_mask(10, 4)
+    assert (bm.num_q_blocks(), bm.num_k_blocks()) == (3, 3) and bm.is_active(1, 0) and not bm.is_active(0, 1)
+    assert bm.allows_position(5, 7) and not bm.allows_position(2, 9) and not bm.allows_position(11, 0)      # block granularity
+    assert N.BlockMask.full_mask(10, 6, 4).keep.all() and N.BlockMask.full_mask(10, 6, 4).keep.shape == (3, 2)
+    sw = N.BlockMask.sliding_window_mask(16, 2, 4)
+    assert sw.is_active(1, 0) and sw.is_active(0, 1) and not sw.is_active(0, 2) and not sw.is_active(3, 1)
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 6), torch.nn.ReLU(), torch.nn.Linear(6, 3))
+    qm = N.QatModel(net, N.QatConfig.int4_weight_int8_activation()).train()
+    x = torch.randn(16, 8)
+    fq_out = qm(x)
+    plain = qm.fake_quantize_weights(False).fake_quantize_activations(False)(x)
+    torch.testing.assert_close(plain, torch.nn.functional.linear(torch.relu(torch.nn.functional.linear(x, qm.model[0].weight, qm.model[0].bias)),
+                                                               qm.model[2].weight, qm.model[2].bias))
+    assert not torch.equal(fq_out, plain)
+    q = qm.fake_quantize_weights(True).convert()
+    assert q.weight_names() == ["0", "2"] and q.num_weights() == 2 and q.weight("0").dtype == torch.int8
+    assert int(q.weight("0").abs().max()) <= 8 and q.weight_qparams("0")[0].shape == (6,)
+    assert q.quantized_size_bytes() == (48 * 4 + 7) // 8 + 24 + (18 * 4 + 7) // 8 + 12 and q.compression_ratio() > 3.5
+    assert float((q.dequantize_weight("0") - qm.model[0].weight.detach()).abs().max()) < float(q.weight_qparams("0")[0].max())
+    with pytest.raises(KeyError):
+        q.weight("9")
+    skipped = N.QatModel(torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.Linear(4, 2)), N.QatConfig(skip=("1",)))
+    assert type(skipped.model[1]) is torch.nn.Linear
+    skipped.register_layer("1")
+    assert isinstance(skipped.model[1], N.QatLinear) and N.QatConfig.default_symmetric_int8().weight_bits == 8
+    fq = N.FakeQuantize(8).train()
+    fq(x)
+    scale, zero = fq.calculate_qparams()
+    assert float(scale) > 0 and float(zero) == 0
+    assert torch.equal(fq.disable_fake_quant()(x), x)
+    lo = fq.enable_fake_quant().disable_observer().observer.max_val.clone()
+    fq(x * 100)
+    assert torch.equal(fq.observer.max_val, lo)                                   # the range is frozen
+    fq.enable_observer()(x * 100)
+    assert float(fq.observer.max_val) > float(lo)

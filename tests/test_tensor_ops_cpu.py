@@ -17,8 +17,19 @@ def test_root_resolves_reference_and_torch_names():
         ft.no_such_name
     with pytest.raises(ft.FerrotorchError):
         ft.from_slice([1, 2], [3])
+    d = ft.Dispatcher()                       # a priority table of Python-level kernels (dispatch.rs)
+    d.register("relu", ft.DispatchKey.Cpu, lambda inputs, keys: torch.relu(inputs[0]))
+    d.register("relu", ft.DispatchKey.Autocast, lambda inputs, keys: d.call("relu", [inputs[0].bfloat16()], keys.remove(ft.DispatchKey.Autocast)))
+    keys = ft.DispatchKeySet.from_keys([ft.DispatchKey.Cpu, ft.DispatchKey.Autocast])
+    assert d.call("relu", [torch.tensor([-1.0, 2.0])], keys).dtype == torch.bfloat16 and keys.highest() is ft.DispatchKey.Autocast
+    assert d.call_direct("relu", ft.DispatchKey.Cpu, [torch.tensor([-1.0])]).tolist() == [0.0] and d.kernel_count() == 2
+    assert [k.name for k in keys.insert(ft.DispatchKey.Tracer).iter_desc()] == ["Tracer", "Autocast", "Cpu"] and ft.DispatchKeySet.all().len() == 11
     with pytest.raises(ft.FerrotorchError):
-        ft.Dispatcher()
+        d.call("relu", [x], ft.DispatchKeySet())
+    with pytest.raises(ft.FerrotorchError):
+        d.call("gelu", [x], keys)
+    with pytest.raises(ft.FerrotorchError):
+        d.call_direct("relu", ft.DispatchKey.Cuda, [x])
 
 
 def test_reductions_clamps_and_selection():
@@ -106,6 +117,6 @@ def test_umbrella_aliases_and_prelude():
         assert name in ns, name
     assert ft.gpu is ft.cuda and ft.distributed is ft.parallel and ft.tokenize is importlib.import_module("ferrotorch_b200.utils.text")
     assert ft.llama.LlamaConfig is ft.models.LlamaConfig and callable(ft.llama.generate) and ft.llama.GptqQ4 and ft.llama.masked_decode_loop
-    assert ft.llama.LlamaKvCache is ft.nn.KVCache and ft.grammar.JsonSchemaProcessor and ft.ml.accuracy_score
+    assert ft.llama.LlamaKvCache.empty().is_empty() and ft.llama.KVCache is ft.nn.KVCache and ft.grammar.JsonSchemaProcessor and ft.ml.accuracy_score
     assert ft.bert.BertModel and ft.whisper.WhisperEncoder and ft.graph.GcnConv and ft.rl.MlpPolicy and ft.diffusion.DDIMScheduler
     assert ft.jit_script.script is ft.jit.script
