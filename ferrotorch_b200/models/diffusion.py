@@ -458,6 +458,29 @@ class _UNetBlock(nn.Module):
         x = self.resnets[j](x, temb)
         return self.attentions[j](x, ctx) if self.attentions is not None else x
 
+    def forward_t(self, x, temb, ctx=None, skips=None):
+        """A whole block under the reference's calling convention (ferrotorch-diffusion/src/unet.rs:160, 340,
+        504, 704).  Down block (``skips is None``): returns ``(output, skips)`` with one skip per resnet and
+        the down-sampled tensor as the last one.  Up block: ``skips`` holds one tensor per resnet, the
+        **last** one is consumed first (the order in which the down path produced them, reversed)."""
+        if skips is None:
+            out_skips = []
+            for j in range(len(self.resnets)):
+                x = self.run(j, x, temb, ctx)
+                out_skips.append(x)
+            if hasattr(self, "downsamplers"):
+                x = self.downsamplers[0](x)
+                out_skips.append(x)
+            return x, out_skips
+        skips = list(skips)
+        if len(skips) != len(self.resnets):
+            raise ValueError("up block with %d resnets got %d skip tensors" % (len(self.resnets), len(skips)))
+        for j in range(len(self.resnets)):
+            x = self.run(j, torch.cat([x, skips.pop()], dim=1), temb, ctx)
+        if hasattr(self, "upsamplers"):
+            x = self.upsamplers[0](x)
+        return x
+
 
 class _UNetMid(nn.Module):
     def __init__(self, c: UNet2DConditionConfig, ch: int, temb: int):
@@ -468,6 +491,8 @@ class _UNetMid(nn.Module):
 
     def forward(self, x, temb, ctx):
         return self.resnets[1](self.attentions[0](self.resnets[0](x, temb), ctx), temb)
+
+    forward_t = forward
 
 
 class UNet2DConditionModel(nn.Module):
@@ -528,6 +553,13 @@ class UNet2DConditionModel(nn.Module):
             if hasattr(blk, "upsamplers"):
                 x = blk.upsamplers[0](x)
         return self.conv_out(F.silu(self.conv_norm_out(x)))
+
+    forward_t = forward
+
+    def load_hf_state_dict(self, sd: dict, strict: bool = True):
+        """The module's parameter names are the ``diffusers`` names, so this is ``load_state_dict``; kept
+        under the name every other model of the stack uses."""
+        return self.load_state_dict(sd, strict=strict)
 
 
 # --------------------------------------------------------------------------- VAE
@@ -885,6 +917,18 @@ DownBlock2D = CrossAttnDownBlock2D = UpBlock2D = CrossAttnUpBlock2D = AnyDownBlo
 UNetMidBlock2DCrossAttn = UNetMidBlock2D = _UNetMid
 DownEncoderBlock2D = UpDecoderBlock2D = _VaeStage
 VaeEncoder, VaeDecoder = Encoder, Decoder
+# multi-argument forwards under the reference's names (its one-argument ``Module::forward`` needed a second
+# entry point for time embeddings / cross-attention context; ``forward`` takes them all here)
+ResnetBlock2D.forward_t = ResnetBlock2D.forward
+for _c in (_Attention, BasicTransformerBlock, Transformer2DModel):
+    _c.forward_xattn = _c.forward
+ClipTextEncoder.forward_from_id_tensor = ClipTextEncoder.forward
+ClipTextEncoder.forward_from_ids = lambda self, ids: self.forward(torch.as_tensor(list(ids), dtype=torch.long)[None].to(
+    next(self.parameters()).device))
+_ClipEmbeddings.forward_from_ids = lambda self, ids: self.forward(torch.as_tensor(list(ids), dtype=torch.long)[None].to(
+    next(self.parameters()).device))
+UNet2DConditionConfig.num_blocks = lambda self: len(self.block_out_channels)
+UNet2DConditionConfig.time_embed_dim = lambda self: 4 * self.block_out_channels[0]
 
 
 class Timesteps(nn.Module):
@@ -896,6 +940,8 @@ class Timesteps(nn.Module):
 
     def forward(self, t: torch.Tensor) -> torch.Tensor:
         return timestep_embedding(t, self.dim, self.flip, self.shift)
+
+    forward_t = forward
 
 
 class BetaSchedule(str, _enum.Enum):

@@ -165,6 +165,12 @@ class SpecDecodeConfig:
     gamma: int = 4                       # draft tokens proposed per target pass
     eos_token_id: int | None = None
 
+    def validate(self) -> None:
+        if self.gamma < 1:
+            raise ValueError("SpecDecodeConfig: gamma (draft tokens per pass) must be >= 1")
+        if self.max_new_tokens < 1:
+            raise ValueError("SpecDecodeConfig: max_new_tokens must be >= 1")
+
 
 @dataclass
 class SpecDecodeOutput:
@@ -178,6 +184,7 @@ class SpecDecodeOutput:
 
 
 def speculative_decode_with_config(target, draft, input_ids: torch.Tensor, cfg: SpecDecodeConfig) -> SpecDecodeOutput:
+    cfg.validate()
     ids, st = speculative_decode(target, draft, input_ids, cfg.max_new_tokens, cfg.gamma, cfg.eos_token_id)
     return SpecDecodeOutput(ids, st["proposed"], st["accepted"], st["target_calls"])
 

@@ -622,6 +622,28 @@ def load_ppo_policy(path: str, config: MlpPolicyConfig | None = None):
 
 # --------------------------------------------------------------------------- the reference's remaining names
 HfBertConfig, HfWhisperConfig = BertConfig, WhisperConfig     # the config classes read Hugging Face's config.json as is
+
+
+def _from_file(cls, path: str):
+    """``path``: a ``config.json`` file or the model directory that holds one."""
+    import os
+
+    return cls.from_hf(os.path.join(path, "config.json") if os.path.isdir(path) else path)
+
+
+def _from_json_str(cls, text: str):
+    import json
+
+    return cls.from_hf(json.loads(text))
+
+
+for _cfg in (BertConfig, WhisperConfig):
+    _cfg.from_file = classmethod(_from_file)
+    _cfg.from_json_str = classmethod(_from_json_str)
+BertSelfOutput.forward_residual = BertSelfOutput.forward
+BertEmbeddings.forward_from_ids = lambda self, ids, token_type_ids=None: self.forward(
+    torch.as_tensor(list(ids), dtype=torch.long, device=self.word_embeddings.weight.device)[None],
+    None if token_type_ids is None else torch.as_tensor(list(token_type_ids), dtype=torch.long, device=self.word_embeddings.weight.device)[None])
 WhisperEncoderSelfAttention = _WhisperAttention
 N_MELS, N_FRAMES = 80, CHUNK_SECONDS * SAMPLE_RATE // HOP_LENGTH      # 80 mel bins, 3000 frames per 30 s chunk
 

@@ -474,6 +474,14 @@ class SubGroup(Group):
     def global_rank(self, local: int) -> int:
         return self.members[local]
 
+    # backend.rs ``SubBackend::{to_global, to_local}``
+    to_global = global_rank
+
+    def to_local(self, global_rank: int) -> int:
+        if global_rank not in self.members:
+            raise InvalidRank("rank %d is not a member of this sub-group %s" % (global_rank, self.members))
+        return self.members.index(global_rank)
+
     def send(self, t, dst):
         self._check_peer(dst)
         self.parent.send(t, self.members[dst])
@@ -557,6 +565,12 @@ class HybridGroup(Group):
                               % (control.rank, control.world_size, data.rank, data.world_size))
         self.control, self.data = control, data
         self.rank, self.world_size = control.rank, control.world_size
+
+    def synchronize_nccl(self) -> None:
+        """Wait for the data group's device work (hybrid_backend.rs): collectives here are stream-ordered, so
+        this is only needed before the host reads a result."""
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
 
     def tcp(self) -> Group:
         return self.control

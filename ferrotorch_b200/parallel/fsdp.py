@@ -174,6 +174,15 @@ class SyncBatchNorm2d(nn.Module):
         self.bias = nn.Parameter(torch.zeros(num_features))
         self.register_buffer("running_mean", torch.zeros(num_features))
         self.register_buffer("running_var", torch.ones(num_features))
+        self.register_buffer("num_batches_tracked", torch.zeros((), dtype=torch.long))
+
+    def with_backend(self, group: Group) -> "SyncBatchNorm2d":
+        """The same layer (shared parameters and statistics) synchronising over another group."""
+        import copy
+
+        out = copy.copy(self)
+        out.group = group
+        return out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.training:
@@ -181,6 +190,7 @@ class SyncBatchNorm2d(nn.Module):
                                             0.0, self.eps)
         y, mean, var = _SyncBNFn.apply(x, self.weight, self.bias, self.group, self.eps)
         with torch.no_grad():
+            self.num_batches_tracked += 1
             n = x.numel() // x.shape[1] * self.group.world_size
             self.running_mean.lerp_(mean, self.momentum)
             self.running_var.lerp_(var * n / max(n - 1, 1), self.momentum)

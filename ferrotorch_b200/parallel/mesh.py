@@ -110,18 +110,34 @@ class DeviceMesh:
         return mine
 
 
+class _PlacementQueries:
+    """The predicates of the reference's ``Placement`` enum (dtensor.rs:70-90)."""
+
+    def is_replicate(self) -> bool:
+        return isinstance(self, Replicate)
+
+    def is_shard(self) -> bool:
+        return isinstance(self, Shard)
+
+    def is_partial(self) -> bool:
+        return isinstance(self, Partial)
+
+    def shard_dim(self):
+        return self.dim if isinstance(self, Shard) else None
+
+
 @dataclass(frozen=True)
-class Replicate:
+class Replicate(_PlacementQueries):
     pass
 
 
 @dataclass(frozen=True)
-class Shard:
+class Shard(_PlacementQueries):
     dim: int
 
 
 @dataclass(frozen=True)
-class Partial:
+class Partial(_PlacementQueries):
     op: str = "sum"
 
 

@@ -21,6 +21,22 @@ class Placement:
     """Namespace for the three placements of a distributed tensor (dtensor.rs:56-67)."""
     from .mesh import Partial, Replicate, Shard  # noqa: F401
 
+    @staticmethod
+    def is_replicate(p) -> bool:
+        return p.is_replicate()
+
+    @staticmethod
+    def is_shard(p) -> bool:
+        return p.is_shard()
+
+    @staticmethod
+    def is_partial(p) -> bool:
+        return p.is_partial()
+
+    @staticmethod
+    def shard_dim(p):
+        return p.shard_dim()
+
 
 def send(group: Group, tensor: torch.Tensor, dst: int) -> None:
     if dst == group.rank:

@@ -94,6 +94,12 @@ class GgufFile:
         buf = (ctypes.c_ubyte * nbytes).from_address(ptr)
         return torch.frombuffer(bytearray(buf), dtype=torch.uint8)
 
+    def data(self, name: str) -> memoryview:
+        """The tensor's bytes as a read-only view of the file mapping (no copy; valid until ``close``)."""
+        _t, _shape, nbytes = self.tensors[name]
+        ptr = self._lib.ftg_tensor_data(self._h, self._index[name])
+        return memoryview((ctypes.c_ubyte * nbytes).from_address(ptr)).toreadonly()
+
     def dequantize(self, name: str, dtype=torch.float32, nibble_order: str = "ggml") -> torch.Tensor:
         t, shape, nbytes = self.tensors[name]
         n = int(np.prod(shape)) if shape else 1

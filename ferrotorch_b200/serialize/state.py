@@ -612,3 +612,14 @@ class AsyncCheckpointer:
         t.start()
         self._last = CheckpointFuture(t, box)
         return self._last
+
+    # checkpoint.rs:575-680 names
+    save = save_async
+
+    def is_saving(self) -> bool:
+        return self._last is not None and not self._last.is_done()
+
+    def wait(self) -> None:
+        """Block until the last save has been written (re-raises its error, if any)."""
+        if self._last is not None:
+            self._last.wait()

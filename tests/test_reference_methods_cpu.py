@@ -666,3 +666,92 @@ def test_core_wrapper_methods():
     assert torch.equal(fq.observer.max_val, lo)                                   # the range is frozen
     fq.enable_observer()(x * 100)
     assert float(fq.observer.max_val) > float(lo)
+
+
+def test_model_and_distributed_leftover_methods(tmp_path):
+    # ferrotorch-llama/src/{attention,layer}.rs forward_with_cache; ferrotorch-diffusion/src/unet.rs forward_t;
+    # ferrotorch-bert / -whisper config loaders; ferrotorch-distributed dtensor / backend / sync_batch_norm; serialize
+    import json as _json
+
+    from ferrotorch_b200.models import diffusion as D
+    from ferrotorch_b200.models import generation as G
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.models.pretrained import BertConfig, BertEmbeddings, WhisperConfig
+    from ferrotorch_b200.parallel import Partial, Replicate, Shard
+    from ferrotorch_b200.parallel.backend import InvalidRank, SimulatedGroup, SubGroup
+    from ferrotorch_b200.parallel.p2p import Placement
+    from ferrotorch_b200.serialize import AsyncCheckpointer, load_checkpoint
+
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(LlamaConfig.tiny()).eval()
+    ids = torch.tensor([[3, 17, 5, 99]])
+    with torch.no_grad():
+        x = m.model.embed_tokens(ids)
+        layer = m.model.layers[0]
+        h, d = layer(x)
+        cache, outs = None, []
+        for t in range(4):
+            o, cache = layer.forward_with_cache(x[:, t:t + 1], cache)
+            outs.append(o)
+        torch.testing.assert_close(torch.cat(outs, 1), h + d)
+        att, hn = layer.self_attn, layer.input_layernorm(x)
+        o1, c1 = att.forward_with_cache(hn[:, :3], None)
+        o2, c2 = att.forward_with_cache(hn[:, 3:], c1, seq_offset=3)
+        torch.testing.assert_close(torch.cat([o1, o2], 1), att(hn))
+    assert (c1.seq_len(), c2.seq_len(), cache.seq_len()) == (3, 4, 4) and (att.num_heads(), att.num_kv_heads()) == (4, 2)
+    with pytest.raises(ValueError):
+        att.forward_with_cache(hn[:, 3:], c1, seq_offset=1)
+    with pytest.raises(ValueError):
+        G.SpecDecodeConfig(gamma=0).validate()
+    # UNet blocks one by one
+    cfg = D.UNet2DConditionConfig(block_out_channels=(32, 64), layers_per_block=1, cross_attention_dim=16, attention_head_dim=4,
+                                  norm_num_groups=8, down_block_types=("CrossAttnDownBlock2D", "DownBlock2D"),
+                                  up_block_types=("UpBlock2D", "CrossAttnUpBlock2D"))
+    assert cfg.num_blocks() == 2 and cfg.time_embed_dim() == 128
+    u = D.UNet2DConditionModel(cfg).eval()
+    lat, ctx = torch.randn(1, 4, 8, 8), torch.randn(1, 5, 16)
+    with torch.no_grad():
+        want = u(lat, 10, ctx)
+        temb = u.time_embedding(D.timestep_embedding(torch.tensor([10]), 32, cfg.flip_sin_to_cos, cfg.freq_shift))
+        hcur = u.conv_in(lat)
+        skips = [hcur]
+        for blk in u.down_blocks:
+            hcur, sk = blk.forward_t(hcur, temb, ctx)
+            skips += sk
+        hcur = u.mid_block.forward_t(hcur, temb, ctx)
+        for blk in u.up_blocks:
+            n = len(blk.resnets)
+            take, skips = skips[-n:], skips[:-n]
+            hcur = blk.forward_t(hcur, temb, ctx, skips=take)
+        got = u.conv_out(torch.nn.functional.silu(u.conv_norm_out(hcur)))
+        assert torch.equal(got, want) and torch.equal(u.forward_t(lat, 10, ctx), want) and not skips
+        with pytest.raises(ValueError):
+            u.up_blocks[0].forward_t(hcur, temb, ctx, skips=[])
+    u.load_hf_state_dict(u.state_dict())
+    raw = {"vocab_size": 50, "hidden_size": 16, "num_hidden_layers": 1, "num_attention_heads": 2, "intermediate_size": 32}
+    (tmp_path / "config.json").write_text(_json.dumps(raw))
+    assert BertConfig.from_file(str(tmp_path)) == BertConfig.from_file(str(tmp_path / "config.json")) == BertConfig.from_json_str(_json.dumps(raw))
+    assert hasattr(WhisperConfig, "from_file") and hasattr(WhisperConfig, "from_json_str")
+    emb = BertEmbeddings(BertConfig.from_json_str(_json.dumps(raw)))
+    assert torch.equal(emb.forward_from_ids([1, 2, 3]), emb(torch.tensor([[1, 2, 3]])))
+    # placements, sub-groups, synchronised batch norm
+    assert Shard(1).is_shard() and Shard(1).shard_dim() == 1 and Replicate().is_replicate() and Partial().is_partial()
+    assert Replicate().shard_dim() is None and Placement.is_shard(Shard(0)) and Placement.shard_dim(Shard(2)) == 2
+    world = SimulatedGroup.create_group(4)
+    sub = SubGroup(world[2], [3, 2])
+    assert sub.to_global(0) == 2 and sub.to_local(3) == 1
+    with pytest.raises(InvalidRank):
+        sub.to_local(0)
+    from ferrotorch_b200.parallel import SyncBatchNorm2d
+
+    one = SimulatedGroup.create_group(1)[0]
+    bn = SyncBatchNorm2d(3, one).train()
+    bn(torch.randn(4, 3, 2, 2))
+    assert int(bn.num_batches_tracked) == 1
+    other = bn.with_backend(SimulatedGroup.create_group(1)[0])
+    assert other.weight is bn.weight and other.group is not bn.group and other.running_mean is bn.running_mean
+    ck = AsyncCheckpointer()
+    assert not ck.is_saving()
+    ck.save(str(tmp_path / "ck.pt"), {"w": torch.arange(4.0)})
+    ck.wait()
+    assert not ck.is_saving() and torch.equal(load_checkpoint(str(tmp_path / "ck.pt"))["model"]["w"], torch.arange(4.0))
