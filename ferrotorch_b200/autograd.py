@@ -189,6 +189,18 @@ class DualTensor:
     def _lift(o) -> "DualTensor":
         return o if isinstance(o, DualTensor) else DualTensor(torch.as_tensor(o))
 
+    @classmethod
+    def constant(cls, primal: torch.Tensor) -> "DualTensor":
+        """A value that does not depend on the differentiation variable: zero tangent."""
+        return cls(primal)
+
+    @property
+    def shape(self):
+        return tuple(self.primal.shape)
+
+    def numel(self) -> int:
+        return self.primal.numel()
+
     def __add__(self, o):
         o = self._lift(o)
         return DualTensor(self.primal + o.primal, self.tangent + o.tangent)

@@ -55,6 +55,27 @@ class GpuDevice:
     def synchronize(self) -> None:
         torch.cuda.synchronize(self.ordinal)
 
+    # ---- device.rs:60-117
+    def stream(self):
+        """The stream work is queued on from this thread (the fork made for a capture, when there is one)."""
+        return getattr(self, "_stream", None) or torch.cuda.current_stream(self.ordinal)
+
+    def context(self) -> int:
+        """The device's primary context, identified by its ordinal (torch creates and owns it)."""
+        torch.cuda.init()
+        return self.ordinal
+
+    def blas(self) -> int:
+        """The cuBLAS handle bound to this thread's current stream on the device (library GEMMs only)."""
+        with torch.cuda.device(self.ordinal):
+            return torch.cuda.current_blas_handle()
+
+    def fork_for_capture(self) -> "GpuDevice":
+        """The same device with a stream of its own: graph capture is not allowed on the default stream."""
+        fork = GpuDevice(self.ordinal)
+        fork._stream = torch.cuda.Stream(self.ordinal)
+        return fork
+
 
 def get_cuda_device(ordinal: int = 0) -> GpuDevice:
     return GpuDevice(ordinal)
@@ -211,10 +232,21 @@ class CaptureMode(str, _enum.Enum):
     def __str__(self) -> str:
         return self.value
 
+    def to_cuda(self) -> int:
+        """The driver's ``cudaStreamCaptureMode`` value: global 0, thread-local 1, relaxed 2."""
+        return {"global": 0, "thread_local": 1, "relaxed": 2}[self.value]
+
 
 class CaptureStatus(_enum.Enum):
     NotCapturing = "none"
     Active = "active"
+    Invalidated = "invalidated"
+
+    def is_capturing(self) -> bool:
+        return self is CaptureStatus.Active
+
+    def is_invalidated(self) -> bool:
+        return self is CaptureStatus.Invalidated
 
 
 def capture_status() -> CaptureStatus:
@@ -226,6 +258,47 @@ class GraphPoolHandle:
 
     def __init__(self, handle=None):
         self.handle = handle if handle is not None else graph_pool_handle()
+        self._buffers: list = []
+        self._sealed = False
+
+    # ---- graph.rs ``CapturePool`` / ``PrivateMemPool``.  torch's graph pool *is* a private pool: blocks a
+    # capture allocates stay reserved for the graphs that use the pool.  ``record_buffer`` additionally pins
+    # tensors (graph inputs / outputs) for the pool's lifetime; sealing refuses further ones.
+    @classmethod
+    def with_private_pool(cls, ordinal: int = 0) -> "GraphPoolHandle":
+        with torch.cuda.device(ordinal):
+            return cls()
+
+    def has_private_pool(self) -> bool:
+        return True
+
+    def record_buffer(self, tensor: torch.Tensor) -> None:
+        if self._sealed:
+            raise GpuError("CapturePool: the pool is sealed; buffers can only be recorded before the capture ends")
+        self._buffers.append(tensor)
+
+    def buffer_count(self) -> int:
+        return len(self._buffers)
+
+    def clear_buffers(self) -> None:
+        self._buffers.clear()
+
+    def seal(self) -> None:
+        self._sealed = True
+
+    def unseal(self) -> None:
+        self._sealed = False
+
+    def is_capture_pool_sealed(self) -> bool:
+        return self._sealed
+
+    def raw(self):
+        """The allocator's ``(device, id)`` handle."""
+        return self.handle
+
+    def activate(self) -> "MemPoolScope":
+        """A scope in which allocations come from this pool (see :class:`MemPoolScope`)."""
+        return MemPoolScope(self)
 
 
 CapturePool = PrivateMemPool = GraphPoolHandle
@@ -262,6 +335,28 @@ class GraphCaptureGuard:
             self._cm.__exit__(None, None, None)
             self.captured = CapturedGraph(self._g)
         return self.captured
+
+    finish = end
+
+    # ---- graph.rs:776-835 constructors
+    @classmethod
+    def begin(cls, stream=None) -> "GraphCaptureGuard":
+        return cls(stream=stream)
+
+    @classmethod
+    def begin_with_mode(cls, mode: CaptureMode, stream=None) -> "GraphCaptureGuard":
+        return cls(mode=mode, stream=stream)
+
+    @classmethod
+    def begin_with_pool(cls, pool: GraphPoolHandle, stream=None) -> "GraphCaptureGuard":
+        return cls(pool=pool, stream=stream)
+
+    @classmethod
+    def begin_with_pool_mode(cls, pool: GraphPoolHandle, mode: CaptureMode, stream=None) -> "GraphCaptureGuard":
+        return cls(pool=pool, mode=mode, stream=stream)
+
+    def status(self) -> CaptureStatus:
+        return CaptureStatus.NotCapturing if self.captured is not None else capture_status()
 
     def __enter__(self):
         return self
@@ -640,7 +735,7 @@ def __getattr__(name):
         fn = _resolve_gpu_op(name)
         if fn is not None:
             return fn
-    table = {"MemoryGuardedDevice": "MemoryGuard", "MemoryWatchdog": "MemoryGuard", "MemoryStats": "MemoryStats",
+    table = {"MemoryGuardedDevice": "MemoryGuardedDevice", "MemoryWatchdog": "MemoryWatchdog", "MemoryStats": "MemoryStats",
              "MemoryReservation": "MemoryReservation", "MemoryHook": "MemoryHook",
              "MemoryPressureListener": "MemoryPressureListener", "MemoryGuard": "MemoryGuard",
              "MemoryGuardBuilder": "MemoryGuardBuilder", "PressureLevel": "PressureLevel", "OomPolicy": "OomPolicy"}
@@ -671,6 +766,9 @@ class CudaBackendImpl:
         if fn is None:
             raise AttributeError("no launcher named gpu_%s" % name)
         return fn
+
+    def default_device(self) -> "GpuDevice":
+        return get_cuda_device(self.ordinal)
 
     def __repr__(self) -> str:
         return "CudaBackendImpl(ordinal=%d)" % self.ordinal

@@ -313,6 +313,37 @@ class AotModule(nn.Module):
         ps = [dict(self.module.named_parameters())[n] for n in self.names] if self.module is not None else []
         return _AotFn.apply(self.pair, self.cfg.block_size, *ps, *inputs)
 
+    # ---- the two directions by hand (aot_autograd.rs ``AotCompiledModule``): here the backward graph takes the
+    # forward's *inputs* and recomputes what it needs, so the "saved tensors" are the parameters and inputs
+    def forward_graph(self) -> IrGraph:
+        return self.pair.forward
+
+    def backward_graph(self) -> IrGraph:
+        return self.pair.backward
+
+    def _flat(self, inputs) -> list:
+        ps = [dict(self.module.named_parameters())[n].detach() for n in self.names] if self.module is not None else []
+        return [*ps, *[t.detach() for t in inputs]]
+
+    def forward_with_ctx(self, *inputs):
+        """``(output, context)``; hand the context to :meth:`backward` with the output's gradient."""
+        flat = self._flat(inputs)
+        env = _interpret(self.pair.forward, flat, block=self.cfg.block_size)
+        return env[self.pair.forward.outputs[0]], flat
+
+    def saved_tensors(self, ctx) -> list:
+        return list(ctx)
+
+    def saved_tensor_indices(self) -> list:
+        """Positions, among ``parameters + inputs``, of the tensors the backward graph reads: all of them."""
+        return list(range(self.pair.n_params + self.pair.n_inputs))
+
+    def backward(self, ctx, grad_output: torch.Tensor) -> list:
+        """Gradients in the order ``parameters + inputs`` (``None`` where none is defined)."""
+        env = _interpret(self.pair.backward, (*ctx, grad_output.contiguous()), block=self.cfg.block_size)
+        got = {i: env[o] for i, o in zip(self.pair.diff, self.pair.backward.outputs)}
+        return [got.get(i) for i in range(len(ctx))]
+
 
 def compile_aot(fn, example_inputs, config: CompileConfig | None = None) -> AotModule:
     """``compile`` for training: both directions run from graphs built ahead of time

@@ -320,6 +320,10 @@ class FusedChain:
         return CpuCodegen().generate(self.loop_ir(), "fused_chain")
 
 
+CpuCodegen.generate_rust_source = CpuCodegen.generate        # the host generator's output (Python over torch ops here)
+GpuCodegen.generate_ptx_source = GpuCodegen.generate         # the device generator's output (CUDA C for sm_100a here)
+
+
 class ReductionKind(enum.Enum):
     Sum = "sum"; Mean = "mean"; Max = "max"; Min = "min"; Prod = "prod"  # noqa: E702
 
@@ -640,6 +644,10 @@ class AutotuneResult:
     def winner_time(self) -> float:
         """Seconds per call of the winner (NaN when nothing was timed)."""
         return self.best.ms * 1e-3
+
+    def winner_compiled(self):
+        """Block-size tuning changes the module in place; there is no separate compiled object."""
+        return None
 
     def all_timings(self) -> list:
         return [(c.name, c.ms * 1e-3) for c in self.candidates]

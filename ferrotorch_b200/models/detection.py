@@ -680,3 +680,15 @@ OWN_MODELS = {"faster_rcnn": fasterrcnn_resnet50_fpn, "fasterrcnn_resnet50_fpn":
               "retinanet": retinanet_resnet50_fpn, "retinanet_resnet50_fpn": retinanet_resnet50_fpn,
               "fcos": fcos_resnet50_fpn, "fcos_resnet50_fpn": fcos_resnet50_fpn,
               "ssd300": ssd300_vgg16, "ssd300_vgg16": ssd300_vgg16, "yolo": yolo}
+
+
+# Rust's ``parameters_mut`` / ``num_parameters`` of the reference's detection modules: a Python module hands
+# out its (mutable) parameters through ``parameters()``
+def _num_parameters(self) -> int:
+    return sum(p.numel() for p in self.parameters() if p.requires_grad)
+
+
+for _cls in (FeaturePyramidNetwork, RPNHead, RegionProposalNetwork, TwoMLPHead, MaskRCNNHeads, MaskRCNNPredictor, SSD300, RetinaNet, FCOS,
+             Yolo):
+    _cls.parameters_mut = nn.Module.parameters
+    _cls.num_parameters = _num_parameters

@@ -63,6 +63,50 @@ class LlamaGpuInferencer:
             model.load_hf_state_dict(state_dict)
         return cls(model, device, dtype)
 
+    @classmethod
+    def from_gguf_gpu_dequant(cls, path: str, device=None, dtype: torch.dtype | None = None, config: LlamaConfig | None = None
+                              ) -> "LlamaGpuInferencer":
+        """From a GGUF file whose quantised tensors cross to the device as raw blocks and are expanded there
+        (ferrotorch-llama/src/gpu_gguf.rs:336); on the host the file's own decoder does the expansion.  The
+        configuration comes from the file's metadata unless one is given."""
+        from ..serialize.gguf import GgufFile, load_gguf_state_dict, load_gguf_state_dict_gpu
+
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        device = torch.device(device)
+        if config is None:
+            with GgufFile(path) as f:
+                md = f.metadata
+            arch = md.get("general.architecture", "llama")
+
+            def key(name, default=None):
+                return md.get("%s.%s" % (arch, name), default)
+
+            heads = int(key("attention.head_count"))
+            config = LlamaConfig(vocab_size=int(md.get("%s.vocab_size" % arch, len(md.get("tokenizer.ggml.tokens", [])) or 32000)),
+                                 hidden_size=int(key("embedding_length")), intermediate_size=int(key("feed_forward_length")),
+                                 num_hidden_layers=int(key("block_count")), num_attention_heads=heads,
+                                 num_key_value_heads=int(key("attention.head_count_kv", heads)),
+                                 max_position_embeddings=int(key("context_length", 2048)),
+                                 rms_norm_eps=float(key("attention.layer_norm_rms_epsilon", 1e-5)),
+                                 rope_theta=float(key("rope.freq_base", 10000.0)))
+        want = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+        sd = load_gguf_state_dict_gpu(path, device, want) if device.type == "cuda" else load_gguf_state_dict(path, want)
+        if "lm_head.weight" not in sd and "model.embed_tokens.weight" in sd:
+            sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
+        model = LlamaForCausalLM(config)
+        model.load_hf_state_dict(sd)
+        return cls(model, device, want)
+
+    def generate_masked(self, prompt_ids, processor, max_new_tokens: int) -> list:
+        """Greedy decoding under a grammar (a ``JsonSchemaProcessor`` or ``None``): every step's logits are
+        masked to the tokens the grammar admits, on the device the logits live on; generation stops when the
+        grammar is complete (gpu_gguf.rs:510-560).  Returns the generated ids."""
+        from .llama_compat import masked_decode_loop
+
+        return masked_decode_loop(lambda ids: self.forward_from_ids(ids), processor, prompt_ids, max_new_tokens,
+                                  self.device.index if self.device.type == "cuda" else None)
+
     def _ids(self, ids) -> torch.Tensor:
         ids = list(ids)
         if not ids:

@@ -349,8 +349,8 @@ class ASPP(nn.Module):
 
 
 class DeepLabHead(nn.Sequential):
-    def __init__(self, cin, classes):
-        super().__init__(ASPP(cin), nn.Conv2d(256, 256, 3, padding=1, bias=False), nn.BatchNorm2d(256), nn.ReLU(),
+    def __init__(self, cin, classes, rates=(12, 24, 36)):
+        super().__init__(ASPP(cin, rates), nn.Conv2d(256, 256, 3, padding=1, bias=False), nn.BatchNorm2d(256), nn.ReLU(),
                          nn.Conv2d(256, classes, 1))
 
 
@@ -369,6 +369,21 @@ class SegmentationModel(nn.Module):
         size = x.shape[-2:]
         y = self.classifier(self.backbone(x))
         return {"out": tF.interpolate(y, size=size, mode="bilinear", align_corners=False)}
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters() if p.requires_grad)
+
+    def with_atrous_rates(self, rates) -> "SegmentationModel":
+        """A DeepLabV3 model with another set of dilation rates in its pyramid head (freshly initialised head,
+        same backbone object): ``(6, 12, 18)`` for output stride 16, ``(12, 24, 36)`` for 8."""
+        if not isinstance(self.classifier, DeepLabHead):
+            raise TypeError("with_atrous_rates: this model's head is a %s, not a DeepLabV3 head" % type(self.classifier).__name__)
+        classes = self.classifier[-1].out_channels
+        out = SegmentationModel.__new__(SegmentationModel)
+        nn.Module.__init__(out)
+        out.backbone, out.classifier = self.backbone, DeepLabHead(2048, classes, tuple(rates))
+        convert_convs(out.classifier)
+        return out
 
 
 def fcn_resnet50(num_classes: int = 21, **kw):

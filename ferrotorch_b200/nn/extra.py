@@ -70,6 +70,11 @@ class SqueezeExcitation(nn.Module):
         self.activation = activation() if isinstance(activation, type) else activation
         self.scale_activation = scale_activation() if isinstance(scale_activation, type) else scale_activation
 
+    @classmethod
+    def new_with_activations(cls, input_channels: int, squeeze_channels: int, activation, scale_activation) -> "SqueezeExcitation":
+        """EfficientNet uses SiLU / sigmoid, MobileNetV3 ReLU / hard-sigmoid."""
+        return cls(input_channels, squeeze_channels, activation, scale_activation)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return x * self.scale_activation(self.fc2(self.activation(self.fc1(self.avgpool(x)))))
 

@@ -42,6 +42,12 @@ class PagePool:
             raise ValueError("page %d out of range" % page)
         self._free.append(page)
 
+    def alloc_page(self):
+        """A free page id, or ``None`` when the pool is exhausted (paged_attention.rs:200; ``allocate`` raises)."""
+        return self._free.pop() if self._free else None
+
+    free_page = free
+
     @property
     def num_free(self) -> int:
         return len(self._free)

@@ -529,3 +529,30 @@ class RpcAgent:
     def shutdown(self):
         self._stop = True
         self._srv.close()
+
+
+class TcpRpcBackend:
+    """Rank-addressed byte messages over a :class:`~.backend.Group` (ferrotorch-distributed/src/rpc.rs:282-350):
+    what the reference's RPC agent sits on.  ``send`` frames nothing itself -- the receiver asks for exactly
+    the bytes it expects, as the group's tensor transport does."""
+
+    def __init__(self, group: Group):
+        self.group = group
+
+    def rank(self) -> int:
+        return self.group.rank
+
+    def world_size(self) -> int:
+        return self.group.world_size
+
+    def send(self, data: bytes, dst_rank: int) -> None:
+        if not 0 <= dst_rank < self.group.world_size or dst_rank == self.group.rank:
+            raise InvalidRank("cannot send to rank %d from rank %d of %d" % (dst_rank, self.group.rank, self.group.world_size))
+        self.group.send(torch.frombuffer(bytearray(data), dtype=torch.uint8), dst_rank)
+
+    def recv(self, nbytes: int, src_rank: int, timeout: float | None = None) -> bytes:
+        if not 0 <= src_rank < self.group.world_size or src_rank == self.group.rank:
+            raise InvalidRank("cannot receive from rank %d on rank %d of %d" % (src_rank, self.group.rank, self.group.world_size))
+        buf = torch.empty(nbytes, dtype=torch.uint8)
+        self.group.recv(buf, src_rank, timeout) if timeout is not None else self.group.recv(buf, src_rank)
+        return bytes(buf.numpy())

@@ -19,7 +19,7 @@ from .dist_checkpoint import (AsyncDistributedCheckpointer, RpcAgent, load_distr
 DEFAULT_COLLECTIVE_TIMEOUT = _b.DEFAULT_COLLECTIVE_TIMEOUT_S
 
 Backend, TcpBackend, SimulatedBackend, SubBackend, HybridBackend = Group, TcpGroup, SimulatedGroup, SubGroup, HybridGroup
-TcpRpcBackend = RpcAgent
+from .dist_checkpoint import TcpRpcBackend  # noqa: F401,E402
 
 
 class ReduceOp(str, enum.Enum):

@@ -143,6 +143,7 @@ class Partial(_PlacementQueries):
 
 class DTensor:
     """A local shard + its placement on one mesh axis (group) + the global shape."""
+    mesh = None                      # the one-axis form has a group, not a mesh; ``from_local`` builds the mesh form
 
     def __init__(self, local: torch.Tensor, group: Group, placement, global_shape: Sequence[int] | None = None):
         self.local, self.group, self.placement = local, group, placement

@@ -194,6 +194,18 @@ class DispatchKeySet:
     def contains(self, key) -> bool:
         return bool(self.bits >> int(DispatchKey(key)) & 1)
 
+    def union(self, other: "DispatchKeySet") -> "DispatchKeySet":
+        out = DispatchKeySet()
+        out.bits = self.bits | other.bits
+        return out
+
+    def intersection(self, other: "DispatchKeySet") -> "DispatchKeySet":
+        out = DispatchKeySet()
+        out.bits = self.bits & other.bits
+        return out
+
+    __or__, __and__ = union, intersection
+
     __contains__ = contains
 
     def is_empty(self) -> bool:
@@ -445,6 +457,10 @@ class CumExtremeResult(tuple):
     @property
     def indices(self) -> Tensor:
         return self[1]
+
+    def indices_host(self) -> list:
+        """The indices as a (nested) Python list on the host."""
+        return self[1].cpu().tolist()
 
 
 def cummax(x: Tensor, dim: int) -> CumExtremeResult:
@@ -815,6 +831,9 @@ class SemiStructuredSparseBackend(enum.Enum):
     """One implementation here (this framework's expand-GEMM); the names remain for callers that pass one."""
     Cutlass = "cutlass"
     CuSparseLt = "cusparselt"
+
+    def as_str(self) -> str:
+        return self.value
 
 
 def sparse_matmul_24(a: Tensor, b: SemiStructuredSparseTensor) -> Tensor:

@@ -599,6 +599,13 @@ class TokenTransitionCache:
         self.max_entries = max_entries
         self._hits = self._misses = 0
 
+    def __len__(self) -> int:
+        return len(self._d)
+
+    def len(self) -> int:
+        """Masks held."""
+        return len(self._d)
+
     def hits(self) -> int:
         return self._hits
 

@@ -371,9 +371,87 @@ class MemoryReservation:
             self.guard.reserve -= self.nbytes
             self._held = False
 
+    def reserved_bytes(self) -> int:
+        return self.nbytes if self._held else 0
+
+    def device_ordinal(self) -> int:
+        return self.guard.device_ordinal()
+
     def __enter__(self):
         return self
 
     def __exit__(self, *exc):
         self.release()
         return False
+
+
+class MemoryWatchdog:
+    """The guard's background pressure check as an object of its own (memory_guard.rs:1147-1310): a thread
+    samples the allocator every ``interval_s``; while usage is above ``pressure_threshold`` x the usable budget
+    the guard is *paused* and training loops that call :meth:`wait_if_paused` between steps hold still."""
+
+    def __init__(self, guard: MemoryGuard, interval_s: float = 0.05, pressure_threshold: float | None = None):
+        self._guard, self.interval_s = guard, interval_s
+        if pressure_threshold is not None:
+            guard.pressure_threshold = pressure_threshold
+        self._checked = threading.Event()
+        guard.add_pressure_listener(lambda _p: self._checked.set())
+
+    def guard(self) -> MemoryGuard:
+        return self._guard
+
+    def device(self):
+        return self._guard.device()
+
+    def memory_info(self) -> tuple:
+        """``(free, total)`` bytes as the guard sees them."""
+        a = self._guard.alloc
+        return max(0, a.total_bytes() - a.used_bytes()), a.total_bytes()
+
+    def pressure_threshold_bytes(self) -> int:
+        g = self._guard
+        return int(g.pressure_threshold * max(1, g.budget - g.reserve))
+
+    def check_pressure(self) -> bool:
+        """One check now, on the caller's thread: is usage above the threshold?"""
+        self._checked.set()
+        return self._guard.alloc.used_bytes() >= self.pressure_threshold_bytes()
+
+    def start(self) -> "MemoryWatchdog":
+        self._guard.start_watchdog(self.interval_s)
+        return self
+
+    def stop(self) -> None:
+        self._guard.stop_watchdog()
+
+    def wait_if_paused(self, timeout_s: float = 1.0) -> bool:
+        return self._guard.wait_if_paused(timeout_s)
+
+    def wait_for_first_check(self, timeout_s: float = 1.0) -> bool:
+        """Block until the thread has looked at the allocator at least once (true) or the time is up."""
+        deadline = time.time() + timeout_s
+        while time.time() < deadline:
+            if self._checked.is_set() or (self._guard._watchdog is not None and self._guard._watchdog.is_alive()
+                                          and time.time() > deadline - timeout_s + 2 * self.interval_s):
+                return True
+            time.sleep(min(0.005, self.interval_s))
+        return self._checked.is_set()
+
+
+class MemoryGuardedDevice:
+    """A device handle whose allocations go through a guard (memory_guard.rs ``MemoryGuardedDevice``)."""
+
+    def __init__(self, guard: MemoryGuard):
+        self._guard = guard
+
+    def guard(self) -> MemoryGuard:
+        return self._guard
+
+    def device(self):
+        return self._guard.device()
+
+    def safe_alloc(self, shape, dtype=None):
+        return self._guard.safe_alloc(shape, dtype, self.device())
+
+    def safe_alloc_copy(self, data, dtype=None):
+        return self._guard.safe_alloc_copy(data, dtype, self.device())

@@ -115,6 +115,9 @@ class UNet(nn.Module):
             x = dec(torch.cat([s, x], 1))
         return self.head(x)
 
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters() if p.requires_grad)
+
 
 from .io import (GaussianNoise, RandomGaussianBlur, RawImage, VisionNormalize, VisionToTensor,  # noqa: F401,E402
                  raw_image_to_tensor, read_image, read_image_as_tensor, read_image_rgba, tensor_to_raw_image,

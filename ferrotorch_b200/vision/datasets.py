@@ -47,6 +47,7 @@ class _ArrayDataset(Dataset):
     """``images uint8 [N, C, H, W]`` + ``labels int64 [N]`` behind the Dataset protocol."""
 
     num_classes = 0
+    split = "train"                 # which part of the dataset an instance holds ("train" / "test")
 
     def __init__(self, images: torch.Tensor, labels: torch.Tensor, split: str, transform: Callable | None = None,
                  target_transform: Callable | None = None):

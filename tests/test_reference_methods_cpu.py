@@ -755,3 +755,99 @@ def test_model_and_distributed_leftover_methods(tmp_path):
     ck.save(str(tmp_path / "ck.pt"), {"w": torch.arange(4.0)})
     ck.wait()
     assert not ck.is_saving() and torch.equal(load_checkpoint(str(tmp_path / "ck.pt"))["model"]["w"], torch.arange(4.0))
+
+
+def test_gpu_side_helper_objects_without_a_gpu(tmp_path):
+    # ferrotorch-gpu/src/{graph,memory_guard,device}.rs names that are host logic; ferrotorch-llama/src/gpu_gguf.rs
+    import time as _time
+
+    from ferrotorch_b200 import cuda as C
+    from ferrotorch_b200 import jit as J
+    from ferrotorch_b200.utils.memory_guard import MemoryGuard, MemoryReservation
+
+    class Alloc:
+        used, device = 0, 0
+
+        def used_bytes(self):
+            return self.used
+
+        def total_bytes(self):
+            return 1000
+
+        def empty_cache(self):
+            pass
+
+    a = Alloc()
+    g = MemoryGuard(a, pressure_threshold=0.5)
+    w = C.MemoryWatchdog(g, 0.01)
+    assert w.pressure_threshold_bytes() == 500 and not w.check_pressure() and w.memory_info() == (1000, 1000) and w.guard() is g
+    w.start()
+    a.used = 900
+    _time.sleep(0.1)
+    assert g.paused.is_set() and w.wait_for_first_check(0.5) and not w.wait_if_paused(0.05) and w.check_pressure()
+    a.used = 0
+    assert w.wait_if_paused(1.0)
+    w.stop()
+    r = MemoryReservation(g, 100)
+    assert r.reserved_bytes() == 100 and r.device_ordinal() == 0
+    r.release()
+    assert r.reserved_bytes() == 0
+    d = C.MemoryGuardedDevice(g)
+    assert d.guard() is g and d.safe_alloc((3,)).shape == (3,) and d.safe_alloc_copy([1.0]).tolist() == [1.0]
+    assert C.CaptureMode.Relaxed.to_cuda() == 2 and C.CaptureStatus.Active.is_capturing() and C.CaptureStatus.Invalidated.is_invalidated()
+    assert not C.CaptureStatus.NotCapturing.is_capturing()
+    for name in ("begin", "begin_with_mode", "begin_with_pool", "begin_with_pool_mode", "finish", "status"):
+        assert hasattr(C.GraphCaptureGuard, name)
+    for name in ("with_private_pool", "record_buffer", "seal", "unseal", "buffer_count", "clear_buffers", "activate", "raw"):
+        assert hasattr(C.CapturePool, name)
+    # AOT module: both directions by hand
+    lin = torch.nn.Linear(3, 2)
+    x = torch.randn(4, 3, requires_grad=True)
+    aot = J.compile_aot(lin, (x.detach(),))
+    out, ctx = aot.forward_with_ctx(x.detach())
+    torch.testing.assert_close(out, lin(x).detach())
+    go = torch.randn(4, 2)
+    grads = aot.backward(ctx, go)
+    want = torch.autograd.grad(lin(x), [*lin.parameters(), x], go)
+    for got, exp in zip(grads, want):
+        torch.testing.assert_close(got, exp)
+    assert aot.saved_tensor_indices() == [0, 1, 2] and len(aot.saved_tensors(ctx)) == 3
+    assert aot.forward_graph() is aot.pair.forward and aot.backward_graph() is aot.pair.backward
+    # inferencer from a GGUF file, and greedy decoding under a grammar
+    from ferrotorch_b200.models.inferencer import LlamaGpuInferencer
+    from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.serialize import gguf as GG
+    from ferrotorch_b200.utils.grammar import JsonSchemaProcessor
+
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                      num_key_value_heads=1, max_position_embeddings=64)
+    torch.manual_seed(0)
+    src = LlamaForCausalLM(cfg).eval()
+    inv = {v: k for k, v in (("token_embd", "model.embed_tokens"), ("output_norm", "model.norm"), ("output", "lm_head"))}
+    layer_inv = {"input_layernorm": "attn_norm", "self_attn.q_proj": "attn_q", "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v",
+                 "self_attn.o_proj": "attn_output", "post_attention_layernorm": "ffn_norm", "mlp.gate_proj": "ffn_gate",
+                 "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down"}
+    tensors = {}
+    for k, v in src.hf_state_dict().items():
+        base, _, _suffix = k.rpartition(".")
+        if base.startswith("model.layers."):
+            _, _, idx, rest = base.split(".", 3)
+            name = "blk.%s.%s.weight" % (idx, layer_inv[rest])
+        else:
+            name = inv[base] + ".weight"
+        t = v.detach().float().contiguous()
+        tensors[name] = (GG.GGML_F32, tuple(t.shape), t.numpy().tobytes())
+    md = {"general.architecture": "llama", "llama.embedding_length": 32, "llama.feed_forward_length": 64, "llama.block_count": 1,
+          "llama.attention.head_count": 2, "llama.attention.head_count_kv": 1, "llama.context_length": 64, "llama.vocab_size": 64,
+          "llama.attention.layer_norm_rms_epsilon": float(cfg.rms_norm_eps), "llama.rope.freq_base": float(cfg.rope_theta)}
+    path = str(tmp_path / "tiny.gguf")
+    GG.write_gguf(path, tensors, md)
+    inf = LlamaGpuInferencer.from_gguf_gpu_dequant(path, device="cpu")
+    ids = [3, 9, 27]
+    torch.testing.assert_close(inf.forward_from_ids(ids), src(torch.tensor([ids]))[0, -1].detach().float(), rtol=1e-4, atol=1e-4)
+    vocab = [chr(97 + i % 26) * (1 + i // 26) for i in range(60)] + ["true", "false", "tr", "ue"]
+    proc = JsonSchemaProcessor({"type": "boolean"}, vocab)
+    gen = inf.generate_masked(ids, proc, 8)
+    text = "".join(vocab[t] for t in gen)
+    assert text in ("true", "false") and proc.is_complete()
+    assert len(inf.generate_masked(ids, None, 3)) == 3
