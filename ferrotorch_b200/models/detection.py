@@ -266,6 +266,57 @@ def heatmaps_to_keypoints(maps: torch.Tensor, rois: torch.Tensor):
     return xy.permute(0, 2, 1), sc
 
 
+def decode_per_class(box_regression: torch.Tensor, proposals: torch.Tensor, weights=(10.0, 10.0, 5.0, 5.0)) -> torch.Tensor:
+    """``box_regression [R, C * 4]`` -> boxes ``[R, C, 4]``: every proposal decoded once per class with the
+    Faster R-CNN delta weights (ferrotorch-vision/src/models/detection/roi_heads_postprocess.rs)."""
+    C = box_regression.shape[-1] // 4
+    return D.decode_boxes(box_regression, proposals, weights).reshape(-1, C, 4)
+
+
+def postprocess_detections(class_logits: torch.Tensor, box_regression: torch.Tensor, proposals: list[torch.Tensor],
+                           image_size: tuple[int, int], score_thresh: float = 0.05, nms_thresh: float = 0.5,
+                           detections_per_img: int = 100) -> list[dict]:
+    """Second-stage outputs to detections, per image: soft-max scores, per-class boxes clipped to the image,
+    background dropped, low scores and degenerate boxes removed, per-class NMS, the best
+    ``detections_per_img`` kept."""
+    C = class_logits.shape[-1]
+    boxes = decode_per_class(box_regression, torch.cat(proposals))
+    scores = tF.softmax(class_logits, -1)
+    out, off = [], 0
+    for p in proposals:
+        b, s = D.clip_boxes_to_image(boxes[off:off + len(p)], image_size), scores[off:off + len(p)]
+        off += len(p)
+        labels = torch.arange(C, device=b.device).view(1, -1).expand_as(s)
+        b, s, labels = b[:, 1:].reshape(-1, 4), s[:, 1:].reshape(-1), labels[:, 1:].reshape(-1)     # drop background
+        keep = torch.where(s > score_thresh)[0]
+        b, s, labels = b[keep], s[keep], labels[keep]
+        keep = D.remove_small_boxes(b, 1e-2)
+        b, s, labels = b[keep], s[keep], labels[keep]
+        keep = D.batched_nms(b, s, labels, nms_thresh)[:detections_per_img]
+        out.append({"boxes": b[keep], "labels": labels[keep], "scores": s[keep]})
+    return out
+
+
+def postprocess_masks(mask_logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """``mask_logits [R, C, M, M]`` and the predicted class of every detection -> that class's mask
+    probabilities ``[R, 1, M, M]``."""
+    return torch.sigmoid(mask_logits)[torch.arange(len(labels), device=mask_logits.device), labels][:, None]
+
+
+def apply_bn_buffers_from_state_dict(module: nn.Module, state_dict: dict, prefix: str = "") -> int:
+    """Copy the running statistics (``running_mean`` / ``running_var`` / ``num_batches_tracked``) of every batch-norm
+    layer below ``module`` from a state dict; returns how many buffers were set.  (``load_state_dict`` does this
+    too; the reference loads parameters and buffers in two passes.)"""
+    n = 0
+    with torch.no_grad():
+        for name, buf in module.named_buffers():
+            key = prefix + name
+            if name.rsplit(".", 1)[-1] in ("running_mean", "running_var", "num_batches_tracked") and key in state_dict:
+                buf.copy_(state_dict[key].to(buf.dtype))
+                n += 1
+    return n
+
+
 class RoIHeads(nn.Module):
     """Second stage: pooled box features -> class scores and per-class boxes -> per-class NMS; then,
     on the surviving boxes, the optional mask and keypoint branches."""
@@ -295,26 +346,11 @@ class RoIHeads(nn.Module):
     def forward(self, feats, proposals: list[torch.Tensor], image_size: tuple[int, int]) -> list[dict]:
         x = self.box_head(self.box_roi_pool(feats, proposals, image_size))
         logits, reg = self.box_predictor(x)
-        C = logits.shape[-1]
-        boxes = D.decode_boxes(reg, torch.cat(proposals), (10.0, 10.0, 5.0, 5.0)).reshape(-1, C, 4)
-        scores = tF.softmax(logits, -1)
-        out, off = [], 0
-        for p in proposals:
-            b, s = D.clip_boxes_to_image(boxes[off:off + len(p)], image_size), scores[off:off + len(p)]
-            off += len(p)
-            labels = torch.arange(C, device=b.device).view(1, -1).expand_as(s)
-            b, s, labels = b[:, 1:].reshape(-1, 4), s[:, 1:].reshape(-1), labels[:, 1:].reshape(-1)     # drop background
-            keep = torch.where(s > self.score_thresh)[0]
-            b, s, labels = b[keep], s[keep], labels[keep]
-            keep = D.remove_small_boxes(b, 1e-2)
-            b, s, labels = b[keep], s[keep], labels[keep]
-            keep = D.batched_nms(b, s, labels, self.nms_thresh)[: self.detections_per_img]
-            out.append({"boxes": b[keep], "labels": labels[keep], "scores": s[keep]})
+        out = postprocess_detections(logits, reg, proposals, image_size, self.score_thresh, self.nms_thresh, self.detections_per_img)
         if self.mask_roi_pool is not None:
             det = [o["boxes"] for o in out]
             ml = self.mask_predictor(self.mask_head(self.mask_roi_pool(feats, det, image_size)))
-            labels = torch.cat([o["labels"] for o in out])
-            prob = torch.sigmoid(ml)[torch.arange(len(labels), device=ml.device), labels][:, None]
+            prob = postprocess_masks(ml, torch.cat([o["labels"] for o in out]))
             for o, m in zip(out, prob.split([len(d) for d in det])):
                 o["masks"] = paste_masks_in_image(m, o["boxes"], image_size)
         if self.keypoint_roi_pool is not None:

@@ -32,6 +32,125 @@ def box_iou(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return inter / (box_area(a)[:, None] + box_area(b)[None, :] - inter)
 
 
+def _enclosing_and_iou(a: torch.Tensor, b: torch.Tensor):
+    iou = box_iou(a, b)
+    lt = torch.min(a[:, None, :2], b[None, :, :2])
+    rb = torch.max(a[:, None, 2:], b[None, :, 2:])
+    return iou, lt, rb
+
+
+def generalized_box_iou(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """GIoU ``[len(a), len(b)]``: IoU minus the share of the smallest enclosing box that neither box covers
+    (Rezatofighi et al. 2019); in ``(-1, 1]``."""
+    iou, lt, rb = _enclosing_and_iou(a, b)
+    wh = (rb - lt).clamp(min=0)
+    hull = wh[..., 0] * wh[..., 1]
+    total = box_area(a)[:, None] + box_area(b)[None, :]
+    union = total / (1 + iou)                                  # union = total - intersection, intersection = iou * union
+    return iou - (hull - union) / hull
+
+
+def _diou_terms(a: torch.Tensor, b: torch.Tensor, eps: float):
+    iou, lt, rb = _enclosing_and_iou(a, b)
+    wh = (rb - lt).clamp(min=0)
+    diag = wh[..., 0] ** 2 + wh[..., 1] ** 2 + eps
+    ca, cb = (a[:, :2] + a[:, 2:]) / 2, (b[:, :2] + b[:, 2:]) / 2
+    dist = ((ca[:, None, :] - cb[None, :, :]) ** 2).sum(-1)
+    return iou, dist / diag
+
+
+def distance_box_iou(a: torch.Tensor, b: torch.Tensor, eps: float = 1e-7) -> torch.Tensor:
+    """DIoU: IoU minus the squared centre distance over the squared diagonal of the enclosing box
+    (Zheng et al. 2020)."""
+    iou, penalty = _diou_terms(a, b, eps)
+    return iou - penalty
+
+
+def complete_box_iou(a: torch.Tensor, b: torch.Tensor, eps: float = 1e-7) -> torch.Tensor:
+    """CIoU: DIoU minus an aspect-ratio term ``alpha * v`` with ``v = (4 / pi^2) (atan(w_b / h_b) - atan(w_a / h_a))^2``
+    and ``alpha = v / (1 - IoU + v)`` (no gradient through ``alpha``)."""
+    import math
+
+    iou, penalty = _diou_terms(a, b, eps)
+    wa, ha = a[:, 2] - a[:, 0], a[:, 3] - a[:, 1]
+    wb, hb = b[:, 2] - b[:, 0], b[:, 3] - b[:, 1]
+    v = (4 / math.pi ** 2) * (torch.atan(wa / ha)[:, None] - torch.atan(wb / hb)[None, :]) ** 2
+    with torch.no_grad():
+        alpha = v / (1 - iou + v + eps)
+    return iou - penalty - alpha * v
+
+
+def box_convert(boxes: torch.Tensor, in_fmt: str, out_fmt: str) -> torch.Tensor:
+    """Between ``xyxy`` (corners), ``xywh`` (corner + size) and ``cxcywh`` (centre + size)."""
+    fmts = ("xyxy", "xywh", "cxcywh")
+    if in_fmt not in fmts or out_fmt not in fmts:
+        raise ValueError("box_convert: formats must be among %s, got %r -> %r" % (fmts, in_fmt, out_fmt))
+    if in_fmt == out_fmt:
+        return boxes.clone()
+    a, b, c, d = boxes.unbind(-1)
+    if in_fmt == "xywh":
+        a, b, c, d = a, b, a + c, b + d
+    elif in_fmt == "cxcywh":
+        a, b, c, d = a - c / 2, b - d / 2, a + c / 2, b + d / 2
+    if out_fmt == "xywh":
+        a, b, c, d = a, b, c - a, d - b
+    elif out_fmt == "cxcywh":
+        a, b, c, d = (a + c) / 2, (b + d) / 2, c - a, d - b
+    return torch.stack((a, b, c, d), -1)
+
+
+def sigmoid_focal_loss(inputs: torch.Tensor, targets: torch.Tensor, alpha: float = 0.25, gamma: float = 2.0,
+                       reduction: str = "none") -> torch.Tensor:
+    """Binary focal loss on logits (Lin et al. 2017): ``alpha_t (1 - p_t)^gamma BCE``; ``alpha < 0`` switches the
+    class weighting off."""
+    p = torch.sigmoid(inputs)
+    ce = torch.nn.functional.binary_cross_entropy_with_logits(inputs, targets, reduction="none")
+    p_t = p * targets + (1 - p) * (1 - targets)
+    loss = ce * (1 - p_t) ** gamma
+    if alpha >= 0:
+        loss = (alpha * targets + (1 - alpha) * (1 - targets)) * loss
+    if reduction == "mean":
+        return loss.mean()
+    if reduction == "sum":
+        return loss.sum()
+    if reduction != "none":
+        raise ValueError("sigmoid_focal_loss: reduction must be none, mean or sum, got %r" % reduction)
+    return loss
+
+
+focal_loss = sigmoid_focal_loss
+
+
+def roi_pool(feat: torch.Tensor, rois: torch.Tensor, output_size: int | tuple[int, int], spatial_scale: float = 1.0) -> torch.Tensor:
+    """RoI max pooling (Fast R-CNN): the box, rounded to feature cells, is cut into ``ph x pw`` bins (integer
+    edges: floor of the start, ceil of the end) and every bin gives its maximum; empty bins give zero.
+    ``rois [K, 5]`` = (batch index, x1, y1, x2, y2), or a list with one ``[k, 4]`` tensor per image."""
+    if not torch.is_tensor(rois):
+        rois = torch.cat([torch.cat([b.new_full((len(b), 1), i), b], 1) for i, b in enumerate(rois)])
+    ph, pw = (output_size, output_size) if isinstance(output_size, int) else output_size
+    N, C, H, W = feat.shape
+    out = feat.new_zeros((rois.shape[0], C, ph, pw))
+    import math
+
+    def rnd(v: float) -> int:                                  # halves away from zero, as C's round()
+        return int(math.floor(abs(v) + 0.5)) * (1 if v >= 0 else -1)
+
+    r = rois.detach().cpu().double().tolist()
+    for k in range(rois.shape[0]):
+        n = int(r[k][0])
+        x1, y1, x2, y2 = (rnd(r[k][j] * spatial_scale) for j in range(1, 5))
+        rw, rh = max(x2 - x1 + 1, 1), max(y2 - y1 + 1, 1)
+        for i in range(ph):
+            hs = min(max(math.floor(i * rh / ph) + y1, 0), H)
+            he = min(max(math.ceil((i + 1) * rh / ph) + y1, 0), H)
+            for j in range(pw):
+                ws = min(max(math.floor(j * rw / pw) + x1, 0), W)
+                we = min(max(math.ceil((j + 1) * rw / pw) + x1, 0), W)
+                if he > hs and we > ws:
+                    out[k, :, i, j] = feat[n, :, hs:he, ws:we].amax((-2, -1))
+    return out
+
+
 def _host_lib():
     """The native host library with the prototypes of its detection entry points set (``None`` when
     it cannot be built or loaded)."""
@@ -327,3 +446,8 @@ class DefaultBoxGenerator:
         b = torch.cat(out)                                             # cx, cy, w, h in [0, 1]
         xyxy = torch.cat((b[:, :2] - 0.5 * b[:, 2:], b[:, :2] + 0.5 * b[:, 2:]), 1)
         return xyxy * torch.as_tensor([image_size[1], image_size[0]] * 2, dtype=dtype, device=device)
+
+
+def roi_align_with_aligned(feat, rois, output_size, spatial_scale: float = 1.0, sampling_ratio: int = 2, aligned: bool = True):
+    """:func:`roi_align` with the half-pixel shift as an explicit argument (default on)."""
+    return roi_align(feat, rois, output_size, spatial_scale, sampling_ratio, aligned)

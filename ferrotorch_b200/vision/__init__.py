@@ -22,7 +22,9 @@ from torch import nn
 
 from ..models.resnet import create_model, list_models, register_model, resnet18, resnet34, resnet50  # noqa: F401
 
-from ..ops.det_ops import batched_nms, box_iou, nms, roi_align  # noqa: F401,E402
+from ..ops.det_ops import (batched_nms, box_area, box_convert, box_iou, clip_boxes_to_image, complete_box_iou,  # noqa: F401,E402
+                           decode_boxes, distance_box_iou, focal_loss, generalized_box_iou, nms, remove_small_boxes, roi_align,
+                           roi_align_with_aligned, roi_pool, sigmoid_focal_loss)
 
 try:
     import torchvision
@@ -129,3 +131,23 @@ from .compat import *  # noqa: F401,F403,E402
 from .compat import (FPN_OUT_CHANNELS, IMAGENET_MEAN, IMAGENET_STD, SSD_ANCHORS_PER_SCALE, SSD_FM_SIZES,  # noqa: F401,E402
                      SSD_TOTAL_ANCHORS, CifarSample, Detections, MaskDetections, MnistSample, ModelConstructor,
                      SsdDetections)
+
+
+def __getattr__(name):
+    """Constructor functions of the model zoo under the reference's names (``vision.vgg16()``,
+    ``vision.retinanet_resnet50_fpn()``, ``vision.swin_tiny()`` ...), resolved through the registry on first use,
+    and the detectors' post-processing helpers."""
+    alias = {"swin_tiny": "swin_t"}
+    if name == "mobilenet_v3_large_dilated":
+        return lambda **kw: build("mobilenet_v3_large", dilated=True, **kw)
+    if name == "resnet50_dilated":
+        return lambda num_classes=1000, **kw: resnet50(num_classes=num_classes, replace_stride_with_dilation=(False, True, True), **kw)
+    if name in ("heatmaps_to_keypoints", "paste_masks_in_image", "postprocess_detections", "postprocess_masks", "decode_per_class",
+                "apply_bn_buffers_from_state_dict"):
+        from ..models import detection
+
+        return getattr(detection, name)
+    target = alias.get(name, name)
+    if target in available() or target in CLASSIFIERS or target in set(DETECTORS.values()) | set(SEGMENTERS.values()):
+        return lambda **kw: build(target, **kw)
+    raise AttributeError(name)

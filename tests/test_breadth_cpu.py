@@ -575,7 +575,7 @@ def test_gpu_crate_names_without_a_gpu():
     from ferrotorch_b200.utils import memory_guard as MG
 
     assert C.capture_status() is C.CaptureStatus.NotCapturing and str(C.CaptureMode.ThreadLocal) == "thread_local"
-    assert C.GpuTensor is torch.Tensor and C.MemoryWatchdog is MG.MemoryGuard and C.MemoryStats is MG.MemoryStats
+    assert C.GpuTensor is torch.Tensor and C.MemoryWatchdog is MG.MemoryWatchdog and C.MemoryStats is MG.MemoryStats
     alloc = C.CudaAllocator()
     assert alloc.allocated_bytes() == 0 and alloc.round_len(1000) == 1024 and alloc.round_len(3 << 20) == 4 << 20
     if not torch.cuda.is_available():

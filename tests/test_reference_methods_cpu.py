@@ -851,3 +851,59 @@ def test_gpu_side_helper_objects_without_a_gpu(tmp_path):
     text = "".join(vocab[t] for t in gen)
     assert text in ("true", "false") and proc.is_complete()
     assert len(inf.generate_masked(ids, None, 3)) == 3
+
+
+def test_box_operators_losses_and_roi_pooling_match_torchvision_ops():
+    # ferrotorch-vision/src/ops.rs (box_area / box_convert / *_box_iou / roi_pool / focal loss), roi_heads_postprocess.rs
+    import torchvision.ops as TO
+
+    from ferrotorch_b200 import vision as V
+
+    torch.manual_seed(0)
+
+    def boxes(n):
+        xy, wh = torch.rand(n, 2) * 50, torch.rand(n, 2) * 30 + 1
+        return torch.cat([xy, xy + wh], 1)
+
+    a, b = boxes(7), boxes(5)
+    for ours, theirs in ((V.generalized_box_iou, TO.generalized_box_iou), (V.distance_box_iou, TO.distance_box_iou),
+                         (V.complete_box_iou, TO.complete_box_iou), (V.box_iou, TO.box_iou)):
+        torch.testing.assert_close(ours(a, b), theirs(a, b), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(V.box_area(a), TO.box_area(a))
+    for i in ("xyxy", "xywh", "cxcywh"):
+        src = TO.box_convert(a, "xyxy", i)
+        for o in ("xyxy", "xywh", "cxcywh"):
+            torch.testing.assert_close(V.box_convert(src, i, o), TO.box_convert(src, i, o))
+    with pytest.raises(ValueError):
+        V.box_convert(a, "xyxy", "polar")
+    torch.testing.assert_close(V.clip_boxes_to_image(a * 3 - 20, (40, 60)), TO.clip_boxes_to_image(a * 3 - 20, (40, 60)))
+    assert torch.equal(V.remove_small_boxes(a, 12.0), TO.remove_small_boxes(a, 12.0))
+    x, t = torch.randn(6, 4), (torch.rand(6, 4) > 0.5).float()
+    for red in ("none", "mean", "sum"):
+        torch.testing.assert_close(V.sigmoid_focal_loss(x, t, 0.25, 2.0, red), TO.sigmoid_focal_loss(x, t, 0.25, 2.0, red))
+    torch.testing.assert_close(V.focal_loss(x, t, -1.0, 1.5), TO.sigmoid_focal_loss(x, t, -1.0, 1.5))
+    feat = torch.randn(2, 3, 16, 20)
+    rois = torch.tensor([[0, 2.0, 3.0, 30.0, 25.0], [1, 0.0, 0.0, 39.0, 31.0], [0, 10.0, 4.0, 12.0, 9.0], [1, 35.0, 20.0, 80.0, 60.0]])
+    for scale in (1.0, 0.5, 0.25):
+        for size in ((3, 4), 7, 1):
+            assert torch.equal(V.roi_pool(feat, rois, size, scale), TO.roi_pool(feat, rois, size, scale))
+    assert torch.equal(V.roi_pool(feat, [rois[[0, 2], 1:], rois[[1, 3], 1:]], 2), TO.roi_pool(feat, [rois[[0, 2], 1:], rois[[1, 3], 1:]], 2))
+    torch.testing.assert_close(V.roi_align_with_aligned(feat, rois, 3, 0.5, 2), TO.roi_align(feat, rois, 3, 0.5, 2, True))
+    # second-stage post-processing as free functions
+    logits, reg = torch.randn(6, 4), torch.randn(6, 16) * 0.1
+    props = [boxes(4), boxes(2)]
+    det = V.postprocess_detections(logits, reg, props, (80, 80), score_thresh=0.0, nms_thresh=0.5, detections_per_img=5)
+    assert len(det) == 2 and all(len(d["boxes"]) <= 5 and d["labels"].min() >= 1 for d in det if len(d["boxes"]))
+    per_class = V.decode_per_class(reg, torch.cat(props))
+    assert per_class.shape == (6, 4, 4)
+    ml = torch.randn(3, 4, 5, 5)
+    pm = V.postprocess_masks(ml, torch.tensor([1, 3, 2]))
+    assert pm.shape == (3, 1, 5, 5) and torch.equal(pm[1, 0], torch.sigmoid(ml[1, 3]))
+    bn_src, bn_dst = torch.nn.BatchNorm2d(3), torch.nn.BatchNorm2d(3)
+    bn_src.running_mean.fill_(2.0)
+    assert V.apply_bn_buffers_from_state_dict(bn_dst, bn_src.state_dict()) == 3 and float(bn_dst.running_mean[0]) == 2.0
+    for name in ("vgg11", "swin_tiny", "retinanet_resnet50_fpn", "mobilenet_v3_large_dilated", "resnet50_dilated", "yolo", "unet"):
+        assert callable(getattr(V, name))
+    assert type(V.mobilenet_v3_small(num_classes=7)).__name__ == "MobileNetV3"
+    with pytest.raises(AttributeError):
+        V.no_such_model
