@@ -898,7 +898,7 @@ def test_box_operators_losses_and_roi_pooling_match_torchvision_ops():
     assert per_class.shape == (6, 4, 4)
     ml = torch.randn(3, 4, 5, 5)
     pm = V.postprocess_masks(ml, torch.tensor([1, 3, 2]))
-    assert pm.shape == (3, 1, 5, 5) and torch.equal(pm[1, 0], torch.sigmoid(ml[1, 3]))
+    assert pm.shape == (3, 1, 5, 5) and torch.allclose(pm[1, 0], torch.sigmoid(ml[1, 3]))
     bn_src, bn_dst = torch.nn.BatchNorm2d(3), torch.nn.BatchNorm2d(3)
     bn_src.running_mean.fill_(2.0)
     assert V.apply_bn_buffers_from_state_dict(bn_dst, bn_src.state_dict()) == 3 and float(bn_dst.running_mean[0]) == 2.0
