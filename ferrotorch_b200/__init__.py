@@ -47,7 +47,9 @@ def __getattr__(name):
             pass
         from .ops import ptq
 
-        for home in (core, autograd, ptq, torch):
+        more = importlib.import_module(".tensor_ops_more", __name__)
+        for home in (more, core, autograd, ptq, torch, torch.linalg, torch.special, torch.nn.functional, torch.signal.windows,
+                     torch.fft):
             if hasattr(home, name):
                 return getattr(home, name)
     raise AttributeError("module %r has no attribute %r" % (__name__, name))

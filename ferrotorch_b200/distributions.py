@@ -26,3 +26,50 @@ def kl_expfamily_expfamily(p, q):
         term = (b - a) * g
         out = out - (term if term.dim() == out.dim() else term.reshape(out.shape + (-1,)).sum(-1))
     return out.detach() if not any(t.requires_grad for t in qn) else out
+
+
+# constraint constructors and instances at the top level, as the reference's crate exposes them (constraints.rs)
+from torch.distributions.constraints import (boolean, corr_cholesky, greater_than, greater_than_eq, half_open_interval,  # noqa: F401,E402
+                                             integer_interval, less_than, lower_cholesky, nonnegative, nonnegative_integer,
+                                             positive, real, real_vector, simplex, unit_interval)
+from torch.distributions.constraints import interval as closed_interval  # noqa: F401,E402
+
+
+class _OpenInterval(constraints.Constraint):
+    """``lower < x < upper``."""
+
+    def __init__(self, lower_bound, upper_bound):
+        self.lower_bound, self.upper_bound = lower_bound, upper_bound
+        super().__init__()
+
+    def check(self, value):
+        return (self.lower_bound < value) & (value < self.upper_bound)
+
+    def __repr__(self):
+        return "open_interval(lower_bound=%s, upper_bound=%s)" % (self.lower_bound, self.upper_bound)
+
+
+open_interval = _OpenInterval
+
+
+def try_kl_expfamily(p, q):
+    """``KL(p || q)`` through the exponential-family formula when both operands belong to the same family that
+    defines natural parameters and a log-normaliser, else ``None`` (exp_family.rs:164)."""
+    if type(p) is not type(q) or not isinstance(p, ExponentialFamily):  # noqa: F405
+        return None
+    try:
+        return kl_expfamily_expfamily(p, q)
+    except NotImplementedError:
+        return None
+
+
+def kl_divergence_dyn(p, q):
+    """``KL(p || q)`` for operands whose types are only known at run time: the registered closed form when
+    there is one, else the exponential-family formula, else an error (kl.rs ``kl_divergence_dyn``)."""
+    try:
+        return kl_divergence(p, q)
+    except NotImplementedError:
+        out = try_kl_expfamily(p, q)
+        if out is None:
+            raise
+        return out

@@ -198,7 +198,9 @@ class QuantizedModel:
 
     def compression_ratio(self) -> float:
         """fp32 bytes of the same weights over :meth:`quantized_size_bytes`."""
-        dense = sum(self._entry(n)[0].numel() * 4 for n in self.layers)
+        dense = 0
+        for n in self.layers:
+            dense += self._entry(n)[0].numel() * 4
         return dense / self.quantized_size_bytes() if self.layers else 1.0
 
     def _entry(self, name: str):
@@ -262,6 +264,137 @@ class QatModel(nn.Module):
 
 
 KVPage = tuple      # (layer, page index): pages are slices of the pool's device tensors, addressed by index
+
+
+
+# --------------------------------------------------------------------------- free functions of functional.rs / padding.rs / init.rs
+def _mode(mode) -> str:
+    m = str(getattr(mode, "value", mode)).lower()
+    return {"zeros": "constant", "zero": "constant", "constant": "constant", "reflect": "reflect", "replicate": "replicate",
+            "circular": "circular"}.get(m, m)
+
+
+def functional_pad_1d(x, pad_left: int, pad_right: int, mode="constant", value: float = 0.0):
+    """Pad the last dimension; ``mode``: constant / reflect / replicate / circular.  Negative amounts crop
+    (the ``_signed`` spelling of the reference takes signed amounts; Python integers are signed anyway)."""
+    m = _mode(mode)
+    return nn.functional.pad(x, (pad_left, pad_right), m, value if m == "constant" else None)
+
+
+def functional_pad_2d(x, pad_left: int, pad_right: int, pad_top: int, pad_bottom: int, mode="constant", value: float = 0.0):
+    m = _mode(mode)
+    return nn.functional.pad(x, (pad_left, pad_right, pad_top, pad_bottom), m, value if m == "constant" else None)
+
+
+def functional_pad_3d(x, pad_left: int, pad_right: int, pad_top: int, pad_bottom: int, pad_front: int, pad_back: int,
+                      mode="constant", value: float = 0.0):
+    m = _mode(mode)
+    return nn.functional.pad(x, (pad_left, pad_right, pad_top, pad_bottom, pad_front, pad_back), m, value if m == "constant" else None)
+
+
+functional_pad_1d_signed, functional_pad_2d_signed, functional_pad_3d_signed = functional_pad_1d, functional_pad_2d, functional_pad_3d
+
+
+def gelu_with(x, approximate="none"):
+    return nn.functional.gelu(x, approximate=str(getattr(approximate, "value", approximate)).lower())
+
+
+def elu_with(x, alpha: float = 1.0):
+    return nn.functional.elu(x, alpha)
+
+
+def softplus_with(x, beta: float = 1.0, threshold: float = 20.0):
+    return nn.functional.softplus(x, beta, threshold)
+
+
+def hardtanh_with(x, min_val: float = -1.0, max_val: float = 1.0):
+    return nn.functional.hardtanh(x, min_val, max_val)
+
+
+def log_sigmoid(x):
+    return nn.functional.logsigmoid(x)
+
+
+def sum(x):  # noqa: A001 - the reference's functional module exports the full reductions under these names
+    return x.sum()
+
+
+def mean(x):
+    return x.mean()
+
+
+def zeros(param):
+    """Initialiser: fill with zeros (init.rs:93)."""
+    return nn.init.zeros_(param)
+
+
+def ones(param):
+    return nn.init.ones_(param)
+
+
+def _fan(param, mode) -> int:
+    fan_in, fan_out = nn.init._calculate_fan_in_and_fan_out(param)
+    return fan_in if str(getattr(mode, "value", mode)).lower() in ("fan_in", "fanin") else fan_out
+
+
+def _gain(nonlinearity, a: float = 0.0) -> float:
+    return nn.init.calculate_gain(str(getattr(nonlinearity, "value", nonlinearity)).lower(), a)
+
+
+def kaiming_normal_with_fan_mode_and_generator(param, nonlinearity="relu", mode="fan_in", generator=None, a: float = 0.0):
+    with torch.no_grad():
+        return param.normal_(0.0, _gain(nonlinearity, a) / _fan(param, mode) ** 0.5, generator=generator)
+
+
+def kaiming_uniform_with_fan_mode_and_generator(param, nonlinearity="relu", mode="fan_in", generator=None, a: float = 0.0):
+    bound = 3.0 ** 0.5 * _gain(nonlinearity, a) / _fan(param, mode) ** 0.5
+    with torch.no_grad():
+        return param.uniform_(-bound, bound, generator=generator)
+
+
+def kaiming_normal_with_fan_mode(param, nonlinearity="relu", mode="fan_in"):
+    return kaiming_normal_with_fan_mode_and_generator(param, nonlinearity, mode)
+
+
+def kaiming_uniform_with_fan_mode(param, nonlinearity="relu", mode="fan_in"):
+    return kaiming_uniform_with_fan_mode_and_generator(param, nonlinearity, mode)
+
+
+def kaiming_normal_with_generator(param, nonlinearity="relu", generator=None):
+    return kaiming_normal_with_fan_mode_and_generator(param, nonlinearity, "fan_in", generator)
+
+
+def kaiming_uniform_with_generator(param, nonlinearity="relu", generator=None):
+    return kaiming_uniform_with_fan_mode_and_generator(param, nonlinearity, "fan_in", generator)
+
+
+def xavier_normal_with_generator(param, gain: float = 1.0, generator=None):
+    return nn.init.xavier_normal_(param, gain, generator=generator)
+
+
+def xavier_uniform_with_generator(param, gain: float = 1.0, generator=None):
+    return nn.init.xavier_uniform_(param, gain, generator=generator)
+
+
+def normal_with_generator(param, mean: float = 0.0, std: float = 1.0, generator=None):
+    return nn.init.normal_(param, mean, std, generator=generator)
+
+
+def uniform_with_generator(param, a: float = 0.0, b: float = 1.0, generator=None):
+    return nn.init.uniform_(param, a, b, generator=generator)
+
+
+def trunc_normal_with_generator(param, mean: float = 0.0, std: float = 1.0, a: float = -2.0, b: float = 2.0, generator=None):
+    return nn.init.trunc_normal_(param, mean, std, a, b, generator=generator)
+
+
+def orthogonal_with_generator(param, gain: float = 1.0, generator=None):
+    return nn.init.orthogonal_(param, gain, generator=generator)
+
+
+def sparse_with_generator(param, sparsity: float, std: float = 0.01, generator=None):
+    return nn.init.sparse_(param, sparsity, std, generator=generator)
+
 
 __all__ = [_n for _n, _o in list(globals().items())
            if not _n.startswith("_") and type(_o).__name__ != "module" and _n not in ("annotations", "Callable", "Dict", "Any", "Hashable")]

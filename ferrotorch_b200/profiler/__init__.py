@@ -107,6 +107,12 @@ def estimate_flops(op: str, shapes) -> float | None:
     return None
 
 
+def estimate(op_name: str, input_shapes):
+    """FLOPs of an op from its input shapes as an integer, ``None`` for an op without a formula (flops.rs:53)."""
+    v = estimate_flops(op_name, [tuple(s) for s in input_shapes])
+    return None if v is None else int(v)
+
+
 class Profiler:
     _current: "Profiler | None" = None
 

@@ -907,3 +907,99 @@ def test_box_operators_losses_and_roi_pooling_match_torchvision_ops():
     assert type(V.mobilenet_v3_small(num_classes=7)).__name__ == "MobileNetV3"
     with pytest.raises(AttributeError):
         V.no_such_model
+
+
+def test_free_functions_of_the_core_nn_and_distributions_crates():
+    # ferrotorch-core/src/{ops,linalg,signal,shape,stride_tricks,meta_propagate,vmap}/, ferrotorch-nn/src/{functional,padding,init}.rs,
+    # ferrotorch-distributions/src/{constraints,kl,exp_family}.rs, ferrotorch-profiler/src/flops.rs
+    import numpy as np
+    from scipy.signal import windows as W
+
+    import ferrotorch_b200 as ft
+    from ferrotorch_b200 import distributions as Dn
+    from ferrotorch_b200 import nn as N
+    from ferrotorch_b200 import profiler as Pf
+
+    for n in (1, 2, 7, 16):
+        for sym in (True, False):
+            for name, args in (("parzen", ()), ("tukey", (0.3,)), ("tukey", (0.0,)), ("tukey", (1.0,)), ("taylor", (4, 30.0)),
+                               ("taylor", (3, 40.0, False))):
+                got = getattr(ft, name)(n, *args, sym=sym, dtype=torch.float64).numpy()
+                assert np.allclose(got, getattr(W, name)(n, *args, sym=sym), atol=1e-12), (name, n, sym, args)
+    assert torch.equal(ft.hanning(5), torch.signal.windows.hann(5)) and ft.kaiser(5, beta=3.0).shape == (5,)     # torch's, through the root
+    x = torch.randn(3, 4, 5)
+    assert torch.equal(ft.amax_dim(x, 1), x.amax(1)) and torch.equal(ft.argmin_dim(x, 2, True), x.argmin(2, True))
+    assert torch.equal(ft.reduce_dim(x, 0, "prod"), x.prod(0)) and torch.equal(ft.reverse_cumsum(x, 1), x.flip(1).cumsum(1).flip(1))
+    torch.testing.assert_close(ft.std_with_correction(x, 1, 0), x.std(1, correction=0))
+    torch.testing.assert_close(ft.logsumexp_dim(x, 2), x.logsumexp(2))
+    assert torch.equal(ft.add_scaled(x, x, 0.5), x * 1.5) and torch.equal(ft.mm_bt_differentiable(x[0], x[1]), x[0] @ x[1].t())
+    assert ft.channels_last_strides((2, 3, 4, 5)) == torch.empty(2, 3, 4, 5).contiguous(memory_format=torch.channels_last).stride()
+    assert ft.channels_last_3d_strides((2, 3, 4, 5, 6)) == torch.empty(2, 3, 4, 5, 6).contiguous(memory_format=torch.channels_last_3d).stride()
+    assert ft.c_contiguous_strides((2, 3, 4)) == (12, 4, 1) and ft.checked_numel((2, 3)) == 6 and ft.checked_byte_count((2, 3), 4) == 24
+    with pytest.raises(ft.FerrotorchError):
+        ft.checked_numel((2 ** 40, 2 ** 40))
+    with pytest.raises(ft.FerrotorchError):
+        ft.channels_last_strides((2, 3))
+    assert ft.zeros_meta((2, 3)).device.type == "meta" and ft.meta_like(x).shape == x.shape and ft.fft_norm_from_str(None) == "backward"
+    v, tau = torch.randn(5, 3), torch.rand(3)
+    q = ft.householder_product_full(v, tau)
+    assert q.shape == (5, 5) and torch.allclose(q[:, :3], torch.linalg.householder_product(v, tau), atol=1e-6)
+    g = ft.per_sample_grad(lambda p, row: (p * row).sum() ** 2, torch.ones(3), torch.arange(6.0).view(2, 3))
+    assert torch.equal(g, torch.tensor([[0.0, 6.0, 12.0], [72.0, 96.0, 120.0]]))
+    assert torch.equal(ft.masked_fill_bcast(x, torch.tensor([True, False, False, False, True]), 0.0)[..., 0], torch.zeros(3, 4))
+    assert torch.equal(ft.unary_map_named(x, "erf"), torch.erf(x)) and torch.equal(ft.binary_broadcast(x, x[0], torch.add), x + x[0])
+    with pytest.raises(ft.FerrotorchError):
+        ft.binary_map(x, x[0], torch.add)
+    # torch's own spellings reached through the package root
+    assert ft.pinv(torch.eye(2)).shape == (2, 2) and ft.glu(torch.randn(2, 4)).shape == (2, 2)
+    assert float(ft.chebyshev_polynomial_t(torch.tensor([0.5]), torch.tensor([3]))) == -1.0
+    # autocast / saved-tensor / profiler plumbing
+    assert ft.autocast_log("matmul", "cpu") is None
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        assert (ft.autocast_log("matmul", "cpu"), ft.autocast_log("softmax", "cpu"), ft.autocast_log("relu", "cpu")) == ("reduced", "full", "keep")
+        snap = ft.current_autocast_snapshot()
+    with ft.with_autocast_state(snap):
+        assert (torch.ones(2, 2) @ torch.ones(2, 2)).dtype == torch.bfloat16
+    assert not ft.has_saved_tensor_hooks()
+    with ft.tracked_saved_tensors_hooks(lambda t: t.half(), lambda p: p.float()):
+        assert ft.has_saved_tensor_hooks() and ft.pack_saved_tensor(torch.ones(2)).dtype == torch.float16
+        y = torch.ones(2, requires_grad=True)
+        (y * y).sum().backward()
+    assert torch.equal(y.grad, torch.full((2,), 2.0)) and ft.unpack_saved_tensor(3) == 3
+    prof = Pf.Profiler(Pf.ProfileConfig(cuda_events=False))
+    ft.set_current(prof)
+    with ft.profile_op_scope("matmul", "linalg", [(2, 2), (2, 2)]):
+        pass
+    ft.set_current(None)
+    with ft.profile_op_scope("ignored"):
+        pass
+    assert ft.current() is None and [e.name for e in prof.events] == ["matmul"]
+    before = torch.rand(1)
+    torch.manual_seed(5)
+    a = torch.rand(1)
+    torch.manual_seed(5)
+    ft.with_default_rng_test_lock(lambda: torch.rand(100))
+    assert torch.equal(torch.rand(1), a) and before is not None
+    o1, o2 = ft.checkpoint_multi(lambda p, r: (p * r, p + r), torch.ones(2, requires_grad=True), torch.ones(2))
+    assert o1.requires_grad and torch.equal(o2, torch.full((2,), 2.0))
+    # nn: padding, parameterised activations, seeded initialisers
+    seq = torch.arange(6.0).view(1, 1, 6)
+    assert N.functional_pad_1d(seq, 2, -1, "reflect").tolist() == [[[2.0, 1.0, 0.0, 1.0, 2.0, 3.0, 4.0]]]
+    assert N.functional_pad_2d_signed(torch.ones(1, 1, 2, 2), 1, 0, 0, 1, N.PaddingMode.Zeros if hasattr(N.PaddingMode, "Zeros") else "zeros", 5.0).shape == (1, 1, 3, 3)
+    g1, g2 = torch.Generator().manual_seed(1), torch.Generator().manual_seed(1)
+    p1, p2 = torch.nn.Parameter(torch.empty(8, 4)), torch.nn.Parameter(torch.empty(8, 4))
+    N.kaiming_uniform_with_fan_mode_and_generator(p1, "relu", "fan_out", g1)
+    torch.nn.init.kaiming_uniform_(p2, mode="fan_out", nonlinearity="relu", generator=g2)
+    assert torch.equal(p1, p2)
+    N.trunc_normal_with_generator(p1, 0.0, 1.0, -0.5, 0.5, g1)
+    assert float(p1.detach().abs().max()) <= 0.5 and float(N.log_sigmoid(torch.zeros(1))) == pytest.approx(-0.6931, abs=1e-4)
+    torch.testing.assert_close(N.gelu_with(seq, "tanh"), torch.nn.functional.gelu(seq, approximate="tanh"))
+    torch.testing.assert_close(N.softplus_with(seq, 2.0, 3.0), torch.nn.functional.softplus(seq, 2.0, 3.0))
+    # distributions
+    assert Dn.open_interval(0.0, 1.0).check(torch.tensor([0.0, 0.5, 1.0])).tolist() == [False, True, False]
+    assert Dn.closed_interval(0.0, 1.0).check(torch.tensor([0.0, 0.5, 1.0])).all() and bool(Dn.positive.check(torch.tensor(1.0)))
+    pn, qn = Dn.Normal(0.0, 1.0), Dn.Normal(1.0, 2.0)
+    torch.testing.assert_close(Dn.kl_divergence_dyn(pn, qn), Dn.kl_divergence(pn, qn))
+    torch.testing.assert_close(Dn.try_kl_expfamily(pn, qn), Dn.kl_divergence(pn, qn))
+    assert Dn.try_kl_expfamily(pn, Dn.Gamma(1.0, 1.0)) is None
+    assert Pf.estimate("matmul", [[4, 5], [5, 6]]) == 240 and Pf.estimate("my_custom_op", [[3, 4]]) is None
