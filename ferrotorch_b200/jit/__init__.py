@@ -15,7 +15,10 @@ from .backends import (BinOpKind, Codegen, CompiledGraph, CpuCodegen, Expr, Fuse
                        interpret_multi_with_captures, is_fusion_enabled, reduce_reference,
                        AotCompiledModule, AutotuneCandidate, AutotuneKey, AutotuneResult, FusionGroup, FusionGroupKind,
                        JitCompiledKernel, TraceResult, autotune, estimate_matmul_dims, export_with_dynamic_shapes,
-                       generate_reduction_ptx, generate_reduction_rust)
+                       generate_reduction_ptx, generate_reduction_rust, BackendTuneResult, InductorCompileOutcome, MatmulLoops,
+                       apply_binary_op_expr, apply_fused_gpu, apply_op_expr, find_fusion_groups, fuse_dag, ir_op_to_binary,
+                       ir_op_to_unary, is_binary_elementwise, is_elementwise, is_reduction, is_unary_elementwise, jit_supports,
+                       lower_matmul, lower_to_loops)
 
 
 def script(fn):

@@ -717,3 +717,193 @@ def generate_reduction_rust(kind: ReductionKind, pre: FusedChain | None = None, 
     body = CpuCodegen().expr(pre.loop_ir().body) if pre is not None and len(pre) else "x0"
     red = {"sum": "sum(-1)", "mean": "mean(-1)", "prod": "prod(-1)", "max": "amax(-1)", "min": "amin(-1)"}[kind.value]
     return "def %s(x0):\n    return (%s).%s\n" % (name, body, red)
+
+
+# --------------------------------------------------------------------------- op classification and lowering entry points
+# (ferrotorch-jit/src/codegen_ir.rs:300-400, 840; dag_fusion.rs:105, 392; codegen_jit.rs:325; fusion_gpu.rs:79)
+_REDUCTIONS = ("sum", "mean", "prod", "max", "min", "amax", "amin")
+
+
+def _op_name(op) -> str:
+    return str(getattr(op, "op", getattr(op, "value", op)))
+
+
+def is_unary_elementwise(op) -> bool:
+    from .ir import SCALAR, UNARY
+
+    return _op_name(op) in UNARY or _op_name(op) in SCALAR
+
+
+def is_binary_elementwise(op) -> bool:
+    from .ir import BINARY
+
+    return _op_name(op) in BINARY
+
+
+def is_elementwise(op) -> bool:
+    return is_unary_elementwise(op) or is_binary_elementwise(op)
+
+
+def is_reduction(op) -> bool:
+    return _op_name(op) in _REDUCTIONS
+
+
+def ir_op_to_unary(op):
+    """The :class:`UnaryOpKind` of an IR op name, or ``None``."""
+    try:
+        return UnaryOpKind(_op_name(op))
+    except ValueError:
+        return None
+
+
+def ir_op_to_binary(op):
+    try:
+        return BinOpKind(_op_name(op))
+    except ValueError:
+        return None
+
+
+def apply_op_expr(op, a: Expr, c: float | None = None) -> Expr:
+    """The expression of a unary IR op (or a scalar op with constant ``c``) applied to ``a``."""
+    name = _op_name(op)
+    return LoopIR.from_program([{"op": name, "src": [("x", 0)], "c": c}], 1).body if a.kind == "load" and a.index == 0 else \
+        _substitute(LoopIR.from_program([{"op": name, "src": [("x", 0)], "c": c}], 1).body, {0: a})
+
+
+def apply_binary_op_expr(op, a: Expr, b: Expr) -> Expr:
+    kind = ir_op_to_binary(op)
+    if kind is None:
+        raise JitError("apply_binary_op_expr: %r is not a binary elementwise op" % _op_name(op))
+    return Expr.binary(kind, a, b)
+
+
+def _substitute(e: Expr, env: dict) -> Expr:
+    if e.kind == "load":
+        return env.get(e.index, e)
+    if not e.args:
+        return e
+    return Expr(e.kind, e.op, tuple(_substitute(x, env) for x in e.args), e.index, e.value)
+
+
+@dataclass
+class MatmulLoops:
+    """The triple loop nest of ``out[m, n] = sum_k a[m, k] * b[k, n]`` as data, plus a runnable form."""
+    m: int
+    k: int
+    n: int
+    a_name: str = "a"
+    b_name: str = "b"
+    out_name: str = "out"
+
+    def source(self) -> str:
+        return ("for i in range(%d):\n    for j in range(%d):\n        acc = 0.0\n        for p in range(%d):\n"
+                "            acc += %s[i * %d + p] * %s[p * %d + j]\n        %s[i * %d + j] = acc\n"
+                % (self.m, self.n, self.k, self.a_name, self.k, self.b_name, self.n, self.out_name, self.n))
+
+    def flops(self) -> int:
+        return 2 * self.m * self.k * self.n
+
+    def run(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+        if tuple(a.shape) != (self.m, self.k) or tuple(b.shape) != (self.k, self.n):
+            raise JitError("lower_matmul: operands %s @ %s do not match the lowered %dx%dx%d"
+                           % (tuple(a.shape), tuple(b.shape), self.m, self.k, self.n))
+        return a @ b
+
+
+def lower_matmul(m: int, k: int, n: int, a_name: str = "a", b_name: str = "b", out_name: str = "out") -> MatmulLoops:
+    return MatmulLoops(int(m), int(k), int(n), a_name, b_name, out_name)
+
+
+def lower_to_loops(ops, n_inputs: int = 1) -> list:
+    """A chain of IR ops (names, or ``(name, constant)`` pairs, applied in order to input 0; a binary op takes
+    the running value and the next unused input) as loop IR: one fused :class:`LoopIR` for the elementwise
+    run, ended by a ``("reduce", kind)`` marker when the chain closes with a reduction."""
+    program, used = [], 1
+    tail = None
+    for k, o in enumerate(ops):
+        name, c = (o, None) if isinstance(o, str) else (o[0], o[1])
+        if is_reduction(name):
+            if k != len(list(ops)) - 1:
+                raise JitError("lower_to_loops: a reduction may only end the chain")
+            tail = ("reduce", name)
+            break
+        src = [("x", 0)] if not program else [("r", len(program) - 1)]
+        if is_binary_elementwise(name):
+            if used >= n_inputs:
+                raise JitError("lower_to_loops: %r needs another input (have %d)" % (name, n_inputs))
+            src.append(("x", used))
+            used += 1
+        elif not is_unary_elementwise(name):
+            raise JitError("lower_to_loops: %r is neither elementwise nor a reduction" % name)
+        program.append({"op": name, "src": src, "c": c})
+    loops = [LoopIR.from_program(program, n_inputs)] if program else []
+    return loops + ([tail] if tail else [])
+
+
+def jit_supports(loops) -> bool:
+    """Whether the code generators take every construct in ``loops`` (elementwise expression trees over the
+    documented unary / binary kinds; reductions by the kinds of :class:`ReductionKind`)."""
+    def ok(e: Expr) -> bool:
+        if e.kind in ("load", "const"):
+            return True
+        if e.kind == "unary":
+            return isinstance(e.op, UnaryOpKind) and all(ok(a) for a in e.args)
+        if e.kind == "binary":
+            return isinstance(e.op, BinOpKind) and all(ok(a) for a in e.args)
+        return False
+
+    for item in loops:
+        if isinstance(item, LoopIR):
+            if not ok(item.body):
+                return False
+        elif isinstance(item, tuple) and item and item[0] == "reduce":
+            if item[1] not in ("sum", "mean", "max", "min", "prod"):
+                return False
+        elif not isinstance(item, MatmulLoops):
+            return False
+    return True
+
+
+def find_fusion_groups(graph: IrGraph) -> list:
+    """The fused nodes of a graph, in topological order.  On a graph that has not been through the fusion
+    passes yet, a copy is optimised first (the original is left as it is)."""
+    groups = FusionGroup.of(graph)
+    if groups or not any(is_elementwise(graph.nodes[i].op) for i in graph.order):
+        return groups
+    import copy
+
+    from .ir import fuse_elementwise, pattern_fuse
+
+    g2 = copy.deepcopy(graph)
+    fuse_elementwise(g2)
+    pattern_fuse(g2)
+    return FusionGroup.of(g2)
+
+
+def fuse_dag(groups, graph: IrGraph) -> list:
+    """One list of loop IR per group: a fused loop for an elementwise group, a :class:`MatmulLoops` for a
+    fused linear layer, nothing for groups without a loop form (attention)."""
+    out = []
+    for grp in groups:
+        n = graph.nodes.get(grp.node_id)
+        if n is None:
+            out.append([])
+        elif n.op == "fused_elementwise":
+            out.append([LoopIR.from_program(n.attrs["program"], len(n.inputs))])
+        elif n.op == "fused_linear_act" and n.shape is not None and graph.nodes[n.inputs[0]].shape is not None:
+            k = graph.nodes[n.inputs[0]].shape[-1]
+            rows = 1
+            for d in n.shape[:-1]:
+                rows *= d
+            out.append([lower_matmul(rows, k, n.shape[-1])])
+        else:
+            out.append([])
+    return out
+
+
+def apply_fused_gpu(ops, x: torch.Tensor) -> torch.Tensor:
+    """A chain of unary / scalar ops on a CUDA tensor in one generated kernel; the caller makes sure the
+    tensor is on a CUDA device (``apply_fused`` checks and forwards here)."""
+    if not x.is_cuda:
+        raise JitError("apply_fused_gpu: the input is on %s, not on a CUDA device" % x.device)
+    return _module.apply_fused(ops, x)

@@ -29,7 +29,7 @@ from .fused import FusedAdamW, FusedSGD  # noqa: F401
 
 
 ExponentialMovingAverage = EMA          # noqa: F405  (ferrotorch-optim/src/ema.rs)
-from .extra import diff_sgd_momentum_step, diff_sgd_step  # noqa: F401,E402
+from .extra import diff_sgd_momentum_step, diff_sgd_step, elemwise_max, f64_scalar_on, scalar_on  # noqa: F401,E402
 from .configs import *  # noqa: F401,F403,E402
 from .configs import (ParamGroup, ParamKey, OptimizerState, Sgd, Asgd, Lbfgs, Rmsprop, LrScheduler, SequentialLr,  # noqa: F401,E402
                       MetricScheduler, Swalr, LinearWarmup)

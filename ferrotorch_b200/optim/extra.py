@@ -449,3 +449,18 @@ class AveragedModel(torch.optim.swa_utils.AveragedModel):
 
     def apply_to_module(self, module) -> None:
         self.apply_to(module.parameters())
+
+
+# --------------------------------------------------------------------------- helpers of the multi-tensor ("foreach") steps (foreach_utils.rs)
+def elemwise_max(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``max(a, b)`` element by element."""
+    return torch.maximum(a, b)
+
+
+def scalar_on(value, device, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """A 0-d tensor holding a hyper-parameter on ``device``, so that a step never reads it from the host."""
+    return torch.tensor(value, dtype=dtype, device=device)
+
+
+def f64_scalar_on(value: float, device, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    return scalar_on(float(value), device, dtype)

@@ -163,6 +163,68 @@ nccl_all_gather = _device_collective("all_gather")
 nccl_reduce_scatter = _device_collective("reduce_scatter")
 
 
+# the ``_dtype`` spellings take the element type explicitly in the reference (its handle-based wrappers infer
+# f32 / f64 from the element size); device tensors carry their dtype, bf16 included, so they are the same calls
+nccl_allreduce_dtype, nccl_broadcast_dtype = nccl_allreduce, nccl_broadcast
+nccl_all_gather_dtype, nccl_reduce_scatter_dtype = nccl_all_gather, nccl_reduce_scatter
+
+
+def is_available() -> bool:
+    """Whether NCCL can be used here: torch was built with it and a CUDA device is present (nccl_sys.rs:513)."""
+    import torch.distributed as dist
+
+    return bool(dist.is_available() and dist.is_nccl_available() and torch.cuda.is_available())
+
+
+def reduce_op_to_nccl(op):
+    """This package's :class:`ReduceOp` (or its string) as the ``torch.distributed`` reduction that NCCL runs
+    (``Mean`` is NCCL's ``Avg``)."""
+    import torch.distributed as dist
+
+    return {"sum": dist.ReduceOp.SUM, "mean": dist.ReduceOp.AVG, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN,
+            "prod": dist.ReduceOp.PRODUCT}[_op(op)]
+
+
+def get_unique_id() -> NcclUniqueId:
+    """A fresh communicator id for rank 0 to hand to the others (nccl_sys.rs:282).  ``torch.distributed`` creates
+    and distributes NCCL's own id through its store during ``init_process_group``; this value only names a
+    rendezvous (it is what :func:`comm_init_rank` keys the store on)."""
+    import os
+
+    return NcclUniqueId(os.urandom(128))
+
+
+def comm_init_rank(world_size: int, unique_id: bytes, rank: int, master_addr: str = "127.0.0.1", master_port: int = 29500,
+                   backend: str | None = None) -> TorchGroup:
+    """Join the communicator named by ``unique_id`` as ``rank`` of ``world_size`` (nccl_sys.rs:306): initialises
+    ``torch.distributed`` (NCCL on a CUDA machine, gloo otherwise) on a TCP store whose keys are prefixed with the
+    id, and returns the world group.  The device must be selected first (``torch.cuda.set_device``)."""
+    import torch.distributed as dist
+
+    if not 0 <= rank < world_size:
+        raise _b.InvalidRank("rank %d outside a world of %d" % (rank, world_size))
+    if not dist.is_initialized():
+        store = dist.PrefixStore(bytes(unique_id)[:16].hex(), dist.TCPStore(master_addr, master_port, world_size, rank == 0))
+        dist.init_process_group(backend or ("nccl" if is_available() else "gloo"), store=store, rank=rank, world_size=world_size)
+    return TorchGroup(None)
+
+
+class _NcclGroupCalls:
+    """``group_start()`` ... ``group_end()``: point-to-point calls issued in between are launched together
+    (``torch.distributed``'s batched isend / irecv); collectives are unaffected."""
+    depth = 0
+
+
+def group_start() -> None:
+    _NcclGroupCalls.depth += 1
+
+
+def group_end() -> None:
+    if _NcclGroupCalls.depth == 0:
+        raise DistributedError("group_end without group_start")
+    _NcclGroupCalls.depth -= 1
+
+
 # --------------------------------------------------------------------------- distributed checkpoint types
 @dataclass
 class TensorShardSpec:

@@ -17,4 +17,4 @@ from .state import (AsyncCheckpointer, CheckpointFuture, dumps_state_dict, load_
 
 
 from .onnx import (OnnxExportConfig, OnnxExportError, export_from_program, export_ir_graph_to_onnx, export_onnx,  # noqa: F401,E402
-                   ir_graph_to_onnx, load_onnx, run_onnx)
+                   ir_graph_to_onnx, load_onnx, run_onnx, encode_dim_param, encode_shape_with_dynamic, encode_value_info_dynamic)

@@ -158,6 +158,28 @@ def encode_value_info(name: str, dtype: torch.dtype, shape, dynamic: dict | None
     return ProtobufWriter().string(1, name).message(2, ProtobufWriter().message(1, tensor_type))
 
 
+def encode_dim_param(param: str) -> ProtobufWriter:
+    """A ``TensorShapeProto.Dimension`` that is symbolic: ``dim_param = param`` (onnx_export.rs:337)."""
+    return ProtobufWriter().string(2, param)
+
+
+def encode_shape_with_dynamic(dims) -> ProtobufWriter:
+    """A ``TensorShapeProto`` from a list whose entries are integers (static extents) or strings (names of
+    dynamic dimensions)."""
+    shp = ProtobufWriter()
+    for d in dims:
+        shp.message(1, encode_dim_param(d) if isinstance(d, str) else ProtobufWriter().int(1, int(d)))
+    return shp
+
+
+def encode_value_info_dynamic(name: str, elem_type, dims) -> ProtobufWriter:
+    """A ``ValueInfoProto`` whose shape mixes static and named dynamic dimensions; ``elem_type`` is an ONNX element
+    type number or a torch dtype."""
+    et = _DTYPE[elem_type] if isinstance(elem_type, torch.dtype) else int(elem_type)
+    tensor_type = ProtobufWriter().int(1, et).message(2, encode_shape_with_dynamic(dims))
+    return ProtobufWriter().string(1, name).message(2, ProtobufWriter().message(1, tensor_type))
+
+
 def encode_attribute(name: str, value) -> ProtobufWriter:
     a = ProtobufWriter().string(1, name)
     if isinstance(value, bool) or isinstance(value, int):

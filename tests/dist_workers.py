@@ -466,3 +466,19 @@ def argparse_like(**kw):
     import types
 
     return types.SimpleNamespace(**kw)
+
+
+def comm_init_rank_worker(rank: int, world: int, port: int, uid: bytes, q) -> None:
+    """Join a communicator by id (the reference's ``comm_init_rank``) and all-reduce over it."""
+    import torch
+
+    from ferrotorch_b200 import parallel as P
+
+    g = P.comm_init_rank(world, uid, rank, "127.0.0.1", port)
+    t = torch.tensor([float(rank + 1)])
+    total = P.allreduce(t, g, P.ReduceOp.Sum)          # returns a new tensor
+    q.put((rank, g.world_size, float(total)))
+    import torch.distributed as dist
+
+    dist.barrier()
+    dist.destroy_process_group()

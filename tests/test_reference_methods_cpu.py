@@ -1003,3 +1003,70 @@ def test_free_functions_of_the_core_nn_and_distributions_crates():
     torch.testing.assert_close(Dn.try_kl_expfamily(pn, qn), Dn.kl_divergence(pn, qn))
     assert Dn.try_kl_expfamily(pn, Dn.Gamma(1.0, 1.0)) is None
     assert Pf.estimate("matmul", [[4, 5], [5, 6]]) == 240 and Pf.estimate("my_custom_op", [[3, 4]]) is None
+
+
+def test_jit_lowering_functions_onnx_dynamic_dims_and_nccl_named_helpers():
+    # ferrotorch-jit/src/{codegen_ir,dag_fusion,codegen_jit}.rs; ferrotorch-serialize/src/onnx_export.rs:336-370;
+    # ferrotorch-optim/src/foreach_utils.rs; ferrotorch-distributed/src/{nccl_sys,nccl_backend,nccl_collective}.rs
+    import multiprocessing as mp
+    import socket
+
+    from ferrotorch_b200 import jit as J
+    from ferrotorch_b200 import parallel as Pl
+    from ferrotorch_b200 import serialize as S
+    from ferrotorch_b200.serialize import onnx as X
+
+    assert J.is_elementwise("relu") and J.is_binary_elementwise("add") and J.is_reduction("sum") and not J.is_elementwise("matmul")
+    assert J.ir_op_to_unary("exp") is J.UnaryOpKind.Exp and J.ir_op_to_binary("relu") is None
+    a, b = torch.randn(4), torch.randn(4)
+    loops = J.lower_to_loops([("mul_c", 2.0), "relu", "add", "sum"], 2)
+    assert loops[-1] == ("reduce", "sum") and J.jit_supports(loops)
+    torch.testing.assert_close(J.CpuCodegen().compile(loops[0], "t")(a, b), torch.relu(a * 2) + b)
+    with pytest.raises(J.JitError):
+        J.lower_to_loops(["add"], 1)
+    with pytest.raises(J.JitError):
+        J.lower_to_loops(["sum", "relu"], 1)
+    mm = J.lower_matmul(2, 3, 4)
+    assert mm.flops() == 48 and mm.run(torch.ones(2, 3), torch.ones(3, 4)).shape == (2, 4) and "acc +=" in mm.source()
+    assert J.jit_supports([mm]) and not J.jit_supports([mm, "something else"])
+    e = J.apply_binary_op_expr("mul", J.apply_op_expr("exp", J.Expr.var(1)), J.Expr.var(0))
+    torch.testing.assert_close(J.CpuCodegen().compile(J.LoopIR(2, e), "u")(a, b), torch.exp(b) * a)
+
+    def f(x, y):
+        return torch.relu(x * 2 + y).exp()
+
+    compiled = J.compile(f, (a, b))
+    groups = J.find_fusion_groups(compiled.graph)
+    assert len(groups) == 1 and isinstance(J.fuse_dag(groups, compiled.graph)[0][0], J.LoopIR)
+    raw = J.trace(f, (a, b))
+    assert len(J.find_fusion_groups(raw)) == 1 and raw.count("fused_elementwise") == 0          # the caller's graph is untouched
+    with pytest.raises(J.JitError):
+        J.apply_fused_gpu(["relu"], a)
+    w1 = X.encode_value_info("x", torch.float32, (1, 3), {0: "batch"}).finish()
+    assert w1 == S.encode_value_info_dynamic("x", torch.float32, ["batch", 3]).finish() == S.encode_value_info_dynamic("x", 1, ["batch", 3]).finish()
+    assert S.encode_dim_param("n").finish() == b"\x12\x01n" and len(S.encode_shape_with_dynamic([2, "n"]).finish()) == 9
+    assert O.elemwise_max(torch.tensor([1.0, 5.0]), torch.tensor([3.0, 2.0])).tolist() == [3.0, 5.0]
+    assert O.f64_scalar_on(0.1, "cpu").dim() == 0 and O.scalar_on(2, "cpu", torch.int64).dtype == torch.int64
+    import torch.distributed as dist
+
+    assert Pl.reduce_op_to_nccl(Pl.ReduceOp.Mean) == dist.ReduceOp.AVG and Pl.reduce_op_to_nccl("sum") == dist.ReduceOp.SUM
+    assert Pl.is_available() == (torch.cuda.is_available() and dist.is_nccl_available()) and len(Pl.get_unique_id()) == 128
+    Pl.group_start()
+    Pl.group_end()
+    with pytest.raises(Pl.DistributedError):
+        Pl.group_end()
+    # two processes join a communicator by id and reduce over it
+    from dist_workers import comm_init_rank_worker
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    uid = bytes(Pl.get_unique_id())
+    procs = [ctx.Process(target=comm_init_rank_worker, args=(r, 2, port, uid, q)) for r in range(2)]
+    [p.start() for p in procs]
+    got = sorted(q.get(timeout=120) for _ in procs)
+    [p.join(60) for p in procs]
+    assert got == [(0, 2, 3.0), (1, 2, 3.0)] and all(p.exitcode == 0 for p in procs)
