@@ -5,6 +5,7 @@ from .backend import (BackendUnavailable, DistributedError, Group, HybridGroup, 
                       UnsupportedOp, init_group, run_simulated)
 from .elastic import FileStore, Heartbeat, RankFailure, TorchStore, survivors  # noqa: F401
 from .fsdp import FSDP, ShardingStrategy, SyncBatchNorm2d  # noqa: F401
+from .fsdp_flat import FsdpUnit, auto_wrap  # noqa: F401
 from .host_ddp import DDP  # noqa: F401
 from .mesh import DeviceMesh, DTensor, MeshTensor, Partial, Replicate, Shard  # noqa: F401
 from .pipeline import Pipeline  # noqa: F401

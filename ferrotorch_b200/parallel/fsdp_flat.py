@@ -1,0 +1,220 @@
+"""Fully sharded data parallelism with one flat buffer per wrapped unit.
+
+The reference's FSDP all-gathers and reduce-scatters parameter by parameter
+(ferrotorch-distributed/src/fsdp.rs:411-564 forward, :649-811 ``sync_gradients``), one collective per tensor;
+:class:`~ferrotorch_b200.parallel.fsdp.FSDP` keeps that shape.  Collective cost on an NVSwitch machine is
+dominated by launch latency, not by bytes, so this module shards by *unit* instead: every wrapped sub-module
+(a decoder layer, say) owns
+
+* one flat parameter buffer, padded to a multiple of the group size, of which this rank keeps ``1 / W``
+  (the ``nn.Parameter`` the optimizer sees);
+* one flat gradient buffer of the same size; the unit's parameters and their ``.grad`` are views into the
+  two buffers, so autograd writes gradients straight into the buffer that is reduce-scattered.
+
+A step therefore costs two all-gathers (before forward, before backward) and one reduce-scatter per unit.
+Between its forward and its backward a unit gives its full buffer back (the storage is resized to zero and
+re-filled by the second all-gather; saved tensors stay valid because they alias the same storage object).
+``auto_wrap`` wraps every sub-module of the given classes and lets each unit start the all-gather of the
+next one on a worker thread while it computes (forward prefetch).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .backend import Group, _Lane
+
+
+class _PreBackward(torch.autograd.Function):
+    """Identity on the unit's outputs whose backward runs first: the place to bring the parameters back."""
+
+    @staticmethod
+    def forward(ctx, unit, *outs):
+        ctx.unit = unit
+        return outs if len(outs) > 1 else outs[0]
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.unit.unshard()
+        return (None, *grads)
+
+
+class FsdpUnit(nn.Module):
+    def __init__(self, module: nn.Module, group: Group, reshard_after_forward: bool = True):
+        super().__init__()
+        self.module, self.group, self.reshard_after_forward = module, group, reshard_after_forward
+        W, r = group.world_size, group.rank
+        self._params = [p for p in module.parameters() if p.requires_grad and not getattr(p, "_fsdp_owned", False)]
+        for p in self._params:
+            p._fsdp_owned = True                      # an outer unit must not take it again
+        if not self._params:
+            raise ValueError("FsdpUnit: the module has no trainable parameter of its own (everything below it is wrapped already)")
+        dtype, device = self._params[0].dtype, self._params[0].device
+        if any(p.dtype != dtype or p.device != device for p in self._params):
+            raise ValueError("FsdpUnit: parameters of one unit must share dtype and device")
+        self._shapes = [p.shape for p in self._params]
+        self._offsets, n = [], 0
+        for p in self._params:
+            self._offsets.append(n)
+            n += p.numel()
+        self.numel = n
+        self.padded = (n + W - 1) // W * W
+        self.full = torch.zeros(self.padded, dtype=dtype, device=device)
+        for p, off in zip(self._params, self._offsets):
+            self.full[off:off + p.numel()].copy_(p.detach().reshape(-1))
+        self.flat_grad: torch.Tensor | None = None
+        chunk = self.padded // W
+        self.shard = nn.Parameter(self.full[r * chunk:(r + 1) * chunk].clone())
+        self.shard._fsdp_owned = True                 # an enclosing unit flattens its own parameters only
+        self._nbytes = self.full.untyped_storage().nbytes()
+        self._sharded = False
+        self._point_views()
+        self._prefetched = None
+        object.__setattr__(self, "next_unit", None)       # a plain reference: the next unit is not a sub-module of this one
+        self._lane: _Lane | None = None
+        self.stats = {"all_gathers": 0, "reduce_scatters": 0}
+        self.reshard()
+
+    # ------------------------------------------------------------------ views
+    def _point_views(self) -> None:
+        for p, off, shape in zip(self._params, self._offsets, self._shapes):
+            p.data = self.full[off:off + shape.numel()].view(shape)
+
+    def parameters(self, recurse: bool = True):          # the optimizer trains the shard
+        yield self.shard
+        if recurse:
+            for m in self.module.modules():
+                if isinstance(m, FsdpUnit):
+                    yield m.shard
+
+    def sharded_parameters(self) -> list:
+        return list(self.parameters())
+
+    # ------------------------------------------------------------------ shard <-> full
+    def _gather(self) -> torch.Tensor:
+        self.stats["all_gathers"] += 1
+        return self.group.all_gather(self.shard.detach()).reshape(-1)
+
+    def unshard(self) -> None:
+        """Bring the full parameters back (no-op when they are there)."""
+        if not self._sharded:
+            return
+        if self._prefetched is not None:
+            op, box = self._prefetched
+            op.wait()
+            gathered = box[0]
+        else:
+            gathered = self._gather()
+        self._prefetched = None
+        self.full.untyped_storage().resize_(self._nbytes)
+        self.full.copy_(gathered)
+        self._sharded = False
+
+    def reshard(self) -> None:
+        """Give the full buffer back; the shard is the only copy this rank keeps."""
+        if self._sharded:
+            return
+        self.full.untyped_storage().resize_(0)
+        self._sharded = True
+
+    def prefetch(self) -> None:
+        """Start this unit's all-gather on the worker thread (one collective in flight per group at a time:
+        the lane is shared by the units of a chain)."""
+        if self._sharded and self._prefetched is None and self._lane is not None:
+            box: list = []
+            self._prefetched = (self._lane.post(lambda: box.append(self._gather())), box)
+
+    # ------------------------------------------------------------------ step
+    def forward(self, *a, **kw):
+        self.unshard()
+        if self.next_unit is not None:
+            self.next_unit.prefetch()
+        if torch.is_grad_enabled():
+            if self.flat_grad is None:
+                self.flat_grad = torch.zeros(self.padded, dtype=self.full.dtype, device=self.full.device)
+            for p, off, shape in zip(self._params, self._offsets, self._shapes):
+                if p.grad is None:
+                    p.grad = self.flat_grad[off:off + shape.numel()].view(shape)
+        out = self.module(*a, **kw)
+        if not self.reshard_after_forward:
+            return out
+        if not torch.is_grad_enabled():
+            self.reshard()
+            return out
+        outs = out if isinstance(out, tuple) else (out,)
+        if all(torch.is_tensor(o) for o in outs):         # other output structures keep the parameters until sync_gradients
+            out = _PreBackward.apply(self, *outs)
+            self.reshard()
+        return out
+
+    def sync_gradients(self) -> None:
+        """After backward: one reduce-scatter (mean) of the unit's flat gradient into ``shard.grad``; the full
+        parameters and the flat gradient are released.  Recurses into nested units."""
+        for m in self.module.modules():
+            if isinstance(m, FsdpUnit):
+                m.sync_gradients()
+        if self.flat_grad is not None:
+            W = self.group.world_size
+            self.stats["reduce_scatters"] += 1
+            part = self.group.reduce_scatter(self.flat_grad.view(W, self.padded // W), "mean").reshape(-1)
+            self.shard.grad = part if self.shard.grad is None else self.shard.grad + part
+            self.flat_grad = None
+            for p in self._params:
+                p.grad = None
+        self.reshard()
+
+    def full_state_dict(self) -> dict:
+        """The wrapped module's state dict with full tensors (gathers every unit, then releases them again)."""
+        units = [self] + [m for m in self.module.modules() if isinstance(m, FsdpUnit)]
+        for u in units:
+            u.unshard()
+        sd = {k.replace("module.", ""): v.detach().clone() for k, v in self.module.state_dict().items() if not k.endswith("shard")}
+        for u in units:
+            u.reshard()
+        return sd
+
+
+class _Container(nn.Module):
+    """What ``auto_wrap`` returns when every parameter lives in an inner unit: the model plus the unit list."""
+
+    def __init__(self, module: nn.Module, units: list):
+        super().__init__()
+        self.module = module
+        object.__setattr__(self, "units", units)
+
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def sharded_parameters(self) -> list:
+        return [u.shard for u in self.units]
+
+    def sync_gradients(self) -> None:
+        for u in self.units:
+            u.sync_gradients()
+
+
+def auto_wrap(model: nn.Module, group: Group, wrap_classes: tuple, reshard_after_forward: bool = True, prefetch: bool = True) -> FsdpUnit:
+    """Wrap every sub-module that is an instance of ``wrap_classes`` in its own :class:`FsdpUnit` (innermost
+    first) and the rest of the model in a root unit.  With ``prefetch`` the units are chained in the order of
+    their definition, so each starts the next one's all-gather while it computes."""
+    units: list[FsdpUnit] = []
+
+    def visit(mod: nn.Module) -> None:
+        for name, child in list(mod.named_children()):
+            visit(child)
+            if isinstance(child, wrap_classes) and not isinstance(child, FsdpUnit):
+                u = FsdpUnit(child, group, reshard_after_forward)
+                setattr(mod, name, u)
+                units.append(u)
+
+    visit(model)
+    leftover = any(p.requires_grad and not getattr(p, "_fsdp_owned", False) for p in model.parameters())
+    root = FsdpUnit(model, group, reshard_after_forward) if leftover else _Container(model, units)
+    if prefetch and units:
+        lane = _Lane()
+        for a, b in zip(units, units[1:]):
+            object.__setattr__(a, "next_unit", b)
+        for u in units:
+            u._lane = lane
+    object.__setattr__(root, "units", units)
+    return root

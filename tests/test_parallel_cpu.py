@@ -483,3 +483,82 @@ def test_vocabulary_parallel_sampling_equals_single_device_sampling(world):
                                                              VS.shared_uniform(4000, 3, 0)))[0]
     freq = torch.bincount(g1, minlength=4).float() / 4000
     assert torch.allclose(freq, small[0].softmax(-1), atol=0.03)
+
+
+# --------------------------------------------------------------------------- FSDP with one flat buffer per unit
+def test_flat_fsdp_units_train_like_one_process_and_release_their_buffers():
+    import threading
+
+    from torch import nn
+
+    from ferrotorch_b200.parallel.backend import SimulatedGroup
+    from ferrotorch_b200.parallel.fsdp_flat import FsdpUnit, auto_wrap
+
+    class Block(nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            self.a, self.b = nn.Linear(d, 2 * d), nn.Linear(2 * d, d)
+
+        def forward(self, x):
+            return x + self.b(torch.tanh(self.a(x)))
+
+    def make():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Linear(6, 8), Block(8), Block(8), Block(8), nn.Linear(8, 3))
+
+    W, steps = 4, 4
+    torch.manual_seed(1)
+    X, Y = torch.randn(16, 6), torch.randn(16, 3)
+    ref = make()
+    opt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    ref_losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = nn.functional.mse_loss(ref(X), Y)
+        loss.backward()
+        opt.step()
+        ref_losses.append(float(loss.detach()))
+    groups = SimulatedGroup.create_group(W)
+    out = {}
+    protos = [make() for _ in range(W)]           # built here: the global generator is not thread-safe
+
+    def rank(r):
+        model = auto_wrap(protos[r], groups[r], (Block,), reshard_after_forward=True, prefetch=True)
+        ps = model.sharded_parameters()
+        o = torch.optim.SGD(ps, lr=0.1, momentum=0.9)
+        xs, ys = X.chunk(W)[r], Y.chunk(W)[r]
+        losses, freed = [], None
+        for _ in range(steps):
+            o.zero_grad()
+            loss = nn.functional.mse_loss(model(xs), ys)
+            freed = [u.full.untyped_storage().size() for u in model.units]        # between forward and backward
+            loss.backward()
+            model.sync_gradients()
+            o.step()
+            losses.append(float(loss.detach()))
+        stats = [dict(u.stats) for u in model.units]
+        out[r] = (losses, model.full_state_dict(), freed, stats, sum(p.numel() for p in ps))
+
+    ts = [threading.Thread(target=rank, args=(r,)) for r in range(W)]
+    [t.start() for t in ts]
+    [t.join(120) for t in ts]
+    assert len(out) == W
+    sd_ref = ref.state_dict()
+    for r in range(W):
+        losses, sd, freed, stats, held = out[r]
+        assert set(sd) == set(sd_ref)
+        for k in sd_ref:
+            torch.testing.assert_close(sd[k], sd_ref[k], rtol=1e-5, atol=1e-6)
+        assert freed == [0, 0, 0]                                               # every unit gave its full buffer back
+        # per step and unit: one all-gather before forward, one before backward, one reduce-scatter
+        assert all(s == {"all_gathers": 2 * steps, "reduce_scatters": steps} for s in stats)
+        assert held <= (sum(p.numel() for p in ref.parameters()) + 3 * W * 5) // W + 1               # about 1 / W of the model
+    mean_losses = [sum(out[r][0][i] for r in range(W)) / W for i in range(steps)]
+    torch.testing.assert_close(torch.tensor(mean_losses), torch.tensor(ref_losses), rtol=1e-5, atol=1e-6)
+    one = SimulatedGroup.create_group(1)[0]
+    with pytest.raises(ValueError):
+        FsdpUnit(nn.ReLU(), one)
+    net = nn.Linear(3, 3)
+    u = FsdpUnit(net, one, reshard_after_forward=False)
+    with torch.no_grad():
+        assert u(torch.ones(1, 3)).shape == (1, 3) and u.full.untyped_storage().size() > 0     # kept when asked to
