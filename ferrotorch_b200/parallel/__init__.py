@@ -10,7 +10,7 @@ from .host_ddp import DDP  # noqa: F401
 from .mesh import DeviceMesh, DTensor, MeshTensor, Partial, Replicate, Shard  # noqa: F401
 from .pipeline import Pipeline  # noqa: F401
 from .vocab_sampling import sample_reference, sample_vocab_parallel, shared_uniform  # noqa: F401
-from .dist_checkpoint import (AsyncDistributedCheckpointer, PendingCollective, RpcAgent, all_gather_async,  # noqa: F401,E402
+from .dist_checkpoint import (AsyncDistributedCheckpointer, GroupRpcAgent, PendingCollective, RpcAgent, all_gather_async,  # noqa: F401,E402
                               all_reduce_async, load_distributed, save_distributed)
 from .p2p import (PipelineSchedule, Placement, async_reduce_scatter, gpu_allreduce, gpu_broadcast,  # noqa: F401,E402
                   is_gloo_available, is_mpi_available, is_nccl_available, is_ucc_available, recv, recv_into,

@@ -556,3 +556,126 @@ class TcpRpcBackend:
         buf = torch.empty(nbytes, dtype=torch.uint8)
         self.group.recv(buf, src_rank, timeout) if timeout is not None else self.group.recv(buf, src_rank)
         return bytes(buf.numpy())
+
+
+class GroupRpcAgent:
+    """Remote calls between the ranks of a :class:`~.backend.Group` (the reference's agent sits on its rank-addressed
+    back-end the same way, ferrotorch-distributed/src/rpc.rs:372-610).  Every message is one frame
+    ``kind (1 byte: 0 request, 1 response) + length + body`` sent with the group's point-to-point transport.
+
+    Calls are correlated by request id: several threads of one rank may call the same peer at once, the
+    responses may come back in any order (``serve(..., concurrent=True)`` answers every request on its own thread),
+    and a response that arrives while another call is receiving is kept for its owner.  A request that arrives
+    while this rank waits for a response is served on the spot, so two ranks may call each other at the same time."""
+
+    def __init__(self, group: Group, name: str | None = None):
+        self.group, self.name = group, name or "rank%d" % group.rank
+        self.transport = TcpRpcBackend(group)
+        self.handlers: dict = {}
+        self._counter = 0
+        self._id_lock = threading.Lock()
+        self._buffered: dict = {}
+        self._buf_lock = threading.Lock()
+        self._send_locks = {r: threading.Lock() for r in range(group.world_size)}
+        self._recv_locks = {r: threading.Lock() for r in range(group.world_size)}
+
+    def rank(self) -> int:
+        return self.group.rank
+
+    def world_size(self) -> int:
+        return self.group.world_size
+
+    def register(self, fn_name: str, fn) -> None:
+        self.handlers[fn_name] = fn
+
+    # ---- frames
+    def _send(self, dst: int, kind: int, body: bytes) -> None:
+        if len(body) > MAX_RPC_MSG_SIZE:
+            raise SizeMismatch("RPC message of %d bytes exceeds the 1 GiB cap" % len(body))
+        with self._send_locks[dst]:
+            self.transport.send(bytes([kind]) + struct.pack("<Q", len(body)), dst)
+            self.transport.send(body, dst)
+
+    def _recv(self, src: int, timeout: float | None):
+        head = self.transport.recv(9, src, timeout)
+        (n,) = struct.unpack("<Q", head[1:])
+        if n > MAX_RPC_MSG_SIZE:
+            raise SizeMismatch("RPC frame of %d bytes exceeds the 1 GiB cap" % n)
+        return head[0], self.transport.recv(n, src, timeout)
+
+    def _answer(self, src: int, request: bytes) -> None:
+        helper = RpcAgent.__new__(RpcAgent)
+        helper.handlers, helper.name = self.handlers, self.name
+        self._send(src, 1, RpcAgent.handle_request(helper, src, request))
+
+    # ---- client side
+    def rpc_sync(self, dst_rank: int, fn_name: str, *args, timeout: float | None = 60.0, **kwargs):
+        if not 0 <= dst_rank < self.group.world_size or dst_rank == self.group.rank:
+            raise InvalidRank("rpc_sync: cannot call rank %d from rank %d of %d" % (dst_rank, self.group.rank, self.group.world_size))
+        with self._id_lock:
+            self._counter += 1
+            req_id = (self.group.rank << 40) | self._counter
+        self._send(dst_rank, 0, encode_rpc_request(req_id, fn_name, *args, **kwargs))
+        ok, val = self._await(dst_rank, req_id, timeout)
+        if not ok:
+            raise RuntimeError("remote call %s on rank %d failed: %s" % (fn_name, dst_rank, val))
+        return val
+
+    def rpc_async(self, dst_rank: int, fn_name: str, *args, **kwargs) -> PendingCollective:
+        return PendingCollective(lambda: self.rpc_sync(dst_rank, fn_name, *args, **kwargs), op_name="rpc:" + fn_name)
+
+    def _take_buffered(self, req_id: int):
+        with self._buf_lock:
+            return self._buffered.pop(req_id, None)
+
+    def _await(self, src: int, req_id: int, timeout: float | None):
+        import time
+
+        deadline = None if timeout is None else time.time() + timeout
+        while True:
+            got = self._take_buffered(req_id)
+            if got is not None:
+                return got
+            if not self._recv_locks[src].acquire(timeout=0.01):
+                if deadline is not None and time.time() > deadline:
+                    raise TimeoutError("rpc: no response from rank %d within %.1f s" % (src, timeout))
+                continue                               # another call of this rank is receiving; it will file our response
+            try:
+                got = self._take_buffered(req_id)
+                if got is not None:
+                    return got
+                kind, body = self._recv(src, None if deadline is None else max(0.01, deadline - time.time()))
+            finally:
+                self._recv_locks[src].release()
+            if kind == 0:
+                self._answer(src, body)                # the peer is calling us while we wait for it
+                continue
+            rid, ok, val = decode_rpc_response(body)
+            if rid == req_id:
+                return ok, val
+            with self._buf_lock:
+                self._buffered[rid] = (ok, val)
+
+    # ---- server side
+    def serve(self, src_rank: int, count: int = 1, concurrent: bool = False, timeout: float | None = 60.0) -> None:
+        """Answer ``count`` requests from ``src_rank``; ``concurrent`` runs every handler on its own thread, so a
+        slow call does not hold back the ones behind it."""
+        threads = []
+        served = 0
+        while served < count:
+            with self._recv_locks[src_rank]:
+                kind, body = self._recv(src_rank, timeout)
+            if kind == 1:                              # a response for one of this rank's own calls
+                rid, ok, val = decode_rpc_response(body)
+                with self._buf_lock:
+                    self._buffered[rid] = (ok, val)
+                continue
+            served += 1
+            if concurrent:
+                t = threading.Thread(target=self._answer, args=(src_rank, body), daemon=True)
+                t.start()
+                threads.append(t)
+            else:
+                self._answer(src_rank, body)
+        for t in threads:
+            t.join()

@@ -562,3 +562,62 @@ def test_flat_fsdp_units_train_like_one_process_and_release_their_buffers():
     u = FsdpUnit(net, one, reshard_after_forward=False)
     with torch.no_grad():
         assert u(torch.ones(1, 3)).shape == (1, 3) and u.full.untyped_storage().size() > 0     # kept when asked to
+
+
+# --------------------------------------------------------------------------- rank-addressed RPC over a group
+def test_group_rpc_agent_buffers_out_of_order_responses_and_serves_while_waiting():
+    import threading
+    import time
+
+    from ferrotorch_b200.parallel.backend import InvalidRank, SimulatedGroup
+    from ferrotorch_b200.parallel.dist_checkpoint import GroupRpcAgent
+
+    w = SimulatedGroup.create_group(2)
+    res, errs = {}, []
+
+    def r0():
+        try:
+            a = GroupRpcAgent(w[0])
+            a.register("who", lambda: "rank0")
+            slow = a.rpc_async(1, "work", 0.3, "slow")
+            time.sleep(0.05)
+            fast = a.rpc_async(1, "work", 0.0, "fast")
+            res["fast"], res["t_fast"] = fast.wait(10), time.time()
+            res["slow"], res["t_slow"] = slow.wait(10), time.time()
+            res["tensor"] = a.rpc_sync(1, "double", torch.arange(3.0), scale=3)
+            try:
+                a.rpc_sync(1, "boom")
+            except RuntimeError as e:
+                res["err"] = str(e)
+            res["mutual0"] = a.rpc_sync(1, "who")                 # rank 1 calls "who" here at the same time
+            with pytest.raises(InvalidRank):
+                a.rpc_sync(0, "who")
+            assert (a.rank(), a.world_size()) == (0, 2)
+        except BaseException as e:  # noqa: BLE001
+            errs.append(e)
+
+    def r1():
+        try:
+            a = GroupRpcAgent(w[1])
+
+            def work(delay, tag):
+                time.sleep(delay)
+                return tag
+
+            a.register("work", work)
+            a.register("double", lambda t, scale=2: t * scale)
+            a.register("boom", lambda: 1 / 0)
+            a.register("who", lambda: "rank1")
+            a.serve(0, 2, concurrent=True)                         # the two overlapping calls
+            a.serve(0, 2)                                          # double, boom
+            res["mutual1"] = a.rpc_sync(0, "who")                  # serves rank 0's request while waiting for its own answer
+        except BaseException as e:  # noqa: BLE001
+            errs.append(e)
+
+    ts = [threading.Thread(target=f) for f in (r0, r1)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert not errs, errs
+    assert res["fast"] == "fast" and res["slow"] == "slow" and res["t_fast"] < res["t_slow"]       # answered out of order
+    assert res["tensor"].tolist() == [0.0, 3.0, 6.0] and "ZeroDivisionError" in res["err"]
+    assert res["mutual0"] == "rank1" and res["mutual1"] == "rank0"
