@@ -58,6 +58,12 @@ class MemoryGuard:
         self._stop = threading.Event()
         self.paused = threading.Event()
         self.stats = {"checks": 0, "hook_runs": 0, "freed_by_hooks": 0, "failures": 0, "pauses": 0}
+        self._level_listeners: list = []
+        self._last_level = None
+        self._hook_ids: dict = {}
+        self._next_hook = 0
+        self._peak = 0
+        self._oom_callbacks: list = []
 
     # ---- configuration
     def add_pre_oom_hook(self, fn: Callable[[int], int], priority: int = 0, name: str = "") -> None:
@@ -104,6 +110,8 @@ class MemoryGuard:
         self._fail(nbytes)
 
     def _fail(self, nbytes: int):
+        for fn in self._oom_callbacks:
+            fn()
         self.stats["failures"] += 1
         if self._emergency is not None:
             self._emergency()
@@ -140,6 +148,114 @@ class MemoryGuard:
             time.sleep(0.005)
         return not self.paused.is_set()
 
+    # ---- the reference's method names (memory_guard.rs:254-770)
+    def pressure_level(self) -> PressureLevel:
+        return PressureLevel.of(self.pressure())
+
+    def notify_pressure_change(self) -> PressureLevel:
+        """Call the ``(old, new)`` listeners when the level moved since the last call."""
+        new, old = self.pressure_level(), (self._last_level if self._last_level is not None else PressureLevel.NONE)
+        if new != old:
+            self._last_level = new
+            for fn in self._level_listeners:
+                fn(old, new)
+        return new
+
+    def add_level_listener(self, fn) -> None:
+        self._level_listeners.append(fn)
+
+    def register_hook(self, fn, priority: int = 0, name: str = "") -> int:
+        self.add_pre_oom_hook(fn, priority, name)
+        self._next_hook += 1
+        self._hook_ids[self._next_hook] = fn
+        return self._next_hook
+
+    def remove_hook(self, hid: int) -> bool:
+        fn = self._hook_ids.pop(hid, None)
+        if fn is None:
+            return False
+        self._hooks = [h for h in self._hooks if h[2] is not fn]
+        return True
+
+    def memory_stats(self) -> dict:
+        used = self.alloc.used_bytes()
+        self._peak = max(self._peak, used)
+        return {"used_bytes": used, "peak_bytes": self._peak, "budget_bytes": self.budget,
+                "reserved_bytes": self.reserve, "available_bytes": self.available(), "pressure": self.pressure(),
+                "level": self.pressure_level().name, **self.stats}
+
+    def reset_peak_stats(self) -> None:
+        self._peak = self.alloc.used_bytes()
+
+    def safe_alloc(self, shape, dtype=None, device=None):
+        """``torch.empty`` behind the guard: the size is checked against the budget (running hooks /
+        waiting / failing by policy) before the allocator is asked."""
+        import math
+
+        import torch
+
+        dtype = dtype or torch.float32
+        self.ensure(math.prod(shape) * torch.empty(0, dtype=dtype).element_size())
+        return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+    def on_oom(self, fn) -> None:
+        """``fn()`` runs (after the hooks, before the error is raised) whenever a request cannot be met
+        (memory_guard.rs:373)."""
+        self._oom_callbacks.append(fn)
+
+    def safe_alloc_copy(self, data, dtype=None, device=None):
+        """A guarded allocation filled with ``data`` (a tensor or anything ``torch.as_tensor`` takes)."""
+        import torch
+
+        src = torch.as_tensor(data, dtype=dtype)
+        out = self.safe_alloc(src.shape, src.dtype, device)
+        out.copy_(src)
+        return out
+
+    def safe_alloc_with_hooks(self, shape, dtype=None, device=None):
+        """Like ``safe_alloc`` but the pre-OOM hooks always get their chance, whatever the policy says
+        (memory_guard.rs:479)."""
+        prev = self.policy
+        if prev == OomPolicy.FAIL:
+            self.policy = OomPolicy.RUN_HOOKS_THEN_FAIL
+        try:
+            return self.safe_alloc(shape, dtype, device)
+        finally:
+            self.policy = prev
+
+    def free(self, tensor) -> int:
+        """Give a guarded allocation back: the storage is released to the caching allocator when the last
+        reference goes; returns the bytes the tensor held."""
+        n = tensor.numel() * tensor.element_size()
+        tensor.set_()
+        return n
+
+    def device_ordinal(self) -> int:
+        return int(getattr(self.alloc, "device", 0))
+
+    def device(self):
+        import torch
+
+        return torch.device("cuda", self.device_ordinal()) if isinstance(self.alloc, TorchCudaAllocator) else torch.device("cpu")
+
+    def set_budget(self, nbytes: int) -> None:
+        self.budget = int(nbytes)
+
+    def set_oom_policy(self, policy: OomPolicy) -> None:
+        self.policy = policy
+
+    def has_reservation(self) -> bool:
+        return self.reserve > 0
+
+    def release_reservation(self) -> None:
+        self.reserve = 0
+
+    def reserved_bytes(self) -> int:
+        return self.reserve
+
+    def device_arc(self):
+        return self.device()
+
 
 # --------------------------------------------------------------------------- the reference's vocabulary
 # (memory_guard.rs: OomPolicy::{Fail, RetryAfterFree, WaitAndRetry, CheckpointAndFail}, PressureLevel,
@@ -165,142 +281,7 @@ class PressureLevel(enum.IntEnum):
         return cls.NONE
 
 
-def _pressure_level(self) -> PressureLevel:
-    return PressureLevel.of(self.pressure())
 
-
-def _notify_level_change(self) -> PressureLevel:
-    """Call the ``(old, new)`` listeners when the level moved since the last call."""
-    new, old = self.pressure_level(), getattr(self, "_last_level", PressureLevel.NONE)
-    if new != old:
-        self._last_level = new
-        for fn in getattr(self, "_level_listeners", []):
-            fn(old, new)
-    return new
-
-
-def _add_level_listener(self, fn) -> None:
-    self.__dict__.setdefault("_level_listeners", []).append(fn)
-
-
-def _register_hook(self, fn, priority: int = 0, name: str = "") -> int:
-    self.add_pre_oom_hook(fn, priority, name)
-    ids = self.__dict__.setdefault("_hook_ids", {})
-    hid = self.__dict__["_next_hook"] = self.__dict__.get("_next_hook", 0) + 1
-    ids[hid] = fn
-    return hid
-
-
-def _remove_hook(self, hid: int) -> bool:
-    fn = self.__dict__.get("_hook_ids", {}).pop(hid, None)
-    if fn is None:
-        return False
-    self._hooks = [h for h in self._hooks if h[2] is not fn]
-    return True
-
-
-def _memory_stats(self) -> dict:
-    used = self.alloc.used_bytes()
-    self.__dict__["_peak"] = max(self.__dict__.get("_peak", 0), used)
-    return {"used_bytes": used, "peak_bytes": self.__dict__["_peak"], "budget_bytes": self.budget,
-            "reserved_bytes": self.reserve, "available_bytes": self.available(), "pressure": self.pressure(),
-            "level": self.pressure_level().name, **self.stats}
-
-
-def _reset_peak_stats(self) -> None:
-    self.__dict__["_peak"] = self.alloc.used_bytes()
-
-
-def _safe_alloc(self, shape, dtype=None, device=None):
-    """``torch.empty`` behind the guard: the size is checked against the budget (running hooks /
-    waiting / failing by policy) before the allocator is asked."""
-    import math
-
-    import torch
-
-    dtype = dtype or torch.float32
-    self.ensure(math.prod(shape) * torch.empty(0, dtype=dtype).element_size())
-    return torch.empty(tuple(shape), dtype=dtype, device=device)
-
-
-MemoryGuard.pressure_level = _pressure_level
-MemoryGuard.notify_pressure_change = _notify_level_change
-MemoryGuard.add_level_listener = _add_level_listener
-MemoryGuard.register_hook = _register_hook
-MemoryGuard.remove_hook = _remove_hook
-MemoryGuard.memory_stats = _memory_stats
-MemoryGuard.reset_peak_stats = _reset_peak_stats
-MemoryGuard.safe_alloc = _safe_alloc
-MemoryGuard.set_budget = lambda self, nbytes: setattr(self, "budget", int(nbytes))
-MemoryGuard.set_oom_policy = lambda self, policy: setattr(self, "policy", policy)
-MemoryGuard.has_reservation = lambda self: self.reserve > 0
-MemoryGuard.release_reservation = lambda self: setattr(self, "reserve", 0)
-MemoryGuard.reserved_bytes = lambda self: self.reserve
-
-
-def _on_oom(self, fn) -> None:
-    """``fn()`` runs (after the hooks, before the error is raised) whenever a request cannot be met
-    (memory_guard.rs:373)."""
-    self.__dict__.setdefault("_oom_callbacks", []).append(fn)
-
-
-_plain_fail = MemoryGuard._fail
-
-
-def _fail_with_callbacks(self, nbytes: int):
-    for fn in self.__dict__.get("_oom_callbacks", []):
-        fn()
-    return _plain_fail(self, nbytes)
-
-
-def _safe_alloc_copy(self, data, dtype=None, device=None):
-    """A guarded allocation filled with ``data`` (a tensor or anything ``torch.as_tensor`` takes)."""
-    import torch
-
-    src = torch.as_tensor(data, dtype=dtype)
-    out = self.safe_alloc(src.shape, src.dtype, device)
-    out.copy_(src)
-    return out
-
-
-def _safe_alloc_with_hooks(self, shape, dtype=None, device=None):
-    """Like ``safe_alloc`` but the pre-OOM hooks always get their chance, whatever the policy says
-    (memory_guard.rs:479)."""
-    prev = self.policy
-    if prev == OomPolicy.FAIL:
-        self.policy = OomPolicy.RUN_HOOKS_THEN_FAIL
-    try:
-        return self.safe_alloc(shape, dtype, device)
-    finally:
-        self.policy = prev
-
-
-def _free(self, tensor) -> int:
-    """Give a guarded allocation back: the storage is released to the caching allocator when the last
-    reference goes; returns the bytes the tensor held."""
-    n = tensor.numel() * tensor.element_size()
-    tensor.set_()
-    return n
-
-
-def _device_ordinal(self) -> int:
-    return int(getattr(self.alloc, "device", 0))
-
-
-def _device(self):
-    import torch
-
-    return torch.device("cuda", self.device_ordinal()) if isinstance(self.alloc, TorchCudaAllocator) else torch.device("cpu")
-
-
-MemoryGuard.on_oom = _on_oom
-MemoryGuard._fail = _fail_with_callbacks
-MemoryGuard.safe_alloc_copy = _safe_alloc_copy
-MemoryGuard.safe_alloc_with_hooks = _safe_alloc_with_hooks
-MemoryGuard.free = _free
-MemoryGuard.device_ordinal = _device_ordinal
-MemoryGuard.device = _device
-MemoryGuard.device_arc = _device
 
 
 class MemoryGuardBuilder:
