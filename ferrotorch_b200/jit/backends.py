@@ -466,9 +466,11 @@ class InductorCompileStatus(enum.Enum):
     Partial = "partial"              # some groups were left to the native runner
     Interpreted = "interpreted"      # nothing to generate
 
+    def is_compiled(self) -> bool:
+        return self is InductorCompileStatus.Compiled
 
-InductorCompileStatus.is_compiled = lambda self: self is InductorCompileStatus.Compiled
-InductorCompileStatus.is_fallback = lambda self: self is not InductorCompileStatus.Compiled
+    def is_fallback(self) -> bool:
+        return self is not InductorCompileStatus.Compiled
 
 
 @dataclass
@@ -526,27 +528,19 @@ class InductorBackend(Codegen):
                        InductorCompileStatus.Compiled if done == total else InductorCompileStatus.Partial)
         return CompiledGraph(graph, steps, self.name, sources)
 
+    def with_block_size(self, block_size: int) -> "InductorBackend":
+        self.block_size = int(block_size)
+        return self
 
-def _inductor_with_block_size(self, block_size: int) -> "InductorBackend":
-    self.block_size = int(block_size)
-    return self
+    def compile_with_status(self, graph: IrGraph) -> "InductorCompileOutcome":
+        compiled = self.compile(graph)
+        reason = {InductorCompileStatus.Compiled: "", InductorCompileStatus.Partial: "some fused groups run through the native runner",
+                  InductorCompileStatus.Interpreted: "the graph has no fused group to generate code for"}[self.status]
+        return InductorCompileOutcome(self.status, compiled, reason)
 
-
-def _inductor_compile_with_status(self, graph: IrGraph) -> InductorCompileOutcome:
-    compiled = self.compile(graph)
-    reason = {InductorCompileStatus.Compiled: "", InductorCompileStatus.Partial: "some fused groups run through the native runner",
-              InductorCompileStatus.Interpreted: "the graph has no fused group to generate code for"}[self.status]
-    return InductorCompileOutcome(self.status, compiled, reason)
-
-
-def _inductor_generate(self, graph: IrGraph) -> dict:
-    """Generated source per fused node, without keeping the runnable graph."""
-    return dict(self.compile(graph).sources)
-
-
-InductorBackend.with_block_size = _inductor_with_block_size
-InductorBackend.compile_with_status = _inductor_compile_with_status
-InductorBackend.generate = _inductor_generate
+    def generate(self, graph: IrGraph) -> dict:
+        """Generated source per fused node, without keeping the runnable graph."""
+        return dict(self.compile(graph).sources)
 
 
 def compile_loop_ir_kernel(ir: LoopIR, name: str = "fused_loop"):

@@ -168,18 +168,14 @@ class LlamaDecoderLayer(nn.Module):
         h, x = self.post_attention_layernorm(x, a)
         return x, self.mlp(h)
 
+    def forward_with_cache(self, x: torch.Tensor, layer_cache=None):
+        """One decoder layer on a value cache (layer.rs ``forward_with_cache``): ``(hidden states, new layer
+        cache)`` with the residual additions applied."""
+        from .llama_compat import _GrowingLayerCache
 
-def _layer_forward_with_cache(self, x: torch.Tensor, layer_cache=None):
-    """One decoder layer on a value cache (layer.rs ``forward_with_cache``): ``(hidden states, new layer
-    cache)`` with the residual additions applied."""
-    from .llama_compat import _GrowingLayerCache
-
-    grow = _GrowingLayerCache(layer_cache)
-    h, delta = self.forward(x, cache=grow)
-    return h + delta, grow.as_layer()
-
-
-LlamaDecoderLayer.forward_with_cache = _layer_forward_with_cache
+        grow = _GrowingLayerCache(layer_cache)
+        h, delta = self.forward(x, cache=grow)
+        return h + delta, grow.as_layer()
 
 
 class LlamaModel(nn.Module):

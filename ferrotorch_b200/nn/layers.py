@@ -248,25 +248,25 @@ class GQAAttention(nn.Module):
         o = flash_attention(q, k, v, causal=causal)
         return self.o_proj(o.reshape(B, S, Hq * D))
 
+    def forward_with_cache(self, x: torch.Tensor, layer_cache=None, seq_offset: int | None = None):
+        """``(output, new layer cache)`` for ``x [B, S, hidden]`` on a value cache
+        (ferrotorch-llama/src/attention.rs:121-200 ``forward_with_cache``): keys (after RoPE) and values of the
+        new positions are appended to a copy of ``layer_cache`` (a ``LayerKvCache`` or ``None``), which is
+        returned; the argument is left untouched."""
+        from ..models.llama_compat import _GrowingLayerCache
 
-def _attention_forward_with_cache(self, x: torch.Tensor, layer_cache=None, seq_offset: int | None = None):
-    """``(output, new layer cache)`` for ``x [B, S, hidden]`` on a value cache
-    (ferrotorch-llama/src/attention.rs:121-200 ``forward_with_cache``): keys (after RoPE) and values of the
-    new positions are appended to a copy of ``layer_cache`` (a ``LayerKvCache`` or ``None``), which is
-    returned; the argument is left untouched."""
-    from ..models.llama_compat import _GrowingLayerCache
+        if x.shape[0] != 1:
+            raise ValueError("forward_with_cache serves one sequence; got a batch of %d" % x.shape[0])
+        grow = _GrowingLayerCache(layer_cache)
+        if seq_offset is not None and seq_offset != grow.len:
+            raise ValueError("forward_with_cache: seq_offset %d but the cache holds %d positions" % (seq_offset, grow.len))
+        return self.forward(x, cache=grow), grow.as_layer()
 
-    if x.shape[0] != 1:
-        raise ValueError("forward_with_cache serves one sequence; got a batch of %d" % x.shape[0])
-    grow = _GrowingLayerCache(layer_cache)
-    if seq_offset is not None and seq_offset != grow.len:
-        raise ValueError("forward_with_cache: seq_offset %d but the cache holds %d positions" % (seq_offset, grow.len))
-    return self.forward(x, cache=grow), grow.as_layer()
+    def num_heads(self) -> int:
+        return self.n_heads
 
-
-GQAAttention.forward_with_cache = _attention_forward_with_cache
-GQAAttention.num_heads = lambda self: self.n_heads
-GQAAttention.num_kv_heads = lambda self: self.n_kv_heads
+    def num_kv_heads(self) -> int:
+        return self.n_kv_heads
 
 
 def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
