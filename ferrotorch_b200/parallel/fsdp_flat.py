@@ -14,8 +14,12 @@ dominated by launch latency, not by bytes, so this module shards by *unit* inste
 A step therefore costs two all-gathers (before forward, before backward) and one reduce-scatter per unit.
 Between its forward and its backward a unit gives its full buffer back (the storage is resized to zero and
 re-filled by the second all-gather; saved tensors stay valid because they alias the same storage object).
-``auto_wrap`` wraps every sub-module of the given classes and lets each unit start the all-gather of the
-next one on a worker thread while it computes (forward prefetch).
+``auto_wrap`` wraps every sub-module of the given classes and overlaps communication with compute: every
+collective of the chained units runs on one worker thread, in the order in which it was posted (the same on
+every rank, because the model and the autograd order are), so a unit's forward overlaps the next unit's
+all-gather, its backward overlaps the previous unit's all-gather, and its reduce-scatter starts as soon as
+its last gradient has been accumulated.  ``intra_node_size`` gives hybrid sharding: parameters are sharded
+inside groups of that many ranks and gradients are additionally averaged across the groups.
 """
 from __future__ import annotations
 
@@ -36,13 +40,16 @@ class _PreBackward(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         ctx.unit.unshard()
+        if ctx.unit.prev_unit is not None:
+            ctx.unit.prev_unit.prefetch()                 # the previous unit's parameters travel while this one differentiates
         return (None, *grads)
 
 
 class FsdpUnit(nn.Module):
-    def __init__(self, module: nn.Module, group: Group, reshard_after_forward: bool = True):
+    def __init__(self, module: nn.Module, group: Group, reshard_after_forward: bool = True, replica_group: Group | None = None):
         super().__init__()
         self.module, self.group, self.reshard_after_forward = module, group, reshard_after_forward
+        self.replica_group = replica_group
         W, r = group.world_size, group.rank
         self._params = [p for p in module.parameters() if p.requires_grad and not getattr(p, "_fsdp_owned", False)]
         for p in self._params:
@@ -70,8 +77,15 @@ class FsdpUnit(nn.Module):
         self._sharded = False
         self._point_views()
         self._prefetched = None
-        object.__setattr__(self, "next_unit", None)       # a plain reference: the next unit is not a sub-module of this one
+        object.__setattr__(self, "next_unit", None)       # plain references: neighbours are not sub-modules of this unit
+        object.__setattr__(self, "prev_unit", None)
         self._lane: _Lane | None = None
+        self.overlap_grad_sync = False
+        self._grads_left = len(self._params)
+        self._pending_rs = None
+        self._rs_result: torch.Tensor | None = None
+        for p in self._params:
+            p.register_post_accumulate_grad_hook(self._grad_ready)
         self.stats = {"all_gathers": 0, "reduce_scatters": 0}
         self.reshard()
 
@@ -99,6 +113,8 @@ class FsdpUnit(nn.Module):
         """Bring the full parameters back (no-op when they are there)."""
         if not self._sharded:
             return
+        if self._prefetched is None and self._lane is not None:
+            self.prefetch()                               # collectives of chained units all go through the lane, in posting order
         if self._prefetched is not None:
             op, box = self._prefetched
             op.wait()
@@ -147,20 +163,39 @@ class FsdpUnit(nn.Module):
             self.reshard()
         return out
 
+    def _grad_ready(self, _param) -> None:
+        self._grads_left -= 1
+        if self._grads_left == 0 and self.overlap_grad_sync and self._lane is not None and self._pending_rs is None:
+            self._pending_rs = self._lane.post(self._reduce_scatter)
+
+    def _reduce_scatter(self) -> None:
+        W = self.group.world_size
+        self.stats["reduce_scatters"] += 1
+        part = self.group.reduce_scatter(self.flat_grad.view(W, self.padded // W), "mean").reshape(-1)
+        if self.replica_group is not None:
+            part = self.replica_group.all_reduce(part.contiguous(), "mean")
+        self._rs_result = part
+
     def sync_gradients(self) -> None:
-        """After backward: one reduce-scatter (mean) of the unit's flat gradient into ``shard.grad``; the full
-        parameters and the flat gradient are released.  Recurses into nested units."""
+        """After backward: one reduce-scatter (mean) of the unit's flat gradient into ``shard.grad`` (already under
+        way when gradient synchronisation is overlapped); the full parameters and the flat gradient are released.
+        Recurses into nested units."""
         for m in self.module.modules():
             if isinstance(m, FsdpUnit):
                 m.sync_gradients()
         if self.flat_grad is not None:
-            W = self.group.world_size
-            self.stats["reduce_scatters"] += 1
-            part = self.group.reduce_scatter(self.flat_grad.view(W, self.padded // W), "mean").reshape(-1)
+            if self._pending_rs is None:
+                self._pending_rs = self._lane.post(self._reduce_scatter) if self._lane is not None else None
+                if self._pending_rs is None:
+                    self._reduce_scatter()
+            if self._pending_rs is not None:
+                self._pending_rs.wait()
+            part, self._rs_result, self._pending_rs = self._rs_result, None, None
             self.shard.grad = part if self.shard.grad is None else self.shard.grad + part
             self.flat_grad = None
             for p in self._params:
                 p.grad = None
+        self._grads_left = len(self._params)
         self.reshard()
 
     def full_state_dict(self) -> dict:
@@ -193,28 +228,45 @@ class _Container(nn.Module):
             u.sync_gradients()
 
 
-def auto_wrap(model: nn.Module, group: Group, wrap_classes: tuple, reshard_after_forward: bool = True, prefetch: bool = True) -> FsdpUnit:
+def auto_wrap(model: nn.Module, group: Group, wrap_classes: tuple, reshard_after_forward: bool = True, prefetch: bool = True,
+              overlap_grad_sync: bool = True, intra_node_size: int | None = None) -> FsdpUnit:
     """Wrap every sub-module that is an instance of ``wrap_classes`` in its own :class:`FsdpUnit` (innermost
     first) and the rest of the model in a root unit.  With ``prefetch`` the units are chained in the order of
-    their definition, so each starts the next one's all-gather while it computes."""
+    their definition and share one worker thread for their collectives (see the module text);
+    ``overlap_grad_sync`` starts each unit's reduce-scatter from a gradient hook.  ``intra_node_size``: shard
+    inside groups of that many consecutive ranks, average gradients across them (hybrid sharding)."""
+    from .backend import SubGroup
+
     units: list[FsdpUnit] = []
+    replica = None
+    if intra_node_size is not None and intra_node_size != group.world_size:
+        n = intra_node_size
+        if n < 1 or group.world_size % n:
+            raise ValueError("auto_wrap: intra_node_size %d does not divide the world size %d" % (n, group.world_size))
+        node = group.rank // n
+        replica = SubGroup(group, range(group.rank % n, group.world_size, n))
+        group = SubGroup(group, range(node * n, (node + 1) * n))
 
     def visit(mod: nn.Module) -> None:
         for name, child in list(mod.named_children()):
             visit(child)
             if isinstance(child, wrap_classes) and not isinstance(child, FsdpUnit):
-                u = FsdpUnit(child, group, reshard_after_forward)
+                u = FsdpUnit(child, group, reshard_after_forward, replica)
                 setattr(mod, name, u)
                 units.append(u)
 
     visit(model)
     leftover = any(p.requires_grad and not getattr(p, "_fsdp_owned", False) for p in model.parameters())
-    root = FsdpUnit(model, group, reshard_after_forward) if leftover else _Container(model, units)
+    root = FsdpUnit(model, group, reshard_after_forward, replica) if leftover else _Container(model, units)
     if prefetch and units:
         lane = _Lane()
         for a, b in zip(units, units[1:]):
             object.__setattr__(a, "next_unit", b)
+            object.__setattr__(b, "prev_unit", a)
         for u in units:
             u._lane = lane
+            u.overlap_grad_sync = overlap_grad_sync
+        if isinstance(root, FsdpUnit):                    # the root's collectives join the same ordered stream
+            root._lane = lane
     object.__setattr__(root, "units", units)
     return root

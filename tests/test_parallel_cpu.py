@@ -486,7 +486,9 @@ def test_vocabulary_parallel_sampling_equals_single_device_sampling(world):
 
 
 # --------------------------------------------------------------------------- FSDP with one flat buffer per unit
-def test_flat_fsdp_units_train_like_one_process_and_release_their_buffers():
+@pytest.mark.parametrize("prefetch,overlap,intra", [(True, True, None), (False, False, None), (True, True, 2)],
+                         ids=["overlapped", "inline", "hybrid-2x2"])
+def test_flat_fsdp_units_train_like_one_process_and_release_their_buffers(prefetch, overlap, intra):
     import threading
 
     from torch import nn
@@ -523,7 +525,8 @@ def test_flat_fsdp_units_train_like_one_process_and_release_their_buffers():
     protos = [make() for _ in range(W)]           # built here: the global generator is not thread-safe
 
     def rank(r):
-        model = auto_wrap(protos[r], groups[r], (Block,), reshard_after_forward=True, prefetch=True)
+        model = auto_wrap(protos[r], groups[r], (Block,), reshard_after_forward=True, prefetch=prefetch, overlap_grad_sync=overlap,
+                          intra_node_size=intra)
         ps = model.sharded_parameters()
         o = torch.optim.SGD(ps, lr=0.1, momentum=0.9)
         xs, ys = X.chunk(W)[r], Y.chunk(W)[r]
@@ -552,7 +555,8 @@ def test_flat_fsdp_units_train_like_one_process_and_release_their_buffers():
         assert freed == [0, 0, 0]                                               # every unit gave its full buffer back
         # per step and unit: one all-gather before forward, one before backward, one reduce-scatter
         assert all(s == {"all_gathers": 2 * steps, "reduce_scatters": steps} for s in stats)
-        assert held <= (sum(p.numel() for p in ref.parameters()) + 3 * W * 5) // W + 1               # about 1 / W of the model
+        shard_ways = intra or W
+        assert held <= (sum(p.numel() for p in ref.parameters()) + 3 * W * 5) // shard_ways + 1      # about 1 / ways of the model
     mean_losses = [sum(out[r][0][i] for r in range(W)) / W for i in range(steps)]
     torch.testing.assert_close(torch.tensor(mean_losses), torch.tensor(ref_losses), rtol=1e-5, atol=1e-6)
     one = SimulatedGroup.create_group(1)[0]
