@@ -18,6 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("coming_from_ferrotorch.py", []),
     ("detect_objects.py", ["--model", "fcos"]),
     ("pipeline_and_context_parallel.py", []),
+    ("fsdp_flat_units.py", []),
     ("train_mnist_synthetic.py", ["--epochs", "2", "--samples", "600"]),
 ])
 def test_example_runs(script, args):
