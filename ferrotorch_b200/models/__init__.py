@@ -9,8 +9,8 @@ from .resnet import create_model, list_models, register_model, resnet18, resnet3
 
 def __getattr__(name):
     """Loaded on first use: the batched, paged, tensor-parallel
-    :class:`~ferrotorch_b200.models.engine.LlamaEngine` (binds the kernel library) and the
-    reference's single-sequence inference objects (ferrotorch-llama/src/gpu.rs) from
+    :class:`~ferrotorch_b200.models.engine.LlamaEngine` (binds the kernel library), the continuous-batching
+    server of :mod:`~ferrotorch_b200.models.serving` and the reference's single-sequence inference objects (ferrotorch-llama/src/gpu.rs) from
     :mod:`~ferrotorch_b200.models.inferencer`."""
     if name == "LlamaEngine":
         from .engine import LlamaEngine
@@ -24,6 +24,10 @@ def __getattr__(name):
         from . import spec_decode
 
         return getattr(spec_decode, name)
+    if name in ("ContinuousBatcher", "Request", "RequestState", "SamplingParams", "ServingStats"):
+        from . import serving
+
+        return getattr(serving, name)
     if name == "KVCache":
         from ..nn.layers import KVCache
 

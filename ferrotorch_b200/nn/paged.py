@@ -117,12 +117,13 @@ class PagedKVCache:
         T = k_new.shape[0]
         table = self.sync_table()
         if not k_new.is_cuda:
-            sid = seq_ids if seq_ids is not None else torch.arange(T) // tokens_per_seq
-            for i in range(T):
-                p = int(positions[i])
-                blk = int(self._table_host[int(sid[i]), p // self.block_size])
-                self.k[layer][blk, p % self.block_size] = k_new[i]
-                self.v[layer][blk, p % self.block_size] = v_new[i]
+            sid = (seq_ids if seq_ids is not None else torch.arange(T) // tokens_per_seq).long()
+            pos = positions.long()
+            blk = self._table_host[sid, pos // self.block_size].long()
+            if bool((blk < 0).any()):
+                raise ValueError("PagedKVCache.append: a position has no page (reserve the sequence first)")
+            self.k[layer][blk, pos % self.block_size] = k_new.to(self.k[layer].dtype)
+            self.v[layer][blk, pos % self.block_size] = v_new.to(self.v[layer].dtype)
             return
         ldk = k_new.stride(0)
         ldv = v_new.stride(0)
@@ -134,13 +135,17 @@ class PagedKVCache:
         _native.check(rc, "ft_kv_append")
 
     def decode(self, layer: int, q: torch.Tensor, ctx_len: torch.Tensor, scale: float | None = None,
-               n_splits: int = 0) -> torch.Tensor:
-        """One query token per sequence: ``q [B, Hq, D]``, ``ctx_len [B]`` int32 -> ``[B, Hq, D]``."""
+               n_splits: int = 0, seq_ids: torch.Tensor | None = None) -> torch.Tensor:
+        """One query token per sequence: ``q [B, Hq, D]``, ``ctx_len [B]`` int32 -> ``[B, Hq, D]``.  Row b
+        reads sequence b, or sequence ``seq_ids[b]`` (a batch of any subset of the live sequences: the rows of
+        the block table are gathered in that order)."""
         B, Hq, D = q.shape
         scale = scale if scale is not None else D ** -0.5
         table = self.sync_table()
         if not q.is_cuda:
-            return self._decode_reference(layer, q, ctx_len, scale)
+            return self._decode_reference(layer, q, ctx_len, scale, seq_ids)
+        if seq_ids is not None:
+            table = table.index_select(0, seq_ids.to(device=table.device, dtype=torch.long)).contiguous()
         lib = _native.kernels()
         if n_splits <= 0:
             ctas = B * self.n_kv_heads
@@ -188,12 +193,12 @@ class PagedKVCache:
             if self._pages[s]:
                 self.free_sequence(s)
 
-    def _decode_reference(self, layer, q, ctx_len, scale):
+    def _decode_reference(self, layer, q, ctx_len, scale, seq_ids=None):
         from ..ops import reference as ref
 
         outs = []
         for b in range(q.shape[0]):
-            k, v = self.gather(layer, b, int(ctx_len[b]))
+            k, v = self.gather(layer, b if seq_ids is None else int(seq_ids[b]), int(ctx_len[b]))
             o, _ = ref.attention(q[b][None, None], k[None], v[None], causal=False, scale=scale)
             outs.append(o[0, 0])
         return torch.stack(outs)

@@ -19,6 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("detect_objects.py", ["--model", "fcos"]),
     ("pipeline_and_context_parallel.py", []),
     ("fsdp_flat_units.py", []),
+    ("serve_many_requests.py", []),
     ("train_mnist_synthetic.py", ["--epochs", "2", "--samples", "600"]),
 ])
 def test_example_runs(script, args):
