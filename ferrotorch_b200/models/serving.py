@@ -15,7 +15,11 @@ sequences and gives every step one flat token batch:
   (its pages are freed, it re-enters the queue at the front and recomputes its prompt plus what it has generated),
   so the earliest requests always finish and the pool can be smaller than the sum of all contexts;
 * waiting requests are admitted first come first served while there are sequence slots, step-token budget and
-  pages above a watermark.
+  pages above a watermark;
+* with ``prefix_caching`` whole pages of finished (or still running) prompts stay in a table keyed by a hash chain
+  of their tokens; a new request whose prompt starts with the same tokens adopts those pages (reference-counted
+  in the pool) and computes only the rest.  Unused entries are evicted, deepest page of the least recently used
+  chain first, before any sequence is preempted.
 
 Greedy requests are sampled on the device in one ``argmax``; sampled requests carry their own generator, so
 the tokens of a request do not depend on which other requests share its steps.
@@ -24,7 +28,9 @@ from __future__ import annotations
 
 import collections
 import enum
+import hashlib
 import queue
+import struct
 import threading
 import time
 from dataclasses import dataclass, field
@@ -108,10 +114,78 @@ class ServingStats:
     finished: int = 0
     peak_running: int = 0
     peak_pages: int = 0
+    prefix_hit_tokens: int = 0                            # prompt tokens that were adopted from the prefix table
     batch_tokens: list = field(default_factory=list)      # tokens of every step's flat batch
 
     def mean_batch_tokens(self) -> float:
         return sum(self.batch_tokens) / len(self.batch_tokens) if self.batch_tokens else 0.0
+
+
+class PrefixCache:
+    """Full pages of token prefixes, shared between sequences.  The key of page i of a sequence is a digest of
+    the key of page i - 1 and of the page's tokens, so equal keys mean equal prefixes; the table holds one
+    reference on every page it lists."""
+
+    def __init__(self, pool, block_size: int):
+        self.pool, self.block_size = pool, block_size
+        self._table: collections.OrderedDict = collections.OrderedDict()      # digest -> page, least recently used first
+        self.hits = self.misses = self.evictions = 0
+
+    def __len__(self) -> int:
+        return len(self._table)
+
+    def keys_for(self, tokens: list) -> list:
+        keys, prev, bs = [], b"", self.block_size
+        for i in range(len(tokens) // bs):
+            prev = hashlib.blake2b(prev + struct.pack("<%dq" % bs, *tokens[i * bs:(i + 1) * bs]), digest_size=16).digest()
+            keys.append(prev)
+        return keys
+
+    def match(self, tokens: list) -> list:
+        """Pages of the longest listed prefix of ``tokens`` (whole pages only)."""
+        keys, pages = self.keys_for(tokens), []
+        for k in keys:
+            page = self._table.get(k)
+            if page is None:
+                break
+            pages.append(page)
+        for k in reversed(keys[:len(pages)]):             # the root of a chain is its most recently used entry
+            self._table.move_to_end(k)
+        self.hits += len(pages)
+        self.misses += len(keys) - len(pages)
+        return pages
+
+    def insert(self, tokens: list, pages: list) -> int:
+        """List the whole pages of ``tokens`` (``pages[i]`` holds tokens ``i * block_size ..``); returns how many were new."""
+        keys, new = self.keys_for(tokens)[:len(pages)], 0
+        for k, page in reversed(list(zip(keys, pages))):
+            if k not in self._table:
+                self._table[k] = self.pool.retain(page)
+                new += 1
+            self._table.move_to_end(k)
+        return new
+
+    def evictable(self) -> int:
+        return sum(1 for page in self._table.values() if self.pool.ref_count(page) == 1)
+
+    def evict(self, n_pages: int) -> int:
+        """Drop up to ``n_pages`` entries that no sequence holds, least recently used first; returns how many."""
+        done = 0
+        for k in list(self._table):
+            if done >= n_pages:
+                break
+            page = self._table[k]
+            if self.pool.ref_count(page) == 1:
+                del self._table[k]
+                self.pool.free(page)
+                done += 1
+        self.evictions += done
+        return done
+
+    def clear(self) -> None:
+        for page in self._table.values():
+            self.pool.free(page)
+        self._table.clear()
 
 
 class ContinuousBatcher:
@@ -124,7 +198,8 @@ class ContinuousBatcher:
     leaves free for the growth of the sequences that are already running."""
 
     def __init__(self, model, num_blocks: int, block_size: int = 16, max_running: int = 64, max_seq_len: int | None = None,
-                 max_tokens_per_step: int = 2048, prefill_chunk: int = 512, watermark: float = 0.01):
+                 max_tokens_per_step: int = 2048, prefill_chunk: int = 512, watermark: float = 0.01,
+                 prefix_caching: bool = False):
         cfg = model.config
         p = next(model.parameters())
         self.model = model
@@ -136,6 +211,7 @@ class ContinuousBatcher:
         if max_tokens_per_step < 1 or prefill_chunk < 1:
             raise ValueError("ContinuousBatcher: max_tokens_per_step and prefill_chunk must be at least 1")
         self.watermark_pages = max(1, int(watermark * num_blocks)) if watermark > 0 else 0
+        self.prefix = PrefixCache(self.cache.pool, block_size) if prefix_caching else None
         self.waiting: collections.deque = collections.deque()
         self.running: list = []                           # in admission order
         self.stats = ServingStats()
@@ -184,8 +260,13 @@ class ContinuousBatcher:
         return bool(self.waiting or self.running or not self._inbox.empty())
 
     # ------------------------------------------------------------------ scheduling
+    def _remember(self, r: Request) -> None:
+        if self.prefix is not None and r.slot >= 0 and r.computed >= self.cache.block_size:
+            self.prefix.insert(r.tokens()[:r.computed], self.cache.pages_of(r.slot))
+
     def _finish(self, r: Request, reason: str) -> None:
         if r.slot >= 0:
+            self._remember(r)
             self.manager.remove_sequence(r.slot)
             r.slot = -1
         if r in self.running:
@@ -196,6 +277,7 @@ class ContinuousBatcher:
         r._done.set()
 
     def _preempt(self, r: Request) -> None:
+        self._remember(r)
         self.manager.remove_sequence(r.slot)
         self.running.remove(r)
         r.slot, r.computed, r.state = -1, 0, RequestState.WAITING
@@ -212,6 +294,8 @@ class ContinuousBatcher:
                 self.manager.active[r.slot] = max(self.manager.active[r.slot], new_len)
                 return True
             except OutOfPages:
+                if self.prefix is not None and self.prefix.evict(1):
+                    continue
                 victims = [v for v in self.running if v is not r and v.id not in protected]
                 if victims:
                     self._preempt(victims[-1])
@@ -238,14 +322,30 @@ class ContinuousBatcher:
         runs = [run for run in runs if run[0].state is RequestState.RUNNING and run[0].slot >= 0]
         while self.waiting and not preempted and budget > 0 and len(self.running) < self.max_running:
             r = self.waiting[0]
-            n = min(len(r.prompt) + len(r.output), self.prefill_chunk, budget)
-            if self._pages_for(n) + (self.watermark_pages if self.running else 0) > self.manager.free_pages:
+            seq = r.tokens()
+            shared = self.prefix.match(seq[:-1]) if self.prefix is not None else []      # at least one token is computed
+            start = len(shared) * self.cache.block_size
+            n = min(len(seq) - start, self.prefill_chunk, budget)
+            need = self._pages_for(start + n) - len(shared) + (self.watermark_pages if self.running else 0)
+            if need > self.manager.free_pages and self.prefix is not None:
+                for page in shared:                           # pages this request is about to adopt must survive the eviction
+                    self.cache.pool.retain(page)
+                self.prefix.evict(need - self.manager.free_pages)
+                for page in shared:
+                    self.cache.pool.free(page)
+            if need > self.manager.free_pages:
                 break
             self.waiting.popleft()
-            r.slot = self.manager.add_sequence(n)
+            r.slot = self.manager.add_sequence(0)
+            if shared:
+                self.cache.adopt(r.slot, shared, start)
+                self.stats.prefix_hit_tokens += start
+            self.cache.reserve(r.slot, start + n)
+            self.manager.active[r.slot] = start + n
+            r.computed = start
             r.state, r._admitted_at = RequestState.RUNNING, self.stats.steps
             self.running.append(r)
-            runs.append((r, 0, n))
+            runs.append((r, start, n))
             budget -= n
         return runs
 
@@ -344,6 +444,8 @@ class ContinuousBatcher:
             else:
                 self.stats.prefill_tokens += n
             if r.computed == len(r.prompt) + len(r.output):
+                if n > 1:
+                    self._remember(r)                         # a prompt that has just been computed can be shared at once
                 emit.append(r)
                 rows.append(i)
         produced = []

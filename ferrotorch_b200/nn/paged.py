@@ -26,25 +26,43 @@ class OutOfPages(RuntimeError):
 
 
 class PagePool:
-    """Free-list of page ids (paged_attention.rs:155-260)."""
+    """Free-list of page ids (paged_attention.rs:155-260) with a reference count per page: a page that several
+    sequences share (a common prompt prefix) returns to the free list when its last holder lets go."""
 
     def __init__(self, num_pages: int):
         self.num_pages = num_pages
         self._free = list(range(num_pages - 1, -1, -1))
+        self._refs = [0] * num_pages
 
     def allocate(self) -> int:
         if not self._free:
             raise OutOfPages("page pool exhausted (%d pages)" % self.num_pages)
-        return self._free.pop()
+        page = self._free.pop()
+        self._refs[page] = 1
+        return page
+
+    def retain(self, page: int) -> int:
+        """One more holder of an allocated page."""
+        if not 0 <= page < self.num_pages or self._refs[page] == 0:
+            raise ValueError("page %d is not allocated" % page)
+        self._refs[page] += 1
+        return page
+
+    def ref_count(self, page: int) -> int:
+        return self._refs[page]
 
     def free(self, page: int) -> None:
         if not 0 <= page < self.num_pages:
             raise ValueError("page %d out of range" % page)
-        self._free.append(page)
+        if self._refs[page] == 0:
+            raise ValueError("page %d is free already" % page)
+        self._refs[page] -= 1
+        if self._refs[page] == 0:
+            self._free.append(page)
 
     def alloc_page(self):
         """A free page id, or ``None`` when the pool is exhausted (paged_attention.rs:200; ``allocate`` raises)."""
-        return self._free.pop() if self._free else None
+        return self.allocate() if self._free else None
 
     free_page = free
 
@@ -94,6 +112,22 @@ class PagedKVCache:
             pages.append(p)
             self._dirty = True
         self.lengths[seq] = max(self.lengths[seq], new_len)
+
+    def adopt(self, seq: int, pages: list, length: int) -> None:
+        """Start sequence ``seq`` on pages that already hold its first ``length`` tokens (whole pages that
+        another sequence filled; every one gains a holder).  The sequence must be empty."""
+        if self._pages[seq]:
+            raise ValueError("adopt: sequence %d already has pages" % seq)
+        if length != len(pages) * self.block_size or len(pages) > self.max_blocks:
+            raise ValueError("adopt: %d pages of %d tokens cannot hold a prefix of %d" % (len(pages), self.block_size, length))
+        for i, p in enumerate(pages):
+            self._table_host[seq, i] = self.pool.retain(p)
+        self._pages[seq] = list(pages)
+        self.lengths[seq] = length
+        self._dirty = bool(pages) or self._dirty
+
+    def pages_of(self, seq: int) -> list:
+        return list(self._pages[seq])
 
     def free_sequence(self, seq: int) -> None:
         for p in self._pages[seq]:

@@ -140,3 +140,62 @@ def test_paged_decode_reads_the_sequences_it_is_given():
         assert torch.allclose(out[b], torch.einsum("hn,nhd->hd", p, vv), atol=1e-5)
     with pytest.raises(ValueError):
         c.append(0, torch.zeros(1, 2, 16), torch.zeros(1, 2, 16), torch.tensor([20], dtype=torch.int32), torch.tensor([0], dtype=torch.int32))
+
+
+def test_prefix_caching_shares_the_pages_of_a_common_prompt(served):
+    model, prompts, news, alone = served
+    g = torch.Generator().manual_seed(9)
+    system = torch.randint(0, 160, (37,), generator=g).tolist()
+    tails = [torch.randint(0, 160, (n,), generator=g).tolist() for n in (6, 11, 3, 8, 14, 1)]
+    full = [system + t for t in tails]
+    want = [generate(model, torch.tensor([p]), GenerationConfig.greedy(8))[0, len(p):].tolist() for p in full]
+
+    plain = ContinuousBatcher(model, num_blocks=40, block_size=8, max_running=2, max_seq_len=128, watermark=0.0)
+    assert plain.generate(full, 8) == want
+    b = ContinuousBatcher(model, num_blocks=40, block_size=8, max_running=2, max_seq_len=128, watermark=0.0, prefix_caching=True)
+    assert b.generate(full, 8) == want
+    # the first two requests start together and compute the system prompt; the other four adopt its four whole pages
+    assert b.stats.prefix_hit_tokens == 4 * 32 and b.stats.prefill_tokens == plain.stats.prefill_tokens - 4 * 32
+    assert b.stats.steps <= plain.stats.steps and b.prefix.hits >= 16
+    pool = b.cache.pool
+    assert b.manager.num_sequences() == 0 and pool.num_used == len(b.prefix) > 0
+    assert all(pool.ref_count(p) == 1 for p in b.prefix._table.values())
+    # the same prompt again: everything but its last partial page is adopted, the answer is the same
+    again = b.submit(full[1], 8)
+    b.run()
+    assert again.output == want[1] and b.stats.prefix_hit_tokens == 4 * 32 + 40
+    b.prefix.clear()
+    assert pool.num_used == 0 and pool.num_free == 40
+
+    # a pool so small that listed pages have to be evicted to make room, and sequences preempted after that
+    tight = ContinuousBatcher(model, num_blocks=14, block_size=8, max_running=3, max_seq_len=128, watermark=0.0, prefix_caching=True)
+    assert tight.generate(full + [prompts[i] for i in (0, 2, 4, 5)], 8) == want + [alone[i][:8] for i in (0, 2, 4, 5)]
+    assert tight.prefix.evictions > 0 and tight.cache.pool.num_used == len(tight.prefix)
+    tight.prefix.clear()
+    assert tight.cache.pool.num_free == 14
+
+
+def test_page_pool_counts_holders():
+    from ferrotorch_b200.nn.paged import PagePool
+
+    pool = PagePool(3)
+    a = pool.allocate()
+    assert pool.retain(a) == a and pool.ref_count(a) == 2
+    pool.free(a)
+    assert pool.num_used == 1
+    pool.free(a)
+    assert pool.num_used == 0 and pool.ref_count(a) == 0
+    with pytest.raises(ValueError):
+        pool.free(a)
+    with pytest.raises(ValueError):
+        pool.retain(a)
+    c = PagedKVCache(1, 1, 4, num_blocks=4, max_seqs=2, max_seq_len=16, block_size=4, device="cpu", dtype=torch.float32)
+    c.reserve(0, 8)
+    c.adopt(1, c.pages_of(0), 8)
+    assert c.len(1) == 8 and c.pool.num_used == 2
+    c.free_sequence(0)
+    assert c.pool.num_used == 2
+    c.free_sequence(1)
+    assert c.pool.num_used == 0
+    with pytest.raises(ValueError):
+        c.adopt(1, [0], 3)
