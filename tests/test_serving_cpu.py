@@ -199,3 +199,73 @@ def test_page_pool_counts_holders():
     assert c.pool.num_used == 0
     with pytest.raises(ValueError):
         c.adopt(1, [0], 3)
+
+
+def test_http_front_serves_concurrent_completions_streams_and_reports_metrics(served):
+    import json
+    import urllib.error
+    import urllib.request
+
+    from ferrotorch_b200.models.server import ServingApp
+
+    model, prompts, news, alone = served
+    b = ContinuousBatcher(model, num_blocks=24, block_size=8, max_running=4, max_seq_len=128, prefix_caching=True)
+    app = ServingApp(b, encode=lambda s: [ord(c) % 160 for c in s], decode=lambda ids: "".join(chr(65 + i % 26) for i in ids)).start()
+    base = "http://127.0.0.1:%d" % app.port
+
+    def post(body, raw=False):
+        req = urllib.request.Request(base + "/v1/completions", json.dumps(body).encode(), {"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as resp:
+            data = resp.read()
+        return data if raw else json.loads(data)
+
+    try:
+        got = {}
+        ts = [threading.Thread(target=lambda i=i: got.__setitem__(i, post({"prompt": prompts[i], "max_tokens": news[i]}))) for i in range(6)]
+        [t.start() for t in ts]
+        [t.join(120) for t in ts]
+        for i in range(6):
+            c = got[i]["choices"][0]
+            assert c["token_ids"] == alone[i] and c["finish_reason"] == "length"
+            assert c["text"] == "".join(chr(65 + t % 26) for t in alone[i])
+            assert got[i]["usage"] == {"prompt_tokens": len(prompts[i]), "completion_tokens": news[i], "total_tokens": len(prompts[i]) + news[i]}
+        assert len({got[i]["id"] for i in got}) == 6
+
+        events = [json.loads(line[6:]) for line in post({"prompt": prompts[2], "max_tokens": 20, "stream": True, "stop_token_ids": [alone[2][7]]},
+                                                        raw=True).decode().split("\n\n") if line.startswith("data: {")]
+        upto = alone[2].index(alone[2][7]) + 1
+        assert [e["token_id"] for e in events[:-1]] == alone[2][:upto] and [e["index"] for e in events[:-1]] == list(range(upto))
+        assert events[-1]["finish_reason"] == "stop" and events[-1]["completion_tokens"] == upto
+
+        text = post({"prompt": "hello there", "max_tokens": 4, "temperature": 0.7, "seed": 3})
+        again = post({"prompt": "hello there", "max_tokens": 4, "temperature": 0.7, "seed": 3})
+        assert text["choices"][0]["token_ids"] == again["choices"][0]["token_ids"] and len(text["choices"][0]["text"]) == 4
+
+        for bad in ({"max_tokens": 4}, {"prompt": [], "max_tokens": 4}, {"prompt": [1, -2]}, {"prompt": [1], "max_tokens": 0},
+                    {"prompt": [1], "top_p": 0}, {"prompt": [1] * 100, "max_tokens": 100}):
+            with pytest.raises(urllib.error.HTTPError) as e:
+                post(bad)
+            assert e.value.code == 400 and "error" in json.loads(e.value.read())
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(base + "/nothing", timeout=30)
+        assert e.value.code == 404
+
+        health = json.loads(urllib.request.urlopen(base + "/health", timeout=30).read())
+        assert health == {"status": "ok", "running": 0, "waiting": 0}
+        metrics = urllib.request.urlopen(base + "/metrics", timeout=30).read().decode()
+        values = {l.split()[0]: int(l.split()[1]) for l in metrics.splitlines() if not l.startswith("#")}
+        assert values["ferrotorch_serving_requests_finished_total"] == 9 and values["ferrotorch_serving_kv_pages_total"] == 24
+        assert values["ferrotorch_serving_decode_tokens_total"] == b.stats.decode_tokens > 0
+        assert values["ferrotorch_serving_prefix_hit_tokens_total"] >= 16      # the streamed and the repeated prompts were listed
+    finally:
+        app.shutdown()
+    assert not app._loop.is_alive() and app.loop_error is None
+
+
+def test_server_command_line_starts_a_tiny_model_and_stops(capsys):
+    from ferrotorch_b200.models import server
+
+    assert server.main(["--tiny", "--device", "cpu", "--port", "0", "--kv-pages", "16", "--serve-seconds", "0.2"]) == 0
+    assert "serving on http://127.0.0.1:" in capsys.readouterr().out
+    with pytest.raises(SystemExit):
+        server.main([])
