@@ -71,6 +71,7 @@ class Request:
     stop_ids: tuple = ()
     sampling: SamplingParams = field(default_factory=SamplingParams)
     on_token: Callable[[int], object] | None = None       # called with every new token; returning False stops the request
+    logits_processor: Callable | None = None              # (generated ids [1, n], logits [1, V]) -> logits, before sampling
     # ---- filled in by the batcher
     id: int = -1
     output: list = field(default_factory=list)
@@ -400,7 +401,8 @@ class ContinuousBatcher:
         return self.model.lm_head(h[0, torch.tensor(last, device=dev)])
 
     def _sample(self, requests: list, logits: torch.Tensor) -> list:
-        greedy = [i for i, r in enumerate(requests) if r.sampling.temperature == 0.0 and r.sampling.repetition_penalty == 1.0]
+        greedy = [i for i, r in enumerate(requests)
+                  if r.sampling.temperature == 0.0 and r.sampling.repetition_penalty == 1.0 and r.logits_processor is None]
         out = [0] * len(requests)
         if greedy:
             for i, t in zip(greedy, logits[greedy].float().argmax(-1).tolist()):
@@ -410,6 +412,8 @@ class ContinuousBatcher:
                 continue
             s = r.sampling
             z = logits[i].float().cpu()[None]
+            if r.logits_processor is not None:            # e.g. a grammar mask (models.generation.GrammarLogitsProcessor)
+                z = r.logits_processor(torch.tensor([r.output], dtype=torch.long), z)
             z = apply_repetition_penalty(z, torch.tensor([r.tokens()], dtype=torch.long), s.repetition_penalty)
             if s.temperature == 0.0:
                 out[i] = int(z.argmax(-1))

@@ -269,3 +269,29 @@ def test_server_command_line_starts_a_tiny_model_and_stops(capsys):
     assert "serving on http://127.0.0.1:" in capsys.readouterr().out
     with pytest.raises(SystemExit):
         server.main([])
+
+
+def test_a_request_can_carry_a_grammar_while_its_neighbours_run_free():
+    import json
+
+    from ferrotorch_b200.models.generation import GrammarLogitsProcessor
+    from ferrotorch_b200.utils.text import JsonGrammar
+
+    vocab = ["{", "}", '"a"', '"b"', ":", ",", "1", "2", "[", "]", "true", " ", "<eos>", "x", "y", "z"]
+    cfg = LlamaConfig(vocab_size=len(vocab), hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                      num_attention_heads=2, num_key_value_heads=1, head_dim=16, max_position_embeddings=128)
+    torch.manual_seed(3)
+    model = LlamaForCausalLM(cfg).float().eval()
+    eos = vocab.index("<eos>")
+    g = JsonGrammar()
+    b = ContinuousBatcher(model, num_blocks=32, block_size=8, max_running=8, max_seq_len=64)
+    constrained = [b.submit(Request([0, 4, 6], 24, (eos,), SamplingParams(temperature=1.5, seed=s),
+                                    logits_processor=GrammarLogitsProcessor(g, vocab, eos))) for s in range(4)]
+    free = [b.submit(Request([0, 4, 6], 24, (eos,), SamplingParams(temperature=1.5, seed=s))) for s in range(4)]
+    b.run()
+    for r in constrained:
+        text = "".join(vocab[t] for t in r.output if t != eos)
+        assert g.accepts_prefix(text), text
+        if r.finish_reason == "stop":
+            json.loads(text)
+    assert any(not g.accepts_prefix("".join(vocab[t] for t in r.output if t != eos)) for r in free)
