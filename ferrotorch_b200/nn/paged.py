@@ -228,14 +228,22 @@ class PagedKVCache:
                 self.free_sequence(s)
 
     def _decode_reference(self, layer, q, ctx_len, scale, seq_ids=None):
-        from ..ops import reference as ref
-
-        outs = []
-        for b in range(q.shape[0]):
-            k, v = self.gather(layer, b if seq_ids is None else int(seq_ids[b]), int(ctx_len[b]))
-            o, _ = ref.attention(q[b][None, None], k[None], v[None], causal=False, scale=scale)
-            outs.append(o[0, 0])
-        return torch.stack(outs)
+        """Host form of the paged-decode kernel, all rows at once: the pages of every row are gathered through
+        the block table into a padded ``[B, L, Hkv, D]`` view and positions past a row's length are masked."""
+        B, Hq, D = q.shape
+        rows = torch.arange(B) if seq_ids is None else seq_ids.long().cpu()
+        ctx = ctx_len.long().cpu()
+        n_blk = int((int(ctx.max()) + self.block_size - 1) // self.block_size)
+        pages = self._table_host[rows, :n_blk].long().clamp_(min=0)          # unreserved slots read page 0 and are masked
+        k = self.k[layer][pages].reshape(B, n_blk * self.block_size, self.n_kv_heads, D).float()
+        v = self.v[layer][pages].reshape(B, n_blk * self.block_size, self.n_kv_heads, D).float()
+        g = Hq // self.n_kv_heads
+        qf = q.float().reshape(B, self.n_kv_heads, g, D)
+        s = torch.einsum("bhgd,blhd->bhgl", qf, k) * scale
+        dead = torch.arange(n_blk * self.block_size)[None] >= ctx[:, None]
+        s = s.masked_fill(dead[:, None, None, :], float("-inf"))
+        o = torch.einsum("bhgl,blhd->bhgd", torch.softmax(s, -1), v)
+        return o.reshape(B, Hq, D).to(q.dtype)
 
 
 class PagedAttentionManager:
