@@ -6,7 +6,8 @@ through a callback).  For serving, requests arrive concurrently and leave as the
 
 ``POST /v1/completions``
     ``{"prompt": "text" | [token ids], "max_tokens": 16, "temperature": 0, "top_p": 1, "top_k": 0, "seed": null,
-    "repetition_penalty": 1, "stop_token_ids": [], "stream": false}``.  The answer carries the generated ids, the
+    "repetition_penalty": 1, "stop_token_ids": [], "lookahead": 0, "stream": false}`` (``lookahead``: look-up
+    speculation of greedy requests).  The answer carries the generated ids, the
     text when a tokenizer is attached, the finish reason and token counts.  With ``"stream": true`` the answer is
     a ``text/event-stream``: one ``data: {...}`` event per token as the serving loop produces it, then
     ``data: [DONE]``.  A client that goes away in mid-stream cancels its request.
@@ -33,7 +34,7 @@ class BadRequest(ValueError):
 
 
 def parse_completion_request(body: dict, encode=None) -> tuple:
-    """``(prompt ids, max_tokens, stop ids, SamplingParams, stream)`` from the JSON body of a completion call."""
+    """``(prompt ids, max_tokens, stop ids, SamplingParams, stream, lookahead)`` from the JSON body of a completion call."""
     if not isinstance(body, dict) or "prompt" not in body:
         raise BadRequest("the body must be a JSON object with a 'prompt'")
     prompt = body["prompt"]
@@ -49,11 +50,12 @@ def parse_completion_request(body: dict, encode=None) -> tuple:
         sp.validate()
         max_tokens = int(body.get("max_tokens", 16))
         stops = tuple(int(t) for t in body.get("stop_token_ids", ()))
+        lookahead = max(0, int(body.get("lookahead", 0)))
     except (TypeError, ValueError) as e:
         raise BadRequest(str(e)) from None
     if max_tokens < 1:
         raise BadRequest("'max_tokens' must be at least 1")
-    return prompt, max_tokens, stops, sp, bool(body.get("stream", False))
+    return prompt, max_tokens, stops, sp, bool(body.get("stream", False)), lookahead
 
 
 def prometheus_text(batcher: ContinuousBatcher) -> str:
@@ -61,6 +63,7 @@ def prometheus_text(batcher: ContinuousBatcher) -> str:
     rows = [("steps_total", "counter", s.steps), ("prefill_tokens_total", "counter", s.prefill_tokens),
             ("decode_tokens_total", "counter", s.decode_tokens), ("preemptions_total", "counter", s.preemptions),
             ("requests_finished_total", "counter", s.finished), ("prefix_hit_tokens_total", "counter", s.prefix_hit_tokens),
+            ("speculated_tokens_total", "counter", s.spec_proposed), ("speculated_tokens_accepted_total", "counter", s.spec_accepted),
             ("requests_running", "gauge", len(batcher.running)), ("requests_waiting", "gauge", len(batcher.waiting)),
             ("kv_pages_used", "gauge", pool.num_used), ("kv_pages_total", "gauge", pool.num_total)]
     return "".join("# TYPE ferrotorch_serving_%s %s\nferrotorch_serving_%s %d\n" % (n, t, n, v) for n, t, v in rows)
@@ -154,9 +157,9 @@ class ServingApp:
         try:
             n = int(h.headers.get("Content-Length", "0"))
             body = json.loads(h.rfile.read(n) or b"null")
-            prompt, max_tokens, stops, sp, stream = parse_completion_request(body, self.encode)
+            prompt, max_tokens, stops, sp, stream, lookahead = parse_completion_request(body, self.encode)
             events: queue.Queue | None = queue.Queue() if stream else None
-            req = Request(prompt, max_tokens, stops, sp, on_token=events.put if stream else None)
+            req = Request(prompt, max_tokens, stops, sp, on_token=events.put if stream else None, lookahead=lookahead)
             self.batcher.submit(req)
         except (BadRequest, json.JSONDecodeError, ValueError, RuntimeError) as e:      # RuntimeError: the pool cannot hold it
             return self._send(h, 400, {"error": str(e)})

@@ -16,6 +16,11 @@ sequences and gives every step one flat token batch:
   so the earliest requests always finish and the pool can be smaller than the sum of all contexts;
 * waiting requests are admitted first come first served while there are sequence slots, step-token budget and
   pages above a watermark;
+* a greedy request with ``lookahead`` decodes speculatively without a draft model: the continuation of the most
+  recent earlier occurrence of its last few tokens (in its own prompt and output) is fed along with the last
+  token, one forward pass scores all of them, and the longest run that equals the model's own choices is kept
+  plus the token after it.  The output is the plain greedy output; repetitive text needs fewer steps.  Keys and
+  values of rejected positions are simply overwritten later;
 * with ``prefix_caching`` whole pages of finished (or still running) prompts stay in a table keyed by a hash chain
   of their tokens; a new request whose prompt starts with the same tokens adopts those pages (reference-counted
   in the pool) and computes only the rest.  Unused entries are evicted, deepest page of the least recently used
@@ -72,6 +77,8 @@ class Request:
     sampling: SamplingParams = field(default_factory=SamplingParams)
     on_token: Callable[[int], object] | None = None       # called with every new token; returning False stops the request
     logits_processor: Callable | None = None              # (generated ids [1, n], logits [1, V]) -> logits, before sampling
+    lookahead: int = 0                                    # greedy requests: verify up to this many looked-up tokens per step
+    ngram: int = 3                                        # longest suffix that the look-up matches
     # ---- filled in by the batcher
     id: int = -1
     output: list = field(default_factory=list)
@@ -116,6 +123,8 @@ class ServingStats:
     peak_running: int = 0
     peak_pages: int = 0
     prefix_hit_tokens: int = 0                            # prompt tokens that were adopted from the prefix table
+    spec_proposed: int = 0                                # looked-up tokens that were verified
+    spec_accepted: int = 0                                # ... and were what the model would have produced
     batch_tokens: list = field(default_factory=list)      # tokens of every step's flat batch
 
     def mean_batch_tokens(self) -> float:
@@ -213,6 +222,7 @@ class ContinuousBatcher:
             raise ValueError("ContinuousBatcher: max_tokens_per_step and prefill_chunk must be at least 1")
         self.watermark_pages = max(1, int(watermark * num_blocks)) if watermark > 0 else 0
         self.prefix = PrefixCache(self.cache.pool, block_size) if prefix_caching else None
+        self._drafts: dict = {}
         self.waiting: collections.deque = collections.deque()
         self.running: list = []                           # in admission order
         self.stats = ServingStats()
@@ -263,7 +273,7 @@ class ContinuousBatcher:
     # ------------------------------------------------------------------ scheduling
     def _remember(self, r: Request) -> None:
         if self.prefix is not None and r.slot >= 0 and r.computed >= self.cache.block_size:
-            self.prefix.insert(r.tokens()[:r.computed], self.cache.pages_of(r.slot))
+            self.prefix.insert(r.tokens()[:r.computed], self.cache.pages_of(r.slot))      # a slice: never past the tokens kept
 
     def _finish(self, r: Request, reason: str) -> None:
         if r.slot >= 0:
@@ -306,16 +316,37 @@ class ContinuousBatcher:
                     return False
                 raise
 
+    @staticmethod
+    def _look_up(tokens: list, ngram: int, k: int) -> list:
+        """Up to ``k`` tokens that followed the most recent earlier occurrence of the last ``ngram`` (or fewer) tokens."""
+        L = len(tokens)
+        for g in range(min(ngram, L - 1), 0, -1):
+            tail = tokens[L - g:]
+            for i in range(L - g - 1, -1, -1):
+                if tokens[i:i + g] == tail:
+                    return tokens[i + g:i + g + k]
+        return []
+
     def _schedule(self) -> list:
-        """This step's runs: ``(request, first position, number of tokens)``."""
+        """This step's runs: ``(request, first position, number of tokens)``; ``self._drafts`` holds the looked-up
+        tokens of the runs that speculate."""
         budget = self.max_tokens_per_step
         runs, scheduled, preempted = [], set(), False
+        self._drafts = {}
         before = self.stats.preemptions
         for r in list(self.running):                      # admission order: the oldest sequences are served first
             if r not in self.running or budget == 0:
                 continue
             n = min(len(r.prompt) + len(r.output) - r.computed, self.prefill_chunk, budget)
+            draft = []
+            if (r.lookahead > 0 and r.output and r.computed == len(r.prompt) + len(r.output) - 1 and r.sampling.temperature == 0.0
+                    and r.sampling.repetition_penalty == 1.0 and r.logits_processor is None):
+                k = min(r.lookahead, r.max_new_tokens - len(r.output) - 1, budget - 1, self.prefill_chunk - 1)
+                draft = self._look_up(r.tokens(), r.ngram, k) if k > 0 else []
+                n += len(draft)
             if self._reserve(r, r.computed + n, scheduled):
+                if draft:
+                    self._drafts[r.id] = draft
                 runs.append((r, r.computed, n))
                 scheduled.add(r.id)
                 budget -= n
@@ -373,17 +404,18 @@ class ContinuousBatcher:
 
     @torch.no_grad()
     def _forward(self, runs: list) -> torch.Tensor:
-        """Logits ``[len(runs), V]`` of the last token of every run."""
+        """Logits of the last token of every run (of its last ``1 + len(draft)`` tokens when it speculates), run after run."""
         dev = self.cache.device
         toks, poss, sids, spans, last, row = [], [], [], [], [], 0
         for r, start, n in runs:
-            seq = r.tokens()
+            draft = self._drafts.get(r.id, [])
+            seq = r.tokens() + draft
             toks += seq[start:start + n]
             poss += range(start, start + n)
             sids += [r.slot] * n
             spans.append((r.slot, row, start, n))
             row += n
-            last.append(row - 1)
+            last += range(row - 1 - len(draft), row)
         tok = torch.tensor(toks, dtype=torch.long, device=dev)
         pos = torch.tensor(poss, dtype=torch.int32, device=dev)
         sid = torch.tensor(sids, dtype=torch.int32, device=dev)
@@ -440,22 +472,38 @@ class ContinuousBatcher:
         self.stats.batch_tokens.append(sum(n for _, _, n in runs))
         self.stats.peak_running = max(self.stats.peak_running, len(self.running))
         self.stats.peak_pages = max(self.stats.peak_pages, self.cache.pool.num_used)
-        emit, rows = [], []
-        for i, (r, start, n) in enumerate(runs):
+        emit, rows, spec, at = [], [], [], 0
+        for r, start, n in runs:
+            draft = self._drafts.get(r.id)
             r.computed = start + n
-            if n == 1 and r.output:
-                self.stats.decode_tokens += 1
+            if draft or (n == 1 and r.output):
+                self.stats.decode_tokens += n
             else:
                 self.stats.prefill_tokens += n
-            if r.computed == len(r.prompt) + len(r.output):
+            if draft:
+                spec.append((r, start, draft, at))
+            elif r.computed == len(r.prompt) + len(r.output):
                 if n > 1:
                     self._remember(r)                         # a prompt that has just been computed can be shared at once
                 emit.append(r)
-                rows.append(i)
-        produced = []
+                rows.append(at)
+            at += 1 + len(draft or ())
+        new_tokens = []
         if emit:
-            now = time.perf_counter()
-            for r, t in zip(emit, self._sample(emit, logits[rows])):
+            new_tokens += [(r, [t]) for r, t in zip(emit, self._sample(emit, logits[rows]))]
+        for r, start, draft, at in spec:
+            choice = logits[at:at + len(draft) + 1].float().argmax(-1).tolist()
+            kept = 0
+            while kept < len(draft) and choice[kept] == draft[kept]:
+                kept += 1
+            self.stats.spec_proposed += len(draft)
+            self.stats.spec_accepted += kept
+            r.computed = start + 1 + kept                     # the last token and the drafts that were right
+            new_tokens.append((r, choice[:kept + 1]))
+        produced = []
+        now = time.perf_counter()
+        for r, toks in new_tokens:
+            for t in toks:
                 r.output.append(t)
                 if r.first_token_step < 0:
                     r.first_token_step, r.first_token_time = self.stats.steps, now
@@ -463,8 +511,10 @@ class ContinuousBatcher:
                 stop = r.on_token is not None and r.on_token(t) is False
                 if t in r.stop_ids or stop:
                     self._finish(r, "stop")
-                elif len(r.output) >= r.max_new_tokens:
+                    break
+                if len(r.output) >= r.max_new_tokens:
                     self._finish(r, "length")
+                    break
         return produced
 
     def run(self, max_steps: int | None = None) -> ServingStats:

@@ -231,7 +231,7 @@ def test_http_front_serves_concurrent_completions_streams_and_reports_metrics(se
             assert got[i]["usage"] == {"prompt_tokens": len(prompts[i]), "completion_tokens": news[i], "total_tokens": len(prompts[i]) + news[i]}
         assert len({got[i]["id"] for i in got}) == 6
 
-        events = [json.loads(line[6:]) for line in post({"prompt": prompts[2], "max_tokens": 20, "stream": True, "stop_token_ids": [alone[2][7]]},
+        events = [json.loads(line[6:]) for line in post({"prompt": prompts[2], "max_tokens": 20, "stream": True, "stop_token_ids": [alone[2][7]], "lookahead": 3},
                                                         raw=True).decode().split("\n\n") if line.startswith("data: {")]
         upto = alone[2].index(alone[2][7]) + 1
         assert [e["token_id"] for e in events[:-1]] == alone[2][:upto] and [e["index"] for e in events[:-1]] == list(range(upto))
@@ -295,3 +295,36 @@ def test_a_request_can_carry_a_grammar_while_its_neighbours_run_free():
         if r.finish_reason == "stop":
             json.loads(text)
     assert any(not g.accepts_prefix("".join(vocab[t] for t in r.output if t != eos)) for r in free)
+
+
+def test_lookup_speculation_keeps_the_greedy_output_and_saves_steps(served):
+    model, prompts, news, alone = served
+    assert ContinuousBatcher._look_up([1, 2, 3, 9, 1, 2, 3], 3, 4) == [9, 1, 2, 3]
+    assert ContinuousBatcher._look_up([5, 6, 7, 8, 6], 3, 2) == [7, 8] and ContinuousBatcher._look_up([1, 2, 3], 3, 4) == []
+    # random weights make greedy decoding fall into a loop, which is what the look-up finds
+    loop_prompt = prompts[0]
+    want = generate(model, torch.tensor([loop_prompt]), GenerationConfig.greedy(60))[0, len(loop_prompt):].tolist()
+    plain = ContinuousBatcher(model, num_blocks=32, block_size=8, max_seq_len=128)
+    plain.submit(loop_prompt, 60)
+    plain.run()
+    for pool in (32, 11):
+        b = ContinuousBatcher(model, num_blocks=pool, block_size=8, max_running=4, max_seq_len=128, watermark=0.0, prefix_caching=True)
+        r = b.submit(Request(loop_prompt, 60, lookahead=5))
+        others = [b.submit(Request(p, n, lookahead=3 if i % 2 else 0)) for i, (p, n) in enumerate(zip(prompts[1:5], news[1:5]))]
+        stop_at = b.submit(Request(prompts[2], 20, (alone[2][9],), lookahead=4))
+        b.run()
+        assert r.output == want and [o.output for o in others] == alone[1:5]
+        assert stop_at.output == alone[2][:alone[2].index(alone[2][9]) + 1] and stop_at.finish_reason == "stop"
+        st = b.stats
+        assert 0 < st.spec_accepted <= st.spec_proposed and st.decode_tokens + st.prefill_tokens == sum(st.batch_tokens)
+        assert b.manager.num_sequences() == 0 and b.cache.pool.num_used == len(b.prefix)
+    if len(set(want)) < 30:                                   # the output does loop: speculation must have paid
+        solo = ContinuousBatcher(model, num_blocks=32, block_size=8, max_seq_len=128)
+        solo.submit(Request(loop_prompt, 60, lookahead=5))
+        solo.run()
+        assert solo.stats.steps < plain.stats.steps
+    # sampled requests ignore the option
+    a = ContinuousBatcher(model, num_blocks=32, block_size=8, max_seq_len=128)
+    x = a.submit(Request(prompts[1], 10, sampling=SamplingParams(temperature=0.9, seed=5), lookahead=4))
+    a.run()
+    assert a.stats.spec_proposed == 0 and len(x.output) == 10
