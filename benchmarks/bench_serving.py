@@ -25,7 +25,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from ferrotorch_b200.models.generation import GenerationConfig, generate  # noqa: E402
 from ferrotorch_b200.models.llama import LlamaConfig, LlamaForCausalLM  # noqa: E402
-from ferrotorch_b200.models.serving import ContinuousBatcher  # noqa: E402
+from ferrotorch_b200.models.serving import ContinuousBatcher, Request  # noqa: E402
 
 
 def main(argv=None):
@@ -36,6 +36,7 @@ def main(argv=None):
     ap.add_argument("--max-new", type=int, default=48)
     ap.add_argument("--shared-prefix", type=int, default=0)
     ap.add_argument("--max-running", type=int, default=16)
+    ap.add_argument("--lookahead", type=int, default=0, help="look-up speculation of the batched arm (same tokens, fewer steps)")
     ap.add_argument("--hidden", type=int, default=256)
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--vocab", type=int, default=4096)
@@ -64,7 +65,7 @@ def main(argv=None):
         pages = sum((len(p) + n + 15) // 16 for p, n in zip(prompts, new))
         b = ContinuousBatcher(model, num_blocks=pages, block_size=16, max_running=args.max_running, max_seq_len=cfg.max_position_embeddings,
                               prefix_caching=args.shared_prefix > 0)
-        reqs = [b.submit(p, n) for p, n in zip(prompts, new)]
+        reqs = [b.submit(Request(p, n, lookahead=args.lookahead)) for p, n in zip(prompts, new)]
         b.run()
         return [r.output for r in reqs], b.stats
 
@@ -84,6 +85,7 @@ def main(argv=None):
                       "prompt_tokens": sum(map(len, prompts)), "sequential_tok_s": round(total / t_seq, 1), "batched_tok_s": round(total / t_bat, 1),
                       "speedup": round(t_seq / t_bat, 2), "steps": stats.steps, "mean_tokens_per_step": round(stats.mean_batch_tokens(), 1),
                       "prefix_hit_tokens": stats.prefix_hit_tokens, "preemptions": stats.preemptions,
+                      "speculated": "%d of %d accepted" % (stats.spec_accepted, stats.spec_proposed),
                       "requests_with_identical_tokens": "%d / %d" % (same, args.requests)}))
     return same
 

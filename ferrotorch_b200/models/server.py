@@ -166,7 +166,10 @@ class ServingApp:
         with self._lock:
             rid, self._next = "cmpl-%d" % self._next, self._next + 1
         if not stream:
-            req._done.wait()
+            while not req._done.wait(0.5):
+                if self.loop_error is not None:           # the request was still in the inbox when the loop stopped
+                    req.finish_reason = "error"
+                    break
             if req.finish_reason == "error":
                 return self._send(h, 500, {"error": "the serving loop stopped: %r" % (self.loop_error,)})
             return self._send(h, 200, {"id": rid, "object": "text_completion", "model": self.model_name, "choices": [self._choice(req)],
@@ -183,7 +186,7 @@ class ServingApp:
                 try:
                     tok = events.get(timeout=0.05)
                 except queue.Empty:
-                    if req._done.is_set() and events.empty():
+                    if (req._done.is_set() or self.loop_error is not None) and events.empty():
                         break
                     continue
                 ev = {"id": rid, "index": sent, "token_id": tok}

@@ -328,3 +328,31 @@ def test_lookup_speculation_keeps_the_greedy_output_and_saves_steps(served):
     x = a.submit(Request(prompts[1], 10, sampling=SamplingParams(temperature=0.9, seed=5), lookahead=4))
     a.run()
     assert a.stats.spec_proposed == 0 and len(x.output) == 10
+
+
+def test_http_front_reports_a_failed_serving_loop(served):
+    import json
+    import urllib.error
+    import urllib.request
+
+    from ferrotorch_b200.models.server import ServingApp
+
+    model, prompts, _, _ = served
+    b = ContinuousBatcher(model, num_blocks=16, block_size=8, max_seq_len=128)
+
+    def broken(runs):
+        raise RuntimeError("injected on the host")
+
+    b._forward = broken
+    app = ServingApp(b).start()
+    try:
+        req = urllib.request.Request("http://127.0.0.1:%d/v1/completions" % app.port, json.dumps({"prompt": prompts[0], "max_tokens": 4}).encode())
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(req, timeout=60)
+        assert e.value.code == 500 and "injected on the host" in json.loads(e.value.read())["error"]
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen("http://127.0.0.1:%d/health" % app.port, timeout=60)
+        assert e.value.code == 500
+    finally:
+        app.shutdown()
+    assert isinstance(app.loop_error, RuntimeError)
